@@ -1,0 +1,902 @@
+/*
+ * ny_oracle.c -- CPU restatement of ny's IBP / CROWN / beta-CROWN path.
+ *
+ * TEST INFRASTRUCTURE ONLY (parity checker and timed CPU baseline); see ny_oracle.h.
+ * Build with -ffp-contract=off: the double-double code below relies on explicit fma().
+ *
+ * Reference files restated here (paths inside the ny project, crates/...):
+ *   ny-tensor/src/rounding.rs:17-63                       next_up/next_down
+ *   ny-core/src/dd.rs:184-340                             two_sum, two_prod, dd_fma, gamma_n_dd
+ *   ny-propagate/src/bounds/certified_reduction.rs:26-129 certified_affine_sum_f32
+ *   ny-propagate/src/bounds/concretize.rs:26-130,374-489  concretize_row_directed
+ *   ny-propagate/src/layers/linear/ibp.rs:464-523         propagate_ibp_1d
+ *   ny-propagate/src/layers/linear/bias.rs:38-284         directed bias arithmetic
+ *   ny-propagate/src/layers/linear/crown_single.rs:124-135,1931-2226  linear backward
+ *   ny-propagate/src/layers/activations/mod.rs:99-121     upper chord
+ *   ny-propagate/src/layers/activations/relu/mod.rs:105-132  relu_linear_relaxation
+ *   ny-propagate/src/layers/common/compose.rs:84-185      compose_lower/upper
+ *   ny-propagate/src/layers/common/crown_dense.rs:41-286  elementwise backward + error
+ *   ny-propagate/src/network/ibp/crown_ibp.rs:32-420, crown_partial.rs:147-560,
+ *   ny-propagate/src/network/ibp/sparse_merge.rs:118-146, crown_ibp_forward.rs:25-100
+ *   ny-propagate/src/network/core/sequential/crown.rs:168-330 (+ crown/tighten.rs)
+ *   ny-propagate/src/beta_crown/engine/backward/relu_backward.rs:33-185
+ *   ny-propagate/src/beta_crown/engine/optimization/bound_compute.rs:90-167
+ *   ny-propagate/src/beta_crown/engine/domain/child.rs:51-118
+ *   ny-propagate/src/beta_crown/engine/graph/propagation/constraints/mod.rs:184-760
+ *   ny-propagate/src/beta_crown/engine/branching/sequential.rs:49-104
+ *   ny-propagate/src/beta_crown/config/beta_config.rs:1552-1610
+ */
+#include "ny_oracle.h"
+
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+#include <pthread.h>
+#include <unistd.h>
+
+/* ------------------------------------------------------------------ bit helpers */
+static inline uint32_t f2u(float x) { uint32_t u; memcpy(&u, &x, 4); return u; }
+static inline float u2f(uint32_t u) { float x; memcpy(&x, &u, 4); return x; }
+static inline uint64_t d2u(double x) { uint64_t u; memcpy(&u, &x, 8); return u; }
+static inline double u2d(uint64_t u) { double x; memcpy(&x, &u, 8); return x; }
+
+/* ny-tensor/src/rounding.rs:17-33 */
+float nyo_next_up_f32(float x) {
+    uint32_t b = f2u(x), mag = b & 0x7fffffffu;
+    if (mag >= 0x7f800000u) return x;
+    if (mag == 0) return u2f(1u);
+    return (b & 0x80000000u) ? u2f(b - 1) : u2f(b + 1);
+}
+/* ny-tensor/src/rounding.rs:47-63 */
+float nyo_next_down_f32(float x) {
+    uint32_t b = f2u(x), mag = b & 0x7fffffffu;
+    if (mag >= 0x7f800000u) return x;
+    if (mag == 0) return u2f(0x80000001u);
+    return (b & 0x80000000u) ? u2f(b + 1) : u2f(b - 1);
+}
+#define NUP32 nyo_next_up_f32
+#define NDN32 nyo_next_down_f32
+
+/* ny-core/src/dd.rs:312-340 */
+static inline double nup64(double x) {
+    uint64_t b = d2u(x), mag = b & 0x7fffffffffffffffull;
+    if (mag >= 0x7ff0000000000000ull) return x;
+    if (mag == 0) return u2d(1ull);
+    return (b >> 63) ? u2d(b - 1) : u2d(b + 1);
+}
+static inline double ndn64(double x) {
+    uint64_t b = d2u(x), mag = b & 0x7fffffffffffffffull;
+    if (mag >= 0x7ff0000000000000ull) return x;
+    if (mag == 0) return u2d(0x8000000000000001ull);
+    return (b >> 63) ? u2d(b + 1) : u2d(b - 1);
+}
+
+#define F32_MIN_POSITIVE 1.17549435e-38f
+#define CROWN_COEFF_MAX 1e10f /* ny-core/src/gemm.rs:116 */
+static inline int coeff_safe(float v) { return isfinite(v) && fabsf(v) < CROWN_COEFF_MAX; }
+
+/* ------------------------------------------------------------------ bias.rs directed casts */
+/* layers/linear/bias.rs:73-105 */
+static float f64_to_f32_down_ns(double v) {
+    if (isnan(v) || v == -INFINITY) return -INFINITY;
+    if (v == INFINITY) return INFINITY;
+    if (v == 0.0) return 0.0f;
+    if (fabs(v) < (double)F32_MIN_POSITIVE) return signbit(v) ? -F32_MIN_POSITIVE : 0.0f;
+    float n = (float)v;
+    if (n == INFINITY) return 3.4028234663852886e38f;
+    if (n == -INFINITY) return -INFINITY;
+    return ((double)n <= v) ? n : NDN32(n);
+}
+/* layers/linear/bias.rs:110-142 */
+static float f64_to_f32_up_ns(double v) {
+    if (isnan(v) || v == INFINITY) return INFINITY;
+    if (v == -INFINITY) return -INFINITY;
+    if (v == 0.0) return 0.0f;
+    if (fabs(v) < (double)F32_MIN_POSITIVE) return signbit(v) ? 0.0f : F32_MIN_POSITIVE;
+    float n = (float)v;
+    if (n == -INFINITY) return -3.4028234663852886e38f;
+    if (n == INFINITY) return INFINITY;
+    return ((double)n >= v) ? n : NUP32(n);
+}
+/* layers/linear/bias.rs:146-154 */
+static float publish_error_up_normal(double v) {
+    if (isnan(v) || v < 0.0 || v == INFINITY) return INFINITY;
+    if (v == 0.0) return 0.0f;
+    return NUP32(f64_to_f32_up_ns(v));
+}
+/* layers/linear/bias.rs:158-167 */
+static double nonneg_err_or_inf(float v) {
+    uint32_t b = f2u(v), mag = b & 0x7fffffffu;
+    if ((mag >> 23) == 0xff || ((b >> 31) != 0 && mag != 0)) return INFINITY;
+    return (double)v;
+}
+/* layers/linear/bias.rs:174-204 */
+static inline double add_f64_down(double acc, double term) {
+    if (isnan(acc) || isnan(term)) return -INFINITY;
+    if (term == 0.0) return acc;
+    double s = acc + term;
+    return isnan(s) ? -INFINITY : ndn64(s);
+}
+static inline double add_f64_up(double acc, double term) {
+    if (isnan(acc) || isnan(term)) return INFINITY;
+    if (term == 0.0) return acc;
+    double s = acc + term;
+    return isnan(s) ? INFINITY : nup64(s);
+}
+
+/* ------------------------------------------------------------------ certified reduction */
+/* ny-core/src/dd.rs:184-237 */
+static inline void two_sum(double a, double b, double *s, double *e) {
+    double ss = a + b, bb = ss - a;
+    *e = (a - (ss - bb)) + (b - bb);
+    *s = ss;
+}
+static inline void dd_fma(double *hi, double *lo, double a, double b) {
+    double p = a * b, e = fma(a, b, -p);
+    double s, e2;
+    two_sum(*hi, p, &s, &e2);
+    double ee = e2 + e + *lo;
+    two_sum(s, ee, hi, lo);
+}
+/* ny-core/src/dd.rs:284-304 with U_DD = 2^-102 */
+static double gamma_n_dd(size_t n) {
+    const double u = ldexp(1.0, -102);
+    double nu_hi = nup64((double)n * u);
+    double den = 1.0 - nu_hi;
+    if (!(den > 0.0) || !isfinite(nu_hi)) return INFINITY;
+    return nup64(nu_hi / den);
+}
+/* bounds/safe_math.rs:45-53 */
+static inline double safe_mul(double a, double x) {
+    if (a == 0.0 || x == 0.0) return 0.0;
+    if (isnan(a) || isnan(x)) return NAN;
+    return a * x;
+}
+
+/* bounds/certified_reduction.rs:40-129.  The term sequence is produced by a callback-free
+ * gather: the caller supplies parallel arrays. */
+double nyo_certified_affine_sum(float bias, const float *coef, const float *val, int n, int upper) {
+    double bias64 = (double)bias;
+    double hi = bias64, lo = 0.0;
+    double abs_sum = fabs(bias64);
+    double directed = bias64;
+    size_t count = 0;
+    int dd_ok = isfinite(bias);
+    int exact_zero = (f2u(bias) & 0x7fffffffu) == 0;
+    for (int i = 0; i < n; ++i) {
+        float c = coef[i], v = val[i];
+        ++count;
+        double c64 = (double)c, v64 = (double)v;
+        double prod = safe_mul(c64, v64);
+        int cz = (f2u(c) & 0x7fffffffu) == 0, vz = (f2u(v) & 0x7fffffffu) == 0;
+        exact_zero &= (cz || vz);
+        double s = directed + prod;
+        if (upper) directed = isnan(s) ? INFINITY : nup64(s);
+        else directed = isnan(s) ? -INFINITY : ndn64(s);
+        if (dd_ok && isfinite(c) && isfinite(v)) {
+            dd_fma(&hi, &lo, c64, v64);
+            double pm = fabs(prod);
+            if (pm != 0.0) abs_sum = nup64(abs_sum + pm);
+            dd_ok = isfinite(hi) && isfinite(lo) && isfinite(abs_sum);
+        } else {
+            dd_ok = 0;
+        }
+    }
+    if (exact_zero) return 0.0;
+    if (!dd_ok) return directed;
+    double gamma = gamma_n_dd(count);
+    double err = (gamma == 0.0 || abs_sum == 0.0) ? 0.0 : nup64(gamma * abs_sum);
+    if (upper) return nup64(nup64(hi + lo) + err);
+    return ndn64(ndn64(hi + lo) - err);
+}
+
+/* bounds/concretize.rs:68-130 */
+static float publish_lower(double v) {
+    if (isnan(v) || v == -INFINITY) return -INFINITY;
+    if (v == INFINITY) return INFINITY;
+    if (v == 0.0) return (float)v;
+    if (fabs(v) < (double)F32_MIN_POSITIVE) return signbit(v) ? -F32_MIN_POSITIVE : 0.0f;
+    float p = NDN32((float)v);
+    uint32_t mag = f2u(p) & 0x7fffffffu;
+    if (mag != 0 && mag < f2u(F32_MIN_POSITIVE)) return signbit(v) ? -F32_MIN_POSITIVE : 0.0f;
+    return p;
+}
+static float publish_upper(double v) {
+    if (isnan(v) || v == INFINITY) return INFINITY;
+    if (v == -INFINITY) return -INFINITY;
+    if (v == 0.0) return (float)v;
+    if (fabs(v) < (double)F32_MIN_POSITIVE) return signbit(v) ? -0.0f : F32_MIN_POSITIVE;
+    float p = NUP32((float)v);
+    uint32_t mag = f2u(p) & 0x7fffffffu;
+    if (mag != 0 && mag < f2u(F32_MIN_POSITIVE)) return signbit(v) ? -0.0f : F32_MIN_POSITIVE;
+    return p;
+}
+static inline int coef_nonneg(float v) { uint32_t b = f2u(v); return (b >> 31) == 0 || (b & 0x7fffffffu) == 0; }
+static inline float max_abs_bits(float l, float u) {
+    uint32_t a = f2u(l) & 0x7fffffffu, b = f2u(u) & 0x7fffffffu;
+    if (a > 0x7f800000u || b > 0x7f800000u) return NAN;
+    return u2f(a > b ? a : b);
+}
+static inline float nonneg_err_or_inf_f32(float v) {
+    uint32_t b = f2u(v), mag = b & 0x7fffffffu;
+    if ((mag >> 23) == 0xff || ((b >> 31) != 0 && mag != 0)) return INFINITY;
+    return v;
+}
+
+/* ------------------------------------------------------------------ linear bounds carrier */
+/* bounds/linear.rs:320-347 */
+typedef struct {
+    int rows, n;
+    float *la, *ua, *lb, *ub;
+    float *le, *ue; /* certified per-coefficient error, or NULL */
+} lbounds;
+
+static lbounds lb_alloc(int rows, int n, int with_err) {
+    lbounds b;
+    b.rows = rows; b.n = n;
+    b.la = (float *)calloc((size_t)rows * n, 4);
+    b.ua = (float *)calloc((size_t)rows * n, 4);
+    b.lb = (float *)calloc(rows, 4);
+    b.ub = (float *)calloc(rows, 4);
+    b.le = with_err ? (float *)calloc((size_t)rows * n, 4) : NULL;
+    b.ue = with_err ? (float *)calloc((size_t)rows * n, 4) : NULL;
+    return b;
+}
+static void lb_free(lbounds *b) {
+    free(b->la); free(b->ua); free(b->lb); free(b->ub); free(b->le); free(b->ue);
+    memset(b, 0, sizeof(*b));
+}
+static lbounds lb_identity(int n) {
+    lbounds b = lb_alloc(n, n, 0);
+    for (int i = 0; i < n; ++i) { b.la[(size_t)i * n + i] = 1.0f; b.ua[(size_t)i * n + i] = 1.0f; }
+    return b;
+}
+
+/* bounds/concretize.rs:374-489 (identical arithmetic to :717-880) */
+static void concretize_row(float lb, float ub, const float *in_l, const float *in_u, int n,
+                           const float *la, const float *ua, const float *le, const float *ue,
+                           float *tmp_c, float *tmp_v, float *out_l, float *out_u) {
+    int lower_deg = (lb == -INFINITY), upper_deg = (ub == INFINITY);
+    int lower_of = 0, upper_of = 0;
+    if (!lower_deg || !upper_deg) {
+        for (int j = 0; j < n; ++j) {
+            if (!lower_deg && !coeff_safe(la[j])) lower_of = 1;
+            if (!upper_deg && !coeff_safe(ua[j])) upper_of = 1;
+            if ((lower_deg || lower_of) && (upper_deg || upper_of)) break;
+        }
+    }
+    double lower64 = 0.0, upper64 = 0.0;
+    if (lower_deg || lower_of) lower64 = -INFINITY;
+    if (upper_deg || upper_of) upper64 = INFINITY;
+    if (!((lower_deg || lower_of) && (upper_deg || upper_of))) {
+        for (int j = 0; j < n; ++j) { tmp_c[j] = la[j]; tmp_v[j] = coef_nonneg(la[j]) ? in_l[j] : in_u[j]; }
+        double sum_l = nyo_certified_affine_sum(lb, tmp_c, tmp_v, n, 0);
+        for (int j = 0; j < n; ++j) { tmp_c[j] = ua[j]; tmp_v[j] = coef_nonneg(ua[j]) ? in_u[j] : in_l[j]; }
+        double sum_u = nyo_certified_affine_sum(ub, tmp_c, tmp_v, n, 1);
+        if (le) {
+            for (int j = 0; j < n; ++j) { tmp_c[j] = nonneg_err_or_inf_f32(le[j]); tmp_v[j] = max_abs_bits(in_l[j], in_u[j]); }
+            double pen = nyo_certified_affine_sum(0.0f, tmp_c, tmp_v, n, 1);
+            sum_l = ndn64(sum_l - pen);
+        }
+        if (ue) {
+            for (int j = 0; j < n; ++j) { tmp_c[j] = nonneg_err_or_inf_f32(ue[j]); tmp_v[j] = max_abs_bits(in_l[j], in_u[j]); }
+            double pen = nyo_certified_affine_sum(0.0f, tmp_c, tmp_v, n, 1);
+            sum_u = nup64(sum_u + pen);
+        }
+        if (!(lower_deg || lower_of)) lower64 = isnan(sum_l) ? -INFINITY : sum_l;
+        if (!(upper_deg || upper_of)) upper64 = isnan(sum_u) ? INFINITY : sum_u;
+    }
+    float l = publish_lower(lower64), u = publish_upper(upper64);
+    if (!isfinite(l) || !isfinite(u) || l > u) { l = -INFINITY; u = INFINITY; }
+    *out_l = l; *out_u = u;
+}
+
+static void concretize(const lbounds *b, const float *in_l, const float *in_u, float *out_l, float *out_u) {
+    float *tc = (float *)malloc(sizeof(float) * (size_t)(b->n > 0 ? b->n : 1));
+    float *tv = (float *)malloc(sizeof(float) * (size_t)(b->n > 0 ? b->n : 1));
+    for (int i = 0; i < b->rows; ++i) {
+        size_t o = (size_t)i * b->n;
+        concretize_row(b->lb[i], b->ub[i], in_l, in_u, b->n, b->la + o, b->ua + o,
+                       b->le ? b->le + o : NULL, b->ue ? b->ue + o : NULL, tc, tv, out_l + i, out_u + i);
+    }
+    free(tc); free(tv);
+}
+
+/* ------------------------------------------------------------------ network access */
+typedef struct { const float *W; const float *b; int n_in, n_out; } lin_layer;
+
+static lin_layer net_layer(const nyo_net *net, int k) {
+    size_t wo = 0, bo = 0;
+    for (int i = 0; i < k; ++i) {
+        wo += (size_t)net->dims[i] * net->dims[i + 1];
+        if (net->has_bias[i]) bo += (size_t)net->dims[i + 1];
+    }
+    lin_layer l;
+    l.W = net->wflat + wo;
+    l.b = net->has_bias[k] ? net->bflat + bo : NULL;
+    l.n_in = net->dims[k]; l.n_out = net->dims[k + 1];
+    return l;
+}
+static size_t pre_offset(const nyo_net *net, int k) { /* offset of Linear_k's output block */
+    size_t o = 0;
+    for (int i = 0; i < k; ++i) o += (size_t)net->dims[i + 1];
+    return o;
+}
+
+/* ------------------------------------------------------------------ IBP */
+/* layers/linear/ibp.rs:464-523: W+ l + W- u + b accumulated in binary64, cast outward. */
+static void linear_ibp(const lin_layer *L, const float *xl, const float *xu, float *yl, float *yu) {
+    for (int o = 0; o < L->n_out; ++o) {
+        const float *w = L->W + (size_t)o * L->n_in;
+        double pl = 0.0, nu = 0.0, pu = 0.0, nl = 0.0;
+        for (int i = 0; i < L->n_in; ++i) {
+            double wp = (double)fmaxf(w[i], 0.0f), wn = (double)fminf(w[i], 0.0f);
+            if (isnan(w[i])) { wp = NAN; wn = NAN; }
+            pl += wp * (double)xl[i]; nu += wn * (double)xu[i];
+            pu += wp * (double)xu[i]; nl += wn * (double)xl[i];
+        }
+        double lo = pl + nu, hi = pu + nl;
+        if (L->b) { lo += (double)L->b[o]; hi += (double)L->b[o]; }
+        float l = NDN32((float)lo), u = NUP32((float)hi);
+        /* BoundedTensor::new_repaired(Conservative): NaN or inverted -> [-inf, +inf] */
+        if (isnan(l) || isnan(u) || l > u) { l = -INFINITY; u = INFINITY; }
+        yl[o] = l; yu[o] = u;
+    }
+}
+/* layers/activations/relu/ibp.rs:14-18 (NaN-propagating max) */
+static inline float nanmax(float a, float b) { return (isnan(a) || isnan(b)) ? NAN : (a > b ? a : b); }
+static inline float nanmin(float a, float b) { return (isnan(a) || isnan(b)) ? NAN : (a < b ? a : b); }
+
+int nyo_ibp_forward(const nyo_net *net, const float *in_lo, const float *in_hi, float *pre_lo, float *pre_hi) {
+    int L = net->n_linear;
+    int maxn = 0;
+    for (int k = 0; k <= L; ++k) if (net->dims[k] > maxn) maxn = net->dims[k];
+    float *zl = (float *)malloc(4 * (size_t)maxn), *zu = (float *)malloc(4 * (size_t)maxn);
+    memcpy(zl, in_lo, 4 * (size_t)net->dims[0]); memcpy(zu, in_hi, 4 * (size_t)net->dims[0]);
+    for (int k = 0; k < L; ++k) {
+        lin_layer Lk = net_layer(net, k);
+        size_t o = pre_offset(net, k);
+        linear_ibp(&Lk, zl, zu, pre_lo + o, pre_hi + o);
+        for (int j = 0; j < Lk.n_out; ++j) { zl[j] = nanmax(pre_lo[o + j], 0.0f); zu[j] = nanmax(pre_hi[o + j], 0.0f); }
+    }
+    free(zl); free(zu);
+    return 0;
+}
+
+/* ------------------------------------------------------------------ linear backward */
+/* layers/linear/crown_single.rs:124-135 */
+static double gamma_n_f64(size_t n) {
+    double d = (double)n * ldexp(1.0, -53);
+    return d >= 1.0 ? INFINITY : d / (1.0 - d);
+}
+
+/* layers/linear/crown_single.rs:1931-2226.  in: rows x n_out; returns rows x n_in with
+ * certified error matrices. */
+static lbounds linear_backward(const lin_layer *L, const lbounds *in) {
+    int rows = in->rows, K = L->n_out, N = L->n_in;
+    lbounds out = lb_alloc(rows, N, 1);
+    double gamma = gamma_n_f64((size_t)K);
+    double *a64 = (double *)malloc(sizeof(double) * (size_t)N);
+    double *s64 = (double *)malloc(sizeof(double) * (size_t)N);
+    double *p64 = (double *)malloc(sizeof(double) * (size_t)N);
+    for (int side = 0; side < 2; ++side) {
+        const float *A = side ? in->ua : in->la;
+        const float *E = side ? in->ue : in->le;
+        const float *Bin = side ? in->ub : in->lb;
+        float *Ao = side ? out.ua : out.la, *Eo = side ? out.ue : out.le, *Bo = side ? out.ub : out.lb;
+        for (int i = 0; i < rows; ++i) {
+            const float *a = A + (size_t)i * K;
+            for (int j = 0; j < N; ++j) { a64[j] = 0.0; s64[j] = 0.0; p64[j] = 0.0; }
+            /* aw_f64_with_abssum (:170): exact products, binary64 accumulation */
+            for (int k = 0; k < K; ++k) {
+                double ak = (double)a[k];
+                const float *w = L->W + (size_t)k * N;
+                if (ak != 0.0) {
+                    double aak = fabs(ak);
+                    for (int j = 0; j < N; ++j) { a64[j] += ak * (double)w[j]; s64[j] += aak * fabs((double)w[j]); }
+                } else if (isnan(ak)) {
+                    for (int j = 0; j < N; ++j) { a64[j] = NAN; }
+                }
+            }
+            /* incoming_error_product (:1238): upward-directed sum of err * |W| published as f32 */
+            if (E) {
+                const float *e = E + (size_t)i * K;
+                for (int k = 0; k < K; ++k) {
+                    double ek = nonneg_err_or_inf(e[k]);
+                    if (ek == 0.0) continue;
+                    const float *w = L->W + (size_t)k * N;
+                    for (int j = 0; j < N; ++j) {
+                        double aw = fabs((double)w[j]);
+                        if (aw != 0.0) p64[j] = add_f64_up(p64[j], ek * aw);
+                    }
+                }
+            }
+            int nonfinite = 0;
+            for (int j = 0; j < N; ++j) {
+                float v = (float)a64[j];
+                double cast_err = fabs(a64[j] - (double)v);
+                double prop = E ? (double)publish_error_up_normal(p64[j]) : 0.0;
+                float err = publish_error_up_normal(cast_err + gamma * s64[j] + prop);
+                if (coeff_safe(v) && isfinite(err)) { Ao[(size_t)i * N + j] = v; Eo[(size_t)i * N + j] = err; }
+                else nonfinite = 1;
+            }
+            /* bias: accumulate_bias_f64 (bias.rs:238-255) + error fold (:2142-2166) + finalize */
+            float bnew = Bin[i];
+            if (L->b) {
+                double acc = 0.0;
+                for (int k = 0; k < K; ++k) {
+                    double t = (double)a[k] * (double)L->b[k];
+                    acc = side ? add_f64_up(acc, t) : add_f64_down(acc, t);
+                }
+                if (E) {
+                    const float *e = E + (size_t)i * K;
+                    double ee = 0.0;
+                    for (int k = 0; k < K; ++k) {
+                        double ba = fabs((double)L->b[k]);
+                        if (ba == 0.0) continue;
+                        ee = add_f64_up(ee, nonneg_err_or_inf(e[k]) * ba);
+                    }
+                    acc = side ? add_f64_up(acc, ee) : add_f64_down(acc, -ee);
+                }
+                bnew = side ? f64_to_f32_up_ns(add_f64_up((double)Bin[i], acc))
+                            : f64_to_f32_down_ns(add_f64_down((double)Bin[i], acc));
+            }
+            if (nonfinite) {
+                for (int j = 0; j < N; ++j) { Ao[(size_t)i * N + j] = 0.0f; Eo[(size_t)i * N + j] = 0.0f; }
+                bnew = side ? INFINITY : -INFINITY;
+            }
+            Bo[i] = bnew;
+        }
+    }
+    free(a64); free(s64); free(p64);
+    return out;
+}
+
+/* ------------------------------------------------------------------ ReLU relaxations */
+typedef struct { float ls, li, us, ui; } relax_t; /* lower slope/intercept, upper slope/intercept */
+
+/* activations/relu/mod.rs:105-132 + activations/mod.rs:99-121 */
+static relax_t relu_relaxation(float l, float u) {
+    relax_t r;
+    if (isnan(l) || isnan(u)) { r.ls = 0; r.li = -INFINITY; r.us = 0; r.ui = INFINITY; return r; }
+    if (l >= 0.0f) { r.ls = 1; r.li = 0; r.us = 1; r.ui = 0; return r; }
+    if (u <= 0.0f) { r.ls = 0; r.li = 0; r.us = 0; r.ui = 0; return r; }
+    if (isinf(l) && isinf(u)) { r.ls = 0; r.li = 0; r.us = 0; r.ui = INFINITY; return r; }
+    if (isinf(u)) { r.ls = 1; r.li = 0; r.us = 1; r.ui = -l; return r; }
+    if (isinf(l)) { r.ls = 0; r.li = 0; r.us = 0; r.ui = u; return r; }
+    double width = (double)u - (double)l;
+    float lam = NUP32((float)((double)u / width));
+    float icp = NUP32((float)(-(double)lam * (double)l));
+    r.ls = (u > -l) ? 1.0f : 0.0f; r.li = 0.0f; r.us = lam; r.ui = icp;
+    return r;
+}
+
+/* layers/common/crown_dense.rs:41-286 with compose.rs:84-185 (default exact-zero-slope gate off) */
+static lbounds relu_backward_crown(const lbounds *in, const float *pl, const float *pu) {
+    int rows = in->rows, n = in->n;
+    lbounds out = lb_alloc(rows, n, 1);
+    relax_t *rx = (relax_t *)malloc(sizeof(relax_t) * (size_t)n);
+    for (int i = 0; i < n; ++i) rx[i] = relu_relaxation(pl[i], pu[i]);
+    for (int j = 0; j < rows; ++j) {
+        double lb64 = (double)in->lb[j], ub64 = (double)in->ub[j];
+        double lberr = 0.0, uberr = 0.0;
+        int lnf = 0, unf = 0;
+        for (int i = 0; i < n; ++i) {
+            size_t o = (size_t)j * n + i;
+            float la = in->la[o], ua = in->ua[o];
+            const relax_t *r = &rx[i];
+            /* compose_lower */
+            float lc = 0.0f; double lslope = 0.0;
+            if (la > 0.0f) {
+                float p = la * r->ls; lslope = (double)r->ls;
+                lc = isfinite(p) ? NDN32(p) : 0.0f; lnf |= !isfinite(p);
+                lb64 += (double)la * (double)r->li;
+            } else if (la < 0.0f) {
+                float p = la * r->us; lslope = (double)r->us;
+                lc = isfinite(p) ? NDN32(p) : 0.0f; lnf |= !isfinite(p);
+                lb64 += (double)la * (double)r->ui;
+            }
+            out.la[o] = lc;
+            /* compose_upper */
+            float uc = 0.0f; double uslope = 0.0;
+            if (ua > 0.0f) {
+                float p = ua * r->us; uslope = (double)r->us;
+                uc = isfinite(p) ? NUP32(p) : 0.0f; unf |= !isfinite(p);
+                ub64 += (double)ua * (double)r->ui;
+            } else if (ua < 0.0f) {
+                float p = ua * r->ls; uslope = (double)r->ls;
+                uc = isfinite(p) ? NUP32(p) : 0.0f; unf |= !isfinite(p);
+                ub64 += (double)ua * (double)r->li;
+            }
+            out.ua[o] = uc;
+            double slope_sum = (double)(fabsf(r->ls) + fabsf(r->us));
+            double int_sum = (double)(fabsf(r->li) + fabsf(r->ui));
+            {
+                double gap = (la != 0.0f) ? fabs((double)la * lslope - (double)lc) : 0.0;
+                double ea = in->le ? (double)in->le[o] : 0.0;
+                if (gap != 0.0 || ea != 0.0) {
+                    double sc, ic;
+                    if (fabs((double)la) > ea) { sc = fabs(lslope); ic = (la > 0.0f) ? (double)fabsf(r->li) : (double)fabsf(r->ui); }
+                    else { sc = slope_sum; ic = int_sum; }
+                    out.le[o] = NUP32((float)(ea * sc + gap));
+                    if (ea != 0.0) lberr += ea * ic;
+                }
+            }
+            {
+                double gap = (ua != 0.0f) ? fabs((double)ua * uslope - (double)uc) : 0.0;
+                double ea = in->ue ? (double)in->ue[o] : 0.0;
+                if (gap != 0.0 || ea != 0.0) {
+                    double sc, ic;
+                    if (fabs((double)ua) > ea) { sc = fabs(uslope); ic = (ua > 0.0f) ? (double)fabsf(r->ui) : (double)fabsf(r->li); }
+                    else { sc = slope_sum; ic = int_sum; }
+                    out.ue[o] = NUP32((float)(ea * sc + gap));
+                    if (ea != 0.0) uberr += ea * ic;
+                }
+            }
+        }
+        lb64 -= lberr; ub64 += uberr;
+        out.lb[j] = (lb64 == 0.0) ? 0.0f : NDN32((float)lb64);
+        out.ub[j] = (ub64 == 0.0) ? 0.0f : NUP32((float)ub64);
+        if (lnf) { for (int i = 0; i < n; ++i) { out.la[(size_t)j * n + i] = 0; out.le[(size_t)j * n + i] = 0; } out.lb[j] = -INFINITY; }
+        if (unf) { for (int i = 0; i < n; ++i) { out.ua[(size_t)j * n + i] = 0; out.ue[(size_t)j * n + i] = 0; } out.ub[j] = INFINITY; }
+    }
+    free(rx);
+    return out;
+}
+
+/* beta_crown/engine/backward/relu_backward.rs:33-185.  split[i]: 0 none, +1 active, -1 inactive;
+ * sbeta[i]: signed beta (beta * sign) or 0; has_sb[i] marks neurons that carry a beta entry.
+ * The result carries no error matrices (LinearBounds::new_or_conservative). */
+#define RELU_RELAX_MIN_WIDTH 1e-8f
+static lbounds relu_backward_beta(const lbounds *in, const float *pl, const float *pu,
+                                  const signed char *split, const float *sbeta, const unsigned char *has_sb,
+                                  const float *alpha) {
+    int rows = in->rows, n = in->n;
+    lbounds out = lb_alloc(rows, n, 0);
+    double *lb64 = (double *)malloc(sizeof(double) * (size_t)rows);
+    double *ub64 = (double *)malloc(sizeof(double) * (size_t)rows);
+    for (int i = 0; i < rows; ++i) { lb64[i] = (double)in->lb[i]; ub64[i] = (double)in->ub[i]; }
+    int nonfinite = 0;
+    for (int j = 0; j < n; ++j) {
+        float l = pl[j], u = pu[j];
+        float ls, li, us, ui;
+        if (split && split[j] != 0) {
+            if (split[j] > 0) { ls = 1; li = 0; us = 1; ui = 0; } else { ls = 0; li = 0; us = 0; ui = 0; }
+        } else if (isnan(l) || isnan(u)) { ls = 0; li = -INFINITY; us = 0; ui = INFINITY; }
+        else if (l >= 0.0f) { ls = 1; li = 0; us = 1; ui = 0; }
+        else if (u <= 0.0f) { ls = 0; li = 0; us = 0; ui = 0; }
+        else if (isinf(l) && isinf(u)) { ls = 0; li = 0; us = 0; ui = INFINITY; }
+        else if (isinf(u)) { ls = 1; li = 0; us = 1; ui = -l; }
+        else if (isinf(l)) { ls = 0; li = 0; us = 0; ui = u; }
+        else {
+            float width = fmaxf(u - l, RELU_RELAX_MIN_WIDTH);
+            us = u / width; ui = -l * u / width;
+            ls = alpha ? alpha[j] : ((u > -l) ? 1.0f : 0.0f); li = 0.0f;
+        }
+        for (int i = 0; i < rows; ++i) {
+            size_t o = (size_t)i * n + j;
+            float la = in->la[o], ua = in->ua[o];
+            if (la > 0.0f) {
+                float p = la * ls;
+                if (isfinite(p)) out.la[o] = NDN32(p); else { nonfinite = 1; out.la[o] = 0; }
+                lb64[i] += (double)la * (double)li;
+            } else if (la < 0.0f) {
+                float p = la * us;
+                if (isfinite(p)) out.la[o] = NDN32(p); else { nonfinite = 1; out.la[o] = 0; }
+                lb64[i] += (double)la * (double)ui;
+            } else out.la[o] = 0.0f;
+            if (ua > 0.0f) {
+                float p = ua * us;
+                if (isfinite(p)) out.ua[o] = NUP32(p); else { nonfinite = 1; out.ua[o] = 0; }
+                ub64[i] += (double)ua * (double)ui;
+            } else if (ua < 0.0f) {
+                float p = ua * ls;
+                if (isfinite(p)) out.ua[o] = NUP32(p); else { nonfinite = 1; out.ua[o] = 0; }
+                ub64[i] += (double)ua * (double)li;
+            } else out.ua[o] = 0.0f;
+        }
+        if (has_sb && has_sb[j] && isfinite(sbeta[j])) {
+            for (int i = 0; i < rows; ++i) { out.la[(size_t)i * n + j] -= sbeta[j]; out.ua[(size_t)i * n + j] += sbeta[j]; }
+        }
+    }
+    if (nonfinite) { /* LinearBounds::conservative: zero coefficients, bias -inf/+inf */
+        memset(out.la, 0, 4 * (size_t)rows * n); memset(out.ua, 0, 4 * (size_t)rows * n);
+        for (int i = 0; i < rows; ++i) { out.lb[i] = -INFINITY; out.ub[i] = INFINITY; }
+    } else {
+        for (int i = 0; i < rows; ++i) { out.lb[i] = NDN32((float)lb64[i]); out.ub[i] = NUP32((float)ub64[i]); }
+    }
+    free(lb64); free(ub64);
+    return out;
+}
+
+/* ------------------------------------------------------------------ plain CROWN pipeline */
+/* Backward from `seed` (rows x dims[top+1]) through Linear_top, ReLU_{top-1}, ..., Linear_0,
+ * then concretize on the input box.  pre_* hold the pre-activation bounds used by the ReLUs. */
+static void crown_backward_concretize(const nyo_net *net, int top, lbounds seed, const float *pre_lo,
+                                      const float *pre_hi, const float *in_lo, const float *in_hi,
+                                      float *out_l, float *out_u) {
+    lbounds cur = seed;
+    for (int k = top; k >= 0; --k) {
+        lin_layer Lk = net_layer(net, k);
+        lbounds nxt = linear_backward(&Lk, &cur);
+        lb_free(&cur); cur = nxt;
+        if (k > 0) {
+            size_t o = pre_offset(net, k - 1);
+            lbounds r = relu_backward_crown(&cur, pre_lo + o, pre_hi + o);
+            lb_free(&cur); cur = r;
+        }
+    }
+    concretize(&cur, in_lo, in_hi, out_l, out_u);
+    lb_free(&cur);
+}
+
+/* ny-tensor bounded_tensor/core/numeric.rs:316-360: intersection with union fallback; returns 0
+ * (and leaves a untouched) if any endpoint is NaN. */
+static int intersect_per_element(float *al, float *au, const float *bl, const float *bu, int n) {
+    for (int i = 0; i < n; ++i) if (isnan(al[i]) || isnan(au[i]) || isnan(bl[i]) || isnan(bu[i])) return 0;
+    for (int i = 0; i < n; ++i) {
+        float tl = fmaxf(al[i], bl[i]), tu = fminf(au[i], bu[i]);
+        if (tl <= tu) { al[i] = tl; au[i] = tu; }
+        else { al[i] = fminf(al[i], bl[i]); au[i] = fmaxf(au[i], bu[i]); }
+    }
+    return 1;
+}
+
+int nyo_crown(const nyo_net *net, const float *in_lo, const float *in_hi, float *out_lo, float *out_hi,
+              float *inter_lo, float *inter_hi) {
+    int L = net->n_linear;
+    size_t total = pre_offset(net, L);
+    float *ibp_l = (float *)malloc(4 * total), *ibp_u = (float *)malloc(4 * total);
+    float *t_l = (float *)malloc(4 * total), *t_u = (float *)malloc(4 * total);
+    nyo_ibp_forward(net, in_lo, in_hi, ibp_l, ibp_u);
+    int maxn = 0;
+    for (int k = 0; k <= L; ++k) if (net->dims[k] > maxn) maxn = net->dims[k];
+    float *zl = (float *)malloc(4 * (size_t)maxn), *zu = (float *)malloc(4 * (size_t)maxn);
+    float *fl = (float *)malloc(4 * (size_t)maxn), *fu = (float *)malloc(4 * (size_t)maxn);
+    float *cl = (float *)malloc(4 * (size_t)maxn), *cu = (float *)malloc(4 * (size_t)maxn);
+    /* CROWN-IBP collection (network/ibp/crown_ibp.rs:32-420).  In the reference's layer list
+     * [Linear, ReLU, Linear, ...] every Linear output needs a partial CROWN pass (its successor is a
+     * ReLU, or it is the last layer); ReLU outputs take the forward shortcut and are recomputed from
+     * the tightened pre-activation when the next Linear needs them. */
+    for (int k = 0; k < L; ++k) {
+        lin_layer Lk = net_layer(net, k);
+        size_t o = pre_offset(net, k);
+        int n = Lk.n_out;
+        const float *il = ibp_l + o, *iu = ibp_u + o;
+        int all_stable = 1;
+        for (int j = 0; j < n; ++j) if (!(il[j] >= 0.0f || iu[j] <= 0.0f)) { all_stable = 0; break; }
+        if (k < L - 1 && all_stable) { /* ReLU-stable skip (:113-140) */
+            memcpy(t_l + o, il, 4 * (size_t)n); memcpy(t_u + o, iu, 4 * (size_t)n);
+            continue;
+        }
+        /* crown_partial.rs:166-182: forward bound of this layer from the tightened prior bounds */
+        if (k == 0) { memcpy(zl, in_lo, 4 * (size_t)Lk.n_in); memcpy(zu, in_hi, 4 * (size_t)Lk.n_in); }
+        else {
+            /* the ReLU output bound stored by the collection: relu IBP of the tightened
+             * pre-activation intersected with the plain IBP ReLU output (crown_ibp_forward.rs:25-100) */
+            size_t po = pre_offset(net, k - 1);
+            for (int j = 0; j < Lk.n_in; ++j) {
+                zl[j] = nanmax(t_l[po + j], 0.0f); zu[j] = nanmax(t_u[po + j], 0.0f);
+                fl[j] = nanmax(ibp_l[po + j], 0.0f); fu[j] = nanmax(ibp_u[po + j], 0.0f);
+            }
+            float *tmpl = (float *)malloc(4 * (size_t)Lk.n_in), *tmpu = (float *)malloc(4 * (size_t)Lk.n_in);
+            memcpy(tmpl, fl, 4 * (size_t)Lk.n_in); memcpy(tmpu, fu, 4 * (size_t)Lk.n_in);
+            if (intersect_per_element(tmpl, tmpu, zl, zu, Lk.n_in)) { memcpy(zl, tmpl, 4 * (size_t)Lk.n_in); memcpy(zu, tmpu, 4 * (size_t)Lk.n_in); }
+            else { memcpy(zl, fl, 4 * (size_t)Lk.n_in); memcpy(zu, fu, 4 * (size_t)Lk.n_in); }
+            free(tmpl); free(tmpu);
+        }
+        linear_ibp(&Lk, zl, zu, fl, fu);
+        /* sparse_merge.rs:118-146: when >= 90% of the neurons are stable only the unstable rows
+         * are propagated; stable rows keep the forward bound. */
+        int n_unst = 0;
+        for (int j = 0; j < n; ++j) if (fl[j] < 0.0f && fu[j] > 0.0f) ++n_unst;
+        int sparse = 0;
+        if (n_unst > 0) {
+            float stable_frac = 1.0f - ((float)n_unst / (float)n);
+            if (!(stable_frac < 0.9f)) sparse = 1;
+        }
+        lbounds seed;
+        int *rowmap = NULL;
+        if (sparse) {
+            seed = lb_alloc(n_unst, n, 0);
+            rowmap = (int *)malloc(sizeof(int) * (size_t)n_unst);
+            int r = 0;
+            for (int j = 0; j < n; ++j) if (fl[j] < 0.0f && fu[j] > 0.0f) {
+                seed.la[(size_t)r * n + j] = 1.0f; seed.ua[(size_t)r * n + j] = 1.0f; rowmap[r++] = j;
+            }
+        } else seed = lb_identity(n);
+        int rows = seed.rows;
+        float *rl = (float *)malloc(4 * (size_t)rows), *ru = (float *)malloc(4 * (size_t)rows);
+        crown_backward_concretize(net, k, seed, t_l, t_u, in_lo, in_hi, rl, ru);
+        if (sparse) {
+            memcpy(cl, fl, 4 * (size_t)n); memcpy(cu, fu, 4 * (size_t)n);
+            for (int r = 0; r < rows; ++r) { cl[rowmap[r]] = rl[r]; cu[rowmap[r]] = ru[r]; }
+            free(rowmap);
+        } else { memcpy(cl, rl, 4 * (size_t)n); memcpy(cu, ru, 4 * (size_t)n); }
+        free(rl); free(ru);
+        /* crown_ibp.rs:186-215: intersect the plain IBP bound with the CROWN bound */
+        memcpy(t_l + o, il, 4 * (size_t)n); memcpy(t_u + o, iu, 4 * (size_t)n);
+        intersect_per_element(t_l + o, t_u + o, cl, cu, n);
+    }
+    /* final backward (crown.rs:262-...) + tighten (crown/tighten.rs:126-190) */
+    {
+        int n = net->dims[L];
+        lbounds seed = lb_identity(n);
+        crown_backward_concretize(net, L - 1, seed, t_l, t_u, in_lo, in_hi, out_lo, out_hi);
+        size_t o = pre_offset(net, L - 1);
+        int has_nan = 0;
+        for (int j = 0; j < n; ++j) if (isnan(out_lo[j]) || isnan(out_hi[j])) has_nan = 1;
+        if (has_nan) { memcpy(out_lo, t_l + o, 4 * (size_t)n); memcpy(out_hi, t_u + o, 4 * (size_t)n); }
+        else intersect_per_element(out_lo, out_hi, t_l + o, t_u + o, n);
+    }
+    if (inter_lo) memcpy(inter_lo, t_l, 4 * total);
+    if (inter_hi) memcpy(inter_hi, t_u, 4 * total);
+    free(ibp_l); free(ibp_u); free(t_l); free(t_u); free(zl); free(zu); free(fl); free(fu); free(cl); free(cu);
+    return 0;
+}
+
+/* ------------------------------------------------------------------ beta-CROWN */
+/* beta_crown/engine/optimization/bound_compute.rs:90-167: identity at the output, backward through
+ * every layer with the alpha/beta ReLU rule, concretize_sound on the input box. */
+int nyo_beta_crown_bound(const nyo_net *net, const float *in_lo, const float *in_hi, const float *pre_lo,
+                         const float *pre_hi, const nyo_split *splits, int n_splits, const float *alpha,
+                         float *out_lo, float *out_hi) {
+    int L = net->n_linear;
+    lbounds cur = lb_identity(net->dims[L]);
+    for (int k = L - 1; k >= 0; --k) {
+        lin_layer Lk = net_layer(net, k);
+        lbounds nxt = linear_backward(&Lk, &cur);
+        lb_free(&cur); cur = nxt;
+        if (k > 0) {
+            int r = k - 1, n = net->dims[k];
+            size_t o = pre_offset(net, r);
+            signed char *sp = (signed char *)calloc((size_t)n, 1);
+            unsigned char *hs = (unsigned char *)calloc((size_t)n, 1);
+            float *sb = (float *)calloc((size_t)n, 4);
+            for (int s = 0; s < n_splits; ++s) if (splits[s].relu == r) {
+                int j = splits[s].neuron;
+                sp[j] = (signed char)(splits[s].sign > 0 ? 1 : -1);
+                hs[j] = 1; sb[j] = splits[s].beta * (splits[s].sign > 0 ? 1.0f : -1.0f);
+            }
+            lbounds rb = relu_backward_beta(&cur, pre_lo + o, pre_hi + o, sp, sb, hs, alpha ? alpha + o : NULL);
+            lb_free(&cur); cur = rb;
+            free(sp); free(hs); free(sb);
+        }
+    }
+    concretize(&cur, in_lo, in_hi, out_lo, out_hi);
+    lb_free(&cur);
+    return 0;
+}
+
+/* Intermediate bounds of a domain.
+ * mode 0: engine/domain/child.rs:51-118 (clamp the split neuron only).
+ * mode 1: engine/graph/propagation/constraints/mod.rs:400-760: walk the layers, re-propagate interval
+ *         bounds, intersect with the inherited bound, then apply the pre-activation clamps
+ *         (lookups.rs:138-185); ReLU outputs honour the split (active [max(l,0),u], inactive [0,0]). */
+int nyo_domain_bounds(const nyo_net *net, const float *in_lo, const float *in_hi, const float *inh_lo,
+                      const float *inh_hi, const nyo_split *splits, int n_splits, int mode,
+                      float *pre_lo, float *pre_hi) {
+    int L = net->n_linear;
+    size_t total = pre_offset(net, L);
+    memcpy(pre_lo, inh_lo, 4 * total); memcpy(pre_hi, inh_hi, 4 * total);
+    if (mode == 0) {
+        for (int s = 0; s < n_splits; ++s) {
+            size_t o = pre_offset(net, splits[s].relu) + (size_t)splits[s].neuron;
+            if (splits[s].sign > 0) pre_lo[o] = nanmax(pre_lo[o], 0.0f); else pre_hi[o] = nanmin(pre_hi[o], 0.0f);
+            if (pre_lo[o] > pre_hi[o]) return 1;
+        }
+        return 0;
+    }
+    int maxn = 0;
+    for (int k = 0; k <= L; ++k) if (net->dims[k] > maxn) maxn = net->dims[k];
+    float *zl = (float *)malloc(4 * (size_t)maxn), *zu = (float *)malloc(4 * (size_t)maxn);
+    float *nl = (float *)malloc(4 * (size_t)maxn), *nu = (float *)malloc(4 * (size_t)maxn);
+    memcpy(zl, in_lo, 4 * (size_t)net->dims[0]); memcpy(zu, in_hi, 4 * (size_t)net->dims[0]);
+    int infeasible = 0;
+    for (int k = 0; k < L && !infeasible; ++k) {
+        lin_layer Lk = net_layer(net, k);
+        size_t o = pre_offset(net, k);
+        int n = Lk.n_out;
+        linear_ibp(&Lk, zl, zu, nl, nu);
+        /* repropagated.intersection_per_element(current) (:738-741): self = re-propagated */
+        if (intersect_per_element(nl, nu, pre_lo + o, pre_hi + o, n)) { memcpy(pre_lo + o, nl, 4 * (size_t)n); memcpy(pre_hi + o, nu, 4 * (size_t)n); }
+        else { memcpy(pre_lo + o, nl, 4 * (size_t)n); memcpy(pre_hi + o, nu, 4 * (size_t)n); }
+        if (k == L - 1) break;
+        for (int s = 0; s < n_splits; ++s) if (splits[s].relu == k) {
+            size_t q = o + (size_t)splits[s].neuron;
+            if (splits[s].sign > 0) pre_lo[q] = nanmax(pre_lo[q], 0.0f); else pre_hi[q] = nanmin(pre_hi[q], 0.0f);
+            if (pre_lo[q] > pre_hi[q]) infeasible = 1;
+        }
+        /* ReLU node (:428-548).  The inherited post-activation bound is relu(inherited pre-activation);
+         * it never conflicts with the fresh bound because the pre-activation was already intersected. */
+        for (int j = 0; j < n; ++j) { zl[j] = nanmax(pre_lo[o + j], 0.0f); zu[j] = nanmax(pre_hi[o + j], 0.0f); }
+        for (int s = 0; s < n_splits; ++s) if (splits[s].relu == k) {
+            int j = splits[s].neuron;
+            if (splits[s].sign > 0) { if (pre_hi[o + j] < 0.0f) infeasible = 1; zl[j] = nanmax(pre_lo[o + j], 0.0f); zu[j] = pre_hi[o + j]; }
+            else { if (pre_lo[o + j] > 0.0f) infeasible = 1; zl[j] = 0.0f; zu[j] = 0.0f; }
+        }
+    }
+    free(zl); free(zu); free(nl); free(nu);
+    return infeasible;
+}
+
+typedef struct {
+    const nyo_net *net; const float *in_lo, *in_hi, *inh_lo, *inh_hi;
+    const nyo_split *splits; const int32_t *n_splits; int max_splits, D, mode;
+    float *out_lo, *out_hi; int32_t *infeasible;
+    int next; pthread_mutex_t mu;
+} batch_job;
+
+static void *batch_worker(void *arg) {
+    batch_job *J = (batch_job *)arg;
+    int L = J->net->n_linear;
+    size_t total = pre_offset(J->net, L);
+    int S = J->net->dims[L];
+    float *pl = (float *)malloc(4 * total), *pu = (float *)malloc(4 * total);
+    for (;;) {
+        pthread_mutex_lock(&J->mu);
+        int d = J->next++;
+        pthread_mutex_unlock(&J->mu);
+        if (d >= J->D) break;
+        const nyo_split *sp = J->splits + (size_t)d * J->max_splits;
+        int inf = nyo_domain_bounds(J->net, J->in_lo, J->in_hi, J->inh_lo, J->inh_hi, sp, J->n_splits[d], J->mode, pl, pu);
+        if (J->infeasible) J->infeasible[d] = inf;
+        if (inf) {
+            for (int s = 0; s < S; ++s) { J->out_lo[(size_t)d * S + s] = INFINITY; J->out_hi[(size_t)d * S + s] = -INFINITY; }
+        } else {
+            nyo_beta_crown_bound(J->net, J->in_lo, J->in_hi, pl, pu, sp, J->n_splits[d], NULL,
+                                 J->out_lo + (size_t)d * S, J->out_hi + (size_t)d * S);
+        }
+    }
+    free(pl); free(pu);
+    return NULL;
+}
+
+/* The reference parallelises BaB children with rayon over domains
+ * (beta_crown/engine/core.rs:651-684); this driver uses a pthread pool the same way. */
+int nyo_bab_bound_batch(const nyo_net *net, const float *in_lo, const float *in_hi, const float *inh_lo,
+                        const float *inh_hi, const nyo_split *splits, const int32_t *n_splits, int max_splits,
+                        int D, int mode, float *out_lo, float *out_hi, int32_t *infeasible, int n_threads) {
+    if (n_threads <= 0) { long c = sysconf(_SC_NPROCESSORS_ONLN); n_threads = c > 0 ? (int)c : 1; }
+    if (n_threads > D) n_threads = D > 0 ? D : 1;
+    batch_job J = { net, in_lo, in_hi, inh_lo, inh_hi, splits, n_splits, max_splits, D, mode, out_lo, out_hi, infeasible, 0, PTHREAD_MUTEX_INITIALIZER };
+    pthread_t *th = (pthread_t *)malloc(sizeof(pthread_t) * (size_t)n_threads);
+    for (int t = 1; t < n_threads; ++t) pthread_create(&th[t], NULL, batch_worker, &J);
+    batch_worker(&J);
+    for (int t = 1; t < n_threads; ++t) pthread_join(th[t], NULL);
+    free(th);
+    return n_threads;
+}
+
+/* beta_crown/engine/branching/sequential.rs:49-104 */
+int nyo_select_largest_width(const nyo_net *net, const float *pre_lo, const float *pre_hi, const nyo_split *splits,
+                             int n_splits, int32_t *relu, int32_t *neuron, float *width) {
+    int L = net->n_linear, found = 0;
+    float best = 0.0f;
+    for (int r = 0; r < L - 1; ++r) {
+        size_t o = pre_offset(net, r);
+        for (int j = 0; j < net->dims[r + 1]; ++j) {
+            float l = pre_lo[o + j], u = pre_hi[o + j];
+            if (l >= 0.0f || u <= 0.0f) continue;
+            int constrained = 0;
+            for (int s = 0; s < n_splits; ++s) if (splits[s].relu == r && splits[s].neuron == j) { constrained = 1; break; }
+            if (constrained) continue;
+            float w = u - l;
+            if (isnan(w)) continue;
+            if (!found || w > best) { found = 1; best = w; *relu = r; *neuron = j; }
+        }
+    }
+    if (found && width) *width = best;
+    return found;
+}
+
+/* beta_crown/config/beta_config.rs:1552-1610 (lower mode) */
+int nyo_domain_verified(float lower, float upper, float threshold) {
+    if (!isfinite(lower) || !isfinite(upper) || !isfinite(threshold) || lower > upper) return 0;
+    return lower > threshold;
+}
+int nyo_domain_violated(float lower, float upper, float threshold) {
+    if (!isfinite(lower) || !isfinite(upper) || !isfinite(threshold)) return 0;
+    if (lower > upper) return 0;
+    return upper < threshold;
+}

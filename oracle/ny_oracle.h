@@ -1,0 +1,104 @@
+/*
+ * ny_oracle.h -- CPU restatement of ny's bound-propagation path (TEST INFRASTRUCTURE).
+ *
+ * This library is the parity checker and the timed CPU baseline.  It is never part of
+ * the product path: only the test-suite, the smoke check and the benchmark's CPU legs
+ * may load it.  Every function cites the reference source (path inside the ny project)
+ * whose arithmetic it restates.  The reference is Rust and cannot be compiled in this
+ * environment, so this restatement is pinned against the golden values of the
+ * reference's own tests (crates/ny-propagate/src/tests/crown/reference.rs).
+ *
+ * Network model: a sequential ReLU MLP
+ *     x -> Linear_0 -> ReLU -> Linear_1 -> ReLU -> ... -> Linear_{L-1}
+ * dims[0..L] are the widths; weights are row-major [dims[k+1] x dims[k]] concatenated in
+ * `wflat`; biases are concatenated in `bflat` (has_bias[k]==0 means the layer has none and
+ * contributes no entries to bflat).  Convolutions are handled by the caller lowering them
+ * to their dense matrix (exact products summed in binary64 are unaffected by the zeros).
+ */
+#ifndef NY_ORACLE_H
+#define NY_ORACLE_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct {
+    int32_t n_linear;        /* L */
+    const int32_t *dims;     /* L+1 */
+    const float *wflat;
+    const float *bflat;
+    const int32_t *has_bias; /* L */
+} nyo_net;
+
+/* A split constraint on ReLU `relu` (0-based, the ReLU that follows Linear_relu),
+ * neuron `neuron`; sign +1 = active (pre-activation >= 0), -1 = inactive. */
+typedef struct {
+    int32_t relu;
+    int32_t neuron;
+    int32_t sign;
+    float beta;
+} nyo_split;
+
+/* scalar helpers (exported for unit tests) */
+float nyo_next_up_f32(float x);
+float nyo_next_down_f32(float x);
+double nyo_certified_affine_sum(float bias, const float *coef, const float *val, int n, int upper);
+
+/* IBP forward: writes pre-activation bounds of every Linear layer, concatenated
+ * (sum_{k=1..L} dims[k] floats each).  Returns 0. */
+int nyo_ibp_forward(const nyo_net *net, const float *in_lo, const float *in_hi,
+                    float *pre_lo, float *pre_hi);
+
+/* Plain CROWN of the sequential engine: IBP, CROWN-IBP intermediate tightening,
+ * final backward from identity, concretize, intersect with the forward bound.
+ * out_lo/out_hi have dims[L] entries.  If inter_lo/inter_hi are non-NULL they receive the
+ * tightened pre-activation bounds (same layout as nyo_ibp_forward). */
+int nyo_crown(const nyo_net *net, const float *in_lo, const float *in_hi,
+              float *out_lo, float *out_hi, float *inter_lo, float *inter_hi);
+
+/* beta-CROWN bound of one BaB domain given its pre-activation bounds
+ * (layout as nyo_ibp_forward, only the first L-1 blocks are read), its split list, and
+ * per-neuron lower slopes alpha (concatenated over the L-1 ReLUs; NULL = the
+ * heuristic [u > -l]).  out_lo/out_hi have dims[L] entries. */
+int nyo_beta_crown_bound(const nyo_net *net, const float *in_lo, const float *in_hi,
+                         const float *pre_lo, const float *pre_hi,
+                         const nyo_split *splits, int n_splits, const float *alpha,
+                         float *out_lo, float *out_hi);
+
+/* Per-domain intermediate bounds under a split history.
+ * mode 0 ("clamp only", sequential engine): copy the inherited bounds and clamp the split neurons.
+ * mode 1 ("constrained forward", graph engine): additionally re-propagate interval bounds
+ * downstream and keep the tighter of inherited / re-propagated per element.
+ * Returns 1 if the domain is infeasible (a clamp inverted an interval), else 0. */
+int nyo_domain_bounds(const nyo_net *net, const float *in_lo, const float *in_hi,
+                      const float *inh_lo, const float *inh_hi,
+                      const nyo_split *splits, int n_splits, int mode,
+                      float *pre_lo, float *pre_hi);
+
+/* Batch driver (a thread pool over domains): nyo_domain_bounds + nyo_beta_crown_bound for D
+ * domains sharing net, input box and inherited bounds.  splits is [D x max_splits],
+ * n_splits[d] valid entries each.  out_* are [D x dims[L]]; infeasible[d] is set to 1
+ * (and the bounds to +inf/-inf... i.e. lower=+inf, upper=-inf) for empty domains.
+ * Returns the number of threads used. */
+int nyo_bab_bound_batch(const nyo_net *net, const float *in_lo, const float *in_hi,
+                        const float *inh_lo, const float *inh_hi,
+                        const nyo_split *splits, const int32_t *n_splits, int max_splits,
+                        int D, int mode, float *out_lo, float *out_hi, int32_t *infeasible,
+                        int n_threads);
+
+/* Largest-width branching choice (first maximum wins, NaN skipped).
+ * Returns 1 and fills relu/neuron if an unstable unsplit neuron exists, else 0. */
+int nyo_select_largest_width(const nyo_net *net, const float *pre_lo, const float *pre_hi,
+                             const nyo_split *splits, int n_splits,
+                             int32_t *relu, int32_t *neuron, float *width);
+
+/* Verdict predicates (lower mode): verified iff finite and lower > threshold. */
+int nyo_domain_verified(float lower, float upper, float threshold);
+int nyo_domain_violated(float lower, float upper, float threshold);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

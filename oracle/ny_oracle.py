@@ -1,0 +1,183 @@
+"""ctypes binding of the CPU oracle (libny_oracle.so).
+
+TEST INFRASTRUCTURE ONLY: imported by tests/, by the smoke check and by the benchmark's
+CPU-baseline legs.  The product package never imports this module.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "libny_oracle.so")
+
+
+class _Net(C.Structure):
+    _fields_ = [
+        ("n_linear", C.c_int32),
+        ("dims", C.POINTER(C.c_int32)),
+        ("wflat", C.POINTER(C.c_float)),
+        ("bflat", C.POINTER(C.c_float)),
+        ("has_bias", C.POINTER(C.c_int32)),
+    ]
+
+
+SPLIT_DTYPE = np.dtype([("relu", "<i4"), ("neuron", "<i4"), ("sign", "<i4"), ("beta", "<f4")])
+
+
+def build(force: bool = False) -> str:
+    """Compile the oracle with the Makefile beside this file; returns the library path."""
+    src = os.path.join(_HERE, "ny_oracle.c")
+    if force or not os.path.exists(_LIB_PATH) or os.path.getmtime(_LIB_PATH) < os.path.getmtime(src):
+        subprocess.check_call(["make", "-C", _HERE, "-s"])
+    return _LIB_PATH
+
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        build()
+        L = C.CDLL(_LIB_PATH)
+        fp = C.POINTER(C.c_float)
+        ip = C.POINTER(C.c_int32)
+        np_ = C.POINTER(_Net)
+        L.nyo_next_up_f32.restype = C.c_float
+        L.nyo_next_up_f32.argtypes = [C.c_float]
+        L.nyo_next_down_f32.restype = C.c_float
+        L.nyo_next_down_f32.argtypes = [C.c_float]
+        L.nyo_certified_affine_sum.restype = C.c_double
+        L.nyo_certified_affine_sum.argtypes = [C.c_float, fp, fp, C.c_int, C.c_int]
+        L.nyo_ibp_forward.argtypes = [np_, fp, fp, fp, fp]
+        L.nyo_crown.argtypes = [np_, fp, fp, fp, fp, fp, fp]
+        L.nyo_beta_crown_bound.argtypes = [np_, fp, fp, fp, fp, C.c_void_p, C.c_int, fp, fp, fp]
+        L.nyo_domain_bounds.argtypes = [np_, fp, fp, fp, fp, C.c_void_p, C.c_int, C.c_int, fp, fp]
+        L.nyo_bab_bound_batch.argtypes = [np_, fp, fp, fp, fp, C.c_void_p, ip, C.c_int, C.c_int, C.c_int,
+                                          fp, fp, ip, C.c_int]
+        L.nyo_select_largest_width.argtypes = [np_, fp, fp, C.c_void_p, C.c_int, ip, ip, fp]
+        L.nyo_domain_verified.argtypes = [C.c_float, C.c_float, C.c_float]
+        L.nyo_domain_violated.argtypes = [C.c_float, C.c_float, C.c_float]
+        _lib = L
+    return _lib
+
+
+def _fp(a):
+    return a.ctypes.data_as(C.POINTER(C.c_float)) if a is not None else None
+
+
+def _ip(a):
+    return a.ctypes.data_as(C.POINTER(C.c_int32)) if a is not None else None
+
+
+class Net:
+    """Sequential ReLU MLP: weights[k] is [out, in] (row-major), biases[k] is [out] or None."""
+
+    def __init__(self, weights, biases=None):
+        self.weights = [np.ascontiguousarray(w, dtype=np.float32) for w in weights]
+        L = len(self.weights)
+        biases = biases if biases is not None else [None] * L
+        self.biases = [None if b is None else np.ascontiguousarray(b, dtype=np.float32) for b in biases]
+        self.dims = np.array([self.weights[0].shape[1]] + [w.shape[0] for w in self.weights], dtype=np.int32)
+        self._w = np.concatenate([w.ravel() for w in self.weights]).astype(np.float32)
+        bl = [b for b in self.biases if b is not None]
+        self._b = np.concatenate(bl).astype(np.float32) if bl else np.zeros(1, np.float32)
+        self._hb = np.array([0 if b is None else 1 for b in self.biases], dtype=np.int32)
+        self.c = _Net(L, _ip(self.dims), _fp(self._w), _fp(self._b), _ip(self._hb))
+
+    @property
+    def n_pre(self) -> int:
+        return int(self.dims[1:].sum())
+
+    def with_spec(self, spec) -> "Net":
+        """Append the specification rows as a bias-free Linear layer, the way ny's CLI does
+        (ny-cli commands/beta_crown/constraint_eval.rs:80-91)."""
+        return Net(self.weights + [np.asarray(spec, np.float32)], self.biases + [None])
+
+    def forward(self, x):
+        z = np.asarray(x, np.float64)
+        for k, w in enumerate(self.weights):
+            z = z @ w.astype(np.float64).T
+            if self.biases[k] is not None:
+                z = z + self.biases[k].astype(np.float64)
+            if k + 1 < len(self.weights):
+                z = np.maximum(z, 0.0)
+        return z
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def ibp_forward(net: Net, lo, hi):
+    lo, hi = _f32(lo), _f32(hi)
+    pl = np.empty(net.n_pre, np.float32)
+    pu = np.empty(net.n_pre, np.float32)
+    lib().nyo_ibp_forward(C.byref(net.c), _fp(lo), _fp(hi), _fp(pl), _fp(pu))
+    return pl, pu
+
+
+def crown(net: Net, lo, hi, want_intermediate=False):
+    lo, hi = _f32(lo), _f32(hi)
+    n = int(net.dims[-1])
+    ol, ou = np.empty(n, np.float32), np.empty(n, np.float32)
+    il = np.empty(net.n_pre, np.float32) if want_intermediate else None
+    iu = np.empty(net.n_pre, np.float32) if want_intermediate else None
+    lib().nyo_crown(C.byref(net.c), _fp(lo), _fp(hi), _fp(ol), _fp(ou), _fp(il), _fp(iu))
+    return (ol, ou, il, iu) if want_intermediate else (ol, ou)
+
+
+def make_splits(items) -> np.ndarray:
+    """items: iterable of (relu, neuron, sign, beta)."""
+    a = np.zeros(len(items), SPLIT_DTYPE)
+    for i, (r, j, s, b) in enumerate(items):
+        a[i] = (r, j, s, b)
+    return a
+
+
+def beta_crown_bound(net: Net, lo, hi, pre_lo, pre_hi, splits: np.ndarray, alpha=None):
+    lo, hi, pre_lo, pre_hi = _f32(lo), _f32(hi), _f32(pre_lo), _f32(pre_hi)
+    alpha = None if alpha is None else _f32(alpha)
+    n = int(net.dims[-1])
+    ol, ou = np.empty(n, np.float32), np.empty(n, np.float32)
+    splits = np.ascontiguousarray(splits, SPLIT_DTYPE)
+    lib().nyo_beta_crown_bound(C.byref(net.c), _fp(lo), _fp(hi), _fp(pre_lo), _fp(pre_hi),
+                               splits.ctypes.data, len(splits), _fp(alpha), _fp(ol), _fp(ou))
+    return ol, ou
+
+
+def domain_bounds(net: Net, lo, hi, inh_lo, inh_hi, splits: np.ndarray, mode: int):
+    lo, hi, inh_lo, inh_hi = _f32(lo), _f32(hi), _f32(inh_lo), _f32(inh_hi)
+    pl, pu = np.empty(net.n_pre, np.float32), np.empty(net.n_pre, np.float32)
+    splits = np.ascontiguousarray(splits, SPLIT_DTYPE)
+    inf = lib().nyo_domain_bounds(C.byref(net.c), _fp(lo), _fp(hi), _fp(inh_lo), _fp(inh_hi),
+                                  splits.ctypes.data, len(splits), mode, _fp(pl), _fp(pu))
+    return pl, pu, bool(inf)
+
+
+def bab_bound_batch(net: Net, lo, hi, inh_lo, inh_hi, splits: np.ndarray, n_splits, mode: int, n_threads: int = 0):
+    """splits: [D, max_splits] structured array; returns (lower [D,S], upper [D,S], infeasible [D], threads)."""
+    lo, hi, inh_lo, inh_hi = _f32(lo), _f32(hi), _f32(inh_lo), _f32(inh_hi)
+    splits = np.ascontiguousarray(splits, SPLIT_DTYPE)
+    D, M = splits.shape
+    n_splits = np.ascontiguousarray(n_splits, np.int32)
+    S = int(net.dims[-1])
+    ol, ou = np.empty((D, S), np.float32), np.empty((D, S), np.float32)
+    inf = np.zeros(D, np.int32)
+    used = lib().nyo_bab_bound_batch(C.byref(net.c), _fp(lo), _fp(hi), _fp(inh_lo), _fp(inh_hi),
+                                     splits.ctypes.data, _ip(n_splits), M, D, mode, _fp(ol), _fp(ou), _ip(inf),
+                                     n_threads)
+    return ol, ou, inf, used
+
+
+def select_largest_width(net: Net, pre_lo, pre_hi, splits: np.ndarray):
+    pre_lo, pre_hi = _f32(pre_lo), _f32(pre_hi)
+    splits = np.ascontiguousarray(splits, SPLIT_DTYPE)
+    r, j, w = C.c_int32(-1), C.c_int32(-1), C.c_float(0)
+    ok = lib().nyo_select_largest_width(C.byref(net.c), _fp(pre_lo), _fp(pre_hi), splits.ctypes.data, len(splits),
+                                        C.byref(r), C.byref(j), C.byref(w))
+    return (r.value, j.value, w.value) if ok else None

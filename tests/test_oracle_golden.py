@@ -1,0 +1,102 @@
+"""Pins the CPU oracle against the known answers held by the reference's own tests.
+
+Sources (paths inside the ny project):
+  crates/ny-propagate/src/tests/crown/reference.rs:22-158   toy 2-2-1 net (IBP [-6,4], CROWN [-3,3])
+  crates/ny-propagate/src/tests/crown/reference.rs:160-380  3-4-4-2 MLP, eps 0.1 (8-digit IBP/CROWN values)
+  crates/ny-propagate/src/tests/crown/reference.rs:382-467  tiny 2-2-2 net, CROWN after IBP intersection
+  crates/ny-propagate/src/beta_crown/config/tests.rs        verdict predicates (strictness, NaN, inf)
+The reference asserts |ny - value| < 1e-4 (1e-5 for the tiny net); the same tolerances are used here.
+"""
+import math
+
+import numpy as np
+
+FC1 = [[0.16834518, 0.06440470, 0.11723118], [0.11516652, -0.56142819, -0.09316415],
+       [1.10410070, -0.31899852, 0.23082861], [0.13367544, 0.26745233, 0.40467861]]
+B1 = [0.11102903, -0.16897990, -0.09889599, 0.09579718]
+FC2 = [[-0.69233710, -0.43561807, -0.11168297, 0.85868055], [0.15943986, -0.21225949, 0.15286016, -0.38729626],
+       [-0.77878612, 0.49781805, -0.43989292, -0.30057147], [-0.63707572, 1.06139255, -0.61732668, -0.24395694]]
+B2 = [0.02815196, 0.00561635, 0.05227160, -0.02383569]
+FC3 = [[-0.02495167, 0.26316848, -0.00424941, 0.36453030], [0.06657098, 0.43198884, -0.50783736, -0.44437426]]
+B3 = [0.01497797, -0.02088939]
+
+
+def test_toy_model(oracle):
+    net = oracle.Net([[[1, -1], [2, -1]], [[1, -1]]])
+    lo, hi = [-1, -2], [2, 1]
+    pl, pu = oracle.ibp_forward(net, lo, hi)
+    assert abs(pl[-1] - (-6.0)) < 1e-4 and abs(pu[-1] - 4.0) < 1e-4
+    cl, cu = oracle.crown(net, lo, hi)
+    assert abs(cl[0] - (-3.0)) < 1e-4 and abs(cu[0] - 3.0) < 1e-4
+    for x in ([-1, -2], [2, 1], [0.5, -0.5]):
+        y = net.forward(x)[0]
+        assert pl[-1] - 1e-5 <= y <= pu[-1] + 1e-5
+        assert cl[0] - 1e-5 <= y <= cu[0] + 1e-5
+
+
+def test_deep_model(oracle):
+    net = oracle.Net([FC1, FC2, FC3], [B1, B2, B3])
+    lo, hi = [0.4] * 3, [0.6] * 3
+    pl, pu = oracle.ibp_forward(net, lo, hi)
+    np.testing.assert_allclose(pl[-2:], [0.00687957, -0.01418082], atol=1e-4, rtol=0)
+    np.testing.assert_allclose(pu[-2:], [0.01246351, 0.00071711], atol=1e-4, rtol=0)
+    cl, cu = oracle.crown(net, lo, hi)
+    np.testing.assert_allclose(cl, [0.00820859, -0.01063502], atol=1e-4, rtol=0)
+    np.testing.assert_allclose(cu, [0.01113450, -0.00282869], atol=1e-4, rtol=0)
+    # the published values carry 8 digits; the restatement agrees far inside the reference's tolerance
+    np.testing.assert_allclose(cl, [0.00820859, -0.01063502], atol=5e-8, rtol=0)
+    np.testing.assert_allclose(cu, [0.01113450, -0.00282869], atol=5e-8, rtol=0)
+    assert np.all(cu - cl <= pu[-2:] - pl[-2:] + 1e-5)
+    y = net.forward([0.5] * 3)
+    assert np.all(y >= cl - 1e-5) and np.all(y <= cu + 1e-5)
+
+
+def test_tiny_model_intersection(oracle):
+    net = oracle.Net([[[1, 1], [1, -1]], [[1, 0], [0, 1]]], [[-0.5, 0], [0, 0]])
+    pl, pu = oracle.ibp_forward(net, [0, 0], [1, 1])
+    np.testing.assert_allclose(np.maximum(pl[:2], 0), [0, 0], atol=1e-5)
+    np.testing.assert_allclose(pl[2:], [0, 0], atol=1e-5)
+    np.testing.assert_allclose(pu[2:], [1.5, 1.0], atol=1e-5)
+    cl, cu = oracle.crown(net, [0, 0], [1, 1])
+    np.testing.assert_allclose(cl, [0, 0], atol=1e-5)
+    np.testing.assert_allclose(cu, [1.5, 1.0], atol=1e-5)
+
+
+def test_directed_rounding_steps(oracle):
+    L = oracle.lib()
+    assert L.nyo_next_up_f32(0.0) == np.float32(1e-45)
+    assert L.nyo_next_down_f32(0.0) == -np.float32(1e-45)
+    assert L.nyo_next_up_f32(1.0) == np.nextafter(np.float32(1), np.float32(2))
+    assert L.nyo_next_down_f32(-1.0) == np.nextafter(np.float32(-1), np.float32(-2))
+    assert math.isinf(L.nyo_next_up_f32(float("inf"))) and math.isnan(L.nyo_next_up_f32(float("nan")))
+
+
+def test_certified_reduction_known_answers(oracle):
+    # crates/ny-propagate/src/bounds/certified_reduction.rs `mod tests`
+    big = np.float32(2.0 ** 30)
+    coef = np.array([big, 1.0, -big], np.float32)
+    val = np.array([big, 1.0, big], np.float32)
+    lo = oracle.lib().nyo_certified_affine_sum(0.0, oracle._fp(coef), oracle._fp(val), 3, 0)
+    hi = oracle.lib().nyo_certified_affine_sum(0.0, oracle._fp(coef), oracle._fp(val), 3, 1)
+    assert lo <= 1.0 <= hi and lo > 0.99 and hi < 1.01
+    coef = np.array([0.0, -0.0, 5.0, 0.0, -np.inf], np.float32)
+    val = np.array([3.0, -7.0, 0.0, np.inf, -0.0], np.float32)
+    assert oracle.lib().nyo_certified_affine_sum(0.0, oracle._fp(coef), oracle._fp(val), 5, 0) == 0.0
+    assert oracle.lib().nyo_certified_affine_sum(-0.0, oracle._fp(coef), oracle._fp(val), 5, 1) == 0.0
+    tiny = np.array([np.float32(1e-45)], np.float32)
+    one = np.array([1.0], np.float32)
+    lo = oracle.lib().nyo_certified_affine_sum(0.0, oracle._fp(tiny), oracle._fp(one), 1, 0)
+    hi = oracle.lib().nyo_certified_affine_sum(0.0, oracle._fp(tiny), oracle._fp(one), 1, 1)
+    assert 0.0 < lo <= float(tiny[0]) <= hi
+
+
+def test_verdict_predicates(oracle):
+    L = oracle.lib()
+    assert L.nyo_domain_verified(0.1, 1.0, 0.0) == 1
+    assert L.nyo_domain_verified(0.0, 1.0, 0.0) == 0  # strict
+    assert L.nyo_domain_verified(float("nan"), 1.0, 0.0) == 0
+    assert L.nyo_domain_verified(0.5, float("inf"), 0.0) == 0
+    assert L.nyo_domain_verified(2.0, 1.0, 0.0) == 0  # inverted
+    assert L.nyo_domain_violated(-2.0, -1.0, 0.0) == 1
+    assert L.nyo_domain_violated(-2.0, 0.0, 0.0) == 0
+    assert L.nyo_domain_violated(-1.0, -2.0, 0.0) == 0
