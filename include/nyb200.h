@@ -1,0 +1,148 @@
+/*
+ * nyb200.h -- C ABI of the B200 (sm_100a) bound-propagation engine.
+ *
+ * Every entry point takes plain pointers and sizes and returns an int32 status; no C++ or
+ * framework types cross this boundary.  The functions are what a Rust (or any FFI) binding of
+ * ny's engine plugin traits would bind; each comment names the reference interface it stands in
+ * for (paths inside the ny project).  Host pointers unless a comment says "device".
+ *
+ * Threading: an engine handle serialises its own calls (as ny-cuda does behind a mutex,
+ * crates/ny-cuda/src/lib.rs:1402-1420); distinct handles are independent.
+ *
+ * There is no CPU fallback: a call on a machine without a usable CUDA device fails with
+ * NYB200_ERR_UNSUPPORTED from nyb200_create and nothing else can be called.
+ */
+#ifndef NYB200_H
+#define NYB200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes: one per ny_core::NyError variant the engine boundary uses
+ * (crates/ny-core/src/error.rs:18).  UNSUPPORTED is a decline, never fatal. */
+#define NYB200_OK 0
+#define NYB200_ERR_UNSUPPORTED 1 /* NyError::UnsupportedOp      */
+#define NYB200_ERR_SHAPE 2       /* NyError::ShapeMismatch      */
+#define NYB200_ERR_INVALID 3     /* NyError::InvalidSpec        */
+#define NYB200_ERR_NUMERICAL 4   /* NyError::NumericalInstability */
+#define NYB200_ERR_DEADLINE 5    /* NyError::DeadlineExceeded   */
+#define NYB200_ERR_OOM 6         /* NyError::CpuMemoryExceeded / device allocation failure */
+#define NYB200_ERR_INTERNAL 7    /* NyError::InternalError      */
+
+typedef struct nyb200_engine nyb200_engine;
+
+/* One ReLU split of a BaB domain: `relu` is the 0-based index of the ReLU layer (the one
+ * after Linear_relu), `neuron` its flat neuron index, `sign` +1 active / -1 inactive and
+ * `beta` the Lagrange multiplier (>= 0).  Mirrors NeuronConstraint + BetaEntry
+ * (crates/ny-propagate/src/beta_crown/state/beta.rs:20-40). */
+typedef struct {
+    int32_t relu;
+    int32_t neuron;
+    int32_t sign;
+    float beta;
+} nyb200_split;
+
+/* Arithmetic used for the A*W contraction of the backward pass. */
+#define NYB200_PATH_F64 0   /* binary64 FMA accumulation of exact fp32 products */
+#define NYB200_PATH_TF32X3 1 /* tcgen05 3xTF32 split products, chunked TMEM accumulators */
+
+/* ---- lifecycle ---------------------------------------------------------------------------
+ * Engine construction/provenance: GemmEngine::backend_provenance (crates/ny-core/src/gemm.rs:313)
+ * and the CLI's factory seams (crates/ny-cli/src/main.rs:577-700). */
+int32_t nyb200_create(int32_t device_ordinal, nyb200_engine **out);
+void nyb200_destroy(nyb200_engine *e);
+const char *nyb200_backend_provenance(void);
+const char *nyb200_last_error(const nyb200_engine *e);
+/* Launch all work of this engine on the given cudaStream_t (NULL = the default stream). */
+int32_t nyb200_set_stream(nyb200_engine *e, void *cuda_stream);
+/* Select the contraction arithmetic (NYB200_PATH_*).  Default NYB200_PATH_F64. */
+int32_t nyb200_set_path(nyb200_engine *e, int32_t path);
+/* Number of kernels this engine has launched since creation (bench bookkeeping). */
+int64_t nyb200_launch_count(const nyb200_engine *e);
+/* GpuCrownBackward::clear_crown_working_set (crates/ny-core/src/gemm.rs:3205). */
+int32_t nyb200_clear_working_set(nyb200_engine *e);
+
+/* ---- GemmEngine::gemm_f32 (crates/ny-core/src/gemm.rs:325): C[m,n] = A[m,k] * B[k,n], row-major. */
+int32_t nyb200_gemm_f32(nyb200_engine *e, int32_t m, int32_t k, int32_t n, const float *a, const float *b,
+                        float *c_out);
+
+/* ---- network residency -------------------------------------------------------------------
+ * Stands in for the Arc<[f32]> pointer-identity cache key of GpuCrownLayer::Linear
+ * (crates/ny-core/src/gemm.rs:1524-1547): weights are uploaded once and named by an id.
+ * Sequential ReLU MLP: dims[0..n_linear]; weights row-major [dims[k+1] x dims[k]] concatenated;
+ * has_bias[k]==0 layers contribute nothing to bflat. */
+int32_t nyb200_net_create(nyb200_engine *e, int32_t n_linear, const int32_t *dims, const float *wflat,
+                          const float *bflat, const int32_t *has_bias, int32_t *net_id);
+int32_t nyb200_net_destroy(nyb200_engine *e, int32_t net_id);
+
+/* ---- GpuIbpForward::ibp_forward_gpu_sound (crates/ny-core/src/gemm_gpu_ibp.rs:78-135) ------
+ * Interval forward pass for D boxes.  in_lo/in_hi are [D x dims[0]] (box_stride = dims[0]) or a
+ * single shared box (box_stride = 0).  pre_lo/pre_hi receive the pre-activation bounds of every
+ * Linear layer, [D x sum_{k>=1} dims[k]]. */
+int32_t nyb200_ibp_forward(nyb200_engine *e, int32_t net_id, int32_t D, const float *in_lo, const float *in_hi,
+                           int32_t box_stride, float *pre_lo, float *pre_hi);
+
+/* ---- beta-CROWN bound of a batch of BaB domains --------------------------------------------
+ * One call = for every domain: intermediate bounds under its splits, alpha/beta ReLU relaxation,
+ * CROWN backward of the spec rows, concretisation on the input box.  It fuses the host
+ * preparation and the engine call of process_gpu_batched Phase 2
+ * (crates/ny-propagate/src/beta_crown/engine/graph/gpu_bab/batched_gpu.rs:89,
+ *  engine/graph/propagation/batched.rs:1695-1708 ->
+ *  GpuCrownBackward::crown_backward_gpu_resnet_sound_beta_batched, crates/ny-core/src/gemm.rs:3944)
+ * and returns what compute_bounds_with_alpha_beta returns per domain
+ * (crates/ny-propagate/src/beta_crown/engine/optimization/bound_compute.rs:90).
+ *
+ *   spec          [S x dims[L]] specification rows (appended as a bias-free Linear layer by ny's CLI)
+ *   in_lo/in_hi   input box, shared (box_stride 0) or per domain (box_stride dims[0])
+ *   inh_lo/inh_hi inherited pre-activation bounds [sum_{k>=1} dims[k]] (root or parent bounds)
+ *   splits        [D x max_splits], n_splits[d] valid entries per domain
+ *   mode          0 clamp-only intermediate bounds (sequential engine, engine/domain/child.rs:51-118)
+ *                 1 constrained forward re-propagation (graph engine, constraints/mod.rs:184-760)
+ *   alpha         NULL (heuristic [u > -l]) or [D x sum_{k=1..L-1} dims[k]] lower slopes
+ *   out_lo/out_hi [D x S]; an infeasible domain gets lower=+inf, upper=-inf and infeasible[d]=1
+ */
+int32_t nyb200_bab_bound_batch(nyb200_engine *e, int32_t net_id, const float *spec, int32_t S, const float *in_lo,
+                               const float *in_hi, int32_t box_stride, const float *inh_lo, const float *inh_hi,
+                               const nyb200_split *splits, const int32_t *n_splits, int32_t max_splits, int32_t D,
+                               int32_t mode, const float *alpha, float *out_lo, float *out_hi,
+                               int32_t *infeasible);
+
+/* ---- resident batch (extension: keeps the domain batch in HBM between calls) ----------------
+ * upload copies the same arguments as nyb200_bab_bound_batch to the device; run launches the
+ * whole bound evaluation asynchronously on the engine stream with no host<->device traffic;
+ * download copies the results back (synchronises the stream).  The reference keeps operands
+ * resident only within one call (crates/ny-core/src/gemm.rs:568-578); this is the frontier
+ * residency a BaB driver needs to reach the memory roofline. */
+int32_t nyb200_batch_upload(nyb200_engine *e, int32_t net_id, const float *spec, int32_t S, const float *in_lo,
+                            const float *in_hi, int32_t box_stride, const float *inh_lo, const float *inh_hi,
+                            const nyb200_split *splits, const int32_t *n_splits, int32_t max_splits, int32_t D,
+                            int32_t mode, const float *alpha);
+int32_t nyb200_batch_run(nyb200_engine *e);
+int32_t nyb200_batch_download(nyb200_engine *e, float *out_lo, float *out_hi, int32_t *infeasible);
+/* Smallest lower bound over all feasible domains and rows of the last run (the per-round global
+ * lower bound that the multi-GPU driver min-reduces).  Synchronises the stream. */
+int32_t nyb200_batch_min_lower(nyb200_engine *e, float *min_lower);
+/* Device pointer to that value (float, valid until the next run) for an in-stream collective. */
+int32_t nyb200_batch_min_lower_device(nyb200_engine *e, void **dev_ptr);
+/* Pre-activation bounds of the last run, [D x sum_{k>=1} dims[k]] (what BabDomain::layer_bounds
+ * holds, crates/ny-propagate/src/beta_crown/domain.rs). */
+int32_t nyb200_batch_download_pre_bounds(nyb200_engine *e, float *pre_lo, float *pre_hi);
+/* Largest-width branching choice per domain of the last run (first maximum wins, NaN skipped,
+ * split neurons excluded): select_largest_width_neuron,
+ * crates/ny-propagate/src/beta_crown/engine/branching/sequential.rs:49-104.
+ * relu[d] = -1 when the domain has no unstable unsplit neuron. */
+int32_t nyb200_batch_select_branch(nyb200_engine *e, int32_t *relu, int32_t *neuron, float *width);
+
+/* Kernel-only timing of the last nyb200_batch_run calls: average milliseconds per run of the
+ * named phase ("forward", "backward", "total") measured with CUDA events on the engine stream
+ * since the last reset. */
+int32_t nyb200_timing_reset(nyb200_engine *e);
+int32_t nyb200_timing_read(nyb200_engine *e, const char *phase, double *avg_ms, int32_t *n_runs);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,559 @@
+// Host side of the C ABI declared in include/nyb200.h: engine lifecycle, network residency,
+// workspace management and the launch sequences.  No CPU arithmetic path exists here: every
+// numeric result is produced by the kernels in this directory.
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+
+#include "nyb200_internal.cuh"
+
+using namespace nyb;
+
+namespace nyb {
+
+int set_err(nyb200_engine *e, int code, const std::string &msg) {
+    if (e) e->err = msg;
+    return code;
+}
+
+int check_cuda(nyb200_engine *e, cudaError_t st, const char *what) {
+    if (st == cudaSuccess) return NYB200_OK;
+    std::string m = std::string(what) + ": " + cudaGetErrorString(st);
+    int code = (st == cudaErrorMemoryAllocation) ? NYB200_ERR_OOM : NYB200_ERR_INTERNAL;
+    return set_err(e, code, m);
+}
+
+void *ws_get(nyb200_engine *e, const char *name, size_t bytes) {
+    DevBuf &b = e->ws[name];
+    if (b.bytes >= bytes && b.p) return b.p;
+    if (b.p) { cudaFree(b.p); b.p = nullptr; b.bytes = 0; }
+    size_t want = bytes < 256 ? 256 : bytes;
+    void *p = nullptr;
+    cudaError_t st = cudaMalloc(&p, want);
+    if (st != cudaSuccess) { check_cuda(e, st, (std::string("cudaMalloc ") + name).c_str()); return nullptr; }
+    b.p = p; b.bytes = want;
+    return p;
+}
+
+}  // namespace nyb
+
+#define NYB_TRY(expr)                      \
+    do {                                   \
+        int _st = (expr);                  \
+        if (_st != NYB200_OK) return _st;  \
+    } while (0)
+#define NYB_CUDA(e, call) NYB_TRY(check_cuda((e), (call), #call))
+#define NYB_WS(var, type, e, name, bytes)                          \
+    type var = (type)ws_get((e), (name), (bytes));                 \
+    if (!var) return NYB200_ERR_OOM;
+
+extern "C" {
+
+const char *nyb200_backend_provenance(void) {
+    return "nyb200 sm_100a engine (hand-written CUDA kernels; no library GEMM; no CPU fallback)";
+}
+
+int32_t nyb200_create(int32_t device_ordinal, nyb200_engine **out) {
+    if (!out) return NYB200_ERR_INVALID;
+    *out = nullptr;
+    int count = 0;
+    cudaError_t st = cudaGetDeviceCount(&count);
+    if (st != cudaSuccess || count <= 0) return NYB200_ERR_UNSUPPORTED;
+    if (device_ordinal < 0 || device_ordinal >= count) return NYB200_ERR_INVALID;
+    if (cudaSetDevice(device_ordinal) != cudaSuccess) return NYB200_ERR_UNSUPPORTED;
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, device_ordinal) != cudaSuccess) return NYB200_ERR_UNSUPPORTED;
+    if (prop.major != 10) return NYB200_ERR_UNSUPPORTED;  // kernels are built for sm_100a only
+    nyb200_engine *e = new nyb200_engine();
+    e->device = device_ordinal;
+    for (int i = 0; i < 3; ++i) cudaEventCreate(&e->timing.ev[i]);
+    *out = e;
+    return NYB200_OK;
+}
+
+void nyb200_destroy(nyb200_engine *e) {
+    if (!e) return;
+    cudaSetDevice(e->device);
+    cudaStreamSynchronize(e->stream);
+    for (auto &kv : e->ws) if (kv.second.p) cudaFree(kv.second.p);
+    for (auto &kv : e->nets) for (float *p : kv.second.owned) cudaFree(p);
+    for (int i = 0; i < 3; ++i) if (e->timing.ev[i]) cudaEventDestroy(e->timing.ev[i]);
+    delete e;
+}
+
+const char *nyb200_last_error(const nyb200_engine *e) { return e ? e->err.c_str() : "null engine"; }
+
+int32_t nyb200_set_stream(nyb200_engine *e, void *cuda_stream) {
+    if (!e) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    e->stream = (cudaStream_t)cuda_stream;
+    return NYB200_OK;
+}
+
+int32_t nyb200_set_path(nyb200_engine *e, int32_t path) {
+    if (!e) return NYB200_ERR_INVALID;
+    if (path != NYB200_PATH_F64 && path != NYB200_PATH_TF32X3) return set_err(e, NYB200_ERR_INVALID, "unknown path");
+    std::lock_guard<std::mutex> g(e->mu);
+    e->path = path;
+    return NYB200_OK;
+}
+
+int64_t nyb200_launch_count(const nyb200_engine *e) { return e ? e->launches : 0; }
+
+int32_t nyb200_clear_working_set(nyb200_engine *e) {
+    if (!e) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    cudaSetDevice(e->device);
+    cudaStreamSynchronize(e->stream);
+    for (auto &kv : e->ws) if (kv.second.p) cudaFree(kv.second.p);
+    e->ws.clear();
+    e->batch = Batch();
+    return NYB200_OK;
+}
+
+int32_t nyb200_net_create(nyb200_engine *e, int32_t n_linear, const int32_t *dims, const float *wflat,
+                          const float *bflat, const int32_t *has_bias, int32_t *net_id) {
+    if (!e || !dims || !wflat || !has_bias || !net_id) return NYB200_ERR_INVALID;
+    if (n_linear < 1 || n_linear > kMaxLinear) return set_err(e, NYB200_ERR_UNSUPPORTED, "layer count out of range");
+    std::lock_guard<std::mutex> g(e->mu);
+    NYB_CUDA(e, cudaSetDevice(e->device));
+    Net net;
+    memset(&net.v, 0, sizeof(net.v));
+    net.v.L = n_linear;
+    int off = 0;
+    for (int k = 0; k <= n_linear; ++k) {
+        if (dims[k] <= 0) return set_err(e, NYB200_ERR_SHAPE, "non-positive layer width");
+        net.v.dims[k] = dims[k];
+        if (dims[k] > net.max_dim) net.max_dim = dims[k];
+        if (k >= 1) { net.v.pre_off[k - 1] = off; off += dims[k]; }
+    }
+    net.v.pre_off[n_linear] = off;
+    net.v.n_pre = off;
+    size_t wo = 0, bo = 0;
+    for (int k = 0; k < n_linear; ++k) {
+        size_t nw = (size_t)dims[k] * dims[k + 1];
+        float *dw = nullptr;
+        NYB_CUDA(e, cudaMalloc(&dw, nw * sizeof(float)));
+        net.owned.push_back(dw);
+        NYB_CUDA(e, cudaMemcpy(dw, wflat + wo, nw * sizeof(float), cudaMemcpyHostToDevice));
+        net.v.W[k] = dw;
+        wo += nw;
+        if (has_bias[k]) {
+            if (!bflat) return set_err(e, NYB200_ERR_INVALID, "has_bias set but bflat is null");
+            float *db = nullptr;
+            NYB_CUDA(e, cudaMalloc(&db, (size_t)dims[k + 1] * sizeof(float)));
+            net.owned.push_back(db);
+            NYB_CUDA(e, cudaMemcpy(db, bflat + bo, (size_t)dims[k + 1] * sizeof(float), cudaMemcpyHostToDevice));
+            net.v.b[k] = db;
+            bo += dims[k + 1];
+        }
+    }
+    int id = e->next_net++;
+    e->nets[id] = net;
+    *net_id = id;
+    return NYB200_OK;
+}
+
+int32_t nyb200_net_destroy(nyb200_engine *e, int32_t net_id) {
+    if (!e) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    auto it = e->nets.find(net_id);
+    if (it == e->nets.end()) return set_err(e, NYB200_ERR_INVALID, "unknown net id");
+    cudaSetDevice(e->device);
+    cudaStreamSynchronize(e->stream);
+    for (float *p : it->second.owned) cudaFree(p);
+    e->nets.erase(it);
+    if (e->batch.net_id == net_id) e->batch = Batch();
+    return NYB200_OK;
+}
+
+int32_t nyb200_gemm_f32(nyb200_engine *e, int32_t m, int32_t k, int32_t n, const float *a, const float *b,
+                        float *c_out) {
+    if (!e || !a || !b || !c_out) return NYB200_ERR_INVALID;
+    if (m <= 0 || k <= 0 || n <= 0) return set_err(e, NYB200_ERR_SHAPE, "gemm_f32: non-positive dimension");
+    std::lock_guard<std::mutex> g(e->mu);
+    NYB_CUDA(e, cudaSetDevice(e->device));
+    NYB_WS(da, float *, e, "gemm_a", (size_t)m * k * 4);
+    NYB_WS(db, float *, e, "gemm_b", (size_t)k * n * 4);
+    NYB_WS(dc, float *, e, "gemm_c", (size_t)m * n * 4);
+    NYB_CUDA(e, cudaMemcpyAsync(da, a, (size_t)m * k * 4, cudaMemcpyHostToDevice, e->stream));
+    NYB_CUDA(e, cudaMemcpyAsync(db, b, (size_t)k * n * 4, cudaMemcpyHostToDevice, e->stream));
+    launch_gemm_f64(e, m, n, k, da, k, db, n, dc, n, 1, nullptr, nullptr, 0, nullptr);
+    NYB_CUDA(e, cudaGetLastError());
+    NYB_CUDA(e, cudaMemcpyAsync(c_out, dc, (size_t)m * n * 4, cudaMemcpyDeviceToHost, e->stream));
+    NYB_CUDA(e, cudaStreamSynchronize(e->stream));
+    return NYB200_OK;
+}
+
+}  // extern "C"
+
+// ------------------------------------------------------------------ batch plumbing
+namespace {
+
+struct BatchPtrs {
+    float *spec, *in_lo, *in_hi, *inh_lo, *inh_hi, *alpha;
+    nyb200_split *splits;
+    int *nsplits, *flags;
+    signed char *code;
+    float *sbeta, *raw_lo, *raw_hi, *q, *pre_lo, *pre_hi, *zl, *zu, *zabs;
+    float4 *tab;
+    float *A0, *A1;
+    double *rb, *rabs, *rpen;
+    float *out_lo, *out_hi, *min_lower;
+    int lda;
+};
+
+int batch_ptrs(nyb200_engine *e, const Net &net, const Batch &b, BatchPtrs &p) {
+    const NetView &nv = net.v;
+    size_t D = (size_t)b.D, np = (size_t)nv.n_pre;
+    size_t M = D * b.R;
+    p.lda = (net.max_dim + 3) & ~3;
+    size_t box = (size_t)nv.dims[0] * (b.box_stride ? D : 1);
+#define GET(field, type, name, bytes)                                   \
+    p.field = (type)ws_get(e, name, (bytes));                            \
+    if (!p.field) return NYB200_ERR_OOM;
+    GET(spec, float *, "spec", (size_t)b.S * nv.dims[nv.L] * 4)
+    GET(in_lo, float *, "in_lo", box * 4)
+    GET(in_hi, float *, "in_hi", box * 4)
+    GET(inh_lo, float *, "inh_lo", np * 4)
+    GET(inh_hi, float *, "inh_hi", np * 4)
+    GET(alpha, float *, "alpha", b.has_alpha ? D * np * 4 : 4)
+    GET(splits, nyb200_split *, "splits", D * (size_t)(b.max_splits > 0 ? b.max_splits : 1) * sizeof(nyb200_split))
+    GET(nsplits, int *, "nsplits", D * 4)
+    GET(flags, int *, "flags", D * 4)
+    GET(code, signed char *, "code", D * np)
+    GET(sbeta, float *, "sbeta", D * np * 4)
+    GET(raw_lo, float *, "raw_lo", D * np * 4)
+    GET(raw_hi, float *, "raw_hi", D * np * 4)
+    GET(q, float *, "q", D * np * 4)
+    GET(pre_lo, float *, "pre_lo", D * np * 4)
+    GET(pre_hi, float *, "pre_hi", D * np * 4)
+    GET(zl, float *, "zl", D * np * 4)
+    GET(zu, float *, "zu", D * np * 4)
+    GET(zabs, float *, "zabs", D * np * 4)
+    GET(tab, float4 *, "tab", D * np * 16)
+    GET(A0, float *, "A0", M * p.lda * 4)
+    GET(A1, float *, "A1", M * p.lda * 4)
+    GET(rb, double *, "rb", M * 8)
+    GET(rabs, double *, "rabs", M * 8)
+    GET(rpen, double *, "rpen", M * 8)
+    GET(out_lo, float *, "out_lo", D * b.S * 4)
+    GET(out_hi, float *, "out_hi", D * b.S * 4)
+    GET(min_lower, float *, "min_lower", 256)
+#undef GET
+    return NYB200_OK;
+}
+
+int find_net(nyb200_engine *e, int net_id, Net **out) {
+    auto it = e->nets.find(net_id);
+    if (it == e->nets.end()) return set_err(e, NYB200_ERR_INVALID, "unknown net id");
+    *out = &it->second;
+    return NYB200_OK;
+}
+
+// Interval forward pass for the resident batch.  fwd_mode: 0 clamp-only, 1 constrained, 2 plain IBP.
+int run_forward(nyb200_engine *e, const Net &net, const Batch &b, BatchPtrs &p, int fwd_mode) {
+    const NetView &nv = net.v;
+    int D = b.D;
+    size_t np = nv.n_pre;
+    NYB_CUDA(e, cudaMemsetAsync(p.flags, 0, (size_t)D * 4, e->stream));
+    NYB_CUDA(e, cudaMemsetAsync(p.code, 0, (size_t)D * np, e->stream));
+    NYB_CUDA(e, cudaMemsetAsync(p.sbeta, 0, (size_t)D * np * 4, e->stream));
+    if (fwd_mode != 2 && b.max_splits > 0)
+        launch_scatter_splits(e, nv, p.splits, p.nsplits, b.max_splits, D, p.code, p.sbeta, p.flags);
+    for (int k = 0; k < nv.L; ++k) {
+        const float *zl, *zu;
+        long in_ds;
+        int Deff;
+        if (k == 0) { zl = p.in_lo; zu = p.in_hi; in_ds = b.box_stride; Deff = b.box_stride ? D : 1; }
+        else { zl = p.zl + nv.pre_off[k - 1]; zu = p.zu + nv.pre_off[k - 1]; in_ds = (long)np; Deff = D; }
+        launch_ibp_linear(e, nv, k, Deff, zl, zu, in_ds, p.raw_lo, p.raw_hi, p.q, (long)np);
+        long raw_ds = (Deff == 1 && D > 1) ? 0 : (long)np;
+        launch_ibp_finish(e, nv, k, D, fwd_mode, p.raw_lo, p.raw_hi, raw_ds, fwd_mode == 2 ? nullptr : p.inh_lo,
+                          fwd_mode == 2 ? nullptr : p.inh_hi, p.code, p.sbeta, b.has_alpha ? p.alpha : nullptr, p.pre_lo,
+                          p.pre_hi, p.zl, p.zu, p.tab, p.zabs, p.flags);
+    }
+    NYB_CUDA(e, cudaGetLastError());
+    return NYB200_OK;
+}
+
+int run_backward(nyb200_engine *e, const Net &net, const Batch &b, BatchPtrs &p) {
+    const NetView &nv = net.v;
+    int D = b.D, S = b.S, R = b.R, L = nv.L;
+    int M = D * R;
+    long np = nv.n_pre;
+    bool shared_box = (b.box_stride == 0 && D > 1);
+    NYB_CUDA(e, cudaMemsetAsync(p.rb, 0, (size_t)M * 8, e->stream));
+    NYB_CUDA(e, cudaMemsetAsync(p.rabs, 0, (size_t)M * 8, e->stream));
+    NYB_CUDA(e, cudaMemsetAsync(p.rpen, 0, (size_t)M * 8, e->stream));
+    const float inf = INFINITY;
+    NYB_CUDA(e, cudaMemcpyAsync(p.min_lower, &inf, 4, cudaMemcpyHostToDevice, e->stream));
+    float *cur = p.A0, *nxt = p.A1;
+    launch_seed(e, p.spec, S, nv.dims[L], D, p.lda, cur);
+    auto eps_for = [&](int K) { return (double)(K + 2) * 1.1102230246251565e-16 * 1.000001; };
+    auto q_ds = [&](int lin_k) { return (lin_k == 0 && shared_box) ? 0L : np; };
+    launch_relax(e, nv, -1, L - 1, M, R, S, cur, p.lda, p.tab, p.zabs, p.q, q_ds(L - 1), eps_for(nv.dims[L]), p.rb, p.rabs,
+                 p.rpen);
+    for (int k = L - 1; k >= 0; --k) {
+        int K = nv.dims[k + 1], N = nv.dims[k];
+        const float *zin_lo, *zin_hi;
+        long zin_ds;
+        if (k > 0) { zin_lo = p.zl + nv.pre_off[k - 1]; zin_hi = p.zu + nv.pre_off[k - 1]; zin_ds = np; }
+        else { zin_lo = p.in_lo; zin_hi = p.in_hi; zin_ds = b.box_stride; }
+        launch_gemm_f64(e, M, N, K, cur, p.lda, nv.W[k], N, nxt, p.lda, R, zin_lo, zin_hi, zin_ds, p.rpen);
+        if (k > 0)
+            launch_relax(e, nv, k - 1, k - 1, M, R, S, nxt, p.lda, p.tab, p.zabs, p.q, q_ds(k - 1), eps_for(N), p.rb, p.rabs,
+                         p.rpen);
+        float *t = cur; cur = nxt; nxt = t;
+    }
+    launch_concretize(e, M, R, S, nv.dims[0], cur, p.lda, p.in_lo, p.in_hi, b.box_stride, p.rb, p.rabs, p.rpen, p.flags,
+                      p.out_lo, p.out_hi, p.min_lower);
+    NYB_CUDA(e, cudaGetLastError());
+    return NYB200_OK;
+}
+
+int upload_batch(nyb200_engine *e, int32_t net_id, const float *spec, int32_t S, const float *in_lo, const float *in_hi,
+                 int32_t box_stride, const float *inh_lo, const float *inh_hi, const nyb200_split *splits,
+                 const int32_t *n_splits, int32_t max_splits, int32_t D, int32_t mode, const float *alpha) {
+    Net *net;
+    NYB_TRY(find_net(e, net_id, &net));
+    const NetView &nv = net->v;
+    if (D <= 0 || S <= 0) return set_err(e, NYB200_ERR_SHAPE, "D and S must be positive");
+    if (!spec || !in_lo || !in_hi) return set_err(e, NYB200_ERR_INVALID, "null spec or input box");
+    if (box_stride != 0 && box_stride != nv.dims[0]) return set_err(e, NYB200_ERR_SHAPE, "box_stride must be 0 or dims[0]");
+    if (mode != 0 && mode != 1) return set_err(e, NYB200_ERR_INVALID, "mode must be 0 or 1");
+    if (!inh_lo || !inh_hi) return set_err(e, NYB200_ERR_INVALID, "inherited bounds are required");
+    if (max_splits < 0 || (max_splits > 0 && (!splits || !n_splits))) return set_err(e, NYB200_ERR_INVALID, "bad split list");
+    if ((long)D * 2 * S > 0x7fffffffL / 64) return set_err(e, NYB200_ERR_UNSUPPORTED, "batch too large for one call");
+    for (int d = 0; d < D && n_splits; ++d)
+        if (n_splits[d] < 0 || n_splits[d] > max_splits) return set_err(e, NYB200_ERR_INVALID, "n_splits out of range");
+    NYB_CUDA(e, cudaSetDevice(e->device));
+    Batch b;
+    b.net_id = net_id; b.S = S; b.R = 2 * S; b.D = D; b.mode = mode; b.box_stride = box_stride; b.max_splits = max_splits;
+    b.has_alpha = alpha != nullptr;
+    BatchPtrs p;
+    NYB_TRY(batch_ptrs(e, *net, b, p));
+    size_t np = nv.n_pre;
+    size_t box = (size_t)nv.dims[0] * (box_stride ? (size_t)D : 1);
+    cudaStream_t s = e->stream;
+    NYB_CUDA(e, cudaMemcpyAsync(p.spec, spec, (size_t)S * nv.dims[nv.L] * 4, cudaMemcpyHostToDevice, s));
+    NYB_CUDA(e, cudaMemcpyAsync(p.in_lo, in_lo, box * 4, cudaMemcpyHostToDevice, s));
+    NYB_CUDA(e, cudaMemcpyAsync(p.in_hi, in_hi, box * 4, cudaMemcpyHostToDevice, s));
+    NYB_CUDA(e, cudaMemcpyAsync(p.inh_lo, inh_lo, np * 4, cudaMemcpyHostToDevice, s));
+    NYB_CUDA(e, cudaMemcpyAsync(p.inh_hi, inh_hi, np * 4, cudaMemcpyHostToDevice, s));
+    if (alpha) NYB_CUDA(e, cudaMemcpyAsync(p.alpha, alpha, (size_t)D * np * 4, cudaMemcpyHostToDevice, s));
+    if (max_splits > 0) {
+        NYB_CUDA(e, cudaMemcpyAsync(p.splits, splits, (size_t)D * max_splits * sizeof(nyb200_split), cudaMemcpyHostToDevice, s));
+        NYB_CUDA(e, cudaMemcpyAsync(p.nsplits, n_splits, (size_t)D * 4, cudaMemcpyHostToDevice, s));
+    }
+    b.valid = true;
+    e->batch = b;
+    return NYB200_OK;
+}
+
+int run_batch(nyb200_engine *e) {
+    if (!e->batch.valid) return set_err(e, NYB200_ERR_INVALID, "no batch uploaded");
+    Net *net;
+    NYB_TRY(find_net(e, e->batch.net_id, &net));
+    if (e->path != NYB200_PATH_F64) return set_err(e, NYB200_ERR_UNSUPPORTED, "contraction path not available in this build");
+    BatchPtrs p;
+    NYB_TRY(batch_ptrs(e, *net, e->batch, p));
+    Timing &t = e->timing;
+    if (t.pending) {  // fold the previous run's events before reusing them
+        if (cudaEventSynchronize(t.ev[2]) == cudaSuccess) {
+            float f = 0, bw = 0;
+            cudaEventElapsedTime(&f, t.ev[0], t.ev[1]);
+            cudaEventElapsedTime(&bw, t.ev[1], t.ev[2]);
+            t.fwd_ms += f; t.bwd_ms += bw; t.tot_ms += f + bw; t.runs++;
+        }
+        t.pending = false;
+    }
+    cudaEventRecord(t.ev[0], e->stream);
+    NYB_TRY(run_forward(e, *net, e->batch, p, e->batch.mode));
+    cudaEventRecord(t.ev[1], e->stream);
+    NYB_TRY(run_backward(e, *net, e->batch, p));
+    cudaEventRecord(t.ev[2], e->stream);
+    t.pending = true;
+    e->batch.ran = true;
+    return NYB200_OK;
+}
+
+int download_batch(nyb200_engine *e, float *out_lo, float *out_hi, int32_t *infeasible) {
+    if (!e->batch.valid || !e->batch.ran) return set_err(e, NYB200_ERR_INVALID, "no batch has been run");
+    Net *net;
+    NYB_TRY(find_net(e, e->batch.net_id, &net));
+    BatchPtrs p;
+    NYB_TRY(batch_ptrs(e, *net, e->batch, p));
+    size_t n = (size_t)e->batch.D * e->batch.S;
+    if (out_lo) NYB_CUDA(e, cudaMemcpyAsync(out_lo, p.out_lo, n * 4, cudaMemcpyDeviceToHost, e->stream));
+    if (out_hi) NYB_CUDA(e, cudaMemcpyAsync(out_hi, p.out_hi, n * 4, cudaMemcpyDeviceToHost, e->stream));
+    if (infeasible) NYB_CUDA(e, cudaMemcpyAsync(infeasible, p.flags, (size_t)e->batch.D * 4, cudaMemcpyDeviceToHost, e->stream));
+    NYB_CUDA(e, cudaStreamSynchronize(e->stream));
+    if (infeasible) {
+        for (int d = 0; d < e->batch.D; ++d) {
+            if (infeasible[d] & kFlagInvalid) return set_err(e, NYB200_ERR_INVALID, "split entry out of range");
+            infeasible[d] = (infeasible[d] & kFlagInfeasible) ? 1 : 0;
+        }
+    }
+    return NYB200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t nyb200_batch_upload(nyb200_engine *e, int32_t net_id, const float *spec, int32_t S, const float *in_lo,
+                            const float *in_hi, int32_t box_stride, const float *inh_lo, const float *inh_hi,
+                            const nyb200_split *splits, const int32_t *n_splits, int32_t max_splits, int32_t D,
+                            int32_t mode, const float *alpha) {
+    if (!e) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    return upload_batch(e, net_id, spec, S, in_lo, in_hi, box_stride, inh_lo, inh_hi, splits, n_splits, max_splits, D, mode,
+                        alpha);
+}
+
+int32_t nyb200_batch_run(nyb200_engine *e) {
+    if (!e) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    NYB_CUDA(e, cudaSetDevice(e->device));
+    return run_batch(e);
+}
+
+int32_t nyb200_batch_download(nyb200_engine *e, float *out_lo, float *out_hi, int32_t *infeasible) {
+    if (!e) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    NYB_CUDA(e, cudaSetDevice(e->device));
+    return download_batch(e, out_lo, out_hi, infeasible);
+}
+
+int32_t nyb200_bab_bound_batch(nyb200_engine *e, int32_t net_id, const float *spec, int32_t S, const float *in_lo,
+                               const float *in_hi, int32_t box_stride, const float *inh_lo, const float *inh_hi,
+                               const nyb200_split *splits, const int32_t *n_splits, int32_t max_splits, int32_t D,
+                               int32_t mode, const float *alpha, float *out_lo, float *out_hi, int32_t *infeasible) {
+    if (!e || !out_lo || !out_hi) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    NYB_TRY(upload_batch(e, net_id, spec, S, in_lo, in_hi, box_stride, inh_lo, inh_hi, splits, n_splits, max_splits, D, mode,
+                         alpha));
+    NYB_TRY(run_batch(e));
+    return download_batch(e, out_lo, out_hi, infeasible);
+}
+
+int32_t nyb200_batch_min_lower_device(nyb200_engine *e, void **dev_ptr) {
+    if (!e || !dev_ptr) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    if (!e->batch.valid) return set_err(e, NYB200_ERR_INVALID, "no batch uploaded");
+    void *p = ws_get(e, "min_lower", 256);
+    if (!p) return NYB200_ERR_OOM;
+    *dev_ptr = p;
+    return NYB200_OK;
+}
+
+int32_t nyb200_batch_min_lower(nyb200_engine *e, float *min_lower) {
+    if (!e || !min_lower) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    if (!e->batch.valid || !e->batch.ran) return set_err(e, NYB200_ERR_INVALID, "no batch has been run");
+    NYB_CUDA(e, cudaSetDevice(e->device));
+    void *p = ws_get(e, "min_lower", 256);
+    if (!p) return NYB200_ERR_OOM;
+    NYB_CUDA(e, cudaMemcpyAsync(min_lower, p, 4, cudaMemcpyDeviceToHost, e->stream));
+    NYB_CUDA(e, cudaStreamSynchronize(e->stream));
+    return NYB200_OK;
+}
+
+int32_t nyb200_batch_download_pre_bounds(nyb200_engine *e, float *pre_lo, float *pre_hi) {
+    if (!e || !pre_lo || !pre_hi) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    if (!e->batch.valid || !e->batch.ran) return set_err(e, NYB200_ERR_INVALID, "no batch has been run");
+    NYB_CUDA(e, cudaSetDevice(e->device));
+    Net *net;
+    NYB_TRY(find_net(e, e->batch.net_id, &net));
+    BatchPtrs p;
+    NYB_TRY(batch_ptrs(e, *net, e->batch, p));
+    size_t n = (size_t)e->batch.D * net->v.n_pre;
+    NYB_CUDA(e, cudaMemcpyAsync(pre_lo, p.pre_lo, n * 4, cudaMemcpyDeviceToHost, e->stream));
+    NYB_CUDA(e, cudaMemcpyAsync(pre_hi, p.pre_hi, n * 4, cudaMemcpyDeviceToHost, e->stream));
+    NYB_CUDA(e, cudaStreamSynchronize(e->stream));
+    return NYB200_OK;
+}
+
+int32_t nyb200_batch_select_branch(nyb200_engine *e, int32_t *relu, int32_t *neuron, float *width) {
+    if (!e || !relu || !neuron) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    if (!e->batch.valid || !e->batch.ran) return set_err(e, NYB200_ERR_INVALID, "no batch has been run");
+    NYB_CUDA(e, cudaSetDevice(e->device));
+    Net *net;
+    NYB_TRY(find_net(e, e->batch.net_id, &net));
+    BatchPtrs p;
+    NYB_TRY(batch_ptrs(e, *net, e->batch, p));
+    int D = e->batch.D;
+    NYB_WS(dr, int *, e, "br_relu", (size_t)D * 4);
+    NYB_WS(dn, int *, e, "br_neuron", (size_t)D * 4);
+    NYB_WS(dw, float *, e, "br_width", (size_t)D * 4);
+    launch_select_branch(e, net->v, D, p.pre_lo, p.pre_hi, p.code, dr, dn, dw);
+    NYB_CUDA(e, cudaGetLastError());
+    NYB_CUDA(e, cudaMemcpyAsync(relu, dr, (size_t)D * 4, cudaMemcpyDeviceToHost, e->stream));
+    NYB_CUDA(e, cudaMemcpyAsync(neuron, dn, (size_t)D * 4, cudaMemcpyDeviceToHost, e->stream));
+    if (width) NYB_CUDA(e, cudaMemcpyAsync(width, dw, (size_t)D * 4, cudaMemcpyDeviceToHost, e->stream));
+    NYB_CUDA(e, cudaStreamSynchronize(e->stream));
+    return NYB200_OK;
+}
+
+int32_t nyb200_ibp_forward(nyb200_engine *e, int32_t net_id, int32_t D, const float *in_lo, const float *in_hi,
+                           int32_t box_stride, float *pre_lo, float *pre_hi) {
+    if (!e || !in_lo || !in_hi || !pre_lo || !pre_hi) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    Net *net;
+    NYB_TRY(find_net(e, net_id, &net));
+    const NetView &nv = net->v;
+    if (D <= 0) return set_err(e, NYB200_ERR_SHAPE, "D must be positive");
+    if (box_stride != 0 && box_stride != nv.dims[0]) return set_err(e, NYB200_ERR_SHAPE, "box_stride must be 0 or dims[0]");
+    NYB_CUDA(e, cudaSetDevice(e->device));
+    Batch b;
+    b.net_id = net_id; b.S = 1; b.R = 2; b.D = D; b.mode = 1; b.box_stride = box_stride; b.max_splits = 0;
+    BatchPtrs p;
+    NYB_TRY(batch_ptrs(e, *net, b, p));
+    size_t box = (size_t)nv.dims[0] * (box_stride ? (size_t)D : 1);
+    NYB_CUDA(e, cudaMemcpyAsync(p.in_lo, in_lo, box * 4, cudaMemcpyHostToDevice, e->stream));
+    NYB_CUDA(e, cudaMemcpyAsync(p.in_hi, in_hi, box * 4, cudaMemcpyHostToDevice, e->stream));
+    e->batch = Batch();  // the resident batch's buffers are being reused
+    NYB_TRY(run_forward(e, *net, b, p, 2));
+    size_t n = (size_t)D * nv.n_pre;
+    NYB_CUDA(e, cudaMemcpyAsync(pre_lo, p.pre_lo, n * 4, cudaMemcpyDeviceToHost, e->stream));
+    NYB_CUDA(e, cudaMemcpyAsync(pre_hi, p.pre_hi, n * 4, cudaMemcpyDeviceToHost, e->stream));
+    NYB_CUDA(e, cudaStreamSynchronize(e->stream));
+    return NYB200_OK;
+}
+
+int32_t nyb200_timing_reset(nyb200_engine *e) {
+    if (!e) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    if (e->timing.pending) { cudaEventSynchronize(e->timing.ev[2]); e->timing.pending = false; }
+    e->timing.fwd_ms = e->timing.bwd_ms = e->timing.tot_ms = 0;
+    e->timing.runs = 0;
+    return NYB200_OK;
+}
+
+int32_t nyb200_timing_read(nyb200_engine *e, const char *phase, double *avg_ms, int32_t *n_runs) {
+    if (!e || !phase || !avg_ms) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    Timing &t = e->timing;
+    if (t.pending) {
+        if (cudaEventSynchronize(t.ev[2]) == cudaSuccess) {
+            float f = 0, bw = 0;
+            cudaEventElapsedTime(&f, t.ev[0], t.ev[1]);
+            cudaEventElapsedTime(&bw, t.ev[1], t.ev[2]);
+            t.fwd_ms += f; t.bwd_ms += bw; t.tot_ms += f + bw; t.runs++;
+        }
+        t.pending = false;
+    }
+    double tot = 0;
+    if (!strcmp(phase, "forward")) tot = t.fwd_ms;
+    else if (!strcmp(phase, "backward")) tot = t.bwd_ms;
+    else if (!strcmp(phase, "total")) tot = t.tot_ms;
+    else return set_err(e, NYB200_ERR_INVALID, "unknown phase");
+    *avg_ms = t.runs ? tot / t.runs : 0.0;
+    if (n_runs) *n_runs = t.runs;
+    return NYB200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,108 @@
+// Internal declarations shared by the engine's translation units (not part of the C ABI).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <map>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/nyb200.h"
+
+namespace nyb {
+
+constexpr int kMaxLinear = 32;
+
+// Per-domain flag bits written by the kernels.
+constexpr int kFlagInfeasible = 1;  // a split clamp inverted an interval: the domain is empty
+constexpr int kFlagDegraded = 2;    // NaN / infinite pre-activation bound: bounds degrade to [-inf, +inf]
+constexpr int kFlagInvalid = 4;     // split entry out of range
+
+// Device-side view of a registered network (passed by value to kernels).
+struct NetView {
+    int L;                        // number of Linear layers
+    int dims[kMaxLinear + 1];     // widths
+    int pre_off[kMaxLinear + 1];  // offset of Linear_k's output block inside a [n_pre] row
+    int n_pre;                    // sum_{k>=1} dims[k]
+    const float *W[kMaxLinear];   // device, row-major [dims[k+1] x dims[k]]
+    const float *b[kMaxLinear];   // device or nullptr
+};
+
+struct Net {
+    NetView v;
+    std::vector<float *> owned;
+    int max_dim = 0;
+};
+
+struct DevBuf {
+    void *p = nullptr;
+    size_t bytes = 0;
+};
+
+struct Batch {
+    bool valid = false;
+    int net_id = -1;
+    int S = 0, R = 0, D = 0, mode = 0, box_stride = 0, max_splits = 0;
+    bool has_alpha = false;
+    bool ran = false;
+};
+
+struct Timing {
+    cudaEvent_t ev[3] = {nullptr, nullptr, nullptr};  // start, after forward, end
+    double fwd_ms = 0, bwd_ms = 0, tot_ms = 0;
+    int runs = 0;
+    bool pending = false;
+};
+
+}  // namespace nyb
+
+struct nyb200_engine {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    int path = NYB200_PATH_F64;
+    std::string err;
+    std::mutex mu;
+    std::map<int, nyb::Net> nets;
+    int next_net = 1;
+    int64_t launches = 0;
+    nyb::Batch batch;
+    nyb::Timing timing;
+    std::map<std::string, nyb::DevBuf> ws;  // named grow-only device workspace
+};
+
+namespace nyb {
+
+// Returns a device buffer of at least `bytes` under `name` (grow-only); nullptr on failure.
+void *ws_get(nyb200_engine *e, const char *name, size_t bytes);
+int set_err(nyb200_engine *e, int code, const std::string &msg);
+int check_cuda(nyb200_engine *e, cudaError_t st, const char *what);
+
+// ---- kernel launchers (nyb200_kernels.cu) ----
+void launch_scatter_splits(nyb200_engine *e, const NetView &nv, const nyb200_split *sp, const int *ns, int max_splits,
+                           int D, signed char *code, float *sbeta, int *flags);
+// Interval mat-vec of Linear_k for Deff boxes (binary64 accumulation, outward rounded).
+void launch_ibp_linear(nyb200_engine *e, const NetView &nv, int k, int Deff, const float *zl, const float *zu,
+                       long in_dstride, float *raw_lo, float *raw_hi, float *q, long out_dstride);
+// Per-domain finish of Linear_k's output: intersect / clamp / relaxation tables / post-activation.
+void launch_ibp_finish(nyb200_engine *e, const NetView &nv, int k, int D, int mode, const float *raw_lo,
+                       const float *raw_hi, long raw_dstride, const float *inh_lo, const float *inh_hi,
+                       const signed char *code, const float *sbeta, const float *alpha, float *pre_lo, float *pre_hi,
+                       float *zl, float *zu, float4 *tab, float *zabs, int *flags);
+void launch_seed(nyb200_engine *e, const float *spec, int S, int nL, int D, int lda, float *A);
+// In-place ReLU relaxation of A [M x n] (ReLU r) or identity pass (r < 0), accumulating the row sums.
+void launch_relax(nyb200_engine *e, const NetView &nv, int r, int lin_k, int M, int R, int S, float *A, int lda,
+                  const float4 *tab, const float *zabs, const float *q, long q_dstride, double eps_gemm, double *rb,
+                  double *rabs, double *rpen);
+// C[M x N] = A[M x K] * W_k (binary64 accumulation), cast error charged to rpen.
+void launch_gemm_f64(nyb200_engine *e, int M, int N, int K, const float *A, int lda, const float *B, int ldb, float *C,
+                     int ldc, int R, const float *zin_lo, const float *zin_hi, long zin_dstride, double *rpen);
+void launch_concretize(nyb200_engine *e, int M, int R, int S, int n0, const float *A, int lda, const float *in_lo,
+                       const float *in_hi, long box_dstride, const double *rb, const double *rabs, const double *rpen,
+                       const int *flags, float *out_lo, float *out_hi, float *min_lower);
+void launch_select_branch(nyb200_engine *e, const NetView &nv, int D, const float *pre_lo, const float *pre_hi,
+                          const signed char *code, int *relu, int *neuron, float *width);
+void launch_fill_f64(nyb200_engine *e, double *p, size_t n, double v);
+
+}  // namespace nyb

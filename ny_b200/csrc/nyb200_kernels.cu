@@ -1,0 +1,512 @@
+// CUDA kernels of the bound-propagation engine (sm_100a): interval forward pass, ReLU
+// relaxation with alpha slopes and beta multipliers, binary64-accumulated A*W contraction,
+// concretisation and branching.  The tcgen05 contraction lives in nyb200_umma.cu.
+//
+// Soundness bookkeeping used by every kernel here.  Each row of the coefficient tensor A
+// carries three binary64 scalars:
+//   rb    the bias accumulated so far (round-to-nearest sums of exact fp32 x fp32 products),
+//   rabs  the sum of the magnitudes of everything added to rb (bounds the rounding of rb),
+//   rpen  a non-negative penalty: every rounding committed on a coefficient is immediately
+//         multiplied by the largest magnitude the variable it multiplies can take (known from
+//         the interval forward pass) and added here.  At the end the lower bound is
+//         rb + (concretised A) - rpen - slack, rounded toward -inf; the upper bound mirrors it.
+// This is the role the per-coefficient error matrices play in the reference
+// (crates/ny-propagate/src/layers/linear/crown_single.rs:2092-2103, discharged at
+// bounds/concretize.rs:443-466), but discharged layer by layer against the layer's own interval
+// (as the reference's device path does with node_abs/frontier_abs,
+// crates/ny-core/src/gemm.rs:2939-2952) so that no |W| chain is ever formed.
+#include "nyb200_internal.cuh"
+
+namespace nyb {
+
+// ---------------------------------------------------------------- device helpers
+__device__ __forceinline__ float next_up_f(float x) {  // crates/ny-tensor/src/rounding.rs:17-33
+    unsigned b = __float_as_uint(x), mag = b & 0x7fffffffu;
+    if (mag >= 0x7f800000u) return x;
+    if (mag == 0) return __uint_as_float(1u);
+    return (b & 0x80000000u) ? __uint_as_float(b - 1) : __uint_as_float(b + 1);
+}
+__device__ __forceinline__ float next_down_f(float x) {  // crates/ny-tensor/src/rounding.rs:47-63
+    unsigned b = __float_as_uint(x), mag = b & 0x7fffffffu;
+    if (mag >= 0x7f800000u) return x;
+    if (mag == 0) return __uint_as_float(0x80000001u);
+    return (b & 0x80000000u) ? __uint_as_float(b + 1) : __uint_as_float(b - 1);
+}
+__device__ __forceinline__ double warp_sum(double v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// ---------------------------------------------------------------- split scatter
+__global__ void k_scatter_splits(NetView nv, const nyb200_split *__restrict__ sp, const int *__restrict__ ns,
+                                 int max_splits, int D, signed char *__restrict__ code, float *__restrict__ sbeta,
+                                 int *__restrict__ flags) {
+    long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= (long)D * max_splits) return;
+    int d = (int)(t / max_splits), s = (int)(t % max_splits);
+    if (s >= ns[d]) return;
+    nyb200_split c = sp[t];
+    if (c.relu < 0 || c.relu >= nv.L - 1 || c.neuron < 0 || c.neuron >= nv.dims[c.relu + 1] ||
+        (c.sign != 1 && c.sign != -1)) {
+        atomicOr(&flags[d], kFlagInvalid);
+        return;
+    }
+    long o = (long)d * nv.n_pre + nv.pre_off[c.relu] + c.neuron;
+    code[o] = (signed char)c.sign;
+    // A non-finite multiplier is skipped, as relu_backward.rs:156-173 does.
+    sbeta[o] = isfinite(c.beta) ? c.beta * (float)c.sign : 0.0f;
+}
+
+// ---------------------------------------------------------------- interval mat-vec (Linear IBP)
+// lo = W+ zl + W- zu + b, hi = W+ zu + W- zl + b (crates/ny-propagate/src/layers/linear/ibp.rs:489-515),
+// q = |W| max(|zl|,|zu|).  Exact fp32 products are accumulated in binary64; the accumulation error is
+// bounded by gamma_{K+1} * q (Higham) and removed outward before the directed cast to fp32.
+constexpr int IB_M = 64, IB_N = 64, IB_K = 16;
+__global__ void __launch_bounds__(256)
+k_ibp_linear(int Deff, int n_in, int n_out, const float *__restrict__ W, const float *__restrict__ bias,
+             const float *__restrict__ zl, const float *__restrict__ zu, long in_ds, float *__restrict__ raw_lo,
+             float *__restrict__ raw_hi, float *__restrict__ q, long out_ds) {
+    __shared__ float sL[IB_K][IB_M + 1], sU[IB_K][IB_M + 1], sW[IB_K][IB_N + 1];
+    int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    int d0 = blockIdx.y * IB_M, o0 = blockIdx.x * IB_N;
+    double lo[4][4], hi[4][4], qq[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) lo[i][j] = hi[i][j] = qq[i][j] = 0.0;
+    for (int k0 = 0; k0 < n_in; k0 += IB_K) {
+        for (int t = threadIdx.x; t < IB_M * IB_K; t += 256) {
+            int r = t / IB_K, kk = t % IB_K;
+            int d = d0 + r, k = k0 + kk;
+            float a = 0.f, b = 0.f;
+            if (d < Deff && k < n_in) { a = zl[(long)d * in_ds + k]; b = zu[(long)d * in_ds + k]; }
+            sL[kk][r] = a; sU[kk][r] = b;
+        }
+        for (int t = threadIdx.x; t < IB_N * IB_K; t += 256) {
+            int r = t / IB_K, kk = t % IB_K;
+            int o = o0 + r, k = k0 + kk;
+            sW[kk][r] = (o < n_out && k < n_in) ? W[(long)o * n_in + k] : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < IB_K; ++kk) {
+            double zlv[4], zuv[4], zm[4], w[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float a = sL[kk][ty * 4 + i], b = sU[kk][ty * 4 + i];
+                zlv[i] = a; zuv[i] = b; zm[i] = fmaxf(fabsf(a), fabsf(b));
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) w[j] = sW[kk][tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    bool pos = w[j] > 0.0;
+                    lo[i][j] = fma(w[j], pos ? zlv[i] : zuv[i], lo[i][j]);
+                    hi[i][j] = fma(w[j], pos ? zuv[i] : zlv[i], hi[i][j]);
+                    qq[i][j] = fma(fabs(w[j]), zm[i], qq[i][j]);
+                }
+        }
+        __syncthreads();
+    }
+    const double gam = (double)(n_in + 2) * 1.1102230246251565e-16 * 1.000001;  // gamma_{n+2}, 2^-53
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        int d = d0 + ty * 4 + i;
+        if (d >= Deff) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            int o = o0 + tx * 4 + j;
+            if (o >= n_out) continue;
+            double bv = bias ? (double)bias[o] : 0.0;
+            double slack = gam * (qq[i][j] + fabs(bv));
+            double l = lo[i][j] + bv - slack, h = hi[i][j] + bv + slack;
+            // fma accumulations are not exact products + exact sums: charge one more ulp each way.
+            float lf = __double2float_rd(l), hf = __double2float_ru(h);
+            float qf = __double2float_ru(qq[i][j] * (1.0 + gam));
+            if (isnan(lf) || isnan(hf)) { lf = -INFINITY; hf = INFINITY; }
+            raw_lo[(long)d * out_ds + o] = lf;
+            raw_hi[(long)d * out_ds + o] = hf;
+            q[(long)d * out_ds + o] = qf;
+        }
+    }
+}
+
+// ---------------------------------------------------------------- per-domain finish of a Linear output
+// mode 0: bounds = inherited (clamp only: beta_crown/engine/domain/child.rs:51-118);
+// mode 1: bounds = re-propagated intersected with inherited (graph/propagation/constraints/mod.rs:738-741);
+// mode 2: bounds = re-propagated (plain IBP).
+// Then the split clamps (constraints/lookups.rs:160-175), the beta-CROWN relaxation
+// (beta_crown/engine/backward/relu_backward.rs:63-101) and the post-activation interval (:428-548).
+__global__ void k_ibp_finish(NetView nv, int k, int D, int mode, int last, const float *__restrict__ raw_lo,
+                             const float *__restrict__ raw_hi, long raw_ds, const float *__restrict__ inh_lo,
+                             const float *__restrict__ inh_hi, const signed char *__restrict__ code,
+                             const float *__restrict__ sbeta, const float *__restrict__ alpha,
+                             float *__restrict__ pre_lo, float *__restrict__ pre_hi, float *__restrict__ zl,
+                             float *__restrict__ zu, float4 *__restrict__ tab, float *__restrict__ zabs,
+                             int *__restrict__ flags) {
+    int n = nv.dims[k + 1], off = nv.pre_off[k];
+    long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= (long)D * n) return;
+    int d = (int)(t / n), j = (int)(t % n);
+    long o = (long)d * nv.n_pre + off + j;
+    float l = raw_lo[(long)d * raw_ds + off + j], u = raw_hi[(long)d * raw_ds + off + j];
+    if (mode == 0 && inh_lo) { l = inh_lo[off + j]; u = inh_hi[off + j]; }
+    else if (mode == 1 && inh_lo) {
+        float il = inh_lo[off + j], iu = inh_hi[off + j];
+        if (!(isnan(l) || isnan(u) || isnan(il) || isnan(iu))) {
+            float tl = fmaxf(l, il), tu = fminf(u, iu);
+            if (tl <= tu) { l = tl; u = tu; } else { l = fminf(l, il); u = fmaxf(u, iu); }
+        }
+    }
+    if (last) { pre_lo[o] = l; pre_hi[o] = u; return; }
+    int s = code[o];
+    if (s > 0) l = (isnan(l)) ? l : fmaxf(l, 0.f);
+    else if (s < 0) u = (isnan(u)) ? u : fminf(u, 0.f);
+    if (s != 0 && l > u) atomicOr(&flags[d], kFlagInfeasible);
+    pre_lo[o] = l; pre_hi[o] = u;
+    float ls, us, ui;
+    if (s > 0) { ls = 1.f; us = 1.f; ui = 0.f; }
+    else if (s < 0) { ls = 0.f; us = 0.f; ui = 0.f; }
+    else if (isnan(l) || isnan(u) || isinf(l) || isinf(u)) {
+        // The reference has closed forms for these arms (relu_backward.rs:75-93); a domain that reaches
+        // them is returned as [-inf, +inf] here, which every one of those arms also implies or encloses.
+        atomicOr(&flags[d], kFlagDegraded);
+        ls = 0.f; us = 0.f; ui = 0.f;
+    } else if (l >= 0.f) { ls = 1.f; us = 1.f; ui = 0.f; }
+    else if (u <= 0.f) { ls = 0.f; us = 0.f; ui = 0.f; }
+    else {
+        float w = fmaxf(u - l, 1e-8f);  // RELU_RELAX_MIN_WIDTH, relu/mod.rs:24
+        us = __fdiv_rn(u, w);
+        // The reference uses ui = -l*u/w in round-to-nearest.  The chord is only a valid upper line if
+        // us*l + ui >= 0 and us*u + ui >= u, so the intercept is taken as the smallest fp32 that
+        // provably satisfies both; it differs from the reference value by at most a few ulps.
+        float i1 = __fmul_ru(us, -l);
+        float i2 = __fsub_ru(u, __fmul_rd(us, u));
+        ui = fmaxf(fmaxf(i1, i2), 0.f);
+        if (alpha) { float a = alpha[o]; ls = isnan(a) ? 0.f : fminf(fmaxf(a, 0.f), 1.f); }
+        else ls = (u > -l) ? 1.f : 0.f;  // beta_crown/state/alpha/domain.rs:161
+    }
+    tab[o] = make_float4(ls, us, ui, sbeta[o]);
+    zabs[o] = fmaxf(fabsf(l), fabsf(u));
+    float pl = fmaxf(l, 0.f), pu = fmaxf(u, 0.f);
+    if (s > 0) { pu = u; }
+    else if (s < 0) { pl = 0.f; pu = 0.f; }
+    if (isnan(l)) pl = l;
+    if (isnan(u)) pu = u;
+    zl[o] = pl; zu[o] = pu;
+}
+
+// ---------------------------------------------------------------- seed
+__global__ void k_seed(const float *__restrict__ spec, int S, int nL, int D, int lda, float *__restrict__ A) {
+    long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    long total = (long)D * 2 * S * nL;
+    if (t >= total) return;
+    int j = (int)(t % nL);
+    long m = t / nL;
+    int rr = (int)(m % (2 * S));
+    A[m * lda + j] = spec[(long)(rr % S) * nL + j];
+}
+
+// ---------------------------------------------------------------- ReLU relaxation pass
+// One warp per row of A.  With r >= 0 the row is composed with ReLU r's relaxation
+// (relu_backward.rs:105-175): lower rows take a*ls (a>0) or a*us and a*ui into the bias (a<0), stepped
+// one ulp down; upper rows mirror it, stepped up; then the signed beta is subtracted / added.
+// With r < 0 the coefficients are left as they are (seed pass).  In both cases the row then pays for
+// the contraction that follows: bias += a'.bias_k, rpen += eps * |a'| . q_k.
+__global__ void __launch_bounds__(256)
+k_relax(int n, int off, int M, int R, int S, int n_pre, int identity, float *__restrict__ A, int lda,
+        const float4 *__restrict__ tab, const float *__restrict__ zabs, const float *__restrict__ q, long q_ds,
+        const float *__restrict__ bias_k, double eps, double *__restrict__ rb, double *__restrict__ rabs,
+        double *__restrict__ rpen) {
+    int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= M) return;
+    int m = warp, d = m / R;
+    bool upper = (m % R) >= S;
+    float *row = A + (long)m * lda;
+    double sb = 0.0, sa = 0.0, sp = 0.0;
+    for (int j = lane; j < n; j += 32) {
+        float a = row[j];
+        float nw = a;
+        if (!identity) {
+            float4 t = tab[(long)d * n_pre + off + j];
+            float za = zabs[(long)d * n_pre + off + j];
+            float slope = 0.f, icp = 0.f;
+            if (a > 0.f) { slope = upper ? t.y : t.x; icp = upper ? t.z : 0.f; }
+            else if (a < 0.f) { slope = upper ? t.x : t.y; icp = upper ? 0.f : t.z; }
+            if (a == 0.f || slope == 0.f) nw = 0.f;  // exact product: no outward step needed
+            else {
+                float p = a * slope;
+                nw = upper ? next_up_f(p) : next_down_f(p);
+                double gap = fabs((double)a * (double)slope - (double)nw);
+                sp += gap * (double)za;
+            }
+            if (icp != 0.f) { double c = (double)a * (double)icp; sb += c; sa += fabs(c); }
+            if (t.w != 0.f) nw = upper ? nw + t.w : nw - t.w;
+            row[j] = nw;
+        }
+        if (bias_k) { double c = (double)nw * (double)bias_k[j]; sb += c; sa += fabs(c); }
+        sp += eps * fabs((double)nw) * (double)q[(long)d * q_ds + off + j];
+    }
+    sb = warp_sum(sb); sa = warp_sum(sa); sp = warp_sum(sp);
+    if (lane == 0) { rb[m] += sb; rabs[m] += sa; rpen[m] += sp; }
+}
+
+// ---------------------------------------------------------------- binary64-accumulated contraction
+// C[M x N] = A[M x K] * B[K x N]; the fp32 products are exact in binary64, the running sums round to
+// nearest (bounded by eps*|A||B|, charged in k_relax), and the final cast to fp32 is measured exactly
+// and charged against the interval of the variable the coefficient multiplies.
+constexpr int GM = 64, GN = 64, GK = 16;
+__global__ void __launch_bounds__(256)
+k_gemm_f64(int M, int N, int K, const float *__restrict__ A, int lda, const float *__restrict__ B, int ldb,
+           float *__restrict__ C, int ldc, int R, const float *__restrict__ zin_lo, const float *__restrict__ zin_hi,
+           long zin_ds, double *__restrict__ rpen) {
+    __shared__ float sA[GK][GM + 1], sB[GK][GN + 1];
+    int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    int m0 = blockIdx.y * GM, n0 = blockIdx.x * GN;
+    double acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.0;
+    for (int k0 = 0; k0 < K; k0 += GK) {
+        for (int t = threadIdx.x; t < GM * GK; t += 256) {
+            int r = t / GK, kk = t % GK;
+            int m = m0 + r, k = k0 + kk;
+            sA[kk][r] = (m < M && k < K) ? A[(long)m * lda + k] : 0.f;
+        }
+        for (int t = threadIdx.x; t < GK * GN; t += 256) {
+            int kk = t / GN, c = t % GN;
+            int k = k0 + kk, n = n0 + c;
+            sB[kk][c] = (k < K && n < N) ? B[(long)k * ldb + n] : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < GK; ++kk) {
+            double a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = sA[kk][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) b[j] = sB[kk][tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fma(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        int m = m0 + ty * 4 + i;
+        double pen = 0.0;
+        if (m < M) {
+            int d = m / R;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                int n = n0 + tx * 4 + j;
+                if (n >= N) continue;
+                float c = (float)acc[i][j];
+                C[(long)m * ldc + n] = c;
+                if (rpen) {
+                    double err = fabs(acc[i][j] - (double)c);
+                    float zm = fmaxf(fabsf(zin_lo[(long)d * zin_ds + n]), fabsf(zin_hi[(long)d * zin_ds + n]));
+                    pen += err * (double)zm;
+                }
+            }
+        }
+        if (rpen) {
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) pen += __shfl_xor_sync(0xffffffffu, pen, o);
+            if (tx == 0 && m < M && pen != 0.0) atomicAdd(&rpen[m], pen);
+        }
+    }
+}
+
+// ---------------------------------------------------------------- concretisation
+// lb_s = b_s + sum_j A_sj * (A_sj >= 0 ? x_l : x_u) - penalty (bounds/concretize.rs:374-489), one warp
+// per row, exact products accumulated in binary64, directed cast.
+__global__ void __launch_bounds__(256)
+k_concretize(int M, int R, int S, int n0, const float *__restrict__ A, int lda, const float *__restrict__ in_lo,
+             const float *__restrict__ in_hi, long box_ds, const double *__restrict__ rb,
+             const double *__restrict__ rabs, const double *__restrict__ rpen, float *__restrict__ out_lo,
+             float *__restrict__ out_hi) {
+    int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= M) return;
+    int m = warp, d = m / R, rr = m % R;
+    bool upper = rr >= S;
+    const float *row = A + (long)m * lda;
+    const float *xl = in_lo + (long)d * box_ds, *xu = in_hi + (long)d * box_ds;
+    double s = 0.0, sa = 0.0;
+    bool bad = false;
+    for (int j = lane; j < n0; j += 32) {
+        float a = row[j];
+        bool nonneg = !(__float_as_uint(a) >> 31) || (__float_as_uint(a) & 0x7fffffffu) == 0;
+        float x = (nonneg != upper) ? xl[j] : xu[j];
+        if (!(fabsf(a) < 1e10f)) bad = true;  // is_crown_coeff_safe, crates/ny-core/src/gemm.rs:127
+        if (a != 0.f && x != 0.f) { double c = (double)a * (double)x; s += c; sa += fabs(c); }
+    }
+    s = warp_sum(s); sa = warp_sum(sa);
+    bad = __any_sync(0xffffffffu, bad);
+    if (lane == 0) {
+        double tot_abs = sa + rabs[m] + fabs(rb[m]);
+        double slack = tot_abs * 9.094947017729282e-13;  // 2^-40 >> (number of binary64 additions) * 2^-53
+        float v;
+        if (!upper) {
+            double x = rb[m] + s - rpen[m] - slack;
+            v = (bad || isnan(x)) ? -INFINITY : __double2float_rd(x);
+            out_lo[(long)d * S + rr] = v;
+        } else {
+            double x = rb[m] + s + rpen[m] + slack;
+            v = (bad || isnan(x)) ? INFINITY : __double2float_ru(x);
+            out_hi[(long)d * S + (rr - S)] = v;
+        }
+    }
+}
+
+__device__ __forceinline__ void atomic_min_float(float *addr, float v) {
+    if (v >= 0.f) atomicMin((int *)addr, __float_as_int(v));
+    else atomicMax((unsigned *)addr, __float_as_uint(v));
+}
+
+// Per (domain, spec row): apply the domain flags and the reference's repair rule
+// (non-finite endpoint or inversion -> [-inf, +inf], concretize.rs:481-488); fold the global minimum.
+__global__ void k_finalize(int D, int S, const int *__restrict__ flags, float *__restrict__ out_lo,
+                           float *__restrict__ out_hi, float *__restrict__ min_lower) {
+    int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= D * S) return;
+    int d = t / S;
+    int f = flags[d];
+    float l = out_lo[t], u = out_hi[t];
+    if (f & kFlagInfeasible) { l = INFINITY; u = -INFINITY; }
+    else if ((f & (kFlagDegraded | kFlagInvalid)) || !isfinite(l) || !isfinite(u) || l > u) { l = -INFINITY; u = INFINITY; }
+    out_lo[t] = l; out_hi[t] = u;
+    if (!(f & kFlagInfeasible)) atomic_min_float(min_lower, l);
+}
+
+// ---------------------------------------------------------------- branching
+// select_largest_width_neuron (beta_crown/engine/branching/sequential.rs:49-104): widest unstable,
+// unsplit neuron; strict '>' so the first maximum in (relu, neuron) order wins; NaN widths skipped.
+__global__ void __launch_bounds__(256)
+k_select_branch(NetView nv, int D, const float *__restrict__ pre_lo, const float *__restrict__ pre_hi,
+                const signed char *__restrict__ code, int *__restrict__ relu, int *__restrict__ neuron,
+                float *__restrict__ width) {
+    int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= D) return;
+    int d = warp;
+    int n_hidden = nv.pre_off[nv.L - 1];
+    float best = -1.f;
+    int bidx = 0x7fffffff;
+    for (int i = lane; i < n_hidden; i += 32) {
+        long o = (long)d * nv.n_pre + i;
+        float l = pre_lo[o], u = pre_hi[o];
+        if (l >= 0.f || u <= 0.f || code[o] != 0) continue;
+        float w = u - l;
+        if (isnan(w)) continue;
+        if (w > best) { best = w; bidx = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        int oi = __shfl_xor_sync(0xffffffffu, bidx, o);
+        if (ob > best || (ob == best && oi < bidx)) { best = ob; bidx = oi; }
+    }
+    if (lane == 0) {
+        if (bidx == 0x7fffffff) { relu[d] = -1; neuron[d] = -1; width[d] = 0.f; }
+        else {
+            int r = 0;
+            while (r + 1 < nv.L - 1 && bidx >= nv.pre_off[r + 1]) ++r;
+            relu[d] = r; neuron[d] = bidx - nv.pre_off[r]; width[d] = best;
+        }
+    }
+}
+
+__global__ void k_fill_f64(double *p, size_t n, double v) {
+    size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t < n) p[t] = v;
+}
+
+// ---------------------------------------------------------------- launchers
+#define NYB_COUNT(e) ((e)->launches++)
+
+void launch_scatter_splits(nyb200_engine *e, const NetView &nv, const nyb200_split *sp, const int *ns, int max_splits,
+                           int D, signed char *code, float *sbeta, int *flags) {
+    long total = (long)D * max_splits;
+    if (total == 0) return;
+    k_scatter_splits<<<(unsigned)((total + 255) / 256), 256, 0, e->stream>>>(nv, sp, ns, max_splits, D, code, sbeta, flags);
+    NYB_COUNT(e);
+}
+
+void launch_ibp_linear(nyb200_engine *e, const NetView &nv, int k, int Deff, const float *zl, const float *zu,
+                       long in_dstride, float *raw_lo, float *raw_hi, float *q, long out_dstride) {
+    int n_in = nv.dims[k], n_out = nv.dims[k + 1];
+    dim3 grid((n_out + IB_N - 1) / IB_N, (Deff + IB_M - 1) / IB_M);
+    k_ibp_linear<<<grid, 256, 0, e->stream>>>(Deff, n_in, n_out, nv.W[k], nv.b[k], zl, zu, in_dstride,
+                                               raw_lo + nv.pre_off[k], raw_hi + nv.pre_off[k], q + nv.pre_off[k],
+                                               out_dstride);
+    NYB_COUNT(e);
+}
+
+void launch_ibp_finish(nyb200_engine *e, const NetView &nv, int k, int D, int mode, const float *raw_lo,
+                       const float *raw_hi, long raw_dstride, const float *inh_lo, const float *inh_hi,
+                       const signed char *code, const float *sbeta, const float *alpha, float *pre_lo, float *pre_hi,
+                       float *zl, float *zu, float4 *tab, float *zabs, int *flags) {
+    long total = (long)D * nv.dims[k + 1];
+    int last = (k == nv.L - 1);
+    k_ibp_finish<<<(unsigned)((total + 255) / 256), 256, 0, e->stream>>>(nv, k, D, mode, last, raw_lo, raw_hi, raw_dstride,
+                                                                         inh_lo, inh_hi, code, sbeta, alpha, pre_lo,
+                                                                         pre_hi, zl, zu, tab, zabs, flags);
+    NYB_COUNT(e);
+}
+
+void launch_seed(nyb200_engine *e, const float *spec, int S, int nL, int D, int lda, float *A) {
+    long total = (long)D * 2 * S * nL;
+    k_seed<<<(unsigned)((total + 255) / 256), 256, 0, e->stream>>>(spec, S, nL, D, lda, A);
+    NYB_COUNT(e);
+}
+
+void launch_relax(nyb200_engine *e, const NetView &nv, int r, int lin_k, int M, int R, int S, float *A, int lda,
+                  const float4 *tab, const float *zabs, const float *q, long q_dstride, double eps_gemm, double *rb,
+                  double *rabs, double *rpen) {
+    int n = nv.dims[lin_k + 1], off = nv.pre_off[lin_k];
+    long threads = (long)M * 32;
+    k_relax<<<(unsigned)((threads + 255) / 256), 256, 0, e->stream>>>(n, off, M, R, S, nv.n_pre, r < 0 ? 1 : 0, A, lda, tab,
+                                                                      zabs, q, q_dstride, nv.b[lin_k], eps_gemm, rb,
+                                                                      rabs, rpen);
+    NYB_COUNT(e);
+}
+
+void launch_gemm_f64(nyb200_engine *e, int M, int N, int K, const float *A, int lda, const float *B, int ldb, float *C,
+                     int ldc, int R, const float *zin_lo, const float *zin_hi, long zin_dstride, double *rpen) {
+    dim3 grid((N + GN - 1) / GN, (M + GM - 1) / GM);
+    k_gemm_f64<<<grid, 256, 0, e->stream>>>(M, N, K, A, lda, B, ldb, C, ldc, R, zin_lo, zin_hi, zin_dstride, rpen);
+    NYB_COUNT(e);
+}
+
+void launch_concretize(nyb200_engine *e, int M, int R, int S, int n0, const float *A, int lda, const float *in_lo,
+                       const float *in_hi, long box_dstride, const double *rb, const double *rabs, const double *rpen,
+                       const int *flags, float *out_lo, float *out_hi, float *min_lower) {
+    long threads = (long)M * 32;
+    k_concretize<<<(unsigned)((threads + 255) / 256), 256, 0, e->stream>>>(M, R, S, n0, A, lda, in_lo, in_hi, box_dstride,
+                                                                           rb, rabs, rpen, out_lo, out_hi);
+    NYB_COUNT(e);
+    int D = M / R;
+    k_finalize<<<(D * S + 255) / 256, 256, 0, e->stream>>>(D, S, flags, out_lo, out_hi, min_lower);
+    NYB_COUNT(e);
+}
+
+void launch_select_branch(nyb200_engine *e, const NetView &nv, int D, const float *pre_lo, const float *pre_hi,
+                          const signed char *code, int *relu, int *neuron, float *width) {
+    long threads = (long)D * 32;
+    k_select_branch<<<(unsigned)((threads + 255) / 256), 256, 0, e->stream>>>(nv, D, pre_lo, pre_hi, code, relu, neuron,
+                                                                              width);
+    NYB_COUNT(e);
+}
+
+void launch_fill_f64(nyb200_engine *e, double *p, size_t n, double v) {
+    k_fill_f64<<<(unsigned)((n + 255) / 256), 256, 0, e->stream>>>(p, n, v);
+    NYB_COUNT(e);
+}
+
+}  // namespace nyb

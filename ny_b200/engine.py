@@ -1,0 +1,290 @@
+"""Python host mirror of ny's engine plugin interface over the nyb200 C ABI.
+
+Method names and argument meaning follow the reference traits so that parity tests read like
+the reference's own (paths inside the ny project):
+  GemmEngine::gemm_f32                      crates/ny-core/src/gemm.rs:325
+  GpuIbpForward::ibp_forward_gpu_sound      crates/ny-core/src/gemm_gpu_ibp.rs:78-135
+  GpuCrownBackward::*_beta_batched          crates/ny-core/src/gemm.rs:3944
+  BetaCrownVerifier (batched BaB round)     crates/ny-propagate/src/beta_crown/engine/graph/gpu_bab/batched_gpu.rs:89
+Errors map NyError variants (crates/ny-core/src/error.rs:18) onto EngineError.code.
+
+There is no CPU fallback: constructing an engine without the compiled library or without a
+CUDA device raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "libnyb200.so")
+
+SPLIT_DTYPE = np.dtype([("relu", "<i4"), ("neuron", "<i4"), ("sign", "<i4"), ("beta", "<f4")])
+
+OK, UNSUPPORTED, SHAPE, INVALID, NUMERICAL, DEADLINE, OOM, INTERNAL = range(8)
+_NAMES = {
+    UNSUPPORTED: "UnsupportedOp", SHAPE: "ShapeMismatch", INVALID: "InvalidSpec", NUMERICAL: "NumericalInstability",
+    DEADLINE: "DeadlineExceeded", OOM: "MemoryExceeded", INTERNAL: "InternalError",
+}
+PATH_F64, PATH_TF32X3 = 0, 1
+
+EXPORTS = [
+    "nyb200_create", "nyb200_destroy", "nyb200_backend_provenance", "nyb200_last_error", "nyb200_set_stream",
+    "nyb200_set_path", "nyb200_launch_count", "nyb200_clear_working_set", "nyb200_gemm_f32", "nyb200_net_create",
+    "nyb200_net_destroy", "nyb200_ibp_forward", "nyb200_bab_bound_batch", "nyb200_batch_upload", "nyb200_batch_run",
+    "nyb200_batch_download", "nyb200_batch_min_lower", "nyb200_batch_min_lower_device",
+    "nyb200_batch_download_pre_bounds", "nyb200_batch_select_branch", "nyb200_timing_reset", "nyb200_timing_read",
+]
+
+
+class EngineError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"{_NAMES.get(code, code)}: {message}")
+        self.code = code
+
+
+_lib = None
+
+
+def load_library():
+    """Load libnyb200.so; raises if it has not been built (python -m ny_b200.build)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(_LIB_PATH):
+        raise EngineError(UNSUPPORTED, f"{_LIB_PATH} is missing: build it with `python -m ny_b200.build`")
+    L = C.CDLL(_LIB_PATH)
+    fp, ip, vp = C.POINTER(C.c_float), C.POINTER(C.c_int32), C.c_void_p
+    L.nyb200_create.argtypes = [C.c_int32, C.POINTER(vp)]
+    L.nyb200_destroy.argtypes = [vp]
+    L.nyb200_destroy.restype = None
+    L.nyb200_backend_provenance.restype = C.c_char_p
+    L.nyb200_last_error.argtypes = [vp]
+    L.nyb200_last_error.restype = C.c_char_p
+    L.nyb200_set_stream.argtypes = [vp, vp]
+    L.nyb200_set_path.argtypes = [vp, C.c_int32]
+    L.nyb200_launch_count.argtypes = [vp]
+    L.nyb200_launch_count.restype = C.c_int64
+    L.nyb200_clear_working_set.argtypes = [vp]
+    L.nyb200_gemm_f32.argtypes = [vp, C.c_int32, C.c_int32, C.c_int32, fp, fp, fp]
+    L.nyb200_net_create.argtypes = [vp, C.c_int32, ip, fp, fp, ip, ip]
+    L.nyb200_net_destroy.argtypes = [vp, C.c_int32]
+    L.nyb200_ibp_forward.argtypes = [vp, C.c_int32, C.c_int32, fp, fp, C.c_int32, fp, fp]
+    batch_args = [vp, C.c_int32, fp, C.c_int32, fp, fp, C.c_int32, fp, fp, vp, ip, C.c_int32, C.c_int32, C.c_int32, fp]
+    L.nyb200_bab_bound_batch.argtypes = batch_args + [fp, fp, ip]
+    L.nyb200_batch_upload.argtypes = batch_args
+    L.nyb200_batch_run.argtypes = [vp]
+    L.nyb200_batch_download.argtypes = [vp, fp, fp, ip]
+    L.nyb200_batch_min_lower.argtypes = [vp, fp]
+    L.nyb200_batch_min_lower_device.argtypes = [vp, C.POINTER(vp)]
+    L.nyb200_batch_download_pre_bounds.argtypes = [vp, fp, fp]
+    L.nyb200_batch_select_branch.argtypes = [vp, ip, ip, fp]
+    L.nyb200_timing_reset.argtypes = [vp]
+    L.nyb200_timing_read.argtypes = [vp, C.c_char_p, C.POINTER(C.c_double), ip]
+    _lib = L
+    return L
+
+
+def _fp(a):
+    return None if a is None else a.ctypes.data_as(C.POINTER(C.c_float))
+
+
+def _ip(a):
+    return None if a is None else a.ctypes.data_as(C.POINTER(C.c_int32))
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+class Network:
+    """Sequential ReLU MLP description (host side): weights[k] is [out, in] row-major."""
+
+    def __init__(self, weights, biases=None):
+        self.weights = [_f32(w) for w in weights]
+        L = len(self.weights)
+        biases = biases if biases is not None else [None] * L
+        self.biases = [None if b is None else _f32(b) for b in biases]
+        self.dims = np.array([self.weights[0].shape[1]] + [w.shape[0] for w in self.weights], dtype=np.int32)
+        for k, w in enumerate(self.weights):
+            if w.shape != (self.dims[k + 1], self.dims[k]):
+                raise EngineError(SHAPE, f"layer {k}: weight shape {w.shape}")
+
+    @property
+    def n_pre(self) -> int:
+        return int(self.dims[1:].sum())
+
+
+class B200Engine:
+    """One engine per GPU (and per thread of control); mirrors `Arc<dyn GemmEngine>`."""
+
+    def __init__(self, device: int = 0, stream: int | None = None):
+        self._L = load_library()
+        h = C.c_void_p()
+        st = self._L.nyb200_create(device, C.byref(h))
+        if st != OK:
+            raise EngineError(st, "no usable sm_100 CUDA device for nyb200_create (there is no CPU fallback)")
+        self._h = h
+        self._nets = {}
+        if stream is not None:
+            self.set_stream(stream)
+
+    def close(self):
+        if getattr(self, "_h", None):
+            self._L.nyb200_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, st: int):
+        if st != OK:
+            raise EngineError(st, self._L.nyb200_last_error(self._h).decode())
+
+    # -- configuration ---------------------------------------------------------------------
+    def backend_provenance(self) -> str:
+        return self._L.nyb200_backend_provenance().decode()
+
+    def set_stream(self, cuda_stream: int):
+        self._check(self._L.nyb200_set_stream(self._h, C.c_void_p(cuda_stream)))
+
+    def set_path(self, path: int):
+        self._check(self._L.nyb200_set_path(self._h, path))
+
+    def launch_count(self) -> int:
+        return int(self._L.nyb200_launch_count(self._h))
+
+    def clear_crown_working_set(self):
+        self._check(self._L.nyb200_clear_working_set(self._h))
+
+    # -- GemmEngine ------------------------------------------------------------------------
+    def gemm_f32(self, m: int, k: int, n: int, a, b) -> np.ndarray:
+        a, b = _f32(a).reshape(-1), _f32(b).reshape(-1)
+        if a.size != m * k or b.size != k * n:
+            raise EngineError(SHAPE, f"gemm_f32: expected {m * k} and {k * n} elements, got {a.size} and {b.size}")
+        c = np.empty(m * n, np.float32)
+        self._check(self._L.nyb200_gemm_f32(self._h, m, k, n, _fp(a), _fp(b), _fp(c)))
+        return c.reshape(m, n)
+
+    # -- network residency -----------------------------------------------------------------
+    def register_network(self, net: Network) -> int:
+        w = np.concatenate([x.ravel() for x in net.weights]).astype(np.float32)
+        bl = [b for b in net.biases if b is not None]
+        b = np.concatenate(bl).astype(np.float32) if bl else np.zeros(1, np.float32)
+        hb = np.array([0 if x is None else 1 for x in net.biases], np.int32)
+        nid = C.c_int32(0)
+        self._check(self._L.nyb200_net_create(self._h, len(net.weights), _ip(net.dims), _fp(w), _fp(b), _ip(hb),
+                                              C.byref(nid)))
+        self._nets[nid.value] = net
+        return nid.value
+
+    def release_network(self, net_id: int):
+        self._check(self._L.nyb200_net_destroy(self._h, net_id))
+        self._nets.pop(net_id, None)
+
+    # -- GpuIbpForward ---------------------------------------------------------------------
+    def ibp_forward_gpu(self, net_id: int, in_lo, in_hi):
+        """in_lo/in_hi: [n0] (one box) or [D, n0].  Returns pre-activation bounds [D, n_pre] x2."""
+        net = self._nets[net_id]
+        lo, hi = _f32(in_lo), _f32(in_hi)
+        if lo.ndim == 1:
+            lo, hi = lo[None, :], hi[None, :]
+        D = lo.shape[0]
+        if lo.shape != hi.shape or lo.shape[1] != net.dims[0]:
+            raise EngineError(SHAPE, f"ibp_forward_gpu: box shape {lo.shape}")
+        pl = np.empty((D, net.n_pre), np.float32)
+        pu = np.empty((D, net.n_pre), np.float32)
+        self._check(self._L.nyb200_ibp_forward(self._h, net_id, D, _fp(lo), _fp(hi), int(net.dims[0]), _fp(pl), _fp(pu)))
+        return pl, pu
+
+    # -- batched beta-CROWN ----------------------------------------------------------------
+    def _batch_args(self, net_id, spec, in_lo, in_hi, inh_lo, inh_hi, splits, n_splits, mode, alpha):
+        net = self._nets[net_id]
+        spec = _f32(spec)
+        if spec.ndim != 2 or spec.shape[1] != net.dims[-1]:
+            raise EngineError(SHAPE, f"spec shape {spec.shape}, expected [S, {net.dims[-1]}]")
+        lo, hi = _f32(in_lo), _f32(in_hi)
+        splits = np.ascontiguousarray(splits, SPLIT_DTYPE)
+        if splits.ndim != 2:
+            raise EngineError(SHAPE, "splits must be [D, max_splits]")
+        D, M = splits.shape
+        n_splits = np.ascontiguousarray(n_splits, np.int32)
+        if n_splits.shape != (D,):
+            raise EngineError(SHAPE, "n_splits must be [D]")
+        if lo.ndim == 1:
+            stride = 0
+            if lo.shape[0] != net.dims[0]:
+                raise EngineError(SHAPE, "input box width")
+        else:
+            stride = int(net.dims[0])
+            if lo.shape != (D, net.dims[0]):
+                raise EngineError(SHAPE, "per-domain input box shape")
+        inh_lo, inh_hi = _f32(inh_lo), _f32(inh_hi)
+        if inh_lo.shape != (net.n_pre,) or inh_hi.shape != (net.n_pre,):
+            raise EngineError(SHAPE, "inherited bounds must be [n_pre]")
+        if alpha is not None:
+            alpha = _f32(alpha)
+            if alpha.shape != (D, net.n_pre):
+                raise EngineError(SHAPE, "alpha must be [D, n_pre]")
+        keep = (spec, lo, hi, inh_lo, inh_hi, splits, n_splits, alpha)
+        args = [self._h, net_id, _fp(spec), spec.shape[0], _fp(lo), _fp(hi), stride, _fp(inh_lo), _fp(inh_hi),
+                C.c_void_p(splits.ctypes.data), _ip(n_splits), M, D, mode, _fp(alpha)]
+        return args, keep, D, spec.shape[0]
+
+    def bab_bound_batch(self, net_id, spec, in_lo, in_hi, inh_lo, inh_hi, splits, n_splits, mode=1, alpha=None):
+        """Host buffers in, host buffers out: (lower [D,S], upper [D,S], infeasible [D])."""
+        args, keep, D, S = self._batch_args(net_id, spec, in_lo, in_hi, inh_lo, inh_hi, splits, n_splits, mode, alpha)
+        ol, ou = np.empty((D, S), np.float32), np.empty((D, S), np.float32)
+        inf = np.zeros(D, np.int32)
+        self._check(self._L.nyb200_bab_bound_batch(*args, _fp(ol), _fp(ou), _ip(inf)))
+        return ol, ou, inf
+
+    def batch_upload(self, net_id, spec, in_lo, in_hi, inh_lo, inh_hi, splits, n_splits, mode=1, alpha=None):
+        args, keep, D, S = self._batch_args(net_id, spec, in_lo, in_hi, inh_lo, inh_hi, splits, n_splits, mode, alpha)
+        self._check(self._L.nyb200_batch_upload(*args))
+        self._batch_shape = (D, S, self._nets[net_id].n_pre)
+
+    def batch_run(self):
+        self._check(self._L.nyb200_batch_run(self._h))
+
+    def batch_download(self):
+        D, S, _ = self._batch_shape
+        ol, ou = np.empty((D, S), np.float32), np.empty((D, S), np.float32)
+        inf = np.zeros(D, np.int32)
+        self._check(self._L.nyb200_batch_download(self._h, _fp(ol), _fp(ou), _ip(inf)))
+        return ol, ou, inf
+
+    def batch_min_lower(self) -> float:
+        v = C.c_float(0)
+        self._check(self._L.nyb200_batch_min_lower(self._h, C.byref(v)))
+        return float(v.value)
+
+    def batch_min_lower_device(self) -> int:
+        p = C.c_void_p()
+        self._check(self._L.nyb200_batch_min_lower_device(self._h, C.byref(p)))
+        return int(p.value)
+
+    def batch_download_pre_bounds(self):
+        D, _, n_pre = self._batch_shape
+        pl, pu = np.empty((D, n_pre), np.float32), np.empty((D, n_pre), np.float32)
+        self._check(self._L.nyb200_batch_download_pre_bounds(self._h, _fp(pl), _fp(pu)))
+        return pl, pu
+
+    def batch_select_branch(self):
+        D = self._batch_shape[0]
+        r, j, w = np.empty(D, np.int32), np.empty(D, np.int32), np.empty(D, np.float32)
+        self._check(self._L.nyb200_batch_select_branch(self._h, _ip(r), _ip(j), _fp(w)))
+        return r, j, w
+
+    def timing_reset(self):
+        self._check(self._L.nyb200_timing_reset(self._h))
+
+    def timing_read(self, phase: str):
+        ms, n = C.c_double(0), C.c_int32(0)
+        self._check(self._L.nyb200_timing_read(self._h, phase.encode(), C.byref(ms), C.byref(n)))
+        return float(ms.value), int(n.value)

@@ -1,0 +1,142 @@
+"""Seeded synthetic workloads with the shapes of the benchmark configurations.
+
+They stand in for ACAS-Xu / MNIST / CIFAR style verification instances (no benchmark-suite item
+is used): random He-initialised networks, a random nominal input, an L-inf box, specification
+rows y_c - y_j, and BaB domains that fix seeded unstable neurons.  Everything is derived from
+numpy's PCG64 streams so the same arrays are produced on every machine.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+
+from .engine import SPLIT_DTYPE, Network
+
+
+def _rng(seed: int) -> np.random.Generator:
+    return np.random.Generator(np.random.PCG64(seed))
+
+
+def make_mlp(dims, seed: int) -> Network:
+    """Weights N(0, 2/fan_in), biases N(0, 0.01) (variances), fp32."""
+    g = _rng(seed)
+    ws, bs = [], []
+    for k in range(len(dims) - 1):
+        fan_in = dims[k]
+        ws.append((g.standard_normal((dims[k + 1], dims[k])) * np.sqrt(2.0 / fan_in)).astype(np.float32))
+        bs.append((g.standard_normal(dims[k + 1]) * 0.1).astype(np.float32))
+    return Network(ws, bs)
+
+
+def forward(net: Network, x) -> np.ndarray:
+    z = np.asarray(x, np.float64)
+    for k, w in enumerate(net.weights):
+        z = z @ w.astype(np.float64).T
+        if net.biases[k] is not None:
+            z = z + net.biases[k].astype(np.float64)
+        if k + 1 < len(net.weights):
+            z = np.maximum(z, 0.0)
+    return z
+
+
+def margin_spec(n_out: int, c: int) -> np.ndarray:
+    """Rows e_c - e_j for every j != c."""
+    rows = []
+    for j in range(n_out):
+        if j == c:
+            continue
+        r = np.zeros(n_out, np.float32)
+        r[c] = 1.0
+        r[j] = -1.0
+        rows.append(r)
+    return np.stack(rows)
+
+
+@dataclass
+class Workload:
+    name: str
+    net: Network
+    x0: np.ndarray
+    in_lo: np.ndarray
+    in_hi: np.ndarray
+    spec: np.ndarray
+    n_fix: int = 0
+    seed: int = 0
+    meta: dict = field(default_factory=dict)
+
+
+def config_mlp_small(seed: int = 1) -> Workload:
+    """MLP 5 -> 6x50 -> 5, box x0 +- 0.05 with x0 ~ U(-1,1)^5, 4 rows y0 - yj."""
+    net = make_mlp([5] + [50] * 6 + [5], seed)
+    g = _rng(seed + 1000)
+    x0 = g.uniform(-1, 1, 5).astype(np.float32)
+    return Workload("mlp_5_6x50_5", net, x0, x0 - np.float32(0.05), x0 + np.float32(0.05), margin_spec(5, 0), 0, seed)
+
+
+def config_mlp_bab(seed: int = 2, hidden: int = 256, depth: int = 8, n_in: int = 784, n_out: int = 10,
+                   eps: float = 0.02, n_fix: int = 8) -> Workload:
+    """MLP 784 -> 8x256 -> 10, box x0 +- 0.02 clipped to [0,1], 9 rows y_c - y_j (c = argmax f(x0))."""
+    net = make_mlp([n_in] + [hidden] * depth + [n_out], seed)
+    g = _rng(seed + 1000)
+    x0 = g.uniform(0, 1, n_in).astype(np.float32)
+    lo = np.clip(x0 - np.float32(eps), 0, 1).astype(np.float32)
+    hi = np.clip(x0 + np.float32(eps), 0, 1).astype(np.float32)
+    c = int(np.argmax(forward(net, x0)))
+    return Workload(f"mlp_{n_in}_{depth}x{hidden}_{n_out}", net, x0, lo, hi, margin_spec(n_out, c), n_fix, seed,
+                    {"eps": eps, "label": c})
+
+
+def draw_domains(wl: Workload, root_lo: np.ndarray, root_hi: np.ndarray, D: int, first: int = 0):
+    """D BaB domains: domain d fixes n_fix neurons drawn without replacement (stream seed+d) from the
+    root-unstable set, sign ~ Bernoulli(1/2), beta ~ U(0,1).  Returns (splits [D, n_fix], n_splits [D]).
+    `first` offsets the domain index so that ranks can draw disjoint shards of one global batch."""
+    net = wl.net
+    n_hidden = int(net.dims[1:-1].sum())
+    unstable = np.flatnonzero((root_lo[:n_hidden] < 0) & (root_hi[:n_hidden] > 0))
+    offs = np.concatenate([[0], np.cumsum(net.dims[1:-1])])
+    n_fix = min(wl.n_fix, len(unstable))
+    splits = np.zeros((D, max(n_fix, 1)), SPLIT_DTYPE)
+    n_splits = np.full(D, n_fix, np.int32)
+    for d in range(D):
+        g = _rng(wl.seed * 1_000_003 + first + d)
+        pick = g.choice(unstable, size=n_fix, replace=False) if n_fix else np.zeros(0, np.int64)
+        sign = np.where(g.random(n_fix) < 0.5, 1, -1)
+        beta = g.random(n_fix).astype(np.float32)
+        relu = np.searchsorted(offs, pick, side="right") - 1
+        splits["relu"][d, :n_fix] = relu
+        splits["neuron"][d, :n_fix] = pick - offs[relu]
+        splits["sign"][d, :n_fix] = sign
+        splits["beta"][d, :n_fix] = beta
+    return splits, n_splits
+
+
+def sample_min_margin(wl: Workload, n_samples: int, seed: int, splits=None, chunk: int = 8192) -> np.ndarray:
+    """Empirical minimum of the specification rows over seeded concrete points of the box that also
+    satisfy the domain's split constraints (points violating a split are discarded).  Used by the
+    soundness check: a valid lower bound must not exceed it."""
+    g = _rng(seed)
+    net = wl.net
+    S = wl.spec.shape[0]
+    best = np.full(S, np.inf)
+    offs = np.concatenate([[0], np.cumsum(net.dims[1:-1])])
+    done = 0
+    while done < n_samples:
+        n = min(chunk, n_samples - done)
+        done += n
+        x = wl.in_lo.astype(np.float64) + g.random((n, len(wl.in_lo))) * (wl.in_hi.astype(np.float64) - wl.in_lo)
+        z = x
+        ok = np.ones(n, bool)
+        for k, w in enumerate(net.weights):
+            z = z @ w.astype(np.float64).T + (0 if net.biases[k] is None else net.biases[k].astype(np.float64))
+            if k + 1 < len(net.weights):
+                if splits is not None:
+                    for s in splits:
+                        if s["relu"] == k:
+                            v = z[:, s["neuron"]]
+                            ok &= (v >= 0) if s["sign"] > 0 else (v <= 0)
+                z = np.maximum(z, 0.0)
+        m = z @ wl.spec.astype(np.float64).T
+        if ok.any():
+            best = np.minimum(best, m[ok].min(axis=0))
+    return best

@@ -1,0 +1,208 @@
+"""GPU parity tests: the CUDA path, called through the C ABI, against the CPU oracle on the same
+seeded inputs.  Tolerances: interval forward bounds within 4 ulp of the oracle; output bounds within
+1e-4 relative (the bar stated for this path), soundness against sampled concrete executions."""
+import numpy as np
+import pytest
+
+from ny_b200 import workloads as W
+
+pytestmark = pytest.mark.gpu
+
+REL_TOL = 1e-4
+
+
+@pytest.fixture(scope="module")
+def eng():
+    from ny_b200 import B200Engine
+
+    e = B200Engine(0)
+    yield e
+    e.close()
+
+
+def _rel(a, b):
+    a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
+    fin = np.isfinite(a) & np.isfinite(b)
+    same_inf = (~fin) & (a == b)
+    assert np.all(fin | same_inf), "non-finite mismatch"
+    if not fin.any():
+        return 0.0
+    return float(np.max(np.abs(a[fin] - b[fin]) / np.maximum(np.abs(b[fin]), 1e-6)))
+
+
+def _spec_net(wl):
+    from ny_b200 import Network
+
+    return Network(wl.net.weights + [wl.spec], wl.net.biases + [None])
+
+
+def _setup(eng, oracle, wl):
+    onet = oracle.Net(wl.net.weights, wl.net.biases)
+    ospec = onet.with_spec(wl.spec)
+    nid = eng.register_network(wl.net)
+    rl, ru = oracle.ibp_forward(onet, wl.in_lo, wl.in_hi)
+    return onet, ospec, nid, rl, ru
+
+
+def _oracle_batch(oracle, ospec, wl, rl, ru, splits, ns, mode):
+    # the oracle's network carries the spec as its last layer: extend the inherited bounds with that
+    # layer's (unused) block
+    S = wl.spec.shape[0]
+    rl2 = np.concatenate([rl, np.full(S, -np.inf, np.float32)])
+    ru2 = np.concatenate([ru, np.full(S, np.inf, np.float32)])
+    return oracle.bab_bound_batch(ospec, wl.in_lo, wl.in_hi, rl2, ru2, splits, ns, mode)
+
+
+@pytest.mark.parametrize("cfg", ["small", "mid"])
+def test_ibp_forward_matches_oracle(eng, oracle, cfg):
+    wl = W.config_mlp_small() if cfg == "small" else W.config_mlp_bab(seed=4, hidden=96, depth=4, n_in=200)
+    onet, _, nid, rl, ru = _setup(eng, oracle, wl)
+    pl, pu = eng.ibp_forward_gpu(nid, wl.in_lo, wl.in_hi)
+    ulp = np.spacing(np.maximum(np.abs(rl), np.abs(ru)).astype(np.float32))
+    assert np.all(np.abs(pl[0] - rl) <= 4 * ulp) and np.all(np.abs(pu[0] - ru) <= 4 * ulp)
+    # per-domain boxes: two different boxes in one call
+    lo2 = np.stack([wl.in_lo, wl.in_lo + 0.01 * (wl.in_hi - wl.in_lo)])
+    hi2 = np.stack([wl.in_hi, wl.in_hi])
+    pl2, pu2 = eng.ibp_forward_gpu(nid, lo2, hi2)
+    assert np.array_equal(pl2[0], pl[0]) and np.array_equal(pu2[0], pu[0])
+    r2l, r2u = oracle.ibp_forward(onet, lo2[1], hi2[1])
+    assert np.all(np.abs(pl2[1] - r2l) <= 4 * ulp) and np.all(np.abs(pu2[1] - r2u) <= 4 * ulp)
+    eng.release_network(nid)
+
+
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("cfg", ["small", "mid"])
+def test_bab_bound_batch_matches_oracle(eng, oracle, cfg, mode):
+    if cfg == "small":
+        wl = W.config_mlp_small()
+        wl.n_fix = 4
+        D = 96
+    else:
+        wl = W.config_mlp_bab(seed=6, hidden=64, depth=4, n_in=196, eps=0.01, n_fix=8)
+        D = 200
+    onet, ospec, nid, rl, ru = _setup(eng, oracle, wl)
+    splits, ns = W.draw_domains(wl, rl, ru, D)
+    ns = ns.copy()
+    ns[0] = 0          # an unsplit (root) domain
+    ns[1] = 1          # ragged split lists
+    ns[2] = max(int(ns[2]) - 1, 0)
+    glo, ghi, ginf = eng.bab_bound_batch(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, splits, ns, mode=mode)
+    olo, ohi, oinf, _ = _oracle_batch(oracle, ospec, wl, rl, ru, splits, ns, mode)
+    assert np.array_equal(ginf.astype(bool), oinf.astype(bool))
+    feas = ~oinf.astype(bool)
+    assert feas.sum() > D // 2
+    assert _rel(glo[feas], olo[feas]) <= REL_TOL
+    assert _rel(ghi[feas], ohi[feas]) <= REL_TOL
+    # verdicts (lower > 0) identical wherever the oracle is not within tolerance of the threshold
+    clear = np.abs(olo) > REL_TOL * np.maximum(1.0, np.abs(olo))
+    assert np.array_equal((glo > 0)[feas & clear.all(axis=1)], (olo > 0)[feas & clear.all(axis=1)])
+    eng.release_network(nid)
+
+
+def test_soundness_against_sampled_executions(eng, oracle):
+    wl = W.config_mlp_bab(seed=8, hidden=48, depth=3, n_in=64, eps=0.03, n_fix=4)
+    onet, ospec, nid, rl, ru = _setup(eng, oracle, wl)
+    splits, ns = W.draw_domains(wl, rl, ru, 16)
+    glo, ghi, ginf = eng.bab_bound_batch(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, splits, ns, mode=1)
+    for d in range(16):
+        if ginf[d]:
+            continue
+        mn = W.sample_min_margin(wl, 100000, 500 + d, splits[d][: ns[d]])
+        ok = np.isfinite(mn)
+        assert np.all(glo[d][ok] <= mn[ok]), d
+    eng.release_network(nid)
+
+
+def test_infeasible_and_empty_batches(eng, oracle):
+    wl = W.config_mlp_bab(seed=5, hidden=32, depth=2, n_in=16, eps=0.01, n_fix=2)
+    onet, ospec, nid, rl, ru = _setup(eng, oracle, wl)
+    from ny_b200 import SPLIT_DTYPE, EngineError
+
+    stable = np.flatnonzero(rl[:32] > 0)
+    assert len(stable) > 0
+    sp = np.zeros((2, 1), SPLIT_DTYPE)
+    sp[0, 0] = (0, int(stable[0]), -1, 0.25)   # inactive split on a provably active neuron: empty domain
+    sp[1, 0] = (0, int(stable[0]), 1, 0.25)    # consistent split
+    ns = np.array([1, 1], np.int32)
+    glo, ghi, ginf = eng.bab_bound_batch(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, sp, ns, mode=1)
+    olo, ohi, oinf, _ = _oracle_batch(oracle, ospec, wl, rl, ru, sp, ns, 1)
+    assert ginf.tolist() == [1, 0] and oinf.tolist() == [1, 0]
+    assert np.all(glo[0] == np.inf) and np.all(ghi[0] == -np.inf)
+    assert _rel(glo[1], olo[1]) <= REL_TOL
+    # max_splits = 0: plain CROWN-style bound of the root domain
+    sp0 = np.zeros((3, 0), SPLIT_DTYPE)
+    glo0, _, _ = eng.bab_bound_batch(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, sp0, np.zeros(3, np.int32), mode=1)
+    olo0, _, _, _ = _oracle_batch(oracle, ospec, wl, rl, ru, np.zeros((3, 1), SPLIT_DTYPE), np.zeros(3, np.int32), 1)
+    assert _rel(glo0, olo0) <= REL_TOL and np.array_equal(glo0[0], glo0[2])
+    # out-of-range split entries are refused, never silently used
+    bad = np.zeros((1, 1), SPLIT_DTYPE)
+    bad[0, 0] = (0, 9999, 1, 0.0)
+    with pytest.raises(EngineError) as ei:
+        eng.bab_bound_batch(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, bad, np.array([1], np.int32))
+    assert ei.value.code == 3
+    with pytest.raises(EngineError):
+        eng.bab_bound_batch(nid, wl.spec[:, :5], wl.in_lo, wl.in_hi, rl, ru, sp, ns)
+    eng.release_network(nid)
+
+
+def test_branching_matches_oracle_and_min_lower(eng, oracle):
+    wl = W.config_mlp_bab(seed=12, hidden=40, depth=3, n_in=30, eps=0.02, n_fix=3)
+    onet, ospec, nid, rl, ru = _setup(eng, oracle, wl)
+    splits, ns = W.draw_domains(wl, rl, ru, 40)
+    eng.batch_upload(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, splits, ns, mode=1)
+    eng.batch_run()
+    glo, ghi, ginf = eng.batch_download()
+    pl, pu = eng.batch_download_pre_bounds()
+    r, j, w = eng.batch_select_branch()
+    feas = ginf == 0
+    assert np.isclose(eng.batch_min_lower(), glo[feas].min())
+    for d in range(40):
+        if ginf[d]:
+            continue
+        got = oracle.select_largest_width(onet, pl[d], pu[d], splits[d][: ns[d]])
+        assert got is not None and (int(r[d]), int(j[d])) == got[:2] and w[d] == np.float32(got[2])
+        opl, opu, oinf = oracle.domain_bounds(onet, wl.in_lo, wl.in_hi, rl, ru, splits[d][: ns[d]], 1)
+        hid = int(wl.net.dims[1:-1].sum())
+        ulp = np.spacing(np.maximum(np.abs(opl[:hid]), np.abs(opu[:hid])).astype(np.float32))
+        assert np.all(np.abs(pl[d][:hid] - opl[:hid]) <= 8 * ulp)
+    eng.release_network(nid)
+
+
+def test_gemm_f32_entry_point(eng):
+    g = np.random.Generator(np.random.PCG64(3))
+    a = g.standard_normal((37, 129)).astype(np.float32)
+    b = g.standard_normal((129, 65)).astype(np.float32)
+    c = eng.gemm_f32(37, 129, 65, a, b)
+    ref = (a.astype(np.float64) @ b.astype(np.float64)).astype(np.float32)
+    assert np.array_equal(c, ref)  # binary64 accumulation, one rounding to fp32
+
+
+def test_full_size_batch_properties(eng, oracle):
+    """Configuration of the benchmark (784 -> 8x256 -> 10, 4096 domains, 8 splits each): checked through
+    size-independent properties, plus oracle parity on a 32-domain sample."""
+    wl = W.config_mlp_bab()
+    nid = eng.register_network(wl.net)
+    pl, pu = eng.ibp_forward_gpu(nid, wl.in_lo, wl.in_hi)
+    rl, ru = pl[0], pu[0]
+    D = 4096
+    splits, ns = W.draw_domains(wl, rl, ru, D)
+    lo, hi, inf = eng.bab_bound_batch(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, splits, ns, mode=1)
+    lo2, hi2, inf2 = eng.bab_bound_batch(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, splits, ns, mode=1)
+    assert np.array_equal(lo, lo2) and np.array_equal(hi, hi2)            # deterministic
+    perm = np.random.Generator(np.random.PCG64(1)).permutation(D)
+    lop, hip, infp = eng.bab_bound_batch(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, splits[perm], ns[perm], mode=1)
+    assert np.array_equal(lop, lo[perm]) and np.array_equal(infp, inf[perm])  # domains are independent
+    feas = inf == 0
+    assert np.all(lo[feas] <= hi[feas]) and np.all(np.isfinite(lo[feas]))
+    onet = oracle.Net(wl.net.weights, wl.net.biases)
+    ospec = onet.with_spec(wl.spec)
+    sel = np.arange(0, D, D // 32)
+    olo, ohi, oinf, _ = _oracle_batch(oracle, ospec, wl, rl, ru, splits[sel], ns[sel], 1)
+    assert np.array_equal(oinf.astype(bool), inf[sel].astype(bool))
+    f = ~oinf.astype(bool)
+    assert _rel(lo[sel][f], olo[f]) <= REL_TOL and _rel(hi[sel][f], ohi[f]) <= REL_TOL
+    d = int(np.flatnonzero(feas)[0])
+    mn = W.sample_min_margin(wl, 100000, 77, splits[d][: ns[d]])
+    ok = np.isfinite(mn)
+    assert np.all(lo[d][ok] <= mn[ok])
+    eng.release_network(nid)

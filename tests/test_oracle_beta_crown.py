@@ -1,0 +1,82 @@
+"""Properties of the oracle's beta-CROWN restatement on small seeded networks (CPU only): it must
+reduce to plain CROWN's backward when nothing is split, enclose concrete executions, and treat
+splits the way the reference's tests expect (beta_crown/engine/tests/*.rs)."""
+import numpy as np
+
+from ny_b200 import workloads as W
+
+
+def _small(seed=7, depth=3, hidden=24, n_in=12):
+    wl = W.config_mlp_bab(seed=seed, hidden=hidden, depth=depth, n_in=n_in, n_out=5, eps=0.05, n_fix=3)
+    return wl
+
+
+def _onet(oracle, wl):
+    return oracle.Net(wl.net.weights, wl.net.biases)
+
+
+def test_unsplit_domain_encloses_samples(oracle):
+    wl = _small()
+    net = _onet(oracle, wl).with_spec(wl.spec)
+    base = _onet(oracle, wl)
+    pl, pu = oracle.ibp_forward(base, wl.in_lo, wl.in_hi)
+    spl, spu = oracle.ibp_forward(net, wl.in_lo, wl.in_hi)
+    lo, hi = oracle.beta_crown_bound(net, wl.in_lo, wl.in_hi, spl, spu, oracle.make_splits([]))
+    mn = W.sample_min_margin(wl, 20000, 11)
+    assert np.all(lo <= mn + 1e-6) and np.all(np.isfinite(lo)) and np.all(lo <= hi)
+    assert np.allclose(pl, spl[: len(pl)])
+
+
+def test_split_domains_enclose_constrained_samples_and_modes_nest(oracle):
+    wl = _small(seed=9)
+    net = _onet(oracle, wl).with_spec(wl.spec)
+    rl, ru = oracle.ibp_forward(net, wl.in_lo, wl.in_hi)
+    splits, ns = W.draw_domains(wl, rl, ru, 12)
+    for mode in (0, 1):
+        lo, hi, inf, _ = oracle.bab_bound_batch(net, wl.in_lo, wl.in_hi, rl, ru, splits, ns, mode, 2)
+        for d in range(12):
+            if inf[d]:
+                continue
+            mn = W.sample_min_margin(wl, 4000, 100 + d, splits[d][: ns[d]])
+            ok = np.isfinite(mn)
+            assert np.all(lo[d][ok] <= mn[ok] + 1e-5), (mode, d)
+
+
+def test_beta_zero_inactive_split_zeroes_neuron(oracle):
+    # with beta = 0, an inactive split behaves as a stable-inactive neuron: slopes (0, 0)
+    wl = _small(seed=3)
+    net = _onet(oracle, wl).with_spec(wl.spec)
+    rl, ru = oracle.ibp_forward(net, wl.in_lo, wl.in_hi)
+    unstable = np.flatnonzero((rl[:24] < 0) & (ru[:24] > 0))
+    j = int(unstable[0])
+    sp = oracle.make_splits([(0, j, -1, 0.0)])
+    lo_s, _ = oracle.beta_crown_bound(net, wl.in_lo, wl.in_hi, rl, ru, sp)
+    rl2, ru2 = rl.copy(), ru.copy()
+    ru2[j] = 0.0  # the same relaxation arises from u <= 0
+    lo_c, _ = oracle.beta_crown_bound(net, wl.in_lo, wl.in_hi, rl2, ru2, oracle.make_splits([]))
+    assert np.array_equal(lo_s, lo_c)
+
+
+def test_infeasible_clamp_is_reported(oracle):
+    wl = _small(seed=5)
+    net = _onet(oracle, wl).with_spec(wl.spec)
+    rl, ru = oracle.ibp_forward(net, wl.in_lo, wl.in_hi)
+    stable_pos = np.flatnonzero(rl[:24] > 0)
+    if len(stable_pos) == 0:
+        rl = rl.copy()
+        rl[0] = 0.5
+        ru = np.maximum(ru, 1.0)
+        stable_pos = np.array([0])
+    sp = oracle.make_splits([(0, int(stable_pos[0]), -1, 0.3)])
+    _, _, inf = oracle.domain_bounds(net, wl.in_lo, wl.in_hi, rl, ru, sp, 0)
+    assert inf
+
+
+def test_largest_width_first_maximum_wins(oracle):
+    net = oracle.Net([np.eye(4, 3), np.eye(3, 4), np.eye(2, 3)])
+    pl = np.array([-1, -2, -2, 1, -1, -3, 5, 0, 0], np.float32)
+    pu = np.array([1, 2, 2, 2, 1, 1, 6, 0, 0], np.float32)
+    assert oracle.select_largest_width(net, pl, pu, oracle.make_splits([]))[:2] == (0, 1)
+    assert oracle.select_largest_width(net, pl, pu, oracle.make_splits([(0, 1, 1, 0.0)]))[:2] == (0, 2)
+    pl[4], pu[4] = np.nan, np.nan
+    assert oracle.select_largest_width(net, pl, pu, oracle.make_splits([(0, 1, 1, 0), (0, 2, -1, 0)]))[:2] == (1, 1)
