@@ -101,7 +101,8 @@ int32_t nyb200_ibp_forward(nyb200_engine *e, int32_t net_id, int32_t D, const fl
  *   splits        [D x max_splits], n_splits[d] valid entries per domain
  *   mode          0 clamp-only intermediate bounds (sequential engine, engine/domain/child.rs:51-118)
  *                 1 constrained forward re-propagation (graph engine, constraints/mod.rs:184-760)
- *   alpha         NULL (heuristic [u > -l]) or [D x sum_{k=1..L-1} dims[k]] lower slopes
+ *   alpha         NULL (heuristic [u > -l]) or lower slopes laid out like the pre-activation bounds,
+ *                 [D x sum_{k>=1} dims[k]] (the last layer's block is ignored)
  *   out_lo/out_hi [D x S]; an infeasible domain gets lower=+inf, upper=-inf and infeasible[d]=1
  */
 int32_t nyb200_bab_bound_batch(nyb200_engine *e, int32_t net_id, const float *spec, int32_t S, const float *in_lo,
@@ -138,7 +139,10 @@ int32_t nyb200_batch_select_branch(nyb200_engine *e, int32_t *relu, int32_t *neu
 
 /* Kernel-only timing of the last nyb200_batch_run calls: average milliseconds per run of the
  * named phase ("forward", "backward", "total") measured with CUDA events on the engine stream
- * since the last reset. */
+ * since the last reset.  With nyb200_timing_enable(e, 1) every launch of the A*W contraction kernel
+ * is additionally bracketed by its own event pair and reported as phase "gemm" (average milliseconds
+ * per run, summed over that run's launches; n_runs counts runs). */
+int32_t nyb200_timing_enable(nyb200_engine *e, int32_t per_kernel);
 int32_t nyb200_timing_reset(nyb200_engine *e);
 int32_t nyb200_timing_read(nyb200_engine *e, const char *phase, double *avg_ms, int32_t *n_runs);
 

@@ -78,6 +78,7 @@ void nyb200_destroy(nyb200_engine *e) {
     for (auto &kv : e->ws) if (kv.second.p) cudaFree(kv.second.p);
     for (auto &kv : e->nets) for (float *p : kv.second.owned) cudaFree(p);
     for (int i = 0; i < 3; ++i) if (e->timing.ev[i]) cudaEventDestroy(e->timing.ev[i]);
+    for (cudaEvent_t ev : e->timing.kev) cudaEventDestroy(ev);
     delete e;
 }
 
@@ -190,6 +191,28 @@ int32_t nyb200_gemm_f32(nyb200_engine *e, int32_t m, int32_t k, int32_t n, const
 // ------------------------------------------------------------------ batch plumbing
 namespace {
 
+// Adds the finished run's event intervals to the accumulators.
+void fold_timing(nyb::Timing &t) {
+    if (!t.pending) return;
+    if (cudaEventSynchronize(t.ev[2]) == cudaSuccess) {
+        float f = 0, bw = 0;
+        cudaEventElapsedTime(&f, t.ev[0], t.ev[1]);
+        cudaEventElapsedTime(&bw, t.ev[1], t.ev[2]);
+        t.fwd_ms += f; t.bwd_ms += bw; t.tot_ms += f + bw; t.runs++;
+        for (int i = 0; i + 1 < t.kev_used; i += 2) {
+            float g = 0;
+            if (cudaEventElapsedTime(&g, t.kev[i], t.kev[i + 1]) == cudaSuccess) t.gemm_ms += g;
+        }
+    }
+    t.kev_used = 0;
+    t.pending = false;
+}
+
+cudaEvent_t next_kev(nyb::Timing &t) {
+    if (t.kev_used == (int)t.kev.size()) { cudaEvent_t ev; cudaEventCreate(&ev); t.kev.push_back(ev); }
+    return t.kev[t.kev_used++];
+}
+
 struct BatchPtrs {
     float *spec, *in_lo, *in_hi, *inh_lo, *inh_hi, *alpha;
     nyb200_split *splits;
@@ -300,7 +323,9 @@ int run_backward(nyb200_engine *e, const Net &net, const Batch &b, BatchPtrs &p)
         long zin_ds;
         if (k > 0) { zin_lo = p.zl + nv.pre_off[k - 1]; zin_hi = p.zu + nv.pre_off[k - 1]; zin_ds = np; }
         else { zin_lo = p.in_lo; zin_hi = p.in_hi; zin_ds = b.box_stride; }
+        if (e->timing.per_kernel) cudaEventRecord(next_kev(e->timing), e->stream);
         launch_gemm_f64(e, M, N, K, cur, p.lda, nv.W[k], N, nxt, p.lda, R, zin_lo, zin_hi, zin_ds, p.rpen);
+        if (e->timing.per_kernel) cudaEventRecord(next_kev(e->timing), e->stream);
         if (k > 0)
             launch_relax(e, nv, k - 1, k - 1, M, R, S, nxt, p.lda, p.tab, p.zabs, p.q, q_ds(k - 1), eps_for(N), p.rb, p.rabs,
                          p.rpen);
@@ -359,15 +384,7 @@ int run_batch(nyb200_engine *e) {
     BatchPtrs p;
     NYB_TRY(batch_ptrs(e, *net, e->batch, p));
     Timing &t = e->timing;
-    if (t.pending) {  // fold the previous run's events before reusing them
-        if (cudaEventSynchronize(t.ev[2]) == cudaSuccess) {
-            float f = 0, bw = 0;
-            cudaEventElapsedTime(&f, t.ev[0], t.ev[1]);
-            cudaEventElapsedTime(&bw, t.ev[1], t.ev[2]);
-            t.fwd_ms += f; t.bwd_ms += bw; t.tot_ms += f + bw; t.runs++;
-        }
-        t.pending = false;
-    }
+    fold_timing(t);  // the previous run's events are about to be reused
     cudaEventRecord(t.ev[0], e->stream);
     NYB_TRY(run_forward(e, *net, e->batch, p, e->batch.mode));
     cudaEventRecord(t.ev[1], e->stream);
@@ -524,11 +541,18 @@ int32_t nyb200_ibp_forward(nyb200_engine *e, int32_t net_id, int32_t D, const fl
     return NYB200_OK;
 }
 
+int32_t nyb200_timing_enable(nyb200_engine *e, int32_t per_kernel) {
+    if (!e) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    e->timing.per_kernel = per_kernel != 0;
+    return NYB200_OK;
+}
+
 int32_t nyb200_timing_reset(nyb200_engine *e) {
     if (!e) return NYB200_ERR_INVALID;
     std::lock_guard<std::mutex> g(e->mu);
-    if (e->timing.pending) { cudaEventSynchronize(e->timing.ev[2]); e->timing.pending = false; }
-    e->timing.fwd_ms = e->timing.bwd_ms = e->timing.tot_ms = 0;
+    if (e->timing.pending) { cudaEventSynchronize(e->timing.ev[2]); e->timing.pending = false; e->timing.kev_used = 0; }
+    e->timing.fwd_ms = e->timing.bwd_ms = e->timing.tot_ms = e->timing.gemm_ms = 0;
     e->timing.runs = 0;
     return NYB200_OK;
 }
@@ -537,19 +561,12 @@ int32_t nyb200_timing_read(nyb200_engine *e, const char *phase, double *avg_ms, 
     if (!e || !phase || !avg_ms) return NYB200_ERR_INVALID;
     std::lock_guard<std::mutex> g(e->mu);
     Timing &t = e->timing;
-    if (t.pending) {
-        if (cudaEventSynchronize(t.ev[2]) == cudaSuccess) {
-            float f = 0, bw = 0;
-            cudaEventElapsedTime(&f, t.ev[0], t.ev[1]);
-            cudaEventElapsedTime(&bw, t.ev[1], t.ev[2]);
-            t.fwd_ms += f; t.bwd_ms += bw; t.tot_ms += f + bw; t.runs++;
-        }
-        t.pending = false;
-    }
+    fold_timing(t);
     double tot = 0;
     if (!strcmp(phase, "forward")) tot = t.fwd_ms;
     else if (!strcmp(phase, "backward")) tot = t.bwd_ms;
     else if (!strcmp(phase, "total")) tot = t.tot_ms;
+    else if (!strcmp(phase, "gemm")) tot = t.gemm_ms;
     else return set_err(e, NYB200_ERR_INVALID, "unknown phase");
     *avg_ms = t.runs ? tot / t.runs : 0.0;
     if (n_runs) *n_runs = t.runs;

@@ -51,9 +51,12 @@ struct Batch {
 
 struct Timing {
     cudaEvent_t ev[3] = {nullptr, nullptr, nullptr};  // start, after forward, end
-    double fwd_ms = 0, bwd_ms = 0, tot_ms = 0;
+    double fwd_ms = 0, bwd_ms = 0, tot_ms = 0, gemm_ms = 0;
     int runs = 0;
     bool pending = false;
+    bool per_kernel = false;
+    std::vector<cudaEvent_t> kev;  // start/stop pairs around the contraction launches of the last run
+    int kev_used = 0;
 };
 
 }  // namespace nyb

@@ -35,7 +35,8 @@ EXPORTS = [
     "nyb200_set_path", "nyb200_launch_count", "nyb200_clear_working_set", "nyb200_gemm_f32", "nyb200_net_create",
     "nyb200_net_destroy", "nyb200_ibp_forward", "nyb200_bab_bound_batch", "nyb200_batch_upload", "nyb200_batch_run",
     "nyb200_batch_download", "nyb200_batch_min_lower", "nyb200_batch_min_lower_device",
-    "nyb200_batch_download_pre_bounds", "nyb200_batch_select_branch", "nyb200_timing_reset", "nyb200_timing_read",
+    "nyb200_batch_download_pre_bounds", "nyb200_batch_select_branch", "nyb200_timing_enable", "nyb200_timing_reset",
+    "nyb200_timing_read",
 ]
 
 
@@ -81,6 +82,7 @@ def load_library():
     L.nyb200_batch_min_lower_device.argtypes = [vp, C.POINTER(vp)]
     L.nyb200_batch_download_pre_bounds.argtypes = [vp, fp, fp]
     L.nyb200_batch_select_branch.argtypes = [vp, ip, ip, fp]
+    L.nyb200_timing_enable.argtypes = [vp, C.c_int32]
     L.nyb200_timing_reset.argtypes = [vp]
     L.nyb200_timing_read.argtypes = [vp, C.c_char_p, C.POINTER(C.c_double), ip]
     _lib = L
@@ -280,6 +282,9 @@ class B200Engine:
         r, j, w = np.empty(D, np.int32), np.empty(D, np.int32), np.empty(D, np.float32)
         self._check(self._L.nyb200_batch_select_branch(self._h, _ip(r), _ip(j), _fp(w)))
         return r, j, w
+
+    def timing_enable(self, per_kernel: bool):
+        self._check(self._L.nyb200_timing_enable(self._h, 1 if per_kernel else 0))
 
     def timing_reset(self):
         self._check(self._L.nyb200_timing_reset(self._h))

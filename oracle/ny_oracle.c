@@ -317,6 +317,10 @@ static lin_layer net_layer(const nyo_net *net, int k) {
     l.n_in = net->dims[k]; l.n_out = net->dims[k + 1];
     return l;
 }
+static inline int relu_after(const nyo_net *net, int k) {
+    if (k >= net->n_linear - 1) return 0;
+    return net->relu_after ? (net->relu_after[k] != 0) : 1;
+}
 static size_t pre_offset(const nyo_net *net, int k) { /* offset of Linear_k's output block */
     size_t o = 0;
     for (int i = 0; i < k; ++i) o += (size_t)net->dims[i + 1];
@@ -357,7 +361,11 @@ int nyo_ibp_forward(const nyo_net *net, const float *in_lo, const float *in_hi, 
         lin_layer Lk = net_layer(net, k);
         size_t o = pre_offset(net, k);
         linear_ibp(&Lk, zl, zu, pre_lo + o, pre_hi + o);
-        for (int j = 0; j < Lk.n_out; ++j) { zl[j] = nanmax(pre_lo[o + j], 0.0f); zu[j] = nanmax(pre_hi[o + j], 0.0f); }
+        int act = relu_after(net, k);
+        for (int j = 0; j < Lk.n_out; ++j) {
+            zl[j] = act ? nanmax(pre_lo[o + j], 0.0f) : pre_lo[o + j];
+            zu[j] = act ? nanmax(pre_hi[o + j], 0.0f) : pre_hi[o + j];
+        }
     }
     free(zl); free(zu);
     return 0;
@@ -620,7 +628,7 @@ static void crown_backward_concretize(const nyo_net *net, int top, lbounds seed,
         lin_layer Lk = net_layer(net, k);
         lbounds nxt = linear_backward(&Lk, &cur);
         lb_free(&cur); cur = nxt;
-        if (k > 0) {
+        if (k > 0 && relu_after(net, k - 1)) {
             size_t o = pre_offset(net, k - 1);
             lbounds r = relu_backward_crown(&cur, pre_lo + o, pre_hi + o);
             lb_free(&cur); cur = r;
@@ -665,7 +673,7 @@ int nyo_crown(const nyo_net *net, const float *in_lo, const float *in_hi, float 
         const float *il = ibp_l + o, *iu = ibp_u + o;
         int all_stable = 1;
         for (int j = 0; j < n; ++j) if (!(il[j] >= 0.0f || iu[j] <= 0.0f)) { all_stable = 0; break; }
-        if (k < L - 1 && all_stable) { /* ReLU-stable skip (:113-140) */
+        if (k < L - 1 && relu_after(net, k) && all_stable) { /* ReLU-stable skip (:113-140) */
             memcpy(t_l + o, il, 4 * (size_t)n); memcpy(t_u + o, iu, 4 * (size_t)n);
             continue;
         }
@@ -675,9 +683,10 @@ int nyo_crown(const nyo_net *net, const float *in_lo, const float *in_hi, float 
             /* the ReLU output bound stored by the collection: relu IBP of the tightened
              * pre-activation intersected with the plain IBP ReLU output (crown_ibp_forward.rs:25-100) */
             size_t po = pre_offset(net, k - 1);
+            int act = relu_after(net, k - 1);
             for (int j = 0; j < Lk.n_in; ++j) {
-                zl[j] = nanmax(t_l[po + j], 0.0f); zu[j] = nanmax(t_u[po + j], 0.0f);
-                fl[j] = nanmax(ibp_l[po + j], 0.0f); fu[j] = nanmax(ibp_u[po + j], 0.0f);
+                zl[j] = act ? nanmax(t_l[po + j], 0.0f) : t_l[po + j]; zu[j] = act ? nanmax(t_u[po + j], 0.0f) : t_u[po + j];
+                fl[j] = act ? nanmax(ibp_l[po + j], 0.0f) : ibp_l[po + j]; fu[j] = act ? nanmax(ibp_u[po + j], 0.0f) : ibp_u[po + j];
             }
             float *tmpl = (float *)malloc(4 * (size_t)Lk.n_in), *tmpu = (float *)malloc(4 * (size_t)Lk.n_in);
             memcpy(tmpl, fl, 4 * (size_t)Lk.n_in); memcpy(tmpu, fu, 4 * (size_t)Lk.n_in);
@@ -686,6 +695,14 @@ int nyo_crown(const nyo_net *net, const float *in_lo, const float *in_hi, float 
             free(tmpl); free(tmpu);
         }
         linear_ibp(&Lk, zl, zu, fl, fu);
+        if (k < L - 1 && !relu_after(net, k)) {
+            /* Linear feeding a Linear: the successor's backward step is exact and does not read the
+             * interval, so the collection takes the forward shortcut (ibp/helpers.rs:99-107,
+             * crown_ibp_forward.rs:25-100): forward bound from the tightened input, intersected with IBP. */
+            memcpy(t_l + o, il, 4 * (size_t)n); memcpy(t_u + o, iu, 4 * (size_t)n);
+            intersect_per_element(t_l + o, t_u + o, fl, fu, n);
+            continue;
+        }
         /* sparse_merge.rs:118-146: when >= 90% of the neurons are stable only the unstable rows
          * are propagated; stable rows keep the forward bound. */
         int n_unst = 0;
@@ -747,7 +764,7 @@ int nyo_beta_crown_bound(const nyo_net *net, const float *in_lo, const float *in
         lin_layer Lk = net_layer(net, k);
         lbounds nxt = linear_backward(&Lk, &cur);
         lb_free(&cur); cur = nxt;
-        if (k > 0) {
+        if (k > 0 && relu_after(net, k - 1)) {
             int r = k - 1, n = net->dims[k];
             size_t o = pre_offset(net, r);
             signed char *sp = (signed char *)calloc((size_t)n, 1);
@@ -802,6 +819,10 @@ int nyo_domain_bounds(const nyo_net *net, const float *in_lo, const float *in_hi
         if (intersect_per_element(nl, nu, pre_lo + o, pre_hi + o, n)) { memcpy(pre_lo + o, nl, 4 * (size_t)n); memcpy(pre_hi + o, nu, 4 * (size_t)n); }
         else { memcpy(pre_lo + o, nl, 4 * (size_t)n); memcpy(pre_hi + o, nu, 4 * (size_t)n); }
         if (k == L - 1) break;
+        if (!relu_after(net, k)) {
+            for (int j = 0; j < n; ++j) { zl[j] = pre_lo[o + j]; zu[j] = pre_hi[o + j]; }
+            continue;
+        }
         for (int s = 0; s < n_splits; ++s) if (splits[s].relu == k) {
             size_t q = o + (size_t)splits[s].neuron;
             if (splits[s].sign > 0) pre_lo[q] = nanmax(pre_lo[q], 0.0f); else pre_hi[q] = nanmin(pre_hi[q], 0.0f);
@@ -874,6 +895,7 @@ int nyo_select_largest_width(const nyo_net *net, const float *pre_lo, const floa
     int L = net->n_linear, found = 0;
     float best = 0.0f;
     for (int r = 0; r < L - 1; ++r) {
+        if (!relu_after(net, r)) continue;
         size_t o = pre_offset(net, r);
         for (int j = 0; j < net->dims[r + 1]; ++j) {
             float l = pre_lo[o + j], u = pre_hi[o + j];

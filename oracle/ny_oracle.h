@@ -30,6 +30,9 @@ typedef struct {
     const float *wflat;
     const float *bflat;
     const int32_t *has_bias; /* L */
+    const int32_t *relu_after; /* L entries or NULL (= a ReLU after every Linear but the last);
+                                  relu_after[k]==0 means Linear_k feeds Linear_{k+1} directly, which is
+                                  how ny's CLI appends specification rows as a final Linear layer */
 } nyo_net;
 
 /* A split constraint on ReLU `relu` (0-based, the ReLU that follows Linear_relu),

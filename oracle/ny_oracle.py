@@ -22,6 +22,7 @@ class _Net(C.Structure):
         ("wflat", C.POINTER(C.c_float)),
         ("bflat", C.POINTER(C.c_float)),
         ("has_bias", C.POINTER(C.c_int32)),
+        ("relu_after", C.POINTER(C.c_int32)),
     ]
 
 
@@ -77,9 +78,10 @@ def _ip(a):
 class Net:
     """Sequential ReLU MLP: weights[k] is [out, in] (row-major), biases[k] is [out] or None."""
 
-    def __init__(self, weights, biases=None):
+    def __init__(self, weights, biases=None, relu_after=None):
         self.weights = [np.ascontiguousarray(w, dtype=np.float32) for w in weights]
         L = len(self.weights)
+        self.relu_after = None if relu_after is None else np.ascontiguousarray(relu_after, np.int32)
         biases = biases if biases is not None else [None] * L
         self.biases = [None if b is None else np.ascontiguousarray(b, dtype=np.float32) for b in biases]
         self.dims = np.array([self.weights[0].shape[1]] + [w.shape[0] for w in self.weights], dtype=np.int32)
@@ -87,7 +89,7 @@ class Net:
         bl = [b for b in self.biases if b is not None]
         self._b = np.concatenate(bl).astype(np.float32) if bl else np.zeros(1, np.float32)
         self._hb = np.array([0 if b is None else 1 for b in self.biases], dtype=np.int32)
-        self.c = _Net(L, _ip(self.dims), _fp(self._w), _fp(self._b), _ip(self._hb))
+        self.c = _Net(L, _ip(self.dims), _fp(self._w), _fp(self._b), _ip(self._hb), _ip(self.relu_after))
 
     @property
     def n_pre(self) -> int:
@@ -96,7 +98,9 @@ class Net:
     def with_spec(self, spec) -> "Net":
         """Append the specification rows as a bias-free Linear layer, the way ny's CLI does
         (ny-cli commands/beta_crown/constraint_eval.rs:80-91)."""
-        return Net(self.weights + [np.asarray(spec, np.float32)], self.biases + [None])
+        L = len(self.weights)
+        ra = [1] * (L - 1) + [0, 0] if self.relu_after is None else list(self.relu_after[: L - 1]) + [0, 0]
+        return Net(self.weights + [np.asarray(spec, np.float32)], self.biases + [None], ra)
 
     def forward(self, x):
         z = np.asarray(x, np.float64)
@@ -104,7 +108,7 @@ class Net:
             z = z @ w.astype(np.float64).T
             if self.biases[k] is not None:
                 z = z + self.biases[k].astype(np.float64)
-            if k + 1 < len(self.weights):
+            if k + 1 < len(self.weights) and (self.relu_after is None or self.relu_after[k]):
                 z = np.maximum(z, 0.0)
         return z
 
