@@ -1,0 +1,330 @@
+"""Benchmark of the hot path: beta-CROWN bounding of a batch of BaB domains.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One step = one pass of the hot path over one batch: for every domain the interval forward pass
+under its splits, the CROWN backward pass with alpha slopes / beta multipliers for both bound
+directions of every specification row, and concretisation.  Workload: ReLU MLP 784 -> 8x256 -> 10,
+9 specification rows, 4096 domains per GPU each fixing 8 seeded unstable neurons (synthetic, seeded).
+With N > 1 (launched by torch.distributed.run) every rank bounds its own shard of N*4096 domains
+(weak scaling); the only exchange is the per-round min-reduce of the global lower bound over NCCL.
+
+Prints ONE JSON line (rank 0).  `value` is timed with inputs resident in HBM; `e2e` is the same metric
+through the host-buffer C-ABI call (host->device copy of the step's inputs from pinned memory,
+device->host read of the bounds, inside the timed region).  `--impl reference` times the CPU
+restatement of the reference's own path (oracle/, a thread pool over domains) on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+D_PER_GPU = 4096
+METRIC = "BaB domains bounded/sec (beta-CROWN)"
+UNIT = "domains/s"
+# Algorithmic work per domain for this network (fp32 coefficients, both bound directions carried):
+# contraction FLOPs 2*S*2*(10*256 + 7*256^2 + 256*784) and layer-by-layer bytes (each coefficient tile
+# written once and read once per layer, per-neuron relaxation inputs, 2*S outputs).
+S_ROWS = 9
+FLOPS_PER_DOMAIN = 2 * (2 * S_ROWS) * (10 * 256 + 7 * 256 * 256 + 256 * 784)
+BYTES_PER_DOMAIN = 2 * (2 * S_ROWS * 8 * 256 * 4) + 2 * S_ROWS * 784 * 4 + 8 * 256 * 3 * 4 + 2 * S_ROWS * 4
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i",
+                 str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_baseline(wl, rl, ru, sample_domains: int, repeats: int = 1):
+    """Times the oracle (CPU restatement of the reference path) on `sample_domains` domains of the same
+    workload with all host threads.  Returns (domains/s, threads)."""
+    from oracle import ny_oracle as O
+    from ny_b200 import workloads as W
+
+    onet = O.Net(wl.net.weights, wl.net.biases).with_spec(wl.spec)
+    S = wl.spec.shape[0]
+    rl2 = np.concatenate([rl, np.full(S, -np.inf, np.float32)])
+    ru2 = np.concatenate([ru, np.full(S, np.inf, np.float32)])
+    splits, ns = W.draw_domains(wl, rl, ru, sample_domains)
+    best = None
+    used = 1
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        _, _, _, used = O.bab_bound_batch(onet, wl.in_lo, wl.in_hi, rl2, ru2, splits, ns, 1, 0)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return sample_domains / best, used
+
+
+def run_reference(args, rank, world):
+    """Reference arm: the reference's CPU path (restated in oracle/) on the host cores."""
+    if rank != 0:
+        return
+    from oracle import ny_oracle as O
+    from ny_b200 import workloads as W
+
+    wl = W.config_mlp_bab()
+    onet = O.Net(wl.net.weights, wl.net.biases)
+    rl, ru = O.ibp_forward(onet, wl.in_lo, wl.in_hi)
+    sample = int(os.environ.get("NYB200_REF_SAMPLE", "1024"))
+    for _ in range(min(args.warmup, 1)):
+        cpu_baseline(wl, rl, ru, max(8, sample // 8))
+    times = []
+    threads = 1
+    for _ in range(args.steps):
+        t0 = time.perf_counter()
+        _, threads = cpu_baseline(wl, rl, ru, sample)
+        times.append(time.perf_counter() - t0)
+    ms = 1e3 * float(np.mean(times))
+    value = sample / (ms / 1e3)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f64", "data": "synthetic",
+        "config": {"workload": "beta-CROWN bound of BaB domains, ReLU MLP 784->8x256->10, 9 spec rows, 8 splits/domain",
+                   "domains_per_step": sample, "note": "CPU restatement of the reference path; the Rust reference cannot be built here"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": f"{sample} domains per step of the 4096-domain workload"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+class _DevPtr:
+    """Exposes a raw device pointer to torch through __cuda_array_interface__."""
+
+    def __init__(self, ptr, n):
+        self.__cuda_array_interface__ = {"shape": (n,), "typestr": "<f4", "data": (ptr, False), "version": 3}
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch
+
+    from ny_b200 import B200Engine
+    from ny_b200 import workloads as W
+
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    stream = torch.cuda.current_stream()
+    eng = B200Engine(local_rank, stream.cuda_stream)
+    from ny_b200 import engine as E
+
+    eng.set_path(E.PATH_TF32X3 if args.path == "tf32x3" else E.PATH_F64)
+    eng._path_name = args.path
+    wl = W.config_mlp_bab()
+    nid = eng.register_network(wl.net)
+    pl, pu = eng.ibp_forward_gpu(nid, wl.in_lo, wl.in_hi)  # root interval bounds, computed on the device
+    rl, ru = pl[0].copy(), pu[0].copy()
+    D = args.domains
+    splits, ns = W.draw_domains(wl, rl, ru, D, first=rank * D)
+    S = wl.spec.shape[0]
+
+    # ---- resident timing ------------------------------------------------------------------
+    eng.batch_upload(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, splits, ns, mode=1)
+    min_t = torch.as_tensor(_DevPtr(eng.batch_min_lower_device(), 1), device=f"cuda:{local_rank}")
+    global_lb = torch.empty(1, device=f"cuda:{local_rank}")
+
+    def step():
+        eng.batch_run()
+        if dist is not None:
+            global_lb.copy_(min_t)
+            dist.all_reduce(global_lb, op=dist.ReduceOp.MIN)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    eng.timing_enable(True)
+    eng.timing_reset()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    l0 = eng.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t0 = time.perf_counter()
+    ev0.record(stream)
+    for _ in range(args.steps):
+        step()
+    ev1.record(stream)
+    barrier()
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    dev_ms = ev0.elapsed_time(ev1)
+    launches = eng.launch_count() - l0
+    gemm_ms, _ = eng.timing_read("gemm")
+    fwd_ms, _ = eng.timing_read("forward")
+    bwd_ms, _ = eng.timing_read("backward")
+    eng.timing_enable(False)
+    lo, hi, inf = eng.batch_download()
+
+    # ---- end-to-end: host buffers in pinned memory through the C-ABI call ------------------
+    def pinned(a):
+        t = torch.empty(a.nbytes, dtype=torch.uint8, pin_memory=True)
+        v = t.numpy().view(a.dtype).reshape(a.shape)
+        v[...] = a
+        return v, t
+
+    sp_p, _k1 = pinned(splits)
+    ns_p, _k2 = pinned(ns)
+    e2e_steps = max(2, min(args.steps, 10))
+    for _ in range(2):
+        eng.bab_bound_batch(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, sp_p, ns_p, mode=1)
+    barrier()
+    t1 = time.perf_counter()
+    for _ in range(e2e_steps):
+        elo, ehi, einf = eng.bab_bound_batch(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, sp_p, ns_p, mode=1)
+    barrier()
+    e2e_ms = (time.perf_counter() - t1) * 1e3 / e2e_steps
+    clocks = sampler.stop()
+    assert np.array_equal(elo, lo), "resident and host-buffer paths disagree"
+    h2d = splits.nbytes + ns.nbytes + wl.spec.nbytes + wl.in_lo.nbytes + wl.in_hi.nbytes + rl.nbytes + ru.nbytes
+    d2h = lo.nbytes + hi.nbytes + inf.nbytes
+
+    ms_per_step = dev_ms / args.steps
+    e2e_val = D / (e2e_ms / 1e3)
+    if dist is not None:
+        t = torch.tensor([ms_per_step, e2e_ms, wall_ms / args.steps], device=f"cuda:{local_rank}", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_per_step, e2e_ms = float(t[0]), float(t[1])
+        e2e_val = D * world / (e2e_ms / 1e3)
+    value = D * world / (ms_per_step / 1e3)
+
+    if rank == 0:
+        peaks = load_peaks()
+        n_layers = len(wl.net.weights)
+        per_launch_s = (gemm_ms / 1e3) / n_layers if gemm_ms > 0 else None
+        flops_per_launch = FLOPS_PER_DOMAIN * D / n_layers
+        # fp32 operands fed to the tensor pipe as TF32: the dense TF32 rate is half the measured bf16 rate
+        peak_tf = peaks["bf16_tflops"] / 2.0
+        achieved = flops_per_launch / per_launch_s / 1e12 if per_launch_s else None
+        roofline = {
+            "bound": "tensor", "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
+            "frac": (achieved / peak_tf) if achieved else None, "traffic": None,
+            "kernel": "k_gemm_f64" if eng_path_name(eng) == "f64" else "k_umma_tf32x3",
+            "peak_source": f"{peaks['source']} bf16 GEMM / 2 (TF32 operand rate)",
+            "hbm_view": {"achieved_gbs": BYTES_PER_DOMAIN * D / ((fwd_ms + bwd_ms) / 1e3) / 1e9 if (fwd_ms + bwd_ms) > 0 else None,
+                         "peak_gbs": peaks["hbm_gbs"]},
+            "phase_ms": {"forward": fwd_ms, "backward": bwd_ms, "contraction": gemm_ms},
+        }
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f64" if eng_path_name(eng) == "f64" else "tf32x3", "data": "synthetic",
+            "config": {"workload": "beta-CROWN bound of BaB domains, ReLU MLP 784->8x256->10, 9 spec rows (both bound "
+                                   "directions), 8 splits/domain, constrained forward re-propagation",
+                       "domains_per_gpu": D, "global_batch": D * world, "parallelism": f"domain-sharded x{world}",
+                       "l2": "per-step working set (coefficient ping-pong buffers 2 x 231 MB) exceeds the 126 MB L2",
+                       "feasible_domains": int((inf == 0).sum())},
+            "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+                    "ms_per_step": e2e_ms},
+            "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline,
+            "wall_ms_per_step": wall_ms / args.steps,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            sample = int(os.environ.get("NYB200_CPU_SAMPLE", "4096"))
+            v, threads = cpu_baseline(wl, rl, ru, sample)
+            line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
+                                    "sample": f"{sample} domains of the same workload, one pass, all host threads"}
+        print(json.dumps(line))
+    eng.close()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def eng_path_name(eng):
+    return getattr(eng, "_path_name", "f64")
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--path", default=os.environ.get("NYB200_PATH", "f64"), choices=["f64", "tf32x3"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--domains", type=int, default=D_PER_GPU, help="domains per GPU (profiling runs use a smaller batch)")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()
