@@ -76,7 +76,10 @@ void nyb200_destroy(nyb200_engine *e) {
     cudaSetDevice(e->device);
     cudaStreamSynchronize(e->stream);
     for (auto &kv : e->ws) if (kv.second.p) cudaFree(kv.second.p);
-    for (auto &kv : e->nets) for (float *p : kv.second.owned) cudaFree(p);
+    for (auto &kv : e->nets) {
+        for (float *p : kv.second.owned) cudaFree(p);
+        for (auto &u : kv.second.umma) { cudaFree(u.wh); cudaFree(u.wl); }
+    }
     for (int i = 0; i < 3; ++i) if (e->timing.ev[i]) cudaEventDestroy(e->timing.ev[i]);
     for (cudaEvent_t ev : e->timing.kev) cudaEventDestroy(ev);
     delete e;
@@ -163,6 +166,7 @@ int32_t nyb200_net_destroy(nyb200_engine *e, int32_t net_id) {
     cudaSetDevice(e->device);
     cudaStreamSynchronize(e->stream);
     for (float *p : it->second.owned) cudaFree(p);
+    for (auto &u : it->second.umma) { cudaFree(u.wh); cudaFree(u.wl); }
     e->nets.erase(it);
     if (e->batch.net_id == net_id) e->batch = Batch();
     return NYB200_OK;
@@ -179,6 +183,23 @@ int32_t nyb200_gemm_f32(nyb200_engine *e, int32_t m, int32_t k, int32_t n, const
     NYB_WS(dc, float *, e, "gemm_c", (size_t)m * n * 4);
     NYB_CUDA(e, cudaMemcpyAsync(da, a, (size_t)m * k * 4, cudaMemcpyHostToDevice, e->stream));
     NYB_CUDA(e, cudaMemcpyAsync(db, b, (size_t)k * n * 4, cudaMemcpyHostToDevice, e->stream));
+    if (e->path == NYB200_PATH_TF32X3) {
+        NYB_WS(derr, int *, e, "umma_err", 256);
+        NYB_CUDA(e, cudaMemsetAsync(derr, 0, 4, e->stream));
+        UmmaLayer ul;
+        NYB_TRY(umma_prepare_layer(e, db, k, n, &ul));
+        int st = launch_umma(e, ul, m, da, k, dc, n, derr);
+        int herr = 0;
+        cudaError_t cs = cudaGetLastError();
+        if (cs == cudaSuccess) cs = cudaMemcpyAsync(&herr, derr, 4, cudaMemcpyDeviceToHost, e->stream);
+        if (cs == cudaSuccess) cs = cudaMemcpyAsync(c_out, dc, (size_t)m * n * 4, cudaMemcpyDeviceToHost, e->stream);
+        if (cs == cudaSuccess) cs = cudaStreamSynchronize(e->stream);
+        cudaFree(ul.wh); cudaFree(ul.wl);
+        NYB_TRY(st);
+        NYB_CUDA(e, cs);
+        if (herr) return set_err(e, NYB200_ERR_INTERNAL, "tcgen05 pipeline wait expired (code " + std::to_string(herr) + ")");
+        return NYB200_OK;
+    }
     launch_gemm_f64(e, m, n, k, da, k, db, n, dc, n, 1, nullptr, nullptr, 0, nullptr);
     NYB_CUDA(e, cudaGetLastError());
     NYB_CUDA(e, cudaMemcpyAsync(c_out, dc, (size_t)m * n * 4, cudaMemcpyDeviceToHost, e->stream));
@@ -300,8 +321,19 @@ int run_forward(nyb200_engine *e, const Net &net, const Batch &b, BatchPtrs &p, 
     return NYB200_OK;
 }
 
-int run_backward(nyb200_engine *e, const Net &net, const Batch &b, BatchPtrs &p) {
+int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p) {
     const NetView &nv = net.v;
+    const bool tensor = (e->path == NYB200_PATH_TF32X3);
+    int *derr = nullptr;
+    if (tensor) {
+        if (net.umma.empty()) {
+            net.umma.resize(nv.L);
+            for (int k = 0; k < nv.L; ++k) NYB_TRY(umma_prepare_layer(e, nv.W[k], nv.dims[k + 1], nv.dims[k], &net.umma[k]));
+        }
+        derr = (int *)ws_get(e, "umma_err", 256);
+        if (!derr) return NYB200_ERR_OOM;
+        NYB_CUDA(e, cudaMemsetAsync(derr, 0, 4, e->stream));
+    }
     int D = b.D, S = b.S, R = b.R, L = nv.L;
     int M = D * R;
     long np = nv.n_pre;
@@ -313,7 +345,9 @@ int run_backward(nyb200_engine *e, const Net &net, const Batch &b, BatchPtrs &p)
     NYB_CUDA(e, cudaMemcpyAsync(p.min_lower, &inf, 4, cudaMemcpyHostToDevice, e->stream));
     float *cur = p.A0, *nxt = p.A1;
     launch_seed(e, p.spec, S, nv.dims[L], D, p.lda, cur);
-    auto eps_for = [&](int K) { return (double)(K + 2) * 1.1102230246251565e-16 * 1.000001; };
+    auto eps_for = [&](int K) {
+        return tensor ? umma_eps(K) * 1.000001 : (double)(K + 2) * 1.1102230246251565e-16 * 1.000001;
+    };
     auto q_ds = [&](int lin_k) { return (lin_k == 0 && shared_box) ? 0L : np; };
     launch_relax(e, nv, -1, L - 1, M, R, S, cur, p.lda, p.tab, p.zabs, p.q, q_ds(L - 1), eps_for(nv.dims[L]), p.rb, p.rabs,
                  p.rpen);
@@ -324,7 +358,8 @@ int run_backward(nyb200_engine *e, const Net &net, const Batch &b, BatchPtrs &p)
         if (k > 0) { zin_lo = p.zl + nv.pre_off[k - 1]; zin_hi = p.zu + nv.pre_off[k - 1]; zin_ds = np; }
         else { zin_lo = p.in_lo; zin_hi = p.in_hi; zin_ds = b.box_stride; }
         if (e->timing.per_kernel) cudaEventRecord(next_kev(e->timing), e->stream);
-        launch_gemm_f64(e, M, N, K, cur, p.lda, nv.W[k], N, nxt, p.lda, R, zin_lo, zin_hi, zin_ds, p.rpen);
+        if (tensor) NYB_TRY(launch_umma(e, net.umma[k], M, cur, p.lda, nxt, p.lda, derr));
+        else launch_gemm_f64(e, M, N, K, cur, p.lda, nv.W[k], N, nxt, p.lda, R, zin_lo, zin_hi, zin_ds, p.rpen);
         if (e->timing.per_kernel) cudaEventRecord(next_kev(e->timing), e->stream);
         if (k > 0)
             launch_relax(e, nv, k - 1, k - 1, M, R, S, nxt, p.lda, p.tab, p.zabs, p.q, q_ds(k - 1), eps_for(N), p.rb, p.rabs,
@@ -380,7 +415,6 @@ int run_batch(nyb200_engine *e) {
     if (!e->batch.valid) return set_err(e, NYB200_ERR_INVALID, "no batch uploaded");
     Net *net;
     NYB_TRY(find_net(e, e->batch.net_id, &net));
-    if (e->path != NYB200_PATH_F64) return set_err(e, NYB200_ERR_UNSUPPORTED, "contraction path not available in this build");
     BatchPtrs p;
     NYB_TRY(batch_ptrs(e, *net, e->batch, p));
     Timing &t = e->timing;
@@ -405,7 +439,13 @@ int download_batch(nyb200_engine *e, float *out_lo, float *out_hi, int32_t *infe
     if (out_lo) NYB_CUDA(e, cudaMemcpyAsync(out_lo, p.out_lo, n * 4, cudaMemcpyDeviceToHost, e->stream));
     if (out_hi) NYB_CUDA(e, cudaMemcpyAsync(out_hi, p.out_hi, n * 4, cudaMemcpyDeviceToHost, e->stream));
     if (infeasible) NYB_CUDA(e, cudaMemcpyAsync(infeasible, p.flags, (size_t)e->batch.D * 4, cudaMemcpyDeviceToHost, e->stream));
+    int herr = 0;
+    if (e->path == NYB200_PATH_TF32X3) {
+        int *derr = (int *)ws_get(e, "umma_err", 256);
+        if (derr) NYB_CUDA(e, cudaMemcpyAsync(&herr, derr, 4, cudaMemcpyDeviceToHost, e->stream));
+    }
     NYB_CUDA(e, cudaStreamSynchronize(e->stream));
+    if (herr) return set_err(e, NYB200_ERR_INTERNAL, "tcgen05 pipeline wait expired (code " + std::to_string(herr) + ")");
     if (infeasible) {
         for (int d = 0; d < e->batch.D; ++d) {
             if (infeasible[d] & kFlagInvalid) return set_err(e, NYB200_ERR_INVALID, "split entry out of range");

@@ -30,10 +30,20 @@ struct NetView {
     const float *b[kMaxLinear];   // device or nullptr
 };
 
+// Per-layer operands of the tcgen05 contraction: W split into TF32 high/low parts, transposed to
+// [N x kpad] (K contiguous, zero padded to a multiple of 32) with one TMA tensor map each.
+struct UmmaLayer {
+    float *wh = nullptr, *wl = nullptr;
+    int K = 0, N = 0, kpad = 0;
+    alignas(64) unsigned char tm_hi[128];
+    alignas(64) unsigned char tm_lo[128];
+};
+
 struct Net {
     NetView v;
     std::vector<float *> owned;
     int max_dim = 0;
+    std::vector<UmmaLayer> umma;  // filled on first use of the tcgen05 path
 };
 
 struct DevBuf {
@@ -107,5 +117,10 @@ void launch_concretize(nyb200_engine *e, int M, int R, int S, int n0, const floa
 void launch_select_branch(nyb200_engine *e, const NetView &nv, int D, const float *pre_lo, const float *pre_hi,
                           const signed char *code, int *relu, int *neuron, float *width);
 void launch_fill_f64(nyb200_engine *e, double *p, size_t n, double v);
+
+// ---- tcgen05 contraction (nyb200_umma.cu) ----
+int umma_prepare_layer(nyb200_engine *e, const float *W, int K, int N, UmmaLayer *out);
+int launch_umma(nyb200_engine *e, const UmmaLayer &L, int M, const float *A, int lda, float *C, int ldc, int *err);
+double umma_eps(int K);
 
 }  // namespace nyb

@@ -1,0 +1,80 @@
+"""tcgen05 (3xTF32) contraction: checked through the C ABI against exact binary64 products, and
+the whole beta-CROWN batch on that path against the CPU oracle."""
+import numpy as np
+import pytest
+
+from ny_b200 import workloads as W
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def eng():
+    from ny_b200 import B200Engine, engine
+
+    e = B200Engine(0)
+    e.set_path(engine.PATH_TF32X3)
+    yield e
+    e.close()
+
+
+def _umma_eps(K):
+    steps = ((K + 31) // 32) * 4 * 3
+    return 0.75 * 2.0 ** -20 + steps * 2.0 ** -23
+
+
+@pytest.mark.parametrize("m,k,n", [(128, 32, 256), (128, 256, 256), (300, 256, 256), (1000, 10, 256),
+                                   (257, 256, 784), (64, 50, 50), (5, 7, 3), (4096, 512, 512)])
+def test_umma_gemm_within_rounding_model(eng, m, k, n):
+    g = np.random.Generator(np.random.PCG64(m * 7 + k * 3 + n))
+    a = (g.standard_normal((m, k)) * np.exp(g.uniform(-3, 3, (m, 1)))).astype(np.float32)
+    b = g.standard_normal((k, n)).astype(np.float32)
+    c = eng.gemm_f32(m, k, n, a, b)
+    exact = a.astype(np.float64) @ b.astype(np.float64)
+    S = np.abs(a).astype(np.float64) @ np.abs(b).astype(np.float64)
+    err = np.abs(c.astype(np.float64) - exact)
+    ratio = float(np.max(err / np.maximum(S, 1e-300)))
+    assert np.all(np.isfinite(c))
+    assert ratio <= _umma_eps(k), (ratio, _umma_eps(k))
+
+
+def test_umma_gemm_adversarial_same_sign_and_cancellation(eng):
+    # all-positive operands maximise the accumulator magnitude; alternating signs maximise cancellation
+    m, k, n = 256, 256, 256
+    g = np.random.Generator(np.random.PCG64(99))
+    for kind in ("positive", "alternating", "tiny_plus_huge"):
+        a = g.random((m, k)).astype(np.float32) + 0.5
+        b = g.random((k, n)).astype(np.float32) + 0.5
+        if kind == "alternating":
+            a[:, ::2] *= -1
+        if kind == "tiny_plus_huge":
+            a[:, :8] *= 1e6
+            b[8:, :] *= 1e-3
+        c = eng.gemm_f32(m, k, n, a, b)
+        exact = a.astype(np.float64) @ b.astype(np.float64)
+        S = np.abs(a).astype(np.float64) @ np.abs(b).astype(np.float64)
+        ratio = float(np.max(np.abs(c - exact) / S))
+        assert ratio <= _umma_eps(k), (kind, ratio)
+
+
+def test_batch_on_tensor_path_matches_oracle(eng, oracle):
+    from tests.test_gpu_parity import REL_TOL, _oracle_batch, _rel, _setup
+
+    wl = W.config_mlp_bab(seed=6, hidden=64, depth=4, n_in=196, eps=0.01, n_fix=8)
+    onet, ospec, nid, rl, ru = _setup(eng, oracle, wl)
+    splits, ns = W.draw_domains(wl, rl, ru, 200)
+    glo, ghi, ginf = eng.bab_bound_batch(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, splits, ns, mode=1)
+    olo, ohi, oinf, _ = _oracle_batch(oracle, ospec, wl, rl, ru, splits, ns, 1)
+    assert np.array_equal(ginf.astype(bool), oinf.astype(bool))
+    f = ~oinf.astype(bool)
+    both = np.concatenate([olo, ohi], axis=1)
+    dev = _rel(np.concatenate([glo, ghi], axis=1)[f], both[f])
+    print("max relative deviation on the tensor path:", dev)
+    assert dev <= REL_TOL
+    for d in range(0, 200, 25):
+        if ginf[d]:
+            continue
+        mn = W.sample_min_margin(wl, 20000, 900 + d, splits[d][: ns[d]])
+        ok = np.isfinite(mn)
+        assert np.all(glo[d][ok] <= mn[ok])
+    eng.release_network(nid)
