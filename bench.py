@@ -193,11 +193,13 @@ def run_ours(args, rank, world, local_rank):
     min_t = torch.as_tensor(_DevPtr(eng.batch_min_lower_device(), 1), device=f"cuda:{local_rank}")
     global_lb = torch.empty(1, device=f"cuda:{local_rank}")
 
+    from ny_b200 import sharding
+
     def step():
         eng.batch_run()
-        if dist is not None:
+        if dist is not None:  # the round's only exchange: min-reduce of the global lower bound
             global_lb.copy_(min_t)
-            dist.all_reduce(global_lb, op=dist.ReduceOp.MIN)
+            sharding.allreduce_min(global_lb, dist)
 
     def barrier():
         if dist is not None:

@@ -3,6 +3,7 @@
 // numeric result is produced by the kernels in this directory.
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "nyb200_internal.cuh"
@@ -79,6 +80,7 @@ void nyb200_destroy(nyb200_engine *e) {
     for (auto &kv : e->nets) {
         for (float *p : kv.second.owned) cudaFree(p);
         for (auto &u : kv.second.umma) { cudaFree(u.wh); cudaFree(u.wl); }
+        for (auto &u : kv.second.umma_fwd) { cudaFree(u.wh); cudaFree(u.wl); }
     }
     for (int i = 0; i < 3; ++i) if (e->timing.ev[i]) cudaEventDestroy(e->timing.ev[i]);
     for (cudaEvent_t ev : e->timing.kev) cudaEventDestroy(ev);
@@ -133,6 +135,7 @@ int32_t nyb200_net_create(nyb200_engine *e, int32_t n_linear, const int32_t *dim
     }
     net.v.pre_off[n_linear] = off;
     net.v.n_pre = off;
+    net.v.nps = (off + 3) & ~3;
     size_t wo = 0, bo = 0;
     for (int k = 0; k < n_linear; ++k) {
         size_t nw = (size_t)dims[k] * dims[k + 1];
@@ -167,6 +170,7 @@ int32_t nyb200_net_destroy(nyb200_engine *e, int32_t net_id) {
     cudaStreamSynchronize(e->stream);
     for (float *p : it->second.owned) cudaFree(p);
     for (auto &u : it->second.umma) { cudaFree(u.wh); cudaFree(u.wl); }
+    for (auto &u : it->second.umma_fwd) { cudaFree(u.wh); cudaFree(u.wl); }
     e->nets.erase(it);
     if (e->batch.net_id == net_id) e->batch = Batch();
     return NYB200_OK;
@@ -249,7 +253,7 @@ struct BatchPtrs {
 
 int batch_ptrs(nyb200_engine *e, const Net &net, const Batch &b, BatchPtrs &p) {
     const NetView &nv = net.v;
-    size_t D = (size_t)b.D, np = (size_t)nv.n_pre;
+    size_t D = (size_t)b.D, np = (size_t)nv.nps;
     size_t M = D * b.R;
     p.lda = (net.max_dim + 3) & ~3;
     size_t box = (size_t)nv.dims[0] * (b.box_stride ? D : 1);
@@ -272,8 +276,8 @@ int batch_ptrs(nyb200_engine *e, const Net &net, const Batch &b, BatchPtrs &p) {
     GET(q, float *, "q", D * np * 4)
     GET(pre_lo, float *, "pre_lo", D * np * 4)
     GET(pre_hi, float *, "pre_hi", D * np * 4)
-    GET(zl, float *, "zl", D * np * 4)
-    GET(zu, float *, "zu", D * np * 4)
+    GET(zl, float *, "zlu", 2 * D * np * 4)  // lower ends, then upper ends: one [2D x nps] operand
+    p.zu = p.zl + D * np;
     GET(zabs, float *, "zabs", D * np * 4)
     GET(tab, float4 *, "tab", D * np * 16)
     GET(A0, float *, "A0", M * p.lda * 4)
@@ -296,10 +300,29 @@ int find_net(nyb200_engine *e, int net_id, Net **out) {
 }
 
 // Interval forward pass for the resident batch.  fwd_mode: 0 clamp-only, 1 constrained, 2 plain IBP.
-int run_forward(nyb200_engine *e, const Net &net, const Batch &b, BatchPtrs &p, int fwd_mode) {
+int run_forward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int fwd_mode) {
     const NetView &nv = net.v;
     int D = b.D;
-    size_t np = nv.n_pre;
+    // The tcgen05 path covers every layer whose input is a post-ReLU interval (lower end >= 0) of a
+    // per-domain batch; the first layer (arbitrary-sign box, usually shared) stays on the binary64 kernel.
+    const bool tensor = (e->path == NYB200_PATH_TF32X3) && D >= 64 && nv.L > 1;
+    float *Fl = nullptr;
+    int ldf = 0;
+    int *derr = nullptr;
+    if (tensor) {
+        if (net.umma_fwd.empty()) {
+            net.umma_fwd.resize(nv.L);
+            for (int k = 1; k < nv.L; ++k)
+                NYB_TRY(umma_prepare_forward_layer(e, nv.W[k], nv.dims[k], nv.dims[k + 1], &net.umma_fwd[k]));
+        }
+        int mo = 0;
+        for (int k = 2; k <= nv.L; ++k) mo = nv.dims[k] > mo ? nv.dims[k] : mo;
+        ldf = (2 * mo + 3) & ~3;
+        Fl = (float *)ws_get(e, "fwd", (size_t)2 * D * ldf * 4);
+        derr = (int *)ws_get(e, "umma_err", 256);
+        if (!Fl || !derr) return NYB200_ERR_OOM;
+    }
+    size_t np = nv.nps;
     NYB_CUDA(e, cudaMemsetAsync(p.flags, 0, (size_t)D * 4, e->stream));
     NYB_CUDA(e, cudaMemsetAsync(p.code, 0, (size_t)D * np, e->stream));
     NYB_CUDA(e, cudaMemsetAsync(p.sbeta, 0, (size_t)D * np * 4, e->stream));
@@ -311,11 +334,14 @@ int run_forward(nyb200_engine *e, const Net &net, const Batch &b, BatchPtrs &p, 
         int Deff;
         if (k == 0) { zl = p.in_lo; zu = p.in_hi; in_ds = b.box_stride; Deff = b.box_stride ? D : 1; }
         else { zl = p.zl + nv.pre_off[k - 1]; zu = p.zu + nv.pre_off[k - 1]; in_ds = (long)np; Deff = D; }
-        launch_ibp_linear(e, nv, k, Deff, zl, zu, in_ds, p.raw_lo, p.raw_hi, p.q, (long)np);
+        const bool tk = tensor && k >= 1;
+        if (tk) NYB_TRY(launch_umma(e, net.umma_fwd[k], 2 * D, zl, (int)np, Fl, ldf, derr));  // zl rows, then zu rows
+        else launch_ibp_linear(e, nv, k, Deff, zl, zu, in_ds, p.raw_lo, p.raw_hi, p.q, (long)np);
         long raw_ds = (Deff == 1 && D > 1) ? 0 : (long)np;
         launch_ibp_finish(e, nv, k, D, fwd_mode, p.raw_lo, p.raw_hi, raw_ds, fwd_mode == 2 ? nullptr : p.inh_lo,
                           fwd_mode == 2 ? nullptr : p.inh_hi, p.code, p.sbeta, b.has_alpha ? p.alpha : nullptr, p.pre_lo,
-                          p.pre_hi, p.zl, p.zu, p.tab, p.zabs, p.flags);
+                          p.pre_hi, p.zl, p.zu, p.tab, p.zabs, p.flags, tk ? Fl : nullptr, ldf,
+                          tk ? umma_eps(nv.dims[k]) * 1.000001 : 0.0, p.q);
     }
     NYB_CUDA(e, cudaGetLastError());
     return NYB200_OK;
@@ -324,6 +350,9 @@ int run_forward(nyb200_engine *e, const Net &net, const Batch &b, BatchPtrs &p, 
 int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p) {
     const NetView &nv = net.v;
     const bool tensor = (e->path == NYB200_PATH_TF32X3);
+    // The contraction kernel can apply the relaxation in its A producers (one kernel per layer), but with
+    // 128 producer threads per SM that is slower than a separate streaming pass; kept selectable.
+    static const bool fuse = getenv("NYB200_FUSE_RELAX") != nullptr;
     int *derr = nullptr;
     if (tensor) {
         if (net.umma.empty()) {
@@ -332,11 +361,10 @@ int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p) {
         }
         derr = (int *)ws_get(e, "umma_err", 256);
         if (!derr) return NYB200_ERR_OOM;
-        NYB_CUDA(e, cudaMemsetAsync(derr, 0, 4, e->stream));
     }
     int D = b.D, S = b.S, R = b.R, L = nv.L;
     int M = D * R;
-    long np = nv.n_pre;
+    long np = nv.nps;
     bool shared_box = (b.box_stride == 0 && D > 1);
     NYB_CUDA(e, cudaMemsetAsync(p.rb, 0, (size_t)M * 8, e->stream));
     NYB_CUDA(e, cudaMemsetAsync(p.rabs, 0, (size_t)M * 8, e->stream));
@@ -349,8 +377,9 @@ int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p) {
         return tensor ? umma_eps(K) * 1.000001 : (double)(K + 2) * 1.1102230246251565e-16 * 1.000001;
     };
     auto q_ds = [&](int lin_k) { return (lin_k == 0 && shared_box) ? 0L : np; };
-    launch_relax(e, nv, -1, L - 1, M, R, S, cur, p.lda, p.tab, p.zabs, p.q, q_ds(L - 1), eps_for(nv.dims[L]), p.rb, p.rabs,
-                 p.rpen);
+    if (!(tensor && fuse))
+        launch_relax(e, nv, -1, L - 1, M, R, S, cur, p.lda, p.tab, p.zabs, p.q, q_ds(L - 1), eps_for(nv.dims[L]), p.rb,
+                     p.rabs, p.rpen);
     for (int k = L - 1; k >= 0; --k) {
         int K = nv.dims[k + 1], N = nv.dims[k];
         const float *zin_lo, *zin_hi;
@@ -358,10 +387,21 @@ int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p) {
         if (k > 0) { zin_lo = p.zl + nv.pre_off[k - 1]; zin_hi = p.zu + nv.pre_off[k - 1]; zin_ds = np; }
         else { zin_lo = p.in_lo; zin_hi = p.in_hi; zin_ds = b.box_stride; }
         if (e->timing.per_kernel) cudaEventRecord(next_kev(e->timing), e->stream);
-        if (tensor) NYB_TRY(launch_umma(e, net.umma[k], M, cur, p.lda, nxt, p.lda, derr));
-        else launch_gemm_f64(e, M, N, K, cur, p.lda, nv.W[k], N, nxt, p.lda, R, zin_lo, zin_hi, zin_ds, p.rpen);
+        if (tensor) {
+            // The relaxation of the incoming rows (ReLU k, or a pass-through for the seed rows) and the row
+            // sums this product owes are done by the kernel's A producers.
+            UmmaRelax rx;
+            rx.mode = !fuse ? 0 : (k == L - 1) ? 1 : 2;
+            rx.R = R; rx.S = S; rx.nps = np; rx.off = nv.pre_off[k]; rx.q_ds = q_ds(k);
+            rx.tab = p.tab; rx.zabs = p.zabs; rx.q = p.q; rx.bias_k = nv.b[k];
+            rx.eps = (float)(eps_for(K) * 1.0000002);
+            rx.rb = p.rb; rx.rabs = p.rabs; rx.rpen = p.rpen;
+            NYB_TRY(launch_umma(e, net.umma[k], M, cur, p.lda, nxt, p.lda, derr, &rx));
+        } else {
+            launch_gemm_f64(e, M, N, K, cur, p.lda, nv.W[k], N, nxt, p.lda, R, zin_lo, zin_hi, zin_ds, p.rpen);
+        }
         if (e->timing.per_kernel) cudaEventRecord(next_kev(e->timing), e->stream);
-        if (k > 0)
+        if (k > 0 && !(tensor && fuse))
             launch_relax(e, nv, k - 1, k - 1, M, R, S, nxt, p.lda, p.tab, p.zabs, p.q, q_ds(k - 1), eps_for(N), p.rb, p.rabs,
                          p.rpen);
         float *t = cur; cur = nxt; nxt = t;
@@ -401,7 +441,8 @@ int upload_batch(nyb200_engine *e, int32_t net_id, const float *spec, int32_t S,
     NYB_CUDA(e, cudaMemcpyAsync(p.in_hi, in_hi, box * 4, cudaMemcpyHostToDevice, s));
     NYB_CUDA(e, cudaMemcpyAsync(p.inh_lo, inh_lo, np * 4, cudaMemcpyHostToDevice, s));
     NYB_CUDA(e, cudaMemcpyAsync(p.inh_hi, inh_hi, np * 4, cudaMemcpyHostToDevice, s));
-    if (alpha) NYB_CUDA(e, cudaMemcpyAsync(p.alpha, alpha, (size_t)D * np * 4, cudaMemcpyHostToDevice, s));
+    if (alpha)
+        NYB_CUDA(e, cudaMemcpy2DAsync(p.alpha, (size_t)nv.nps * 4, alpha, np * 4, np * 4, (size_t)D, cudaMemcpyHostToDevice, s));
     if (max_splits > 0) {
         NYB_CUDA(e, cudaMemcpyAsync(p.splits, splits, (size_t)D * max_splits * sizeof(nyb200_split), cudaMemcpyHostToDevice, s));
         NYB_CUDA(e, cudaMemcpyAsync(p.nsplits, n_splits, (size_t)D * 4, cudaMemcpyHostToDevice, s));
@@ -419,6 +460,11 @@ int run_batch(nyb200_engine *e) {
     NYB_TRY(batch_ptrs(e, *net, e->batch, p));
     Timing &t = e->timing;
     fold_timing(t);  // the previous run's events are about to be reused
+    if (e->path == NYB200_PATH_TF32X3) {
+        int *derr = (int *)ws_get(e, "umma_err", 256);
+        if (!derr) return NYB200_ERR_OOM;
+        NYB_CUDA(e, cudaMemsetAsync(derr, 0, 4, e->stream));
+    }
     cudaEventRecord(t.ev[0], e->stream);
     NYB_TRY(run_forward(e, *net, e->batch, p, e->batch.mode));
     cudaEventRecord(t.ev[1], e->stream);
@@ -526,9 +572,9 @@ int32_t nyb200_batch_download_pre_bounds(nyb200_engine *e, float *pre_lo, float 
     NYB_TRY(find_net(e, e->batch.net_id, &net));
     BatchPtrs p;
     NYB_TRY(batch_ptrs(e, *net, e->batch, p));
-    size_t n = (size_t)e->batch.D * net->v.n_pre;
-    NYB_CUDA(e, cudaMemcpyAsync(pre_lo, p.pre_lo, n * 4, cudaMemcpyDeviceToHost, e->stream));
-    NYB_CUDA(e, cudaMemcpyAsync(pre_hi, p.pre_hi, n * 4, cudaMemcpyDeviceToHost, e->stream));
+    size_t w = (size_t)net->v.n_pre * 4, ws = (size_t)net->v.nps * 4;
+    NYB_CUDA(e, cudaMemcpy2DAsync(pre_lo, w, p.pre_lo, ws, w, (size_t)e->batch.D, cudaMemcpyDeviceToHost, e->stream));
+    NYB_CUDA(e, cudaMemcpy2DAsync(pre_hi, w, p.pre_hi, ws, w, (size_t)e->batch.D, cudaMemcpyDeviceToHost, e->stream));
     NYB_CUDA(e, cudaStreamSynchronize(e->stream));
     return NYB200_OK;
 }
@@ -573,10 +619,15 @@ int32_t nyb200_ibp_forward(nyb200_engine *e, int32_t net_id, int32_t D, const fl
     NYB_CUDA(e, cudaMemcpyAsync(p.in_lo, in_lo, box * 4, cudaMemcpyHostToDevice, e->stream));
     NYB_CUDA(e, cudaMemcpyAsync(p.in_hi, in_hi, box * 4, cudaMemcpyHostToDevice, e->stream));
     e->batch = Batch();  // the resident batch's buffers are being reused
+    if (e->path == NYB200_PATH_TF32X3) {
+        int *derr = (int *)ws_get(e, "umma_err", 256);
+        if (!derr) return NYB200_ERR_OOM;
+        NYB_CUDA(e, cudaMemsetAsync(derr, 0, 4, e->stream));
+    }
     NYB_TRY(run_forward(e, *net, b, p, 2));
-    size_t n = (size_t)D * nv.n_pre;
-    NYB_CUDA(e, cudaMemcpyAsync(pre_lo, p.pre_lo, n * 4, cudaMemcpyDeviceToHost, e->stream));
-    NYB_CUDA(e, cudaMemcpyAsync(pre_hi, p.pre_hi, n * 4, cudaMemcpyDeviceToHost, e->stream));
+    size_t w = (size_t)nv.n_pre * 4, ws = (size_t)nv.nps * 4;
+    NYB_CUDA(e, cudaMemcpy2DAsync(pre_lo, w, p.pre_lo, ws, w, (size_t)D, cudaMemcpyDeviceToHost, e->stream));
+    NYB_CUDA(e, cudaMemcpy2DAsync(pre_hi, w, p.pre_hi, ws, w, (size_t)D, cudaMemcpyDeviceToHost, e->stream));
     NYB_CUDA(e, cudaStreamSynchronize(e->stream));
     return NYB200_OK;
 }

@@ -26,6 +26,7 @@ struct NetView {
     int dims[kMaxLinear + 1];     // widths
     int pre_off[kMaxLinear + 1];  // offset of Linear_k's output block inside a [n_pre] row
     int n_pre;                    // sum_{k>=1} dims[k]
+    int nps;                      // row stride of the per-domain device arrays: n_pre rounded up to 4
     const float *W[kMaxLinear];   // device, row-major [dims[k+1] x dims[k]]
     const float *b[kMaxLinear];   // device or nullptr
 };
@@ -44,6 +45,7 @@ struct Net {
     std::vector<float *> owned;
     int max_dim = 0;
     std::vector<UmmaLayer> umma;  // filled on first use of the tcgen05 path
+    std::vector<UmmaLayer> umma_fwd;  // interval forward operands [W+ | W-] per layer (entry 0 unused)
 };
 
 struct DevBuf {
@@ -102,7 +104,8 @@ void launch_ibp_linear(nyb200_engine *e, const NetView &nv, int k, int Deff, con
 void launch_ibp_finish(nyb200_engine *e, const NetView &nv, int k, int D, int mode, const float *raw_lo,
                        const float *raw_hi, long raw_dstride, const float *inh_lo, const float *inh_hi,
                        const signed char *code, const float *sbeta, const float *alpha, float *pre_lo, float *pre_hi,
-                       float *zl, float *zu, float4 *tab, float *zabs, int *flags);
+                       float *zl, float *zu, float4 *tab, float *zabs, int *flags, const float *F = nullptr, int ldf = 0,
+                       double eps = 0.0, float *q = nullptr);
 void launch_seed(nyb200_engine *e, const float *spec, int S, int nL, int D, int lda, float *A);
 // In-place ReLU relaxation of A [M x n] (ReLU r) or identity pass (r < 0), accumulating the row sums.
 void launch_relax(nyb200_engine *e, const NetView &nv, int r, int lin_k, int M, int R, int S, float *A, int lda,
@@ -118,9 +121,30 @@ void launch_select_branch(nyb200_engine *e, const NetView &nv, int D, const floa
                           const signed char *code, int *relu, int *neuron, float *width);
 void launch_fill_f64(nyb200_engine *e, double *p, size_t n, double v);
 
+// Optional work fused into the A-operand producers of the tcgen05 contraction: the ReLU relaxation of
+// the incoming coefficient rows (mode 2) or a pass-through (mode 1), plus the row sums the contraction
+// owes (bias += a'.bias_k, penalty += eps |a'| . q).  mode 0: plain product.
+struct UmmaRelax {
+    int mode = 0;
+    int R = 1, S = 1;          // rows per domain, spec rows (rows >= S of a domain are upper-bound rows)
+    long nps = 0;              // row stride of tab / zabs / q
+    int off = 0;               // column offset of this layer's block inside those rows
+    long q_ds = 0;             // domain stride of q (0 when the layer's q is shared by all domains)
+    const float4 *tab = nullptr;
+    const float *zabs = nullptr, *q = nullptr, *bias_k = nullptr;
+    float eps = 0.f;           // rounding of the contraction relative to |a'| . q, rounded up to fp32
+    double *rb = nullptr, *rabs = nullptr, *rpen = nullptr;
+};
+
 // ---- tcgen05 contraction (nyb200_umma.cu) ----
 int umma_prepare_layer(nyb200_engine *e, const float *W, int K, int N, UmmaLayer *out);
-int launch_umma(nyb200_engine *e, const UmmaLayer &L, int M, const float *A, int lda, float *C, int ldc, int *err);
+int launch_umma(nyb200_engine *e, const UmmaLayer &L, int M, const float *A, int lda, float *C, int ldc, int *err,
+                const UmmaRelax *relax = nullptr);
 double umma_eps(int K);
+// Builds the forward-pass operand of Linear_k: the [n_in x 2 n_out] matrix (W+^T | W-^T).
+int umma_prepare_forward_layer(nyb200_engine *e, const float *W, int n_in, int n_out, UmmaLayer *out);
+// raw_lo/raw_hi/q of Linear_k from the two products Fl = zl * (W+|W-), Fu = zu * (W+|W-) (zl >= 0).
+void launch_ibp_combine(nyb200_engine *e, int D, int n_out, const float *Fl, const float *Fu, int ldf, const float *bias,
+                        double eps, float *raw_lo, float *raw_hi, float *q, long out_ds);
 
 }  // namespace nyb

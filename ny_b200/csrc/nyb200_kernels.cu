@@ -52,7 +52,7 @@ __global__ void k_scatter_splits(NetView nv, const nyb200_split *__restrict__ sp
         atomicOr(&flags[d], kFlagInvalid);
         return;
     }
-    long o = (long)d * nv.n_pre + nv.pre_off[c.relu] + c.neuron;
+    long o = (long)d * nv.nps + nv.pre_off[c.relu] + c.neuron;
     code[o] = (signed char)c.sign;
     // A non-finite multiplier is skipped, as relu_backward.rs:156-173 does.
     sbeta[o] = isfinite(c.beta) ? c.beta * (float)c.sign : 0.0f;
@@ -146,13 +146,32 @@ __global__ void k_ibp_finish(NetView nv, int k, int D, int mode, int last, const
                              const float *__restrict__ sbeta, const float *__restrict__ alpha,
                              float *__restrict__ pre_lo, float *__restrict__ pre_hi, float *__restrict__ zl,
                              float *__restrict__ zu, float4 *__restrict__ tab, float *__restrict__ zabs,
-                             int *__restrict__ flags) {
+                             int *__restrict__ flags, const float *__restrict__ F, int ldf, double eps,
+                             float *__restrict__ q) {
     int n = nv.dims[k + 1], off = nv.pre_off[k];
     long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= (long)D * n) return;
     int d = (int)(t / n), j = (int)(t % n);
-    long o = (long)d * nv.n_pre + off + j;
-    float l = raw_lo[(long)d * raw_ds + off + j], u = raw_hi[(long)d * raw_ds + off + j];
+    long o = (long)d * nv.nps + off + j;
+    float l, u;
+    if (F) {
+        // Tensor-core forward: F rows [0, D) hold zl (W+|W-), rows [D, 2D) hold zu (W+|W-), valid for
+        // 0 <= zl <= zu.  lo = W+ zl + W- zu + b, hi = W+ zu + W- zl + b, q = |W| zu.  Every product carries
+        // a rounding of at most eps times the sum of its own term magnitudes, each bounded by q, so both
+        // ends move outward by eps * q (q inflated by its own relative error) before the directed cast.
+        double pl = F[(long)d * ldf + j], nl = F[(long)d * ldf + n + j];
+        double pu = F[(long)(D + d) * ldf + j], nu = F[(long)(D + d) * ldf + n + j];
+        double b = nv.b[k] ? (double)nv.b[k][j] : 0.0;
+        double qq = (fabs(pu) + fabs(nu)) / (1.0 - 2.0 * eps);
+        double slack = eps * qq + 2.3e-16 * (qq + fabs(b));
+        l = __double2float_rd(pl + nu + b - slack);
+        u = __double2float_ru(pu + nl + b + slack);
+        if (isnan(l) || isnan(u)) { l = -INFINITY; u = INFINITY; }
+        q[o] = __double2float_ru(qq);
+    } else {
+        l = raw_lo[(long)d * raw_ds + off + j];
+        u = raw_hi[(long)d * raw_ds + off + j];
+    }
     if (mode == 0 && inh_lo) { l = inh_lo[off + j]; u = inh_hi[off + j]; }
     else if (mode == 1 && inh_lo) {
         float il = inh_lo[off + j], iu = inh_hi[off + j];
@@ -252,6 +271,68 @@ k_relax(int n, int off, int M, int R, int S, int n_pre, int identity, float *__r
     }
     sb = warp_sum(sb); sa = warp_sum(sa); sp = warp_sum(sp);
     if (lane == 0) { rb[m] += sb; rabs[m] += sa; rpen[m] += sp; }
+}
+
+// Vectorised form of k_relax for 16-byte aligned layouts (n, off, lda, row strides multiples of 4): one
+// warp per row, every lane handles float4 groups and issues all loads of a group before using them.
+// Penalties are accumulated in fp32 with upward-directed operations (an upper bound is all that is
+// needed); the bias stays in binary64.
+__device__ __forceinline__ void relax_one(float a, float ls, float us, float ui, float sbt, float za, float qv, float bk,
+                                          bool upper, bool identity, bool has_bias, float eps, float &nw_out, double &sb,
+                                          float &sa, float &sp) {
+    float nw = a;
+    if (!identity) {
+        float slope = 0.f, icp = 0.f;
+        if (a > 0.f) { slope = upper ? us : ls; icp = upper ? ui : 0.f; }
+        else if (a < 0.f) { slope = upper ? ls : us; icp = upper ? 0.f : ui; }
+        if (a == 0.f || slope == 0.f) nw = 0.f;
+        else {
+            float p = a * slope;
+            nw = upper ? next_up_f(p) : next_down_f(p);
+            float gap = __fmul_ru(fabsf(fmaf(a, slope, -nw)), 1.000001f);  // |a*slope - nw| to one rounding, inflated
+            sp = __fmaf_ru(gap, za, sp);
+        }
+        if (icp != 0.f) { sb += (double)a * (double)icp; sa = __fmaf_ru(fabsf(a), fabsf(icp), sa); }
+        if (sbt != 0.f) nw = upper ? nw + sbt : nw - sbt;
+    }
+    if (has_bias) { sb += (double)nw * (double)bk; sa = __fmaf_ru(fabsf(nw), fabsf(bk), sa); }
+    sp = __fmaf_ru(__fmul_ru(eps, fabsf(nw)), qv, sp);
+    nw_out = nw;
+}
+
+__global__ void __launch_bounds__(256)
+k_relax_v4(int n, int off, int M, int R, int S, long nps, int identity, float *__restrict__ A, int lda,
+           const float4 *__restrict__ tab, const float *__restrict__ zabs, const float *__restrict__ q, long q_ds,
+           const float *__restrict__ bias_k, float eps, double *__restrict__ rb, double *__restrict__ rabs,
+           double *__restrict__ rpen) {
+    int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= M) return;
+    int m = warp, d = m / R;
+    bool upper = (m % R) >= S;
+    float *row = A + (long)m * lda;
+    const long tb = (long)d * nps + off, qb = (long)d * q_ds + off;
+    double sb = 0.0;
+    float sa = 0.f, sp = 0.f;
+    const bool has_bias = bias_k != nullptr;
+    for (int j = lane * 4; j < n; j += 128) {
+        float4 a = *(const float4 *)(row + j);
+        float4 qv = *(const float4 *)(q + qb + j);
+        float4 bk = has_bias ? *(const float4 *)(bias_k + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 t0 = make_float4(0.f, 0.f, 0.f, 0.f), t1 = t0, t2 = t0, t3 = t0, za = t0;
+        if (!identity) {
+            t0 = tab[tb + j]; t1 = tab[tb + j + 1]; t2 = tab[tb + j + 2]; t3 = tab[tb + j + 3];
+            za = *(const float4 *)(zabs + tb + j);
+        }
+        float4 o;
+        relax_one(a.x, t0.x, t0.y, t0.z, t0.w, za.x, qv.x, bk.x, upper, identity, has_bias, eps, o.x, sb, sa, sp);
+        relax_one(a.y, t1.x, t1.y, t1.z, t1.w, za.y, qv.y, bk.y, upper, identity, has_bias, eps, o.y, sb, sa, sp);
+        relax_one(a.z, t2.x, t2.y, t2.z, t2.w, za.z, qv.z, bk.z, upper, identity, has_bias, eps, o.z, sb, sa, sp);
+        relax_one(a.w, t3.x, t3.y, t3.z, t3.w, za.w, qv.w, bk.w, upper, identity, has_bias, eps, o.w, sb, sa, sp);
+        if (!identity) *(float4 *)(row + j) = o;
+    }
+    double da = (double)sa, dp = (double)sp;
+    sb = warp_sum(sb); da = warp_sum(da); dp = warp_sum(dp);
+    if (lane == 0) { rb[m] += sb; rabs[m] += da * 1.0000001; rpen[m] += dp * 1.0000001; }
 }
 
 // ---------------------------------------------------------------- binary64-accumulated contraction
@@ -399,7 +480,7 @@ k_select_branch(NetView nv, int D, const float *__restrict__ pre_lo, const float
     float best = -1.f;
     int bidx = 0x7fffffff;
     for (int i = lane; i < n_hidden; i += 32) {
-        long o = (long)d * nv.n_pre + i;
+        long o = (long)d * nv.nps + i;
         float l = pre_lo[o], u = pre_hi[o];
         if (l >= 0.f || u <= 0.f || code[o] != 0) continue;
         float w = u - l;
@@ -451,12 +532,13 @@ void launch_ibp_linear(nyb200_engine *e, const NetView &nv, int k, int Deff, con
 void launch_ibp_finish(nyb200_engine *e, const NetView &nv, int k, int D, int mode, const float *raw_lo,
                        const float *raw_hi, long raw_dstride, const float *inh_lo, const float *inh_hi,
                        const signed char *code, const float *sbeta, const float *alpha, float *pre_lo, float *pre_hi,
-                       float *zl, float *zu, float4 *tab, float *zabs, int *flags) {
+                       float *zl, float *zu, float4 *tab, float *zabs, int *flags, const float *F, int ldf, double eps,
+                       float *q) {
     long total = (long)D * nv.dims[k + 1];
     int last = (k == nv.L - 1);
     k_ibp_finish<<<(unsigned)((total + 255) / 256), 256, 0, e->stream>>>(nv, k, D, mode, last, raw_lo, raw_hi, raw_dstride,
                                                                          inh_lo, inh_hi, code, sbeta, alpha, pre_lo,
-                                                                         pre_hi, zl, zu, tab, zabs, flags);
+                                                                         pre_hi, zl, zu, tab, zabs, flags, F, ldf, eps, q);
     NYB_COUNT(e);
 }
 
@@ -471,9 +553,15 @@ void launch_relax(nyb200_engine *e, const NetView &nv, int r, int lin_k, int M, 
                   double *rabs, double *rpen) {
     int n = nv.dims[lin_k + 1], off = nv.pre_off[lin_k];
     long threads = (long)M * 32;
-    k_relax<<<(unsigned)((threads + 255) / 256), 256, 0, e->stream>>>(n, off, M, R, S, nv.n_pre, r < 0 ? 1 : 0, A, lda, tab,
-                                                                      zabs, q, q_dstride, nv.b[lin_k], eps_gemm, rb,
-                                                                      rabs, rpen);
+    unsigned grid = (unsigned)((threads + 255) / 256);
+    bool aligned = (n % 4 == 0) && (off % 4 == 0) && (lda % 4 == 0) && (nv.nps % 4 == 0) && (q_dstride % 4 == 0) &&
+                   ((reinterpret_cast<uintptr_t>(A) & 15) == 0);
+    if (aligned)
+        k_relax_v4<<<grid, 256, 0, e->stream>>>(n, off, M, R, S, (long)nv.nps, r < 0 ? 1 : 0, A, lda, tab, zabs, q, q_dstride,
+                                                nv.b[lin_k], (float)(eps_gemm * 1.0000002), rb, rabs, rpen);
+    else
+        k_relax<<<grid, 256, 0, e->stream>>>(n, off, M, R, S, nv.nps, r < 0 ? 1 : 0, A, lda, tab, zabs, q, q_dstride,
+                                             nv.b[lin_k], eps_gemm, rb, rabs, rpen);
     NYB_COUNT(e);
 }
 

@@ -2,17 +2,20 @@
 // computed as three TF32 tensor-core products on split operands (A = Ah + Al, W = Wh + Wl;
 // Ah*Wh + Ah*Wl + Al*Wh) with fp32 accumulators in tensor memory.
 //
-// Layout of one CTA (persistent, one per SM, 384 threads):
+// Layout of one CTA (persistent, one per SM, 512 threads, register budget re-split with setmaxnreg):
 //   warp 0      TMA producer: streams the pre-split, pre-transposed weight tiles Wh^T, Wl^T
 //               (K-major, 128-byte swizzle) into shared memory, one 32-wide K chunk per stage.
 //   warp 1      MMA issuer: one elected thread issues tcgen05.mma (M=128, N=256, K=8, kind::tf32),
-//               commits each stage back to the producers and each finished tile to the epilogue.
+//               commits each stage back to the producers and each finished chunk to the epilogue.
 //   warp 2      allocates / frees the 512 tensor-memory columns (two 128x256 fp32 accumulators).
-//   warps 4-7   epilogue: tcgen05.ld the accumulator (one TMEM lane = one output row per thread)
-//               and store the fp32 rows to global memory; overlaps the next tile's MMAs.
-//   warps 8-11  A producers: each thread owns one row of the 128-row tile, loads 32 fp32 of it,
-//               splits every value into TF32 high and low parts and writes both to shared memory
-//               in the swizzled K-major layout the tensor core reads.
+//   warps 4-11  epilogue: a K range is accumulated in tensor memory only over a short chain
+//               (CHUNK_STAGES stages = 12 MMA steps); each finished chunk is read with tcgen05.ld (one
+//               TMEM lane = one output row per thread, 128 columns per warp) and added in fp32
+//               registers, alternating between the two accumulators so that the drain of one chunk
+//               overlaps the MMAs of the next; the row sums are stored after the last chunk.
+//   warps 12-15 A producers: each thread owns one row of the 128-row tile, loads 32 fp32 of it
+//               (prefetched one stage ahead), splits every value into TF32 high and low parts and
+//               writes both to shared memory in the swizzled K-major layout the tensor core reads.
 // Every wait on an mbarrier is bounded; on expiry the kernel records an error code, stops issuing
 // work, frees its tensor memory and returns.
 //
@@ -21,7 +24,11 @@
 //   (same for W), the product Al*Wl (<= 2^-22 |A||W|) is dropped: total <= 0.75 * 2^-20 |A||W|;
 //   accumulation: each tcgen05.mma step adds 8 exact products to the fp32 accumulator; the model
 //   assumes the step's error is at most one fp32 ulp of the magnitude sum accumulated so far
-//   (truncating adder), i.e. <= 2^-23 * S per step, so a chain of n steps is within n * 2^-23 * S.
+//   (truncating adder), i.e. <= 2^-23 * (accumulated magnitude) per step.  Inside a chain the eight
+//   cross-term steps are issued first, while the accumulator holds only terms of size 2^-10 S, so they
+//   cost 8 * 2^-33 S; the four Ah*Wh steps cost 4 * 2^-23 S.  The chunk sums are added in
+//   round-to-nearest fp32 (2^-24 * S each).  Keeping the full-scale chain at 4 steps instead of
+//   12 * K/32 is what keeps the certified bounds within 1e-4 of the binary64 path.
 #include <cuda.h>
 
 #include "nyb200_internal.cuh"
@@ -35,7 +42,8 @@ constexpr int A_BYTES = BM * BK * 4;   // 16 KB per half
 constexpr int B_BYTES = BN * BK * 4;   // 32 KB per half
 constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
-constexpr int THREADS = 384;
+constexpr int THREADS = 512;
+constexpr int CHUNK_STAGES = 1;  // K stages (of 32) accumulated in one tensor-memory chain
 constexpr unsigned SPIN_LIMIT = 1u << 24;
 
 __device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -117,6 +125,17 @@ __device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
         : "memory");
 }
 
+__device__ __forceinline__ float nudge_up(float x) {  // next fp32 toward +inf (finite x)
+    unsigned b = __float_as_uint(x);
+    if ((b & 0x7fffffffu) == 0) return __uint_as_float(1u);
+    return (b & 0x80000000u) ? __uint_as_float(b - 1) : __uint_as_float(b + 1);
+}
+__device__ __forceinline__ float nudge_down(float x) {  // next fp32 toward -inf (finite x)
+    unsigned b = __float_as_uint(x);
+    if ((b & 0x7fffffffu) == 0) return __uint_as_float(0x80000001u);
+    return (b & 0x80000000u) ? __uint_as_float(b + 1) : __uint_as_float(b - 1);
+}
+
 // Round an fp32 value to the nearest TF32 value (10 explicit mantissa bits); ties away from zero.
 __device__ __forceinline__ float rn_tf32(float x) {
     unsigned b = __float_as_uint(x);
@@ -146,7 +165,7 @@ __global__ void k_split_weights(const float *__restrict__ W, int K, int N, int K
 __global__ void __launch_bounds__(THREADS, 1)
 k_umma_tf32x3(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__ CUtensorMap tm_lo,
               const float *__restrict__ A, int lda, float *__restrict__ C, int ldc, int M, int N, int K,
-              int *__restrict__ err) {
+              int chunk_stages, int *__restrict__ err, const UmmaRelax rx) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned long long *bars = (unsigned long long *)(smem + STAGES * STAGE_BYTES);
@@ -159,6 +178,7 @@ k_umma_tf32x3(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__
     int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
     int total_tiles = m_tiles * n_tiles;
     int k_stages = (K + BK - 1) / BK;
+    int n_chunks = (k_stages + chunk_stages - 1) / chunk_stages;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -168,7 +188,7 @@ k_umma_tf32x3(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&bars[ACC_FULL + b]), 1);
-            mbar_init(smem_u32(&bars[ACC_EMPTY + b]), 128);
+            mbar_init(smem_u32(&bars[ACC_EMPTY + b]), 256);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -182,9 +202,10 @@ k_umma_tf32x3(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     unsigned tmem_base = *tmem_slot;
 
-    if (warp == 0) {
-        // ---------------------------------------------------------------- weight producer (TMA)
-        if (lane == 0) {
+    if (warp < 4) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+        if (warp == 0 && lane == 0) {
+            // ------------------------------------------------------------ weight producer (TMA)
             unsigned it = 0;
             for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
                 int tn = t % n_tiles;
@@ -199,118 +220,197 @@ k_umma_tf32x3(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__
                     tma_load_2d(smem_u32(st + 2 * A_BYTES + B_BYTES), &tm_lo, ks * BK, tn * BN, bar);
                 }
             }
-        }
-    } else if (warp == 1) {
-        // ---------------------------------------------------------------- MMA issuer
-        if (lane == 0) {
+        } else if (warp == 1 && lane == 0) {
+            // ------------------------------------------------------------ MMA issuer
             unsigned idesc = make_idesc(BM, BN);
-            unsigned it = 0, tile_it = 0;
-            for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x, ++tile_it) {
-                int buf = tile_it & 1;
-                unsigned aph = (tile_it >> 1) & 1;
-                if (!mbar_wait(smem_u32(&bars[ACC_EMPTY + buf]), aph ^ 1)) { atomicExch(err, 2); *abort_flag = 1; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                unsigned d_tmem = tmem_base + (unsigned)(buf * BN);
-                bool failed = false;
-                for (int ks = 0; ks < k_stages; ++ks, ++it) {
-                    int s = it % STAGES;
-                    unsigned ph = (it / STAGES) & 1;
-                    if (!mbar_wait(smem_u32(&bars[FULL_A + s]), ph) || !mbar_wait(smem_u32(&bars[FULL_B + s]), ph)) {
-                        atomicExch(err, 3); *abort_flag = 1; failed = true; break;
-                    }
+            unsigned it = 0, chunk_it = 0;
+            bool failed = false;
+            for (int t = blockIdx.x; t < total_tiles && !*abort_flag && !failed; t += gridDim.x) {
+                for (int ch = 0; ch < n_chunks && !failed; ++ch, ++chunk_it) {
+                    int buf = chunk_it & 1;
+                    unsigned aph = (chunk_it >> 1) & 1;
+                    if (!mbar_wait(smem_u32(&bars[ACC_EMPTY + buf]), aph ^ 1)) { atomicExch(err, 2); *abort_flag = 1; failed = true; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    unsigned char *st = smem + s * STAGE_BYTES;
-                    unsigned long long a_hi = make_desc(smem_u32(st)), a_lo = make_desc(smem_u32(st + A_BYTES));
-                    unsigned long long b_hi = make_desc(smem_u32(st + 2 * A_BYTES));
-                    unsigned long long b_lo = make_desc(smem_u32(st + 2 * A_BYTES + B_BYTES));
+                    unsigned d_tmem = tmem_base + (unsigned)(buf * BN);
+                    int ks_end = min(k_stages, (ch + 1) * chunk_stages);
+                    for (int ks = ch * chunk_stages; ks < ks_end; ++ks, ++it) {
+                        int s = it % STAGES;
+                        unsigned ph = (it / STAGES) & 1;
+                        if (!mbar_wait(smem_u32(&bars[FULL_A + s]), ph) || !mbar_wait(smem_u32(&bars[FULL_B + s]), ph)) {
+                            atomicExch(err, 3); *abort_flag = 1; failed = true; break;
+                        }
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        unsigned char *st = smem + s * STAGE_BYTES;
+                        unsigned long long a_hi = make_desc(smem_u32(st)), a_lo = make_desc(smem_u32(st + A_BYTES));
+                        unsigned long long b_hi = make_desc(smem_u32(st + 2 * A_BYTES));
+                        unsigned long long b_lo = make_desc(smem_u32(st + 2 * A_BYTES + B_BYTES));
+                        // Small products first: the eight cross-term steps (|Al*Wh|, |Ah*Wl| <= 2^-10 |A||W|)
+                        // run while the accumulator is still small, so only the four Ah*Wh steps round at
+                        // the scale of S.
+                        bool first = (ks == ch * chunk_stages);
 #pragma unroll
-                    for (int k4 = 0; k4 < BK / 8; ++k4) {
-                        unsigned long long adv = (unsigned long long)(k4 * 2);  // 8 TF32 = 32 bytes = 2 x 16 B
-                        unsigned acc0 = (ks > 0 || k4 > 0) ? 1u : 0u;
-                        mma_tf32(d_tmem, a_lo + adv, b_hi + adv, idesc, acc0);
-                        mma_tf32(d_tmem, a_hi + adv, b_lo + adv, idesc, 1u);
-                        mma_tf32(d_tmem, a_hi + adv, b_hi + adv, idesc, 1u);
+                        for (int k4 = 0; k4 < BK / 8; ++k4) {
+                            unsigned long long adv = (unsigned long long)(k4 * 2);  // 8 TF32 = 32 bytes = 2 x 16 B
+                            mma_tf32(d_tmem, a_lo + adv, b_hi + adv, idesc, (first && k4 == 0) ? 0u : 1u);
+                            mma_tf32(d_tmem, a_hi + adv, b_lo + adv, idesc, 1u);
+                        }
+#pragma unroll
+                        for (int k4 = 0; k4 < BK / 8; ++k4) {
+                            unsigned long long adv = (unsigned long long)(k4 * 2);
+                            mma_tf32(d_tmem, a_hi + adv, b_hi + adv, idesc, 1u);
+                        }
+                        mma_commit(smem_u32(&bars[EMPTY + s]));
                     }
-                    mma_commit(smem_u32(&bars[EMPTY + s]));
-                }
-                if (failed) break;
-                mma_commit(smem_u32(&bars[ACC_FULL + buf]));
-            }
-        }
-    } else if (warp >= 4 && warp < 8) {
-        // ---------------------------------------------------------------- epilogue
-        int q = warp & 3;
-        unsigned tile_it = 0;
-        for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++tile_it) {
-            int tm = t / n_tiles, tn = t % n_tiles;
-            int buf = tile_it & 1;
-            unsigned aph = (tile_it >> 1) & 1;
-            bool ok = mbar_wait(smem_u32(&bars[ACC_FULL + buf]), aph);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) { if (lane == 0) { atomicExch(err, 4); *abort_flag = 1; } break; }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            int row = tm * BM + q * 32 + lane;
-            float *crow = C + (long)row * ldc + tn * BN;
-            int ncols = min(BN, N - tn * BN);
-#pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
-                unsigned r[32];
-                unsigned taddr = tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)(buf * BN + c);
-                tmem_ld32(taddr, r);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (row < M && c < ncols) {
-                    if (c + 32 <= ncols && ((ldc & 3) == 0)) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4)
-                            *(float4 *)(crow + c + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                                                     __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) if (c + j < ncols) crow[c + j] = __uint_as_float(r[j]);
-                    }
+                    if (!failed) mma_commit(smem_u32(&bars[ACC_FULL + buf]));
                 }
             }
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(smem_u32(&bars[ACC_EMPTY + buf]));
         }
-    } else if (warp >= 8) {
-        // ---------------------------------------------------------------- A producers (split to TF32 hi/lo)
-        int r = threadIdx.x - 256;  // row of the tile owned by this thread
-        unsigned it = 0;
+    } else if (warp < 12) {
+        // ---------------------------------------------------------------- epilogue (8 warps)
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 184;");
+        int q = warp & 3, half = (warp - 4) >> 2;
+        unsigned chunk_it = 0;
         bool dead = false;
         for (int t = blockIdx.x; t < total_tiles && !dead; t += gridDim.x) {
-            int tm = t / n_tiles;
-            int row = tm * BM + r;
+            int tm = t / n_tiles, tn = t % n_tiles;
+            float sum[128];
+#pragma unroll
+            for (int j = 0; j < 128; ++j) sum[j] = 0.f;
+            for (int ch = 0; ch < n_chunks; ++ch, ++chunk_it) {
+                int buf = chunk_it & 1;
+                unsigned aph = (chunk_it >> 1) & 1;
+                bool ok = mbar_wait(smem_u32(&bars[ACC_FULL + buf]), aph);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) { if (lane == 0) { atomicExch(err, 4); *abort_flag = 1; } dead = true; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (int c = 0; c < 128; c += 32) {
+                    unsigned r[32];
+                    unsigned taddr = tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)(buf * BN + half * 128 + c);
+                    tmem_ld32(taddr, r);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) sum[c + j] += __uint_as_float(r[j]);
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                mbar_arrive(smem_u32(&bars[ACC_EMPTY + buf]));
+            }
+            if (dead) break;
+            int row = tm * BM + q * 32 + lane;
+            int col0 = tn * BN + half * 128;
+            int ncols = min(128, N - col0);
+            if (row < M && ncols > 0) {
+                float *crow = C + (long)row * ldc + col0;
+                if (ncols == 128 && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0)) {
+#pragma unroll
+                    for (int j = 0; j < 128; j += 4) *(float4 *)(crow + j) = make_float4(sum[j], sum[j + 1], sum[j + 2], sum[j + 3]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 128; ++j) if (j < ncols) crow[j] = sum[j];
+                }
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- A producers (split to TF32 hi/lo)
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
+        int r = threadIdx.x - 384;  // row of the tile owned by this thread
+        unsigned it = 0;
+        bool dead = false;
+        float4 v[8];
+        auto load_stage = [&](int t, int ks) {
+            int row = (t / n_tiles) * BM + r;
             const float *arow = A + (long)row * lda;
+            int k0 = ks * BK;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                int k = k0 + c * 4;
+                float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (row < M) {
+                    if (k + 3 < K && ((reinterpret_cast<uintptr_t>(arow + k) & 15) == 0)) x = *(const float4 *)(arow + k);
+                    else {
+                        if (k < K) x.x = arow[k];
+                        if (k + 1 < K) x.y = arow[k + 1];
+                        if (k + 2 < K) x.z = arow[k + 2];
+                        if (k + 3 < K) x.w = arow[k + 3];
+                    }
+                }
+                v[c] = x;
+            }
+        };
+        if ((int)blockIdx.x < total_tiles) load_stage(blockIdx.x, 0);
+        for (int t = blockIdx.x; t < total_tiles && !dead; t += gridDim.x) {
+            const int row = (t / n_tiles) * BM + r;
+            const bool sums = (rx.mode != 0) && (t % n_tiles == 0) && row < M;
+            const int dom = row / rx.R;
+            const bool upper = (row % rx.R) >= rx.S;
+            const long tbase = (long)dom * rx.nps + rx.off;      // index of this domain's block in tab / zabs
+            const long qbase = (long)dom * rx.q_ds + rx.off;
+            double sb = 0.0;
+            float sa = 0.f, sp = 0.f;
             for (int ks = 0; ks < k_stages; ++ks, ++it) {
                 int s = it % STAGES;
                 unsigned ph = (it / STAGES) & 1;
                 if (!mbar_wait(smem_u32(&bars[EMPTY + s]), ph ^ 1)) { atomicExch(err, 5); *abort_flag = 1; dead = true; break; }
                 unsigned char *st = smem + s * STAGE_BYTES;
                 float *ah = (float *)st, *al = (float *)(st + A_BYTES);
-                int k0 = ks * BK;
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
-                    float v[4] = {0.f, 0.f, 0.f, 0.f};
-                    int k = k0 + c * 4;
-                    if (row < M) {
-                        if (k + 3 < K && ((lda & 3) == 0)) {
-                            float4 x = *(const float4 *)(arow + k);
-                            v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
-                        } else {
+                    float xs[4] = {v[c].x, v[c].y, v[c].z, v[c].w};
+                    if (rx.mode != 0 && row < M) {
+                        int k = ks * BK + c * 4;
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) if (k + j < K) v[j] = arow[k + j];
+                        for (int j = 0; j < 4; ++j) {
+                            if (k + j >= K) continue;
+                            float a = xs[j], nw = a;
+                            if (rx.mode == 2) {
+                                // beta-CROWN ReLU step (crates/ny-propagate/src/beta_crown/engine/backward/
+                                // relu_backward.rs:105-175): sign-routed slope, product stepped one ulp outward,
+                                // intercept into the bias, signed beta subtracted (lower) / added (upper).
+                                float4 tb = rx.tab[tbase + k + j];
+                                float slope = 0.f, icp = 0.f;
+                                if (a > 0.f) { slope = upper ? tb.y : tb.x; icp = upper ? tb.z : 0.f; }
+                                else if (a < 0.f) { slope = upper ? tb.x : tb.y; icp = upper ? 0.f : tb.z; }
+                                if (a == 0.f || slope == 0.f) nw = 0.f;  // exact product: no outward step needed
+                                else {
+                                    float pr = a * slope;
+                                    nw = upper ? nudge_up(pr) : nudge_down(pr);
+                                    if (sums) {
+                                        // |a*slope - nw| to one rounding, inflated, times the pre-activation magnitude
+                                        float gap = __fmul_ru(fabsf(fmaf(a, slope, -nw)), 1.000001f);
+                                        sp = __fmaf_ru(gap, rx.zabs[tbase + k + j], sp);
+                                    }
+                                }
+                                if (sums && icp != 0.f) { sb += (double)a * (double)icp; sa = __fmaf_ru(fabsf(a), fabsf(icp), sa); }
+                                if (tb.w != 0.f) nw = upper ? nw + tb.w : nw - tb.w;
+                                xs[j] = nw;
+                            }
+                            if (sums) {
+                                if (rx.bias_k) {
+                                    float bk = rx.bias_k[k + j];
+                                    sb += (double)nw * (double)bk;
+                                    sa = __fmaf_ru(fabsf(nw), fabsf(bk), sa);
+                                }
+                                sp = __fmaf_ru(__fmul_ru(rx.eps, fabsf(nw)), rx.q[qbase + k + j], sp);
+                            }
                         }
                     }
-                    float h[4], l[4];
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) { h[j] = rn_tf32(v[j]); l[j] = rn_tf32(v[j] - h[j]); }
+                    float4 h = make_float4(rn_tf32(xs[0]), rn_tf32(xs[1]), rn_tf32(xs[2]), rn_tf32(xs[3]));
+                    float4 l = make_float4(rn_tf32(xs[0] - h.x), rn_tf32(xs[1] - h.y), rn_tf32(xs[2] - h.z), rn_tf32(xs[3] - h.w));
                     int off = r * 32 + ((c ^ (r & 7)) << 2);  // in floats: row * 128 B + swizzled 16 B chunk
-                    *(float4 *)(ah + off) = make_float4(h[0], h[1], h[2], h[3]);
-                    *(float4 *)(al + off) = make_float4(l[0], l[1], l[2], l[3]);
+                    *(float4 *)(ah + off) = h;
+                    *(float4 *)(al + off) = l;
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 mbar_arrive(smem_u32(&bars[FULL_A + s]));
+                // prefetch the next stage's row segment while the tensor core works on this one
+                int nks = ks + 1, nt = t;
+                if (nks == k_stages) { nks = 0; nt = t + gridDim.x; }
+                if (nt < total_tiles) load_stage(nt, nks);
+            }
+            if (sums && !dead) {  // one writer per row: only the CTA holding column tile 0 of this row tile
+                rx.rb[row] += sb;
+                rx.rabs[row] += (double)sa;
+                rx.rpen[row] += (double)sp;
             }
         }
     }
@@ -366,7 +466,10 @@ int umma_prepare_layer(nyb200_engine *e, const float *W, int K, int N, UmmaLayer
     return NYB200_OK;
 }
 
-int launch_umma(nyb200_engine *e, const UmmaLayer &L, int M, const float *A, int lda, float *C, int ldc, int *err) {
+int launch_umma(nyb200_engine *e, const UmmaLayer &L, int M, const float *A, int lda, float *C, int ldc, int *err,
+                const UmmaRelax *relax) {
+    UmmaRelax rx;
+    if (relax) rx = *relax;
     static bool attr_set = false;
     if (!attr_set) {
         if (cudaFuncSetAttribute(k_umma_tf32x3, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
@@ -378,15 +481,75 @@ int launch_umma(nyb200_engine *e, const UmmaLayer &L, int M, const float *A, int
     int tiles = ((M + BM - 1) / BM) * ((L.N + BN - 1) / BN);
     int grid = tiles < sms ? tiles : sms;
     k_umma_tf32x3<<<grid, THREADS, SMEM_BYTES, e->stream>>>(*(const CUtensorMap *)L.tm_hi, *(const CUtensorMap *)L.tm_lo, A,
-                                                            lda, C, ldc, M, L.N, L.K, err);
+                                                            lda, C, ldc, M, L.N, L.K, CHUNK_STAGES, err, rx);
     e->launches++;
     return NYB200_OK;
 }
 
+// (W+^T | W-^T) as a row-major [n_in x 2 n_out] matrix from W [n_out x n_in].
+__global__ void k_build_wpm(const float *__restrict__ W, int n_in, int n_out, float *__restrict__ out) {
+    long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= (long)n_in * 2 * n_out) return;
+    int k = (int)(t / (2 * n_out)), n = (int)(t % (2 * n_out));
+    float w = W[(long)(n % n_out) * n_in + k];
+    out[t] = (n < n_out) ? fmaxf(w, 0.f) : fminf(w, 0.f);
+}
+
+int umma_prepare_forward_layer(nyb200_engine *e, const float *W, int n_in, int n_out, UmmaLayer *out) {
+    float *tmp = nullptr;
+    size_t n = (size_t)n_in * 2 * n_out;
+    if (cudaMalloc(&tmp, n * 4) != cudaSuccess) return NYB200_ERR_OOM;
+    k_build_wpm<<<(unsigned)((n + 255) / 256), 256, 0, e->stream>>>(W, n_in, n_out, tmp);
+    e->launches++;
+    int st = umma_prepare_layer(e, tmp, n_in, 2 * n_out, out);
+    cudaStreamSynchronize(e->stream);
+    cudaFree(tmp);
+    return st;
+}
+
+// Interval bounds of Linear_k from Fl = zl (W+|W-) and Fu = zu (W+|W-), valid for 0 <= zl <= zu:
+// lo = W+ zl + W- zu + b, hi = W+ zu + W- zl + b, q = |W| zu = W+ zu - W- zu.  Every product carries a
+// rounding of at most eps times the sum of its own term magnitudes, each of which is bounded by q, so
+// both ends move outward by eps * q (q itself inflated by its own relative error) before the directed cast.
+__global__ void k_ibp_combine(int D, int n_out, const float *__restrict__ Fl, const float *__restrict__ Fu, int ldf,
+                              const float *__restrict__ bias, double eps, float *__restrict__ raw_lo,
+                              float *__restrict__ raw_hi, float *__restrict__ q, long out_ds) {
+    long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= (long)D * n_out) return;
+    int d = (int)(t / n_out), o = (int)(t % n_out);
+    double pl = Fl[(long)d * ldf + o], nl = Fl[(long)d * ldf + n_out + o];
+    double pu = Fu[(long)d * ldf + o], nu = Fu[(long)d * ldf + n_out + o];
+    double b = bias ? (double)bias[o] : 0.0;
+    double qq = (fabs(pu) + fabs(nu)) / (1.0 - 2.0 * eps);
+    double slack = eps * qq + 2.3e-16 * (qq + fabs(b));
+    float lf = __double2float_rd(pl + nu + b - slack);
+    float hf = __double2float_ru(pu + nl + b + slack);
+    if (isnan(lf) || isnan(hf)) { lf = -INFINITY; hf = INFINITY; }
+    raw_lo[(long)d * out_ds + o] = lf;
+    raw_hi[(long)d * out_ds + o] = hf;
+    q[(long)d * out_ds + o] = __double2float_ru(qq);
+}
+
+void launch_ibp_combine(nyb200_engine *e, int D, int n_out, const float *Fl, const float *Fu, int ldf, const float *bias,
+                        double eps, float *raw_lo, float *raw_hi, float *q, long out_ds) {
+    long total = (long)D * n_out;
+    k_ibp_combine<<<(unsigned)((total + 255) / 256), 256, 0, e->stream>>>(D, n_out, Fl, Fu, ldf, bias, eps, raw_lo, raw_hi, q,
+                                                                          out_ds);
+    e->launches++;
+}
+
 // Worst-case relative rounding of this kernel's product against S = |A||W| (see the model above).
 double umma_eps(int K) {
-    int steps = ((K + BK - 1) / BK) * (BK / 8) * 3;
-    return 0.75 * 9.5367431640625e-07 /* 2^-20 */ + (double)steps * 1.1920928955078125e-07 /* 2^-23 */;
+    int k_stages = (K + BK - 1) / BK;
+    int cs = k_stages < CHUNK_STAGES ? k_stages : CHUNK_STAGES;
+    int chunks = (k_stages + CHUNK_STAGES - 1) / CHUNK_STAGES;
+    const double u23 = 1.1920928955078125e-07, u24 = 5.9604644775390625e-08;
+    double rep = 0.75 * 9.5367431640625e-07;                    // operand split, 0.75 * 2^-20
+    double chain_main = (double)(cs * (BK / 8)) * u23;          // Ah*Wh steps round at the scale of S
+    // the cross-term steps of the first stage meet an accumulator of size 2^-10 S; with more than one
+    // stage per chain those of later stages meet a full-size accumulator
+    double chain_cross = (double)((BK / 8) * 2) * u23 * (cs > 1 ? (double)cs : 9.765625e-04 /* 2^-10 */);
+    return rep + chain_main + chain_cross + (double)chunks * u24;
 }
 
 }  // namespace nyb

@@ -19,8 +19,10 @@ def eng():
 
 
 def _umma_eps(K):
-    steps = ((K + 31) // 32) * 4 * 3
-    return 0.75 * 2.0 ** -20 + steps * 2.0 ** -23
+    # rounding model of the kernel: operand split + 4 full-scale and 8 small tensor-memory steps per
+    # 32-wide K chunk + fp32 chunk sums
+    chunks = (K + 31) // 32
+    return 0.75 * 2.0 ** -20 + 4 * 2.0 ** -23 + 8 * 2.0 ** -33 + chunks * 2.0 ** -24
 
 
 @pytest.mark.parametrize("m,k,n", [(128, 32, 256), (128, 256, 256), (300, 256, 256), (1000, 10, 256),
@@ -77,4 +79,41 @@ def test_batch_on_tensor_path_matches_oracle(eng, oracle):
         mn = W.sample_min_margin(wl, 20000, 900 + d, splits[d][: ns[d]])
         ok = np.isfinite(mn)
         assert np.all(glo[d][ok] <= mn[ok])
+    eng.release_network(nid)
+
+
+def test_full_size_batch_on_tensor_path(eng, oracle):
+    """Benchmark configuration (784 -> 8x256 -> 10, 4096 domains) on the tcgen05 path: parity with the
+    oracle on a 32-domain sample, agreement with the binary64 device path, soundness on one domain."""
+    from ny_b200 import B200Engine
+    from tests.test_gpu_parity import REL_TOL, _oracle_batch, _rel
+
+    wl = W.config_mlp_bab()
+    nid = eng.register_network(wl.net)
+    pl, pu = eng.ibp_forward_gpu(nid, wl.in_lo, wl.in_hi)
+    rl, ru = pl[0], pu[0]
+    D = 4096
+    splits, ns = W.draw_domains(wl, rl, ru, D)
+    lo, hi, inf = eng.bab_bound_batch(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, splits, ns, mode=1)
+    lo2, hi2, _ = eng.bab_bound_batch(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, splits, ns, mode=1)
+    assert np.array_equal(lo, lo2) and np.array_equal(hi, hi2)
+    ref = B200Engine(0)  # binary64 path
+    rid = ref.register_network(wl.net)
+    flo, fhi, finf = ref.bab_bound_batch(rid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, splits, ns, mode=1)
+    ref.close()
+    assert np.array_equal(inf, finf)
+    feas = inf == 0
+    dev64 = _rel(np.concatenate([lo, hi], 1)[feas], np.concatenate([flo, fhi], 1)[feas])
+    onet = oracle.Net(wl.net.weights, wl.net.biases)
+    sel = np.arange(0, D, D // 32)
+    olo, ohi, oinf, _ = _oracle_batch(oracle, onet.with_spec(wl.spec), wl, rl, ru, splits[sel], ns[sel], 1)
+    f = ~oinf.astype(bool)
+    dev = _rel(np.concatenate([lo, hi], 1)[sel][f], np.concatenate([olo, ohi], 1)[f])
+    print("full-size tensor path: deviation vs binary64 device path", dev64, "vs oracle", dev)
+    assert dev <= REL_TOL
+    assert np.all(lo[feas] <= flo[feas] + 1e-6 * np.abs(flo[feas]).max(axis=1, keepdims=True))
+    d = int(np.flatnonzero(feas)[0])
+    mn = W.sample_min_margin(wl, 100000, 77, splits[d][: ns[d]])
+    ok = np.isfinite(mn)
+    assert np.all(lo[d][ok] <= mn[ok])
     eng.release_network(nid)
