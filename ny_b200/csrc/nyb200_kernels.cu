@@ -134,6 +134,35 @@ k_ibp_linear(int Deff, int n_in, int n_out, const float *__restrict__ W, const f
     }
 }
 
+// Same arithmetic for a single box (the shared input box of the first layer): one warp per output
+// neuron, lanes stride over the inputs, binary64 partial sums reduced with shuffles.
+__global__ void __launch_bounds__(256)
+k_ibp_linear_vec(int n_in, int n_out, const float *__restrict__ W, const float *__restrict__ bias,
+                 const float *__restrict__ zl, const float *__restrict__ zu, float *__restrict__ raw_lo,
+                 float *__restrict__ raw_hi, float *__restrict__ q) {
+    int o = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (o >= n_out) return;
+    const float *w = W + (long)o * n_in;
+    double lo = 0.0, hi = 0.0, qq = 0.0;
+    for (int i = lane; i < n_in; i += 32) {
+        double wv = w[i], a = zl[i], b = zu[i];
+        bool pos = wv > 0.0;
+        lo = fma(wv, pos ? a : b, lo);
+        hi = fma(wv, pos ? b : a, hi);
+        qq = fma(fabs(wv), fmax(fabs(a), fabs(b)), qq);
+    }
+    lo = warp_sum(lo); hi = warp_sum(hi); qq = warp_sum(qq);
+    if (lane == 0) {
+        const double gam = (double)(n_in + 2) * 1.1102230246251565e-16 * 1.000001;
+        double bv = bias ? (double)bias[o] : 0.0;
+        double slack = gam * (qq + fabs(bv));
+        float lf = __double2float_rd(lo + bv - slack), hf = __double2float_ru(hi + bv + slack);
+        if (isnan(lf) || isnan(hf)) { lf = -INFINITY; hf = INFINITY; }
+        raw_lo[o] = lf; raw_hi[o] = hf;
+        q[o] = __double2float_ru(qq * (1.0 + gam));
+    }
+}
+
 // ---------------------------------------------------------------- per-domain finish of a Linear output
 // mode 0: bounds = inherited (clamp only: beta_crown/engine/domain/child.rs:51-118);
 // mode 1: bounds = re-propagated intersected with inherited (graph/propagation/constraints/mod.rs:738-741);
@@ -300,7 +329,7 @@ __device__ __forceinline__ void relax_one(float a, float ls, float us, float ui,
     nw_out = nw;
 }
 
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)
 k_relax_v4(int n, int off, int M, int R, int S, long nps, int identity, float *__restrict__ A, int lda,
            const float4 *__restrict__ tab, const float *__restrict__ zabs, const float *__restrict__ q, long q_ds,
            const float *__restrict__ bias_k, float eps, double *__restrict__ rb, double *__restrict__ rabs,
@@ -332,7 +361,11 @@ k_relax_v4(int n, int off, int M, int R, int S, long nps, int identity, float *_
     }
     double da = (double)sa, dp = (double)sp;
     sb = warp_sum(sb); da = warp_sum(da); dp = warp_sum(dp);
-    if (lane == 0) { rb[m] += sb; rabs[m] += da * 1.0000001; rpen[m] += dp * 1.0000001; }
+    if (lane == 0) {  // reductions without a dependent read: the row is owned by this warp for this launch
+        atomicAdd(&rb[m], sb);
+        atomicAdd(&rabs[m], da * 1.0000001);
+        atomicAdd(&rpen[m], dp * 1.0000001);
+    }
 }
 
 // ---------------------------------------------------------------- binary64-accumulated contraction
@@ -421,12 +454,23 @@ k_concretize(int M, int R, int S, int n0, const float *__restrict__ A, int lda, 
     const float *xl = in_lo + (long)d * box_ds, *xu = in_hi + (long)d * box_ds;
     double s = 0.0, sa = 0.0;
     bool bad = false;
-    for (int j = lane; j < n0; j += 32) {
-        float a = row[j];
+    auto term = [&](float a, float l, float u) {
         bool nonneg = !(__float_as_uint(a) >> 31) || (__float_as_uint(a) & 0x7fffffffu) == 0;
-        float x = (nonneg != upper) ? xl[j] : xu[j];
+        float x = (nonneg != upper) ? l : u;
         if (!(fabsf(a) < 1e10f)) bad = true;  // is_crown_coeff_safe, crates/ny-core/src/gemm.rs:127
         if (a != 0.f && x != 0.f) { double c = (double)a * (double)x; s += c; sa += fabs(c); }
+    };
+    const bool vec = (n0 % 4 == 0) && (lda % 4 == 0) && (box_ds % 4 == 0) &&
+                     (((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(in_lo) |
+                        reinterpret_cast<uintptr_t>(in_hi)) & 15) == 0);
+    if (vec) {
+#pragma unroll 4
+        for (int j = lane * 4; j < n0; j += 128) {
+            float4 a = *(const float4 *)(row + j), l = *(const float4 *)(xl + j), u = *(const float4 *)(xu + j);
+            term(a.x, l.x, u.x); term(a.y, l.y, u.y); term(a.z, l.z, u.z); term(a.w, l.w, u.w);
+        }
+    } else {
+        for (int j = lane; j < n0; j += 32) term(row[j], xl[j], xu[j]);
     }
     s = warp_sum(s); sa = warp_sum(sa);
     bad = __any_sync(0xffffffffu, bad);
@@ -522,6 +566,13 @@ void launch_scatter_splits(nyb200_engine *e, const NetView &nv, const nyb200_spl
 void launch_ibp_linear(nyb200_engine *e, const NetView &nv, int k, int Deff, const float *zl, const float *zu,
                        long in_dstride, float *raw_lo, float *raw_hi, float *q, long out_dstride) {
     int n_in = nv.dims[k], n_out = nv.dims[k + 1];
+    if (Deff == 1) {
+        k_ibp_linear_vec<<<(n_out * 32 + 255) / 256, 256, 0, e->stream>>>(n_in, n_out, nv.W[k], nv.b[k], zl, zu,
+                                                                         raw_lo + nv.pre_off[k], raw_hi + nv.pre_off[k],
+                                                                         q + nv.pre_off[k]);
+        NYB_COUNT(e);
+        return;
+    }
     dim3 grid((n_out + IB_N - 1) / IB_N, (Deff + IB_M - 1) / IB_M);
     k_ibp_linear<<<grid, 256, 0, e->stream>>>(Deff, n_in, n_out, nv.W[k], nv.b[k], zl, zu, in_dstride,
                                                raw_lo + nv.pre_off[k], raw_hi + nv.pre_off[k], q + nv.pre_off[k],
