@@ -255,7 +255,7 @@ int batch_ptrs(nyb200_engine *e, const Net &net, const Batch &b, BatchPtrs &p) {
     const NetView &nv = net.v;
     size_t D = (size_t)b.D, np = (size_t)nv.nps;
     size_t M = D * b.R;
-    p.lda = (net.max_dim + 3) & ~3;
+    p.lda = (net.max_dim + 7) & ~7;
     size_t box = (size_t)nv.dims[0] * (b.box_stride ? D : 1);
 #define GET(field, type, name, bytes)                                   \
     p.field = (type)ws_get(e, name, (bytes));                            \
@@ -317,7 +317,7 @@ int run_forward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int fw
         }
         int mo = 0;
         for (int k = 2; k <= nv.L; ++k) mo = nv.dims[k] > mo ? nv.dims[k] : mo;
-        ldf = (2 * mo + 3) & ~3;
+        ldf = (2 * mo + 7) & ~7;
         Fl = (float *)ws_get(e, "fwd", (size_t)2 * D * ldf * 4);
         derr = (int *)ws_get(e, "umma_err", 256);
         if (!Fl || !derr) return NYB200_ERR_OOM;
@@ -350,9 +350,6 @@ int run_forward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int fw
 int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p) {
     const NetView &nv = net.v;
     const bool tensor = (e->path == NYB200_PATH_TF32X3);
-    // The contraction kernel can apply the relaxation in its A producers (one kernel per layer), but with
-    // 128 producer threads per SM that is slower than a separate streaming pass; kept selectable.
-    static const bool fuse = getenv("NYB200_FUSE_RELAX") != nullptr;
     int *derr = nullptr;
     if (tensor) {
         if (net.umma.empty()) {
@@ -377,8 +374,7 @@ int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p) {
         return tensor ? umma_eps(K) * 1.000001 : (double)(K + 2) * 1.1102230246251565e-16 * 1.000001;
     };
     auto q_ds = [&](int lin_k) { return (lin_k == 0 && shared_box) ? 0L : np; };
-    if (!(tensor && fuse))
-        launch_relax(e, nv, -1, L - 1, M, R, S, cur, p.lda, p.tab, p.zabs, p.q, q_ds(L - 1), eps_for(nv.dims[L]), p.rb,
+    launch_relax(e, nv, -1, L - 1, M, R, S, cur, p.lda, p.tab, p.zabs, p.q, q_ds(L - 1), eps_for(nv.dims[L]), p.rb,
                      p.rabs, p.rpen);
     for (int k = L - 1; k >= 0; --k) {
         int K = nv.dims[k + 1], N = nv.dims[k];
@@ -388,20 +384,12 @@ int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p) {
         else { zin_lo = p.in_lo; zin_hi = p.in_hi; zin_ds = b.box_stride; }
         if (e->timing.per_kernel) cudaEventRecord(next_kev(e->timing), e->stream);
         if (tensor) {
-            // The relaxation of the incoming rows (ReLU k, or a pass-through for the seed rows) and the row
-            // sums this product owes are done by the kernel's A producers.
-            UmmaRelax rx;
-            rx.mode = !fuse ? 0 : (k == L - 1) ? 1 : 2;
-            rx.R = R; rx.S = S; rx.nps = np; rx.off = nv.pre_off[k]; rx.q_ds = q_ds(k);
-            rx.tab = p.tab; rx.zabs = p.zabs; rx.q = p.q; rx.bias_k = nv.b[k];
-            rx.eps = (float)(eps_for(K) * 1.0000002);
-            rx.rb = p.rb; rx.rabs = p.rabs; rx.rpen = p.rpen;
-            NYB_TRY(launch_umma(e, net.umma[k], M, cur, p.lda, nxt, p.lda, derr, &rx));
+            NYB_TRY(launch_umma(e, net.umma[k], M, cur, p.lda, nxt, p.lda, derr));
         } else {
             launch_gemm_f64(e, M, N, K, cur, p.lda, nv.W[k], N, nxt, p.lda, R, zin_lo, zin_hi, zin_ds, p.rpen);
         }
         if (e->timing.per_kernel) cudaEventRecord(next_kev(e->timing), e->stream);
-        if (k > 0 && !(tensor && fuse))
+        if (k > 0)
             launch_relax(e, nv, k - 1, k - 1, M, R, S, nxt, p.lda, p.tab, p.zabs, p.q, q_ds(k - 1), eps_for(N), p.rb, p.rabs,
                          p.rpen);
         float *t = cur; cur = nxt; nxt = t;

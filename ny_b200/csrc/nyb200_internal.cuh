@@ -121,25 +121,9 @@ void launch_select_branch(nyb200_engine *e, const NetView &nv, int D, const floa
                           const signed char *code, int *relu, int *neuron, float *width);
 void launch_fill_f64(nyb200_engine *e, double *p, size_t n, double v);
 
-// Optional work fused into the A-operand producers of the tcgen05 contraction: the ReLU relaxation of
-// the incoming coefficient rows (mode 2) or a pass-through (mode 1), plus the row sums the contraction
-// owes (bias += a'.bias_k, penalty += eps |a'| . q).  mode 0: plain product.
-struct UmmaRelax {
-    int mode = 0;
-    int R = 1, S = 1;          // rows per domain, spec rows (rows >= S of a domain are upper-bound rows)
-    long nps = 0;              // row stride of tab / zabs / q
-    int off = 0;               // column offset of this layer's block inside those rows
-    long q_ds = 0;             // domain stride of q (0 when the layer's q is shared by all domains)
-    const float4 *tab = nullptr;
-    const float *zabs = nullptr, *q = nullptr, *bias_k = nullptr;
-    float eps = 0.f;           // rounding of the contraction relative to |a'| . q, rounded up to fp32
-    double *rb = nullptr, *rabs = nullptr, *rpen = nullptr;
-};
-
 // ---- tcgen05 contraction (nyb200_umma.cu) ----
 int umma_prepare_layer(nyb200_engine *e, const float *W, int K, int N, UmmaLayer *out);
-int launch_umma(nyb200_engine *e, const UmmaLayer &L, int M, const float *A, int lda, float *C, int ldc, int *err,
-                const UmmaRelax *relax = nullptr);
+int launch_umma(nyb200_engine *e, const UmmaLayer &L, int M, const float *A, int lda, float *C, int ldc, int *err);
 double umma_eps(int K);
 // Builds the forward-pass operand of Linear_k: the [n_in x 2 n_out] matrix (W+^T | W-^T).
 int umma_prepare_forward_layer(nyb200_engine *e, const float *W, int n_in, int n_out, UmmaLayer *out);

@@ -31,6 +31,8 @@
 //   12 * K/32 is what keeps the certified bounds within 1e-4 of the binary64 path.
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "nyb200_internal.cuh"
 
 namespace nyb {
@@ -43,7 +45,16 @@ constexpr int B_BYTES = BN * BK * 4;   // 32 KB per half
 constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
 constexpr int THREADS = 512;
-constexpr int CHUNK_STAGES = 1;  // K stages (of 32) accumulated in one tensor-memory chain
+// K stages (of 32) accumulated in one tensor-memory chain before the chunk is drained (default 1;
+// NYB200_CHUNK_STAGES overrides it for experiments, the rounding model follows the value in use).
+static int dbg_cfg() {
+    static int v = [] { const char *s = getenv("NYB200_UMMA_DBG"); return s ? atoi(s) : 0; }();
+    return v;
+}
+static int chunk_stages_cfg() {
+    static int v = [] { const char *s = getenv("NYB200_CHUNK_STAGES"); int x = s ? atoi(s) : 1; return x < 1 ? 1 : (x > 64 ? 64 : x); }();
+    return v;
+}
 constexpr unsigned SPIN_LIMIT = 1u << 24;
 
 __device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -125,23 +136,11 @@ __device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
         : "memory");
 }
 
-__device__ __forceinline__ float nudge_up(float x) {  // next fp32 toward +inf (finite x)
-    unsigned b = __float_as_uint(x);
-    if ((b & 0x7fffffffu) == 0) return __uint_as_float(1u);
-    return (b & 0x80000000u) ? __uint_as_float(b - 1) : __uint_as_float(b + 1);
-}
-__device__ __forceinline__ float nudge_down(float x) {  // next fp32 toward -inf (finite x)
-    unsigned b = __float_as_uint(x);
-    if ((b & 0x7fffffffu) == 0) return __uint_as_float(0x80000001u);
-    return (b & 0x80000000u) ? __uint_as_float(b + 1) : __uint_as_float(b - 1);
-}
-
-// Round an fp32 value to the nearest TF32 value (10 explicit mantissa bits); ties away from zero.
+// Round an fp32 value to the nearest TF32 value (10 explicit mantissa bits), ties away from zero.
 __device__ __forceinline__ float rn_tf32(float x) {
-    unsigned b = __float_as_uint(x);
-    if ((b & 0x7f800000u) == 0x7f800000u) return x;
-    b = (b + 0x1000u) & 0xffffe000u;
-    return __uint_as_float(b);
+    unsigned r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return __uint_as_float(r);
 }
 
 }  // namespace umma
@@ -165,7 +164,7 @@ __global__ void k_split_weights(const float *__restrict__ W, int K, int N, int K
 __global__ void __launch_bounds__(THREADS, 1)
 k_umma_tf32x3(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__ CUtensorMap tm_lo,
               const float *__restrict__ A, int lda, float *__restrict__ C, int ldc, int M, int N, int K,
-              int chunk_stages, int *__restrict__ err, const UmmaRelax rx) {
+              int chunk_stages, int *__restrict__ err, int dbg) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned long long *bars = (unsigned long long *)(smem + STAGES * STAGE_BYTES);
@@ -215,6 +214,7 @@ k_umma_tf32x3(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__
                     if (!mbar_wait(smem_u32(&bars[EMPTY + s]), ph ^ 1)) { atomicExch(err, 1); *abort_flag = 1; break; }
                     unsigned char *st = smem + s * STAGE_BYTES;
                     unsigned bar = smem_u32(&bars[FULL_B + s]);
+                    if (dbg & 2) { mbar_arrive(bar); continue; }
                     mbar_expect_tx(bar, 2 * B_BYTES);
                     tma_load_2d(smem_u32(st + 2 * A_BYTES), &tm_hi, ks * BK, tn * BN, bar);
                     tma_load_2d(smem_u32(st + 2 * A_BYTES + B_BYTES), &tm_lo, ks * BK, tn * BN, bar);
@@ -222,10 +222,12 @@ k_umma_tf32x3(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__
             }
         } else if (warp == 1 && lane == 0) {
             // ------------------------------------------------------------ MMA issuer
-            unsigned idesc = make_idesc(BM, BN);
             unsigned it = 0, chunk_it = 0;
             bool failed = false;
             for (int t = blockIdx.x; t < total_tiles && !*abort_flag && !failed; t += gridDim.x) {
+                // a partial column tile only multiplies the columns it has (rounded up to the MMA granule of 16)
+                int n_eff = min(BN, (N - (t % n_tiles) * BN + 15) & ~15);
+                unsigned idesc = make_idesc(BM, n_eff);
                 for (int ch = 0; ch < n_chunks && !failed; ++ch, ++chunk_it) {
                     int buf = chunk_it & 1;
                     unsigned aph = (chunk_it >> 1) & 1;
@@ -273,6 +275,8 @@ k_umma_tf32x3(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__
         bool dead = false;
         for (int t = blockIdx.x; t < total_tiles && !dead; t += gridDim.x) {
             int tm = t / n_tiles, tn = t % n_tiles;
+            const int col0 = tn * BN + half * 128;
+            const int ncols = min(128, N - col0);
             float sum[128];
 #pragma unroll
             for (int j = 0; j < 128; ++j) sum[j] = 0.f;
@@ -283,8 +287,10 @@ k_umma_tf32x3(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) { if (lane == 0) { atomicExch(err, 4); *abort_flag = 1; } dead = true; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (!(dbg & 16) && ncols > 0)
 #pragma unroll
                 for (int c = 0; c < 128; c += 32) {
+                    if (c >= ncols) break;
                     unsigned r[32];
                     unsigned taddr = tmem_base + ((unsigned)(q * 32) << 16) + (unsigned)(buf * BN + half * 128 + c);
                     tmem_ld32(taddr, r);
@@ -297,11 +303,17 @@ k_umma_tf32x3(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__
             }
             if (dead) break;
             int row = tm * BM + q * 32 + lane;
-            int col0 = tn * BN + half * 128;
-            int ncols = min(128, N - col0);
-            if (row < M && ncols > 0) {
+            if (row < M && ncols > 0 && !(dbg & 4)) {
                 float *crow = C + (long)row * ldc + col0;
-                if (ncols == 128 && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0)) {
+                if (ncols == 128 && ((reinterpret_cast<uintptr_t>(crow) & 31) == 0)) {
+                    // 32-byte stores: every instruction writes whole sectors of this thread's row
+#pragma unroll
+                    for (int j = 0; j < 128; j += 8)
+                        asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(crow + j), "f"(sum[j]),
+                                     "f"(sum[j + 1]), "f"(sum[j + 2]), "f"(sum[j + 3]), "f"(sum[j + 4]), "f"(sum[j + 5]),
+                                     "f"(sum[j + 6]), "f"(sum[j + 7])
+                                     : "memory");
+                } else if (ncols == 128 && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0)) {
 #pragma unroll
                     for (int j = 0; j < 128; j += 4) *(float4 *)(crow + j) = make_float4(sum[j], sum[j + 1], sum[j + 2], sum[j + 3]);
                 } else {
@@ -325,7 +337,7 @@ k_umma_tf32x3(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__
             for (int c = 0; c < 8; ++c) {
                 int k = k0 + c * 4;
                 float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (row < M) {
+                if (row < M && !(dbg & 1)) {
                     if (k + 3 < K && ((reinterpret_cast<uintptr_t>(arow + k) & 15) == 0)) x = *(const float4 *)(arow + k);
                     else {
                         if (k < K) x.x = arow[k];
@@ -339,63 +351,18 @@ k_umma_tf32x3(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__
         };
         if ((int)blockIdx.x < total_tiles) load_stage(blockIdx.x, 0);
         for (int t = blockIdx.x; t < total_tiles && !dead; t += gridDim.x) {
-            const int row = (t / n_tiles) * BM + r;
-            const bool sums = (rx.mode != 0) && (t % n_tiles == 0) && row < M;
-            const int dom = row / rx.R;
-            const bool upper = (row % rx.R) >= rx.S;
-            const long tbase = (long)dom * rx.nps + rx.off;      // index of this domain's block in tab / zabs
-            const long qbase = (long)dom * rx.q_ds + rx.off;
-            double sb = 0.0;
-            float sa = 0.f, sp = 0.f;
             for (int ks = 0; ks < k_stages; ++ks, ++it) {
                 int s = it % STAGES;
                 unsigned ph = (it / STAGES) & 1;
                 if (!mbar_wait(smem_u32(&bars[EMPTY + s]), ph ^ 1)) { atomicExch(err, 5); *abort_flag = 1; dead = true; break; }
                 unsigned char *st = smem + s * STAGE_BYTES;
                 float *ah = (float *)st, *al = (float *)(st + A_BYTES);
+                if (!(dbg & 8))
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
-                    float xs[4] = {v[c].x, v[c].y, v[c].z, v[c].w};
-                    if (rx.mode != 0 && row < M) {
-                        int k = ks * BK + c * 4;
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            if (k + j >= K) continue;
-                            float a = xs[j], nw = a;
-                            if (rx.mode == 2) {
-                                // beta-CROWN ReLU step (crates/ny-propagate/src/beta_crown/engine/backward/
-                                // relu_backward.rs:105-175): sign-routed slope, product stepped one ulp outward,
-                                // intercept into the bias, signed beta subtracted (lower) / added (upper).
-                                float4 tb = rx.tab[tbase + k + j];
-                                float slope = 0.f, icp = 0.f;
-                                if (a > 0.f) { slope = upper ? tb.y : tb.x; icp = upper ? tb.z : 0.f; }
-                                else if (a < 0.f) { slope = upper ? tb.x : tb.y; icp = upper ? 0.f : tb.z; }
-                                if (a == 0.f || slope == 0.f) nw = 0.f;  // exact product: no outward step needed
-                                else {
-                                    float pr = a * slope;
-                                    nw = upper ? nudge_up(pr) : nudge_down(pr);
-                                    if (sums) {
-                                        // |a*slope - nw| to one rounding, inflated, times the pre-activation magnitude
-                                        float gap = __fmul_ru(fabsf(fmaf(a, slope, -nw)), 1.000001f);
-                                        sp = __fmaf_ru(gap, rx.zabs[tbase + k + j], sp);
-                                    }
-                                }
-                                if (sums && icp != 0.f) { sb += (double)a * (double)icp; sa = __fmaf_ru(fabsf(a), fabsf(icp), sa); }
-                                if (tb.w != 0.f) nw = upper ? nw + tb.w : nw - tb.w;
-                                xs[j] = nw;
-                            }
-                            if (sums) {
-                                if (rx.bias_k) {
-                                    float bk = rx.bias_k[k + j];
-                                    sb += (double)nw * (double)bk;
-                                    sa = __fmaf_ru(fabsf(nw), fabsf(bk), sa);
-                                }
-                                sp = __fmaf_ru(__fmul_ru(rx.eps, fabsf(nw)), rx.q[qbase + k + j], sp);
-                            }
-                        }
-                    }
-                    float4 h = make_float4(rn_tf32(xs[0]), rn_tf32(xs[1]), rn_tf32(xs[2]), rn_tf32(xs[3]));
-                    float4 l = make_float4(rn_tf32(xs[0] - h.x), rn_tf32(xs[1] - h.y), rn_tf32(xs[2] - h.z), rn_tf32(xs[3] - h.w));
+                    float4 x = v[c];
+                    float4 h = make_float4(rn_tf32(x.x), rn_tf32(x.y), rn_tf32(x.z), rn_tf32(x.w));
+                    float4 l = make_float4(rn_tf32(x.x - h.x), rn_tf32(x.y - h.y), rn_tf32(x.z - h.z), rn_tf32(x.w - h.w));
                     int off = r * 32 + ((c ^ (r & 7)) << 2);  // in floats: row * 128 B + swizzled 16 B chunk
                     *(float4 *)(ah + off) = h;
                     *(float4 *)(al + off) = l;
@@ -406,11 +373,6 @@ k_umma_tf32x3(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__
                 int nks = ks + 1, nt = t;
                 if (nks == k_stages) { nks = 0; nt = t + gridDim.x; }
                 if (nt < total_tiles) load_stage(nt, nks);
-            }
-            if (sums && !dead) {  // one writer per row: only the CTA holding column tile 0 of this row tile
-                rx.rb[row] += sb;
-                rx.rabs[row] += (double)sa;
-                rx.rpen[row] += (double)sp;
             }
         }
     }
@@ -466,10 +428,7 @@ int umma_prepare_layer(nyb200_engine *e, const float *W, int K, int N, UmmaLayer
     return NYB200_OK;
 }
 
-int launch_umma(nyb200_engine *e, const UmmaLayer &L, int M, const float *A, int lda, float *C, int ldc, int *err,
-                const UmmaRelax *relax) {
-    UmmaRelax rx;
-    if (relax) rx = *relax;
+int launch_umma(nyb200_engine *e, const UmmaLayer &L, int M, const float *A, int lda, float *C, int ldc, int *err) {
     static bool attr_set = false;
     if (!attr_set) {
         if (cudaFuncSetAttribute(k_umma_tf32x3, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
@@ -481,7 +440,7 @@ int launch_umma(nyb200_engine *e, const UmmaLayer &L, int M, const float *A, int
     int tiles = ((M + BM - 1) / BM) * ((L.N + BN - 1) / BN);
     int grid = tiles < sms ? tiles : sms;
     k_umma_tf32x3<<<grid, THREADS, SMEM_BYTES, e->stream>>>(*(const CUtensorMap *)L.tm_hi, *(const CUtensorMap *)L.tm_lo, A,
-                                                            lda, C, ldc, M, L.N, L.K, CHUNK_STAGES, err, rx);
+                                                            lda, C, ldc, M, L.N, L.K, chunk_stages_cfg(), err, dbg_cfg());
     e->launches++;
     return NYB200_OK;
 }
@@ -541,8 +500,9 @@ void launch_ibp_combine(nyb200_engine *e, int D, int n_out, const float *Fl, con
 // Worst-case relative rounding of this kernel's product against S = |A||W| (see the model above).
 double umma_eps(int K) {
     int k_stages = (K + BK - 1) / BK;
-    int cs = k_stages < CHUNK_STAGES ? k_stages : CHUNK_STAGES;
-    int chunks = (k_stages + CHUNK_STAGES - 1) / CHUNK_STAGES;
+    const int CS = chunk_stages_cfg();
+    int cs = k_stages < CS ? k_stages : CS;
+    int chunks = (k_stages + CS - 1) / CS;
     const double u23 = 1.1920928955078125e-07, u24 = 5.9604644775390625e-08;
     double rep = 0.75 * 9.5367431640625e-07;                    // operand split, 0.75 * 2^-20
     double chain_main = (double)(cs * (BK / 8)) * u23;          // Ah*Wh steps round at the scale of S
