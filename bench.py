@@ -307,7 +307,7 @@ def run_ours(args, rank, world, local_rank):
 
 
 def eng_path_name(eng):
-    return getattr(eng, "_path_name", "f64")
+    return getattr(eng, "_path_name", "tf32x3")
 
 
 def main():
@@ -316,7 +316,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--path", default=os.environ.get("NYB200_PATH", "f64"), choices=["f64", "tf32x3"])
+    ap.add_argument("--path", default=os.environ.get("NYB200_PATH", "tf32x3"), choices=["f64", "tf32x3"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--domains", type=int, default=D_PER_GPU, help="domains per GPU (profiling runs use a smaller batch)")
     args = ap.parse_args()

@@ -58,7 +58,8 @@ const char *nyb200_backend_provenance(void);
 const char *nyb200_last_error(const nyb200_engine *e);
 /* Launch all work of this engine on the given cudaStream_t (NULL = the default stream). */
 int32_t nyb200_set_stream(nyb200_engine *e, void *cuda_stream);
-/* Select the contraction arithmetic (NYB200_PATH_*).  Default NYB200_PATH_F64. */
+/* Select the contraction arithmetic (NYB200_PATH_*).  Default NYB200_PATH_TF32X3; NYB200_PATH_F64 is the
+ * slower binary64 reference arithmetic on the same device. */
 int32_t nyb200_set_path(nyb200_engine *e, int32_t path);
 /* Number of kernels this engine has launched since creation (bench bookkeeping). */
 int64_t nyb200_launch_count(const nyb200_engine *e);

@@ -76,7 +76,7 @@ struct Timing {
 struct nyb200_engine {
     int device = 0;
     cudaStream_t stream = nullptr;
-    int path = NYB200_PATH_F64;
+    int path = NYB200_PATH_TF32X3;
     std::string err;
     std::mutex mu;
     std::map<int, nyb::Net> nets;

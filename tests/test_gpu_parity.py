@@ -12,11 +12,14 @@ REL_TOL = 1e-4
 IBP_REL = 1e-5
 
 
-@pytest.fixture(scope="module")
-def eng():
-    from ny_b200 import B200Engine
+@pytest.fixture(scope="module", params=["tf32x3", "f64"])
+def eng(request):
+    """Every parity case runs on both contraction paths: the tcgen05 3xTF32 default and the binary64 one."""
+    from ny_b200 import B200Engine, engine
 
     e = B200Engine(0)
+    e.set_path(engine.PATH_TF32X3 if request.param == "tf32x3" else engine.PATH_F64)
+    e.path_name = request.param
     yield e
     e.close()
 
@@ -188,8 +191,12 @@ def test_gemm_f32_entry_point(eng):
     a = g.standard_normal((37, 129)).astype(np.float32)
     b = g.standard_normal((129, 65)).astype(np.float32)
     c = eng.gemm_f32(37, 129, 65, a, b)
-    ref = (a.astype(np.float64) @ b.astype(np.float64)).astype(np.float32)
-    assert np.array_equal(c, ref)  # binary64 accumulation, one rounding to fp32
+    exact = a.astype(np.float64) @ b.astype(np.float64)
+    if eng.path_name == "f64":
+        assert np.array_equal(c, exact.astype(np.float32))  # binary64 accumulation, one rounding to fp32
+    else:
+        S = np.abs(a).astype(np.float64) @ np.abs(b).astype(np.float64)
+        assert np.max(np.abs(c - exact) / S) <= 2e-6  # within the rounding model of the 3xTF32 product
 
 
 def test_full_size_batch_properties(eng, oracle):

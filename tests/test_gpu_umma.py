@@ -97,7 +97,10 @@ def test_full_size_batch_on_tensor_path(eng, oracle):
     lo, hi, inf = eng.bab_bound_batch(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, splits, ns, mode=1)
     lo2, hi2, _ = eng.bab_bound_batch(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, splits, ns, mode=1)
     assert np.array_equal(lo, lo2) and np.array_equal(hi, hi2)
-    ref = B200Engine(0)  # binary64 path
+    from ny_b200 import engine
+
+    ref = B200Engine(0)
+    ref.set_path(engine.PATH_F64)
     rid = ref.register_network(wl.net)
     flo, fhi, finf = ref.bab_bound_batch(rid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, splits, ns, mode=1)
     ref.close()
