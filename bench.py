@@ -230,6 +230,7 @@ def run_ours(args, rank, world, local_rank):
     bwd_ms, _ = eng.timing_read("backward")
     eng.timing_enable(False)
     lo, hi, inf = eng.batch_download()
+    refined = eng.batch_refined()
 
     # ---- end-to-end: host buffers in pinned memory through the C-ABI call ------------------
     def pinned(a):
@@ -289,7 +290,8 @@ def run_ours(args, rank, world, local_rank):
                                    "directions), 8 splits/domain, constrained forward re-propagation",
                        "domains_per_gpu": D, "global_batch": D * world, "parallelism": f"domain-sharded x{world}",
                        "l2": "per-step working set (coefficient ping-pong buffers 2 x 231 MB) exceeds the 126 MB L2",
-                       "feasible_domains": int((inf == 0).sum())},
+                       "feasible_domains": int((inf == 0).sum()),
+                       "domains_sent_to_binary64_rerun": int(refined)},
             "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                     "ms_per_step": e2e_ms},
             "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline,

@@ -61,6 +61,15 @@ int32_t nyb200_set_stream(nyb200_engine *e, void *cuda_stream);
 /* Select the contraction arithmetic (NYB200_PATH_*).  Default NYB200_PATH_TF32X3; NYB200_PATH_F64 is the
  * slower binary64 reference arithmetic on the same device. */
 int32_t nyb200_set_path(nyb200_engine *e, int32_t path);
+/* Adaptive precision of the NYB200_PATH_TF32X3 path.  Every rounding of that path is charged to the
+ * bounds as a penalty; when, for some domain of a batch, that penalty exceeds `tol` times
+ * max(|bound|, 1% of the domain's largest bound) -- which happens for narrow boxes, where a bound is much
+ * smaller than the terms it is made of -- the batch is evaluated again with binary64 contractions before
+ * results are returned, so the returned bounds stay within the parity tolerance of the reference's
+ * binary64 CPU path.  Default 5e-5; 0 disables the re-run (bounds remain sound, only looser).
+ * nyb200_batch_refined reports how many domains of the last run triggered it (0 = fast path only). */
+int32_t nyb200_set_refine_tolerance(nyb200_engine *e, float tol);
+int32_t nyb200_batch_refined(nyb200_engine *e, int32_t *n_domains);
 /* Number of kernels this engine has launched since creation (bench bookkeeping). */
 int64_t nyb200_launch_count(const nyb200_engine *e);
 /* GpuCrownBackward::clear_crown_working_set (crates/ny-core/src/gemm.rs:3205). */

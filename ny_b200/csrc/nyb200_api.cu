@@ -366,8 +366,8 @@ int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p) {
     NYB_CUDA(e, cudaMemsetAsync(p.rb, 0, (size_t)M * 8, e->stream));
     NYB_CUDA(e, cudaMemsetAsync(p.rabs, 0, (size_t)M * 8, e->stream));
     NYB_CUDA(e, cudaMemsetAsync(p.rpen, 0, (size_t)M * 8, e->stream));
-    const float inf = INFINITY;
-    NYB_CUDA(e, cudaMemcpyAsync(p.min_lower, &inf, 4, cudaMemcpyHostToDevice, e->stream));
+    static const float init_words[8] = {INFINITY, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};  // min lower; loose-domain counter at word 4
+    NYB_CUDA(e, cudaMemcpyAsync(p.min_lower, init_words, sizeof(init_words), cudaMemcpyHostToDevice, e->stream));
     float *cur = p.A0, *nxt = p.A1;
     launch_seed(e, p.spec, S, nv.dims[L], D, p.lda, cur);
     auto eps_for = [&](int K) {
@@ -395,7 +395,7 @@ int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p) {
         float *t = cur; cur = nxt; nxt = t;
     }
     launch_concretize(e, M, R, S, nv.dims[0], cur, p.lda, p.in_lo, p.in_hi, b.box_stride, p.rb, p.rabs, p.rpen, p.flags,
-                      p.out_lo, p.out_hi, p.min_lower);
+                      p.out_lo, p.out_hi, p.min_lower, tensor ? e->refine_tol : 0.f);
     NYB_CUDA(e, cudaGetLastError());
     return NYB200_OK;
 }
@@ -460,11 +460,43 @@ int run_batch(nyb200_engine *e) {
     cudaEventRecord(t.ev[2], e->stream);
     t.pending = true;
     e->batch.ran = true;
+    e->batch.finished = false;
+    e->batch.refined = 0;
+    return NYB200_OK;
+}
+
+// Completes the last run: waits for it and, if the fast path reported domains whose rounding penalty
+// is visible at the requested tolerance, evaluates the batch again with binary64 contractions.
+int finish_batch(nyb200_engine *e) {
+    if (!e->batch.valid || !e->batch.ran) return set_err(e, NYB200_ERR_INVALID, "no batch has been run");
+    if (e->batch.finished) return NYB200_OK;
+    Net *net;
+    NYB_TRY(find_net(e, e->batch.net_id, &net));
+    BatchPtrs p;
+    NYB_TRY(batch_ptrs(e, *net, e->batch, p));
+    int herr = 0, loose = 0;
+    if (e->path == NYB200_PATH_TF32X3) {
+        int *derr = (int *)ws_get(e, "umma_err", 256);
+        if (derr) NYB_CUDA(e, cudaMemcpyAsync(&herr, derr, 4, cudaMemcpyDeviceToHost, e->stream));
+        NYB_CUDA(e, cudaMemcpyAsync(&loose, (int *)p.min_lower + 4, 4, cudaMemcpyDeviceToHost, e->stream));
+    }
+    NYB_CUDA(e, cudaStreamSynchronize(e->stream));
+    if (herr) return set_err(e, NYB200_ERR_INTERNAL, "tcgen05 pipeline wait expired (code " + std::to_string(herr) + ")");
+    if (loose > 0 && e->path == NYB200_PATH_TF32X3 && e->refine_tol > 0.f) {
+        e->path = NYB200_PATH_F64;
+        int st = run_forward(e, *net, e->batch, p, e->batch.mode);
+        if (st == NYB200_OK) st = run_backward(e, *net, e->batch, p);
+        e->path = NYB200_PATH_TF32X3;
+        NYB_TRY(st);
+        NYB_CUDA(e, cudaStreamSynchronize(e->stream));
+        e->batch.refined = loose;
+    }
+    e->batch.finished = true;
     return NYB200_OK;
 }
 
 int download_batch(nyb200_engine *e, float *out_lo, float *out_hi, int32_t *infeasible) {
-    if (!e->batch.valid || !e->batch.ran) return set_err(e, NYB200_ERR_INVALID, "no batch has been run");
+    NYB_TRY(finish_batch(e));
     Net *net;
     NYB_TRY(find_net(e, e->batch.net_id, &net));
     BatchPtrs p;
@@ -473,13 +505,7 @@ int download_batch(nyb200_engine *e, float *out_lo, float *out_hi, int32_t *infe
     if (out_lo) NYB_CUDA(e, cudaMemcpyAsync(out_lo, p.out_lo, n * 4, cudaMemcpyDeviceToHost, e->stream));
     if (out_hi) NYB_CUDA(e, cudaMemcpyAsync(out_hi, p.out_hi, n * 4, cudaMemcpyDeviceToHost, e->stream));
     if (infeasible) NYB_CUDA(e, cudaMemcpyAsync(infeasible, p.flags, (size_t)e->batch.D * 4, cudaMemcpyDeviceToHost, e->stream));
-    int herr = 0;
-    if (e->path == NYB200_PATH_TF32X3) {
-        int *derr = (int *)ws_get(e, "umma_err", 256);
-        if (derr) NYB_CUDA(e, cudaMemcpyAsync(&herr, derr, 4, cudaMemcpyDeviceToHost, e->stream));
-    }
     NYB_CUDA(e, cudaStreamSynchronize(e->stream));
-    if (herr) return set_err(e, NYB200_ERR_INTERNAL, "tcgen05 pipeline wait expired (code " + std::to_string(herr) + ")");
     if (infeasible) {
         for (int d = 0; d < e->batch.D; ++d) {
             if (infeasible[d] & kFlagInvalid) return set_err(e, NYB200_ERR_INVALID, "split entry out of range");
@@ -542,8 +568,8 @@ int32_t nyb200_batch_min_lower_device(nyb200_engine *e, void **dev_ptr) {
 int32_t nyb200_batch_min_lower(nyb200_engine *e, float *min_lower) {
     if (!e || !min_lower) return NYB200_ERR_INVALID;
     std::lock_guard<std::mutex> g(e->mu);
-    if (!e->batch.valid || !e->batch.ran) return set_err(e, NYB200_ERR_INVALID, "no batch has been run");
     NYB_CUDA(e, cudaSetDevice(e->device));
+    NYB_TRY(finish_batch(e));
     void *p = ws_get(e, "min_lower", 256);
     if (!p) return NYB200_ERR_OOM;
     NYB_CUDA(e, cudaMemcpyAsync(min_lower, p, 4, cudaMemcpyDeviceToHost, e->stream));
@@ -554,8 +580,8 @@ int32_t nyb200_batch_min_lower(nyb200_engine *e, float *min_lower) {
 int32_t nyb200_batch_download_pre_bounds(nyb200_engine *e, float *pre_lo, float *pre_hi) {
     if (!e || !pre_lo || !pre_hi) return NYB200_ERR_INVALID;
     std::lock_guard<std::mutex> g(e->mu);
-    if (!e->batch.valid || !e->batch.ran) return set_err(e, NYB200_ERR_INVALID, "no batch has been run");
     NYB_CUDA(e, cudaSetDevice(e->device));
+    NYB_TRY(finish_batch(e));
     Net *net;
     NYB_TRY(find_net(e, e->batch.net_id, &net));
     BatchPtrs p;
@@ -570,8 +596,8 @@ int32_t nyb200_batch_download_pre_bounds(nyb200_engine *e, float *pre_lo, float 
 int32_t nyb200_batch_select_branch(nyb200_engine *e, int32_t *relu, int32_t *neuron, float *width) {
     if (!e || !relu || !neuron) return NYB200_ERR_INVALID;
     std::lock_guard<std::mutex> g(e->mu);
-    if (!e->batch.valid || !e->batch.ran) return set_err(e, NYB200_ERR_INVALID, "no batch has been run");
     NYB_CUDA(e, cudaSetDevice(e->device));
+    NYB_TRY(finish_batch(e));
     Net *net;
     NYB_TRY(find_net(e, e->batch.net_id, &net));
     BatchPtrs p;
@@ -617,6 +643,22 @@ int32_t nyb200_ibp_forward(nyb200_engine *e, int32_t net_id, int32_t D, const fl
     NYB_CUDA(e, cudaMemcpy2DAsync(pre_lo, w, p.pre_lo, ws, w, (size_t)D, cudaMemcpyDeviceToHost, e->stream));
     NYB_CUDA(e, cudaMemcpy2DAsync(pre_hi, w, p.pre_hi, ws, w, (size_t)D, cudaMemcpyDeviceToHost, e->stream));
     NYB_CUDA(e, cudaStreamSynchronize(e->stream));
+    return NYB200_OK;
+}
+
+int32_t nyb200_set_refine_tolerance(nyb200_engine *e, float tol) {
+    if (!e || !(tol >= 0.f)) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    e->refine_tol = tol;
+    return NYB200_OK;
+}
+
+int32_t nyb200_batch_refined(nyb200_engine *e, int32_t *n_domains) {
+    if (!e || !n_domains) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    NYB_CUDA(e, cudaSetDevice(e->device));
+    NYB_TRY(finish_batch(e));
+    *n_domains = e->batch.refined;
     return NYB200_OK;
 }
 

@@ -59,6 +59,8 @@ struct Batch {
     int S = 0, R = 0, D = 0, mode = 0, box_stride = 0, max_splits = 0;
     bool has_alpha = false;
     bool ran = false;
+    bool finished = false;  // results of the last run have been checked (and refined if needed)
+    int refined = 0;        // domains that triggered the binary64 re-run of the last batch
 };
 
 struct Timing {
@@ -77,6 +79,7 @@ struct nyb200_engine {
     int device = 0;
     cudaStream_t stream = nullptr;
     int path = NYB200_PATH_TF32X3;
+    float refine_tol = 5e-5f;  // see nyb200_set_refine_tolerance
     std::string err;
     std::mutex mu;
     std::map<int, nyb::Net> nets;
@@ -116,7 +119,7 @@ void launch_gemm_f64(nyb200_engine *e, int M, int N, int K, const float *A, int 
                      int ldc, int R, const float *zin_lo, const float *zin_hi, long zin_dstride, double *rpen);
 void launch_concretize(nyb200_engine *e, int M, int R, int S, int n0, const float *A, int lda, const float *in_lo,
                        const float *in_hi, long box_dstride, const double *rb, const double *rabs, const double *rpen,
-                       const int *flags, float *out_lo, float *out_hi, float *min_lower);
+                       const int *flags, float *out_lo, float *out_hi, float *min_lower, float loose_tol);
 void launch_select_branch(nyb200_engine *e, const NetView &nv, int D, const float *pre_lo, const float *pre_hi,
                           const signed char *code, int *relu, int *neuron, float *width);
 void launch_fill_f64(nyb200_engine *e, double *p, size_t n, double v);

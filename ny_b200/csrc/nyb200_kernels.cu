@@ -495,6 +495,31 @@ __device__ __forceinline__ void atomic_min_float(float *addr, float v) {
     else atomicMax((unsigned *)addr, __float_as_uint(v));
 }
 
+// Counts the domains whose accumulated rounding penalty is not small against their bounds: a row is
+// "loose" when rpen > tol * max(|bound|, 1% of the domain's largest bound magnitude).  The host re-runs
+// the batch on the binary64 path when the count is non-zero, so that the fast path never returns a
+// bound that its own rounding model has visibly loosened.
+__global__ void k_count_loose(int D, int S, int R, const float *__restrict__ out_lo, const float *__restrict__ out_hi,
+                              const double *__restrict__ rpen, const int *__restrict__ flags, float tol,
+                              int *__restrict__ n_loose) {
+    int d = blockIdx.x * blockDim.x + threadIdx.x;
+    if (d >= D || flags[d] != 0) return;
+    float scale = 0.f;
+    for (int s = 0; s < S; ++s) {
+        float l = out_lo[d * S + s], u = out_hi[d * S + s];
+        if (isfinite(l)) scale = fmaxf(scale, fabsf(l));
+        if (isfinite(u)) scale = fmaxf(scale, fabsf(u));
+    }
+    bool loose = false;
+    for (int s = 0; s < S; ++s) {
+        float l = out_lo[d * S + s], u = out_hi[d * S + s];
+        if (!isfinite(l) || !isfinite(u)) continue;
+        double pl = rpen[(long)d * R + s], pu = rpen[(long)d * R + S + s];
+        if (pl > (double)tol * fmaxf(fabsf(l), 0.01f * scale) || pu > (double)tol * fmaxf(fabsf(u), 0.01f * scale)) loose = true;
+    }
+    if (loose) atomicAdd(n_loose, 1);
+}
+
 // Per (domain, spec row): apply the domain flags and the reference's repair rule
 // (non-finite endpoint or inversion -> [-inf, +inf], concretize.rs:481-488); fold the global minimum.
 __global__ void k_finalize(int D, int S, const int *__restrict__ flags, float *__restrict__ out_lo,
@@ -625,12 +650,17 @@ void launch_gemm_f64(nyb200_engine *e, int M, int N, int K, const float *A, int 
 
 void launch_concretize(nyb200_engine *e, int M, int R, int S, int n0, const float *A, int lda, const float *in_lo,
                        const float *in_hi, long box_dstride, const double *rb, const double *rabs, const double *rpen,
-                       const int *flags, float *out_lo, float *out_hi, float *min_lower) {
+                       const int *flags, float *out_lo, float *out_hi, float *min_lower, float loose_tol) {
     long threads = (long)M * 32;
     k_concretize<<<(unsigned)((threads + 255) / 256), 256, 0, e->stream>>>(M, R, S, n0, A, lda, in_lo, in_hi, box_dstride,
                                                                            rb, rabs, rpen, out_lo, out_hi);
     NYB_COUNT(e);
     int D = M / R;
+    if (loose_tol > 0.f) {
+        k_count_loose<<<(D + 255) / 256, 256, 0, e->stream>>>(D, S, R, out_lo, out_hi, rpen, flags, loose_tol,
+                                                              (int *)min_lower + 4);
+        NYB_COUNT(e);
+    }
     k_finalize<<<(D * S + 255) / 256, 256, 0, e->stream>>>(D, S, flags, out_lo, out_hi, min_lower);
     NYB_COUNT(e);
 }

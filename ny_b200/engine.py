@@ -32,7 +32,7 @@ PATH_F64, PATH_TF32X3 = 0, 1
 
 EXPORTS = [
     "nyb200_create", "nyb200_destroy", "nyb200_backend_provenance", "nyb200_last_error", "nyb200_set_stream",
-    "nyb200_set_path", "nyb200_launch_count", "nyb200_clear_working_set", "nyb200_gemm_f32", "nyb200_net_create",
+    "nyb200_set_path", "nyb200_set_refine_tolerance", "nyb200_batch_refined", "nyb200_launch_count", "nyb200_clear_working_set", "nyb200_gemm_f32", "nyb200_net_create",
     "nyb200_net_destroy", "nyb200_ibp_forward", "nyb200_bab_bound_batch", "nyb200_batch_upload", "nyb200_batch_run",
     "nyb200_batch_download", "nyb200_batch_min_lower", "nyb200_batch_min_lower_device",
     "nyb200_batch_download_pre_bounds", "nyb200_batch_select_branch", "nyb200_timing_enable", "nyb200_timing_reset",
@@ -66,6 +66,8 @@ def load_library():
     L.nyb200_last_error.restype = C.c_char_p
     L.nyb200_set_stream.argtypes = [vp, vp]
     L.nyb200_set_path.argtypes = [vp, C.c_int32]
+    L.nyb200_set_refine_tolerance.argtypes = [vp, C.c_float]
+    L.nyb200_batch_refined.argtypes = [vp, ip]
     L.nyb200_launch_count.argtypes = [vp]
     L.nyb200_launch_count.restype = C.c_int64
     L.nyb200_clear_working_set.argtypes = [vp]
@@ -157,6 +159,14 @@ class B200Engine:
 
     def set_path(self, path: int):
         self._check(self._L.nyb200_set_path(self._h, path))
+
+    def set_refine_tolerance(self, tol: float):
+        self._check(self._L.nyb200_set_refine_tolerance(self._h, tol))
+
+    def batch_refined(self) -> int:
+        n = C.c_int32(0)
+        self._check(self._L.nyb200_batch_refined(self._h, C.byref(n)))
+        return int(n.value)
 
     def launch_count(self) -> int:
         return int(self._L.nyb200_launch_count(self._h))

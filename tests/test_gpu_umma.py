@@ -120,3 +120,32 @@ def test_full_size_batch_on_tensor_path(eng, oracle):
     ok = np.isfinite(mn)
     assert np.all(lo[d][ok] <= mn[ok])
     eng.release_network(nid)
+
+
+def test_narrow_box_triggers_binary64_rerun(eng, oracle):
+    """A narrow input box makes every bound a small difference of large terms; the tensor path's rounding
+    penalty is then visible at 1e-4, the engine notices it and re-evaluates the batch in binary64.  With the
+    re-run disabled the bounds stay sound (never above the oracle's by more than fp32 noise) but looser."""
+    from tests.test_gpu_parity import REL_TOL, _oracle_batch, _rel, _setup
+
+    wl = W.config_mlp_bab(seed=21, hidden=64, depth=3, n_in=96, eps=0.01, n_fix=4)
+    onet, ospec, nid, rl, ru = _setup(eng, oracle, wl)
+    splits, ns = W.draw_domains(wl, rl, ru, 64)
+    olo, ohi, oinf, _ = _oracle_batch(oracle, ospec, wl, rl, ru, splits, ns, 1)
+    f = ~oinf.astype(bool)
+    eng.batch_upload(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, splits, ns, mode=1)
+    eng.batch_run()
+    glo, ghi, ginf = eng.batch_download()
+    assert eng.batch_refined() > 0
+    assert _rel(np.concatenate([glo, ghi], 1)[f], np.concatenate([olo, ohi], 1)[f]) <= REL_TOL
+    eng.set_refine_tolerance(0.0)
+    try:
+        eng.batch_run()
+        llo, lhi, _ = eng.batch_download()
+        assert eng.batch_refined() == 0
+        scale = np.abs(np.concatenate([olo, ohi], 1)).max(axis=1, keepdims=True)
+        assert np.all(llo[f] <= olo[f] + 1e-6 * scale[f]) and np.all(lhi[f] >= ohi[f] - 1e-6 * scale[f])
+        assert np.all(llo[f] <= glo[f] + 1e-6 * scale[f])
+    finally:
+        eng.set_refine_tolerance(5e-5)
+    eng.release_network(nid)
