@@ -147,6 +147,21 @@ int32_t nyb200_batch_download_pre_bounds(nyb200_engine *e, float *pre_lo, float 
  * relu[d] = -1 when the domain has no unstable unsplit neuron. */
 int32_t nyb200_batch_select_branch(nyb200_engine *e, int32_t *relu, int32_t *neuron, float *width);
 
+/* ---- interval forward pass of ONE box without any device allocation ------------------------------
+ * No counterpart in the reference: an addition for hosts that cannot let a library allocate device
+ * memory at call time (a service that gave the whole GPU to its own arena at start-up, or a BaB loop
+ * that cannot afford the device-wide synchronisation an allocation implies).  Same arithmetic and
+ * output layout as nyb200_ibp_forward with D = 1, but in_lo/in_hi [dims[0]] and pre_lo/pre_hi
+ * [sum_{k>=1} dims[k]] are DEVICE pointers owned by the caller, and the intermediate intervals live in
+ * a fixed array inside the library image (about 128 KB per GPU, held from first use until exit).
+ *   - every layer width, the input included, must be <= 8192, otherwise NYB200_ERR_UNSUPPORTED;
+ *   - all calls on a GPU share that array: calls that overlap on the device (other streams or engines)
+ *     race and their results are undefined; calls on one stream are safe back to back;
+ *   - the first call on a GPU resolves the array's device address: make it outside stream capture;
+ *   - the call returns after the engine stream has drained (it reads one status word back). */
+int32_t nyb200_ibp_forward_noalloc(nyb200_engine *e, int32_t net_id, const float *dev_in_lo, const float *dev_in_hi,
+                                   float *dev_pre_lo, float *dev_pre_hi);
+
 /* Kernel-only timing of the last nyb200_batch_run calls: average milliseconds per run of the
  * named phase ("forward", "backward", "total") measured with CUDA events on the engine stream
  * since the last reset.  With nyb200_timing_enable(e, 1) every launch of the A*W contraction kernel

@@ -33,7 +33,7 @@ PATH_F64, PATH_TF32X3 = 0, 1
 EXPORTS = [
     "nyb200_create", "nyb200_destroy", "nyb200_backend_provenance", "nyb200_last_error", "nyb200_set_stream",
     "nyb200_set_path", "nyb200_set_refine_tolerance", "nyb200_batch_refined", "nyb200_launch_count", "nyb200_clear_working_set", "nyb200_gemm_f32", "nyb200_net_create",
-    "nyb200_net_destroy", "nyb200_ibp_forward", "nyb200_bab_bound_batch", "nyb200_batch_upload", "nyb200_batch_run",
+    "nyb200_net_destroy", "nyb200_ibp_forward", "nyb200_ibp_forward_noalloc", "nyb200_bab_bound_batch", "nyb200_batch_upload", "nyb200_batch_run",
     "nyb200_batch_download", "nyb200_batch_min_lower", "nyb200_batch_min_lower_device",
     "nyb200_batch_download_pre_bounds", "nyb200_batch_select_branch", "nyb200_timing_enable", "nyb200_timing_reset",
     "nyb200_timing_read",
@@ -75,6 +75,7 @@ def load_library():
     L.nyb200_net_create.argtypes = [vp, C.c_int32, ip, fp, fp, ip, ip]
     L.nyb200_net_destroy.argtypes = [vp, C.c_int32]
     L.nyb200_ibp_forward.argtypes = [vp, C.c_int32, C.c_int32, fp, fp, C.c_int32, fp, fp]
+    L.nyb200_ibp_forward_noalloc.argtypes = [vp, C.c_int32, vp, vp, vp, vp]
     batch_args = [vp, C.c_int32, fp, C.c_int32, fp, fp, C.c_int32, fp, fp, vp, ip, C.c_int32, C.c_int32, C.c_int32, fp]
     L.nyb200_bab_bound_batch.argtypes = batch_args + [fp, fp, ip]
     L.nyb200_batch_upload.argtypes = batch_args
@@ -213,6 +214,12 @@ class B200Engine:
         pu = np.empty((D, net.n_pre), np.float32)
         self._check(self._L.nyb200_ibp_forward(self._h, net_id, D, _fp(lo), _fp(hi), int(net.dims[0]), _fp(pl), _fp(pu)))
         return pl, pu
+
+    def ibp_forward_noalloc(self, net_id: int, dev_in_lo: int, dev_in_hi: int, dev_pre_lo: int, dev_pre_hi: int):
+        """Single-box interval forward pass on caller-owned DEVICE buffers (raw addresses); the library
+        allocates nothing.  Widths above 8192 are refused; concurrent calls on one GPU race."""
+        self._check(self._L.nyb200_ibp_forward_noalloc(self._h, net_id, C.c_void_p(dev_in_lo), C.c_void_p(dev_in_hi),
+                                                       C.c_void_p(dev_pre_lo), C.c_void_p(dev_pre_hi)))
 
     # -- batched beta-CROWN ----------------------------------------------------------------
     def _batch_args(self, net_id, spec, in_lo, in_hi, inh_lo, inh_hi, splits, n_splits, mode, alpha):
