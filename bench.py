@@ -30,6 +30,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 D_PER_GPU = 4096
+_emit = lambda obj: print(json.dumps(obj))
 METRIC = "BaB domains bounded/sec (beta-CROWN)"
 UNIT = "domains/s"
 # Algorithmic work per domain for this network (fp32 coefficients, both bound directions carried):
@@ -151,7 +152,7 @@ def run_reference(args, rank, world):
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line))
+    _emit(line)
 
 
 class _DevPtr:
@@ -302,7 +303,7 @@ def run_ours(args, rank, world, local_rank):
             v, threads = cpu_baseline(wl, rl, ru, sample)
             line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
                                     "sample": f"{sample} domains of the same workload, one pass, all host threads"}
-        print(json.dumps(line))
+        _emit(line)
     eng.close()
     if dist is not None:
         dist.destroy_process_group()
@@ -313,6 +314,13 @@ def eng_path_name(eng):
 
 
 def main():
+    # Libraries (NCCL's version banner, for one) may write to stdout; the contract is ONE JSON line there.
+    # Keep the real stdout aside, send everything else to stderr, and print the result line on the real one.
+    sys.stdout.flush()
+    real_stdout = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
+    global _emit
+    _emit = lambda obj: (real_stdout.write(json.dumps(obj) + "\n"), real_stdout.flush())
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
