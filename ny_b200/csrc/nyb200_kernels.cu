@@ -304,67 +304,78 @@ k_relax(int n, int off, int M, int R, int S, int n_pre, int identity, float *__r
 
 // Vectorised form of k_relax for 16-byte aligned layouts (n, off, lda, row strides multiples of 4): one
 // warp per row, every lane handles float4 groups and issues all loads of a group before using them.
-// Penalties are accumulated in fp32 with upward-directed operations (an upper bound is all that is
-// needed); the bias stays in binary64.
-__device__ __forceinline__ void relax_one(float a, float ls, float us, float ui, float sbt, float za, float qv, float bk,
-                                          bool upper, bool identity, bool has_bias, float eps, float &nw_out, double &sb,
-                                          float &sa, float &sp) {
+// The kernel is instruction-issue bound, so the per-coefficient work is kept branch-free and short:
+// the product a*slope is rounded directly toward the safe side (one instruction; never looser than the
+// reference's round-to-nearest-then-step and at most one ulp tighter), its exact residual is charged as
+// the rounding gap, penalties are accumulated in fp32 with upward-directed operations (an upper bound is
+// all that is needed) and inflated once at the end; the bias stays in binary64.
+template <bool UPPER, bool RELAX, bool BIAS>
+__device__ __forceinline__ float relax_one(float a, float4 t, float za, float qv, float bk, float eps, double &sb,
+                                           float &sa, float &sp) {
     float nw = a;
-    if (!identity) {
-        float slope = 0.f, icp = 0.f;
-        if (a > 0.f) { slope = upper ? us : ls; icp = upper ? ui : 0.f; }
-        else if (a < 0.f) { slope = upper ? ls : us; icp = upper ? 0.f : ui; }
-        if (a == 0.f || slope == 0.f) nw = 0.f;
-        else {
-            float p = a * slope;
-            nw = upper ? next_up_f(p) : next_down_f(p);
-            float gap = __fmul_ru(fabsf(fmaf(a, slope, -nw)), 1.000001f);  // |a*slope - nw| to one rounding, inflated
-            sp = __fmaf_ru(gap, za, sp);
-        }
-        if (icp != 0.f) { sb += (double)a * (double)icp; sa = __fmaf_ru(fabsf(a), fabsf(icp), sa); }
-        if (sbt != 0.f) nw = upper ? nw + sbt : nw - sbt;
+    if (RELAX) {
+        const bool pos = a > 0.f;
+        // lower rows: a > 0 takes the lower line (slope ls, no intercept), a < 0 the upper line (us, ui);
+        // upper rows mirror it (relu_backward.rs:105-153)
+        const float slope = (pos != UPPER) ? t.x : t.y;
+        const float icp = ((pos == UPPER) && a != 0.f) ? t.z : 0.f;
+        nw = UPPER ? __fmul_ru(a, slope) : __fmul_rd(a, slope);
+        sp = __fmaf_ru(fabsf(fmaf(a, slope, -nw)), za, sp);
+        sb = fma((double)a, (double)icp, sb);
+        sa = __fmaf_ru(fabsf(a), fabsf(icp), sa);
+        nw = UPPER ? nw + t.w : nw - t.w;  // signed beta (zero for unsplit neurons), relu_backward.rs:156-175
     }
-    if (has_bias) { sb += (double)nw * (double)bk; sa = __fmaf_ru(fabsf(nw), fabsf(bk), sa); }
+    if (BIAS) {
+        sb = fma((double)nw, (double)bk, sb);
+        sa = __fmaf_ru(fabsf(nw), fabsf(bk), sa);
+    }
     sp = __fmaf_ru(__fmul_ru(eps, fabsf(nw)), qv, sp);
-    nw_out = nw;
+    return nw;
 }
 
+template <bool UPPER, bool RELAX, bool BIAS>
+__device__ __forceinline__ void relax_row(int n, int lane, float *__restrict__ row, const float4 *__restrict__ tab,
+                                          const float *__restrict__ zabs, const float *__restrict__ q,
+                                          const float *__restrict__ bias_k, float eps, double &sb, float &sa, float &sp) {
+    for (int j = lane * 4; j < n; j += 128) {
+        float4 a = *(const float4 *)(row + j);
+        float4 qv = *(const float4 *)(q + j);
+        float4 bk = BIAS ? *(const float4 *)(bias_k + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+        float4 t0 = make_float4(0.f, 0.f, 0.f, 0.f), t1 = t0, t2 = t0, t3 = t0, za = t0;
+        if (RELAX) {
+            t0 = tab[j]; t1 = tab[j + 1]; t2 = tab[j + 2]; t3 = tab[j + 3];
+            za = *(const float4 *)(zabs + j);
+        }
+        float4 o;
+        o.x = relax_one<UPPER, RELAX, BIAS>(a.x, t0, za.x, qv.x, bk.x, eps, sb, sa, sp);
+        o.y = relax_one<UPPER, RELAX, BIAS>(a.y, t1, za.y, qv.y, bk.y, eps, sb, sa, sp);
+        o.z = relax_one<UPPER, RELAX, BIAS>(a.z, t2, za.z, qv.z, bk.z, eps, sb, sa, sp);
+        o.w = relax_one<UPPER, RELAX, BIAS>(a.w, t3, za.w, qv.w, bk.w, eps, sb, sa, sp);
+        if (RELAX) *(float4 *)(row + j) = o;
+    }
+}
+
+template <bool RELAX, bool BIAS>
 __global__ void __launch_bounds__(256, 4)
-k_relax_v4(int n, int off, int M, int R, int S, long nps, int identity, float *__restrict__ A, int lda,
-           const float4 *__restrict__ tab, const float *__restrict__ zabs, const float *__restrict__ q, long q_ds,
-           const float *__restrict__ bias_k, float eps, double *__restrict__ rb, double *__restrict__ rabs,
-           double *__restrict__ rpen) {
+k_relax_v4(int n, int off, int M, int R, int S, long nps, float *__restrict__ A, int lda, const float4 *__restrict__ tab,
+           const float *__restrict__ zabs, const float *__restrict__ q, long q_ds, const float *__restrict__ bias_k,
+           float eps, double *__restrict__ rb, double *__restrict__ rabs, double *__restrict__ rpen) {
     int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp >= M) return;
     int m = warp, d = m / R;
-    bool upper = (m % R) >= S;
+    const bool upper = (m % R) >= S;  // uniform in the warp
     float *row = A + (long)m * lda;
     const long tb = (long)d * nps + off, qb = (long)d * q_ds + off;
     double sb = 0.0;
     float sa = 0.f, sp = 0.f;
-    const bool has_bias = bias_k != nullptr;
-    for (int j = lane * 4; j < n; j += 128) {
-        float4 a = *(const float4 *)(row + j);
-        float4 qv = *(const float4 *)(q + qb + j);
-        float4 bk = has_bias ? *(const float4 *)(bias_k + j) : make_float4(0.f, 0.f, 0.f, 0.f);
-        float4 t0 = make_float4(0.f, 0.f, 0.f, 0.f), t1 = t0, t2 = t0, t3 = t0, za = t0;
-        if (!identity) {
-            t0 = tab[tb + j]; t1 = tab[tb + j + 1]; t2 = tab[tb + j + 2]; t3 = tab[tb + j + 3];
-            za = *(const float4 *)(zabs + tb + j);
-        }
-        float4 o;
-        relax_one(a.x, t0.x, t0.y, t0.z, t0.w, za.x, qv.x, bk.x, upper, identity, has_bias, eps, o.x, sb, sa, sp);
-        relax_one(a.y, t1.x, t1.y, t1.z, t1.w, za.y, qv.y, bk.y, upper, identity, has_bias, eps, o.y, sb, sa, sp);
-        relax_one(a.z, t2.x, t2.y, t2.z, t2.w, za.z, qv.z, bk.z, upper, identity, has_bias, eps, o.z, sb, sa, sp);
-        relax_one(a.w, t3.x, t3.y, t3.z, t3.w, za.w, qv.w, bk.w, upper, identity, has_bias, eps, o.w, sb, sa, sp);
-        if (!identity) *(float4 *)(row + j) = o;
-    }
+    if (upper) relax_row<true, RELAX, BIAS>(n, lane, row, tab + tb, zabs + tb, q + qb, bias_k, eps, sb, sa, sp);
+    else relax_row<false, RELAX, BIAS>(n, lane, row, tab + tb, zabs + tb, q + qb, bias_k, eps, sb, sa, sp);
     double da = (double)sa, dp = (double)sp;
     sb = warp_sum(sb); da = warp_sum(da); dp = warp_sum(dp);
     if (lane == 0) {  // reductions without a dependent read: the row is owned by this warp for this launch
         atomicAdd(&rb[m], sb);
-        atomicAdd(&rabs[m], da * 1.0000001);
-        atomicAdd(&rpen[m], dp * 1.0000001);
+        atomicAdd(&rabs[m], da * 1.000001);
+        atomicAdd(&rpen[m], dp * 1.000001);  // covers the single rounding of each fp32 gap / product above
     }
 }
 
@@ -632,10 +643,15 @@ void launch_relax(nyb200_engine *e, const NetView &nv, int r, int lin_k, int M, 
     unsigned grid = (unsigned)((threads + 255) / 256);
     bool aligned = (n % 4 == 0) && (off % 4 == 0) && (lda % 4 == 0) && (nv.nps % 4 == 0) && (q_dstride % 4 == 0) &&
                    ((reinterpret_cast<uintptr_t>(A) & 15) == 0);
-    if (aligned)
-        k_relax_v4<<<grid, 256, 0, e->stream>>>(n, off, M, R, S, (long)nv.nps, r < 0 ? 1 : 0, A, lda, tab, zabs, q, q_dstride,
-                                                nv.b[lin_k], (float)(eps_gemm * 1.0000002), rb, rabs, rpen);
-    else
+    if (aligned) {
+        const float epsf = (float)(eps_gemm * 1.0000002);
+        const float *bk = nv.b[lin_k];
+#define NYB_RELAX_LAUNCH(RELAX, BIAS) \
+    k_relax_v4<RELAX, BIAS><<<grid, 256, 0, e->stream>>>(n, off, M, R, S, (long)nv.nps, A, lda, tab, zabs, q, q_dstride, bk, epsf, rb, rabs, rpen)
+        if (r >= 0) { if (bk) NYB_RELAX_LAUNCH(true, true); else NYB_RELAX_LAUNCH(true, false); }
+        else { if (bk) NYB_RELAX_LAUNCH(false, true); else NYB_RELAX_LAUNCH(false, false); }
+#undef NYB_RELAX_LAUNCH
+    } else
         k_relax<<<grid, 256, 0, e->stream>>>(n, off, M, R, S, nv.nps, r < 0 ? 1 : 0, A, lda, tab, zabs, q, q_dstride,
                                              nv.b[lin_k], eps_gemm, rb, rabs, rpen);
     NYB_COUNT(e);
