@@ -922,3 +922,171 @@ int nyo_domain_violated(float lower, float upper, float threshold) {
     if (lower > upper) return 0;
     return upper < threshold;
 }
+
+/* ------------------------------------------------------------------ alpha/beta optimisation */
+/* Value of the lower rows and its joint gradient with respect to every lower slope alpha and every split
+ * multiplier beta, by the forward fold + reverse adjoint of ny-core/src/joint_alpha_grad.rs:22-50,101-170
+ * (coefficient and bias channels, no certified-error channel: the gradient only proposes the next
+ * parameters, the bound itself is always re-evaluated by the sound fold).  The ReLU lines are the BaB ones
+ * (beta_crown/engine/backward/relu_backward.rs:63-101); beta enters as A' -= beta*sign, so
+ * d(bound_s)/d(beta_j) = -sign_j * Zpre[s,j] (beta_crown/engine/optimization/gradients/joint.rs:447-568).
+ * The objective is the sum of the lower bounds over the spec rows.  Binary64 throughout. */
+int nyo_joint_gradient(const nyo_net *net, const float *in_lo, const float *in_hi, const float *pre_lo,
+                       const float *pre_hi, const nyo_split *splits, int n_splits, const float *alpha,
+                       double *lower_out, float *grad_alpha, float *grad_beta) {
+    int L = net->n_linear, S = net->dims[L];
+    size_t total = pre_offset(net, L);
+    /* per-ReLU records */
+    double **apre = (double **)calloc((size_t)L, sizeof(double *));
+    double **sig = (double **)calloc((size_t)L, sizeof(double *));
+    double **tau = (double **)calloc((size_t)L, sizeof(double *));
+    int n = S;
+    double *A = (double *)calloc((size_t)S * n, 8), *b = (double *)calloc((size_t)S, 8);
+    for (int s = 0; s < S; ++s) A[(size_t)s * n + s] = 1.0;
+    for (int k = L - 1; k >= 0; --k) {
+        lin_layer Lk = net_layer(net, k);
+        double *An = (double *)calloc((size_t)S * Lk.n_in, 8);
+        for (int s = 0; s < S; ++s)
+            for (int o = 0; o < Lk.n_out; ++o) {
+                double a = A[(size_t)s * Lk.n_out + o];
+                if (a == 0.0) continue;
+                const float *w = Lk.W + (size_t)o * Lk.n_in;
+                for (int j = 0; j < Lk.n_in; ++j) An[(size_t)s * Lk.n_in + j] += a * (double)w[j];
+                if (Lk.b) b[s] += a * (double)Lk.b[o];
+            }
+        free(A); A = An; n = Lk.n_in;
+        if (k > 0 && relu_after(net, k - 1)) {
+            int r = k - 1;
+            size_t o = pre_offset(net, r);
+            apre[r] = (double *)malloc(8 * (size_t)S * n);
+            sig[r] = (double *)malloc(8 * (size_t)S * n);
+            tau[r] = (double *)malloc(8 * (size_t)S * n);
+            for (int j = 0; j < n; ++j) {
+                float l = pre_lo[o + j], u = pre_hi[o + j];
+                int sp = 0; float sb = 0.0f;
+                for (int q = 0; q < n_splits; ++q) if (splits[q].relu == r && splits[q].neuron == j) {
+                    sp = splits[q].sign > 0 ? 1 : -1; sb = isfinite(splits[q].beta) ? splits[q].beta * (float)sp : 0.0f;
+                }
+                double ls, us, ui;
+                if (sp > 0) { ls = 1; us = 1; ui = 0; }
+                else if (sp < 0) { ls = 0; us = 0; ui = 0; }
+                else if (l >= 0.0f) { ls = 1; us = 1; ui = 0; }
+                else if (u <= 0.0f) { ls = 0; us = 0; ui = 0; }
+                else {
+                    float w = fmaxf(u - l, RELU_RELAX_MIN_WIDTH);
+                    us = (double)(u / w); ui = (double)(-l * u / w);
+                    ls = alpha ? (double)alpha[o + j] : ((u > -l) ? 1.0 : 0.0);
+                }
+                for (int s = 0; s < S; ++s) {
+                    size_t q = (size_t)s * n + j;
+                    double a = A[q];
+                    apre[r][q] = a;
+                    double sg = (a >= 0.0) ? ls : us, ta = (a >= 0.0) ? 0.0 : ui;
+                    sig[r][q] = sg; tau[r][q] = ta;
+                    b[s] += a * ta;
+                    A[q] = a * sg - (double)sb;
+                }
+            }
+        }
+    }
+    /* concretise and seed the adjoint */
+    int n0 = net->dims[0];
+    double *Z = (double *)malloc(8 * (size_t)S * n0);
+    for (int s = 0; s < S; ++s) {
+        double v = b[s];
+        for (int j = 0; j < n0; ++j) {
+            double a = A[(size_t)s * n0 + j];
+            double x = (a >= 0.0) ? (double)in_lo[j] : (double)in_hi[j];
+            Z[(size_t)s * n0 + j] = x;
+            v += a * x;
+        }
+        if (lower_out) lower_out[s] = v;
+    }
+    if (grad_alpha) memset(grad_alpha, 0, 4 * total);
+    if (grad_beta) memset(grad_beta, 0, 4 * (size_t)(n_splits > 0 ? n_splits : 0));
+    n = n0;
+    for (int k = 0; k < L; ++k) {
+        lin_layer Lk = net_layer(net, k);
+        double *Zn = (double *)calloc((size_t)S * Lk.n_out, 8);
+        for (int s = 0; s < S; ++s)
+            for (int o = 0; o < Lk.n_out; ++o) {
+                const float *w = Lk.W + (size_t)o * Lk.n_in;
+                double acc = Lk.b ? (double)Lk.b[o] : 0.0;
+                for (int j = 0; j < Lk.n_in; ++j) acc += Z[(size_t)s * Lk.n_in + j] * (double)w[j];
+                Zn[(size_t)s * Lk.n_out + o] = acc;
+            }
+        free(Z); Z = Zn; n = Lk.n_out;
+        if (k < L - 1 && relu_after(net, k)) {
+            size_t o = pre_offset(net, k);
+            for (int j = 0; j < n; ++j) {
+                float l = pre_lo[o + j], u = pre_hi[o + j];
+                int split_idx = -1;
+                for (int q = 0; q < n_splits; ++q) if (splits[q].relu == k && splits[q].neuron == j) split_idx = q;
+                double ga = 0.0, gz = 0.0;
+                for (int s = 0; s < S; ++s) {
+                    size_t q = (size_t)s * n + j;
+                    double ap = apre[k][q];
+                    ga += Z[q] * (ap > 0.0 ? ap : 0.0);
+                    gz += Z[q];
+                    Z[q] = Z[q] * sig[k][q] + tau[k][q];
+                }
+                if (split_idx >= 0) { if (grad_beta) grad_beta[split_idx] = (float)(-(double)(splits[split_idx].sign > 0 ? 1 : -1) * gz); }
+                else if (l < 0.0f && u > 0.0f && grad_alpha) grad_alpha[o + j] = (float)ga;
+            }
+        }
+    }
+    for (int r = 0; r < L; ++r) { free(apre[r]); free(sig[r]); free(tau[r]); }
+    free(apre); free(sig); free(tau); free(A); free(b); free(Z);
+    return 0;
+}
+
+/* Projected-Adam ascent on alpha (clamped to [0,1], unstable unsplit neurons only:
+ * bounds/alpha/shared.rs:106-146) and beta (clamped to >= 0, gradient clipped to +-clip:
+ * beta_crown/state/beta.rs:314-441), learning rate lr * decay^(t-1), intermediate bounds fixed.  Each iteration
+ * evaluates the sound bound with the current parameters first and keeps the element-wise best
+ * (network/alpha_crown_loop.rs:928-936), then steps along the joint gradient.  alpha (n_pre layout) and the
+ * beta fields of `splits` are updated in place. */
+int nyo_optimize(const nyo_net *net, const float *in_lo, const float *in_hi, const float *pre_lo, const float *pre_hi,
+                 nyo_split *splits, int n_splits, float *alpha, int iterations, float lr_alpha, float lr_beta,
+                 float lr_decay, float clip_beta, float *best_lo, float *best_hi) {
+    int L = net->n_linear, S = net->dims[L];
+    size_t total = pre_offset(net, L);
+    float *ga = (float *)calloc(total, 4), *ma = (float *)calloc(total, 4), *va = (float *)calloc(total, 4);
+    float *gb = (float *)calloc((size_t)(n_splits + 1), 4), *mb = (float *)calloc((size_t)(n_splits + 1), 4), *vb = (float *)calloc((size_t)(n_splits + 1), 4);
+    float *lo = (float *)malloc(4 * (size_t)S), *hi = (float *)malloc(4 * (size_t)S);
+    const float b1 = 0.9f, b2 = 0.999f, eps = 1e-8f;
+    for (int s = 0; s < S; ++s) { best_lo[s] = -INFINITY; best_hi[s] = INFINITY; }
+    for (int t = 1; t <= iterations; ++t) {
+        nyo_beta_crown_bound(net, in_lo, in_hi, pre_lo, pre_hi, splits, n_splits, alpha, lo, hi);
+        for (int s = 0; s < S; ++s) { if (lo[s] > best_lo[s]) best_lo[s] = lo[s]; if (hi[s] < best_hi[s]) best_hi[s] = hi[s]; }
+        if (t == iterations) break;
+        nyo_joint_gradient(net, in_lo, in_hi, pre_lo, pre_hi, splits, n_splits, alpha, NULL, ga, gb);
+        float bc1 = fmaxf(1.0f - powf(b1, (float)t), 1.1920929e-7f), bc2 = fmaxf(1.0f - powf(b2, (float)t), 1.1920929e-7f);
+        float lra = lr_alpha * powf(lr_decay, (float)(t - 1)), lrb = lr_beta * powf(lr_decay, (float)(t - 1));
+        size_t hidden = pre_offset(net, L - 1);
+        if (alpha && lr_alpha > 0.0f) for (size_t i = 0; i < hidden; ++i) {
+            if (!(pre_lo[i] < 0.0f && pre_hi[i] > 0.0f)) continue;
+            int is_split = 0;
+            for (int q = 0; q < n_splits; ++q) if (pre_offset(net, splits[q].relu) + (size_t)splits[q].neuron == i) is_split = 1;
+            if (is_split) continue;
+            float g = ga[i];
+            ma[i] = b1 * ma[i] + (1.0f - b1) * g;
+            va[i] = b2 * va[i] + (1.0f - b2) * g * g;
+            float a = alpha[i] + lra * (ma[i] / bc1) / (sqrtf(va[i] / bc2) + eps);
+            a = fminf(fmaxf(a, 0.0f), 1.0f);
+            if (isnan(a)) { a = 0.5f; ma[i] = 0.0f; va[i] = 0.0f; }
+            alpha[i] = a;
+        }
+        if (lr_beta > 0.0f) for (int q = 0; q < n_splits; ++q) {
+            float g = gb[q];
+            if (clip_beta > 0.0f) g = fminf(fmaxf(g, -clip_beta), clip_beta);
+            mb[q] = b1 * mb[q] + (1.0f - b1) * g;
+            vb[q] = b2 * vb[q] + (1.0f - b2) * g * g;
+            float bnew = splits[q].beta + lrb * (mb[q] / bc1) / (sqrtf(vb[q] / bc2) + eps);
+            if (isnan(bnew)) { bnew = 0.0f; mb[q] = 0.0f; vb[q] = 0.0f; }
+            splits[q].beta = fmaxf(bnew, 0.0f);
+        }
+    }
+    free(ga); free(ma); free(va); free(gb); free(mb); free(vb); free(lo); free(hi);
+    return 0;
+}

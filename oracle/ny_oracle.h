@@ -91,6 +91,18 @@ int nyo_bab_bound_batch(const nyo_net *net, const float *in_lo, const float *in_
                         int D, int mode, float *out_lo, float *out_hi, int32_t *infeasible,
                         int n_threads);
 
+/* Lower bounds of the spec rows (binary64, no outward rounding) and the joint gradient of their sum with
+ * respect to alpha (n_pre layout, zero for stable or split neurons) and to every split's beta. */
+int nyo_joint_gradient(const nyo_net *net, const float *in_lo, const float *in_hi, const float *pre_lo,
+                       const float *pre_hi, const nyo_split *splits, int n_splits, const float *alpha,
+                       double *lower_out, float *grad_alpha, float *grad_beta);
+
+/* Projected-Adam optimisation of alpha (in [0,1]) and beta (>= 0) with fixed intermediate bounds; keeps the
+ * element-wise best sound bounds.  alpha and the beta fields of `splits` are updated in place. */
+int nyo_optimize(const nyo_net *net, const float *in_lo, const float *in_hi, const float *pre_lo, const float *pre_hi,
+                 nyo_split *splits, int n_splits, float *alpha, int iterations, float lr_alpha, float lr_beta,
+                 float lr_decay, float clip_beta, float *best_lo, float *best_hi);
+
 /* Largest-width branching choice (first maximum wins, NaN skipped).
  * Returns 1 and fills relu/neuron if an unstable unsplit neuron exists, else 0. */
 int nyo_select_largest_width(const nyo_net *net, const float *pre_lo, const float *pre_hi,

@@ -60,6 +60,10 @@ def lib():
         L.nyo_domain_bounds.argtypes = [np_, fp, fp, fp, fp, C.c_void_p, C.c_int, C.c_int, fp, fp]
         L.nyo_bab_bound_batch.argtypes = [np_, fp, fp, fp, fp, C.c_void_p, ip, C.c_int, C.c_int, C.c_int,
                                           fp, fp, ip, C.c_int]
+        dp = C.POINTER(C.c_double)
+        L.nyo_joint_gradient.argtypes = [np_, fp, fp, fp, fp, C.c_void_p, C.c_int, fp, dp, fp, fp]
+        L.nyo_optimize.argtypes = [np_, fp, fp, fp, fp, C.c_void_p, C.c_int, fp, C.c_int, C.c_float, C.c_float,
+                                   C.c_float, C.c_float, fp, fp]
         L.nyo_select_largest_width.argtypes = [np_, fp, fp, C.c_void_p, C.c_int, ip, ip, fp]
         L.nyo_domain_verified.argtypes = [C.c_float, C.c_float, C.c_float]
         L.nyo_domain_violated.argtypes = [C.c_float, C.c_float, C.c_float]
@@ -185,3 +189,36 @@ def select_largest_width(net: Net, pre_lo, pre_hi, splits: np.ndarray):
     ok = lib().nyo_select_largest_width(C.byref(net.c), _fp(pre_lo), _fp(pre_hi), splits.ctypes.data, len(splits),
                                         C.byref(r), C.byref(j), C.byref(w))
     return (r.value, j.value, w.value) if ok else None
+
+
+def heuristic_alpha(net: Net, pre_lo, pre_hi):
+    """alpha_0 = [u > -l] on unstable neurons (beta_crown/state/alpha/domain.rs:161), n_pre layout."""
+    pre_lo, pre_hi = _f32(pre_lo), _f32(pre_hi)
+    return np.where((pre_lo < 0) & (pre_hi > 0), (pre_hi > -pre_lo).astype(np.float32), 0.0).astype(np.float32)
+
+
+def joint_gradient(net: Net, lo, hi, pre_lo, pre_hi, splits: np.ndarray, alpha=None):
+    """Returns (lower bounds [S] in binary64, grad_alpha [n_pre], grad_beta [n_splits])."""
+    lo, hi, pre_lo, pre_hi = _f32(lo), _f32(hi), _f32(pre_lo), _f32(pre_hi)
+    alpha = None if alpha is None else _f32(alpha)
+    splits = np.ascontiguousarray(splits, SPLIT_DTYPE)
+    S = int(net.dims[-1])
+    low = np.empty(S, np.float64)
+    ga = np.zeros(net.n_pre, np.float32)
+    gb = np.zeros(max(len(splits), 1), np.float32)
+    lib().nyo_joint_gradient(C.byref(net.c), _fp(lo), _fp(hi), _fp(pre_lo), _fp(pre_hi), splits.ctypes.data, len(splits),
+                             _fp(alpha), low.ctypes.data_as(C.POINTER(C.c_double)), _fp(ga), _fp(gb))
+    return low, ga, gb[: len(splits)]
+
+
+def optimize(net: Net, lo, hi, pre_lo, pre_hi, splits: np.ndarray, alpha, iterations, lr_alpha, lr_beta,
+             lr_decay=0.98, clip_beta=10.0):
+    """Returns (best_lo [S], best_hi [S], alpha, splits) after projected-Adam optimisation."""
+    lo, hi, pre_lo, pre_hi = _f32(lo), _f32(hi), _f32(pre_lo), _f32(pre_hi)
+    alpha = _f32(alpha).copy()
+    splits = np.ascontiguousarray(splits, SPLIT_DTYPE).copy()
+    S = int(net.dims[-1])
+    bl, bu = np.empty(S, np.float32), np.empty(S, np.float32)
+    lib().nyo_optimize(C.byref(net.c), _fp(lo), _fp(hi), _fp(pre_lo), _fp(pre_hi), splits.ctypes.data, len(splits),
+                       _fp(alpha), iterations, lr_alpha, lr_beta, lr_decay, clip_beta, _fp(bl), _fp(bu))
+    return bl, bu, alpha, splits

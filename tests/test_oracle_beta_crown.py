@@ -80,3 +80,63 @@ def test_largest_width_first_maximum_wins(oracle):
     assert oracle.select_largest_width(net, pl, pu, oracle.make_splits([(0, 1, 1, 0.0)]))[:2] == (0, 2)
     pl[4], pu[4] = np.nan, np.nan
     assert oracle.select_largest_width(net, pl, pu, oracle.make_splits([(0, 1, 1, 0), (0, 2, -1, 0)]))[:2] == (1, 1)
+
+
+def _one_domain(oracle, seed=9):
+    wl = _small(seed=seed)
+    net = _onet(oracle, wl).with_spec(wl.spec)
+    rl, ru = oracle.ibp_forward(net, wl.in_lo, wl.in_hi)
+    splits, ns = W.draw_domains(wl, rl, ru, 1)
+    sp = splits[0][: ns[0]].copy()
+    sp["beta"] = np.linspace(0.05, 0.3, len(sp)).astype(np.float32)
+    pl, pu, inf = oracle.domain_bounds(net, wl.in_lo, wl.in_hi, rl, ru, sp, 1)
+    assert not inf
+    rng = np.random.default_rng(seed)
+    alpha = np.where((pl < 0) & (pu > 0), rng.uniform(0.2, 0.8, pl.shape), 0.0).astype(np.float32)
+    return wl, net, sp, pl, pu, alpha
+
+
+def test_joint_gradient_matches_central_differences(oracle):
+    """The reference pins its joint alpha gradient by central finite differences
+    (ny-core/src/joint_alpha_grad.rs tests; beta_crown/engine/optimization/gradients tests): same here,
+    for alpha and for beta, against the value the same fold returns."""
+    wl, net, sp, pl, pu, alpha = _one_domain(oracle)
+    low, ga, gb = oracle.joint_gradient(net, wl.in_lo, wl.in_hi, pl, pu, sp, alpha)
+    slo, _ = oracle.beta_crown_bound(net, wl.in_lo, wl.in_hi, pl, pu, sp, alpha)
+    assert np.all(slo <= low + 1e-9) and np.allclose(slo, low, rtol=0, atol=1e-4)
+    h = 1e-3
+    unstable = np.flatnonzero((pl < 0) & (pu > 0) & (ga != 0))
+    assert len(unstable) >= 5
+    for i in unstable[:12]:
+        ap, am = alpha.copy(), alpha.copy()
+        ap[i] += h
+        am[i] -= h
+        fd = (oracle.joint_gradient(net, wl.in_lo, wl.in_hi, pl, pu, sp, ap)[0].sum()
+              - oracle.joint_gradient(net, wl.in_lo, wl.in_hi, pl, pu, sp, am)[0].sum()) / (2 * h)
+        assert abs(fd - ga[i]) <= 1e-3 * max(1.0, abs(fd)), (i, fd, ga[i])
+    for q in range(len(sp)):
+        s1, s2 = sp.copy(), sp.copy()
+        s1["beta"][q] += h
+        s2["beta"][q] -= h
+        fd = (oracle.joint_gradient(net, wl.in_lo, wl.in_hi, pl, pu, s1, alpha)[0].sum()
+              - oracle.joint_gradient(net, wl.in_lo, wl.in_hi, pl, pu, s2, alpha)[0].sum()) / (2 * h)
+        assert abs(fd - gb[q]) <= 1e-3 * max(1.0, abs(fd)), (q, fd, gb[q])
+    # stable and split neurons carry no alpha gradient
+    assert np.all(ga[~((pl < 0) & (pu > 0))] == 0)
+
+
+def test_optimisation_improves_and_stays_sound(oracle):
+    wl, net, sp, pl, pu, alpha = _one_domain(oracle, seed=13)
+    sp["beta"] = 0.0
+    a0 = oracle.heuristic_alpha(net, pl, pu)
+    lo0, hi0 = oracle.beta_crown_bound(net, wl.in_lo, wl.in_hi, pl, pu, sp, a0)
+    bl, bu, a1, s1 = oracle.optimize(net, wl.in_lo, wl.in_hi, pl, pu, sp, a0, 20, 0.1, 0.05)
+    assert np.all(bl >= lo0) and np.all(bu <= hi0)          # element-wise best includes iteration 1
+    assert bl.sum() > lo0.sum()
+    assert np.all((a1 >= 0) & (a1 <= 1)) and np.all(s1["beta"] >= 0)
+    mn = W.sample_min_margin(wl, 4000, 5, sp)
+    ok = np.isfinite(mn)
+    assert np.all(bl[ok] <= mn[ok] + 1e-5)
+    # one iteration is the plain bound
+    bl1, bu1, _, _ = oracle.optimize(net, wl.in_lo, wl.in_hi, pl, pu, sp, a0, 1, 0.1, 0.05)
+    assert np.array_equal(bl1, lo0) and np.array_equal(bu1, hi0)
