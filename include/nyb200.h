@@ -147,6 +147,33 @@ int32_t nyb200_batch_download_pre_bounds(nyb200_engine *e, float *pre_lo, float 
  * relu[d] = -1 when the domain has no unstable unsplit neuron. */
 int32_t nyb200_batch_select_branch(nyb200_engine *e, int32_t *relu, int32_t *neuron, float *width);
 
+/* ---- alpha/beta optimisation of the resident batch ---------------------------------------------
+ * Projected-Adam ascent on every domain's lower slopes alpha (unstable unsplit neurons, kept in [0,1]:
+ * update_alphas_adam, crates/ny-propagate/src/bounds/alpha/shared.rs:106-146) and split multipliers beta
+ * (kept >= 0, gradient clipped: crates/ny-propagate/src/beta_crown/state/beta.rs:314-441), with the
+ * intermediate bounds of the uploaded batch fixed, all domains in lock-step on the device
+ * (the role of crown_backward_gpu_resnet_sound_beta_batched_adam and crown_joint_alpha_gradient_resident,
+ * crates/ny-core/src/gemm.rs:4042,4095).  Iteration t evaluates the sound bounds with the current
+ * parameters, folds them into the element-wise best (network/alpha_crown_loop.rs:928-936), then - except
+ * on the last iteration - steps along the joint gradient of sum_s lower[d][s]
+ * (crates/ny-core/src/joint_alpha_grad.rs:22-50) with learning rate lr * lr_decay^(t-1).
+ * iterations = 1 is exactly nyb200_batch_run.  Asynchronous on the engine stream; nyb200_batch_download
+ * then returns the best bounds, nyb200_batch_download_params the final parameters.  On the fast path,
+ * when the last iterate's rounding charge is visible at nyb200_set_refine_tolerance, the final parameters
+ * are evaluated once more with binary64 contractions and folded into the best bounds. */
+typedef struct nyb200_opt_config {
+    int32_t iterations;  /* >= 1 */
+    float lr_alpha;      /* 0 freezes alpha */
+    float lr_beta;       /* 0 freezes beta */
+    float lr_decay;      /* per-iteration factor, the reference uses 0.98 */
+    float beta1, beta2, epsilon; /* Adam moments; zeros select 0.9, 0.999, 1e-8 */
+    float clip_beta;     /* > 0: beta gradients are clipped to [-clip, clip] (reference: 10) */
+} nyb200_opt_config;
+int32_t nyb200_batch_optimize(nyb200_engine *e, const nyb200_opt_config *cfg);
+/* alpha [D x sum_{k>=1} dims[k]] (meaningful on unstable unsplit neurons) and beta [D x max_splits]
+ * (same order as the uploaded split lists) after the last run.  Either pointer may be NULL. */
+int32_t nyb200_batch_download_params(nyb200_engine *e, float *alpha, float *beta);
+
 /* ---- interval forward pass of ONE box without any device allocation ------------------------------
  * No counterpart in the reference: an addition for hosts that cannot let a library allocate device
  * memory at call time (a service that gave the whole GPU to its own arena at start-up, or a BaB loop

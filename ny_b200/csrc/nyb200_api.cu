@@ -38,15 +38,6 @@ void *ws_get(nyb200_engine *e, const char *name, size_t bytes) {
 
 }  // namespace nyb
 
-#define NYB_TRY(expr)                      \
-    do {                                   \
-        int _st = (expr);                  \
-        if (_st != NYB200_OK) return _st;  \
-    } while (0)
-#define NYB_CUDA(e, call) NYB_TRY(check_cuda((e), (call), #call))
-#define NYB_WS(var, type, e, name, bytes)                          \
-    type var = (type)ws_get((e), (name), (bytes));                 \
-    if (!var) return NYB200_ERR_OOM;
 
 extern "C" {
 
@@ -171,6 +162,8 @@ int32_t nyb200_net_destroy(nyb200_engine *e, int32_t net_id) {
     for (float *p : it->second.owned) cudaFree(p);
     for (auto &u : it->second.umma) { cudaFree(u.wh); cudaFree(u.wl); }
     for (auto &u : it->second.umma_fwd) { cudaFree(u.wh); cudaFree(u.wl); }
+    for (auto &u : it->second.umma_adj) { cudaFree(u.wh); cudaFree(u.wl); }
+    for (float *p : it->second.wt) cudaFree(p);
     e->nets.erase(it);
     if (e->batch.net_id == net_id) e->batch = Batch();
     return NYB200_OK;
@@ -214,7 +207,7 @@ int32_t nyb200_gemm_f32(nyb200_engine *e, int32_t m, int32_t k, int32_t n, const
 }  // extern "C"
 
 // ------------------------------------------------------------------ batch plumbing
-namespace {
+namespace nyb {
 
 // Adds the finished run's event intervals to the accumulators.
 void fold_timing(nyb::Timing &t) {
@@ -238,18 +231,6 @@ cudaEvent_t next_kev(nyb::Timing &t) {
     return t.kev[t.kev_used++];
 }
 
-struct BatchPtrs {
-    float *spec, *in_lo, *in_hi, *inh_lo, *inh_hi, *alpha;
-    nyb200_split *splits;
-    int *nsplits, *flags;
-    signed char *code;
-    float *sbeta, *raw_lo, *raw_hi, *q, *pre_lo, *pre_hi, *zl, *zu, *zabs;
-    float4 *tab;
-    float *A0, *A1;
-    double *rb, *rabs, *rpen;
-    float *out_lo, *out_hi, *min_lower;
-    int lda;
-};
 
 int batch_ptrs(nyb200_engine *e, const Net &net, const Batch &b, BatchPtrs &p) {
     const NetView &nv = net.v;
@@ -347,7 +328,7 @@ int run_forward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int fw
     return NYB200_OK;
 }
 
-int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p) {
+int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, float *const *ckpt, int ld_ckpt) {
     const NetView &nv = net.v;
     const bool tensor = (e->path == NYB200_PATH_TF32X3);
     int *derr = nullptr;
@@ -375,30 +356,39 @@ int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p) {
     };
     auto q_ds = [&](int lin_k) { return (lin_k == 0 && shared_box) ? 0L : np; };
     launch_relax(e, nv, -1, L - 1, M, R, S, cur, p.lda, p.tab, p.zabs, p.q, q_ds(L - 1), eps_for(nv.dims[L]), p.rb,
-                     p.rabs, p.rpen);
+                     p.rabs, p.rpen, nullptr, 0);
     for (int k = L - 1; k >= 0; --k) {
         int K = nv.dims[k + 1], N = nv.dims[k];
         const float *zin_lo, *zin_hi;
         long zin_ds;
         if (k > 0) { zin_lo = p.zl + nv.pre_off[k - 1]; zin_hi = p.zu + nv.pre_off[k - 1]; zin_ds = np; }
         else { zin_lo = p.in_lo; zin_hi = p.in_hi; zin_ds = b.box_stride; }
+        // With checkpoints the product (the coefficients entering ReLU k-1) is kept in its own buffer and
+        // the relaxation writes its result into the ping-pong buffer instead of over its input.
+        float *dst = (ckpt && k > 0) ? ckpt[k - 1] : nxt;
+        int ldd = (ckpt && k > 0) ? ld_ckpt : p.lda;
         if (e->timing.per_kernel) cudaEventRecord(next_kev(e->timing), e->stream);
         if (tensor) {
-            NYB_TRY(launch_umma(e, net.umma[k], M, cur, p.lda, nxt, p.lda, derr));
+            NYB_TRY(launch_umma(e, net.umma[k], M, cur, p.lda, dst, ldd, derr));
         } else {
-            launch_gemm_f64(e, M, N, K, cur, p.lda, nv.W[k], N, nxt, p.lda, R, zin_lo, zin_hi, zin_ds, p.rpen);
+            launch_gemm_f64(e, M, N, K, cur, p.lda, nv.W[k], N, dst, ldd, R, zin_lo, zin_hi, zin_ds, p.rpen);
         }
         if (e->timing.per_kernel) cudaEventRecord(next_kev(e->timing), e->stream);
         if (k > 0)
             launch_relax(e, nv, k - 1, k - 1, M, R, S, nxt, p.lda, p.tab, p.zabs, p.q, q_ds(k - 1), eps_for(N), p.rb, p.rabs,
-                         p.rpen);
+                         p.rpen, dst == nxt ? nullptr : dst, ldd);
         float *t = cur; cur = nxt; nxt = t;
     }
+    p.a_final = cur;
     launch_concretize(e, M, R, S, nv.dims[0], cur, p.lda, p.in_lo, p.in_hi, b.box_stride, p.rb, p.rabs, p.rpen, p.flags,
                       p.out_lo, p.out_hi, p.min_lower, tensor ? e->refine_tol : 0.f);
     NYB_CUDA(e, cudaGetLastError());
     return NYB200_OK;
 }
+
+}  // namespace nyb
+
+namespace {
 
 int upload_batch(nyb200_engine *e, int32_t net_id, const float *spec, int32_t S, const float *in_lo, const float *in_hi,
                  int32_t box_stride, const float *inh_lo, const float *inh_hi, const nyb200_split *splits,
@@ -456,11 +446,12 @@ int run_batch(nyb200_engine *e) {
     cudaEventRecord(t.ev[0], e->stream);
     NYB_TRY(run_forward(e, *net, e->batch, p, e->batch.mode));
     cudaEventRecord(t.ev[1], e->stream);
-    NYB_TRY(run_backward(e, *net, e->batch, p));
+    NYB_TRY(run_backward(e, *net, e->batch, p, nullptr, 0));
     cudaEventRecord(t.ev[2], e->stream);
     t.pending = true;
     e->batch.ran = true;
     e->batch.finished = false;
+    e->batch.optimized = false;
     e->batch.refined = 0;
     return NYB200_OK;
 }
@@ -482,10 +473,14 @@ int finish_batch(nyb200_engine *e) {
     }
     NYB_CUDA(e, cudaStreamSynchronize(e->stream));
     if (herr) return set_err(e, NYB200_ERR_INTERNAL, "tcgen05 pipeline wait expired (code " + std::to_string(herr) + ")");
-    if (loose > 0 && e->path == NYB200_PATH_TF32X3 && e->refine_tol > 0.f) {
+    if (loose > 0 && e->path == NYB200_PATH_TF32X3 && e->refine_tol > 0.f && e->batch.optimized) {
+        NYB_TRY(refine_optimized(e, *net, e->batch, p));
+        NYB_CUDA(e, cudaStreamSynchronize(e->stream));
+        e->batch.refined = loose;
+    } else if (loose > 0 && e->path == NYB200_PATH_TF32X3 && e->refine_tol > 0.f) {
         e->path = NYB200_PATH_F64;
         int st = run_forward(e, *net, e->batch, p, e->batch.mode);
-        if (st == NYB200_OK) st = run_backward(e, *net, e->batch, p);
+        if (st == NYB200_OK) st = run_backward(e, *net, e->batch, p, nullptr, 0);
         e->path = NYB200_PATH_TF32X3;
         NYB_TRY(st);
         NYB_CUDA(e, cudaStreamSynchronize(e->stream));

@@ -46,6 +46,8 @@ struct Net {
     int max_dim = 0;
     std::vector<UmmaLayer> umma;  // filled on first use of the tcgen05 path
     std::vector<UmmaLayer> umma_fwd;  // interval forward operands [W+ | W-] per layer (entry 0 unused)
+    std::vector<float *> wt;          // W_k^T, row-major [dims[k] x dims[k+1]] (adjoint pass; built on first use)
+    std::vector<UmmaLayer> umma_adj;  // tcgen05 operands of the adjoint pass (from wt)
 };
 
 struct DevBuf {
@@ -59,6 +61,7 @@ struct Batch {
     int S = 0, R = 0, D = 0, mode = 0, box_stride = 0, max_splits = 0;
     bool has_alpha = false;
     bool ran = false;
+    bool optimized = false;  // the last run was a parameter optimisation: results are the best-so-far bounds
     bool finished = false;  // results of the last run have been checked (and refined if needed)
     int refined = 0;        // domains that triggered the binary64 re-run of the last batch
 };
@@ -90,6 +93,16 @@ struct nyb200_engine {
     std::map<std::string, nyb::DevBuf> ws;  // named grow-only device workspace
 };
 
+#define NYB_TRY(expr)                      \
+    do {                                   \
+        int _st = (expr);                  \
+        if (_st != NYB200_OK) return _st;  \
+    } while (0)
+#define NYB_CUDA(e, call) NYB_TRY(nyb::check_cuda((e), (call), #call))
+#define NYB_WS(var, type, e, name, bytes)                          \
+    type var = (type)nyb::ws_get((e), (name), (bytes));                 \
+    if (!var) return NYB200_ERR_OOM;
+
 namespace nyb {
 
 // Returns a device buffer of at least `bytes` under `name` (grow-only); nullptr on failure.
@@ -111,9 +124,10 @@ void launch_ibp_finish(nyb200_engine *e, const NetView &nv, int k, int D, int mo
                        double eps = 0.0, float *q = nullptr);
 void launch_seed(nyb200_engine *e, const float *spec, int S, int nL, int D, int lda, float *A);
 // In-place ReLU relaxation of A [M x n] (ReLU r) or identity pass (r < 0), accumulating the row sums.
+// With Asrc != nullptr the rows are read from Asrc (row stride lds) and the result written to A.
 void launch_relax(nyb200_engine *e, const NetView &nv, int r, int lin_k, int M, int R, int S, float *A, int lda,
                   const float4 *tab, const float *zabs, const float *q, long q_dstride, double eps_gemm, double *rb,
-                  double *rabs, double *rpen);
+                  double *rabs, double *rpen, const float *Asrc, int lds);
 // C[M x N] = A[M x K] * W_k (binary64 accumulation), cast error charged to rpen.
 void launch_gemm_f64(nyb200_engine *e, int M, int N, int K, const float *A, int lda, const float *B, int ldb, float *C,
                      int ldc, int R, const float *zin_lo, const float *zin_hi, long zin_dstride, double *rpen);
@@ -123,6 +137,36 @@ void launch_concretize(nyb200_engine *e, int M, int R, int S, int n0, const floa
 void launch_select_branch(nyb200_engine *e, const NetView &nv, int D, const float *pre_lo, const float *pre_hi,
                           const signed char *code, int *relu, int *neuron, float *width);
 void launch_fill_f64(nyb200_engine *e, double *p, size_t n, double v);
+
+// ---- resident batch (nyb200_api.cu) ----
+// Device addresses of the resident batch's arrays (all inside the engine's named workspace).
+struct BatchPtrs {
+    float *spec, *in_lo, *in_hi, *inh_lo, *inh_hi, *alpha;
+    nyb200_split *splits;
+    int *nsplits, *flags;
+    signed char *code;
+    float *sbeta, *raw_lo, *raw_hi, *q, *pre_lo, *pre_hi, *zl, *zu, *zabs;
+    float4 *tab;
+    float *A0, *A1;
+    double *rb, *rabs, *rpen;
+    float *out_lo, *out_hi, *min_lower;
+    int lda;
+    float *a_final = nullptr;  // set by run_backward: the coefficients on the input box, [D*R x lda]
+};
+int batch_ptrs(nyb200_engine *e, const Net &net, const Batch &b, BatchPtrs &p);
+int find_net(nyb200_engine *e, int net_id, Net **out);
+// Interval forward pass for the resident batch.  fwd_mode: 0 clamp-only, 1 constrained, 2 plain IBP.
+int run_forward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int fwd_mode);
+// Backward pass + concretisation.  With ckpt != nullptr, ckpt[r] (row stride ld_ckpt) receives the
+// coefficients entering ReLU r before its relaxation is applied.
+int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, float *const *ckpt, int ld_ckpt);
+void fold_timing(Timing &t);
+cudaEvent_t next_kev(Timing &t);
+
+// ---- parameter optimisation (nyb200_optimize.cu) ----
+int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg);
+int refine_optimized(nyb200_engine *e, Net &net, Batch &b, BatchPtrs &p);
+int download_params(nyb200_engine *e, float *alpha, float *beta);
 
 // ---- tcgen05 contraction (nyb200_umma.cu) ----
 int umma_prepare_layer(nyb200_engine *e, const float *W, int K, int N, UmmaLayer *out);

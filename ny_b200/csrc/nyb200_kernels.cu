@@ -265,7 +265,7 @@ __global__ void k_seed(const float *__restrict__ spec, int S, int nL, int D, int
 // With r < 0 the coefficients are left as they are (seed pass).  In both cases the row then pays for
 // the contraction that follows: bias += a'.bias_k, rpen += eps * |a'| . q_k.
 __global__ void __launch_bounds__(256)
-k_relax(int n, int off, int M, int R, int S, int n_pre, int identity, float *__restrict__ A, int lda,
+k_relax(int n, int off, int M, int R, int S, int n_pre, int identity, float *A, int lda, const float *Asrc, int lds,
         const float4 *__restrict__ tab, const float *__restrict__ zabs, const float *__restrict__ q, long q_ds,
         const float *__restrict__ bias_k, double eps, double *__restrict__ rb, double *__restrict__ rabs,
         double *__restrict__ rpen) {
@@ -274,9 +274,10 @@ k_relax(int n, int off, int M, int R, int S, int n_pre, int identity, float *__r
     int m = warp, d = m / R;
     bool upper = (m % R) >= S;
     float *row = A + (long)m * lda;
+    const float *src = Asrc + (long)m * lds;
     double sb = 0.0, sa = 0.0, sp = 0.0;
     for (int j = lane; j < n; j += 32) {
-        float a = row[j];
+        float a = src[j];
         float nw = a;
         if (!identity) {
             float4 t = tab[(long)d * n_pre + off + j];
@@ -334,11 +335,11 @@ __device__ __forceinline__ float relax_one(float a, float4 t, float za, float qv
 }
 
 template <bool UPPER, bool RELAX, bool BIAS>
-__device__ __forceinline__ void relax_row(int n, int lane, float *__restrict__ row, const float4 *__restrict__ tab,
+__device__ __forceinline__ void relax_row(int n, int lane, float *row, const float *src, const float4 *__restrict__ tab,
                                           const float *__restrict__ zabs, const float *__restrict__ q,
                                           const float *__restrict__ bias_k, float eps, double &sb, float &sa, float &sp) {
     for (int j = lane * 4; j < n; j += 128) {
-        float4 a = *(const float4 *)(row + j);
+        float4 a = *(const float4 *)(src + j);
         float4 qv = *(const float4 *)(q + j);
         float4 bk = BIAS ? *(const float4 *)(bias_k + j) : make_float4(0.f, 0.f, 0.f, 0.f);
         float4 t0 = make_float4(0.f, 0.f, 0.f, 0.f), t1 = t0, t2 = t0, t3 = t0, za = t0;
@@ -357,7 +358,8 @@ __device__ __forceinline__ void relax_row(int n, int lane, float *__restrict__ r
 
 template <bool RELAX, bool BIAS>
 __global__ void __launch_bounds__(256, 4)
-k_relax_v4(int n, int off, int M, int R, int S, long nps, float *__restrict__ A, int lda, const float4 *__restrict__ tab,
+k_relax_v4(int n, int off, int M, int R, int S, long nps, float *A, int lda, const float *Asrc, int lds,
+           const float4 *__restrict__ tab,
            const float *__restrict__ zabs, const float *__restrict__ q, long q_ds, const float *__restrict__ bias_k,
            float eps, double *__restrict__ rb, double *__restrict__ rabs, double *__restrict__ rpen) {
     int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
@@ -365,11 +367,12 @@ k_relax_v4(int n, int off, int M, int R, int S, long nps, float *__restrict__ A,
     int m = warp, d = m / R;
     const bool upper = (m % R) >= S;  // uniform in the warp
     float *row = A + (long)m * lda;
+    const float *src = Asrc + (long)m * lds;  // the row itself when the pass runs in place
     const long tb = (long)d * nps + off, qb = (long)d * q_ds + off;
     double sb = 0.0;
     float sa = 0.f, sp = 0.f;
-    if (upper) relax_row<true, RELAX, BIAS>(n, lane, row, tab + tb, zabs + tb, q + qb, bias_k, eps, sb, sa, sp);
-    else relax_row<false, RELAX, BIAS>(n, lane, row, tab + tb, zabs + tb, q + qb, bias_k, eps, sb, sa, sp);
+    if (upper) relax_row<true, RELAX, BIAS>(n, lane, row, src, tab + tb, zabs + tb, q + qb, bias_k, eps, sb, sa, sp);
+    else relax_row<false, RELAX, BIAS>(n, lane, row, src, tab + tb, zabs + tb, q + qb, bias_k, eps, sb, sa, sp);
     double da = (double)sa, dp = (double)sp;
     sb = warp_sum(sb); da = warp_sum(da); dp = warp_sum(dp);
     if (lane == 0) {  // reductions without a dependent read: the row is owned by this warp for this launch
@@ -637,22 +640,24 @@ void launch_seed(nyb200_engine *e, const float *spec, int S, int nL, int D, int 
 
 void launch_relax(nyb200_engine *e, const NetView &nv, int r, int lin_k, int M, int R, int S, float *A, int lda,
                   const float4 *tab, const float *zabs, const float *q, long q_dstride, double eps_gemm, double *rb,
-                  double *rabs, double *rpen) {
+                  double *rabs, double *rpen, const float *Asrc, int lds) {
     int n = nv.dims[lin_k + 1], off = nv.pre_off[lin_k];
+    if (!Asrc) { Asrc = A; lds = lda; }
     long threads = (long)M * 32;
     unsigned grid = (unsigned)((threads + 255) / 256);
     bool aligned = (n % 4 == 0) && (off % 4 == 0) && (lda % 4 == 0) && (nv.nps % 4 == 0) && (q_dstride % 4 == 0) &&
-                   ((reinterpret_cast<uintptr_t>(A) & 15) == 0);
+                   ((reinterpret_cast<uintptr_t>(A) & 15) == 0) && (lds % 4 == 0) &&
+                   ((reinterpret_cast<uintptr_t>(Asrc) & 15) == 0);
     if (aligned) {
         const float epsf = (float)(eps_gemm * 1.0000002);
         const float *bk = nv.b[lin_k];
 #define NYB_RELAX_LAUNCH(RELAX, BIAS) \
-    k_relax_v4<RELAX, BIAS><<<grid, 256, 0, e->stream>>>(n, off, M, R, S, (long)nv.nps, A, lda, tab, zabs, q, q_dstride, bk, epsf, rb, rabs, rpen)
+    k_relax_v4<RELAX, BIAS><<<grid, 256, 0, e->stream>>>(n, off, M, R, S, (long)nv.nps, A, lda, Asrc, lds, tab, zabs, q, q_dstride, bk, epsf, rb, rabs, rpen)
         if (r >= 0) { if (bk) NYB_RELAX_LAUNCH(true, true); else NYB_RELAX_LAUNCH(true, false); }
         else { if (bk) NYB_RELAX_LAUNCH(false, true); else NYB_RELAX_LAUNCH(false, false); }
 #undef NYB_RELAX_LAUNCH
     } else
-        k_relax<<<grid, 256, 0, e->stream>>>(n, off, M, R, S, nv.nps, r < 0 ? 1 : 0, A, lda, tab, zabs, q, q_dstride,
+        k_relax<<<grid, 256, 0, e->stream>>>(n, off, M, R, S, nv.nps, r < 0 ? 1 : 0, A, lda, Asrc, lds, tab, zabs, q, q_dstride,
                                              nv.b[lin_k], eps_gemm, rb, rabs, rpen);
     NYB_COUNT(e);
 }

@@ -1,0 +1,328 @@
+// Projected-Adam optimisation of the relaxation parameters of the resident batch: every domain's lower
+// slopes alpha and split multipliers beta, all domains in lock-step.
+//
+// One iteration is
+//   1. the sound backward pass (nyb200_api.cu: run_backward) with the current parameters, which also
+//      keeps, per ReLU, the coefficients that entered its relaxation (the "checkpoints");
+//   2. an element-wise best-so-far fold of the bounds (network/alpha_crown_loop.rs:928-936);
+//   3. the reverse adjoint of crates/ny-core/src/joint_alpha_grad.rs:22-50 over the lower rows:
+//        Z^0[s, j]   = x_lo[j] if A^0[s, j] >= 0 else x_hi[j]
+//        Zpre_k      = Z^k W_k^T + b_k                                  (tcgen05 or binary64 contraction)
+//        d/d alpha_i = sum_s Zpre_k[s, i] * max(Apre_k[s, i], 0)        (unstable, unsplit neurons)
+//        d/d beta_i  = -sign_i * sum_s Zpre_k[s, i]                     (split neurons)
+//        Z^{k+1}     = Zpre_k * sigma + tau,  (sigma, tau) = (alpha, 0) if Apre >= 0 else (us, ui)
+//      fused with the Adam step of each parameter (bounds/alpha/shared.rs:106-146 for alpha,
+//      beta_crown/state/beta.rs:314-441 for beta), because a parameter's gradient is complete inside
+//      the one thread that owns its (domain, neuron) pair.
+// The gradient only proposes the next parameters; its arithmetic carries no rounding bookkeeping.  Every
+// bound that is ever reported comes from step 1.
+#include "nyb200_internal.cuh"
+
+namespace nyb {
+
+namespace {
+
+struct AdamStep {
+    float lr_alpha, lr_beta, beta1, beta2, epsilon, bc1, bc2, clip_beta;
+};
+
+__global__ void k_transpose(const float *__restrict__ W, int n_out, int n_in, float *__restrict__ WT) {
+    __shared__ float tile[32][33];
+    int o0 = blockIdx.y * 32, i0 = blockIdx.x * 32;
+    for (int r = threadIdx.y; r < 32; r += 8) {
+        int o = o0 + r, i = i0 + threadIdx.x;
+        tile[r][threadIdx.x] = (o < n_out && i < n_in) ? W[(long)o * n_in + i] : 0.f;
+    }
+    __syncthreads();
+    for (int r = threadIdx.y; r < 32; r += 8) {
+        int i = i0 + r, o = o0 + threadIdx.x;
+        if (i < n_in && o < n_out) WT[(long)i * n_out + o] = tile[threadIdx.x][r];
+    }
+}
+
+// Z[d*S + s][j] = the box corner the lower row (d, s) concretises on.
+__global__ void k_adjoint_seed(int D, int S, int R, int n0, const float *__restrict__ A, int lda,
+                               const float *__restrict__ in_lo, const float *__restrict__ in_hi, long box_ds,
+                               float *__restrict__ Z, int ldz) {
+    long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= (long)D * S * n0) return;
+    int j = (int)(t % n0);
+    long ds = t / n0;
+    int d = (int)(ds / S), s = (int)(ds % S);
+    float a = A[((long)d * R + s) * lda + j];
+    Z[ds * ldz + j] = (a >= 0.f) ? in_lo[(long)d * box_ds + j] : in_hi[(long)d * box_ds + j];
+}
+
+// One thread per (domain, neuron) of ReLU `k`: adds the bias, harvests the parameter gradient over the
+// domain's S lower rows, maps Zpre to the post-activation adjoint in place, then takes the Adam step of the
+// parameter this neuron owns (alpha if unstable and unsplit, beta if split, none otherwise) and writes it
+// into the relaxation table the next backward pass reads.
+__global__ void __launch_bounds__(256)
+k_adjoint_relu(int n, int off, int D, int S, int R, long nps, float *__restrict__ Z, int ldz,
+               const float *__restrict__ bias, const float *__restrict__ Apre, int ldc, float4 *__restrict__ tab,
+               const signed char *__restrict__ code, const float *__restrict__ pre_lo,
+               const float *__restrict__ pre_hi, float *__restrict__ mom, float *__restrict__ var, AdamStep h) {
+    long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= (long)D * n) return;
+    int d = (int)(t / n), i = (int)(t % n);
+    long o = (long)d * nps + off + i;
+    float4 tb = tab[o];
+    float bk = bias ? bias[i] : 0.f;
+    float g_alpha = 0.f, g_sum = 0.f;
+    for (int s = 0; s < S; ++s) {
+        long zr = ((long)d * S + s) * ldz + i;
+        float g = Z[zr] + bk;
+        float ap = Apre[((long)d * R + s) * ldc + i];
+        g_alpha = fmaf(g, fmaxf(ap, 0.f), g_alpha);
+        g_sum += g;
+        bool pos = ap >= 0.f;
+        Z[zr] = fmaf(g, pos ? tb.x : tb.y, pos ? 0.f : tb.z);
+    }
+    int c = code[o];
+    float l = pre_lo[o], u = pre_hi[o];
+    bool is_alpha = (c == 0) && (l < 0.f) && (u > 0.f) && h.lr_alpha > 0.f;
+    bool is_beta = (c != 0) && h.lr_beta > 0.f;
+    if (!is_alpha && !is_beta) return;
+    float g = is_alpha ? g_alpha : (c > 0 ? -g_sum : g_sum);
+    if (is_beta && h.clip_beta > 0.f) g = fminf(fmaxf(g, -h.clip_beta), h.clip_beta);
+    float m = h.beta1 * mom[o] + (1.f - h.beta1) * g;
+    float v = h.beta2 * var[o] + (1.f - h.beta2) * g * g;
+    float step = (m / h.bc1) / (sqrtf(v / h.bc2) + h.epsilon);
+    if (is_alpha) {
+        float a = tb.x + h.lr_alpha * step;
+        a = fminf(fmaxf(a, 0.f), 1.f);
+        if (isnan(a)) { a = 0.5f; m = 0.f; v = 0.f; }
+        tb.x = a;
+    } else {
+        float sgn = c > 0 ? 1.f : -1.f;
+        float b = fabsf(tb.w) + h.lr_beta * step;
+        if (isnan(b)) { b = 0.f; m = 0.f; v = 0.f; }
+        tb.w = sgn * fmaxf(b, 0.f);
+    }
+    mom[o] = m; var[o] = v;
+    tab[o] = tb;
+}
+
+__global__ void k_fold_best(long n, int first, const float *__restrict__ lo, const float *__restrict__ hi,
+                            float *__restrict__ best_lo, float *__restrict__ best_hi) {
+    long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= n) return;
+    float l = lo[t], u = hi[t];
+    if (!first) {
+        // infeasible domains report (+inf, -inf) and degraded ones (-inf, +inf) on every iteration, so
+        // max / min keep those markers
+        l = fmaxf(l, best_lo[t]); u = fminf(u, best_hi[t]);
+    }
+    best_lo[t] = l; best_hi[t] = u;
+}
+
+__device__ __forceinline__ void atomic_min_f(float *addr, float v) {
+    if (v >= 0.f) atomicMin((int *)addr, __float_as_int(v));
+    else atomicMax((unsigned *)addr, __float_as_uint(v));
+}
+
+// Publishes the best bounds as the run's result and folds the global minimum lower bound.
+__global__ void k_publish_best(int D, int S, const int *__restrict__ flags, const float *__restrict__ best_lo,
+                               const float *__restrict__ best_hi, float *__restrict__ out_lo,
+                               float *__restrict__ out_hi, float *__restrict__ min_lower) {
+    int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= D * S) return;
+    float l = best_lo[t];
+    out_lo[t] = l; out_hi[t] = best_hi[t];
+    if (!(flags[t / S] & kFlagInfeasible)) atomic_min_f(min_lower, l);
+}
+
+__global__ void k_gather_params(NetView nv, int D, int max_splits, const float4 *__restrict__ tab,
+                                const nyb200_split *__restrict__ sp, const int *__restrict__ ns,
+                                float *__restrict__ alpha, float *__restrict__ beta) {
+    long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    long na = (long)D * nv.n_pre, nb = (long)D * max_splits;
+    if (t < na) {
+        if (alpha) { int d = (int)(t / nv.n_pre), j = (int)(t % nv.n_pre); alpha[t] = tab[(long)d * nv.nps + j].x; }
+        return;
+    }
+    t -= na;
+    if (t >= nb || !beta) return;
+    int d = (int)(t / max_splits), q = (int)(t % max_splits);
+    float b = 0.f;
+    if (q < ns[d]) {
+        nyb200_split s = sp[t];
+        if (s.relu >= 0 && s.relu < nv.L - 1 && s.neuron >= 0 && s.neuron < nv.dims[s.relu + 1])
+            b = fabsf(tab[(long)d * nv.nps + nv.pre_off[s.relu] + s.neuron].w);
+    }
+    beta[t] = b;
+}
+
+}  // namespace
+
+int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg) {
+    if (!e->batch.valid) return set_err(e, NYB200_ERR_INVALID, "no batch uploaded");
+    if (cfg.iterations < 1) return set_err(e, NYB200_ERR_INVALID, "iterations must be >= 1");
+    if (!(cfg.lr_alpha >= 0.f) || !(cfg.lr_beta >= 0.f) || !(cfg.lr_decay > 0.f))
+        return set_err(e, NYB200_ERR_INVALID, "learning rates must be >= 0 and the decay > 0");
+    Net *net;
+    NYB_TRY(find_net(e, e->batch.net_id, &net));
+    Batch &b = e->batch;
+    BatchPtrs p;
+    NYB_TRY(batch_ptrs(e, *net, b, p));
+    const NetView &nv = net->v;
+    const int L = nv.L, D = b.D, S = b.S, R = b.R;
+    const long M = (long)D * R, np = nv.nps;
+    const bool tensor = e->path == NYB200_PATH_TF32X3;
+    const int T = (L >= 2) ? cfg.iterations : 1;
+    const float b1 = cfg.beta1 > 0.f ? cfg.beta1 : 0.9f, b2 = cfg.beta2 > 0.f ? cfg.beta2 : 0.999f;
+    const float eps = cfg.epsilon > 0.f ? cfg.epsilon : 1e-8f;
+
+    // workspace
+    const int ldc = p.lda, ldz = p.lda;
+    std::vector<float *> ckpt((size_t)(L > 1 ? L - 1 : 0), nullptr);
+    float *z0 = nullptr, *z1 = nullptr, *mom = nullptr, *var = nullptr;
+    if (T > 1) {
+        NYB_WS(ck, float *, e, "ckpt", (size_t)(L - 1) * M * ldc * 4);
+        for (int r = 0; r < L - 1; ++r) ckpt[r] = ck + (size_t)r * M * ldc;
+        z0 = (float *)ws_get(e, "adj0", (size_t)D * S * ldz * 4);
+        z1 = (float *)ws_get(e, "adj1", (size_t)D * S * ldz * 4);
+        mom = (float *)ws_get(e, "adam_m", (size_t)D * np * 4);
+        var = (float *)ws_get(e, "adam_v", (size_t)D * np * 4);
+        if (!z0 || !z1 || !mom || !var) return NYB200_ERR_OOM;
+        if (net->wt.empty()) {
+            net->wt.resize(L, nullptr);
+            for (int k = 0; k < L - 1; ++k) {
+                NYB_CUDA(e, cudaMalloc(&net->wt[k], (size_t)nv.dims[k] * nv.dims[k + 1] * 4));
+                dim3 grid((nv.dims[k] + 31) / 32, (nv.dims[k + 1] + 31) / 32), blk(32, 8);
+                k_transpose<<<grid, blk, 0, e->stream>>>(nv.W[k], nv.dims[k + 1], nv.dims[k], net->wt[k]);
+                e->launches++;
+            }
+        }
+        if (tensor && net->umma_adj.empty()) {
+            net->umma_adj.resize(L);
+            for (int k = 0; k < L - 1; ++k)
+                NYB_TRY(umma_prepare_layer(e, net->wt[k], nv.dims[k], nv.dims[k + 1], &net->umma_adj[k]));
+        }
+        NYB_CUDA(e, cudaMemsetAsync(mom, 0, (size_t)D * np * 4, e->stream));
+        NYB_CUDA(e, cudaMemsetAsync(var, 0, (size_t)D * np * 4, e->stream));
+    }
+    NYB_WS(best_lo, float *, e, "best_lo", (size_t)D * S * 4);
+    NYB_WS(best_hi, float *, e, "best_hi", (size_t)D * S * 4);
+    int *derr = nullptr;
+    if (tensor) {
+        derr = (int *)ws_get(e, "umma_err", 256);
+        if (!derr) return NYB200_ERR_OOM;
+        NYB_CUDA(e, cudaMemsetAsync(derr, 0, 4, e->stream));
+    }
+
+    Timing &tm = e->timing;
+    fold_timing(tm);
+    cudaEventRecord(tm.ev[0], e->stream);
+    NYB_TRY(run_forward(e, *net, b, p, b.mode));
+    cudaEventRecord(tm.ev[1], e->stream);
+    const long nres = (long)D * S;
+    const unsigned gres = (unsigned)((nres + 255) / 256);
+    for (int t = 1; t <= T; ++t) {
+        const bool last = (t == T);
+        NYB_TRY(run_backward(e, *net, b, p, last ? nullptr : ckpt.data(), ldc));
+        k_fold_best<<<gres, 256, 0, e->stream>>>(nres, t == 1, p.out_lo, p.out_hi, best_lo, best_hi);
+        e->launches++;
+        if (last) break;
+        AdamStep h;
+        float decay = powf(cfg.lr_decay, (float)(t - 1));
+        h.lr_alpha = cfg.lr_alpha * decay; h.lr_beta = cfg.lr_beta * decay;
+        h.beta1 = b1; h.beta2 = b2; h.epsilon = eps; h.clip_beta = cfg.clip_beta;
+        h.bc1 = fmaxf(1.f - powf(b1, (float)t), 1.1920929e-7f);
+        h.bc2 = fmaxf(1.f - powf(b2, (float)t), 1.1920929e-7f);
+        long nseed = (long)D * S * nv.dims[0];
+        k_adjoint_seed<<<(unsigned)((nseed + 255) / 256), 256, 0, e->stream>>>(D, S, R, nv.dims[0], p.a_final, p.lda, p.in_lo,
+                                                                              p.in_hi, (long)b.box_stride, z0, ldz);
+        e->launches++;
+        float *zc = z0, *zn = z1;
+        for (int k = 0; k < L - 1; ++k) {
+            int K = nv.dims[k], N = nv.dims[k + 1];
+            if (tensor) NYB_TRY(launch_umma(e, net->umma_adj[k], D * S, zc, ldz, zn, ldz, derr));
+            else launch_gemm_f64(e, D * S, N, K, zc, ldz, net->wt[k], N, zn, ldz, 1, nullptr, nullptr, 0, nullptr);
+            long nt = (long)D * N;
+            k_adjoint_relu<<<(unsigned)((nt + 255) / 256), 256, 0, e->stream>>>(N, nv.pre_off[k], D, S, R, np, zn, ldz, nv.b[k],
+                                                                               ckpt[k], ldc, p.tab, p.code, p.pre_lo,
+                                                                               p.pre_hi, mom, var, h);
+            e->launches++;
+            float *tmp = zc; zc = zn; zn = tmp;
+        }
+    }
+    static const float inf_word = INFINITY;
+    NYB_CUDA(e, cudaMemcpyAsync(p.min_lower, &inf_word, 4, cudaMemcpyHostToDevice, e->stream));
+    k_publish_best<<<gres, 256, 0, e->stream>>>(D, S, p.flags, best_lo, best_hi, p.out_lo, p.out_hi, p.min_lower);
+    e->launches++;
+    NYB_CUDA(e, cudaGetLastError());
+    cudaEventRecord(tm.ev[2], e->stream);
+    tm.pending = true;
+    b.ran = true;
+    b.finished = false;
+    b.optimized = true;
+    b.refined = 0;
+    return NYB200_OK;
+}
+
+// Re-evaluates the final parameters of an optimised batch with binary64 contractions and folds the result
+// into the best bounds (called after the fast path flagged a visible rounding charge on the last iterate).
+int refine_optimized(nyb200_engine *e, Net &net, Batch &b, BatchPtrs &p) {
+    NYB_WS(best_lo, float *, e, "best_lo", (size_t)b.D * b.S * 4);
+    NYB_WS(best_hi, float *, e, "best_hi", (size_t)b.D * b.S * 4);
+    int saved = e->path;
+    e->path = NYB200_PATH_F64;
+    int st = run_backward(e, net, b, p, nullptr, 0);
+    e->path = saved;
+    NYB_TRY(st);
+    const long nres = (long)b.D * b.S;
+    const unsigned gres = (unsigned)((nres + 255) / 256);
+    k_fold_best<<<gres, 256, 0, e->stream>>>(nres, 0, p.out_lo, p.out_hi, best_lo, best_hi);
+    static const float inf_word = INFINITY;
+    NYB_CUDA(e, cudaMemcpyAsync(p.min_lower, &inf_word, 4, cudaMemcpyHostToDevice, e->stream));
+    k_publish_best<<<gres, 256, 0, e->stream>>>(b.D, b.S, p.flags, best_lo, best_hi, p.out_lo, p.out_hi, p.min_lower);
+    e->launches += 2;
+    NYB_CUDA(e, cudaGetLastError());
+    return NYB200_OK;
+}
+
+int download_params(nyb200_engine *e, float *alpha, float *beta) {
+    if (!e->batch.valid || !e->batch.ran) return set_err(e, NYB200_ERR_INVALID, "no batch has been run");
+    Net *net;
+    NYB_TRY(find_net(e, e->batch.net_id, &net));
+    Batch &b = e->batch;
+    BatchPtrs p;
+    NYB_TRY(batch_ptrs(e, *net, b, p));
+    const NetView &nv = net->v;
+    size_t na = (size_t)b.D * nv.n_pre, nb = (size_t)b.D * (size_t)(b.max_splits > 0 ? b.max_splits : 0);
+    float *da = nullptr, *db = nullptr;
+    if (alpha) { da = (float *)ws_get(e, "par_alpha", na * 4); if (!da) return NYB200_ERR_OOM; }
+    if (beta && nb) { db = (float *)ws_get(e, "par_beta", nb * 4); if (!db) return NYB200_ERR_OOM; }
+    size_t total = na + nb;
+    k_gather_params<<<(unsigned)((total + 255) / 256), 256, 0, e->stream>>>(nv, b.D, b.max_splits, p.tab, p.splits, p.nsplits,
+                                                                           da, db);
+    e->launches++;
+    NYB_CUDA(e, cudaGetLastError());
+    if (da) NYB_CUDA(e, cudaMemcpyAsync(alpha, da, na * 4, cudaMemcpyDeviceToHost, e->stream));
+    if (db) NYB_CUDA(e, cudaMemcpyAsync(beta, db, nb * 4, cudaMemcpyDeviceToHost, e->stream));
+    NYB_CUDA(e, cudaStreamSynchronize(e->stream));
+    return NYB200_OK;
+}
+
+}  // namespace nyb
+
+extern "C" {
+
+int32_t nyb200_batch_optimize(nyb200_engine *e, const nyb200_opt_config *cfg) {
+    if (!e || !cfg) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    cudaError_t st = cudaSetDevice(e->device);
+    if (st != cudaSuccess) return nyb::check_cuda(e, st, "cudaSetDevice");
+    return nyb::optimize_batch(e, *cfg);
+}
+
+int32_t nyb200_batch_download_params(nyb200_engine *e, float *alpha, float *beta) {
+    if (!e) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    cudaError_t st = cudaSetDevice(e->device);
+    if (st != cudaSuccess) return nyb::check_cuda(e, st, "cudaSetDevice");
+    return nyb::download_params(e, alpha, beta);
+}
+
+}  // extern "C"

@@ -36,8 +36,14 @@ EXPORTS = [
     "nyb200_net_destroy", "nyb200_ibp_forward", "nyb200_ibp_forward_noalloc", "nyb200_bab_bound_batch", "nyb200_batch_upload", "nyb200_batch_run",
     "nyb200_batch_download", "nyb200_batch_min_lower", "nyb200_batch_min_lower_device",
     "nyb200_batch_download_pre_bounds", "nyb200_batch_select_branch", "nyb200_timing_enable", "nyb200_timing_reset",
-    "nyb200_timing_read",
+    "nyb200_timing_read", "nyb200_batch_optimize", "nyb200_batch_download_params",
 ]
+
+
+class OptConfig(C.Structure):
+    """nyb200_opt_config: projected-Adam settings of nyb200_batch_optimize (zeros select Adam's defaults)."""
+    _fields_ = [("iterations", C.c_int32), ("lr_alpha", C.c_float), ("lr_beta", C.c_float), ("lr_decay", C.c_float),
+                ("beta1", C.c_float), ("beta2", C.c_float), ("epsilon", C.c_float), ("clip_beta", C.c_float)]
 
 
 class EngineError(RuntimeError):
@@ -88,6 +94,8 @@ def load_library():
     L.nyb200_timing_enable.argtypes = [vp, C.c_int32]
     L.nyb200_timing_reset.argtypes = [vp]
     L.nyb200_timing_read.argtypes = [vp, C.c_char_p, C.POINTER(C.c_double), ip]
+    L.nyb200_batch_optimize.argtypes = [vp, C.POINTER(OptConfig)]
+    L.nyb200_batch_download_params.argtypes = [vp, fp, fp]
     _lib = L
     return L
 
@@ -267,9 +275,26 @@ class B200Engine:
         args, keep, D, S = self._batch_args(net_id, spec, in_lo, in_hi, inh_lo, inh_hi, splits, n_splits, mode, alpha)
         self._check(self._L.nyb200_batch_upload(*args))
         self._batch_shape = (D, S, self._nets[net_id].n_pre)
+        self._batch_max_splits = int(np.asarray(splits).shape[1])
 
     def batch_run(self):
         self._check(self._L.nyb200_batch_run(self._h))
+
+    def batch_optimize(self, iterations: int, lr_alpha: float = 0.1, lr_beta: float = 0.05, lr_decay: float = 0.98,
+                       clip_beta: float = 10.0):
+        """alpha/beta projected-Adam optimisation of the resident batch (asynchronous); results through
+        batch_download (element-wise best bounds) and batch_download_params."""
+        cfg = OptConfig(iterations, lr_alpha, lr_beta, lr_decay, 0.0, 0.0, 0.0, clip_beta)
+        self._check(self._L.nyb200_batch_optimize(self._h, C.byref(cfg)))
+
+    def batch_download_params(self):
+        """(alpha [D, n_pre], beta [D, max_splits]) after the last run."""
+        D, _, n_pre = self._batch_shape
+        ms = self._batch_max_splits
+        alpha = np.empty((D, n_pre), np.float32)
+        beta = np.zeros((D, max(ms, 1)), np.float32)
+        self._check(self._L.nyb200_batch_download_params(self._h, _fp(alpha), _fp(beta) if ms > 0 else None))
+        return alpha, beta[:, :ms]
 
     def batch_download(self):
         D, S, _ = self._batch_shape

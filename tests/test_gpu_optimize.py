@@ -1,0 +1,163 @@
+"""GPU parity of the alpha/beta projected-Adam optimisation (nyb200_batch_optimize) against the oracle's loop
+on the same seeded domains.  Both sides evaluate sound bounds with the same parameters trajectory up to
+floating-point noise in the gradient (the device contracts in 3xTF32 or binary64 from fp32 operands, the
+oracle in binary64 throughout), so the optimised bounds are compared at 1e-3 relative (same floor rule as the
+single-pass parity tests) and the one-pass case (iterations = 1) at the single-pass tolerance."""
+import numpy as np
+import pytest
+
+from ny_b200 import workloads as W
+from test_gpu_parity import _rel, _setup, REL_TOL
+
+pytestmark = pytest.mark.gpu
+
+OPT_TOL = 1e-3
+
+
+@pytest.fixture(scope="module", params=["tf32x3", "f64"])
+def eng(request):
+    from ny_b200 import B200Engine, engine
+
+    e = B200Engine(0)
+    e.set_path(engine.PATH_TF32X3 if request.param == "tf32x3" else engine.PATH_F64)
+    e.path_name = request.param
+    yield e
+    e.close()
+
+
+def _oracle_optimize(oracle, ospec, wl, rl, ru, splits, ns, iters, lr_a, lr_b, mode=1):
+    S = wl.spec.shape[0]
+    rl2 = np.concatenate([rl, np.full(S, -np.inf, np.float32)])
+    ru2 = np.concatenate([ru, np.full(S, np.inf, np.float32)])
+    D = len(ns)
+    lo, hi = np.empty((D, S), np.float32), np.empty((D, S), np.float32)
+    inf = np.zeros(D, bool)
+    alphas, betas = [], []
+    for d in range(D):
+        sp = splits[d][: ns[d]]
+        pl, pu, bad = oracle.domain_bounds(ospec, wl.in_lo, wl.in_hi, rl2, ru2, sp, mode)
+        inf[d] = bad
+        if bad:
+            lo[d], hi[d] = np.inf, -np.inf
+            alphas.append(None)
+            betas.append(None)
+            continue
+        a0 = oracle.heuristic_alpha(ospec, pl, pu)
+        lo[d], hi[d], a1, s1 = oracle.optimize(ospec, wl.in_lo, wl.in_hi, pl, pu, sp, a0, iters, lr_a, lr_b)
+        alphas.append((a1, (pl < 0) & (pu > 0)))
+        betas.append(s1["beta"].copy())
+    return lo, hi, inf, alphas, betas
+
+
+def test_one_iteration_is_the_plain_bound(eng, oracle):
+    wl = W.config_mlp_bab(seed=21, hidden=48, depth=3, n_in=64, eps=0.02, n_fix=4)
+    onet, ospec, nid, rl, ru = _setup(eng, oracle, wl)
+    splits, ns = W.draw_domains(wl, rl, ru, 80)
+    eng.batch_upload(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, splits, ns, mode=1)
+    eng.set_refine_tolerance(0.0)  # compare the two entry points on the same contraction path
+    try:
+        eng.batch_run()
+        plain = eng.batch_download()
+        ml = eng.batch_min_lower()
+        eng.batch_optimize(1)
+        got = eng.batch_download()
+    finally:
+        eng.set_refine_tolerance(5e-5)
+    for a, b in zip(plain, got):
+        assert np.array_equal(a, b)
+    assert eng.batch_min_lower() == ml
+    eng.release_network(nid)
+
+
+@pytest.mark.parametrize("cfg", ["small", "mid"])
+def test_optimised_bounds_match_oracle(eng, oracle, cfg):
+    if cfg == "small":
+        wl = W.config_mlp_bab(seed=22, hidden=32, depth=3, n_in=24, eps=0.04, n_fix=3)
+        D, iters = 48, 8
+    else:
+        wl = W.config_mlp_bab(seed=23, hidden=64, depth=4, n_in=196, eps=0.01, n_fix=6)
+        D, iters = 96, 12
+    lr_a, lr_b = 0.1, 0.05
+    onet, ospec, nid, rl, ru = _setup(eng, oracle, wl)
+    splits, ns = W.draw_domains(wl, rl, ru, D)
+    ns = ns.copy()
+    ns[0] = 0
+    eng.batch_upload(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, splits, ns, mode=1)
+    eng.set_refine_tolerance(0.0)  # first iterate on the same contraction path as the optimisation
+    try:
+        eng.batch_run()
+        plo, phi, _ = eng.batch_download()
+    finally:
+        eng.set_refine_tolerance(5e-5)
+    eng.batch_optimize(iters, lr_a, lr_b)
+    glo, ghi, ginf = eng.batch_download()
+    galpha, gbeta = eng.batch_download_params()
+    olo, ohi, oinf, oalpha, obeta = _oracle_optimize(oracle, ospec, wl, rl, ru, splits, ns, iters, lr_a, lr_b)
+    assert np.array_equal(ginf.astype(bool), oinf)
+    feas = ~oinf
+    assert feas.sum() > D // 2
+    # best-so-far never loses against the first iterate, and improves the batch as a whole
+    assert np.all(glo[feas] >= plo[feas]) and np.all(ghi[feas] <= phi[feas])
+    assert glo[feas].sum() > plo[feas].sum()
+    assert _rel(np.concatenate([glo, ghi], axis=1)[feas], np.concatenate([olo, ohi], axis=1)[feas]) <= OPT_TOL
+    # parameters: inside their feasible sets, and close to the oracle's trajectory on average (single neurons
+    # whose gradient is numerically zero may step the other way: Adam normalises the step to +-lr)
+    n_hidden = int(wl.net.dims[1:-1].sum())
+    dev, cnt = 0.0, 0
+    for d in np.flatnonzero(feas):
+        a1, unstable = oalpha[d]
+        m = unstable[:n_hidden].copy()
+        for q in range(ns[d]):
+            m[int(wl.net.dims[1:1 + splits[d][q]["relu"]].sum()) + splits[d][q]["neuron"]] = False
+        ga = galpha[d][:n_hidden][m]
+        assert np.all((ga >= 0) & (ga <= 1))
+        dev += np.abs(ga - a1[:n_hidden][m]).sum()
+        cnt += int(m.sum())
+        assert np.all(gbeta[d][: ns[d]] >= 0)
+        assert np.allclose(gbeta[d][: ns[d]], obeta[d], atol=0.05)
+    assert cnt > 0 and dev / cnt < 0.02
+    eng.release_network(nid)
+
+
+def test_optimised_bounds_stay_sound(eng, oracle):
+    wl = W.config_mlp_bab(seed=24, hidden=48, depth=3, n_in=64, eps=0.03, n_fix=4)
+    onet, ospec, nid, rl, ru = _setup(eng, oracle, wl)
+    splits, ns = W.draw_domains(wl, rl, ru, 16)
+    eng.batch_upload(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, splits, ns, mode=1)
+    eng.batch_optimize(15, 0.1, 0.05)
+    glo, ghi, ginf = eng.batch_download()
+    for d in range(16):
+        if ginf[d]:
+            continue
+        mn = W.sample_min_margin(wl, 100000, 900 + d, splits[d][: ns[d]])
+        ok = np.isfinite(mn)
+        assert np.all(glo[d][ok] <= mn[ok]), d
+    eng.release_network(nid)
+
+
+def test_frozen_parameters_and_bad_configs(eng, oracle):
+    from ny_b200 import EngineError
+
+    wl = W.config_mlp_bab(seed=25, hidden=32, depth=2, n_in=16, eps=0.02, n_fix=2)
+    onet, ospec, nid, rl, ru = _setup(eng, oracle, wl)
+    splits, ns = W.draw_domains(wl, rl, ru, 8)
+    eng.batch_upload(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, splits, ns, mode=1)
+    eng.set_refine_tolerance(0.0)
+    try:
+        eng.batch_run()
+        plain = eng.batch_download()
+        a0, b0 = eng.batch_download_params()
+        eng.batch_optimize(5, 0.0, 0.0)     # both learning rates zero: every iterate is the first one
+        got = eng.batch_download()
+        a1, b1 = eng.batch_download_params()
+    finally:
+        eng.set_refine_tolerance(5e-5)
+    assert np.array_equal(plain[0], got[0]) and np.array_equal(plain[1], got[1])
+    assert np.array_equal(a0, a1) and np.array_equal(b0, b1)
+    for d in range(8):  # the multipliers read back are the uploaded ones
+        assert np.array_equal(b0[d][: ns[d]], np.abs(splits[d]["beta"][: ns[d]]))
+    with pytest.raises(EngineError):
+        eng.batch_optimize(0)
+    with pytest.raises(EngineError):
+        eng.batch_optimize(3, -1.0, 0.0)
+    eng.release_network(nid)
