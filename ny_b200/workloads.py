@@ -87,6 +87,35 @@ def config_mlp_bab(seed: int = 2, hidden: int = 256, depth: int = 8, n_in: int =
                     {"eps": eps, "label": c})
 
 
+def config_alpha_crown(seed: int = 4, hidden: int = 512, depth: int = 9, n_in: int = 784, n_out: int = 10,
+                       eps: float = 0.015) -> Workload:
+    """MLP 784 -> 9x512 -> 10, box x0 +- 0.015 clipped to [0,1], 9 margin rows: the alpha-CROWN optimisation case."""
+    wl = config_mlp_bab(seed=seed, hidden=hidden, depth=depth, n_in=n_in, n_out=n_out, eps=eps, n_fix=0)
+    wl.name = f"alpha_crown_mlp_{n_in}_{depth}x{hidden}_{n_out}"
+    return wl
+
+
+def draw_input_cells(wl: Workload, n_bits: int, first: int = 0, count: int | None = None):
+    """Input-split BaB domains: the root box halved along n_bits seeded coordinates gives 2^n_bits cells;
+    returns the boxes (lo [D, n_in], hi [D, n_in]) of cells first .. first+count-1 (cell index bit b selects the
+    lower or upper half of coordinate dims[b])."""
+    g = _rng(wl.seed * 7919 + 17)
+    n_in = wl.in_lo.shape[0]
+    wide = np.flatnonzero(wl.in_hi > wl.in_lo)
+    dims = g.choice(wide, size=n_bits, replace=False)
+    total = 1 << n_bits
+    count = total - first if count is None else count
+    idx = (np.arange(first, first + count) % total).astype(np.int64)
+    lo = np.repeat(wl.in_lo[None, :], count, axis=0).astype(np.float32)
+    hi = np.repeat(wl.in_hi[None, :], count, axis=0).astype(np.float32)
+    mid = ((wl.in_lo.astype(np.float64) + wl.in_hi.astype(np.float64)) * 0.5).astype(np.float32)
+    for b, j in enumerate(dims):
+        upper = ((idx >> b) & 1).astype(bool)
+        lo[upper, j] = mid[j]
+        hi[~upper, j] = mid[j]
+    return lo, hi
+
+
 def draw_domains(wl: Workload, root_lo: np.ndarray, root_hi: np.ndarray, D: int, first: int = 0):
     """D BaB domains: domain d fixes n_fix neurons drawn without replacement (stream seed+d) from the
     root-unstable set, sign ~ Bernoulli(1/2), beta ~ U(0,1).  Returns (splits [D, n_fix], n_splits [D]).

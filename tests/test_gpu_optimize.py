@@ -161,3 +161,51 @@ def test_frozen_parameters_and_bad_configs(eng, oracle):
     with pytest.raises(EngineError):
         eng.batch_optimize(3, -1.0, 0.0)
     eng.release_network(nid)
+
+
+def test_alpha_crown_full_size_input_cells(eng, oracle):
+    """The alpha-CROWN configuration at full size: MLP 784 -> 9x512 -> 10, 2048 input-split cells of the
+    x0 +- 0.015 box, 20 projected-Adam iterations at lr 0.1.  Size-independent properties on the whole batch,
+    oracle parity and sampled soundness on a few cells."""
+    import copy
+
+    wl = W.config_alpha_crown()
+    onet, ospec, nid, rl, ru = _setup(eng, oracle, wl)
+    D, iters = 2048, 20
+    lo, hi = W.draw_input_cells(wl, 11)
+    sp0 = np.zeros((D, 0), oracle.SPLIT_DTYPE)
+    ns = np.zeros(D, np.int32)
+    eng.batch_upload(nid, wl.spec, lo, hi, rl, ru, sp0, ns, mode=1)
+    eng.set_refine_tolerance(0.0)
+    try:
+        eng.batch_run()
+        plo, phi, pinf = eng.batch_download()
+    finally:
+        eng.set_refine_tolerance(5e-5)
+    eng.batch_optimize(iters, 0.1, 0.0)
+    glo, ghi, ginf = eng.batch_download()
+    alpha, _ = eng.batch_download_params()
+    assert not ginf.any() and np.all(np.isfinite(glo)) and np.all(glo <= ghi)
+    assert np.all(glo >= plo) and np.all(ghi <= phi)
+    assert np.all((alpha >= 0) & (alpha <= 1))
+    gain = (glo - plo).sum(axis=1)
+    assert np.all(gain >= 0) and np.median(gain) > 0
+    # a cell is contained in the root box: its optimised bound can only beat the root's
+    eng.batch_upload(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, np.zeros((1, 0), oracle.SPLIT_DTYPE), np.zeros(1, np.int32))
+    eng.batch_run()
+    root_lo, _, _ = eng.batch_download()
+    assert np.all(glo >= root_lo[0] - 1e-4 * np.abs(root_lo[0]))
+    S = wl.spec.shape[0]
+    rl2 = np.concatenate([rl, np.full(S, -np.inf, np.float32)])
+    ru2 = np.concatenate([ru, np.full(S, np.inf, np.float32)])
+    for d in (0, 777, 2047):
+        pl, pu, bad = oracle.domain_bounds(ospec, lo[d], hi[d], rl2, ru2, sp0[d], 1)
+        assert not bad
+        a0 = oracle.heuristic_alpha(ospec, pl, pu)
+        olo, ohi, _, _ = oracle.optimize(ospec, lo[d], hi[d], pl, pu, sp0[d], a0, iters, 0.1, 0.0)
+        assert _rel(np.concatenate([glo[d], ghi[d]]), np.concatenate([olo, ohi])) <= OPT_TOL, d
+        cell = copy.copy(wl)
+        cell.in_lo, cell.in_hi = lo[d], hi[d]
+        mn = W.sample_min_margin(cell, 100000, 4000 + d)
+        assert np.all(glo[d] <= mn), d
+    eng.release_network(nid)
