@@ -86,6 +86,25 @@ int32_t nyb200_gemm_f32(nyb200_engine *e, int32_t m, int32_t k, int32_t n, const
  * has_bias[k]==0 layers contribute nothing to bflat. */
 int32_t nyb200_net_create(nyb200_engine *e, int32_t n_linear, const int32_t *dims, const float *wflat,
                           const float *bflat, const int32_t *has_bias, int32_t *net_id);
+/* Sequential network of Linear and Conv2d layers, every layer but the last followed by a ReLU: the
+ * Linear / Conv2d members of GpuCrownLayer (crates/ny-core/src/gemm.rs:1524-1600) and of the IBP layer
+ * enum (crates/ny-core/src/gemm_gpu_ibp.rs:31-67).  Tensors are NCHW flattened; a Conv2d layer has
+ * dilation 1 and one group, weights W_col [out_channels x in_channels*kernel_h*kernel_w] row-major and an
+ * optional per-channel bias [out_channels] (expanded on the device).  A Linear layer has weights
+ * [out_features x in_features] and bias [out_features].  wflat / bflat concatenate the layers in order;
+ * layer k's in_features must equal layer k-1's out_features (= out_channels*out_h*out_w for a conv). */
+#define NYB200_LAYER_LINEAR 0
+#define NYB200_LAYER_CONV2D 1
+typedef struct nyb200_layer_desc {
+    int32_t kind;
+    int32_t in_features, out_features;
+    int32_t has_bias;
+    /* Conv2d only (ConvTranspose2dParams, crates/ny-core/src/gemm.rs:150-178) */
+    int32_t in_channels, in_h, in_w, out_channels, out_h, out_w;
+    int32_t kernel_h, kernel_w, stride_h, stride_w, pad_h, pad_w;
+} nyb200_layer_desc;
+int32_t nyb200_net_create_layers(nyb200_engine *e, int32_t n_layers, const nyb200_layer_desc *layers,
+                                 const float *wflat, const float *bflat, int32_t *net_id);
 int32_t nyb200_net_destroy(nyb200_engine *e, int32_t net_id);
 
 /* ---- GpuIbpForward::ibp_forward_gpu_sound (crates/ny-core/src/gemm_gpu_ibp.rs:78-135) ------

@@ -108,48 +108,109 @@ int32_t nyb200_clear_working_set(nyb200_engine *e) {
     return NYB200_OK;
 }
 
-int32_t nyb200_net_create(nyb200_engine *e, int32_t n_linear, const int32_t *dims, const float *wflat,
-                          const float *bflat, const int32_t *has_bias, int32_t *net_id) {
-    if (!e || !dims || !wflat || !has_bias || !net_id) return NYB200_ERR_INVALID;
-    if (n_linear < 1 || n_linear > kMaxLinear) return set_err(e, NYB200_ERR_UNSUPPORTED, "layer count out of range");
-    std::lock_guard<std::mutex> g(e->mu);
+// Expands a per-channel bias to one value per output element (GpuCrownLayer::Conv2d::bias_expanded).
+static void expand_bias(const float *b, int oc, int plane, std::vector<float> &out) {
+    out.resize((size_t)oc * plane);
+    for (int c = 0; c < oc; ++c)
+        for (int i = 0; i < plane; ++i) out[(size_t)c * plane + i] = b[c];
+}
+
+static int create_net(nyb200_engine *e, int32_t n_layers, const nyb200_layer_desc *ld, const float *wflat,
+                      const float *bflat, int32_t *net_id) {
+    if (n_layers < 1 || n_layers > kMaxLinear) return set_err(e, NYB200_ERR_UNSUPPORTED, "layer count out of range");
     NYB_CUDA(e, cudaSetDevice(e->device));
     Net net;
     memset(&net.v, 0, sizeof(net.v));
-    net.v.L = n_linear;
+    net.v.L = n_layers;
+    net.kind.resize(n_layers);
+    net.geom.resize(n_layers);
     int off = 0;
-    for (int k = 0; k <= n_linear; ++k) {
-        if (dims[k] <= 0) return set_err(e, NYB200_ERR_SHAPE, "non-positive layer width");
-        net.v.dims[k] = dims[k];
-        if (dims[k] > net.max_dim) net.max_dim = dims[k];
-        if (k >= 1) { net.v.pre_off[k - 1] = off; off += dims[k]; }
+    for (int k = 0; k < n_layers; ++k) {
+        const nyb200_layer_desc &l = ld[k];
+        if (l.in_features <= 0 || l.out_features <= 0) return set_err(e, NYB200_ERR_SHAPE, "non-positive layer width");
+        if (k > 0 && l.in_features != ld[k - 1].out_features) return set_err(e, NYB200_ERR_SHAPE, "layer widths do not chain");
+        if (l.kind == NYB200_LAYER_CONV2D) {
+            ConvGeom g{l.in_channels, l.in_h, l.in_w, l.out_channels, l.out_h, l.out_w,
+                       l.kernel_h, l.kernel_w, l.stride_h, l.stride_w, l.pad_h, l.pad_w};
+            if (g.ic <= 0 || g.oc <= 0 || g.ih <= 0 || g.iw <= 0 || g.kh <= 0 || g.kw <= 0 || g.sh <= 0 || g.sw <= 0 ||
+                g.ph < 0 || g.pw < 0)
+                return set_err(e, NYB200_ERR_SHAPE, "conv2d: non-positive geometry (zero stride or kernel)");
+            if (g.ih + 2 * g.ph < g.kh || g.iw + 2 * g.pw < g.kw) return set_err(e, NYB200_ERR_SHAPE, "conv2d: kernel larger than the padded input");
+            if (g.oh != (g.ih + 2 * g.ph - g.kh) / g.sh + 1 || g.ow != (g.iw + 2 * g.pw - g.kw) / g.sw + 1)
+                return set_err(e, NYB200_ERR_SHAPE, "conv2d: output size does not match the geometry");
+            if ((long)g.ic * g.ih * g.iw != l.in_features || (long)g.oc * g.oh * g.ow != l.out_features)
+                return set_err(e, NYB200_ERR_SHAPE, "conv2d: flattened sizes do not match the geometry");
+            net.geom[k] = g;
+        } else if (l.kind != NYB200_LAYER_LINEAR) {
+            return set_err(e, NYB200_ERR_UNSUPPORTED, "unknown layer kind");
+        }
+        net.kind[k] = l.kind;
+        if (k == 0) { net.v.dims[0] = l.in_features; net.max_dim = l.in_features; }
+        net.v.dims[k + 1] = l.out_features;
+        if (l.out_features > net.max_dim) net.max_dim = l.out_features;
+        net.v.pre_off[k] = off;
+        off += l.out_features;
     }
-    net.v.pre_off[n_linear] = off;
+    net.v.pre_off[n_layers] = off;
     net.v.n_pre = off;
     net.v.nps = (off + 3) & ~3;
     size_t wo = 0, bo = 0;
-    for (int k = 0; k < n_linear; ++k) {
-        size_t nw = (size_t)dims[k] * dims[k + 1];
+    std::vector<float> expanded;
+    for (int k = 0; k < n_layers; ++k) {
+        const nyb200_layer_desc &l = ld[k];
+        const bool conv = l.kind == NYB200_LAYER_CONV2D;
+        size_t nw = conv ? (size_t)l.out_channels * l.in_channels * l.kernel_h * l.kernel_w
+                         : (size_t)l.in_features * l.out_features;
+        for (size_t i = 0; i < nw; ++i)
+            if (!std::isfinite(wflat[wo + i])) return set_err(e, NYB200_ERR_NUMERICAL, "non-finite weight");
         float *dw = nullptr;
         NYB_CUDA(e, cudaMalloc(&dw, nw * sizeof(float)));
         net.owned.push_back(dw);
         NYB_CUDA(e, cudaMemcpy(dw, wflat + wo, nw * sizeof(float), cudaMemcpyHostToDevice));
         net.v.W[k] = dw;
         wo += nw;
-        if (has_bias[k]) {
+        if (l.has_bias) {
             if (!bflat) return set_err(e, NYB200_ERR_INVALID, "has_bias set but bflat is null");
+            size_t nb = conv ? (size_t)l.out_channels : (size_t)l.out_features;
+            for (size_t i = 0; i < nb; ++i)
+                if (!std::isfinite(bflat[bo + i])) return set_err(e, NYB200_ERR_NUMERICAL, "non-finite bias");
+            const float *src = bflat + bo;
+            if (conv) { expand_bias(bflat + bo, l.out_channels, l.out_h * l.out_w, expanded); src = expanded.data(); }
             float *db = nullptr;
-            NYB_CUDA(e, cudaMalloc(&db, (size_t)dims[k + 1] * sizeof(float)));
+            NYB_CUDA(e, cudaMalloc(&db, (size_t)l.out_features * sizeof(float)));
             net.owned.push_back(db);
-            NYB_CUDA(e, cudaMemcpy(db, bflat + bo, (size_t)dims[k + 1] * sizeof(float), cudaMemcpyHostToDevice));
+            NYB_CUDA(e, cudaMemcpy(db, src, (size_t)l.out_features * sizeof(float), cudaMemcpyHostToDevice));
             net.v.b[k] = db;
-            bo += dims[k + 1];
+            bo += nb;
         }
     }
     int id = e->next_net++;
     e->nets[id] = net;
     *net_id = id;
     return NYB200_OK;
+}
+
+int32_t nyb200_net_create(nyb200_engine *e, int32_t n_linear, const int32_t *dims, const float *wflat,
+                          const float *bflat, const int32_t *has_bias, int32_t *net_id) {
+    if (!e || !dims || !wflat || !has_bias || !net_id) return NYB200_ERR_INVALID;
+    if (n_linear < 1 || n_linear > kMaxLinear) return set_err(e, NYB200_ERR_UNSUPPORTED, "layer count out of range");
+    std::lock_guard<std::mutex> g(e->mu);
+    std::vector<nyb200_layer_desc> ld((size_t)n_linear);
+    for (int k = 0; k < n_linear; ++k) {
+        memset(&ld[k], 0, sizeof(ld[k]));
+        ld[k].kind = NYB200_LAYER_LINEAR;
+        ld[k].in_features = dims[k];
+        ld[k].out_features = dims[k + 1];
+        ld[k].has_bias = has_bias[k];
+    }
+    return create_net(e, n_linear, ld.data(), wflat, bflat, net_id);
+}
+
+int32_t nyb200_net_create_layers(nyb200_engine *e, int32_t n_layers, const nyb200_layer_desc *layers,
+                                 const float *wflat, const float *bflat, int32_t *net_id) {
+    if (!e || !layers || !wflat || !net_id) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    return create_net(e, n_layers, layers, wflat, bflat, net_id);
 }
 
 int32_t nyb200_net_destroy(nyb200_engine *e, int32_t net_id) {
@@ -294,10 +355,13 @@ int run_forward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int fw
         if (net.umma_fwd.empty()) {
             net.umma_fwd.resize(nv.L);
             for (int k = 1; k < nv.L; ++k)
-                NYB_TRY(umma_prepare_forward_layer(e, nv.W[k], nv.dims[k], nv.dims[k + 1], &net.umma_fwd[k]));
+                if (!net.is_conv(k))
+                    NYB_TRY(umma_prepare_forward_layer(e, nv.W[k], nv.dims[k], nv.dims[k + 1], &net.umma_fwd[k]));
         }
         int mo = 0;
-        for (int k = 2; k <= nv.L; ++k) mo = nv.dims[k] > mo ? nv.dims[k] : mo;
+        for (int k = 1; k < nv.L; ++k)
+            if (!net.is_conv(k)) mo = nv.dims[k + 1] > mo ? nv.dims[k + 1] : mo;
+        if (mo == 0) mo = 8;
         ldf = (2 * mo + 7) & ~7;
         Fl = (float *)ws_get(e, "fwd", (size_t)2 * D * ldf * 4);
         derr = (int *)ws_get(e, "umma_err", 256);
@@ -315,8 +379,9 @@ int run_forward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int fw
         int Deff;
         if (k == 0) { zl = p.in_lo; zu = p.in_hi; in_ds = b.box_stride; Deff = b.box_stride ? D : 1; }
         else { zl = p.zl + nv.pre_off[k - 1]; zu = p.zu + nv.pre_off[k - 1]; in_ds = (long)np; Deff = D; }
-        const bool tk = tensor && k >= 1;
+        const bool tk = tensor && k >= 1 && !net.is_conv(k);
         if (tk) NYB_TRY(launch_umma(e, net.umma_fwd[k], 2 * D, zl, (int)np, Fl, ldf, derr));  // zl rows, then zu rows
+        else if (net.is_conv(k)) launch_ibp_conv(e, nv, net.geom[k], k, Deff, zl, zu, in_ds, p.raw_lo, p.raw_hi, p.q, (long)np);
         else launch_ibp_linear(e, nv, k, Deff, zl, zu, in_ds, p.raw_lo, p.raw_hi, p.q, (long)np);
         long raw_ds = (Deff == 1 && D > 1) ? 0 : (long)np;
         launch_ibp_finish(e, nv, k, D, fwd_mode, p.raw_lo, p.raw_hi, raw_ds, fwd_mode == 2 ? nullptr : p.inh_lo,
@@ -335,7 +400,8 @@ int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, float
     if (tensor) {
         if (net.umma.empty()) {
             net.umma.resize(nv.L);
-            for (int k = 0; k < nv.L; ++k) NYB_TRY(umma_prepare_layer(e, nv.W[k], nv.dims[k + 1], nv.dims[k], &net.umma[k]));
+            for (int k = 0; k < nv.L; ++k)
+                if (!net.is_conv(k)) NYB_TRY(umma_prepare_layer(e, nv.W[k], nv.dims[k + 1], nv.dims[k], &net.umma[k]));
         }
         derr = (int *)ws_get(e, "umma_err", 256);
         if (!derr) return NYB200_ERR_OOM;
@@ -351,11 +417,14 @@ int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, float
     NYB_CUDA(e, cudaMemcpyAsync(p.min_lower, init_words, sizeof(init_words), cudaMemcpyHostToDevice, e->stream));
     float *cur = p.A0, *nxt = p.A1;
     launch_seed(e, p.spec, S, nv.dims[L], D, p.lda, cur);
-    auto eps_for = [&](int K) {
-        return tensor ? umma_eps(K) * 1.000001 : (double)(K + 2) * 1.1102230246251565e-16 * 1.000001;
+    // rounding rate of the contraction through layer `lin` (accumulation length dims[lin + 1]); convolutions
+    // accumulate in binary64 on both paths
+    auto eps_for = [&](int lin) {
+        int K = nv.dims[lin + 1];
+        return (tensor && !net.is_conv(lin)) ? umma_eps(K) * 1.000001 : (double)(K + 2) * 1.1102230246251565e-16 * 1.000001;
     };
     auto q_ds = [&](int lin_k) { return (lin_k == 0 && shared_box) ? 0L : np; };
-    launch_relax(e, nv, -1, L - 1, M, R, S, cur, p.lda, p.tab, p.zabs, p.q, q_ds(L - 1), eps_for(nv.dims[L]), p.rb,
+    launch_relax(e, nv, -1, L - 1, M, R, S, cur, p.lda, p.tab, p.zabs, p.q, q_ds(L - 1), eps_for(L - 1), p.rb,
                      p.rabs, p.rpen, nullptr, 0);
     for (int k = L - 1; k >= 0; --k) {
         int K = nv.dims[k + 1], N = nv.dims[k];
@@ -368,14 +437,16 @@ int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, float
         float *dst = (ckpt && k > 0) ? ckpt[k - 1] : nxt;
         int ldd = (ckpt && k > 0) ? ld_ckpt : p.lda;
         if (e->timing.per_kernel) cudaEventRecord(next_kev(e->timing), e->stream);
-        if (tensor) {
+        if (net.is_conv(k)) {
+            launch_conv_transpose(e, net.geom[k], M, cur, p.lda, dst, ldd, nv.W[k], R, zin_lo, zin_hi, zin_ds, p.rpen);
+        } else if (tensor) {
             NYB_TRY(launch_umma(e, net.umma[k], M, cur, p.lda, dst, ldd, derr));
         } else {
             launch_gemm_f64(e, M, N, K, cur, p.lda, nv.W[k], N, dst, ldd, R, zin_lo, zin_hi, zin_ds, p.rpen);
         }
         if (e->timing.per_kernel) cudaEventRecord(next_kev(e->timing), e->stream);
         if (k > 0)
-            launch_relax(e, nv, k - 1, k - 1, M, R, S, nxt, p.lda, p.tab, p.zabs, p.q, q_ds(k - 1), eps_for(N), p.rb, p.rabs,
+            launch_relax(e, nv, k - 1, k - 1, M, R, S, nxt, p.lda, p.tab, p.zabs, p.q, q_ds(k - 1), eps_for(k - 1), p.rb, p.rabs,
                          p.rpen, dst == nxt ? nullptr : dst, ldd);
         float *t = cur; cur = nxt; nxt = t;
     }

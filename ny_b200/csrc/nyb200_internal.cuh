@@ -31,6 +31,11 @@ struct NetView {
     const float *b[kMaxLinear];   // device or nullptr
 };
 
+// Geometry of a Conv2d layer (NCHW flattened, dilation 1, one group).
+struct ConvGeom {
+    int ic, ih, iw, oc, oh, ow, kh, kw, sh, sw, ph, pw;
+};
+
 // Per-layer operands of the tcgen05 contraction: W split into TF32 high/low parts, transposed to
 // [N x kpad] (K contiguous, zero padded to a multiple of 32) with one TMA tensor map each.
 struct UmmaLayer {
@@ -44,6 +49,9 @@ struct Net {
     NetView v;
     std::vector<float *> owned;
     int max_dim = 0;
+    std::vector<int> kind;        // per layer: NYB200_LAYER_LINEAR or NYB200_LAYER_CONV2D
+    std::vector<ConvGeom> geom;   // per layer; meaningful for conv layers
+    bool is_conv(int k) const { return !kind.empty() && kind[k] == NYB200_LAYER_CONV2D; }
     std::vector<UmmaLayer> umma;  // filled on first use of the tcgen05 path
     std::vector<UmmaLayer> umma_fwd;  // interval forward operands [W+ | W-] per layer (entry 0 unused)
     std::vector<float *> wt;          // W_k^T, row-major [dims[k] x dims[k+1]] (adjoint pass; built on first use)
@@ -167,6 +175,16 @@ cudaEvent_t next_kev(Timing &t);
 int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg);
 int refine_optimized(nyb200_engine *e, Net &net, Batch &b, BatchPtrs &p);
 int download_params(nyb200_engine *e, float *alpha, float *beta);
+
+// ---- Conv2d layers (nyb200_conv.cu) ----
+void launch_ibp_conv(nyb200_engine *e, const NetView &nv, const ConvGeom &g, int k, int Deff, const float *zl,
+                     const float *zu, long in_dstride, float *raw_lo, float *raw_hi, float *q, long out_dstride);
+// C[M x ic*ih*iw] = transposed convolution of A[M x oc*oh*ow] (binary64 accumulation, cast error charged to rpen).
+void launch_conv_transpose(nyb200_engine *e, const ConvGeom &g, int M, const float *A, int lda, float *C, int ldc,
+                           const float *W, int R, const float *zin_lo, const float *zin_hi, long zin_dstride,
+                           double *rpen);
+void launch_conv_plain(nyb200_engine *e, const ConvGeom &g, int rows, const float *Z, int ldz, const float *W, float *out,
+                       int ldo);
 
 // ---- tcgen05 contraction (nyb200_umma.cu) ----
 int umma_prepare_layer(nyb200_engine *e, const float *W, int K, int N, UmmaLayer *out);

@@ -188,6 +188,7 @@ int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg) {
         if (net->wt.empty()) {
             net->wt.resize(L, nullptr);
             for (int k = 0; k < L - 1; ++k) {
+                if (net->is_conv(k)) continue;  // the adjoint of a convolution runs the forward convolution
                 NYB_CUDA(e, cudaMalloc(&net->wt[k], (size_t)nv.dims[k] * nv.dims[k + 1] * 4));
                 dim3 grid((nv.dims[k] + 31) / 32, (nv.dims[k + 1] + 31) / 32), blk(32, 8);
                 k_transpose<<<grid, blk, 0, e->stream>>>(nv.W[k], nv.dims[k + 1], nv.dims[k], net->wt[k]);
@@ -197,7 +198,7 @@ int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg) {
         if (tensor && net->umma_adj.empty()) {
             net->umma_adj.resize(L);
             for (int k = 0; k < L - 1; ++k)
-                NYB_TRY(umma_prepare_layer(e, net->wt[k], nv.dims[k], nv.dims[k + 1], &net->umma_adj[k]));
+                if (!net->is_conv(k)) NYB_TRY(umma_prepare_layer(e, net->wt[k], nv.dims[k], nv.dims[k + 1], &net->umma_adj[k]));
         }
         NYB_CUDA(e, cudaMemsetAsync(mom, 0, (size_t)D * np * 4, e->stream));
         NYB_CUDA(e, cudaMemsetAsync(var, 0, (size_t)D * np * 4, e->stream));
@@ -237,7 +238,8 @@ int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg) {
         float *zc = z0, *zn = z1;
         for (int k = 0; k < L - 1; ++k) {
             int K = nv.dims[k], N = nv.dims[k + 1];
-            if (tensor) NYB_TRY(launch_umma(e, net->umma_adj[k], D * S, zc, ldz, zn, ldz, derr));
+            if (net->is_conv(k)) launch_conv_plain(e, net->geom[k], D * S, zc, ldz, nv.W[k], zn, ldz);
+            else if (tensor) NYB_TRY(launch_umma(e, net->umma_adj[k], D * S, zc, ldz, zn, ldz, derr));
             else launch_gemm_f64(e, D * S, N, K, zc, ldz, net->wt[k], N, zn, ldz, 1, nullptr, nullptr, 0, nullptr);
             long nt = (long)D * N;
             k_adjoint_relu<<<(unsigned)((nt + 255) / 256), 256, 0, e->stream>>>(N, nv.pre_off[k], D, S, R, np, zn, ldz, nv.b[k],

@@ -37,6 +37,7 @@ EXPORTS = [
     "nyb200_batch_download", "nyb200_batch_min_lower", "nyb200_batch_min_lower_device",
     "nyb200_batch_download_pre_bounds", "nyb200_batch_select_branch", "nyb200_timing_enable", "nyb200_timing_reset",
     "nyb200_timing_read", "nyb200_batch_optimize", "nyb200_batch_download_params",
+    "nyb200_net_create_layers",
 ]
 
 
@@ -79,6 +80,7 @@ def load_library():
     L.nyb200_clear_working_set.argtypes = [vp]
     L.nyb200_gemm_f32.argtypes = [vp, C.c_int32, C.c_int32, C.c_int32, fp, fp, fp]
     L.nyb200_net_create.argtypes = [vp, C.c_int32, ip, fp, fp, ip, ip]
+    L.nyb200_net_create_layers.argtypes = [vp, C.c_int32, C.POINTER(LayerDesc), fp, fp, ip]
     L.nyb200_net_destroy.argtypes = [vp, C.c_int32]
     L.nyb200_ibp_forward.argtypes = [vp, C.c_int32, C.c_int32, fp, fp, C.c_int32, fp, fp]
     L.nyb200_ibp_forward_noalloc.argtypes = [vp, C.c_int32, vp, vp, vp, vp]
@@ -112,18 +114,87 @@ def _f32(a):
     return np.ascontiguousarray(a, dtype=np.float32)
 
 
+class LayerDesc(C.Structure):
+    """nyb200_layer_desc."""
+    _fields_ = [(n, C.c_int32) for n in (
+        "kind", "in_features", "out_features", "has_bias", "in_channels", "in_h", "in_w", "out_channels", "out_h",
+        "out_w", "kernel_h", "kernel_w", "stride_h", "stride_w", "pad_h", "pad_w")]
+
+
+class Conv2d:
+    """Conv2d layer description (host side): weight [oc, ic, kh, kw], optional per-channel bias [oc]; tensors
+    are NCHW flattened, dilation 1, one group (the Conv2d member of GpuCrownLayer)."""
+
+    def __init__(self, weight, bias=None, stride=(1, 1), pad=(0, 0), in_hw=None):
+        self.weight = _f32(weight)
+        if self.weight.ndim != 4:
+            raise EngineError(SHAPE, "conv2d kernel must be 4-D [oc, ic, kh, kw]")
+        if in_hw is None:
+            raise EngineError(SHAPE, "conv2d needs its input height and width")
+        self.oc, self.ic, self.kh, self.kw = (int(x) for x in self.weight.shape)
+        self.sh, self.sw = int(stride[0]), int(stride[1])
+        self.ph, self.pw = int(pad[0]), int(pad[1])
+        self.ih, self.iw = int(in_hw[0]), int(in_hw[1])
+        if min(self.sh, self.sw) <= 0 or min(self.kh, self.kw) <= 0:
+            raise EngineError(SHAPE, "conv2d: zero stride or kernel")
+        if self.ih + 2 * self.ph < self.kh or self.iw + 2 * self.pw < self.kw:
+            raise EngineError(SHAPE, "conv2d: kernel larger than the padded input")
+        self.oh = (self.ih + 2 * self.ph - self.kh) // self.sh + 1
+        self.ow = (self.iw + 2 * self.pw - self.kw) // self.sw + 1
+        self.bias = None if bias is None else _f32(bias)
+        if self.bias is not None and self.bias.shape != (self.oc,):
+            raise EngineError(SHAPE, "conv2d bias must be [oc]")
+        self.in_features = self.ic * self.ih * self.iw
+        self.out_features = self.oc * self.oh * self.ow
+
+    def apply(self, x: np.ndarray) -> np.ndarray:
+        """Concrete forward convolution of rows x [N, in_features] in binary64 (used by sampling checks)."""
+        x = np.asarray(x, np.float64).reshape(-1, self.ic, self.ih, self.iw)
+        xp = np.pad(x, ((0, 0), (0, 0), (self.ph, self.ph), (self.pw, self.pw)))
+        win = np.lib.stride_tricks.sliding_window_view(xp, (self.kh, self.kw), axis=(2, 3))
+        win = win[:, :, :: self.sh, :: self.sw][:, :, : self.oh, : self.ow]
+        y = np.einsum("nchwyx,ocyx->nohw", win, self.weight.astype(np.float64), optimize=True)
+        if self.bias is not None:
+            y = y + self.bias.astype(np.float64)[None, :, None, None]
+        return y.reshape(x.shape[0], self.out_features)
+
+    def desc(self) -> LayerDesc:
+        return LayerDesc(1, self.in_features, self.out_features, 0 if self.bias is None else 1, self.ic, self.ih, self.iw,
+                         self.oc, self.oh, self.ow, self.kh, self.kw, self.sh, self.sw, self.ph, self.pw)
+
+
 class Network:
-    """Sequential ReLU MLP description (host side): weights[k] is [out, in] row-major."""
+    """Sequential ReLU network description (host side): weights[k] is a [out, in] row-major matrix (Linear) or a
+    Conv2d; every layer but the last is followed by a ReLU."""
 
     def __init__(self, weights, biases=None):
-        self.weights = [_f32(w) for w in weights]
+        self.weights = [w if isinstance(w, Conv2d) else _f32(w) for w in weights]
         L = len(self.weights)
         biases = biases if biases is not None else [None] * L
-        self.biases = [None if b is None else _f32(b) for b in biases]
-        self.dims = np.array([self.weights[0].shape[1]] + [w.shape[0] for w in self.weights], dtype=np.int32)
+        self.biases = [w.bias if isinstance(w, Conv2d) else (None if b is None else _f32(b))
+                       for w, b in zip(self.weights, biases)]
+        first = self.weights[0]
+        n0 = first.in_features if isinstance(first, Conv2d) else first.shape[1]
+        self.dims = np.array([n0] + [w.out_features if isinstance(w, Conv2d) else w.shape[0] for w in self.weights],
+                             dtype=np.int32)
         for k, w in enumerate(self.weights):
-            if w.shape != (self.dims[k + 1], self.dims[k]):
+            if isinstance(w, Conv2d):
+                if w.in_features != self.dims[k]:
+                    raise EngineError(SHAPE, f"layer {k}: conv input size {w.in_features} != {self.dims[k]}")
+            elif w.shape != (self.dims[k + 1], self.dims[k]):
                 raise EngineError(SHAPE, f"layer {k}: weight shape {w.shape}")
+
+    @property
+    def has_conv(self) -> bool:
+        return any(isinstance(w, Conv2d) for w in self.weights)
+
+    def layer_forward(self, k: int, z: np.ndarray) -> np.ndarray:
+        """Concrete image of rows z under layer k (binary64, bias included, no activation)."""
+        w = self.weights[k]
+        if isinstance(w, Conv2d):
+            return w.apply(z)
+        z = z @ w.astype(np.float64).T
+        return z if self.biases[k] is None else z + self.biases[k].astype(np.float64)
 
     @property
     def n_pre(self) -> int:
@@ -194,6 +265,8 @@ class B200Engine:
 
     # -- network residency -----------------------------------------------------------------
     def register_network(self, net: Network) -> int:
+        if net.has_conv:
+            return self._register_layers(net)
         w = np.concatenate([x.ravel() for x in net.weights]).astype(np.float32)
         bl = [b for b in net.biases if b is not None]
         b = np.concatenate(bl).astype(np.float32) if bl else np.zeros(1, np.float32)
@@ -201,6 +274,25 @@ class B200Engine:
         nid = C.c_int32(0)
         self._check(self._L.nyb200_net_create(self._h, len(net.weights), _ip(net.dims), _fp(w), _fp(b), _ip(hb),
                                               C.byref(nid)))
+        self._nets[nid.value] = net
+        return nid.value
+
+    def _register_layers(self, net: Network) -> int:
+        descs = (LayerDesc * len(net.weights))()
+        ws, bs = [], []
+        for k, w in enumerate(net.weights):
+            if isinstance(w, Conv2d):
+                descs[k] = w.desc()
+                ws.append(w.weight.ravel())
+            else:
+                descs[k] = LayerDesc(0, w.shape[1], w.shape[0], 0 if net.biases[k] is None else 1)
+                ws.append(w.ravel())
+            if net.biases[k] is not None:
+                bs.append(net.biases[k])
+        wf = np.concatenate(ws).astype(np.float32)
+        bf = np.concatenate(bs).astype(np.float32) if bs else np.zeros(1, np.float32)
+        nid = C.c_int32(0)
+        self._check(self._L.nyb200_net_create_layers(self._h, len(net.weights), descs, _fp(wf), _fp(bf), C.byref(nid)))
         self._nets[nid.value] = net
         return nid.value
 

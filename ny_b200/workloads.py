@@ -11,7 +11,7 @@ from dataclasses import dataclass, field
 
 import numpy as np
 
-from .engine import SPLIT_DTYPE, Network
+from .engine import SPLIT_DTYPE, Conv2d, Network
 
 
 def _rng(seed: int) -> np.random.Generator:
@@ -31,13 +31,14 @@ def make_mlp(dims, seed: int) -> Network:
 
 def forward(net: Network, x) -> np.ndarray:
     z = np.asarray(x, np.float64)
-    for k, w in enumerate(net.weights):
-        z = z @ w.astype(np.float64).T
-        if net.biases[k] is not None:
-            z = z + net.biases[k].astype(np.float64)
+    one = z.ndim == 1
+    if one:
+        z = z[None, :]
+    for k in range(len(net.weights)):
+        z = net.layer_forward(k, z)
         if k + 1 < len(net.weights):
             z = np.maximum(z, 0.0)
-    return z
+    return z[0] if one else z
 
 
 def margin_spec(n_out: int, c: int) -> np.ndarray:
@@ -84,6 +85,43 @@ def config_mlp_bab(seed: int = 2, hidden: int = 256, depth: int = 8, n_in: int =
     hi = np.clip(x0 + np.float32(eps), 0, 1).astype(np.float32)
     c = int(np.argmax(forward(net, x0)))
     return Workload(f"mlp_{n_in}_{depth}x{hidden}_{n_out}", net, x0, lo, hi, margin_spec(n_out, c), n_fix, seed,
+                    {"eps": eps, "label": c})
+
+
+def make_cnn(seed: int, in_chw=(3, 32, 32), convs=((16, 4, 2, 1), (32, 4, 2, 1)), fcs=(100, 10)) -> Network:
+    """Conv layers (out_channels, kernel, stride, pad) then fully connected widths; He-initialised fp32
+    (weights N(0, 2/fan_in), biases N(0, 0.01))."""
+    g = _rng(seed)
+    c, h, w = in_chw
+    layers = []
+    for (oc, k, s, p) in convs:
+        fan_in = c * k * k
+        wt = (g.standard_normal((oc, c, k, k)) * np.sqrt(2.0 / fan_in)).astype(np.float32)
+        b = (g.standard_normal(oc) * 0.1).astype(np.float32)
+        conv = Conv2d(wt, b, (s, s), (p, p), (h, w))
+        layers.append(conv)
+        c, h, w = oc, conv.oh, conv.ow
+    n = c * h * w
+    ws, bs = list(layers), [None] * len(layers)
+    for width in fcs:
+        ws.append((g.standard_normal((width, n)) * np.sqrt(2.0 / n)).astype(np.float32))
+        bs.append((g.standard_normal(width) * 0.1).astype(np.float32))
+        n = width
+    return Network(ws, bs)
+
+
+def config_cnn(seed: int = 3, eps: float = 2.0 / 255.0, n_fix: int = 8, **kw) -> Workload:
+    """CNN on 3x32x32: conv(16,k4,s2,p1)-ReLU, conv(32,k4,s2,p1)-ReLU, FC 2048->100-ReLU, FC 100->10; box
+    x0 +- 2/255 with x0 ~ U(0,1) clipped to [0,1]; 9 margin rows."""
+    net = make_cnn(seed, **kw)
+    g = _rng(seed + 1000)
+    n_in = int(net.dims[0])
+    x0 = g.uniform(0, 1, n_in).astype(np.float32)
+    lo = np.clip(x0 - np.float32(eps), 0, 1).astype(np.float32)
+    hi = np.clip(x0 + np.float32(eps), 0, 1).astype(np.float32)
+    c = int(np.argmax(forward(net, x0)))
+    n_out = int(net.dims[-1])
+    return Workload("cnn_" + "_".join(str(int(d)) for d in net.dims), net, x0, lo, hi, margin_spec(n_out, c), n_fix, seed,
                     {"eps": eps, "label": c})
 
 
@@ -156,8 +194,8 @@ def sample_min_margin(wl: Workload, n_samples: int, seed: int, splits=None, chun
         x = wl.in_lo.astype(np.float64) + g.random((n, len(wl.in_lo))) * (wl.in_hi.astype(np.float64) - wl.in_lo)
         z = x
         ok = np.ones(n, bool)
-        for k, w in enumerate(net.weights):
-            z = z @ w.astype(np.float64).T + (0 if net.biases[k] is None else net.biases[k].astype(np.float64))
+        for k in range(len(net.weights)):
+            z = net.layer_forward(k, z)
             if k + 1 < len(net.weights):
                 if splits is not None:
                     for s in splits:

@@ -121,6 +121,57 @@ def _f32(a):
     return np.ascontiguousarray(a, dtype=np.float32)
 
 
+def conv2d_dense(weight, bias, stride, pad, in_hw):
+    """The linear map of a Conv2d layer as a dense matrix over NCHW-flattened tensors.
+
+    weight [oc, ic, kh, kw], bias [oc] or None, dilation 1, one group.  Returns (W [oc*oh*ow, ic*ih*iw],
+    b [oc*oh*ow] or None) with W[(co,oy,ox), (ci,iy,ix)] = weight[co,ci,ky,kx] for iy = oy*sh - ph + ky,
+    ix = ox*sw - pw + kx inside the input.  With this matrix the interval pass W+ l + W- u + b is the
+    reference's interval convolution (layers/convolution/conv2d/bound.rs:86-268) and the CROWN backward
+    A * W is its transposed convolution (conv2d/bound.rs:601-900, conv2d/ops_transpose_gemm.rs): the same
+    products, summed per output element; the bias is expanded per channel (GpuCrownLayer::Conv2d::bias_expanded,
+    ny-core/src/gemm.rs:1566)."""
+    weight = np.asarray(weight, np.float32)
+    oc, ic, kh, kw = weight.shape
+    sh, sw = stride
+    ph, pw = pad
+    ih, iw = in_hw
+    if sh <= 0 or sw <= 0 or kh <= 0 or kw <= 0:
+        raise ValueError("conv2d: zero stride or kernel")
+    if ih + 2 * ph < kh or iw + 2 * pw < kw:
+        raise ValueError("conv2d: kernel larger than the padded input")
+    oh, ow = (ih + 2 * ph - kh) // sh + 1, (iw + 2 * pw - kw) // sw + 1
+    W = np.zeros((oc, oh, ow, ic, ih, iw), np.float32)
+    for oy in range(oh):
+        for ky in range(kh):
+            iy = oy * sh - ph + ky
+            if iy < 0 or iy >= ih:
+                continue
+            for ox in range(ow):
+                for kx in range(kw):
+                    ix = ox * sw - pw + kx
+                    if ix < 0 or ix >= iw:
+                        continue
+                    W[:, oy, ox, :, iy, ix] = weight[:, :, ky, kx]
+    b = None if bias is None else np.repeat(np.asarray(bias, np.float32), oh * ow)
+    return W.reshape(oc * oh * ow, ic * ih * iw), b
+
+
+def lower_network(layers, biases):
+    """Dense (weights, biases) lists for a sequential network whose entries are matrices or conv layer
+    descriptions (objects with weight, bias, sh, sw, ph, pw, ih, iw attributes)."""
+    ws, bs = [], []
+    for w, b in zip(layers, biases):
+        if hasattr(w, "kh"):
+            dw, db = conv2d_dense(w.weight, w.bias, (w.sh, w.sw), (w.ph, w.pw), (w.ih, w.iw))
+            ws.append(dw)
+            bs.append(db)
+        else:
+            ws.append(w)
+            bs.append(b)
+    return ws, bs
+
+
 def ibp_forward(net: Net, lo, hi):
     lo, hi = _f32(lo), _f32(hi)
     pl = np.empty(net.n_pre, np.float32)

@@ -10,6 +10,7 @@ The reference asserts |ny - value| < 1e-4 (1e-5 for the tiny net); the same tole
 import math
 
 import numpy as np
+import pytest
 
 FC1 = [[0.16834518, 0.06440470, 0.11723118], [0.11516652, -0.56142819, -0.09316415],
        [1.10410070, -0.31899852, 0.23082861], [0.13367544, 0.26745233, 0.40467861]]
@@ -100,3 +101,63 @@ def test_verdict_predicates(oracle):
     assert L.nyo_domain_violated(-2.0, -1.0, 0.0) == 1
     assert L.nyo_domain_violated(-2.0, 0.0, 0.0) == 0
     assert L.nyo_domain_violated(-1.0, -2.0, 0.0) == 0
+
+
+# ---- Conv2d known answers (crates/ny-propagate/src/layers/convolution/conv2d/tests.rs) -------------------
+def _conv_net(oracle, weight, bias, in_hw, stride=(1, 1), pad=(0, 0)):
+    W, b = oracle.conv2d_dense(np.asarray(weight, np.float32), bias, stride, pad, in_hw)
+    n_out = W.shape[0]
+    # one conv layer followed by an identity read-out, so the conv's own interval is a pre-activation block
+    return oracle.Net([W, np.eye(n_out, dtype=np.float32)], [b, None], [0, 0]), W, b
+
+
+def test_conv2d_ibp_positive_and_negative_kernels(oracle):
+    """tests.rs:46-66 (y = 2x + 0.5) and :561-584 (y = -2x + 1: the bounds swap)."""
+    lo = np.array([1, 2, 3, 4], np.float32)
+    hi = np.array([5, 6, 7, 8], np.float32)
+    net, _, _ = _conv_net(oracle, [[[[2.0]]]], np.array([0.5], np.float32), (2, 2))
+    pl, pu = oracle.ibp_forward(net, lo, hi)
+    assert np.allclose(pl[:4], [2.5, 4.5, 6.5, 8.5], atol=1e-5) and np.allclose(pu[:4], [10.5, 12.5, 14.5, 16.5], atol=1e-5)
+    assert np.all(pl[:4] <= [2.5, 4.5, 6.5, 8.5]) and np.all(pu[:4] >= [10.5, 12.5, 14.5, 16.5])
+    net, _, _ = _conv_net(oracle, [[[[-2.0]]]], np.array([1.0], np.float32), (2, 2))
+    pl, pu = oracle.ibp_forward(net, lo, hi)
+    assert np.allclose(pl[:4], [-9, -11, -13, -15], atol=1e-5) and np.allclose(pu[:4], [-1, -3, -5, -7], atol=1e-5)
+
+
+def test_conv2d_backward_identity_and_2x2_kernel(oracle):
+    """tests.rs:287-306: identity coefficients through a 1x1 kernel of 2 give 2*I and bias 0.5;
+    tests.rs:620-654: a 2x2 kernel on a 2x2 input gives the kernel weights as coefficients."""
+    _, W, b = _conv_net(oracle, [[[[2.0]]]], np.array([0.5], np.float32), (2, 2))
+    assert np.array_equal(np.eye(4, dtype=np.float32) @ W, 2 * np.eye(4, dtype=np.float32))
+    assert np.array_equal(b, np.full(4, 0.5, np.float32))
+    _, W, b = _conv_net(oracle, [[[[1.0, 2.0], [3.0, 4.0]]]], None, (2, 2))
+    assert W.shape == (1, 4) and np.array_equal(W[0], [1, 2, 3, 4]) and b is None
+
+
+def test_conv2d_strided_padded_matches_direct_convolution(oracle):
+    """The dense lowering against a direct NCHW convolution loop, stride 2, pad 1, several channels."""
+    g = np.random.Generator(np.random.PCG64(5))
+    w = g.standard_normal((3, 2, 4, 4)).astype(np.float32)
+    bias = g.standard_normal(3).astype(np.float32)
+    ih = iw = 6
+    W, b = oracle.conv2d_dense(w, bias, (2, 2), (1, 1), (ih, iw))
+    oh = ow = (ih + 2 - 4) // 2 + 1
+    x = g.standard_normal((2, ih, iw))
+    want = np.zeros((3, oh, ow))
+    for co in range(3):
+        for oy in range(oh):
+            for ox in range(ow):
+                acc = float(bias[co])
+                for ci in range(2):
+                    for ky in range(4):
+                        for kx in range(4):
+                            iy, ix = oy * 2 - 1 + ky, ox * 2 - 1 + kx
+                            if 0 <= iy < ih and 0 <= ix < iw:
+                                acc += float(w[co, ci, ky, kx]) * x[ci, iy, ix]
+                want[co, oy, ox] = acc
+    got = W.astype(np.float64) @ x.ravel() + b
+    assert np.allclose(got, want.ravel(), atol=1e-12)
+    with pytest.raises(ValueError):
+        oracle.conv2d_dense(w, None, (0, 1), (0, 0), (6, 6))       # tests.rs:874-897: zero stride rejected
+    with pytest.raises(ValueError):
+        oracle.conv2d_dense(w, None, (1, 1), (0, 0), (2, 2))       # tests.rs:913-927: output size underflow
