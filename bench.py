@@ -394,6 +394,102 @@ def run_alpha_crown(args, rank, world, local_rank):
     eng.close()
 
 
+def run_cnn(args, local_rank):
+    """Secondary workload (--workload cnn): beta-CROWN bound of 1024 BaB domains (8 splits each) of the CNN
+    3x32x32 -> conv(16,k4,s2,p1) -> conv(32,k4,s2,p1) -> FC 2048->100 -> FC 100->10, box x0 +- 2/255, 9 spec rows.
+    One step = one bound evaluation of the whole batch (interval convolutions forward, transposed convolutions
+    backward)."""
+    import torch
+
+    from ny_b200 import B200Engine
+    from ny_b200 import engine as E
+    from ny_b200 import workloads as W
+    from oracle import ny_oracle as O  # cpu_baseline leg only (below)
+
+    torch.cuda.set_device(local_rank)
+    stream = torch.cuda.current_stream()
+    eng = B200Engine(local_rank, stream.cuda_stream)
+    eng.set_path(E.PATH_TF32X3 if args.path == "tf32x3" else E.PATH_F64)
+    wl = W.config_cnn()
+    nid = eng.register_network(wl.net)
+    pl, pu = eng.ibp_forward_gpu(nid, wl.in_lo, wl.in_hi)
+    rl, ru = pl[0].copy(), pu[0].copy()
+    D = args.domains if args.domains != D_PER_GPU else 1024
+    splits, ns = W.draw_domains(wl, rl, ru, D)
+    eng.batch_upload(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, splits, ns, mode=1)
+    for _ in range(max(args.warmup, 3)):
+        eng.batch_run()
+    torch.cuda.synchronize()
+    eng.timing_enable(True)
+    eng.timing_reset()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    l0 = eng.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(stream)
+    for _ in range(args.steps):
+        eng.batch_run()
+    ev1.record(stream)
+    torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1) / args.steps
+    launches = eng.launch_count() - l0
+    gemm_ms, _ = eng.timing_read("gemm")
+    fwd_ms, _ = eng.timing_read("forward")
+    bwd_ms, _ = eng.timing_read("backward")
+    eng.timing_enable(False)
+    glo, ghi, ginf = eng.batch_download()
+    refined = eng.batch_refined()
+    e2e_steps = max(2, min(args.steps, 5))
+    t1 = time.perf_counter()
+    for _ in range(e2e_steps):
+        elo, ehi, einf = eng.bab_bound_batch(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, splits, ns, mode=1)
+    e2e_ms = (time.perf_counter() - t1) * 1e3 / e2e_steps
+    clocks = sampler.stop()
+    assert np.array_equal(elo, glo)
+    S = wl.spec.shape[0]
+    # algorithmic work per domain: backward MACs per coefficient row through each layer (a convolution costs
+    # out_features * in_channels * kh * kw), both bound directions; bytes = every coefficient tile written and
+    # read once per layer (fp32)
+    macs = 0
+    for w in wl.net.weights:
+        macs += w.out_features * w.ic * w.kh * w.kw if hasattr(w, "kh") else w.shape[0] * w.shape[1]
+    flops = 2.0 * D * 2 * S * macs
+    dims = [int(x) for x in wl.net.dims]
+    bytes_alg = D * 2 * S * 4.0 * (2 * sum(dims[1:-1]) + dims[0] + dims[-1])
+    peaks = load_peaks()
+    line = {
+        "metric": METRIC, "value": D / (ms / 1e3), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f64 convolutions, " + args.path + " fully connected", "data": "synthetic",
+        "config": {"workload": "beta-CROWN bound of BaB domains, CNN 3x32x32 conv(16,k4,s2,p1)-conv(32,k4,s2,p1)-FC100-FC10, "
+                               "box x0+-2/255, 9 spec rows (both directions), 8 splits/domain, transposed-convolution backward",
+                   "domains_per_gpu": D, "feasible_domains": int((ginf == 0).sum()),
+                   "domains_sent_to_binary64_rerun": int(refined),
+                   "l2": "coefficient ping-pong buffers (2 x 302 MB) exceed the 126 MB L2"},
+        "e2e": {"value": D / (e2e_ms / 1e3), "unit": UNIT, "h2d_bytes_per_step": int(splits.nbytes + ns.nbytes + rl.nbytes * 2 + wl.in_lo.nbytes * 2 + wl.spec.nbytes),
+                "d2h_bytes_per_step": int(glo.nbytes + ghi.nbytes + ginf.nbytes), "ms_per_step": e2e_ms},
+        "gpu_launches": int(launches), "clocks": clocks,
+        "roofline": {"bound": "hbm", "achieved": bytes_alg / (bwd_ms / 1e3) / 1e9 if bwd_ms > 0 else None, "peak": peaks["hbm_gbs"],
+                     "unit": "GB/s", "frac": (bytes_alg / (bwd_ms / 1e3) / 1e9 / peaks["hbm_gbs"]) if bwd_ms > 0 else None,
+                     "traffic": None, "kernel": "backward pass (k_conv_transpose dominates)",
+                     "peak_source": peaks["source"] + " copy bandwidth",
+                     "flops_view": {"achieved_tflops": flops / (gemm_ms / 1e3) / 1e12 if gemm_ms > 0 else None},
+                     "phase_ms": {"forward": fwd_ms, "backward": bwd_ms, "contraction": gemm_ms}},
+    }
+    if not args.no_cpu_baseline:
+        ws, bs = O.lower_network(wl.net.weights, wl.net.biases)
+        onet = O.Net(ws, bs).with_spec(wl.spec)
+        rl2 = np.concatenate([rl, np.full(S, -np.inf, np.float32)])
+        ru2 = np.concatenate([ru, np.full(S, np.inf, np.float32)])
+        n = 64
+        t0 = time.perf_counter()
+        _, _, _, threads = O.bab_bound_batch(onet, wl.in_lo, wl.in_hi, rl2, ru2, splits[:n], ns[:n], 1)
+        line["cpu_baseline"] = {"value": n / (time.perf_counter() - t0), "unit": UNIT, "cores": int(threads), "kind": "port",
+                                "sample": f"{n} domains of the same workload on the dense lowering of the convolutions, all host threads"}
+    _emit(line)
+    eng.close()
+
+
 def eng_path_name(eng):
     return getattr(eng, "_path_name", "tf32x3")
 
@@ -413,8 +509,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--path", default=os.environ.get("NYB200_PATH", "tf32x3"), choices=["f64", "tf32x3"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="bab", choices=["bab", "alpha-crown"],
-                    help="bab: the headline beta-CROWN batch (default); alpha-crown: the alpha optimisation case, 1 GPU")
+    ap.add_argument("--workload", default="bab", choices=["bab", "alpha-crown", "cnn"],
+                    help="bab: the headline beta-CROWN batch (default); alpha-crown: the alpha optimisation case; "
+                         "cnn: the convolutional case (both 1 GPU)")
     ap.add_argument("--domains", type=int, default=D_PER_GPU, help="domains per GPU (profiling runs use a smaller batch)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -426,6 +523,10 @@ def main():
     if args.workload == "alpha-crown":
         if rank == 0:
             run_alpha_crown(args, 0, 1, local_rank)
+        return
+    if args.workload == "cnn":
+        if rank == 0:
+            run_cnn(args, local_rank)
         return
     run_ours(args, rank, world, local_rank)
 

@@ -400,8 +400,13 @@ int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, float
     if (tensor) {
         if (net.umma.empty()) {
             net.umma.resize(nv.L);
-            for (int k = 0; k < nv.L; ++k)
+            for (int k = 0; k < nv.L; ++k) {
                 if (!net.is_conv(k)) NYB_TRY(umma_prepare_layer(e, nv.W[k], nv.dims[k + 1], nv.dims[k], &net.umma[k]));
+                else {  // W_col [oc x ic*kh*kw] is the [K x N] operand of the im2col-space product
+                    const ConvGeom &g = net.geom[k];
+                    NYB_TRY(umma_prepare_layer(e, nv.W[k], g.oc, g.ic * g.kh * g.kw, &net.umma[k]));
+                }
+            }
         }
         derr = (int *)ws_get(e, "umma_err", 256);
         if (!derr) return NYB200_ERR_OOM;
@@ -420,8 +425,12 @@ int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, float
     // rounding rate of the contraction through layer `lin` (accumulation length dims[lin + 1]); convolutions
     // accumulate in binary64 on both paths
     auto eps_for = [&](int lin) {
+        // a transposed convolution on the tensor path accumulates oc products per im2col entry, adds the few
+        // entries of an output in binary64 and casts the sum once: the contraction's rate at K = oc plus 2^-24
         int K = nv.dims[lin + 1];
-        return (tensor && !net.is_conv(lin)) ? umma_eps(K) * 1.000001 : (double)(K + 2) * 1.1102230246251565e-16 * 1.000001;
+        if (tensor && net.is_conv(lin)) return (umma_eps(net.geom[lin].oc) + 5.97e-8) * 1.000001;
+        if (tensor) return umma_eps(K) * 1.000001;
+        return (double)(K + 2) * 1.1102230246251565e-16 * 1.000001;
     };
     auto q_ds = [&](int lin_k) { return (lin_k == 0 && shared_box) ? 0L : np; };
     launch_relax(e, nv, -1, L - 1, M, R, S, cur, p.lda, p.tab, p.zabs, p.q, q_ds(L - 1), eps_for(L - 1), p.rb,
@@ -437,7 +446,16 @@ int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, float
         float *dst = (ckpt && k > 0) ? ckpt[k - 1] : nxt;
         int ldd = (ckpt && k > 0) ? ld_ckpt : p.lda;
         if (e->timing.per_kernel) cudaEventRecord(next_kev(e->timing), e->stream);
-        if (net.is_conv(k)) {
+        if (net.is_conv(k) && tensor) {
+            // reshape (implicit: channel-strided operand) + GEMM with W_col on the tensor cores + col2im gather
+            const ConvGeom &g = net.geom[k];
+            const int plane = g.oh * g.ow, taps = g.ic * g.kh * g.kw;
+            if ((long)M * plane > 0x7fffffffL) return set_err(e, NYB200_ERR_UNSUPPORTED, "batch too large for the convolution's im2col space");
+            float *cols = (float *)ws_get(e, "conv_cols", (size_t)M * plane * taps * 4);
+            if (!cols) return NYB200_ERR_OOM;
+            NYB_TRY(launch_umma(e, net.umma[k], M * plane, cur, p.lda, cols, taps, derr, plane));
+            launch_col2im(e, g, M, cols, dst, ldd);
+        } else if (net.is_conv(k)) {
             launch_conv_transpose(e, net.geom[k], M, cur, p.lda, dst, ldd, nv.W[k], R, zin_lo, zin_hi, zin_ds, p.rpen);
         } else if (tensor) {
             NYB_TRY(launch_umma(e, net.umma[k], M, cur, p.lda, dst, ldd, derr));

@@ -1,10 +1,13 @@
 // Conv2d layers of the bound-propagation path (NCHW flattened, dilation 1, one group): the interval forward
 // pass, the CROWN backward step as a transposed convolution of the coefficient rows, and the plain forward
-// convolution the parameter adjoint needs.  All three accumulate exact fp32 x fp32 products in binary64, as
-// the reference does for convolutions on every path ("always recomputed in f64",
+// convolution the parameter adjoint needs.  The kernels here accumulate exact fp32 x fp32 products in
+// binary64, as the reference does for convolutions ("always recomputed in f64",
 // crates/ny-propagate/src/layers/convolution/conv2d/bound.rs:601-900; engine op conv_transpose_2d,
 // crates/ny-core/src/gemm.rs:540-566, geometry :150-178), so their rounding model is the binary64 one of
 // k_ibp_linear / k_gemm_f64: gamma_{n+2} with n the longest accumulation, and an exactly measured cast error.
+// On the tensor-core path the backward step is instead the reference's own decomposition - reshape, GEMM with
+// W_col, col2im - with the GEMM on the tcgen05 contraction (reading the coefficient rows channel-strided, so
+// the reshape costs nothing) and k_col2im below as the gather; its rounding rate is the contraction's.
 // The weights are W_col [oc x ic*kh*kw] row-major (the layout of GpuCrownLayer::Conv2d::weight_col).
 #include "nyb200_internal.cuh"
 
@@ -115,6 +118,84 @@ k_conv_transpose(ConvGeom g, int M, const float *__restrict__ A, int lda, float 
     }
 }
 
+// Quotient of small non-negative integers by a runtime divisor through its float reciprocal (exact for
+// n < 2^22: the +0.5 keeps the product away from the integer boundaries the rounding of 1/d could cross).
+__device__ __forceinline__ int small_div(int n, float inv_d) { return __float2int_rd(((float)n + 0.5f) * inv_d); }
+
+// col2im as a gather: C[m, (ci, y, x)] = sum over the taps (ky, kx) that reach (y, x) of the im2col-space
+// products, the second half of the reference's reshape + GEMM + col2im decomposition (GpuCrownLayer::Conv2d,
+// crates/ny-core/src/gemm.rs:1553-1562).  The products arrive tap-major, cols[(m * taps + tap) * plane + (oy, ox)],
+// so threads with consecutive x read consecutive words of one tap's plane.  The few fp32 entries of an output
+// are summed in binary64 and cast once; that cast (at most 2^-24 of the sum of the term magnitudes) is part of
+// the rounding rate the relaxation pass charges for this layer, so nothing is accumulated here.
+__global__ void __launch_bounds__(256)
+k_col2im(ConvGeom g, const float *__restrict__ cols, float *__restrict__ C, int ldc, float inv_iw, float inv_sh,
+         float inv_sw) {
+    const int in_plane = g.ih * g.iw, plane = g.oh * g.ow, kk = g.kh * g.kw;
+    const int m = blockIdx.x, ci = blockIdx.y;
+    const int pix = blockIdx.z * blockDim.x + threadIdx.x;
+    if (pix >= in_plane) return;
+    const int y = small_div(pix, inv_iw), x = pix - y * g.iw;
+    // valid taps: ky = ky0 + i*sh with oy = yq - i, kx = kx0 + i*sw with ox = xq - i
+    const int yq = small_div(y + g.ph, inv_sh), ky0 = (y + g.ph) - yq * g.sh;
+    const int xq = small_div(x + g.pw, inv_sw), kx0 = (x + g.pw) - xq * g.sw;
+    const float *base = cols + ((long)m * g.ic + ci) * kk * plane;
+    double acc = 0.0;
+    for (int ky = ky0, oy = yq; ky < g.kh && oy >= 0; ky += g.sh, --oy) {
+        if (oy >= g.oh) continue;
+        for (int kx = kx0, ox = xq; kx < g.kw && ox >= 0; kx += g.sw, --ox) {
+            if (ox >= g.ow) continue;
+            acc += (double)base[(ky * g.kw + kx) * plane + oy * g.ow + ox];
+        }
+    }
+    C[(long)m * ldc + ci * in_plane + pix] = (float)acc;
+}
+
+// Same gather for layers whose outputs have at most 16 taps each (every stride >= kernel / 4): one thread per
+// pixel keeps the tap offsets in registers and walks the input channels, four at a time, so that sixteen or
+// more independent loads are in flight per thread (the one-output-per-thread form above is latency bound).
+__global__ void __launch_bounds__(256)
+k_col2im_t16(ConvGeom g, const float *__restrict__ cols, float *__restrict__ C, int ldc, float inv_iw, float inv_sh,
+             float inv_sw) {
+    const int in_plane = g.ih * g.iw, plane = g.oh * g.ow, kk = g.kh * g.kw;
+    const int m = blockIdx.x;
+    const int pix = blockIdx.y * blockDim.x + threadIdx.x;
+    if (pix >= in_plane) return;
+    const int y = small_div(pix, inv_iw), x = pix - y * g.iw;
+    const int yq = small_div(y + g.ph, inv_sh), ky0 = (y + g.ph) - yq * g.sh;
+    const int xq = small_div(x + g.pw, inv_sw), kx0 = (x + g.pw) - xq * g.sw;
+    int off[16];
+    int nt = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        int ky = ky0 + i * g.sh, oy = yq - i;
+        bool vy = ky < g.kh && oy >= 0 && oy < g.oh;
+#pragma unroll
+        for (int i2 = 0; i2 < 4; ++i2) {
+            int kx = kx0 + i2 * g.sw, ox = xq - i2;
+            bool v = vy && kx < g.kw && ox >= 0 && ox < g.ow;
+            off[i * 4 + i2] = v ? (ky * g.kw + kx) * plane + oy * g.ow + ox : -1;
+            nt += v ? 1 : 0;
+        }
+    }
+    const float *base = cols + (long)m * g.ic * kk * plane;
+    float *out = C + (long)m * ldc + pix;
+    const int cstride = kk * plane;
+    for (int ci = 0; ci < g.ic; ci += 4) {
+        double acc[4] = {0.0, 0.0, 0.0, 0.0};
+#pragma unroll
+        for (int t = 0; t < 16; ++t) {
+            if (off[t] < 0) continue;
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (ci + u < g.ic) acc[u] += (double)base[(long)(ci + u) * cstride + off[t]];
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (ci + u < g.ic) out[(long)(ci + u) * in_plane] = (float)acc[u];
+    }
+}
+
 // Plain forward convolution of `rows` vectors (no bias): out[r, o] = sum W[co, ci, ky, kx] Z[r, (ci, iy, ix)].
 __global__ void __launch_bounds__(256)
 k_conv_plain(ConvGeom g, int rows, const float *__restrict__ Z, int ldz, const float *__restrict__ W,
@@ -158,6 +239,19 @@ void launch_conv_transpose(nyb200_engine *e, const ConvGeom &g, int M, const flo
     int stage = row_bytes <= 48 * 1024 ? 1 : 0;  // larger rows are read through the caches
     k_conv_transpose<<<(unsigned)M, 256, stage ? row_bytes : 0, e->stream>>>(g, M, A, lda, C, ldc, W, R, zin_lo, zin_hi,
                                                                             zin_dstride, rpen, stage);
+    e->launches++;
+}
+
+void launch_col2im(nyb200_engine *e, const ConvGeom &g, int M, const float *cols, float *C, int ldc) {
+    const float inv_iw = 1.0f / (float)g.iw, inv_sh = 1.0f / (float)g.sh, inv_sw = 1.0f / (float)g.sw;
+    const unsigned chunks = (unsigned)((g.ih * g.iw + 255) / 256);
+    if ((g.kh + g.sh - 1) / g.sh <= 4 && (g.kw + g.sw - 1) / g.sw <= 4) {
+        dim3 grid((unsigned)M, chunks);
+        k_col2im_t16<<<grid, 256, 0, e->stream>>>(g, cols, C, ldc, inv_iw, inv_sh, inv_sw);
+    } else {
+        dim3 grid((unsigned)M, (unsigned)g.ic, chunks);
+        k_col2im<<<grid, 256, 0, e->stream>>>(g, cols, C, ldc, inv_iw, inv_sh, inv_sw);
+    }
     e->launches++;
 }
 

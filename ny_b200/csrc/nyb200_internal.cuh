@@ -183,12 +183,18 @@ void launch_ibp_conv(nyb200_engine *e, const NetView &nv, const ConvGeom &g, int
 void launch_conv_transpose(nyb200_engine *e, const ConvGeom &g, int M, const float *A, int lda, float *C, int ldc,
                            const float *W, int R, const float *zin_lo, const float *zin_hi, long zin_dstride,
                            double *rpen);
+// Sums the tap-major im2col-space products cols[(m * taps + tap) * plane + (oy, ox)] into C[m, (ci, y, x)]
+// (binary64 sums of the fp32 entries, one cast: charged through the layer's rounding rate).
+void launch_col2im(nyb200_engine *e, const ConvGeom &g, int M, const float *cols, float *C, int ldc);
 void launch_conv_plain(nyb200_engine *e, const ConvGeom &g, int rows, const float *Z, int ldz, const float *W, float *out,
                        int ldo);
 
 // ---- tcgen05 contraction (nyb200_umma.cu) ----
 int umma_prepare_layer(nyb200_engine *e, const float *W, int K, int N, UmmaLayer *out);
-int launch_umma(nyb200_engine *e, const UmmaLayer &L, int M, const float *A, int lda, float *C, int ldc, int *err);
+// a_plane > 0 selects the transposed-convolution form: GEMM row r = (m, p) with p < a_plane, operand element
+// k at A[m * lda + k * a_plane + p], result column n at C[(m * N + n) * a_plane + p] (ldc unused).
+int launch_umma(nyb200_engine *e, const UmmaLayer &L, int M, const float *A, int lda, float *C, int ldc, int *err,
+                int a_plane = 0);
 double umma_eps(int K);
 // Builds the forward-pass operand of Linear_k: the [n_in x 2 n_out] matrix (W+^T | W-^T).
 int umma_prepare_forward_layer(nyb200_engine *e, const float *W, int n_in, int n_out, UmmaLayer *out);

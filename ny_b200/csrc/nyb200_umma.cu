@@ -164,7 +164,7 @@ __global__ void k_split_weights(const float *__restrict__ W, int K, int N, int K
 __global__ void __launch_bounds__(THREADS, 1)
 k_umma_tf32x3(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__ CUtensorMap tm_lo,
               const float *__restrict__ A, int lda, float *__restrict__ C, int ldc, int M, int N, int K,
-              int chunk_stages, int *__restrict__ err, int dbg) {
+              int chunk_stages, int *__restrict__ err, int dbg, int a_plane) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned long long *bars = (unsigned long long *)(smem + STAGES * STAGE_BYTES);
@@ -303,7 +303,15 @@ k_umma_tf32x3(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__
             }
             if (dead) break;
             int row = tm * BM + q * 32 + lane;
-            if (row < M && ncols > 0 && !(dbg & 4)) {
+            if (a_plane > 0) {
+                // transposed convolution: the products go out tap-major, C[(m * N + tap) * a_plane + p], so that
+                // lanes (consecutive pixels p) write consecutive words and the col2im gather reads them the same way
+                if (row < M && ncols > 0) {
+                    float *cb = C + ((long)(row / a_plane) * N + col0) * a_plane + (row % a_plane);
+#pragma unroll
+                    for (int j = 0; j < 128; ++j) if (j < ncols) cb[(long)j * a_plane] = sum[j];
+                }
+            } else if (row < M && ncols > 0 && !(dbg & 4)) {
                 float *crow = C + (long)row * ldc + col0;
                 if (ncols == 128 && ((reinterpret_cast<uintptr_t>(crow) & 31) == 0)) {
                     // 32-byte stores: every instruction writes whole sectors of this thread's row
@@ -316,6 +324,17 @@ k_umma_tf32x3(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__
                 } else if (ncols == 128 && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0)) {
 #pragma unroll
                     for (int j = 0; j < 128; j += 4) *(float4 *)(crow + j) = make_float4(sum[j], sum[j + 1], sum[j + 2], sum[j + 3]);
+                } else if ((reinterpret_cast<uintptr_t>(crow) & 15) == 0) {
+                    // partial column tile: whole 16-byte groups of this thread's row, then the ragged tail
+#pragma unroll
+                    for (int j = 0; j < 128; j += 4) {
+                        if (j + 3 < ncols) *(float4 *)(crow + j) = make_float4(sum[j], sum[j + 1], sum[j + 2], sum[j + 3]);
+                        else {
+                            if (j < ncols) crow[j] = sum[j];
+                            if (j + 1 < ncols) crow[j + 1] = sum[j + 1];
+                            if (j + 2 < ncols) crow[j + 2] = sum[j + 2];
+                        }
+                    }
                 } else {
 #pragma unroll
                     for (int j = 0; j < 128; ++j) if (j < ncols) crow[j] = sum[j];
@@ -331,8 +350,26 @@ k_umma_tf32x3(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__
         float4 v[8];
         auto load_stage = [&](int t, int ks) {
             int row = (t / n_tiles) * BM + r;
-            const float *arow = A + (long)row * lda;
             int k0 = ks * BK;
+            if (a_plane > 0) {
+                // Channel-strided operand (transposed convolution): GEMM row = (coefficient row m, pixel p),
+                // element k = channel k of that pixel, stored at A[m * lda + k * a_plane + p].  Lanes hold
+                // consecutive pixels, so every k is one coalesced load across the warp.
+                const float *base = A + (long)(row / a_plane) * lda + (row % a_plane);
+                const bool in = row < M;
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    int k = k0 + c * 4;
+                    float4 x;
+                    x.x = (in && k < K) ? base[(long)k * a_plane] : 0.f;
+                    x.y = (in && k + 1 < K) ? base[(long)(k + 1) * a_plane] : 0.f;
+                    x.z = (in && k + 2 < K) ? base[(long)(k + 2) * a_plane] : 0.f;
+                    x.w = (in && k + 3 < K) ? base[(long)(k + 3) * a_plane] : 0.f;
+                    v[c] = x;
+                }
+                return;
+            }
+            const float *arow = A + (long)row * lda;
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
                 int k = k0 + c * 4;
@@ -428,7 +465,8 @@ int umma_prepare_layer(nyb200_engine *e, const float *W, int K, int N, UmmaLayer
     return NYB200_OK;
 }
 
-int launch_umma(nyb200_engine *e, const UmmaLayer &L, int M, const float *A, int lda, float *C, int ldc, int *err) {
+int launch_umma(nyb200_engine *e, const UmmaLayer &L, int M, const float *A, int lda, float *C, int ldc, int *err,
+                int a_plane) {
     static bool attr_set = false;
     if (!attr_set) {
         if (cudaFuncSetAttribute(k_umma_tf32x3, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
@@ -440,7 +478,7 @@ int launch_umma(nyb200_engine *e, const UmmaLayer &L, int M, const float *A, int
     int tiles = ((M + BM - 1) / BM) * ((L.N + BN - 1) / BN);
     int grid = tiles < sms ? tiles : sms;
     k_umma_tf32x3<<<grid, THREADS, SMEM_BYTES, e->stream>>>(*(const CUtensorMap *)L.tm_hi, *(const CUtensorMap *)L.tm_lo, A,
-                                                            lda, C, ldc, M, L.N, L.K, chunk_stages_cfg(), err, dbg_cfg());
+                                                            lda, C, ldc, M, L.N, L.K, chunk_stages_cfg(), err, dbg_cfg(), a_plane);
     e->launches++;
     return NYB200_OK;
 }
