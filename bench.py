@@ -471,7 +471,7 @@ def run_cnn(args, local_rank):
         "gpu_launches": int(launches), "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": bytes_alg / (bwd_ms / 1e3) / 1e9 if bwd_ms > 0 else None, "peak": peaks["hbm_gbs"],
                      "unit": "GB/s", "frac": (bytes_alg / (bwd_ms / 1e3) / 1e9 / peaks["hbm_gbs"]) if bwd_ms > 0 else None,
-                     "traffic": None, "kernel": "backward pass (k_conv_transpose dominates)",
+                     "traffic": None, "kernel": "backward pass (tcgen05 im2col-space contraction + col2im gather for the convolutions)",
                      "peak_source": peaks["source"] + " copy bandwidth",
                      "flops_view": {"achieved_tflops": flops / (gemm_ms / 1e3) / 1e12 if gemm_ms > 0 else None},
                      "phase_ms": {"forward": fwd_ms, "backward": bwd_ms, "contraction": gemm_ms}},

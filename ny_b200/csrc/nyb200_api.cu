@@ -456,7 +456,14 @@ int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, float
             NYB_TRY(launch_umma(e, net.umma[k], M * plane, cur, p.lda, cols, taps, derr, plane));
             launch_col2im(e, g, M, cols, dst, ldd);
         } else if (net.is_conv(k)) {
-            launch_conv_transpose(e, net.geom[k], M, cur, p.lda, dst, ldd, nv.W[k], R, zin_lo, zin_hi, zin_ds, p.rpen);
+            const ConvGeom &g = net.geom[k];
+            size_t cols_bytes = (size_t)M * g.oh * g.ow * g.ic * g.kh * g.kw * 8;
+            double *cols = nullptr;  // scratch for the GEMM form when it is affordable, else the direct kernel
+            if ((long)M * g.oh * g.ow <= 0x7fffffffL && cols_bytes <= ((size_t)8 << 30)) {
+                cols = (double *)ws_get(e, "conv_cols", cols_bytes);
+                if (!cols) return NYB200_ERR_OOM;
+            }
+            launch_conv_transpose(e, g, M, cur, p.lda, dst, ldd, nv.W[k], R, zin_lo, zin_hi, zin_ds, p.rpen, cols);
         } else if (tensor) {
             NYB_TRY(launch_umma(e, net.umma[k], M, cur, p.lda, dst, ldd, derr));
         } else {

@@ -196,6 +196,111 @@ k_col2im_t16(ConvGeom g, const float *__restrict__ cols, float *__restrict__ C, 
     }
 }
 
+// Binary64 form of the same decomposition (the path used when binary64 contractions are selected, and by the
+// re-evaluation of batches the fast path flags): the im2col-space product as a 64 x 64 x 16 register-tiled
+// binary64 GEMM whose rows read the coefficient tensor channel-strided and whose results are kept in binary64,
+// tap-major, so that the gather below adds exact products' sums and only the final cast rounds.
+constexpr int CG_M = 64, CG_N = 64, CG_K = 16;
+__global__ void __launch_bounds__(256)
+k_conv_gemm_f64(int Mrows, int N, int K, int plane, const float *__restrict__ A, int lda, const float *__restrict__ B,
+                double *__restrict__ cols) {
+    __shared__ float sA[CG_K][CG_M + 1], sB[CG_K][CG_N + 1];
+    int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    int m0 = blockIdx.x * CG_M, n0 = blockIdx.y * CG_N;
+    double acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.0;
+    for (int k0 = 0; k0 < K; k0 += CG_K) {
+        for (int t = threadIdx.x; t < CG_M * CG_K; t += 256) {
+            int kk = t / CG_M, r = t % CG_M;  // consecutive threads: consecutive rows = consecutive pixels
+            int row = m0 + r, k = k0 + kk;
+            sA[kk][r] = (row < Mrows && k < K) ? A[(long)(row / plane) * lda + (long)k * plane + (row % plane)] : 0.f;
+        }
+        for (int t = threadIdx.x; t < CG_K * CG_N; t += 256) {
+            int kk = t / CG_N, c = t % CG_N;
+            int k = k0 + kk, n = n0 + c;
+            sB[kk][c] = (k < K && n < N) ? B[(long)k * N + n] : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < CG_K; ++kk) {
+            double a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = sA[kk][ty + 16 * i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) b[j] = sB[kk][tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fma(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        int row = m0 + ty + 16 * i;
+        if (row >= Mrows) continue;
+        long m = row / plane;
+        int p = row % plane;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            int n = n0 + tx * 4 + j;
+            if (n < N) cols[(m * N + n) * plane + p] = acc[i][j];
+        }
+    }
+}
+
+// Gather of the binary64 products: one thread per pixel walks the input channels; the cast of each sum to fp32
+// is measured and charged against the magnitude of the variable the coefficient multiplies.
+__global__ void __launch_bounds__(256)
+k_col2im_f64(ConvGeom g, const double *__restrict__ cols, float *__restrict__ C, int ldc, int R,
+             const float *__restrict__ zin_lo, const float *__restrict__ zin_hi, long zin_ds, double *__restrict__ rpen,
+             float inv_iw, float inv_sh, float inv_sw) {
+    const int in_plane = g.ih * g.iw, plane = g.oh * g.ow, kk = g.kh * g.kw;
+    const int m = blockIdx.x;
+    const int pix = blockIdx.y * blockDim.x + threadIdx.x;
+    double pen = 0.0;
+    if (pix < in_plane) {
+        const int y = small_div(pix, inv_iw), x = pix - y * g.iw;
+        const int yq = small_div(y + g.ph, inv_sh), ky0 = (y + g.ph) - yq * g.sh;
+        const int xq = small_div(x + g.pw, inv_sw), kx0 = (x + g.pw) - xq * g.sw;
+        const double *base = cols + (long)m * g.ic * kk * plane;
+        const int d = m / R;
+        for (int ci = 0; ci < g.ic; ++ci) {
+            const double *bc = base + (long)ci * kk * plane;
+            double acc = 0.0;
+            for (int ky = ky0, oy = yq; ky < g.kh && oy >= 0; ky += g.sh, --oy) {
+                if (oy >= g.oh) continue;
+                for (int kx = kx0, ox = xq; kx < g.kw && ox >= 0; kx += g.sw, --ox) {
+                    if (ox >= g.ow) continue;
+                    acc += bc[(ky * g.kw + kx) * plane + oy * g.ow + ox];
+                }
+            }
+            int j = ci * in_plane + pix;
+            float c = (float)acc;
+            C[(long)m * ldc + j] = c;
+            if (rpen) {
+                float zm = fmaxf(fabsf(zin_lo[(long)d * zin_ds + j]), fabsf(zin_hi[(long)d * zin_ds + j]));
+                pen += fabs(acc - (double)c) * (double)zm;
+            }
+        }
+    }
+    if (rpen) {
+        __shared__ double s_pen[8];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) pen += __shfl_xor_sync(0xffffffffu, pen, o);
+        if ((threadIdx.x & 31) == 0) s_pen[threadIdx.x >> 5] = pen;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            double tot = 0.0;
+            for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += s_pen[i];
+            if (tot != 0.0) atomicAdd(&rpen[m], tot);
+        }
+    }
+}
+
 // Plain forward convolution of `rows` vectors (no bias): out[r, o] = sum W[co, ci, ky, kx] Z[r, (ci, iy, ix)].
 __global__ void __launch_bounds__(256)
 k_conv_plain(ConvGeom g, int rows, const float *__restrict__ Z, int ldz, const float *__restrict__ W,
@@ -234,7 +339,18 @@ void launch_ibp_conv(nyb200_engine *e, const NetView &nv, const ConvGeom &g, int
 
 void launch_conv_transpose(nyb200_engine *e, const ConvGeom &g, int M, const float *A, int lda, float *C, int ldc,
                            const float *W, int R, const float *zin_lo, const float *zin_hi, long zin_dstride,
-                           double *rpen) {
+                           double *rpen, double *cols) {
+    if (cols) {
+        const int plane = g.oh * g.ow, taps = g.ic * g.kh * g.kw;
+        const long rows = (long)M * plane;
+        dim3 grid((unsigned)((rows + CG_M - 1) / CG_M), (unsigned)((taps + CG_N - 1) / CG_N));
+        k_conv_gemm_f64<<<grid, 256, 0, e->stream>>>((int)rows, taps, g.oc, plane, A, lda, W, cols);
+        dim3 g2((unsigned)M, (unsigned)((g.ih * g.iw + 255) / 256));
+        k_col2im_f64<<<g2, 256, 0, e->stream>>>(g, cols, C, ldc, R, zin_lo, zin_hi, zin_dstride, rpen, 1.0f / (float)g.iw,
+                                                 1.0f / (float)g.sh, 1.0f / (float)g.sw);
+        e->launches += 2;
+        return;
+    }
     size_t row_bytes = (size_t)g.oc * g.oh * g.ow * sizeof(float);
     int stage = row_bytes <= 48 * 1024 ? 1 : 0;  // larger rows are read through the caches
     k_conv_transpose<<<(unsigned)M, 256, stage ? row_bytes : 0, e->stream>>>(g, M, A, lda, C, ldc, W, R, zin_lo, zin_hi,

@@ -180,9 +180,11 @@ int download_params(nyb200_engine *e, float *alpha, float *beta);
 void launch_ibp_conv(nyb200_engine *e, const NetView &nv, const ConvGeom &g, int k, int Deff, const float *zl,
                      const float *zu, long in_dstride, float *raw_lo, float *raw_hi, float *q, long out_dstride);
 // C[M x ic*ih*iw] = transposed convolution of A[M x oc*oh*ow] (binary64 accumulation, cast error charged to rpen).
+// With `cols` (M * oh*ow * ic*kh*kw doubles of scratch) it runs as an im2col-space binary64 GEMM plus a gather,
+// without it as one direct gather kernel.
 void launch_conv_transpose(nyb200_engine *e, const ConvGeom &g, int M, const float *A, int lda, float *C, int ldc,
                            const float *W, int R, const float *zin_lo, const float *zin_hi, long zin_dstride,
-                           double *rpen);
+                           double *rpen, double *cols);
 // Sums the tap-major im2col-space products cols[(m * taps + tap) * plane + (oy, ox)] into C[m, (ci, y, x)]
 // (binary64 sums of the fp32 entries, one cast: charged through the layer's rounding rate).
 void launch_col2im(nyb200_engine *e, const ConvGeom &g, int M, const float *cols, float *C, int ldc);
