@@ -193,6 +193,31 @@ int32_t nyb200_batch_optimize(nyb200_engine *e, const nyb200_opt_config *cfg);
  * (same order as the uploaded split lists) after the last run.  Either pointer may be NULL. */
 int32_t nyb200_batch_download_params(nyb200_engine *e, float *alpha, float *beta);
 
+/* ---- PGD attack batched over restarts ----------------------------------------------------------
+ * All K restarts advance in lock-step (PgdAttacker::attack_batched,
+ * crates/ny-propagate/src/pgd_attack/attacker/batched.rs:33-215) with the exact gradient of the objective
+ * (the role of crown_point_vjp_batched, crates/ny-core/src/gemm.rs:4180-4222).  The property holds where every
+ * row spec[s] . f(x) > 0; a restart's objective is its smallest row (the worst conjunct,
+ * ny-cli commands/beta_crown/verify/graph_pgd.rs:655-685), which the attack minimises.  Step rule
+ * (AdamClippingState::step, pgd_attack/adam_state.rs:46-88): Adam moments of the gradient, direction
+ * sign(m / (sqrt(v / bc2) + epsilon)) with sign(+0) = +1 and 0 for non-finite values, uniform step
+ * step_size * lr_decay^(t-1) / bc1, projection onto the box (NaN -> lower end).  x0 [K x dims[0]] are the
+ * starting points (the caller draws them; the reference seeds one generator per restart).  Every step's point
+ * competes for the restart's best objective; after the last step the best point of every restart is evaluated
+ * once more with binary64 contractions and that value is what is returned ("re-validated by an independent
+ * forward").  Outputs: best_margin [K], best_x [K x dims[0]] (may be NULL), *counterexample = index of the
+ * restart with the smallest validated objective if that objective is <= 0, else -1.
+ * The attack can only produce counterexample candidates; it never affects a bound. */
+typedef struct nyb200_pgd_config {
+    int32_t steps;
+    float step_size;              /* initial L-inf step (config 5 uses 0.25 * eps) */
+    float lr_decay;               /* per-step factor; 0 selects the reference's 0.99 */
+    float beta1, beta2, epsilon;  /* zeros select 0.9, 0.999, 1e-8 */
+} nyb200_pgd_config;
+int32_t nyb200_pgd_attack(nyb200_engine *e, int32_t net_id, const float *spec, int32_t S, const float *in_lo,
+                          const float *in_hi, const float *x0, int32_t K, const nyb200_pgd_config *cfg,
+                          float *best_margin, float *best_x, int32_t *counterexample);
+
 /* ---- interval forward pass of ONE box without any device allocation ------------------------------
  * No counterpart in the reference: an addition for hosts that cannot let a library allocate device
  * memory at call time (a service that gave the whole GPU to its own arena at start-up, or a BaB loop

@@ -393,21 +393,28 @@ int run_forward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int fw
     return NYB200_OK;
 }
 
+// tcgen05 operands of the backward products A * W_k (Linear) and of the im2col-space product of a
+// transposed convolution (W_col [oc x ic*kh*kw] is its [K x N] operand).
+int prepare_backward_operands(nyb200_engine *e, Net &net) {
+    const NetView &nv = net.v;
+    if (!net.umma.empty()) return NYB200_OK;
+    net.umma.resize(nv.L);
+    for (int k = 0; k < nv.L; ++k) {
+        if (!net.is_conv(k)) NYB_TRY(umma_prepare_layer(e, nv.W[k], nv.dims[k + 1], nv.dims[k], &net.umma[k]));
+        else {
+            const ConvGeom &g = net.geom[k];
+            NYB_TRY(umma_prepare_layer(e, nv.W[k], g.oc, g.ic * g.kh * g.kw, &net.umma[k]));
+        }
+    }
+    return NYB200_OK;
+}
+
 int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, float *const *ckpt, int ld_ckpt) {
     const NetView &nv = net.v;
     const bool tensor = (e->path == NYB200_PATH_TF32X3);
     int *derr = nullptr;
     if (tensor) {
-        if (net.umma.empty()) {
-            net.umma.resize(nv.L);
-            for (int k = 0; k < nv.L; ++k) {
-                if (!net.is_conv(k)) NYB_TRY(umma_prepare_layer(e, nv.W[k], nv.dims[k + 1], nv.dims[k], &net.umma[k]));
-                else {  // W_col [oc x ic*kh*kw] is the [K x N] operand of the im2col-space product
-                    const ConvGeom &g = net.geom[k];
-                    NYB_TRY(umma_prepare_layer(e, nv.W[k], g.oc, g.ic * g.kh * g.kw, &net.umma[k]));
-                }
-            }
-        }
+        NYB_TRY(prepare_backward_operands(e, net));
         derr = (int *)ws_get(e, "umma_err", 256);
         if (!derr) return NYB200_ERR_OOM;
     }

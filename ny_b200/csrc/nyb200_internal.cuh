@@ -168,6 +168,8 @@ int run_forward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int fw
 // Backward pass + concretisation.  With ckpt != nullptr, ckpt[r] (row stride ld_ckpt) receives the
 // coefficients entering ReLU r before its relaxation is applied.
 int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, float *const *ckpt, int ld_ckpt);
+int prepare_backward_operands(nyb200_engine *e, Net &net);
+int prepare_transposed(nyb200_engine *e, Net &net, bool tensor);
 void fold_timing(Timing &t);
 cudaEvent_t next_kev(Timing &t);
 

@@ -155,6 +155,29 @@ __global__ void k_gather_params(NetView nv, int D, int max_splits, const float4 
 
 }  // namespace
 
+// W_k^T (row-major [dims[k] x dims[k+1]]) for every Linear layer, and its tcgen05 operands: what a forward
+// product Z * W_k^T needs (the parameter adjoint and the concrete forward pass of the attack).
+int prepare_transposed(nyb200_engine *e, Net &net, bool tensor) {
+    const NetView &nv = net.v;
+    const int L = nv.L;
+    if (net.wt.empty()) {
+        net.wt.resize(L, nullptr);
+        for (int k = 0; k < L; ++k) {
+            if (net.is_conv(k)) continue;  // a convolution's forward product runs the convolution itself
+            NYB_CUDA(e, cudaMalloc(&net.wt[k], (size_t)nv.dims[k] * nv.dims[k + 1] * 4));
+            dim3 grid((nv.dims[k] + 31) / 32, (nv.dims[k + 1] + 31) / 32), blk(32, 8);
+            k_transpose<<<grid, blk, 0, e->stream>>>(nv.W[k], nv.dims[k + 1], nv.dims[k], net.wt[k]);
+            e->launches++;
+        }
+    }
+    if (tensor && net.umma_adj.empty()) {
+        net.umma_adj.resize(L);
+        for (int k = 0; k < L; ++k)
+            if (!net.is_conv(k)) NYB_TRY(umma_prepare_layer(e, net.wt[k], nv.dims[k], nv.dims[k + 1], &net.umma_adj[k]));
+    }
+    return NYB200_OK;
+}
+
 int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg) {
     if (!e->batch.valid) return set_err(e, NYB200_ERR_INVALID, "no batch uploaded");
     if (cfg.iterations < 1) return set_err(e, NYB200_ERR_INVALID, "iterations must be >= 1");
@@ -185,21 +208,7 @@ int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg) {
         mom = (float *)ws_get(e, "adam_m", (size_t)D * np * 4);
         var = (float *)ws_get(e, "adam_v", (size_t)D * np * 4);
         if (!z0 || !z1 || !mom || !var) return NYB200_ERR_OOM;
-        if (net->wt.empty()) {
-            net->wt.resize(L, nullptr);
-            for (int k = 0; k < L - 1; ++k) {
-                if (net->is_conv(k)) continue;  // the adjoint of a convolution runs the forward convolution
-                NYB_CUDA(e, cudaMalloc(&net->wt[k], (size_t)nv.dims[k] * nv.dims[k + 1] * 4));
-                dim3 grid((nv.dims[k] + 31) / 32, (nv.dims[k + 1] + 31) / 32), blk(32, 8);
-                k_transpose<<<grid, blk, 0, e->stream>>>(nv.W[k], nv.dims[k + 1], nv.dims[k], net->wt[k]);
-                e->launches++;
-            }
-        }
-        if (tensor && net->umma_adj.empty()) {
-            net->umma_adj.resize(L);
-            for (int k = 0; k < L - 1; ++k)
-                if (!net->is_conv(k)) NYB_TRY(umma_prepare_layer(e, net->wt[k], nv.dims[k], nv.dims[k + 1], &net->umma_adj[k]));
-        }
+        NYB_TRY(prepare_transposed(e, *net, tensor));
         NYB_CUDA(e, cudaMemsetAsync(mom, 0, (size_t)D * np * 4, e->stream));
         NYB_CUDA(e, cudaMemsetAsync(var, 0, (size_t)D * np * 4, e->stream));
     }

@@ -37,7 +37,7 @@ EXPORTS = [
     "nyb200_batch_download", "nyb200_batch_min_lower", "nyb200_batch_min_lower_device",
     "nyb200_batch_download_pre_bounds", "nyb200_batch_select_branch", "nyb200_timing_enable", "nyb200_timing_reset",
     "nyb200_timing_read", "nyb200_batch_optimize", "nyb200_batch_download_params",
-    "nyb200_net_create_layers",
+    "nyb200_net_create_layers", "nyb200_pgd_attack",
 ]
 
 
@@ -96,6 +96,7 @@ def load_library():
     L.nyb200_timing_enable.argtypes = [vp, C.c_int32]
     L.nyb200_timing_reset.argtypes = [vp]
     L.nyb200_timing_read.argtypes = [vp, C.c_char_p, C.POINTER(C.c_double), ip]
+    L.nyb200_pgd_attack.argtypes = [vp, C.c_int32, fp, C.c_int32, fp, fp, fp, C.c_int32, C.POINTER(PgdConfig), fp, fp, ip]
     L.nyb200_batch_optimize.argtypes = [vp, C.POINTER(OptConfig)]
     L.nyb200_batch_download_params.argtypes = [vp, fp, fp]
     _lib = L
@@ -112,6 +113,12 @@ def _ip(a):
 
 def _f32(a):
     return np.ascontiguousarray(a, dtype=np.float32)
+
+
+class PgdConfig(C.Structure):
+    """nyb200_pgd_config (zeros select the reference's defaults for decay and the Adam moments)."""
+    _fields_ = [("steps", C.c_int32), ("step_size", C.c_float), ("lr_decay", C.c_float), ("beta1", C.c_float),
+                ("beta2", C.c_float), ("epsilon", C.c_float)]
 
 
 class LayerDesc(C.Structure):
@@ -371,6 +378,24 @@ class B200Engine:
 
     def batch_run(self):
         self._check(self._L.nyb200_batch_run(self._h))
+
+    def pgd_attack(self, net_id, spec, in_lo, in_hi, x0, steps: int, step_size: float, lr_decay: float = 0.99):
+        """PGD batched over the K rows of x0 [K, n0]; returns (best objective per restart [K], best points [K, n0],
+        index of the counterexample restart or -1).  The objective of a point is min_s spec[s] . f(x)."""
+        net = self._nets[net_id]
+        spec, lo, hi, x0 = _f32(spec), _f32(in_lo), _f32(in_hi), _f32(x0)
+        if spec.ndim != 2 or spec.shape[1] != net.dims[-1]:
+            raise EngineError(SHAPE, f"spec shape {spec.shape}")
+        if x0.ndim != 2 or x0.shape[1] != net.dims[0] or lo.shape != (net.dims[0],) or hi.shape != lo.shape:
+            raise EngineError(SHAPE, "pgd_attack: x0 must be [K, n0] and the box [n0]")
+        K = x0.shape[0]
+        best = np.empty(K, np.float32)
+        bx = np.empty((K, int(net.dims[0])), np.float32)
+        ce = C.c_int32(-1)
+        cfg = PgdConfig(steps, step_size, lr_decay, 0.0, 0.0, 0.0)
+        self._check(self._L.nyb200_pgd_attack(self._h, net_id, _fp(spec), spec.shape[0], _fp(lo), _fp(hi), _fp(x0), K,
+                                              C.byref(cfg), _fp(best), _fp(bx), C.byref(ce)))
+        return best, bx, int(ce.value)
 
     def batch_optimize(self, iterations: int, lr_alpha: float = 0.1, lr_beta: float = 0.05, lr_decay: float = 0.98,
                        clip_beta: float = 10.0):

@@ -273,3 +273,63 @@ def optimize(net: Net, lo, hi, pre_lo, pre_hi, splits: np.ndarray, alpha, iterat
     lib().nyo_optimize(C.byref(net.c), _fp(lo), _fp(hi), _fp(pre_lo), _fp(pre_hi), splits.ctypes.data, len(splits),
                        _fp(alpha), iterations, lr_alpha, lr_beta, lr_decay, clip_beta, _fp(bl), _fp(bu))
     return bl, bu, alpha, splits
+
+
+def pgd_attack(weights, biases, spec, lo, hi, x0, steps, step_size, lr_decay=0.99, beta1=0.9, beta2=0.999, eps=1e-8):
+    """numpy restatement of the lock-step PGD attack on a dense sequential ReLU network (convolutions lowered
+    with conv2d_dense): objective min_s spec[s] . f(x) per restart, exact gradient of the worst row
+    (ny-cli commands/beta_crown/verify/graph_pgd.rs:655-685), AdamClipping step
+    (ny-propagate/src/pgd_attack/adam_state.rs:46-88: direction sign(m / (sqrt(v / bc2) + eps)) with
+    sign(+0) = +1 and 0 for non-finite values, step lr0 * decay^(t-1) / bc1, projection onto the box), best
+    point per restart over all visited points (attacker/batched.rs:33-215), points kept in fp32.
+    Returns (best objective [K], best points [K, n0])."""
+    Ws = [np.asarray(w, np.float64) for w in weights]
+    bs = [None if b is None else np.asarray(b, np.float64) for b in biases]
+    spec = np.asarray(spec, np.float64)
+    lo32, hi32 = np.asarray(lo, np.float32), np.asarray(hi, np.float32)
+    x = np.asarray(x0, np.float32).copy()
+    K = x.shape[0]
+    m = np.zeros(x.shape, np.float32)
+    v = np.zeros(x.shape, np.float32)
+    best = np.full(K, np.inf, np.float32)
+    best_x = x.copy()
+    f32 = np.float32
+
+    def forward(xx):
+        acts, z = [], xx.astype(np.float64)
+        for k, w in enumerate(Ws):
+            z = z @ w.T
+            if bs[k] is not None:
+                z = z + bs[k]
+            if k + 1 < len(Ws):
+                z = np.maximum(z, 0.0)
+            acts.append(z)
+        return acts
+
+    for t in range(1, steps + 2):
+        acts = forward(x)
+        marg = (acts[-1] @ spec.T).astype(np.float32)
+        row = np.argmin(marg, axis=1)
+        val = marg[np.arange(K), row]
+        imp = val < best
+        best[imp] = val[imp]
+        best_x[imp] = x[imp]
+        if t == steps + 1:
+            break
+        g = spec[row]
+        for k in range(len(Ws) - 1, -1, -1):
+            if k + 1 < len(Ws):
+                g = g * (acts[k] > 0)
+            g = g @ Ws[k]
+        g = g.astype(np.float32)
+        m = f32(beta1) * m + f32(1 - beta1) * g
+        v = f32(beta2) * v + f32(1 - beta2) * g * g
+        bc1, bc2 = f32(1 - beta1 ** t), f32(1 - beta2 ** t)
+        denom = np.sqrt(v / bc2) + f32(eps)
+        with np.errstate(invalid="ignore", divide="ignore"):
+            q = m / denom
+        d = np.where(np.isfinite(denom) & np.isfinite(m) & ~np.isnan(q), np.copysign(f32(1), q), f32(0)).astype(np.float32)
+        step = f32(step_size * lr_decay ** (t - 1)) / bc1
+        x = np.clip(x - d * step, lo32, hi32).astype(np.float32)
+    vals = (forward(best_x)[-1] @ spec.T).min(axis=1).astype(np.float32)
+    return vals, best_x
