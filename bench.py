@@ -490,6 +490,63 @@ def run_cnn(args, local_rank):
     eng.close()
 
 
+def run_pgd(args, local_rank):
+    """Secondary workload (--workload pgd): PGD attack, 100 steps x 1024 restarts, step 0.25 * eps, margin loss,
+    on the CNN 3x32x32 conv(16,k4,s2,p1)-conv(32,k4,s2,p1)-FC100-FC10 with box x0 +- 2/255.  One step of this bench =
+    one whole attack (101 forward passes, 100 gradients, the binary64 re-validation); value = restart-steps/s."""
+    import torch
+
+    from ny_b200 import B200Engine
+    from ny_b200 import engine as E
+    from ny_b200 import workloads as W
+    from oracle import ny_oracle as O  # cpu_baseline leg only (below)
+
+    torch.cuda.set_device(local_rank)
+    eng = B200Engine(local_rank, torch.cuda.current_stream().cuda_stream)
+    eng.set_path(E.PATH_TF32X3 if args.path == "tf32x3" else E.PATH_F64)
+    wl = W.config_cnn()
+    nid = eng.register_network(wl.net)
+    K, steps = 1024, 100
+    g = np.random.Generator(np.random.PCG64(7))
+    x0 = (wl.in_lo + g.random((K, len(wl.in_lo)), dtype=np.float32) * (wl.in_hi - wl.in_lo)).astype(np.float32)
+    eps = float((wl.in_hi - wl.in_lo).max()) / 2
+    for _ in range(2):
+        eng.pgd_attack(nid, wl.spec, wl.in_lo, wl.in_hi, x0, steps, 0.25 * eps)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    l0 = eng.launch_count()
+    n = max(2, min(args.steps, 5))
+    t0 = time.perf_counter()
+    for _ in range(n):
+        best, bx, ce = eng.pgd_attack(nid, wl.spec, wl.in_lo, wl.in_hi, x0, steps, 0.25 * eps)
+    ms = (time.perf_counter() - t0) * 1e3 / n   # host buffers in and out: this is the end-to-end call
+    launches = (eng.launch_count() - l0) // n
+    clocks = sampler.stop()
+    start = (W.forward(wl.net, x0[:64]) @ wl.spec.astype(np.float64).T).min(axis=1)
+    line = {
+        "metric": "PGD restart-steps/sec", "value": K * steps / (ms / 1e3), "unit": "restart-steps/s", "n_gpus": 1,
+        "steps": n, "warmup": 2, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": args.path, "data": "synthetic",
+        "config": {"workload": "PGD attack, 1024 restarts x 100 steps, step 0.25*eps, margin loss, CNN 3x32x32 "
+                               "conv(16,k4,s2,p1)-conv(32,k4,s2,p1)-FC100-FC10, box x0+-2/255",
+                   "restarts": K, "pgd_steps": steps, "timing": "wall clock around the host-buffer C-ABI call",
+                   "mean_objective_start": float(start.mean()), "mean_objective_end": float(best.mean()),
+                   "counterexample": int(ce)},
+        "e2e": {"value": K * steps / (ms / 1e3), "unit": "restart-steps/s", "h2d_bytes_per_step": int(x0.nbytes + wl.in_lo.nbytes * 2 + wl.spec.nbytes),
+                "d2h_bytes_per_step": int(best.nbytes + bx.nbytes), "ms_per_step": ms},
+        "gpu_launches": int(launches), "clocks": clocks,
+    }
+    if not args.no_cpu_baseline:
+        ws, bs = O.lower_network(wl.net.weights, wl.net.biases)
+        kk, ss = 64, 10
+        t0 = time.perf_counter()
+        O.pgd_attack(ws, bs, wl.spec, wl.in_lo, wl.in_hi, x0[:kk], ss, 0.25 * eps)
+        line["cpu_baseline"] = {"value": kk * ss / (time.perf_counter() - t0), "unit": "restart-steps/s", "cores": "numpy BLAS threads",
+                                "kind": "port", "sample": f"{kk} restarts x {ss} steps on the dense lowering"}
+    _emit(line)
+    eng.close()
+
+
 def eng_path_name(eng):
     return getattr(eng, "_path_name", "tf32x3")
 
@@ -509,7 +566,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--path", default=os.environ.get("NYB200_PATH", "tf32x3"), choices=["f64", "tf32x3"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="bab", choices=["bab", "alpha-crown", "cnn"],
+    ap.add_argument("--workload", default="bab", choices=["bab", "alpha-crown", "cnn", "pgd"],
                     help="bab: the headline beta-CROWN batch (default); alpha-crown: the alpha optimisation case; "
                          "cnn: the convolutional case (both 1 GPU)")
     ap.add_argument("--domains", type=int, default=D_PER_GPU, help="domains per GPU (profiling runs use a smaller batch)")
@@ -523,6 +580,10 @@ def main():
     if args.workload == "alpha-crown":
         if rank == 0:
             run_alpha_crown(args, 0, 1, local_rank)
+        return
+    if args.workload == "pgd":
+        if rank == 0:
+            run_pgd(args, local_rank)
         return
     if args.workload == "cnn":
         if rank == 0:
