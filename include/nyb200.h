@@ -165,6 +165,12 @@ int32_t nyb200_batch_download_pre_bounds(nyb200_engine *e, float *pre_lo, float 
  * crates/ny-propagate/src/beta_crown/engine/branching/sequential.rs:49-104.
  * relu[d] = -1 when the domain has no unstable unsplit neuron. */
 int32_t nyb200_batch_select_branch(nyb200_engine *e, int32_t *relu, int32_t *neuron, float *width);
+/* Same with the score chosen: NYB200_BRANCH_WIDTH (u - l, the sequential engine's default, as above) or
+ * NYB200_BRANCH_INTERCEPT ((-l*u)/(u-l) in fp32: PickedDomains::select_branch_batched,
+ * crates/ny-propagate/src/batched_domain/domain_list/picked.rs:153-233).  `score` receives the winning value. */
+#define NYB200_BRANCH_WIDTH 0
+#define NYB200_BRANCH_INTERCEPT 1
+int32_t nyb200_batch_select_branch_scored(nyb200_engine *e, int32_t kind, int32_t *relu, int32_t *neuron, float *score);
 
 /* ---- alpha/beta optimisation of the resident batch ---------------------------------------------
  * Projected-Adam ascent on every domain's lower slopes alpha (unstable unsplit neurons, kept in [0,1]:
@@ -187,6 +193,9 @@ typedef struct nyb200_opt_config {
     float lr_decay;      /* per-iteration factor, the reference uses 0.98 */
     float beta1, beta2, epsilon; /* Adam moments; zeros select 0.9, 0.999, 1e-8 */
     float clip_beta;     /* > 0: beta gradients are clipped to [-clip, clip] (reference: 10) */
+    int32_t objective;   /* 0: sum over the spec rows of the lower bounds (joint_alpha_gradient);
+                            1: the row whose current lower bound is smallest (optimize_joint_bounds,
+                            beta_crown/engine/optimization/optimize_loop.rs:77-333) */
 } nyb200_opt_config;
 int32_t nyb200_batch_optimize(nyb200_engine *e, const nyb200_opt_config *cfg);
 /* alpha [D x sum_{k>=1} dims[k]] (meaningful on unstable unsplit neurons) and beta [D x max_splits]

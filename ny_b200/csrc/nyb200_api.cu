@@ -692,7 +692,12 @@ int32_t nyb200_batch_download_pre_bounds(nyb200_engine *e, float *pre_lo, float 
 }
 
 int32_t nyb200_batch_select_branch(nyb200_engine *e, int32_t *relu, int32_t *neuron, float *width) {
+    return nyb200_batch_select_branch_scored(e, NYB200_BRANCH_WIDTH, relu, neuron, width);
+}
+
+int32_t nyb200_batch_select_branch_scored(nyb200_engine *e, int32_t kind, int32_t *relu, int32_t *neuron, float *width) {
     if (!e || !relu || !neuron) return NYB200_ERR_INVALID;
+    if (kind != NYB200_BRANCH_WIDTH && kind != NYB200_BRANCH_INTERCEPT) return set_err(e, NYB200_ERR_INVALID, "unknown branching score");
     std::lock_guard<std::mutex> g(e->mu);
     NYB_CUDA(e, cudaSetDevice(e->device));
     NYB_TRY(finish_batch(e));
@@ -704,7 +709,7 @@ int32_t nyb200_batch_select_branch(nyb200_engine *e, int32_t *relu, int32_t *neu
     NYB_WS(dr, int *, e, "br_relu", (size_t)D * 4);
     NYB_WS(dn, int *, e, "br_neuron", (size_t)D * 4);
     NYB_WS(dw, float *, e, "br_width", (size_t)D * 4);
-    launch_select_branch(e, net->v, D, p.pre_lo, p.pre_hi, p.code, dr, dn, dw);
+    launch_select_branch(e, net->v, D, p.pre_lo, p.pre_hi, p.code, dr, dn, dw, kind);
     NYB_CUDA(e, cudaGetLastError());
     NYB_CUDA(e, cudaMemcpyAsync(relu, dr, (size_t)D * 4, cudaMemcpyDeviceToHost, e->stream));
     NYB_CUDA(e, cudaMemcpyAsync(neuron, dn, (size_t)D * 4, cudaMemcpyDeviceToHost, e->stream));

@@ -143,7 +143,7 @@ void launch_concretize(nyb200_engine *e, int M, int R, int S, int n0, const floa
                        const float *in_hi, long box_dstride, const double *rb, const double *rabs, const double *rpen,
                        const int *flags, float *out_lo, float *out_hi, float *min_lower, float loose_tol);
 void launch_select_branch(nyb200_engine *e, const NetView &nv, int D, const float *pre_lo, const float *pre_hi,
-                          const signed char *code, int *relu, int *neuron, float *width);
+                          const signed char *code, int *relu, int *neuron, float *width, int kind);
 void launch_fill_f64(nyb200_engine *e, double *p, size_t n, double v);
 
 // ---- resident batch (nyb200_api.cu) ----

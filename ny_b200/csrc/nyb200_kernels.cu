@@ -555,12 +555,12 @@ __global__ void k_finalize(int D, int S, const int *__restrict__ flags, float *_
 __global__ void __launch_bounds__(256)
 k_select_branch(NetView nv, int D, const float *__restrict__ pre_lo, const float *__restrict__ pre_hi,
                 const signed char *__restrict__ code, int *__restrict__ relu, int *__restrict__ neuron,
-                float *__restrict__ width) {
+                float *__restrict__ width, int kind) {
     int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp >= D) return;
     int d = warp;
     int n_hidden = nv.pre_off[nv.L - 1];
-    float best = -1.f;
+    float best = -1.f;  // every candidate's score is > 0 (width, or -l*u/(u-l) with l < 0 < u)
     int bidx = 0x7fffffff;
     for (int i = lane; i < n_hidden; i += 32) {
         long o = (long)d * nv.nps + i;
@@ -568,6 +568,11 @@ k_select_branch(NetView nv, int D, const float *__restrict__ pre_lo, const float
         if (l >= 0.f || u <= 0.f || code[o] != 0) continue;
         float w = u - l;
         if (isnan(w)) continue;
+        if (kind == 1) {  // intercept score of the batched graph engine (batched_domain/domain_list/picked.rs:153-233)
+            if (!(w > 0.f)) continue;
+            w = __fdiv_rn(-l * u, w);
+            if (isnan(w)) continue;
+        }
         if (w > best) { best = w; bidx = i; }
     }
 #pragma unroll
@@ -687,10 +692,10 @@ void launch_concretize(nyb200_engine *e, int M, int R, int S, int n0, const floa
 }
 
 void launch_select_branch(nyb200_engine *e, const NetView &nv, int D, const float *pre_lo, const float *pre_hi,
-                          const signed char *code, int *relu, int *neuron, float *width) {
+                          const signed char *code, int *relu, int *neuron, float *width, int kind) {
     long threads = (long)D * 32;
     k_select_branch<<<(unsigned)((threads + 255) / 256), 256, 0, e->stream>>>(nv, D, pre_lo, pre_hi, code, relu, neuron,
-                                                                              width);
+                                                                              width, kind);
     NYB_COUNT(e);
 }
 

@@ -61,7 +61,8 @@ __global__ void __launch_bounds__(256)
 k_adjoint_relu(int n, int off, int D, int S, int R, long nps, float *__restrict__ Z, int ldz,
                const float *__restrict__ bias, const float *__restrict__ Apre, int ldc, float4 *__restrict__ tab,
                const signed char *__restrict__ code, const float *__restrict__ pre_lo,
-               const float *__restrict__ pre_hi, float *__restrict__ mom, float *__restrict__ var, AdamStep h) {
+               const float *__restrict__ pre_hi, float *__restrict__ mom, float *__restrict__ var,
+               const int *__restrict__ only_row, AdamStep h) {
     long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= (long)D * n) return;
     int d = (int)(t / n), i = (int)(t % n);
@@ -69,12 +70,15 @@ k_adjoint_relu(int n, int off, int D, int S, int R, long nps, float *__restrict_
     float4 tb = tab[o];
     float bk = bias ? bias[i] : 0.f;
     float g_alpha = 0.f, g_sum = 0.f;
+    const int pick = only_row ? only_row[d] : -1;  // objective: one row of the domain, or the sum over its rows
     for (int s = 0; s < S; ++s) {
         long zr = ((long)d * S + s) * ldz + i;
         float g = Z[zr] + bk;
         float ap = Apre[((long)d * R + s) * ldc + i];
-        g_alpha = fmaf(g, fmaxf(ap, 0.f), g_alpha);
-        g_sum += g;
+        if (pick < 0 || s == pick) {
+            g_alpha = fmaf(g, fmaxf(ap, 0.f), g_alpha);
+            g_sum += g;
+        }
         bool pos = ap >= 0.f;
         Z[zr] = fmaf(g, pos ? tb.x : tb.y, pos ? 0.f : tb.z);
     }
@@ -101,6 +105,16 @@ k_adjoint_relu(int n, int off, int D, int S, int R, long nps, float *__restrict_
     }
     mom[o] = m; var[o] = v;
     tab[o] = tb;
+}
+
+// Row with the smallest current lower bound per domain (first minimum wins).
+__global__ void k_argmin_row(int D, int S, const float *__restrict__ lo, int *__restrict__ row) {
+    int d = blockIdx.x * blockDim.x + threadIdx.x;
+    if (d >= D) return;
+    int best = 0;
+    for (int s = 1; s < S; ++s)
+        if (lo[d * S + s] < lo[d * S + best]) best = s;
+    row[d] = best;
 }
 
 __global__ void k_fold_best(long n, int first, const float *__restrict__ lo, const float *__restrict__ hi,
@@ -181,6 +195,7 @@ int prepare_transposed(nyb200_engine *e, Net &net, bool tensor) {
 int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg) {
     if (!e->batch.valid) return set_err(e, NYB200_ERR_INVALID, "no batch uploaded");
     if (cfg.iterations < 1) return set_err(e, NYB200_ERR_INVALID, "iterations must be >= 1");
+    if (cfg.objective != 0 && cfg.objective != 1) return set_err(e, NYB200_ERR_INVALID, "objective must be 0 or 1");
     if (!(cfg.lr_alpha >= 0.f) || !(cfg.lr_beta >= 0.f) || !(cfg.lr_decay > 0.f))
         return set_err(e, NYB200_ERR_INVALID, "learning rates must be >= 0 and the decay > 0");
     Net *net;
@@ -214,6 +229,11 @@ int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg) {
     }
     NYB_WS(best_lo, float *, e, "best_lo", (size_t)D * S * 4);
     NYB_WS(best_hi, float *, e, "best_hi", (size_t)D * S * 4);
+    int *only_row = nullptr;
+    if (cfg.objective == 1) {
+        only_row = (int *)ws_get(e, "opt_row", (size_t)D * 4);
+        if (!only_row) return NYB200_ERR_OOM;
+    }
     int *derr = nullptr;
     if (tensor) {
         derr = (int *)ws_get(e, "umma_err", 256);
@@ -234,6 +254,10 @@ int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg) {
         k_fold_best<<<gres, 256, 0, e->stream>>>(nres, t == 1, p.out_lo, p.out_hi, best_lo, best_hi);
         e->launches++;
         if (last) break;
+        if (only_row) {
+            k_argmin_row<<<(unsigned)((D + 255) / 256), 256, 0, e->stream>>>(D, S, p.out_lo, only_row);
+            e->launches++;
+        }
         AdamStep h;
         float decay = powf(cfg.lr_decay, (float)(t - 1));
         h.lr_alpha = cfg.lr_alpha * decay; h.lr_beta = cfg.lr_beta * decay;
@@ -253,7 +277,7 @@ int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg) {
             long nt = (long)D * N;
             k_adjoint_relu<<<(unsigned)((nt + 255) / 256), 256, 0, e->stream>>>(N, nv.pre_off[k], D, S, R, np, zn, ldz, nv.b[k],
                                                                                ckpt[k], ldc, p.tab, p.code, p.pre_lo,
-                                                                               p.pre_hi, mom, var, h);
+                                                                               p.pre_hi, mom, var, only_row, h);
             e->launches++;
             float *tmp = zc; zc = zn; zn = tmp;
         }

@@ -37,14 +37,15 @@ EXPORTS = [
     "nyb200_batch_download", "nyb200_batch_min_lower", "nyb200_batch_min_lower_device",
     "nyb200_batch_download_pre_bounds", "nyb200_batch_select_branch", "nyb200_timing_enable", "nyb200_timing_reset",
     "nyb200_timing_read", "nyb200_batch_optimize", "nyb200_batch_download_params",
-    "nyb200_net_create_layers", "nyb200_pgd_attack",
+    "nyb200_net_create_layers", "nyb200_pgd_attack", "nyb200_batch_select_branch_scored",
 ]
 
 
 class OptConfig(C.Structure):
     """nyb200_opt_config: projected-Adam settings of nyb200_batch_optimize (zeros select Adam's defaults)."""
     _fields_ = [("iterations", C.c_int32), ("lr_alpha", C.c_float), ("lr_beta", C.c_float), ("lr_decay", C.c_float),
-                ("beta1", C.c_float), ("beta2", C.c_float), ("epsilon", C.c_float), ("clip_beta", C.c_float)]
+                ("beta1", C.c_float), ("beta2", C.c_float), ("epsilon", C.c_float), ("clip_beta", C.c_float),
+                ("objective", C.c_int32)]
 
 
 class EngineError(RuntimeError):
@@ -93,6 +94,7 @@ def load_library():
     L.nyb200_batch_min_lower_device.argtypes = [vp, C.POINTER(vp)]
     L.nyb200_batch_download_pre_bounds.argtypes = [vp, fp, fp]
     L.nyb200_batch_select_branch.argtypes = [vp, ip, ip, fp]
+    L.nyb200_batch_select_branch_scored.argtypes = [vp, C.c_int32, ip, ip, fp]
     L.nyb200_timing_enable.argtypes = [vp, C.c_int32]
     L.nyb200_timing_reset.argtypes = [vp]
     L.nyb200_timing_read.argtypes = [vp, C.c_char_p, C.POINTER(C.c_double), ip]
@@ -398,10 +400,10 @@ class B200Engine:
         return best, bx, int(ce.value)
 
     def batch_optimize(self, iterations: int, lr_alpha: float = 0.1, lr_beta: float = 0.05, lr_decay: float = 0.98,
-                       clip_beta: float = 10.0):
+                       clip_beta: float = 10.0, objective: int = 0):
         """alpha/beta projected-Adam optimisation of the resident batch (asynchronous); results through
         batch_download (element-wise best bounds) and batch_download_params."""
-        cfg = OptConfig(iterations, lr_alpha, lr_beta, lr_decay, 0.0, 0.0, 0.0, clip_beta)
+        cfg = OptConfig(iterations, lr_alpha, lr_beta, lr_decay, 0.0, 0.0, 0.0, clip_beta, objective)
         self._check(self._L.nyb200_batch_optimize(self._h, C.byref(cfg)))
 
     def batch_download_params(self):
@@ -436,10 +438,11 @@ class B200Engine:
         self._check(self._L.nyb200_batch_download_pre_bounds(self._h, _fp(pl), _fp(pu)))
         return pl, pu
 
-    def batch_select_branch(self):
+    def batch_select_branch(self, kind: int = 0):
+        """kind 0: largest width (sequential engine); 1: intercept score (batched graph engine)."""
         D = self._batch_shape[0]
         r, j, w = np.empty(D, np.int32), np.empty(D, np.int32), np.empty(D, np.float32)
-        self._check(self._L.nyb200_batch_select_branch(self._h, _ip(r), _ip(j), _fp(w)))
+        self._check(self._L.nyb200_batch_select_branch_scored(self._h, kind, _ip(r), _ip(j), _fp(w)))
         return r, j, w
 
     def timing_enable(self, per_kernel: bool):

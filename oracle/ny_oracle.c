@@ -912,6 +912,33 @@ int nyo_select_largest_width(const nyo_net *net, const float *pre_lo, const floa
     return found;
 }
 
+/* Intercept-score branching of the batched graph engine (batched_domain/domain_list/picked.rs:153-233):
+ * score (-l*u)/(u-l) in fp32 over unstable unsplit neurons with u-l > 0, strict '>' so the first maximum in
+ * (relu, neuron) order wins, NaN bounds skipped. */
+int nyo_select_intercept(const nyo_net *net, const float *pre_lo, const float *pre_hi, const nyo_split *splits,
+                         int n_splits, int32_t *relu, int32_t *neuron, float *score) {
+    int L = net->n_linear, found = 0;
+    float best = 0.0f;
+    for (int r = 0; r < L - 1; ++r) {
+        if (!relu_after(net, r)) continue;
+        size_t o = pre_offset(net, r);
+        for (int j = 0; j < net->dims[r + 1]; ++j) {
+            float l = pre_lo[o + j], u = pre_hi[o + j];
+            if (isnan(l) || isnan(u)) continue;
+            if (l >= 0.0f || u <= 0.0f) continue;
+            int constrained = 0;
+            for (int s = 0; s < n_splits; ++s) if (splits[s].relu == r && splits[s].neuron == j) { constrained = 1; break; }
+            if (constrained) continue;
+            float w = u - l;
+            if (!(w > 0.0f)) continue;
+            float sc = (-l * u) / w;
+            if (!found || sc > best) { found = 1; best = sc; *relu = r; *neuron = j; }
+        }
+    }
+    if (found && score) *score = best;
+    return found;
+}
+
 /* beta_crown/config/beta_config.rs:1552-1610 (lower mode) */
 int nyo_domain_verified(float lower, float upper, float threshold) {
     if (!isfinite(lower) || !isfinite(upper) || !isfinite(threshold) || lower > upper) return 0;
@@ -934,6 +961,15 @@ int nyo_domain_violated(float lower, float upper, float threshold) {
 int nyo_joint_gradient(const nyo_net *net, const float *in_lo, const float *in_hi, const float *pre_lo,
                        const float *pre_hi, const nyo_split *splits, int n_splits, const float *alpha,
                        double *lower_out, float *grad_alpha, float *grad_beta) {
+    return nyo_joint_gradient_rows(net, in_lo, in_hi, pre_lo, pre_hi, splits, n_splits, alpha, lower_out, grad_alpha,
+                                   grad_beta, -1);
+}
+
+/* only_row >= 0: the objective is that single row's lower bound (the argmin-lower row of
+ * beta_crown/engine/optimization/optimize_loop.rs:77-333) instead of the sum over rows. */
+int nyo_joint_gradient_rows(const nyo_net *net, const float *in_lo, const float *in_hi, const float *pre_lo,
+                            const float *pre_hi, const nyo_split *splits, int n_splits, const float *alpha,
+                            double *lower_out, float *grad_alpha, float *grad_beta, int only_row) {
     int L = net->n_linear, S = net->dims[L];
     size_t total = pre_offset(net, L);
     /* per-ReLU records */
@@ -1026,8 +1062,10 @@ int nyo_joint_gradient(const nyo_net *net, const float *in_lo, const float *in_h
                 for (int s = 0; s < S; ++s) {
                     size_t q = (size_t)s * n + j;
                     double ap = apre[k][q];
-                    ga += Z[q] * (ap > 0.0 ? ap : 0.0);
-                    gz += Z[q];
+                    if (only_row < 0 || s == only_row) {
+                        ga += Z[q] * (ap > 0.0 ? ap : 0.0);
+                        gz += Z[q];
+                    }
                     Z[q] = Z[q] * sig[k][q] + tau[k][q];
                 }
                 if (split_idx >= 0) { if (grad_beta) grad_beta[split_idx] = (float)(-(double)(splits[split_idx].sign > 0 ? 1 : -1) * gz); }
@@ -1049,6 +1087,15 @@ int nyo_joint_gradient(const nyo_net *net, const float *in_lo, const float *in_h
 int nyo_optimize(const nyo_net *net, const float *in_lo, const float *in_hi, const float *pre_lo, const float *pre_hi,
                  nyo_split *splits, int n_splits, float *alpha, int iterations, float lr_alpha, float lr_beta,
                  float lr_decay, float clip_beta, float *best_lo, float *best_hi) {
+    return nyo_optimize_objective(net, in_lo, in_hi, pre_lo, pre_hi, splits, n_splits, alpha, iterations, lr_alpha, lr_beta,
+                                  lr_decay, clip_beta, 0, best_lo, best_hi);
+}
+
+/* objective 0: sum of the rows' lower bounds; 1: the row whose current lower bound is smallest. */
+int nyo_optimize_objective(const nyo_net *net, const float *in_lo, const float *in_hi, const float *pre_lo,
+                           const float *pre_hi, nyo_split *splits, int n_splits, float *alpha, int iterations,
+                           float lr_alpha, float lr_beta, float lr_decay, float clip_beta, int objective, float *best_lo,
+                           float *best_hi) {
     int L = net->n_linear, S = net->dims[L];
     size_t total = pre_offset(net, L);
     float *ga = (float *)calloc(total, 4), *ma = (float *)calloc(total, 4), *va = (float *)calloc(total, 4);
@@ -1060,7 +1107,9 @@ int nyo_optimize(const nyo_net *net, const float *in_lo, const float *in_hi, con
         nyo_beta_crown_bound(net, in_lo, in_hi, pre_lo, pre_hi, splits, n_splits, alpha, lo, hi);
         for (int s = 0; s < S; ++s) { if (lo[s] > best_lo[s]) best_lo[s] = lo[s]; if (hi[s] < best_hi[s]) best_hi[s] = hi[s]; }
         if (t == iterations) break;
-        nyo_joint_gradient(net, in_lo, in_hi, pre_lo, pre_hi, splits, n_splits, alpha, NULL, ga, gb);
+        int row = -1;
+        if (objective == 1) { row = 0; for (int s = 1; s < S; ++s) if (lo[s] < lo[row]) row = s; }
+        nyo_joint_gradient_rows(net, in_lo, in_hi, pre_lo, pre_hi, splits, n_splits, alpha, NULL, ga, gb, row);
         float bc1 = fmaxf(1.0f - powf(b1, (float)t), 1.1920929e-7f), bc2 = fmaxf(1.0f - powf(b2, (float)t), 1.1920929e-7f);
         float lra = lr_alpha * powf(lr_decay, (float)(t - 1)), lrb = lr_beta * powf(lr_decay, (float)(t - 1));
         size_t hidden = pre_offset(net, L - 1);

@@ -97,6 +97,16 @@ int nyo_joint_gradient(const nyo_net *net, const float *in_lo, const float *in_h
                        const float *pre_hi, const nyo_split *splits, int n_splits, const float *alpha,
                        double *lower_out, float *grad_alpha, float *grad_beta);
 
+int nyo_joint_gradient_rows(const nyo_net *net, const float *in_lo, const float *in_hi, const float *pre_lo,
+                            const float *pre_hi, const nyo_split *splits, int n_splits, const float *alpha,
+                            double *lower_out, float *grad_alpha, float *grad_beta, int only_row);
+int nyo_optimize_objective(const nyo_net *net, const float *in_lo, const float *in_hi, const float *pre_lo,
+                           const float *pre_hi, nyo_split *splits, int n_splits, float *alpha, int iterations,
+                           float lr_alpha, float lr_beta, float lr_decay, float clip_beta, int objective, float *best_lo,
+                           float *best_hi);
+int nyo_select_intercept(const nyo_net *net, const float *pre_lo, const float *pre_hi, const nyo_split *splits,
+                         int n_splits, int32_t *relu, int32_t *neuron, float *score);
+
 /* Projected-Adam optimisation of alpha (in [0,1]) and beta (>= 0) with fixed intermediate bounds; keeps the
  * element-wise best sound bounds.  alpha and the beta fields of `splits` are updated in place. */
 int nyo_optimize(const nyo_net *net, const float *in_lo, const float *in_hi, const float *pre_lo, const float *pre_hi,

@@ -64,7 +64,11 @@ def lib():
         L.nyo_joint_gradient.argtypes = [np_, fp, fp, fp, fp, C.c_void_p, C.c_int, fp, dp, fp, fp]
         L.nyo_optimize.argtypes = [np_, fp, fp, fp, fp, C.c_void_p, C.c_int, fp, C.c_int, C.c_float, C.c_float,
                                    C.c_float, C.c_float, fp, fp]
+        L.nyo_optimize_objective.argtypes = [np_, fp, fp, fp, fp, C.c_void_p, C.c_int, fp, C.c_int, C.c_float, C.c_float,
+                                             C.c_float, C.c_float, C.c_int, fp, fp]
+        L.nyo_joint_gradient_rows.argtypes = [np_, fp, fp, fp, fp, C.c_void_p, C.c_int, fp, dp, fp, fp, C.c_int]
         L.nyo_select_largest_width.argtypes = [np_, fp, fp, C.c_void_p, C.c_int, ip, ip, fp]
+        L.nyo_select_intercept.argtypes = [np_, fp, fp, C.c_void_p, C.c_int, ip, ip, fp]
         L.nyo_domain_verified.argtypes = [C.c_float, C.c_float, C.c_float]
         L.nyo_domain_violated.argtypes = [C.c_float, C.c_float, C.c_float]
         _lib = L
@@ -242,6 +246,16 @@ def select_largest_width(net: Net, pre_lo, pre_hi, splits: np.ndarray):
     return (r.value, j.value, w.value) if ok else None
 
 
+def select_intercept(net: Net, pre_lo, pre_hi, splits: np.ndarray):
+    """Intercept-score branching choice (relu, neuron, score) or None (picked.rs:153-233)."""
+    pre_lo, pre_hi = _f32(pre_lo), _f32(pre_hi)
+    splits = np.ascontiguousarray(splits, SPLIT_DTYPE)
+    r, j, w = C.c_int32(-1), C.c_int32(-1), C.c_float(0)
+    ok = lib().nyo_select_intercept(C.byref(net.c), _fp(pre_lo), _fp(pre_hi), splits.ctypes.data, len(splits),
+                                    C.byref(r), C.byref(j), C.byref(w))
+    return (r.value, j.value, w.value) if ok else None
+
+
 def heuristic_alpha(net: Net, pre_lo, pre_hi):
     """alpha_0 = [u > -l] on unstable neurons (beta_crown/state/alpha/domain.rs:161), n_pre layout."""
     pre_lo, pre_hi = _f32(pre_lo), _f32(pre_hi)
@@ -263,15 +277,16 @@ def joint_gradient(net: Net, lo, hi, pre_lo, pre_hi, splits: np.ndarray, alpha=N
 
 
 def optimize(net: Net, lo, hi, pre_lo, pre_hi, splits: np.ndarray, alpha, iterations, lr_alpha, lr_beta,
-             lr_decay=0.98, clip_beta=10.0):
+             lr_decay=0.98, clip_beta=10.0, objective=0):
     """Returns (best_lo [S], best_hi [S], alpha, splits) after projected-Adam optimisation."""
     lo, hi, pre_lo, pre_hi = _f32(lo), _f32(hi), _f32(pre_lo), _f32(pre_hi)
     alpha = _f32(alpha).copy()
     splits = np.ascontiguousarray(splits, SPLIT_DTYPE).copy()
     S = int(net.dims[-1])
     bl, bu = np.empty(S, np.float32), np.empty(S, np.float32)
-    lib().nyo_optimize(C.byref(net.c), _fp(lo), _fp(hi), _fp(pre_lo), _fp(pre_hi), splits.ctypes.data, len(splits),
-                       _fp(alpha), iterations, lr_alpha, lr_beta, lr_decay, clip_beta, _fp(bl), _fp(bu))
+    lib().nyo_optimize_objective(C.byref(net.c), _fp(lo), _fp(hi), _fp(pre_lo), _fp(pre_hi), splits.ctypes.data,
+                                 len(splits), _fp(alpha), iterations, lr_alpha, lr_beta, lr_decay, clip_beta, objective,
+                                 _fp(bl), _fp(bu))
     return bl, bu, alpha, splits
 
 

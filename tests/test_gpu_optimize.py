@@ -119,6 +119,40 @@ def test_optimised_bounds_match_oracle(eng, oracle, cfg):
     eng.release_network(nid)
 
 
+def test_worst_row_objective_matches_oracle(eng, oracle):
+    """objective = 1: every domain ascends the row whose current lower bound is smallest
+    (optimize_joint_bounds), compared with the oracle's loop under the same rule."""
+    wl = W.config_mlp_bab(seed=26, hidden=48, depth=3, n_in=40, eps=0.03, n_fix=4)
+    onet, ospec, nid, rl, ru = _setup(eng, oracle, wl)
+    D, iters = 40, 10
+    splits, ns = W.draw_domains(wl, rl, ru, D)
+    eng.batch_upload(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, splits, ns, mode=1)
+    eng.set_refine_tolerance(0.0)
+    try:
+        eng.batch_run()
+        plo, _, _ = eng.batch_download()
+    finally:
+        eng.set_refine_tolerance(5e-5)
+    eng.batch_optimize(iters, 0.1, 0.05, objective=1)
+    glo, ghi, ginf = eng.batch_download()
+    S = wl.spec.shape[0]
+    rl2 = np.concatenate([rl, np.full(S, -np.inf, np.float32)])
+    ru2 = np.concatenate([ru, np.full(S, np.inf, np.float32)])
+    n = 0
+    for d in range(D):
+        sp = splits[d][: ns[d]]
+        pl, pu, bad = oracle.domain_bounds(ospec, wl.in_lo, wl.in_hi, rl2, ru2, sp, 1)
+        if bad:
+            continue
+        olo, ohi, _, _ = oracle.optimize(ospec, wl.in_lo, wl.in_hi, pl, pu, sp, oracle.heuristic_alpha(ospec, pl, pu),
+                                         iters, 0.1, 0.05, objective=1)
+        assert _rel(np.concatenate([glo[d], ghi[d]]), np.concatenate([olo, ohi])) <= OPT_TOL, d
+        assert glo[d].min() >= plo[d].min() - 1e-6 * abs(plo[d].min())   # the worst row never gets worse
+        n += 1
+    assert n > D // 2
+    eng.release_network(nid)
+
+
 def test_optimised_bounds_stay_sound(eng, oracle):
     wl = W.config_mlp_bab(seed=24, hidden=48, depth=3, n_in=64, eps=0.03, n_fix=4)
     onet, ospec, nid, rl, ru = _setup(eng, oracle, wl)

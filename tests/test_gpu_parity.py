@@ -172,6 +172,7 @@ def test_branching_matches_oracle_and_min_lower(eng, oracle):
     glo, ghi, ginf = eng.batch_download()
     pl, pu = eng.batch_download_pre_bounds()
     r, j, w = eng.batch_select_branch()
+    r1, j1, w1 = eng.batch_select_branch(kind=1)
     feas = ginf == 0
     assert np.isclose(eng.batch_min_lower(), glo[feas].min())
     for d in range(40):
@@ -179,6 +180,8 @@ def test_branching_matches_oracle_and_min_lower(eng, oracle):
             continue
         got = oracle.select_largest_width(onet, pl[d], pu[d], splits[d][: ns[d]])
         assert got is not None and (int(r[d]), int(j[d])) == got[:2] and w[d] == np.float32(got[2])
+        got1 = oracle.select_intercept(onet, pl[d], pu[d], splits[d][: ns[d]])
+        assert got1 is not None and (int(r1[d]), int(j1[d])) == got1[:2] and w1[d] == np.float32(got1[2])
         opl, opu, oinf = oracle.domain_bounds(onet, wl.in_lo, wl.in_hi, rl, ru, splits[d][: ns[d]], 1)
         hid = int(wl.net.dims[1:-1].sum())
         tol = IBP_REL * np.maximum(np.abs(opl[:hid]), np.abs(opu[:hid]))

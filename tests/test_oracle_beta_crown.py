@@ -140,3 +140,39 @@ def test_optimisation_improves_and_stays_sound(oracle):
     # one iteration is the plain bound
     bl1, bu1, _, _ = oracle.optimize(net, wl.in_lo, wl.in_hi, pl, pu, sp, a0, 1, 0.1, 0.05)
     assert np.array_equal(bl1, lo0) and np.array_equal(bu1, hi0)
+
+
+def test_intercept_branching_first_maximum_and_nan(oracle):
+    """picked.rs:153-233: score (-l*u)/(u-l), strict '>' (first maximum wins), NaN bounds and split neurons skipped."""
+    net = oracle.Net([np.eye(4, dtype=np.float32), np.ones((1, 4), np.float32)], [None, None])
+    pre_lo = np.array([-1.0, -2.0, -2.0, np.nan, 0.0], np.float32)
+    pre_hi = np.array([1.0, 2.0, 2.0, 5.0, 0.0], np.float32)
+    got = oracle.select_intercept(net, pre_lo, pre_hi, oracle.make_splits([]))
+    assert got[:2] == (0, 1) and got[2] == np.float32(1.0)            # neurons 1 and 2 tie at 1.0: the first wins
+    got = oracle.select_intercept(net, pre_lo, pre_hi, oracle.make_splits([(0, 1, 1, 0.0)]))
+    assert got[:2] == (0, 2)
+    assert oracle.select_intercept(net, np.full(5, 1, np.float32), np.full(5, 2, np.float32), oracle.make_splits([])) is None
+
+
+def test_worst_row_gradient_is_that_rows_gradient(oracle):
+    """With the single-row objective the gradient is the finite difference of that row's bound alone."""
+    wl, net, sp, pl, pu, alpha = _one_domain(oracle, seed=17)
+    low, _, _ = oracle.joint_gradient(net, wl.in_lo, wl.in_hi, pl, pu, sp, alpha)
+    row = int(np.argmin(low))
+    import ctypes as C
+    ga = np.zeros(net.n_pre, np.float32)
+    gb = np.zeros(len(sp), np.float32)
+    f = lambda a: a.ctypes.data_as(C.POINTER(C.c_float))
+    args = [np.ascontiguousarray(x, np.float32) for x in (wl.in_lo, wl.in_hi, pl, pu)]
+    oracle.lib().nyo_joint_gradient_rows(C.byref(net.c), f(args[0]), f(args[1]), f(args[2]), f(args[3]), sp.ctypes.data,
+                                         len(sp), f(alpha), None, f(ga), f(gb), row)
+    h = 1e-3
+    idx = np.flatnonzero(ga != 0)[:8]
+    assert len(idx) > 0
+    for i in idx:
+        ap, am = alpha.copy(), alpha.copy()
+        ap[i] += h
+        am[i] -= h
+        fd = (oracle.joint_gradient(net, wl.in_lo, wl.in_hi, pl, pu, sp, ap)[0][row]
+              - oracle.joint_gradient(net, wl.in_lo, wl.in_hi, pl, pu, sp, am)[0][row]) / (2 * h)
+        assert abs(fd - ga[i]) <= 1e-3 * max(1.0, abs(fd))
