@@ -140,6 +140,20 @@ int32_t nyb200_bab_bound_batch(nyb200_engine *e, int32_t net_id, const float *sp
                                int32_t mode, const float *alpha, float *out_lo, float *out_hi,
                                int32_t *infeasible);
 
+/* ---- plain CROWN with CROWN-IBP intermediate bounds ---------------------------------------------
+ * GpuCrownBackward::crown_backward_gpu_sound(layers, spec, num_specs, in_lo, in_hi)
+ * (crates/ny-core/src/gemm.rs:3357) with the intermediate bounds the reference's `crown` pipeline collects
+ * (crates/ny-propagate/src/network/core/sequential/crown.rs:168-330, network/ibp/crown_ibp.rs:32-420): every
+ * layer that feeds a ReLU is bounded by a partial CROWN pass with the plain-CROWN relaxation
+ * (activations/relu/mod.rs:105-132) and merged with its IBP and forward bounds; the spec rows are bounded by
+ * the full pass and tightened (crown/tighten.rs:126-190).  D boxes in lock-step: in_lo/in_hi [D x dims[0]]
+ * with box_stride = dims[0], or one box with box_stride = 0 and D = 1.  out_lo/out_hi [D x S];
+ * inter_lo/inter_hi (may be NULL) receive the tightened pre-activation bounds [D x sum_{k>=1} dims[k]].
+ * Linear layers only (NYB200_ERR_UNSUPPORTED otherwise). */
+int32_t nyb200_crown_bounds(nyb200_engine *e, int32_t net_id, const float *spec, int32_t S, const float *in_lo,
+                            const float *in_hi, int32_t box_stride, int32_t D, float *out_lo, float *out_hi,
+                            float *inter_lo, float *inter_hi);
+
 /* ---- resident batch (extension: keeps the domain batch in HBM between calls) ----------------
  * upload copies the same arguments as nyb200_bab_bound_batch to the device; run launches the
  * whole bound evaluation asynchronously on the engine stream with no host<->device traffic;

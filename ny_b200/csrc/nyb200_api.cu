@@ -409,7 +409,7 @@ int prepare_backward_operands(nyb200_engine *e, Net &net) {
     return NYB200_OK;
 }
 
-int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, float *const *ckpt, int ld_ckpt) {
+int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, float *const *ckpt, int ld_ckpt, int top) {
     const NetView &nv = net.v;
     const bool tensor = (e->path == NYB200_PATH_TF32X3);
     int *derr = nullptr;
@@ -418,7 +418,10 @@ int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, float
         derr = (int *)ws_get(e, "umma_err", 256);
         if (!derr) return NYB200_ERR_OOM;
     }
-    int D = b.D, S = b.S, R = b.R, L = nv.L;
+    // top < 0: the whole network, seeded with the spec rows.  top >= 0: the pass starts at Linear_top's output
+    // with one identity row per neuron (b.S = dims[top + 1]): the partial pass of the CROWN-IBP collection.
+    const bool partial = top >= 0;
+    int D = b.D, S = b.S, R = b.R, L = partial ? top + 1 : nv.L;
     int M = D * R;
     long np = nv.nps;
     bool shared_box = (b.box_stride == 0 && D > 1);
@@ -428,7 +431,8 @@ int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, float
     static const float init_words[8] = {INFINITY, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};  // min lower; loose-domain counter at word 4
     NYB_CUDA(e, cudaMemcpyAsync(p.min_lower, init_words, sizeof(init_words), cudaMemcpyHostToDevice, e->stream));
     float *cur = p.A0, *nxt = p.A1;
-    launch_seed(e, p.spec, S, nv.dims[L], D, p.lda, cur);
+    if (partial) launch_seed_identity(e, S, D, p.lda, cur);
+    else launch_seed(e, p.spec, S, nv.dims[L], D, p.lda, cur);
     // rounding rate of the contraction through layer `lin` (accumulation length dims[lin + 1]); convolutions
     // accumulate in binary64 on both paths
     auto eps_for = [&](int lin) {

@@ -131,6 +131,8 @@ void launch_ibp_finish(nyb200_engine *e, const NetView &nv, int k, int D, int mo
                        float *zl, float *zu, float4 *tab, float *zabs, int *flags, const float *F = nullptr, int ldf = 0,
                        double eps = 0.0, float *q = nullptr);
 void launch_seed(nyb200_engine *e, const float *spec, int S, int nL, int D, int lda, float *A);
+// A [D*2n x lda] = per domain the n x n identity for the lower rows, then again for the upper rows.
+void launch_seed_identity(nyb200_engine *e, int n, int D, int lda, float *A);
 // In-place ReLU relaxation of A [M x n] (ReLU r) or identity pass (r < 0), accumulating the row sums.
 // With Asrc != nullptr the rows are read from Asrc (row stride lds) and the result written to A.
 void launch_relax(nyb200_engine *e, const NetView &nv, int r, int lin_k, int M, int R, int S, float *A, int lda,
@@ -167,11 +169,16 @@ int find_net(nyb200_engine *e, int net_id, Net **out);
 int run_forward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int fwd_mode);
 // Backward pass + concretisation.  With ckpt != nullptr, ckpt[r] (row stride ld_ckpt) receives the
 // coefficients entering ReLU r before its relaxation is applied.
-int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, float *const *ckpt, int ld_ckpt);
+// top >= 0 starts the pass at Linear_top's output with identity rows (b.S = dims[top + 1]) instead of the spec.
+int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, float *const *ckpt, int ld_ckpt, int top = -1);
 int prepare_backward_operands(nyb200_engine *e, Net &net);
 int prepare_transposed(nyb200_engine *e, Net &net, bool tensor);
 void fold_timing(Timing &t);
 cudaEvent_t next_kev(Timing &t);
+
+// ---- plain CROWN with CROWN-IBP intermediate bounds (nyb200_crown.cu) ----
+int crown_bounds(nyb200_engine *e, int net_id, const float *spec, int S, const float *in_lo, const float *in_hi,
+                 int box_stride, int D, float *out_lo, float *out_hi, float *inter_lo, float *inter_hi);
 
 // ---- parameter optimisation (nyb200_optimize.cu) ----
 int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg);

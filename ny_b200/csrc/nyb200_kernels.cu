@@ -258,6 +258,15 @@ __global__ void k_seed(const float *__restrict__ spec, int S, int nL, int D, int
     A[m * lda + j] = spec[(long)(rr % S) * nL + j];
 }
 
+__global__ void k_seed_identity(int n, int D, int lda, float *__restrict__ A) {
+    long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    long total = (long)D * 2 * n * n;
+    if (t >= total) return;
+    int j = (int)(t % n);
+    long m = t / n;
+    A[m * lda + j] = ((int)(m % n) == j) ? 1.f : 0.f;
+}
+
 // ---------------------------------------------------------------- ReLU relaxation pass
 // One warp per row of A.  With r >= 0 the row is composed with ReLU r's relaxation
 // (relu_backward.rs:105-175): lower rows take a*ls (a>0) or a*us and a*ui into the bias (a<0), stepped
@@ -640,6 +649,12 @@ void launch_ibp_finish(nyb200_engine *e, const NetView &nv, int k, int D, int mo
 void launch_seed(nyb200_engine *e, const float *spec, int S, int nL, int D, int lda, float *A) {
     long total = (long)D * 2 * S * nL;
     k_seed<<<(unsigned)((total + 255) / 256), 256, 0, e->stream>>>(spec, S, nL, D, lda, A);
+    NYB_COUNT(e);
+}
+
+void launch_seed_identity(nyb200_engine *e, int n, int D, int lda, float *A) {
+    long total = (long)D * 2 * n * n;
+    k_seed_identity<<<(unsigned)((total + 255) / 256), 256, 0, e->stream>>>(n, D, lda, A);
     NYB_COUNT(e);
 }
 

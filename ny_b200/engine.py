@@ -38,6 +38,7 @@ EXPORTS = [
     "nyb200_batch_download_pre_bounds", "nyb200_batch_select_branch", "nyb200_timing_enable", "nyb200_timing_reset",
     "nyb200_timing_read", "nyb200_batch_optimize", "nyb200_batch_download_params",
     "nyb200_net_create_layers", "nyb200_pgd_attack", "nyb200_batch_select_branch_scored",
+    "nyb200_crown_bounds",
 ]
 
 
@@ -98,6 +99,7 @@ def load_library():
     L.nyb200_timing_enable.argtypes = [vp, C.c_int32]
     L.nyb200_timing_reset.argtypes = [vp]
     L.nyb200_timing_read.argtypes = [vp, C.c_char_p, C.POINTER(C.c_double), ip]
+    L.nyb200_crown_bounds.argtypes = [vp, C.c_int32, fp, C.c_int32, fp, fp, C.c_int32, C.c_int32, fp, fp, fp, fp]
     L.nyb200_pgd_attack.argtypes = [vp, C.c_int32, fp, C.c_int32, fp, fp, fp, C.c_int32, C.POINTER(PgdConfig), fp, fp, ip]
     L.nyb200_batch_optimize.argtypes = [vp, C.POINTER(OptConfig)]
     L.nyb200_batch_download_params.argtypes = [vp, fp, fp]
@@ -380,6 +382,24 @@ class B200Engine:
 
     def batch_run(self):
         self._check(self._L.nyb200_batch_run(self._h))
+
+    def crown_bounds(self, net_id, spec, in_lo, in_hi):
+        """Plain CROWN with CROWN-IBP intermediate bounds.  in_lo/in_hi: [n0] (one box) or [D, n0].
+        Returns (lower [D, S], upper [D, S], inter_lo [D, n_pre], inter_hi [D, n_pre])."""
+        net = self._nets[net_id]
+        spec, lo, hi = _f32(spec), _f32(in_lo), _f32(in_hi)
+        if spec.ndim != 2 or spec.shape[1] != net.dims[-1]:
+            raise EngineError(SHAPE, f"spec shape {spec.shape}")
+        one = lo.ndim == 1
+        D = 1 if one else lo.shape[0]
+        if lo.shape != hi.shape or lo.shape[-1] != net.dims[0]:
+            raise EngineError(SHAPE, "crown_bounds: box shape")
+        S = spec.shape[0]
+        ol, ou = np.empty((D, S), np.float32), np.empty((D, S), np.float32)
+        il, iu = np.empty((D, net.n_pre), np.float32), np.empty((D, net.n_pre), np.float32)
+        self._check(self._L.nyb200_crown_bounds(self._h, net_id, _fp(spec), S, _fp(lo), _fp(hi), 0 if one else int(net.dims[0]),
+                                                D, _fp(ol), _fp(ou), _fp(il), _fp(iu)))
+        return ol, ou, il, iu
 
     def pgd_attack(self, net_id, spec, in_lo, in_hi, x0, steps: int, step_size: float, lr_decay: float = 0.99):
         """PGD batched over the K rows of x0 [K, n0]; returns (best objective per restart [K], best points [K, n0],

@@ -97,6 +97,9 @@ int nyo_joint_gradient(const nyo_net *net, const float *in_lo, const float *in_h
                        const float *pre_hi, const nyo_split *splits, int n_splits, const float *alpha,
                        double *lower_out, float *grad_alpha, float *grad_beta);
 
+/* 1 (default): the certified per-coefficient error channel of the plain-CROWN path is discharged, as in the
+ * reference; 0: it is left out (test use: isolates the error chain from the bound). */
+void nyo_set_error_channel(int on);
 int nyo_joint_gradient_rows(const nyo_net *net, const float *in_lo, const float *in_hi, const float *pre_lo,
                             const float *pre_hi, const nyo_split *splits, int n_splits, const float *alpha,
                             double *lower_out, float *grad_alpha, float *grad_beta, int only_row);

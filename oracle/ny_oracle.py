@@ -68,6 +68,8 @@ def lib():
                                              C.c_float, C.c_float, C.c_int, fp, fp]
         L.nyo_joint_gradient_rows.argtypes = [np_, fp, fp, fp, fp, C.c_void_p, C.c_int, fp, dp, fp, fp, C.c_int]
         L.nyo_select_largest_width.argtypes = [np_, fp, fp, C.c_void_p, C.c_int, ip, ip, fp]
+        L.nyo_set_error_channel.argtypes = [C.c_int]
+        L.nyo_set_error_channel.restype = None
         L.nyo_select_intercept.argtypes = [np_, fp, fp, C.c_void_p, C.c_int, ip, ip, fp]
         L.nyo_domain_verified.argtypes = [C.c_float, C.c_float, C.c_float]
         L.nyo_domain_violated.argtypes = [C.c_float, C.c_float, C.c_float]
@@ -184,8 +186,18 @@ def ibp_forward(net: Net, lo, hi):
     return pl, pu
 
 
-def crown(net: Net, lo, hi, want_intermediate=False):
+def crown(net: Net, lo, hi, want_intermediate=False, error_channel=True):
+    """Plain CROWN with CROWN-IBP intermediates.  error_channel=False leaves the reference's certified
+    per-coefficient error matrices out of the result (see nyo_set_error_channel)."""
     lo, hi = _f32(lo), _f32(hi)
+    lib().nyo_set_error_channel(1 if error_channel else 0)
+    try:
+        return _crown(net, lo, hi, want_intermediate)
+    finally:
+        lib().nyo_set_error_channel(1)
+
+
+def _crown(net: Net, lo, hi, want_intermediate):
     n = int(net.dims[-1])
     ol, ou = np.empty(n, np.float32), np.empty(n, np.float32)
     il = np.empty(net.n_pre, np.float32) if want_intermediate else None
@@ -348,3 +360,66 @@ def pgd_attack(weights, biases, spec, lo, hi, x0, steps, step_size, lr_decay=0.9
         x = np.clip(x - d * step, lo32, hi32).astype(np.float32)
     vals = (forward(best_x)[-1] @ spec.T).min(axis=1).astype(np.float32)
     return vals, best_x
+
+
+def crown_exact_f64(ws, bs, spec, lo, hi, sparse_rule=True):
+    """The plain-CROWN pipeline of nyo_crown (CROWN-IBP collection, merge rules, sparse rule, final tighten) in
+    plain binary64 numpy with NO outward rounding and no error accounting: the value an exact-arithmetic
+    implementation of the same algorithm returns, up to binary64 noise.  A sound floating-point implementation
+    can only be looser than this; tests use it to order the device result between the reference's certified
+    bound and the exact value.  Returns ((lower [S], upper [S]), per-layer tightened bounds)."""
+    ws = [np.asarray(w, np.float64) for w in ws] + [np.asarray(spec, np.float64)]
+    bs = [None if b is None else np.asarray(b, np.float64) for b in bs] + [None]
+    L = len(ws)
+    relu_after = [1] * (L - 2) + [0, 0]
+    lo = np.asarray(lo, np.float64); hi = np.asarray(hi, np.float64)
+    def lin_ibp(k, l, u):
+        wp, wn = np.maximum(ws[k], 0), np.minimum(ws[k], 0)
+        b = 0 if bs[k] is None else bs[k]
+        return wp @ l + wn @ u + b, wp @ u + wn @ l + b
+    ibp = []
+    l, u = lo, hi
+    for k in range(L):
+        a, b = lin_ibp(k, l, u); ibp.append((a, b))
+        l, u = (np.maximum(a, 0), np.maximum(b, 0)) if relu_after[k] else (a, b)
+    t = [None] * L
+    def backward(top, seedn):
+        la = np.eye(seedn); ua = np.eye(seedn); lb = np.zeros(seedn); ub = np.zeros(seedn)
+        for k in range(top, -1, -1):
+            if bs[k] is not None:
+                lb = lb + la @ bs[k]; ub = ub + ua @ bs[k]
+            la = la @ ws[k]; ua = ua @ ws[k]
+            if k > 0 and relu_after[k - 1]:
+                pl, pu = t[k - 1]
+                ls = np.where(pl >= 0, 1.0, np.where(pu <= 0, 0.0, (pu > -pl) * 1.0))
+                us = np.where(pl >= 0, 1.0, np.where(pu <= 0, 0.0, pu / np.where(pu - pl == 0, 1, pu - pl)))
+                ui = np.where((pl < 0) & (pu > 0), -us * pl, 0.0)
+                lb = lb + np.minimum(la, 0) @ ui; ub = ub + np.maximum(ua, 0) @ ui
+                la = np.maximum(la, 0) * ls + np.minimum(la, 0) * us
+                ua = np.maximum(ua, 0) * us + np.minimum(ua, 0) * ls
+        return (np.maximum(la, 0) @ lo + np.minimum(la, 0) @ hi + lb, np.maximum(ua, 0) @ hi + np.minimum(ua, 0) @ lo + ub)
+    def inter(a, b):
+        l, u = np.maximum(a[0], b[0]), np.minimum(a[1], b[1])
+        bad = l > u
+        return np.where(bad, np.minimum(a[0], b[0]), l), np.where(bad, np.maximum(a[1], b[1]), u)
+    for k in range(L):
+        il, iu = ibp[k]
+        if k < L - 1 and relu_after[k] and np.all((il >= 0) | (iu <= 0)):
+            t[k] = (il, iu); continue
+        if k == 0: zl, zu = lo, hi
+        else:
+            act = relu_after[k - 1]
+            z = (np.maximum(t[k-1][0], 0), np.maximum(t[k-1][1], 0)) if act else t[k-1]
+            f0 = (np.maximum(ibp[k-1][0], 0), np.maximum(ibp[k-1][1], 0)) if act else ibp[k-1]
+            zl, zu = inter(f0, z)
+        f = lin_ibp(k, zl, zu)
+        if k < L - 1 and not relu_after[k]:
+            t[k] = inter((il, iu), f); continue
+        c = backward(k, ws[k].shape[0])
+        unst = (f[0] < 0) & (f[1] > 0)
+        n = len(il)
+        if sparse_rule and unst.sum() > 0 and not (np.float32(1.0) - np.float32(unst.sum()) / np.float32(n) < np.float32(0.9)):
+            c = (np.where(unst, c[0], f[0]), np.where(unst, c[1], f[1]))
+        t[k] = inter((il, iu), c)
+    c = backward(L - 1, ws[-1].shape[0])
+    return inter(c, t[L - 1]), t
