@@ -91,7 +91,9 @@ int32_t nyb200_net_create(nyb200_engine *e, int32_t n_linear, const int32_t *dim
  * enum (crates/ny-core/src/gemm_gpu_ibp.rs:31-67).  Tensors are NCHW flattened; a Conv2d layer has
  * dilation 1 and one group, weights W_col [out_channels x in_channels*kernel_h*kernel_w] row-major and an
  * optional per-channel bias [out_channels] (expanded on the device).  A Linear layer has weights
- * [out_features x in_features] and bias [out_features].  wflat / bflat concatenate the layers in order;
+ * [out_features x in_features] and bias [out_features].  A global average pool followed by a Linear layer is
+ * registered as that one Linear layer with the pool folded into its weights (W[i][c] / (H*W) repeated over the
+ * pixels: the backward broadcast A/(H*W) of layers/pooling/average.rs:347,457).  wflat / bflat concatenate the layers in order;
  * layer k's in_features must equal layer k-1's out_features (= out_channels*out_h*out_w for a conv). */
 #define NYB200_LAYER_LINEAR 0
 #define NYB200_LAYER_CONV2D 1
@@ -102,6 +104,12 @@ typedef struct nyb200_layer_desc {
     /* Conv2d only (ConvTranspose2dParams, crates/ny-core/src/gemm.rs:150-178) */
     int32_t in_channels, in_h, in_w, out_channels, out_h, out_w;
     int32_t kernel_h, kernel_w, stride_h, stride_w, pad_h, pad_w;
+    /* Residual connection (GpuResnetSegment::Residual, crates/ny-core/src/gemm.rs:1640-1669): 0 = none;
+     * j + 1 = the post-activation output of layer j (j <= this layer - 2, same width as this layer's output)
+     * is added to this layer's output before its ReLU: pre = W z + b + relu(pre_j).  Skips must not overlap
+     * or nest.  Supported by the interval pass, the bound batch entry points and the attack; the parameter
+     * optimisation and the CROWN-IBP pipeline decline such networks (NYB200_ERR_UNSUPPORTED). */
+    int32_t skip_from;
 } nyb200_layer_desc;
 int32_t nyb200_net_create_layers(nyb200_engine *e, int32_t n_layers, const nyb200_layer_desc *layers,
                                  const float *wflat, const float *bflat, int32_t *net_id);

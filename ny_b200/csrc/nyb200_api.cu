@@ -124,6 +124,8 @@ static int create_net(nyb200_engine *e, int32_t n_layers, const nyb200_layer_des
     net.v.L = n_layers;
     net.kind.resize(n_layers);
     net.geom.resize(n_layers);
+    net.skip.assign(n_layers, -1);
+    int open_until = -1;  // skips may not overlap or nest: the previous one must be consumed first
     int off = 0;
     for (int k = 0; k < n_layers; ++k) {
         const nyb200_layer_desc &l = ld[k];
@@ -145,6 +147,15 @@ static int create_net(nyb200_engine *e, int32_t n_layers, const nyb200_layer_des
             return set_err(e, NYB200_ERR_UNSUPPORTED, "unknown layer kind");
         }
         net.kind[k] = l.kind;
+        if (l.skip_from != 0) {
+            int j = l.skip_from - 1;
+            if (j < 0 || j > k - 2) return set_err(e, NYB200_ERR_INVALID, "skip_from must name a layer at least two before this one");
+            if (ld[j].out_features != l.out_features) return set_err(e, NYB200_ERR_SHAPE, "residual branch widths differ");
+            if (k == n_layers - 1) return set_err(e, NYB200_ERR_UNSUPPORTED, "the last layer cannot take a residual connection");
+            if (j < open_until) return set_err(e, NYB200_ERR_UNSUPPORTED, "overlapping residual connections");
+            open_until = k;
+            net.skip[k] = j;
+        }
         if (k == 0) { net.v.dims[0] = l.in_features; net.max_dim = l.in_features; }
         net.v.dims[k + 1] = l.out_features;
         if (l.out_features > net.max_dim) net.max_dim = l.out_features;
@@ -379,11 +390,14 @@ int run_forward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int fw
         int Deff;
         if (k == 0) { zl = p.in_lo; zu = p.in_hi; in_ds = b.box_stride; Deff = b.box_stride ? D : 1; }
         else { zl = p.zl + nv.pre_off[k - 1]; zu = p.zu + nv.pre_off[k - 1]; in_ds = (long)np; Deff = D; }
-        const bool tk = tensor && k >= 1 && !net.is_conv(k);
+        const bool tk = tensor && k >= 1 && !net.is_conv(k) && net.skip_of(k) < 0;
         if (tk) NYB_TRY(launch_umma(e, net.umma_fwd[k], 2 * D, zl, (int)np, Fl, ldf, derr));  // zl rows, then zu rows
         else if (net.is_conv(k)) launch_ibp_conv(e, nv, net.geom[k], k, Deff, zl, zu, in_ds, p.raw_lo, p.raw_hi, p.q, (long)np);
         else launch_ibp_linear(e, nv, k, Deff, zl, zu, in_ds, p.raw_lo, p.raw_hi, p.q, (long)np);
         long raw_ds = (Deff == 1 && D > 1) ? 0 : (long)np;
+        if (net.skip_of(k) >= 0)  // pre_k = W z + b + relu(pre_j): interval sum, outward
+            launch_skip_interval(e, D, nv.dims[k + 1], (long)np, p.raw_lo, p.raw_hi, nv.pre_off[k], p.zl, p.zu,
+                                 nv.pre_off[net.skip_of(k)]);
         launch_ibp_finish(e, nv, k, D, fwd_mode, p.raw_lo, p.raw_hi, raw_ds, fwd_mode == 2 ? nullptr : p.inh_lo,
                           fwd_mode == 2 ? nullptr : p.inh_hi, p.code, p.sbeta, b.has_alpha ? p.alpha : nullptr, p.pre_lo,
                           p.pre_hi, p.zl, p.zu, p.tab, p.zabs, p.flags, tk ? Fl : nullptr, ldf,
@@ -431,6 +445,8 @@ int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, float
     static const float init_words[8] = {INFINITY, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};  // min lower; loose-domain counter at word 4
     NYB_CUDA(e, cudaMemcpyAsync(p.min_lower, init_words, sizeof(init_words), cudaMemcpyHostToDevice, e->stream));
     float *cur = p.A0, *nxt = p.A1;
+    float *stash = nullptr;
+    int stash_for = -1;
     if (partial) launch_seed_identity(e, S, D, p.lda, cur);
     else launch_seed(e, p.spec, S, nv.dims[L], D, p.lda, cur);
     // rounding rate of the contraction through layer `lin` (accumulation length dims[lin + 1]); convolutions
@@ -456,6 +472,15 @@ int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, float
         // the relaxation writes its result into the ping-pong buffer instead of over its input.
         float *dst = (ckpt && k > 0) ? ckpt[k - 1] : nxt;
         int ldd = (ckpt && k > 0) ? ld_ckpt : p.lda;
+        if (net.skip_of(k) >= 0) {
+            // residual block: these coefficients also multiply relu(pre_j) directly; keep them until the pass
+            // reaches that variable (iteration j + 1 below)
+            stash = (float *)ws_get(e, "skip_coeff", (size_t)M * p.lda * 4);
+            if (!stash) return NYB200_ERR_OOM;
+            NYB_CUDA(e, cudaMemcpy2DAsync(stash, (size_t)p.lda * 4, cur, (size_t)p.lda * 4, (size_t)K * 4, (size_t)M,
+                                          cudaMemcpyDeviceToDevice, e->stream));
+            stash_for = net.skip_of(k);
+        }
         if (e->timing.per_kernel) cudaEventRecord(next_kev(e->timing), e->stream);
         if (net.is_conv(k) && tensor) {
             // reshape (implicit: channel-strided operand) + GEMM with W_col on the tensor cores + col2im gather
@@ -481,6 +506,10 @@ int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, float
             launch_gemm_f64(e, M, N, K, cur, p.lda, nv.W[k], N, dst, ldd, R, zin_lo, zin_hi, zin_ds, p.rpen);
         }
         if (e->timing.per_kernel) cudaEventRecord(next_kev(e->timing), e->stream);
+        if (stash && stash_for == k - 1) {  // dst holds the coefficients of relu(pre_{k-1}): add the identity branch
+            launch_skip_coeff(e, M, N, dst, ldd, stash, p.lda, R, p.zl, p.zu, np, nv.pre_off[k - 1], p.rpen);
+            stash = nullptr;
+        }
         if (k > 0)
             launch_relax(e, nv, k - 1, k - 1, M, R, S, nxt, p.lda, p.tab, p.zabs, p.q, q_ds(k - 1), eps_for(k - 1), p.rb, p.rabs,
                          p.rpen, dst == nxt ? nullptr : dst, ldd);

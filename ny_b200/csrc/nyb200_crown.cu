@@ -195,14 +195,6 @@ __global__ void k_accumulate_loose(const float *__restrict__ min_lower_block, in
     if (threadIdx.x == 0 && blockIdx.x == 0) *acc += ((const int *)min_lower_block)[4];
 }
 
-__global__ void k_gather_block(int D, int n, int off, long stride, const float *__restrict__ src, float *__restrict__ dst,
-                               long dst_stride, int dst_off) {
-    long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (t >= (long)D * n) return;
-    int d = (int)(t / n), j = (int)(t % n);
-    dst[(long)d * dst_stride + dst_off + j] = src[(long)d * stride + off + j];
-}
-
 }  // namespace
 
 static int crown_bounds_once(nyb200_engine *e, int net_id, const float *spec, int S, const float *in_lo,
@@ -216,6 +208,7 @@ static int crown_bounds_once(nyb200_engine *e, int net_id, const float *spec, in
     if (box_stride == 0 && D != 1) return set_err(e, NYB200_ERR_SHAPE, "a shared box is one domain: D must be 1");
     for (int k = 0; k < nv.L; ++k)
         if (net->is_conv(k)) return set_err(e, NYB200_ERR_UNSUPPORTED, "the CROWN-IBP collection is built for Linear layers only");
+    if (net->has_skip()) return set_err(e, NYB200_ERR_UNSUPPORTED, "the CROWN-IBP collection is built for sequential networks only");
     int max_rows = S;
     for (int k = 1; k < nv.L; ++k) max_rows = nv.dims[k] > max_rows ? nv.dims[k] : max_rows;
     if ((long)D * 2 * max_rows > 0x7fffffffL / 64) return set_err(e, NYB200_ERR_UNSUPPORTED, "batch too large for one call");

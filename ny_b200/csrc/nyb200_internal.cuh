@@ -51,7 +51,10 @@ struct Net {
     int max_dim = 0;
     std::vector<int> kind;        // per layer: NYB200_LAYER_LINEAR or NYB200_LAYER_CONV2D
     std::vector<ConvGeom> geom;   // per layer; meaningful for conv layers
+    std::vector<int> skip;        // per layer: index of the layer whose post-activation output is added, or -1
     bool is_conv(int k) const { return !kind.empty() && kind[k] == NYB200_LAYER_CONV2D; }
+    int skip_of(int k) const { return skip.empty() ? -1 : skip[k]; }
+    bool has_skip() const { for (int j : skip) if (j >= 0) return true; return false; }
     std::vector<UmmaLayer> umma;  // filled on first use of the tcgen05 path
     std::vector<UmmaLayer> umma_fwd;  // interval forward operands [W+ | W-] per layer (entry 0 unused)
     std::vector<float *> wt;          // W_k^T, row-major [dims[k] x dims[k+1]] (adjoint pass; built on first use)
@@ -184,6 +187,15 @@ int crown_bounds(nyb200_engine *e, int net_id, const float *spec, int S, const f
 int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg);
 int refine_optimized(nyb200_engine *e, Net &net, Batch &b, BatchPtrs &p);
 int download_params(nyb200_engine *e, float *alpha, float *beta);
+
+// ---- residual connections (nyb200_kernels.cu) ----
+// raw_lo/raw_hi block `off` += the interval [zl, zu] block `src_off`, rounded outward.
+void launch_skip_interval(nyb200_engine *e, int D, int n, long stride, float *raw_lo, float *raw_hi, int off,
+                          const float *zl, const float *zu, int src_off);
+// A[M x n] += S[M x n]; the rounding of every sum is measured exactly and charged against the magnitude of the
+// skipped variable (zl/zu at `src_off`), or ignored when rpen is null.
+void launch_skip_coeff(nyb200_engine *e, int M, int n, float *A, int lda, const float *S, int lds, int R,
+                       const float *zl, const float *zu, long stride, int src_off, double *rpen);
 
 // ---- Conv2d layers (nyb200_conv.cu) ----
 void launch_ibp_conv(nyb200_engine *e, const NetView &nv, const ConvGeom &g, int k, int Deff, const float *zl,

@@ -605,6 +605,45 @@ __global__ void k_fill_f64(double *p, size_t n, double v) {
     if (t < n) p[t] = v;
 }
 
+// ---------------------------------------------------------------- residual connections
+__global__ void k_skip_interval(int D, int n, long stride, float *__restrict__ raw_lo, float *__restrict__ raw_hi, int off,
+                                const float *__restrict__ zl, const float *__restrict__ zu, int src_off) {
+    long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= (long)D * n) return;
+    int d = (int)(t / n), j = (int)(t % n);
+    long o = (long)d * stride + off + j, s = (long)d * stride + src_off + j;
+    raw_lo[o] = __fadd_rd(raw_lo[o], zl[s]);
+    raw_hi[o] = __fadd_ru(raw_hi[o], zu[s]);
+}
+
+// A += S (the identity branch of a residual block meets the coefficients that came through the block:
+// A_in = backward_F(A) + A, crates/ny-core/src/gemm.rs:1640-1669).  One warp per row; the error of each
+// rounded sum is recovered exactly (two-sum) and charged against max|z| of the variable it multiplies.
+__global__ void __launch_bounds__(256)
+k_skip_coeff(int M, int n, float *__restrict__ A, int lda, const float *__restrict__ S, int lds, int R,
+             const float *__restrict__ zl, const float *__restrict__ zu, long stride, int src_off,
+             double *__restrict__ rpen) {
+    int m = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (m >= M) return;
+    int d = m / R;
+    double pen = 0.0;
+    for (int j = lane; j < n; j += 32) {
+        float a = A[(long)m * lda + j], b = S[(long)m * lds + j];
+        float s = a + b;
+        float bb = s - a;
+        float err = (a - (s - bb)) + (b - bb);  // exact residual of the rounded sum
+        A[(long)m * lda + j] = s;
+        if (rpen) {
+            long o = (long)d * stride + src_off + j;
+            pen += fabs((double)err) * (double)fmaxf(fabsf(zl[o]), fabsf(zu[o]));
+        }
+    }
+    if (rpen) {
+        pen = warp_sum(pen);
+        if (lane == 0 && pen != 0.0) atomicAdd(&rpen[m], pen);
+    }
+}
+
 // ---------------------------------------------------------------- launchers
 #define NYB_COUNT(e) ((e)->launches++)
 
@@ -649,6 +688,20 @@ void launch_ibp_finish(nyb200_engine *e, const NetView &nv, int k, int D, int mo
 void launch_seed(nyb200_engine *e, const float *spec, int S, int nL, int D, int lda, float *A) {
     long total = (long)D * 2 * S * nL;
     k_seed<<<(unsigned)((total + 255) / 256), 256, 0, e->stream>>>(spec, S, nL, D, lda, A);
+    NYB_COUNT(e);
+}
+
+void launch_skip_interval(nyb200_engine *e, int D, int n, long stride, float *raw_lo, float *raw_hi, int off,
+                          const float *zl, const float *zu, int src_off) {
+    long tot = (long)D * n;
+    k_skip_interval<<<(unsigned)((tot + 255) / 256), 256, 0, e->stream>>>(D, n, stride, raw_lo, raw_hi, off, zl, zu, src_off);
+    NYB_COUNT(e);
+}
+
+void launch_skip_coeff(nyb200_engine *e, int M, int n, float *A, int lda, const float *S, int lds, int R,
+                       const float *zl, const float *zu, long stride, int src_off, double *rpen) {
+    long threads = (long)M * 32;
+    k_skip_coeff<<<(unsigned)((threads + 255) / 256), 256, 0, e->stream>>>(M, n, A, lda, S, lds, R, zl, zu, stride, src_off, rpen);
     NYB_COUNT(e);
 }
 

@@ -200,6 +200,8 @@ int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg) {
         return set_err(e, NYB200_ERR_INVALID, "learning rates must be >= 0 and the decay > 0");
     Net *net;
     NYB_TRY(find_net(e, e->batch.net_id, &net));
+    if (net->has_skip() && cfg.iterations > 1)
+        return set_err(e, NYB200_ERR_UNSUPPORTED, "parameter optimisation of networks with residual connections is not built");
     Batch &b = e->batch;
     BatchPtrs p;
     NYB_TRY(batch_ptrs(e, *net, b, p));

@@ -105,6 +105,15 @@ __global__ void k_nan_rows(int K, int n0, const float *__restrict__ G, int ldg, 
     if (lane == 0) nan_row[warp] = bad;
 }
 
+// Y[r, j] += X[r, j]
+__global__ void k_add_rows(long rows, int n, float *__restrict__ Y, int ldy, const float *__restrict__ X, int ldx) {
+    long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= rows * n) return;
+    long r = t / n;
+    int j = (int)(t - r * n);
+    Y[r * ldy + j] += X[r * ldx + j];
+}
+
 __global__ void k_fill_f32(float *p, long n, float v) {
     long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (t < n) p[t] = v;
@@ -125,6 +134,10 @@ static int pgd_forward(nyb200_engine *e, Net &net, bool tensor, int rows, const 
         else if (tensor) NYB_TRY(launch_umma(e, net.umma_adj[k], rows, cur, ldc, act[k], ld, derr));
         else launch_gemm_f64(e, rows, N, K, cur, ldc, net.wt[k], N, act[k], ld, 1, nullptr, nullptr, 0, nullptr);
         long tot = (long)rows * N;
+        if (net.skip_of(k) >= 0) {  // residual: the block's input joins before the bias and the ReLU
+            k_add_rows<<<(unsigned)((tot + 255) / 256), 256, 0, e->stream>>>(rows, N, act[k], ld, act[net.skip_of(k)], ld);
+            e->launches++;
+        }
         k_bias_act<<<(unsigned)((tot + 255) / 256), 256, 0, e->stream>>>(rows, N, act[k], ld, nv.b[k], k < nv.L - 1 ? 1 : 0);
         e->launches++;
         cur = act[k];
@@ -194,12 +207,26 @@ int pgd_attack(nyb200_engine *e, int net_id, const float *spec, int S, const flo
         if (last) break;
         // exact gradient of the chosen row: G_k = (G_{k+1} . [z_k > 0]) W_k, down to the input
         float *g = G0, *gn = G1;
+        float *gstash = nullptr;
+        int stash_for = -1;
         for (int k = L - 1; k >= 0; --k) {
             int Kd = nv.dims[k + 1], N = nv.dims[k];
+            if (gstash && stash_for == k) {  // g is the gradient of relu(pre_k): the identity branch joins here
+                long tot = (long)K * Kd;
+                k_add_rows<<<(unsigned)((tot + 255) / 256), 256, 0, st>>>(K, Kd, g, ld, gstash, ld);
+                e->launches++;
+                gstash = nullptr;
+            }
             if (k < L - 1) {
                 long tot = (long)K * Kd;
                 k_relu_mask<<<(unsigned)((tot + 255) / 256), 256, 0, st>>>(K, Kd, g, ld, act[k], ld);
                 e->launches++;
+            }
+            if (net->skip_of(k) >= 0) {  // the gradient of pre_k also reaches relu(pre_j) directly
+                gstash = (float *)ws_get(e, "pgd_skip", (size_t)K * ld * 4);
+                if (!gstash) return NYB200_ERR_OOM;
+                NYB_CUDA(e, cudaMemcpyAsync(gstash, g, (size_t)K * ld * 4, cudaMemcpyDeviceToDevice, st));
+                stash_for = net->skip_of(k);
             }
             if (net->is_conv(k) && tensor) {
                 const ConvGeom &cg = net->geom[k];

@@ -129,7 +129,7 @@ class LayerDesc(C.Structure):
     """nyb200_layer_desc."""
     _fields_ = [(n, C.c_int32) for n in (
         "kind", "in_features", "out_features", "has_bias", "in_channels", "in_h", "in_w", "out_channels", "out_h",
-        "out_w", "kernel_h", "kernel_w", "stride_h", "stride_w", "pad_h", "pad_w")]
+        "out_w", "kernel_h", "kernel_w", "stride_h", "stride_w", "pad_h", "pad_w", "skip_from")]
 
 
 class Conv2d:
@@ -178,9 +178,12 @@ class Network:
     """Sequential ReLU network description (host side): weights[k] is a [out, in] row-major matrix (Linear) or a
     Conv2d; every layer but the last is followed by a ReLU."""
 
-    def __init__(self, weights, biases=None):
+    def __init__(self, weights, biases=None, skips=None):
+        """skips: optional {k: j}: the post-activation output of layer j is added to layer k's output before its
+        ReLU (a residual block's identity branch); j <= k - 2, equal widths."""
         self.weights = [w if isinstance(w, Conv2d) else _f32(w) for w in weights]
         L = len(self.weights)
+        self.skips = dict(skips or {})
         biases = biases if biases is not None else [None] * L
         self.biases = [w.bias if isinstance(w, Conv2d) else (None if b is None else _f32(b))
                        for w, b in zip(self.weights, biases)]
@@ -194,6 +197,10 @@ class Network:
                     raise EngineError(SHAPE, f"layer {k}: conv input size {w.in_features} != {self.dims[k]}")
             elif w.shape != (self.dims[k + 1], self.dims[k]):
                 raise EngineError(SHAPE, f"layer {k}: weight shape {w.shape}")
+
+        for k, j in self.skips.items():
+            if not (0 <= j <= k - 2) or k >= L - 1 or self.dims[j + 1] != self.dims[k + 1]:
+                raise EngineError(SHAPE, f"residual connection {j} -> {k}")
 
     @property
     def has_conv(self) -> bool:
@@ -276,7 +283,7 @@ class B200Engine:
 
     # -- network residency -----------------------------------------------------------------
     def register_network(self, net: Network) -> int:
-        if net.has_conv:
+        if net.has_conv or net.skips:
             return self._register_layers(net)
         w = np.concatenate([x.ravel() for x in net.weights]).astype(np.float32)
         bl = [b for b in net.biases if b is not None]
@@ -298,6 +305,7 @@ class B200Engine:
             else:
                 descs[k] = LayerDesc(0, w.shape[1], w.shape[0], 0 if net.biases[k] is None else 1)
                 ws.append(w.ravel())
+            descs[k].skip_from = net.skips.get(k, -1) + 1
             if net.biases[k] is not None:
                 bs.append(net.biases[k])
         wf = np.concatenate(ws).astype(np.float32)

@@ -34,10 +34,14 @@ def forward(net: Network, x) -> np.ndarray:
     one = z.ndim == 1
     if one:
         z = z[None, :]
+    posts = []
     for k in range(len(net.weights)):
         z = net.layer_forward(k, z)
+        if k in net.skips:
+            z = z + posts[net.skips[k]]
         if k + 1 < len(net.weights):
             z = np.maximum(z, 0.0)
+        posts.append(z)
     return z[0] if one else z
 
 
@@ -108,6 +112,42 @@ def make_cnn(seed: int, in_chw=(3, 32, 32), convs=((16, 4, 2, 1), (32, 4, 2, 1))
         bs.append((g.standard_normal(width) * 0.1).astype(np.float32))
         n = width
     return Network(ws, bs)
+
+
+def make_resnet(seed: int, in_chw=(3, 32, 32), channels: int = 64, blocks: int = 4, n_out: int = 10) -> Network:
+    """conv stem (channels, k3, s1, p1) + `blocks` residual blocks (two 3x3 convs, ReLU, identity skip) + global
+    average pool + FC channels -> n_out, He-initialised.  The pool and the FC are one Linear layer (the pool folded
+    into its weights: W[i][c] / (H*W) over the pixels, exact in fp32 for power-of-two H*W)."""
+    g = _rng(seed)
+    c, h, w = in_chw
+    layers, skips = [], {}
+    def conv(ci, co):
+        wt = (g.standard_normal((co, ci, 3, 3)) * np.sqrt(2.0 / (ci * 9))).astype(np.float32)
+        b = (g.standard_normal(co) * 0.1).astype(np.float32)
+        return Conv2d(wt, b, (1, 1), (1, 1), (h, w))
+    layers.append(conv(c, channels))
+    for _ in range(blocks):
+        layers.append(conv(channels, channels))
+        layers.append(conv(channels, channels))
+        skips[len(layers) - 1] = len(layers) - 3
+    fc = (g.standard_normal((n_out, channels)) * np.sqrt(2.0 / channels)).astype(np.float32)
+    fb = (g.standard_normal(n_out) * 0.1).astype(np.float32)
+    pooled = np.repeat(fc / np.float32(h * w), h * w, axis=1).astype(np.float32)
+    return Network(layers + [pooled], [None] * len(layers) + [fb], skips)
+
+
+def config_resnet(seed: int = 5, eps: float = 1.0 / 255.0, n_fix: int = 8, **kw) -> Workload:
+    """Residual CNN on 3x32x32 (stem + 4 blocks of two 3x3 convs, 64 channels, avgpool, FC 64->10), box x0 +- 1/255
+    clipped to [0,1], 9 margin rows."""
+    net = make_resnet(seed, **kw)
+    g = _rng(seed + 1000)
+    n_in = int(net.dims[0])
+    x0 = g.uniform(0, 1, n_in).astype(np.float32)
+    lo = np.clip(x0 - np.float32(eps), 0, 1).astype(np.float32)
+    hi = np.clip(x0 + np.float32(eps), 0, 1).astype(np.float32)
+    c = int(np.argmax(forward(net, x0)))
+    return Workload("resnet_" + "_".join(str(int(d)) for d in net.dims[:3]), net, x0, lo, hi,
+                    margin_spec(int(net.dims[-1]), c), n_fix, seed, {"eps": eps, "label": c})
 
 
 def config_cnn(seed: int = 3, eps: float = 2.0 / 255.0, n_fix: int = 8, **kw) -> Workload:
@@ -194,8 +234,12 @@ def sample_min_margin(wl: Workload, n_samples: int, seed: int, splits=None, chun
         x = wl.in_lo.astype(np.float64) + g.random((n, len(wl.in_lo))) * (wl.in_hi.astype(np.float64) - wl.in_lo)
         z = x
         ok = np.ones(n, bool)
+        posts = []
         for k in range(len(net.weights)):
             z = net.layer_forward(k, z)
+            if k in net.skips:
+                z = z + posts[net.skips[k]]
+            posts.append(None)
             if k + 1 < len(net.weights):
                 if splits is not None:
                     for s in splits:
@@ -203,6 +247,7 @@ def sample_min_margin(wl: Workload, n_samples: int, seed: int, splits=None, chun
                             v = z[:, s["neuron"]]
                             ok &= (v >= 0) if s["sign"] > 0 else (v <= 0)
                 z = np.maximum(z, 0.0)
+            posts[k] = z
         m = z @ wl.spec.astype(np.float64).T
         if ok.any():
             best = np.minimum(best, m[ok].min(axis=0))

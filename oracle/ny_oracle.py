@@ -163,6 +163,38 @@ def conv2d_dense(weight, bias, stride, pad, in_hw):
     return W.reshape(oc * oh * ow, ic * ih * iw), b
 
 
+def lower_residual(ws, bs, skips):
+    """Sequential (dense) form of a network with identity skips {k: j} (relu(pre_j) added to layer k's output):
+    the skipped activation is carried alongside as extra neurons through identity rows - relu is the identity on
+    them, their interval being non-negative - and joins through an identity block of layer k:
+        layers j+1 .. k-1:  [[W, 0], [0, I]],   layer k:  [W | I].
+    The bounds of the original neurons are those of the leading dims of every layer.  Returns
+    (weights, biases, widths) where widths[k] is the number of original neurons of layer k."""
+    ws = [np.asarray(w, np.float32) for w in ws]
+    out_w, out_b, widths = [], [], []
+    carry = None  # (layer that consumes the carried activation, its width)
+    for k, w in enumerate(ws):
+        n_out, n_in = w.shape
+        b = np.zeros(n_out, np.float32) if bs[k] is None else np.asarray(bs[k], np.float32)
+        if carry is not None and carry[0] == k:      # the identity branch joins: [W | I]
+            w = np.concatenate([w, np.eye(carry[1], dtype=np.float32)], axis=1)
+            carry = None
+        elif carry is not None:                      # pass the carried activation through: [[W, 0], [0, I]]
+            c = carry[1]
+            w = np.block([[w, np.zeros((n_out, c), np.float32)], [np.zeros((c, n_in), np.float32), np.eye(c, dtype=np.float32)]])
+            b = np.concatenate([b, np.zeros(c, np.float32)])
+        opens = [kk for kk, j in skips.items() if j == k - 1]
+        if opens:                                     # this layer's input is skipped forward: duplicate it
+            assert carry is None and len(opens) == 1 and w.shape[1] == n_in, "nested or overlapping skips"
+            w = np.concatenate([w, np.eye(n_in, dtype=np.float32)], axis=0)
+            b = np.concatenate([b, np.zeros(n_in, np.float32)])
+            carry = (opens[0], n_in)
+        out_w.append(np.ascontiguousarray(w, np.float32))
+        out_b.append(b)
+        widths.append(n_out)
+    return out_w, out_b, widths
+
+
 def lower_network(layers, biases):
     """Dense (weights, biases) lists for a sequential network whose entries are matrices or conv layer
     descriptions (objects with weight, bias, sh, sw, ph, pw, ih, iw attributes)."""

@@ -1,0 +1,117 @@
+"""GPU parity tests for networks with residual connections (identity skips around two convolutions) against the
+oracle evaluated on a sequential lowering of the same network: the skipped activation is carried as extra neurons
+through identity rows (oracle.lower_residual), which changes no value - relu is the identity on a non-negative
+interval - so the bounds of the original neurons are the same network's bounds."""
+import numpy as np
+import pytest
+
+from ny_b200 import workloads as W
+from test_gpu_parity import _rel, REL_TOL, IBP_REL
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module", params=["tf32x3", "f64"])
+def eng(request):
+    from ny_b200 import B200Engine, engine
+
+    e = B200Engine(0)
+    e.set_path(engine.PATH_TF32X3 if request.param == "tf32x3" else engine.PATH_F64)
+    e.path_name = request.param
+    yield e
+    e.close()
+
+
+def _small(seed=61, eps=0.02, n_fix=3):
+    return W.config_resnet(seed=seed, eps=eps, n_fix=n_fix, in_chw=(2, 8, 8), channels=4, blocks=2, n_out=5)
+
+
+def _lowered(oracle, wl):
+    ws, bs = oracle.lower_network(wl.net.weights, wl.net.biases)
+    lw, lb, widths = oracle.lower_residual(ws, bs, wl.net.skips)
+    onet = oracle.Net(lw, lb)
+    wide = [w.shape[0] for w in lw]
+    # index of every original neuron inside the lowered network's pre-activation layout
+    idx, off = [], 0
+    for k, n in enumerate(widths):
+        idx.append(off + np.arange(n))
+        off += wide[k]
+    return onet, np.concatenate(idx)
+
+
+def test_lowering_is_the_same_function(oracle):
+    wl = _small()
+    onet, _ = _lowered(oracle, wl)
+    g = np.random.Generator(np.random.PCG64(1))
+    x = wl.in_lo + g.random((16, len(wl.in_lo))) * (wl.in_hi - wl.in_lo)
+    assert np.abs(onet.forward(x) - W.forward(wl.net, x)).max() < 1e-12
+
+
+def test_residual_ibp_matches_oracle(eng, oracle):
+    wl = _small()
+    onet, idx = _lowered(oracle, wl)
+    nid = eng.register_network(wl.net)
+    pl, pu = eng.ibp_forward_gpu(nid, wl.in_lo, wl.in_hi)
+    rl, ru = oracle.ibp_forward(onet, wl.in_lo, wl.in_hi)
+    tol = IBP_REL * np.maximum(np.abs(rl[idx]), np.abs(ru[idx])) + 1e-7
+    assert np.all(np.abs(pl[0] - rl[idx]) <= tol) and np.all(np.abs(pu[0] - ru[idx]) <= tol)
+    eng.release_network(nid)
+
+
+@pytest.mark.parametrize("mode", [0, 1])
+def test_residual_bab_bound_batch_matches_oracle(eng, oracle, mode):
+    wl = _small(seed=62)
+    onet, idx = _lowered(oracle, wl)
+    ospec = onet.with_spec(wl.spec)
+    nid = eng.register_network(wl.net)
+    rl, ru = oracle.ibp_forward(onet, wl.in_lo, wl.in_hi)
+    D = 64
+    splits, ns = W.draw_domains(wl, rl[idx], ru[idx], D)
+    ns = ns.copy()
+    ns[0] = 0
+    glo, ghi, ginf = eng.bab_bound_batch(nid, wl.spec, wl.in_lo, wl.in_hi, rl[idx], ru[idx], splits, ns, mode=mode)
+    S = wl.spec.shape[0]
+    rl2 = np.concatenate([rl, np.full(S, -np.inf, np.float32)])
+    ru2 = np.concatenate([ru, np.full(S, np.inf, np.float32)])
+    olo, ohi, oinf, _ = oracle.bab_bound_batch(ospec, wl.in_lo, wl.in_hi, rl2, ru2, splits, ns, mode)
+    assert np.array_equal(ginf.astype(bool), oinf.astype(bool))
+    feas = ~oinf.astype(bool)
+    assert feas.sum() > D // 2
+    assert _rel(np.concatenate([glo, ghi], axis=1)[feas], np.concatenate([olo, ohi], axis=1)[feas]) <= REL_TOL
+    for d in np.flatnonzero(feas)[:5]:
+        mn = W.sample_min_margin(wl, 20000, 300 + d, splits[d][: ns[d]])
+        ok = np.isfinite(mn)
+        assert np.all(glo[d][ok] <= mn[ok]), d
+    eng.release_network(nid)
+
+
+def test_residual_pgd_and_declined_entry_points(eng, oracle):
+    from ny_b200 import EngineError
+
+    wl = _small(seed=63, eps=0.08)
+    onet, idx = _lowered(oracle, wl)
+    nid = eng.register_network(wl.net)
+    g = np.random.Generator(np.random.PCG64(4))
+    K, steps = 64, 25
+    x0 = (wl.in_lo + g.random((K, len(wl.in_lo)), dtype=np.float32) * (wl.in_hi - wl.in_lo)).astype(np.float32)
+    best0, bx0, _ = eng.pgd_attack(nid, wl.spec, wl.in_lo, wl.in_hi, x0, 0, 0.01)
+    start = (W.forward(wl.net, x0) @ wl.spec.astype(np.float64).T).min(axis=1)
+    assert np.allclose(best0, start, rtol=1e-5, atol=1e-6)
+    eps = float((wl.in_hi - wl.in_lo).max()) / 2
+    best, bx, ce = eng.pgd_attack(nid, wl.spec, wl.in_lo, wl.in_hi, x0, steps, 0.25 * eps)
+    true = (W.forward(wl.net, bx) @ wl.spec.astype(np.float64).T).min(axis=1)
+    assert np.allclose(best, true, rtol=1e-5, atol=1e-6) and np.all(best <= start + 1e-6) and best.mean() < start.mean()
+    obest, _ = oracle.pgd_attack(onet.weights, onet.biases, wl.spec, wl.in_lo, wl.in_hi, x0, steps, 0.25 * eps)
+    scale = np.abs(start).mean()
+    assert np.abs(best - obest).max() <= 0.05 * scale and np.abs(best - obest).mean() <= 0.005 * scale
+    # entry points that are not built for residual networks decline instead of returning something else
+    rl, ru = oracle.ibp_forward(onet, wl.in_lo, wl.in_hi)
+    splits, ns = W.draw_domains(wl, rl[idx], ru[idx], 4)
+    eng.batch_upload(nid, wl.spec, wl.in_lo, wl.in_hi, rl[idx], ru[idx], splits, ns, mode=1)
+    with pytest.raises(EngineError) as ei:
+        eng.batch_optimize(3)
+    assert ei.value.code == 1
+    with pytest.raises(EngineError) as ei:
+        eng.crown_bounds(nid, wl.spec, wl.in_lo, wl.in_hi)
+    assert ei.value.code == 1
+    eng.release_network(nid)
