@@ -394,7 +394,7 @@ def run_alpha_crown(args, rank, world, local_rank):
     eng.close()
 
 
-def run_cnn(args, local_rank):
+def run_cnn(args, local_rank, kind="cnn"):
     """Secondary workload (--workload cnn): beta-CROWN bound of 1024 BaB domains (8 splits each) of the CNN
     3x32x32 -> conv(16,k4,s2,p1) -> conv(32,k4,s2,p1) -> FC 2048->100 -> FC 100->10, box x0 +- 2/255, 9 spec rows.
     One step = one bound evaluation of the whole batch (interval convolutions forward, transposed convolutions
@@ -410,11 +410,11 @@ def run_cnn(args, local_rank):
     stream = torch.cuda.current_stream()
     eng = B200Engine(local_rank, stream.cuda_stream)
     eng.set_path(E.PATH_TF32X3 if args.path == "tf32x3" else E.PATH_F64)
-    wl = W.config_cnn()
+    wl = W.config_cnn() if kind == "cnn" else W.config_resnet()
     nid = eng.register_network(wl.net)
     pl, pu = eng.ibp_forward_gpu(nid, wl.in_lo, wl.in_hi)
     rl, ru = pl[0].copy(), pu[0].copy()
-    D = args.domains if args.domains != D_PER_GPU else 1024
+    D = args.domains if args.domains != D_PER_GPU else (1024 if kind == "cnn" else 256)
     splits, ns = W.draw_domains(wl, rl, ru, D)
     eng.batch_upload(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, splits, ns, mode=1)
     for _ in range(max(args.warmup, 3)):
@@ -461,8 +461,11 @@ def run_cnn(args, local_rank):
         "metric": METRIC, "value": D / (ms / 1e3), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f64 convolutions, " + args.path + " fully connected", "data": "synthetic",
-        "config": {"workload": "beta-CROWN bound of BaB domains, CNN 3x32x32 conv(16,k4,s2,p1)-conv(32,k4,s2,p1)-FC100-FC10, "
-                               "box x0+-2/255, 9 spec rows (both directions), 8 splits/domain, transposed-convolution backward",
+        "config": {"workload": ("beta-CROWN bound of BaB domains, CNN 3x32x32 conv(16,k4,s2,p1)-conv(32,k4,s2,p1)-FC100-FC10, "
+                                "box x0+-2/255, 9 spec rows (both directions), 8 splits/domain, transposed-convolution backward")
+                               if kind == "cnn" else
+                               ("beta-CROWN bound of BaB domains, residual CNN 3x32x32: conv stem (64,k3) + 4 residual blocks "
+                                "(two 3x3 convs, 64 ch) + avgpool + FC 64->10, box x0+-1/255, 9 spec rows, 8 splits/domain"),
                    "domains_per_gpu": D, "feasible_domains": int((ginf == 0).sum()),
                    "domains_sent_to_binary64_rerun": int(refined),
                    "l2": "coefficient ping-pong buffers (2 x 302 MB) exceed the 126 MB L2"},
@@ -476,7 +479,7 @@ def run_cnn(args, local_rank):
                      "flops_view": {"achieved_tflops": flops / (gemm_ms / 1e3) / 1e12 if gemm_ms > 0 else None},
                      "phase_ms": {"forward": fwd_ms, "backward": bwd_ms, "contraction": gemm_ms}},
     }
-    if not args.no_cpu_baseline:
+    if not args.no_cpu_baseline and kind == "cnn":  # (the residual network's dense lowering does not fit in memory)
         ws, bs = O.lower_network(wl.net.weights, wl.net.biases)
         onet = O.Net(ws, bs).with_spec(wl.spec)
         rl2 = np.concatenate([rl, np.full(S, -np.inf, np.float32)])
@@ -566,7 +569,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--path", default=os.environ.get("NYB200_PATH", "tf32x3"), choices=["f64", "tf32x3"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="bab", choices=["bab", "alpha-crown", "cnn", "pgd"],
+    ap.add_argument("--workload", default="bab", choices=["bab", "alpha-crown", "cnn", "resnet", "pgd"],
                     help="bab: the headline beta-CROWN batch (default); alpha-crown: the alpha optimisation case; "
                          "cnn: the convolutional case (both 1 GPU)")
     ap.add_argument("--domains", type=int, default=D_PER_GPU, help="domains per GPU (profiling runs use a smaller batch)")
@@ -585,9 +588,9 @@ def main():
         if rank == 0:
             run_pgd(args, local_rank)
         return
-    if args.workload == "cnn":
+    if args.workload in ("cnn", "resnet"):
         if rank == 0:
-            run_cnn(args, local_rank)
+            run_cnn(args, local_rank, args.workload)
         return
     run_ours(args, rank, world, local_rank)
 

@@ -365,9 +365,10 @@ int run_forward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int fw
     if (tensor) {
         if (net.umma_fwd.empty()) {
             net.umma_fwd.resize(nv.L);
-            for (int k = 1; k < nv.L; ++k)
-                if (!net.is_conv(k))
-                    NYB_TRY(umma_prepare_forward_layer(e, nv.W[k], nv.dims[k], nv.dims[k + 1], &net.umma_fwd[k]));
+            for (int k = 1; k < nv.L; ++k) {
+                if (!net.is_conv(k)) NYB_TRY(umma_prepare_forward_layer(e, nv.W[k], nv.dims[k], nv.dims[k + 1], &net.umma_fwd[k]));
+                else NYB_TRY(prepare_conv_forward_operand(e, nv.W[k], net.geom[k], true, &net.umma_fwd[k]));
+            }
         }
         int mo = 0;
         for (int k = 1; k < nv.L; ++k)
@@ -391,7 +392,18 @@ int run_forward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int fw
         if (k == 0) { zl = p.in_lo; zu = p.in_hi; in_ds = b.box_stride; Deff = b.box_stride ? D : 1; }
         else { zl = p.zl + nv.pre_off[k - 1]; zu = p.zu + nv.pre_off[k - 1]; in_ds = (long)np; Deff = D; }
         const bool tk = tensor && k >= 1 && !net.is_conv(k) && net.skip_of(k) < 0;
+        const bool tconv = tensor && k >= 1 && net.is_conv(k);
         if (tk) NYB_TRY(launch_umma(e, net.umma_fwd[k], 2 * D, zl, (int)np, Fl, ldf, derr));  // zl rows, then zu rows
+        else if (tconv) {
+            // per-pixel products of the lower-end rows, then the upper-end rows, with [W+ | W-]; then the gather
+            const ConvGeom &g = net.geom[k];
+            const int plane = g.ih * g.iw, N = 2 * g.oc * g.kh * g.kw;
+            if ((long)2 * D * plane > 0x7fffffffL) return set_err(e, NYB200_ERR_UNSUPPORTED, "batch too large for the convolution's product space");
+            float *cols = (float *)ws_get(e, "conv_cols", (size_t)2 * D * plane * N * 4);
+            if (!cols) return NYB200_ERR_OOM;
+            NYB_TRY(launch_umma(e, net.umma_fwd[k], 2 * D * plane, zl, (int)np, cols, N, derr, plane));
+            launch_ibp_conv_gather(e, nv, g, k, D, cols, umma_eps(g.ic) * 1.000001, p.raw_lo, p.raw_hi, p.q, (long)np);
+        }
         else if (net.is_conv(k)) launch_ibp_conv(e, nv, net.geom[k], k, Deff, zl, zu, in_ds, p.raw_lo, p.raw_hi, p.q, (long)np);
         else launch_ibp_linear(e, nv, k, Deff, zl, zu, in_ds, p.raw_lo, p.raw_hi, p.q, (long)np);
         long raw_ds = (Deff == 1 && D > 1) ? 0 : (long)np;

@@ -326,7 +326,120 @@ k_conv_plain(ConvGeom g, int rows, const float *__restrict__ Z, int ldz, const f
     out[(long)r * ldo + o] = (float)acc;
 }
 
+// ---- forward convolutions on the tensor cores -----------------------------------------------------------------
+// A convolution is, per input pixel, a product of that pixel's channel vector with every (output channel, tap)
+// weight, followed by a gather: y[co, oy, ox] = sum_{ky, kx} P[(iy, ix), (co, ky, kx)] with iy = oy*sh - ph + ky.
+// The product P = x[:, pixel] * Wf, Wf [ic x oc*kh*kw], is the same contraction as the transposed convolution's
+// (channel-strided operand, tap-major result); only the gather differs.  Any stride is covered (a stride s uses
+// one tap in s*s per pixel; the unused products are wasted tensor work, not traffic that matters here).
+
+// Wf[ci][(co, ky, kx)] = W_col[co][(ci, ky, kx)]; with `split`: [max(W, 0) | min(W, 0)], 2*oc*kk columns.
+__global__ void k_build_conv_fwd(const float *__restrict__ W, int oc, int ic, int kk, int split, float *__restrict__ out) {
+    const int N = (split ? 2 : 1) * oc * kk;
+    long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= (long)ic * N) return;
+    int ci = (int)(t / N), n = (int)(t % N);
+    int neg = n >= oc * kk;
+    int r = n - (neg ? oc * kk : 0);
+    int co = r / kk, tap = r % kk;
+    float w = W[((long)co * ic + ci) * kk + tap];
+    out[t] = split ? (neg ? fminf(w, 0.f) : fmaxf(w, 0.f)) : w;
+}
+
+// Interval convolution from the products of the lower-end rows (m = d) and upper-end rows (m = D + d) of a
+// non-negative input interval with [W+ | W-]: lo = W+ zl + W- zu + b, hi = W+ zu + W- zl + b, q = |W| zu.
+// The taps of an output are summed in binary64; every product carries a rounding of at most eps times the sum of
+// its term magnitudes, all bounded by q, so both ends move outward by eps * q before the directed cast (the same
+// accounting as the fully connected tensor forward pass).
+__global__ void __launch_bounds__(256)
+k_ibp_conv_gather(ConvGeom g, int D, const float *__restrict__ cols, const float *__restrict__ bias, double eps,
+                  float *__restrict__ raw_lo, float *__restrict__ raw_hi, float *__restrict__ q, long out_ds,
+                  float inv_ow, float inv_plane) {
+    const int plane_out = g.oh * g.ow, plane_in = g.ih * g.iw, kk = g.kh * g.kw, N = 2 * g.oc * kk;
+    const int d = blockIdx.y;
+    const int o = blockIdx.x * blockDim.x + threadIdx.x;
+    if (o >= g.oc * plane_out) return;
+    const int co = small_div(o, inv_plane), pix = o - co * plane_out;
+    const int oy = small_div(pix, inv_ow), ox = pix - oy * g.ow;
+    const float *lo_rows = cols + (long)d * N * plane_in, *hi_rows = cols + (long)(D + d) * N * plane_in;
+    const long pos_off = (long)co * kk * plane_in, neg_off = (long)(g.oc + co) * kk * plane_in;
+    double pl = 0.0, nl = 0.0, pu = 0.0, nu = 0.0;
+    for (int ky = 0; ky < g.kh; ++ky) {
+        int iy = oy * g.sh - g.ph + ky;
+        if (iy < 0 || iy >= g.ih) continue;
+        for (int kx = 0; kx < g.kw; ++kx) {
+            int ix = ox * g.sw - g.pw + kx;
+            if (ix < 0 || ix >= g.iw) continue;
+            long t = (long)(ky * g.kw + kx) * plane_in + iy * g.iw + ix;
+            pl += (double)lo_rows[pos_off + t]; nl += (double)lo_rows[neg_off + t];
+            pu += (double)hi_rows[pos_off + t]; nu += (double)hi_rows[neg_off + t];
+        }
+    }
+    double b = bias ? (double)bias[o] : 0.0;
+    double qq = (fabs(pu) + fabs(nu)) / (1.0 - 2.0 * eps);
+    double slack = eps * qq + 2.3e-16 * (qq + fabs(b));
+    float l = __double2float_rd(pl + nu + b - slack), u = __double2float_ru(pu + nl + b + slack);
+    if (isnan(l) || isnan(u)) { l = -INFINITY; u = INFINITY; }
+    raw_lo[(long)d * out_ds + o] = l;
+    raw_hi[(long)d * out_ds + o] = u;
+    q[(long)d * out_ds + o] = __double2float_ru(qq);
+}
+
+// Plain forward convolution from the per-pixel products (no bias).
+__global__ void __launch_bounds__(256)
+k_conv_fwd_gather(ConvGeom g, const float *__restrict__ cols, float *__restrict__ out, int ldo, float inv_ow,
+                  float inv_plane) {
+    const int plane_out = g.oh * g.ow, plane_in = g.ih * g.iw, kk = g.kh * g.kw, N = g.oc * kk;
+    const int r = blockIdx.y;
+    const int o = blockIdx.x * blockDim.x + threadIdx.x;
+    if (o >= g.oc * plane_out) return;
+    const int co = small_div(o, inv_plane), pix = o - co * plane_out;
+    const int oy = small_div(pix, inv_ow), ox = pix - oy * g.ow;
+    const float *base = cols + ((long)r * N + (long)co * kk) * plane_in;
+    double acc = 0.0;
+    for (int ky = 0; ky < g.kh; ++ky) {
+        int iy = oy * g.sh - g.ph + ky;
+        if (iy < 0 || iy >= g.ih) continue;
+        for (int kx = 0; kx < g.kw; ++kx) {
+            int ix = ox * g.sw - g.pw + kx;
+            if (ix < 0 || ix >= g.iw) continue;
+            acc += (double)base[(long)(ky * g.kw + kx) * plane_in + iy * g.iw + ix];
+        }
+    }
+    out[(long)r * ldo + o] = (float)acc;
+}
+
 }  // namespace
+
+int prepare_conv_forward_operand(nyb200_engine *e, const float *W, const ConvGeom &g, bool split, UmmaLayer *out) {
+    const int kk = g.kh * g.kw, N = (split ? 2 : 1) * g.oc * kk;
+    float *tmp = nullptr;
+    size_t n = (size_t)g.ic * N;
+    if (cudaMalloc(&tmp, n * 4) != cudaSuccess) return NYB200_ERR_OOM;
+    k_build_conv_fwd<<<(unsigned)((n + 255) / 256), 256, 0, e->stream>>>(W, g.oc, g.ic, kk, split ? 1 : 0, tmp);
+    e->launches++;
+    int st = umma_prepare_layer(e, tmp, g.ic, N, out);
+    cudaStreamSynchronize(e->stream);
+    cudaFree(tmp);
+    return st;
+}
+
+void launch_ibp_conv_gather(nyb200_engine *e, const NetView &nv, const ConvGeom &g, int k, int D, const float *cols, double eps,
+                            float *raw_lo, float *raw_hi, float *q, long out_dstride) {
+    int n_out = g.oc * g.oh * g.ow;
+    dim3 grid((unsigned)((n_out + 255) / 256), (unsigned)D);
+    k_ibp_conv_gather<<<grid, 256, 0, e->stream>>>(g, D, cols, nv.b[k], eps, raw_lo + nv.pre_off[k], raw_hi + nv.pre_off[k],
+                                                  q + nv.pre_off[k], out_dstride, 1.0f / (float)g.ow,
+                                                  1.0f / (float)(g.oh * g.ow));
+    e->launches++;
+}
+
+void launch_conv_fwd_gather(nyb200_engine *e, const ConvGeom &g, int rows, const float *cols, float *out, int ldo) {
+    int n_out = g.oc * g.oh * g.ow;
+    dim3 grid((unsigned)((n_out + 255) / 256), (unsigned)rows);
+    k_conv_fwd_gather<<<grid, 256, 0, e->stream>>>(g, cols, out, ldo, 1.0f / (float)g.ow, 1.0f / (float)(g.oh * g.ow));
+    e->launches++;
+}
 
 void launch_ibp_conv(nyb200_engine *e, const NetView &nv, const ConvGeom &g, int k, int Deff, const float *zl,
                      const float *zu, long in_dstride, float *raw_lo, float *raw_hi, float *q, long out_dstride) {

@@ -176,6 +176,7 @@ int run_forward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int fw
 int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, float *const *ckpt, int ld_ckpt, int top = -1);
 int prepare_backward_operands(nyb200_engine *e, Net &net);
 int prepare_transposed(nyb200_engine *e, Net &net, bool tensor);
+int conv_forward_tensor(nyb200_engine *e, Net &net, int k, int rows, const float *Z, int ldz, float *out, int ldo, int *derr);
 void fold_timing(Timing &t);
 cudaEvent_t next_kev(Timing &t);
 
@@ -209,6 +210,12 @@ void launch_conv_transpose(nyb200_engine *e, const ConvGeom &g, int M, const flo
 // Sums the tap-major im2col-space products cols[(m * taps + tap) * plane + (oy, ox)] into C[m, (ci, y, x)]
 // (binary64 sums of the fp32 entries, one cast: charged through the layer's rounding rate).
 void launch_col2im(nyb200_engine *e, const ConvGeom &g, int M, const float *cols, float *C, int ldc);
+// Forward convolutions on the tensor path: operand Wf [ic x oc*kh*kw] (or [W+ | W-] with `split`), the per-pixel
+// products through launch_umma(a_plane = ih*iw), then one of the gathers.
+int prepare_conv_forward_operand(nyb200_engine *e, const float *W, const ConvGeom &g, bool split, UmmaLayer *out);
+void launch_ibp_conv_gather(nyb200_engine *e, const NetView &nv, const ConvGeom &g, int k, int D, const float *cols, double eps,
+                            float *raw_lo, float *raw_hi, float *q, long out_dstride);
+void launch_conv_fwd_gather(nyb200_engine *e, const ConvGeom &g, int rows, const float *cols, float *out, int ldo);
 void launch_conv_plain(nyb200_engine *e, const ConvGeom &g, int rows, const float *Z, int ldz, const float *W, float *out,
                        int ldo);
 

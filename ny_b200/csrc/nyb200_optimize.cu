@@ -186,9 +186,23 @@ int prepare_transposed(nyb200_engine *e, Net &net, bool tensor) {
     }
     if (tensor && net.umma_adj.empty()) {
         net.umma_adj.resize(L);
-        for (int k = 0; k < L; ++k)
+        for (int k = 0; k < L; ++k) {
             if (!net.is_conv(k)) NYB_TRY(umma_prepare_layer(e, net.wt[k], nv.dims[k], nv.dims[k + 1], &net.umma_adj[k]));
+            else NYB_TRY(prepare_conv_forward_operand(e, nv.W[k], net.geom[k], false, &net.umma_adj[k]));
+        }
     }
+    return NYB200_OK;
+}
+
+// out[rows x oc*oh*ow] = convolution k of the rows of Z (no bias), on the tensor path: per-pixel products, gather.
+int conv_forward_tensor(nyb200_engine *e, Net &net, int k, int rows, const float *Z, int ldz, float *out, int ldo, int *derr) {
+    const ConvGeom &g = net.geom[k];
+    const int plane = g.ih * g.iw, N = g.oc * g.kh * g.kw;
+    if ((long)rows * plane > 0x7fffffffL) return set_err(e, NYB200_ERR_UNSUPPORTED, "batch too large for the convolution's product space");
+    float *cols = (float *)ws_get(e, "conv_cols", (size_t)rows * plane * N * 4);
+    if (!cols) return NYB200_ERR_OOM;
+    NYB_TRY(launch_umma(e, net.umma_adj[k], rows * plane, Z, ldz, cols, N, derr, plane));
+    launch_conv_fwd_gather(e, g, rows, cols, out, ldo);
     return NYB200_OK;
 }
 
@@ -273,7 +287,8 @@ int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg) {
         float *zc = z0, *zn = z1;
         for (int k = 0; k < L - 1; ++k) {
             int K = nv.dims[k], N = nv.dims[k + 1];
-            if (net->is_conv(k)) launch_conv_plain(e, net->geom[k], D * S, zc, ldz, nv.W[k], zn, ldz);
+            if (net->is_conv(k) && tensor) NYB_TRY(conv_forward_tensor(e, *net, k, D * S, zc, ldz, zn, ldz, derr));
+            else if (net->is_conv(k)) launch_conv_plain(e, net->geom[k], D * S, zc, ldz, nv.W[k], zn, ldz);
             else if (tensor) NYB_TRY(launch_umma(e, net->umma_adj[k], D * S, zc, ldz, zn, ldz, derr));
             else launch_gemm_f64(e, D * S, N, K, zc, ldz, net->wt[k], N, zn, ldz, 1, nullptr, nullptr, 0, nullptr);
             long nt = (long)D * N;

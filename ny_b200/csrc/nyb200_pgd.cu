@@ -130,7 +130,8 @@ static int pgd_forward(nyb200_engine *e, Net &net, bool tensor, int rows, const 
     int ldc = ldx;
     for (int k = 0; k < nv.L; ++k) {
         int K = nv.dims[k], N = nv.dims[k + 1];
-        if (net.is_conv(k)) launch_conv_plain(e, net.geom[k], rows, cur, ldc, nv.W[k], act[k], ld);
+        if (net.is_conv(k) && tensor) NYB_TRY(conv_forward_tensor(e, net, k, rows, cur, ldc, act[k], ld, derr));
+        else if (net.is_conv(k)) launch_conv_plain(e, net.geom[k], rows, cur, ldc, nv.W[k], act[k], ld);
         else if (tensor) NYB_TRY(launch_umma(e, net.umma_adj[k], rows, cur, ldc, act[k], ld, derr));
         else launch_gemm_f64(e, rows, N, K, cur, ldc, net.wt[k], N, act[k], ld, 1, nullptr, nullptr, 0, nullptr);
         long tot = (long)rows * N;
