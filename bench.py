@@ -493,7 +493,7 @@ def run_cnn(args, local_rank, kind="cnn"):
     eng.close()
 
 
-def run_pgd(args, local_rank):
+def run_pgd(args, local_rank, kind="cnn"):
     """Secondary workload (--workload pgd): PGD attack, 100 steps x 1024 restarts, step 0.25 * eps, margin loss,
     on the CNN 3x32x32 conv(16,k4,s2,p1)-conv(32,k4,s2,p1)-FC100-FC10 with box x0 +- 2/255.  One step of this bench =
     one whole attack (101 forward passes, 100 gradients, the binary64 re-validation); value = restart-steps/s."""
@@ -507,7 +507,7 @@ def run_pgd(args, local_rank):
     torch.cuda.set_device(local_rank)
     eng = B200Engine(local_rank, torch.cuda.current_stream().cuda_stream)
     eng.set_path(E.PATH_TF32X3 if args.path == "tf32x3" else E.PATH_F64)
-    wl = W.config_cnn()
+    wl = W.config_cnn() if kind == "cnn" else W.config_resnet()
     nid = eng.register_network(wl.net)
     K, steps = 1024, 100
     g = np.random.Generator(np.random.PCG64(7))
@@ -525,13 +525,15 @@ def run_pgd(args, local_rank):
     ms = (time.perf_counter() - t0) * 1e3 / n   # host buffers in and out: this is the end-to-end call
     launches = (eng.launch_count() - l0) // n
     clocks = sampler.stop()
-    start = (W.forward(wl.net, x0[:64]) @ wl.spec.astype(np.float64).T).min(axis=1)
+    start = (W.forward(wl.net, x0[:16]) @ wl.spec.astype(np.float64).T).min(axis=1)
     line = {
         "metric": "PGD restart-steps/sec", "value": K * steps / (ms / 1e3), "unit": "restart-steps/s", "n_gpus": 1,
         "steps": n, "warmup": 2, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": args.path, "data": "synthetic",
-        "config": {"workload": "PGD attack, 1024 restarts x 100 steps, step 0.25*eps, margin loss, CNN 3x32x32 "
-                               "conv(16,k4,s2,p1)-conv(32,k4,s2,p1)-FC100-FC10, box x0+-2/255",
+        "config": {"workload": ("PGD attack, 1024 restarts x 100 steps, step 0.25*eps, margin loss, CNN 3x32x32 "
+                                "conv(16,k4,s2,p1)-conv(32,k4,s2,p1)-FC100-FC10, box x0+-2/255") if kind == "cnn" else
+                               ("PGD attack, 1024 restarts x 100 steps, step 0.25*eps, margin loss, residual CNN 3x32x32 "
+                                "(conv stem 64,k3 + 4 residual blocks + avgpool + FC 64->10), box x0+-1/255"),
                    "restarts": K, "pgd_steps": steps, "timing": "wall clock around the host-buffer C-ABI call",
                    "mean_objective_start": float(start.mean()), "mean_objective_end": float(best.mean()),
                    "counterexample": int(ce)},
@@ -539,7 +541,7 @@ def run_pgd(args, local_rank):
                 "d2h_bytes_per_step": int(best.nbytes + bx.nbytes), "ms_per_step": ms},
         "gpu_launches": int(launches), "clocks": clocks,
     }
-    if not args.no_cpu_baseline:
+    if not args.no_cpu_baseline and kind == "cnn":
         ws, bs = O.lower_network(wl.net.weights, wl.net.biases)
         kk, ss = 64, 10
         t0 = time.perf_counter()
@@ -569,7 +571,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--path", default=os.environ.get("NYB200_PATH", "tf32x3"), choices=["f64", "tf32x3"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="bab", choices=["bab", "alpha-crown", "cnn", "resnet", "pgd"],
+    ap.add_argument("--workload", default="bab", choices=["bab", "alpha-crown", "cnn", "resnet", "pgd", "pgd-resnet"],
                     help="bab: the headline beta-CROWN batch (default); alpha-crown: the alpha optimisation case; "
                          "cnn: the convolutional case (both 1 GPU)")
     ap.add_argument("--domains", type=int, default=D_PER_GPU, help="domains per GPU (profiling runs use a smaller batch)")
@@ -584,9 +586,9 @@ def main():
         if rank == 0:
             run_alpha_crown(args, 0, 1, local_rank)
         return
-    if args.workload == "pgd":
+    if args.workload in ("pgd", "pgd-resnet"):
         if rank == 0:
-            run_pgd(args, local_rank)
+            run_pgd(args, local_rank, "cnn" if args.workload == "pgd" else "resnet")
         return
     if args.workload in ("cnn", "resnet"):
         if rank == 0:

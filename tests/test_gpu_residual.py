@@ -115,3 +115,33 @@ def test_residual_pgd_and_declined_entry_points(eng, oracle):
         eng.crown_bounds(nid, wl.spec, wl.in_lo, wl.in_hi)
     assert ei.value.code == 1
     eng.release_network(nid)
+
+
+def test_resnet_full_size(eng, oracle):
+    """The residual configuration at full size (3x32x32, conv stem 64 + 4 residual blocks + avgpool + FC, box
+    +-1/255, 9 rows): 64 split domains through the bound batch, the unsplit domain against sampled executions, a
+    short attack against the concrete network."""
+    wl = W.config_resnet()
+    nid = eng.register_network(wl.net)
+    pl, pu = eng.ibp_forward_gpu(nid, wl.in_lo, wl.in_hi)
+    rl, ru = pl[0], pu[0]
+    assert np.all(rl <= ru)
+    D = 64
+    splits, ns = W.draw_domains(wl, rl, ru, D)
+    ns = ns.copy()
+    ns[0] = 0
+    glo, ghi, ginf = eng.bab_bound_batch(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, splits, ns, mode=1)
+    feas = ginf == 0
+    assert feas.sum() > D // 2 and np.all(np.isfinite(glo[feas])) and np.all(glo[feas] <= ghi[feas])
+    mn = W.sample_min_margin(wl, 300, 9000, splits[0][:0], chunk=100)
+    assert np.all(np.isfinite(mn)) and np.all(glo[0] <= mn) and np.all(ghi[0] >= mn - 1e30)
+    g = np.random.Generator(np.random.PCG64(8))
+    K = 32
+    x0 = (wl.in_lo + g.random((K, len(wl.in_lo)), dtype=np.float32) * (wl.in_hi - wl.in_lo)).astype(np.float32)
+    eps = float((wl.in_hi - wl.in_lo).max()) / 2
+    best, bx, ce = eng.pgd_attack(nid, wl.spec, wl.in_lo, wl.in_hi, x0, 10, 0.25 * eps)
+    true = (W.forward(wl.net, bx) @ wl.spec.astype(np.float64).T).min(axis=1)
+    start = (W.forward(wl.net, x0) @ wl.spec.astype(np.float64).T).min(axis=1)
+    assert np.allclose(best, true, rtol=1e-4, atol=1e-5) and np.all(best <= start + 1e-5) and best.mean() < start.mean()
+    assert np.all(glo[0].min() <= best + 1e-5)          # the unsplit domain's bound is below every attacked point
+    eng.release_network(nid)
