@@ -391,6 +391,83 @@ k_relax_v4(int n, int off, int M, int R, int S, long nps, float *A, int lda, con
     }
 }
 
+// Domain-major form of the same pass.  The relaxation table, the magnitudes and the bias of a column are shared
+// by all R rows of a domain; with one warp per row they are fetched R times (36 bytes per coefficient through
+// L1 against 8 for the coefficient itself).  Here a warp owns 128 columns of one domain: every lane keeps the
+// tables of its 4 columns in registers and walks the domain's rows, so the tables are read once.
+template <bool UPPER, bool RELAX, bool BIAS>
+__device__ __forceinline__ void relax_dom_rows(int r0, int r1, long m0, int j, float *A, int lda, const float *Asrc, int lds,
+                                               const float4 &t0, const float4 &t1, const float4 &t2, const float4 &t3,
+                                               const float4 &za, const float4 &qv, const float4 &bk, float eps, int lane,
+                                               bool live, double *__restrict__ rb, double *__restrict__ rabs,
+                                               double *__restrict__ rpen) {
+    // Rows are taken RB at a time: all their loads are issued before the first is used, so a lane has RB
+    // independent 16-byte requests in flight (a warp that walks one row after the other is latency bound).
+    constexpr int RB = 5;
+    for (int rbase = r0; rbase < r1; rbase += RB) {
+        float4 a[RB];
+#pragma unroll
+        for (int u = 0; u < RB; ++u) {
+            const long m = m0 + rbase + u;
+            // lanes past the row's end take part in the reductions with zeros (their tables are zero too)
+            a[u] = (live && rbase + u < r1) ? *(const float4 *)(Asrc + m * lds + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int u = 0; u < RB; ++u) {
+            if (rbase + u >= r1) break;  // uniform in the warp
+            const long m = m0 + rbase + u;
+            double sb = 0.0;
+            float sa = 0.f, sp = 0.f;
+            float4 o;
+            o.x = relax_one<UPPER, RELAX, BIAS>(a[u].x, t0, za.x, qv.x, bk.x, eps, sb, sa, sp);
+            o.y = relax_one<UPPER, RELAX, BIAS>(a[u].y, t1, za.y, qv.y, bk.y, eps, sb, sa, sp);
+            o.z = relax_one<UPPER, RELAX, BIAS>(a[u].z, t2, za.z, qv.z, bk.z, eps, sb, sa, sp);
+            o.w = relax_one<UPPER, RELAX, BIAS>(a[u].w, t3, za.w, qv.w, bk.w, eps, sb, sa, sp);
+            if (RELAX && live) *(float4 *)(A + m * lda + j) = o;
+            // The magnitude sum only ever enters the bound as 2^-40 * rabs (the slack for the binary64 bias
+            // sums), so it is folded into the penalty here instead of being reduced on its own; the penalty
+            // is reduced in fp32 (five shuffles) and inflated for the roundings of that reduction.
+            sp = __fmaf_ru(sa, 9.1e-13f, sp);
+#pragma unroll
+            for (int o2 = 16; o2 > 0; o2 >>= 1) sp = __fadd_ru(sp, __shfl_xor_sync(0xffffffffu, sp, o2));
+            sb = warp_sum(sb);
+            if (lane == 0) {
+                atomicAdd(&rb[m], sb);
+                atomicAdd(&rpen[m], (double)sp * 1.000002);
+            }
+        }
+    }
+}
+
+template <bool RELAX, bool BIAS>
+__global__ void __launch_bounds__(256)
+k_relax_dom(int n, int off, int D, int R, int S, long nps, float *A, int lda, const float *Asrc, int lds,
+            const float4 *__restrict__ tab, const float *__restrict__ zabs, const float *__restrict__ q, long q_ds,
+            const float *__restrict__ bias_k, float eps, double *__restrict__ rb, double *__restrict__ rabs,
+            double *__restrict__ rpen) {
+    const int slabs = (n + 127) >> 7;
+    const long warp = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warp >= (long)D * slabs) return;
+    const int d = (int)(warp / slabs), slab = (int)(warp - (long)d * slabs);
+    const int j = slab * 128 + lane * 4;
+    const bool live = j < n;
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 t0 = zero, t1 = zero, t2 = zero, t3 = zero, za = zero, qv = zero, bk = zero;
+    if (live) {
+        const long tb = (long)d * nps + off + j;
+        qv = *(const float4 *)(q + (long)d * q_ds + off + j);
+        if (BIAS) bk = *(const float4 *)(bias_k + j);
+        if (RELAX) {
+            t0 = tab[tb]; t1 = tab[tb + 1]; t2 = tab[tb + 2]; t3 = tab[tb + 3];
+            za = *(const float4 *)(zabs + tb);
+        }
+    }
+    const long m0 = (long)d * R;
+    relax_dom_rows<false, RELAX, BIAS>(0, S, m0, j, A, lda, Asrc, lds, t0, t1, t2, t3, za, qv, bk, eps, lane, live, rb, rabs, rpen);
+    relax_dom_rows<true, RELAX, BIAS>(S, R, m0, j, A, lda, Asrc, lds, t0, t1, t2, t3, za, qv, bk, eps, lane, live, rb, rabs, rpen);
+}
+
 // ---------------------------------------------------------------- binary64-accumulated contraction
 // C[M x N] = A[M x K] * B[K x N]; the fp32 products are exact in binary64, the running sums round to
 // nearest (bounded by eps*|A||B|, charged in k_relax), and the final cast to fp32 is measured exactly
@@ -726,8 +803,21 @@ void launch_relax(nyb200_engine *e, const NetView &nv, int r, int lin_k, int M, 
         const float *bk = nv.b[lin_k];
 #define NYB_RELAX_LAUNCH(RELAX, BIAS) \
     k_relax_v4<RELAX, BIAS><<<grid, 256, 0, e->stream>>>(n, off, M, R, S, (long)nv.nps, A, lda, Asrc, lds, tab, zabs, q, q_dstride, bk, epsf, rb, rabs, rpen)
-        if (r >= 0) { if (bk) NYB_RELAX_LAUNCH(true, true); else NYB_RELAX_LAUNCH(true, false); }
-        else { if (bk) NYB_RELAX_LAUNCH(false, true); else NYB_RELAX_LAUNCH(false, false); }
+        const int D = M / R;
+        const long dwarps = (long)D * ((n + 127) / 128);
+        const unsigned dgrid = (unsigned)((dwarps * 32 + 255) / 256);
+#define NYB_RELAX_DOM(RELAX, BIAS) \
+    k_relax_dom<RELAX, BIAS><<<dgrid, 256, 0, e->stream>>>(n, off, D, R, S, (long)nv.nps, A, lda, Asrc, lds, tab, zabs, q, q_dstride, bk, epsf, rb, rabs, rpen)
+        // domain-major when a domain's rows amortise the table loads and there are enough warps to fill the GPU
+        const bool dom = R >= 4 && dwarps >= 2048 && !getenv("NYB200_RELAX_ROWMAJOR");
+        if (dom) {
+            if (r >= 0) { if (bk) NYB_RELAX_DOM(true, true); else NYB_RELAX_DOM(true, false); }
+            else { if (bk) NYB_RELAX_DOM(false, true); else NYB_RELAX_DOM(false, false); }
+        } else {
+            if (r >= 0) { if (bk) NYB_RELAX_LAUNCH(true, true); else NYB_RELAX_LAUNCH(true, false); }
+            else { if (bk) NYB_RELAX_LAUNCH(false, true); else NYB_RELAX_LAUNCH(false, false); }
+        }
+#undef NYB_RELAX_DOM
 #undef NYB_RELAX_LAUNCH
     } else
         k_relax<<<grid, 256, 0, e->stream>>>(n, off, M, R, S, nv.nps, r < 0 ? 1 : 0, A, lda, Asrc, lds, tab, zabs, q, q_dstride,
