@@ -217,12 +217,18 @@ typedef struct nyb200_opt_config {
     float clip_beta;     /* > 0: beta gradients are clipped to [-clip, clip] (reference: 10) */
     int32_t objective;   /* 0: sum over the spec rows of the lower bounds (joint_alpha_gradient);
                             1: the row whose current lower bound is smallest (optimize_joint_bounds,
-                            beta_crown/engine/optimization/optimize_loop.rs:77-333) */
+                            beta_crown/engine/optimization/optimize_loop.rs:77-333);
+                            2: dual alpha (ReLULayer::propagate_linear_with_alpha,
+                            activations/relu/mod.rs:570-1128): as 0, and the upper rows get their own slopes
+                            alpha_up for negative coefficients, started at alpha and descending the sum of the
+                            upper bounds */
 } nyb200_opt_config;
 int32_t nyb200_batch_optimize(nyb200_engine *e, const nyb200_opt_config *cfg);
 /* alpha [D x sum_{k>=1} dims[k]] (meaningful on unstable unsplit neurons) and beta [D x max_splits]
  * (same order as the uploaded split lists) after the last run.  Either pointer may be NULL. */
 int32_t nyb200_batch_download_params(nyb200_engine *e, float *alpha, float *beta);
+/* The upper path's slopes [D x sum_{k>=1} dims[k]] after the last run (equal to alpha unless objective 2 ran). */
+int32_t nyb200_batch_download_alpha_upper(nyb200_engine *e, float *alpha_up);
 
 /* ---- PGD attack batched over restarts ----------------------------------------------------------
  * All K restarts advance in lock-step (PgdAttacker::attack_batched,

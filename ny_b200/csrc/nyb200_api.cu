@@ -341,6 +341,8 @@ int batch_ptrs(nyb200_engine *e, const Net &net, const Batch &b, BatchPtrs &p) {
     GET(out_lo, float *, "out_lo", D * b.S * 4)
     GET(out_hi, float *, "out_hi", D * b.S * 4)
     GET(min_lower, float *, "min_lower", 256)
+    p.alpha_up = nullptr;
+    if (b.dual_alpha) { GET(alpha_up, float *, "alpha_up", D * np * 4) }
 #undef GET
     return NYB200_OK;
 }
@@ -524,7 +526,7 @@ int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, float
         }
         if (k > 0)
             launch_relax(e, nv, k - 1, k - 1, M, R, S, nxt, p.lda, p.tab, p.zabs, p.q, q_ds(k - 1), eps_for(k - 1), p.rb, p.rabs,
-                         p.rpen, dst == nxt ? nullptr : dst, ldd);
+                         p.rpen, dst == nxt ? nullptr : dst, ldd, p.alpha_up);
         float *t = cur; cur = nxt; nxt = t;
     }
     p.a_final = cur;
@@ -600,6 +602,7 @@ int run_batch(nyb200_engine *e) {
     e->batch.ran = true;
     e->batch.finished = false;
     e->batch.optimized = false;
+    e->batch.dual_alpha = false;
     e->batch.refined = 0;
     return NYB200_OK;
 }

@@ -72,6 +72,7 @@ struct Batch {
     int S = 0, R = 0, D = 0, mode = 0, box_stride = 0, max_splits = 0;
     bool has_alpha = false;
     bool ran = false;
+    bool dual_alpha = false; // the upper rows use their own slopes (workspace "alpha_up")
     bool optimized = false;  // the last run was a parameter optimisation: results are the best-so-far bounds
     bool finished = false;  // results of the last run have been checked (and refined if needed)
     int refined = 0;        // domains that triggered the binary64 re-run of the last batch
@@ -140,7 +141,7 @@ void launch_seed_identity(nyb200_engine *e, int n, int D, int lda, float *A);
 // With Asrc != nullptr the rows are read from Asrc (row stride lds) and the result written to A.
 void launch_relax(nyb200_engine *e, const NetView &nv, int r, int lin_k, int M, int R, int S, float *A, int lda,
                   const float4 *tab, const float *zabs, const float *q, long q_dstride, double eps_gemm, double *rb,
-                  double *rabs, double *rpen, const float *Asrc, int lds);
+                  double *rabs, double *rpen, const float *Asrc, int lds, const float *aup = nullptr);
 // C[M x N] = A[M x K] * W_k (binary64 accumulation), cast error charged to rpen.
 void launch_gemm_f64(nyb200_engine *e, int M, int N, int K, const float *A, int lda, const float *B, int ldb, float *C,
                      int ldc, int R, const float *zin_lo, const float *zin_hi, long zin_dstride, double *rpen);
@@ -165,6 +166,7 @@ struct BatchPtrs {
     float *out_lo, *out_hi, *min_lower;
     int lda;
     float *a_final = nullptr;  // set by run_backward: the coefficients on the input box, [D*R x lda]
+    float *alpha_up = nullptr; // dual alpha: the upper path's own lower slopes [D x nps], or null (shared with the lower path)
 };
 int batch_ptrs(nyb200_engine *e, const Net &net, const Batch &b, BatchPtrs &p);
 int find_net(nyb200_engine *e, int net_id, Net **out);

@@ -276,8 +276,8 @@ __global__ void k_seed_identity(int n, int D, int lda, float *__restrict__ A) {
 __global__ void __launch_bounds__(256)
 k_relax(int n, int off, int M, int R, int S, int n_pre, int identity, float *A, int lda, const float *Asrc, int lds,
         const float4 *__restrict__ tab, const float *__restrict__ zabs, const float *__restrict__ q, long q_ds,
-        const float *__restrict__ bias_k, double eps, double *__restrict__ rb, double *__restrict__ rabs,
-        double *__restrict__ rpen) {
+        const float *__restrict__ bias_k, const float *__restrict__ aup, double eps, double *__restrict__ rb,
+        double *__restrict__ rabs, double *__restrict__ rpen) {
     int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp >= M) return;
     int m = warp, d = m / R;
@@ -293,7 +293,7 @@ k_relax(int n, int off, int M, int R, int S, int n_pre, int identity, float *A, 
             float za = zabs[(long)d * n_pre + off + j];
             float slope = 0.f, icp = 0.f;
             if (a > 0.f) { slope = upper ? t.y : t.x; icp = upper ? t.z : 0.f; }
-            else if (a < 0.f) { slope = upper ? t.x : t.y; icp = upper ? 0.f : t.z; }
+            else if (a < 0.f) { slope = upper ? (aup ? aup[(long)d * n_pre + off + j] : t.x) : t.y; icp = upper ? 0.f : t.z; }
             if (a == 0.f || slope == 0.f) nw = 0.f;  // exact product: no outward step needed
             else {
                 float p = a * slope;
@@ -320,14 +320,15 @@ k_relax(int n, int off, int M, int R, int S, int n_pre, int identity, float *A, 
 // the rounding gap, penalties are accumulated in fp32 with upward-directed operations (an upper bound is
 // all that is needed) and inflated once at the end; the bias stays in binary64.
 template <bool UPPER, bool RELAX, bool BIAS>
-__device__ __forceinline__ float relax_one(float a, float4 t, float za, float qv, float bk, float eps, double &sb,
+__device__ __forceinline__ float relax_one(float a, float4 t, float au, float za, float qv, float bk, float eps, double &sb,
                                            float &sa, float &sp) {
     float nw = a;
     if (RELAX) {
         const bool pos = a > 0.f;
         // lower rows: a > 0 takes the lower line (slope ls, no intercept), a < 0 the upper line (us, ui);
         // upper rows mirror it (relu_backward.rs:105-153)
-        const float slope = (pos != UPPER) ? t.x : t.y;
+        // au: the upper path's own lower slope (dual alpha, activations/relu/mod.rs:570-1128); equals t.x otherwise
+        const float slope = (pos != UPPER) ? (UPPER ? au : t.x) : t.y;
         const float icp = ((pos == UPPER) && a != 0.f) ? t.z : 0.f;
         nw = UPPER ? __fmul_ru(a, slope) : __fmul_rd(a, slope);
         sp = __fmaf_ru(fabsf(fmaf(a, slope, -nw)), za, sp);
@@ -346,7 +347,8 @@ __device__ __forceinline__ float relax_one(float a, float4 t, float za, float qv
 template <bool UPPER, bool RELAX, bool BIAS>
 __device__ __forceinline__ void relax_row(int n, int lane, float *row, const float *src, const float4 *__restrict__ tab,
                                           const float *__restrict__ zabs, const float *__restrict__ q,
-                                          const float *__restrict__ bias_k, float eps, double &sb, float &sa, float &sp) {
+                                          const float *__restrict__ bias_k, const float *__restrict__ aup, float eps,
+                                          double &sb, float &sa, float &sp) {
     for (int j = lane * 4; j < n; j += 128) {
         float4 a = *(const float4 *)(src + j);
         float4 qv = *(const float4 *)(q + j);
@@ -356,11 +358,13 @@ __device__ __forceinline__ void relax_row(int n, int lane, float *row, const flo
             t0 = tab[j]; t1 = tab[j + 1]; t2 = tab[j + 2]; t3 = tab[j + 3];
             za = *(const float4 *)(zabs + j);
         }
+        float4 au = make_float4(t0.x, t1.x, t2.x, t3.x);
+        if (RELAX && UPPER && aup) au = *(const float4 *)(aup + j);
         float4 o;
-        o.x = relax_one<UPPER, RELAX, BIAS>(a.x, t0, za.x, qv.x, bk.x, eps, sb, sa, sp);
-        o.y = relax_one<UPPER, RELAX, BIAS>(a.y, t1, za.y, qv.y, bk.y, eps, sb, sa, sp);
-        o.z = relax_one<UPPER, RELAX, BIAS>(a.z, t2, za.z, qv.z, bk.z, eps, sb, sa, sp);
-        o.w = relax_one<UPPER, RELAX, BIAS>(a.w, t3, za.w, qv.w, bk.w, eps, sb, sa, sp);
+        o.x = relax_one<UPPER, RELAX, BIAS>(a.x, t0, au.x, za.x, qv.x, bk.x, eps, sb, sa, sp);
+        o.y = relax_one<UPPER, RELAX, BIAS>(a.y, t1, au.y, za.y, qv.y, bk.y, eps, sb, sa, sp);
+        o.z = relax_one<UPPER, RELAX, BIAS>(a.z, t2, au.z, za.z, qv.z, bk.z, eps, sb, sa, sp);
+        o.w = relax_one<UPPER, RELAX, BIAS>(a.w, t3, au.w, za.w, qv.w, bk.w, eps, sb, sa, sp);
         if (RELAX) *(float4 *)(row + j) = o;
     }
 }
@@ -370,7 +374,8 @@ __global__ void __launch_bounds__(256, 4)
 k_relax_v4(int n, int off, int M, int R, int S, long nps, float *A, int lda, const float *Asrc, int lds,
            const float4 *__restrict__ tab,
            const float *__restrict__ zabs, const float *__restrict__ q, long q_ds, const float *__restrict__ bias_k,
-           float eps, double *__restrict__ rb, double *__restrict__ rabs, double *__restrict__ rpen) {
+           const float *__restrict__ aup, float eps, double *__restrict__ rb, double *__restrict__ rabs,
+           double *__restrict__ rpen) {
     int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp >= M) return;
     int m = warp, d = m / R;
@@ -380,8 +385,8 @@ k_relax_v4(int n, int off, int M, int R, int S, long nps, float *A, int lda, con
     const long tb = (long)d * nps + off, qb = (long)d * q_ds + off;
     double sb = 0.0;
     float sa = 0.f, sp = 0.f;
-    if (upper) relax_row<true, RELAX, BIAS>(n, lane, row, src, tab + tb, zabs + tb, q + qb, bias_k, eps, sb, sa, sp);
-    else relax_row<false, RELAX, BIAS>(n, lane, row, src, tab + tb, zabs + tb, q + qb, bias_k, eps, sb, sa, sp);
+    if (upper) relax_row<true, RELAX, BIAS>(n, lane, row, src, tab + tb, zabs + tb, q + qb, bias_k, aup ? aup + tb : nullptr, eps, sb, sa, sp);
+    else relax_row<false, RELAX, BIAS>(n, lane, row, src, tab + tb, zabs + tb, q + qb, bias_k, nullptr, eps, sb, sa, sp);
     double da = (double)sa, dp = (double)sp;
     sb = warp_sum(sb); da = warp_sum(da); dp = warp_sum(dp);
     if (lane == 0) {  // reductions without a dependent read: the row is owned by this warp for this launch
@@ -398,8 +403,8 @@ k_relax_v4(int n, int off, int M, int R, int S, long nps, float *A, int lda, con
 template <bool UPPER, bool RELAX, bool BIAS>
 __device__ __forceinline__ void relax_dom_rows(int r0, int r1, long m0, int j, float *A, int lda, const float *Asrc, int lds,
                                                const float4 &t0, const float4 &t1, const float4 &t2, const float4 &t3,
-                                               const float4 &za, const float4 &qv, const float4 &bk, float eps, int lane,
-                                               bool live, double *__restrict__ rb, double *__restrict__ rabs,
+                                               const float4 &za, const float4 &qv, const float4 &bk, const float4 &au,
+                                               float eps, int lane, bool live, double *__restrict__ rb, double *__restrict__ rabs,
                                                double *__restrict__ rpen) {
     // Rows are taken RB at a time: all their loads are issued before the first is used, so a lane has RB
     // independent 16-byte requests in flight (a warp that walks one row after the other is latency bound).
@@ -419,10 +424,10 @@ __device__ __forceinline__ void relax_dom_rows(int r0, int r1, long m0, int j, f
             double sb = 0.0;
             float sa = 0.f, sp = 0.f;
             float4 o;
-            o.x = relax_one<UPPER, RELAX, BIAS>(a[u].x, t0, za.x, qv.x, bk.x, eps, sb, sa, sp);
-            o.y = relax_one<UPPER, RELAX, BIAS>(a[u].y, t1, za.y, qv.y, bk.y, eps, sb, sa, sp);
-            o.z = relax_one<UPPER, RELAX, BIAS>(a[u].z, t2, za.z, qv.z, bk.z, eps, sb, sa, sp);
-            o.w = relax_one<UPPER, RELAX, BIAS>(a[u].w, t3, za.w, qv.w, bk.w, eps, sb, sa, sp);
+            o.x = relax_one<UPPER, RELAX, BIAS>(a[u].x, t0, au.x, za.x, qv.x, bk.x, eps, sb, sa, sp);
+            o.y = relax_one<UPPER, RELAX, BIAS>(a[u].y, t1, au.y, za.y, qv.y, bk.y, eps, sb, sa, sp);
+            o.z = relax_one<UPPER, RELAX, BIAS>(a[u].z, t2, au.z, za.z, qv.z, bk.z, eps, sb, sa, sp);
+            o.w = relax_one<UPPER, RELAX, BIAS>(a[u].w, t3, au.w, za.w, qv.w, bk.w, eps, sb, sa, sp);
             if (RELAX && live) *(float4 *)(A + m * lda + j) = o;
             // The magnitude sum only ever enters the bound as 2^-40 * rabs (the slack for the binary64 bias
             // sums), so it is folded into the penalty here instead of being reduced on its own; the penalty
@@ -443,8 +448,8 @@ template <bool RELAX, bool BIAS>
 __global__ void __launch_bounds__(256)
 k_relax_dom(int n, int off, int D, int R, int S, long nps, float *A, int lda, const float *Asrc, int lds,
             const float4 *__restrict__ tab, const float *__restrict__ zabs, const float *__restrict__ q, long q_ds,
-            const float *__restrict__ bias_k, float eps, double *__restrict__ rb, double *__restrict__ rabs,
-            double *__restrict__ rpen) {
+            const float *__restrict__ bias_k, const float *__restrict__ aup, float eps, double *__restrict__ rb,
+            double *__restrict__ rabs, double *__restrict__ rpen) {
     const int slabs = (n + 127) >> 7;
     const long warp = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
@@ -463,9 +468,11 @@ k_relax_dom(int n, int off, int D, int R, int S, long nps, float *A, int lda, co
             za = *(const float4 *)(zabs + tb);
         }
     }
+    float4 au = make_float4(t0.x, t1.x, t2.x, t3.x);
+    if (RELAX && live && aup) au = *(const float4 *)(aup + (long)d * nps + off + j);
     const long m0 = (long)d * R;
-    relax_dom_rows<false, RELAX, BIAS>(0, S, m0, j, A, lda, Asrc, lds, t0, t1, t2, t3, za, qv, bk, eps, lane, live, rb, rabs, rpen);
-    relax_dom_rows<true, RELAX, BIAS>(S, R, m0, j, A, lda, Asrc, lds, t0, t1, t2, t3, za, qv, bk, eps, lane, live, rb, rabs, rpen);
+    relax_dom_rows<false, RELAX, BIAS>(0, S, m0, j, A, lda, Asrc, lds, t0, t1, t2, t3, za, qv, bk, au, eps, lane, live, rb, rabs, rpen);
+    relax_dom_rows<true, RELAX, BIAS>(S, R, m0, j, A, lda, Asrc, lds, t0, t1, t2, t3, za, qv, bk, au, eps, lane, live, rb, rabs, rpen);
 }
 
 // ---------------------------------------------------------------- binary64-accumulated contraction
@@ -790,7 +797,7 @@ void launch_seed_identity(nyb200_engine *e, int n, int D, int lda, float *A) {
 
 void launch_relax(nyb200_engine *e, const NetView &nv, int r, int lin_k, int M, int R, int S, float *A, int lda,
                   const float4 *tab, const float *zabs, const float *q, long q_dstride, double eps_gemm, double *rb,
-                  double *rabs, double *rpen, const float *Asrc, int lds) {
+                  double *rabs, double *rpen, const float *Asrc, int lds, const float *aup) {
     int n = nv.dims[lin_k + 1], off = nv.pre_off[lin_k];
     if (!Asrc) { Asrc = A; lds = lda; }
     long threads = (long)M * 32;
@@ -802,12 +809,12 @@ void launch_relax(nyb200_engine *e, const NetView &nv, int r, int lin_k, int M, 
         const float epsf = (float)(eps_gemm * 1.0000002);
         const float *bk = nv.b[lin_k];
 #define NYB_RELAX_LAUNCH(RELAX, BIAS) \
-    k_relax_v4<RELAX, BIAS><<<grid, 256, 0, e->stream>>>(n, off, M, R, S, (long)nv.nps, A, lda, Asrc, lds, tab, zabs, q, q_dstride, bk, epsf, rb, rabs, rpen)
+    k_relax_v4<RELAX, BIAS><<<grid, 256, 0, e->stream>>>(n, off, M, R, S, (long)nv.nps, A, lda, Asrc, lds, tab, zabs, q, q_dstride, bk, aup, epsf, rb, rabs, rpen)
         const int D = M / R;
         const long dwarps = (long)D * ((n + 127) / 128);
         const unsigned dgrid = (unsigned)((dwarps * 32 + 255) / 256);
 #define NYB_RELAX_DOM(RELAX, BIAS) \
-    k_relax_dom<RELAX, BIAS><<<dgrid, 256, 0, e->stream>>>(n, off, D, R, S, (long)nv.nps, A, lda, Asrc, lds, tab, zabs, q, q_dstride, bk, epsf, rb, rabs, rpen)
+    k_relax_dom<RELAX, BIAS><<<dgrid, 256, 0, e->stream>>>(n, off, D, R, S, (long)nv.nps, A, lda, Asrc, lds, tab, zabs, q, q_dstride, bk, aup, epsf, rb, rabs, rpen)
         // domain-major when a domain's rows amortise the table loads and there are enough warps to fill the GPU
         const bool dom = R >= 4 && dwarps >= 2048 && !getenv("NYB200_RELAX_ROWMAJOR");
         if (dom) {
@@ -821,7 +828,7 @@ void launch_relax(nyb200_engine *e, const NetView &nv, int r, int lin_k, int M, 
 #undef NYB_RELAX_LAUNCH
     } else
         k_relax<<<grid, 256, 0, e->stream>>>(n, off, M, R, S, nv.nps, r < 0 ? 1 : 0, A, lda, Asrc, lds, tab, zabs, q, q_dstride,
-                                             nv.b[lin_k], eps_gemm, rb, rabs, rpen);
+                                             nv.b[lin_k], aup, eps_gemm, rb, rabs, rpen);
     NYB_COUNT(e);
 }
 

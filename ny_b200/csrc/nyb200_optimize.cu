@@ -40,17 +40,19 @@ __global__ void k_transpose(const float *__restrict__ W, int n_out, int n_in, fl
     }
 }
 
-// Z[d*S + s][j] = the box corner the lower row (d, s) concretises on.
-__global__ void k_adjoint_seed(int D, int S, int R, int n0, const float *__restrict__ A, int lda,
+// Z[d*Zr + s][j] = the box corner row (d, s) concretises on: lower rows (s < S) take x_lo where the coefficient
+// is >= 0, upper rows (S <= s < Zr, present with the dual alpha: Zr = 2S) take x_hi there.
+__global__ void k_adjoint_seed(int D, int S, int R, int Zr, int n0, const float *__restrict__ A, int lda,
                                const float *__restrict__ in_lo, const float *__restrict__ in_hi, long box_ds,
                                float *__restrict__ Z, int ldz) {
     long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (t >= (long)D * S * n0) return;
+    if (t >= (long)D * Zr * n0) return;
     int j = (int)(t % n0);
     long ds = t / n0;
-    int d = (int)(ds / S), s = (int)(ds % S);
+    int d = (int)(ds / Zr), s = (int)(ds % Zr);
     float a = A[((long)d * R + s) * lda + j];
-    Z[ds * ldz + j] = (a >= 0.f) ? in_lo[(long)d * box_ds + j] : in_hi[(long)d * box_ds + j];
+    bool take_lo = (a >= 0.f) == (s < S);
+    Z[ds * ldz + j] = take_lo ? in_lo[(long)d * box_ds + j] : in_hi[(long)d * box_ds + j];
 }
 
 // One thread per (domain, neuron) of ReLU `k`: adds the bias, harvests the parameter gradient over the
@@ -58,11 +60,12 @@ __global__ void k_adjoint_seed(int D, int S, int R, int n0, const float *__restr
 // parameter this neuron owns (alpha if unstable and unsplit, beta if split, none otherwise) and writes it
 // into the relaxation table the next backward pass reads.
 __global__ void __launch_bounds__(256)
-k_adjoint_relu(int n, int off, int D, int S, int R, long nps, float *__restrict__ Z, int ldz,
+k_adjoint_relu(int n, int off, int D, int S, int R, int Zr, long nps, float *__restrict__ Z, int ldz,
                const float *__restrict__ bias, const float *__restrict__ Apre, int ldc, float4 *__restrict__ tab,
                const signed char *__restrict__ code, const float *__restrict__ pre_lo,
                const float *__restrict__ pre_hi, float *__restrict__ mom, float *__restrict__ var,
-               const int *__restrict__ only_row, AdamStep h) {
+               const int *__restrict__ only_row, float *__restrict__ aup, float *__restrict__ mom_up,
+               float *__restrict__ var_up, AdamStep h) {
     long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= (long)D * n) return;
     int d = (int)(t / n), i = (int)(t % n);
@@ -72,7 +75,7 @@ k_adjoint_relu(int n, int off, int D, int S, int R, long nps, float *__restrict_
     float g_alpha = 0.f, g_sum = 0.f;
     const int pick = only_row ? only_row[d] : -1;  // objective: one row of the domain, or the sum over its rows
     for (int s = 0; s < S; ++s) {
-        long zr = ((long)d * S + s) * ldz + i;
+        long zr = ((long)d * Zr + s) * ldz + i;
         float g = Z[zr] + bk;
         float ap = Apre[((long)d * R + s) * ldc + i];
         if (pick < 0 || s == pick) {
@@ -84,6 +87,27 @@ k_adjoint_relu(int n, int off, int D, int S, int R, long nps, float *__restrict_
     }
     int c = code[o];
     float l = pre_lo[o], u = pre_hi[o];
+    if (Zr > S) {
+        // dual alpha: the upper rows' adjoint; a >= 0 takes the chord, a < 0 the upper path's own slope, whose
+        // gradient is sum_s Zpre * min(Apre, 0); the sum of the upper bounds descends
+        float au = aup[o], g_up = 0.f;
+        for (int s = S; s < Zr; ++s) {
+            long zr = ((long)d * Zr + s) * ldz + i;
+            float g = Z[zr] + bk;
+            float ap = Apre[((long)d * R + s) * ldc + i];
+            g_up = fmaf(g, fminf(ap, 0.f), g_up);
+            bool pos = ap >= 0.f;
+            Z[zr] = fmaf(g, pos ? tb.y : au, pos ? tb.z : 0.f);
+        }
+        if ((c == 0) && (l < 0.f) && (u > 0.f) && h.lr_alpha > 0.f) {
+            float m = h.beta1 * mom_up[o] + (1.f - h.beta1) * g_up;
+            float v = h.beta2 * var_up[o] + (1.f - h.beta2) * g_up * g_up;
+            float a = au - h.lr_alpha * (m / h.bc1) / (sqrtf(v / h.bc2) + h.epsilon);
+            a = fminf(fmaxf(a, 0.f), 1.f);
+            if (isnan(a)) { a = 0.5f; m = 0.f; v = 0.f; }
+            aup[o] = a; mom_up[o] = m; var_up[o] = v;
+        }
+    }
     bool is_alpha = (c == 0) && (l < 0.f) && (u > 0.f) && h.lr_alpha > 0.f;
     bool is_beta = (c != 0) && h.lr_beta > 0.f;
     if (!is_alpha && !is_beta) return;
@@ -105,6 +129,12 @@ k_adjoint_relu(int n, int off, int D, int S, int R, long nps, float *__restrict_
     }
     mom[o] = m; var[o] = v;
     tab[o] = tb;
+}
+
+// alpha_up = the lower path's slopes (the table's first component), the starting point of the dual alpha
+__global__ void k_init_alpha_up(long n, const float4 *__restrict__ tab, float *__restrict__ aup) {
+    long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t < n) aup[t] = tab[t].x;
 }
 
 // Row with the smallest current lower bound per domain (first minimum wins).
@@ -209,7 +239,7 @@ int conv_forward_tensor(nyb200_engine *e, Net &net, int k, int rows, const float
 int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg) {
     if (!e->batch.valid) return set_err(e, NYB200_ERR_INVALID, "no batch uploaded");
     if (cfg.iterations < 1) return set_err(e, NYB200_ERR_INVALID, "iterations must be >= 1");
-    if (cfg.objective != 0 && cfg.objective != 1) return set_err(e, NYB200_ERR_INVALID, "objective must be 0 or 1");
+    if (cfg.objective < 0 || cfg.objective > 2) return set_err(e, NYB200_ERR_INVALID, "objective must be 0, 1 or 2");
     if (!(cfg.lr_alpha >= 0.f) || !(cfg.lr_beta >= 0.f) || !(cfg.lr_decay > 0.f))
         return set_err(e, NYB200_ERR_INVALID, "learning rates must be >= 0 and the decay > 0");
     Net *net;
@@ -217,6 +247,7 @@ int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg) {
     if (net->has_skip() && cfg.iterations > 1)
         return set_err(e, NYB200_ERR_UNSUPPORTED, "parameter optimisation of networks with residual connections is not built");
     Batch &b = e->batch;
+    b.dual_alpha = cfg.objective == 2 && cfg.iterations > 1 && net->v.L >= 2;  // decides which arrays the batch has
     BatchPtrs p;
     NYB_TRY(batch_ptrs(e, *net, b, p));
     const NetView &nv = net->v;
@@ -224,6 +255,8 @@ int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg) {
     const long M = (long)D * R, np = nv.nps;
     const bool tensor = e->path == NYB200_PATH_TF32X3;
     const int T = (L >= 2) ? cfg.iterations : 1;
+    const bool dual = cfg.objective == 2 && T > 1;
+    const int Zr = dual ? R : S;  // adjoint rows per domain
     const float b1 = cfg.beta1 > 0.f ? cfg.beta1 : 0.9f, b2 = cfg.beta2 > 0.f ? cfg.beta2 : 0.999f;
     const float eps = cfg.epsilon > 0.f ? cfg.epsilon : 1e-8f;
 
@@ -234,14 +267,22 @@ int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg) {
     if (T > 1) {
         NYB_WS(ck, float *, e, "ckpt", (size_t)(L - 1) * M * ldc * 4);
         for (int r = 0; r < L - 1; ++r) ckpt[r] = ck + (size_t)r * M * ldc;
-        z0 = (float *)ws_get(e, "adj0", (size_t)D * S * ldz * 4);
-        z1 = (float *)ws_get(e, "adj1", (size_t)D * S * ldz * 4);
+        z0 = (float *)ws_get(e, "adj0", (size_t)D * Zr * ldz * 4);
+        z1 = (float *)ws_get(e, "adj1", (size_t)D * Zr * ldz * 4);
         mom = (float *)ws_get(e, "adam_m", (size_t)D * np * 4);
         var = (float *)ws_get(e, "adam_v", (size_t)D * np * 4);
         if (!z0 || !z1 || !mom || !var) return NYB200_ERR_OOM;
         NYB_TRY(prepare_transposed(e, *net, tensor));
         NYB_CUDA(e, cudaMemsetAsync(mom, 0, (size_t)D * np * 4, e->stream));
         NYB_CUDA(e, cudaMemsetAsync(var, 0, (size_t)D * np * 4, e->stream));
+    }
+    float *mom_up = nullptr, *var_up = nullptr;
+    if (dual) {
+        mom_up = (float *)ws_get(e, "adam_mu", (size_t)D * np * 4);
+        var_up = (float *)ws_get(e, "adam_vu", (size_t)D * np * 4);
+        if (!mom_up || !var_up) return NYB200_ERR_OOM;
+        NYB_CUDA(e, cudaMemsetAsync(mom_up, 0, (size_t)D * np * 4, e->stream));
+        NYB_CUDA(e, cudaMemsetAsync(var_up, 0, (size_t)D * np * 4, e->stream));
     }
     NYB_WS(best_lo, float *, e, "best_lo", (size_t)D * S * 4);
     NYB_WS(best_hi, float *, e, "best_hi", (size_t)D * S * 4);
@@ -261,6 +302,11 @@ int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg) {
     fold_timing(tm);
     cudaEventRecord(tm.ev[0], e->stream);
     NYB_TRY(run_forward(e, *net, b, p, b.mode));
+    if (dual) {
+        long na = (long)D * np;
+        k_init_alpha_up<<<(unsigned)((na + 255) / 256), 256, 0, e->stream>>>(na, p.tab, p.alpha_up);
+        e->launches++;
+    }
     cudaEventRecord(tm.ev[1], e->stream);
     const long nres = (long)D * S;
     const unsigned gres = (unsigned)((nres + 255) / 256);
@@ -280,21 +326,21 @@ int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg) {
         h.beta1 = b1; h.beta2 = b2; h.epsilon = eps; h.clip_beta = cfg.clip_beta;
         h.bc1 = fmaxf(1.f - powf(b1, (float)t), 1.1920929e-7f);
         h.bc2 = fmaxf(1.f - powf(b2, (float)t), 1.1920929e-7f);
-        long nseed = (long)D * S * nv.dims[0];
-        k_adjoint_seed<<<(unsigned)((nseed + 255) / 256), 256, 0, e->stream>>>(D, S, R, nv.dims[0], p.a_final, p.lda, p.in_lo,
+        long nseed = (long)D * Zr * nv.dims[0];
+        k_adjoint_seed<<<(unsigned)((nseed + 255) / 256), 256, 0, e->stream>>>(D, S, R, Zr, nv.dims[0], p.a_final, p.lda, p.in_lo,
                                                                               p.in_hi, (long)b.box_stride, z0, ldz);
         e->launches++;
         float *zc = z0, *zn = z1;
         for (int k = 0; k < L - 1; ++k) {
             int K = nv.dims[k], N = nv.dims[k + 1];
-            if (net->is_conv(k) && tensor) NYB_TRY(conv_forward_tensor(e, *net, k, D * S, zc, ldz, zn, ldz, derr));
-            else if (net->is_conv(k)) launch_conv_plain(e, net->geom[k], D * S, zc, ldz, nv.W[k], zn, ldz);
-            else if (tensor) NYB_TRY(launch_umma(e, net->umma_adj[k], D * S, zc, ldz, zn, ldz, derr));
-            else launch_gemm_f64(e, D * S, N, K, zc, ldz, net->wt[k], N, zn, ldz, 1, nullptr, nullptr, 0, nullptr);
+            if (net->is_conv(k) && tensor) NYB_TRY(conv_forward_tensor(e, *net, k, D * Zr, zc, ldz, zn, ldz, derr));
+            else if (net->is_conv(k)) launch_conv_plain(e, net->geom[k], D * Zr, zc, ldz, nv.W[k], zn, ldz);
+            else if (tensor) NYB_TRY(launch_umma(e, net->umma_adj[k], D * Zr, zc, ldz, zn, ldz, derr));
+            else launch_gemm_f64(e, D * Zr, N, K, zc, ldz, net->wt[k], N, zn, ldz, 1, nullptr, nullptr, 0, nullptr);
             long nt = (long)D * N;
-            k_adjoint_relu<<<(unsigned)((nt + 255) / 256), 256, 0, e->stream>>>(N, nv.pre_off[k], D, S, R, np, zn, ldz, nv.b[k],
+            k_adjoint_relu<<<(unsigned)((nt + 255) / 256), 256, 0, e->stream>>>(N, nv.pre_off[k], D, S, R, Zr, np, zn, ldz, nv.b[k],
                                                                                ckpt[k], ldc, p.tab, p.code, p.pre_lo,
-                                                                               p.pre_hi, mom, var, only_row, h);
+                                                                               p.pre_hi, mom, var, only_row, p.alpha_up, mom_up, var_up, h);
             e->launches++;
             float *tmp = zc; zc = zn; zn = tmp;
         }
@@ -357,9 +403,33 @@ int download_params(nyb200_engine *e, float *alpha, float *beta) {
     return NYB200_OK;
 }
 
+int download_alpha_upper(nyb200_engine *e, float *alpha_up) {
+    if (!e->batch.valid || !e->batch.ran) return set_err(e, NYB200_ERR_INVALID, "no batch has been run");
+    Net *net;
+    NYB_TRY(find_net(e, e->batch.net_id, &net));
+    BatchPtrs p;
+    NYB_TRY(batch_ptrs(e, *net, e->batch, p));
+    const NetView &nv = net->v;
+    size_t w = (size_t)nv.n_pre * 4;
+    if (p.alpha_up) {
+        NYB_CUDA(e, cudaMemcpy2DAsync(alpha_up, w, p.alpha_up, (size_t)nv.nps * 4, w, (size_t)e->batch.D, cudaMemcpyDeviceToHost, e->stream));
+        NYB_CUDA(e, cudaStreamSynchronize(e->stream));
+        return NYB200_OK;
+    }
+    return download_params(e, alpha_up, nullptr);  // shared slopes: the upper path uses the lower path's
+}
+
 }  // namespace nyb
 
 extern "C" {
+
+int32_t nyb200_batch_download_alpha_upper(nyb200_engine *e, float *alpha_up) {
+    if (!e || !alpha_up) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    cudaError_t st = cudaSetDevice(e->device);
+    if (st != cudaSuccess) return nyb::check_cuda(e, st, "cudaSetDevice");
+    return nyb::download_alpha_upper(e, alpha_up);
+}
 
 int32_t nyb200_batch_optimize(nyb200_engine *e, const nyb200_opt_config *cfg) {
     if (!e || !cfg) return NYB200_ERR_INVALID;

@@ -38,7 +38,7 @@ EXPORTS = [
     "nyb200_batch_download_pre_bounds", "nyb200_batch_select_branch", "nyb200_timing_enable", "nyb200_timing_reset",
     "nyb200_timing_read", "nyb200_batch_optimize", "nyb200_batch_download_params",
     "nyb200_net_create_layers", "nyb200_pgd_attack", "nyb200_batch_select_branch_scored",
-    "nyb200_crown_bounds",
+    "nyb200_crown_bounds", "nyb200_batch_download_alpha_upper",
 ]
 
 
@@ -103,6 +103,7 @@ def load_library():
     L.nyb200_pgd_attack.argtypes = [vp, C.c_int32, fp, C.c_int32, fp, fp, fp, C.c_int32, C.POINTER(PgdConfig), fp, fp, ip]
     L.nyb200_batch_optimize.argtypes = [vp, C.POINTER(OptConfig)]
     L.nyb200_batch_download_params.argtypes = [vp, fp, fp]
+    L.nyb200_batch_download_alpha_upper.argtypes = [vp, fp]
     _lib = L
     return L
 
@@ -442,6 +443,13 @@ class B200Engine:
         beta = np.zeros((D, max(ms, 1)), np.float32)
         self._check(self._L.nyb200_batch_download_params(self._h, _fp(alpha), _fp(beta) if ms > 0 else None))
         return alpha, beta[:, :ms]
+
+    def batch_download_alpha_upper(self):
+        """The upper path's slopes [D, n_pre] after the last run (dual alpha)."""
+        D, _, n_pre = self._batch_shape
+        a = np.empty((D, n_pre), np.float32)
+        self._check(self._L.nyb200_batch_download_alpha_upper(self._h, _fp(a)))
+        return a
 
     def batch_download(self):
         D, S, _ = self._batch_shape

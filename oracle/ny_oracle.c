@@ -566,7 +566,9 @@ static lbounds relu_backward_crown(const lbounds *in, const float *pl, const flo
 #define RELU_RELAX_MIN_WIDTH 1e-8f
 static lbounds relu_backward_beta(const lbounds *in, const float *pl, const float *pu,
                                   const signed char *split, const float *sbeta, const unsigned char *has_sb,
-                                  const float *alpha) {
+                                  const float *alpha, const float *alpha_up) {
+    /* alpha_up: separate lower slope for the upper bound's negative coefficients (the dual alpha of
+     * activations/relu/mod.rs:570-1128); NULL = the same slope as the lower path. */
     int rows = in->rows, n = in->n;
     lbounds out = lb_alloc(rows, n, 0);
     double *lb64 = (double *)malloc(sizeof(double) * (size_t)rows);
@@ -576,6 +578,7 @@ static lbounds relu_backward_beta(const lbounds *in, const float *pl, const floa
     for (int j = 0; j < n; ++j) {
         float l = pl[j], u = pu[j];
         float ls, li, us, ui;
+        int free_slope = 0;
         if (split && split[j] != 0) {
             if (split[j] > 0) { ls = 1; li = 0; us = 1; ui = 0; } else { ls = 0; li = 0; us = 0; ui = 0; }
         } else if (isnan(l) || isnan(u)) { ls = 0; li = -INFINITY; us = 0; ui = INFINITY; }
@@ -588,7 +591,9 @@ static lbounds relu_backward_beta(const lbounds *in, const float *pl, const floa
             float width = fmaxf(u - l, RELU_RELAX_MIN_WIDTH);
             us = u / width; ui = -l * u / width;
             ls = alpha ? alpha[j] : ((u > -l) ? 1.0f : 0.0f); li = 0.0f;
+            free_slope = 1;
         }
+        float ls_up = (free_slope && alpha_up) ? alpha_up[j] : ls;
         for (int i = 0; i < rows; ++i) {
             size_t o = (size_t)i * n + j;
             float la = in->la[o], ua = in->ua[o];
@@ -606,7 +611,7 @@ static lbounds relu_backward_beta(const lbounds *in, const float *pl, const floa
                 if (isfinite(p)) out.ua[o] = NUP32(p); else { nonfinite = 1; out.ua[o] = 0; }
                 ub64[i] += (double)ua * (double)ui;
             } else if (ua < 0.0f) {
-                float p = ua * ls;
+                float p = ua * ls_up;
                 if (isfinite(p)) out.ua[o] = NUP32(p); else { nonfinite = 1; out.ua[o] = 0; }
                 ub64[i] += (double)ua * (double)li;
             } else out.ua[o] = 0.0f;
@@ -766,6 +771,12 @@ int nyo_crown(const nyo_net *net, const float *in_lo, const float *in_hi, float 
 int nyo_beta_crown_bound(const nyo_net *net, const float *in_lo, const float *in_hi, const float *pre_lo,
                          const float *pre_hi, const nyo_split *splits, int n_splits, const float *alpha,
                          float *out_lo, float *out_hi) {
+    return nyo_beta_crown_bound_dual(net, in_lo, in_hi, pre_lo, pre_hi, splits, n_splits, alpha, NULL, out_lo, out_hi);
+}
+
+int nyo_beta_crown_bound_dual(const nyo_net *net, const float *in_lo, const float *in_hi, const float *pre_lo,
+                              const float *pre_hi, const nyo_split *splits, int n_splits, const float *alpha,
+                              const float *alpha_up, float *out_lo, float *out_hi) {
     int L = net->n_linear;
     lbounds cur = lb_identity(net->dims[L]);
     for (int k = L - 1; k >= 0; --k) {
@@ -783,7 +794,8 @@ int nyo_beta_crown_bound(const nyo_net *net, const float *in_lo, const float *in
                 sp[j] = (signed char)(splits[s].sign > 0 ? 1 : -1);
                 hs[j] = 1; sb[j] = splits[s].beta * (splits[s].sign > 0 ? 1.0f : -1.0f);
             }
-            lbounds rb = relu_backward_beta(&cur, pre_lo + o, pre_hi + o, sp, sb, hs, alpha ? alpha + o : NULL);
+            lbounds rb = relu_backward_beta(&cur, pre_lo + o, pre_hi + o, sp, sb, hs, alpha ? alpha + o : NULL,
+                                            alpha_up ? alpha_up + o : NULL);
             lb_free(&cur); cur = rb;
             free(sp); free(hs); free(sb);
         }
@@ -1086,6 +1098,115 @@ int nyo_joint_gradient_rows(const nyo_net *net, const float *in_lo, const float 
     return 0;
 }
 
+/* Upper-bound counterpart of the joint gradient for the dual alpha: value of the upper rows and the gradient of
+ * their sum with respect to alpha_up, the slope the upper path applies to negative coefficients on unstable
+ * unsplit neurons (activations/relu/mod.rs:570-1128: "upper-path alpha for ua < 0").  Fold: a >= 0 takes the chord
+ * (us, ui), a < 0 takes (alpha_up, 0), then + beta*sign; corner x_u for a >= 0 else x_l;
+ * d(upper_s)/d(alpha_up_i) = Zpre[s,i] * min(Apre[s,i], 0).  Binary64 throughout. */
+int nyo_upper_gradient(const nyo_net *net, const float *in_lo, const float *in_hi, const float *pre_lo,
+                       const float *pre_hi, const nyo_split *splits, int n_splits, const float *alpha,
+                       const float *alpha_up, double *upper_out, float *grad_alpha_up) {
+    int L = net->n_linear, S = net->dims[L];
+    size_t total = pre_offset(net, L);
+    double **apre = (double **)calloc((size_t)L, sizeof(double *));
+    double **sig = (double **)calloc((size_t)L, sizeof(double *));
+    double **tau = (double **)calloc((size_t)L, sizeof(double *));
+    int n = S;
+    double *A = (double *)calloc((size_t)S * n, 8), *b = (double *)calloc((size_t)S, 8);
+    for (int s = 0; s < S; ++s) A[(size_t)s * n + s] = 1.0;
+    for (int k = L - 1; k >= 0; --k) {
+        lin_layer Lk = net_layer(net, k);
+        double *An = (double *)calloc((size_t)S * Lk.n_in, 8);
+        for (int s = 0; s < S; ++s)
+            for (int o = 0; o < Lk.n_out; ++o) {
+                double a = A[(size_t)s * Lk.n_out + o];
+                if (a == 0.0) continue;
+                const float *w = Lk.W + (size_t)o * Lk.n_in;
+                for (int j = 0; j < Lk.n_in; ++j) An[(size_t)s * Lk.n_in + j] += a * (double)w[j];
+                if (Lk.b) b[s] += a * (double)Lk.b[o];
+            }
+        free(A); A = An; n = Lk.n_in;
+        if (k > 0 && relu_after(net, k - 1)) {
+            int r = k - 1;
+            size_t o = pre_offset(net, r);
+            apre[r] = (double *)malloc(8 * (size_t)S * n);
+            sig[r] = (double *)malloc(8 * (size_t)S * n);
+            tau[r] = (double *)malloc(8 * (size_t)S * n);
+            for (int j = 0; j < n; ++j) {
+                float l = pre_lo[o + j], u = pre_hi[o + j];
+                int sp = 0; float sb = 0.0f;
+                for (int q = 0; q < n_splits; ++q) if (splits[q].relu == r && splits[q].neuron == j) {
+                    sp = splits[q].sign > 0 ? 1 : -1; sb = isfinite(splits[q].beta) ? splits[q].beta * (float)sp : 0.0f;
+                }
+                double lsu, us, ui;
+                if (sp > 0) { lsu = 1; us = 1; ui = 0; }
+                else if (sp < 0) { lsu = 0; us = 0; ui = 0; }
+                else if (l >= 0.0f) { lsu = 1; us = 1; ui = 0; }
+                else if (u <= 0.0f) { lsu = 0; us = 0; ui = 0; }
+                else {
+                    float w = fmaxf(u - l, RELU_RELAX_MIN_WIDTH);
+                    us = (double)(u / w); ui = (double)(-l * u / w);
+                    lsu = alpha_up ? (double)alpha_up[o + j] : (alpha ? (double)alpha[o + j] : ((u > -l) ? 1.0 : 0.0));
+                }
+                for (int s = 0; s < S; ++s) {
+                    size_t q = (size_t)s * n + j;
+                    double a = A[q];
+                    apre[r][q] = a;
+                    double sg = (a >= 0.0) ? us : lsu, ta = (a >= 0.0) ? ui : 0.0;
+                    sig[r][q] = sg; tau[r][q] = ta;
+                    b[s] += a * ta;
+                    A[q] = a * sg + (double)sb;
+                }
+            }
+        }
+    }
+    int n0 = net->dims[0];
+    double *Z = (double *)malloc(8 * (size_t)S * n0);
+    for (int s = 0; s < S; ++s) {
+        double v = b[s];
+        for (int j = 0; j < n0; ++j) {
+            double a = A[(size_t)s * n0 + j];
+            double x = (a >= 0.0) ? (double)in_hi[j] : (double)in_lo[j];
+            Z[(size_t)s * n0 + j] = x;
+            v += a * x;
+        }
+        if (upper_out) upper_out[s] = v;
+    }
+    if (grad_alpha_up) memset(grad_alpha_up, 0, 4 * total);
+    n = n0;
+    for (int k = 0; k < L; ++k) {
+        lin_layer Lk = net_layer(net, k);
+        double *Zn = (double *)calloc((size_t)S * Lk.n_out, 8);
+        for (int s = 0; s < S; ++s)
+            for (int o = 0; o < Lk.n_out; ++o) {
+                const float *w = Lk.W + (size_t)o * Lk.n_in;
+                double acc = Lk.b ? (double)Lk.b[o] : 0.0;
+                for (int j = 0; j < Lk.n_in; ++j) acc += Z[(size_t)s * Lk.n_in + j] * (double)w[j];
+                Zn[(size_t)s * Lk.n_out + o] = acc;
+            }
+        free(Z); Z = Zn; n = Lk.n_out;
+        if (k < L - 1 && relu_after(net, k)) {
+            size_t o = pre_offset(net, k);
+            for (int j = 0; j < n; ++j) {
+                float l = pre_lo[o + j], u = pre_hi[o + j];
+                int is_split = 0;
+                for (int q = 0; q < n_splits; ++q) if (splits[q].relu == k && splits[q].neuron == j) is_split = 1;
+                double ga = 0.0;
+                for (int s = 0; s < S; ++s) {
+                    size_t q = (size_t)s * n + j;
+                    double ap = apre[k][q];
+                    ga += Z[q] * (ap < 0.0 ? ap : 0.0);
+                    Z[q] = Z[q] * sig[k][q] + tau[k][q];
+                }
+                if (!is_split && l < 0.0f && u > 0.0f && grad_alpha_up) grad_alpha_up[o + j] = (float)ga;
+            }
+        }
+    }
+    for (int r = 0; r < L; ++r) { free(apre[r]); free(sig[r]); free(tau[r]); }
+    free(apre); free(sig); free(tau); free(A); free(b); free(Z);
+    return 0;
+}
+
 /* Projected-Adam ascent on alpha (clamped to [0,1], unstable unsplit neurons only:
  * bounds/alpha/shared.rs:106-146) and beta (clamped to >= 0, gradient clipped to +-clip:
  * beta_crown/state/beta.rs:314-441), learning rate lr * decay^(t-1), intermediate bounds fixed.  Each iteration
@@ -1099,22 +1220,39 @@ int nyo_optimize(const nyo_net *net, const float *in_lo, const float *in_hi, con
                                   lr_decay, clip_beta, 0, best_lo, best_hi);
 }
 
-/* objective 0: sum of the rows' lower bounds; 1: the row whose current lower bound is smallest. */
+/* objective 0: sum of the rows' lower bounds; 1: the row whose current lower bound is smallest; 2: dual alpha -
+ * as 0 for alpha and beta, and in addition a separate upper-path slope alpha_up (started at alpha) descends the sum
+ * of the upper bounds.  alpha_up_out (n_pre floats, may be NULL) receives the final upper-path slopes. */
 int nyo_optimize_objective(const nyo_net *net, const float *in_lo, const float *in_hi, const float *pre_lo,
                            const float *pre_hi, nyo_split *splits, int n_splits, float *alpha, int iterations,
                            float lr_alpha, float lr_beta, float lr_decay, float clip_beta, int objective, float *best_lo,
                            float *best_hi) {
+    return nyo_optimize_dual(net, in_lo, in_hi, pre_lo, pre_hi, splits, n_splits, alpha, iterations, lr_alpha, lr_beta,
+                             lr_decay, clip_beta, objective, best_lo, best_hi, NULL);
+}
+
+int nyo_optimize_dual(const nyo_net *net, const float *in_lo, const float *in_hi, const float *pre_lo,
+                      const float *pre_hi, nyo_split *splits, int n_splits, float *alpha, int iterations,
+                      float lr_alpha, float lr_beta, float lr_decay, float clip_beta, int objective, float *best_lo,
+                      float *best_hi, float *alpha_up_out) {
     int L = net->n_linear, S = net->dims[L];
     size_t total = pre_offset(net, L);
     float *ga = (float *)calloc(total, 4), *ma = (float *)calloc(total, 4), *va = (float *)calloc(total, 4);
     float *gb = (float *)calloc((size_t)(n_splits + 1), 4), *mb = (float *)calloc((size_t)(n_splits + 1), 4), *vb = (float *)calloc((size_t)(n_splits + 1), 4);
     float *lo = (float *)malloc(4 * (size_t)S), *hi = (float *)malloc(4 * (size_t)S);
     const float b1 = 0.9f, b2 = 0.999f, eps = 1e-8f;
+    const int dual = objective == 2 && alpha != NULL;
+    float *aup = NULL, *gu = NULL, *mu = NULL, *vu = NULL;
+    if (dual) {
+        aup = (float *)malloc(4 * total); memcpy(aup, alpha, 4 * total);
+        gu = (float *)calloc(total, 4); mu = (float *)calloc(total, 4); vu = (float *)calloc(total, 4);
+    }
     for (int s = 0; s < S; ++s) { best_lo[s] = -INFINITY; best_hi[s] = INFINITY; }
     for (int t = 1; t <= iterations; ++t) {
-        nyo_beta_crown_bound(net, in_lo, in_hi, pre_lo, pre_hi, splits, n_splits, alpha, lo, hi);
+        nyo_beta_crown_bound_dual(net, in_lo, in_hi, pre_lo, pre_hi, splits, n_splits, alpha, aup, lo, hi);
         for (int s = 0; s < S; ++s) { if (lo[s] > best_lo[s]) best_lo[s] = lo[s]; if (hi[s] < best_hi[s]) best_hi[s] = hi[s]; }
         if (t == iterations) break;
+        if (dual) nyo_upper_gradient(net, in_lo, in_hi, pre_lo, pre_hi, splits, n_splits, alpha, aup, NULL, gu);
         int row = -1;
         if (objective == 1) { row = 0; for (int s = 1; s < S; ++s) if (lo[s] < lo[row]) row = s; }
         nyo_joint_gradient_rows(net, in_lo, in_hi, pre_lo, pre_hi, splits, n_splits, alpha, NULL, ga, gb, row);
@@ -1134,6 +1272,19 @@ int nyo_optimize_objective(const nyo_net *net, const float *in_lo, const float *
             if (isnan(a)) { a = 0.5f; ma[i] = 0.0f; va[i] = 0.0f; }
             alpha[i] = a;
         }
+        if (dual && lr_alpha > 0.0f) for (size_t i = 0; i < hidden; ++i) {
+            if (!(pre_lo[i] < 0.0f && pre_hi[i] > 0.0f)) continue;
+            int is_split = 0;
+            for (int q = 0; q < n_splits; ++q) if (pre_offset(net, splits[q].relu) + (size_t)splits[q].neuron == i) is_split = 1;
+            if (is_split) continue;
+            float g = gu[i];
+            mu[i] = b1 * mu[i] + (1.0f - b1) * g;
+            vu[i] = b2 * vu[i] + (1.0f - b2) * g * g;
+            float a = aup[i] - lra * (mu[i] / bc1) / (sqrtf(vu[i] / bc2) + eps);   /* descent: the upper bound shrinks */
+            a = fminf(fmaxf(a, 0.0f), 1.0f);
+            if (isnan(a)) { a = 0.5f; mu[i] = 0.0f; vu[i] = 0.0f; }
+            aup[i] = a;
+        }
         if (lr_beta > 0.0f) for (int q = 0; q < n_splits; ++q) {
             float g = gb[q];
             if (clip_beta > 0.0f) g = fminf(fmaxf(g, -clip_beta), clip_beta);
@@ -1144,6 +1295,8 @@ int nyo_optimize_objective(const nyo_net *net, const float *in_lo, const float *
             splits[q].beta = fmaxf(bnew, 0.0f);
         }
     }
+    if (dual && alpha_up_out) memcpy(alpha_up_out, aup, 4 * total);
+    free(aup); free(gu); free(mu); free(vu);
     free(ga); free(ma); free(va); free(gb); free(mb); free(vb); free(lo); free(hi);
     return 0;
 }

@@ -107,6 +107,16 @@ int nyo_optimize_objective(const nyo_net *net, const float *in_lo, const float *
                            const float *pre_hi, nyo_split *splits, int n_splits, float *alpha, int iterations,
                            float lr_alpha, float lr_beta, float lr_decay, float clip_beta, int objective, float *best_lo,
                            float *best_hi);
+int nyo_beta_crown_bound_dual(const nyo_net *net, const float *in_lo, const float *in_hi, const float *pre_lo,
+                              const float *pre_hi, const nyo_split *splits, int n_splits, const float *alpha,
+                              const float *alpha_up, float *out_lo, float *out_hi);
+int nyo_upper_gradient(const nyo_net *net, const float *in_lo, const float *in_hi, const float *pre_lo,
+                       const float *pre_hi, const nyo_split *splits, int n_splits, const float *alpha,
+                       const float *alpha_up, double *upper_out, float *grad_alpha_up);
+int nyo_optimize_dual(const nyo_net *net, const float *in_lo, const float *in_hi, const float *pre_lo,
+                      const float *pre_hi, nyo_split *splits, int n_splits, float *alpha, int iterations,
+                      float lr_alpha, float lr_beta, float lr_decay, float clip_beta, int objective, float *best_lo,
+                      float *best_hi, float *alpha_up_out);
 int nyo_select_intercept(const nyo_net *net, const float *pre_lo, const float *pre_hi, const nyo_split *splits,
                          int n_splits, int32_t *relu, int32_t *neuron, float *score);
 

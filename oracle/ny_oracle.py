@@ -68,6 +68,10 @@ def lib():
                                              C.c_float, C.c_float, C.c_int, fp, fp]
         L.nyo_joint_gradient_rows.argtypes = [np_, fp, fp, fp, fp, C.c_void_p, C.c_int, fp, dp, fp, fp, C.c_int]
         L.nyo_select_largest_width.argtypes = [np_, fp, fp, C.c_void_p, C.c_int, ip, ip, fp]
+        L.nyo_beta_crown_bound_dual.argtypes = [np_, fp, fp, fp, fp, C.c_void_p, C.c_int, fp, fp, fp, fp]
+        L.nyo_upper_gradient.argtypes = [np_, fp, fp, fp, fp, C.c_void_p, C.c_int, fp, fp, dp, fp]
+        L.nyo_optimize_dual.argtypes = [np_, fp, fp, fp, fp, C.c_void_p, C.c_int, fp, C.c_int, C.c_float, C.c_float,
+                                        C.c_float, C.c_float, C.c_int, fp, fp, fp]
         L.nyo_set_error_channel.argtypes = [C.c_int]
         L.nyo_set_error_channel.restype = None
         L.nyo_select_intercept.argtypes = [np_, fp, fp, C.c_void_p, C.c_int, ip, ip, fp]
@@ -455,3 +459,40 @@ def crown_exact_f64(ws, bs, spec, lo, hi, sparse_rule=True):
         t[k] = inter((il, iu), c)
     c = backward(L - 1, ws[-1].shape[0])
     return inter(c, t[L - 1]), t
+
+
+def beta_crown_bound_dual(net: Net, lo, hi, pre_lo, pre_hi, splits: np.ndarray, alpha, alpha_up):
+    """beta-CROWN bound with a separate upper-path slope alpha_up (dual alpha)."""
+    lo, hi, pre_lo, pre_hi, alpha, alpha_up = (_f32(x) for x in (lo, hi, pre_lo, pre_hi, alpha, alpha_up))
+    splits = np.ascontiguousarray(splits, SPLIT_DTYPE)
+    S = int(net.dims[-1])
+    ol, ou = np.empty(S, np.float32), np.empty(S, np.float32)
+    lib().nyo_beta_crown_bound_dual(C.byref(net.c), _fp(lo), _fp(hi), _fp(pre_lo), _fp(pre_hi), splits.ctypes.data,
+                                    len(splits), _fp(alpha), _fp(alpha_up), _fp(ol), _fp(ou))
+    return ol, ou
+
+
+def upper_gradient(net: Net, lo, hi, pre_lo, pre_hi, splits: np.ndarray, alpha, alpha_up):
+    """(upper bounds [S] in binary64, gradient of their sum with respect to alpha_up [n_pre])."""
+    lo, hi, pre_lo, pre_hi, alpha, alpha_up = (_f32(x) for x in (lo, hi, pre_lo, pre_hi, alpha, alpha_up))
+    splits = np.ascontiguousarray(splits, SPLIT_DTYPE)
+    S = int(net.dims[-1])
+    up = np.empty(S, np.float64)
+    g = np.zeros(net.n_pre, np.float32)
+    lib().nyo_upper_gradient(C.byref(net.c), _fp(lo), _fp(hi), _fp(pre_lo), _fp(pre_hi), splits.ctypes.data, len(splits),
+                             _fp(alpha), _fp(alpha_up), up.ctypes.data_as(C.POINTER(C.c_double)), _fp(g))
+    return up, g
+
+
+def optimize_dual(net: Net, lo, hi, pre_lo, pre_hi, splits: np.ndarray, alpha, iterations, lr_alpha, lr_beta,
+                  lr_decay=0.98, clip_beta=10.0):
+    """Dual-alpha optimisation: returns (best_lo, best_hi, alpha, alpha_up, splits)."""
+    lo, hi, pre_lo, pre_hi = _f32(lo), _f32(hi), _f32(pre_lo), _f32(pre_hi)
+    alpha = _f32(alpha).copy()
+    splits = np.ascontiguousarray(splits, SPLIT_DTYPE).copy()
+    S = int(net.dims[-1])
+    bl, bu = np.empty(S, np.float32), np.empty(S, np.float32)
+    aup = np.zeros(net.n_pre, np.float32)
+    lib().nyo_optimize_dual(C.byref(net.c), _fp(lo), _fp(hi), _fp(pre_lo), _fp(pre_hi), splits.ctypes.data, len(splits),
+                            _fp(alpha), iterations, lr_alpha, lr_beta, lr_decay, clip_beta, 2, _fp(bl), _fp(bu), _fp(aup))
+    return bl, bu, alpha, aup, splits

@@ -243,3 +243,45 @@ def test_alpha_crown_full_size_input_cells(eng, oracle):
         mn = W.sample_min_margin(cell, 100000, 4000 + d)
         assert np.all(glo[d] <= mn), d
     eng.release_network(nid)
+
+
+def test_dual_alpha_matches_oracle(eng, oracle):
+    """objective = 2: the upper rows get their own slopes (dual alpha), which descend the sum of the upper bounds
+    while alpha / beta ascend the lower bounds exactly as with objective 0."""
+    wl = W.config_mlp_bab(seed=27, hidden=48, depth=3, n_in=40, eps=0.03, n_fix=3)
+    onet, ospec, nid, rl, ru = _setup(eng, oracle, wl)
+    D, iters = 40, 12
+    splits, ns = W.draw_domains(wl, rl, ru, D)
+    ns = ns.copy()
+    ns[0] = 0
+    eng.batch_upload(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, splits, ns, mode=1)
+    eng.batch_optimize(iters, 0.1, 0.05, objective=0)
+    slo, shi, _ = eng.batch_download()
+    eng.batch_optimize(iters, 0.1, 0.05, objective=2)
+    glo, ghi, ginf = eng.batch_download()
+    gaup = eng.batch_download_alpha_upper()
+    galpha, _ = eng.batch_download_params()
+    S = wl.spec.shape[0]
+    rl2 = np.concatenate([rl, np.full(S, -np.inf, np.float32)])
+    ru2 = np.concatenate([ru, np.full(S, np.inf, np.float32)])
+    n_hidden = int(wl.net.dims[1:-1].sum())
+    n, moved = 0, 0
+    for d in range(D):
+        sp = splits[d][: ns[d]]
+        pl, pu, bad = oracle.domain_bounds(ospec, wl.in_lo, wl.in_hi, rl2, ru2, sp, 1)
+        assert bool(ginf[d]) == bool(bad)
+        if bad:
+            continue
+        olo, ohi, _, oaup, _ = oracle.optimize_dual(ospec, wl.in_lo, wl.in_hi, pl, pu, sp, oracle.heuristic_alpha(ospec, pl, pu),
+                                                    iters, 0.1, 0.05)
+        assert _rel(np.concatenate([glo[d], ghi[d]]), np.concatenate([olo, ohi])) <= OPT_TOL, d
+        unstable = ((pl < 0) & (pu > 0))[:n_hidden]
+        assert np.all((gaup[d][:n_hidden][unstable] >= 0) & (gaup[d][:n_hidden][unstable] <= 1))
+        moved += int(np.any(gaup[d][:n_hidden][unstable] != galpha[d][:n_hidden][unstable]))
+        n += 1
+    assert n > D // 2 and moved > n // 2          # the two paths really use different slopes
+    feas = ginf == 0
+    # the lower bounds follow the same trajectory as with shared slopes; the upper bounds only get better
+    assert _rel(glo[feas], slo[feas]) <= 1e-5
+    assert np.all(ghi[feas] <= shi[feas] + 1e-5 * np.abs(shi[feas])) and ghi[feas].sum() < shi[feas].sum()
+    eng.release_network(nid)

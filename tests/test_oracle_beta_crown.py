@@ -176,3 +176,29 @@ def test_worst_row_gradient_is_that_rows_gradient(oracle):
         fd = (oracle.joint_gradient(net, wl.in_lo, wl.in_hi, pl, pu, sp, ap)[0][row]
               - oracle.joint_gradient(net, wl.in_lo, wl.in_hi, pl, pu, sp, am)[0][row]) / (2 * h)
         assert abs(fd - ga[i]) <= 1e-3 * max(1.0, abs(fd))
+
+
+def test_dual_alpha_upper_gradient_and_optimisation(oracle):
+    """Upper-path slopes: gradient against central differences of the upper bounds; the dual optimisation leaves the
+    lower bounds where shared slopes put them and tightens the upper ones."""
+    wl, net, sp, pl, pu, alpha = _one_domain(oracle, seed=19)
+    rng = np.random.default_rng(3)
+    aup = np.where((pl < 0) & (pu > 0), rng.uniform(0.2, 0.8, pl.shape), 0.0).astype(np.float32)
+    up, g = oracle.upper_gradient(net, wl.in_lo, wl.in_hi, pl, pu, sp, alpha, aup)
+    _, shi = oracle.beta_crown_bound_dual(net, wl.in_lo, wl.in_hi, pl, pu, sp, alpha, aup)
+    assert np.all(shi >= up - 1e-9) and np.allclose(shi, up, rtol=0, atol=1e-4)
+    h = 1e-3
+    idx = np.flatnonzero(g != 0)[:10]
+    assert len(idx) >= 3
+    for i in idx:
+        p_, m_ = aup.copy(), aup.copy()
+        p_[i] += h
+        m_[i] -= h
+        fd = (oracle.upper_gradient(net, wl.in_lo, wl.in_hi, pl, pu, sp, alpha, p_)[0].sum()
+              - oracle.upper_gradient(net, wl.in_lo, wl.in_hi, pl, pu, sp, alpha, m_)[0].sum()) / (2 * h)
+        assert abs(fd - g[i]) <= 1e-3 * max(1.0, abs(fd))
+    a0 = oracle.heuristic_alpha(net, pl, pu)
+    bl, bu, _, _ = oracle.optimize(net, wl.in_lo, wl.in_hi, pl, pu, sp, a0, 15, 0.1, 0.05)
+    dl, du, _, aup1, _ = oracle.optimize_dual(net, wl.in_lo, wl.in_hi, pl, pu, sp, a0, 15, 0.1, 0.05)
+    assert np.array_equal(dl, bl) and np.all(du <= bu + 1e-6) and du.sum() < bu.sum()
+    assert np.all((aup1 >= 0) & (aup1 <= 1))
