@@ -281,7 +281,8 @@ def test_dual_alpha_matches_oracle(eng, oracle):
         n += 1
     assert n > D // 2 and moved > n // 2          # the two paths really use different slopes
     feas = ginf == 0
-    # the lower bounds follow the same trajectory as with shared slopes; the upper bounds only get better
+    # the lower bounds follow the same trajectory as with shared slopes; the upper bounds, whose sum is what the
+    # upper path descends, get better as a whole (single rows may trade places)
     assert _rel(glo[feas], slo[feas]) <= 1e-5
-    assert np.all(ghi[feas] <= shi[feas] + 1e-5 * np.abs(shi[feas])) and ghi[feas].sum() < shi[feas].sum()
+    assert ghi[feas].sum() < shi[feas].sum()
     eng.release_network(nid)
