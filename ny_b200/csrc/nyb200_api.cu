@@ -382,6 +382,9 @@ int run_forward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int fw
         if (!Fl || !derr) return NYB200_ERR_OOM;
     }
     size_t np = nv.nps;
+    // a slack-to-width ratio above this marks the domain for the binary64 re-evaluation (same switch as the
+    // penalty criterion: 0 disables)
+    const float fwd_tol = e->refine_tol;
     NYB_CUDA(e, cudaMemsetAsync(p.flags, 0, (size_t)D * 4, e->stream));
     NYB_CUDA(e, cudaMemsetAsync(p.code, 0, (size_t)D * np, e->stream));
     NYB_CUDA(e, cudaMemsetAsync(p.sbeta, 0, (size_t)D * np * 4, e->stream));
@@ -415,7 +418,7 @@ int run_forward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int fw
         launch_ibp_finish(e, nv, k, D, fwd_mode, p.raw_lo, p.raw_hi, raw_ds, fwd_mode == 2 ? nullptr : p.inh_lo,
                           fwd_mode == 2 ? nullptr : p.inh_hi, p.code, p.sbeta, b.has_alpha ? p.alpha : nullptr, p.pre_lo,
                           p.pre_hi, p.zl, p.zu, p.tab, p.zabs, p.flags, tk ? Fl : nullptr, ldf,
-                          tk ? umma_eps(nv.dims[k]) * 1.000001 : 0.0, p.q);
+                          tk ? umma_eps(nv.dims[k]) * 1.000001 : 0.0, p.q, tk ? fwd_tol : 0.f);
     }
     NYB_CUDA(e, cudaGetLastError());
     return NYB200_OK;

@@ -19,6 +19,7 @@ constexpr int kMaxLinear = 32;
 constexpr int kFlagInfeasible = 1;  // a split clamp inverted an interval: the domain is empty
 constexpr int kFlagDegraded = 2;    // NaN / infinite pre-activation bound: bounds degrade to [-inf, +inf]
 constexpr int kFlagInvalid = 4;     // split entry out of range
+constexpr int kFlagLooseFwd = 8;    // fast-path interval pass: rounding slack visible against an unstable neuron's width
 
 // Device-side view of a registered network (passed by value to kernels).
 struct NetView {
@@ -133,7 +134,7 @@ void launch_ibp_finish(nyb200_engine *e, const NetView &nv, int k, int D, int mo
                        const float *raw_hi, long raw_dstride, const float *inh_lo, const float *inh_hi,
                        const signed char *code, const float *sbeta, const float *alpha, float *pre_lo, float *pre_hi,
                        float *zl, float *zu, float4 *tab, float *zabs, int *flags, const float *F = nullptr, int ldf = 0,
-                       double eps = 0.0, float *q = nullptr);
+                       double eps = 0.0, float *q = nullptr, float fwd_tol = 0.f);
 void launch_seed(nyb200_engine *e, const float *spec, int S, int nL, int D, int lda, float *A);
 // A [D*2n x lda] = per domain the n x n identity for the lower rows, then again for the upper rows.
 void launch_seed_identity(nyb200_engine *e, int n, int D, int lda, float *A);

@@ -176,7 +176,7 @@ __global__ void k_ibp_finish(NetView nv, int k, int D, int mode, int last, const
                              float *__restrict__ pre_lo, float *__restrict__ pre_hi, float *__restrict__ zl,
                              float *__restrict__ zu, float4 *__restrict__ tab, float *__restrict__ zabs,
                              int *__restrict__ flags, const float *__restrict__ F, int ldf, double eps,
-                             float *__restrict__ q) {
+                             float *__restrict__ q, float fwd_tol) {
     int n = nv.dims[k + 1], off = nv.pre_off[k];
     long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= (long)D * n) return;
@@ -197,6 +197,12 @@ __global__ void k_ibp_finish(NetView nv, int k, int D, int mode, int last, const
         u = __double2float_ru(pu + nl + b + slack);
         if (isnan(l) || isnan(u)) { l = -INFINITY; u = INFINITY; }
         q[o] = __double2float_ru(qq);
+        // The slack widens the interval; where that is visible against the width of an unstable neuron the
+        // relaxation built from it (and everything downstream) is visibly looser than the binary64 pass's:
+        // such a domain is flagged and the batch re-evaluated with binary64 contractions.
+        if (!last && l < 0.f && u > 0.f) {
+            if (fwd_tol > 0.f && (float)(2.0 * slack) > fwd_tol * (u - l)) atomicOr(&flags[d], kFlagLooseFwd);
+        }
     } else {
         l = raw_lo[(long)d * raw_ds + off + j];
         u = raw_hi[(long)d * raw_ds + off + j];
@@ -314,9 +320,8 @@ k_relax(int n, int off, int M, int R, int S, int n_pre, int identity, float *A, 
 
 // Vectorised form of k_relax for 16-byte aligned layouts (n, off, lda, row strides multiples of 4): one
 // warp per row, every lane handles float4 groups and issues all loads of a group before using them.
-// The kernel is instruction-issue bound, so the per-coefficient work is kept branch-free and short:
-// the product a*slope is rounded directly toward the safe side (one instruction; never looser than the
-// reference's round-to-nearest-then-step and at most one ulp tighter), its exact residual is charged as
+// The kernel is instruction-issue bound, so the per-coefficient work is kept short: the product a*slope is
+// rounded as the reference does (to nearest, then one ulp outward), its exact residual is charged as
 // the rounding gap, penalties are accumulated in fp32 with upward-directed operations (an upper bound is
 // all that is needed) and inflated once at the end; the bias stays in binary64.
 template <bool UPPER, bool RELAX, bool BIAS>
@@ -330,7 +335,18 @@ __device__ __forceinline__ float relax_one(float a, float4 t, float au, float za
         // au: the upper path's own lower slope (dual alpha, activations/relu/mod.rs:570-1128); equals t.x otherwise
         const float slope = (pos != UPPER) ? (UPPER ? au : t.x) : t.y;
         const float icp = ((pos == UPPER) && a != 0.f) ? t.z : 0.f;
-        nw = UPPER ? __fmul_ru(a, slope) : __fmul_rd(a, slope);
+        // the reference's rounding: round to nearest, then one ulp outward (relu_backward.rs:105-153); an exact
+        // zero product (a == 0 or slope == 0) needs no step.  A directed product would be up to one ulp tighter,
+        // which is visible on bounds that cancel to almost nothing; staying on the reference's values is worth
+        // more here than that ulp.
+        const float prod = __fmul_rn(a, slope);
+        const unsigned pb = __float_as_uint(prod);
+        const int neg = (int)pb >> 31;  // 0 or -1: one ulp outward is +-1 on the bit pattern, mirrored for negatives
+        const float stepped = __uint_as_float(UPPER ? pb + 1u + 2u * (unsigned)neg : pb - 1u - 2u * (unsigned)neg);
+        // a product that underflowed to zero takes the directed product instead (the bit step would wrap); an
+        // overflowed one steps into a NaN pattern, which the concretisation turns into [-inf, +inf] for the row
+        nw = (prod == 0.f) ? (UPPER ? __fmul_ru(a, slope) : __fmul_rd(a, slope)) : stepped;
+        nw = (a == 0.f || slope == 0.f) ? 0.f : nw;
         sp = __fmaf_ru(fabsf(fmaf(a, slope, -nw)), za, sp);
         sb = fma((double)a, (double)icp, sb);
         sa = __fmaf_ru(fabsf(a), fabsf(icp), sa);
@@ -610,7 +626,10 @@ __global__ void k_count_loose(int D, int S, int R, const float *__restrict__ out
                               const double *__restrict__ rpen, const int *__restrict__ flags, float tol,
                               int *__restrict__ n_loose) {
     int d = blockIdx.x * blockDim.x + threadIdx.x;
-    if (d >= D || flags[d] != 0) return;
+    if (d >= D) return;
+    const int f = flags[d];
+    if (f & ~kFlagLooseFwd) return;  // infeasible / degraded / invalid domains are not re-evaluated
+    if (f & kFlagLooseFwd) { atomicAdd(n_loose, 1); return; }
     float scale = 0.f;
     for (int s = 0; s < S; ++s) {
         float l = out_lo[d * S + s], u = out_hi[d * S + s];
@@ -760,12 +779,12 @@ void launch_ibp_finish(nyb200_engine *e, const NetView &nv, int k, int D, int mo
                        const float *raw_hi, long raw_dstride, const float *inh_lo, const float *inh_hi,
                        const signed char *code, const float *sbeta, const float *alpha, float *pre_lo, float *pre_hi,
                        float *zl, float *zu, float4 *tab, float *zabs, int *flags, const float *F, int ldf, double eps,
-                       float *q) {
+                       float *q, float fwd_tol) {
     long total = (long)D * nv.dims[k + 1];
     int last = (k == nv.L - 1);
     k_ibp_finish<<<(unsigned)((total + 255) / 256), 256, 0, e->stream>>>(nv, k, D, mode, last, raw_lo, raw_hi, raw_dstride,
                                                                          inh_lo, inh_hi, code, sbeta, alpha, pre_lo,
-                                                                         pre_hi, zl, zu, tab, zabs, flags, F, ldf, eps, q);
+                                                                         pre_hi, zl, zu, tab, zabs, flags, F, ldf, eps, q, fwd_tol);
     NYB_COUNT(e);
 }
 

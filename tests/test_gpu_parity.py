@@ -231,3 +231,10 @@ def test_full_size_batch_properties(eng, oracle):
     ok = np.isfinite(mn)
     assert np.all(lo[d][ok] <= mn[ok])
     eng.release_network(nid)
+
+
+def test_entry_point_smoke():
+    """The repository's smoke entry (one small invocation of the hot path checked against the oracle) stays green."""
+    import __graft_entry__
+
+    __graft_entry__.smoke()
