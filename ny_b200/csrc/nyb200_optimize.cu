@@ -131,6 +131,15 @@ k_adjoint_relu(int n, int off, int D, int S, int R, int Zr, long nps, float *__r
     tab[o] = tb;
 }
 
+// Y[r, j] += X[r, j]
+__global__ void k_add_adjoint(long rows, int n, float *__restrict__ Y, int ldy, const float *__restrict__ X, int ldx) {
+    long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= rows * n) return;
+    long r = t / n;
+    int j = (int)(t - r * n);
+    Y[r * ldy + j] += X[r * ldx + j];
+}
+
 // alpha_up = the lower path's slopes (the table's first component), the starting point of the dual alpha
 __global__ void k_init_alpha_up(long n, const float4 *__restrict__ tab, float *__restrict__ aup) {
     long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -244,8 +253,6 @@ int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg) {
         return set_err(e, NYB200_ERR_INVALID, "learning rates must be >= 0 and the decay > 0");
     Net *net;
     NYB_TRY(find_net(e, e->batch.net_id, &net));
-    if (net->has_skip() && cfg.iterations > 1)
-        return set_err(e, NYB200_ERR_UNSUPPORTED, "parameter optimisation of networks with residual connections is not built");
     Batch &b = e->batch;
     b.dual_alpha = cfg.objective == 2 && cfg.iterations > 1 && net->v.L >= 2;  // decides which arrays the batch has
     BatchPtrs p;
@@ -331,17 +338,31 @@ int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg) {
                                                                               p.in_hi, (long)b.box_stride, z0, ldz);
         e->launches++;
         float *zc = z0, *zn = z1;
+        float *zstash = nullptr;
         for (int k = 0; k < L - 1; ++k) {
             int K = nv.dims[k], N = nv.dims[k + 1];
             if (net->is_conv(k) && tensor) NYB_TRY(conv_forward_tensor(e, *net, k, D * Zr, zc, ldz, zn, ldz, derr));
             else if (net->is_conv(k)) launch_conv_plain(e, net->geom[k], D * Zr, zc, ldz, nv.W[k], zn, ldz);
             else if (tensor) NYB_TRY(launch_umma(e, net->umma_adj[k], D * Zr, zc, ldz, zn, ldz, derr));
             else launch_gemm_f64(e, D * Zr, N, K, zc, ldz, net->wt[k], N, zn, ldz, 1, nullptr, nullptr, 0, nullptr);
+            if (net->skip_of(k) >= 0 && zstash) {
+                // residual block: pre_k = W z + b + relu(pre_j), so the adjoint of relu(pre_j) joins here
+                long tot = (long)D * Zr * N;
+                k_add_adjoint<<<(unsigned)((tot + 255) / 256), 256, 0, e->stream>>>((long)D * Zr, N, zn, ldz, zstash, ldz);
+                e->launches++;
+            }
             long nt = (long)D * N;
             k_adjoint_relu<<<(unsigned)((nt + 255) / 256), 256, 0, e->stream>>>(N, nv.pre_off[k], D, S, R, Zr, np, zn, ldz, nv.b[k],
                                                                                ckpt[k], ldc, p.tab, p.code, p.pre_lo,
                                                                                p.pre_hi, mom, var, only_row, p.alpha_up, mom_up, var_up, h);
             e->launches++;
+            bool opens = false;  // is this layer's post-activation adjoint skipped forward to a later layer?
+            for (int kk = k + 2; kk < L - 1; ++kk) opens |= net->skip_of(kk) == k;
+            if (opens) {
+                zstash = (float *)ws_get(e, "adj_skip", (size_t)D * Zr * ldz * 4);
+                if (!zstash) return NYB200_ERR_OOM;
+                NYB_CUDA(e, cudaMemcpyAsync(zstash, zn, (size_t)D * Zr * ldz * 4, cudaMemcpyDeviceToDevice, e->stream));
+            }
             float *tmp = zc; zc = zn; zn = tmp;
         }
     }

@@ -174,3 +174,19 @@ def test_cnn_full_size_split_domains(eng, oracle):
             mn = W.sample_min_margin(wl, 4000, 8000, sp, chunk=1000)
             assert np.all(np.isfinite(mn)) and np.all(glo[d] <= mn)
     eng.release_network(nid)
+
+
+def test_conv_crown_pipeline_matches_oracle(eng, oracle):
+    """Plain CROWN with CROWN-IBP intermediates through convolutions (partial passes run transposed convolutions)
+    against the oracle's pipeline on the dense lowering; this network is shallow enough for direct parity."""
+    wl = _small_cnn(seed=34, eps=0.01)
+    onet, ospec, nid, rl, ru = _setup_conv(eng, oracle, wl)
+    glo, ghi, gil, giu = eng.crown_bounds(nid, wl.spec, wl.in_lo, wl.in_hi)
+    olo, ohi = oracle.crown(ospec, wl.in_lo, wl.in_hi)
+    nlo, nhi = oracle.crown(ospec, wl.in_lo, wl.in_hi, error_channel=False)
+    scale = max(np.abs(olo).max(), np.abs(ohi).max())
+    assert np.all(glo[0] >= olo - 1e-6 * scale) and np.all(ghi[0] <= ohi + 1e-6 * scale)   # never looser than the reference
+    assert np.abs(glo[0] - nlo).max() <= 2e-4 * scale and np.abs(ghi[0] - nhi).max() <= 2e-4 * scale
+    mn = W.sample_min_margin(wl, 50000, 31)
+    assert np.all(glo[0] <= mn)
+    eng.release_network(nid)
