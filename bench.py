@@ -263,8 +263,7 @@ def run_ours(args, rank, world, local_rank):
         torch.cuda.synchronize()
 
     clocks = sampler.stop(busy)
-    if not os.environ.get("NYB200_UMMA_DBG"):  # (kernel knock-out experiments produce garbage on purpose)
-        assert np.array_equal(elo, lo), "resident and host-buffer paths disagree"
+    assert np.array_equal(elo, lo), "resident and host-buffer paths disagree"
     h2d = splits.nbytes + ns.nbytes + wl.spec.nbytes + wl.in_lo.nbytes + wl.in_hi.nbytes + rl.nbytes + ru.nbytes
     d2h = lo.nbytes + hi.nbytes + inf.nbytes
 

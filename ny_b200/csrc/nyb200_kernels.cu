@@ -835,7 +835,7 @@ void launch_relax(nyb200_engine *e, const NetView &nv, int r, int lin_k, int M, 
 #define NYB_RELAX_DOM(RELAX, BIAS) \
     k_relax_dom<RELAX, BIAS><<<dgrid, 256, 0, e->stream>>>(n, off, D, R, S, (long)nv.nps, A, lda, Asrc, lds, tab, zabs, q, q_dstride, bk, aup, epsf, rb, rabs, rpen)
         // domain-major when a domain's rows amortise the table loads and there are enough warps to fill the GPU
-        const bool dom = R >= 4 && dwarps >= 2048 && !getenv("NYB200_RELAX_ROWMAJOR");
+        const bool dom = R >= 4 && dwarps >= 2048;
         if (dom) {
             if (r >= 0) { if (bk) NYB_RELAX_DOM(true, true); else NYB_RELAX_DOM(true, false); }
             else { if (bk) NYB_RELAX_DOM(false, true); else NYB_RELAX_DOM(false, false); }

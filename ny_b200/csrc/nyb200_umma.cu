@@ -47,10 +47,6 @@ constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*bar
 constexpr int THREADS = 512;
 // K stages (of 32) accumulated in one tensor-memory chain before the chunk is drained (default 1;
 // NYB200_CHUNK_STAGES overrides it for experiments, the rounding model follows the value in use).
-static int dbg_cfg() {
-    static int v = [] { const char *s = getenv("NYB200_UMMA_DBG"); return s ? atoi(s) : 0; }();
-    return v;
-}
 static int chunk_stages_cfg() {
     static int v = [] { const char *s = getenv("NYB200_CHUNK_STAGES"); int x = s ? atoi(s) : 1; return x < 1 ? 1 : (x > 64 ? 64 : x); }();
     return v;
@@ -164,7 +160,7 @@ __global__ void k_split_weights(const float *__restrict__ W, int K, int N, int K
 __global__ void __launch_bounds__(THREADS, 1)
 k_umma_tf32x3(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__ CUtensorMap tm_lo,
               const float *__restrict__ A, int lda, float *__restrict__ C, int ldc, int M, int N, int K,
-              int chunk_stages, int *__restrict__ err, int dbg, int a_plane) {
+              int chunk_stages, int *__restrict__ err, int a_plane) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned long long *bars = (unsigned long long *)(smem + STAGES * STAGE_BYTES);
@@ -214,7 +210,6 @@ k_umma_tf32x3(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__
                     if (!mbar_wait(smem_u32(&bars[EMPTY + s]), ph ^ 1)) { atomicExch(err, 1); *abort_flag = 1; break; }
                     unsigned char *st = smem + s * STAGE_BYTES;
                     unsigned bar = smem_u32(&bars[FULL_B + s]);
-                    if (dbg & 2) { mbar_arrive(bar); continue; }
                     mbar_expect_tx(bar, 2 * B_BYTES);
                     tma_load_2d(smem_u32(st + 2 * A_BYTES), &tm_hi, ks * BK, tn * BN, bar);
                     tma_load_2d(smem_u32(st + 2 * A_BYTES + B_BYTES), &tm_lo, ks * BK, tn * BN, bar);
@@ -287,7 +282,7 @@ k_umma_tf32x3(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) { if (lane == 0) { atomicExch(err, 4); *abort_flag = 1; } dead = true; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                if (!(dbg & 16) && ncols > 0)
+                if (ncols > 0)
 #pragma unroll
                 for (int c = 0; c < 128; c += 32) {
                     if (c >= ncols) break;
@@ -311,7 +306,7 @@ k_umma_tf32x3(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__
 #pragma unroll
                     for (int j = 0; j < 128; ++j) if (j < ncols) cb[(long)j * a_plane] = sum[j];
                 }
-            } else if (row < M && ncols > 0 && !(dbg & 4)) {
+            } else if (row < M && ncols > 0) {
                 float *crow = C + (long)row * ldc + col0;
                 if (ncols == 128 && ((reinterpret_cast<uintptr_t>(crow) & 31) == 0)) {
                     // 32-byte stores: every instruction writes whole sectors of this thread's row
@@ -374,7 +369,7 @@ k_umma_tf32x3(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__
             for (int c = 0; c < 8; ++c) {
                 int k = k0 + c * 4;
                 float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (row < M && !(dbg & 1)) {
+                if (row < M) {
                     if (k + 3 < K && ((reinterpret_cast<uintptr_t>(arow + k) & 15) == 0)) x = *(const float4 *)(arow + k);
                     else {
                         if (k < K) x.x = arow[k];
@@ -394,7 +389,6 @@ k_umma_tf32x3(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__
                 if (!mbar_wait(smem_u32(&bars[EMPTY + s]), ph ^ 1)) { atomicExch(err, 5); *abort_flag = 1; dead = true; break; }
                 unsigned char *st = smem + s * STAGE_BYTES;
                 float *ah = (float *)st, *al = (float *)(st + A_BYTES);
-                if (!(dbg & 8))
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
                     float4 x = v[c];
@@ -467,18 +461,24 @@ int umma_prepare_layer(nyb200_engine *e, const float *W, int K, int N, UmmaLayer
 
 int launch_umma(nyb200_engine *e, const UmmaLayer &L, int M, const float *A, int lda, float *C, int ldc, int *err,
                 int a_plane) {
-    static bool attr_set = false;
-    if (!attr_set) {
-        if (cudaFuncSetAttribute(k_umma_tf32x3, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
-            return set_err(e, NYB200_ERR_INTERNAL, "cannot raise the dynamic shared-memory limit");
-        attr_set = true;
+    // the attribute is a per-device property of the function: set it once on every device that launches it
+    static std::mutex attr_mu;
+    static bool attr_set[64] = {false};
+    {
+        std::lock_guard<std::mutex> g(attr_mu);
+        const int dev = (e->device >= 0 && e->device < 64) ? e->device : 0;
+        if (!attr_set[dev]) {
+            if (cudaFuncSetAttribute(k_umma_tf32x3, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+                return set_err(e, NYB200_ERR_INTERNAL, "cannot raise the dynamic shared-memory limit");
+            attr_set[dev] = true;
+        }
     }
     int sms = 0;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, e->device);
     int tiles = ((M + BM - 1) / BM) * ((L.N + BN - 1) / BN);
     int grid = tiles < sms ? tiles : sms;
     k_umma_tf32x3<<<grid, THREADS, SMEM_BYTES, e->stream>>>(*(const CUtensorMap *)L.tm_hi, *(const CUtensorMap *)L.tm_lo, A,
-                                                            lda, C, ldc, M, L.N, L.K, chunk_stages_cfg(), err, dbg_cfg(), a_plane);
+                                                            lda, C, ldc, M, L.N, L.K, chunk_stages_cfg(), err, a_plane);
     e->launches++;
     return NYB200_OK;
 }
