@@ -134,9 +134,11 @@ __device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
 
 // Round an fp32 value to the nearest TF32 value (10 explicit mantissa bits), ties away from zero.
 __device__ __forceinline__ float rn_tf32(float x) {
-    unsigned r;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-    return __uint_as_float(r);
+    // Half an ulp of the 10-bit mantissa added to the magnitude bits, then the 13 low bits cleared: the value
+    // cvt.rna.tf32.f32 returns (a carry into the exponent is the correct rounding to the next binade or to
+    // infinity; infinities and NaNs keep their class), in two full-rate integer instructions instead of one
+    // conversion-pipe instruction.
+    return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u);
 }
 
 }  // namespace umma
@@ -365,6 +367,12 @@ k_umma_tf32x3(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__
                 return;
             }
             const float *arow = A + (long)row * lda;
+            if (row < M && k0 + BK <= K && ((reinterpret_cast<uintptr_t>(arow + k0) & 15) == 0)) {
+                // whole, aligned chunk (the usual case): eight unconditional 16-byte loads
+#pragma unroll
+                for (int c = 0; c < 8; ++c) v[c] = *(const float4 *)(arow + k0 + c * 4);
+                return;
+            }
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
                 int k = k0 + c * 4;
