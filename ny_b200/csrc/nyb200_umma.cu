@@ -45,6 +45,13 @@ constexpr int B_BYTES = BN * BK * 4;   // 32 KB per half
 constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
 constexpr int THREADS = 512;
+// Register budget after the roles re-split it with setmaxnreg: 4 control warps, 8 epilogue warps, 4 producer warps.
+// setmaxnreg.inc blocks until the registers it asks for have been released by the other warps' setmaxnreg.dec, so
+// the targets must fit what the CTA was launched with (65536 / THREADS per thread); no bounded wait can catch a
+// shortfall.
+constexpr int REGS_LAUNCH = 65536 / THREADS, REGS_CONTROL = 40, REGS_EPILOGUE = 184, REGS_PRODUCER = 104;
+static_assert(4 * 32 * REGS_CONTROL + 8 * 32 * REGS_EPILOGUE + 4 * 32 * REGS_PRODUCER <= THREADS * REGS_LAUNCH,
+              "setmaxnreg targets exceed the CTA's register allocation: the epilogue's setmaxnreg.inc would block");
 // K stages (of 32) accumulated in one tensor-memory chain before the chunk is drained (default 1;
 // NYB200_CHUNK_STAGES overrides it for experiments, the rounding model follows the value in use).
 static int chunk_stages_cfg() {
@@ -200,7 +207,7 @@ k_umma_tf32x3(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__
     unsigned tmem_base = *tmem_slot;
 
     if (warp < 4) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS_CONTROL));
         if (warp == 0 && lane == 0) {
             // ------------------------------------------------------------ weight producer (TMA)
             unsigned it = 0;
@@ -266,7 +273,7 @@ k_umma_tf32x3(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__
         }
     } else if (warp < 12) {
         // ---------------------------------------------------------------- epilogue (8 warps)
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 184;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS_EPILOGUE));
         int q = warp & 3, half = (warp - 4) >> 2;
         unsigned chunk_it = 0;
         bool dead = false;
@@ -340,7 +347,7 @@ k_umma_tf32x3(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__
         }
     } else {
         // ---------------------------------------------------------------- A producers (split to TF32 hi/lo)
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS_PRODUCER));
         int r = threadIdx.x - 384;  // row of the tile owned by this thread
         unsigned it = 0;
         bool dead = false;
