@@ -238,3 +238,20 @@ def test_entry_point_smoke():
     import __graft_entry__
 
     __graft_entry__.smoke()
+
+
+def test_domain_major_relaxation_with_ragged_column_slab(eng, oracle):
+    """A batch large enough for the domain-major relaxation kernel whose layer width (200) leaves the last
+    128-column slab partly empty: lanes past the row's end must take part in the row reductions with zeros."""
+    wl = W.config_mlp_bab(seed=71, hidden=200, depth=2, n_in=60, eps=0.03, n_fix=3)
+    onet, ospec, nid, rl, ru = _setup(eng, oracle, wl)
+    D = 1100
+    splits, ns = W.draw_domains(wl, rl, ru, D)
+    glo, ghi, ginf = eng.bab_bound_batch(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, splits, ns, mode=1)
+    pick = np.r_[0:40, D - 40:D]
+    olo, ohi, oinf, _ = _oracle_batch(oracle, ospec, wl, rl, ru, splits[pick], ns[pick], 1)
+    assert np.array_equal(ginf[pick].astype(bool), oinf.astype(bool))
+    feas = ~oinf.astype(bool)
+    assert feas.sum() > 40
+    assert _rel(np.concatenate([glo[pick], ghi[pick]], axis=1)[feas], np.concatenate([olo, ohi], axis=1)[feas]) <= REL_TOL
+    eng.release_network(nid)
