@@ -610,6 +610,87 @@ int run_batch(nyb200_engine *e) {
     return NYB200_OK;
 }
 
+// Binary64 re-evaluation of the flagged domains only.  Their inputs (split lists, slopes, boxes) are gathered into
+// a compact sub-batch that runs through the same scratch arrays; the arrays of the full batch that later calls
+// read (bounds, flags, pre-activation bounds, split codes) are saved first, receive the sub-batch's rows, and are
+// put back.
+int refine_subset(nyb200_engine *e, Net &net, BatchPtrs &p) {
+    const Batch &b = e->batch;
+    const NetView &nv = net.v;
+    const int D = b.D, S = b.S;
+    const size_t np = nv.nps;
+    cudaStream_t st = e->stream;
+    std::vector<int> flags((size_t)D), idx;
+    NYB_CUDA(e, cudaMemcpyAsync(flags.data(), p.flags, (size_t)D * 4, cudaMemcpyDeviceToHost, st));
+    NYB_CUDA(e, cudaStreamSynchronize(st));
+    for (int d = 0; d < D; ++d)
+        if ((flags[d] & (kFlagLoose | kFlagLooseFwd)) && !(flags[d] & (kFlagInfeasible | kFlagDegraded | kFlagInvalid))) idx.push_back(d);
+    const int Ds = (int)idx.size();
+    if (Ds == 0) return NYB200_OK;
+    const int ms = b.max_splits > 0 ? b.max_splits : 0;
+    NYB_WS(didx, int *, e, "sub_idx", (size_t)Ds * 4);
+    NYB_WS(keep_lo, float *, e, "keep_out_lo", (size_t)D * S * 4);
+    NYB_WS(keep_hi, float *, e, "keep_out_hi", (size_t)D * S * 4);
+    NYB_WS(keep_fl, int *, e, "keep_flags", (size_t)D * 4);
+    NYB_WS(keep_pl, float *, e, "keep_pre_lo", (size_t)D * np * 4);
+    NYB_WS(keep_pu, float *, e, "keep_pre_hi", (size_t)D * np * 4);
+    NYB_WS(keep_code, signed char *, e, "keep_code", (size_t)D * np);
+    NYB_WS(keep_tab, float4 *, e, "keep_tab", (size_t)D * np * 16);
+    NYB_WS(sub_ns, int *, e, "sub_nsplits", (size_t)Ds * 4);
+    NYB_WS(sub_sp, nyb200_split *, e, "sub_splits", (size_t)Ds * (ms > 0 ? ms : 1) * sizeof(nyb200_split));
+    NYB_CUDA(e, cudaMemcpyAsync(didx, idx.data(), (size_t)Ds * 4, cudaMemcpyHostToDevice, st));
+    NYB_CUDA(e, cudaMemcpyAsync(keep_lo, p.out_lo, (size_t)D * S * 4, cudaMemcpyDeviceToDevice, st));
+    NYB_CUDA(e, cudaMemcpyAsync(keep_hi, p.out_hi, (size_t)D * S * 4, cudaMemcpyDeviceToDevice, st));
+    NYB_CUDA(e, cudaMemcpyAsync(keep_fl, p.flags, (size_t)D * 4, cudaMemcpyDeviceToDevice, st));
+    NYB_CUDA(e, cudaMemcpyAsync(keep_pl, p.pre_lo, (size_t)D * np * 4, cudaMemcpyDeviceToDevice, st));
+    NYB_CUDA(e, cudaMemcpyAsync(keep_pu, p.pre_hi, (size_t)D * np * 4, cudaMemcpyDeviceToDevice, st));
+    NYB_CUDA(e, cudaMemcpyAsync(keep_code, p.code, (size_t)D * np, cudaMemcpyDeviceToDevice, st));
+    NYB_CUDA(e, cudaMemcpyAsync(keep_tab, p.tab, (size_t)D * np * 16, cudaMemcpyDeviceToDevice, st));
+    BatchPtrs ps = p;
+    Batch bs = b;
+    bs.D = Ds;
+    launch_gather_rows(e, sub_ns, p.nsplits, didx, Ds, 1);
+    ps.nsplits = sub_ns;
+    if (ms > 0) {
+        launch_gather_rows(e, sub_sp, p.splits, didx, Ds, (long)ms * (long)(sizeof(nyb200_split) / 4));
+        ps.splits = sub_sp;
+    }
+    if (b.has_alpha) {
+        NYB_WS(sub_alpha, float *, e, "sub_alpha", (size_t)Ds * np * 4);
+        launch_gather_rows(e, sub_alpha, p.alpha, didx, Ds, (long)np);
+        ps.alpha = sub_alpha;
+    }
+    if (b.box_stride) {
+        NYB_WS(sub_lo, float *, e, "sub_in_lo", (size_t)Ds * nv.dims[0] * 4);
+        NYB_WS(sub_hi, float *, e, "sub_in_hi", (size_t)Ds * nv.dims[0] * 4);
+        launch_gather_rows(e, sub_lo, p.in_lo, didx, Ds, nv.dims[0]);
+        launch_gather_rows(e, sub_hi, p.in_hi, didx, Ds, nv.dims[0]);
+        ps.in_lo = sub_lo; ps.in_hi = sub_hi;
+    }
+    e->path = NYB200_PATH_F64;
+    int rc = run_forward(e, net, bs, ps, bs.mode);
+    if (rc == NYB200_OK) rc = run_backward(e, net, bs, ps, nullptr, 0);
+    e->path = NYB200_PATH_TF32X3;
+    NYB_TRY(rc);
+    // rows of the sub-batch go to their places in the saved arrays, which then replace the scratch arrays
+    launch_scatter_rows(e, keep_lo, ps.out_lo, didx, Ds, S);
+    launch_scatter_rows(e, keep_hi, ps.out_hi, didx, Ds, S);
+    launch_scatter_rows(e, keep_fl, ps.flags, didx, Ds, 1);
+    launch_scatter_rows(e, keep_pl, ps.pre_lo, didx, Ds, (long)np);
+    launch_scatter_rows(e, keep_pu, ps.pre_hi, didx, Ds, (long)np);
+    launch_scatter_rows(e, keep_tab, ps.tab, didx, Ds, (long)np * 4);
+    NYB_CUDA(e, cudaMemcpyAsync(p.out_lo, keep_lo, (size_t)D * S * 4, cudaMemcpyDeviceToDevice, st));
+    NYB_CUDA(e, cudaMemcpyAsync(p.out_hi, keep_hi, (size_t)D * S * 4, cudaMemcpyDeviceToDevice, st));
+    NYB_CUDA(e, cudaMemcpyAsync(p.flags, keep_fl, (size_t)D * 4, cudaMemcpyDeviceToDevice, st));
+    NYB_CUDA(e, cudaMemcpyAsync(p.pre_lo, keep_pl, (size_t)D * np * 4, cudaMemcpyDeviceToDevice, st));
+    NYB_CUDA(e, cudaMemcpyAsync(p.pre_hi, keep_pu, (size_t)D * np * 4, cudaMemcpyDeviceToDevice, st));
+    NYB_CUDA(e, cudaMemcpyAsync(p.code, keep_code, (size_t)D * np, cudaMemcpyDeviceToDevice, st));
+    NYB_CUDA(e, cudaMemcpyAsync(p.tab, keep_tab, (size_t)D * np * 16, cudaMemcpyDeviceToDevice, st));
+    launch_min_lower(e, D, S, p.out_lo, p.flags, p.min_lower);
+    NYB_CUDA(e, cudaGetLastError());
+    return NYB200_OK;
+}
+
 // Completes the last run: waits for it and, if the fast path reported domains whose rounding penalty
 // is visible at the requested tolerance, evaluates the batch again with binary64 contractions.
 int finish_batch(nyb200_engine *e) {
@@ -632,10 +713,16 @@ int finish_batch(nyb200_engine *e) {
         NYB_CUDA(e, cudaStreamSynchronize(e->stream));
         e->batch.refined = loose;
     } else if (loose > 0 && e->path == NYB200_PATH_TF32X3 && e->refine_tol > 0.f) {
-        e->path = NYB200_PATH_F64;
-        int st = run_forward(e, *net, e->batch, p, e->batch.mode);
-        if (st == NYB200_OK) st = run_backward(e, *net, e->batch, p, nullptr, 0);
-        e->path = NYB200_PATH_TF32X3;
+        const Batch &b = e->batch;
+        int st;
+        if (2 * loose >= b.D) {  // most of the batch is flagged: evaluate all of it again
+            e->path = NYB200_PATH_F64;
+            st = run_forward(e, *net, b, p, b.mode);
+            if (st == NYB200_OK) st = run_backward(e, *net, b, p, nullptr, 0);
+            e->path = NYB200_PATH_TF32X3;
+        } else {
+            st = refine_subset(e, *net, p);
+        }
         NYB_TRY(st);
         NYB_CUDA(e, cudaStreamSynchronize(e->stream));
         e->batch.refined = loose;

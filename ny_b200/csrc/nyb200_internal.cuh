@@ -20,6 +20,7 @@ constexpr int kFlagInfeasible = 1;  // a split clamp inverted an interval: the d
 constexpr int kFlagDegraded = 2;    // NaN / infinite pre-activation bound: bounds degrade to [-inf, +inf]
 constexpr int kFlagInvalid = 4;     // split entry out of range
 constexpr int kFlagLooseFwd = 8;    // fast-path interval pass: rounding slack visible against an unstable neuron's width
+constexpr int kFlagLoose = 16;      // fast-path backward pass: rounding penalty visible against the bound
 
 // Device-side view of a registered network (passed by value to kernels).
 struct NetView {
@@ -148,7 +149,12 @@ void launch_gemm_f64(nyb200_engine *e, int M, int N, int K, const float *A, int 
                      int ldc, int R, const float *zin_lo, const float *zin_hi, long zin_dstride, double *rpen);
 void launch_concretize(nyb200_engine *e, int M, int R, int S, int n0, const float *A, int lda, const float *in_lo,
                        const float *in_hi, long box_dstride, const double *rb, const double *rabs, const double *rpen,
-                       const int *flags, float *out_lo, float *out_hi, float *min_lower, float loose_tol);
+                       int *flags, float *out_lo, float *out_hi, float *min_lower, float loose_tol);
+// dst row i = src row idx[i] (gather) or dst row idx[i] = src row i (scatter); rows of `row_words` 32-bit words.
+void launch_gather_rows(nyb200_engine *e, void *dst, const void *src, const int *idx, int n_rows, long row_words);
+void launch_scatter_rows(nyb200_engine *e, void *dst, const void *src, const int *idx, int n_rows, long row_words);
+// min over feasible domains and rows of out_lo (the value the concretisation folds), recomputed from scratch
+void launch_min_lower(nyb200_engine *e, int D, int S, const float *out_lo, const int *flags, float *min_lower);
 void launch_select_branch(nyb200_engine *e, const NetView &nv, int D, const float *pre_lo, const float *pre_hi,
                           const signed char *code, int *relu, int *neuron, float *width, int kind);
 void launch_fill_f64(nyb200_engine *e, double *p, size_t n, double v);

@@ -623,7 +623,7 @@ __device__ __forceinline__ void atomic_min_float(float *addr, float v) {
 // the batch on the binary64 path when the count is non-zero, so that the fast path never returns a
 // bound that its own rounding model has visibly loosened.
 __global__ void k_count_loose(int D, int S, int R, const float *__restrict__ out_lo, const float *__restrict__ out_hi,
-                              const double *__restrict__ rpen, const int *__restrict__ flags, float tol,
+                              const double *__restrict__ rpen, int *__restrict__ flags, float tol,
                               int *__restrict__ n_loose) {
     int d = blockIdx.x * blockDim.x + threadIdx.x;
     if (d >= D) return;
@@ -643,7 +643,25 @@ __global__ void k_count_loose(int D, int S, int R, const float *__restrict__ out
         double pl = rpen[(long)d * R + s], pu = rpen[(long)d * R + S + s];
         if (pl > (double)tol * fmaxf(fabsf(l), 0.01f * scale) || pu > (double)tol * fmaxf(fabsf(u), 0.01f * scale)) loose = true;
     }
-    if (loose) atomicAdd(n_loose, 1);
+    if (loose) { atomicAdd(n_loose, 1); flags[d] = f | kFlagLoose; }
+}
+
+// ---------------------------------------------------------------- row gather / scatter (subset re-evaluation)
+__global__ void k_move_rows(unsigned *__restrict__ dst, const unsigned *__restrict__ src, const int *__restrict__ idx,
+                            int n_rows, long row_words, int scatter) {
+    long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= (long)n_rows * row_words) return;
+    long i = t / row_words, w = t - i * row_words;
+    long other = idx[i];
+    if (scatter) dst[other * row_words + w] = src[i * row_words + w];
+    else dst[i * row_words + w] = src[other * row_words + w];
+}
+
+__global__ void k_min_lower(int D, int S, const float *__restrict__ out_lo, const int *__restrict__ flags,
+                            float *__restrict__ min_lower) {
+    int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= D * S) return;
+    if (!(flags[t / S] & kFlagInfeasible)) atomic_min_float(min_lower, out_lo[t]);
 }
 
 // Per (domain, spec row): apply the domain flags and the reference's repair rule
@@ -860,7 +878,7 @@ void launch_gemm_f64(nyb200_engine *e, int M, int N, int K, const float *A, int 
 
 void launch_concretize(nyb200_engine *e, int M, int R, int S, int n0, const float *A, int lda, const float *in_lo,
                        const float *in_hi, long box_dstride, const double *rb, const double *rabs, const double *rpen,
-                       const int *flags, float *out_lo, float *out_hi, float *min_lower, float loose_tol) {
+                       int *flags, float *out_lo, float *out_hi, float *min_lower, float loose_tol) {
     long threads = (long)M * 32;
     k_concretize<<<(unsigned)((threads + 255) / 256), 256, 0, e->stream>>>(M, R, S, n0, A, lda, in_lo, in_hi, box_dstride,
                                                                            rb, rabs, rpen, out_lo, out_hi);
@@ -872,6 +890,27 @@ void launch_concretize(nyb200_engine *e, int M, int R, int S, int n0, const floa
         NYB_COUNT(e);
     }
     k_finalize<<<(D * S + 255) / 256, 256, 0, e->stream>>>(D, S, flags, out_lo, out_hi, min_lower);
+    NYB_COUNT(e);
+}
+
+void launch_gather_rows(nyb200_engine *e, void *dst, const void *src, const int *idx, int n_rows, long row_words) {
+    long tot = (long)n_rows * row_words;
+    if (tot == 0) return;
+    k_move_rows<<<(unsigned)((tot + 255) / 256), 256, 0, e->stream>>>((unsigned *)dst, (const unsigned *)src, idx, n_rows, row_words, 0);
+    NYB_COUNT(e);
+}
+
+void launch_scatter_rows(nyb200_engine *e, void *dst, const void *src, const int *idx, int n_rows, long row_words) {
+    long tot = (long)n_rows * row_words;
+    if (tot == 0) return;
+    k_move_rows<<<(unsigned)((tot + 255) / 256), 256, 0, e->stream>>>((unsigned *)dst, (const unsigned *)src, idx, n_rows, row_words, 1);
+    NYB_COUNT(e);
+}
+
+void launch_min_lower(nyb200_engine *e, int D, int S, const float *out_lo, const int *flags, float *min_lower) {
+    static const float inf_word = INFINITY;
+    cudaMemcpyAsync(min_lower, &inf_word, 4, cudaMemcpyHostToDevice, e->stream);
+    k_min_lower<<<(unsigned)((D * S + 255) / 256), 256, 0, e->stream>>>(D, S, out_lo, flags, min_lower);
     NYB_COUNT(e);
 }
 

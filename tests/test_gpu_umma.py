@@ -149,3 +149,50 @@ def test_narrow_box_triggers_binary64_rerun(eng, oracle):
     finally:
         eng.set_refine_tolerance(5e-5)
     eng.release_network(nid)
+
+
+def test_partial_rerun_touches_only_flagged_domains(eng, oracle):
+    """A batch with a shared wide box where only some domains are narrow enough... is not constructible with one
+    box, so the mix is built with per-domain boxes: a few cells of a wide box shrunk to slivers.  Only those are
+    re-evaluated with binary64 contractions; every domain must agree with the oracle, and the ones that were not
+    flagged must be bit-identical to a run with the re-evaluation switched off."""
+    wl = W.config_mlp_bab(seed=72, hidden=96, depth=3, n_in=48, eps=0.05, n_fix=0)
+    onet = oracle.Net(wl.net.weights, wl.net.biases)
+    ospec = onet.with_spec(wl.spec)
+    nid = eng.register_network(wl.net)
+    rl, ru = oracle.ibp_forward(onet, wl.in_lo, wl.in_hi)
+    lo, hi = W.draw_input_cells(wl, 7)          # 128 cells
+    D = lo.shape[0]
+    narrow = np.arange(0, D, 9)
+    mid = (lo[narrow].astype(np.float64) + hi[narrow]) / 2
+    lo[narrow] = (mid - 1e-5 * (hi[narrow] - lo[narrow])).astype(np.float32)
+    hi[narrow] = (mid + 1e-5 * (hi[narrow] - mid)).astype(np.float32)
+    from ny_b200 import SPLIT_DTYPE
+    sp0, ns = np.zeros((D, 0), SPLIT_DTYPE), np.zeros(D, np.int32)
+    eng.batch_upload(nid, wl.spec, lo, hi, rl, ru, sp0, ns, mode=1)
+    eng.set_refine_tolerance(0.0)
+    try:
+        eng.batch_run()
+        flo, fhi, _ = eng.batch_download()
+    finally:
+        eng.set_refine_tolerance(5e-5)
+    eng.batch_run()
+    glo, ghi, ginf = eng.batch_download()
+    refined = eng.batch_refined()
+    assert 0 < refined < D // 2, refined
+    changed = np.any(glo != flo, axis=1) | np.any(ghi != fhi, axis=1)
+    assert 0 < changed.sum() <= refined
+    assert np.all(np.isin(np.flatnonzero(changed), narrow))       # only slivers were re-evaluated
+    S = wl.spec.shape[0]
+    rl2 = np.concatenate([rl, np.full(S, -np.inf, np.float32)])
+    ru2 = np.concatenate([ru, np.full(S, np.inf, np.float32)])
+    for d in list(narrow[:6]) + [1, 2, D - 1]:
+        pl, pu, bad = oracle.domain_bounds(ospec, lo[d], hi[d], rl2, ru2, sp0[d], 1)
+        olo, ohi = oracle.beta_crown_bound(ospec, lo[d], hi[d], pl, pu, sp0[d])
+        both = np.concatenate([olo, ohi])
+        den = np.maximum(np.abs(both), 1e-2 * np.abs(both).max())
+        assert np.max(np.abs(np.concatenate([glo[d], ghi[d]]) - both) / den) <= 1e-4, d
+    pl_all, pu_all = eng.batch_download_pre_bounds()
+    assert np.all(pl_all <= pu_all)
+    assert np.isclose(eng.batch_min_lower(), glo[ginf == 0].min())
+    eng.release_network(nid)
