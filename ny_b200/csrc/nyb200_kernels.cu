@@ -628,7 +628,7 @@ __global__ void k_count_loose(int D, int S, int R, const float *__restrict__ out
     int d = blockIdx.x * blockDim.x + threadIdx.x;
     if (d >= D) return;
     const int f = flags[d];
-    if (f & ~kFlagLooseFwd) return;  // infeasible / degraded / invalid domains are not re-evaluated
+    if (f & ~(kFlagLooseFwd | kFlagLoose)) return;  // infeasible / degraded / invalid domains are not re-evaluated
     if (f & kFlagLooseFwd) { atomicAdd(n_loose, 1); return; }
     float scale = 0.f;
     for (int s = 0; s < S; ++s) {
