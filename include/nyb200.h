@@ -255,6 +255,19 @@ int32_t nyb200_pgd_attack(nyb200_engine *e, int32_t net_id, const float *spec, i
                           const float *in_hi, const float *x0, int32_t K, const nyb200_pgd_config *cfg,
                           float *best_margin, float *best_x, int32_t *counterexample);
 
+/* ---- verdicts of the last run ------------------------------------------------------------------
+ * Per domain, lower mode (the property holds where every spec row stays above `threshold`), with the reference's
+ * predicates (domain_is_verified_for_mode / domain_is_violation_for_mode,
+ * crates/ny-propagate/src/beta_crown/config/beta_config.rs:1552-1610): VERIFIED when every row has finite,
+ * non-inverted bounds and lower > threshold (strict); VIOLATED when some row has finite, non-inverted bounds and
+ * upper < threshold; INFEASIBLE for an empty domain; UNKNOWN otherwise (a non-finite threshold verifies and
+ * violates nothing). */
+#define NYB200_VERDICT_UNKNOWN 0
+#define NYB200_VERDICT_VERIFIED 1
+#define NYB200_VERDICT_VIOLATED 2
+#define NYB200_VERDICT_INFEASIBLE 3
+int32_t nyb200_batch_verdicts(nyb200_engine *e, float threshold, int32_t *status);
+
 /* ---- interval forward pass of ONE box without any device allocation ------------------------------
  * No counterpart in the reference: an addition for hosts that cannot let a library allocate device
  * memory at call time (a service that gave the whole GPU to its own arena at start-up, or a BaB loop

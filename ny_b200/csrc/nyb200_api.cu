@@ -829,6 +829,24 @@ int32_t nyb200_batch_download_pre_bounds(nyb200_engine *e, float *pre_lo, float 
     return NYB200_OK;
 }
 
+int32_t nyb200_batch_verdicts(nyb200_engine *e, float threshold, int32_t *status) {
+    if (!e || !status) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    NYB_CUDA(e, cudaSetDevice(e->device));
+    NYB_TRY(finish_batch(e));
+    Net *net;
+    NYB_TRY(find_net(e, e->batch.net_id, &net));
+    BatchPtrs p;
+    NYB_TRY(batch_ptrs(e, *net, e->batch, p));
+    int D = e->batch.D;
+    NYB_WS(ds, int *, e, "verdicts", (size_t)D * 4);
+    launch_verdicts(e, D, e->batch.S, p.out_lo, p.out_hi, p.flags, threshold, ds);
+    NYB_CUDA(e, cudaGetLastError());
+    NYB_CUDA(e, cudaMemcpyAsync(status, ds, (size_t)D * 4, cudaMemcpyDeviceToHost, e->stream));
+    NYB_CUDA(e, cudaStreamSynchronize(e->stream));
+    return NYB200_OK;
+}
+
 int32_t nyb200_batch_select_branch(nyb200_engine *e, int32_t *relu, int32_t *neuron, float *width) {
     return nyb200_batch_select_branch_scored(e, NYB200_BRANCH_WIDTH, relu, neuron, width);
 }

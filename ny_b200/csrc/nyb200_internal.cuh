@@ -150,6 +150,8 @@ void launch_gemm_f64(nyb200_engine *e, int M, int N, int K, const float *A, int 
 void launch_concretize(nyb200_engine *e, int M, int R, int S, int n0, const float *A, int lda, const float *in_lo,
                        const float *in_hi, long box_dstride, const double *rb, const double *rabs, const double *rpen,
                        int *flags, float *out_lo, float *out_hi, float *min_lower, float loose_tol);
+void launch_verdicts(nyb200_engine *e, int D, int S, const float *out_lo, const float *out_hi, const int *flags,
+                     float threshold, int *status);
 // dst row i = src row idx[i] (gather) or dst row idx[i] = src row i (scatter); rows of `row_words` 32-bit words.
 void launch_gather_rows(nyb200_engine *e, void *dst, const void *src, const int *idx, int n_rows, long row_words);
 void launch_scatter_rows(nyb200_engine *e, void *dst, const void *src, const int *idx, int n_rows, long row_words);

@@ -646,6 +646,26 @@ __global__ void k_count_loose(int D, int S, int R, const float *__restrict__ out
     if (loose) { atomicAdd(n_loose, 1); flags[d] = f | kFlagLoose; }
 }
 
+// ---------------------------------------------------------------- verdicts
+// Per domain, lower mode (every spec row must stay above the threshold): verified when every row passes
+// domain_is_verified_for_mode (all of lower, upper, threshold finite, lower <= upper, lower > threshold: strict);
+// violated when some row passes domain_is_violation_for_mode (finite, not inverted, upper < threshold)
+// (beta_crown/config/beta_config.rs:1552-1610).  Infeasible domains are reported as such.
+__global__ void k_verdicts(int D, int S, const float *__restrict__ out_lo, const float *__restrict__ out_hi,
+                           const int *__restrict__ flags, float threshold, int *__restrict__ status) {
+    int d = blockIdx.x * blockDim.x + threadIdx.x;
+    if (d >= D) return;
+    if (flags[d] & kFlagInfeasible) { status[d] = NYB200_VERDICT_INFEASIBLE; return; }
+    bool all_verified = isfinite(threshold), any_violated = false;
+    for (int s = 0; s < S; ++s) {
+        float l = out_lo[d * S + s], u = out_hi[d * S + s];
+        bool sane = isfinite(l) && isfinite(u) && isfinite(threshold);
+        if (!(sane && l <= u && l > threshold)) all_verified = false;
+        if (sane && l <= u && u < threshold) any_violated = true;
+    }
+    status[d] = all_verified ? NYB200_VERDICT_VERIFIED : (any_violated ? NYB200_VERDICT_VIOLATED : NYB200_VERDICT_UNKNOWN);
+}
+
 // ---------------------------------------------------------------- row gather / scatter (subset re-evaluation)
 __global__ void k_move_rows(unsigned *__restrict__ dst, const unsigned *__restrict__ src, const int *__restrict__ idx,
                             int n_rows, long row_words, int scatter) {
@@ -890,6 +910,12 @@ void launch_concretize(nyb200_engine *e, int M, int R, int S, int n0, const floa
         NYB_COUNT(e);
     }
     k_finalize<<<(D * S + 255) / 256, 256, 0, e->stream>>>(D, S, flags, out_lo, out_hi, min_lower);
+    NYB_COUNT(e);
+}
+
+void launch_verdicts(nyb200_engine *e, int D, int S, const float *out_lo, const float *out_hi, const int *flags,
+                     float threshold, int *status) {
+    k_verdicts<<<(unsigned)((D + 255) / 256), 256, 0, e->stream>>>(D, S, out_lo, out_hi, flags, threshold, status);
     NYB_COUNT(e);
 }
 

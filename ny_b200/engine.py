@@ -39,6 +39,7 @@ EXPORTS = [
     "nyb200_timing_read", "nyb200_batch_optimize", "nyb200_batch_download_params",
     "nyb200_net_create_layers", "nyb200_pgd_attack", "nyb200_batch_select_branch_scored",
     "nyb200_crown_bounds", "nyb200_batch_download_alpha_upper",
+    "nyb200_batch_verdicts",
 ]
 
 
@@ -94,6 +95,7 @@ def load_library():
     L.nyb200_batch_min_lower.argtypes = [vp, fp]
     L.nyb200_batch_min_lower_device.argtypes = [vp, C.POINTER(vp)]
     L.nyb200_batch_download_pre_bounds.argtypes = [vp, fp, fp]
+    L.nyb200_batch_verdicts.argtypes = [vp, C.c_float, ip]
     L.nyb200_batch_select_branch.argtypes = [vp, ip, ip, fp]
     L.nyb200_batch_select_branch_scored.argtypes = [vp, C.c_int32, ip, ip, fp]
     L.nyb200_timing_enable.argtypes = [vp, C.c_int32]
@@ -473,6 +475,13 @@ class B200Engine:
         pl, pu = np.empty((D, n_pre), np.float32), np.empty((D, n_pre), np.float32)
         self._check(self._L.nyb200_batch_download_pre_bounds(self._h, _fp(pl), _fp(pu)))
         return pl, pu
+
+    def batch_verdicts(self, threshold: float = 0.0) -> np.ndarray:
+        """Per-domain verdict of the last run: 0 unknown, 1 verified, 2 violated, 3 infeasible."""
+        D = self._batch_shape[0]
+        st = np.empty(D, np.int32)
+        self._check(self._L.nyb200_batch_verdicts(self._h, threshold, _ip(st)))
+        return st
 
     def batch_select_branch(self, kind: int = 0):
         """kind 0: largest width (sequential engine); 1: intercept score (batched graph engine)."""

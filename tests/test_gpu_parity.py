@@ -175,6 +175,17 @@ def test_branching_matches_oracle_and_min_lower(eng, oracle):
     r1, j1, w1 = eng.batch_select_branch(kind=1)
     feas = ginf == 0
     assert np.isclose(eng.batch_min_lower(), glo[feas].min())
+    # verdicts with the reference's predicates, at thresholds that split the batch
+    L = oracle.lib()
+    for thr in (0.0, float(np.median(glo[feas].min(axis=1))), float(np.median(ghi[feas].max(axis=1))), float("inf")):
+        st = eng.batch_verdicts(thr)
+        for d in range(40):
+            if ginf[d]:
+                assert st[d] == 3
+                continue
+            ver = all(L.nyo_domain_verified(float(glo[d][s]), float(ghi[d][s]), thr) for s in range(glo.shape[1]))
+            vio = any(L.nyo_domain_violated(float(glo[d][s]), float(ghi[d][s]), thr) for s in range(glo.shape[1]))
+            assert st[d] == (1 if ver else (2 if vio else 0)), (thr, d)
     for d in range(40):
         if ginf[d]:
             continue
