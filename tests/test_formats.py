@@ -1,0 +1,91 @@
+"""NNet and VNN-LIB readers (CPU only)."""
+import numpy as np
+import pytest
+
+from ny_b200 import EngineError, formats
+
+# The |x| network of the reference's quick-start (tests/models/crossing_relu.nnet: 1 -> 2 -> 1, weights (1, -1) then
+# (1, 1), no biases), written out in the NNet layout.
+ABS_NNET = """// NNet format - f(x) = |x|
+2,1,1,2,
+1,2,1,
+0,
+0.0,
+1.0,
+0.0,
+1.0,
+1.0,
+-1.0,
+0.0,
+0.0,
+1.0,1.0,
+0.0,
+"""
+
+
+def test_nnet_abs_network():
+    n = formats.parse_nnet(ABS_NNET)
+    assert n.layer_sizes == [1, 2, 1]
+    assert np.array_equal(n.weights[0], [[1.0], [-1.0]]) and np.array_equal(n.weights[1], [[1.0, 1.0]])
+    assert np.array_equal(n.biases[0], [0.0, 0.0]) and np.array_equal(n.biases[1], [0.0])
+    assert n.output_mean == 0.0 and n.output_range == 1.0      # means / ranges lines without the output entry
+    net = n.to_network()
+    assert net.dims.tolist() == [1, 2, 1]
+
+
+def test_nnet_round_trip_and_errors():
+    g = np.random.Generator(np.random.PCG64(1))
+    ws = [g.standard_normal((7, 5)).astype(np.float32), g.standard_normal((3, 7)).astype(np.float32)]
+    bs = [g.standard_normal(7).astype(np.float32), g.standard_normal(3).astype(np.float32)]
+    n = formats.parse_nnet(formats.write_nnet(ws, bs))
+    assert all(np.array_equal(a, b) for a, b in zip(n.weights, ws)) and all(np.array_equal(a, b) for a, b in zip(n.biases, bs))
+    with pytest.raises(EngineError):
+        formats.parse_nnet("2,1,1,\n")                                  # short header
+    with pytest.raises(EngineError):
+        formats.parse_nnet("1,2,1,2,\n2,1,\n0,\n0,0,\n1,1,\n0,0,0,\n1,1,1,\n1.0,\n0.0,\n")   # short weight row
+    with pytest.raises(EngineError):
+        formats.parse_nnet(ABS_NNET.rsplit("\n", 2)[0])                    # missing last bias
+
+
+def test_vnnlib_box_and_single_atom():
+    text = """; violation: the output reaches 2.0 or above
+(declare-const X_0 Real)
+(declare-const Y_0 Real)
+(assert (>= X_0 -1.0))
+(assert (<= X_0 1.0))
+(assert (>= Y_0 2.0))
+"""
+    p = formats.parse_vnnlib(text, 1, 1)
+    assert p.in_lo.tolist() == [-1.0] and p.in_hi.tolist() == [1.0]
+    assert len(p.violation) == 1 and len(p.violation[0]) == 1
+    a = p.violation[0][0]
+    assert a.c.tolist() == [1.0] and a.d == -2.0                       # Y_0 - 2 >= 0
+
+
+def test_vnnlib_and_or_relations():
+    text = """(declare-const X_0 Real)(declare-const X_1 Real)(declare-const Y_0 Real)(declare-const Y_1 Real)(declare-const Y_2 Real)
+(assert (and (>= X_0 0.1) (<= X_0 0.2)))
+(assert (<= 0.3 X_1)) (assert (>= 0.4 X_1))
+(assert (or (and (>= Y_0 Y_1) (>= Y_0 Y_2)) (<= Y_1 -1.5)))
+"""
+    p = formats.parse_vnnlib(text, 2, 3)
+    assert np.allclose(p.in_lo, [0.1, 0.3]) and np.allclose(p.in_hi, [0.2, 0.4])
+    assert np.all(p.in_lo.astype(np.float64) <= [0.1, 0.3]) and np.all(p.in_hi.astype(np.float64) >= [0.2, 0.4])  # outward
+    assert len(p.violation) == 2 and len(p.violation[0]) == 2 and len(p.violation[1]) == 1
+    assert p.violation[0][0].c.tolist() == [1, -1, 0] and p.violation[0][1].c.tolist() == [1, 0, -1]
+    assert p.violation[1][0].c.tolist() == [0, -1, 0] and p.violation[1][0].d == -1.5      # -Y_1 - 1.5 >= 0
+
+
+def test_vnnlib_rejections():
+    decl = "(declare-const X_0 Real)(declare-const Y_0 Real)"
+    with pytest.raises(EngineError):
+        formats.parse_vnnlib(decl + "(assert (>= X_0 0.0))(assert (>= Y_0 1.0))", 1, 1)       # no upper bound on X_0
+    with pytest.raises(EngineError):
+        formats.parse_vnnlib(decl + "(assert (>= X_0 1.0))(assert (<= X_0 0.0))", 1, 1)       # empty box
+    with pytest.raises(EngineError) as ei:
+        formats.parse_vnnlib(decl + "(assert (>= X_0 0))(assert (<= X_0 1))(assert (>= (+ Y_0 1.0) 2.0))", 1, 1)
+    assert ei.value.code == 1                                                                   # declined, not mis-read
+    with pytest.raises(EngineError):
+        formats.parse_vnnlib(decl + "(assert (>= X_0 0))(assert (<= X_0 1))(assert (>= Y_3 2.0))", 1, 1)
+    with pytest.raises(EngineError):
+        formats.parse_vnnlib("(assert (>= X_0 0)", 1, 1)
