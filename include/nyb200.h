@@ -268,6 +268,50 @@ int32_t nyb200_pgd_attack(nyb200_engine *e, int32_t net_id, const float *spec, i
 #define NYB200_VERDICT_INFEASIBLE 3
 int32_t nyb200_batch_verdicts(nyb200_engine *e, float threshold, int32_t *status);
 
+/* ---- stand-alone operators of the GemmEngine trait ------------------------------------------------
+ * nyb200_gemm_f64 replaces GemmEngine::gemm_f64 (crates/ny-core/src/gemm.rs:356): C = A B for row-major binary64
+ * matrices, host buffers, every output element one chain of fused multiply-adds over k in increasing order
+ * (deterministic; |error| <= gamma_k |A||B|).
+ * nyb200_conv_transpose_2d replaces GemmEngine::conv_transpose_2d (gemm.rs:556; parameters
+ * ConvTranspose2dParams, gemm.rs:150-177): the Conv2d CROWN backward of one group.  a_reshaped is
+ * [(num_specs*out_h*out_w) x out_channels] row-major, weight_col [out_channels x (in_channels*kernel_h*kernel_w)],
+ * out [num_specs x (in_channels*in_h*in_w)].  The product and the col2im scatter run as one device pass; every
+ * output element is accumulated in binary64 and rounded to fp32 once. */
+int32_t nyb200_gemm_f64(nyb200_engine *e, int32_t m, int32_t k, int32_t n, const double *a, const double *b,
+                        double *c_out);
+typedef struct nyb200_conv_transpose_params {
+    int32_t num_specs, out_channels, in_channels, out_h, out_w, in_h, in_w;
+    int32_t kernel_h, kernel_w, stride_h, stride_w, pad_h, pad_w;
+} nyb200_conv_transpose_params;
+int32_t nyb200_conv_transpose_2d(nyb200_engine *e, const float *a_reshaped, const float *weight_col,
+                                 const nyb200_conv_transpose_params *params, float *out);
+
+/* ---- cooperative deadline (GpuCrownBackward::set_crown_backward_deadline, gemm.rs:4260-4279) ------
+ * ns_from_now >= 0 arms a deadline that many nanoseconds after the call (monotonic clock); a negative value
+ * clears it.  While armed, every multi-launch call (interval pass, backward pass, CROWN-IBP collection,
+ * optimisation, attack) polls the clock between its units of work (one layer, one iteration, one step); past the
+ * deadline it stops enqueuing, waits for the stream, invalidates the run's results and returns
+ * NYB200_ERR_DEADLINE.  A launch in flight is never interrupted.  The caller clears the deadline afterwards. */
+int32_t nyb200_set_deadline_ns(nyb200_engine *e, int64_t ns_from_now);
+
+/* ---- joint gradient of the uploaded batch (crown_joint_alpha_gradient_resident, gemm.rs:4095;
+ * crown_backward_gpu_resnet_sound_beta_batched_grad, gemm.rs:3999) --------------------------------
+ * One bound evaluation at the batch's current parameters plus the adjoint pass, no parameter update.
+ * objective 0: gradient of the sum of every domain's lower bounds; 1: of the domain's smallest lower bound.
+ * grad [D x n_pre]: for an unstable unsplit neuron d(objective)/d(alpha); for a split neuron
+ * d(objective)/d(beta) of its multiplier (beta >= 0); zero elsewhere.  The bounds of that evaluation are then
+ * available through nyb200_batch_download. */
+int32_t nyb200_batch_gradient(nyb200_engine *e, int32_t objective, float *grad);
+
+/* ---- exact point gradients for K attack restarts (crown_point_vjp_batched[_resnet], gemm.rs:4207,4246) ----
+ * grads[k] = spec_rows[k] . d f / d x at restart k, with the ReLU derivative taken from 0/1 masks.
+ * Exactly one of x [K x dims[0]] (the masks are those of the concrete forward pass at x, [pre > 0]) and
+ * masks [K x n_pre] (caller-supplied, a value > 0 passes the gradient; the last dims[L] entries of a row are
+ * ignored) is non-NULL.  spec_rows [K x dims[L]], grads [K x dims[0]]; values [K] (optional, only with x)
+ * receives spec_rows[k] . f(x_k).  Attack-only arithmetic: it never enters a bound. */
+int32_t nyb200_point_vjp_batched(nyb200_engine *e, int32_t net_id, int32_t K, const float *x, const float *masks,
+                                 const float *spec_rows, float *grads, float *values);
+
 /* ---- interval forward pass of ONE box without any device allocation ------------------------------
  * No counterpart in the reference: an addition for hosts that cannot let a library allocate device
  * memory at call time (a service that gave the whole GPU to its own arena at start-up, or a BaB loop

@@ -391,6 +391,7 @@ int run_forward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int fw
     if (fwd_mode != 2 && b.max_splits > 0)
         launch_scatter_splits(e, nv, p.splits, p.nsplits, b.max_splits, D, p.code, p.sbeta, p.flags);
     for (int k = 0; k < nv.L; ++k) {
+        NYB_DEADLINE(e, "interval pass");
         const float *zl, *zu;
         long in_ds;
         int Deff;
@@ -480,6 +481,7 @@ int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, float
     launch_relax(e, nv, -1, L - 1, M, R, S, cur, p.lda, p.tab, p.zabs, p.q, q_ds(L - 1), eps_for(L - 1), p.rb,
                      p.rabs, p.rpen, nullptr, 0);
     for (int k = L - 1; k >= 0; --k) {
+        NYB_DEADLINE(e, "backward pass");
         int K = nv.dims[k + 1], N = nv.dims[k];
         const float *zin_lo, *zin_hi;
         long zin_ds;

@@ -102,6 +102,7 @@ struct nyb200_engine {
     std::map<int, nyb::Net> nets;
     int next_net = 1;
     int64_t launches = 0;
+    int64_t deadline_ns = -1;  // monotonic-clock deadline of the cooperative cancellation, or -1
     nyb::Batch batch;
     nyb::Timing timing;
     std::map<std::string, nyb::DevBuf> ws;  // named grow-only device workspace
@@ -196,7 +197,14 @@ int crown_bounds(nyb200_engine *e, int net_id, const float *spec, int S, const f
                  int box_stride, int D, float *out_lo, float *out_hi, float *inter_lo, float *inter_hi);
 
 // ---- parameter optimisation (nyb200_optimize.cu) ----
-int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg);
+// grad_host != nullptr: one evaluation plus the adjoint pass, gradients [D x n_pre] to the host, no update
+int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg, float *grad_host = nullptr);
+// Cooperative cancellation: true once the armed deadline has passed.
+bool deadline_passed(const nyb200_engine *e);
+// What a multi-launch call does when the deadline has passed: drain the stream, drop the run, report.
+int deadline_abort(nyb200_engine *e, const char *where);
+#define NYB_DEADLINE(e, where) \
+    do { if (nyb::deadline_passed(e)) return nyb::deadline_abort((e), (where)); } while (0)
 int refine_optimized(nyb200_engine *e, Net &net, Batch &b, BatchPtrs &p);
 int download_params(nyb200_engine *e, float *alpha, float *beta);
 

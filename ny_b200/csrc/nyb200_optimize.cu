@@ -16,6 +16,8 @@
 //      the one thread that owns its (domain, neuron) pair.
 // The gradient only proposes the next parameters; its arithmetic carries no rounding bookkeeping.  Every
 // bound that is ever reported comes from step 1.
+#include <string.h>
+
 #include "nyb200_internal.cuh"
 
 namespace nyb {
@@ -65,7 +67,7 @@ k_adjoint_relu(int n, int off, int D, int S, int R, int Zr, long nps, float *__r
                const signed char *__restrict__ code, const float *__restrict__ pre_lo,
                const float *__restrict__ pre_hi, float *__restrict__ mom, float *__restrict__ var,
                const int *__restrict__ only_row, float *__restrict__ aup, float *__restrict__ mom_up,
-               float *__restrict__ var_up, AdamStep h) {
+               float *__restrict__ var_up, float *__restrict__ grad_out, AdamStep h) {
     long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= (long)D * n) return;
     int d = (int)(t / n), i = (int)(t % n);
@@ -108,6 +110,8 @@ k_adjoint_relu(int n, int off, int D, int S, int R, int Zr, long nps, float *__r
             aup[o] = a; mom_up[o] = m; var_up[o] = v;
         }
     }
+    if (grad_out)  // export: the slope's gradient of an unstable unsplit neuron, the multiplier's of a split one
+        grad_out[o] = ((c == 0) && (l < 0.f) && (u > 0.f)) ? g_alpha : (c != 0 ? (c > 0 ? -g_sum : g_sum) : 0.f);
     bool is_alpha = (c == 0) && (l < 0.f) && (u > 0.f) && h.lr_alpha > 0.f;
     bool is_beta = (c != 0) && h.lr_beta > 0.f;
     if (!is_alpha && !is_beta) return;
@@ -245,8 +249,10 @@ int conv_forward_tensor(nyb200_engine *e, Net &net, int k, int rows, const float
     return NYB200_OK;
 }
 
-int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg) {
+int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg, float *grad_host) {
     if (!e->batch.valid) return set_err(e, NYB200_ERR_INVALID, "no batch uploaded");
+    if (grad_host && (cfg.objective == 2 || cfg.iterations != 2))
+        return set_err(e, NYB200_ERR_INVALID, "gradient export: objective 0 or 1");
     if (cfg.iterations < 1) return set_err(e, NYB200_ERR_INVALID, "iterations must be >= 1");
     if (cfg.objective < 0 || cfg.objective > 2) return set_err(e, NYB200_ERR_INVALID, "objective must be 0, 1 or 2");
     if (!(cfg.lr_alpha >= 0.f) || !(cfg.lr_beta >= 0.f) || !(cfg.lr_decay > 0.f))
@@ -304,6 +310,12 @@ int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg) {
         if (!derr) return NYB200_ERR_OOM;
         NYB_CUDA(e, cudaMemsetAsync(derr, 0, 4, e->stream));
     }
+    float *grad_dev = nullptr;
+    if (grad_host) {
+        grad_dev = (float *)ws_get(e, "par_grad", (size_t)D * np * 4);
+        if (!grad_dev) return NYB200_ERR_OOM;
+        NYB_CUDA(e, cudaMemsetAsync(grad_dev, 0, (size_t)D * np * 4, e->stream));
+    }
 
     Timing &tm = e->timing;
     fold_timing(tm);
@@ -318,6 +330,7 @@ int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg) {
     const long nres = (long)D * S;
     const unsigned gres = (unsigned)((nres + 255) / 256);
     for (int t = 1; t <= T; ++t) {
+        NYB_DEADLINE(e, "optimisation");
         const bool last = (t == T);
         NYB_TRY(run_backward(e, *net, b, p, last ? nullptr : ckpt.data(), ldc));
         k_fold_best<<<gres, 256, 0, e->stream>>>(nres, t == 1, p.out_lo, p.out_hi, best_lo, best_hi);
@@ -354,7 +367,7 @@ int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg) {
             long nt = (long)D * N;
             k_adjoint_relu<<<(unsigned)((nt + 255) / 256), 256, 0, e->stream>>>(N, nv.pre_off[k], D, S, R, Zr, np, zn, ldz, nv.b[k],
                                                                                ckpt[k], ldc, p.tab, p.code, p.pre_lo,
-                                                                               p.pre_hi, mom, var, only_row, p.alpha_up, mom_up, var_up, h);
+                                                                               p.pre_hi, mom, var, only_row, p.alpha_up, mom_up, var_up, grad_dev, h);
             e->launches++;
             bool opens = false;  // is this layer's post-activation adjoint skipped forward to a later layer?
             for (int kk = k + 2; kk < L - 1; ++kk) opens |= net->skip_of(kk) == k;
@@ -365,6 +378,7 @@ int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg) {
             }
             float *tmp = zc; zc = zn; zn = tmp;
         }
+        if (grad_host) break;  // gradient export: one evaluation and its adjoint, no second pass
     }
     static const float inf_word = INFINITY;
     NYB_CUDA(e, cudaMemcpyAsync(p.min_lower, &inf_word, 4, cudaMemcpyHostToDevice, e->stream));
@@ -377,6 +391,15 @@ int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg) {
     b.finished = false;
     b.optimized = true;
     b.refined = 0;
+    if (grad_host) {
+        if (L >= 2) {
+            NYB_CUDA(e, cudaMemcpy2DAsync(grad_host, (size_t)nv.n_pre * 4, grad_dev, (size_t)np * 4, (size_t)nv.n_pre * 4, (size_t)D,
+                                          cudaMemcpyDeviceToHost, e->stream));
+            NYB_CUDA(e, cudaStreamSynchronize(e->stream));
+        } else {
+            memset(grad_host, 0, (size_t)D * nv.n_pre * 4);
+        }
+    }
     return NYB200_OK;
 }
 
@@ -458,6 +481,18 @@ int32_t nyb200_batch_optimize(nyb200_engine *e, const nyb200_opt_config *cfg) {
     cudaError_t st = cudaSetDevice(e->device);
     if (st != cudaSuccess) return nyb::check_cuda(e, st, "cudaSetDevice");
     return nyb::optimize_batch(e, *cfg);
+}
+
+int32_t nyb200_batch_gradient(nyb200_engine *e, int32_t objective, float *grad) {
+    if (!e || !grad) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    cudaError_t st = cudaSetDevice(e->device);
+    if (st != cudaSuccess) return nyb::check_cuda(e, st, "cudaSetDevice");
+    nyb200_opt_config cfg = {};
+    cfg.iterations = 2;  // one evaluation with checkpoints and its adjoint; the second evaluation is skipped
+    cfg.lr_decay = 1.f;
+    cfg.objective = objective;
+    return nyb::optimize_batch(e, cfg, grad);
 }
 
 int32_t nyb200_batch_download_params(nyb200_engine *e, float *alpha, float *beta) {

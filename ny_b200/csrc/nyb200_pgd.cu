@@ -114,6 +114,17 @@ __global__ void k_add_rows(long rows, int n, float *__restrict__ Y, int ldy, con
     Y[r * ldy + j] += X[r * ldx + j];
 }
 
+// out[r] = X[r, :] . Y[r, :], one warp per row, binary64 accumulation
+__global__ void k_row_dot(int rows, int n, const float *__restrict__ X, int ldx, const float *__restrict__ Y, int ldy,
+                          float *__restrict__ out) {
+    int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= rows) return;
+    double acc = 0.0;
+    for (int j = lane; j < n; j += 32) acc = fma((double)X[(long)warp * ldx + j], (double)Y[(long)warp * ldy + j], acc);
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) out[warp] = (float)acc;
+}
+
 __global__ void k_fill_f32(float *p, long n, float v) {
     long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (t < n) p[t] = v;
@@ -144,6 +155,60 @@ static int pgd_forward(nyb200_engine *e, Net &net, bool tensor, int rows, const 
         cur = act[k];
         ldc = ld;
     }
+    return NYB200_OK;
+}
+
+// Exact gradient chain of K rows: G_k = (G_{k+1} . [mask_k > 0]) W_k from the output down to the input, where
+// mask_k is act[k] (a concrete forward pass's activations, or caller-supplied 0/1 masks).  G0 holds the output
+// cotangents on entry; *result points at the buffer (G0 or G1) that holds the input gradients.
+static int pgd_backward(nyb200_engine *e, Net &net, bool tensor, int K, float *G0, float *G1, float *const *act, int ld,
+                        int *derr, float **result) {
+    const NetView &nv = net.v;
+    const int L = nv.L;
+    cudaStream_t st = e->stream;
+    double *cols64 = nullptr;
+    float *g = G0, *gn = G1;
+    float *gstash = nullptr;
+    int stash_for = -1;
+    for (int k = L - 1; k >= 0; --k) {
+        int Kd = nv.dims[k + 1], N = nv.dims[k];
+        if (gstash && stash_for == k) {  // g is the gradient of relu(pre_k): the identity branch joins here
+            long tot = (long)K * Kd;
+            k_add_rows<<<(unsigned)((tot + 255) / 256), 256, 0, st>>>(K, Kd, g, ld, gstash, ld);
+            e->launches++;
+            gstash = nullptr;
+        }
+        if (k < L - 1) {
+            long tot = (long)K * Kd;
+            k_relu_mask<<<(unsigned)((tot + 255) / 256), 256, 0, st>>>(K, Kd, g, ld, act[k], ld);
+            e->launches++;
+        }
+        if (net.skip_of(k) >= 0) {  // the gradient of pre_k also reaches relu(pre_j) directly
+            gstash = (float *)ws_get(e, "pgd_skip", (size_t)K * ld * 4);
+            if (!gstash) return NYB200_ERR_OOM;
+            NYB_CUDA(e, cudaMemcpyAsync(gstash, g, (size_t)K * ld * 4, cudaMemcpyDeviceToDevice, st));
+            stash_for = net.skip_of(k);
+        }
+        if (net.is_conv(k) && tensor) {
+            const ConvGeom &cg = net.geom[k];
+            const int plane = cg.oh * cg.ow, taps = cg.ic * cg.kh * cg.kw;
+            float *cols = (float *)ws_get(e, "conv_cols", (size_t)K * plane * taps * 4);
+            if (!cols) return NYB200_ERR_OOM;
+            NYB_TRY(launch_umma(e, net.umma[k], K * plane, g, ld, cols, taps, derr, plane));
+            launch_col2im(e, cg, K, cols, gn, ld);
+        } else if (net.is_conv(k)) {
+            const ConvGeom &cg = net.geom[k];
+            cols64 = (double *)ws_get(e, "conv_cols", (size_t)K * cg.oh * cg.ow * cg.ic * cg.kh * cg.kw * 8);
+            if (!cols64) return NYB200_ERR_OOM;
+            launch_conv_transpose(e, cg, K, g, ld, gn, ld, nv.W[k], 1, nullptr, nullptr, 0, nullptr, cols64);
+        } else if (tensor) {
+            NYB_TRY(launch_umma(e, net.umma[k], K, g, ld, gn, ld, derr));
+        } else {
+            launch_gemm_f64(e, K, N, Kd, g, ld, nv.W[k], N, gn, ld, 1, nullptr, nullptr, 0, nullptr);
+        }
+        float *tmp = g; g = gn; gn = tmp;
+    }
+    *result = g;
     return NYB200_OK;
 }
 
@@ -197,57 +262,17 @@ int pgd_attack(nyb200_engine *e, int net_id, const float *spec, int S, const flo
     const unsigned gk = (unsigned)((K + 255) / 256);
     const long nx = (long)K * n0;
     const unsigned gx = (unsigned)((nx + 255) / 256);
-    double *cols64 = nullptr;
 
     for (int t = 1; t <= cfg.steps + 1; ++t) {
+        NYB_DEADLINE(e, "attack");
         NYB_TRY(pgd_forward(e, *net, tensor, K, X, ld, act.data(), ld, derr));
         const bool last = t == cfg.steps + 1;
         k_pgd_objective<<<gk, 256, 0, st>>>(K, S, nL, act[L - 1], ld, dspec, dbest, dimp, last ? nullptr : G0, ld, nullptr);
         k_keep_best<<<gx, 256, 0, st>>>(K, n0, X, ld, dimp, dbx);
         e->launches += 2;
         if (last) break;
-        // exact gradient of the chosen row: G_k = (G_{k+1} . [z_k > 0]) W_k, down to the input
-        float *g = G0, *gn = G1;
-        float *gstash = nullptr;
-        int stash_for = -1;
-        for (int k = L - 1; k >= 0; --k) {
-            int Kd = nv.dims[k + 1], N = nv.dims[k];
-            if (gstash && stash_for == k) {  // g is the gradient of relu(pre_k): the identity branch joins here
-                long tot = (long)K * Kd;
-                k_add_rows<<<(unsigned)((tot + 255) / 256), 256, 0, st>>>(K, Kd, g, ld, gstash, ld);
-                e->launches++;
-                gstash = nullptr;
-            }
-            if (k < L - 1) {
-                long tot = (long)K * Kd;
-                k_relu_mask<<<(unsigned)((tot + 255) / 256), 256, 0, st>>>(K, Kd, g, ld, act[k], ld);
-                e->launches++;
-            }
-            if (net->skip_of(k) >= 0) {  // the gradient of pre_k also reaches relu(pre_j) directly
-                gstash = (float *)ws_get(e, "pgd_skip", (size_t)K * ld * 4);
-                if (!gstash) return NYB200_ERR_OOM;
-                NYB_CUDA(e, cudaMemcpyAsync(gstash, g, (size_t)K * ld * 4, cudaMemcpyDeviceToDevice, st));
-                stash_for = net->skip_of(k);
-            }
-            if (net->is_conv(k) && tensor) {
-                const ConvGeom &cg = net->geom[k];
-                const int plane = cg.oh * cg.ow, taps = cg.ic * cg.kh * cg.kw;
-                float *cols = (float *)ws_get(e, "conv_cols", (size_t)K * plane * taps * 4);
-                if (!cols) return NYB200_ERR_OOM;
-                NYB_TRY(launch_umma(e, net->umma[k], K * plane, g, ld, cols, taps, derr, plane));
-                launch_col2im(e, cg, K, cols, gn, ld);
-            } else if (net->is_conv(k)) {
-                const ConvGeom &cg = net->geom[k];
-                cols64 = (double *)ws_get(e, "conv_cols", (size_t)K * cg.oh * cg.ow * cg.ic * cg.kh * cg.kw * 8);
-                if (!cols64) return NYB200_ERR_OOM;
-                launch_conv_transpose(e, cg, K, g, ld, gn, ld, nv.W[k], 1, nullptr, nullptr, 0, nullptr, cols64);
-            } else if (tensor) {
-                NYB_TRY(launch_umma(e, net->umma[k], K, g, ld, gn, ld, derr));
-            } else {
-                launch_gemm_f64(e, K, N, Kd, g, ld, nv.W[k], N, gn, ld, 1, nullptr, nullptr, 0, nullptr);
-            }
-            float *tmp = g; g = gn; gn = tmp;
-        }
+        float *g = nullptr;
+        NYB_TRY(pgd_backward(e, *net, tensor, K, G0, G1, act.data(), ld, derr, &g));
         k_nan_rows<<<(unsigned)(((long)K * 32 + 255) / 256), 256, 0, st>>>(K, n0, g, ld, dnan);
         PgdStep h;
         float bc1 = 1.f - powf(b1, (float)t);
@@ -277,7 +302,74 @@ int pgd_attack(nyb200_engine *e, int net_id, const float *spec, int S, const flo
     return NYB200_OK;
 }
 
+
+// Exact point gradients of K restarts: spec_rows[k] . df/dx, ReLU derivatives from the forward pass at x or from
+// caller-supplied masks.
+int point_vjp(nyb200_engine *e, int net_id, int K, const float *x, const float *masks, const float *spec_rows, float *grads,
+              float *values) {
+    Net *net;
+    NYB_TRY(find_net(e, net_id, &net));
+    const NetView &nv = net->v;
+    if (K <= 0) return set_err(e, NYB200_ERR_SHAPE, "K must be positive");
+    if ((x != nullptr) == (masks != nullptr)) return set_err(e, NYB200_ERR_INVALID, "exactly one of x and masks must be given");
+    if (values && !x) return set_err(e, NYB200_ERR_INVALID, "values need the points x");
+    const int L = nv.L, n0 = nv.dims[0], nL = nv.dims[L];
+    const bool tensor = e->path == NYB200_PATH_TF32X3;
+    const int ld = (net->max_dim + 7) & ~7;
+    e->batch = Batch();  // workspace names are shared with the resident batch
+    NYB_TRY(prepare_transposed(e, *net, tensor));
+    if (tensor) NYB_TRY(prepare_backward_operands(e, *net));
+    NYB_WS(X, float *, e, "pgd_x", (size_t)K * ld * 4);
+    NYB_WS(acts, float *, e, "pgd_act", (size_t)L * K * ld * 4);
+    NYB_WS(G0, float *, e, "pgd_g0", (size_t)K * ld * 4);
+    NYB_WS(G1, float *, e, "pgd_g1", (size_t)K * ld * 4);
+    NYB_WS(dval, float *, e, "pgd_best", (size_t)K * 4);
+    int *derr = nullptr;
+    if (tensor) {
+        derr = (int *)ws_get(e, "umma_err", 256);
+        if (!derr) return NYB200_ERR_OOM;
+        NYB_CUDA(e, cudaMemsetAsync(derr, 0, 4, e->stream));
+    }
+    std::vector<float *> act((size_t)L);
+    for (int k = 0; k < L; ++k) act[k] = acts + (size_t)k * K * ld;
+    cudaStream_t st = e->stream;
+    NYB_CUDA(e, cudaMemcpy2DAsync(G0, (size_t)ld * 4, spec_rows, (size_t)nL * 4, (size_t)nL * 4, (size_t)K, cudaMemcpyHostToDevice, st));
+    if (x) {
+        NYB_CUDA(e, cudaMemcpy2DAsync(X, (size_t)ld * 4, x, (size_t)n0 * 4, (size_t)n0 * 4, (size_t)K, cudaMemcpyHostToDevice, st));
+        NYB_TRY(pgd_forward(e, *net, tensor, K, X, ld, act.data(), ld, derr));
+        if (values) {
+            k_row_dot<<<(unsigned)(((long)K * 32 + 255) / 256), 256, 0, st>>>(K, nL, act[L - 1], ld, G0, ld, dval);
+            e->launches++;
+        }
+    } else {
+        for (int k = 0; k < L - 1; ++k)  // layer k's mask block of every restart's [n_pre] row
+            NYB_CUDA(e, cudaMemcpy2DAsync(act[k], (size_t)ld * 4, masks + nv.pre_off[k], (size_t)nv.n_pre * 4,
+                                          (size_t)nv.dims[k + 1] * 4, (size_t)K, cudaMemcpyHostToDevice, st));
+    }
+    float *g = nullptr;
+    NYB_TRY(pgd_backward(e, *net, tensor, K, G0, G1, act.data(), ld, derr, &g));
+    NYB_CUDA(e, cudaGetLastError());
+    NYB_CUDA(e, cudaMemcpy2DAsync(grads, (size_t)n0 * 4, g, (size_t)ld * 4, (size_t)n0 * 4, (size_t)K, cudaMemcpyDeviceToHost, st));
+    if (values) NYB_CUDA(e, cudaMemcpyAsync(values, dval, (size_t)K * 4, cudaMemcpyDeviceToHost, st));
+    int herr = 0;
+    if (derr) NYB_CUDA(e, cudaMemcpyAsync(&herr, derr, 4, cudaMemcpyDeviceToHost, st));
+    NYB_CUDA(e, cudaStreamSynchronize(st));
+    if (herr) return set_err(e, NYB200_ERR_INTERNAL, "tcgen05 pipeline wait expired (code " + std::to_string(herr) + ")");
+    for (long i = 0; i < (long)K * n0; ++i)  // never a silently wrong gradient batch
+        if (!(grads[i] == grads[i]) || grads[i] - grads[i] != 0.f) return set_err(e, NYB200_ERR_NUMERICAL, "non-finite point gradient");
+    return NYB200_OK;
+}
+
 }  // namespace nyb
+
+extern "C" int32_t nyb200_point_vjp_batched(nyb200_engine *e, int32_t net_id, int32_t K, const float *x, const float *masks,
+                                            const float *spec_rows, float *grads, float *values) {
+    if (!e || !spec_rows || !grads) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    cudaError_t st = cudaSetDevice(e->device);
+    if (st != cudaSuccess) return nyb::check_cuda(e, st, "cudaSetDevice");
+    return nyb::point_vjp(e, net_id, K, x, masks, spec_rows, grads, values);
+}
 
 extern "C" int32_t nyb200_pgd_attack(nyb200_engine *e, int32_t net_id, const float *spec, int32_t S, const float *in_lo,
                                      const float *in_hi, const float *x0, int32_t K, const nyb200_pgd_config *cfg,

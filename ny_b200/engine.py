@@ -39,7 +39,8 @@ EXPORTS = [
     "nyb200_timing_read", "nyb200_batch_optimize", "nyb200_batch_download_params",
     "nyb200_net_create_layers", "nyb200_pgd_attack", "nyb200_batch_select_branch_scored",
     "nyb200_crown_bounds", "nyb200_batch_download_alpha_upper",
-    "nyb200_batch_verdicts",
+    "nyb200_batch_verdicts", "nyb200_gemm_f64", "nyb200_conv_transpose_2d", "nyb200_set_deadline_ns",
+    "nyb200_batch_gradient", "nyb200_point_vjp_batched",
 ]
 
 
@@ -48,6 +49,12 @@ class OptConfig(C.Structure):
     _fields_ = [("iterations", C.c_int32), ("lr_alpha", C.c_float), ("lr_beta", C.c_float), ("lr_decay", C.c_float),
                 ("beta1", C.c_float), ("beta2", C.c_float), ("epsilon", C.c_float), ("clip_beta", C.c_float),
                 ("objective", C.c_int32)]
+
+
+class ConvTransposeParams(C.Structure):
+    """nyb200_conv_transpose_params (ConvTranspose2dParams, crates/ny-core/src/gemm.rs:150-177)."""
+    _fields_ = [(n, C.c_int32) for n in ("num_specs", "out_channels", "in_channels", "out_h", "out_w", "in_h", "in_w",
+                                         "kernel_h", "kernel_w", "stride_h", "stride_w", "pad_h", "pad_w")]
 
 
 class EngineError(RuntimeError):
@@ -106,6 +113,12 @@ def load_library():
     L.nyb200_batch_optimize.argtypes = [vp, C.POINTER(OptConfig)]
     L.nyb200_batch_download_params.argtypes = [vp, fp, fp]
     L.nyb200_batch_download_alpha_upper.argtypes = [vp, fp]
+    dp = C.POINTER(C.c_double)
+    L.nyb200_gemm_f64.argtypes = [vp, C.c_int32, C.c_int32, C.c_int32, dp, dp, dp]
+    L.nyb200_conv_transpose_2d.argtypes = [vp, fp, fp, C.POINTER(ConvTransposeParams), fp]
+    L.nyb200_set_deadline_ns.argtypes = [vp, C.c_int64]
+    L.nyb200_batch_gradient.argtypes = [vp, C.c_int32, fp]
+    L.nyb200_point_vjp_batched.argtypes = [vp, C.c_int32, C.c_int32, fp, fp, fp, fp, fp]
     _lib = L
     return L
 
@@ -284,6 +297,35 @@ class B200Engine:
         self._check(self._L.nyb200_gemm_f32(self._h, m, k, n, _fp(a), _fp(b), _fp(c)))
         return c.reshape(m, n)
 
+    def gemm_f64(self, m: int, k: int, n: int, a, b) -> np.ndarray:
+        """GemmEngine::gemm_f64: row-major binary64 product."""
+        a = np.ascontiguousarray(a, np.float64).reshape(-1)
+        b = np.ascontiguousarray(b, np.float64).reshape(-1)
+        if a.size != m * k or b.size != k * n:
+            raise EngineError(SHAPE, f"gemm_f64: got {a.size} and {b.size} values for {m}x{k} and {k}x{n}")
+        c = np.empty(m * n, np.float64)
+        dp = C.POINTER(C.c_double)
+        self._check(self._L.nyb200_gemm_f64(self._h, m, k, n, a.ctypes.data_as(dp), b.ctypes.data_as(dp), c.ctypes.data_as(dp)))
+        return c.reshape(m, n)
+
+    def conv_transpose_2d(self, a_reshaped, weight_col, params: ConvTransposeParams) -> np.ndarray:
+        """GemmEngine::conv_transpose_2d: a_reshaped [(S*OH*OW) x OC], weight_col [OC x IC*KH*KW] ->
+        [S x IC*IH*IW]."""
+        p = params
+        a, w = _f32(a_reshaped).reshape(-1), _f32(weight_col).reshape(-1)
+        if a.size != p.num_specs * p.out_h * p.out_w * p.out_channels:
+            raise EngineError(SHAPE, "conv_transpose_2d: a_reshaped size")
+        if w.size != p.out_channels * p.in_channels * p.kernel_h * p.kernel_w:
+            raise EngineError(SHAPE, "conv_transpose_2d: weight_col size")
+        out = np.empty((max(p.num_specs, 0), max(p.in_channels * p.in_h * p.in_w, 0)), np.float32)
+        self._check(self._L.nyb200_conv_transpose_2d(self._h, _fp(a), _fp(w), C.byref(p), _fp(out)))
+        return out
+
+    def set_deadline(self, seconds_from_now: float | None):
+        """GpuCrownBackward::set_crown_backward_deadline: None clears it."""
+        ns = -1 if seconds_from_now is None else max(0, int(seconds_from_now * 1e9))
+        self._check(self._L.nyb200_set_deadline_ns(self._h, ns))
+
     # -- network residency -----------------------------------------------------------------
     def register_network(self, net: Network) -> int:
         if net.has_conv or net.skips:
@@ -436,6 +478,39 @@ class B200Engine:
         batch_download (element-wise best bounds) and batch_download_params."""
         cfg = OptConfig(iterations, lr_alpha, lr_beta, lr_decay, 0.0, 0.0, 0.0, clip_beta, objective)
         self._check(self._L.nyb200_batch_optimize(self._h, C.byref(cfg)))
+
+    def batch_gradient(self, objective: int = 0) -> np.ndarray:
+        """Joint gradient at the batch's current parameters, [D, n_pre]: d/d alpha on unstable unsplit neurons,
+        d/d beta on split neurons, zero elsewhere.  The evaluation's bounds are then available through
+        batch_download()."""
+        D, S, n_pre = self._batch_shape
+        g = np.empty((D, n_pre), np.float32)
+        self._check(self._L.nyb200_batch_gradient(self._h, objective, _fp(g)))
+        return g
+
+    def point_vjp_batched(self, net_id: int, spec_rows, x=None, masks=None):
+        """crown_point_vjp_batched: per-restart exact gradients spec_rows[k] . df/dx.  Give the points x [K, n0]
+        (returns (grads, values)) or the 0/1 masks [K, n_pre] (returns grads)."""
+        net = self._nets[net_id]
+        spec_rows = _f32(spec_rows)
+        K = spec_rows.shape[0]
+        if spec_rows.ndim != 2 or spec_rows.shape[1] != net.dims[-1]:
+            raise EngineError(SHAPE, f"spec_rows shape {spec_rows.shape}")
+        grads = np.empty((K, int(net.dims[0])), np.float32)
+        if x is not None and masks is None:
+            x = _f32(x)
+            if x.shape != (K, net.dims[0]):
+                raise EngineError(SHAPE, "x must be [K, n0]")
+            vals = np.empty(K, np.float32)
+            self._check(self._L.nyb200_point_vjp_batched(self._h, net_id, K, _fp(x), None, _fp(spec_rows), _fp(grads), _fp(vals)))
+            return grads, vals
+        if masks is not None and x is None:
+            masks = _f32(masks)
+            if masks.shape != (K, net.n_pre):
+                raise EngineError(SHAPE, "masks must be [K, n_pre]")
+            self._check(self._L.nyb200_point_vjp_batched(self._h, net_id, K, None, _fp(masks), _fp(spec_rows), _fp(grads), None))
+            return grads
+        raise EngineError(INVALID, "exactly one of x and masks must be given")
 
     def batch_download_params(self):
         """(alpha [D, n_pre], beta [D, max_splits]) after the last run."""

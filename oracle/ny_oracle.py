@@ -310,8 +310,9 @@ def heuristic_alpha(net: Net, pre_lo, pre_hi):
     return np.where((pre_lo < 0) & (pre_hi > 0), (pre_hi > -pre_lo).astype(np.float32), 0.0).astype(np.float32)
 
 
-def joint_gradient(net: Net, lo, hi, pre_lo, pre_hi, splits: np.ndarray, alpha=None):
-    """Returns (lower bounds [S] in binary64, grad_alpha [n_pre], grad_beta [n_splits])."""
+def joint_gradient(net: Net, lo, hi, pre_lo, pre_hi, splits: np.ndarray, alpha=None, only_row: int = -1):
+    """Returns (lower bounds [S] in binary64, grad_alpha [n_pre], grad_beta [n_splits]): the gradient of the sum of
+    the rows' lower bounds, or of row `only_row` alone when it is >= 0."""
     lo, hi, pre_lo, pre_hi = _f32(lo), _f32(hi), _f32(pre_lo), _f32(pre_hi)
     alpha = None if alpha is None else _f32(alpha)
     splits = np.ascontiguousarray(splits, SPLIT_DTYPE)
@@ -319,8 +320,9 @@ def joint_gradient(net: Net, lo, hi, pre_lo, pre_hi, splits: np.ndarray, alpha=N
     low = np.empty(S, np.float64)
     ga = np.zeros(net.n_pre, np.float32)
     gb = np.zeros(max(len(splits), 1), np.float32)
-    lib().nyo_joint_gradient(C.byref(net.c), _fp(lo), _fp(hi), _fp(pre_lo), _fp(pre_hi), splits.ctypes.data, len(splits),
-                             _fp(alpha), low.ctypes.data_as(C.POINTER(C.c_double)), _fp(ga), _fp(gb))
+    lib().nyo_joint_gradient_rows(C.byref(net.c), _fp(lo), _fp(hi), _fp(pre_lo), _fp(pre_hi), splits.ctypes.data,
+                                  len(splits), _fp(alpha), low.ctypes.data_as(C.POINTER(C.c_double)), _fp(ga), _fp(gb),
+                                  int(only_row))
     return low, ga, gb[: len(splits)]
 
 
