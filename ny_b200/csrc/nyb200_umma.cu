@@ -13,9 +13,15 @@
 //               TMEM lane = one output row per thread, 128 columns per warp) and added in fp32
 //               registers, alternating between the two accumulators so that the drain of one chunk
 //               overlaps the MMAs of the next; the row sums are stored after the last chunk.
-//   warps 12-15 A producers: each thread owns one row of the 128-row tile, loads 32 fp32 of it
+//   warps 12-15 A producers: each thread owns one row of the 128-row tile, takes 32 fp32 of it
 //               (prefetched one stage ahead), splits every value into TF32 high and low parts and
 //               writes both to shared memory in the swizzled K-major layout the tensor core reads.
+//               The fp32 tile itself arrives by TMA in a two-deep ring of 16 KB staging buffers (warp 0
+//               issues it next to the weight tiles), so the producers read their rows from shared
+//               memory; with one row per lane a direct global load touches 32 sectors per instruction
+//               and the load/store unit becomes the pipeline's bottleneck.  Operands a tensor map
+//               cannot describe (unaligned base or row stride, the channel-strided convolution form)
+//               take the direct loads.
 // Every wait on an mbarrier is bounded; on expiry the kernel records an error code, stops issuing
 // work, frees its tensor memory and returns.
 //
@@ -43,7 +49,9 @@ constexpr int BM = 128, BN = 256, BK = 32, STAGES = 2;
 constexpr int A_BYTES = BM * BK * 4;   // 16 KB per half
 constexpr int B_BYTES = BN * BK * 4;   // 32 KB per half
 constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+constexpr int RAW_STAGES = 2;           // fp32 A tiles in flight between the TMA and the split
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + RAW_STAGES * A_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+static_assert(SMEM_BYTES <= 232448, "more than the 227 KB a CTA can opt into");
 constexpr int THREADS = 512;
 // Register budget after the roles re-split it with setmaxnreg: 4 control warps, 8 epilogue warps, 4 producer warps.
 // setmaxnreg.inc blocks until the registers it asks for have been released by the other warps' setmaxnreg.dec, so
@@ -168,14 +176,16 @@ __global__ void k_split_weights(const float *__restrict__ W, int K, int N, int K
 
 __global__ void __launch_bounds__(THREADS, 1)
 k_umma_tf32x3(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__ CUtensorMap tm_lo,
-              const float *__restrict__ A, int lda, float *__restrict__ C, int ldc, int M, int N, int K,
-              int chunk_stages, int *__restrict__ err, int a_plane) {
+              const __grid_constant__ CUtensorMap tm_a, const float *__restrict__ A, int lda, float *__restrict__ C,
+              int ldc, int M, int N, int K, int chunk_stages, int *__restrict__ err, int a_plane, int a_tma) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    unsigned long long *bars = (unsigned long long *)(smem + STAGES * STAGE_BYTES);
+    unsigned char *raw_base = smem + STAGES * STAGE_BYTES;  // RAW_STAGES fp32 A tiles (128-byte swizzle, as TMA wrote them)
+    unsigned long long *bars = (unsigned long long *)(raw_base + RAW_STAGES * A_BYTES);
     // barrier indices
     const int FULL_A = 0, FULL_B = STAGES, EMPTY = 2 * STAGES, ACC_FULL = 3 * STAGES, ACC_EMPTY = 3 * STAGES + 2;
-    unsigned *tmem_slot = (unsigned *)(bars + 3 * STAGES + 4);
+    const int RAW_FULL = 3 * STAGES + 4, RAW_EMPTY = RAW_FULL + RAW_STAGES;
+    unsigned *tmem_slot = (unsigned *)(bars + 3 * STAGES + 4 + 2 * RAW_STAGES);
     volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
 
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -194,6 +204,10 @@ k_umma_tf32x3(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__
             mbar_init(smem_u32(&bars[ACC_FULL + b]), 1);
             mbar_init(smem_u32(&bars[ACC_EMPTY + b]), 256);
         }
+        for (int b = 0; b < RAW_STAGES; ++b) {
+            mbar_init(smem_u32(&bars[RAW_FULL + b]), 1);
+            mbar_init(smem_u32(&bars[RAW_EMPTY + b]), 128);
+        }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -211,9 +225,26 @@ k_umma_tf32x3(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__
         if (warp == 0 && lane == 0) {
             // ------------------------------------------------------------ weight producer (TMA)
             unsigned it = 0;
+            // The fp32 A tile of pipeline step `step` (tile t, K stage ks) into the staging ring, once the producers
+            // have taken the tile that used the slot before.  It runs one step ahead of the weight tiles.
+            auto stage_a = [&](unsigned step, int t, int ks) -> bool {
+                int rb = step % RAW_STAGES;
+                unsigned rph = (step / RAW_STAGES) & 1;
+                if (!mbar_wait(smem_u32(&bars[RAW_EMPTY + rb]), rph ^ 1)) return false;
+                unsigned rbar = smem_u32(&bars[RAW_FULL + rb]);
+                mbar_expect_tx(rbar, A_BYTES);
+                tma_load_2d(smem_u32(raw_base + rb * A_BYTES), &tm_a, ks * BK, (t / n_tiles) * BM, rbar);
+                return true;
+            };
+            if (a_tma && (int)blockIdx.x < total_tiles && !stage_a(0, blockIdx.x, 0)) { atomicExch(err, 6); *abort_flag = 1; }
             for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
                 int tn = t % n_tiles;
                 for (int ks = 0; ks < k_stages; ++ks, ++it) {
+                    if (a_tma) {
+                        int nks = ks + 1, nt = t;
+                        if (nks == k_stages) { nks = 0; nt = t + gridDim.x; }
+                        if (nt < total_tiles && !stage_a(it + 1, nt, nks)) { atomicExch(err, 6); *abort_flag = 1; break; }
+                    }
                     int s = it % STAGES;
                     unsigned ph = (it / STAGES) & 1;
                     if (!mbar_wait(smem_u32(&bars[EMPTY + s]), ph ^ 1)) { atomicExch(err, 1); *abort_flag = 1; break; }
@@ -396,7 +427,26 @@ k_umma_tf32x3(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__
                 v[c] = x;
             }
         };
-        if ((int)blockIdx.x < total_tiles) load_stage(blockIdx.x, 0);
+        // Staged form: this thread's row of the fp32 tile of pipeline step `step`, out of the TMA ring.  Chunk c of
+        // row r sits at chunk c ^ (r & 7) of the row's 128 bytes; a quarter-warp reads eight different chunks.
+        auto take_staged = [&](unsigned step) -> bool {
+            int rb = step % RAW_STAGES;
+            unsigned rph = (step / RAW_STAGES) & 1;
+            if (!mbar_wait(smem_u32(&bars[RAW_FULL + rb]), rph)) return false;
+            const float *raw = (const float *)(raw_base + rb * A_BYTES);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) v[c] = *(const float4 *)(raw + r * 32 + ((c ^ (r & 7)) << 2));
+            // The slot is refilled by the async proxy (TMA) once all 128 threads have arrived: order this thread's
+            // generic-proxy reads before that write.  Without the fence later tiles of a CTA were seen to read a
+            // refilled slot whenever the tensor core, not the loads, paced the pipeline.
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(smem_u32(&bars[RAW_EMPTY + rb]));
+            return true;
+        };
+        if ((int)blockIdx.x < total_tiles) {
+            if (a_tma) { if (!take_staged(0)) { atomicExch(err, 7); *abort_flag = 1; dead = true; } }
+            else load_stage(blockIdx.x, 0);
+        }
         for (int t = blockIdx.x; t < total_tiles && !dead; t += gridDim.x) {
             for (int ks = 0; ks < k_stages; ++ks, ++it) {
                 int s = it % STAGES;
@@ -418,7 +468,10 @@ k_umma_tf32x3(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__
                 // prefetch the next stage's row segment while the tensor core works on this one
                 int nks = ks + 1, nt = t;
                 if (nks == k_stages) { nks = 0; nt = t + gridDim.x; }
-                if (nt < total_tiles) load_stage(nt, nks);
+                if (nt < total_tiles) {
+                    if (a_tma) { if (!take_staged(it + 1)) { atomicExch(err, 7); *abort_flag = 1; dead = true; break; } }
+                    else load_stage(nt, nks);
+                }
             }
         }
     }
@@ -446,12 +499,12 @@ static EncodeTiledFn get_encode() {
 
 // Tensor map over a [rows x kpad] fp32 matrix (K contiguous): box 32 (K) x 256 (rows), 128-byte swizzle,
 // out-of-range elements read as zero.
-static int make_tmap(CUtensorMap *tm, const float *base, int rows, int kpad) {
+static int make_tmap(CUtensorMap *tm, const float *base, int rows, int kpad, int ld = 0, int box_rows = BN) {
     EncodeTiledFn enc = get_encode();
     if (!enc) return 1;
     cuuint64_t dims[2] = {(cuuint64_t)kpad, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)kpad * 4};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)BN};
+    cuuint64_t strides[1] = {(cuuint64_t)(ld > 0 ? ld : kpad) * 4};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void *)base, dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -492,8 +545,19 @@ int launch_umma(nyb200_engine *e, const UmmaLayer &L, int M, const float *A, int
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, e->device);
     int tiles = ((M + BM - 1) / BM) * ((L.N + BN - 1) / BN);
     int grid = tiles < sms ? tiles : sms;
-    k_umma_tf32x3<<<grid, THREADS, SMEM_BYTES, e->stream>>>(*(const CUtensorMap *)L.tm_hi, *(const CUtensorMap *)L.tm_lo, A,
-                                                            lda, C, ldc, M, L.N, L.K, chunk_stages_cfg(), err, a_plane);
+    // The fp32 operand goes through TMA when a tensor map can describe it: rows of K contiguous values, base and row
+    // stride multiples of 16 bytes.  Columns past K and rows past M read as zero, like the direct loads.
+    alignas(64) CUtensorMap tm_a;
+    int a_tma = 0;
+    static const bool staged = [] { const char *s = getenv("NYB200_A_DIRECT"); return !(s && atoi(s) != 0); }();
+    if (staged && a_plane == 0 && (reinterpret_cast<uintptr_t>(A) & 15) == 0 && (lda & 3) == 0 && lda >= L.K) {
+        if (make_tmap(&tm_a, A, M, L.K, lda, BM)) return set_err(e, NYB200_ERR_INTERNAL, "cuTensorMapEncodeTiled failed for the A operand");
+        a_tma = 1;
+    } else {
+        tm_a = *(const CUtensorMap *)L.tm_hi;  // unused by the kernel in this form; any valid map
+    }
+    k_umma_tf32x3<<<grid, THREADS, SMEM_BYTES, e->stream>>>(*(const CUtensorMap *)L.tm_hi, *(const CUtensorMap *)L.tm_lo, tm_a, A,
+                                                            lda, C, ldc, M, L.N, L.K, chunk_stages_cfg(), err, a_plane, a_tma);
     e->launches++;
     return NYB200_OK;
 }
