@@ -161,6 +161,11 @@ int32_t nyb200_bab_bound_batch(nyb200_engine *e, int32_t net_id, const float *sp
 int32_t nyb200_crown_bounds(nyb200_engine *e, int32_t net_id, const float *spec, int32_t S, const float *in_lo,
                             const float *in_hi, int32_t box_stride, int32_t D, float *out_lo, float *out_hi,
                             float *inter_lo, float *inter_hi);
+/* Input-level linear coefficients of the last nyb200_crown_bounds call (LinearBounds::lower_a / upper_a of the
+ * reference's CROWN result, used by the input-split heuristic, beta_crown/engine/input_split.rs:111-260):
+ * lower_a / upper_a [D x S x dims[0]], either may be NULL.  The rows stay on the device only until the next call
+ * that uses the batch workspace (upload, attack, another CROWN call); after that NYB200_ERR_INVALID. */
+int32_t nyb200_crown_input_coeffs(nyb200_engine *e, float *lower_a, float *upper_a);
 
 /* ---- resident batch (extension: keeps the domain batch in HBM between calls) ----------------
  * upload copies the same arguments as nyb200_bab_bound_batch to the device; run launches the

@@ -144,3 +144,107 @@ def verify(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: i
     if not frontier:
         res.status = "verified"
     return res
+
+
+# ------------------------------------------------------------------------------------------- input split
+def input_split_scores(in_lo, in_hi, lower_a=None, lower=None, thr=None, coeff_thresh: float = 1e-3,
+                       margin_weight: float = 1.0):
+    """Score of every input dimension for a midpoint split, the margin-weighted smart-branching rule of the
+    reference (BetaCrownVerifier::input_split_scores, beta_crown/engine/input_split.rs:111-243, default mode):
+    max over spec rows of |lA[s, d]|.clamp(min = coeff_thresh) * width[d] / 2 + (lower[s] - thr[s]) * margin_weight;
+    width only when there are no coefficients or all of them are zero; dimensions of zero or non-finite width get
+    no score.  Returns (dims, scores), unsorted."""
+    in_lo, in_hi = np.asarray(in_lo, np.float32), np.asarray(in_hi, np.float32)
+    width = in_hi - in_lo
+    ok = np.isfinite(width) & (width > 0)
+    dims = np.flatnonzero(ok)
+    if lower_a is None or not np.any(np.abs(lower_a) > 0):
+        return dims, width[ok]
+    a = np.abs(np.asarray(lower_a, np.float32))
+    margin = np.zeros(a.shape[0], np.float32)
+    if lower is not None and thr is not None:
+        margin = (np.asarray(lower, np.float32) - np.asarray(thr, np.float32)) * np.float32(margin_weight)
+    per_spec = np.maximum(a, np.float32(coeff_thresh)) * (width * np.float32(0.5))[None, :] + margin[:, None]
+    score = per_spec.max(axis=0)
+    keep = ok & np.isfinite(score)
+    return np.flatnonzero(keep), score[keep]
+
+
+def select_input_dimension(in_lo, in_hi, lower_a=None, lower=None, thr=None, **kw) -> int:
+    """First maximum of input_split_scores; NaN scores never win (select_input_dimension_sb, input_split.rs:47-72).
+    -1 when no dimension can be split."""
+    dims, scores = input_split_scores(in_lo, in_hi, lower_a, lower, thr, **kw)
+    best, best_score = -1, np.float32(-np.inf)
+    for d, s in zip(dims, scores):
+        if np.isnan(s):
+            continue
+        if best < 0 or s > best_score:
+            best, best_score = int(d), s
+    return best
+
+
+def verify_input_split(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: int = 200,
+                       max_domains: int = 1 << 20, pgd_restarts: int = 256, pgd_steps: int = 50,
+                       timeout_s: float | None = None) -> VerifyResult:
+    """Branch and bound over the INPUT box (the loop of the reference's input-split engine,
+    beta_crown/engine/input_split.rs:262-460, batched): attack, then repeatedly bound a batch of sub-boxes with
+    plain CROWN (all boxes in one device call), drop the verified ones, test the centre of every open box as a
+    counterexample, and midpoint-split each along the dimension the smart-branching score picks.  What low-dimensional
+    inputs (ACAS-shaped networks) use instead of ReLU splits."""
+    t0 = time.time()
+    if not prop.violation:
+        return VerifyResult("verified")
+    spec, thr, owner = _rows(prop)
+    S, n0 = spec.shape[0], len(prop.in_lo)
+    n_clauses = len(prop.violation)
+    ce = attack(eng, net_id, net, prop, pgd_restarts, pgd_steps)
+    if ce is not None:
+        return VerifyResult("violated", ce[0], ce[1])
+    res = VerifyResult("unknown")
+    frontier_lo = [np.asarray(prop.in_lo, np.float32)]
+    frontier_hi = [np.asarray(prop.in_hi, np.float32)]
+    while frontier_lo and res.rounds < max_rounds:
+        if timeout_s is not None and time.time() - t0 > timeout_s:
+            res.status = "timeout"
+            res.open_domains = len(frontier_lo)
+            return res
+        lo = np.stack(frontier_lo[:batch])
+        hi = np.stack(frontier_hi[:batch])
+        frontier_lo, frontier_hi = frontier_lo[batch:], frontier_hi[batch:]
+        D = lo.shape[0]
+        lower, _, _, _ = eng.crown_bounds(net_id, spec, lo, hi)
+        lower_a, _ = eng.crown_input_coeffs(D, S, n0)
+        if res.rounds == 0:
+            res.root_lower = lower[0].copy()
+        res.rounds += 1
+        res.domains_bounded += D
+        done = _verified_mask(lower, thr, owner, n_clauses)
+        open_idx = np.flatnonzero(~done)
+        if len(open_idx) == 0:
+            continue
+        centres = ((lo[open_idx].astype(np.float64) + hi[open_idx].astype(np.float64)) * 0.5).astype(np.float32)
+        centres = np.clip(centres, lo[open_idx], hi[open_idx])
+        ys = forward(net, centres)
+        for x, y in zip(centres, ys):
+            if _violates(prop, y):
+                return VerifyResult("violated", x, y, res.rounds, res.domains_bounded, len(frontier_lo), res.root_lower)
+        for d in open_idx:
+            dim = select_input_dimension(lo[d], hi[d], lower_a[d], lower[d], thr)
+            if dim < 0:
+                res.open_domains = len(frontier_lo) + 1      # a point box that is neither verified nor violated
+                return res
+            mid = np.float32((np.float64(lo[d][dim]) + np.float64(hi[d][dim])) * 0.5)
+            if not (lo[d][dim] < mid < hi[d][dim]):           # adjacent floats: the box cannot be split further
+                res.open_domains = len(frontier_lo) + 1
+                return res
+            left_hi, right_lo = hi[d].copy(), lo[d].copy()
+            left_hi[dim] = mid
+            right_lo[dim] = mid
+            frontier_lo += [lo[d], right_lo]
+            frontier_hi += [left_hi, hi[d]]
+        if len(frontier_lo) > max_domains:
+            break
+    res.open_domains = len(frontier_lo)
+    if not frontier_lo:
+        res.status = "verified"
+    return res

@@ -299,6 +299,26 @@ static int crown_bounds_once(nyb200_engine *e, int net_id, const float *spec, in
     NYB_CUDA(e, cudaMemcpyAsync(loose_out, loose_acc, 4, cudaMemcpyDeviceToHost, st));
     NYB_CUDA(e, cudaStreamSynchronize(st));
     if (herr) return set_err(e, NYB200_ERR_INTERNAL, "tcgen05 pipeline wait expired (code " + std::to_string(herr) + ")");
+    e->batch.crown_a = ps.a_final;
+    e->batch.crown_lda = ps.lda; e->batch.crown_D = D; e->batch.crown_S = S; e->batch.crown_n0 = nv.dims[0];
+    return NYB200_OK;
+}
+
+// Input-level coefficient rows of the last plain-CROWN call: lower_a / upper_a [D x S x dims[0]] (either may be null).
+int crown_input_coeffs(nyb200_engine *e, float *lower_a, float *upper_a) {
+    const Batch &b = e->batch;
+    if (!b.crown_a) return set_err(e, NYB200_ERR_INVALID, "no plain-CROWN result is held (another call has reused the workspace)");
+    const size_t w = (size_t)b.crown_n0 * 4, pitch = (size_t)b.crown_lda * 4;
+    for (int d = 0; d < b.crown_D; ++d) {
+        const float *base = b.crown_a + (size_t)d * 2 * b.crown_S * b.crown_lda;
+        if (lower_a)
+            NYB_CUDA(e, cudaMemcpy2DAsync(lower_a + (size_t)d * b.crown_S * b.crown_n0, w, base, pitch, w, (size_t)b.crown_S,
+                                          cudaMemcpyDeviceToHost, e->stream));
+        if (upper_a)
+            NYB_CUDA(e, cudaMemcpy2DAsync(upper_a + (size_t)d * b.crown_S * b.crown_n0, w, base + (size_t)b.crown_S * b.crown_lda,
+                                          pitch, w, (size_t)b.crown_S, cudaMemcpyDeviceToHost, e->stream));
+    }
+    NYB_CUDA(e, cudaStreamSynchronize(e->stream));
     return NYB200_OK;
 }
 
@@ -319,6 +339,14 @@ int crown_bounds(nyb200_engine *e, int net_id, const float *spec, int S, const f
 }
 
 }  // namespace nyb
+
+extern "C" int32_t nyb200_crown_input_coeffs(nyb200_engine *e, float *lower_a, float *upper_a) {
+    if (!e || (!lower_a && !upper_a)) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    cudaError_t st = cudaSetDevice(e->device);
+    if (st != cudaSuccess) return nyb::check_cuda(e, st, "cudaSetDevice");
+    return nyb::crown_input_coeffs(e, lower_a, upper_a);
+}
 
 extern "C" int32_t nyb200_crown_bounds(nyb200_engine *e, int32_t net_id, const float *spec, int32_t S, const float *in_lo,
                                        const float *in_hi, int32_t box_stride, int32_t D, float *out_lo, float *out_hi,

@@ -78,6 +78,10 @@ struct Batch {
     bool optimized = false;  // the last run was a parameter optimisation: results are the best-so-far bounds
     bool finished = false;  // results of the last run have been checked (and refined if needed)
     int refined = 0;        // domains that triggered the binary64 re-run of the last batch
+    // Left behind by the last plain-CROWN call: the input-level coefficient rows of its final pass
+    // ([crown_D * 2 * crown_S x crown_lda], per box S lower rows then S upper rows), until any call reuses the workspace.
+    const float *crown_a = nullptr;
+    int crown_lda = 0, crown_D = 0, crown_S = 0, crown_n0 = 0;
 };
 
 struct Timing {

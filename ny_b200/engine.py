@@ -40,7 +40,7 @@ EXPORTS = [
     "nyb200_net_create_layers", "nyb200_pgd_attack", "nyb200_batch_select_branch_scored",
     "nyb200_crown_bounds", "nyb200_batch_download_alpha_upper",
     "nyb200_batch_verdicts", "nyb200_gemm_f64", "nyb200_conv_transpose_2d", "nyb200_set_deadline_ns",
-    "nyb200_batch_gradient", "nyb200_point_vjp_batched",
+    "nyb200_batch_gradient", "nyb200_point_vjp_batched", "nyb200_crown_input_coeffs",
 ]
 
 
@@ -118,6 +118,7 @@ def load_library():
     L.nyb200_conv_transpose_2d.argtypes = [vp, fp, fp, C.POINTER(ConvTransposeParams), fp]
     L.nyb200_set_deadline_ns.argtypes = [vp, C.c_int64]
     L.nyb200_batch_gradient.argtypes = [vp, C.c_int32, fp]
+    L.nyb200_crown_input_coeffs.argtypes = [vp, fp, fp]
     L.nyb200_point_vjp_batched.argtypes = [vp, C.c_int32, C.c_int32, fp, fp, fp, fp, fp]
     _lib = L
     return L
@@ -453,6 +454,12 @@ class B200Engine:
         self._check(self._L.nyb200_crown_bounds(self._h, net_id, _fp(spec), S, _fp(lo), _fp(hi), 0 if one else int(net.dims[0]),
                                                 D, _fp(ol), _fp(ou), _fp(il), _fp(iu)))
         return ol, ou, il, iu
+
+    def crown_input_coeffs(self, D: int, S: int, n0: int):
+        """(lower_a, upper_a), each [D, S, n0]: input-level coefficients of the last crown_bounds call."""
+        la, ua = np.empty((D, S, n0), np.float32), np.empty((D, S, n0), np.float32)
+        self._check(self._L.nyb200_crown_input_coeffs(self._h, _fp(la), _fp(ua)))
+        return la, ua
 
     def pgd_attack(self, net_id, spec, in_lo, in_hi, x0, steps: int, step_size: float, lr_decay: float = 0.99):
         """PGD batched over the K rows of x0 [K, n0]; returns (best objective per restart [K], best points [K, n0],

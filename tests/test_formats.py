@@ -89,3 +89,24 @@ def test_vnnlib_rejections():
         formats.parse_vnnlib(decl + "(assert (>= X_0 0))(assert (<= X_0 1))(assert (>= Y_3 2.0))", 1, 1)
     with pytest.raises(EngineError):
         formats.parse_vnnlib("(assert (>= X_0 0)", 1, 1)
+
+
+def test_input_split_scores_known_answers():
+    """The smart-branching score of the input-split driver, on hand-computed cases."""
+    from ny_b200 import bab
+
+    lo, hi = np.array([0, 0, 1], np.float32), np.array([1, 2, 1], np.float32)
+    dims, sc = bab.input_split_scores(lo, hi)                       # no coefficients: width, zero-width dims dropped
+    assert dims.tolist() == [0, 1] and sc.tolist() == [1.0, 2.0]
+    assert bab.select_input_dimension(lo, hi) == 1
+    a = np.array([[1.0, 0.1, 5.0], [0.0, 0.0, 9.0]], np.float32)
+    assert bab.select_input_dimension(lo, hi, a) == 0                # max(1 * .5, thresh * .5) > max(.1 * 1, thresh * 1)
+    dims, sc = bab.input_split_scores(lo, hi, a, lower=np.array([0.5, 2.0]), thr=np.array([0.0, 0.0]))
+    assert np.allclose(sc, [2.0005, 2.001])                          # row 1: clamped coefficient * width / 2 + margin 2
+    assert bab.select_input_dimension(lo, hi, a, np.array([0.5, 2.0]), np.array([0.0, 0.0])) == 1
+    assert bab.select_input_dimension(lo, hi, np.zeros((2, 3), np.float32)) == 1       # all-zero rows: width rule
+    assert bab.select_input_dimension(lo, lo) == -1                                     # nothing to split
+    nan_a = np.array([[np.nan, 1.0, 0.0]], np.float32)
+    assert bab.select_input_dimension(lo, hi, nan_a) == 1                               # a NaN score never wins
+    eq = np.array([[2.0, 1.0, 0.0]], np.float32)
+    assert bab.select_input_dimension(lo, hi, eq) == 0                                  # tie 1.0 == 1.0: first wins

@@ -77,3 +77,59 @@ def test_bab_closes_the_gap_between_root_bound_and_true_minimum(eng):
     y = W.forward(net, r.counterexample)
     assert float(row @ y) <= t_unsafe and np.all(r.counterexample >= wl.in_lo) and np.all(r.counterexample <= wl.in_hi)
     eng.release_network(nid)
+
+
+def test_crown_input_coefficients(eng):
+    """Linear network: the exported rows are spec . W exactly on both sides; they go stale with the next batch call."""
+    from ny_b200 import EngineError, Network
+
+    g = np.random.Generator(np.random.PCG64(12))
+    w = g.standard_normal((4, 6)).astype(np.float32)
+    b = g.standard_normal(4).astype(np.float32)
+    net = Network([w], [b])
+    nid = eng.register_network(net)
+    spec = g.standard_normal((3, 4)).astype(np.float32)
+    lo = g.standard_normal((5, 6)).astype(np.float32)
+    hi = lo + 0.1
+    lower, upper, _, _ = eng.crown_bounds(nid, spec, lo, hi)
+    la, ua = eng.crown_input_coeffs(5, 3, 6)
+    want = spec.astype(np.float64) @ w.astype(np.float64)
+    assert np.allclose(la, want[None], rtol=1e-5, atol=1e-6) and np.allclose(ua, want[None], rtol=1e-5, atol=1e-6)
+    conc = np.where(want > 0, lo[:, None, :], hi[:, None, :])
+    assert np.allclose(lower, (want[None] * conc).sum(-1) + spec @ b, rtol=1e-4, atol=1e-4)
+    eng.pgd_attack(nid, spec, lo[0], hi[0], lo[:1], 1, 0.01)
+    with pytest.raises(EngineError):
+        eng.crown_input_coeffs(5, 3, 6)
+    eng.release_network(nid)
+
+
+def test_input_split_on_an_acas_shaped_network(eng):
+    wl = W.config_mlp_small(seed=7)                     # 5 -> 6 x 50 -> 5
+    net = wl.net
+    nid = eng.register_network(net)
+    lo = (wl.x0 - np.float32(0.25)).astype(np.float32)
+    hi = (wl.x0 + np.float32(0.25)).astype(np.float32)
+    g = np.random.Generator(np.random.PCG64(2))
+    xs = (lo + g.random((300000, 5), dtype=np.float32) * (hi - lo)).astype(np.float32)
+    ys = W.forward(net, xs) @ wl.spec.astype(np.float64).T
+    mn = ys.min(axis=0)
+    for s in range(wl.spec.shape[0]):
+        best, _, _ = eng.pgd_attack(nid, wl.spec[s:s + 1], lo, hi, xs[:512], 60, 0.05)
+        mn[s] = min(mn[s], best.min())
+    root, _, _, _ = eng.crown_bounds(nid, wl.spec, lo, hi)
+    s = int(np.argmax(mn - root[0]))
+    assert mn[s] - root[0][s] > 1e-3
+    row = wl.spec[s]
+
+    def prop(t):
+        return formats.Property(lo, hi, [[formats.Atom(-row, float(t))]])
+
+    t_safe = float(root[0][s] + 0.7 * (mn[s] - root[0][s]))
+    r = bab.verify_input_split(eng, nid, net, prop(t_safe), batch=512)
+    assert r.status == "verified" and r.rounds >= 2 and r.domains_bounded > 1 and r.open_domains == 0
+    t_unsafe = float(mn[s] + 1e-3 * max(1.0, abs(mn[s])))
+    r = bab.verify_input_split(eng, nid, net, prop(t_unsafe), batch=512)
+    assert r.status == "violated"
+    assert float(row @ W.forward(net, r.counterexample)) <= t_unsafe
+    assert np.all(r.counterexample >= lo) and np.all(r.counterexample <= hi)
+    eng.release_network(nid)
