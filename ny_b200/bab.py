@@ -12,6 +12,9 @@ when one of its atoms is; a domain is verified when every clause is refuted.
 """
 from __future__ import annotations
 
+import json
+import os
+import sys
 import time
 from dataclasses import dataclass
 
@@ -58,6 +61,69 @@ def _verified_mask(lower: np.ndarray, thr: np.ndarray, owner: np.ndarray, n_clau
     return ok
 
 
+def frontier_to_arrays(frontier):
+    """Structure-of-arrays form of a list of split histories: (splits [N, depth], n_splits [N])."""
+    depth = max([1] + [len(s) for s in frontier])
+    splits = np.zeros((len(frontier), depth), SPLIT_DTYPE)
+    ns = np.zeros(len(frontier), np.int32)
+    for d, s in enumerate(frontier):
+        splits[d, : len(s)] = s
+        ns[d] = len(s)
+    return splits, ns
+
+
+def save_frontier(path, frontier, inh_lo, inh_hi, prop: Property, rounds: int, domains_bounded: int):
+    """Dump of the open domain set (the reference's BaB has no checkpoint; its sweep resumes from metadata,
+    README.md:203-260).  One .npz: split histories as structure of arrays, the inherited root bounds, the property's
+    box and rows (so that a resume against another property is refused), and the counters."""
+    splits, ns = frontier_to_arrays(frontier)
+    spec, thr, owner = _rows(prop)
+    tmp = str(path) + ".tmp.npz"
+    np.savez(tmp, splits=splits, n_splits=ns, inh_lo=inh_lo, inh_hi=inh_hi, in_lo=prop.in_lo, in_hi=prop.in_hi, spec=spec,
+             thr=thr, owner=owner, rounds=np.int64(rounds), domains_bounded=np.int64(domains_bounded))
+    os.replace(tmp, path)
+
+
+def load_frontier(path, prop: Property):
+    """Inverse of save_frontier: (frontier, inh_lo, inh_hi, rounds, domains_bounded); ValueError when the dump
+    belongs to another property."""
+    z = np.load(path)
+    spec, thr, owner = _rows(prop)
+    same = (np.array_equal(z["in_lo"], prop.in_lo) and np.array_equal(z["in_hi"], prop.in_hi)
+            and z["spec"].shape == spec.shape and np.array_equal(z["spec"], spec) and np.array_equal(z["thr"], thr)
+            and np.array_equal(z["owner"], owner))
+    if not same:
+        raise ValueError("the frontier dump was written for another property")
+    splits, ns = z["splits"].astype(SPLIT_DTYPE), z["n_splits"]
+    frontier = [splits[d, : ns[d]].copy() for d in range(len(ns))]
+    return frontier, z["inh_lo"], z["inh_hi"], int(z["rounds"]), int(z["domains_bounded"])
+
+
+class _Metrics:
+    """Per-round records as JSON lines (the shape of the reference's GraphDomainBatchMetricsSink records:
+    --domain-batch-metrics-jsonl), and with NYB200_PROF=1 a stderr line per round like the reference's NY_ACASXU_PROF
+    probe (`explored= ... rate=.../s`, beta_crown/engine/core.rs:372-394)."""
+
+    def __init__(self, path):
+        self._f = open(path, "a") if path else None
+        self._prof = os.environ.get("NYB200_PROF", "") not in ("", "0")
+        self._t0 = time.time()
+
+    def round(self, **rec):
+        rec["elapsed_s"] = round(time.time() - self._t0, 6)
+        if self._f:
+            self._f.write(json.dumps(rec) + "\n")
+            self._f.flush()
+        if self._prof:
+            rate = rec["explored"] / max(rec["elapsed_s"], 1e-9)
+            print(f"[nyb200] round={rec['round']} explored={rec['explored']} open={rec['open']} "
+                  f"min_lower={rec['min_lower']:.6g} rate={rate:.0f}/s", file=sys.stderr)
+
+    def close(self):
+        if self._f:
+            self._f.close()
+
+
 def attack(eng, net_id, net, prop: Property, restarts: int = 256, steps: int = 50, seed: int = 0):
     """PGD on every atom's row from seeded uniform starts; a candidate counts only if an independent concrete forward
     pass (binary64, host) puts it inside the violation region.  Returns (x, y) or None."""
@@ -80,8 +146,11 @@ def attack(eng, net_id, net, prop: Property, restarts: int = 256, steps: int = 5
 
 def verify(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: int = 64, max_domains: int = 1 << 20,
            pgd_restarts: int = 256, pgd_steps: int = 50, optimize_iterations: int = 0, branching: int = 1,
-           timeout_s: float | None = None) -> VerifyResult:
-    """batch: domains bounded per device call; optimize_iterations: projected-Adam steps on the slopes and split
+           timeout_s: float | None = None, metrics_jsonl=None, checkpoint=None, resume=None) -> VerifyResult:
+    """metrics_jsonl: append one JSON record per round; checkpoint: path that receives the open frontier whenever the
+    run stops unresolved (round limit, timeout, domain limit); resume: path of such a dump to continue from (the attack
+    and the root bound are skipped).
+    batch: domains bounded per device call; optimize_iterations: projected-Adam steps on the slopes and split
     multipliers of every domain (0, the reference's throughput default `beta_iterations: 0`
     (beta_crown/config/beta_config.rs:1244), bounds each domain once with multipliers at zero: sound, but the search
     may then end "unknown" on properties that need the multipliers; 20 is the reference's root-level count);
@@ -91,30 +160,39 @@ def verify(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: i
         return VerifyResult("verified")
     spec, thr, owner = _rows(prop)
     n_clauses = len(prop.violation)
-    ce = attack(eng, net_id, net, prop, pgd_restarts, pgd_steps)
-    if ce is not None:
-        return VerifyResult("violated", ce[0], ce[1])
-    # root: plain CROWN with CROWN-tightened intermediate bounds
-    rlo, _, inter_lo, inter_hi = eng.crown_bounds(net_id, spec, prop.in_lo, prop.in_hi)
-    res = VerifyResult("unknown", root_lower=rlo[0].copy(), domains_bounded=1)
-    if _verified_mask(rlo, thr, owner, n_clauses)[0]:
-        res.status = "verified"
+    metrics = _Metrics(metrics_jsonl)
+    if resume is not None:
+        frontier, inh_lo, inh_hi, r0, b0 = load_frontier(resume, prop)
+        res = VerifyResult("unknown", rounds=0, domains_bounded=b0)   # max_rounds counts this call's rounds
+    else:
+        ce = attack(eng, net_id, net, prop, pgd_restarts, pgd_steps)
+        if ce is not None:
+            metrics.close()
+            return VerifyResult("violated", ce[0], ce[1])
+        # root: plain CROWN with CROWN-tightened intermediate bounds
+        rlo, _, inter_lo, inter_hi = eng.crown_bounds(net_id, spec, prop.in_lo, prop.in_hi)
+        res = VerifyResult("unknown", root_lower=rlo[0].copy(), domains_bounded=1)
+        if _verified_mask(rlo, thr, owner, n_clauses)[0]:
+            res.status = "verified"
+            metrics.close()
+            return res
+        inh_lo, inh_hi = inter_lo[0], inter_hi[0]
+        frontier = [np.zeros(0, SPLIT_DTYPE)]
+
+    def stop(status):
+        res.status = status
+        res.open_domains = len(frontier)
+        if checkpoint is not None and frontier:
+            save_frontier(checkpoint, frontier, inh_lo, inh_hi, prop, res.rounds, res.domains_bounded)
+        metrics.close()
         return res
-    inh_lo, inh_hi = inter_lo[0], inter_hi[0]
-    frontier = [np.zeros(0, SPLIT_DTYPE)]
+
     while frontier and res.rounds < max_rounds:
         if timeout_s is not None and time.time() - t0 > timeout_s:
-            res.status = "timeout"
-            res.open_domains = len(frontier)
-            return res
+            return stop("timeout")
         take, frontier = frontier[:batch], frontier[batch:]
-        depth = max(1, max(len(s) for s in take))
         D = len(take)
-        splits = np.zeros((D, depth), SPLIT_DTYPE)
-        ns = np.zeros(D, np.int32)
-        for d, s in enumerate(take):
-            splits[d, : len(s)] = s
-            ns[d] = len(s)
+        splits, ns = frontier_to_arrays(take)
         eng.batch_upload(net_id, spec, prop.in_lo, prop.in_hi, inh_lo, inh_hi, splits, ns, mode=1)
         if optimize_iterations > 1:
             eng.batch_optimize(optimize_iterations, 0.1, 0.05)
@@ -124,6 +202,11 @@ def verify(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: i
         res.rounds += 1
         res.domains_bounded += D
         done = _verified_mask(lower, thr, owner, n_clauses) | (infeasible != 0)
+        feas = lower[infeasible == 0]
+        metrics.round(round=res.rounds, batch=D, explored=res.domains_bounded, verified=int(done.sum()),
+                      infeasible=int((infeasible != 0).sum()), open=len(frontier) + int((~done).sum()),
+                      min_lower=float(feas.min()) if feas.size else float("inf"),
+                      max_depth=int(ns.max()) if D else 0)
         if done.all():
             continue
         relu, neuron, _ = eng.batch_select_branch(branching)
@@ -131,8 +214,8 @@ def verify(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: i
             if relu[d] < 0:
                 # every neuron is fixed: the bound is exact on this piece, so the piece contains a violation
                 # candidate; without a witness the honest answer is unknown
-                res.open_domains = len(frontier) + 1
-                return res
+                frontier = [take[i] for i in np.flatnonzero(~done) if i >= d] + frontier
+                return stop("unknown")
             for sign in (1, -1):
                 child = np.zeros(len(take[d]) + 1, SPLIT_DTYPE)
                 child[: len(take[d])] = take[d]
@@ -140,10 +223,7 @@ def verify(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: i
                 frontier.append(child)
         if len(frontier) > max_domains:
             break
-    res.open_domains = len(frontier)
-    if not frontier:
-        res.status = "verified"
-    return res
+    return stop("verified" if not frontier else "unknown")
 
 
 # ------------------------------------------------------------------------------------------- input split

@@ -110,3 +110,22 @@ def test_input_split_scores_known_answers():
     assert bab.select_input_dimension(lo, hi, nan_a) == 1                               # a NaN score never wins
     eq = np.array([[2.0, 1.0, 0.0]], np.float32)
     assert bab.select_input_dimension(lo, hi, eq) == 0                                  # tie 1.0 == 1.0: first wins
+
+
+def test_frontier_dump_round_trip(tmp_path):
+    from ny_b200 import bab
+    from ny_b200.engine import SPLIT_DTYPE
+
+    prop = formats.Property(np.zeros(2, np.float32), np.ones(2, np.float32),
+                            [[formats.Atom(np.array([1, -1], np.float32), 0.5)]])
+    fr = [np.zeros(0, SPLIT_DTYPE), np.array([(0, 3, 1, 0.0), (1, 2, -1, 0.25)], SPLIT_DTYPE)]
+    path = tmp_path / "frontier.npz"
+    bab.save_frontier(path, fr, np.arange(4, dtype=np.float32), np.arange(4, dtype=np.float32) + 1, prop, 3, 17)
+    f2, il, ih, rounds, bounded = bab.load_frontier(path, prop)
+    assert len(f2) == 2 and len(f2[0]) == 0 and np.array_equal(f2[1], fr[1])
+    assert il.tolist() == [0, 1, 2, 3] and ih.tolist() == [1, 2, 3, 4] and (rounds, bounded) == (3, 17)
+    other = formats.Property(prop.in_lo, prop.in_hi, [[formats.Atom(np.array([1, -1], np.float32), 0.75)]])
+    with pytest.raises(ValueError):
+        bab.load_frontier(path, other)
+    splits, ns = bab.frontier_to_arrays(fr)
+    assert splits.shape == (2, 2) and ns.tolist() == [0, 2]

@@ -43,7 +43,7 @@ def test_abs_network_quick_start_verdicts(eng):
     eng.release_network(nid)
 
 
-def test_bab_closes_the_gap_between_root_bound_and_true_minimum(eng):
+def test_bab_closes_the_gap_between_root_bound_and_true_minimum(eng, tmp_path):
     wl = W.config_mlp_bab(seed=81, hidden=12, depth=2, n_in=4, n_out=3, eps=0.4, n_fix=0)
     net = wl.net
     nid = eng.register_network(net)
@@ -71,6 +71,20 @@ def test_bab_closes_the_gap_between_root_bound_and_true_minimum(eng):
     r2 = bab.verify(eng, nid, net, prop(t_safe), batch=256, max_rounds=200, optimize_iterations=20)
     assert r2.status == "verified" and r2.rounds >= 1 and r2.open_domains == 0
     assert r2.domains_bounded < r.domains_bounded            # optimised bounds prune earlier
+    # stop after two rounds, dump the frontier, resume from the dump: same verdict, and the two legs together bound
+    # exactly the domains of the uninterrupted run; one metrics record per round
+    import json
+
+    ck, mj = tmp_path / "frontier.npz", tmp_path / "rounds.jsonl"
+    ra = bab.verify(eng, nid, net, prop(t_safe), batch=256, max_rounds=2, optimize_iterations=20, checkpoint=ck,
+                    metrics_jsonl=mj)
+    assert ra.status == "unknown" and ra.open_domains > 0 and ck.exists()
+    rb = bab.verify(eng, nid, net, prop(t_safe), batch=256, max_rounds=200, optimize_iterations=20, resume=ck,
+                    metrics_jsonl=mj)
+    assert rb.status == "verified" and rb.domains_bounded == r2.domains_bounded and ra.rounds + rb.rounds == r2.rounds
+    recs = [json.loads(line) for line in open(mj)]
+    assert len(recs) == r2.rounds and recs[-1]["open"] == 0 and recs[-1]["explored"] == r2.domains_bounded
+    assert all(rec["verified"] + rec["infeasible"] <= rec["batch"] for rec in recs)
     t_unsafe = float(mn[s] + 1e-3 * max(1.0, abs(mn[s])))
     r = bab.verify(eng, nid, net, prop(t_unsafe))
     assert r.status == "violated"
