@@ -129,3 +129,45 @@ def test_frontier_dump_round_trip(tmp_path):
         bab.load_frontier(path, other)
     splits, ns = bab.frontier_to_arrays(fr)
     assert splits.shape == (2, 2) and ns.tolist() == [0, 2]
+
+
+def test_onnx_round_trip_and_declines():
+    from ny_b200 import onnx_reader as R
+    from ny_b200 import workloads as W
+
+    g = np.random.Generator(np.random.PCG64(4))
+    mlp = W.make_mlp([7, 12, 9, 3], 5)
+    n2, shape = R.parse_onnx(R.write_onnx(mlp, (7,)))
+    assert shape == (7,) and n2.dims.tolist() == [7, 12, 9, 3]
+    assert all(np.array_equal(a, b) for a, b in zip(n2.weights, mlp.weights))
+    assert all(np.array_equal(a, b) for a, b in zip(n2.biases, mlp.biases))
+    cnn = W.make_cnn(3, in_chw=(2, 8, 8), convs=((4, 3, 1, 1), (6, 4, 2, 1)), fcs=(20, 5))
+    data = R.write_onnx(cnn, (2, 8, 8))
+    n3, shape = R.parse_onnx(data)
+    assert shape == (2, 8, 8) and n3.dims.tolist() == cnn.dims.tolist()
+    x = g.standard_normal((4, 128)).astype(np.float32)
+    assert np.array_equal(W.forward(cnn, x), W.forward(n3, x))
+    c0 = n3.weights[0]
+    assert (c0.sh, c0.ph, c0.kh, c0.oc) == (1, 1, 3, 4) and np.array_equal(c0.bias, cnn.weights[0].bias)
+    # a model that ends in a Relu gets an identity output layer
+    tail = R._enc_node("Relu", ["z2"], ["y"])
+    body = R.write_onnx(mlp, (7,))
+    graph = [v for num, wt, v in R._fields(memoryview(body)) if num == 7][0]
+    ended = R._vi(1, 8) + R._ld(7, bytes(graph) + R._ld(1, tail))
+    n4, _ = R.parse_onnx(ended)
+    assert n4.dims.tolist() == [7, 12, 9, 3, 3] and np.array_equal(n4.weights[-1], np.eye(3, dtype=np.float32))
+    # declines: an operator outside the subset, two affine layers in a row, damaged bytes
+    pool = R._vi(1, 8) + R._ld(7, bytes(graph) + R._ld(1, R._enc_node("MaxPool", ["z2"], ["y"])))
+    with pytest.raises(EngineError) as ei:
+        R.parse_onnx(pool)
+    assert ei.value.code == 1
+    lin2 = R._ld(1, R._enc_node("Gemm", ["input", "W"], ["a"], [R._enc_attr_int("transB", 1)]))
+    lin2 += R._ld(1, R._enc_node("Gemm", ["a", "W"], ["b"], [R._enc_attr_int("transB", 1)]))
+    lin2 += R._ld(5, R._enc_tensor("W", np.eye(3, dtype=np.float32))) + R._ld(11, R._enc_value_info("input", [1, 3]))
+    with pytest.raises(EngineError) as ei:
+        R.parse_onnx(R._ld(7, lin2))
+    assert ei.value.code == 1
+    with pytest.raises(EngineError):
+        R.parse_onnx(body[: len(body) // 2])
+    with pytest.raises(EngineError):
+        R.parse_onnx(b"")
