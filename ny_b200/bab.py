@@ -146,7 +146,8 @@ def attack(eng, net_id, net, prop: Property, restarts: int = 256, steps: int = 5
 
 def verify(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: int = 64, max_domains: int = 1 << 20,
            pgd_restarts: int = 256, pgd_steps: int = 50, optimize_iterations: int = 0, branching: int = 1,
-           timeout_s: float | None = None, metrics_jsonl=None, checkpoint=None, resume=None) -> VerifyResult:
+           timeout_s: float | None = None, metrics_jsonl=None, checkpoint=None, resume=None,
+           warm_start: bool = True) -> VerifyResult:
     """metrics_jsonl: append one JSON record per round; checkpoint: path that receives the open frontier whenever the
     run stops unresolved (round limit, timeout, domain limit); resume: path of such a dump to continue from (the attack
     and the root bound are skipped).
@@ -154,7 +155,8 @@ def verify(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: i
     multipliers of every domain (0, the reference's throughput default `beta_iterations: 0`
     (beta_crown/config/beta_config.rs:1244), bounds each domain once with multipliers at zero: sound, but the search
     may then end "unknown" on properties that need the multipliers; 20 is the reference's root-level count);
-    branching: 0 widest interval, 1 intercept score."""
+    branching: 0 widest interval, 1 intercept score; warm_start: with optimisation on, children start from their
+    parent's optimised slopes and split multipliers instead of the heuristic slopes and zero."""
     t0 = time.time()
     if not prop.violation:
         return VerifyResult("verified")
@@ -179,6 +181,8 @@ def verify(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: i
         inh_lo, inh_hi = inter_lo[0], inter_hi[0]
         frontier = [np.zeros(0, SPLIT_DTYPE)]
 
+    warm = {}    # id(split history) -> the parent's optimised slopes [n_pre], for children not yet bounded
+
     def stop(status):
         res.status = status
         res.open_domains = len(frontier)
@@ -193,9 +197,17 @@ def verify(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: i
         take, frontier = frontier[:batch], frontier[batch:]
         D = len(take)
         splits, ns = frontier_to_arrays(take)
-        eng.batch_upload(net_id, spec, prop.in_lo, prop.in_hi, inh_lo, inh_hi, splits, ns, mode=1)
+        alpha0 = None
+        if warm_start and optimize_iterations > 1 and all(id(s) in warm for s in take):
+            alpha0 = np.stack([warm.pop(id(s)) for s in take])
+        for s in take:
+            warm.pop(id(s), None)
+        eng.batch_upload(net_id, spec, prop.in_lo, prop.in_hi, inh_lo, inh_hi, splits, ns, mode=1, alpha=alpha0)
+        alpha1 = beta1 = None
         if optimize_iterations > 1:
             eng.batch_optimize(optimize_iterations, 0.1, 0.05)
+            if warm_start:
+                alpha1, beta1 = eng.batch_download_params()
         else:
             eng.batch_run()
         lower, _, infeasible = eng.batch_download()
@@ -219,6 +231,11 @@ def verify(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: i
             for sign in (1, -1):
                 child = np.zeros(len(take[d]) + 1, SPLIT_DTYPE)
                 child[: len(take[d])] = take[d]
+                if beta1 is not None:
+                    # children start from the parent's optimised slopes and multipliers, the new split's multiplier
+                    # from zero (AlphaState / BetaState inheritance, beta_crown/domain/child.rs)
+                    child["beta"][: len(take[d])] = beta1[d][: len(take[d])]
+                    warm[id(child)] = alpha1[d]
                 child[-1] = (int(relu[d]), int(neuron[d]), sign, 0.0)
                 frontier.append(child)
         if len(frontier) > max_domains:
