@@ -197,7 +197,16 @@ int32_t nyb200_batch_select_branch(nyb200_engine *e, int32_t *relu, int32_t *neu
  * crates/ny-propagate/src/batched_domain/domain_list/picked.rs:153-233).  `score` receives the winning value. */
 #define NYB200_BRANCH_WIDTH 0
 #define NYB200_BRANCH_INTERCEPT 1
+/* NYB200_BRANCH_BABSR: the BaBSR score (select_babsr_neuron / compute_babsr_scores,
+ * beta_crown/engine/branching/sequential.rs:106-198,784-882; score kernel branching/score.rs:28-97): per domain the
+ * specification rows are carried backwards through the Linear layers with the ReLUs' upper slopes, and a neuron's score is
+ * the mean over rows of |min(b c (r0 - 1), b c r0) + min(c, 0) r1| with r0 = max(u,0)/(max(u,0) - min(l,0)),
+ * r1 = -min(l,0) r0, b the producing layer's bias.  Linear layers only (NYB200_ERR_UNSUPPORTED otherwise).
+ * nyb200_batch_download_branch_scores returns the scores of the last BaBSR selection, [D x n_pre], -1 for neurons that
+ * are not candidates (stable or split) and for the output block. */
+#define NYB200_BRANCH_BABSR 2
 int32_t nyb200_batch_select_branch_scored(nyb200_engine *e, int32_t kind, int32_t *relu, int32_t *neuron, float *score);
+int32_t nyb200_batch_download_branch_scores(nyb200_engine *e, float *scores);
 
 /* ---- alpha/beta optimisation of the resident batch ---------------------------------------------
  * Projected-Adam ascent on every domain's lower slopes alpha (unstable unsplit neurons, kept in [0,1]:

@@ -155,7 +155,7 @@ def verify(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: i
     multipliers of every domain (0, the reference's throughput default `beta_iterations: 0`
     (beta_crown/config/beta_config.rs:1244), bounds each domain once with multipliers at zero: sound, but the search
     may then end "unknown" on properties that need the multipliers; 20 is the reference's root-level count);
-    branching: 0 widest interval, 1 intercept score; warm_start: with optimisation on, children start from their
+    branching: 0 widest interval, 1 intercept score, 2 BaBSR (Linear layers only); warm_start: with optimisation on, children start from their
     parent's optimised slopes and split multipliers instead of the heuristic slopes and zero."""
     t0 = time.time()
     if not prop.violation:

@@ -855,7 +855,8 @@ int32_t nyb200_batch_select_branch(nyb200_engine *e, int32_t *relu, int32_t *neu
 
 int32_t nyb200_batch_select_branch_scored(nyb200_engine *e, int32_t kind, int32_t *relu, int32_t *neuron, float *width) {
     if (!e || !relu || !neuron) return NYB200_ERR_INVALID;
-    if (kind != NYB200_BRANCH_WIDTH && kind != NYB200_BRANCH_INTERCEPT) return set_err(e, NYB200_ERR_INVALID, "unknown branching score");
+    if (kind != NYB200_BRANCH_WIDTH && kind != NYB200_BRANCH_INTERCEPT && kind != NYB200_BRANCH_BABSR)
+        return set_err(e, NYB200_ERR_INVALID, "unknown branching score");
     std::lock_guard<std::mutex> g(e->mu);
     NYB_CUDA(e, cudaSetDevice(e->device));
     NYB_TRY(finish_batch(e));
@@ -867,11 +868,29 @@ int32_t nyb200_batch_select_branch_scored(nyb200_engine *e, int32_t kind, int32_
     NYB_WS(dr, int *, e, "br_relu", (size_t)D * 4);
     NYB_WS(dn, int *, e, "br_neuron", (size_t)D * 4);
     NYB_WS(dw, float *, e, "br_width", (size_t)D * 4);
-    launch_select_branch(e, net->v, D, p.pre_lo, p.pre_hi, p.code, dr, dn, dw, kind);
+    if (kind == NYB200_BRANCH_BABSR) NYB_TRY(babsr_select(e, *net, e->batch, p, dr, dn, dw, nullptr));
+    else launch_select_branch(e, net->v, D, p.pre_lo, p.pre_hi, p.code, dr, dn, dw, kind);
     NYB_CUDA(e, cudaGetLastError());
     NYB_CUDA(e, cudaMemcpyAsync(relu, dr, (size_t)D * 4, cudaMemcpyDeviceToHost, e->stream));
     NYB_CUDA(e, cudaMemcpyAsync(neuron, dn, (size_t)D * 4, cudaMemcpyDeviceToHost, e->stream));
     if (width) NYB_CUDA(e, cudaMemcpyAsync(width, dw, (size_t)D * 4, cudaMemcpyDeviceToHost, e->stream));
+    NYB_CUDA(e, cudaStreamSynchronize(e->stream));
+    return NYB200_OK;
+}
+
+int32_t nyb200_batch_download_branch_scores(nyb200_engine *e, float *scores) {
+    if (!e || !scores) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    NYB_CUDA(e, cudaSetDevice(e->device));
+    if (!e->batch.valid || !e->batch.ran) return set_err(e, NYB200_ERR_INVALID, "no batch has been run");
+    Net *net;
+    NYB_TRY(find_net(e, e->batch.net_id, &net));
+    auto it = e->ws.find("babsr_score");
+    const NetView &nv = net->v;
+    if (it == e->ws.end() || it->second.bytes < (size_t)e->batch.D * nv.nps * 4)
+        return set_err(e, NYB200_ERR_INVALID, "no BaBSR selection has been made for this batch");
+    size_t w = (size_t)nv.n_pre * 4;
+    NYB_CUDA(e, cudaMemcpy2DAsync(scores, w, it->second.p, (size_t)nv.nps * 4, w, (size_t)e->batch.D, cudaMemcpyDeviceToHost, e->stream));
     NYB_CUDA(e, cudaStreamSynchronize(e->stream));
     return NYB200_OK;
 }

@@ -203,6 +203,8 @@ int crown_bounds(nyb200_engine *e, int net_id, const float *spec, int S, const f
 // ---- parameter optimisation (nyb200_optimize.cu) ----
 // grad_host != nullptr: one evaluation plus the adjoint pass, gradients [D x n_pre] to the host, no update
 int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg, float *grad_host = nullptr);
+int babsr_select(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int *relu, int *neuron, float *best,
+                 float **score_dev);
 // Cooperative cancellation: true once the armed deadline has passed.
 bool deadline_passed(const nyb200_engine *e);
 // What a multi-launch call does when the deadline has passed: drain the stream, drop the run, report.

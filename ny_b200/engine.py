@@ -40,7 +40,7 @@ EXPORTS = [
     "nyb200_net_create_layers", "nyb200_pgd_attack", "nyb200_batch_select_branch_scored",
     "nyb200_crown_bounds", "nyb200_batch_download_alpha_upper",
     "nyb200_batch_verdicts", "nyb200_gemm_f64", "nyb200_conv_transpose_2d", "nyb200_set_deadline_ns",
-    "nyb200_batch_gradient", "nyb200_point_vjp_batched", "nyb200_crown_input_coeffs",
+    "nyb200_batch_gradient", "nyb200_point_vjp_batched", "nyb200_crown_input_coeffs", "nyb200_batch_download_branch_scores",
 ]
 
 
@@ -119,6 +119,7 @@ def load_library():
     L.nyb200_set_deadline_ns.argtypes = [vp, C.c_int64]
     L.nyb200_batch_gradient.argtypes = [vp, C.c_int32, fp]
     L.nyb200_crown_input_coeffs.argtypes = [vp, fp, fp]
+    L.nyb200_batch_download_branch_scores.argtypes = [vp, fp]
     L.nyb200_point_vjp_batched.argtypes = [vp, C.c_int32, C.c_int32, fp, fp, fp, fp, fp]
     _lib = L
     return L
@@ -571,6 +572,13 @@ class B200Engine:
         r, j, w = np.empty(D, np.int32), np.empty(D, np.int32), np.empty(D, np.float32)
         self._check(self._L.nyb200_batch_select_branch_scored(self._h, kind, _ip(r), _ip(j), _fp(w)))
         return r, j, w
+
+    def batch_branch_scores(self) -> np.ndarray:
+        """Scores of the last BaBSR selection (batch_select_branch(2)), [D, n_pre]; -1 marks non-candidates."""
+        D, S, n_pre = self._batch_shape
+        sc = np.empty((D, n_pre), np.float32)
+        self._check(self._L.nyb200_batch_download_branch_scores(self._h, _fp(sc)))
+        return sc
 
     def timing_enable(self, per_kernel: bool):
         self._check(self._L.nyb200_timing_enable(self._h, 1 if per_kernel else 0))

@@ -498,3 +498,69 @@ def optimize_dual(net: Net, lo, hi, pre_lo, pre_hi, splits: np.ndarray, alpha, i
     lib().nyo_optimize_dual(C.byref(net.c), _fp(lo), _fp(hi), _fp(pre_lo), _fp(pre_hi), splits.ctypes.data, len(splits),
                             _fp(alpha), iterations, lr_alpha, lr_beta, lr_decay, clip_beta, 2, _fp(bl), _fp(bu), _fp(aup))
     return bl, bu, alpha, aup, splits
+
+
+def babsr_scores(weights, biases, spec, pre_lo, pre_hi, split_mask=None):
+    """numpy restatement of the reference's BaBSR scores for one domain of a dense sequential ReLU network
+    (compute_babsr_scores, crates/ny-propagate/src/beta_crown/engine/branching/sequential.rs:784-882, with
+    compute_babsr_score_parts, branching/score.rs:28-97, and relu_upper_slope, branching/mod.rs:93-111; reduce op Min
+    as select_babsr_neuron uses it).  The specification rows play the role of the last Linear layer.
+    pre_lo / pre_hi: [n_pre] pre-activation bounds of the domain (already clamped by its splits); split_mask: [n_pre]
+    bool, True for split neurons.  Returns (scores [n_hidden] float32, -1 for neurons that are not candidates,
+    (relu, neuron) of the first maximum or (-1, -1))."""
+    f32 = np.float32
+    dims = [w.shape[0] for w in weights]
+    offs = np.concatenate([[0], np.cumsum(dims)]).astype(int)
+    n_hidden = int(offs[len(weights) - 1])
+    scores = np.full(n_hidden, -1.0, f32)
+    C = np.asarray(spec, f32)
+    for k in range(len(weights) - 1, 0, -1):
+        C = (C.astype(np.float64) @ np.asarray(weights[k], np.float64)).astype(f32)
+        off, n = int(offs[k - 1]), dims[k - 1]
+        b = np.zeros(n, f32) if biases[k - 1] is None else np.asarray(biases[k - 1], f32)
+        for j in range(n):
+            l, u = f32(pre_lo[off + j]), f32(pre_hi[off + j])
+            have = np.isfinite(l) and np.isfinite(u)
+            r0 = r1 = f32(0)
+            if have:
+                lt, ut = min(l, f32(0)), max(u, f32(0))
+                w = f32(ut - lt)
+                if abs(w) <= f32(1e-6):
+                    have = False
+                else:
+                    r0 = f32(ut / w)
+                    r1 = f32(-lt * r0)
+                    have = bool(np.isfinite(r0) and np.isfinite(r1))
+            col = C[:, j]
+            ok, total = have, 0.0
+            if ok:
+                for c in col:
+                    if not np.isfinite(c):
+                        ok = False
+                        break
+                    ic = f32(min(c, f32(0)) * r1)
+                    bs = f32(b[j] * c)
+                    bc = min(f32(bs * f32(r0 - f32(1))), f32(bs * r0))
+                    mc = f32(abs(f32(bc + ic)))
+                    if not (np.isfinite(ic) and np.isfinite(mc)):
+                        ok = False
+                        break
+                    total += float(mc)
+            cand = l < 0 and u > 0 and not (split_mask is not None and split_mask[off + j])
+            if cand:
+                scores[off + j] = f32(total / len(col)) if ok else f32(0)
+            if not (np.isfinite(l) and np.isfinite(u)) or l >= 0:
+                slope = f32(1)
+            elif u <= 0:
+                slope = f32(0)
+            else:
+                slope = f32(u / max(f32(u - l), f32(1e-8)))
+            C[:, j] = (col * slope).astype(f32)
+    best, pick = f32(-1), -1
+    for i, s in enumerate(scores):
+        if s > best:
+            best, pick = s, i
+    if pick < 0:
+        return scores, (-1, -1)
+    r = int(np.searchsorted(offs[1:], pick, side="right"))
+    return scores, (r, pick - int(offs[r]))

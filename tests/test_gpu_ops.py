@@ -196,3 +196,49 @@ def test_point_vjp_batched_matches_numpy(eng):
     with pytest.raises(EngineError):
         eng.point_vjp_batched(nid, rows, x=x, masks=mk)
     eng.release_network(nid)
+
+
+def test_babsr_scores_and_picks_match_oracle(eng, oracle):
+    wl = W.config_mlp_bab(seed=37, hidden=40, depth=3, n_in=30, eps=0.04, n_fix=3)
+    onet, ospec, nid, rl, ru = _setup(eng, oracle, wl)
+    D = 32
+    splits, ns = W.draw_domains(wl, rl, ru, D)
+    ns = ns.copy()
+    ns[0] = 0
+    eng.batch_upload(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, splits, ns, mode=1)
+    eng.batch_run()
+    _, _, inf = eng.batch_download()
+    relu, neuron, best = eng.batch_select_branch(2)
+    scores = eng.batch_branch_scores()
+    pl, pu = eng.batch_download_pre_bounds()
+    dims = wl.net.dims
+    offs = np.concatenate([[0], np.cumsum(dims[1:])]).astype(int)
+    n_hidden = int(offs[len(wl.net.weights) - 1])
+    tol = 1e-5 if eng.path_name == "f64" else 1e-3
+    agree = 0
+    for d in range(D):
+        mask = np.zeros(wl.net.n_pre, bool)
+        for s in splits[d][: ns[d]]:
+            mask[int(offs[s["relu"]] + s["neuron"])] = True
+        sc, pick = oracle.babsr_scores(wl.net.weights, wl.net.biases, wl.spec, pl[d], pu[d], mask)
+        got = scores[d][:n_hidden]
+        assert np.array_equal(got < 0, sc < 0)                          # same candidate set
+        assert np.all(scores[d][n_hidden:] == -1)
+        cand = sc >= 0
+        if cand.any():
+            assert np.abs(got[cand] - sc[cand]).max() <= tol * max(float(sc[cand].max()), 1e-6)
+            top = np.sort(sc[cand])[::-1]
+            clear = len(top) == 1 or top[0] - top[1] > 4 * tol * top[0]
+            if clear:
+                assert (int(relu[d]), int(neuron[d])) == pick
+                agree += 1
+            assert abs(best[d] - top[0]) <= tol * max(float(top[0]), 1e-6)
+        else:
+            assert relu[d] == -1 and neuron[d] == -1
+    assert agree >= D // 2
+    # driven from the search: the BaBSR choice is a valid split everywhere (unstable, unsplit neuron)
+    for d in range(D):
+        if relu[d] >= 0:
+            o = int(offs[relu[d]] + neuron[d])
+            assert pl[d][o] < 0 < pu[d][o]
+    eng.release_network(nid)

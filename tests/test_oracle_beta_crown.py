@@ -202,3 +202,26 @@ def test_dual_alpha_upper_gradient_and_optimisation(oracle):
     dl, du, _, aup1, _ = oracle.optimize_dual(net, wl.in_lo, wl.in_hi, pl, pu, sp, a0, 15, 0.1, 0.05)
     assert np.array_equal(dl, bl) and np.all(du <= bu + 1e-6) and du.sum() < bu.sum()
     assert np.all((aup1 >= 0) & (aup1 <= 1))
+
+
+def test_babsr_scores_hand_case():
+    """1 -> 2 -> 1 with W1 = (1, -1), b1 = (0.5, 0), W2 = (1, 1), one spec row (1), both neurons on [-1, 1]:
+    r0 = 1/2, r1 = 1/2, c = 1 for both; neuron 0: |min(0.5 * (-1/2), 0.5 * 1/2) + 0| = 0.25, neuron 1 (no bias): 0.
+    A split neuron and a stable one are not candidates (-1)."""
+    import numpy as np
+    from oracle import ny_oracle as O
+
+    ws = [np.array([[1.0], [-1.0]], np.float32), np.array([[1.0, 1.0]], np.float32)]
+    bs = [np.array([0.5, 0.0], np.float32), None]
+    spec = np.array([[1.0]], np.float32)
+    sc, pick = O.babsr_scores(ws, bs, spec, np.array([-1, -1, 0], np.float32), np.array([1, 1, 0], np.float32))
+    assert sc.tolist() == [0.25, 0.0] and pick == (0, 0)
+    sc, pick = O.babsr_scores(ws, bs, spec, np.array([-1, -1, 0], np.float32), np.array([1, 1, 0], np.float32),
+                              split_mask=np.array([True, False, False]))
+    assert sc.tolist() == [-1.0, 0.0] and pick == (0, 1)
+    sc, pick = O.babsr_scores(ws, bs, spec, np.array([0.5, 0.1, 0], np.float32), np.array([1, 1, 0], np.float32))
+    assert sc.tolist() == [-1.0, -1.0] and pick == (-1, -1)
+    # negative coefficient: the intercept term min(c, 0) * r1 enters; spec row (-1): c = -1, b = 0.5:
+    # |min(-0.5 * (-1/2), -0.5 * 1/2) + (-1) * 1/2| = |-0.25 - 0.5| = 0.75
+    sc, _ = O.babsr_scores(ws, bs, -spec, np.array([-1, -1, 0], np.float32), np.array([1, 1, 0], np.float32))
+    assert sc.tolist() == [0.75, 0.5]
