@@ -108,7 +108,7 @@ typedef struct nyb200_layer_desc {
      * j + 1 = the post-activation output of layer j (j <= this layer - 2, same width as this layer's output)
      * is added to this layer's output before its ReLU: pre = W z + b + relu(pre_j).  Skips must not overlap
      * or nest.  Supported by the interval pass, the bound batch entry points, the parameter optimisation and the
-     * attack; the CROWN-IBP pipeline declines such networks (NYB200_ERR_UNSUPPORTED). */
+     * attack, and the CROWN-IBP pipeline. */
     int32_t skip_from;
 } nyb200_layer_desc;
 int32_t nyb200_net_create_layers(nyb200_engine *e, int32_t n_layers, const nyb200_layer_desc *layers,
@@ -157,7 +157,7 @@ int32_t nyb200_bab_bound_batch(nyb200_engine *e, int32_t net_id, const float *sp
  * the full pass and tightened (crown/tighten.rs:126-190).  D boxes in lock-step: in_lo/in_hi [D x dims[0]]
  * with box_stride = dims[0], or one box with box_stride = 0 and D = 1.  out_lo/out_hi [D x S];
  * inter_lo/inter_hi (may be NULL) receive the tightened pre-activation bounds [D x sum_{k>=1} dims[k]].
- * Linear and Conv2d layers; networks with residual connections are declined (NYB200_ERR_UNSUPPORTED). */
+ * Linear and Conv2d layers, identity skips included. */
 int32_t nyb200_crown_bounds(nyb200_engine *e, int32_t net_id, const float *spec, int32_t S, const float *in_lo,
                             const float *in_hi, int32_t box_stride, int32_t D, float *out_lo, float *out_hi,
                             float *inter_lo, float *inter_hi);

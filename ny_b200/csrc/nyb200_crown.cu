@@ -206,7 +206,6 @@ static int crown_bounds_once(nyb200_engine *e, int net_id, const float *spec, in
     if (D <= 0 || S <= 0) return set_err(e, NYB200_ERR_SHAPE, "D and S must be positive");
     if (box_stride != 0 && box_stride != nv.dims[0]) return set_err(e, NYB200_ERR_SHAPE, "box_stride must be 0 or dims[0]");
     if (box_stride == 0 && D != 1) return set_err(e, NYB200_ERR_SHAPE, "a shared box is one domain: D must be 1");
-    if (net->has_skip()) return set_err(e, NYB200_ERR_UNSUPPORTED, "the CROWN-IBP collection is built for sequential networks only");
     int max_rows = S;
     for (int k = 1; k < nv.L; ++k) max_rows = nv.dims[k] > max_rows ? nv.dims[k] : max_rows;
     if ((long)D * 2 * max_rows > 0x7fffffffL / 64) return set_err(e, NYB200_ERR_UNSUPPORTED, "batch too large for one call");
@@ -250,6 +249,8 @@ static int crown_bounds_once(nyb200_engine *e, int net_id, const float *spec, in
         const float *zl = k == 0 ? p.in_lo : p.zl + nv.pre_off[k - 1], *zu = k == 0 ? p.in_hi : p.zu + nv.pre_off[k - 1];
         if (net->is_conv(k)) launch_ibp_conv(e, nv, net->geom[k], k, D, zl, zu, k == 0 ? (long)box_stride : np, p.raw_lo, p.raw_hi, p.q, np);
         else launch_ibp_linear(e, nv, k, D, zl, zu, k == 0 ? (long)box_stride : np, p.raw_lo, p.raw_hi, p.q, np);
+        if (net->skip_of(k) >= 0)  // pre_k = W z + b + relu(pre_j): the identity branch joins with its tightened interval
+            launch_skip_interval(e, D, n, np, p.raw_lo, p.raw_hi, off, p.zl, p.zu, nv.pre_off[net->skip_of(k)]);
         const float *c_lo = nullptr, *c_hi = nullptr;
         if (relu) {
             Batch bk = b;
