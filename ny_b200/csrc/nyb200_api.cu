@@ -408,7 +408,7 @@ int run_forward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int fw
             float *cols = (float *)ws_get(e, "conv_cols", (size_t)2 * D * plane * N * 4);
             if (!cols) return NYB200_ERR_OOM;
             NYB_TRY(launch_umma(e, net.umma_fwd[k], 2 * D * plane, zl, (int)np, cols, N, derr, plane));
-            launch_ibp_conv_gather(e, nv, g, k, D, cols, umma_eps(g.ic) * 1.000001, p.raw_lo, p.raw_hi, p.q, (long)np);
+            launch_ibp_conv_gather(e, nv, g, k, D, cols, umma_eps(g.ic, 1) * 1.000001, p.raw_lo, p.raw_hi, p.q, (long)np);
         }
         else if (net.is_conv(k)) launch_ibp_conv(e, nv, net.geom[k], k, Deff, zl, zu, in_ds, p.raw_lo, p.raw_hi, p.q, (long)np);
         else launch_ibp_linear(e, nv, k, Deff, zl, zu, in_ds, p.raw_lo, p.raw_hi, p.q, (long)np);
@@ -419,7 +419,7 @@ int run_forward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int fw
         launch_ibp_finish(e, nv, k, D, fwd_mode, p.raw_lo, p.raw_hi, raw_ds, fwd_mode == 2 ? nullptr : p.inh_lo,
                           fwd_mode == 2 ? nullptr : p.inh_hi, p.code, p.sbeta, b.has_alpha ? p.alpha : nullptr, p.pre_lo,
                           p.pre_hi, p.zl, p.zu, p.tab, p.zabs, p.flags, tk ? Fl : nullptr, ldf,
-                          tk ? umma_eps(nv.dims[k]) * 1.000001 : 0.0, p.q, tk ? fwd_tol : 0.f);
+                          tk ? umma_eps(nv.dims[k], 1) * 1.000001 : 0.0, p.q, tk ? fwd_tol : 0.f);
     }
     NYB_CUDA(e, cudaGetLastError());
     return NYB200_OK;

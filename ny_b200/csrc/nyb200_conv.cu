@@ -419,6 +419,7 @@ int prepare_conv_forward_operand(nyb200_engine *e, const float *W, const ConvGeo
     k_build_conv_fwd<<<(unsigned)((n + 255) / 256), 256, 0, e->stream>>>(W, g.oc, g.ic, kk, split ? 1 : 0, tmp);
     e->launches++;
     int st = umma_prepare_layer(e, tmp, g.ic, N, out);
+    if (split) out->chain = 1;  // interval products: see umma_prepare_forward_layer
     cudaStreamSynchronize(e->stream);
     cudaFree(tmp);
     return st;

@@ -43,6 +43,7 @@ struct ConvGeom {
 struct UmmaLayer {
     float *wh = nullptr, *wl = nullptr;
     int K = 0, N = 0, kpad = 0;
+    int chain = 0;  // K stages per tensor-memory accumulation chain for this operand; 0 = the kernel's default
     alignas(64) unsigned char tm_hi[128];
     alignas(64) unsigned char tm_lo[128];
 };
@@ -250,7 +251,7 @@ int umma_prepare_layer(nyb200_engine *e, const float *W, int K, int N, UmmaLayer
 // k at A[m * lda + k * a_plane + p], result column n at C[(m * N + n) * a_plane + p] (ldc unused).
 int launch_umma(nyb200_engine *e, const UmmaLayer &L, int M, const float *A, int lda, float *C, int ldc, int *err,
                 int a_plane = 0);
-double umma_eps(int K);
+double umma_eps(int K, int chain = 0);
 // Builds the forward-pass operand of Linear_k: the [n_in x 2 n_out] matrix (W+^T | W-^T).
 int umma_prepare_forward_layer(nyb200_engine *e, const float *W, int n_in, int n_out, UmmaLayer *out);
 // raw_lo/raw_hi/q of Linear_k from the two products Fl = zl * (W+|W-), Fu = zu * (W+|W-) (zl >= 0).

@@ -9,7 +9,7 @@
 //               commits each stage back to the producers and each finished chunk to the epilogue.
 //   warp 2      allocates / frees the 512 tensor-memory columns (two 128x256 fp32 accumulators).
 //   warps 4-11  epilogue: a K range is accumulated in tensor memory only over a short chain
-//               (CHUNK_STAGES stages = 12 MMA steps); each finished chunk is read with tcgen05.ld (one
+//               (CHUNK_STAGES stages of 12 MMA steps each); each finished chunk is read with tcgen05.ld (one
 //               TMEM lane = one output row per thread, 128 columns per warp) and added in fp32
 //               registers, alternating between the two accumulators so that the drain of one chunk
 //               overlaps the MMAs of the next; the row sums are stored after the last chunk.
@@ -33,8 +33,12 @@
 //   (truncating adder), i.e. <= 2^-23 * (accumulated magnitude) per step.  Inside a chain the eight
 //   cross-term steps are issued first, while the accumulator holds only terms of size 2^-10 S, so they
 //   cost 8 * 2^-33 S; the four Ah*Wh steps cost 4 * 2^-23 S.  The chunk sums are added in
-//   round-to-nearest fp32 (2^-24 * S each).  Keeping the full-scale chain at 4 steps instead of
-//   12 * K/32 is what keeps the certified bounds within 1e-4 of the binary64 path.
+//   round-to-nearest fp32 (2^-24 * S each).  A chain holds CHUNK_STAGES stages: with two (the default) the
+//   second stage's eight cross-term steps meet a full-size accumulator, so a chain costs
+//   (8 + 8) * 2^-23 of its own magnitude instead of 4 * 2^-23, and the kernel hands an accumulator to the
+//   epilogue half as often: 12% off the contraction time of the 8 x 256 network for a rate of 2.9e-6 instead of
+//   1.7e-6 at K = 256.  Keeping the chain short (instead of 12 * K/32 steps) is what keeps the certified bounds
+//   within 1e-4 of the binary64 path; a batch whose charge still shows is re-evaluated in binary64 by the caller.
 #include <cuda.h>
 
 #include <cstdlib>
@@ -60,11 +64,15 @@ constexpr int THREADS = 512;
 constexpr int REGS_LAUNCH = 65536 / THREADS, REGS_CONTROL = 40, REGS_EPILOGUE = 184, REGS_PRODUCER = 104;
 static_assert(4 * 32 * REGS_CONTROL + 8 * 32 * REGS_EPILOGUE + 4 * 32 * REGS_PRODUCER <= THREADS * REGS_LAUNCH,
               "setmaxnreg targets exceed the CTA's register allocation: the epilogue's setmaxnreg.inc would block");
-// K stages (of 32) accumulated in one tensor-memory chain before the chunk is drained (default 1;
-// NYB200_CHUNK_STAGES overrides it for experiments, the rounding model follows the value in use).
-static int chunk_stages_cfg() {
-    static int v = [] { const char *s = getenv("NYB200_CHUNK_STAGES"); int x = s ? atoi(s) : 1; return x < 1 ? 1 : (x > 64 ? 64 : x); }();
-    return v;
+// K stages (of 32) accumulated in one tensor-memory chain before the chunk is drained: two for contractions of
+// eight stages or more (K > 224), where halving the hand-offs to the epilogue pays (12% of the contraction time of
+// the 8 x 256 network), one for shorter ones, which hand over at most seven times per tile anyway and whose callers
+// (convolutions, narrow layers on small boxes) are the ones sensitive to the rounding rate.  NYB200_CHUNK_STAGES
+// overrides the choice for every launch; the rounding model follows the value in use.
+static int chunk_stages_cfg(int K) {
+    static int forced = [] { const char *s = getenv("NYB200_CHUNK_STAGES"); int x = s ? atoi(s) : 0; return x < 0 ? 0 : (x > 64 ? 64 : x); }();
+    if (forced > 0) return forced;
+    return (K + BK - 1) / BK >= 8 ? 2 : 1;
 }
 constexpr unsigned SPIN_LIMIT = 1u << 24;
 
@@ -557,7 +565,7 @@ int launch_umma(nyb200_engine *e, const UmmaLayer &L, int M, const float *A, int
         tm_a = *(const CUtensorMap *)L.tm_hi;  // unused by the kernel in this form; any valid map
     }
     k_umma_tf32x3<<<grid, THREADS, SMEM_BYTES, e->stream>>>(*(const CUtensorMap *)L.tm_hi, *(const CUtensorMap *)L.tm_lo, tm_a, A,
-                                                            lda, C, ldc, M, L.N, L.K, chunk_stages_cfg(), err, a_plane, a_tma);
+                                                            lda, C, ldc, M, L.N, L.K, L.chain > 0 ? L.chain : chunk_stages_cfg(L.K), err, a_plane, a_tma);
     e->launches++;
     return NYB200_OK;
 }
@@ -578,6 +586,9 @@ int umma_prepare_forward_layer(nyb200_engine *e, const float *W, int n_in, int n
     k_build_wpm<<<(unsigned)((n + 255) / 256), 256, 0, e->stream>>>(W, n_in, n_out, tmp);
     e->launches++;
     int st = umma_prepare_layer(e, tmp, n_in, 2 * n_out, out);
+    // interval products keep one stage per chain: their slack is compared against every unstable neuron's width
+    // and compounds through the layers, where the coefficient products' charge is only compared against the bound
+    out->chain = 1;
     cudaStreamSynchronize(e->stream);
     cudaFree(tmp);
     return st;
@@ -615,17 +626,17 @@ void launch_ibp_combine(nyb200_engine *e, int D, int n_out, const float *Fl, con
 }
 
 // Worst-case relative rounding of this kernel's product against S = |A||W| (see the model above).
-double umma_eps(int K) {
+double umma_eps(int K, int chain) {
     int k_stages = (K + BK - 1) / BK;
-    const int CS = chunk_stages_cfg();
+    const int CS = chain > 0 ? chain : chunk_stages_cfg(K);
     int cs = k_stages < CS ? k_stages : CS;
     int chunks = (k_stages + CS - 1) / CS;
     const double u23 = 1.1920928955078125e-07, u24 = 5.9604644775390625e-08;
     double rep = 0.75 * 9.5367431640625e-07;                    // operand split, 0.75 * 2^-20
     double chain_main = (double)(cs * (BK / 8)) * u23;          // Ah*Wh steps round at the scale of S
-    // the cross-term steps of the first stage meet an accumulator of size 2^-10 S; with more than one
-    // stage per chain those of later stages meet a full-size accumulator
-    double chain_cross = (double)((BK / 8) * 2) * u23 * (cs > 1 ? (double)cs : 9.765625e-04 /* 2^-10 */);
+    // the cross-term steps of a chain's first stage meet an accumulator of size 2^-10 S, those of its later
+    // stages a full-size one
+    double chain_cross = (double)((BK / 8) * 2) * u23 * ((double)(cs - 1) + 9.765625e-04 /* 2^-10 */);
     return rep + chain_main + chain_cross + (double)chunks * u24;
 }
 
