@@ -243,6 +243,36 @@ def verify(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: i
     return stop("verified" if not frontier else "unknown")
 
 
+def verify_root(eng, net_id, net, prop: Property, method: str = "crown") -> VerifyResult:
+    """One bound of the whole box, no search (`ny verify --method ibp|crown`): verified when the interval pass (ibp)
+    or plain CROWN with CROWN-tightened intermediates (crown) refutes every clause, violated when the box's centre
+    is a counterexample, unknown otherwise."""
+    if not prop.violation:
+        return VerifyResult("verified")
+    spec, thr, owner = _rows(prop)
+    if method == "ibp":
+        pl, pu = eng.ibp_forward_gpu(net_id, prop.in_lo, prop.in_hi)
+        n_out = int(net.dims[-1])
+        ylo, yhi = pl[0][-n_out:].astype(np.float64), pu[0][-n_out:].astype(np.float64)
+        s64 = spec.astype(np.float64)
+        low = (np.maximum(s64, 0) * ylo[None] + np.minimum(s64, 0) * yhi[None]).sum(axis=1)
+        lower = np.nextafter(low.astype(np.float32), np.float32(-np.inf))[None]   # binary64 sum, cast, one ulp down
+    elif method == "crown":
+        lower, _, _, _ = eng.crown_bounds(net_id, spec, prop.in_lo, prop.in_hi)
+    else:
+        raise ValueError(f"unknown method {method}")
+    res = VerifyResult("unknown", root_lower=lower[0].copy(), domains_bounded=1)
+    if _verified_mask(lower, thr, owner, len(prop.violation))[0]:
+        res.status = "verified"
+        return res
+    x = ((prop.in_lo.astype(np.float64) + prop.in_hi.astype(np.float64)) * 0.5).astype(np.float32)
+    y = forward(net, x)
+    if _violates(prop, y):
+        return VerifyResult("violated", x, y, 0, 1, 0, res.root_lower)
+    res.open_domains = 1
+    return res
+
+
 # ------------------------------------------------------------------------------------------- input split
 def input_split_scores(in_lo, in_hi, lower_a=None, lower=None, thr=None, coeff_thresh: float = 1e-3,
                        margin_weight: float = 1.0):

@@ -150,3 +150,38 @@ def test_input_split_on_an_acas_shaped_network(eng):
     assert float(row @ W.forward(net, r.counterexample)) <= t_unsafe
     assert np.all(r.counterexample >= lo) and np.all(r.counterexample <= hi)
     eng.release_network(nid)
+
+
+def test_command_line_surface_and_exit_codes(tmp_path):
+    """`python -m ny_b200 beta-crown|verify MODEL -p PROPERTY`: the reference's result block and exit codes
+    (0 proved, 1 falsified, 2 unknown, 4 operational error) on the quick-start network."""
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    model = tmp_path / "abs.nnet"
+    model.write_text(ABS_NNET)
+    safe, unsafe = tmp_path / "safe.vnnlib", tmp_path / "unsafe.vnnlib"
+    safe.write_text(_prop(">=", 2.0))
+    unsafe.write_text(_prop(">=", 0.5))
+    env = dict(os.environ, PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
+
+    def run(*args):
+        r = subprocess.run([sys.executable, "-m", "ny_b200", *args], env=env, cwd=root, capture_output=True, text=True, timeout=300)
+        return r.returncode, r.stdout
+
+    rc, out = run("beta-crown", str(model), "-p", str(safe))
+    assert rc == 0 and "Status: VERIFIED" in out
+    rc, out = run("beta-crown", str(model), "-p", str(unsafe))
+    assert rc == 1 and "Status: VIOLATED" in out and "Counterexample input" in out
+    rc, out = run("beta-crown", str(model), "-p", str(safe), "--input-split")
+    assert rc == 0 and "Status: VERIFIED" in out
+    rc, out = run("verify", str(model), "-p", str(safe), "--method", "crown")
+    assert rc == 0
+    rc, out = run("verify", str(model), "-p", str(safe), "--method", "ibp")      # the interval pass only reaches y <= 2
+    assert rc == 2 and "Status: UNKNOWN" in out
+    rc, out = run("verify", str(model), "-p", str(safe), "--method", "ibp", "--allow-unknown")
+    assert rc == 0
+    rc, out = run("beta-crown", str(tmp_path / "missing.nnet"), "-p", str(safe))
+    assert rc == 4
