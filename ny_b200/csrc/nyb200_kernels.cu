@@ -444,7 +444,7 @@ __device__ __forceinline__ void relax_dom_rows(int r0, int r1, long m0, int j, f
             o.y = relax_one<UPPER, RELAX, BIAS>(a[u].y, t1, au.y, za.y, qv.y, bk.y, eps, sb, sa, sp);
             o.z = relax_one<UPPER, RELAX, BIAS>(a[u].z, t2, au.z, za.z, qv.z, bk.z, eps, sb, sa, sp);
             o.w = relax_one<UPPER, RELAX, BIAS>(a[u].w, t3, au.w, za.w, qv.w, bk.w, eps, sb, sa, sp);
-            if (RELAX && live) *(float4 *)(A + m * lda + j) = o;
+            if (RELAX && live) __stcs((float4 *)(A + m * lda + j), o);  // streamed: the next reader is another kernel
             // The magnitude sum only ever enters the bound as 2^-40 * rabs (the slack for the binary64 bias
             // sums), so it is folded into the penalty here instead of being reduced on its own; the penalty
             // is reduced in fp32 (five shuffles) and inflated for the roundings of that reduction.
