@@ -244,8 +244,8 @@ int32_t nyb200_net_destroy(nyb200_engine *e, int32_t net_id) {
 int32_t nyb200_gemm_f32(nyb200_engine *e, int32_t m, int32_t k, int32_t n, const float *a, const float *b,
                         float *c_out) {
     if (!e || !a || !b || !c_out) return NYB200_ERR_INVALID;
-    if (m <= 0 || k <= 0 || n <= 0) return set_err(e, NYB200_ERR_SHAPE, "gemm_f32: non-positive dimension");
     std::lock_guard<std::mutex> g(e->mu);
+    if (m <= 0 || k <= 0 || n <= 0) return set_err(e, NYB200_ERR_SHAPE, "gemm_f32: non-positive dimension");
     NYB_CUDA(e, cudaSetDevice(e->device));
     NYB_WS(da, float *, e, "gemm_a", (size_t)m * k * 4);
     NYB_WS(db, float *, e, "gemm_b", (size_t)k * n * 4);
@@ -855,9 +855,9 @@ int32_t nyb200_batch_select_branch(nyb200_engine *e, int32_t *relu, int32_t *neu
 
 int32_t nyb200_batch_select_branch_scored(nyb200_engine *e, int32_t kind, int32_t *relu, int32_t *neuron, float *width) {
     if (!e || !relu || !neuron) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
     if (kind != NYB200_BRANCH_WIDTH && kind != NYB200_BRANCH_INTERCEPT && kind != NYB200_BRANCH_BABSR)
         return set_err(e, NYB200_ERR_INVALID, "unknown branching score");
-    std::lock_guard<std::mutex> g(e->mu);
     NYB_CUDA(e, cudaSetDevice(e->device));
     NYB_TRY(finish_batch(e));
     Net *net;

@@ -117,8 +117,8 @@ int32_t nyb200_set_deadline_ns(nyb200_engine *e, int64_t ns_from_now) {
 int32_t nyb200_gemm_f64(nyb200_engine *e, int32_t m, int32_t k, int32_t n, const double *a, const double *b,
                         double *c_out) {
     if (!e || !a || !b || !c_out) return NYB200_ERR_INVALID;
-    if (m <= 0 || k <= 0 || n <= 0) return set_err(e, NYB200_ERR_SHAPE, "gemm_f64: non-positive dimension");
     std::lock_guard<std::mutex> g(e->mu);
+    if (m <= 0 || k <= 0 || n <= 0) return set_err(e, NYB200_ERR_SHAPE, "gemm_f64: non-positive dimension");
     NYB_CUDA(e, cudaSetDevice(e->device));
     NYB_DEADLINE(e, "binary64 product");
     NYB_WS(da, double *, e, "gemm_a", (size_t)m * k * 8);
@@ -139,6 +139,7 @@ int32_t nyb200_conv_transpose_2d(nyb200_engine *e, const float *a_reshaped, cons
                                  const nyb200_conv_transpose_params *params, float *out) {
     if (!e || !a_reshaped || !weight_col || !params || !out) return NYB200_ERR_INVALID;
     const nyb200_conv_transpose_params &g = *params;
+    std::lock_guard<std::mutex> lk(e->mu);
     if (g.num_specs <= 0 || g.out_channels <= 0 || g.in_channels <= 0 || g.out_h <= 0 || g.out_w <= 0 || g.in_h <= 0 ||
         g.in_w <= 0 || g.kernel_h <= 0 || g.kernel_w <= 0 || g.stride_h <= 0 || g.stride_w <= 0 || g.pad_h < 0 || g.pad_w < 0)
         return set_err(e, NYB200_ERR_SHAPE, "conv_transpose_2d: non-positive dimension");
@@ -146,7 +147,6 @@ int32_t nyb200_conv_transpose_2d(nyb200_engine *e, const float *a_reshaped, cons
     if ((g.in_h + 2 * g.pad_h - g.kernel_h) / g.stride_h + 1 != g.out_h || (g.in_w + 2 * g.pad_w - g.kernel_w) / g.stride_w + 1 != g.out_w ||
         g.in_h + 2 * g.pad_h < g.kernel_h || g.in_w + 2 * g.pad_w < g.kernel_w)
         return set_err(e, NYB200_ERR_SHAPE, "conv_transpose_2d: output size does not follow from input, kernel, stride and padding");
-    std::lock_guard<std::mutex> lk(e->mu);
     NYB_CUDA(e, cudaSetDevice(e->device));
     NYB_DEADLINE(e, "transposed convolution");
     const size_t na = (size_t)g.num_specs * g.out_h * g.out_w * g.out_channels;
