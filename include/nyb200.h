@@ -203,10 +203,12 @@ int32_t nyb200_batch_select_branch(nyb200_engine *e, int32_t *relu, int32_t *neu
  * the mean over rows of |min(b c (r0 - 1), b c r0) + min(c, 0) r1| with r0 = max(u,0)/(max(u,0) - min(l,0)),
  * r1 = -min(l,0) r0, b the producing layer's bias.  Linear layers only (NYB200_ERR_UNSUPPORTED otherwise).
  * nyb200_batch_download_branch_scores returns the scores of the last BaBSR selection, [D x n_pre], -1 for neurons that
- * are not candidates (stable or split) and for the output block. */
+ * are not candidates (stable or split) and for the output block; backup (may be NULL) receives the "backup" score
+ * of the filtered heuristics (select_fsb_neuron, sequential.rs:200-358), the mean intercept term min(c, 0) r1 (<= 0;
+ * +1 for non-candidates). */
 #define NYB200_BRANCH_BABSR 2
 int32_t nyb200_batch_select_branch_scored(nyb200_engine *e, int32_t kind, int32_t *relu, int32_t *neuron, float *score);
-int32_t nyb200_batch_download_branch_scores(nyb200_engine *e, float *scores);
+int32_t nyb200_batch_download_branch_scores(nyb200_engine *e, float *scores, float *backup);
 
 /* ---- alpha/beta optimisation of the resident batch ---------------------------------------------
  * Projected-Adam ascent on every domain's lower slopes alpha (unstable unsplit neurons, kept in [0,1]:

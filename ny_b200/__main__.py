@@ -49,7 +49,7 @@ def main(argv=None) -> int:
             p.add_argument("--batch-size", type=int, default=1024)
             p.add_argument("--max-domains", type=int, default=100_000)
             p.add_argument("--beta-iterations", type=int, default=20)
-            p.add_argument("--branching", choices=("width", "intercept", "babsr"), default="intercept")
+            p.add_argument("--branching", choices=("width", "intercept", "babsr", "fsb"), default="intercept")
             p.add_argument("--input-split", action="store_true", help="branch on input dimensions instead of ReLUs")
             p.add_argument("--domain-batch-metrics-jsonl", default=None)
             p.add_argument("--checkpoint", default=None)
@@ -72,7 +72,7 @@ def main(argv=None) -> int:
                 res = bab.verify_input_split(eng, nid, net, prop, batch=args.batch_size, max_domains=args.max_domains,
                                              timeout_s=args.timeout)
             else:
-                kind = {"width": 0, "intercept": 1, "babsr": 2}[args.branching]
+                kind = {"width": 0, "intercept": 1, "babsr": 2, "fsb": 3}[args.branching]
                 res = bab.verify(eng, nid, net, prop, batch=args.batch_size, max_domains=args.max_domains, max_rounds=1 << 30,
                                  optimize_iterations=args.beta_iterations, branching=kind, timeout_s=args.timeout,
                                  metrics_jsonl=args.domain_batch_metrics_jsonl, checkpoint=args.checkpoint, resume=args.resume)

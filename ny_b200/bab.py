@@ -144,10 +144,69 @@ def attack(eng, net_id, net, prop: Property, restarts: int = 256, steps: int = 5
     return None
 
 
+def fsb_candidates(main, backup, k: int):
+    """Candidate neurons of one domain for the filtered heuristic (select_fsb_neuron,
+    beta_crown/engine/branching/sequential.rs:200-300): the k largest BaBSR scores, then the k smallest (most
+    negative) backup scores that are not among them; non-candidates carry main < 0.  Stable order on ties."""
+    cand = np.flatnonzero(main >= 0)
+    if cand.size == 0:
+        return cand
+    by_main = cand[np.argsort(-main[cand], kind="stable")][:k]
+    by_backup = cand[np.argsort(backup[cand], kind="stable")][:k]
+    seen = set(int(i) for i in by_main)
+    return np.array(list(by_main) + [int(i) for i in by_backup if int(i) not in seen], np.int64)
+
+
+def _margin(lower, thr, owner, n_clauses):
+    """Scalar progress of a domain: min over clauses of the best atom's (lower - threshold); > 0 means verified."""
+    gap = lower - thr[None, :]
+    out = np.full(lower.shape[0], np.inf, np.float32)
+    for c in range(n_clauses):
+        out = np.minimum(out, gap[:, owner == c].max(axis=1))
+    return out
+
+
+def select_fsb(eng, net_id, net, prop: Property, inh_lo, inh_hi, take, open_idx, k: int = 3):
+    """Filtered smart branching for the open domains `open_idx` of the batch `take` that has just been run (and
+    scored with BaBSR): every candidate of fsb_candidates is tried - both children bounded in one device batch - and
+    the split whose worse child has the best margin wins (fsb_worst_case_score,
+    beta_crown/config/beta_config.rs:1722-1755); within 1e-6 the larger BaBSR score decides.  Returns
+    {domain index: (relu, neuron)}; a domain without candidates is missing from it."""
+    spec, thr, owner = _rows(prop)
+    n_clauses = len(prop.violation)
+    main, backup = eng.batch_branch_scores(with_backup=True)
+    offs = np.concatenate([[0], np.cumsum(net.dims[1:])]).astype(np.int64)
+    trial, meta = [], []          # child split histories; (domain, flat neuron index) per pair of children
+    for d in open_idx:
+        for o in fsb_candidates(main[d], backup[d], k):
+            r = int(np.searchsorted(offs[1:], o, side="right"))
+            for sign in (1, -1):
+                child = np.zeros(len(take[d]) + 1, SPLIT_DTYPE)
+                child[: len(take[d])] = take[d]
+                child[-1] = (r, int(o - offs[r]), sign, 0.0)
+                trial.append(child)
+            meta.append((int(d), int(o), r, int(o - offs[r])))
+    if not trial:
+        return {}
+    splits, ns = frontier_to_arrays(trial)
+    lower, _, infeasible = eng.bab_bound_batch(net_id, spec, prop.in_lo, prop.in_hi, inh_lo, inh_hi, splits, ns, mode=1)
+    m = _margin(lower, thr, owner, n_clauses)
+    m = np.where(infeasible != 0, np.float32(np.inf), m)       # an empty child needs no further work
+    worst = np.minimum(m[0::2], m[1::2])
+    best = {}
+    for (d, o, r, j), w in zip(meta, worst):
+        if np.isnan(w):
+            continue
+        cur = best.get(d)
+        if cur is None or w > cur[0] + 1e-6 or (abs(w - cur[0]) <= 1e-6 and main[d][o] > cur[1]):
+            best[d] = (float(w), float(main[d][o]), r, j)
+    return {d: (v[2], v[3]) for d, v in best.items()}
+
+
 def verify(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: int = 64, max_domains: int = 1 << 20,
            pgd_restarts: int = 256, pgd_steps: int = 50, optimize_iterations: int = 0, branching: int = 1,
            timeout_s: float | None = None, metrics_jsonl=None, checkpoint=None, resume=None,
-           warm_start: bool = True) -> VerifyResult:
+           warm_start: bool = True, fsb_k: int = 3) -> VerifyResult:
     """metrics_jsonl: append one JSON record per round; checkpoint: path that receives the open frontier whenever the
     run stops unresolved (round limit, timeout, domain limit); resume: path of such a dump to continue from (the attack
     and the root bound are skipped).
@@ -155,7 +214,8 @@ def verify(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: i
     multipliers of every domain (0, the reference's throughput default `beta_iterations: 0`
     (beta_crown/config/beta_config.rs:1244), bounds each domain once with multipliers at zero: sound, but the search
     may then end "unknown" on properties that need the multipliers; 20 is the reference's root-level count);
-    branching: 0 widest interval, 1 intercept score, 2 BaBSR (Linear layers only); warm_start: with optimisation on, children start from their
+    branching: 0 widest interval, 1 intercept score, 2 BaBSR, 3 filtered smart branching over the fsb_k best BaBSR and
+    intercept candidates (2 and 3: Linear layers only); warm_start: with optimisation on, children start from their
     parent's optimised slopes and split multipliers instead of the heuristic slopes and zero."""
     t0 = time.time()
     if not prop.violation:
@@ -221,7 +281,10 @@ def verify(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: i
                       max_depth=int(ns.max()) if D else 0)
         if done.all():
             continue
-        relu, neuron, _ = eng.batch_select_branch(branching)
+        relu, neuron, _ = eng.batch_select_branch(2 if branching == 3 else branching)
+        if branching == 3:   # filtered smart branching: the BaBSR / intercept candidates are tried on the device
+            for d, (r, j) in select_fsb(eng, net_id, net, prop, inh_lo, inh_hi, take, np.flatnonzero(~done), fsb_k).items():
+                relu[d], neuron[d] = r, j
         for d in np.flatnonzero(~done):
             if relu[d] < 0:
                 # every neuron is fixed: the bound is exact on this piece, so the piece contains a violation

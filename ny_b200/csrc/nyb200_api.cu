@@ -878,7 +878,7 @@ int32_t nyb200_batch_select_branch_scored(nyb200_engine *e, int32_t kind, int32_
     return NYB200_OK;
 }
 
-int32_t nyb200_batch_download_branch_scores(nyb200_engine *e, float *scores) {
+int32_t nyb200_batch_download_branch_scores(nyb200_engine *e, float *scores, float *backup) {
     if (!e || !scores) return NYB200_ERR_INVALID;
     std::lock_guard<std::mutex> g(e->mu);
     NYB_CUDA(e, cudaSetDevice(e->device));
@@ -887,10 +887,13 @@ int32_t nyb200_batch_download_branch_scores(nyb200_engine *e, float *scores) {
     NYB_TRY(find_net(e, e->batch.net_id, &net));
     auto it = e->ws.find("babsr_score");
     const NetView &nv = net->v;
-    if (it == e->ws.end() || it->second.bytes < (size_t)e->batch.D * nv.nps * 4)
+    if (it == e->ws.end() || it->second.bytes < (size_t)2 * e->batch.D * nv.nps * 4)
         return set_err(e, NYB200_ERR_INVALID, "no BaBSR selection has been made for this batch");
     size_t w = (size_t)nv.n_pre * 4;
     NYB_CUDA(e, cudaMemcpy2DAsync(scores, w, it->second.p, (size_t)nv.nps * 4, w, (size_t)e->batch.D, cudaMemcpyDeviceToHost, e->stream));
+    if (backup)
+        NYB_CUDA(e, cudaMemcpy2DAsync(backup, w, (const float *)it->second.p + (size_t)e->batch.D * nv.nps, (size_t)nv.nps * 4, w,
+                                      (size_t)e->batch.D, cudaMemcpyDeviceToHost, e->stream));
     NYB_CUDA(e, cudaStreamSynchronize(e->stream));
     return NYB200_OK;
 }

@@ -36,7 +36,7 @@ __global__ void k_babsr_fill(long n, float v, float *__restrict__ p) {
 __global__ void __launch_bounds__(256)
 k_babsr_relu(int n, int off, int D, int S, long nps, float *__restrict__ C, int ldc, const float *__restrict__ pre_lo,
              const float *__restrict__ pre_hi, const signed char *__restrict__ code, const float *__restrict__ bias,
-             float *__restrict__ score) {
+             float *__restrict__ score, float *__restrict__ backup) {
     long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= (long)D * n) return;
     const int d = (int)(t / n), j = (int)(t - (long)d * n);
@@ -61,7 +61,7 @@ k_babsr_relu(int n, int off, int D, int S, long nps, float *__restrict__ C, int 
     else if (l >= 0.f) slope = 1.f;
     else if (u <= 0.f) slope = 0.f;
     else slope = __fdiv_rn(u, fmaxf(__fsub_rn(u, l), 1e-8f));
-    double sum = 0.0;
+    double sum = 0.0, bsum = 0.0;
     bool ok = have;
     float *col = C + (long)d * S * ldc + j;
     for (int s = 0; s < S; ++s) {
@@ -74,13 +74,15 @@ k_babsr_relu(int n, int off, int D, int S, long nps, float *__restrict__ C, int 
                 const float bc = fminf(__fmul_rn(bs, __fsub_rn(r0, 1.f)), __fmul_rn(bs, r0));
                 const float mc = fabsf(__fadd_rn(bc, ic));
                 if (!isfinite(ic) || !isfinite(mc)) ok = false;
-                else sum += (double)mc;
+                else { sum += (double)mc; bsum += (double)ic; }
             }
         }
         col[(long)s * ldc] = __fmul_rn(c, slope);
     }
     const bool candidate = l < 0.f && u > 0.f && code[o] == 0;
     score[o] = candidate ? (ok ? (float)(sum / (double)S) : 0.f) : -1.f;
+    // the "backup" score of the filtered heuristics: mean intercept term, <= 0, more negative = looser relaxation
+    backup[o] = candidate ? (ok ? (float)(bsum / (double)S) : 0.f) : 1.f;
 }
 
 // First maximum of the scores (non-candidates hold -1, NaN never wins), one warp per domain.
@@ -128,7 +130,8 @@ int babsr_select(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int *
     const bool tensor = e->path == NYB200_PATH_TF32X3;
     NYB_WS(c0, float *, e, "babsr_c0", (size_t)rows * ldc * 4);
     NYB_WS(c1, float *, e, "babsr_c1", (size_t)rows * ldc * 4);
-    NYB_WS(score, float *, e, "babsr_score", (size_t)D * np * 4);
+    NYB_WS(score, float *, e, "babsr_score", (size_t)2 * D * np * 4);  // main scores, then the backup scores
+    float *backup = score + (size_t)D * np;
     int *derr = nullptr;
     if (tensor) {
         NYB_TRY(prepare_backward_operands(e, net));
@@ -138,7 +141,8 @@ int babsr_select(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int *
     }
     const int nL = nv.dims[L];
     k_babsr_fill<<<(unsigned)(((long)D * np + 255) / 256), 256, 0, e->stream>>>((long)D * np, -1.f, score);  // output block, padding
-    e->launches++;
+    k_babsr_fill<<<(unsigned)(((long)D * np + 255) / 256), 256, 0, e->stream>>>((long)D * np, 1.f, backup);
+    e->launches += 2;
     k_babsr_seed<<<(unsigned)((rows * nL + 255) / 256), 256, 0, e->stream>>>(rows, S, nL, p.spec, c0, ldc);
     e->launches++;
     float *cur = c0, *nxt = c1;
@@ -149,7 +153,7 @@ int babsr_select(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int *
         else launch_gemm_f64(e, (int)rows, N, K, cur, ldc, nv.W[k], N, nxt, ldc, 1, nullptr, nullptr, 0, nullptr);
         const long tot = (long)D * N;
         k_babsr_relu<<<(unsigned)((tot + 255) / 256), 256, 0, e->stream>>>(N, nv.pre_off[k - 1], D, S, np, nxt, ldc, p.pre_lo,
-                                                                          p.pre_hi, p.code, nv.b[k - 1], score);
+                                                                          p.pre_hi, p.code, nv.b[k - 1], score, backup);
         e->launches++;
         float *t = cur; cur = nxt; nxt = t;
     }

@@ -119,7 +119,7 @@ def load_library():
     L.nyb200_set_deadline_ns.argtypes = [vp, C.c_int64]
     L.nyb200_batch_gradient.argtypes = [vp, C.c_int32, fp]
     L.nyb200_crown_input_coeffs.argtypes = [vp, fp, fp]
-    L.nyb200_batch_download_branch_scores.argtypes = [vp, fp]
+    L.nyb200_batch_download_branch_scores.argtypes = [vp, fp, fp]
     L.nyb200_point_vjp_batched.argtypes = [vp, C.c_int32, C.c_int32, fp, fp, fp, fp, fp]
     _lib = L
     return L
@@ -573,12 +573,14 @@ class B200Engine:
         self._check(self._L.nyb200_batch_select_branch_scored(self._h, kind, _ip(r), _ip(j), _fp(w)))
         return r, j, w
 
-    def batch_branch_scores(self) -> np.ndarray:
-        """Scores of the last BaBSR selection (batch_select_branch(2)), [D, n_pre]; -1 marks non-candidates."""
+    def batch_branch_scores(self, with_backup: bool = False):
+        """Scores of the last BaBSR selection (batch_select_branch(2)), [D, n_pre]; -1 marks non-candidates.
+        with_backup: also the intercept ("backup") scores, <= 0 for candidates and +1 otherwise."""
         D, S, n_pre = self._batch_shape
         sc = np.empty((D, n_pre), np.float32)
-        self._check(self._L.nyb200_batch_download_branch_scores(self._h, _fp(sc)))
-        return sc
+        bk = np.empty((D, n_pre), np.float32) if with_backup else None
+        self._check(self._L.nyb200_batch_download_branch_scores(self._h, _fp(sc), _fp(bk)))
+        return (sc, bk) if with_backup else sc
 
     def timing_enable(self, per_kernel: bool):
         self._check(self._L.nyb200_timing_enable(self._h, 1 if per_kernel else 0))

@@ -500,7 +500,7 @@ def optimize_dual(net: Net, lo, hi, pre_lo, pre_hi, splits: np.ndarray, alpha, i
     return bl, bu, alpha, aup, splits
 
 
-def babsr_scores(weights, biases, spec, pre_lo, pre_hi, split_mask=None):
+def babsr_scores(weights, biases, spec, pre_lo, pre_hi, split_mask=None, with_backup=False):
     """numpy restatement of the reference's BaBSR scores for one domain of a dense sequential ReLU network
     (compute_babsr_scores, crates/ny-propagate/src/beta_crown/engine/branching/sequential.rs:784-882, with
     compute_babsr_score_parts, branching/score.rs:28-97, and relu_upper_slope, branching/mod.rs:93-111; reduce op Min
@@ -513,6 +513,7 @@ def babsr_scores(weights, biases, spec, pre_lo, pre_hi, split_mask=None):
     offs = np.concatenate([[0], np.cumsum(dims)]).astype(int)
     n_hidden = int(offs[len(weights) - 1])
     scores = np.full(n_hidden, -1.0, f32)
+    backup = np.full(n_hidden, 1.0, f32)   # BabsrScoreParts::backup_score: mean intercept term (+1: not a candidate)
     C = np.asarray(spec, f32)
     for k in range(len(weights) - 1, 0, -1):
         C = (C.astype(np.float64) @ np.asarray(weights[k], np.float64)).astype(f32)
@@ -532,7 +533,7 @@ def babsr_scores(weights, biases, spec, pre_lo, pre_hi, split_mask=None):
                     r1 = f32(-lt * r0)
                     have = bool(np.isfinite(r0) and np.isfinite(r1))
             col = C[:, j]
-            ok, total = have, 0.0
+            ok, total, btotal = have, 0.0, 0.0
             if ok:
                 for c in col:
                     if not np.isfinite(c):
@@ -546,9 +547,11 @@ def babsr_scores(weights, biases, spec, pre_lo, pre_hi, split_mask=None):
                         ok = False
                         break
                     total += float(mc)
+                    btotal += float(ic)
             cand = l < 0 and u > 0 and not (split_mask is not None and split_mask[off + j])
             if cand:
                 scores[off + j] = f32(total / len(col)) if ok else f32(0)
+                backup[off + j] = f32(btotal / len(col)) if ok else f32(0)
             if not (np.isfinite(l) and np.isfinite(u)) or l >= 0:
                 slope = f32(1)
             elif u <= 0:
@@ -561,6 +564,8 @@ def babsr_scores(weights, biases, spec, pre_lo, pre_hi, split_mask=None):
         if s > best:
             best, pick = s, i
     if pick < 0:
-        return scores, (-1, -1)
-    r = int(np.searchsorted(offs[1:], pick, side="right"))
-    return scores, (r, pick - int(offs[r]))
+        sel = (-1, -1)
+    else:
+        r = int(np.searchsorted(offs[1:], pick, side="right"))
+        sel = (r, pick - int(offs[r]))
+    return (scores, sel, backup) if with_backup else (scores, sel)

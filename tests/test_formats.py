@@ -171,3 +171,18 @@ def test_onnx_round_trip_and_declines():
         R.parse_onnx(body[: len(body) // 2])
     with pytest.raises(EngineError):
         R.parse_onnx(b"")
+
+
+def test_fsb_candidate_filter_and_margin():
+    from ny_b200 import bab
+
+    main = np.array([0.5, -1, 0.2, 0.9, 0.2, -1], np.float32)
+    backup = np.array([-0.1, 1, -0.9, 0.0, -0.3, 1], np.float32)
+    assert bab.fsb_candidates(main, backup, 2).tolist() == [3, 0, 2, 4]       # two best scores, two most negative intercepts
+    assert bab.fsb_candidates(main, backup, 1).tolist() == [3, 2]
+    assert bab.fsb_candidates(main, backup, 10).tolist() == [3, 0, 2, 4]      # k beyond the candidate count: all, once
+    assert bab.fsb_candidates(np.full(4, -1, np.float32), np.ones(4, np.float32), 3).size == 0
+    # clause 0 = atoms 0, 1 (any refutes it), clause 1 = atom 2: margin = min over clauses of the best atom's gap
+    m = bab._margin(np.array([[1.0, 0.5, -2.0], [0.5, 3.0, 0.25]], np.float32), np.array([0.0, 1.0, 0.0], np.float32),
+                    np.array([0, 0, 1]), 2)
+    assert m.tolist() == [-2.0, 0.25]

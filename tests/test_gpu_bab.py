@@ -74,6 +74,10 @@ def test_bab_closes_the_gap_between_root_bound_and_true_minimum(eng, tmp_path):
     # children that inherit their parent's optimised slopes and multipliers need no more domains than cold starts
     r3 = bab.verify(eng, nid, net, prop(t_safe), batch=256, max_rounds=200, optimize_iterations=20, warm_start=False)
     assert r3.status == "verified" and r2.domains_bounded <= r3.domains_bounded
+    # BaBSR and filtered smart branching drive the same search to the same verdict
+    for kind in (2, 3):
+        rk = bab.verify(eng, nid, net, prop(t_safe), batch=256, max_rounds=200, optimize_iterations=20, branching=kind)
+        assert rk.status == "verified" and rk.open_domains == 0
     # stop after two rounds, dump the frontier, resume from the dump: same verdict, and the two legs together bound
     # exactly the domains of the uninterrupted run; one metrics record per round
     import json

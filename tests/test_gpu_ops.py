@@ -209,7 +209,8 @@ def test_babsr_scores_and_picks_match_oracle(eng, oracle):
     eng.batch_run()
     _, _, inf = eng.batch_download()
     relu, neuron, best = eng.batch_select_branch(2)
-    scores = eng.batch_branch_scores()
+    scores, backups = eng.batch_branch_scores(with_backup=True)
+    assert np.array_equal(scores, eng.batch_branch_scores())
     pl, pu = eng.batch_download_pre_bounds()
     dims = wl.net.dims
     offs = np.concatenate([[0], np.cumsum(dims[1:])]).astype(int)
@@ -220,8 +221,12 @@ def test_babsr_scores_and_picks_match_oracle(eng, oracle):
         mask = np.zeros(wl.net.n_pre, bool)
         for s in splits[d][: ns[d]]:
             mask[int(offs[s["relu"]] + s["neuron"])] = True
-        sc, pick = oracle.babsr_scores(wl.net.weights, wl.net.biases, wl.spec, pl[d], pu[d], mask)
+        sc, pick, bk = oracle.babsr_scores(wl.net.weights, wl.net.biases, wl.spec, pl[d], pu[d], mask, with_backup=True)
         got = scores[d][:n_hidden]
+        gb = backups[d][:n_hidden]
+        assert np.array_equal(gb > 0.5, bk > 0.5) and np.all(gb[bk <= 0.5] <= 0)
+        if (bk <= 0.5).any():
+            assert np.abs(gb - bk)[bk <= 0.5].max() <= tol * max(float(np.abs(bk[bk <= 0.5]).max()), 1e-6)
         assert np.array_equal(got < 0, sc < 0)                          # same candidate set
         assert np.all(scores[d][n_hidden:] == -1)
         cand = sc >= 0
