@@ -163,6 +163,38 @@ k_ibp_linear_vec(int n_in, int n_out, const float *__restrict__ W, const float *
     }
 }
 
+// The same for a few domains (the binary64 re-evaluation of a flagged subset): the tiled kernel above would start
+// a handful of CTAs that walk the whole contraction one after the other; here one warp owns one (domain, output)
+// pair and the lanes stride over the inputs.
+__global__ void __launch_bounds__(256)
+k_ibp_linear_warp(int Deff, int n_in, int n_out, const float *__restrict__ W, const float *__restrict__ bias,
+                  const float *__restrict__ zl, const float *__restrict__ zu, long in_ds, float *__restrict__ raw_lo,
+                  float *__restrict__ raw_hi, float *__restrict__ q, long out_ds) {
+    long warp = ((long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    int lane = threadIdx.x & 31;
+    if (warp >= (long)Deff * n_out) return;
+    int d = (int)(warp / n_out), o = (int)(warp - (long)d * n_out);
+    const float *w = W + (long)o * n_in, *a_row = zl + (long)d * in_ds, *b_row = zu + (long)d * in_ds;
+    double lo = 0.0, hi = 0.0, qq = 0.0;
+    for (int i = lane; i < n_in; i += 32) {
+        double wv = w[i], a = a_row[i], b = b_row[i];
+        bool pos = wv > 0.0;
+        lo = fma(wv, pos ? a : b, lo);
+        hi = fma(wv, pos ? b : a, hi);
+        qq = fma(fabs(wv), fmax(fabs(a), fabs(b)), qq);
+    }
+    lo = warp_sum(lo); hi = warp_sum(hi); qq = warp_sum(qq);
+    if (lane == 0) {
+        const double gam = (double)(n_in + 2) * 1.1102230246251565e-16 * 1.000001;
+        double bv = bias ? (double)bias[o] : 0.0;
+        double slack = gam * (qq + fabs(bv));
+        float lf = __double2float_rd(lo + bv - slack), hf = __double2float_ru(hi + bv + slack);
+        if (isnan(lf) || isnan(hf)) { lf = -INFINITY; hf = INFINITY; }
+        raw_lo[(long)d * out_ds + o] = lf; raw_hi[(long)d * out_ds + o] = hf;
+        q[(long)d * out_ds + o] = __double2float_ru(qq * (1.0 + gam));
+    }
+}
+
 // ---------------------------------------------------------------- per-domain finish of a Linear output
 // mode 0: bounds = inherited (clamp only: beta_crown/engine/domain/child.rs:51-118);
 // mode 1: bounds = re-propagated intersected with inherited (graph/propagation/constraints/mod.rs:738-741);
@@ -807,6 +839,14 @@ void launch_ibp_linear(nyb200_engine *e, const NetView &nv, int k, int Deff, con
         return;
     }
     dim3 grid((n_out + IB_N - 1) / IB_N, (Deff + IB_M - 1) / IB_M);
+    if ((long)grid.x * grid.y < 96) {  // too few tiles to occupy the GPU: one warp per (domain, output)
+        long warps = (long)Deff * n_out;
+        k_ibp_linear_warp<<<(unsigned)((warps * 32 + 255) / 256), 256, 0, e->stream>>>(
+            Deff, n_in, n_out, nv.W[k], nv.b[k], zl, zu, in_dstride, raw_lo + nv.pre_off[k], raw_hi + nv.pre_off[k],
+            q + nv.pre_off[k], out_dstride);
+        NYB_COUNT(e);
+        return;
+    }
     k_ibp_linear<<<grid, 256, 0, e->stream>>>(Deff, n_in, n_out, nv.W[k], nv.b[k], zl, zu, in_dstride,
                                                raw_lo + nv.pre_off[k], raw_hi + nv.pre_off[k], q + nv.pre_off[k],
                                                out_dstride);
