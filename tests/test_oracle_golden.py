@@ -12,23 +12,23 @@ import math
 import numpy as np
 import pytest
 
-FC1 = [[0.16834518, 0.06440470, 0.11723118], [0.11516652, -0.56142819, -0.09316415],
-       [1.10410070, -0.31899852, 0.23082861], [0.13367544, 0.26745233, 0.40467861]]
-B1 = [0.11102903, -0.16897990, -0.09889599, 0.09579718]
-FC2 = [[-0.69233710, -0.43561807, -0.11168297, 0.85868055], [0.15943986, -0.21225949, 0.15286016, -0.38729626],
-       [-0.77878612, 0.49781805, -0.43989292, -0.30057147], [-0.63707572, 1.06139255, -0.61732668, -0.24395694]]
-B2 = [0.02815196, 0.00561635, 0.05227160, -0.02383569]
-FC3 = [[-0.02495167, 0.26316848, -0.00424941, 0.36453030], [0.06657098, 0.43198884, -0.50783736, -0.44437426]]
-B3 = [0.01497797, -0.02088939]
+import json
+import os
+
+with open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "crown_reference.json")) as _f:
+    GOLDEN = json.load(_f)
+FC1, FC2, FC3 = GOLDEN["deep_3_4_4_2"]["weights"]
+B1, B2, B3 = GOLDEN["deep_3_4_4_2"]["biases"]
 
 
 def test_toy_model(oracle):
-    net = oracle.Net([[[1, -1], [2, -1]], [[1, -1]]])
-    lo, hi = [-1, -2], [2, 1]
+    g = GOLDEN["toy_2_2_1"]
+    net = oracle.Net(g["weights"])
+    lo, hi = g["in_lo"], g["in_hi"]
     pl, pu = oracle.ibp_forward(net, lo, hi)
-    assert abs(pl[-1] - (-6.0)) < 1e-4 and abs(pu[-1] - 4.0) < 1e-4
+    assert abs(pl[-1] - g["ibp"][0]) < g["tolerance"] and abs(pu[-1] - g["ibp"][1]) < g["tolerance"]
     cl, cu = oracle.crown(net, lo, hi)
-    assert abs(cl[0] - (-3.0)) < 1e-4 and abs(cu[0] - 3.0) < 1e-4
+    assert abs(cl[0] - g["crown"][0]) < g["tolerance"] and abs(cu[0] - g["crown"][1]) < g["tolerance"]
     for x in ([-1, -2], [2, 1], [0.5, -0.5]):
         y = net.forward(x)[0]
         assert pl[-1] - 1e-5 <= y <= pu[-1] + 1e-5
@@ -39,28 +39,30 @@ def test_deep_model(oracle):
     net = oracle.Net([FC1, FC2, FC3], [B1, B2, B3])
     lo, hi = [0.4] * 3, [0.6] * 3
     pl, pu = oracle.ibp_forward(net, lo, hi)
-    np.testing.assert_allclose(pl[-2:], [0.00687957, -0.01418082], atol=1e-4, rtol=0)
-    np.testing.assert_allclose(pu[-2:], [0.01246351, 0.00071711], atol=1e-4, rtol=0)
+    g = GOLDEN["deep_3_4_4_2"]
+    np.testing.assert_allclose(pl[-2:], g["ibp_lo"], atol=g["tolerance"], rtol=0)
+    np.testing.assert_allclose(pu[-2:], g["ibp_hi"], atol=g["tolerance"], rtol=0)
     cl, cu = oracle.crown(net, lo, hi)
-    np.testing.assert_allclose(cl, [0.00820859, -0.01063502], atol=1e-4, rtol=0)
-    np.testing.assert_allclose(cu, [0.01113450, -0.00282869], atol=1e-4, rtol=0)
+    np.testing.assert_allclose(cl, g["crown_lo"], atol=g["tolerance"], rtol=0)
+    np.testing.assert_allclose(cu, g["crown_hi"], atol=g["tolerance"], rtol=0)
     # the published values carry 8 digits; the restatement agrees far inside the reference's tolerance
-    np.testing.assert_allclose(cl, [0.00820859, -0.01063502], atol=5e-8, rtol=0)
-    np.testing.assert_allclose(cu, [0.01113450, -0.00282869], atol=5e-8, rtol=0)
+    np.testing.assert_allclose(cl, g["crown_lo"], atol=5e-8, rtol=0)
+    np.testing.assert_allclose(cu, g["crown_hi"], atol=5e-8, rtol=0)
     assert np.all(cu - cl <= pu[-2:] - pl[-2:] + 1e-5)
     y = net.forward([0.5] * 3)
     assert np.all(y >= cl - 1e-5) and np.all(y <= cu + 1e-5)
 
 
 def test_tiny_model_intersection(oracle):
-    net = oracle.Net([[[1, 1], [1, -1]], [[1, 0], [0, 1]]], [[-0.5, 0], [0, 0]])
-    pl, pu = oracle.ibp_forward(net, [0, 0], [1, 1])
+    g = GOLDEN["tiny_2_2_2"]
+    net = oracle.Net(g["weights"], g["biases"])
+    pl, pu = oracle.ibp_forward(net, g["in_lo"], g["in_hi"])
     np.testing.assert_allclose(np.maximum(pl[:2], 0), [0, 0], atol=1e-5)
     np.testing.assert_allclose(pl[2:], [0, 0], atol=1e-5)
     np.testing.assert_allclose(pu[2:], [1.5, 1.0], atol=1e-5)
-    cl, cu = oracle.crown(net, [0, 0], [1, 1])
-    np.testing.assert_allclose(cl, [0, 0], atol=1e-5)
-    np.testing.assert_allclose(cu, [1.5, 1.0], atol=1e-5)
+    cl, cu = oracle.crown(net, g["in_lo"], g["in_hi"])
+    np.testing.assert_allclose(cl, g["crown_lo"], atol=g["tolerance"])
+    np.testing.assert_allclose(cu, g["crown_hi"], atol=g["tolerance"])
 
 
 def test_directed_rounding_steps(oracle):
