@@ -72,6 +72,82 @@ def frontier_to_arrays(frontier):
     return splits, ns
 
 
+class Frontier:
+    """The open domain set as a structure of arrays: split histories [N, depth] with their lengths [N] and,
+    optionally, warm-start slopes [N, n_pre] (NaN rows where a domain has none).  Batches leave from the front,
+    children are appended at the back (breadth-first), rebalancing between ranks takes from the back."""
+
+    def __init__(self, n_pre: int):
+        self.splits = np.zeros((0, 1), SPLIT_DTYPE)
+        self.ns = np.zeros(0, np.int32)
+        self.alpha = np.zeros((0, n_pre), np.float32)
+        self.n_pre = n_pre
+
+    def __len__(self):
+        return len(self.ns)
+
+    def _widen(self, depth: int):
+        if depth > self.splits.shape[1]:
+            grown = np.zeros((len(self.ns), depth), SPLIT_DTYPE)
+            grown[:, : self.splits.shape[1]] = self.splits
+            self.splits = grown
+
+    def push(self, splits, ns, alpha=None):
+        if len(ns) == 0:
+            return
+        splits = np.asarray(splits, SPLIT_DTYPE).reshape(len(ns), -1)
+        self._widen(splits.shape[1])
+        block = np.zeros((len(ns), self.splits.shape[1]), SPLIT_DTYPE)
+        block[:, : splits.shape[1]] = splits
+        self.splits = np.concatenate([self.splits, block])
+        self.ns = np.concatenate([self.ns, np.asarray(ns, np.int32)])
+        if alpha is None:
+            alpha = np.full((len(ns), self.n_pre), np.nan, np.float32)
+        self.alpha = np.concatenate([self.alpha, np.asarray(alpha, np.float32)])
+
+    def push_front(self, splits, ns):
+        rest = (self.splits, self.ns, self.alpha)
+        self.splits, self.ns, self.alpha = np.zeros((0, 1), SPLIT_DTYPE), np.zeros(0, np.int32), np.zeros((0, self.n_pre), np.float32)
+        self.push(splits, ns)
+        self.push(*rest)
+
+    def pop(self, n: int):
+        """The first n domains: (splits [n, depth of the deepest], ns [n], alpha [n, n_pre] or None)."""
+        n = min(n, len(self.ns))
+        ns = self.ns[:n]
+        depth = max(1, int(ns.max()) if n else 1)
+        splits, alpha = self.splits[:n, :depth].copy(), self.alpha[:n]
+        self.splits, self.ns, self.alpha = self.splits[n:], self.ns[n:], self.alpha[n:]
+        return splits, ns.copy(), (None if n == 0 or np.isnan(alpha[:, :1]).any() else alpha.copy())
+
+    def as_list(self):
+        return [self.splits[d, : self.ns[d]].copy() for d in range(len(self.ns))]
+
+
+def make_children(splits, ns, open_idx, relu, neuron, beta=None):
+    """Both children of every open domain, in the order (d0 active, d0 inactive, d1 active, ...): the parent's history
+    with the new split appended (multiplier 0); `beta` [D, depth] replaces the parents' multipliers."""
+    k = len(open_idx)
+    depth = int(ns[open_idx].max()) + 1 if k else 1
+    out = np.zeros((2 * k, max(depth, splits.shape[1])), SPLIT_DTYPE)
+    par = splits[open_idx]
+    if beta is not None:
+        par = par.copy()
+        width = min(par.shape[1], beta.shape[1])
+        par["beta"][:, :width] = beta[open_idx][:, :width]
+    live = np.arange(par.shape[1])[None, :] < ns[open_idx][:, None]
+    par = np.where(live, par, np.zeros((), SPLIT_DTYPE))
+    out[0::2, : par.shape[1]] = par
+    out[1::2, : par.shape[1]] = par
+    rows = np.arange(k)
+    pos = ns[open_idx].astype(np.int64)
+    for sign, start in ((1, 0), (-1, 1)):
+        new = np.zeros(k, SPLIT_DTYPE)
+        new["relu"], new["neuron"], new["sign"], new["beta"] = relu[open_idx], neuron[open_idx], sign, 0.0
+        out[2 * rows + start, pos] = new
+    return out[:, :depth] if out.shape[1] > depth else out, np.repeat(ns[open_idx] + 1, 2).astype(np.int32)
+
+
 def save_frontier(path, frontier, inh_lo, inh_hi, prop: Property, rounds: int, domains_bounded: int):
     """Dump of the open domain set (the reference's BaB has no checkpoint; its sweep resumes from metadata,
     README.md:203-260).  One .npz: split histories as structure of arrays, the inherited root bounds, the property's
@@ -206,7 +282,7 @@ def select_fsb(eng, net_id, net, prop: Property, inh_lo, inh_hi, take, open_idx,
 def verify(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: int = 64, max_domains: int = 1 << 20,
            pgd_restarts: int = 256, pgd_steps: int = 50, optimize_iterations: int = 0, branching: int = 1,
            timeout_s: float | None = None, metrics_jsonl=None, checkpoint=None, resume=None,
-           warm_start: bool = True, fsb_k: int = 3) -> VerifyResult:
+           warm_start: bool = True, fsb_k: int = 3, dist=None, dist_device="cpu") -> VerifyResult:
     """metrics_jsonl: append one JSON record per round; checkpoint: path that receives the open frontier whenever the
     run stops unresolved (round limit, timeout, domain limit); resume: path of such a dump to continue from (the attack
     and the root bound are skipped).
@@ -216,94 +292,148 @@ def verify(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: i
     may then end "unknown" on properties that need the multipliers; 20 is the reference's root-level count);
     branching: 0 widest interval, 1 intercept score, 2 BaBSR, 3 filtered smart branching over the fsb_k best BaBSR and
     intercept candidates (2 and 3: Linear layers only); warm_start: with optimisation on, children start from their
-    parent's optimised slopes and split multipliers instead of the heuristic slopes and zero."""
+    parent's optimised slopes and split multipliers instead of the heuristic slopes and zero.
+    dist: an initialised torch.distributed module, one process per GPU: every rank runs this function with the same
+    arguments, rank 0 attacks and bounds the root, and from then on every rank bounds its own shard of the frontier;
+    per round the ranks exchange one small all-reduce (open domains, stop flags, the global lower bound) and level
+    their shards point to point when they drift apart (ny_b200/sharding.py).  All ranks return the same status."""
+    from . import sharding
+
     t0 = time.time()
     if not prop.violation:
         return VerifyResult("verified")
     spec, thr, owner = _rows(prop)
     n_clauses = len(prop.violation)
-    metrics = _Metrics(metrics_jsonl)
-    if resume is not None:
-        frontier, inh_lo, inh_hi, r0, b0 = load_frontier(resume, prop)
-        res = VerifyResult("unknown", rounds=0, domains_bounded=b0)   # max_rounds counts this call's rounds
-    else:
-        ce = attack(eng, net_id, net, prop, pgd_restarts, pgd_steps)
-        if ce is not None:
-            metrics.close()
-            return VerifyResult("violated", ce[0], ce[1])
-        # root: plain CROWN with CROWN-tightened intermediate bounds
-        rlo, _, inter_lo, inter_hi = eng.crown_bounds(net_id, spec, prop.in_lo, prop.in_hi)
-        res = VerifyResult("unknown", root_lower=rlo[0].copy(), domains_bounded=1)
-        if _verified_mask(rlo, thr, owner, n_clauses)[0]:
-            res.status = "verified"
-            metrics.close()
-            return res
-        inh_lo, inh_hi = inter_lo[0], inter_hi[0]
-        frontier = [np.zeros(0, SPLIT_DTYPE)]
-
-    warm = {}    # id(split history) -> the parent's optimised slopes [n_pre], for children not yet bounded
+    world = dist.get_world_size() if dist is not None else 1
+    rank = dist.get_rank() if dist is not None else 0
+    metrics = _Metrics(metrics_jsonl if rank == 0 else None)
+    n_pre = int(net.n_pre)
+    frontier = Frontier(n_pre)
+    res = VerifyResult("unknown")
+    root = {"status": "unknown", "inh": None}
+    if rank == 0:
+        if resume is not None:
+            hist, inh_lo, inh_hi, _, b0 = load_frontier(resume, prop)
+            frontier.push(*frontier_to_arrays(hist))
+            res.domains_bounded = b0                        # max_rounds counts this call's rounds
+        else:
+            ce = attack(eng, net_id, net, prop, pgd_restarts, pgd_steps)
+            if ce is not None:
+                res = VerifyResult("violated", ce[0], ce[1])
+                root["status"] = "violated"
+            else:
+                # root: plain CROWN with CROWN-tightened intermediate bounds
+                rlo, _, inter_lo, inter_hi = eng.crown_bounds(net_id, spec, prop.in_lo, prop.in_hi)
+                res = VerifyResult("unknown", root_lower=rlo[0].copy(), domains_bounded=1)
+                if _verified_mask(rlo, thr, owner, n_clauses)[0]:
+                    res.status = root["status"] = "verified"
+                inh_lo, inh_hi = inter_lo[0], inter_hi[0]
+                frontier.push(np.zeros((1, 1), SPLIT_DTYPE), np.zeros(1, np.int32))
+        root["bounded"] = res.domains_bounded
+        if root["status"] == "unknown":
+            root["inh"] = (np.asarray(inh_lo, np.float32), np.asarray(inh_hi, np.float32))
+    if world > 1:   # every rank needs the verdict of the root phase and the inherited bounds
+        box = [root]
+        dist.broadcast_object_list(box, src=0)
+        root = box[0]
+    if root["status"] != "unknown":
+        metrics.close()
+        if rank != 0:
+            res.status = root["status"]
+        return res
+    inh_lo, inh_hi = root["inh"]
+    res.domains_bounded = root["bounded"]
 
     def stop(status):
         res.status = status
         res.open_domains = len(frontier)
-        if checkpoint is not None and frontier:
-            save_frontier(checkpoint, frontier, inh_lo, inh_hi, prop, res.rounds, res.domains_bounded)
+        if checkpoint is not None and len(frontier) and world == 1:
+            save_frontier(checkpoint, frontier.as_list(), inh_lo, inh_hi, prop, res.rounds, res.domains_bounded)
         metrics.close()
         return res
 
-    while frontier and res.rounds < max_rounds:
-        if timeout_s is not None and time.time() - t0 > timeout_s:
-            return stop("timeout")
-        take, frontier = frontier[:batch], frontier[batch:]
-        D = len(take)
-        splits, ns = frontier_to_arrays(take)
-        alpha0 = None
-        if warm_start and optimize_iterations > 1 and all(id(s) in warm for s in take):
-            alpha0 = np.stack([warm.pop(id(s)) for s in take])
-        for s in take:
-            warm.pop(id(s), None)
-        eng.batch_upload(net_id, spec, prop.in_lo, prop.in_hi, inh_lo, inh_hi, splits, ns, mode=1, alpha=alpha0)
-        alpha1 = beta1 = None
-        if optimize_iterations > 1:
-            eng.batch_optimize(optimize_iterations, 0.1, 0.05)
-            if warm_start:
-                alpha1, beta1 = eng.batch_download_params()
-        else:
-            eng.batch_run()
-        lower, _, infeasible = eng.batch_download()
+    def agree(open_local, flag_local, min_local, bounded_local):
+        """(open domains of all ranks, largest stop flag, global lower bound, domains bounded by all ranks this round)"""
+        if world == 1:
+            return open_local, flag_local, min_local, bounded_local
+        import torch
+
+        t = torch.tensor([float(open_local), float(bounded_local)], dtype=torch.float64, device=dist_device)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        f = torch.tensor([float(flag_local)], dtype=torch.float64, device=dist_device)
+        dist.all_reduce(f, op=dist.ReduceOp.MAX)
+        m = torch.tensor([min_local], dtype=torch.float32, device=dist_device)
+        sharding.allreduce_min(m, dist)
+        return int(t[0].item()), int(f[0].item()), float(m[0].item()), int(t[1].item())
+
+    STUCK, TIMEOUT = 1, 2
+    total_open = agree(len(frontier), 0, float("inf"), 0)[0]
+    while total_open > 0 and res.rounds < max_rounds:
+        flag = TIMEOUT if (timeout_s is not None and time.time() - t0 > timeout_s) else 0
+        if world > 1:   # level the shards before the round (also hands the root's first children around)
+            frontier.splits, frontier.ns = _rebalance(frontier, dist, dist_device, sharding)
+            frontier.alpha = np.full((len(frontier.ns), n_pre), np.nan, np.float32)
+        splits, ns, alpha0 = frontier.pop(batch)
+        D = len(ns)
+        min_lower, n_done, n_inf = float("inf"), 0, 0
+        if D and not flag:
+            if not (warm_start and optimize_iterations > 1):
+                alpha0 = None
+            eng.batch_upload(net_id, spec, prop.in_lo, prop.in_hi, inh_lo, inh_hi, splits, ns, mode=1, alpha=alpha0)
+            alpha1 = beta1 = None
+            if optimize_iterations > 1:
+                eng.batch_optimize(optimize_iterations, 0.1, 0.05)
+                if warm_start:
+                    alpha1, beta1 = eng.batch_download_params()
+            else:
+                eng.batch_run()
+            lower, _, infeasible = eng.batch_download()
+            done = _verified_mask(lower, thr, owner, n_clauses) | (infeasible != 0)
+            feas = lower[infeasible == 0]
+            min_lower = float(feas.min()) if feas.size else float("inf")
+            n_done, n_inf = int(done.sum()), int((infeasible != 0).sum())
+            open_idx = np.flatnonzero(~done)
+            if len(open_idx):
+                relu, neuron, _ = eng.batch_select_branch(2 if branching == 3 else branching)
+                if branching == 3:   # filtered smart branching: the BaBSR / intercept candidates are tried on the device
+                    take = [splits[d, : ns[d]] for d in range(D)]
+                    for d, (r, j) in select_fsb(eng, net_id, net, prop, inh_lo, inh_hi, take, open_idx, fsb_k).items():
+                        relu[d], neuron[d] = r, j
+                if np.any(relu[open_idx] < 0):
+                    # every neuron of some domain is fixed and its bound still does not decide it: without a witness the
+                    # honest answer is unknown; the undecided domains go back to the front of the queue
+                    frontier.push_front(splits[open_idx], ns[open_idx])
+                    flag = max(flag, STUCK)
+                else:
+                    child, child_ns = make_children(splits, ns, open_idx, relu, neuron, beta1)
+                    child_alpha = None if alpha1 is None else np.repeat(alpha1[open_idx], 2, axis=0)
+                    frontier.push(child, child_ns, child_alpha)
+        elif D:
+            frontier.push_front(splits, ns)
+            D = 0
+        total_open, flag, min_lower, bounded = agree(len(frontier), flag, min_lower, D)
         res.rounds += 1
-        res.domains_bounded += D
-        done = _verified_mask(lower, thr, owner, n_clauses) | (infeasible != 0)
-        feas = lower[infeasible == 0]
-        metrics.round(round=res.rounds, batch=D, explored=res.domains_bounded, verified=int(done.sum()),
-                      infeasible=int((infeasible != 0).sum()), open=len(frontier) + int((~done).sum()),
-                      min_lower=float(feas.min()) if feas.size else float("inf"),
-                      max_depth=int(ns.max()) if D else 0)
-        if done.all():
-            continue
-        relu, neuron, _ = eng.batch_select_branch(2 if branching == 3 else branching)
-        if branching == 3:   # filtered smart branching: the BaBSR / intercept candidates are tried on the device
-            for d, (r, j) in select_fsb(eng, net_id, net, prop, inh_lo, inh_hi, take, np.flatnonzero(~done), fsb_k).items():
-                relu[d], neuron[d] = r, j
-        for d in np.flatnonzero(~done):
-            if relu[d] < 0:
-                # every neuron is fixed: the bound is exact on this piece, so the piece contains a violation
-                # candidate; without a witness the honest answer is unknown
-                frontier = [take[i] for i in np.flatnonzero(~done) if i >= d] + frontier
-                return stop("unknown")
-            for sign in (1, -1):
-                child = np.zeros(len(take[d]) + 1, SPLIT_DTYPE)
-                child[: len(take[d])] = take[d]
-                if beta1 is not None:
-                    # children start from the parent's optimised slopes and multipliers, the new split's multiplier
-                    # from zero (AlphaState / BetaState inheritance, beta_crown/domain/child.rs)
-                    child["beta"][: len(take[d])] = beta1[d][: len(take[d])]
-                    warm[id(child)] = alpha1[d]
-                child[-1] = (int(relu[d]), int(neuron[d]), sign, 0.0)
-                frontier.append(child)
-        if len(frontier) > max_domains:
+        res.domains_bounded += bounded
+        if bounded:
+            metrics.round(round=res.rounds, batch=bounded, explored=res.domains_bounded, verified=n_done, infeasible=n_inf,
+                          open=total_open, min_lower=min_lower, max_depth=int(ns.max()) if D else 0)
+        if flag == TIMEOUT:
+            return stop("timeout")
+        if flag == STUCK:
+            return stop("unknown")
+        if total_open > max_domains:
             break
-    return stop("verified" if not frontier else "unknown")
+    return stop("verified" if total_open == 0 else "unknown")
+
+
+def _rebalance(frontier: "Frontier", dist, device, sharding):
+    """Levels the ranks' shards: the histories are padded to the deepest one of any rank, then moved point to point."""
+    import torch
+
+    depth = torch.tensor([frontier.splits.shape[1]], dtype=torch.int64, device=device)
+    dist.all_reduce(depth, op=dist.ReduceOp.MAX)
+    frontier._widen(int(depth.item()))
+    return sharding.exchange_domains(frontier.splits, frontier.ns, dist, device)
 
 
 def verify_root(eng, net_id, net, prop: Property, method: str = "crown") -> VerifyResult:

@@ -189,3 +189,63 @@ def test_command_line_surface_and_exit_codes(tmp_path):
     assert rc == 0
     rc, out = run("beta-crown", str(tmp_path / "missing.nnet"), "-p", str(safe))
     assert rc == 4
+
+
+_SHARDED = r"""
+import json, os, sys
+import numpy as np
+import torch
+import torch.distributed as dist
+from ny_b200 import B200Engine, bab, formats
+from ny_b200 import workloads as W
+
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+dist.init_process_group("nccl")
+eng = B200Engine(int(os.environ["LOCAL_RANK"]))
+wl = W.config_mlp_bab(seed=83, hidden=24, depth=3, n_in=4, n_out=3, eps=0.2, n_fix=0)
+nid = eng.register_network(wl.net)
+mn = W.sample_min_margin(wl, 200000, 3)
+root, _, _, _ = eng.crown_bounds(nid, wl.spec, wl.in_lo, wl.in_hi)
+s = int(np.argmax(mn - root[0]))
+t = float(root[0][s] + 0.9 * (mn[s] - root[0][s]))
+prop = formats.Property(wl.in_lo, wl.in_hi, [[formats.Atom(-wl.spec[s], t)]])
+one = bab.verify(eng, nid, wl.net, prop, batch=32, max_rounds=400, optimize_iterations=20, warm_start=False)
+many = bab.verify(eng, nid, wl.net, prop, batch=32, max_rounds=400, optimize_iterations=20, warm_start=False, dist=dist,
+                  dist_device=f"cuda:{os.environ['LOCAL_RANK']}")
+out = dict(rank=rank, one=[one.status, one.rounds, one.domains_bounded], many=[many.status, many.rounds, many.domains_bounded])
+gathered = [None] * world
+dist.all_gather_object(gathered, out)
+if rank == 0:
+    print("RESULT " + json.dumps(gathered))
+dist.destroy_process_group()
+"""
+
+
+def test_sharded_search_over_nccl(tmp_path):
+    """The same search on one GPU and sharded over two (one process per GPU, NCCL): same verdict, the same domains
+    bounded in total (the order of a breadth-first search does not change what is explored without warm starts),
+    fewer rounds."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    import torch
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = tmp_path / "sharded.py"
+    script.write_text(_SHARDED)
+    env = dict(os.environ, PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""), NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+                        "127.0.0.1", "--master-port", "29577", str(script)], env=env, cwd=root, capture_output=True, text=True,
+                       timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    line = [ln for ln in r.stdout.splitlines() if ln.startswith("RESULT ")][-1]
+    res = json.loads(line[len("RESULT "):])
+    assert all(x["one"] == res[0]["one"] and x["many"] == res[0]["many"] for x in res)
+    one, many = res[0]["one"], res[0]["many"]
+    assert one[0] == many[0] == "verified"
+    assert many[2] == one[2] and many[1] < one[1]

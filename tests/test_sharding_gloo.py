@@ -85,3 +85,104 @@ def test_rebalance_plan_properties():
         assert f == tot
         tot += n
     assert tot == 1003
+
+
+class _OracleEngine:
+    """Stand-in for the device engine in the sharded-search test: the same calls, answered by the CPU oracle (test
+    infrastructure; the product path never does this).  Root bounds are the interval pass's, branching is the
+    intercept score on the constrained-forward bounds."""
+
+    def __init__(self, oracle, net):
+        self.o = oracle
+        self.onet = oracle.Net(net.weights, net.biases)
+        self.bounded = 0
+
+    def _with(self, spec):
+        self.ospec = self.onet.with_spec(np.asarray(spec, np.float32))
+        self.S = len(spec)
+
+    def pgd_attack(self, net_id, spec, lo, hi, x0, steps, step):
+        return np.full(len(x0), np.inf, np.float32), np.asarray(x0, np.float32), -1
+
+    def crown_bounds(self, net_id, spec, lo, hi):
+        self._with(spec)
+        rl, ru = self.o.ibp_forward(self.ospec, lo, hi)
+        cl, cu = self.o.crown(self.ospec, lo, hi)
+        return cl[None].astype(np.float32), cu[None].astype(np.float32), rl[None, : -self.S], ru[None, : -self.S]
+
+    def batch_upload(self, net_id, spec, lo, hi, inh_lo, inh_hi, splits, ns, mode=1, alpha=None):
+        self._with(spec)
+        self._b = (lo, hi, np.concatenate([inh_lo, np.full(self.S, -np.inf, np.float32)]),
+                   np.concatenate([inh_hi, np.full(self.S, np.inf, np.float32)]), splits.copy(), ns.copy())
+
+    def batch_run(self):
+        lo, hi, il, iu, splits, ns = self._b
+        self._r = self.o.bab_bound_batch(self.ospec, lo, hi, il, iu, splits, ns, 1)[:3]
+        self.bounded += len(ns)
+
+    def batch_download(self):
+        return self._r
+
+    def batch_select_branch(self, kind):
+        lo, hi, il, iu, splits, ns = self._b
+        relu, neuron = np.full(len(ns), -1, np.int32), np.full(len(ns), -1, np.int32)
+        for d in range(len(ns)):
+            pl, pu, bad = self.o.domain_bounds(self.ospec, lo, hi, il, iu, splits[d][: ns[d]], 1)
+            pick = None if bad else self.o.select_intercept(self.ospec, pl, pu, splits[d][: ns[d]])
+            if pick is not None:
+                relu[d], neuron[d] = pick[0], pick[1]
+        return relu, neuron, np.zeros(len(ns), np.float32)
+
+
+def _search_problem():
+    from ny_b200 import formats
+    from ny_b200 import workloads as W
+
+    wl = W.config_mlp_bab(seed=84, hidden=12, depth=2, n_in=3, n_out=3, eps=0.15, n_fix=0)
+    mn = W.sample_min_margin(wl, 100000, 3)
+    return wl, mn, formats
+
+
+def _search_worker(rank, world, port, ret):
+    import torch.distributed as dist
+
+    from ny_b200 import bab
+    from oracle import ny_oracle
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    if world > 1:
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        wl, mn, formats = _search_problem()
+        eng = _OracleEngine(ny_oracle, wl.net)
+        eng._with(wl.spec)
+        root = ny_oracle.crown(eng.ospec, wl.in_lo, wl.in_hi)[0]
+        s = int(np.argmax(mn - root))
+        t = float(root[s] + 0.4 * (mn[s] - root[s]))
+        prop = formats.Property(wl.in_lo, wl.in_hi, [[formats.Atom(-wl.spec[s], t)]])
+        r = bab.verify(eng, 0, wl.net, prop, batch=2, max_rounds=400, dist=dist if world > 1 else None)
+        ret[rank] = dict(status=r.status, rounds=r.rounds, bounded=r.domains_bounded, local=eng.bounded, open=r.open_domains)
+    finally:
+        if world > 1:
+            dist.destroy_process_group()
+
+
+def test_sharded_search_reaches_the_single_rank_verdict():
+    """The branch-and-bound loop over two gloo ranks (bounds from the CPU oracle in place of the device): same
+    verdict as one rank, both ranks do part of the work, and the ranks agree on the counters."""
+    import torch.multiprocessing as mp
+
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        _search_worker(0, 1, 0, ret)
+        single = dict(ret[0])
+        port = _free_port()
+        mp.spawn(_search_worker, args=(2, port, ret), nprocs=2, join=True)
+        r0, r1 = dict(ret[0]), dict(ret[1])
+    assert single["status"] == "verified" and single["bounded"] > 8, single
+    assert r0["status"] == r1["status"] == "verified"
+    assert r0["rounds"] == r1["rounds"] and r0["bounded"] == r1["bounded"] and r0["open"] == r1["open"] == 0
+    assert r0["local"] > 0 and r1["local"] > 0                     # the frontier really was shared out
+    assert r0["local"] + r1["local"] == r0["bounded"] - 1          # every domain bounded once (+ the root bound)
+    assert r0["rounds"] < single["rounds"]                         # two shards per round: fewer rounds
