@@ -73,55 +73,67 @@ def frontier_to_arrays(frontier):
 
 
 class Frontier:
-    """The open domain set as a structure of arrays: split histories [N, depth] with their lengths [N] and,
-    optionally, warm-start slopes [N, n_pre] (NaN rows where a domain has none).  Batches leave from the front,
-    children are appended at the back (breadth-first), rebalancing between ranks takes from the back."""
+    """The open domain set as blocks of structure-of-arrays records: split histories [n, depth] with their lengths
+    [n] and, optionally, warm-start slopes [n, n_pre].  Batches leave from the front, children are appended at the
+    back (breadth-first); nothing is copied when a block is appended."""
 
     def __init__(self, n_pre: int):
-        self.splits = np.zeros((0, 1), SPLIT_DTYPE)
-        self.ns = np.zeros(0, np.int32)
-        self.alpha = np.zeros((0, n_pre), np.float32)
+        from collections import deque
+
+        self.blocks = deque()     # (splits, ns, alpha or None)
+        self.n = 0
         self.n_pre = n_pre
 
     def __len__(self):
-        return len(self.ns)
-
-    def _widen(self, depth: int):
-        if depth > self.splits.shape[1]:
-            grown = np.zeros((len(self.ns), depth), SPLIT_DTYPE)
-            grown[:, : self.splits.shape[1]] = self.splits
-            self.splits = grown
+        return self.n
 
     def push(self, splits, ns, alpha=None):
         if len(ns) == 0:
             return
         splits = np.asarray(splits, SPLIT_DTYPE).reshape(len(ns), -1)
-        self._widen(splits.shape[1])
-        block = np.zeros((len(ns), self.splits.shape[1]), SPLIT_DTYPE)
-        block[:, : splits.shape[1]] = splits
-        self.splits = np.concatenate([self.splits, block])
-        self.ns = np.concatenate([self.ns, np.asarray(ns, np.int32)])
-        if alpha is None:
-            alpha = np.full((len(ns), self.n_pre), np.nan, np.float32)
-        self.alpha = np.concatenate([self.alpha, np.asarray(alpha, np.float32)])
+        self.blocks.append((splits, np.asarray(ns, np.int32), None if alpha is None else np.asarray(alpha, np.float32)))
+        self.n += len(ns)
 
     def push_front(self, splits, ns):
-        rest = (self.splits, self.ns, self.alpha)
-        self.splits, self.ns, self.alpha = np.zeros((0, 1), SPLIT_DTYPE), np.zeros(0, np.int32), np.zeros((0, self.n_pre), np.float32)
-        self.push(splits, ns)
-        self.push(*rest)
+        if len(ns) == 0:
+            return
+        splits = np.asarray(splits, SPLIT_DTYPE).reshape(len(ns), -1)
+        self.blocks.appendleft((splits, np.asarray(ns, np.int32), None))
+        self.n += len(ns)
 
     def pop(self, n: int):
-        """The first n domains: (splits [n, depth of the deepest], ns [n], alpha [n, n_pre] or None)."""
-        n = min(n, len(self.ns))
-        ns = self.ns[:n]
-        depth = max(1, int(ns.max()) if n else 1)
-        splits, alpha = self.splits[:n, :depth].copy(), self.alpha[:n]
-        self.splits, self.ns, self.alpha = self.splits[n:], self.ns[n:], self.alpha[n:]
-        return splits, ns.copy(), (None if n == 0 or np.isnan(alpha[:, :1]).any() else alpha.copy())
+        """The first n domains: (splits [n, depth of the deepest], ns [n], alpha [n, n_pre], or None unless every one
+        of them has warm-start slopes)."""
+        parts, got = [], 0
+        while self.blocks and got < n:
+            sp, ns, al = self.blocks.popleft()
+            take = min(n - got, len(ns))
+            if take < len(ns):
+                self.blocks.appendleft((sp[take:], ns[take:], None if al is None else al[take:]))
+            parts.append((sp[:take], ns[:take], None if al is None else al[:take]))
+            got += take
+        self.n -= got
+        if not parts:
+            return np.zeros((0, 1), SPLIT_DTYPE), np.zeros(0, np.int32), None
+        ns = np.concatenate([p[1] for p in parts])
+        depth = max(1, int(ns.max()))
+        splits = np.zeros((got, depth), SPLIT_DTYPE)
+        row = 0
+        for sp, n_, _ in parts:
+            w = min(depth, sp.shape[1])
+            splits[row: row + len(n_), :w] = sp[:, :w]
+            row += len(n_)
+        alpha = None if any(p[2] is None for p in parts) else np.concatenate([p[2] for p in parts])
+        return splits, ns, alpha
+
+    def arrays(self):
+        """Everything as two arrays (splits [N, deepest], ns [N]); the warm-start slopes are dropped."""
+        return self.pop(self.n)[:2] if self.n else (np.zeros((0, 1), SPLIT_DTYPE), np.zeros(0, np.int32))
 
     def as_list(self):
-        return [self.splits[d, : self.ns[d]].copy() for d in range(len(self.ns))]
+        splits, ns = self.arrays()
+        self.push(splits, ns)
+        return [splits[d, : ns[d]].copy() for d in range(len(ns))]
 
 
 def make_children(splits, ns, open_idx, relu, neuron, beta=None):
@@ -371,8 +383,7 @@ def verify(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: i
     while total_open > 0 and res.rounds < max_rounds:
         flag = TIMEOUT if (timeout_s is not None and time.time() - t0 > timeout_s) else 0
         if world > 1:   # level the shards before the round (also hands the root's first children around)
-            frontier.splits, frontier.ns = _rebalance(frontier, dist, dist_device, sharding)
-            frontier.alpha = np.full((len(frontier.ns), n_pre), np.nan, np.float32)
+            _rebalance(frontier, dist, dist_device, sharding)
         splits, ns, alpha0 = frontier.pop(batch)
         D = len(ns)
         min_lower, n_done, n_inf = float("inf"), 0, 0
@@ -430,10 +441,15 @@ def _rebalance(frontier: "Frontier", dist, device, sharding):
     """Levels the ranks' shards: the histories are padded to the deepest one of any rank, then moved point to point."""
     import torch
 
-    depth = torch.tensor([frontier.splits.shape[1]], dtype=torch.int64, device=device)
+    splits, ns = frontier.arrays()
+    depth = torch.tensor([splits.shape[1]], dtype=torch.int64, device=device)
     dist.all_reduce(depth, op=dist.ReduceOp.MAX)
-    frontier._widen(int(depth.item()))
-    return sharding.exchange_domains(frontier.splits, frontier.ns, dist, device)
+    if int(depth.item()) > splits.shape[1]:
+        grown = np.zeros((len(ns), int(depth.item())), SPLIT_DTYPE)
+        grown[:, : splits.shape[1]] = splits
+        splits = grown
+    splits, ns = sharding.exchange_domains(splits, ns, dist, device)
+    frontier.push(splits, ns)
 
 
 def verify_root(eng, net_id, net, prop: Property, method: str = "crown") -> VerifyResult:
