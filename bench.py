@@ -290,10 +290,10 @@ def run_ours(args, rank, world, local_rank):
         roofline = {
             "bound": "tensor", "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
             "frac": (achieved / peak_tf) if achieved else None,
-            # dram__bytes_read.sum + dram__bytes_write.sum of one hidden-layer launch from the ncu capture summarised in
-            # profiles/k_umma_tf32x3_mlp784_8x256.md (21.5 MB at 1024 domains: the operand comes from DRAM, the result
-            # stays in L2), scaled to this launch by the number of domains
-            "traffic": 21.5e6 * D / 1024 if eng_path_name(eng) != "f64" else None,
+            # dram__bytes_read.sum + dram__bytes_write.sum of one hidden-layer launch from the committed ncu capture of
+            # this kernel (20.7 MB at 1024 domains: the operand comes from DRAM, the result stays in L2), scaled to this
+            # launch by the number of domains
+            "traffic": 20.7e6 * D / 1024 if eng_path_name(eng) != "f64" else None,
             "kernel": "k_gemm_f64" if eng_path_name(eng) == "f64" else "k_umma_tf32x3",
             "peak_source": f"{peaks['source']} bf16 GEMM / 2 (TF32 operand rate)",
             "hbm_view": {"achieved_gbs": BYTES_PER_DOMAIN * D / ((fwd_ms + bwd_ms) / 1e3) / 1e9 if (fwd_ms + bwd_ms) > 0 else None,

@@ -161,8 +161,8 @@ def make_children(splits, ns, open_idx, relu, neuron, beta=None):
 
 
 def save_frontier(path, frontier, inh_lo, inh_hi, prop: Property, rounds: int, domains_bounded: int):
-    """Dump of the open domain set (the reference's BaB has no checkpoint; its sweep resumes from metadata,
-    README.md:203-260).  One .npz: split histories as structure of arrays, the inherited root bounds, the property's
+    """Dump of the open domain set (the reference's BaB has no checkpoint; its benchmark sweep resumes from metadata,
+    lines 203-260 of the reference's README).  One .npz: split histories as structure of arrays, the inherited root bounds, the property's
     box and rows (so that a resume against another property is refused), and the counters."""
     splits, ns = frontier_to_arrays(frontier)
     spec, thr, owner = _rows(prop)
