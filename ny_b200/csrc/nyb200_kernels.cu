@@ -651,7 +651,8 @@ __device__ __forceinline__ void atomic_min_float(float *addr, float v) {
 }
 
 // Counts the domains whose accumulated rounding penalty is not small against their bounds: a row is
-// "loose" when rpen > tol * max(|bound|, 1% of the domain's largest bound magnitude).  The host re-runs
+// "loose" when rpen > tol * max(|bound|, 1% of the domain's largest bound magnitude), or when the row's width is
+// smaller than the charges on its two ends.  The host re-runs
 // the batch on the binary64 path when the count is non-zero, so that the fast path never returns a
 // bound that its own rounding model has visibly loosened.
 __global__ void k_count_loose(int D, int S, int R, const float *__restrict__ out_lo, const float *__restrict__ out_hi,
@@ -674,6 +675,9 @@ __global__ void k_count_loose(int D, int S, int R, const float *__restrict__ out
         if (!isfinite(l) || !isfinite(u)) continue;
         double pl = rpen[(long)d * R + s], pu = rpen[(long)d * R + S + s];
         if (pl > (double)tol * fmaxf(fabsf(l), 0.01f * scale) || pu > (double)tol * fmaxf(fabsf(u), 0.01f * scale)) loose = true;
+        // the charge alone keeps the row from inverting (lower > upper marks an empty domain and is published as
+        // [-inf, +inf], bounds/concretize.rs:717-880): let the binary64 pass decide
+        if ((double)u - (double)l < pl + pu) loose = true;
     }
     if (loose) { atomicAdd(n_loose, 1); flags[d] = f | kFlagLoose; }
 }
