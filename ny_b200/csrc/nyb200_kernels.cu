@@ -525,8 +525,8 @@ k_relax_dom(int n, int off, int D, int R, int S, long nps, float *A, int lda, co
 
 // ---------------------------------------------------------------- binary64-accumulated contraction
 // C[M x N] = A[M x K] * B[K x N]; the fp32 products are exact in binary64, the running sums round to
-// nearest (bounded by eps*|A||B|, charged in k_relax), and the final cast to fp32 is measured exactly
-// and charged against the interval of the variable the coefficient multiplies.
+// nearest (bounded by eps*|A||B|, charged in k_relax), and the final cast to fp32 is measured exactly,
+// sign included, and charged against the interval of the variable the coefficient multiplies.
 constexpr int GM = 64, GN = 64, GK = 16;
 __global__ void __launch_bounds__(256)
 k_gemm_f64(int M, int N, int K, const float *__restrict__ A, int lda, const float *__restrict__ B, int ldb,
@@ -572,6 +572,7 @@ k_gemm_f64(int M, int N, int K, const float *__restrict__ A, int lda, const floa
         double pen = 0.0;
         if (m < M) {
             int d = m / R;
+            const bool upper_row = (m % R) >= (R >> 1);  // a domain's rows: the lower half, then the upper half
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 int n = n0 + tx * 4 + j;
@@ -579,9 +580,13 @@ k_gemm_f64(int M, int N, int K, const float *__restrict__ A, int lda, const floa
                 float c = (float)acc[i][j];
                 C[(long)m * ldc + n] = c;
                 if (rpen) {
-                    double err = fabs(acc[i][j] - (double)c);
-                    float zm = fmaxf(fabsf(zin_lo[(long)d * zin_ds + n]), fabsf(zin_hi[(long)d * zin_ds + n]));
-                    pen += err * (double)zm;
+                    // The exact coefficient is c + e with e known, and it multiplies z in [zl, zu]: a lower row loses at
+                    // most -min(e zl, e zu), an upper row gains at most max(e zl, e zu).  Signed, so the roundings of a
+                    // row cancel against one another the way they do in the exact sum (|e| max|z| would add them up).
+                    const double e = acc[i][j] - (double)c;
+                    const double zl = zin_lo[(long)d * zin_ds + n], zu = zin_hi[(long)d * zin_ds + n];
+                    const double a = e * zl, b = e * zu;
+                    pen += (upper_row ? fmax(a, b) : fmax(-a, -b)) + 2.9e-14 * fabs(e) * fmax(fabs(zl), fabs(zu));
                 }
             }
         }
