@@ -337,7 +337,7 @@ k_relax(int n, int off, int M, int R, int S, int n_pre, int identity, float *A, 
                 float p = a * slope;
                 nw = upper ? next_up_f(p) : next_down_f(p);
                 double gap = fabs((double)a * (double)slope - (double)nw);
-                sp += gap * (double)za;
+                if (!(t.y == 1.f && t.z == 0.f)) sp += gap * (double)za;  // see relax_one: no charge where z >= 0
             }
             if (icp != 0.f) { double c = (double)a * (double)icp; sb += c; sa += fabs(c); }
             if (t.w != 0.f) nw = upper ? nw + t.w : nw - t.w;
@@ -379,7 +379,12 @@ __device__ __forceinline__ float relax_one(float a, float4 t, float au, float za
         // overflowed one steps into a NaN pattern, which the concretisation turns into [-inf, +inf] for the row
         nw = (prod == 0.f) ? (UPPER ? __fmul_ru(a, slope) : __fmul_rd(a, slope)) : stepped;
         nw = (a == 0.f || slope == 0.f) ? 0.f : nw;
-        sp = __fmaf_ru(fabsf(fmaf(a, slope, -nw)), za, sp);
+        // The step above is outward in the coefficient.  That alone is sound where the variable it multiplies cannot
+        // be negative: a neuron that is active on the whole domain (table (1, 1, 0): pre-activation lower bound >= 0,
+        // by its interval or by a split).  Everywhere else the pre-activation may be negative and the gap between the
+        // exact product and the stepped one is charged against its magnitude.
+        const bool nonneg = (t.y == 1.f) && (t.z == 0.f);
+        sp = __fmaf_ru(nonneg ? 0.f : fabsf(fmaf(a, slope, -nw)), za, sp);
         sb = fma((double)a, (double)icp, sb);
         sa = __fmaf_ru(fabsf(a), fabsf(icp), sa);
         nw = UPPER ? nw + t.w : nw - t.w;  // signed beta (zero for unsplit neurons), relu_backward.rs:156-175
