@@ -186,3 +186,18 @@ def test_fsb_candidate_filter_and_margin():
     m = bab._margin(np.array([[1.0, 0.5, -2.0], [0.5, 3.0, 0.25]], np.float32), np.array([0.0, 1.0, 0.0], np.float32),
                     np.array([0, 0, 1]), 2)
     assert m.tolist() == [-2.0, 0.25]
+
+
+def test_command_line_errors_exit_with_code_4(tmp_path):
+    """Operational errors (missing model, malformed property, unknown format) leave with the reference's code 4 before any
+    device is touched."""
+    from ny_b200.__main__ import main
+
+    model = tmp_path / "abs.nnet"
+    model.write_text(ABS_NNET)
+    bad_prop = tmp_path / "bad.vnnlib"
+    bad_prop.write_text("(declare-const X_0 Real)(declare-const Y_0 Real)(assert (>= X_0 0.0))(assert (>= Y_0 1.0))")
+    assert main(["beta-crown", str(tmp_path / "missing.nnet"), "-p", str(bad_prop)]) == 4
+    assert main(["beta-crown", str(model), "-p", str(bad_prop)]) == 4            # no upper bound on X_0
+    assert main(["verify", str(tmp_path / "model.pt"), "-p", str(bad_prop)]) == 4
+    assert main(["beta-crown", str(model)]) == 4                                  # -p is required
