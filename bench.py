@@ -513,6 +513,62 @@ def run_cnn(args, local_rank, kind="cnn"):
     eng.close()
 
 
+
+def run_search(args, local_rank):
+    """Secondary workload (--workload bab-search): the whole branch-and-bound loop (ny_b200/bab.py) on a seeded MLP
+    64 -> 4x256 -> 10 with a property it cannot close in the given rounds, so that every round bounds a full batch:
+    upload of the children's split lists, bound, download, branching choice, child creation on the host.  One step =
+    one search of `rounds` rounds; value = domains bounded per second of wall clock, host work included."""
+    import torch
+
+    from ny_b200 import B200Engine, bab, formats
+    from ny_b200 import engine as E
+    from ny_b200 import workloads as W
+
+    torch.cuda.set_device(local_rank)
+    eng = B200Engine(local_rank, torch.cuda.current_stream().cuda_stream)
+    eng.set_path(E.PATH_TF32X3 if args.path == "tf32x3" else E.PATH_F64)
+    wl = W.config_mlp_bab(seed=7, hidden=256, depth=4, n_in=64, n_out=10, eps=0.05, n_fix=0)
+    nid = eng.register_network(wl.net)
+    root, _, _, _ = eng.crown_bounds(nid, wl.spec, wl.in_lo, wl.in_hi)
+    s = int(np.argmin(root[0]))
+    prop = formats.Property(wl.in_lo, wl.in_hi, [[formats.Atom(-wl.spec[s], float(root[0][s] + 0.5 * abs(root[0][s]) + 0.5))]])
+    batch = args.domains if args.domains != D_PER_GPU else 4096
+    rounds = 40
+
+    def search():
+        return bab.verify(eng, nid, wl.net, prop, batch=batch, max_rounds=rounds, optimize_iterations=0, branching=1,
+                          pgd_restarts=64, pgd_steps=10)
+
+    for _ in range(max(args.warmup, 3)):
+        r = search()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    l0 = eng.launch_count()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    bounded = 0
+    for _ in range(args.steps):
+        r = search()
+        bounded += r.domains_bounded
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    launches = eng.launch_count() - l0
+    clocks = sampler.stop()
+    value = bounded / dt
+    _emit({
+        "metric": "BaB domains bounded/sec (beta-CROWN), whole search loop", "value": value, "unit": UNIT, "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": dt * 1e3 / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": args.path, "data": "synthetic",
+        "config": {"workload": f"branch and bound on a ReLU MLP 64->4x256->10, box x0+-0.05, one property row, {rounds} rounds "
+                               f"of up to {batch} domains, intercept branching, one bound per domain, attack and root bound included",
+                   "timing": "wall clock around the search calls", "status": r.status, "domains_per_search": r.domains_bounded,
+                   "open_at_stop": r.open_domains},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": None, "d2h_bytes_per_step": None, "ms_per_step": dt * 1e3 / args.steps},
+        "gpu_launches": int(launches), "clocks": clocks,
+    })
+    eng.close()
+
 def run_pgd(args, local_rank, kind="cnn"):
     """Secondary workload (--workload pgd): PGD attack, 100 steps x 1024 restarts, step 0.25 * eps, margin loss,
     on the CNN 3x32x32 conv(16,k4,s2,p1)-conv(32,k4,s2,p1)-FC100-FC10 with box x0 +- 2/255.  One step of this bench =
@@ -591,7 +647,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--path", default=os.environ.get("NYB200_PATH", "tf32x3"), choices=["f64", "tf32x3"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="bab", choices=["bab", "alpha-crown", "cnn", "resnet", "pgd", "pgd-resnet"],
+    ap.add_argument("--workload", default="bab", choices=["bab", "alpha-crown", "cnn", "resnet", "pgd", "pgd-resnet", "bab-search"],
                     help="bab: the headline beta-CROWN batch (default); alpha-crown: the alpha optimisation case; "
                          "cnn: the convolutional case (both 1 GPU)")
     ap.add_argument("--domains", type=int, default=D_PER_GPU, help="domains per GPU (profiling runs use a smaller batch)")
@@ -605,6 +661,10 @@ def main():
     if args.workload == "alpha-crown":
         if rank == 0:
             run_alpha_crown(args, 0, 1, local_rank)
+        return
+    if args.workload == "bab-search":
+        if rank == 0:
+            run_search(args, local_rank)
         return
     if args.workload in ("pgd", "pgd-resnet"):
         if rank == 0:
