@@ -138,27 +138,28 @@ class Frontier:
 
 def make_children(splits, ns, open_idx, relu, neuron, beta=None):
     """Both children of every open domain, in the order (d0 active, d0 inactive, d1 active, ...): the parent's history
-    with the new split appended (multiplier 0); `beta` [D, depth] replaces the parents' multipliers."""
+    with the new split appended (multiplier 0); `beta` [D, depth] replaces the parents' multipliers.  Works on the
+    records as rows of four 32-bit words (relu, neuron, sign, multiplier bits)."""
     k = len(open_idx)
-    depth = int(ns[open_idx].max()) + 1 if k else 1
-    out = np.zeros((2 * k, max(depth, splits.shape[1])), SPLIT_DTYPE)
-    par = splits[open_idx]
+    open_idx = np.asarray(open_idx, np.int64)
+    n_par = ns[open_idx].astype(np.int64)
+    depth = int(n_par.max()) + 1 if k else 1
+    words = np.ascontiguousarray(splits).view(np.int32).reshape(splits.shape[0], splits.shape[1], 4)
+    w = min(depth, splits.shape[1])
+    par = words[open_idx, :w].copy()                                     # [k, w, 4]
     if beta is not None:
-        par = par.copy()
-        width = min(par.shape[1], beta.shape[1])
-        par["beta"][:, :width] = beta[open_idx][:, :width]
-    live = np.arange(par.shape[1])[None, :] < ns[open_idx][:, None]
-    par = np.where(live, par, np.zeros((), SPLIT_DTYPE))
-    out[0::2, : par.shape[1]] = par
-    out[1::2, : par.shape[1]] = par
+        bw = min(w, beta.shape[1])
+        par[:, :bw, 3] = np.ascontiguousarray(beta[open_idx, :bw], np.float32).view(np.int32)
+    par *= (np.arange(w)[None, :] < n_par[:, None])[:, :, None]          # records past a history's end are zero
+    out = np.zeros((2 * k, depth, 4), np.int32)
+    out[0::2, :w] = par
+    out[1::2, :w] = par
     rows = np.arange(k)
-    pos = ns[open_idx].astype(np.int64)
-    for sign, start in ((1, 0), (-1, 1)):
-        new = np.zeros(k, SPLIT_DTYPE)
-        new["relu"], new["neuron"], new["sign"], new["beta"] = relu[open_idx], neuron[open_idx], sign, 0.0
-        out[2 * rows + start, pos] = new
-    return out[:, :depth] if out.shape[1] > depth else out, np.repeat(ns[open_idx] + 1, 2).astype(np.int32)
-
+    out[2 * rows, n_par, 0] = out[2 * rows + 1, n_par, 0] = relu[open_idx]
+    out[2 * rows, n_par, 1] = out[2 * rows + 1, n_par, 1] = neuron[open_idx]
+    out[2 * rows, n_par, 2] = 1
+    out[2 * rows + 1, n_par, 2] = -1
+    return out.reshape(2 * k, depth * 4).view(SPLIT_DTYPE).reshape(2 * k, depth), np.repeat(n_par + 1, 2).astype(np.int32)
 
 def save_frontier(path, frontier, inh_lo, inh_hi, prop: Property, rounds: int, domains_bounded: int):
     """Dump of the open domain set (the reference's BaB has no checkpoint; its benchmark sweep resumes from metadata,

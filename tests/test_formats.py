@@ -201,3 +201,22 @@ def test_command_line_errors_exit_with_code_4(tmp_path):
     assert main(["beta-crown", str(model), "-p", str(bad_prop)]) == 4            # no upper bound on X_0
     assert main(["verify", str(tmp_path / "model.pt"), "-p", str(bad_prop)]) == 4
     assert main(["beta-crown", str(model)]) == 4                                  # -p is required
+
+
+def test_make_children_appends_the_split_and_keeps_histories():
+    from ny_b200 import bab
+    from ny_b200.engine import SPLIT_DTYPE
+
+    sp = np.zeros((3, 2), SPLIT_DTYPE)
+    ns = np.array([0, 1, 2], np.int32)
+    sp[1, 0] = (1, 5, -1, 0.5)
+    sp[1, 1] = (9, 9, 9, 9.0)                       # junk past the end of history 1 must not travel
+    sp[2, 0], sp[2, 1] = (0, 3, 1, 0.25), (1, 7, -1, 0.75)
+    beta = np.array([[0, 0], [0.125, 0], [1.5, 2.5]], np.float32)
+    ch, cn = bab.make_children(sp, ns, np.array([0, 1, 2]), np.array([2, 0, 1]), np.array([4, 6, 8]), beta=beta)
+    assert cn.tolist() == [1, 1, 2, 2, 3, 3] and ch.shape == (6, 3)
+    assert ch[0, 0].tolist() == (2, 4, 1, 0.0) and ch[1, 0].tolist() == (2, 4, -1, 0.0)
+    assert ch[2, 0].tolist() == (1, 5, -1, 0.125) and ch[2, 1].tolist() == (0, 6, 1, 0.0) and ch[2, 2].tolist() == (0, 0, 0, 0.0)
+    assert ch[5, 0].tolist() == (0, 3, 1, 1.5) and ch[5, 1].tolist() == (1, 7, -1, 2.5) and ch[5, 2].tolist() == (1, 8, -1, 0.0)
+    ch2, _ = bab.make_children(sp, ns, np.array([2]), np.array([2, 0, 1]), np.array([4, 6, 8]))     # multipliers kept
+    assert ch2[0, 0].tolist() == (0, 3, 1, 0.25) and ch2[1, 1].tolist() == (1, 7, -1, 0.75)
