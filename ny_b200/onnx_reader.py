@@ -1,4 +1,5 @@
-"""A minimal ONNX reader for feed-forward ReLU networks: Gemm / MatMul+Add / Conv / Relu / Flatten / Reshape.
+"""A minimal ONNX reader for feed-forward ReLU networks: Gemm / MatMul+Add / Conv / Relu / Flatten / Reshape, constant
+Transpose of weights, and Sub / Div / Mul input normalisation folded into the first dense layer.
 
 The reference loads ONNX through its own protobuf parser (crates/ny-onnx/src/onnx); here the protobuf wire format
 is decoded directly with the field numbers of the public onnx.proto3 schema (ModelProto.graph = 7; GraphProto
@@ -192,6 +193,10 @@ def parse_onnx(data: bytes):
     for op, ins, outs, attrs in nodes:                 # Constant nodes are initialisers under another name
         if op == "Constant" and "value" in attrs and outs:
             inits[outs[0]] = attrs["value"]
+    for op, ins, outs, attrs in nodes:                 # a Transpose of a constant is a constant (MatMul(x, W^T) exports)
+        if op == "Transpose" and ins and ins[0] in inits and outs:
+            perm = attrs.get("perm")
+            inits[outs[0]] = np.transpose(inits[ins[0]], perm) if perm else inits[ins[0]].T
     data_inputs = [(n, d) for n, d in inputs if n not in inits]
     if len(data_inputs) != 1:
         raise EngineError(_UNSUPPORTED, f"onnx: {len(data_inputs)} graph inputs, expected one")
@@ -211,8 +216,9 @@ def parse_onnx(data: bytes):
             raise EngineError(_UNSUPPORTED, f"onnx: {what} is not a constant")
         return inits[name]
 
+    pre_scale, pre_shift = None, None      # input normalisation (x - shift) * scale in front of the first layer
     for op, ins, outs, attrs in nodes:
-        if op == "Constant":
+        if op == "Constant" or (op == "Transpose" and ins and ins[0] in inits):
             continue
         if cur not in ins:
             raise EngineError(_UNSUPPORTED, f"onnx: node {op} is off the single data path")
@@ -251,8 +257,31 @@ def parse_onnx(data: bytes):
                 bias = np.broadcast_to(np.asarray(need_const(ins[2], "Gemm bias"), np.float64).reshape(-1), (w.shape[0],)) * beta
             if layers and not layers[-1][3]:
                 raise EngineError(_UNSUPPORTED, "onnx: two affine layers without a Relu between them")
-            layers.append(["linear", (w * alpha).astype(np.float32), None if bias is None else bias.astype(np.float32), False])
+            w = w * alpha
+            if pre_scale is not None and not layers:     # W ((x - sh) * sc) + b = (W * sc) x + (b - (W * sc) sh)
+                w = w * pre_scale[None, :]
+                bias = (np.zeros(w.shape[0]) if bias is None else np.asarray(bias, np.float64)) - w @ pre_shift
+                pre_scale = pre_shift = None
+            layers.append(["linear", w.astype(np.float32), None if bias is None else np.asarray(bias).astype(np.float32), False])
             shape = (w.shape[0],)
+        elif op in ("Sub", "Div", "Mul") and not layers:
+            # (x - mean) / std in front of the network: folded into the first affine layer below
+            if ins[0] != cur:
+                raise EngineError(_UNSUPPORTED, f"onnx: {op} with the data as right operand")
+            c = np.broadcast_to(np.asarray(need_const(ins[1], f"{op} operand"), np.float64), shape).reshape(-1)
+            sc = np.ones(flat(shape)) if pre_scale is None else pre_scale
+            sh = np.zeros(flat(shape)) if pre_shift is None else pre_shift
+            if op == "Sub":      # (x - sh) * sc - c = (x - (sh + c / sc)) * sc
+                if np.any(sc == 0):
+                    raise EngineError(_UNSUPPORTED, "onnx: normalisation with a zero scale")
+                sh = sh + c / sc
+            elif op == "Div":
+                if np.any(c == 0):
+                    raise EngineError(_INVALID, "onnx: division by zero in the input normalisation")
+                sc = sc / c
+            else:
+                sc = sc * c
+            pre_scale, pre_shift = sc, sh
         elif op == "Add":
             other = ins[1] if ins[0] == cur else ins[0]
             c = np.asarray(need_const(other, "Add operand"), np.float32).reshape(-1)
@@ -278,6 +307,8 @@ def parse_onnx(data: bytes):
                 bias = np.asarray(need_const(ins[2], "Conv bias"), np.float32).reshape(-1)
             if layers and not layers[-1][3]:
                 raise EngineError(_UNSUPPORTED, "onnx: two affine layers without a Relu between them")
+            if pre_scale is not None:
+                raise EngineError(_UNSUPPORTED, "onnx: input normalisation in front of a convolution")
             conv = Conv2d(w, bias, (strides[0], strides[1]), (pads[0], pads[1]), (shape[1], shape[2]))
             layers.append(["conv", conv, None, False])
             shape = (conv.oc, conv.oh, conv.ow)

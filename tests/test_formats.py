@@ -220,3 +220,34 @@ def test_make_children_appends_the_split_and_keeps_histories():
     assert ch[5, 0].tolist() == (0, 3, 1, 1.5) and ch[5, 1].tolist() == (1, 7, -1, 2.5) and ch[5, 2].tolist() == (1, 8, -1, 0.0)
     ch2, _ = bab.make_children(sp, ns, np.array([2]), np.array([2, 0, 1]), np.array([4, 6, 8]))     # multipliers kept
     assert ch2[0, 0].tolist() == (0, 3, 1, 0.25) and ch2[1, 1].tolist() == (1, 7, -1, 0.75)
+
+
+def test_onnx_input_normalisation_and_constant_transpose_are_folded():
+    from ny_b200 import onnx_reader as R
+    from ny_b200 import workloads as W
+
+    g = np.random.Generator(np.random.PCG64(8))
+    w1 = g.standard_normal((5, 4)).astype(np.float32)
+    b1 = g.standard_normal(5).astype(np.float32)
+    w2 = g.standard_normal((3, 5)).astype(np.float32)
+    mean = g.standard_normal(4).astype(np.float32)
+    std = (0.5 + g.random(4)).astype(np.float32)
+    nodes = [R._enc_node("Sub", ["input", "mean"], ["c"]), R._enc_node("Div", ["c", "std"], ["n"]),
+             R._enc_node("Gemm", ["n", "W1", "B1"], ["z1"], [R._enc_attr_int("transB", 1)]), R._enc_node("Relu", ["z1"], ["a1"]),
+             R._enc_node("Transpose", ["W2t"], ["W2"]), R._enc_node("MatMul", ["a1", "W2"], ["y"])]
+    graph = b"".join(R._ld(1, n) for n in nodes)
+    for name, arr in (("mean", mean), ("std", std), ("W1", w1), ("B1", b1), ("W2t", w2)):     # W2t is [out, in]: MatMul needs its transpose
+        graph += R._ld(5, R._enc_tensor(name, arr))
+    graph += R._ld(11, R._enc_value_info("input", [1, 4]))
+    net, shape = R.parse_onnx(R._ld(7, graph))
+    assert shape == (4,) and net.dims.tolist() == [4, 5, 3]
+    x = g.standard_normal((6, 4)).astype(np.float32)
+    want = np.maximum(((x.astype(np.float64) - mean) / std) @ w1.astype(np.float64).T + b1, 0) @ w2.astype(np.float64).T
+    assert np.allclose(W.forward(net, x), want, rtol=1e-5, atol=1e-6)
+    # a normalisation in front of a convolution is declined, not mis-folded
+    conv = [R._enc_node("Sub", ["input", "m"], ["c"]), R._enc_node("Conv", ["c", "K"], ["y"])]
+    gr = b"".join(R._ld(1, n) for n in conv) + R._ld(5, R._enc_tensor("m", np.zeros(1, np.float32)))
+    gr += R._ld(5, R._enc_tensor("K", np.ones((1, 1, 1, 1), np.float32))) + R._ld(11, R._enc_value_info("input", [1, 1, 2, 2]))
+    with pytest.raises(EngineError) as ei:
+        R.parse_onnx(R._ld(7, gr))
+    assert ei.value.code == 1
