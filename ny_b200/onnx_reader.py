@@ -1,5 +1,6 @@
 """A minimal ONNX reader for feed-forward ReLU networks: Gemm / MatMul+Add / Conv / Relu / Flatten / Reshape, constant
-Transpose of weights, and Sub / Div / Mul input normalisation folded into the first dense layer.
+Transpose of weights, Sub / Div / Mul input normalisation folded into the first dense layer, and residual Add of an
+earlier post-activation tensor (an identity skip around two or more layers).
 
 The reference loads ONNX through its own protobuf parser (crates/ny-onnx/src/onnx); here the protobuf wire format
 is decoded directly with the field numbers of the public onnx.proto3 schema (ModelProto.graph = 7; GraphProto
@@ -217,13 +218,16 @@ def parse_onnx(data: bytes):
         return inits[name]
 
     pre_scale, pre_shift = None, None      # input normalisation (x - shift) * scale in front of the first layer
+    post_of = {}                           # tensor name -> index of the layer whose post-activation output it is
+    skips = {}                             # layer k -> layer j: relu(pre_j) joins layer k's output before its Relu
     for op, ins, outs, attrs in nodes:
         if op == "Constant" or (op == "Transpose" and ins and ins[0] in inits):
             continue
         if cur not in ins:
             raise EngineError(_UNSUPPORTED, f"onnx: node {op} is off the single data path")
         if op in ("Identity", "Dropout"):
-            pass
+            if cur in post_of:
+                post_of[outs[0]] = post_of[cur]
         elif op == "Flatten":
             shape = (flat(shape),)
         elif op == "Reshape":
@@ -236,6 +240,7 @@ def parse_onnx(data: bytes):
             if not layers or layers[-1][3]:
                 raise EngineError(_UNSUPPORTED, "onnx: Relu without a layer before it")
             layers[-1][3] = True
+            post_of[outs[0]] = len(layers) - 1
         elif op in ("Gemm", "MatMul"):
             if ins[0] != cur:
                 raise EngineError(_UNSUPPORTED, f"onnx: {op} with the data as right operand")
@@ -282,6 +287,13 @@ def parse_onnx(data: bytes):
             else:
                 sc = sc * c
             pre_scale, pre_shift = sc, sh
+        elif op == "Add" and (ins[1] if ins[0] == cur else ins[0]) in post_of:
+            # residual connection: the post-activation output of an earlier layer joins this layer's output before its
+            # Relu (an identity skip around at least two layers)
+            j, k = post_of[ins[1] if ins[0] == cur else ins[0]], len(layers) - 1
+            if not layers or layers[-1][3] or k in skips or j > k - 2:
+                raise EngineError(_UNSUPPORTED, "onnx: residual Add outside the supported form")
+            skips[k] = j
         elif op == "Add":
             other = ins[1] if ins[0] == cur else ins[0]
             c = np.asarray(need_const(other, "Add operand"), np.float32).reshape(-1)
@@ -321,7 +333,7 @@ def parse_onnx(data: bytes):
         layers.append(["linear", np.eye(flat(shape), dtype=np.float32), None, False])
     if not all(l[3] for l in layers[:-1]):
         raise EngineError(_UNSUPPORTED, "onnx: the network must be (affine, Relu)* affine")
-    return Network([l[1] for l in layers], [l[2] for l in layers]), in_shape
+    return Network([l[1] for l in layers], [l[2] for l in layers], skips or None), in_shape
 
 
 # ------------------------------------------------------------------------------------------- writer

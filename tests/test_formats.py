@@ -251,3 +251,40 @@ def test_onnx_input_normalisation_and_constant_transpose_are_folded():
     with pytest.raises(EngineError) as ei:
         R.parse_onnx(R._ld(7, gr))
     assert ei.value.code == 1
+
+
+def test_onnx_residual_add_becomes_an_identity_skip():
+    from ny_b200 import onnx_reader as R
+    from ny_b200 import workloads as W
+
+    g = np.random.Generator(np.random.PCG64(9))
+    ws = [g.standard_normal(s).astype(np.float32) * 0.5 for s in ((6, 4), (6, 6), (6, 6), (3, 6))]
+    bs = [g.standard_normal(w.shape[0]).astype(np.float32) for w in ws]
+    # x -> L0 -> relu (a0) -> L1 -> relu -> L2 -> + a0 -> relu -> L3
+    nodes = [R._enc_node("Gemm", ["input", "W0", "B0"], ["z0"], [R._enc_attr_int("transB", 1)]), R._enc_node("Relu", ["z0"], ["a0"]),
+             R._enc_node("Gemm", ["a0", "W1", "B1"], ["z1"], [R._enc_attr_int("transB", 1)]), R._enc_node("Relu", ["z1"], ["a1"]),
+             R._enc_node("Gemm", ["a1", "W2", "B2"], ["z2"], [R._enc_attr_int("transB", 1)]), R._enc_node("Add", ["z2", "a0"], ["s2"]),
+             R._enc_node("Relu", ["s2"], ["a2"]), R._enc_node("Gemm", ["a2", "W3", "B3"], ["y"], [R._enc_attr_int("transB", 1)])]
+    graph = b"".join(R._ld(1, n) for n in nodes)
+    for k, (w, b) in enumerate(zip(ws, bs)):
+        graph += R._ld(5, R._enc_tensor(f"W{k}", w)) + R._ld(5, R._enc_tensor(f"B{k}", b))
+    graph += R._ld(11, R._enc_value_info("input", [1, 4]))
+    net, _ = R.parse_onnx(R._ld(7, graph))
+    assert net.skips == {2: 0} and net.dims.tolist() == [4, 6, 6, 6, 3]
+    x = g.standard_normal((5, 4))
+    a0 = np.maximum(x @ ws[0].astype(np.float64).T + bs[0], 0)
+    a1 = np.maximum(a0 @ ws[1].astype(np.float64).T + bs[1], 0)
+    a2 = np.maximum(a1 @ ws[2].astype(np.float64).T + bs[2] + a0, 0)
+    want = a2 @ ws[3].astype(np.float64).T + bs[3]
+    assert np.allclose(W.forward(net, x.astype(np.float32)), want, rtol=1e-5, atol=1e-5)
+    # a skip around a single layer is outside what the engine's blocks express: declined
+    bad = [R._enc_node("Gemm", ["input", "W0", "B0"], ["z0"], [R._enc_attr_int("transB", 1)]), R._enc_node("Relu", ["z0"], ["a0"]),
+           R._enc_node("Gemm", ["a0", "W1", "B1"], ["z1"], [R._enc_attr_int("transB", 1)]), R._enc_node("Add", ["z1", "a0"], ["s1"]),
+           R._enc_node("Relu", ["s1"], ["a1"]), R._enc_node("Gemm", ["a1", "W3", "B3"], ["y"], [R._enc_attr_int("transB", 1)])]
+    gb = b"".join(R._ld(1, n) for n in bad)
+    for k in (0, 1, 3):
+        gb += R._ld(5, R._enc_tensor(f"W{k}", ws[k])) + R._ld(5, R._enc_tensor(f"B{k}", bs[k]))
+    gb += R._ld(11, R._enc_value_info("input", [1, 4]))
+    with pytest.raises(EngineError) as ei:
+        R.parse_onnx(R._ld(7, gb))
+    assert ei.value.code == 1
