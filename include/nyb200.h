@@ -335,6 +335,8 @@ int32_t nyb200_point_vjp_batched(nyb200_engine *e, int32_t net_id, int32_t K, co
  * output layout as nyb200_ibp_forward with D = 1, but in_lo/in_hi [dims[0]] and pre_lo/pre_hi
  * [sum_{k>=1} dims[k]] are DEVICE pointers owned by the caller, and the intermediate intervals live in
  * a fixed array inside the library image (about 128 KB per GPU, held from first use until exit).
+ *   - Linear layers without residual connections only: a network registered with a Conv2d layer or a
+ *     skip_from is refused with NYB200_ERR_UNSUPPORTED before anything is launched;
  *   - every layer width, the input included, must be <= 8192, otherwise NYB200_ERR_UNSUPPORTED;
  *   - all calls on a GPU share that array: calls that overlap on the device (other streams or engines)
  *     race and their results are undefined; calls on one stream are safe back to back;

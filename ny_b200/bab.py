@@ -41,7 +41,11 @@ def _rows(prop: Property):
     for ci, clause in enumerate(prop.violation):
         for atom in clause:
             spec.append(-np.asarray(atom.c, np.float32))
-            thr.append(np.float32(atom.d))
+            # the clause is refuted when lower > d in real arithmetic: the fp32 threshold may only round upwards
+            t32 = np.float32(atom.d)
+            if float(t32) < float(atom.d):
+                t32 = np.nextafter(t32, np.float32(np.inf))
+            thr.append(t32)
             owner.append(ci)
     return np.stack(spec).astype(np.float32), np.array(thr, np.float32), np.array(owner, np.int32)
 
@@ -465,8 +469,13 @@ def verify_root(eng, net_id, net, prop: Property, method: str = "crown") -> Veri
         n_out = int(net.dims[-1])
         ylo, yhi = pl[0][-n_out:].astype(np.float64), pu[0][-n_out:].astype(np.float64)
         s64 = spec.astype(np.float64)
-        low = (np.maximum(s64, 0) * ylo[None] + np.minimum(s64, 0) * yhi[None]).sum(axis=1)
-        lower = np.nextafter(low.astype(np.float32), np.float32(-np.inf))[None]   # binary64 sum, cast, one ulp down
+        terms = np.maximum(s64, 0) * ylo[None] + np.minimum(s64, 0) * yhi[None]
+        # binary64 sum of exact products: its error is at most gamma_n * sum|terms|; remove it, then cast downwards
+        n = terms.shape[1]
+        gam = (n + 2) * 2.0 ** -53
+        low = terms.sum(axis=1) - gam * np.abs(terms).sum(axis=1)
+        l32 = low.astype(np.float32)
+        lower = np.where(l32.astype(np.float64) > low, np.nextafter(l32, np.float32(-np.inf)), l32).astype(np.float32)[None]
     elif method == "crown":
         lower, _, _, _ = eng.crown_bounds(net_id, spec, prop.in_lo, prop.in_hi)
     else:

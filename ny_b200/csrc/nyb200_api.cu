@@ -36,6 +36,17 @@ void *ws_get(nyb200_engine *e, const char *name, size_t bytes) {
     return p;
 }
 
+// Releases every device allocation a registered network owns (weights, biases, the operands built for the
+// tensor-core passes, the transposed weights of the adjoint pass).
+void free_net(Net &net) {
+    for (float *p : net.owned) cudaFree(p);
+    for (auto &u : net.umma) { cudaFree(u.wh); cudaFree(u.wl); }
+    for (auto &u : net.umma_fwd) { cudaFree(u.wh); cudaFree(u.wl); }
+    for (auto &u : net.umma_adj) { cudaFree(u.wh); cudaFree(u.wl); }
+    for (float *p : net.wt) cudaFree(p);
+    net.owned.clear(); net.umma.clear(); net.umma_fwd.clear(); net.umma_adj.clear(); net.wt.clear();
+}
+
 }  // namespace nyb
 
 
@@ -68,11 +79,7 @@ void nyb200_destroy(nyb200_engine *e) {
     cudaSetDevice(e->device);
     cudaStreamSynchronize(e->stream);
     for (auto &kv : e->ws) if (kv.second.p) cudaFree(kv.second.p);
-    for (auto &kv : e->nets) {
-        for (float *p : kv.second.owned) cudaFree(p);
-        for (auto &u : kv.second.umma) { cudaFree(u.wh); cudaFree(u.wl); }
-        for (auto &u : kv.second.umma_fwd) { cudaFree(u.wh); cudaFree(u.wl); }
-    }
+    for (auto &kv : e->nets) free_net(kv.second);
     for (int i = 0; i < 3; ++i) if (e->timing.ev[i]) cudaEventDestroy(e->timing.ev[i]);
     for (cudaEvent_t ev : e->timing.kev) cudaEventDestroy(ev);
     delete e;
@@ -165,6 +172,8 @@ static int create_net(nyb200_engine *e, int32_t n_layers, const nyb200_layer_des
     net.v.pre_off[n_layers] = off;
     net.v.n_pre = off;
     net.v.nps = (off + 3) & ~3;
+    // a failed upload releases what the earlier layers allocated
+    struct Guard { Net &n; bool armed = true; ~Guard() { if (armed) free_net(n); } } guard{net};
     size_t wo = 0, bo = 0;
     std::vector<float> expanded;
     for (int k = 0; k < n_layers; ++k) {
@@ -197,6 +206,7 @@ static int create_net(nyb200_engine *e, int32_t n_layers, const nyb200_layer_des
     }
     int id = e->next_net++;
     e->nets[id] = net;
+    guard.armed = false;
     *net_id = id;
     return NYB200_OK;
 }
@@ -231,11 +241,7 @@ int32_t nyb200_net_destroy(nyb200_engine *e, int32_t net_id) {
     if (it == e->nets.end()) return set_err(e, NYB200_ERR_INVALID, "unknown net id");
     cudaSetDevice(e->device);
     cudaStreamSynchronize(e->stream);
-    for (float *p : it->second.owned) cudaFree(p);
-    for (auto &u : it->second.umma) { cudaFree(u.wh); cudaFree(u.wl); }
-    for (auto &u : it->second.umma_fwd) { cudaFree(u.wh); cudaFree(u.wl); }
-    for (auto &u : it->second.umma_adj) { cudaFree(u.wh); cudaFree(u.wl); }
-    for (float *p : it->second.wt) cudaFree(p);
+    free_net(it->second);
     e->nets.erase(it);
     if (e->batch.net_id == net_id) e->batch = Batch();
     return NYB200_OK;
@@ -922,6 +928,27 @@ int32_t nyb200_ibp_forward(nyb200_engine *e, int32_t net_id, int32_t D, const fl
         NYB_CUDA(e, cudaMemsetAsync(derr, 0, 4, e->stream));
     }
     NYB_TRY(run_forward(e, *net, b, p, 2));
+    if (e->path == NYB200_PATH_TF32X3) {
+        // The tensor-core products widen every interval by their rounding slack.  A pipeline wait that expired
+        // leaves garbage rows (error word), and a box whose slack shows against an unstable neuron's width is
+        // flagged: in the first case the call fails, in the second the pass is repeated with binary64 products.
+        int herr = 0;
+        std::vector<int> flags((size_t)D);
+        int *derr = (int *)ws_get(e, "umma_err", 256);
+        if (!derr) return NYB200_ERR_OOM;
+        NYB_CUDA(e, cudaMemcpyAsync(&herr, derr, 4, cudaMemcpyDeviceToHost, e->stream));
+        NYB_CUDA(e, cudaMemcpyAsync(flags.data(), p.flags, (size_t)D * 4, cudaMemcpyDeviceToHost, e->stream));
+        NYB_CUDA(e, cudaStreamSynchronize(e->stream));
+        if (herr) return set_err(e, NYB200_ERR_INTERNAL, "tcgen05 pipeline wait expired (code " + std::to_string(herr) + ")");
+        bool loose = false;
+        for (int d = 0; d < D; ++d) loose = loose || (flags[d] & kFlagLooseFwd);
+        if (loose) {
+            e->path = NYB200_PATH_F64;
+            int st = run_forward(e, *net, b, p, 2);
+            e->path = NYB200_PATH_TF32X3;
+            NYB_TRY(st);
+        }
+    }
     size_t w = (size_t)nv.n_pre * 4, ws = (size_t)nv.nps * 4;
     NYB_CUDA(e, cudaMemcpy2DAsync(pre_lo, w, p.pre_lo, ws, w, (size_t)D, cudaMemcpyDeviceToHost, e->stream));
     NYB_CUDA(e, cudaMemcpy2DAsync(pre_hi, w, p.pre_hi, ws, w, (size_t)D, cudaMemcpyDeviceToHost, e->stream));

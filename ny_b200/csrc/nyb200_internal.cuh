@@ -185,6 +185,7 @@ struct BatchPtrs {
 };
 int batch_ptrs(nyb200_engine *e, const Net &net, const Batch &b, BatchPtrs &p);
 int find_net(nyb200_engine *e, int net_id, Net **out);
+void free_net(Net &net);
 // Interval forward pass for the resident batch.  fwd_mode: 0 clamp-only, 1 constrained, 2 plain IBP.
 int run_forward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int fwd_mode);
 // Backward pass + concretisation.  With ckpt != nullptr, ckpt[r] (row stride ld_ckpt) receives the

@@ -12,6 +12,8 @@
 // process exits, whether or not this entry point is ever called.
 //
 // Rules for callers (also stated at the declaration in include/nyb200.h):
+//   * Linear layers without residual connections only: a network with a Conv2d layer or a skip is refused
+//     (NYB200_ERR_UNSUPPORTED) before any launch;
 //   * layer widths (including the input width) above NYB200_NOALLOC_MAX_WIDTH are refused;
 //   * all calls on one GPU share the same scratch: two calls that overlap on the device (different
 //     streams or engines) race on it and both results are undefined; calls on one stream are ordered
@@ -100,7 +102,21 @@ extern "C" int32_t nyb200_ibp_forward_noalloc(nyb200_engine *e, int32_t net_id, 
     std::lock_guard<std::mutex> g(e->mu);
     auto it = e->nets.find(net_id);
     if (it == e->nets.end()) return nyb::set_err(e, NYB200_ERR_INVALID, "unknown net id");
-    const nyb::NetView &nv = it->second.v;
+    const nyb::Net &net = it->second;
+    const nyb::NetView &nv = net.v;
+    // The layer kernel below is a dense mat-vec over W[n_out x n_in]: a Conv2d layer stores only its
+    // [out_channels x in_channels*kh*kw] filter bank and a residual layer needs the skipped activation,
+    // so both are refused here, before anything is launched.
+    for (int k = 0; k < nv.L; ++k) {
+        if (net.is_conv(k))
+            return nyb::set_err(e, NYB200_ERR_UNSUPPORTED,
+                                "nyb200_ibp_forward_noalloc: layer " + std::to_string(k) +
+                                    " is a Conv2d layer; only Linear layers without skips are supported, use nyb200_ibp_forward");
+        if (net.skip_of(k) >= 0)
+            return nyb::set_err(e, NYB200_ERR_UNSUPPORTED,
+                                "nyb200_ibp_forward_noalloc: layer " + std::to_string(k) +
+                                    " takes a residual connection; only Linear layers without skips are supported, use nyb200_ibp_forward");
+    }
     for (int k = 0; k <= nv.L; ++k)
         if (nv.dims[k] > NYB200_NOALLOC_MAX_WIDTH)
             return nyb::set_err(e, NYB200_ERR_UNSUPPORTED,

@@ -383,7 +383,8 @@ class B200Engine:
 
     def ibp_forward_noalloc(self, net_id: int, dev_in_lo: int, dev_in_hi: int, dev_pre_lo: int, dev_pre_hi: int):
         """Single-box interval forward pass on caller-owned DEVICE buffers (raw addresses); the library
-        allocates nothing.  Widths above 8192 are refused; concurrent calls on one GPU race."""
+        allocates nothing.  Linear layers without skips only; widths above 8192 are refused; concurrent calls on
+        one GPU race."""
         self._check(self._L.nyb200_ibp_forward_noalloc(self._h, net_id, C.c_void_p(dev_in_lo), C.c_void_p(dev_in_hi),
                                                        C.c_void_p(dev_pre_lo), C.c_void_p(dev_pre_hi)))
 

@@ -161,11 +161,15 @@ def _term(t, n_in, n_out):
         raise EngineError(_INVALID, f"vnnlib: unknown term {t}") from None
 
 
-def _dnf(expr, n_in, n_out, box):
-    """Disjunctive normal form of an output expression; input atoms tighten `box` in place and drop out."""
+def _dnf(expr, n_in, n_out, box, under_or=False):
+    """Disjunctive normal form of an output expression; input atoms tighten `box` in place and drop out.
+    An input atom anywhere below an `or` would make the input set a union of boxes (the reference keeps one box
+    per disjunct, crates/ny-onnx/src/vnnlib/parser.rs:384,438); tightening the one shared box with it would
+    intersect the disjuncts' boxes and could certify a property that fails elsewhere in the union, so it is
+    declined."""
     op = expr[0]
     if op == "and":
-        parts = [_dnf(e, n_in, n_out, box) for e in expr[1:]]
+        parts = [_dnf(e, n_in, n_out, box, under_or) for e in expr[1:]]
         acc = [[]]
         for part in parts:
             if part is None:
@@ -175,9 +179,11 @@ def _dnf(expr, n_in, n_out, box):
     if op == "or":
         out = []
         for e in expr[1:]:
-            part = _dnf(e, n_in, n_out, box)
+            part = _dnf(e, n_in, n_out, box, True)
             if part is None:
                 raise EngineError(1, "vnnlib: input constraints inside a disjunction are outside the supported subset")
+            if any(len(c) == 0 for c in part):
+                raise EngineError(1, "vnnlib: a disjunct without output constraints is outside the supported subset")
             out.extend(part)
         return out
     if op in ("<=", ">="):
@@ -189,6 +195,8 @@ def _dnf(expr, n_in, n_out, box):
         # now: a >= b
         kinds = (a[0], b[0])
         if "x" in kinds:
+            if under_or:
+                raise EngineError(1, "vnnlib: input constraints inside a disjunction are outside the supported subset")
             if kinds == ("x", "const"):
                 box[0][a[1]] = max(box[0][a[1]], b[2])
             elif kinds == ("const", "x"):
@@ -226,6 +234,9 @@ def parse_vnnlib(text: str, n_in: int, n_out: int) -> Property:
     if np.any(box[0] > box[1]):
         raise EngineError(_INVALID, "vnnlib: empty input box")
     clauses = [c for c in clauses if c]
+    if not clauses:
+        # no output atom at all: the violation set would be the whole box, not the empty set
+        raise EngineError(1, "vnnlib: a property without output constraints is outside the supported subset")
     # the fp32 box must contain the stated one: round the ends outward
     lo32, hi32 = box[0].astype(np.float32), box[1].astype(np.float32)
     lo32 = np.where(lo32.astype(np.float64) > box[0], np.nextafter(lo32, np.float32(-np.inf)), lo32).astype(np.float32)

@@ -91,6 +91,39 @@ def test_vnnlib_rejections():
         formats.parse_vnnlib("(assert (>= X_0 0)", 1, 1)
 
 
+def test_vnnlib_union_of_boxes_and_empty_disjuncts_are_declined():
+    """Input atoms below an `or` describe a union of boxes (one box per disjunct in the reference's parser);
+    folding them into one box would intersect the disjuncts.  Declined, as is a disjunct or a whole property
+    without output atoms (its violation set would be everything, not nothing)."""
+    decl = "(declare-const X_0 Real)(declare-const Y_0 Real)"
+    union = decl + """(assert (or (and (>= X_0 0.0) (<= X_0 0.5) (>= Y_0 1.0))
+                                 (and (>= X_0 0.5) (<= X_0 1.0) (>= Y_0 2.0))))"""
+    with pytest.raises(EngineError) as ei:
+        formats.parse_vnnlib(union, 1, 1)
+    assert ei.value.code == 1
+    box = "(assert (>= X_0 0))(assert (<= X_0 1))"
+    with pytest.raises(EngineError) as ei:
+        formats.parse_vnnlib(decl + box + "(assert (or (and (<= X_0 1)) (>= Y_0 5)))", 1, 1)
+    assert ei.value.code == 1
+    with pytest.raises(EngineError) as ei:
+        formats.parse_vnnlib(decl + box + "(assert (or (and) (>= Y_0 5)))", 1, 1)
+    assert ei.value.code == 1
+    with pytest.raises(EngineError) as ei:
+        formats.parse_vnnlib(decl + box, 1, 1)                     # input box only: nothing to refute
+    assert ei.value.code == 1
+
+
+def test_threshold_of_a_clause_rounds_upwards():
+    from ny_b200 import bab
+
+    d = 0.1  # not representable: float32(0.1) > 0.1, float32(0.3) < 0.3 ...
+    for d in (0.1, 0.3, -0.7, 1.0, 1e-9):
+        prop = formats.Property(np.zeros(1, np.float32), np.ones(1, np.float32),
+                                [[formats.Atom(np.array([1.0], np.float32), d)]])
+        _, thr, _ = bab._rows(prop)
+        assert float(thr[0]) >= d and float(np.nextafter(thr[0], np.float32(-np.inf))) < d
+
+
 def test_input_split_scores_known_answers():
     """The smart-branching score of the input-split driver, on hand-computed cases."""
     from ny_b200 import bab

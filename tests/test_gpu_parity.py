@@ -87,6 +87,28 @@ def test_ibp_forward_matches_oracle(eng, oracle, cfg):
     eng.release_network(nid)
 
 
+def test_ibp_forward_many_boxes_matches_oracle(eng, oracle):
+    """96 different boxes in one call: on the default path this is the tensor-core interval pass (D >= 64).  Its
+    rounding slack widens every interval, so the device may sit outside the oracle's interval by that slack but
+    never inside it by more than the oracle's own outward ulps; a box whose slack shows is re-run in binary64."""
+    wl = W.config_mlp_bab(seed=9, hidden=128, depth=4, n_in=160)
+    onet, _, nid, rl, ru = _setup(eng, oracle, wl)
+    rng = np.random.default_rng(12)
+    D = 96
+    mid, rad = 0.5 * (wl.in_lo + wl.in_hi), 0.5 * (wl.in_hi - wl.in_lo)
+    shrink = rng.uniform(0.1, 1.0, size=(D, 1)).astype(np.float32)
+    shift = rng.uniform(-1, 1, size=(D, wl.in_lo.shape[0])).astype(np.float32) * (1 - shrink) * rad
+    lo = (mid + shift - shrink * rad).astype(np.float32)
+    hi = np.maximum((mid + shift + shrink * rad).astype(np.float32), lo)
+    pl, pu = eng.ibp_forward_gpu(nid, lo, hi)
+    for d in range(0, D, 7):
+        ol, ou = oracle.ibp_forward(onet, lo[d], hi[d])
+        tol = IBP_REL * np.maximum(np.abs(ol), np.abs(ou))
+        assert np.all(np.abs(pl[d] - ol) <= tol) and np.all(np.abs(pu[d] - ou) <= tol), d
+        assert np.all(pl[d] <= pu[d])
+    eng.release_network(nid)
+
+
 @pytest.mark.parametrize("mode", [0, 1])
 @pytest.mark.parametrize("cfg", ["small", "mid"])
 def test_bab_bound_batch_matches_oracle(eng, oracle, cfg, mode):

@@ -41,3 +41,32 @@ def test_noalloc_forward_matches_regular_entry_point_twice():
         eng.ibp_forward_noalloc(nid, x.data_ptr(), x.data_ptr(), o.data_ptr(), o.data_ptr())
     assert ei.value.code == 1 and "8192" in str(ei.value)
     eng.close()
+
+
+def test_noalloc_refuses_conv_and_skip_networks_before_any_launch():
+    """The allocation-free pass is a dense mat-vec per layer: a Conv2d layer (whose weights are a filter bank, not
+    a dense matrix) and a residual connection are refused with UnsupportedOp.  The refusal happens on the host,
+    so the launch counter does not move."""
+    import torch
+
+    from ny_b200 import B200Engine, EngineError, Network
+    from ny_b200.engine import Conv2d
+
+    eng = B200Engine(0, torch.cuda.current_stream().cuda_stream)
+    rng = np.random.default_rng(3)
+    conv = Conv2d(rng.standard_normal((4, 2, 3, 3)).astype(np.float32), None, stride=(1, 1), pad=(1, 1), in_hw=(6, 6))
+    cnn = Network([conv, rng.standard_normal((3, conv.out_features)).astype(np.float32)])
+    w = [rng.standard_normal((8, 5)).astype(np.float32), rng.standard_normal((8, 8)).astype(np.float32),
+         rng.standard_normal((8, 8)).astype(np.float32), rng.standard_normal((2, 8)).astype(np.float32)]
+    skipnet = Network(w, skips={2: 0})
+    for net, word in ((cnn, "Conv2d"), (skipnet, "residual")):
+        nid = eng.register_network(net)
+        x = torch.zeros(int(net.dims[0]), device="cuda")
+        o = torch.zeros(net.n_pre, device="cuda")
+        before = eng.launch_count()
+        with pytest.raises(EngineError) as ei:
+            eng.ibp_forward_noalloc(nid, x.data_ptr(), x.data_ptr(), o.data_ptr(), o.data_ptr())
+        assert ei.value.code == 1 and word in str(ei.value)
+        assert eng.launch_count() == before
+        eng.release_network(nid)
+    eng.close()
