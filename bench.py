@@ -185,6 +185,7 @@ def run_ours(args, rank, world, local_rank):
     from ny_b200 import engine as E
 
     eng.set_path(E.PATH_TF32X3 if args.path == "tf32x3" else E.PATH_F64)
+    eng._L.nyb200_set_fusion(eng._h, args.fusion)
     eng._path_name = args.path
     wl = W.config_mlp_bab()
     nid = eng.register_network(wl.net)
@@ -647,6 +648,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--path", default=os.environ.get("NYB200_PATH", "tf32x3"), choices=["f64", "tf32x3"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--fusion", type=int, default=1, help="0: one launch per layer; 1: fused backward chain (default); 2: fused, two epilogue warps per lane quarter")
     ap.add_argument("--workload", default="bab", choices=["bab", "alpha-crown", "cnn", "resnet", "pgd", "pgd-resnet", "bab-search"],
                     help="bab: the headline beta-CROWN batch (default); alpha-crown: the alpha optimisation case; "
                          "cnn: the convolutional case (both 1 GPU)")

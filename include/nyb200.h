@@ -61,6 +61,15 @@ int32_t nyb200_set_stream(nyb200_engine *e, void *cuda_stream);
 /* Select the contraction arithmetic (NYB200_PATH_*).  Default NYB200_PATH_TF32X3; NYB200_PATH_F64 is the
  * slower binary64 reference arithmetic on the same device. */
 int32_t nyb200_set_path(nyb200_engine *e, int32_t path);
+/* Layer fusion of the NYB200_PATH_TF32X3 backward pass.  On (default): where the network allows it (Linear layers
+ * without skips, hidden widths <= 256 and multiples of 4) the contractions of all hidden layers and their ReLU
+ * relaxations run as one kernel that keeps a tile of coefficient rows on the SM from the specification rows down to
+ * the first layer's input; only the first layer's (wide) contraction and the concretisation follow as separate
+ * launches.  Off: one contraction launch and one relaxation launch per layer.  Both compute the same quantities
+ * with the same per-coefficient arithmetic; they differ in the accumulation order of the tensor-core sums (and its
+ * certified rounding charge), i.e. by a few ulps of the coefficients.  No counterpart in the reference, whose
+ * engines launch per layer (crates/ny-cuda/src/sound_crown.rs:348-376). */
+int32_t nyb200_set_fusion(nyb200_engine *e, int32_t on);
 /* Adaptive precision of the NYB200_PATH_TF32X3 path.  Every rounding of that path is charged to the
  * bounds as a penalty; when, for some domain of a batch, that penalty exceeds `tol` times
  * max(|bound|, 1% of the domain's largest bound) -- which happens for narrow boxes, where a bound is much
@@ -161,6 +170,19 @@ int32_t nyb200_bab_bound_batch(nyb200_engine *e, int32_t net_id, const float *sp
 int32_t nyb200_crown_bounds(nyb200_engine *e, int32_t net_id, const float *spec, int32_t S, const float *in_lo,
                             const float *in_hi, int32_t box_stride, int32_t D, float *out_lo, float *out_hi,
                             float *inter_lo, float *inter_hi);
+/* Convention for the certified rounding error of nyb200_crown_bounds.
+ *   NYB200_ERRCH_IMMEDIATE (default): every rounding is discharged at the layer where it occurs, against the interval
+ *     of the variable the coefficient multiplies.  Sound and tighter than the reference on deep networks (by about
+ *     2e-3 of the bound at depth 6), hence NOT identical to it there.
+ *   NYB200_ERRCH_REFERENCE: the reference's own channel - a per-coefficient error matrix
+ *     err' = |cast| + gamma_K |A||W| + err |W| carried through every layer (LinearBounds::lower_a_err / upper_a_err,
+ *     crates/ny-propagate/src/bounds/linear.rs:320-347; layers/linear/crown_single.rs:2092-2103; ReLU carry
+ *     layers/common/crown_dense.rs:41-290) and discharged at the input box (bounds/concretize.rs:443-466), in
+ *     binary64 whatever nyb200_set_path says.  Returns the reference's CPU CROWN bounds to within 1e-4 relative.
+ *     Linear layers without residual connections only (NYB200_ERR_UNSUPPORTED otherwise). */
+#define NYB200_ERRCH_IMMEDIATE 0
+#define NYB200_ERRCH_REFERENCE 1
+int32_t nyb200_set_error_channel(nyb200_engine *e, int32_t mode);
 /* Input-level linear coefficients of the last nyb200_crown_bounds call (LinearBounds::lower_a / upper_a of the
  * reference's CROWN result, used by the input-split heuristic, beta_crown/engine/input_split.rs:111-260):
  * lower_a / upper_a [D x S x dims[0]], either may be NULL.  The rows stay on the device only until the next call

@@ -471,8 +471,13 @@ int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, float
     float *cur = p.A0, *nxt = p.A1;
     float *stash = nullptr;
     int stash_for = -1;
-    if (partial) launch_seed_identity(e, S, D, p.lda, cur);
-    else launch_seed(e, p.spec, S, nv.dims[L], D, p.lda, cur);
+    // Fused chain: seed, identity pass and the contractions L-1 .. 1 with their relaxations run as one kernel that
+    // keeps the rows on the SM; what is left for the loop below is Linear_0's (wide) contraction.
+    const bool fused = tensor && e->fuse_chain && !ckpt && chain_eligible(net, L) && (nv.nps % 4 == 0) && (p.lda % 4 == 0);
+    if (!fused) {
+        if (partial) launch_seed_identity(e, S, D, p.lda, cur);
+        else launch_seed(e, p.spec, S, nv.dims[L], D, p.lda, cur);
+    }
     // rounding rate of the contraction through layer `lin` (accumulation length dims[lin + 1]); convolutions
     // accumulate in binary64 on both paths
     auto eps_for = [&](int lin) {
@@ -484,9 +489,16 @@ int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, float
         return (double)(K + 2) * 1.1102230246251565e-16 * 1.000001;
     };
     auto q_ds = [&](int lin_k) { return (lin_k == 0 && shared_box) ? 0L : np; };
-    launch_relax(e, nv, -1, L - 1, M, R, S, cur, p.lda, p.tab, p.zabs, p.q, q_ds(L - 1), eps_for(L - 1), p.rb,
+    int k_start = L - 1;
+    if (fused) {
+        if (e->timing.per_kernel) cudaEventRecord(next_kev(e->timing), e->stream);
+        NYB_TRY(launch_chain(e, net, b, p, L, partial, shared_box, cur, eps_for(0), derr));
+        if (e->timing.per_kernel) cudaEventRecord(next_kev(e->timing), e->stream);
+        k_start = 0;
+    } else
+        launch_relax(e, nv, -1, L - 1, M, R, S, cur, p.lda, p.tab, p.zabs, p.q, q_ds(L - 1), eps_for(L - 1), p.rb,
                      p.rabs, p.rpen, nullptr, 0);
-    for (int k = L - 1; k >= 0; --k) {
+    for (int k = k_start; k >= 0; --k) {
         NYB_DEADLINE(e, "backward pass");
         int K = nv.dims[k + 1], N = nv.dims[k];
         const float *zin_lo, *zin_hi;
@@ -922,37 +934,27 @@ int32_t nyb200_ibp_forward(nyb200_engine *e, int32_t net_id, int32_t D, const fl
     NYB_CUDA(e, cudaMemcpyAsync(p.in_lo, in_lo, box * 4, cudaMemcpyHostToDevice, e->stream));
     NYB_CUDA(e, cudaMemcpyAsync(p.in_hi, in_hi, box * 4, cudaMemcpyHostToDevice, e->stream));
     e->batch = Batch();  // the resident batch's buffers are being reused
-    if (e->path == NYB200_PATH_TF32X3) {
-        int *derr = (int *)ws_get(e, "umma_err", 256);
-        if (!derr) return NYB200_ERR_OOM;
-        NYB_CUDA(e, cudaMemsetAsync(derr, 0, 4, e->stream));
-    }
-    NYB_TRY(run_forward(e, *net, b, p, 2));
-    if (e->path == NYB200_PATH_TF32X3) {
-        // The tensor-core products widen every interval by their rounding slack.  A pipeline wait that expired
-        // leaves garbage rows (error word), and a box whose slack shows against an unstable neuron's width is
-        // flagged: in the first case the call fails, in the second the pass is repeated with binary64 products.
-        int herr = 0;
-        std::vector<int> flags((size_t)D);
-        int *derr = (int *)ws_get(e, "umma_err", 256);
-        if (!derr) return NYB200_ERR_OOM;
-        NYB_CUDA(e, cudaMemcpyAsync(&herr, derr, 4, cudaMemcpyDeviceToHost, e->stream));
-        NYB_CUDA(e, cudaMemcpyAsync(flags.data(), p.flags, (size_t)D * 4, cudaMemcpyDeviceToHost, e->stream));
-        NYB_CUDA(e, cudaStreamSynchronize(e->stream));
-        if (herr) return set_err(e, NYB200_ERR_INTERNAL, "tcgen05 pipeline wait expired (code " + std::to_string(herr) + ")");
-        bool loose = false;
-        for (int d = 0; d < D; ++d) loose = loose || (flags[d] & kFlagLooseFwd);
-        if (loose) {
-            e->path = NYB200_PATH_F64;
-            int st = run_forward(e, *net, b, p, 2);
-            e->path = NYB200_PATH_TF32X3;
-            NYB_TRY(st);
-        }
-    }
+    // This entry point returns the interval bounds themselves, so it always uses the binary64 interval products:
+    // the tensor-core products widen every interval by their rounding slack, which compounds with depth to a few
+    // 1e-5 of the bound - accounted for inside the batch calls (flags + binary64 re-evaluation of the bounds that
+    // show it), but visible to a caller who compares these numbers with the CPU path's.
+    const int saved_path = e->path;
+    e->path = NYB200_PATH_F64;
+    int fst = run_forward(e, *net, b, p, 2);
+    e->path = saved_path;
+    NYB_TRY(fst);
     size_t w = (size_t)nv.n_pre * 4, ws = (size_t)nv.nps * 4;
     NYB_CUDA(e, cudaMemcpy2DAsync(pre_lo, w, p.pre_lo, ws, w, (size_t)D, cudaMemcpyDeviceToHost, e->stream));
     NYB_CUDA(e, cudaMemcpy2DAsync(pre_hi, w, p.pre_hi, ws, w, (size_t)D, cudaMemcpyDeviceToHost, e->stream));
     NYB_CUDA(e, cudaStreamSynchronize(e->stream));
+    return NYB200_OK;
+}
+
+int32_t nyb200_set_fusion(nyb200_engine *e, int32_t on) {
+    if (!e) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    e->fuse_chain = on != 0;
+    e->fuse_variant = on == 2 ? 2 : 4;
     return NYB200_OK;
 }
 

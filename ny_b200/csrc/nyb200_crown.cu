@@ -257,7 +257,8 @@ static int crown_bounds_once(nyb200_engine *e, int net_id, const float *spec, in
             bk.S = n; bk.R = 2 * n;
             BatchPtrs pk;
             NYB_TRY(batch_ptrs(e, *net, bk, pk));
-            NYB_TRY(run_backward(e, *net, bk, pk, nullptr, 0, k));
+            if (e->error_channel == NYB200_ERRCH_REFERENCE) NYB_TRY(run_backward_ref(e, *net, bk, pk, k));
+            else NYB_TRY(run_backward(e, *net, bk, pk, nullptr, 0, k));
             k_accumulate_loose<<<1, 32, 0, st>>>(pk.min_lower, loose_acc);
             e->launches++;
             c_lo = pk.out_lo; c_hi = pk.out_hi;
@@ -280,7 +281,8 @@ static int crown_bounds_once(nyb200_engine *e, int net_id, const float *spec, in
     bs.S = S; bs.R = 2 * S;
     BatchPtrs ps;
     NYB_TRY(batch_ptrs(e, *net, bs, ps));
-    NYB_TRY(run_backward(e, *net, bs, ps, nullptr, 0, -1));
+    if (e->error_channel == NYB200_ERRCH_REFERENCE) NYB_TRY(run_backward_ref(e, *net, bs, ps, -1));
+    else NYB_TRY(run_backward(e, *net, bs, ps, nullptr, 0, -1));
     k_accumulate_loose<<<1, 32, 0, st>>>(ps.min_lower, loose_acc);
     e->launches++;
     k_crown_final<<<(unsigned)((D + 255) / 256), 256, 0, st>>>(D, S, sp_ibp_lo, sp_ibp_hi, sp_f_lo, sp_f_hi, ps.out_lo, ps.out_hi,
@@ -328,6 +330,15 @@ int crown_input_coeffs(nyb200_engine *e, float *lower_a, float *upper_a) {
 // like the batch entry points do.
 int crown_bounds(nyb200_engine *e, int net_id, const float *spec, int S, const float *in_lo, const float *in_hi,
                  int box_stride, int D, float *out_lo, float *out_hi, float *inter_lo, float *inter_hi) {
+    if (e->error_channel == NYB200_ERRCH_REFERENCE) {
+        // the reference's convention is a binary64 computation throughout (interval products included)
+        const int saved = e->path;
+        e->path = NYB200_PATH_F64;
+        int loose_unused = 0;
+        int st = crown_bounds_once(e, net_id, spec, S, in_lo, in_hi, box_stride, D, out_lo, out_hi, inter_lo, inter_hi, &loose_unused);
+        e->path = saved;
+        return st;
+    }
     int loose = 0;
     NYB_TRY(crown_bounds_once(e, net_id, spec, S, in_lo, in_hi, box_stride, D, out_lo, out_hi, inter_lo, inter_hi, &loose));
     if (loose > 0 && e->path == NYB200_PATH_TF32X3 && e->refine_tol > 0.f) {

@@ -102,6 +102,9 @@ struct nyb200_engine {
     cudaStream_t stream = nullptr;
     int path = NYB200_PATH_TF32X3;
     float refine_tol = 5e-5f;  // see nyb200_set_refine_tolerance
+    int error_channel = NYB200_ERRCH_IMMEDIATE;  // see nyb200_set_error_channel
+    bool fuse_chain = true;                       // see nyb200_set_fusion
+    int fuse_variant = 4;                         // epilogue warps per tensor-memory lane quarter (2 or 4)
     std::string err;
     std::mutex mu;
     std::map<int, nyb::Net> nets;
@@ -156,6 +159,8 @@ void launch_gemm_f64(nyb200_engine *e, int M, int N, int K, const float *A, int 
 void launch_concretize(nyb200_engine *e, int M, int R, int S, int n0, const float *A, int lda, const float *in_lo,
                        const float *in_hi, long box_dstride, const double *rb, const double *rabs, const double *rpen,
                        int *flags, float *out_lo, float *out_hi, float *min_lower, float loose_tol);
+// Per (domain, spec row): domain flags and the repair rule applied to the bounds, global minimum folded.
+void launch_finalize(nyb200_engine *e, int D, int S, const int *flags, float *out_lo, float *out_hi, float *min_lower);
 void launch_verdicts(nyb200_engine *e, int D, int S, const float *out_lo, const float *out_hi, const int *flags,
                      float threshold, int *status);
 // dst row i = src row idx[i] (gather) or dst row idx[i] = src row i (scatter); rows of `row_words` 32-bit words.
@@ -192,7 +197,15 @@ int run_forward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int fw
 // coefficients entering ReLU r before its relaxation is applied.
 // top >= 0 starts the pass at Linear_top's output with identity rows (b.S = dims[top + 1]) instead of the spec.
 int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, float *const *ckpt, int ld_ckpt, int top = -1);
+// The same pass in the reference's error convention (per-coefficient error matrices carried to the input box,
+// binary64 arithmetic; nyb200_ref.cu).
+int run_backward_ref(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int top);
 int prepare_backward_operands(nyb200_engine *e, Net &net);
+// ---- fused backward chain (nyb200_chain.cu) ----
+bool chain_eligible(const Net &net, int L);
+double chain_eps(int K);
+int launch_chain(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int L, bool identity_seed, bool shared_box,
+                 float *A_out, double eps0, int *derr);
 int prepare_transposed(nyb200_engine *e, Net &net, bool tensor);
 int conv_forward_tensor(nyb200_engine *e, Net &net, int k, int rows, const float *Z, int ldz, float *out, int ldo, int *derr);
 void fold_timing(Timing &t);

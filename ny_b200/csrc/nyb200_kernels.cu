@@ -16,6 +16,7 @@
 // (as the reference's device path does with node_abs/frontier_abs,
 // crates/ny-core/src/gemm.rs:2939-2952) so that no |W| chain is ever formed.
 #include "nyb200_internal.cuh"
+#include "nyb200_relax.cuh"
 
 namespace nyb {
 
@@ -359,42 +360,7 @@ k_relax(int n, int off, int M, int R, int S, int n_pre, int identity, float *A, 
 template <bool UPPER, bool RELAX, bool BIAS>
 __device__ __forceinline__ float relax_one(float a, float4 t, float au, float za, float qv, float bk, float eps, double &sb,
                                            float &sa, float &sp) {
-    float nw = a;
-    if (RELAX) {
-        const bool pos = a > 0.f;
-        // lower rows: a > 0 takes the lower line (slope ls, no intercept), a < 0 the upper line (us, ui);
-        // upper rows mirror it (relu_backward.rs:105-153)
-        // au: the upper path's own lower slope (dual alpha, activations/relu/mod.rs:570-1128); equals t.x otherwise
-        const float slope = (pos != UPPER) ? (UPPER ? au : t.x) : t.y;
-        const float icp = ((pos == UPPER) && a != 0.f) ? t.z : 0.f;
-        // the reference's rounding: round to nearest, then one ulp outward (relu_backward.rs:105-153); an exact
-        // zero product (a == 0 or slope == 0) needs no step.  A directed product would be up to one ulp tighter,
-        // which is visible on bounds that cancel to almost nothing; staying on the reference's values is worth
-        // more here than that ulp.
-        const float prod = __fmul_rn(a, slope);
-        const unsigned pb = __float_as_uint(prod);
-        const int neg = (int)pb >> 31;  // 0 or -1: one ulp outward is +-1 on the bit pattern, mirrored for negatives
-        const float stepped = __uint_as_float(UPPER ? pb + 1u + 2u * (unsigned)neg : pb - 1u - 2u * (unsigned)neg);
-        // a product that underflowed to zero takes the directed product instead (the bit step would wrap); an
-        // overflowed one steps into a NaN pattern, which the concretisation turns into [-inf, +inf] for the row
-        nw = (prod == 0.f) ? (UPPER ? __fmul_ru(a, slope) : __fmul_rd(a, slope)) : stepped;
-        nw = (a == 0.f || slope == 0.f) ? 0.f : nw;
-        // The step above is outward in the coefficient.  That alone is sound where the variable it multiplies cannot
-        // be negative: a neuron that is active on the whole domain (table (1, 1, 0): pre-activation lower bound >= 0,
-        // by its interval or by a split).  Everywhere else the pre-activation may be negative and the gap between the
-        // exact product and the stepped one is charged against its magnitude.
-        const bool nonneg = (t.y == 1.f) && (t.z == 0.f);
-        sp = __fmaf_ru(nonneg ? 0.f : fabsf(fmaf(a, slope, -nw)), za, sp);
-        sb = fma((double)a, (double)icp, sb);
-        sa = __fmaf_ru(fabsf(a), fabsf(icp), sa);
-        nw = UPPER ? nw + t.w : nw - t.w;  // signed beta (zero for unsplit neurons), relu_backward.rs:156-175
-    }
-    if (BIAS) {
-        sb = fma((double)nw, (double)bk, sb);
-        sa = __fmaf_ru(fabsf(nw), fabsf(bk), sa);
-    }
-    sp = __fmaf_ru(__fmul_ru(eps, fabsf(nw)), qv, sp);
-    return nw;
+    return relax_coeff<RELAX, BIAS>(UPPER, a, t, au, za, qv, bk, eps, sb, sa, sp);
 }
 
 template <bool UPPER, bool RELAX, bool BIAS>
@@ -963,6 +929,11 @@ void launch_concretize(nyb200_engine *e, int M, int R, int S, int n0, const floa
                                                               (int *)min_lower + 4);
         NYB_COUNT(e);
     }
+    k_finalize<<<(D * S + 255) / 256, 256, 0, e->stream>>>(D, S, flags, out_lo, out_hi, min_lower);
+    NYB_COUNT(e);
+}
+
+void launch_finalize(nyb200_engine *e, int D, int S, const int *flags, float *out_lo, float *out_hi, float *min_lower) {
     k_finalize<<<(D * S + 255) / 256, 256, 0, e->stream>>>(D, S, flags, out_lo, out_hi, min_lower);
     NYB_COUNT(e);
 }

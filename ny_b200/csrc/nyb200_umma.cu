@@ -44,6 +44,7 @@
 #include <cstdlib>
 
 #include "nyb200_internal.cuh"
+#include "nyb200_tcgen05.cuh"
 
 namespace nyb {
 
@@ -74,96 +75,6 @@ static int chunk_stages_cfg(int K) {
     if (forced > 0) return forced;
     return (K + BK - 1) / BK >= 8 ? 2 : 1;
 }
-constexpr unsigned SPIN_LIMIT = 1u << 24;
-
-__device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(unsigned bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-// Bounded wait: returns false when the limit expires.
-__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
-    for (unsigned it = 0; it < SPIN_LIMIT; ++it) {
-        unsigned ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok)
-            : "r"(bar), "r"(parity)
-            : "memory");
-        if (ok) return true;
-        if (it > 1024) __nanosleep(64);
-    }
-    return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap *tm, int x, int y, unsigned bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(tm), "r"(x), "r"(y), "r"(bar)
-        : "memory");
-}
-
-// K-major, 128-byte swizzle shared-memory operand descriptor: start address >> 4 in bits [0,14),
-// leading byte offset (unused for this layout) = 1 in [16,30), stride byte offset = 1024 B (8 rows of
-// 128 B) >> 4 in [32,46), descriptor version 1 in [46,48), layout type 2 (128B swizzle) in [61,64).
-__device__ __forceinline__ unsigned long long make_desc(unsigned smem_addr) {
-    unsigned long long d = 0;
-    d |= (unsigned long long)((smem_addr & 0x3FFFF) >> 4);
-    d |= 1ull << 16;
-    d |= (unsigned long long)(1024 >> 4) << 32;
-    d |= 1ull << 46;
-    d |= 2ull << 61;
-    return d;
-}
-
-// Instruction descriptor: D fp32 (bits [4,6) = 1), A and B TF32 (format 2 at [7,10) and [10,13)),
-// both K-major, N >> 3 at [17,23), M >> 4 at [24,29).
-__device__ __forceinline__ unsigned make_idesc(int m, int n) {
-    return (1u << 4) | (2u << 7) | (2u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(m >> 4) << 24);
-}
-
-__device__ __forceinline__ void mma_tf32(unsigned d_tmem, unsigned long long adesc, unsigned long long bdesc,
-                                         unsigned idesc, unsigned accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void mma_commit(unsigned bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-}
-
-// Round an fp32 value to the nearest TF32 value (10 explicit mantissa bits), ties away from zero.
-__device__ __forceinline__ float rn_tf32(float x) {
-    // Half an ulp of the 10-bit mantissa added to the magnitude bits, then the 13 low bits cleared: the value
-    // cvt.rna.tf32.f32 returns (a carry into the exponent is the correct rounding to the next binade or to
-    // infinity; infinities and NaNs keep their class), in two full-rate integer instructions instead of one
-    // conversion-pipe instruction.
-    return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u);
-}
-
 }  // namespace umma
 
 using namespace umma;

@@ -29,6 +29,7 @@ _NAMES = {
     DEADLINE: "DeadlineExceeded", OOM: "MemoryExceeded", INTERNAL: "InternalError",
 }
 PATH_F64, PATH_TF32X3 = 0, 1
+ERRCH_IMMEDIATE, ERRCH_REFERENCE = 0, 1
 
 EXPORTS = [
     "nyb200_create", "nyb200_destroy", "nyb200_backend_provenance", "nyb200_last_error", "nyb200_set_stream",
@@ -41,6 +42,7 @@ EXPORTS = [
     "nyb200_crown_bounds", "nyb200_batch_download_alpha_upper",
     "nyb200_batch_verdicts", "nyb200_gemm_f64", "nyb200_conv_transpose_2d", "nyb200_set_deadline_ns",
     "nyb200_batch_gradient", "nyb200_point_vjp_batched", "nyb200_crown_input_coeffs", "nyb200_batch_download_branch_scores",
+    "nyb200_set_error_channel", "nyb200_set_fusion",
 ]
 
 
@@ -83,6 +85,8 @@ def load_library():
     L.nyb200_last_error.restype = C.c_char_p
     L.nyb200_set_stream.argtypes = [vp, vp]
     L.nyb200_set_path.argtypes = [vp, C.c_int32]
+    L.nyb200_set_error_channel.argtypes = [vp, C.c_int32]
+    L.nyb200_set_fusion.argtypes = [vp, C.c_int32]
     L.nyb200_set_refine_tolerance.argtypes = [vp, C.c_float]
     L.nyb200_batch_refined.argtypes = [vp, ip]
     L.nyb200_launch_count.argtypes = [vp]
@@ -275,6 +279,16 @@ class B200Engine:
 
     def set_path(self, path: int):
         self._check(self._L.nyb200_set_path(self._h, path))
+
+    def set_error_channel(self, mode: int):
+        """ERRCH_IMMEDIATE (default: roundings discharged layer by layer, tighter than the reference on deep nets) or
+        ERRCH_REFERENCE (the reference's carried per-coefficient error matrices, binary64: plain-CROWN bounds equal to
+        the reference's CPU bounds within 1e-4)."""
+        self._check(self._L.nyb200_set_error_channel(self._h, mode))
+
+    def set_fusion(self, on: bool):
+        """Fused backward chain (default on) or one launch per layer."""
+        self._check(self._L.nyb200_set_fusion(self._h, 1 if on else 0))
 
     def set_refine_tolerance(self, tol: float):
         self._check(self._L.nyb200_set_refine_tolerance(self._h, tol))

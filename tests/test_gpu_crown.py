@@ -92,6 +92,44 @@ def test_crown_between_reference_and_exact_arithmetic(eng, oracle, cfg):
     eng.release_network(nid)
 
 
+@pytest.mark.parametrize("cfg", ["cpu_config", "mid", "deep8"])
+def test_crown_reference_error_channel_matches_the_reference_bound(eng, oracle, cfg):
+    """With the reference's own error convention selected (per-coefficient error matrices carried to the input box,
+    nyb200_set_error_channel(REFERENCE)), plain CROWN returns the reference's CPU bound: every output bound and
+    every tightened intermediate bound within 1e-4 relative (no floor other than 1e-6 of the vector's scale for
+    entries that are exactly or nearly zero), on the CPU-runnable configuration (5 -> 6x50 -> 5), a mid-size
+    network and an 8-layer one, where the default convention is 2e-3 tighter."""
+    from ny_b200 import engine as E
+
+    wl = {"cpu_config": lambda: W.config_mlp_small(),
+          "mid": lambda: W.config_mlp_bab(seed=51, hidden=64, depth=4, n_in=100, eps=0.01),
+          "deep8": lambda: W.config_mlp_bab(seed=53, hidden=48, depth=8, n_in=40, eps=0.005)}[cfg]()
+    onet = oracle.Net(wl.net.weights, wl.net.biases).with_spec(wl.spec)
+    nid = eng.register_network(wl.net)
+    eng.set_error_channel(E.ERRCH_REFERENCE)
+    try:
+        glo, ghi, gil, giu = eng.crown_bounds(nid, wl.spec, wl.in_lo, wl.in_hi)
+    finally:
+        eng.set_error_channel(E.ERRCH_IMMEDIATE)
+    olo, ohi, oil, oiu = oracle.crown(onet, wl.in_lo, wl.in_hi, want_intermediate=True)
+
+    def close(a, b):
+        a, b = np.asarray(a, np.float64), np.asarray(b, np.float64)
+        scale = np.abs(b[np.isfinite(b)]).max()
+        return np.all(np.abs(a - b) <= 1e-4 * np.maximum(np.abs(b), 1e-2 * scale))
+
+    assert close(glo[0], olo) and close(ghi[0], ohi)
+    n_pre = wl.net.n_pre
+    assert close(gil[0], oil[:n_pre]) and close(giu[0], oiu[:n_pre])
+    # and it is the looser of the two conventions
+    dlo, dhi, _, _ = eng.crown_bounds(nid, wl.spec, wl.in_lo, wl.in_hi)
+    scale = np.abs(olo).max()
+    assert np.all(dlo[0] >= glo[0] - 1e-6 * scale) and np.all(dhi[0] <= ghi[0] + 1e-6 * scale)
+    mn = W.sample_min_margin(wl, 100000, 78)
+    assert np.all(glo[0] <= mn)
+    eng.release_network(nid)
+
+
 def test_crown_batch_of_boxes(eng, oracle):
     wl = W.config_mlp_bab(seed=52, hidden=48, depth=3, n_in=32, eps=0.02)
     onet = oracle.Net(wl.net.weights, wl.net.biases).with_spec(wl.spec)
