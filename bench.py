@@ -49,6 +49,72 @@ def load_peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
+def measure_tf32_peak(device):
+    """Dense TF32 GEMM rate of this GPU, measured the way the bf16 figure of MEASURED_PEAKS.json was: torch.matmul
+    (a library GEMM is fine for a peak) on 8192^3 fp32 operands with TF32 allowed, best of 10 after warm-up."""
+    import torch
+
+    old = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    try:
+        n = 8192
+        a = torch.randn(n, n, device=device)
+        b = torch.randn(n, n, device=device)
+        for _ in range(3):
+            a @ b
+        torch.cuda.synchronize(device)
+        best = float("inf")
+        for _ in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            a @ b
+            e1.record()
+            torch.cuda.synchronize(device)
+            best = min(best, e0.elapsed_time(e1))
+        del a, b
+        torch.cuda.empty_cache()
+        return 2.0 * n ** 3 / (best / 1e3) / 1e12
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = old
+
+
+def committed_traffic(kernel: str, domains: int):
+    """DRAM bytes per launch of `kernel` at `domains` domains from the committed ncu captures (profiles/traffic.json:
+    dram__bytes_read.sum + dram__bytes_write.sum of one launch at the listed batch sizes), or None when no capture at
+    this size is on record."""
+    p = os.path.join(ROOT, "profiles", "traffic.json")
+    if not os.path.exists(p):
+        return None
+    rec = json.load(open(p)).get(kernel, {})
+    v = rec.get(str(domains))
+    return None if v is None else float(v)
+
+
+def oracle_parity(eng, nid, wl, rl, ru, splits, ns, lo, hi, inf, n=32):
+    """Outside the timed region: the device bounds of the first n domains against the CPU oracle, with the rule the
+    parity tests use (relative to max(|oracle bound|, floor * the domain's largest bound))."""
+    from oracle import ny_oracle as O
+
+    onet = O.Net(wl.net.weights, wl.net.biases).with_spec(wl.spec)
+    S = wl.spec.shape[0]
+    rl2 = np.concatenate([rl, np.full(S, -np.inf, np.float32)])
+    ru2 = np.concatenate([ru, np.full(S, np.inf, np.float32)])
+    olo, ohi, oinf, _ = O.bab_bound_batch(onet, wl.in_lo, wl.in_hi, rl2, ru2, splits[:n], ns[:n], 1)
+    same_inf = bool(np.array_equal(oinf.astype(bool), inf[:n].astype(bool)))
+    f = ~oinf.astype(bool)
+    floor = 1e-2
+    dev = np.concatenate([lo[:n], hi[:n]], axis=1)[f].astype(np.float64)
+    ref = np.concatenate([olo, ohi], axis=1)[f].astype(np.float64)
+    den = np.maximum(np.abs(ref), floor * np.abs(ref).max(axis=1, keepdims=True))
+    rel = np.abs(dev - ref) / den
+    unfloored = np.abs(dev - ref) / np.maximum(np.abs(ref), 1e-30)
+    verdict_same = bool(np.array_equal((lo[:n][f] > 0).all(axis=1), (olo[f] > 0).all(axis=1)))
+    return {"max_rel": float(rel.max()), "max_rel_unfloored": float(unfloored.max()), "n_domains_checked": int(f.sum()),
+            "tolerance": 1e-4, "floor": "denominator max(|oracle bound|, 1e-2 * the domain's largest |bound|)",
+            "infeasible_flags_identical": same_inf, "verdicts_at_threshold_0_identical": verdict_same,
+            "never_above_oracle_lower_by_more_than_1e-6_scale": bool(np.all(lo[:n][f] <= olo[f] + 1e-6 * np.abs(ref).max(axis=1, keepdims=True)))}
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
 
@@ -135,7 +201,7 @@ def run_reference(args, rank, world):
     wl = W.config_mlp_bab()
     onet = O.Net(wl.net.weights, wl.net.biases)
     rl, ru = O.ibp_forward(onet, wl.in_lo, wl.in_hi)
-    sample = int(os.environ.get("NYB200_REF_SAMPLE", "1024"))
+    sample = args.ref_sample
     for _ in range(min(args.warmup, 1)):
         cpu_baseline(wl, rl, ru, max(8, sample // 8))
     times = []
@@ -151,9 +217,11 @@ def run_reference(args, rank, world):
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f64", "data": "synthetic",
         "config": {"workload": "beta-CROWN bound of BaB domains, ReLU MLP 784->8x256->10, 9 spec rows, 8 splits/domain",
-                   "domains_per_step": sample, "note": "CPU restatement of the reference path; the Rust reference cannot be built here"},
+                   "domains_per_step": sample, "same_config": sample == D_PER_GPU,
+                   "note": "CPU restatement of the reference path (naive binary64 loops over a thread pool; the Rust reference "
+                           "with its faer SIMD GEMMs cannot be built here)"},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
-                         "sample": f"{sample} domains per step of the 4096-domain workload"},
+                         "sample": f"{sample} domains per step of the {D_PER_GPU}-domain workload"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -181,6 +249,9 @@ def run_ours(args, rank, world, local_rank):
         dist = dist_mod
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     stream = torch.cuda.current_stream()
+    tf32_peak = None
+    if rank == 0 and not args.no_peak:
+        tf32_peak = measure_tf32_peak(f"cuda:{local_rank}")   # roofline denominator; well before the timed region
     eng = B200Engine(local_rank, stream.cuda_stream)
     from ny_b200 import engine as E
 
@@ -224,18 +295,24 @@ def run_ours(args, rank, world, local_rank):
     eng.timing_enable(True)
     eng.timing_reset()
     l0 = eng.launch_count()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # The timed region is args.steps steps between two events; it is repeated back to back (`blocks` times, 30 by
+    # default) and the reported step time is the median block's, with the spread next to it: one block of 20 steps
+    # lasts well under 40 ms, too short for a single sample to be a stable number.
+    blocks = max(1, args.blocks)
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(blocks + 1)]
     barrier()
     t0 = time.perf_counter()
-    ev0.record(stream)
-    for _ in range(args.steps):
-        step()
-    ev1.record(stream)
+    evs[0].record(stream)
+    for b in range(blocks):
+        for _ in range(args.steps):
+            step()
+        evs[b + 1].record(stream)
     barrier()
     wall_ms = (time.perf_counter() - t0) * 1e3
-    dev_ms = ev0.elapsed_time(ev1)
-    launches = eng.launch_count() - l0
+    block_ms = np.array([evs[b].elapsed_time(evs[b + 1]) for b in range(blocks)])
+    launches = (eng.launch_count() - l0) // blocks
     gemm_ms, _ = eng.timing_read("gemm")
+    chain_ms, _ = eng.timing_read("chain")
     fwd_ms, _ = eng.timing_read("forward")
     bwd_ms, _ = eng.timing_read("backward")
     eng.timing_enable(False)
@@ -251,15 +328,16 @@ def run_ours(args, rank, world, local_rank):
 
     sp_p, _k1 = pinned(splits)
     ns_p, _k2 = pinned(ns)
-    e2e_steps = max(2, min(args.steps, 10))
+    e2e_calls = max(2, min(args.steps, 10)) * (3 if blocks > 1 else 1)
     for _ in range(2):
         eng.bab_bound_batch(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, sp_p, ns_p, mode=1)
     barrier()
-    t1 = time.perf_counter()
-    for _ in range(e2e_steps):
+    e2e_times = []
+    for _ in range(e2e_calls):
+        t1 = time.perf_counter()
         elo, ehi, einf = eng.bab_bound_batch(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, sp_p, ns_p, mode=1)
+        e2e_times.append((time.perf_counter() - t1) * 1e3)   # the call returns with the bounds on the host
     barrier()
-    e2e_ms = (time.perf_counter() - t1) * 1e3 / e2e_steps
 
     def busy():
         for _ in range(20):
@@ -271,53 +349,77 @@ def run_ours(args, rank, world, local_rank):
     h2d = splits.nbytes + ns.nbytes + wl.spec.nbytes + wl.in_lo.nbytes + wl.in_hi.nbytes + rl.nbytes + ru.nbytes
     d2h = lo.nbytes + hi.nbytes + inf.nbytes
 
-    ms_per_step = dev_ms / args.steps
+    per_step = block_ms / args.steps
+    if dist is not None:  # max over ranks, block by block
+        t = torch.tensor(per_step, device=f"cuda:{local_rank}", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        per_step = t.cpu().numpy()
+    ms_per_step = float(np.median(per_step))
+    e2e_ms = float(np.median(e2e_times))
     e2e_val = D / (e2e_ms / 1e3)
     if dist is not None:
-        t = torch.tensor([ms_per_step, e2e_ms, wall_ms / args.steps], device=f"cuda:{local_rank}", dtype=torch.float64)
+        t = torch.tensor([e2e_ms], device=f"cuda:{local_rank}", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_per_step, e2e_ms = float(t[0]), float(t[1])
+        e2e_ms = float(t[0])
         e2e_val = D * world / (e2e_ms / 1e3)
     value = D * world / (ms_per_step / 1e3)
 
     if rank == 0:
         peaks = load_peaks()
-        n_layers = len(wl.net.weights)
-        per_launch_s = (gemm_ms / 1e3) / n_layers if gemm_ms > 0 else None
-        flops_per_launch = FLOPS_PER_DOMAIN * D / n_layers
-        # fp32 operands fed to the tensor pipe as TF32: the dense TF32 rate is half the measured bf16 rate
-        peak_tf = peaks["bf16_tflops"] / 2.0
-        achieved = flops_per_launch / per_launch_s / 1e12 if per_launch_s else None
+        dims = [int(x) for x in wl.net.dims]
+        S2 = 2 * S
+        fused = chain_ms > 0
+        if eng_path_name(eng) == "f64":
+            kernel, k_ms, k_flops = "k_gemm_f64", gemm_ms, FLOPS_PER_DOMAIN * D
+        elif fused:
+            # the dominant kernel: the fused chain carries the contractions of every layer but the first (wide) one
+            kernel, k_ms = "k_chain", chain_ms
+            k_flops = 2.0 * S2 * (dims[-1] * dims[-2] + sum(dims[k] * dims[k + 1] for k in range(1, len(dims) - 2))) * D
+        else:
+            kernel, k_ms, k_flops = "k_umma_tf32x3", gemm_ms, FLOPS_PER_DOMAIN * D
+        achieved = k_flops / (k_ms / 1e3) / 1e12 if k_ms > 0 else None
+        if tf32_peak:
+            peak_tf, peak_src = tf32_peak, "measured tf32 (torch.matmul with TF32 allowed, 8192^3, best of 10, this run)"
+        else:
+            peak_tf, peak_src = peaks["bf16_tflops"] / 2.0, f"{peaks['source']} bf16 GEMM / 2 (TF32 not measured in this run)"
+        traffic = committed_traffic(kernel, D)
         roofline = {
             "bound": "tensor", "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
             "frac": (achieved / peak_tf) if achieved else None,
-            # dram__bytes_read.sum + dram__bytes_write.sum of one hidden-layer launch from the committed ncu capture of
-            # this kernel (20.7 MB at 1024 domains: the operand comes from DRAM, the result stays in L2), scaled to this
-            # launch by the number of domains
-            "traffic": 20.7e6 * D / 1024 if eng_path_name(eng) != "f64" else None,
-            "kernel": "k_gemm_f64" if eng_path_name(eng) == "f64" else "k_umma_tf32x3",
-            "peak_source": f"{peaks['source']} bf16 GEMM / 2 (TF32 operand rate)",
+            "frac_step": FLOPS_PER_DOMAIN * D / (ms_per_step / 1e3) / 1e12 / peak_tf,
+            "traffic": traffic,
+            "traffic_source": ("dram__bytes_read.sum + dram__bytes_write.sum of one launch at this batch size, committed ncu "
+                               "capture (profiles/traffic.json)") if traffic is not None else "no capture at this batch size on record",
+            "kernel": kernel, "kernel_ms": k_ms, "kernel_algorithmic_gflop": k_flops / 1e9,
+            "peak_source": peak_src,
             "hbm_view": {"achieved_gbs": BYTES_PER_DOMAIN * D / ((fwd_ms + bwd_ms) / 1e3) / 1e9 if (fwd_ms + bwd_ms) > 0 else None,
                          "peak_gbs": peaks["hbm_gbs"]},
-            "phase_ms": {"forward": fwd_ms, "backward": bwd_ms, "contraction": gemm_ms},
+            "phase_ms": {"forward": fwd_ms, "backward": bwd_ms, "fused_chain": chain_ms, "per_layer_contractions": gemm_ms},
         }
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "ms_per_step": ms_per_step,
+            "ms_per_step_spread": {"blocks": int(blocks), "min": float(per_step.min()), "p10": float(np.percentile(per_step, 10)),
+                                   "median": ms_per_step, "p90": float(np.percentile(per_step, 90)), "max": float(per_step.max())},
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f64" if eng_path_name(eng) == "f64" else "tf32x3", "data": "synthetic",
             "config": {"workload": "beta-CROWN bound of BaB domains, ReLU MLP 784->8x256->10, 9 spec rows (both bound "
                                    "directions), 8 splits/domain, constrained forward re-propagation",
                        "domains_per_gpu": D, "global_batch": D * world, "parallelism": f"domain-sharded x{world}",
-                       "l2": "per-step working set (coefficient ping-pong buffers 2 x 231 MB) exceeds the 126 MB L2",
+                       "l2": "per-step working set (per-domain tables 200 MB, coefficient rows 2 x 231 MB) exceeds the 126 MB L2",
+                       "backward": "fused chain" if fused else "one launch per layer",
                        "feasible_domains": int((inf == 0).sum()),
                        "domains_sent_to_binary64_rerun": int(refined)},
             "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
-                    "ms_per_step": e2e_ms},
-            "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline,
-            "wall_ms_per_step": wall_ms / args.steps,
+                    "ms_per_step": e2e_ms, "calls": len(e2e_times),
+                    "ms_per_step_spread": {"min": float(np.min(e2e_times)), "max": float(np.max(e2e_times))}},
+            "gpu_launches": int(launches) * int(blocks), "gpu_launches_per_block": int(launches), "clocks": clocks, "roofline": roofline,
+            "wall_ms_per_step": wall_ms / (args.steps * blocks),
         }
+        if world == 1 and not args.no_parity:
+            line["parity"] = oracle_parity(eng, nid, wl, rl, ru, splits, ns, lo, hi, inf)
         if world == 1 and not args.no_cpu_baseline:
-            sample = int(os.environ.get("NYB200_CPU_SAMPLE", "4096"))
+            sample = args.cpu_sample
             v, threads = cpu_baseline(wl, rl, ru, sample)
             line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
                                     "sample": f"{sample} domains of the same workload, one pass, all host threads"}
@@ -648,6 +750,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--path", default=os.environ.get("NYB200_PATH", "tf32x3"), choices=["f64", "tf32x3"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-parity", action="store_true", help="skip the 32-domain oracle comparison after the timed region")
+    ap.add_argument("--no-peak", action="store_true", help="skip the TF32 GEMM peak measurement (profiling runs)")
+    ap.add_argument("--blocks", type=int, default=30, help="back-to-back repetitions of the timed --steps block")
+    ap.add_argument("--ref-sample", type=int, default=D_PER_GPU, help="domains per step of the reference arm")
+    ap.add_argument("--cpu-sample", type=int, default=D_PER_GPU, help="domains of the cpu_baseline leg")
     ap.add_argument("--fusion", type=int, default=1, help="0: one launch per layer; 1: fused backward chain (default); 2: fused, two epilogue warps per lane quarter")
     ap.add_argument("--workload", default="bab", choices=["bab", "alpha-crown", "cnn", "resnet", "pgd", "pgd-resnet", "bab-search"],
                     help="bab: the headline beta-CROWN batch (default); alpha-crown: the alpha optimisation case; "

@@ -369,9 +369,10 @@ int32_t nyb200_ibp_forward_noalloc(nyb200_engine *e, int32_t net_id, const float
 
 /* Kernel-only timing of the last nyb200_batch_run calls: average milliseconds per run of the
  * named phase ("forward", "backward", "total") measured with CUDA events on the engine stream
- * since the last reset.  With nyb200_timing_enable(e, 1) every launch of the A*W contraction kernel
+ * since the last reset.  With nyb200_timing_enable(e, 1) every per-layer launch of the A*W contraction kernel
  * is additionally bracketed by its own event pair and reported as phase "gemm" (average milliseconds
- * per run, summed over that run's launches; n_runs counts runs). */
+ * per run, summed over that run's launches; n_runs counts runs), and the fused backward chain launch of a run as
+ * phase "chain". */
 int32_t nyb200_timing_enable(nyb200_engine *e, int32_t per_kernel);
 int32_t nyb200_timing_reset(nyb200_engine *e);
 int32_t nyb200_timing_read(nyb200_engine *e, const char *phase, double *avg_ms, int32_t *n_runs);

@@ -82,6 +82,7 @@ void nyb200_destroy(nyb200_engine *e) {
     for (auto &kv : e->nets) free_net(kv.second);
     for (int i = 0; i < 3; ++i) if (e->timing.ev[i]) cudaEventDestroy(e->timing.ev[i]);
     for (cudaEvent_t ev : e->timing.kev) cudaEventDestroy(ev);
+    for (int i = 0; i < 2; ++i) if (e->timing.cev[i]) cudaEventDestroy(e->timing.cev[i]);
     delete e;
 }
 
@@ -299,8 +300,13 @@ void fold_timing(nyb::Timing &t) {
             float g = 0;
             if (cudaEventElapsedTime(&g, t.kev[i], t.kev[i + 1]) == cudaSuccess) t.gemm_ms += g;
         }
+        if (t.cev_used) {
+            float g = 0;
+            if (cudaEventElapsedTime(&g, t.cev[0], t.cev[1]) == cudaSuccess) t.chain_ms += g;
+        }
     }
     t.kev_used = 0;
+    t.cev_used = false;
     t.pending = false;
 }
 
@@ -491,9 +497,13 @@ int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, float
     auto q_ds = [&](int lin_k) { return (lin_k == 0 && shared_box) ? 0L : np; };
     int k_start = L - 1;
     if (fused) {
-        if (e->timing.per_kernel) cudaEventRecord(next_kev(e->timing), e->stream);
+        const bool timed = e->timing.per_kernel && !e->timing.cev_used;
+        if (timed) {
+            for (int i = 0; i < 2; ++i) if (!e->timing.cev[i]) cudaEventCreate(&e->timing.cev[i]);
+            cudaEventRecord(e->timing.cev[0], e->stream);
+        }
         NYB_TRY(launch_chain(e, net, b, p, L, partial, shared_box, cur, eps_for(0), derr));
-        if (e->timing.per_kernel) cudaEventRecord(next_kev(e->timing), e->stream);
+        if (timed) { cudaEventRecord(e->timing.cev[1], e->stream); e->timing.cev_used = true; }
         k_start = 0;
     } else
         launch_relax(e, nv, -1, L - 1, M, R, S, cur, p.lda, p.tab, p.zabs, p.q, q_ds(L - 1), eps_for(L - 1), p.rb,
@@ -984,8 +994,8 @@ int32_t nyb200_timing_enable(nyb200_engine *e, int32_t per_kernel) {
 int32_t nyb200_timing_reset(nyb200_engine *e) {
     if (!e) return NYB200_ERR_INVALID;
     std::lock_guard<std::mutex> g(e->mu);
-    if (e->timing.pending) { cudaEventSynchronize(e->timing.ev[2]); e->timing.pending = false; e->timing.kev_used = 0; }
-    e->timing.fwd_ms = e->timing.bwd_ms = e->timing.tot_ms = e->timing.gemm_ms = 0;
+    if (e->timing.pending) { cudaEventSynchronize(e->timing.ev[2]); e->timing.pending = false; e->timing.kev_used = 0; e->timing.cev_used = false; }
+    e->timing.fwd_ms = e->timing.bwd_ms = e->timing.tot_ms = e->timing.gemm_ms = e->timing.chain_ms = 0;
     e->timing.runs = 0;
     return NYB200_OK;
 }
@@ -1000,6 +1010,7 @@ int32_t nyb200_timing_read(nyb200_engine *e, const char *phase, double *avg_ms, 
     else if (!strcmp(phase, "backward")) tot = t.bwd_ms;
     else if (!strcmp(phase, "total")) tot = t.tot_ms;
     else if (!strcmp(phase, "gemm")) tot = t.gemm_ms;
+    else if (!strcmp(phase, "chain")) tot = t.chain_ms;
     else return set_err(e, NYB200_ERR_INVALID, "unknown phase");
     *avg_ms = t.runs ? tot / t.runs : 0.0;
     if (n_runs) *n_runs = t.runs;

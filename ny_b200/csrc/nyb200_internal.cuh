@@ -87,12 +87,14 @@ struct Batch {
 
 struct Timing {
     cudaEvent_t ev[3] = {nullptr, nullptr, nullptr};  // start, after forward, end
-    double fwd_ms = 0, bwd_ms = 0, tot_ms = 0, gemm_ms = 0;
+    double fwd_ms = 0, bwd_ms = 0, tot_ms = 0, gemm_ms = 0, chain_ms = 0;
     int runs = 0;
     bool pending = false;
     bool per_kernel = false;
     std::vector<cudaEvent_t> kev;  // start/stop pairs around the contraction launches of the last run
     int kev_used = 0;
+    cudaEvent_t cev[2] = {nullptr, nullptr};  // around the fused chain launch of the last run
+    bool cev_used = false;
 };
 
 }  // namespace nyb

@@ -68,13 +68,9 @@ static_assert(4 * 32 * REGS_CONTROL + 8 * 32 * REGS_EPILOGUE + 4 * 32 * REGS_PRO
 // K stages (of 32) accumulated in one tensor-memory chain before the chunk is drained: two for contractions of
 // eight stages or more (K > 224), where halving the hand-offs to the epilogue pays (12% of the contraction time of
 // the 8 x 256 network), one for shorter ones, which hand over at most seven times per tile anyway and whose callers
-// (convolutions, narrow layers on small boxes) are the ones sensitive to the rounding rate.  NYB200_CHUNK_STAGES
-// overrides the choice for every launch; the rounding model follows the value in use.
-static int chunk_stages_cfg(int K) {
-    static int forced = [] { const char *s = getenv("NYB200_CHUNK_STAGES"); int x = s ? atoi(s) : 0; return x < 0 ? 0 : (x > 64 ? 64 : x); }();
-    if (forced > 0) return forced;
-    return (K + BK - 1) / BK >= 8 ? 2 : 1;
-}
+// (convolutions, narrow layers on small boxes) are the ones sensitive to the rounding rate.  The rounding model
+// follows the value in use.
+static int chunk_stages_cfg(int K) { return (K + BK - 1) / BK >= 8 ? 2 : 1; }
 }  // namespace umma
 
 using namespace umma;
@@ -468,8 +464,7 @@ int launch_umma(nyb200_engine *e, const UmmaLayer &L, int M, const float *A, int
     // stride multiples of 16 bytes.  Columns past K and rows past M read as zero, like the direct loads.
     alignas(64) CUtensorMap tm_a;
     int a_tma = 0;
-    static const bool staged = [] { const char *s = getenv("NYB200_A_DIRECT"); return !(s && atoi(s) != 0); }();
-    if (staged && a_plane == 0 && (reinterpret_cast<uintptr_t>(A) & 15) == 0 && (lda & 3) == 0 && lda >= L.K) {
+    if (a_plane == 0 && (reinterpret_cast<uintptr_t>(A) & 15) == 0 && (lda & 3) == 0 && lda >= L.K) {
         if (make_tmap(&tm_a, A, M, L.K, lda, BM)) return set_err(e, NYB200_ERR_INTERNAL, "cuTensorMapEncodeTiled failed for the A operand");
         a_tma = 1;
     } else {

@@ -311,18 +311,35 @@ static void concretize(const lbounds *b, const float *in_l, const float *in_u, f
 }
 
 /* ------------------------------------------------------------------ network access */
-typedef struct { const float *W; const float *b; int n_in, n_out; } lin_layer;
+typedef struct { const float *W; const float *b; int n_in, n_out; const int32_t *g; /* conv geometry or NULL */ } lin_layer;
+enum { G_IC, G_IH, G_IW, G_OC, G_OH, G_OW, G_KH, G_KW, G_SH, G_SW, G_PH, G_PW };
+static const int32_t *layer_geom(const nyo_net *net, int k) {
+    if (!net->conv_geom) return NULL;
+    const int32_t *g = net->conv_geom + 12 * (size_t)k;
+    return g[G_OC] > 0 ? g : NULL;
+}
+static int skip_of(const nyo_net *net, int k) { return net->skip_from ? net->skip_from[k] : -1; }
+static int net_has_skip(const nyo_net *net) {
+    for (int k = 0; k < net->n_linear; ++k) if (skip_of(net, k) >= 0) return 1;
+    return 0;
+}
+static int net_has_conv(const nyo_net *net) {
+    for (int k = 0; k < net->n_linear; ++k) if (layer_geom(net, k)) return 1;
+    return 0;
+}
 
 static lin_layer net_layer(const nyo_net *net, int k) {
     size_t wo = 0, bo = 0;
     for (int i = 0; i < k; ++i) {
-        wo += (size_t)net->dims[i] * net->dims[i + 1];
-        if (net->has_bias[i]) bo += (size_t)net->dims[i + 1];
+        const int32_t *g = layer_geom(net, i);
+        wo += g ? (size_t)g[G_OC] * g[G_IC] * g[G_KH] * g[G_KW] : (size_t)net->dims[i] * net->dims[i + 1];
+        if (net->has_bias[i]) bo += g ? (size_t)g[G_OC] : (size_t)net->dims[i + 1];
     }
     lin_layer l;
     l.W = net->wflat + wo;
     l.b = net->has_bias[k] ? net->bflat + bo : NULL;
     l.n_in = net->dims[k]; l.n_out = net->dims[k + 1];
+    l.g = layer_geom(net, k);
     return l;
 }
 static inline int relu_after(const nyo_net *net, int k) {
@@ -336,8 +353,45 @@ static size_t pre_offset(const nyo_net *net, int k) { /* offset of Linear_k's ou
 }
 
 /* ------------------------------------------------------------------ IBP */
+/* layers/convolution/conv2d/bound.rs:86-268 with ops_ibp_fwd.rs:131-395: the interval convolution
+ * lower = conv(l, W+) + conv(u, W-) + b, upper = conv(u, W+) + conv(l, W-) + b over the im2col taps
+ * (row = output position, column = (ic, ki, kj); taps outside the input contribute zero).  The reference runs
+ * the four products as fp32 GEMMs; here they are accumulated in binary64 and cast outward like the Linear
+ * layer's, which encloses the reference's values (they differ by fp32 summation noise, ~1e-7 relative). */
+static void conv_ibp(const lin_layer *L, const float *xl, const float *xu, float *yl, float *yu) {
+    const int32_t *g = L->g;
+    const int ic = g[G_IC], ih = g[G_IH], iw = g[G_IW], oc = g[G_OC], oh = g[G_OH], ow = g[G_OW];
+    const int kh = g[G_KH], kw = g[G_KW], sh = g[G_SH], sw = g[G_SW], ph = g[G_PH], pw = g[G_PW];
+    for (int co = 0; co < oc; ++co)
+        for (int oy = 0; oy < oh; ++oy)
+            for (int ox = 0; ox < ow; ++ox) {
+                double lo = 0.0, hi = 0.0;
+                for (int ci = 0; ci < ic; ++ci)
+                    for (int ky = 0; ky < kh; ++ky) {
+                        int iy = oy * sh + ky - ph;
+                        if (iy < 0 || iy >= ih) continue;
+                        for (int kx = 0; kx < kw; ++kx) {
+                            int ix = ox * sw + kx - pw;
+                            if (ix < 0 || ix >= iw) continue;
+                            float w = L->W[(((size_t)co * ic + ci) * kh + ky) * kw + kx];
+                            double wp = (double)fmaxf(w, 0.0f), wn = (double)fminf(w, 0.0f);
+                            if (isnan(w)) { wp = NAN; wn = NAN; }
+                            size_t i = ((size_t)ci * ih + iy) * iw + ix;
+                            lo += wp * (double)xl[i] + wn * (double)xu[i];
+                            hi += wp * (double)xu[i] + wn * (double)xl[i];
+                        }
+                    }
+                if (L->b) { lo += (double)L->b[co]; hi += (double)L->b[co]; }
+                float l = NDN32((float)lo), u = NUP32((float)hi);
+                if (isnan(l) || isnan(u) || l > u) { l = -INFINITY; u = INFINITY; }
+                size_t o = ((size_t)co * oh + oy) * ow + ox;
+                yl[o] = l; yu[o] = u;
+            }
+}
+
 /* layers/linear/ibp.rs:464-523: W+ l + W- u + b accumulated in binary64, cast outward. */
 static void linear_ibp(const lin_layer *L, const float *xl, const float *xu, float *yl, float *yu) {
+    if (L->g) { conv_ibp(L, xl, xu, yl, yu); return; }
     for (int o = 0; o < L->n_out; ++o) {
         const float *w = L->W + (size_t)o * L->n_in;
         double pl = 0.0, nu = 0.0, pu = 0.0, nl = 0.0;
@@ -369,6 +423,13 @@ int nyo_ibp_forward(const nyo_net *net, const float *in_lo, const float *in_hi, 
         lin_layer Lk = net_layer(net, k);
         size_t o = pre_offset(net, k);
         linear_ibp(&Lk, zl, zu, pre_lo + o, pre_hi + o);
+        if (skip_of(net, k) >= 0) {  /* identity branch: + relu(pre_j), whose interval is relu of the stored bounds */
+            size_t so = pre_offset(net, skip_of(net, k));
+            for (int j = 0; j < Lk.n_out; ++j) {
+                pre_lo[o + j] = f64_to_f32_down_ns((double)pre_lo[o + j] + (double)nanmax(pre_lo[so + j], 0.0f));
+                pre_hi[o + j] = f64_to_f32_up_ns((double)pre_hi[o + j] + (double)nanmax(pre_hi[so + j], 0.0f));
+            }
+        }
         int act = relu_after(net, k);
         for (int j = 0; j < Lk.n_out; ++j) {
             zl[j] = act ? nanmax(pre_lo[o + j], 0.0f) : pre_lo[o + j];
@@ -391,7 +452,8 @@ static double gamma_n_f64(size_t n) {
 static lbounds linear_backward(const lin_layer *L, const lbounds *in) {
     int rows = in->rows, K = L->n_out, N = L->n_in;
     lbounds out = lb_alloc(rows, N, 1);
-    double gamma = gamma_n_f64((size_t)K);
+    /* contraction length: out_features for a Linear layer, oc*kh*kw for a Conv2d (bound.rs:633) */
+    double gamma = gamma_n_f64(L->g ? (size_t)L->g[G_OC] * L->g[G_KH] * L->g[G_KW] : (size_t)K);
     double *a64 = (double *)malloc(sizeof(double) * (size_t)N);
     double *s64 = (double *)malloc(sizeof(double) * (size_t)N);
     double *p64 = (double *)malloc(sizeof(double) * (size_t)N);
@@ -403,6 +465,39 @@ static lbounds linear_backward(const lin_layer *L, const lbounds *in) {
         for (int i = 0; i < rows; ++i) {
             const float *a = A + (size_t)i * K;
             for (int j = 0; j < N; ++j) { a64[j] = 0.0; s64[j] = 0.0; p64[j] = 0.0; }
+            if (L->g) {
+                /* Conv2d: transposed convolution of the row (layers/convolution/conv2d/bound.rs:601-900,
+                 * conv2d_transpose_backward_coeff_f64, ops_transpose_gemm.rs): the coefficient of input element
+                 * (ci, iy, ix) collects a[(co, oy, ox)] * W[co, ci, ky, kx] over the taps with iy = oy*sh + ky - ph,
+                 * ix = ox*sw + kx - pw; binary64 accumulation with the magnitude sum, the incoming error through
+                 * |W| (bound.rs:860-1010). */
+                const int32_t *g = L->g;
+                const int ic = g[G_IC], ih = g[G_IH], iw = g[G_IW], oc = g[G_OC], oh = g[G_OH], ow = g[G_OW];
+                const int kh = g[G_KH], kw = g[G_KW], sh = g[G_SH], sw = g[G_SW], ph = g[G_PH], pw = g[G_PW];
+                const float *e = E ? E + (size_t)i * K : NULL;
+                for (int co = 0; co < oc; ++co)
+                    for (int oy = 0; oy < oh; ++oy)
+                        for (int ox = 0; ox < ow; ++ox) {
+                            size_t k = ((size_t)co * oh + oy) * ow + ox;
+                            double ak = (double)a[k], ek = e ? nonneg_err_or_inf(e[k]) : 0.0;
+                            if (ak == 0.0 && ek == 0.0) continue;
+                            double aak = fabs(ak);
+                            for (int ci = 0; ci < ic; ++ci)
+                                for (int ky = 0; ky < kh; ++ky) {
+                                    int iy = oy * sh + ky - ph;
+                                    if (iy < 0 || iy >= ih) continue;
+                                    for (int kx = 0; kx < kw; ++kx) {
+                                        int ix = ox * sw + kx - pw;
+                                        if (ix < 0 || ix >= iw) continue;
+                                        double w = (double)L->W[(((size_t)co * ic + ci) * kh + ky) * kw + kx];
+                                        size_t j = ((size_t)ci * ih + iy) * iw + ix;
+                                        if (isnan(ak)) a64[j] = NAN;
+                                        else if (ak != 0.0) { a64[j] += ak * w; s64[j] += aak * fabs(w); }
+                                        if (ek != 0.0 && w != 0.0) p64[j] = add_f64_up(p64[j], ek * fabs(w));
+                                    }
+                                }
+                        }
+            } else {
             /* aw_f64_with_abssum (:170): exact products, binary64 accumulation */
             for (int k = 0; k < K; ++k) {
                 double ak = (double)a[k];
@@ -427,6 +522,7 @@ static lbounds linear_backward(const lin_layer *L, const lbounds *in) {
                     }
                 }
             }
+            }
             int nonfinite = 0;
             for (int j = 0; j < N; ++j) {
                 float v = (float)a64[j];
@@ -440,15 +536,18 @@ static lbounds linear_backward(const lin_layer *L, const lbounds *in) {
             float bnew = Bin[i];
             if (L->b) {
                 double acc = 0.0;
+                /* a Conv2d bias is per channel: element k belongs to channel k / (oh*ow)
+                 * (compute_conv_bias_f64, layers/crown_helpers.rs:748-800) */
+                const int plane = L->g ? L->g[G_OH] * L->g[G_OW] : 1;
                 for (int k = 0; k < K; ++k) {
-                    double t = (double)a[k] * (double)L->b[k];
+                    double t = (double)a[k] * (double)L->b[k / plane];
                     acc = side ? add_f64_up(acc, t) : add_f64_down(acc, t);
                 }
                 if (E) {
                     const float *e = E + (size_t)i * K;
                     double ee = 0.0;
                     for (int k = 0; k < K; ++k) {
-                        double ba = fabs((double)L->b[k]);
+                        double ba = fabs((double)L->b[k / plane]);
                         if (ba == 0.0) continue;
                         ee = add_f64_up(ee, nonneg_err_or_inf(e[k]) * ba);
                     }
@@ -665,6 +764,7 @@ static int intersect_per_element(float *al, float *au, const float *bl, const fl
 
 int nyo_crown(const nyo_net *net, const float *in_lo, const float *in_hi, float *out_lo, float *out_hi,
               float *inter_lo, float *inter_hi) {
+    if (net_has_skip(net)) return -2;
     int L = net->n_linear;
     size_t total = pre_offset(net, L);
     float *ibp_l = (float *)malloc(4 * total), *ibp_u = (float *)malloc(4 * total);
@@ -779,10 +879,37 @@ int nyo_beta_crown_bound_dual(const nyo_net *net, const float *in_lo, const floa
                               const float *alpha_up, float *out_lo, float *out_hi) {
     int L = net->n_linear;
     lbounds cur = lb_identity(net->dims[L]);
+    lbounds stash; memset(&stash, 0, sizeof(stash));
+    int stash_for = -1;
     for (int k = L - 1; k >= 0; --k) {
         lin_layer Lk = net_layer(net, k);
+        if (skip_of(net, k) >= 0) {
+            /* residual block: the coefficients at pre_k also multiply relu(pre_j) directly; keep a copy until the pass
+             * reaches that variable (A_in = backward_F(A) + A, ny-core/src/gemm.rs:1640-1669) */
+            stash = lb_alloc(cur.rows, cur.n, cur.le != NULL);
+            memcpy(stash.la, cur.la, 4 * (size_t)cur.rows * cur.n); memcpy(stash.ua, cur.ua, 4 * (size_t)cur.rows * cur.n);
+            if (cur.le) { memcpy(stash.le, cur.le, 4 * (size_t)cur.rows * cur.n); memcpy(stash.ue, cur.ue, 4 * (size_t)cur.rows * cur.n); }
+            stash_for = skip_of(net, k);
+        }
         lbounds nxt = linear_backward(&Lk, &cur);
         lb_free(&cur); cur = nxt;
+        if (stash_for >= 0 && stash_for == k - 1) {
+            /* cur holds the coefficients of relu(pre_{k-1}): the identity branch joins.  The rounded sums carry their
+             * exact residual and both branches' certified errors in the error matrices (RESIDENT_SEG_MERGE). */
+            size_t cnt = (size_t)cur.rows * cur.n;
+            for (int side = 0; side < 2; ++side) {
+                float *A = side ? cur.ua : cur.la, *E = side ? cur.ue : cur.le;
+                const float *SA = side ? stash.ua : stash.la, *SE = side ? stash.ue : stash.le;
+                for (size_t i = 0; i < cnt; ++i) {
+                    double ex = (double)A[i] + (double)SA[i];
+                    float v = (float)ex;
+                    double e = fabs(ex - (double)v) + (E ? nonneg_err_or_inf(E[i]) : 0.0) + (SE ? nonneg_err_or_inf(SE[i]) : 0.0);
+                    A[i] = v;
+                    if (E) E[i] = (e == 0.0) ? 0.0f : publish_error_up_normal(e);
+                }
+            }
+            lb_free(&stash); stash_for = -1;
+        }
         if (k > 0 && relu_after(net, k - 1)) {
             int r = k - 1, n = net->dims[k];
             size_t o = pre_offset(net, r);
@@ -828,6 +955,8 @@ int nyo_domain_bounds(const nyo_net *net, const float *in_lo, const float *in_hi
     for (int k = 0; k <= L; ++k) if (net->dims[k] > maxn) maxn = net->dims[k];
     float *zl = (float *)malloc(4 * (size_t)maxn), *zu = (float *)malloc(4 * (size_t)maxn);
     float *nl = (float *)malloc(4 * (size_t)maxn), *nu = (float *)malloc(4 * (size_t)maxn);
+    /* post-activation intervals of every layer, kept for the identity branches of residual blocks */
+    float *post_l = net_has_skip(net) ? (float *)malloc(4 * total) : NULL, *post_u = post_l ? (float *)malloc(4 * total) : NULL;
     memcpy(zl, in_lo, 4 * (size_t)net->dims[0]); memcpy(zu, in_hi, 4 * (size_t)net->dims[0]);
     int infeasible = 0;
     for (int k = 0; k < L && !infeasible; ++k) {
@@ -835,6 +964,13 @@ int nyo_domain_bounds(const nyo_net *net, const float *in_lo, const float *in_hi
         size_t o = pre_offset(net, k);
         int n = Lk.n_out;
         linear_ibp(&Lk, zl, zu, nl, nu);
+        if (skip_of(net, k) >= 0) {  /* pre_k = W z + b + relu(pre_j): interval sum, rounded outward */
+            size_t so = pre_offset(net, skip_of(net, k));
+            for (int j = 0; j < n; ++j) {
+                nl[j] = f64_to_f32_down_ns((double)nl[j] + (double)post_l[so + j]);
+                nu[j] = f64_to_f32_up_ns((double)nu[j] + (double)post_u[so + j]);
+            }
+        }
         /* repropagated.intersection_per_element(current) (:738-741): self = re-propagated */
         if (intersect_per_element(nl, nu, pre_lo + o, pre_hi + o, n)) { memcpy(pre_lo + o, nl, 4 * (size_t)n); memcpy(pre_hi + o, nu, 4 * (size_t)n); }
         else { memcpy(pre_lo + o, nl, 4 * (size_t)n); memcpy(pre_hi + o, nu, 4 * (size_t)n); }
@@ -856,8 +992,9 @@ int nyo_domain_bounds(const nyo_net *net, const float *in_lo, const float *in_hi
             if (splits[s].sign > 0) { if (pre_hi[o + j] < 0.0f) infeasible = 1; zl[j] = nanmax(pre_lo[o + j], 0.0f); zu[j] = pre_hi[o + j]; }
             else { if (pre_lo[o + j] > 0.0f) infeasible = 1; zl[j] = 0.0f; zu[j] = 0.0f; }
         }
+        if (post_l) { memcpy(post_l + o, zl, 4 * (size_t)n); memcpy(post_u + o, zu, 4 * (size_t)n); }
     }
-    free(zl); free(zu); free(nl); free(nu);
+    free(zl); free(zu); free(nl); free(nu); free(post_l); free(post_u);
     return infeasible;
 }
 
@@ -990,6 +1127,7 @@ int nyo_joint_gradient(const nyo_net *net, const float *in_lo, const float *in_h
 int nyo_joint_gradient_rows(const nyo_net *net, const float *in_lo, const float *in_hi, const float *pre_lo,
                             const float *pre_hi, const nyo_split *splits, int n_splits, const float *alpha,
                             double *lower_out, float *grad_alpha, float *grad_beta, int only_row) {
+    if (net_has_conv(net) || net_has_skip(net)) return -2;
     int L = net->n_linear, S = net->dims[L];
     size_t total = pre_offset(net, L);
     /* per-ReLU records */
@@ -1106,6 +1244,7 @@ int nyo_joint_gradient_rows(const nyo_net *net, const float *in_lo, const float 
 int nyo_upper_gradient(const nyo_net *net, const float *in_lo, const float *in_hi, const float *pre_lo,
                        const float *pre_hi, const nyo_split *splits, int n_splits, const float *alpha,
                        const float *alpha_up, double *upper_out, float *grad_alpha_up) {
+    if (net_has_conv(net) || net_has_skip(net)) return -2;
     int L = net->n_linear, S = net->dims[L];
     size_t total = pre_offset(net, L);
     double **apre = (double **)calloc((size_t)L, sizeof(double *));

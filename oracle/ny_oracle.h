@@ -12,8 +12,10 @@
  *     x -> Linear_0 -> ReLU -> Linear_1 -> ReLU -> ... -> Linear_{L-1}
  * dims[0..L] are the widths; weights are row-major [dims[k+1] x dims[k]] concatenated in
  * `wflat`; biases are concatenated in `bflat` (has_bias[k]==0 means the layer has none and
- * contributes no entries to bflat).  Convolutions are handled by the caller lowering them
- * to their dense matrix (exact products summed in binary64 are unaffected by the zeros).
+ * contributes no entries to bflat).  A layer may instead be a Conv2d (see conv_geom): the interval
+ * pass and the backward pass then walk the kernel taps directly (im2col order of
+ * layers/convolution/conv2d/ops_ibp_fwd.rs and the transposed convolution of conv2d/bound.rs:601-900),
+ * which is the reference's algorithm rather than a dense lowering of it.
  */
 #ifndef NY_ORACLE_H
 #define NY_ORACLE_H
@@ -33,6 +35,19 @@ typedef struct {
     const int32_t *relu_after; /* L entries or NULL (= a ReLU after every Linear but the last);
                                   relu_after[k]==0 means Linear_k feeds Linear_{k+1} directly, which is
                                   how ny's CLI appends specification rows as a final Linear layer */
+    const int32_t *conv_geom;  /* NULL (all layers dense) or L blocks of 12 ints
+                                  (ic, ih, iw, oc, oh, ow, kh, kw, sh, sw, ph, pw); a block of zeros marks a
+                                  dense layer.  A Conv2d layer (NCHW flattened, dilation 1, one group) stores
+                                  its kernel [oc x ic*kh*kw] in wflat and a per-channel bias [oc] in bflat;
+                                  dims[k] = ic*ih*iw, dims[k+1] = oc*oh*ow.  Supported by the interval pass,
+                                  plain CROWN, the beta-CROWN bound and the batch entry points; the gradient
+                                  and optimisation entry points return -2 for such a network. */
+    const int32_t *skip_from;  /* NULL or L entries: skip_from[k] = j >= 0 adds the post-activation output of layer j
+                                  (j <= k - 2, same width) to layer k's output before its ReLU,
+                                  pre_k = W_k z + b_k + relu(pre_j): the identity branch of a residual block
+                                  (GpuResnetSegment::Residual, crates/ny-core/src/gemm.rs:1640-1669); -1 = none.
+                                  Supported by nyo_domain_bounds (mode 1), nyo_beta_crown_bound and the batch entry
+                                  point; the other entry points return -2 for such a network. */
 } nyo_net;
 
 /* A split constraint on ReLU `relu` (0-based, the ReLU that follows Linear_relu),

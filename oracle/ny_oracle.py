@@ -23,6 +23,8 @@ class _Net(C.Structure):
         ("bflat", C.POINTER(C.c_float)),
         ("has_bias", C.POINTER(C.c_int32)),
         ("relu_after", C.POINTER(C.c_int32)),
+        ("conv_geom", C.POINTER(C.c_int32)),
+        ("skip_from", C.POINTER(C.c_int32)),
     ]
 
 
@@ -90,20 +92,45 @@ def _ip(a):
 
 
 class Net:
-    """Sequential ReLU MLP: weights[k] is [out, in] (row-major), biases[k] is [out] or None."""
+    """Sequential ReLU network: weights[k] is a dense [out, in] matrix (row-major) or a Conv2d description (any
+    object with weight [oc, ic, kh, kw], sh, sw, ph, pw, ih, iw, oh, ow attributes, e.g. ny_b200.engine.Conv2d);
+    biases[k] is [out] ([oc] for a convolution) or None.  Convolutions are evaluated natively (kernel taps), not
+    through a dense lowering."""
 
-    def __init__(self, weights, biases=None, relu_after=None):
-        self.weights = [np.ascontiguousarray(w, dtype=np.float32) for w in weights]
-        L = len(self.weights)
+    def __init__(self, weights, biases=None, relu_after=None, skips=None):
+        """skips: optional {k: j}: the post-activation output of layer j joins layer k's output before its ReLU."""
+        L = len(weights)
+        self.skips = dict(skips or {})
+        self._skip = None
+        if self.skips:
+            self._skip = np.full(L, -1, np.int32)
+            for k, j in self.skips.items():
+                self._skip[k] = j
+        self.weights = [w if hasattr(w, "kh") else np.ascontiguousarray(w, dtype=np.float32) for w in weights]
         self.relu_after = None if relu_after is None else np.ascontiguousarray(relu_after, np.int32)
         biases = biases if biases is not None else [None] * L
+        biases = [(w.bias if hasattr(w, "kh") and b is None else b) for w, b in zip(self.weights, biases)]
         self.biases = [None if b is None else np.ascontiguousarray(b, dtype=np.float32) for b in biases]
-        self.dims = np.array([self.weights[0].shape[1]] + [w.shape[0] for w in self.weights], dtype=np.int32)
-        self._w = np.concatenate([w.ravel() for w in self.weights]).astype(np.float32)
+        dims, flat, geom = [], [], np.zeros((L, 12), np.int32)
+        for k, w in enumerate(self.weights):
+            if hasattr(w, "kh"):
+                if k == 0:
+                    dims.append(w.ic * w.ih * w.iw)
+                dims.append(w.oc * w.oh * w.ow)
+                geom[k] = (w.ic, w.ih, w.iw, w.oc, w.oh, w.ow, w.kh, w.kw, w.sh, w.sw, w.ph, w.pw)
+                flat.append(np.ascontiguousarray(w.weight, np.float32).ravel())
+            else:
+                if k == 0:
+                    dims.append(w.shape[1])
+                dims.append(w.shape[0])
+                flat.append(w.ravel())
+        self.dims = np.array(dims, dtype=np.int32)
+        self._w = np.concatenate(flat).astype(np.float32)
         bl = [b for b in self.biases if b is not None]
         self._b = np.concatenate(bl).astype(np.float32) if bl else np.zeros(1, np.float32)
         self._hb = np.array([0 if b is None else 1 for b in self.biases], dtype=np.int32)
-        self.c = _Net(L, _ip(self.dims), _fp(self._w), _fp(self._b), _ip(self._hb), _ip(self.relu_after))
+        self._geom = np.ascontiguousarray(geom) if geom.any() else None
+        self.c = _Net(L, _ip(self.dims), _fp(self._w), _fp(self._b), _ip(self._hb), _ip(self.relu_after), _ip(self._geom), _ip(self._skip))
 
     @property
     def n_pre(self) -> int:
@@ -114,17 +141,28 @@ class Net:
         (ny-cli commands/beta_crown/constraint_eval.rs:80-91)."""
         L = len(self.weights)
         ra = [1] * (L - 1) + [0, 0] if self.relu_after is None else list(self.relu_after[: L - 1]) + [0, 0]
-        return Net(self.weights + [np.asarray(spec, np.float32)], self.biases + [None], ra)
+        return Net(self.weights + [np.asarray(spec, np.float32)], self.biases + [None], ra, self.skips)
 
     def forward(self, x):
-        z = np.asarray(x, np.float64)
+        """Concrete forward pass in binary64 (rows of x are points)."""
+        one = np.asarray(x).ndim == 1
+        z = np.asarray(x, np.float64).reshape(1, -1) if one else np.asarray(x, np.float64)
+        posts = []
         for k, w in enumerate(self.weights):
-            z = z @ w.astype(np.float64).T
-            if self.biases[k] is not None:
-                z = z + self.biases[k].astype(np.float64)
+            if hasattr(w, "kh"):
+                z = w.apply(z)   # the description's own concrete convolution, its bias included
+                if w.bias is None and self.biases[k] is not None:
+                    z = z + np.repeat(self.biases[k].astype(np.float64), w.oh * w.ow)[None, :]
+            else:
+                z = z @ w.astype(np.float64).T
+                if self.biases[k] is not None:
+                    z = z + self.biases[k].astype(np.float64)
+            if k in self.skips:
+                z = z + posts[self.skips[k]]
             if k + 1 < len(self.weights) and (self.relu_after is None or self.relu_after[k]):
                 z = np.maximum(z, 0.0)
-        return z
+            posts.append(z)
+        return z[0] if one else z
 
 
 def _f32(a):

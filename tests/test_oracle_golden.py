@@ -163,3 +163,120 @@ def test_conv2d_strided_padded_matches_direct_convolution(oracle):
         oracle.conv2d_dense(w, None, (0, 1), (0, 0), (6, 6))       # tests.rs:874-897: zero stride rejected
     with pytest.raises(ValueError):
         oracle.conv2d_dense(w, None, (1, 1), (0, 0), (2, 2))       # tests.rs:913-927: output size underflow
+
+
+# ---- the oracle's native Conv2d (kernel taps, no dense lowering) on the same known answers ----------------
+def _native(weight, bias, in_hw, stride=(1, 1), pad=(0, 0)):
+    from ny_b200.engine import Conv2d
+
+    return Conv2d(np.asarray(weight, np.float32), None if bias is None else np.asarray(bias, np.float32),
+                  stride=stride, pad=pad, in_hw=in_hw)
+
+
+def test_native_conv2d_known_answers(oracle):
+    """The same known answers of conv2d/tests.rs (:46-66, :561-584 interval pass; :287-306, :620-654 backward) through
+    the native convolution of the oracle: interval pass values, and the backward coefficients read off plain CROWN
+    of a single stable layer (on a box where every output is positive the bound is exactly the affine map)."""
+    lo = np.array([1, 2, 3, 4], np.float32)
+    hi = np.array([5, 6, 7, 8], np.float32)
+    for k, want_lo, want_hi in ((2.0, [2.5, 4.5, 6.5, 8.5], [10.5, 12.5, 14.5, 16.5]),):
+        c = _native([[[[k]]]], [0.5], (2, 2))
+        net = oracle.Net([c, np.eye(4, dtype=np.float32)], [None, None], [0, 0])
+        pl, pu = oracle.ibp_forward(net, lo, hi)
+        assert np.allclose(pl[:4], want_lo, atol=1e-5) and np.allclose(pu[:4], want_hi, atol=1e-5)
+        assert np.all(pl[:4] <= want_lo) and np.all(pu[:4] >= want_hi)
+    c = _native([[[[-2.0]]]], [1.0], (2, 2))
+    net = oracle.Net([c, np.eye(4, dtype=np.float32)], [None, None], [0, 0])
+    pl, pu = oracle.ibp_forward(net, lo, hi)
+    assert np.allclose(pl[:4], [-9, -11, -13, -15], atol=1e-5) and np.allclose(pu[:4], [-1, -3, -5, -7], atol=1e-5)
+    # backward: CROWN through [conv 1x1 (2x + 0.5)] then identity read-out equals the interval of 2x + 0.5 exactly
+    c = _native([[[[2.0]]]], [0.5], (2, 2))
+    net = oracle.Net([c, np.eye(4, dtype=np.float32)], [None, None], [0, 0])
+    ol, ou = oracle.crown(net, lo, hi)
+    assert np.allclose(ol, [2.5, 4.5, 6.5, 8.5], atol=1e-5) and np.allclose(ou, [10.5, 12.5, 14.5, 16.5], atol=1e-5)
+    # 2x2 kernel on a 2x2 input: one output = 1 x00 + 2 x01 + 3 x10 + 4 x11
+    c = _native([[[[1.0, 2.0], [3.0, 4.0]]]], None, (2, 2))
+    net = oracle.Net([c, np.eye(1, dtype=np.float32)], [None, None], [0, 0])
+    ol, ou = oracle.crown(net, lo, hi)
+    assert np.allclose(ol, [1 * 1 + 2 * 2 + 3 * 3 + 4 * 4], atol=1e-4) and np.allclose(ou, [1 * 5 + 2 * 6 + 3 * 7 + 4 * 8], atol=1e-4)
+
+
+def test_native_conv2d_equals_dense_lowering(oracle):
+    """Strided, padded, multi-channel CNN: interval pass, plain CROWN and the beta-CROWN bound of split domains through
+    the native convolution agree with the dense lowering of the same network (same exact products; the sums differ
+    only in the zeros the lowering adds)."""
+    from ny_b200.engine import SPLIT_DTYPE
+
+    g = np.random.Generator(np.random.PCG64(8))
+    c1 = _native(g.standard_normal((4, 2, 4, 4)) * 0.3, g.standard_normal(4) * 0.1, (8, 8), (2, 2), (1, 1))
+    c2 = _native(g.standard_normal((3, 4, 3, 3)) * 0.3, None, (c1.oh, c1.ow), (1, 1), (1, 1))
+    fc = (g.standard_normal((6, c2.out_features)) * 0.3).astype(np.float32)
+    fb = (g.standard_normal(6) * 0.1).astype(np.float32)
+    spec = (np.eye(6, dtype=np.float32)[:1] - np.eye(6, dtype=np.float32)[1:]).astype(np.float32)
+    ws, bs = oracle.lower_network([c1, c2, fc], [c1.bias, None, fb])
+    dense, native = oracle.Net(ws, bs), oracle.Net([c1, c2, fc], [None, None, fb])
+    assert np.array_equal(dense.dims, native.dims)
+    x0 = g.uniform(0, 1, c1.in_features).astype(np.float32)
+    lo, hi = x0 - np.float32(0.03), x0 + np.float32(0.03)
+    dl, du = oracle.ibp_forward(dense, lo, hi)
+    nl, nu = oracle.ibp_forward(native, lo, hi)
+    assert np.array_equal(dl, nl) and np.array_equal(du, nu)
+    a = oracle.crown(dense.with_spec(spec), lo, hi)
+    b = oracle.crown(native.with_spec(spec), lo, hi)
+    assert np.allclose(a[0], b[0], rtol=1e-6, atol=1e-7) and np.allclose(a[1], b[1], rtol=1e-6, atol=1e-7)
+    # a split domain through the batch entry point
+    unstable = np.flatnonzero((dl[: c1.out_features] < 0) & (du[: c1.out_features] > 0))
+    sp = np.zeros((2, 2), SPLIT_DTYPE)
+    sp[0, 0] = (0, int(unstable[0]), 1, 0.3)
+    sp[0, 1] = (0, int(unstable[1]), -1, 0.1)
+    sp[1, 0] = (0, int(unstable[2]), -1, 0.0)
+    ns = np.array([2, 1], np.int32)
+    S = spec.shape[0]
+    rl = np.concatenate([dl, np.full(S, -np.inf, np.float32)])
+    ru = np.concatenate([du, np.full(S, np.inf, np.float32)])
+    r1 = oracle.bab_bound_batch(dense.with_spec(spec), lo, hi, rl, ru, sp, ns, 1)
+    r2 = oracle.bab_bound_batch(native.with_spec(spec), lo, hi, rl, ru, sp, ns, 1)
+    assert np.array_equal(r1[2], r2[2])
+    assert np.allclose(r1[0], r2[0], rtol=1e-6, atol=1e-7) and np.allclose(r1[1], r2[1], rtol=1e-6, atol=1e-7)
+    # sampled soundness of the native path
+    xs = lo + g.random((20000, lo.shape[0])).astype(np.float32) * (hi - lo)
+    ys = native.forward(xs) @ spec.astype(np.float64).T
+    assert np.all(b[0] <= ys.min(axis=0)) and np.all(b[1] >= ys.max(axis=0))
+
+
+def test_native_residual_network_equals_its_sequential_lowering(oracle):
+    """A small residual CNN (conv stem + two residual blocks + pooled read-out): the oracle's native evaluation
+    (kernel taps, identity branches joined in place) against the dense sequential lowering that carries the skipped
+    activation as extra neurons.  Same function, same interval bounds on the original neurons, same beta-CROWN bounds
+    of split domains."""
+    from ny_b200 import workloads as W
+
+    wl = W.config_resnet(seed=61, eps=0.02, n_fix=3, in_chw=(2, 8, 8), channels=4, blocks=2, n_out=5)
+    ws, bs = oracle.lower_network(wl.net.weights, wl.net.biases)
+    lw, lb, widths = oracle.lower_residual(ws, bs, wl.net.skips)
+    low = oracle.Net(lw, lb)
+    nat = oracle.Net(wl.net.weights, wl.net.biases, skips=wl.net.skips)
+    idx, off = [], 0
+    for k, n in enumerate(widths):
+        idx.append(off + np.arange(n))
+        off += lw[k].shape[0]
+    idx = np.concatenate(idx)
+    g = np.random.Generator(np.random.PCG64(2))
+    x = wl.in_lo + g.random((8, len(wl.in_lo))) * (wl.in_hi - wl.in_lo)
+    assert np.abs(nat.forward(x) - low.forward(x)).max() < 1e-10
+    ll, lu = oracle.ibp_forward(low, wl.in_lo, wl.in_hi)
+    nl, nu = oracle.ibp_forward(nat, wl.in_lo, wl.in_hi)
+    tol = 1e-6 * np.maximum(np.abs(nl), np.abs(nu)) + 1e-7
+    assert np.all(np.abs(ll[idx] - nl) <= tol) and np.all(np.abs(lu[idx] - nu) <= tol)
+    D = 12
+    splits, ns = W.draw_domains(wl, nl, nu, D)
+    S = wl.spec.shape[0]
+    ext = lambda a, v: np.concatenate([a, np.full(S, v, np.float32)])
+    n_lo, n_hi, n_inf, _ = oracle.bab_bound_batch(nat.with_spec(wl.spec), wl.in_lo, wl.in_hi, ext(nl, -np.inf), ext(nu, np.inf), splits, ns, 1)
+    # the lowered network's neuron indices differ: map the split neurons of layer r through idx
+    lsp = splits.copy()
+    l_lo, l_hi, l_inf, _ = oracle.bab_bound_batch(low.with_spec(wl.spec), wl.in_lo, wl.in_hi, ext(ll, -np.inf), ext(lu, np.inf), lsp, ns, 1)
+    assert np.array_equal(n_inf, l_inf)
+    f = n_inf == 0
+    scale = np.abs(l_lo[f]).max(axis=1, keepdims=True)
+    assert np.all(np.abs(n_lo[f] - l_lo[f]) <= 2e-6 * scale) and np.all(np.abs(n_hi[f] - l_hi[f]) <= 2e-6 * scale)
