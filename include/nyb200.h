@@ -260,8 +260,29 @@ typedef struct nyb200_opt_config {
                             activations/relu/mod.rs:570-1128): as 0, and the upper rows get their own slopes
                             alpha_up for negative coefficients, started at alpha and descending the sum of the
                             upper bounds */
+    int32_t rule;        /* update rule of alpha and beta.  0: projected Adam (above).
+                            1: the plain projected step that is the reference's default (use_adaptive = false):
+                               beta <- max(0, beta + lr g) (BetaState::gradient_step, beta_crown/state/beta.rs:272-305),
+                               alpha <- clamp(alpha + lr g, 0, 1); no moments, no gradient clip.
+                            2: Adam with AMSGrad's running maximum of the second moment (beta.rs:369-376; the resident
+                               contract GpuBetaAdamConfig, crates/ny-core/src/gemm.rs:2960-2993) */
+    float tolerance;     /* > 0: a domain stops once max |gradient| over its parameters (clipped beta gradients, raw
+                            alpha gradients) is below it: the reference's beta_tolerance
+                            (beta_crown/engine/optimization/optimize_loop.rs:272-279).  Evaluated per domain on the device;
+                            a stopped domain keeps its parameters while the others continue in lock-step. */
+    int32_t patience;    /* > 0: a domain stops once its objective's best value has not improved for more than `patience`
+                            iterations (patience_exhausted_after_iteration, optimize_loop.rs:45-57) */
+    float start_save_best; /* in (0, 1): the element-wise best bounds are only updated at the first iteration, after
+                            iterations * start_save_best iterations and at the last one, and for a domain that has
+                            stopped (AlphaCrownConfig::should_save_best, bounds/alpha_config.rs:1085-1091, used at
+                            network/alpha_crown_loop.rs:928-936; the reference's 0.5).  0: every iteration. */
 } nyb200_opt_config;
 int32_t nyb200_batch_optimize(nyb200_engine *e, const nyb200_opt_config *cfg);
+/* After nyb200_batch_optimize: evaluations[d] = number of bound evaluations domain d took part in before it stopped
+ * (tolerance or patience), the stopping iteration's update included; equal to `iterations` for a domain that never
+ * stopped.  A stop takes effect after the update of its iteration; the parameters it leaves are evaluated once more
+ * and folded into the best bounds (the reference returns without that evaluation: this can only be tighter). */
+int32_t nyb200_batch_download_opt_evaluations(nyb200_engine *e, int32_t *evaluations);
 /* alpha [D x sum_{k>=1} dims[k]] (meaningful on unstable unsplit neurons) and beta [D x max_splits]
  * (same order as the uploaded split lists) after the last run.  Either pointer may be NULL. */
 int32_t nyb200_batch_download_params(nyb200_engine *e, float *alpha, float *beta);

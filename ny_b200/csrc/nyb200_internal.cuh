@@ -79,6 +79,7 @@ struct Batch {
     bool optimized = false;  // the last run was a parameter optimisation: results are the best-so-far bounds
     bool finished = false;  // results of the last run have been checked (and refined if needed)
     int refined = 0;        // domains that triggered the binary64 re-run of the last batch
+    int opt_iterations = 0; // iterations of the last parameter optimisation
     // Left behind by the last plain-CROWN call: the input-level coefficient rows of its final pass
     // ([crown_D * 2 * crown_S x crown_lda], per box S lower rows then S upper rows), until any call reuses the workspace.
     const float *crown_a = nullptr;
@@ -173,6 +174,7 @@ void launch_min_lower(nyb200_engine *e, int D, int S, const float *out_lo, const
 void launch_select_branch(nyb200_engine *e, const NetView &nv, int D, const float *pre_lo, const float *pre_hi,
                           const signed char *code, int *relu, int *neuron, float *width, int kind);
 void launch_fill_f64(nyb200_engine *e, double *p, size_t n, double v);
+void launch_fill_f32(nyb200_engine *e, float *p, size_t n, float v);
 
 // ---- resident batch (nyb200_api.cu) ----
 // Device addresses of the resident batch's arrays (all inside the engine's named workspace).

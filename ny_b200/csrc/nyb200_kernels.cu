@@ -973,6 +973,15 @@ void launch_select_branch(nyb200_engine *e, const NetView &nv, int D, const floa
     NYB_COUNT(e);
 }
 
+__global__ void k_fill_f32(float *p, size_t n, float v) {
+    size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t < n) p[t] = v;
+}
+void launch_fill_f32(nyb200_engine *e, float *p, size_t n, float v) {
+    k_fill_f32<<<(unsigned)((n + 255) / 256), 256, 0, e->stream>>>(p, n, v);
+    NYB_COUNT(e);
+}
+
 void launch_fill_f64(nyb200_engine *e, double *p, size_t n, double v) {
     k_fill_f64<<<(unsigned)((n + 255) / 256), 256, 0, e->stream>>>(p, n, v);
     NYB_COUNT(e);

@@ -26,7 +26,18 @@ namespace {
 
 struct AdamStep {
     float lr_alpha, lr_beta, beta1, beta2, epsilon, bc1, bc2, clip_beta;
+    int rule;  // 0 Adam, 1 plain projected step, 2 Adam + AMSGrad
 };
+
+// Per-domain optimisation state (workspace "opt_state", D entries each).
+struct OptState {
+    int *stopped;        // 0 = running, t = stopped by the rules after the update of iteration t
+    unsigned *maxg;      // bit pattern of max |gradient| of the iteration in flight (non-negative floats order as integers; NaN sorts above inf)
+    float *best_obj;     // best objective value so far
+    int *no_improve;     // iterations without improvement
+};
+
+__device__ __forceinline__ float nan_max(float a, float b) { return (isnan(a) || isnan(b)) ? NAN : fmaxf(a, b); }
 
 __global__ void k_transpose(const float *__restrict__ W, int n_out, int n_in, float *__restrict__ WT) {
     __shared__ float tile[32][33];
@@ -67,10 +78,12 @@ k_adjoint_relu(int n, int off, int D, int S, int R, int Zr, long nps, float *__r
                const signed char *__restrict__ code, const float *__restrict__ pre_lo,
                const float *__restrict__ pre_hi, float *__restrict__ mom, float *__restrict__ var,
                const int *__restrict__ only_row, float *__restrict__ aup, float *__restrict__ mom_up,
-               float *__restrict__ var_up, float *__restrict__ grad_out, AdamStep h) {
+               float *__restrict__ var_up, float *__restrict__ grad_out, AdamStep h, const int *__restrict__ stopped,
+               unsigned *__restrict__ maxg, float *__restrict__ vmax, float *__restrict__ vmax_up) {
     long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= (long)D * n) return;
     int d = (int)(t / n), i = (int)(t % n);
+    const bool frozen = stopped && stopped[d] != 0;  // a stopped domain keeps its parameters
     long o = (long)d * nps + off + i;
     float4 tb = tab[o];
     float bk = bias ? bias[i] : 0.f;
@@ -101,37 +114,51 @@ k_adjoint_relu(int n, int off, int D, int S, int R, int Zr, long nps, float *__r
             bool pos = ap >= 0.f;
             Z[zr] = fmaf(g, pos ? tb.y : au, pos ? tb.z : 0.f);
         }
-        if ((c == 0) && (l < 0.f) && (u > 0.f) && h.lr_alpha > 0.f) {
-            float m = h.beta1 * mom_up[o] + (1.f - h.beta1) * g_up;
-            float v = h.beta2 * var_up[o] + (1.f - h.beta2) * g_up * g_up;
-            float a = au - h.lr_alpha * (m / h.bc1) / (sqrtf(v / h.bc2) + h.epsilon);
+        if ((c == 0) && (l < 0.f) && (u > 0.f) && h.lr_alpha > 0.f && !frozen) {
+            float a, m = 0.f, v = 0.f;
+            if (h.rule == 1) a = au - h.lr_alpha * g_up;
+            else {
+                m = h.beta1 * mom_up[o] + (1.f - h.beta1) * g_up;
+                v = h.beta2 * var_up[o] + (1.f - h.beta2) * g_up * g_up;
+                float vu = v;
+                if (h.rule == 2) { vu = nan_max(vmax_up[o], v); vmax_up[o] = vu; }
+                a = au - h.lr_alpha * (m / h.bc1) / (sqrtf(vu / h.bc2) + h.epsilon);
+            }
             a = fminf(fmaxf(a, 0.f), 1.f);
-            if (isnan(a)) { a = 0.5f; m = 0.f; v = 0.f; }
-            aup[o] = a; mom_up[o] = m; var_up[o] = v;
+            if (isnan(a)) { a = 0.5f; m = 0.f; v = 0.f; if (h.rule == 2) vmax_up[o] = 0.f; }
+            aup[o] = a;
+            if (h.rule != 1) { mom_up[o] = m; var_up[o] = v; }
         }
     }
     if (grad_out)  // export: the slope's gradient of an unstable unsplit neuron, the multiplier's of a split one
         grad_out[o] = ((c == 0) && (l < 0.f) && (u > 0.f)) ? g_alpha : (c != 0 ? (c > 0 ? -g_sum : g_sum) : 0.f);
     bool is_alpha = (c == 0) && (l < 0.f) && (u > 0.f) && h.lr_alpha > 0.f;
     bool is_beta = (c != 0) && h.lr_beta > 0.f;
-    if (!is_alpha && !is_beta) return;
+    if ((!is_alpha && !is_beta) || frozen) return;
     float g = is_alpha ? g_alpha : (c > 0 ? -g_sum : g_sum);
-    if (is_beta && h.clip_beta > 0.f) g = fminf(fmaxf(g, -h.clip_beta), h.clip_beta);
-    float m = h.beta1 * mom[o] + (1.f - h.beta1) * g;
-    float v = h.beta2 * var[o] + (1.f - h.beta2) * g * g;
-    float step = (m / h.bc1) / (sqrtf(v / h.bc2) + h.epsilon);
+    if (is_beta && h.rule != 1 && h.clip_beta > 0.f) g = fminf(fmaxf(g, -h.clip_beta), h.clip_beta);
+    if (maxg) atomicMax(&maxg[d], __float_as_uint(fabsf(g)));  // the domain's convergence measure (NaN wins, as in the reference)
+    float m = 0.f, v = 0.f, step;
+    if (h.rule == 1) step = g;
+    else {
+        m = h.beta1 * mom[o] + (1.f - h.beta1) * g;
+        v = h.beta2 * var[o] + (1.f - h.beta2) * g * g;
+        float vu = v;
+        if (h.rule == 2) { vu = nan_max(vmax[o], v); vmax[o] = vu; }
+        step = (m / h.bc1) / (sqrtf(vu / h.bc2) + h.epsilon);
+    }
     if (is_alpha) {
         float a = tb.x + h.lr_alpha * step;
         a = fminf(fmaxf(a, 0.f), 1.f);
-        if (isnan(a)) { a = 0.5f; m = 0.f; v = 0.f; }
+        if (isnan(a)) { a = 0.5f; m = 0.f; v = 0.f; if (h.rule == 2) vmax[o] = 0.f; }
         tb.x = a;
     } else {
         float sgn = c > 0 ? 1.f : -1.f;
         float b = fabsf(tb.w) + h.lr_beta * step;
-        if (isnan(b)) { b = 0.f; m = 0.f; v = 0.f; }
+        if (isnan(b) || isinf(b)) { b = 0.f; m = 0.f; v = 0.f; if (h.rule == 2) vmax[o] = 0.f; }
         tb.w = sgn * fmaxf(b, 0.f);
     }
-    mom[o] = m; var[o] = v;
+    if (h.rule != 1) { mom[o] = m; var[o] = v; }
     tab[o] = tb;
 }
 
@@ -160,10 +187,14 @@ __global__ void k_argmin_row(int D, int S, const float *__restrict__ lo, int *__
     row[d] = best;
 }
 
+// save: this iteration updates the best bounds of every domain; otherwise only of the domains that have stopped
+// (their last parameters are being evaluated for the first time: the forced save of the reference's early exits)
 __global__ void k_fold_best(long n, int first, const float *__restrict__ lo, const float *__restrict__ hi,
-                            float *__restrict__ best_lo, float *__restrict__ best_hi) {
+                            float *__restrict__ best_lo, float *__restrict__ best_hi, int S = 1, int save = 1,
+                            const int *__restrict__ stopped = nullptr) {
     long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= n) return;
+    if (!save && !(stopped && stopped[t / S] != 0)) return;
     float l = lo[t], u = hi[t];
     if (!first) {
         // infeasible domains report (+inf, -inf) and degraded ones (-inf, +inf) on every iteration, so
@@ -171,6 +202,25 @@ __global__ void k_fold_best(long n, int first, const float *__restrict__ lo, con
         l = fmaxf(l, best_lo[t]); u = fminf(u, best_hi[t]);
     }
     best_lo[t] = l; best_hi[t] = u;
+}
+
+// After the updates of iteration t: per domain, the objective of this iteration's evaluation against the best so far
+// (patience), the iteration's largest gradient against the tolerance; a domain that meets a rule is marked stopped.
+__global__ void k_opt_rules(int D, int S, int t, int objective, float tolerance, int patience, const float *__restrict__ lo,
+                            OptState st) {
+    int d = blockIdx.x * blockDim.x + threadIdx.x;
+    if (d >= D) return;
+    const float mg = __uint_as_float(st.maxg[d]);
+    st.maxg[d] = 0u;
+    if (st.stopped[d] != 0) return;
+    float obj = 0.f;
+    if (objective == 1) { obj = lo[d * S]; for (int s = 1; s < S; ++s) obj = fminf(obj, lo[d * S + s]); }
+    else for (int s = 0; s < S; ++s) { float l = lo[d * S + s]; if (isfinite(l)) obj += l; }
+    int ni = st.no_improve[d];
+    if (obj > st.best_obj[d]) { st.best_obj[d] = obj; ni = 0; } else ++ni;
+    st.no_improve[d] = ni;
+    bool stop = (tolerance > 0.f && mg < tolerance) || (patience > 0 && ni > patience);
+    if (stop) st.stopped[d] = t;
 }
 
 __device__ __forceinline__ void atomic_min_f(float *addr, float v) {
@@ -257,6 +307,9 @@ int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg, float *grad_h
     if (cfg.objective < 0 || cfg.objective > 2) return set_err(e, NYB200_ERR_INVALID, "objective must be 0, 1 or 2");
     if (!(cfg.lr_alpha >= 0.f) || !(cfg.lr_beta >= 0.f) || !(cfg.lr_decay > 0.f))
         return set_err(e, NYB200_ERR_INVALID, "learning rates must be >= 0 and the decay > 0");
+    if (cfg.rule < 0 || cfg.rule > 2) return set_err(e, NYB200_ERR_INVALID, "rule must be 0 (Adam), 1 (plain projected step) or 2 (AMSGrad)");
+    if (!(cfg.tolerance >= 0.f) || cfg.patience < 0 || !(cfg.start_save_best >= 0.f) || !(cfg.start_save_best < 1.f))
+        return set_err(e, NYB200_ERR_INVALID, "tolerance and patience must be >= 0, start_save_best in [0, 1)");
     Net *net;
     NYB_TRY(find_net(e, e->batch.net_id, &net));
     Batch &b = e->batch;
@@ -299,6 +352,26 @@ int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg, float *grad_h
     }
     NYB_WS(best_lo, float *, e, "best_lo", (size_t)D * S * 4);
     NYB_WS(best_hi, float *, e, "best_hi", (size_t)D * S * 4);
+    // per-domain state of the stopping rules; AMSGrad's running maxima
+    NYB_WS(opt_words, int *, e, "opt_state", (size_t)D * 16);
+    OptState ost;
+    ost.stopped = opt_words; ost.maxg = (unsigned *)(opt_words + D); ost.best_obj = (float *)(opt_words + 2 * (size_t)D);
+    ost.no_improve = opt_words + 3 * (size_t)D;
+    NYB_CUDA(e, cudaMemsetAsync(opt_words, 0, (size_t)D * 16, e->stream));
+    launch_fill_f32(e, ost.best_obj, (size_t)D, -INFINITY);
+    const bool rules = (cfg.tolerance > 0.f || cfg.patience > 0) && T > 1 && !grad_host;
+    float *vmax = nullptr, *vmax_up = nullptr;
+    if (cfg.rule == 2 && T > 1) {
+        vmax = (float *)ws_get(e, "adam_vmax", (size_t)D * np * 4);
+        if (!vmax) return NYB200_ERR_OOM;
+        NYB_CUDA(e, cudaMemsetAsync(vmax, 0, (size_t)D * np * 4, e->stream));
+        if (dual) {
+            vmax_up = (float *)ws_get(e, "adam_vmax_up", (size_t)D * np * 4);
+            if (!vmax_up) return NYB200_ERR_OOM;
+            NYB_CUDA(e, cudaMemsetAsync(vmax_up, 0, (size_t)D * np * 4, e->stream));
+        }
+    }
+    const int save_from = (int)((float)T * cfg.start_save_best);  // zero-based iteration threshold of should_save_best
     int *only_row = nullptr;
     if (cfg.objective == 1) {
         only_row = (int *)ws_get(e, "opt_row", (size_t)D * 4);
@@ -333,7 +406,8 @@ int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg, float *grad_h
         NYB_DEADLINE(e, "optimisation");
         const bool last = (t == T);
         NYB_TRY(run_backward(e, *net, b, p, last ? nullptr : ckpt.data(), ldc));
-        k_fold_best<<<gres, 256, 0, e->stream>>>(nres, t == 1, p.out_lo, p.out_hi, best_lo, best_hi);
+        const int save = (t == 1 || (t - 1) > save_from || last || !(cfg.start_save_best > 0.f)) ? 1 : 0;
+        k_fold_best<<<gres, 256, 0, e->stream>>>(nres, t == 1, p.out_lo, p.out_hi, best_lo, best_hi, S, save, ost.stopped);
         e->launches++;
         if (last) break;
         if (only_row) {
@@ -343,7 +417,7 @@ int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg, float *grad_h
         AdamStep h;
         float decay = powf(cfg.lr_decay, (float)(t - 1));
         h.lr_alpha = cfg.lr_alpha * decay; h.lr_beta = cfg.lr_beta * decay;
-        h.beta1 = b1; h.beta2 = b2; h.epsilon = eps; h.clip_beta = cfg.clip_beta;
+        h.beta1 = b1; h.beta2 = b2; h.epsilon = eps; h.clip_beta = cfg.clip_beta; h.rule = cfg.rule;
         h.bc1 = fmaxf(1.f - powf(b1, (float)t), 1.1920929e-7f);
         h.bc2 = fmaxf(1.f - powf(b2, (float)t), 1.1920929e-7f);
         long nseed = (long)D * Zr * nv.dims[0];
@@ -367,7 +441,8 @@ int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg, float *grad_h
             long nt = (long)D * N;
             k_adjoint_relu<<<(unsigned)((nt + 255) / 256), 256, 0, e->stream>>>(N, nv.pre_off[k], D, S, R, Zr, np, zn, ldz, nv.b[k],
                                                                                ckpt[k], ldc, p.tab, p.code, p.pre_lo,
-                                                                               p.pre_hi, mom, var, only_row, p.alpha_up, mom_up, var_up, grad_dev, h);
+                                                                               p.pre_hi, mom, var, only_row, p.alpha_up, mom_up, var_up, grad_dev, h,
+                                                                               rules ? ost.stopped : nullptr, rules ? ost.maxg : nullptr, vmax, vmax_up);
             e->launches++;
             bool opens = false;  // is this layer's post-activation adjoint skipped forward to a later layer?
             for (int kk = k + 2; kk < L - 1; ++kk) opens |= net->skip_of(kk) == k;
@@ -379,7 +454,12 @@ int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg, float *grad_h
             float *tmp = zc; zc = zn; zn = tmp;
         }
         if (grad_host) break;  // gradient export: one evaluation and its adjoint, no second pass
+        if (rules) {
+            k_opt_rules<<<(unsigned)((D + 255) / 256), 256, 0, e->stream>>>(D, S, t, cfg.objective, cfg.tolerance, cfg.patience, p.out_lo, ost);
+            e->launches++;
+        }
     }
+    b.opt_iterations = T;
     static const float inf_word = INFINITY;
     NYB_CUDA(e, cudaMemcpyAsync(p.min_lower, &inf_word, 4, cudaMemcpyHostToDevice, e->stream));
     k_publish_best<<<gres, 256, 0, e->stream>>>(D, S, p.flags, best_lo, best_hi, p.out_lo, p.out_hi, p.min_lower);
@@ -481,6 +561,22 @@ int32_t nyb200_batch_optimize(nyb200_engine *e, const nyb200_opt_config *cfg) {
     cudaError_t st = cudaSetDevice(e->device);
     if (st != cudaSuccess) return nyb::check_cuda(e, st, "cudaSetDevice");
     return nyb::optimize_batch(e, *cfg);
+}
+
+int32_t nyb200_batch_download_opt_evaluations(nyb200_engine *e, int32_t *evaluations) {
+    if (!e || !evaluations) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    cudaError_t st = cudaSetDevice(e->device);
+    if (st != cudaSuccess) return nyb::check_cuda(e, st, "cudaSetDevice");
+    if (!e->batch.valid || !e->batch.optimized) return nyb::set_err(e, NYB200_ERR_INVALID, "no optimisation has been run on this batch");
+    const int D = e->batch.D;
+    int *w = (int *)nyb::ws_get(e, "opt_state", (size_t)D * 16);
+    if (!w) return NYB200_ERR_OOM;
+    st = cudaMemcpyAsync(evaluations, w, (size_t)D * 4, cudaMemcpyDeviceToHost, e->stream);
+    if (st == cudaSuccess) st = cudaStreamSynchronize(e->stream);
+    if (st != cudaSuccess) return nyb::check_cuda(e, st, "opt evaluations");
+    for (int d = 0; d < D; ++d) evaluations[d] = evaluations[d] > 0 ? evaluations[d] + 1 : e->batch.opt_iterations;
+    return NYB200_OK;
 }
 
 int32_t nyb200_batch_gradient(nyb200_engine *e, int32_t objective, float *grad) {

@@ -42,7 +42,7 @@ EXPORTS = [
     "nyb200_crown_bounds", "nyb200_batch_download_alpha_upper",
     "nyb200_batch_verdicts", "nyb200_gemm_f64", "nyb200_conv_transpose_2d", "nyb200_set_deadline_ns",
     "nyb200_batch_gradient", "nyb200_point_vjp_batched", "nyb200_crown_input_coeffs", "nyb200_batch_download_branch_scores",
-    "nyb200_set_error_channel", "nyb200_set_fusion",
+    "nyb200_set_error_channel", "nyb200_set_fusion", "nyb200_batch_download_opt_evaluations",
 ]
 
 
@@ -50,7 +50,8 @@ class OptConfig(C.Structure):
     """nyb200_opt_config: projected-Adam settings of nyb200_batch_optimize (zeros select Adam's defaults)."""
     _fields_ = [("iterations", C.c_int32), ("lr_alpha", C.c_float), ("lr_beta", C.c_float), ("lr_decay", C.c_float),
                 ("beta1", C.c_float), ("beta2", C.c_float), ("epsilon", C.c_float), ("clip_beta", C.c_float),
-                ("objective", C.c_int32)]
+                ("objective", C.c_int32), ("rule", C.c_int32), ("tolerance", C.c_float), ("patience", C.c_int32),
+                ("start_save_best", C.c_float)]
 
 
 class ConvTransposeParams(C.Structure):
@@ -87,6 +88,7 @@ def load_library():
     L.nyb200_set_path.argtypes = [vp, C.c_int32]
     L.nyb200_set_error_channel.argtypes = [vp, C.c_int32]
     L.nyb200_set_fusion.argtypes = [vp, C.c_int32]
+    L.nyb200_batch_download_opt_evaluations.argtypes = [vp, ip]
     L.nyb200_set_refine_tolerance.argtypes = [vp, C.c_float]
     L.nyb200_batch_refined.argtypes = [vp, ip]
     L.nyb200_launch_count.argtypes = [vp]
@@ -496,11 +498,22 @@ class B200Engine:
         return best, bx, int(ce.value)
 
     def batch_optimize(self, iterations: int, lr_alpha: float = 0.1, lr_beta: float = 0.05, lr_decay: float = 0.98,
-                       clip_beta: float = 10.0, objective: int = 0):
-        """alpha/beta projected-Adam optimisation of the resident batch (asynchronous); results through
-        batch_download (element-wise best bounds) and batch_download_params."""
-        cfg = OptConfig(iterations, lr_alpha, lr_beta, lr_decay, 0.0, 0.0, 0.0, clip_beta, objective)
+                       clip_beta: float = 10.0, objective: int = 0, rule: int = 0, tolerance: float = 0.0, patience: int = 0,
+                       start_save_best: float = 0.0):
+        """alpha/beta optimisation of the resident batch (asynchronous); results through batch_download (element-wise
+        best bounds) and batch_download_params.  rule: 0 projected Adam, 1 the reference's default plain projected
+        step, 2 Adam with AMSGrad; tolerance / patience: the reference's per-domain stopping rules
+        (beta_tolerance, early_stop_patience); start_save_best: the alpha loop's best-saving window."""
+        cfg = OptConfig(iterations, lr_alpha, lr_beta, lr_decay, 0.0, 0.0, 0.0, clip_beta, objective, rule, tolerance,
+                        patience, start_save_best)
         self._check(self._L.nyb200_batch_optimize(self._h, C.byref(cfg)))
+
+    def batch_opt_evaluations(self) -> np.ndarray:
+        """Bound evaluations every domain took part in before it stopped (== iterations when it never did)."""
+        D = self._batch_shape[0]
+        out = np.zeros(D, np.int32)
+        self._check(self._L.nyb200_batch_download_opt_evaluations(self._h, _ip(out)))
+        return out
 
     def batch_gradient(self, objective: int = 0) -> np.ndarray:
         """Joint gradient at the batch's current parameters, [D, n_pre]: d/d alpha on unstable unsplit neurons,

@@ -1374,10 +1374,39 @@ int nyo_optimize_dual(const nyo_net *net, const float *in_lo, const float *in_hi
                       const float *pre_hi, nyo_split *splits, int n_splits, float *alpha, int iterations,
                       float lr_alpha, float lr_beta, float lr_decay, float clip_beta, int objective, float *best_lo,
                       float *best_hi, float *alpha_up_out) {
+    nyo_opt_cfg c;
+    memset(&c, 0, sizeof(c));
+    c.iterations = iterations; c.lr_alpha = lr_alpha; c.lr_beta = lr_beta; c.lr_decay = lr_decay; c.clip_beta = clip_beta;
+    c.objective = objective;
+    return nyo_optimize_ex(net, in_lo, in_hi, pre_lo, pre_hi, splits, n_splits, alpha, &c, best_lo, best_hi, alpha_up_out, NULL);
+}
+
+/* The loop with the reference's update rules and stopping rules selectable:
+ *   rule 0  projected Adam (above);
+ *   rule 1  the plain projected step that is the reference's default (use_adaptive = false):
+ *           beta <- max(0, beta + lr g) (BetaState::gradient_step, beta_crown/state/beta.rs:272-305),
+ *           alpha <- clamp(alpha + lr g, 0, 1); no moments; the gradient clip does not apply;
+ *   rule 2  Adam with AMSGrad's running maximum of the second moment (beta.rs:369-376).
+ *   tolerance > 0: stop once max |gradient| over the domain's parameters (clipped beta gradients, raw alpha gradients)
+ *           is below it (optimize_loop.rs:272-279; NaN never compares below);
+ *   patience > 0: stop once the objective's best value has not improved for more than `patience` iterations
+ *           (patience_exhausted_after_iteration, optimize_loop.rs:45-57);
+ *   start_save_best in (0, 1): the element-wise best bounds are only updated at the first iteration, after
+ *           iterations * start_save_best iterations, at the last one and when stopping
+ *           (should_save_best, bounds/alpha_config.rs:1085-1091; alpha_crown_loop.rs:928-936).
+ * A stop takes effect after the update of its iteration; the parameters it leaves are evaluated once more and that
+ * evaluation is folded into the best bounds (the reference returns without it: this can only be tighter).
+ * iterations_run (may be NULL) receives the number of bound evaluations made. */
+int nyo_optimize_ex(const nyo_net *net, const float *in_lo, const float *in_hi, const float *pre_lo,
+                    const float *pre_hi, nyo_split *splits, int n_splits, float *alpha, const nyo_opt_cfg *cfg,
+                    float *best_lo, float *best_hi, float *alpha_up_out, int *iterations_run) {
+    const int iterations = cfg->iterations, objective = cfg->objective, rule = cfg->rule;
+    const float lr_alpha = cfg->lr_alpha, lr_beta = cfg->lr_beta, lr_decay = cfg->lr_decay, clip_beta = cfg->clip_beta;
     int L = net->n_linear, S = net->dims[L];
     size_t total = pre_offset(net, L);
     float *ga = (float *)calloc(total, 4), *ma = (float *)calloc(total, 4), *va = (float *)calloc(total, 4);
     float *gb = (float *)calloc((size_t)(n_splits + 1), 4), *mb = (float *)calloc((size_t)(n_splits + 1), 4), *vb = (float *)calloc((size_t)(n_splits + 1), 4);
+    float *xa = (float *)calloc(total, 4), *xu = (float *)calloc(total, 4), *xb = (float *)calloc((size_t)(n_splits + 1), 4); /* AMSGrad maxima */
     float *lo = (float *)malloc(4 * (size_t)S), *hi = (float *)malloc(4 * (size_t)S);
     const float b1 = 0.9f, b2 = 0.999f, eps = 1e-8f;
     const int dual = objective == 2 && alpha != NULL;
@@ -1387,10 +1416,18 @@ int nyo_optimize_dual(const nyo_net *net, const float *in_lo, const float *in_hi
         gu = (float *)calloc(total, 4); mu = (float *)calloc(total, 4); vu = (float *)calloc(total, 4);
     }
     for (int s = 0; s < S; ++s) { best_lo[s] = -INFINITY; best_hi[s] = INFINITY; }
+    const int save_from = (int)((float)iterations * cfg->start_save_best);  /* zero-based iteration threshold */
+    float best_obj = -INFINITY;
+    int no_improve = 0, stopping = 0, runs = 0;
     for (int t = 1; t <= iterations; ++t) {
         nyo_beta_crown_bound_dual(net, in_lo, in_hi, pre_lo, pre_hi, splits, n_splits, alpha, aup, lo, hi);
-        for (int s = 0; s < S; ++s) { if (lo[s] > best_lo[s]) best_lo[s] = lo[s]; if (hi[s] < best_hi[s]) best_hi[s] = hi[s]; }
-        if (t == iterations) break;
+        ++runs;
+        if (t == 1 || (t - 1) > save_from || t == iterations || stopping || !(cfg->start_save_best > 0.0f))
+            for (int s = 0; s < S; ++s) { if (lo[s] > best_lo[s]) best_lo[s] = lo[s]; if (hi[s] < best_hi[s]) best_hi[s] = hi[s]; }
+        if (t == iterations || stopping) break;
+        float obj = 0.0f;
+        if (objective == 1) { obj = lo[0]; for (int s = 1; s < S; ++s) if (lo[s] < obj) obj = lo[s]; }
+        else for (int s = 0; s < S; ++s) if (isfinite(lo[s])) obj += lo[s];
         if (dual) nyo_upper_gradient(net, in_lo, in_hi, pre_lo, pre_hi, splits, n_splits, alpha, aup, NULL, gu);
         int row = -1;
         if (objective == 1) { row = 0; for (int s = 1; s < S; ++s) if (lo[s] < lo[row]) row = s; }
@@ -1398,17 +1435,26 @@ int nyo_optimize_dual(const nyo_net *net, const float *in_lo, const float *in_hi
         float bc1 = fmaxf(1.0f - powf(b1, (float)t), 1.1920929e-7f), bc2 = fmaxf(1.0f - powf(b2, (float)t), 1.1920929e-7f);
         float lra = lr_alpha * powf(lr_decay, (float)(t - 1)), lrb = lr_beta * powf(lr_decay, (float)(t - 1));
         size_t hidden = pre_offset(net, L - 1);
+        float max_grad = 0.0f;
+#define NYO_MAXG(g) do { float _a = fabsf(g); if (isnan(_a) || isnan(max_grad)) max_grad = NAN; else if (_a > max_grad) max_grad = _a; } while (0)
         if (alpha && lr_alpha > 0.0f) for (size_t i = 0; i < hidden; ++i) {
             if (!(pre_lo[i] < 0.0f && pre_hi[i] > 0.0f)) continue;
             int is_split = 0;
             for (int q = 0; q < n_splits; ++q) if (pre_offset(net, splits[q].relu) + (size_t)splits[q].neuron == i) is_split = 1;
             if (is_split) continue;
             float g = ga[i];
-            ma[i] = b1 * ma[i] + (1.0f - b1) * g;
-            va[i] = b2 * va[i] + (1.0f - b2) * g * g;
-            float a = alpha[i] + lra * (ma[i] / bc1) / (sqrtf(va[i] / bc2) + eps);
+            NYO_MAXG(g);
+            float a;
+            if (rule == 1) a = alpha[i] + lra * g;
+            else {
+                ma[i] = b1 * ma[i] + (1.0f - b1) * g;
+                va[i] = b2 * va[i] + (1.0f - b2) * g * g;
+                float v = va[i];
+                if (rule == 2) { xa[i] = (isnan(xa[i]) || isnan(v)) ? NAN : fmaxf(xa[i], v); v = xa[i]; }
+                a = alpha[i] + lra * (ma[i] / bc1) / (sqrtf(v / bc2) + eps);
+            }
             a = fminf(fmaxf(a, 0.0f), 1.0f);
-            if (isnan(a)) { a = 0.5f; ma[i] = 0.0f; va[i] = 0.0f; }
+            if (isnan(a)) { a = 0.5f; ma[i] = 0.0f; va[i] = 0.0f; xa[i] = 0.0f; }
             alpha[i] = a;
         }
         if (dual && lr_alpha > 0.0f) for (size_t i = 0; i < hidden; ++i) {
@@ -1417,25 +1463,43 @@ int nyo_optimize_dual(const nyo_net *net, const float *in_lo, const float *in_hi
             for (int q = 0; q < n_splits; ++q) if (pre_offset(net, splits[q].relu) + (size_t)splits[q].neuron == i) is_split = 1;
             if (is_split) continue;
             float g = gu[i];
-            mu[i] = b1 * mu[i] + (1.0f - b1) * g;
-            vu[i] = b2 * vu[i] + (1.0f - b2) * g * g;
-            float a = aup[i] - lra * (mu[i] / bc1) / (sqrtf(vu[i] / bc2) + eps);   /* descent: the upper bound shrinks */
+            float a;
+            if (rule == 1) a = aup[i] - lra * g;
+            else {
+                mu[i] = b1 * mu[i] + (1.0f - b1) * g;
+                vu[i] = b2 * vu[i] + (1.0f - b2) * g * g;
+                float v = vu[i];
+                if (rule == 2) { xu[i] = (isnan(xu[i]) || isnan(v)) ? NAN : fmaxf(xu[i], v); v = xu[i]; }
+                a = aup[i] - lra * (mu[i] / bc1) / (sqrtf(v / bc2) + eps);   /* descent: the upper bound shrinks */
+            }
             a = fminf(fmaxf(a, 0.0f), 1.0f);
-            if (isnan(a)) { a = 0.5f; mu[i] = 0.0f; vu[i] = 0.0f; }
+            if (isnan(a)) { a = 0.5f; mu[i] = 0.0f; vu[i] = 0.0f; xu[i] = 0.0f; }
             aup[i] = a;
         }
         if (lr_beta > 0.0f) for (int q = 0; q < n_splits; ++q) {
             float g = gb[q];
-            if (clip_beta > 0.0f) g = fminf(fmaxf(g, -clip_beta), clip_beta);
-            mb[q] = b1 * mb[q] + (1.0f - b1) * g;
-            vb[q] = b2 * vb[q] + (1.0f - b2) * g * g;
-            float bnew = splits[q].beta + lrb * (mb[q] / bc1) / (sqrtf(vb[q] / bc2) + eps);
-            if (isnan(bnew)) { bnew = 0.0f; mb[q] = 0.0f; vb[q] = 0.0f; }
+            if (rule != 1 && clip_beta > 0.0f) g = fminf(fmaxf(g, -clip_beta), clip_beta);
+            NYO_MAXG(g);
+            float bnew;
+            if (rule == 1) bnew = splits[q].beta + lrb * g;
+            else {
+                mb[q] = b1 * mb[q] + (1.0f - b1) * g;
+                vb[q] = b2 * vb[q] + (1.0f - b2) * g * g;
+                float v = vb[q];
+                if (rule == 2) { xb[q] = (isnan(xb[q]) || isnan(v)) ? NAN : fmaxf(xb[q], v); v = xb[q]; }
+                bnew = splits[q].beta + lrb * (mb[q] / bc1) / (sqrtf(v / bc2) + eps);
+            }
+            if (isnan(bnew) || isinf(bnew)) { bnew = 0.0f; mb[q] = 0.0f; vb[q] = 0.0f; xb[q] = 0.0f; }
             splits[q].beta = fmaxf(bnew, 0.0f);
         }
+#undef NYO_MAXG
+        if (cfg->tolerance > 0.0f && max_grad < cfg->tolerance) stopping = 1;
+        if (obj > best_obj) { best_obj = obj; no_improve = 0; } else ++no_improve;
+        if (cfg->patience > 0 && no_improve > cfg->patience) stopping = 1;
     }
+    if (iterations_run) *iterations_run = runs;
     if (dual && alpha_up_out) memcpy(alpha_up_out, aup, 4 * total);
-    free(aup); free(gu); free(mu); free(vu);
+    free(aup); free(gu); free(mu); free(vu); free(xa); free(xu); free(xb);
     free(ga); free(ma); free(va); free(gb); free(mb); free(vb); free(lo); free(hi);
     return 0;
 }

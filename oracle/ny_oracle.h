@@ -132,6 +132,19 @@ int nyo_optimize_dual(const nyo_net *net, const float *in_lo, const float *in_hi
                       const float *pre_hi, nyo_split *splits, int n_splits, float *alpha, int iterations,
                       float lr_alpha, float lr_beta, float lr_decay, float clip_beta, int objective, float *best_lo,
                       float *best_hi, float *alpha_up_out);
+/* The same loop with the reference's other update and stopping rules (see the definition). */
+typedef struct {
+    int32_t iterations;
+    float lr_alpha, lr_beta, lr_decay, clip_beta;
+    int32_t objective;       /* 0 sum of the rows, 1 smallest row, 2 dual alpha */
+    int32_t rule;            /* 0 Adam, 1 plain projected step (the reference default), 2 Adam + AMSGrad */
+    float tolerance;         /* > 0: stop when max |gradient| < tolerance */
+    int32_t patience;        /* > 0: stop after more than `patience` iterations without improvement */
+    float start_save_best;   /* in (0,1): best bounds updated at iteration 0 and after iterations * this */
+} nyo_opt_cfg;
+int nyo_optimize_ex(const nyo_net *net, const float *in_lo, const float *in_hi, const float *pre_lo,
+                    const float *pre_hi, nyo_split *splits, int n_splits, float *alpha, const nyo_opt_cfg *cfg,
+                    float *best_lo, float *best_hi, float *alpha_up_out, int *iterations_run);
 int nyo_select_intercept(const nyo_net *net, const float *pre_lo, const float *pre_hi, const nyo_split *splits,
                          int n_splits, int32_t *relu, int32_t *neuron, float *score);
 

@@ -378,6 +378,93 @@ def optimize(net: Net, lo, hi, pre_lo, pre_hi, splits: np.ndarray, alpha, iterat
     return bl, bu, alpha, splits
 
 
+class _OptCfg(C.Structure):
+    _fields_ = [("iterations", C.c_int32), ("lr_alpha", C.c_float), ("lr_beta", C.c_float), ("lr_decay", C.c_float),
+                ("clip_beta", C.c_float), ("objective", C.c_int32), ("rule", C.c_int32), ("tolerance", C.c_float),
+                ("patience", C.c_int32), ("start_save_best", C.c_float)]
+
+
+def optimize_ex(net: Net, lo, hi, pre_lo, pre_hi, splits: np.ndarray, alpha, iterations, lr_alpha, lr_beta, lr_decay=0.98,
+                clip_beta=10.0, objective=0, rule=0, tolerance=0.0, patience=0, start_save_best=0.0):
+    """nyo_optimize_ex: the optimisation loop with the update rule (0 Adam, 1 plain projected step, 2 AMSGrad) and the
+    reference's stopping / best-saving rules.  Returns (best_lo, best_hi, alpha, splits, evaluations made)."""
+    lo, hi, pre_lo, pre_hi = _f32(lo), _f32(hi), _f32(pre_lo), _f32(pre_hi)
+    alpha = _f32(alpha).copy()
+    splits = np.ascontiguousarray(splits, SPLIT_DTYPE).copy()
+    S = int(net.dims[-1])
+    bl, bu = np.empty(S, np.float32), np.empty(S, np.float32)
+    cfg = _OptCfg(iterations, lr_alpha, lr_beta, lr_decay, clip_beta, objective, rule, tolerance, patience, start_save_best)
+    runs = C.c_int(0)
+    fn = lib().nyo_optimize_ex
+    fn.argtypes = [C.c_void_p] + [C.POINTER(C.c_float)] * 4 + [C.c_void_p, C.c_int, C.POINTER(C.c_float), C.POINTER(_OptCfg),
+                                                               C.POINTER(C.c_float), C.POINTER(C.c_float), C.POINTER(C.c_float),
+                                                               C.POINTER(C.c_int)]
+    rc = fn(C.addressof(net.c), _fp(lo), _fp(hi), _fp(pre_lo), _fp(pre_hi), splits.ctypes.data, len(splits), _fp(alpha),
+            C.byref(cfg), _fp(bl), _fp(bu), None, C.byref(runs))
+    if rc != 0:
+        raise ValueError(f"nyo_optimize_ex returned {rc}")
+    return bl, bu, alpha, splits, int(runs.value)
+
+
+def beta_plain_step(values, grads, lr):
+    """BetaState::gradient_step (beta_crown/state/beta.rs:272-305), the reference's default multiplier update:
+    beta <- max(0, beta + lr * grad) (ascent on the lower bound, projected onto beta >= 0); a non-finite result resets
+    the entry to zero.  Returns (values', max |grad|)."""
+    v = np.asarray(values, np.float32)
+    g = np.asarray(grads, np.float32)
+    out = np.maximum(v + np.float32(lr) * g, np.float32(0))
+    out = np.where(np.isfinite(v + np.float32(lr) * g), out, np.float32(0)).astype(np.float32)
+    return out, float(np.max(np.abs(g))) if g.size else 0.0
+
+
+def beta_adam_step(state, grads, t, beta_lr=0.05, beta1=0.9, beta2=0.999, epsilon=1e-8, grad_clip=10.0, lr_decay=0.98,
+                   amsgrad=False, bias_correction=True):
+    """BetaState::gradient_step_adam (beta_crown/state/beta.rs:314-441) with the default scheduler
+    (ExponentialDecay: lr_t = beta_lr * lr_decay^(t-1)) and uniform per-layer factors: gradient clipped to
+    [-grad_clip, grad_clip], moments m, v, bias corrections 1 - beta^t (floored at machine epsilon), AMSGrad's running
+    maximum of v when enabled, beta <- max(0, beta + lr_t * m_hat / (sqrt(v_hat) + epsilon)); an entry whose moments
+    became non-finite is reset.  state = dict(value, m, v, v_max) of fp32 arrays; returns (state', max |clipped grad|)."""
+    f32 = np.float32
+    g = np.asarray(grads, np.float32)
+    if grad_clip > 0:
+        g = np.clip(g, f32(-grad_clip), f32(grad_clip))
+    tf = f32(max(t, 1))
+    b1c = max(f32(1) - f32(beta1) ** tf, np.finfo(np.float32).eps) if bias_correction else f32(1)
+    b2c = max(f32(1) - f32(beta2) ** tf, np.finfo(np.float32).eps) if bias_correction else f32(1)
+    lr = f32(beta_lr) * f32(lr_decay) ** f32(max(t, 1) - 1)
+    m = f32(beta1) * state["m"] + f32(1 - beta1) * g
+    v = f32(beta2) * state["v"] + f32(1 - beta2) * g * g
+    v_max = np.maximum(state["v_max"], v) if amsgrad else state["v_max"]
+    v_use = v_max if amsgrad else v
+    upd = lr * (m / f32(b1c)) / (np.sqrt(v_use / f32(b2c)) + f32(epsilon))
+    val = np.maximum(state["value"] + upd, f32(0)).astype(np.float32)
+    bad = ~np.isfinite(m) | ~np.isfinite(v)
+    out = {"value": np.where(bad, f32(0), val).astype(np.float32), "m": np.where(bad, f32(0), m).astype(np.float32),
+           "v": np.where(bad, f32(0), v).astype(np.float32), "v_max": np.where(bad, f32(0), v_max).astype(np.float32)}
+    return out, float(np.max(np.abs(g))) if g.size else 0.0
+
+
+def adam_clipping_step(m, v, t, gradient, x, lo, hi, lr0, lr_decay=0.99, beta1=0.9, beta2=0.999, eps=1e-8):
+    """One AdamClippingState::step (ny-propagate/src/pgd_attack/adam_state.rs:46-88), fp32 state: moments updated
+    with `gradient`, direction sign(m / (sqrt(v / bc2) + eps)) with sign(+0) = +1 and 0 where m or the denominator
+    is not finite, uniform step lr0 * lr_decay^(t-1) / bc1 (step 1 uses lr0: the ExponentialLR ordering), result
+    clamped to [lo, hi].  The caller passes the ascent direction: an attack that minimises flips the gradient first
+    (optimizer.rs:296-305).  t is the 1-based step count.  Returns (x', m', v')."""
+    f32 = np.float32
+    g = np.asarray(gradient, np.float32)
+    m = f32(beta1) * np.asarray(m, np.float32) + f32(1 - beta1) * g
+    v = f32(beta2) * np.asarray(v, np.float32) + f32(1 - beta2) * g * g
+    bc1, bc2 = f32(1 - beta1 ** t), f32(1 - beta2 ** t)
+    with np.errstate(invalid="ignore", divide="ignore"):
+        denom = np.sqrt(v / bc2) + f32(eps)
+        q = m / denom
+    d = np.where(np.isfinite(denom) & np.isfinite(m) & ~np.isnan(q), np.copysign(f32(1), q), f32(0)).astype(np.float32)
+    step = f32(lr0 * lr_decay ** (t - 1)) / bc1
+    xn = np.asarray(x, np.float32) + d * step
+    xn = np.where(np.isnan(xn), np.asarray(lo, np.float32), xn)   # project_to_bounds: NaN -> lower end (optimizer.rs:121-127)
+    return np.clip(xn, np.asarray(lo, np.float32), np.asarray(hi, np.float32)).astype(np.float32), m.astype(np.float32), v.astype(np.float32)
+
+
 def pgd_attack(weights, biases, spec, lo, hi, x0, steps, step_size, lr_decay=0.99, beta1=0.9, beta2=0.999, eps=1e-8):
     """numpy restatement of the lock-step PGD attack on a dense sequential ReLU network (convolutions lowered
     with conv2d_dense): objective min_s spec[s] . f(x) per restart, exact gradient of the worst row
@@ -425,8 +512,8 @@ def pgd_attack(weights, biases, spec, lo, hi, x0, steps, step_size, lr_decay=0.9
                 g = g * (acts[k] > 0)
             g = g @ Ws[k]
         g = g.astype(np.float32)
-        m = f32(beta1) * m + f32(1 - beta1) * g
-        v = f32(beta2) * v + f32(1 - beta2) * g * g
+        # the moments follow the objective's gradient; the point moves against their direction (the attack minimises)
+        _, m, v = adam_clipping_step(m, v, t, g, x, lo32, hi32, step_size, lr_decay, beta1, beta2, eps)
         bc1, bc2 = f32(1 - beta1 ** t), f32(1 - beta2 ** t)
         denom = np.sqrt(v / bc2) + f32(eps)
         with np.errstate(invalid="ignore", divide="ignore"):

@@ -225,3 +225,67 @@ def test_babsr_scores_hand_case():
     # |min(-0.5 * (-1/2), -0.5 * 1/2) + (-1) * 1/2| = |-0.25 - 0.5| = 0.75
     sc, _ = O.babsr_scores(ws, bs, -spec, np.array([-1, -1, 0], np.float32), np.array([1, 1, 0], np.float32))
     assert sc.tolist() == [0.75, 0.5]
+
+
+# ---- optimiser restatements pinned to the reference's own known answers (tests/golden/optimizer_reference.json) ----
+def _golden_opt():
+    import json
+    import os
+
+    with open(os.path.join(os.path.dirname(__file__), "golden", "optimizer_reference.json")) as f:
+        return json.load(f)
+
+
+def test_adam_clipping_step_known_answers(oracle):
+    G = _golden_opt()
+    for c in G["adam_clipping"]:
+        n = len(c["x"])
+        x, m, v = oracle.adam_clipping_step(np.zeros(n, np.float32), np.zeros(n, np.float32), 1, c["gradient"], c["x"], c["lo"],
+                                            c["hi"], c["lr0"], c["lr_decay"], c["beta1"], c["beta2"], c["eps"])
+        assert np.all(np.abs(x - np.array(c["expected"], np.float32)) < c["tol"]), c["name"]
+    c = G["adam_clipping_lr_decay"]
+    x = np.array(c["x0"], np.float32)
+    m = v = np.zeros(1, np.float32)
+    steps = []
+    for t in (1, 2):
+        xn, m, v = oracle.adam_clipping_step(m, v, t, c["gradient"], x, c["lo"], c["hi"], c["lr0"], c["lr_decay"], c["beta1"], c["beta2"], c["eps"])
+        steps.append(float(xn[0] - x[0]))
+        x = xn
+    assert np.all(np.abs(np.array(steps) - np.array(c["expected_steps"])) < c["tol"])      # step 1 uses lr0, then decays
+    c = G["project_nan"]
+    pt = np.array([float(p) for p in c["point"]], np.float32)
+    # a zero step leaves the point where projection puts it: NaN -> lower end, above the box -> upper end
+    xn, _, _ = oracle.adam_clipping_step(np.zeros(2, np.float32), np.zeros(2, np.float32), 1, [0.0, 0.0], pt, c["lo"], c["hi"], 0.0)
+    assert xn.tolist() == c["expected"]
+
+
+def test_beta_updates_known_answers(oracle):
+    G = _golden_opt()
+    c = G["beta_plain_step"]
+    vals, mg = oracle.beta_plain_step(c["values"], c["grads"], c["lr"])
+    assert np.all(np.abs(vals - np.array(c["expected_values"], np.float32)) < c["tol"]) and abs(mg - c["expected_max_grad"]) < c["tol"]
+    c = G["beta_signed"]
+    sp = oracle.make_splits([(0, i, 1 if a else -1, b) for i, (a, b) in enumerate(zip(c["active"], c["values"]))])
+    assert (sp["beta"] * sp["sign"]).tolist() == c["expected"]
+    c = G["beta_adam"]
+    cfg = c["config"]
+    z = lambda: {k: np.zeros(1, np.float32) for k in ("value", "m", "v", "v_max")}
+    st, _ = oracle.beta_adam_step(z(), [c["grad"]], 1, **cfg)
+    s1 = c["step1"]
+    assert abs(st["m"][0] - s1["m"]) < s1["m_tol"] and abs(st["v"][0] - s1["v"]) < s1["v_tol"] and abs(st["value"][0] - s1["value"]) < s1["value_tol"]
+    prev = st["value"][0]
+    for t in range(2, c["monotone_steps"] + 1):
+        st, _ = oracle.beta_adam_step(st, [c["grad"]], t, **cfg)
+        assert st["value"][0] > prev
+        prev = st["value"][0]
+    assert abs(st["m"][0] - c["m_after_5"]) < c["m5_tol"]
+    c = G["beta_adam_clip"]
+    a, _ = oracle.beta_adam_step(z(), [c["grad"]], 1, grad_clip=c["grad_clip"])
+    b, _ = oracle.beta_adam_step(z(), [c["same_value_as_grad"]], 1, grad_clip=c["grad_clip"])
+    assert abs(a["m"][0] - c["m"]) < 1e-6 and abs(a["v"][0] - c["v"]) < 1e-7 and abs(a["value"][0] - b["value"][0]) < c["tol"]
+    # AMSGrad keeps the running maximum of v: after a large gradient a small one moves beta less than plain Adam does
+    sa, sp_ = z(), z()
+    for t, g in enumerate([5.0, 0.1, 0.1], start=1):
+        sa, _ = oracle.beta_adam_step(sa, [g], t, amsgrad=True)
+        sp_, _ = oracle.beta_adam_step(sp_, [g], t, amsgrad=False)
+    assert sa["v_max"][0] >= sa["v"][0] and sa["value"][0] <= sp_["value"][0]
