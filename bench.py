@@ -256,7 +256,7 @@ def run_ours(args, rank, world, local_rank):
     from ny_b200 import engine as E
 
     eng.set_path(E.PATH_TF32X3 if args.path == "tf32x3" else E.PATH_F64)
-    eng._L.nyb200_set_fusion(eng._h, args.fusion)
+    eng.set_fusion(bool(args.fusion))
     eng._path_name = args.path
     wl = W.config_mlp_bab()
     nid = eng.register_network(wl.net)
@@ -269,18 +269,40 @@ def run_ours(args, rank, world, local_rank):
     # ---- resident timing ------------------------------------------------------------------
     eng.batch_upload(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, splits, ns, mode=1)
     min_t = torch.as_tensor(_DevPtr(eng.batch_min_lower_device(), 1), device=f"cuda:{local_rank}")
-    global_lb = torch.empty(1, device=f"cuda:{local_rank}")
 
     from ny_b200 import sharding
 
+    # The round's only exchange, the min-reduce of the global lower bound, runs on a second stream: the main stream
+    # copies the round's minimum into one of two slots, the side stream reduces that slot across ranks while the main
+    # stream is already in the next round's forward pass.  A slot is reused two rounds later, after the side stream's
+    # event of its previous use.
+    side = torch.cuda.Stream(device=local_rank) if dist is not None else None
+    lb_slot = [torch.empty(1, device=f"cuda:{local_rank}") for _ in range(2)]
+    lb_done = [None, None]
+    counter = {"round": 0, "late_reruns": 0}
+
     def step():
         eng.batch_run()
-        # the step ends with final bounds: domains whose rounding charge is visible would be re-evaluated with
-        # binary64 contractions here (none on this workload; the check itself reads one counter back)
-        eng.batch_refined()
-        if dist is not None:  # the round's only exchange: min-reduce of the global lower bound
-            global_lb.copy_(min_t)
-            sharding.allreduce_min(global_lb, dist)
+        # No host synchronisation per round: the run's last kernel publishes its status words to mapped host memory
+        # and the host looks at them without waiting.  A round that flagged domains for the binary64 re-evaluation
+        # (none on this workload) is seen a round or two late and re-evaluated then, inside the timed region.
+        _, attention = eng.batch_poll()
+        if attention:
+            eng.batch_refined()
+            counter["late_reruns"] += 1
+        if dist is not None:
+            i = counter["round"] & 1
+            if lb_done[i] is not None:
+                stream.wait_event(lb_done[i])
+            lb_slot[i].copy_(min_t)
+            ready = torch.cuda.Event()
+            ready.record(stream)
+            with torch.cuda.stream(side):
+                side.wait_event(ready)
+                sharding.allreduce_min(lb_slot[i], dist)
+                lb_done[i] = torch.cuda.Event()
+                lb_done[i].record(side)
+        counter["round"] += 1
 
     def barrier():
         if dist is not None:
@@ -306,6 +328,8 @@ def run_ours(args, rank, world, local_rank):
     for b in range(blocks):
         for _ in range(args.steps):
             step()
+        if b == blocks - 1:
+            eng.batch_refined()   # the last rounds' status, with a synchronisation: the region ends with final bounds
         evs[b + 1].record(stream)
     barrier()
     wall_ms = (time.perf_counter() - t0) * 1e3
@@ -349,6 +373,7 @@ def run_ours(args, rank, world, local_rank):
     h2d = splits.nbytes + ns.nbytes + wl.spec.nbytes + wl.in_lo.nbytes + wl.in_hi.nbytes + rl.nbytes + ru.nbytes
     d2h = lo.nbytes + hi.nbytes + inf.nbytes
 
+    rebalance = rebalance_exercise(dist, rank, world, f"cuda:{local_rank}", int(wl.net.n_pre)) if dist is not None else None
     per_step = block_ms / args.steps
     if dist is not None:  # max over ranks, block by block
         t = torch.tensor(per_step, device=f"cuda:{local_rank}", dtype=torch.float64)
@@ -409,13 +434,19 @@ def run_ours(args, rank, world, local_rank):
                        "l2": "per-step working set (per-domain tables 200 MB, coefficient rows 2 x 231 MB) exceeds the 126 MB L2",
                        "backward": "fused chain" if fused else "one launch per layer",
                        "feasible_domains": int((inf == 0).sum()),
-                       "domains_sent_to_binary64_rerun": int(refined)},
+                       "domains_sent_to_binary64_rerun": int(refined),
+                       "rounds_rerun_after_a_late_status": int(counter["late_reruns"]),
+                       "host_sync": "none per round (status words polled from mapped host memory); one at the end of the timed region",
+                       "exchange": ("1-float MIN all-reduce of the global lower bound per round on a second stream, "
+                                    "overlapping the next round") if world > 1 else "none (single rank)"},
             "e2e": {"value": e2e_val, "unit": UNIT, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
                     "ms_per_step": e2e_ms, "calls": len(e2e_times),
                     "ms_per_step_spread": {"min": float(np.min(e2e_times)), "max": float(np.max(e2e_times))}},
             "gpu_launches": int(launches) * int(blocks), "gpu_launches_per_block": int(launches), "clocks": clocks, "roofline": roofline,
             "wall_ms_per_step": wall_ms / (args.steps * blocks),
         }
+        if rebalance is not None:
+            line["rebalance"] = rebalance
         if world == 1 and not args.no_parity:
             line["parity"] = oracle_parity(eng, nid, wl, rl, ru, splits, ns, lo, hi, inf)
         if world == 1 and not args.no_cpu_baseline:
@@ -617,11 +648,14 @@ def run_cnn(args, local_rank, kind="cnn"):
 
 
 
-def run_search(args, local_rank):
+def run_search(args, rank, world, local_rank):
     """Secondary workload (--workload bab-search): the whole branch-and-bound loop (ny_b200/bab.py) on a seeded MLP
     64 -> 4x256 -> 10 with a property it cannot close in the given rounds, so that every round bounds a full batch:
     upload of the children's split lists, bound, download, branching choice, child creation on the host.  One step =
-    one search of `rounds` rounds; value = domains bounded per second of wall clock, host work included."""
+    one search of `rounds` rounds; value = domains bounded per second of wall clock, host work included.
+    With N > 1 ranks (one process per GPU) every rank bounds its own shard of the frontier, `batch` domains per rank
+    and round; the root's children start on rank 0, so the first rounds exercise the point-to-point rebalancing (split
+    records, and the warm-start slopes when the search optimises), whose traffic the line reports."""
     import torch
 
     from ny_b200 import B200Engine, bab, formats
@@ -629,6 +663,13 @@ def run_search(args, local_rank):
     from ny_b200 import workloads as W
 
     torch.cuda.set_device(local_rank)
+    dist = None
+    dev = f"cuda:{local_rank}"
+    if world > 1:
+        import torch.distributed as dist_mod
+
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     eng = B200Engine(local_rank, torch.cuda.current_stream().cuda_stream)
     eng.set_path(E.PATH_TF32X3 if args.path == "tf32x3" else E.PATH_F64)
     wl = W.config_mlp_bab(seed=7, hidden=256, depth=4, n_in=64, n_out=10, eps=0.05, n_fix=0)
@@ -638,39 +679,89 @@ def run_search(args, local_rank):
     prop = formats.Property(wl.in_lo, wl.in_hi, [[formats.Atom(-wl.spec[s], float(root[0][s] + 0.5 * abs(root[0][s]) + 0.5))]])
     batch = args.domains if args.domains != D_PER_GPU else 4096
     rounds = 40
+    opt_it = args.search_iterations
 
     def search():
-        return bab.verify(eng, nid, wl.net, prop, batch=batch, max_rounds=rounds, optimize_iterations=0, branching=1,
-                          pgd_restarts=64, pgd_steps=10)
+        return bab.verify(eng, nid, wl.net, prop, batch=batch, max_rounds=rounds, optimize_iterations=opt_it, branching=1,
+                          pgd_restarts=64, pgd_steps=10, dist=dist, dist_device=dev)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
 
     for _ in range(max(args.warmup, 3)):
         r = search()
     sampler = ClockSampler(local_rank)
     sampler.start()
     l0 = eng.launch_count()
-    torch.cuda.synchronize()
+    barrier()
     t0 = time.perf_counter()
     bounded = 0
+    moved = {"exchanges": 0, "records_moved": 0, "bytes_moved": 0}
     for _ in range(args.steps):
         r = search()
-        bounded += r.domains_bounded
-    torch.cuda.synchronize()
+        bounded += r.domains_bounded          # already the sum over ranks
+        for k in moved:
+            moved[k] += (r.exchange or {}).get(k, 0)
+    barrier()
     dt = time.perf_counter() - t0
     launches = eng.launch_count() - l0
     clocks = sampler.stop()
+    if dist is not None:
+        t = torch.tensor([dt], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dt = float(t[0])
+        t = torch.tensor([moved["exchanges"], moved["records_moved"], moved["bytes_moved"], launches], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        # every move is counted by its sender and by its receiver; an exchange by every rank
+        moved = {"exchanges": int(t[0]) // world, "records_moved": int(t[1]) // 2, "bytes_moved": int(t[2]) // 2}
+        launches = int(t[3])
     value = bounded / dt
-    _emit({
-        "metric": "BaB domains bounded/sec (beta-CROWN), whole search loop", "value": value, "unit": UNIT, "n_gpus": 1,
-        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": dt * 1e3 / args.steps, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": args.path, "data": "synthetic",
-        "config": {"workload": f"branch and bound on a ReLU MLP 64->4x256->10, box x0+-0.05, one property row, {rounds} rounds "
-                               f"of up to {batch} domains, intercept branching, one bound per domain, attack and root bound included",
-                   "timing": "wall clock around the search calls", "status": r.status, "domains_per_search": r.domains_bounded,
-                   "open_at_stop": r.open_domains},
-        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": None, "d2h_bytes_per_step": None, "ms_per_step": dt * 1e3 / args.steps},
-        "gpu_launches": int(launches), "clocks": clocks,
-    })
+    if rank == 0:
+        _emit({
+            "metric": "BaB domains bounded/sec (beta-CROWN), whole search loop", "value": value, "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": dt * 1e3 / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": args.path, "data": "synthetic",
+            "config": {"workload": f"branch and bound on a ReLU MLP 64->4x256->10, box x0+-0.05, one property row, {rounds} rounds "
+                                   f"of up to {batch} domains per GPU, intercept branching, "
+                                   + (f"{opt_it} optimisation iterations per domain with warm start" if opt_it > 1 else "one bound per domain")
+                                   + ", attack and root bound included",
+                       "parallelism": f"frontier sharded x{world}",
+                       "timing": "wall clock around the search calls, max over ranks", "status": r.status,
+                       "domains_per_search": r.domains_bounded, "open_at_stop": r.open_domains},
+            "rebalance": moved if world > 1 else None,
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": None, "d2h_bytes_per_step": None, "ms_per_step": dt * 1e3 / args.steps},
+            "gpu_launches": int(launches), "clocks": clocks,
+        })
     eng.close()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def rebalance_exercise(dist, rank, world, device, n_pre):
+    """Untimed proof that the exchange runs on this hardware: rank r holds 64 * (r + 1) synthetic domain records with
+    their slopes, the ranks level them point to point over NCCL, and every rank checks that the slopes it ends up
+    with still belong to their records."""
+    import torch
+
+    from ny_b200 import SPLIT_DTYPE, sharding
+
+    n_local, depth = 64 * (rank + 1), 8
+    splits = np.zeros((n_local, depth), SPLIT_DTYPE)
+    splits["neuron"] = (rank << 20) + np.arange(n_local)[:, None]
+    ns = np.full(n_local, depth, np.int32)
+    alpha = np.tile(((rank << 20) + np.arange(n_local)).astype(np.float32)[:, None], (1, n_pre))
+    stats = {}
+    before = sharding.gather_counts(n_local, dist, device)
+    splits, ns, alpha = sharding.exchange_domains(splits, ns, dist, device, alpha=alpha, stats=stats, counts=before)
+    after = sharding.gather_counts(len(ns), dist, device)
+    intact = bool(np.array_equal(splits["neuron"][:, 0].astype(np.float32), alpha[:, 0]) and np.all(alpha == alpha[:, :1]))
+    t = torch.tensor([stats.get("records_moved", 0), stats.get("bytes_moved", 0), 1 if intact else 0], device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return {"counts_before": before, "counts_after": after, "records_moved": int(t[0]) // 2, "bytes_moved": int(t[1]) // 2,
+            "slopes_travel_with_records": int(t[2]) == world, "transport": "torch.distributed send/recv over NCCL, untimed"}
+
 
 def run_pgd(args, local_rank, kind="cnn"):
     """Secondary workload (--workload pgd): PGD attack, 100 steps x 1024 restarts, step 0.25 * eps, margin loss,
@@ -755,10 +846,12 @@ def main():
     ap.add_argument("--blocks", type=int, default=30, help="back-to-back repetitions of the timed --steps block")
     ap.add_argument("--ref-sample", type=int, default=D_PER_GPU, help="domains per step of the reference arm")
     ap.add_argument("--cpu-sample", type=int, default=D_PER_GPU, help="domains of the cpu_baseline leg")
-    ap.add_argument("--fusion", type=int, default=1, help="0: one launch per layer; 1: fused backward chain (default); 2: fused, two epilogue warps per lane quarter")
+    ap.add_argument("--fusion", type=int, default=1, help="0: one launch per layer; 1: fused backward chain (default)")
     ap.add_argument("--workload", default="bab", choices=["bab", "alpha-crown", "cnn", "resnet", "pgd", "pgd-resnet", "bab-search"],
                     help="bab: the headline beta-CROWN batch (default); alpha-crown: the alpha optimisation case; "
                          "cnn: the convolutional case (both 1 GPU)")
+    ap.add_argument("--search-iterations", type=int, default=0,
+                    help="bab-search: optimisation iterations per domain (0 = one bound per domain, the reference's throughput default)")
     ap.add_argument("--domains", type=int, default=D_PER_GPU, help="domains per GPU (profiling runs use a smaller batch)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -772,8 +865,7 @@ def main():
             run_alpha_crown(args, 0, 1, local_rank)
         return
     if args.workload == "bab-search":
-        if rank == 0:
-            run_search(args, local_rank)
+        run_search(args, rank, world, local_rank)
         return
     if args.workload in ("pgd", "pgd-resnet"):
         if rank == 0:

@@ -79,6 +79,15 @@ int32_t nyb200_set_fusion(nyb200_engine *e, int32_t on);
  * nyb200_batch_refined reports how many domains of the last run triggered it (0 = fast path only). */
 int32_t nyb200_set_refine_tolerance(nyb200_engine *e, float tol);
 int32_t nyb200_batch_refined(nyb200_engine *e, int32_t *n_domains);
+/* Non-blocking look at the runs launched so far (no counterpart in the reference, whose calls return finished
+ * results): every nyb200_batch_run ends with a one-thread kernel that publishes, to mapped host memory, the run's
+ * sequence number, the tensor pipeline's error word and the number of domains flagged for the binary64 re-run.
+ * *completed = 1 when the newest run has finished on the device; *attention = 1 when any run since the last
+ * finishing call (download, nyb200_batch_refined, ...) flagged a domain - the caller then calls
+ * nyb200_batch_refined, which synchronises and re-evaluates; a latched pipeline error is returned as
+ * NYB200_ERR_INTERNAL.  A resident loop that launches round after round calls this instead of synchronising each
+ * round and learns of a flagged round one or two rounds late, never not at all. */
+int32_t nyb200_batch_poll(nyb200_engine *e, int32_t *completed, int32_t *attention);
 /* Number of kernels this engine has launched since creation (bench bookkeeping). */
 int64_t nyb200_launch_count(const nyb200_engine *e);
 /* GpuCrownBackward::clear_crown_working_set (crates/ny-core/src/gemm.rs:3205). */
@@ -370,6 +379,86 @@ int32_t nyb200_batch_gradient(nyb200_engine *e, int32_t objective, float *grad);
  * receives spec_rows[k] . f(x_k).  Attack-only arithmetic: it never enters a bound. */
 int32_t nyb200_point_vjp_batched(nyb200_engine *e, int32_t net_id, int32_t K, const float *x, const float *masks,
                                  const float *spec_rows, float *grads, float *values);
+
+/* ---- reference-shaped calls ------------------------------------------------------------------------
+ * The operands of ny's own trait methods, for a binding that wants a drop-in without touching its caller: layer
+ * lists in BACKWARD order (output -> input; crates/ny-cuda/src/sound_crown.rs:1159-1260 walks them that way), whose
+ * Activation members carry relaxation slopes the CALLER baked.  The split-list calls above derive the relaxation
+ * on the device from 128 bytes per domain and are the fast route; these take about 24 bytes per neuron per domain
+ * through host memory and exist for parity with the reference's interface.  Supported members: Linear and
+ * Activation (GpuCrownLayer::{Linear, Activation, ActivationReluDualAlpha with equal slopes},
+ * crates/ny-core/src/gemm.rs:1524-1645), strictly alternating; Conv2d / MaxPool2d members and Residual segments are
+ * declined with NYB200_ERR_UNSUPPORTED (the trait's "decline -> CPU fallback"), never approximated. */
+#define NYB200_CROWN_LINEAR 0
+#define NYB200_CROWN_ACTIVATION 1
+#define NYB200_CROWN_CONV2D 2
+#define NYB200_CROWN_RELU_DUAL_ALPHA 3
+typedef struct nyb200_crown_layer {
+    int32_t kind;
+    /* Linear: weight [out_features x in_features] row-major, bias [out_features] or NULL */
+    const float *weight, *bias;
+    int32_t out_features, in_features;
+    /* Activation: per-neuron relaxation, [num_neurons] each (lower_intercept may be NULL = zeros).
+     * ActivationReluDualAlpha: lower_slope = lower_pos_slope, upper_slope = cross_slope,
+     * upper_intercept = cross_intercept, upper_neg_slope as named. */
+    const float *lower_slope, *upper_slope, *lower_intercept, *upper_intercept, *upper_neg_slope;
+    int32_t num_neurons;
+} nyb200_crown_layer;
+/* GpuCrownSeed (gemm.rs:1684-1691): an asymmetric frontier that starts the pass mid-network. */
+typedef struct nyb200_crown_seed {
+    const float *lower_a, *upper_a; /* [num_specs x current_dim] */
+    const float *lower_b, *upper_b; /* [num_specs] or NULL (zeros) */
+    int32_t num_specs, current_dim;
+} nyb200_crown_seed;
+/* GpuCrownBackward::crown_backward_gpu_sound (gemm.rs:3357) with spec [num_specs x out_features of layers[0]] and
+ * seed == NULL, or ::crown_backward_gpu_seeded_sound (gemm.rs:3387) with a seed (spec ignored; the suffix may open
+ * with the Activation behind which the frontier sits, current_dim = its num_neurons).  One input box
+ * in_lo / in_hi [in_features of the last member].  Computed in the reference's own error convention (per-coefficient
+ * error matrices carried to the box, binary64: layers/linear/crown_single.rs:2092-2103, bounds/concretize.rs:443-466),
+ * so out_lo / out_hi [num_specs] are the reference's CPU CROWN bounds for the same slopes to within 1e-4 relative. */
+int32_t nyb200_crown_backward(nyb200_engine *e, const nyb200_crown_layer *layers, int32_t n_layers, const float *spec,
+                              int32_t num_specs, const nyb200_crown_seed *seed, const float *in_lo, const float *in_hi,
+                              float *out_lo, float *out_hi);
+/* GpuResnetBatchedDomainRef (gemm.rs:2939-2952) for a network that is one Chain segment: the domain's layer list
+ * (shared weight tensors - the same pointers in every domain - and this domain's baked slopes), its input box, per
+ * Activation in fold (backward) order its signed multipliers beta * sign (beta_signed[r], [num_neurons], NULL = none)
+ * and its pre-node abs-max bounds (node_abs[r], [num_neurons]).  frontier_abs is accepted for signature parity and not
+ * read: the rounding charges are discharged against node_abs and the box.  splits / n_splits name the multipliers the
+ * _adam call optimises (GpuBetaAdamMapping, gemm.rs:2996-3012: relu = 0-based ReLU index in FORWARD order, neuron,
+ * sign); the plain call ignores them. */
+typedef struct nyb200_domain_ref {
+    const nyb200_crown_layer *layers;
+    int32_t n_layers;
+    const float *input_lower, *input_upper;
+    const float *const *beta_signed;
+    const float *const *frontier_abs;
+    const float *const *node_abs;
+    const nyb200_split *splits;
+    int32_t n_splits;
+} nyb200_domain_ref;
+/* GpuCrownBackward::crown_backward_gpu_resnet_sound_beta_batched (gemm.rs:3944): D domains, one shared spec
+ * [num_specs x output width]; out_lo / out_hi [D x num_specs].  Same kernels and arithmetic as nyb200_bab_bound_batch
+ * (tensor path with its certified rounding charge, binary64 re-evaluation when that charge shows); a heterogeneous or
+ * non-finite batch is refused as a whole (gemm.rs:3941-3943). */
+int32_t nyb200_crown_resnet_beta_batched(nyb200_engine *e, const nyb200_domain_ref *domains, int32_t D, const float *spec,
+                                         int32_t num_specs, float *out_lo, float *out_hi);
+/* GpuBetaAdamConfig (gemm.rs:2960-2993): projected-Adam ascent on the multipliers only, AMSGrad second moments,
+ * at most `iterations` bound evaluations, a domain stops when its largest |gradient| falls below `tolerance`. */
+typedef struct nyb200_beta_adam_config {
+    int32_t iterations;
+    float beta_lr, beta1, beta2, epsilon, tolerance;
+} nyb200_beta_adam_config;
+/* ::crown_backward_gpu_resnet_sound_beta_batched_adam (gemm.rs:4042): returns the element-wise best bounds over the
+ * evaluated iterates and, in out_beta [D x max_splits] (may be NULL), the final multipliers in the order of each
+ * domain's split mapping. */
+int32_t nyb200_crown_resnet_beta_batched_adam(nyb200_engine *e, const nyb200_domain_ref *domains, int32_t D, const float *spec,
+                                              int32_t num_specs, const nyb200_beta_adam_config *cfg, float *out_lo,
+                                              float *out_hi, float *out_beta, int32_t max_splits);
+/* GemmEngine::gemm_f64_triplet (gemm.rs:523): three same-shape binary64 products C_i = A_i B_i (the centre, magnitude
+ * and propagated-error products of sound CROWN, crates/ny-cuda/src/sound_crown.rs:348-376), queued on one stream and
+ * synchronised once; each obeys nyb200_gemm_f64's contract.  An operand pointer that repeats is uploaded once. */
+int32_t nyb200_gemm_f64_triplet(nyb200_engine *e, int32_t m, int32_t k, int32_t n, const double *const a[3],
+                                const double *const b[3], double *const c_out[3]);
 
 /* ---- interval forward pass of ONE box without any device allocation ------------------------------
  * No counterpart in the reference: an addition for hosts that cannot let a library allocate device

@@ -34,6 +34,7 @@ class VerifyResult:
     domains_bounded: int = 0
     open_domains: int = 0
     root_lower: np.ndarray | None = None
+    exchange: dict | None = None     # multi-rank runs: this rank's rebalancing traffic (exchanges, records_moved, bytes_moved)
 
 
 def _rows(prop: Property):
@@ -326,6 +327,7 @@ def verify(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: i
     metrics = _Metrics(metrics_jsonl if rank == 0 else None)
     n_pre = int(net.n_pre)
     frontier = Frontier(n_pre)
+    exchange = {"exchanges": 0, "records_moved": 0, "bytes_moved": 0} if world > 1 else None
     res = VerifyResult("unknown")
     root = {"status": "unknown", "inh": None}
     if rank == 0:
@@ -363,6 +365,7 @@ def verify(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: i
 
     def stop(status):
         res.status = status
+        res.exchange = exchange
         res.open_domains = len(frontier)
         if checkpoint is not None and len(frontier) and world == 1:
             save_frontier(checkpoint, frontier.as_list(), inh_lo, inh_hi, prop, res.rounds, res.domains_bounded)
@@ -388,7 +391,7 @@ def verify(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: i
     while total_open > 0 and res.rounds < max_rounds:
         flag = TIMEOUT if (timeout_s is not None and time.time() - t0 > timeout_s) else 0
         if world > 1:   # level the shards before the round (also hands the root's first children around)
-            _rebalance(frontier, dist, dist_device, sharding)
+            _rebalance(frontier, dist, dist_device, sharding, exchange)
         splits, ns, alpha0 = frontier.pop(batch)
         D = len(ns)
         min_lower, n_done, n_inf = float("inf"), 0, 0
@@ -442,19 +445,34 @@ def verify(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: i
     return stop("verified" if total_open == 0 else "unknown")
 
 
-def _rebalance(frontier: "Frontier", dist, device, sharding):
-    """Levels the ranks' shards: the histories are padded to the deepest one of any rank, then moved point to point."""
+def _rebalance(frontier: "Frontier", dist, device, sharding, stats=None):
+    """Levels the ranks' shards.  The shard sizes are gathered first and nothing else happens while they are level;
+    otherwise the histories are padded to the deepest one of any rank and moved point to point, the warm-start
+    slopes with them when every rank holds slopes for all of its open domains."""
     import torch
 
-    splits, ns = frontier.arrays()
-    depth = torch.tensor([splits.shape[1]], dtype=torch.int64, device=device)
-    dist.all_reduce(depth, op=dist.ReduceOp.MAX)
-    if int(depth.item()) > splits.shape[1]:
-        grown = np.zeros((len(ns), int(depth.item())), SPLIT_DTYPE)
+    counts = sharding.gather_counts(len(frontier), dist, device)
+    if not sharding.plan_rebalance(counts):
+        return
+    splits, ns, alpha = frontier.pop(len(frontier))
+    meta = torch.tensor([splits.shape[1], 1 if (alpha is not None or len(ns) == 0) else 0], dtype=torch.int64, device=device)
+    agreed = [torch.zeros(2, dtype=torch.int64, device=device) for _ in range(dist.get_world_size())]
+    dist.all_gather(agreed, meta)
+    depth = max(int(t[0].item()) for t in agreed)
+    # a rank with an empty shard holds no slopes to disagree about; one with domains but no slopes vetoes
+    with_alpha = frontier.n_pre > 0 and all(int(t[1].item()) for t in agreed)
+    if depth > splits.shape[1]:
+        grown = np.zeros((len(ns), depth), SPLIT_DTYPE)
         grown[:, : splits.shape[1]] = splits
         splits = grown
-    splits, ns = sharding.exchange_domains(splits, ns, dist, device)
-    frontier.push(splits, ns)
+    if with_alpha:
+        if alpha is None:
+            alpha = np.zeros((0, frontier.n_pre), np.float32)
+        splits, ns, alpha = sharding.exchange_domains(splits, ns, dist, device, alpha=alpha, stats=stats, counts=counts)
+        frontier.push(splits, ns, alpha)
+    else:
+        splits, ns = sharding.exchange_domains(splits, ns, dist, device, stats=stats, counts=counts)
+        frontier.push(splits, ns)
 
 
 def verify_root(eng, net_id, net, prop: Property, method: str = "crown") -> VerifyResult:

@@ -80,6 +80,7 @@ void nyb200_destroy(nyb200_engine *e) {
     cudaStreamSynchronize(e->stream);
     for (auto &kv : e->ws) if (kv.second.p) cudaFree(kv.second.p);
     for (auto &kv : e->nets) free_net(kv.second);
+    if (e->status_host) cudaFreeHost(e->status_host);
     for (int i = 0; i < 3; ++i) if (e->timing.ev[i]) cudaEventDestroy(e->timing.ev[i]);
     for (cudaEvent_t ev : e->timing.kev) cudaEventDestroy(ev);
     for (int i = 0; i < 2; ++i) if (e->timing.cev[i]) cudaEventDestroy(e->timing.cev[i]);
@@ -113,6 +114,12 @@ int32_t nyb200_clear_working_set(nyb200_engine *e) {
     for (auto &kv : e->ws) if (kv.second.p) cudaFree(kv.second.p);
     e->ws.clear();
     e->batch = Batch();
+    // networks registered on behalf of the reference-shaped calls (their weight cache)
+    for (auto &kv : e->boundary_nets) {
+        auto it = e->nets.find(kv.second);
+        if (it != e->nets.end()) { free_net(it->second); e->nets.erase(it); }
+    }
+    e->boundary_nets.clear();
     return NYB200_OK;
 }
 
@@ -123,8 +130,12 @@ static void expand_bias(const float *b, int oc, int plane, std::vector<float> &o
         for (int i = 0; i < plane; ++i) out[(size_t)c * plane + i] = b[c];
 }
 
-static int create_net(nyb200_engine *e, int32_t n_layers, const nyb200_layer_desc *ld, const float *wflat,
-                      const float *bflat, int32_t *net_id) {
+}  // extern "C"
+
+namespace nyb {
+
+int create_net(nyb200_engine *e, int32_t n_layers, const nyb200_layer_desc *ld, const float *wflat,
+               const float *bflat, int32_t *net_id) {
     if (n_layers < 1 || n_layers > kMaxLinear) return set_err(e, NYB200_ERR_UNSUPPORTED, "layer count out of range");
     NYB_CUDA(e, cudaSetDevice(e->device));
     Net net;
@@ -211,6 +222,10 @@ static int create_net(nyb200_engine *e, int32_t n_layers, const nyb200_layer_des
     *net_id = id;
     return NYB200_OK;
 }
+
+}  // namespace nyb
+
+extern "C" {
 
 int32_t nyb200_net_create(nyb200_engine *e, int32_t n_linear, const int32_t *dims, const float *wflat,
                           const float *bflat, const int32_t *has_bias, int32_t *net_id) {
@@ -613,8 +628,31 @@ int upload_batch(nyb200_engine *e, int32_t net_id, const float *spec, int32_t S,
     return NYB200_OK;
 }
 
+// Last kernel of a batch run: folds the run's pipeline error word and flagged-domain count into the engine's sticky
+// accumulators and publishes them, then the run's sequence number, to mapped host memory (writes only: the device
+// never reads across the bus).
+__global__ void k_publish_status(const int *__restrict__ derr, const int *__restrict__ loose, int *__restrict__ acc,
+                                 volatile int *status, int seq) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    const int h = derr ? *derr : 0, l = loose ? *loose : 0;
+    if (h) acc[0] = h;
+    acc[1] += l;
+    status[1] = acc[0];
+    status[2] = acc[1];
+    __threadfence_system();
+    status[0] = seq;
+}
+
 int run_batch(nyb200_engine *e) {
     if (!e->batch.valid) return set_err(e, NYB200_ERR_INVALID, "no batch uploaded");
+    if (!e->status_host) {
+        NYB_CUDA(e, cudaHostAlloc((void **)&e->status_host, 64, cudaHostAllocMapped));
+        memset(e->status_host, 0, 64);
+        NYB_CUDA(e, cudaHostGetDevicePointer((void **)&e->status_dev, e->status_host, 0));
+        int *acc0 = (int *)ws_get(e, "status_acc", 256);
+        if (!acc0) return NYB200_ERR_OOM;
+        NYB_CUDA(e, cudaMemsetAsync(acc0, 0, 8, e->stream));
+    }
     Net *net;
     NYB_TRY(find_net(e, e->batch.net_id, &net));
     BatchPtrs p;
@@ -631,6 +669,15 @@ int run_batch(nyb200_engine *e) {
     cudaEventRecord(t.ev[1], e->stream);
     NYB_TRY(run_backward(e, *net, e->batch, p, nullptr, 0));
     cudaEventRecord(t.ev[2], e->stream);
+    {
+        const bool tensor = e->path == NYB200_PATH_TF32X3;
+        int *acc = (int *)ws_get(e, "status_acc", 256);
+        k_publish_status<<<1, 32, 0, e->stream>>>(tensor ? (const int *)ws_get(e, "umma_err", 256) : nullptr,
+                                                  tensor && e->refine_tol > 0.f ? (const int *)p.min_lower + 4 : nullptr, acc,
+                                                  e->status_dev, ++e->run_seq);
+        e->launches++;
+        NYB_CUDA(e, cudaGetLastError());
+    }
     t.pending = true;
     e->batch.ran = true;
     e->batch.finished = false;
@@ -737,6 +784,11 @@ int finish_batch(nyb200_engine *e) {
         NYB_CUDA(e, cudaMemcpyAsync(&loose, (int *)p.min_lower + 4, 4, cudaMemcpyDeviceToHost, e->stream));
     }
     NYB_CUDA(e, cudaStreamSynchronize(e->stream));
+    if (e->status_host) {  // the stream is idle: whatever earlier runs latched is handled by this call
+        int *acc = (int *)ws_get(e, "status_acc", 256);
+        if (acc) NYB_CUDA(e, cudaMemsetAsync(acc, 0, 8, e->stream));
+        e->status_host[1] = e->status_host[2] = 0;
+    }
     if (herr) return set_err(e, NYB200_ERR_INTERNAL, "tcgen05 pipeline wait expired (code " + std::to_string(herr) + ")");
     if (loose > 0 && e->path == NYB200_PATH_TF32X3 && e->refine_tol > 0.f && e->batch.optimized) {
         NYB_TRY(refine_optimized(e, *net, e->batch, p));
@@ -782,6 +834,10 @@ int download_batch(nyb200_engine *e, float *out_lo, float *out_hi, int32_t *infe
 }
 
 }  // namespace
+
+namespace nyb {
+int finish_batch_public(nyb200_engine *e) { return finish_batch(e); }
+}
 
 extern "C" {
 
@@ -964,7 +1020,6 @@ int32_t nyb200_set_fusion(nyb200_engine *e, int32_t on) {
     if (!e) return NYB200_ERR_INVALID;
     std::lock_guard<std::mutex> g(e->mu);
     e->fuse_chain = on != 0;
-    e->fuse_variant = on == 2 ? 2 : 4;
     return NYB200_OK;
 }
 
@@ -981,6 +1036,18 @@ int32_t nyb200_batch_refined(nyb200_engine *e, int32_t *n_domains) {
     NYB_CUDA(e, cudaSetDevice(e->device));
     NYB_TRY(finish_batch(e));
     *n_domains = e->batch.refined;
+    return NYB200_OK;
+}
+
+int32_t nyb200_batch_poll(nyb200_engine *e, int32_t *completed, int32_t *attention) {
+    if (!e || !completed || !attention) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    if (!e->batch.valid || !e->batch.ran || !e->status_host) return set_err(e, NYB200_ERR_INVALID, "no batch has been run");
+    const volatile int *s = e->status_host;
+    const int seq = s[0], herr = s[1], loose = s[2];
+    *completed = seq == e->run_seq ? 1 : 0;
+    *attention = (herr != 0 || loose > 0) ? 1 : 0;
+    if (herr) return set_err(e, NYB200_ERR_INTERNAL, "tcgen05 pipeline wait expired (code " + std::to_string(herr) + ")");
     return NYB200_OK;
 }
 

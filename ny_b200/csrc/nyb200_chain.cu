@@ -6,12 +6,16 @@
 // after propagate_linear, layers/linear/crown_single.rs:1931-2226, for every hidden layer in turn).
 //
 // Roles of one CTA (4 control warps + NSUB*4 epilogue warps):
-//   warp 0      streams the pre-split weight tiles Wl^T, Wh^T of every layer by TMA into a ring of four 32 KB
+//   warp 0      streams the pre-split weight tiles Wl^T, Wh^T of every layer by TMA into a ring of three 32 KB
 //               slots (K-major, 128-byte swizzle), running ahead of the tensor core across layers and tiles;
 //   warp 1      issues tcgen05.mma (M128 x N<=256 x K8, kind::tf32): per 32-wide K chunk four steps Ah*Wl and four
 //               Al*Wh into the CROSS accumulator and four Ah*Wh into the MAIN accumulator (tensor memory columns
 //               [256, 512) and [0, 256)); every chunk's commit hands its operand slots back;
 //   warp 2      allocates / frees the 512 tensor-memory columns;
+//   warp 3      stages the relaxation tables (slopes, intercept, signed multiplier; the prepared charge weights; the
+//               bias slice) of the tile's domains into a four-slot ring by 1-D bulk copies, 64 columns at a time,
+//               so that the epilogue reads them from shared memory instead of waiting on L2 (the CTA's shared
+//               memory leaves almost no L1);
 //   epilogue    thread = (row of the tile, one slice of every 32-column chunk).  When a layer's products are
 //               complete it drains its slices of both accumulators into registers (main + cross, one fp32 add),
 //               releases the accumulators, then walks its chunks: relaxation step per coefficient (the same
@@ -39,9 +43,18 @@ constexpr int BM = 128, BN = 256, BK = 32;
 constexpr int A_HALF = BM * BK * 4;   // 16 KB: the high or the low part of one operand chunk
 constexpr int A_SLOT = 2 * A_HALF;    // 32 KB
 constexpr int W_SLOT = BN * BK * 4;   // 32 KB: one of Wh / Wl for one K chunk
-constexpr int NA = 3, NW = 4;
+constexpr int NA = 2, NW = 3;
+// Table ring: the relaxation tables of the domains a tile's rows belong to, staged by bulk copies one chunk PAIR (64
+// columns) at a time.  Slot layout: 64 bias values, then per domain 64 table entries (float4), 64 charge weights and
+// 16 bytes of padding (so that the rows of different domains read different banks).
+constexpr int NT = 4;
+constexpr int MAXD = 10;                                   // domains a 128-row tile may span in the staged variant
+constexpr int T_COLS = 2 * BK;
+constexpr int T_DOM = T_COLS * 16 + T_COLS * 4 + 16;       // 1296
+constexpr int T_HEAD = T_COLS * 4;                         // 256: the bias slice
+constexpr int T_SLOT = (T_HEAD + MAXD * T_DOM + 127) & ~127;
 constexpr int BAR_BYTES = 512;
-constexpr int SMEM_BYTES = NA * A_SLOT + NW * W_SLOT + 1024 /*alignment*/ + BAR_BYTES;
+constexpr int SMEM_BYTES = NA * A_SLOT + NW * W_SLOT + NT * T_SLOT + 1024 /*alignment*/ + BAR_BYTES;
 static_assert(SMEM_BYTES <= 232448, "more than the 227 KB a CTA can opt into");
 constexpr int kMaxChain = 16;         // fused contractions per launch
 constexpr int MAX_CHUNKS = BN / BK;   // 8
@@ -70,6 +83,7 @@ struct Params {
     float top_eps;
     const float4 *tab;
     const float *zabs, *q, *aup;
+    const float *cj;     // [D x nps] per-(domain, column) charge weights prepared by k_chain_prep
     long nps;
     float *A_out;
     int lda;
@@ -113,7 +127,15 @@ struct Cfg {
     static_assert(REGS_EPI <= 255, "register target out of range");
 };
 
-template <int NSUB>
+// 1-D bulk copy global -> shared, completion counted in bytes on an mbarrier (addresses and size multiples of 16)
+__device__ __forceinline__ void bulk_load(unsigned dst, const void *src, unsigned bytes, unsigned bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+// STAGED: warp 3 brings the tables into shared memory ahead of the epilogue (tiles that span at most MAXD domains);
+// otherwise every epilogue thread loads its entries from global memory itself.
+template <int NSUB, bool STAGED>
 __global__ void __launch_bounds__(Cfg<NSUB>::THREADS, 1) k_chain(const __grid_constant__ Params P) {
     using C = Cfg<NSUB>;
     constexpr int CPT = C::CPT;
@@ -121,11 +143,13 @@ __global__ void __launch_bounds__(Cfg<NSUB>::THREADS, 1) k_chain(const __grid_co
     unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char *a_ring = smem;
     unsigned char *w_ring = smem + NA * A_SLOT;
-    unsigned long long *bars = (unsigned long long *)(w_ring + NW * W_SLOT);
+    unsigned char *t_ring = w_ring + NW * W_SLOT;
+    unsigned long long *bars = (unsigned long long *)(t_ring + NT * T_SLOT);
     const int A_FULL = 0, A_EMPTY = NA, W_FULL = 2 * NA, W_EMPTY = 2 * NA + NW, ACC_FULL = 2 * NA + 2 * NW, ACC_EMPTY = ACC_FULL + 1;
-    unsigned *tmem_slot = (unsigned *)(bars + ACC_EMPTY + 1);
+    const int T_FULL = ACC_EMPTY + 1, T_EMPTY = T_FULL + NT;
+    unsigned *tmem_slot = (unsigned *)(bars + T_EMPTY + NT);
     volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
-    static_assert((2 * NA + 2 * NW + 2) * 8 + 8 <= BAR_BYTES, "barrier block overflows its slots");
+    static_assert((2 * NA + 2 * NW + 2 + 2 * NT) * 8 + 8 <= BAR_BYTES, "barrier block overflows its slots");
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_tiles = (P.M + BM - 1) / BM;
@@ -135,6 +159,7 @@ __global__ void __launch_bounds__(Cfg<NSUB>::THREADS, 1) k_chain(const __grid_co
         for (int s = 0; s < NW; ++s) { mbar_init(smem_u32(&bars[W_FULL + s]), 1); mbar_init(smem_u32(&bars[W_EMPTY + s]), 1); }
         mbar_init(smem_u32(&bars[ACC_FULL]), 1);
         mbar_init(smem_u32(&bars[ACC_EMPTY]), C::EPI_WARPS);
+        for (int s = 0; s < NT; ++s) { mbar_init(smem_u32(&bars[T_FULL + s]), 1); mbar_init(smem_u32(&bars[T_EMPTY + s]), C::EPI_WARPS); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -223,13 +248,40 @@ __global__ void __launch_bounds__(Cfg<NSUB>::THREADS, 1) k_chain(const __grid_co
                     if (!failed) mma_commit(smem_u32(&bars[ACC_FULL]));
                 }
             }
+        } else if (STAGED && warp == 3 && lane == 0) {
+            // ------------------------------------------------------------ table producer (bulk copies)
+            unsigned tit = 0;
+            bool failed = false;
+            for (int t = blockIdx.x; t < n_tiles && !failed && !*abort_flag; t += gridDim.x) {
+                const long m0 = (long)t * BM;
+                const long m1 = (m0 + BM < (long)P.M ? m0 + BM : (long)P.M) - 1;
+                const int d0 = (int)(m0 / P.R), nd = (int)(m1 / P.R) - d0 + 1;
+                for (int l = 0; l < P.n_layers && !failed; ++l) {
+                    const Layer &Ly = P.layer[l];
+                    const int nch = (Ly.N + BK - 1) / BK;
+                    for (int c2 = 0; c2 < nch; c2 += 2, ++tit) {
+                        const int s = tit % NT;
+                        if (!mbar_wait(smem_u32(&bars[T_EMPTY + s]), ((tit / NT) & 1) ^ 1)) { atomicExch(P.err, 16); *abort_flag = 1; failed = true; break; }
+                        const int w = Ly.N - c2 * BK < T_COLS ? Ly.N - c2 * BK : T_COLS;   // a multiple of 4
+                        const unsigned bar = smem_u32(&bars[T_FULL + s]);
+                        mbar_expect_tx(bar, (unsigned)((Ly.bias ? w * 4 : 0) + nd * w * 20));
+                        const unsigned dst = smem_u32(t_ring + s * T_SLOT);
+                        if (Ly.bias) bulk_load(dst, Ly.bias + c2 * BK, (unsigned)(w * 4), bar);
+                        for (int dd = 0; dd < nd; ++dd) {
+                            const long idx = (long)(d0 + dd) * P.nps + Ly.relu_off + c2 * BK;
+                            bulk_load(dst + T_HEAD + dd * T_DOM, P.tab + idx, (unsigned)(w * 16), bar);
+                            bulk_load(dst + T_HEAD + dd * T_DOM + T_COLS * 16, P.cj + idx, (unsigned)(w * 4), bar);
+                        }
+                    }
+                }
+            }
         }
     } else {
         // ---------------------------------------------------------------- epilogue
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(C::REGS_EPI));
         const int qd = warp & 3, sub = (warp - 4) >> 2;
         const int r = qd * 32 + lane;  // row of the tile = tensor-memory lane
-        unsigned ait = 0, lit = 0;
+        unsigned ait = 0, lit = 0, tit = 0;
         bool dead = false;
         // Writes the thread's CPT columns of chunk `c` (values v, already relaxed) as TF32 high / low parts into ring
         // slot `sa`: row r, 16-byte unit u at position u ^ (r & 7) of the row's 128 bytes.
@@ -264,33 +316,35 @@ __global__ void __launch_bounds__(Cfg<NSUB>::THREADS, 1) k_chain(const __grid_co
             const long m = (long)t * BM + r;
             const bool live = m < P.M;
             const int d = live ? (int)(m / P.R) : 0;
+            const int dd = live ? d - (int)(((long)t * BM) / P.R) : 0;   // the row's domain among the tile's domains
             const int rr = live ? (int)(m - (long)d * P.R) : 0;
             const bool upper = rr >= P.S;
             double sb = 0.0;      // bias of the row (this thread's columns)
             float spt = 0.f;      // rounding penalty and bias magnitude share, rounded upwards
+            const int dir = upper ? 1 : -1;
+            const float dirf = upper ? 1.f : -1.f;
             // ---- seed rows and the identity pass in front of the first contraction
             {
                 const int kc = (P.K_top + BK - 1) / BK;
                 const float *srow = P.spec + (long)(rr % P.S) * P.K_top;
-                const float *qrow = P.q + (long)d * P.top_q_ds + P.top_off;
+                const float *crow = P.cj + (long)d * P.nps + P.top_off;
                 for (int c = 0; c < kc && !dead; ++c, ++ait) {
                     if (!wait_slot(21)) break;
                     float v[CPT];
-                    float sa_ = 0.f, sp_ = 0.f;
+                    float sp_ = 0.f, gb = 0.f;
 #pragma unroll
                     for (int j = 0; j < CPT; ++j) {
                         const int col = c * BK + sub * CPT + j;
                         float a = 0.f;
-                        if (live && col < P.K_top) a = P.seed_identity ? ((rr % P.S) == col ? 1.f : 0.f) : srow[col];
                         if (live && col < P.K_top) {
-                            const float qv = qrow[col];
-                            const float4 z4 = make_float4(0.f, 0.f, 0.f, 0.f);
-                            if (P.top_bias) a = relax_coeff<false, true>(upper, a, z4, 0.f, 0.f, qv, P.top_bias[col], P.top_eps, sb, sa_, sp_);
-                            else a = relax_coeff<false, false>(upper, a, z4, 0.f, 0.f, qv, 0.f, P.top_eps, sb, sa_, sp_);
+                            a = P.seed_identity ? ((rr % P.S) == col ? 1.f : 0.f) : srow[col];
+                            if (P.top_bias) gb = fmaf(a, P.top_bias[col], gb);
+                            sp_ = __fmaf_ru(fabsf(a), crow[col], sp_);
                         }
                         v[j] = a;
                     }
-                    spt = __fadd_ru(spt, __fmaf_ru(sa_, 9.1e-13f, sp_));
+                    sb += (double)gb;
+                    spt = __fadd_ru(spt, sp_);
                     put_chunk(ait % NA, v);
                     publish(ait % NA);
                 }
@@ -323,54 +377,76 @@ __global__ void __launch_bounds__(Cfg<NSUB>::THREADS, 1) k_chain(const __grid_co
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&bars[ACC_EMPTY]));
-                // ---- relaxation, row sums, split, hand-over.  One pass of the loop handles the thread's slice of one
-                // chunk, always out of acc[0 .. CPT); the register array is then shifted down by one slice, so that the
-                // loop body exists once (unrolled eight times it does not fit the instruction cache).
+                // ---- relaxation, row sums, split, hand-over.  One pass of the loop handles the thread's slices of two
+                // chunks, always out of acc[0 .. 2 CPT); the register array is then shifted down by two slices, so that
+                // the loop body exists once (unrolled over all chunks it does not fit the instruction cache).
                 const long tb = (long)d * P.nps + Ly.relu_off;
-                const float *qrow = P.q + (long)d * Ly.q_ds + Ly.relu_off;
                 const bool has_bias = Ly.bias != nullptr;
-                const float eps = Ly.eps;
 #pragma unroll 1
-                for (int c = 0; c < nch && !dead; ++c) {
-                    float v[CPT];
-                    float sa_ = 0.f, sp_ = 0.f, gi = 0.f, gb = 0.f;
-#pragma unroll
-                    for (int g = 0; g < CPT / 4; ++g) {
-                        const int col = c * BK + sub * CPT + 4 * g;
-                        float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-                        if (live && col < N) {
-                            const float4 t0 = P.tab[tb + col], t1 = P.tab[tb + col + 1], t2 = P.tab[tb + col + 2], t3 = P.tab[tb + col + 3];
-                            const float4 za = *(const float4 *)(P.zabs + tb + col);
-                            const float4 qv = *(const float4 *)(qrow + col);
-                            float4 bk = make_float4(0.f, 0.f, 0.f, 0.f);
-                            if (has_bias) bk = *(const float4 *)(Ly.bias + col);
-                            float4 au = make_float4(t0.x, t1.x, t2.x, t3.x);
-                            if (P.aup) au = *(const float4 *)(P.aup + tb + col);
-                            constexpr float kGap = 1.9073487e-7f;  // 1.6 * 2^-23
-                            const float c0 = __fmaf_ru(kGap, za.x, __fmul_ru(eps, qv.x)), c1 = __fmaf_ru(kGap, za.y, __fmul_ru(eps, qv.y));
-                            const float c2 = __fmaf_ru(kGap, za.z, __fmul_ru(eps, qv.z)), c3 = __fmaf_ru(kGap, za.w, __fmul_ru(eps, qv.w));
-                            o.x = relax_coeff_fast(upper, acc[4 * g], t0, au.x, c0, za.x, bk.x, gi, gb, sa_, sp_);
-                            o.y = relax_coeff_fast(upper, acc[4 * g + 1], t1, au.y, c1, za.y, bk.y, gi, gb, sa_, sp_);
-                            o.z = relax_coeff_fast(upper, acc[4 * g + 2], t2, au.z, c2, za.z, bk.z, gi, gb, sa_, sp_);
-                            o.w = relax_coeff_fast(upper, acc[4 * g + 3], t3, au.w, c3, za.w, bk.w, gi, gb, sa_, sp_);
-                            if (Ly.to_global) *(float4 *)(P.A_out + m * P.lda + col) = o;
-                        }
-                        v[4 * g] = o.x; v[4 * g + 1] = o.y; v[4 * g + 2] = o.z; v[4 * g + 3] = o.w;
+                for (int c2 = 0; c2 < nch && !dead; c2 += 2) {
+                    const unsigned char *ts = nullptr;
+                    int tslot = 0;
+                    if constexpr (STAGED) {
+                        tslot = tit % NT;
+                        bool tok = mbar_wait(smem_u32(&bars[T_FULL + tslot]), (tit / NT) & 1);
+                        tok = __all_sync(0xffffffffu, tok);
+                        if (!tok) { if (lane == 0) { atomicExch(P.err, 24); *abort_flag = 1; } dead = true; break; }
+                        ts = t_ring + tslot * T_SLOT + T_HEAD + dd * T_DOM;
                     }
-                    // the two fp32 dot products of this slice join the binary64 bias; their roundings (at most CPT
-                    // fused multiply-adds each, relative to the slice's magnitude sum) and the 2^-40 share of the
-                    // binary64 additions are charged
-                    sb += (double)gi + (double)gb;
-                    spt = __fadd_ru(spt, __fmaf_ru(sa_, (float)CPT * 5.9604645e-8f * 1.0001f + 9.1e-13f, sp_));
 #pragma unroll
-                    for (int i = 0; i + CPT < C::VALS; ++i) acc[i] = acc[i + CPT];
-                    if (!Ly.to_global) {
-                        if (wait_slot(23)) {
-                            put_chunk(ait % NA, v);
-                            publish(ait % NA);
-                            ++ait;
+                    for (int h2 = 0; h2 < 2; ++h2) {
+                        const int c = c2 + h2;
+                        if (c < nch && !dead) {
+                            float v[CPT];
+                            float sp_ = 0.f, gi = 0.f, gb = 0.f;
+#pragma unroll
+                            for (int g = 0; g < CPT / 4; ++g) {
+                                const int col = c * BK + sub * CPT + 4 * g;
+                                float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+                                if (live && col < N) {
+                                    float4 t0, t1, t2, t3, cj, bk = make_float4(0.f, 0.f, 0.f, 0.f);
+                                    if constexpr (STAGED) {
+                                        const int cl = h2 * BK + sub * CPT + 4 * g;   // column inside the staged pair
+                                        const float4 *tp = (const float4 *)ts + cl;
+                                        t0 = tp[0]; t1 = tp[1]; t2 = tp[2]; t3 = tp[3];
+                                        cj = *(const float4 *)(ts + T_COLS * 16 + cl * 4);
+                                        if (has_bias) bk = *(const float4 *)(t_ring + tslot * T_SLOT + cl * 4);
+                                    } else {
+                                        t0 = P.tab[tb + col]; t1 = P.tab[tb + col + 1]; t2 = P.tab[tb + col + 2]; t3 = P.tab[tb + col + 3];
+                                        cj = *(const float4 *)(P.cj + tb + col);
+                                        if (has_bias) bk = *(const float4 *)(Ly.bias + col);
+                                    }
+                                    float4 au = make_float4(t0.x, t1.x, t2.x, t3.x);
+                                    if (P.aup) au = *(const float4 *)(P.aup + tb + col);
+                                    const float *za = P.zabs + tb + col;
+                                    const int b0 = h2 * CPT + 4 * g;
+                                    o.x = relax_coeff_fast(upper, dir, dirf, acc[b0], t0, au.x, cj.x, za, bk.x, gi, gb, sp_);
+                                    o.y = relax_coeff_fast(upper, dir, dirf, acc[b0 + 1], t1, au.y, cj.y, za + 1, bk.y, gi, gb, sp_);
+                                    o.z = relax_coeff_fast(upper, dir, dirf, acc[b0 + 2], t2, au.z, cj.z, za + 2, bk.z, gi, gb, sp_);
+                                    o.w = relax_coeff_fast(upper, dir, dirf, acc[b0 + 3], t3, au.w, cj.w, za + 3, bk.w, gi, gb, sp_);
+                                    if (Ly.to_global) *(float4 *)(P.A_out + m * P.lda + col) = o;
+                                }
+                                v[4 * g] = o.x; v[4 * g + 1] = o.y; v[4 * g + 2] = o.z; v[4 * g + 3] = o.w;
+                            }
+                            // the two fp32 dot products of this slice join the binary64 bias (their roundings are part of cj)
+                            sb += (double)gi + (double)gb;
+                            spt = __fadd_ru(spt, sp_);
+                            if (!Ly.to_global) {
+                                if (wait_slot(23)) {
+                                    put_chunk(ait % NA, v);
+                                    publish(ait % NA);
+                                    ++ait;
+                                }
+                            }
                         }
                     }
+                    if constexpr (STAGED) {   // the pair's tables are consumed: the slot goes back to the producer
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(smem_u32(&bars[T_EMPTY + tslot]));
+                        ++tit;
+                    }
+#pragma unroll
+                    for (int i = 0; i + 2 * CPT < C::VALS; ++i) acc[i] = acc[i + 2 * CPT];
                 }
             }
             if (dead) break;
@@ -387,6 +463,27 @@ __global__ void __launch_bounds__(Cfg<NSUB>::THREADS, 1) k_chain(const __grid_co
     if (warp == 2) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
     }
+}
+
+// Charge weights of the fused relaxation, one per (domain, column) of every fused layer and of the identity pass in
+// front of the first contraction (see relax_coeff_fast): cj = eps * q + (gap + kappa) * max|z| + kappa * |bias|, all
+// rounded upwards.  `ent` describes the blocks: offset and width inside a table row, q's per-domain stride, the bias,
+// the contraction's rounding rate and whether the block is a ReLU (gap and intercept terms apply) or the top block.
+struct PrepBlock { int off, n, relu; long q_ds; const float *bias; float eps; };
+struct PrepParams { int n_blocks; PrepBlock blk[kMaxChain + 1]; };
+__global__ void k_chain_prep(const __grid_constant__ PrepParams PP, int D, long nps, const float *__restrict__ zabs,
+                             const float *__restrict__ q, float kappa, float *__restrict__ cj) {
+    const int bi = blockIdx.y;
+    const PrepBlock &B = PP.blk[bi];
+    long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= (long)D * B.n) return;
+    const int d = (int)(t / B.n), j = (int)(t % B.n);
+    const long o = (long)d * nps + B.off + j;
+    const float qv = q[(long)d * B.q_ds + B.off + j];
+    float c = __fmul_ru(B.eps, qv);
+    if (B.bias) c = __fmaf_ru(kappa, fabsf(B.bias[j]), c);
+    if (B.relu) c = __fmaf_ru(1.9073487e-7f /* 1.6 * 2^-23 */ + kappa * 1.001f, zabs[o], c);
+    cj[o] = c;
 }
 
 }  // namespace chain
@@ -433,7 +530,11 @@ int launch_chain(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int L
     P.top_off = nv.pre_off[L - 1];
     P.top_q_ds = nv.nps;
     P.top_eps = (float)(chain_eps(nv.dims[L]) * 1.000001 * 1.0000002);
-    P.tab = p.tab; P.zabs = p.zabs; P.q = p.q; P.aup = p.alpha_up; P.nps = nv.nps;
+    NYB_WS(cj, float *, e, "chain_cj", (size_t)b.D * nv.nps * 4);
+    P.tab = p.tab; P.zabs = p.zabs; P.q = p.q; P.aup = p.alpha_up; P.nps = nv.nps; P.cj = cj;
+    PrepParams PP;
+    memset(&PP, 0, sizeof(PP));
+    int max_n = nv.dims[L];
     P.A_out = A_out; P.lda = p.lda; P.rb = p.rb; P.rpen = p.rpen; P.err = derr;
     for (int l = 0; l < L - 1; ++l) {
         const int k = L - 1 - l;  // contraction with W_k: K = dims[k + 1], N = dims[k]; then ReLU k-1 and the charges of lin k-1
@@ -447,6 +548,22 @@ int launch_chain(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int L
         const double eps = (k - 1 >= 1) ? chain_eps(nv.dims[k]) * 1.000001 : eps0;
         Ly.eps = (float)(eps * 1.0000002);
         Ly.to_global = (k == 1) ? 1 : 0;
+        PrepBlock &B = PP.blk[l];
+        B.off = Ly.relu_off; B.n = Ly.N; B.relu = 1; B.q_ds = Ly.q_ds; B.bias = Ly.bias; B.eps = Ly.eps;
+        max_n = Ly.N > max_n ? Ly.N : max_n;
+    }
+    {
+        PrepBlock &B = PP.blk[L - 1];  // the identity pass in front of the first contraction
+        B.off = P.top_off; B.n = P.K_top; B.relu = 0; B.q_ds = P.top_q_ds; B.bias = P.top_bias; B.eps = P.top_eps;
+        PP.n_blocks = L;
+    }
+    // kappa: the fp32 dot products run over at most 8 columns per slice (CPT of the narrowest epilogue slice is 8, of the
+    // widest 16: charge the widest), plus the 2^-40 share of the binary64 additions
+    const float kappa = 16.f * 5.9604645e-8f * 1.001f + 9.1e-13f;
+    {
+        dim3 grid((unsigned)(((long)b.D * max_n + 255) / 256), (unsigned)PP.n_blocks);
+        k_chain_prep<<<grid, 256, 0, e->stream>>>(PP, b.D, (long)nv.nps, p.zabs, p.q, kappa, cj);
+        e->launches++;
     }
     static std::mutex attr_mu;
     static bool attr_set[64] = {false};
@@ -454,8 +571,8 @@ int launch_chain(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int L
         std::lock_guard<std::mutex> g(attr_mu);
         const int dev = (e->device >= 0 && e->device < 64) ? e->device : 0;
         if (!attr_set[dev]) {
-            if (cudaFuncSetAttribute(k_chain<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess ||
-                cudaFuncSetAttribute(k_chain<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+            if (cudaFuncSetAttribute(k_chain<4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess ||
+                cudaFuncSetAttribute(k_chain<4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
                 return set_err(e, NYB200_ERR_INTERNAL, "cannot raise the dynamic shared-memory limit");
             attr_set[dev] = true;
         }
@@ -464,8 +581,10 @@ int launch_chain(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int L
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, e->device);
     const int tiles = (P.M + BM - 1) / BM;
     const int grid = tiles < sms ? tiles : sms;
-    if (e->fuse_variant == 2) k_chain<2><<<grid, Cfg<2>::THREADS, SMEM_BYTES, e->stream>>>(P);
-    else k_chain<4><<<grid, Cfg<4>::THREADS, SMEM_BYTES, e->stream>>>(P);
+    // a 128-row tile spans at most (BM - 2) / R + 2 domains; the table ring holds MAXD of them
+    const bool staged = (BM - 2) / b.R + 2 <= MAXD;
+    if (staged) k_chain<4, true><<<grid, Cfg<4>::THREADS, SMEM_BYTES, e->stream>>>(P);
+    else k_chain<4, false><<<grid, Cfg<4>::THREADS, SMEM_BYTES, e->stream>>>(P);
     e->launches++;
     return NYB200_OK;
 }

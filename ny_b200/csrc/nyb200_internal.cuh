@@ -80,6 +80,8 @@ struct Batch {
     bool finished = false;  // results of the last run have been checked (and refined if needed)
     int refined = 0;        // domains that triggered the binary64 re-run of the last batch
     int opt_iterations = 0; // iterations of the last parameter optimisation
+    bool external_tables = false;  // relaxation tables, abs-max tables and q were uploaded by a reference-shaped call:
+                                   // nothing may re-derive them with an interval pass
     // Left behind by the last plain-CROWN call: the input-level coefficient rows of its final pass
     // ([crown_D * 2 * crown_S x crown_lda], per box S lower rows then S upper rows), until any call reuses the workspace.
     const float *crown_a = nullptr;
@@ -107,7 +109,6 @@ struct nyb200_engine {
     float refine_tol = 5e-5f;  // see nyb200_set_refine_tolerance
     int error_channel = NYB200_ERRCH_IMMEDIATE;  // see nyb200_set_error_channel
     bool fuse_chain = true;                       // see nyb200_set_fusion
-    int fuse_variant = 4;                         // epilogue warps per tensor-memory lane quarter (2 or 4)
     std::string err;
     std::mutex mu;
     std::map<int, nyb::Net> nets;
@@ -117,6 +118,13 @@ struct nyb200_engine {
     nyb::Batch batch;
     nyb::Timing timing;
     std::map<std::string, nyb::DevBuf> ws;  // named grow-only device workspace
+    std::map<uint64_t, int> boundary_nets;   // networks registered on behalf of the reference-shaped calls, by weight key
+    // Status words of the batch runs in mapped pinned host memory, written by the last kernel of every run:
+    // [0] sequence number of the newest completed run, [1] pipeline error word seen by any run since the last finish,
+    // [2] domains flagged for the binary64 re-evaluation by any run since the last finish.  See nyb200_batch_poll.
+    int *status_host = nullptr;
+    int *status_dev = nullptr;
+    int run_seq = 0;
 };
 
 #define NYB_TRY(expr)                      \
@@ -203,7 +211,13 @@ int run_forward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int fw
 int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, float *const *ckpt, int ld_ckpt, int top = -1);
 // The same pass in the reference's error convention (per-coefficient error matrices carried to the input box,
 // binary64 arithmetic; nyb200_ref.cu).
-int run_backward_ref(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int top);
+// seed: optional asymmetric starting rows (GpuCrownSeed, crates/ny-core/src/gemm.rs:1684-1691), device pointers:
+// lower_a / upper_a [S x dims[L]], bias [2S] (lower biases, then upper biases)
+struct RefSeed { const float *lower_a = nullptr, *upper_a = nullptr, *bias = nullptr; bool relu_first = false; };
+int run_backward_ref(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int top, const RefSeed *seed = nullptr);
+int create_net(nyb200_engine *e, int32_t n_layers, const nyb200_layer_desc *ld, const float *wflat, const float *bflat, int32_t *net_id);
+int finish_batch_public(nyb200_engine *e);
+void launch_dgemm(nyb200_engine *e, int m, int n, int k, const double *a, const double *b, double *c);
 int prepare_backward_operands(nyb200_engine *e, Net &net);
 // ---- fused backward chain (nyb200_chain.cu) ----
 bool chain_eligible(const Net &net, int L);

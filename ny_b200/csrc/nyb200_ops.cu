@@ -65,6 +65,16 @@ k_dgemm(int M, int N, int K, const double *__restrict__ A, const double *__restr
         }
 }
 
+}  // namespace
+
+void launch_dgemm(nyb200_engine *e, int m, int n, int k, const double *a, const double *b, double *c) {
+    dim3 grid((n + TN - 1) / TN, (m + TM - 1) / TM);
+    k_dgemm<<<grid, 256, 0, e->stream>>>(m, n, k, a, b, c);
+    e->launches++;
+}
+
+namespace {
+
 // Transposed convolution of one group, product and scatter in one pass: every thread owns one input-side
 // element (s, ic, iy, ix), walks the kernel taps whose output pixel exists and contracts over the output
 // channels.  Lanes are consecutive ix, so for stride 1 a warp reads one contiguous run of pixels' channel

@@ -393,7 +393,7 @@ int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg, float *grad_h
     Timing &tm = e->timing;
     fold_timing(tm);
     cudaEventRecord(tm.ev[0], e->stream);
-    NYB_TRY(run_forward(e, *net, b, p, b.mode));
+    if (!b.external_tables) NYB_TRY(run_forward(e, *net, b, p, b.mode));
     if (dual) {
         long na = (long)D * np;
         k_init_alpha_up<<<(unsigned)((na + 255) / 256), 256, 0, e->stream>>>(na, p.tab, p.alpha_up);

@@ -183,7 +183,8 @@ k_ref_bias(int M, int K, int N, int R, int S, const float *__restrict__ A, int l
 }
 
 // Plain-CROWN ReLU step with the error carry (crown_dense.rs:41-290 with compose.rs:84-185): in place on one
-// row per warp.  tab = (lower slope, upper slope, upper intercept, -); the lower line has no intercept.
+// row per warp.  tab = (lower slope, upper slope, upper intercept, lower intercept); ReLU's own lower line has no
+// intercept (0 there), caller-baked tables may carry one.
 __global__ void __launch_bounds__(256)
 k_ref_relu(int M, int n, int R, int S, long nps, int off, float *__restrict__ A, int lda, float *__restrict__ E, int lde,
            const float4 *__restrict__ tab, float *__restrict__ rbf) {
@@ -196,7 +197,7 @@ k_ref_relu(int M, int n, int R, int S, long nps, int off, float *__restrict__ A,
     for (int j = lane; j < n; j += 32) {
         const float4 t = tab[(long)d * nps + off + j];
         const float a = A[(long)m * lda + j];
-        const float ls = t.x, us = t.y, ui = t.z;
+        const float ls = t.x, us = t.y, ui = t.z, li = t.w;
         float c = 0.f;
         double slope = 0.0, icp_used = 0.0;
         if (a > 0.f) {
@@ -205,14 +206,14 @@ k_ref_relu(int M, int n, int R, int S, long nps, int off, float *__restrict__ A,
             slope = (double)s;
             c = isfinite(p) ? (upper ? nup32(p) : ndn32(p)) : 0.f;
             nonfinite |= !isfinite(p);
-            icp_used = upper ? (double)ui : 0.0;
+            icp_used = upper ? (double)ui : (double)li;
         } else if (a < 0.f) {
             const float s = upper ? ls : us;
             const float p = a * s;
             slope = (double)s;
             c = isfinite(p) ? (upper ? nup32(p) : ndn32(p)) : 0.f;
             nonfinite |= !isfinite(p);
-            icp_used = upper ? 0.0 : (double)ui;
+            icp_used = upper ? (double)li : (double)ui;
         }
         b64 += (double)a * icp_used;
         const double gap = (a != 0.f) ? fabs((double)a * slope - (double)c) : 0.0;
@@ -221,7 +222,7 @@ k_ref_relu(int M, int n, int R, int S, long nps, int off, float *__restrict__ A,
         if (gap != 0.0 || ea != 0.0) {
             double sc, ic;
             if (fabs((double)a) > ea) { sc = fabs(slope); ic = fabs(icp_used); }
-            else { sc = (double)(fabsf(ls) + fabsf(us)); ic = (double)fabsf(ui); }
+            else { sc = (double)(fabsf(ls) + fabsf(us)); ic = (double)(fabsf(ui) + fabsf(li)); }
             eo = nup32((float)(ea * sc + gap));
             if (ea != 0.0) berr += ea * ic;
         }
@@ -290,11 +291,22 @@ k_ref_concretize(int M, int R, int S, int n0, const float *__restrict__ A, int l
     }
 }
 
+// rows of A from an asymmetric seed: lower rows take lower_a, upper rows upper_a
+__global__ void k_seed_rows(int S, int dim, int D, int lda, const float *__restrict__ la, const float *__restrict__ ua,
+                            float *__restrict__ A) {
+    long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= (long)D * 2 * S * dim) return;
+    int j = (int)(t % dim);
+    long m = t / dim;
+    int rr = (int)(m % (2 * S));
+    A[m * lda + j] = rr < S ? la[(long)rr * dim + j] : ua[(long)(rr - S) * dim + j];
+}
+
 }  // namespace
 
 // The backward pass of run_backward in the reference's error convention.  Same arguments; checkpoints are not
 // supported (the parameter optimisation keeps the default convention).
-int run_backward_ref(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int top) {
+int run_backward_ref(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int top, const RefSeed *seed) {
     const NetView &nv = net.v;
     for (int k = 0; k < nv.L; ++k)
         if (net.is_conv(k) || net.skip_of(k) >= 0)
@@ -313,10 +325,25 @@ int run_backward_ref(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, i
     static const float init_words[8] = {INFINITY, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     NYB_CUDA(e, cudaMemcpyAsync(p.min_lower, init_words, sizeof(init_words), cudaMemcpyHostToDevice, st));
     float *cur = p.A0, *nxt = p.A1, *ecur = E0, *enxt = E1;
-    if (partial) launch_seed_identity(e, S, D, p.lda, cur);
+    if (seed) {
+        // an asymmetric frontier handed over by the caller: its own lower / upper rows and biases
+        long tot = (long)D * 2 * S * nv.dims[L];
+        k_seed_rows<<<(unsigned)((tot + 255) / 256), 256, 0, st>>>(S, nv.dims[L], D, p.lda, seed->lower_a, seed->upper_a, cur);
+        e->launches++;
+        if (seed->bias)
+            for (int d = 0; d < D; ++d)
+                NYB_CUDA(e, cudaMemcpyAsync(rbf + (size_t)d * 2 * S, seed->bias, (size_t)2 * S * 4, cudaMemcpyDeviceToDevice, st));
+    } else if (partial) launch_seed_identity(e, S, D, p.lda, cur);
     else launch_seed(e, p.spec, S, nv.dims[L], D, p.lda, cur);
     bool have_err = false;  // the seed carries no error matrix
     const unsigned row_grid = (unsigned)(((long)M * 32 + 255) / 256);
+    if (seed && seed->relu_first) {
+        // the frontier sits behind the last activation: relax it first, from an exact (all-zero) error matrix
+        NYB_CUDA(e, cudaMemsetAsync(ecur, 0, (size_t)M * p.lda * 4, st));
+        k_ref_relu<<<row_grid, 256, 0, st>>>(M, nv.dims[L], R, S, np, nv.pre_off[L - 1], cur, p.lda, ecur, p.lda, p.tab, rbf);
+        e->launches++;
+        have_err = true;
+    }
     for (int k = L - 1; k >= 0; --k) {
         NYB_DEADLINE(e, "backward pass");
         const int K = nv.dims[k + 1], N = nv.dims[k];

@@ -55,34 +55,37 @@ __device__ __forceinline__ float relax_coeff(const bool upper, float a, float4 t
 // The same coefficient step for the fused backward chain, with the row sums arranged for issue rate: the coefficient
 // bits are those of relax_coeff (same product, same outward step, same beta addition); what differs is the
 // bookkeeping around them.
-//   * The rounding charge uses a bound instead of the measured residual: the stepped product is within 1.5 ulp of
-//     the exact one, |a slope - nw| <= 1.6 * 2^-23 |nw|, so the coefficient pays |nw| * cj with
-//     cj = eps * q + 1.6 * 2^-23 * max|z| prepared once per column by the caller (it is charged for neurons that
-//     cannot be negative as well: at most 3% more than the contraction's own charge).  A product that underflows
-//     takes the directed product and pays its exact residual.
+//   * One charge per coefficient, |nw| * cj, with cj prepared once per (domain, column) by the caller:
+//         cj = eps * q + (1.6 * 2^-23 + kappa) * max|z| + kappa * |bias|.
+//     1.6 * 2^-23 |nw| bounds the gap between the exact product and the stepped one (within 1.5 ulp); it is charged
+//     for neurons that cannot be negative as well (at most 3% more than the contraction's own charge).  kappa covers
+//     the fp32 accumulation of the two dot products below: a run of n fused multiply-adds errs by at most
+//     n * 2^-24 times the run's magnitude sum, and that sum is bounded term by term: |nw bias| directly, and
+//     |a * intercept| <= |nw| * max|z| * (1 + 2^-21), because an intercept only applies on the upper line, where the
+//     outward step moves nw away from zero (|nw| >= |a| * slope) and intercept / slope = -l up to rounding.
+//     A product that underflows takes the directed product and pays its exact residual.
 //   * The intercept and bias dot products are accumulated in fp32 (gi, gb: one fused multiply-add per term) over a
-//     short run of columns; the caller adds each run to the row's binary64 bias and charges the run's fp32
-//     roundings, at most `terms` * 2^-24 of the run's magnitude sum `sa`, to the penalty.
-__device__ __forceinline__ float relax_coeff_fast(const bool upper, float a, float4 t, float au, float cj, float za, float bk,
-                                                  float &gi, float &gb, float &sa, float &sp) {
+//     short run of columns; the caller adds each run to the row's binary64 bias.
+// dir = +1 for an upper row, -1 for a lower row; dirf the same as a float.
+__device__ __forceinline__ float relax_coeff_fast(const bool upper, const int dir, const float dirf, float a, float4 t, float au,
+                                                  float cj, const float *za_ptr, float bk, float &gi, float &gb, float &sp) {
     const bool pos = a > 0.f;
     const float slope = (pos != upper) ? (upper ? au : t.x) : t.y;
-    const float icp = ((pos == upper) && a != 0.f) ? t.z : 0.f;
+    const float icp = (pos == upper) ? t.z : 0.f;   // times a == 0 it adds nothing
     const float prod = __fmul_rn(a, slope);
-    const unsigned pb = __float_as_uint(prod);
-    const int neg = (int)pb >> 31;
-    const unsigned step = 1u + 2u * (unsigned)neg;
-    float nw = __uint_as_float(upper ? pb + step : pb - step);
+    const int pb = __float_as_int(prod);
+    // one ulp outward on the bit pattern: +dir for a positive product, -dir for a negative one
+    float nw = __int_as_float(pb + dir + 2 * dir * (pb >> 31));
     if (prod == 0.f) {
-        nw = upper ? __fmul_ru(a, slope) : __fmul_rd(a, slope);
-        sp = __fmaf_ru(fabsf(fmaf(a, slope, -nw)), za, sp);
+        if (a == 0.f || slope == 0.f) nw = 0.f;   // exact zero: no step
+        else {
+            nw = upper ? __fmul_ru(a, slope) : __fmul_rd(a, slope);
+            sp = __fmaf_ru(fabsf(fmaf(a, slope, -nw)), *za_ptr, sp);
+        }
     }
-    nw = (a == 0.f || slope == 0.f) ? 0.f : nw;
     gi = fmaf(a, icp, gi);
-    sa = __fmaf_ru(fabsf(a), icp, sa);   // icp >= 0 (an upper intercept)
-    nw = upper ? nw + t.w : nw - t.w;
+    nw = fmaf(t.w, dirf, nw);   // signed beta: nw + t.w on upper rows, nw - t.w on lower rows (t.w * +-1 is exact)
     gb = fmaf(nw, bk, gb);
-    sa = __fmaf_ru(fabsf(nw), fabsf(bk), sa);
     sp = __fmaf_ru(fabsf(nw), cj, sp);
     return nw;
 }

@@ -33,7 +33,7 @@ ERRCH_IMMEDIATE, ERRCH_REFERENCE = 0, 1
 
 EXPORTS = [
     "nyb200_create", "nyb200_destroy", "nyb200_backend_provenance", "nyb200_last_error", "nyb200_set_stream",
-    "nyb200_set_path", "nyb200_set_refine_tolerance", "nyb200_batch_refined", "nyb200_launch_count", "nyb200_clear_working_set", "nyb200_gemm_f32", "nyb200_net_create",
+    "nyb200_set_path", "nyb200_set_refine_tolerance", "nyb200_batch_refined", "nyb200_batch_poll", "nyb200_launch_count", "nyb200_clear_working_set", "nyb200_gemm_f32", "nyb200_net_create",
     "nyb200_net_destroy", "nyb200_ibp_forward", "nyb200_ibp_forward_noalloc", "nyb200_bab_bound_batch", "nyb200_batch_upload", "nyb200_batch_run",
     "nyb200_batch_download", "nyb200_batch_min_lower", "nyb200_batch_min_lower_device",
     "nyb200_batch_download_pre_bounds", "nyb200_batch_select_branch", "nyb200_timing_enable", "nyb200_timing_reset",
@@ -43,6 +43,7 @@ EXPORTS = [
     "nyb200_batch_verdicts", "nyb200_gemm_f64", "nyb200_conv_transpose_2d", "nyb200_set_deadline_ns",
     "nyb200_batch_gradient", "nyb200_point_vjp_batched", "nyb200_crown_input_coeffs", "nyb200_batch_download_branch_scores",
     "nyb200_set_error_channel", "nyb200_set_fusion", "nyb200_batch_download_opt_evaluations",
+    "nyb200_crown_backward", "nyb200_crown_resnet_beta_batched", "nyb200_crown_resnet_beta_batched_adam", "nyb200_gemm_f64_triplet",
 ]
 
 
@@ -58,6 +59,35 @@ class ConvTransposeParams(C.Structure):
     """nyb200_conv_transpose_params (ConvTranspose2dParams, crates/ny-core/src/gemm.rs:150-177)."""
     _fields_ = [(n, C.c_int32) for n in ("num_specs", "out_channels", "in_channels", "out_h", "out_w", "in_h", "in_w",
                                          "kernel_h", "kernel_w", "stride_h", "stride_w", "pad_h", "pad_w")]
+
+
+class CrownLayer(C.Structure):
+    """nyb200_crown_layer (GpuCrownLayer::{Linear, Activation, ActivationReluDualAlpha}, crates/ny-core/src/gemm.rs:1524-1645)."""
+    _fields_ = [("kind", C.c_int32), ("weight", C.POINTER(C.c_float)), ("bias", C.POINTER(C.c_float)),
+                ("out_features", C.c_int32), ("in_features", C.c_int32),
+                ("lower_slope", C.POINTER(C.c_float)), ("upper_slope", C.POINTER(C.c_float)),
+                ("lower_intercept", C.POINTER(C.c_float)), ("upper_intercept", C.POINTER(C.c_float)),
+                ("upper_neg_slope", C.POINTER(C.c_float)), ("num_neurons", C.c_int32)]
+
+
+class CrownSeed(C.Structure):
+    """nyb200_crown_seed (GpuCrownSeed, gemm.rs:1684-1691)."""
+    _fields_ = [("lower_a", C.POINTER(C.c_float)), ("upper_a", C.POINTER(C.c_float)), ("lower_b", C.POINTER(C.c_float)),
+                ("upper_b", C.POINTER(C.c_float)), ("num_specs", C.c_int32), ("current_dim", C.c_int32)]
+
+
+class DomainRef(C.Structure):
+    """nyb200_domain_ref (GpuResnetBatchedDomainRef, gemm.rs:2939-2952)."""
+    _fields_ = [("layers", C.POINTER(CrownLayer)), ("n_layers", C.c_int32), ("input_lower", C.POINTER(C.c_float)),
+                ("input_upper", C.POINTER(C.c_float)), ("beta_signed", C.POINTER(C.POINTER(C.c_float))),
+                ("frontier_abs", C.POINTER(C.POINTER(C.c_float))), ("node_abs", C.POINTER(C.POINTER(C.c_float))),
+                ("splits", C.c_void_p), ("n_splits", C.c_int32)]
+
+
+class BetaAdamConfig(C.Structure):
+    """nyb200_beta_adam_config (GpuBetaAdamConfig, gemm.rs:2960-2993)."""
+    _fields_ = [("iterations", C.c_int32), ("beta_lr", C.c_float), ("beta1", C.c_float), ("beta2", C.c_float),
+                ("epsilon", C.c_float), ("tolerance", C.c_float)]
 
 
 class EngineError(RuntimeError):
@@ -91,6 +121,7 @@ def load_library():
     L.nyb200_batch_download_opt_evaluations.argtypes = [vp, ip]
     L.nyb200_set_refine_tolerance.argtypes = [vp, C.c_float]
     L.nyb200_batch_refined.argtypes = [vp, ip]
+    L.nyb200_batch_poll.argtypes = [vp, ip, ip]
     L.nyb200_launch_count.argtypes = [vp]
     L.nyb200_launch_count.restype = C.c_int64
     L.nyb200_clear_working_set.argtypes = [vp]
@@ -292,8 +323,129 @@ class B200Engine:
         """Fused backward chain (default on) or one launch per layer."""
         self._check(self._L.nyb200_set_fusion(self._h, 1 if on else 0))
 
+    # -- reference-shaped calls (caller-baked relaxation tables, layer lists in backward order) -------------
+    @staticmethod
+    def _crown_layers(layers, keep):
+        """layers: backward-order list of ("linear", W [out, in], b or None) and ("act", lower_slope, upper_slope,
+        lower_intercept or None, upper_intercept) entries -> ctypes array (buffers appended to `keep`)."""
+        arr = (CrownLayer * len(layers))()
+        for i, l in enumerate(layers):
+            if l[0] == "linear":
+                w = _f32(l[1]); b = None if l[2] is None else _f32(l[2])
+                keep += [w, b]
+                arr[i].kind = 0
+                arr[i].weight = _fp(w); arr[i].bias = _fp(b)
+                arr[i].out_features, arr[i].in_features = int(w.shape[0]), int(w.shape[1])
+            elif l[0] == "act":
+                ls, us, ui = _f32(l[1]), _f32(l[2]), _f32(l[4])
+                li = None if l[3] is None else _f32(l[3])
+                keep += [ls, us, li, ui]
+                arr[i].kind = 1
+                arr[i].lower_slope, arr[i].upper_slope, arr[i].lower_intercept, arr[i].upper_intercept = _fp(ls), _fp(us), _fp(li), _fp(ui)
+                arr[i].num_neurons = int(ls.shape[0])
+            else:
+                raise EngineError(UNSUPPORTED, f"layer kind {l[0]}")
+        return arr
+
+    def crown_backward(self, layers, spec, in_lo, in_hi, seed=None):
+        """crown_backward_gpu_sound / _seeded_sound: backward-order layers with caller-baked slopes, one box.
+        seed = (lower_a, upper_a, lower_b, upper_b) starts the pass from an asymmetric frontier.  Returns (lower, upper)."""
+        keep = []
+        arr = self._crown_layers(layers, keep)
+        lo, hi = _f32(in_lo), _f32(in_hi)
+        if seed is None:
+            sp = _f32(spec)
+            S = int(sp.shape[0])
+            sd = None
+        else:
+            la, ua = _f32(seed[0]), _f32(seed[1])
+            lb = None if seed[2] is None else _f32(seed[2])
+            ub = None if seed[3] is None else _f32(seed[3])
+            keep += [la, ua, lb, ub]
+            S = int(la.shape[0])
+            sd = CrownSeed(_fp(la), _fp(ua), _fp(lb), _fp(ub), S, int(la.shape[1]))
+            sp = None
+        ol, ou = np.empty(S, np.float32), np.empty(S, np.float32)
+        fn = self._L.nyb200_crown_backward
+        fn.argtypes = [C.c_void_p, C.POINTER(CrownLayer), C.c_int32, C.POINTER(C.c_float), C.c_int32, C.POINTER(CrownSeed),
+                       C.POINTER(C.c_float), C.POINTER(C.c_float), C.POINTER(C.c_float), C.POINTER(C.c_float)]
+        self._check(fn(self._h, arr, len(layers), _fp(sp), S, C.byref(sd) if sd is not None else None, _fp(lo), _fp(hi), _fp(ol), _fp(ou)))
+        return ol, ou
+
+    def _domain_refs(self, domains, keep):
+        refs = (DomainRef * len(domains))()
+        fpp = C.POINTER(C.c_float)
+        for d, dom in enumerate(domains):
+            arr = self._crown_layers(dom["layers"], keep)
+            lo, hi = _f32(dom["lo"]), _f32(dom["hi"])
+            n_act = len(dom["node_abs"])
+            na = [_f32(a) for a in dom["node_abs"]]
+            bs = [None if b is None else _f32(b) for b in dom.get("beta_signed", [None] * n_act)]
+            na_p = (fpp * n_act)(*[_fp(a) for a in na])
+            bs_p = (fpp * n_act)(*[_fp(b) for b in bs])
+            sp = dom.get("splits")
+            sp = None if sp is None else np.ascontiguousarray(sp, SPLIT_DTYPE)
+            keep += [arr, lo, hi, na, bs, na_p, bs_p, sp]
+            refs[d].layers = arr; refs[d].n_layers = len(dom["layers"])
+            refs[d].input_lower, refs[d].input_upper = _fp(lo), _fp(hi)
+            refs[d].beta_signed = bs_p; refs[d].frontier_abs = None; refs[d].node_abs = na_p
+            refs[d].splits = None if sp is None else sp.ctypes.data
+            refs[d].n_splits = 0 if sp is None else len(sp)
+        return refs
+
+    def crown_resnet_beta_batched(self, domains, spec):
+        """crown_backward_gpu_resnet_sound_beta_batched for Chain networks: domains = list of dicts with layers (backward
+        order, shared weight arrays), lo, hi, node_abs (fold order), beta_signed (fold order).  Returns (lower, upper) [D, S]."""
+        keep = []
+        refs = self._domain_refs(domains, keep)
+        sp = _f32(spec)
+        D, S = len(domains), int(sp.shape[0])
+        ol, ou = np.empty((D, S), np.float32), np.empty((D, S), np.float32)
+        fn = self._L.nyb200_crown_resnet_beta_batched
+        fn.argtypes = [C.c_void_p, C.POINTER(DomainRef), C.c_int32, C.POINTER(C.c_float), C.c_int32, C.POINTER(C.c_float), C.POINTER(C.c_float)]
+        self._check(fn(self._h, refs, D, _fp(sp), S, _fp(ol), _fp(ou)))
+        return ol, ou
+
+    def crown_resnet_beta_batched_adam(self, domains, spec, iterations=3, beta_lr=0.05, beta1=0.9, beta2=0.999, epsilon=1e-8,
+                                       tolerance=1e-5):
+        """..._beta_batched_adam: as above plus `splits` per domain naming the multipliers to optimise.
+        Returns (best lower, best upper, final beta [D, max_splits])."""
+        keep = []
+        refs = self._domain_refs(domains, keep)
+        sp = _f32(spec)
+        D, S = len(domains), int(sp.shape[0])
+        ms = max([1] + [0 if d.get("splits") is None else len(d["splits"]) for d in domains])
+        ol, ou, ob = np.empty((D, S), np.float32), np.empty((D, S), np.float32), np.zeros((D, ms), np.float32)
+        cfg = BetaAdamConfig(iterations, beta_lr, beta1, beta2, epsilon, tolerance)
+        fn = self._L.nyb200_crown_resnet_beta_batched_adam
+        fn.argtypes = [C.c_void_p, C.POINTER(DomainRef), C.c_int32, C.POINTER(C.c_float), C.c_int32, C.POINTER(BetaAdamConfig),
+                       C.POINTER(C.c_float), C.POINTER(C.c_float), C.POINTER(C.c_float), C.c_int32]
+        self._check(fn(self._h, refs, D, _fp(sp), S, C.byref(cfg), _fp(ol), _fp(ou), _fp(ob), ms))
+        return ol, ou, ob
+
+    def gemm_f64_triplet(self, m, k, n, a3, b3):
+        """GemmEngine::gemm_f64_triplet: three same-shape binary64 products."""
+        a3 = [np.ascontiguousarray(a, np.float64) for a in a3]
+        b3 = [np.ascontiguousarray(b, np.float64) for b in b3]
+        c3 = [np.empty((m, n), np.float64) for _ in range(3)]
+        dp = C.POINTER(C.c_double)
+        pa = (dp * 3)(*[a.ctypes.data_as(dp) for a in a3])
+        pb = (dp * 3)(*[b.ctypes.data_as(dp) for b in b3])
+        pc = (dp * 3)(*[c.ctypes.data_as(dp) for c in c3])
+        fn = self._L.nyb200_gemm_f64_triplet
+        fn.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, dp * 3, dp * 3, dp * 3]
+        self._check(fn(self._h, m, k, n, pa, pb, pc))
+        return c3
+
     def set_refine_tolerance(self, tol: float):
         self._check(self._L.nyb200_set_refine_tolerance(self._h, tol))
+
+    def batch_poll(self):
+        """Non-blocking: (newest run finished on the device, some run since the last finishing call flagged a domain
+        for the binary64 re-evaluation - call batch_refined() then).  Raises on a latched pipeline error."""
+        done, att = C.c_int32(0), C.c_int32(0)
+        self._check(self._L.nyb200_batch_poll(self._h, C.byref(done), C.byref(att)))
+        return bool(done.value), bool(att.value)
 
     def batch_refined(self) -> int:
         n = C.c_int32(0)

@@ -62,28 +62,49 @@ def gather_counts(n_local: int, dist, device="cpu"):
     return [int(t.item()) for t in out]
 
 
-def exchange_domains(splits: np.ndarray, n_splits: np.ndarray, dist, device="cpu", trigger: float = 1.25):
+def exchange_domains(splits: np.ndarray, n_splits: np.ndarray, dist, device="cpu", trigger: float = 1.25,
+                     alpha: np.ndarray | None = None, stats: dict | None = None, counts=None):
     """Rebalances the local frontier (splits [D, max_splits], n_splits [D]) across ranks.  Domains leave
-    from the end of the local arrays and arrive appended.  Returns the new (splits, n_splits)."""
+    from the end of the local arrays and arrive appended.  Returns the new (splits, n_splits), or
+    (splits, n_splits, alpha) when `alpha` ([D, n_pre] warm-start slopes; the split multipliers already live in
+    the records) is given: the slopes travel in the same message as the records they belong to, so a moved
+    domain starts on its new rank exactly as it would have on the old one.  Every rank must pass `alpha` or none
+    of them.  `stats` accumulates exchanges, records_moved and bytes_moved (this rank's sends and receives);
+    `counts` may carry the already gathered shard sizes."""
     import torch
 
     rank = dist.get_rank()
-    counts = gather_counts(len(n_splits), dist, device)
+    if counts is None:
+        counts = gather_counts(len(n_splits), dist, device)
     plan = plan_rebalance(counts, trigger)
     max_splits = splits.shape[1]
-    rec = max_splits * 4 + 1  # int32 words per domain: the split records and the count
+    n_al = 0 if alpha is None else int(alpha.shape[1])
+    rec = max_splits * 4 + 1 + n_al  # int32 words per domain: the split records, the count, the slopes' bit patterns
     for src, dst, n in plan:
         if rank == src:
             keep = len(n_splits) - n
-            buf = np.concatenate([splits[keep:].view(np.int32).reshape(n, max_splits * 4),
-                                  n_splits[keep:].astype(np.int32).reshape(n, 1)], axis=1)
+            parts = [splits[keep:].view(np.int32).reshape(n, max_splits * 4), n_splits[keep:].astype(np.int32).reshape(n, 1)]
+            if n_al:
+                parts.append(np.ascontiguousarray(alpha[keep:], np.float32).view(np.int32))
+            buf = np.concatenate(parts, axis=1)
             dist.send(torch.from_numpy(np.ascontiguousarray(buf)).to(device), dst)
             splits, n_splits = splits[:keep], n_splits[:keep]
+            if n_al:
+                alpha = alpha[:keep]
         elif rank == dst:
             t = torch.empty((n, rec), dtype=torch.int32, device=device)
             dist.recv(t, src)
             buf = t.cpu().numpy()
             got = np.ascontiguousarray(buf[:, : max_splits * 4]).view(SPLIT_DTYPE).reshape(n, max_splits)
             splits = np.concatenate([splits, got], axis=0)
-            n_splits = np.concatenate([n_splits, buf[:, -1].astype(np.int32)])
+            n_splits = np.concatenate([n_splits, buf[:, max_splits * 4].astype(np.int32)])
+            if n_al:
+                alpha = np.concatenate([alpha, np.ascontiguousarray(buf[:, max_splits * 4 + 1:]).view(np.float32)], axis=0)
+        if stats is not None and rank in (src, dst):
+            stats["records_moved"] = stats.get("records_moved", 0) + n
+            stats["bytes_moved"] = stats.get("bytes_moved", 0) + n * rec * 4
+    if stats is not None and plan:
+        stats["exchanges"] = stats.get("exchanges", 0) + 1
+    if alpha is not None:
+        return splits, n_splits, alpha
     return splits, n_splits

@@ -321,3 +321,74 @@ def test_onnx_residual_add_becomes_an_identity_skip():
     with pytest.raises(EngineError) as ei:
         R.parse_onnx(R._ld(7, gb))
     assert ei.value.code == 1
+
+
+# ---- the reference's own ONNX fixtures (tests/golden/onnx: copies of its tests/models/*.onnx, data only) ----------
+def _onnx_fixture(name):
+    import os
+
+    with open(os.path.join(os.path.dirname(__file__), "golden", "onnx", name), "rb") as f:
+        return f.read()
+
+
+def test_reader_on_the_reference_single_linear_known_answers(oracle):
+    """crates/ny-onnx/src/tests/core/propagate.rs:12-66: single_linear.onnx is W = [[1,2],[3,-1],[-2,1]],
+    b = [0.5,-0.5,1]; the point [1,1] maps to [3.5,1.5,0] and the box [0,1]^2 to [0.5,-1.5,-1] .. [3.5,2.5,2]."""
+    from ny_b200 import onnx_reader as R
+
+    net, shape = R.parse_onnx(_onnx_fixture("single_linear.onnx"))
+    assert shape == (2,) and len(net.weights) == 1
+    assert np.array_equal(net.weights[0], np.array([[1, 2], [3, -1], [-2, 1]], np.float32))
+    assert np.array_equal(net.biases[0], np.array([0.5, -0.5, 1.0], np.float32))
+    onet = oracle.Net(net.weights, net.biases)
+    lo, hi = oracle.ibp_forward(onet, np.ones(2, np.float32), np.ones(2, np.float32))
+    assert np.allclose(lo[:3], [3.5, 1.5, 0.0], atol=1e-5) and np.allclose(hi[:3], [3.5, 1.5, 0.0], atol=1e-5)
+    lo, hi = oracle.ibp_forward(onet, np.zeros(2, np.float32), np.ones(2, np.float32))
+    assert np.allclose(lo[:3], [0.5, -1.5, -1.0], atol=1e-5) and np.allclose(hi[:3], [3.5, 2.5, 2.0], atol=1e-5)
+
+
+def test_reader_on_the_reference_sequential_fixtures(oracle):
+    """The shapes the reference's differential-translation tests state for its fixtures
+    (crates/ny-onnx/src/tests/core/differential_translation.rs:216-243: simple_mlp is Linear(2->4) + ReLU +
+    Linear(4->2); conv_relu is Conv2d(1->2, 2x2) + ReLU on a 3-D input; mnist_conv is Conv -> ReLU -> Flatten -> Linear)
+    and the soundness check of tests/core/graph.rs:13-66 on linear_relu: interval bounds of [0,1]^2 contain the
+    network's value at the four corners and the centre."""
+    from ny_b200 import onnx_reader as R
+    from ny_b200 import workloads as W
+
+    mlp, shape = R.parse_onnx(_onnx_fixture("simple_mlp.onnx"))
+    assert shape == (2,) and [w.shape for w in mlp.weights] == [(4, 2), (2, 4)]
+    conv, shape = R.parse_onnx(_onnx_fixture("conv_relu.onnx"))
+    assert shape == (1, 4, 4) and (conv.weights[0].oc, conv.weights[0].ic, conv.weights[0].kh, conv.weights[0].kw) == (2, 1, 2, 2)
+    assert int(conv.dims[1]) == 2 * 3 * 3                        # stride 1, no padding: 3x3 outputs per channel
+    mn, shape = R.parse_onnx(_onnx_fixture("mnist_conv.onnx"))
+    assert shape == (1, 8, 8) and hasattr(mn.weights[0], "kh") and mn.weights[1].shape == (5, 72)
+    one, shape = R.parse_onnx(_onnx_fixture("single_conv2d.onnx"))
+    assert shape == (1, 5, 5) and len(one.weights) == 1
+    lr, shape = R.parse_onnx(_onnx_fixture("linear_relu.onnx"))
+    onet = oracle.Net(lr.weights, lr.biases)
+    lo, hi = oracle.ibp_forward(onet, np.zeros(2, np.float32), np.ones(2, np.float32))
+    n_out = int(lr.dims[-1])
+    for pt in ([0, 0], [1, 0], [0, 1], [1, 1], [0.5, 0.5]):
+        y = W.forward(lr, np.array([pt], np.float32))[0]
+        assert np.all(y >= lo[-n_out:] - 1e-5) and np.all(y <= hi[-n_out:] + 1e-5)
+    # every fixture: the network evaluates, and the interval pass of its own box encloses a sample
+    g = np.random.Generator(np.random.PCG64(3))
+    for net, shp in ((mlp, (2,)), (conv, (1, 4, 4)), (mn, (1, 8, 8)), (one, (1, 5, 5))):
+        n0 = int(np.prod(shp))
+        x = g.random((4, n0), dtype=np.float32)
+        on = oracle.Net(net.weights, net.biases)
+        lo, hi = oracle.ibp_forward(on, np.zeros(n0, np.float32), np.ones(n0, np.float32))
+        y = W.forward(net, x)
+        k = y.shape[1]
+        assert np.all(y >= lo[-k:] - 1e-5) and np.all(y <= hi[-k:] + 1e-5)
+
+
+def test_reader_declines_the_reference_maxpool_fixture():
+    """cnn_with_flatten.onnx contains a MaxPool, which the bound kernels do not cover: UnsupportedOp, not a guess."""
+    from ny_b200 import onnx_reader as R
+    from ny_b200.engine import EngineError
+
+    with pytest.raises(EngineError) as ei:
+        R.parse_onnx(_onnx_fixture("cnn_with_flatten.onnx"))
+    assert "MaxPool" in str(ei.value)

@@ -176,6 +176,36 @@ def test_cnn_full_size_split_domains(eng, oracle):
     eng.release_network(nid)
 
 
+def test_cnn_full_size_against_the_native_convolution_oracle(eng, oracle):
+    """The same full-size configuration against the oracle's native convolution (kernel taps and the transposed
+    convolution of the backward pass, layers/convolution/conv2d/bound.rs:86-268, 601-900; no dense lowering): the
+    interval pass and six split domains of the 1024-domain batch."""
+    wl = W.config_cnn()
+    nat = oracle.Net(wl.net.weights, wl.net.biases)
+    nid = eng.register_network(wl.net)
+    nl, nu = oracle.ibp_forward(nat, wl.in_lo, wl.in_hi)
+    pl, pu = eng.ibp_forward_gpu(nid, wl.in_lo, wl.in_hi)
+    n = wl.net.n_pre
+    tol = 1e-5 * np.maximum(np.abs(nl[:n]), np.abs(nu[:n])) + 1e-6
+    assert np.all(np.abs(pl[0] - nl[:n]) <= tol) and np.all(np.abs(pu[0] - nu[:n]) <= tol)
+    rl, ru = pl[0].copy(), pu[0].copy()
+    D = 1024
+    splits, ns = W.draw_domains(wl, rl, ru, D)
+    glo, ghi, ginf = eng.bab_bound_batch(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, splits, ns, mode=1)
+    rl2, ru2 = _ext(rl, ru, wl.spec.shape[0])
+    ospec = nat.with_spec(wl.spec)
+    checked = 0
+    for d in (0, 7, 300, 511, 777, 1023):
+        olo, ohi, oinf, _ = oracle.bab_bound_batch(ospec, wl.in_lo, wl.in_hi, rl2, ru2, splits[d:d + 1], ns[d:d + 1], 1)
+        assert bool(oinf[0]) == bool(ginf[d])
+        if oinf[0]:
+            continue
+        assert _rel(np.concatenate([glo[d], ghi[d]]), np.concatenate([olo[0], ohi[0]])) <= REL_TOL, d
+        checked += 1
+    assert checked >= 4
+    eng.release_network(nid)
+
+
 def test_conv_crown_pipeline_matches_oracle(eng, oracle):
     """Plain CROWN with CROWN-IBP intermediates through convolutions (partial passes run transposed convolutions)
     against the oracle's pipeline on the dense lowering; this network is shallow enough for direct parity."""

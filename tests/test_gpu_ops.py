@@ -115,6 +115,7 @@ def test_joint_gradient_matches_oracle(eng, oracle, objective):
     ns[0] = 0
     eng.batch_upload(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, splits, ns, mode=1)
     eng.set_refine_tolerance(0.0)              # both evaluations on the same contraction path, no binary64 re-run
+    eng.set_fusion(False)                      # the gradient's pass keeps per-layer checkpoints: one launch per layer
     try:
         grad = eng.batch_gradient(objective)
         lo, hi, inf = eng.batch_download()
@@ -122,6 +123,7 @@ def test_joint_gradient_matches_oracle(eng, oracle, objective):
         plo, phi, _ = eng.batch_download()
     finally:
         eng.set_refine_tolerance(5e-5)
+        eng.set_fusion(True)
     assert np.array_equal(lo, plo) and np.array_equal(hi, phi)       # the evaluation is the plain bound
     rl2 = np.concatenate([rl, np.full(S, -np.inf, np.float32)])
     ru2 = np.concatenate([ru, np.full(S, np.inf, np.float32)])

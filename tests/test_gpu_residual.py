@@ -210,3 +210,38 @@ def test_resnet_full_size(eng, oracle):
     assert np.allclose(best, true, rtol=1e-4, atol=1e-5) and np.all(best <= start + 1e-5) and best.mean() < start.mean()
     assert np.all(glo[0].min() <= best + 1e-5)          # the unsplit domain's bound is below every attacked point
     eng.release_network(nid)
+
+
+def test_resnet_full_size_against_the_native_oracle(eng, oracle):
+    """The residual configuration at full size against the oracle's native evaluation (kernel taps, identity branches
+    joined in place: no lowering to dense matrices, which would be 65536 x 65536 here): the interval pass, and four
+    split domains of a 64-domain batch to the parity tolerance."""
+    wl = W.config_resnet()
+    nat = oracle.Net(wl.net.weights, wl.net.biases, skips=wl.net.skips)
+    nid = eng.register_network(wl.net)
+    nl, nu = oracle.ibp_forward(nat, wl.in_lo, wl.in_hi)
+    pl, pu = eng.ibp_forward_gpu(nid, wl.in_lo, wl.in_hi)
+    n = wl.net.n_pre
+    tol = 1e-5 * np.maximum(np.abs(nl[:n]), np.abs(nu[:n])) + 1e-6
+    assert np.all(np.abs(pl[0] - nl[:n]) <= tol) and np.all(np.abs(pu[0] - nu[:n]) <= tol)
+    rl, ru = pl[0].copy(), pu[0].copy()
+    D = 64
+    splits, ns = W.draw_domains(wl, rl, ru, D)
+    glo, ghi, ginf = eng.bab_bound_batch(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, splits, ns, mode=1)
+    S = wl.spec.shape[0]
+    rl2 = np.concatenate([rl, np.full(S, -np.inf, np.float32)])
+    ru2 = np.concatenate([ru, np.full(S, np.inf, np.float32)])
+    ospec = nat.with_spec(wl.spec)
+    pick = np.array([0, 21, 42, 63])
+    olo, ohi, oinf, _ = oracle.bab_bound_batch(ospec, wl.in_lo, wl.in_hi, rl2, ru2, splits[pick], ns[pick], 1)  # one call: the oracle runs its domains on separate threads
+    checked = 0
+    for i, d in enumerate(pick):
+        assert bool(oinf[i]) == bool(ginf[d])
+        if oinf[i]:
+            continue
+        got, ref = np.concatenate([glo[d], ghi[d]]), np.concatenate([olo[i], ohi[i]])
+        scale = np.abs(ref).max()
+        assert np.all(np.abs(got - ref) <= 1e-4 * np.maximum(np.abs(ref), 1e-2 * scale)), d
+        checked += 1
+    assert checked >= 3
+    eng.release_network(nid)

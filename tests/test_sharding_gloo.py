@@ -66,6 +66,56 @@ def test_two_ranks_shard_reduce_and_rebalance():
     assert r1["beta"].count(0.25) == 4 and r1["beta"].count(0.5) == 2
 
 
+def _worker_alpha(rank, world, port, ret):
+    import torch.distributed as dist
+
+    from ny_b200 import SPLIT_DTYPE, bab, sharding
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        n_pre = 7
+        n_local = 9 if rank == 0 else 1
+        fr = bab.Frontier(n_pre)
+        splits = np.zeros((n_local, 2 + rank), SPLIT_DTYPE)          # the ranks' histories differ in depth
+        splits["neuron"] = 100 * rank + np.arange(n_local)[:, None]
+        ns = np.full(n_local, 2 + rank, np.int32)
+        alpha = (1000.0 * rank + np.arange(n_local)[:, None] + 0.125 * np.arange(n_pre)[None, :]).astype(np.float32)
+        fr.push(splits, ns, alpha)
+        stats = {}
+        bab._rebalance(fr, dist, "cpu", sharding, stats)
+        n_after = len(fr)
+        bab._rebalance(fr, dist, "cpu", sharding, stats)              # level now: the early return, nothing popped
+        sp, n2, al = fr.pop(len(fr))
+        ret[rank] = dict(n=n_after, depth=int(sp.shape[1]), has_alpha=al is not None, stats=dict(stats),
+                         pairs=[(int(sp[d, 0]["neuron"]), float(al[d, 0]), float(al[d, 6])) for d in range(len(n2))])
+    finally:
+        dist.destroy_process_group()
+
+
+def test_rebalance_moves_warm_start_slopes_with_their_records():
+    import torch.multiprocessing as mp
+
+    world = 2
+    port = _free_port()
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_worker_alpha, args=(world, port, ret), nprocs=world, join=True)
+        r0, r1 = ret[0], ret[1]
+    assert r0["n"] == 5 and r1["n"] == 5 and r0["has_alpha"] and r1["has_alpha"]
+    assert r0["depth"] == 2 and r1["depth"] == 3      # pop() trims to the deepest history it returns
+    # every record still carries the slopes it was created with: alpha[d, 0] = 1000 * rank + index = its neuron tag
+    for r in (r0, r1):
+        for neuron, a0, a6 in r["pairs"]:
+            rank_of, idx = divmod(neuron, 100)
+            assert a0 == 1000.0 * rank_of + idx and a6 == a0 + 0.75
+    assert sorted(p[0] for p in r0["pairs"] + r1["pairs"]) == list(range(9)) + [100]
+    rec_words = 3 * 4 + 1 + 7
+    for r in (r0, r1):
+        assert r["stats"] == {"records_moved": 4, "bytes_moved": 4 * rec_words * 4, "exchanges": 1}
+
+
 def test_rebalance_plan_properties():
     from ny_b200.sharding import plan_rebalance, shard_bounds
 
