@@ -140,7 +140,9 @@ __global__ void __launch_bounds__(Cfg<NSUB>::THREADS, 1) k_chain(const __grid_co
     using C = Cfg<NSUB>;
     constexpr int CPT = C::CPT;
     extern __shared__ unsigned char smem_raw[];
-    unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    // aligned to 1024 bytes by an offset, not by a cast through an integer: the pointer stays a shared-memory pointer
+    // for the compiler, which then emits shared-space loads and stores instead of generic ones
+    unsigned char *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     unsigned char *a_ring = smem;
     unsigned char *w_ring = smem + NA * A_SLOT;
     unsigned char *t_ring = w_ring + NW * W_SLOT;
@@ -186,7 +188,7 @@ __global__ void __launch_bounds__(Cfg<NSUB>::THREADS, 1) k_chain(const __grid_co
                         for (int part = 0; part < 2; ++part, ++it) {  // the low half first: its steps are issued first
                             const int s = it % NW;
                             const unsigned ph = (it / NW) & 1;
-                            if (!mbar_wait(smem_u32(&bars[W_EMPTY + s]), ph ^ 1)) { atomicExch(P.err, 11); *abort_flag = 1; break; }
+                            if (!mbar_wait(smem_u32(&bars[W_EMPTY + s]), ph ^ 1, 400)) { atomicExch(P.err, 11); *abort_flag = 1; break; }
                             const unsigned bar = smem_u32(&bars[W_FULL + s]);
                             mbar_expect_tx(bar, W_SLOT);
                             tma_load_2d(smem_u32(w_ring + s * W_SLOT), part == 0 ? &Ly.tm_lo : &Ly.tm_hi, c * BK, 0, bar);
@@ -206,17 +208,17 @@ __global__ void __launch_bounds__(Cfg<NSUB>::THREADS, 1) k_chain(const __grid_co
                     const int n_eff = min(BN, (Ly.N + 15) & ~15);
                     const unsigned idesc = make_idesc(BM, n_eff);
                     // both accumulators must have been drained by the epilogue of the previous layer
-                    if (!mbar_wait(smem_u32(&bars[ACC_EMPTY]), (lit & 1) ^ 1)) { atomicExch(P.err, 12); *abort_flag = 1; failed = true; break; }
+                    if (!mbar_wait(smem_u32(&bars[ACC_EMPTY]), (lit & 1) ^ 1, 100)) { atomicExch(P.err, 12); *abort_flag = 1; failed = true; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const unsigned d_main = tmem_base, d_cross = tmem_base + BN;
                     for (int c = 0; c < kc && !failed; ++c, ++ait) {
                         const int sa = ait % NA;
-                        if (!mbar_wait(smem_u32(&bars[A_FULL + sa]), (ait / NA) & 1)) { atomicExch(P.err, 13); *abort_flag = 1; failed = true; break; }
+                        if (!mbar_wait(smem_u32(&bars[A_FULL + sa]), (ait / NA) & 1, 100)) { atomicExch(P.err, 13); *abort_flag = 1; failed = true; break; }
                         const unsigned long long a_hi = make_desc(smem_u32(a_ring + sa * A_SLOT));
                         const unsigned long long a_lo = make_desc(smem_u32(a_ring + sa * A_SLOT + A_HALF));
                         // Ah * Wl
                         int sw = wit % NW;
-                        if (!mbar_wait(smem_u32(&bars[W_FULL + sw]), (wit / NW) & 1)) { atomicExch(P.err, 14); *abort_flag = 1; failed = true; break; }
+                        if (!mbar_wait(smem_u32(&bars[W_FULL + sw]), (wit / NW) & 1, 100)) { atomicExch(P.err, 14); *abort_flag = 1; failed = true; break; }
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                         unsigned long long b = make_desc(smem_u32(w_ring + sw * W_SLOT));
 #pragma unroll
@@ -228,7 +230,7 @@ __global__ void __launch_bounds__(Cfg<NSUB>::THREADS, 1) k_chain(const __grid_co
                         ++wit;
                         // Al * Wh (cross), Ah * Wh (main)
                         sw = wit % NW;
-                        if (!mbar_wait(smem_u32(&bars[W_FULL + sw]), (wit / NW) & 1)) { atomicExch(P.err, 15); *abort_flag = 1; failed = true; break; }
+                        if (!mbar_wait(smem_u32(&bars[W_FULL + sw]), (wit / NW) & 1, 100)) { atomicExch(P.err, 15); *abort_flag = 1; failed = true; break; }
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                         b = make_desc(smem_u32(w_ring + sw * W_SLOT));
 #pragma unroll
@@ -261,7 +263,7 @@ __global__ void __launch_bounds__(Cfg<NSUB>::THREADS, 1) k_chain(const __grid_co
                     const int nch = (Ly.N + BK - 1) / BK;
                     for (int c2 = 0; c2 < nch; c2 += 2, ++tit) {
                         const int s = tit % NT;
-                        if (!mbar_wait(smem_u32(&bars[T_EMPTY + s]), ((tit / NT) & 1) ^ 1)) { atomicExch(P.err, 16); *abort_flag = 1; failed = true; break; }
+                        if (!mbar_wait(smem_u32(&bars[T_EMPTY + s]), ((tit / NT) & 1) ^ 1, 400)) { atomicExch(P.err, 16); *abort_flag = 1; failed = true; break; }
                         const int w = Ly.N - c2 * BK < T_COLS ? Ly.N - c2 * BK : T_COLS;   // a multiple of 4
                         const unsigned bar = smem_u32(&bars[T_FULL + s]);
                         mbar_expect_tx(bar, (unsigned)((Ly.bias ? w * 4 : 0) + nd * w * 20));

@@ -74,11 +74,15 @@ __device__ __forceinline__ float relax_coeff_fast(const bool upper, const int di
     const float icp = (pos == upper) ? t.z : 0.f;   // times a == 0 it adds nothing
     const float prod = __fmul_rn(a, slope);
     const int pb = __float_as_int(prod);
-    // one ulp outward on the bit pattern: +dir for a positive product, -dir for a negative one
+    // one ulp outward on the bit pattern: +dir for a positive product, -dir for a negative one; a zero product (zero
+    // slope or zero coefficient: common, every stably inactive neuron has one) stays zero without a branch
     float nw = __int_as_float(pb + dir + 2 * dir * (pb >> 31));
-    if (prod == 0.f) {
-        if (a == 0.f || slope == 0.f) nw = 0.f;   // exact zero: no step
-        else {
+    const bool zero = prod == 0.f;
+    nw = zero ? 0.f : nw;
+    // a zero product next to a non-zero slope is a zero coefficient or, once in a blue moon, an underflow: the latter
+    // takes the directed product and pays its exact residual
+    if (zero && slope != 0.f) {
+        if (a != 0.f) {
             nw = upper ? __fmul_ru(a, slope) : __fmul_rd(a, slope);
             sp = __fmaf_ru(fabsf(fmaf(a, slope, -nw)), *za_ptr, sp);
         }

@@ -8,7 +8,8 @@
 namespace nyb {
 namespace umma {
 
-constexpr unsigned SPIN_LIMIT = 1u << 24;
+constexpr unsigned WAIT_HINT_NS = 20000;                 // per probe: up to 20 us parked
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;    // per wait: about two seconds of SM clock
 
 __device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
 
@@ -21,21 +22,30 @@ __device__ __forceinline__ void mbar_arrive(unsigned bar) {
 __device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-// Bounded wait: returns false when the limit expires.
-__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
-    for (unsigned it = 0; it < SPIN_LIMIT; ++it) {
-        unsigned ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok)
-            : "r"(bar), "r"(parity)
-            : "memory");
-        if (ok) return true;
-        if (it > 1024) __nanosleep(64);
+// Bounded wait: returns false when the limit expires.  Every probe carries a suspend-time hint, so a waiting warp is
+// parked by the hardware until the phase completes (or the hint runs out) instead of competing for issue slots with
+// the warps that do the work; the bound is on elapsed SM cycles (about two seconds), read only between probes.
+__device__ __forceinline__ bool mbar_probe(unsigned bar, unsigned parity, unsigned hint_ns) {
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
+// sleep_ns > 0: the caller is a role that runs ahead of the work (a producer, the MMA issuer waiting for operands);
+// after a failed probe it sleeps that long, so that it does not take issue slots from the warps it is waiting for.
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, unsigned sleep_ns = 0) {
+    if (mbar_probe(bar, parity, WAIT_HINT_NS)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+        if (sleep_ns) __nanosleep(sleep_ns);
+        if (mbar_probe(bar, parity, WAIT_HINT_NS)) return true;
+        if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
     }
-    return false;
 }
 
 __device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap *tm, int x, int y, unsigned bar) {

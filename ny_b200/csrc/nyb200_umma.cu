@@ -94,7 +94,8 @@ k_umma_tf32x3(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__
               const __grid_constant__ CUtensorMap tm_a, const float *__restrict__ A, int lda, float *__restrict__ C,
               int ldc, int M, int N, int K, int chunk_stages, int *__restrict__ err, int a_plane, int a_tma) {
     extern __shared__ unsigned char smem_raw[];
-    unsigned char *smem = (unsigned char *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    // aligned by an offset (not by a cast through an integer) so that the compiler keeps treating it as shared memory
+    unsigned char *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     unsigned char *raw_base = smem + STAGES * STAGE_BYTES;  // RAW_STAGES fp32 A tiles (128-byte swizzle, as TMA wrote them)
     unsigned long long *bars = (unsigned long long *)(raw_base + RAW_STAGES * A_BYTES);
     // barrier indices
