@@ -144,7 +144,6 @@ int create_net(nyb200_engine *e, int32_t n_layers, const nyb200_layer_desc *ld, 
     net.kind.resize(n_layers);
     net.geom.resize(n_layers);
     net.skip.assign(n_layers, -1);
-    int open_until = -1;  // skips may not overlap or nest: the previous one must be consumed first
     int off = 0;
     for (int k = 0; k < n_layers; ++k) {
         const nyb200_layer_desc &l = ld[k];
@@ -171,8 +170,6 @@ int create_net(nyb200_engine *e, int32_t n_layers, const nyb200_layer_desc *ld, 
             if (j < 0 || j > k - 2) return set_err(e, NYB200_ERR_INVALID, "skip_from must name a layer at least two before this one");
             if (ld[j].out_features != l.out_features) return set_err(e, NYB200_ERR_SHAPE, "residual branch widths differ");
             if (k == n_layers - 1) return set_err(e, NYB200_ERR_UNSUPPORTED, "the last layer cannot take a residual connection");
-            if (j < open_until) return set_err(e, NYB200_ERR_UNSUPPORTED, "overlapping residual connections");
-            open_until = k;
             net.skip[k] = j;
         }
         if (k == 0) { net.v.dims[0] = l.in_features; net.max_dim = l.in_features; }
@@ -490,8 +487,14 @@ int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, float
     static const float init_words[8] = {INFINITY, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};  // min lower; loose-domain counter at word 4
     NYB_CUDA(e, cudaMemcpyAsync(p.min_lower, init_words, sizeof(init_words), cudaMemcpyHostToDevice, e->stream));
     float *cur = p.A0, *nxt = p.A1;
-    float *stash = nullptr;
-    int stash_for = -1;
+    // Open identity branches (blocks may nest or overlap, several may start at the same variable): the coefficient
+    // rows kept at a joining layer until the pass reaches the variable the branch starts from, one buffer per slot.
+    struct OpenSkip { float *buf; int src; };
+    std::vector<OpenSkip> open_skips;
+    auto stash_slot = [&](size_t slot) -> float * {
+        const std::string name = slot == 0 ? std::string("skip_coeff") : "skip_coeff_" + std::to_string(slot);
+        return (float *)ws_get(e, name.c_str(), (size_t)M * p.lda * 4);
+    };
     // Fused chain: seed, identity pass and the contractions L-1 .. 1 with their relaxations run as one kernel that
     // keeps the rows on the SM; what is left for the loop below is Linear_0's (wide) contraction.
     const bool fused = tensor && e->fuse_chain && !ckpt && chain_eligible(net, L) && (nv.nps % 4 == 0) && (p.lda % 4 == 0);
@@ -537,11 +540,16 @@ int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, float
         if (net.skip_of(k) >= 0) {
             // residual block: these coefficients also multiply relu(pre_j) directly; keep them until the pass
             // reaches that variable (iteration j + 1 below)
-            stash = (float *)ws_get(e, "skip_coeff", (size_t)M * p.lda * 4);
+            size_t slot = 0;   // the first buffer no open branch is using
+            for (bool taken = true; taken; ) {
+                taken = false;
+                for (const OpenSkip &o : open_skips) if (o.buf == stash_slot(slot)) { taken = true; ++slot; break; }
+            }
+            float *stash = stash_slot(slot);
             if (!stash) return NYB200_ERR_OOM;
             NYB_CUDA(e, cudaMemcpy2DAsync(stash, (size_t)p.lda * 4, cur, (size_t)p.lda * 4, (size_t)K * 4, (size_t)M,
                                           cudaMemcpyDeviceToDevice, e->stream));
-            stash_for = net.skip_of(k);
+            open_skips.push_back({stash, net.skip_of(k)});
         }
         if (e->timing.per_kernel) cudaEventRecord(next_kev(e->timing), e->stream);
         if (net.is_conv(k) && tensor) {
@@ -568,9 +576,10 @@ int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, float
             launch_gemm_f64(e, M, N, K, cur, p.lda, nv.W[k], N, dst, ldd, R, zin_lo, zin_hi, zin_ds, p.rpen);
         }
         if (e->timing.per_kernel) cudaEventRecord(next_kev(e->timing), e->stream);
-        if (stash && stash_for == k - 1) {  // dst holds the coefficients of relu(pre_{k-1}): add the identity branch
-            launch_skip_coeff(e, M, N, dst, ldd, stash, p.lda, R, p.zl, p.zu, np, nv.pre_off[k - 1], p.rpen);
-            stash = nullptr;
+        for (size_t oi = 0; oi < open_skips.size();) {  // dst holds the coefficients of relu(pre_{k-1}): add the identity branches
+            if (open_skips[oi].src != k - 1) { ++oi; continue; }
+            launch_skip_coeff(e, M, N, dst, ldd, open_skips[oi].buf, p.lda, R, p.zl, p.zu, np, nv.pre_off[k - 1], p.rpen);
+            open_skips.erase(open_skips.begin() + (long)oi);
         }
         if (k > 0)
             launch_relax(e, nv, k - 1, k - 1, M, R, S, nxt, p.lda, p.tab, p.zabs, p.q, q_ds(k - 1), eps_for(k - 1), p.rb, p.rabs,

@@ -425,18 +425,31 @@ int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg, float *grad_h
                                                                               p.in_hi, (long)b.box_stride, z0, ldz);
         e->launches++;
         float *zc = z0, *zn = z1;
-        float *zstash = nullptr;
+        // adjoints of relu(pre_k) that a later layer's identity branch still needs, one buffer per open source layer
+        struct OpenAdj { float *buf; int src; };
+        std::vector<OpenAdj> open_adj;
+        auto adj_slot = [&](size_t slot) -> float * {
+            const std::string name = slot == 0 ? std::string("adj_skip") : "adj_skip_" + std::to_string(slot);
+            return (float *)ws_get(e, name.c_str(), (size_t)D * Zr * ldz * 4);
+        };
         for (int k = 0; k < L - 1; ++k) {
             int K = nv.dims[k], N = nv.dims[k + 1];
             if (net->is_conv(k) && tensor) NYB_TRY(conv_forward_tensor(e, *net, k, D * Zr, zc, ldz, zn, ldz, derr));
             else if (net->is_conv(k)) launch_conv_plain(e, net->geom[k], D * Zr, zc, ldz, nv.W[k], zn, ldz);
             else if (tensor) NYB_TRY(launch_umma(e, net->umma_adj[k], D * Zr, zc, ldz, zn, ldz, derr));
             else launch_gemm_f64(e, D * Zr, N, K, zc, ldz, net->wt[k], N, zn, ldz, 1, nullptr, nullptr, 0, nullptr);
-            if (net->skip_of(k) >= 0 && zstash) {
+            if (net->skip_of(k) >= 0) {
                 // residual block: pre_k = W z + b + relu(pre_j), so the adjoint of relu(pre_j) joins here
-                long tot = (long)D * Zr * N;
-                k_add_adjoint<<<(unsigned)((tot + 255) / 256), 256, 0, e->stream>>>((long)D * Zr, N, zn, ldz, zstash, ldz);
-                e->launches++;
+                for (size_t oi = 0; oi < open_adj.size(); ++oi) {
+                    if (open_adj[oi].src != net->skip_of(k)) continue;
+                    long tot = (long)D * Zr * N;
+                    k_add_adjoint<<<(unsigned)((tot + 255) / 256), 256, 0, e->stream>>>((long)D * Zr, N, zn, ldz, open_adj[oi].buf, ldz);
+                    e->launches++;
+                    bool later = false;   // does another layer further on take the same branch?
+                    for (int kk = k + 1; kk < L - 1; ++kk) later |= net->skip_of(kk) == open_adj[oi].src;
+                    if (!later) open_adj.erase(open_adj.begin() + (long)oi);
+                    break;
+                }
             }
             long nt = (long)D * N;
             k_adjoint_relu<<<(unsigned)((nt + 255) / 256), 256, 0, e->stream>>>(N, nv.pre_off[k], D, S, R, Zr, np, zn, ldz, nv.b[k],
@@ -447,9 +460,15 @@ int optimize_batch(nyb200_engine *e, const nyb200_opt_config &cfg, float *grad_h
             bool opens = false;  // is this layer's post-activation adjoint skipped forward to a later layer?
             for (int kk = k + 2; kk < L - 1; ++kk) opens |= net->skip_of(kk) == k;
             if (opens) {
-                zstash = (float *)ws_get(e, "adj_skip", (size_t)D * Zr * ldz * 4);
+                size_t slot = 0;
+                for (bool taken = true; taken; ) {
+                    taken = false;
+                    for (const OpenAdj &o : open_adj) if (o.buf == adj_slot(slot)) { taken = true; ++slot; break; }
+                }
+                float *zstash = adj_slot(slot);
                 if (!zstash) return NYB200_ERR_OOM;
                 NYB_CUDA(e, cudaMemcpyAsync(zstash, zn, (size_t)D * Zr * ldz * 4, cudaMemcpyDeviceToDevice, e->stream));
+                open_adj.push_back({zstash, k});
             }
             float *tmp = zc; zc = zn; zn = tmp;
         }

@@ -168,15 +168,20 @@ static int pgd_backward(nyb200_engine *e, Net &net, bool tensor, int K, float *G
     cudaStream_t st = e->stream;
     double *cols64 = nullptr;
     float *g = G0, *gn = G1;
-    float *gstash = nullptr;
-    int stash_for = -1;
+    struct OpenGrad { float *buf; int src; };   // gradients kept for identity branches (blocks may nest)
+    std::vector<OpenGrad> open_grad;
+    auto grad_slot = [&](size_t slot) -> float * {
+        const std::string name = slot == 0 ? std::string("pgd_skip") : "pgd_skip_" + std::to_string(slot);
+        return (float *)ws_get(e, name.c_str(), (size_t)K * ld * 4);
+    };
     for (int k = L - 1; k >= 0; --k) {
         int Kd = nv.dims[k + 1], N = nv.dims[k];
-        if (gstash && stash_for == k) {  // g is the gradient of relu(pre_k): the identity branch joins here
+        for (size_t oi = 0; oi < open_grad.size();) {  // g is the gradient of relu(pre_k): identity branches join here
+            if (open_grad[oi].src != k) { ++oi; continue; }
             long tot = (long)K * Kd;
-            k_add_rows<<<(unsigned)((tot + 255) / 256), 256, 0, st>>>(K, Kd, g, ld, gstash, ld);
+            k_add_rows<<<(unsigned)((tot + 255) / 256), 256, 0, st>>>(K, Kd, g, ld, open_grad[oi].buf, ld);
             e->launches++;
-            gstash = nullptr;
+            open_grad.erase(open_grad.begin() + (long)oi);
         }
         if (k < L - 1) {
             long tot = (long)K * Kd;
@@ -184,10 +189,15 @@ static int pgd_backward(nyb200_engine *e, Net &net, bool tensor, int K, float *G
             e->launches++;
         }
         if (net.skip_of(k) >= 0) {  // the gradient of pre_k also reaches relu(pre_j) directly
-            gstash = (float *)ws_get(e, "pgd_skip", (size_t)K * ld * 4);
+            size_t slot = 0;
+            for (bool taken = true; taken; ) {
+                taken = false;
+                for (const OpenGrad &o : open_grad) if (o.buf == grad_slot(slot)) { taken = true; ++slot; break; }
+            }
+            float *gstash = grad_slot(slot);
             if (!gstash) return NYB200_ERR_OOM;
             NYB_CUDA(e, cudaMemcpyAsync(gstash, g, (size_t)K * ld * 4, cudaMemcpyDeviceToDevice, st));
-            stash_for = net.skip_of(k);
+            open_grad.push_back({gstash, net.skip_of(k)});
         }
         if (net.is_conv(k) && tensor) {
             const ConvGeom &cg = net.geom[k];

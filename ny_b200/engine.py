@@ -229,6 +229,100 @@ class Conv2d:
                          self.oc, self.oh, self.ow, self.kh, self.kw, self.sh, self.sw, self.ph, self.pw)
 
 
+def lower_projection_block(function, projection):
+    """A projection residual block `out = F(z) + P(z)` (GpuResnetSegment::ResidualProj, crates/ny-core/src/gemm.rs:
+    1658-1669) as plain sequential layers, for a block input z that is a post-ReLU tensor (z >= 0).
+
+    function: [(weight, bias), ...] the layers of F in forward order, a ReLU between consecutive ones (two or more
+    layers); projection: (weight, bias), one layer without activation.  All Linear ([out, in] matrices) or all Conv2d.
+    Every layer of F but the last is widened by channels (neurons) that carry z through unchanged - an identity row,
+    or for a convolution the tap that reads the output pixel's own input pixel, so a strided first layer carries z
+    subsampled exactly as a strided 1x1 projection reads it; the ReLUs leave the carried values alone because
+    z >= 0 - and the last layer reads P's weights from the carried channels.  The result computes F(z) + P(z) exactly;
+    in bound propagation the carried neurons are stably active, their relaxation is the identity, so the bounds are
+    those of relaxing F and P separately and adding them (the reference's merge).  Returns [(weight, bias), ...]."""
+    (pw, pb) = projection
+    n = len(function)
+    if n < 2:
+        raise EngineError(UNSUPPORTED, "projection block: F needs at least two layers (a one-layer F folds into P)")
+    conv = isinstance(function[0][0], Conv2d)
+    if any(isinstance(w, Conv2d) != conv for w, _ in function) or isinstance(pw, Conv2d) != conv:
+        raise EngineError(UNSUPPORTED, "projection block: mixed Linear and Conv2d layers")
+    out = []
+    if not conv:
+        ws = [_f32(w) for w, _ in function]
+        bs = [None if b is None else _f32(b) for _, b in function]
+        pw = _f32(pw)
+        nz = ws[0].shape[1]
+        if pw.shape != (ws[-1].shape[0], nz):
+            raise EngineError(SHAPE, "projection block: P must map the block input to the block output")
+        # when both F's last layer and P have a bias, their fp32 sum need not be exact: P's bias then rides on one more
+        # carried neuron that holds the constant 1
+        one = 1 if (pb is not None and bs[-1] is not None) else 0
+        nc = nz + one
+        for k in range(n - 1):
+            w, b = ws[k], bs[k]
+            if k == 0:
+                w2 = np.zeros((w.shape[0] + nc, nz), np.float32)
+                w2[: w.shape[0]] = w
+                w2[w.shape[0] + np.arange(nz), np.arange(nz)] = 1.0
+            else:
+                w2 = np.zeros((w.shape[0] + nc, w.shape[1] + nc), np.float32)
+                w2[: w.shape[0], : w.shape[1]] = w
+                w2[w.shape[0] + np.arange(nc), w.shape[1] + np.arange(nc)] = 1.0
+            b2 = np.concatenate([np.zeros(w.shape[0], np.float32) if b is None else b, np.zeros(nc, np.float32)])
+            if one and k == 0:
+                b2[-1] = 1.0
+            out.append((w2, b2))
+        w, b = ws[-1], bs[-1]
+        cols = [w, pw] + ([_f32(pb).reshape(-1, 1)] if one else [])
+        wl = np.concatenate(cols, axis=1)
+        bl = b if b is not None else (None if pb is None else _f32(pb))
+        out.append((wl, bl))
+        return out
+    # convolutions
+    if (pw.kh, pw.kw, pw.ph, pw.pw) != (1, 1, 0, 0):
+        raise EngineError(UNSUPPORTED, "projection block: P must be a 1x1 convolution without padding")
+    first = function[0][0]
+    if (first.sh, first.sw) != (pw.sh, pw.sw) or first.ic != pw.ic or (first.ih, first.iw) != (pw.ih, pw.iw):
+        raise EngineError(UNSUPPORTED, "projection block: P's stride and input must be those of F's first layer")
+    cz = first.ic
+    for k, (w, _) in enumerate(function):
+        if w.ph >= w.kh or w.pw >= w.kw:
+            raise EngineError(UNSUPPORTED, "projection block: a layer of F has no tap on its own input pixel")
+        if k > 0 and (w.sh, w.sw) != (1, 1):
+            raise EngineError(UNSUPPORTED, "projection block: only F's first layer may be strided")
+        if k > 0 and ((w.oh, w.ow) != (w.ih, w.iw)):
+            raise EngineError(UNSUPPORTED, "projection block: F's later layers must keep the image size")
+    if (pw.oh, pw.ow) != (first.oh, first.ow) or pw.oc != function[-1][0].oc:
+        raise EngineError(SHAPE, "projection block: P must map the block input to the block output")
+    one = 1 if (pw.bias is not None and function[-1][0].bias is not None) else 0   # as for Linear: a channel of ones
+    nc = cz + one
+    for k, (w, _) in enumerate(function):
+        last = k == n - 1
+        ic2 = w.ic + (0 if k == 0 else nc)
+        oc2 = w.oc + (0 if last else nc)
+        ker = np.zeros((oc2, ic2, w.kh, w.kw), np.float32)
+        ker[: w.oc, : w.ic] = w.weight
+        if last:
+            ker[: w.oc, w.ic: w.ic + cz, w.ph, w.pw] = pw.weight[:, :, 0, 0]
+            if one:
+                ker[: w.oc, w.ic + cz, w.ph, w.pw] = pw.bias
+        elif k == 0:
+            ker[w.oc + np.arange(cz), np.arange(cz), w.ph, w.pw] = 1.0
+        else:
+            ker[w.oc + np.arange(nc), w.ic + np.arange(nc), w.ph, w.pw] = 1.0
+        b = np.zeros(w.oc, np.float32) if w.bias is None else w.bias
+        if last:
+            b2 = w.bias if w.bias is not None else pw.bias
+        else:
+            b2 = np.concatenate([b, np.zeros(nc, np.float32)])
+            if one and k == 0:
+                b2[-1] = 1.0
+        out.append((Conv2d(ker, None if b2 is None else np.asarray(b2, np.float32), (w.sh, w.sw), (w.ph, w.pw), (w.ih, w.iw)), None))
+    return out
+
+
 class Network:
     """Sequential ReLU network description (host side): weights[k] is a [out, in] row-major matrix (Linear) or a
     Conv2d; every layer but the last is followed by a ReLU."""

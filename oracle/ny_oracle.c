@@ -879,21 +879,26 @@ int nyo_beta_crown_bound_dual(const nyo_net *net, const float *in_lo, const floa
                               const float *alpha_up, float *out_lo, float *out_hi) {
     int L = net->n_linear;
     lbounds cur = lb_identity(net->dims[L]);
-    lbounds stash; memset(&stash, 0, sizeof(stash));
-    int stash_for = -1;
+    /* open identity branches, innermost last: blocks may nest, and several blocks may start at the same variable */
+    enum { MAX_OPEN = 16 };
+    lbounds stashes[MAX_OPEN]; memset(stashes, 0, sizeof(stashes));
+    int stash_src[MAX_OPEN], n_open = 0;
     for (int k = L - 1; k >= 0; --k) {
         lin_layer Lk = net_layer(net, k);
         if (skip_of(net, k) >= 0) {
             /* residual block: the coefficients at pre_k also multiply relu(pre_j) directly; keep a copy until the pass
              * reaches that variable (A_in = backward_F(A) + A, ny-core/src/gemm.rs:1640-1669) */
-            stash = lb_alloc(cur.rows, cur.n, cur.le != NULL);
-            memcpy(stash.la, cur.la, 4 * (size_t)cur.rows * cur.n); memcpy(stash.ua, cur.ua, 4 * (size_t)cur.rows * cur.n);
-            if (cur.le) { memcpy(stash.le, cur.le, 4 * (size_t)cur.rows * cur.n); memcpy(stash.ue, cur.ue, 4 * (size_t)cur.rows * cur.n); }
-            stash_for = skip_of(net, k);
+            if (n_open == MAX_OPEN) { lb_free(&cur); for (int i = 0; i < n_open; ++i) lb_free(&stashes[i]); return -2; }
+            lbounds st = lb_alloc(cur.rows, cur.n, cur.le != NULL);
+            memcpy(st.la, cur.la, 4 * (size_t)cur.rows * cur.n); memcpy(st.ua, cur.ua, 4 * (size_t)cur.rows * cur.n);
+            if (cur.le) { memcpy(st.le, cur.le, 4 * (size_t)cur.rows * cur.n); memcpy(st.ue, cur.ue, 4 * (size_t)cur.rows * cur.n); }
+            stashes[n_open] = st; stash_src[n_open] = skip_of(net, k); ++n_open;
         }
         lbounds nxt = linear_backward(&Lk, &cur);
         lb_free(&cur); cur = nxt;
-        if (stash_for >= 0 && stash_for == k - 1) {
+        for (int oi = 0; oi < n_open; ) {
+            if (stash_src[oi] != k - 1) { ++oi; continue; }
+            lbounds stash = stashes[oi];
             /* cur holds the coefficients of relu(pre_{k-1}): the identity branch joins.  The rounded sums carry their
              * exact residual and both branches' certified errors in the error matrices (RESIDENT_SEG_MERGE). */
             size_t cnt = (size_t)cur.rows * cur.n;
@@ -908,7 +913,9 @@ int nyo_beta_crown_bound_dual(const nyo_net *net, const float *in_lo, const floa
                     if (E) E[i] = (e == 0.0) ? 0.0f : publish_error_up_normal(e);
                 }
             }
-            lb_free(&stash); stash_for = -1;
+            lb_free(&stash);
+            for (int m = oi + 1; m < n_open; ++m) { stashes[m - 1] = stashes[m]; stash_src[m - 1] = stash_src[m]; }
+            --n_open;
         }
         if (k > 0 && relu_after(net, k - 1)) {
             int r = k - 1, n = net->dims[k];

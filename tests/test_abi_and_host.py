@@ -71,3 +71,42 @@ def test_workloads_are_reproducible_and_well_formed():
         keys = set(zip(s1["relu"][d].tolist(), s1["neuron"][d].tolist()))
         assert len(keys) == 8
     assert set(np.unique(s1["sign"])) <= {-1, 1}
+
+
+def test_projection_block_lowering_is_exact():
+    """lower_projection_block (GpuResnetSegment::ResidualProj, crates/ny-core/src/gemm.rs:1658-1669): the widened
+    sequential layers compute F(z) + P(z) for z >= 0 up to binary64 summation order, for Linear and Conv2d blocks, with
+    P's bias carried on a constant neuron when both branches have one; blocks outside the supported form are declined."""
+    from ny_b200 import Conv2d, EngineError, lower_projection_block
+
+    g = np.random.Generator(np.random.PCG64(5))
+    f32 = lambda *s: g.standard_normal(s).astype(np.float32)
+    relu = lambda x: np.maximum(x, 0)
+    nz, h, no = 6, 9, 7
+    W1, b1, W2, W3, b3, Wp, bp = f32(h, nz), f32(h), f32(h, h), f32(no, h), f32(no), f32(no, nz), f32(no)
+    low = lower_projection_block([(W1, b1), (W2, None), (W3, b3)], (Wp, bp))
+    z = np.abs(g.standard_normal((5, nz)))
+    ref = relu(relu(z @ W1.astype(np.float64).T + b1) @ W2.astype(np.float64).T) @ W3.astype(np.float64).T + b3 \
+        + z @ Wp.astype(np.float64).T + bp
+    x = z
+    for k, (w, b) in enumerate(low):
+        x = x @ w.astype(np.float64).T + (0 if b is None else b.astype(np.float64))
+        if k < len(low) - 1:
+            x = relu(x)
+    assert np.abs(x - ref).max() < 1e-12
+    assert low[0][0].shape == (h + nz + 1, nz) and low[-1][0].shape == (no, h + nz + 1)   # z and the constant ride along
+    assert np.array_equal(low[-1][1], b3)                                              # no fp32 sum of two biases
+    cz, c1, co = 3, 4, 5
+    F1 = Conv2d(f32(c1, cz, 3, 3), f32(c1), (2, 2), (1, 1), (8, 8))
+    F2 = Conv2d(f32(co, c1, 3, 3), f32(co), (1, 1), (1, 1), (4, 4))
+    P = Conv2d(f32(co, cz, 1, 1), f32(co), (2, 2), (0, 0), (8, 8))
+    lowc = lower_projection_block([(F1, None), (F2, None)], (P, None))
+    z = np.abs(g.standard_normal((4, cz * 64)))
+    ref = F2.apply(relu(F1.apply(z))) + P.apply(z)
+    assert np.abs(lowc[1][0].apply(relu(lowc[0][0].apply(z))) - ref).max() < 1e-12
+    with pytest.raises(EngineError):
+        lower_projection_block([(W1, b1)], (Wp, bp))                                   # a one-layer F
+    with pytest.raises(EngineError):
+        lower_projection_block([(F1, None), (F2, None)], (Conv2d(f32(co, cz, 3, 3), None, (2, 2), (1, 1), (8, 8)), None))
+    with pytest.raises(EngineError):
+        lower_projection_block([(F1, None), (W3, None)], (P, None))                    # mixed layer kinds

@@ -245,3 +245,136 @@ def test_resnet_full_size_against_the_native_oracle(eng, oracle):
         checked += 1
     assert checked >= 3
     eng.release_network(nid)
+
+
+def _skip_mlp(skips, seed=71, n_in=12, hidden=20, depth=6, n_out=4, eps=0.05, n_fix=3):
+    """A ReLU MLP with the given identity branches {k: j} and a margin specification."""
+    from ny_b200 import Network
+
+    base = W.make_mlp([n_in] + [hidden] * depth + [n_out], seed)
+    net = Network(base.weights, base.biases, skips)
+    g = np.random.Generator(np.random.PCG64(seed + 1))
+    x0 = g.uniform(-1, 1, n_in).astype(np.float32)
+    y = W.forward(net, x0)
+    c = int(np.argmax(y))
+    spec = np.zeros((n_out - 1, n_out), np.float32)
+    for i, j in enumerate([j for j in range(n_out) if j != c]):
+        spec[i, c], spec[i, j] = 1.0, -1.0
+    return W.Workload("skip-mlp", net, x0, (x0 - eps).astype(np.float32), (x0 + eps).astype(np.float32), spec, n_fix, seed)
+
+
+@pytest.mark.parametrize("skips", [{3: 1, 5: 0}, {3: 0, 5: 2}, {3: 1, 5: 1}], ids=["nested", "overlapping", "shared-source"])
+def test_nested_overlapping_and_shared_source_skips_match_oracle(eng, oracle, skips):
+    """Identity branches that nest (a block inside a block), overlap (the second starts inside the first and ends
+    after it) or start at the same variable: the interval pass, the bound batch in both child-bound modes and the
+    attack against the oracle's native evaluation of the same network (identity branches joined in place), and the
+    unsplit domain against sampled executions."""
+    wl = _skip_mlp(skips)
+    nat = oracle.Net(wl.net.weights, wl.net.biases, skips=wl.net.skips)
+    nid = eng.register_network(wl.net)
+    pl, pu = eng.ibp_forward_gpu(nid, wl.in_lo, wl.in_hi)
+    nl, nu = oracle.ibp_forward(nat, wl.in_lo, wl.in_hi)
+    n = wl.net.n_pre
+    tol = IBP_REL * np.maximum(np.abs(nl[:n]), np.abs(nu[:n])) + 1e-7
+    assert np.all(np.abs(pl[0] - nl[:n]) <= tol) and np.all(np.abs(pu[0] - nu[:n]) <= tol)
+    rl, ru = pl[0].copy(), pu[0].copy()
+    D, S = 24, wl.spec.shape[0]
+    splits, ns = W.draw_domains(wl, rl, ru, D)
+    ns = ns.copy()
+    ns[0] = 0
+    rl2 = np.concatenate([rl, np.full(S, -np.inf, np.float32)])
+    ru2 = np.concatenate([ru, np.full(S, np.inf, np.float32)])
+    ospec = nat.with_spec(wl.spec)
+    for mode in (0, 1):
+        glo, ghi, ginf = eng.bab_bound_batch(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, splits, ns, mode=mode)
+        olo, ohi, oinf, _ = oracle.bab_bound_batch(ospec, wl.in_lo, wl.in_hi, rl2, ru2, splits, ns, mode)
+        assert np.array_equal(ginf != 0, oinf != 0)
+        f = oinf == 0
+        assert f.sum() > D // 2
+        assert _rel(np.concatenate([glo[f], ghi[f]], axis=1), np.concatenate([olo[f], ohi[f]], axis=1)) <= REL_TOL
+    mn = W.sample_min_margin(wl, 20000, 123, splits[0][:0])
+    assert np.all(glo[0] <= mn)
+    # the attack's gradient follows the same branches: its reported objective is the network's value at its point
+    g = np.random.Generator(np.random.PCG64(9))
+    x0 = (wl.in_lo + g.random((16, len(wl.in_lo)), dtype=np.float32) * (wl.in_hi - wl.in_lo)).astype(np.float32)
+    best, bx, _ = eng.pgd_attack(nid, wl.spec, wl.in_lo, wl.in_hi, x0, 10, 0.0125)
+    true = (W.forward(wl.net, bx) @ wl.spec.astype(np.float64).T).min(axis=1)
+    start = (W.forward(wl.net, x0) @ wl.spec.astype(np.float64).T).min(axis=1)
+    assert np.allclose(best, true, rtol=1e-4, atol=1e-5) and best.mean() < start.mean()
+    # and the parameter optimisation's adjoint: optimised bounds stay sound and do not get worse
+    eng.batch_upload(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, splits, ns, mode=1)
+    eng.batch_run()
+    plo, _, pinf = eng.batch_download()
+    eng.batch_optimize(8, 0.1, 0.05)
+    qlo, _, _ = eng.batch_download()
+    ok = pinf == 0
+    scale = np.abs(plo[ok]).max()
+    assert np.all(qlo[ok] >= plo[ok] - 1e-5 * scale) and qlo[ok].sum() > plo[ok].sum()
+    assert np.all(qlo[0] <= mn)
+    eng.release_network(nid)
+
+
+@pytest.mark.parametrize("kind", ["linear", "conv"])
+def test_projection_block_lowering_bounds(eng, oracle, kind):
+    """out = F(z) + P(z) (GpuResnetSegment::ResidualProj, crates/ny-core/src/gemm.rs:1658-1669) registered through
+    lower_projection_block: the lowered network is the same function, its device bounds match the oracle on the same
+    layers and enclose sampled executions of the ORIGINAL two-branch network."""
+    from ny_b200 import Conv2d, Network, lower_projection_block
+
+    g = np.random.Generator(np.random.PCG64(77))
+    rn = lambda *s: (g.standard_normal(s) * np.sqrt(2.0 / np.prod(s[1:]))).astype(np.float32)
+    if kind == "linear":
+        n0, nz, h, no, nout = 10, 12, 16, 14, 4
+        stem = (rn(nz, n0), rn(nz))
+        F = [(rn(h, nz), rn(h)), (rn(no, h), rn(no))]
+        P = (rn(no, nz), rn(no))
+        head = (rn(nout, no), rn(nout))
+        low = lower_projection_block(F, P)
+        net = Network([stem[0]] + [w for w, _ in low] + [head[0]], [stem[1]] + [b for _, b in low] + [head[1]])
+
+        def original(x):
+            z = np.maximum(x @ stem[0].astype(np.float64).T + stem[1], 0)
+            f = np.maximum(z @ F[0][0].astype(np.float64).T + F[0][1], 0) @ F[1][0].astype(np.float64).T + F[1][1]
+            out = np.maximum(f + z @ P[0].astype(np.float64).T + P[1], 0)
+            return out @ head[0].astype(np.float64).T + head[1]
+    else:
+        c0, cz, c1, co, nout = 2, 3, 4, 5, 4
+        stem = Conv2d(rn(cz, c0, 3, 3), rn(cz), (1, 1), (1, 1), (8, 8))
+        F1 = Conv2d(rn(c1, cz, 3, 3), rn(c1), (2, 2), (1, 1), (8, 8))
+        F2 = Conv2d(rn(co, c1, 3, 3), rn(co), (1, 1), (1, 1), (4, 4))
+        P = Conv2d(rn(co, cz, 1, 1), rn(co), (2, 2), (0, 0), (8, 8))
+        head = (rn(nout, co * 16), rn(nout))
+        low = lower_projection_block([(F1, None), (F2, None)], (P, None))
+        n0 = c0 * 64
+        net = Network([stem] + [w for w, _ in low] + [head[0]], [None] + [None for _ in low] + [head[1]])
+
+        def original(x):
+            z = np.maximum(stem.apply(x), 0)
+            out = np.maximum(F2.apply(np.maximum(F1.apply(z), 0)) + P.apply(z), 0)
+            return out @ head[0].astype(np.float64).T + head[1]
+    x0 = g.uniform(0.2, 0.8, n0).astype(np.float32)
+    lo, hi = (x0 - 0.03).astype(np.float32), (x0 + 0.03).astype(np.float32)
+    xs = lo + g.random((4000, n0)) * (hi.astype(np.float64) - lo)
+    assert np.abs(W.forward(net, xs[:64]) - original(xs[:64])).max() < 1e-9       # the same function
+    spec = np.zeros((nout - 1, nout), np.float32)
+    spec[:, 0] = 1.0
+    spec[np.arange(nout - 1), 1 + np.arange(nout - 1)] = -1.0
+    wl = W.Workload("proj", net, x0, lo, hi, spec, 3, 77)
+    nid = eng.register_network(net)
+    nat = oracle.Net(net.weights, net.biases)
+    pl, pu = eng.ibp_forward_gpu(nid, lo, hi)
+    rl, ru = pl[0].copy(), pu[0].copy()
+    D, S = 16, spec.shape[0]
+    splits, ns = W.draw_domains(wl, rl, ru, D)
+    ns = ns.copy()
+    ns[0] = 0
+    glo, ghi, ginf = eng.bab_bound_batch(nid, spec, lo, hi, rl, ru, splits, ns, mode=1)
+    rl2 = np.concatenate([rl, np.full(S, -np.inf, np.float32)])
+    ru2 = np.concatenate([ru, np.full(S, np.inf, np.float32)])
+    olo, ohi, oinf, _ = oracle.bab_bound_batch(nat.with_spec(spec), lo, hi, rl2, ru2, splits, ns, 1)
+    assert np.array_equal(ginf != 0, oinf != 0)
+    f = oinf == 0
+    assert _rel(np.concatenate([glo[f], ghi[f]], axis=1), np.concatenate([olo[f], ohi[f]], axis=1)) <= REL_TOL
+    margins = original(xs) @ spec.astype(np.float64).T
+    assert np.all(glo[0] <= margins.min(axis=0)) and np.all(ghi[0] >= margins.max(axis=0))
+    eng.release_network(nid)
