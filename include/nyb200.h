@@ -124,8 +124,9 @@ typedef struct nyb200_layer_desc {
     int32_t kernel_h, kernel_w, stride_h, stride_w, pad_h, pad_w;
     /* Residual connection (GpuResnetSegment::Residual, crates/ny-core/src/gemm.rs:1640-1669): 0 = none;
      * j + 1 = the post-activation output of layer j (j <= this layer - 2, same width as this layer's output)
-     * is added to this layer's output before its ReLU: pre = W z + b + relu(pre_j).  Skips must not overlap
-     * or nest.  Supported by the interval pass, the bound batch entry points, the parameter optimisation and the
+     * is added to this layer's output before its ReLU: pre = W z + b + relu(pre_j).  Blocks may nest, overlap
+     * or start at the same layer.  A projection block (ResidualProj, :1658-1669) is registered as the sequential
+     * layers the host mirror's lower_projection_block produces.  Supported by the interval pass, the bound batch entry points, the parameter optimisation and the
      * attack, and the CROWN-IBP pipeline. */
     int32_t skip_from;
 } nyb200_layer_desc;
