@@ -260,12 +260,27 @@ def _margin(lower, thr, owner, n_clauses):
     return out
 
 
-def select_fsb(eng, net_id, net, prop: Property, inh_lo, inh_hi, take, open_idx, k: int = 3):
-    """Filtered smart branching for the open domains `open_idx` of the batch `take` that has just been run (and
+KFSB_REDUCE = {"min": np.minimum, "max": np.maximum, "mean": lambda a, b: (a + b) * np.float32(0.5)}
+
+
+def kfsb_fallback_index(depth: int, n_candidates: int) -> int:
+    """Which candidate a domain takes when none of its trial splits produced a usable score (the random fallback of
+    select_kfsb_neuron, beta_crown/engine/branching/sequential.rs:535-552): a deterministic choice keyed by the
+    domain's depth.  The reference keys its own by a SipHash of the depth; the key differs, the rule (any candidate
+    is a valid split, the same domain always takes the same one) does not."""
+    return int((np.uint64(depth) * np.uint64(0x9E3779B97F4A7C15) >> np.uint64(33)) % np.uint64(max(n_candidates, 1)))
+
+
+def select_fsb(eng, net_id, net, prop: Property, inh_lo, inh_hi, take, open_idx, k: int = 3, reduce: str = "min"):
+    """Filtered smart branching (kFSB) for the open domains `open_idx` of the batch `take` that has just been run (and
     scored with BaBSR): every candidate of fsb_candidates is tried - both children bounded in one device batch - and
-    the split whose worse child has the best margin wins (fsb_worst_case_score,
-    beta_crown/config/beta_config.rs:1722-1755); within 1e-6 the larger BaBSR score decides.  Returns
+    the two children's margins are combined by `reduce` (KfsbReduceOp, beta_crown/config/beta_config.rs:1942-1953:
+    "min" the worse child - conservative, the default; "max" the better child; "mean" their midpoint;
+    sequential.rs:482-507); the best combined score wins, within 1e-6 the larger BaBSR score decides, NaN scores never
+    win.  A domain all of whose trials are NaN takes the candidate kfsb_fallback_index names.  Returns
     {domain index: (relu, neuron)}; a domain without candidates is missing from it."""
+    if reduce not in KFSB_REDUCE:
+        raise ValueError(f"unknown kFSB reduce operator {reduce!r}")
     spec, thr, owner = _rows(prop)
     n_clauses = len(prop.violation)
     main, backup = eng.batch_branch_scores(with_backup=True)
@@ -286,21 +301,27 @@ def select_fsb(eng, net_id, net, prop: Property, inh_lo, inh_hi, take, open_idx,
     lower, _, infeasible = eng.bab_bound_batch(net_id, spec, prop.in_lo, prop.in_hi, inh_lo, inh_hi, splits, ns, mode=1)
     m = _margin(lower, thr, owner, n_clauses)
     m = np.where(infeasible != 0, np.float32(np.inf), m)       # an empty child needs no further work
-    worst = np.minimum(m[0::2], m[1::2])
-    best = {}
-    for (d, o, r, j), w in zip(meta, worst):
+    with np.errstate(invalid="ignore"):
+        score = KFSB_REDUCE[reduce](m[0::2], m[1::2])
+    best, tried = {}, {}
+    for (d, o, r, j), w in zip(meta, score):
+        tried.setdefault(d, []).append((r, j))
         if np.isnan(w):
             continue
         cur = best.get(d)
         if cur is None or w > cur[0] + 1e-6 or (abs(w - cur[0]) <= 1e-6 and main[d][o] > cur[1]):
             best[d] = (float(w), float(main[d][o]), r, j)
-    return {d: (v[2], v[3]) for d, v in best.items()}
+    out = {d: (v[2], v[3]) for d, v in best.items()}
+    for d, cands in tried.items():
+        if d not in out:
+            out[d] = cands[kfsb_fallback_index(len(take[d]), len(cands))]
+    return out
 
 
 def verify(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: int = 64, max_domains: int = 1 << 20,
            pgd_restarts: int = 256, pgd_steps: int = 50, optimize_iterations: int = 0, branching: int = 1,
            timeout_s: float | None = None, metrics_jsonl=None, checkpoint=None, resume=None,
-           warm_start: bool = True, fsb_k: int = 3, dist=None, dist_device="cpu") -> VerifyResult:
+           warm_start: bool = True, fsb_k: int = 3, kfsb_reduce: str = "min", dist=None, dist_device="cpu") -> VerifyResult:
     """metrics_jsonl: append one JSON record per round; checkpoint: path that receives the open frontier whenever the
     run stops unresolved (round limit, timeout, domain limit); resume: path of such a dump to continue from (the attack
     and the root bound are skipped).
@@ -309,7 +330,8 @@ def verify(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: i
     (beta_crown/config/beta_config.rs:1244), bounds each domain once with multipliers at zero: sound, but the search
     may then end "unknown" on properties that need the multipliers; 20 is the reference's root-level count);
     branching: 0 widest interval, 1 intercept score, 2 BaBSR, 3 filtered smart branching over the fsb_k best BaBSR and
-    intercept candidates (2 and 3: Linear layers only); warm_start: with optimisation on, children start from their
+    intercept candidates, the children's margins combined by kfsb_reduce ("min" | "max" | "mean") (2 and 3: Linear
+    layers only); warm_start: with optimisation on, children start from their
     parent's optimised slopes and split multipliers instead of the heuristic slopes and zero.
     dist: an initialised torch.distributed module, one process per GPU: every rank runs this function with the same
     arguments, rank 0 attacks and bounds the root, and from then on every rank bounds its own shard of the frontier;
@@ -416,7 +438,7 @@ def verify(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: i
                 relu, neuron, _ = eng.batch_select_branch(2 if branching == 3 else branching)
                 if branching == 3:   # filtered smart branching: the BaBSR / intercept candidates are tried on the device
                     take = [splits[d, : ns[d]] for d in range(D)]
-                    for d, (r, j) in select_fsb(eng, net_id, net, prop, inh_lo, inh_hi, take, open_idx, fsb_k).items():
+                    for d, (r, j) in select_fsb(eng, net_id, net, prop, inh_lo, inh_hi, take, open_idx, fsb_k, kfsb_reduce).items():
                         relu[d], neuron[d] = r, j
                 if np.any(relu[open_idx] < 0):
                     # every neuron of some domain is fixed and its bound still does not decide it: without a witness the

@@ -110,3 +110,49 @@ def test_projection_block_lowering_is_exact():
         lower_projection_block([(F1, None), (F2, None)], (Conv2d(f32(co, cz, 3, 3), None, (2, 2), (1, 1), (8, 8)), None))
     with pytest.raises(EngineError):
         lower_projection_block([(F1, None), (W3, None)], (P, None))                    # mixed layer kinds
+
+
+def test_kfsb_reduce_operators_and_fallback():
+    """select_fsb's combination of the two children's margins (KfsbReduceOp: min / max / mean,
+    beta_crown/engine/branching/sequential.rs:482-507), its tie rule, NaN handling and the depth-keyed fallback
+    (:535-552), against a stand-in engine that returns canned scores and child bounds."""
+    from ny_b200 import SPLIT_DTYPE, bab, formats
+
+    class FakeEngine:
+        def __init__(self, lower):
+            self.lower = lower
+
+        def batch_branch_scores(self, with_backup=True):
+            main = np.full((1, 6), -1.0, np.float32)
+            main[0, [1, 3, 4]] = [0.5, 0.9, 0.7]          # three candidates, BaBSR order 3, 4, 1
+            return main, np.zeros((1, 6), np.float32)
+
+        def bab_bound_batch(self, net_id, spec, lo, hi, inh_lo, inh_hi, splits, ns, mode=1):
+            assert len(ns) == 6 and np.all(ns == 1)
+            self.asked = [(int(s[0]["neuron"]), int(s[0]["sign"])) for s in splits]
+            return self.lower.reshape(6, 1), None, np.zeros(6, np.int32)
+
+    class Net:
+        dims = np.array([2, 6, 1])
+
+    prop = formats.Property(np.zeros(2, np.float32), np.ones(2, np.float32), [[formats.Atom(np.array([-1.0], np.float32), 0.0)]])
+    take = [np.zeros(0, SPLIT_DTYPE)]
+    # children (active, inactive) of candidates 3, 4, 1 in that order
+    lower = np.array([-1.0, -5.0, -2.0, -3.0, -4.0, -0.5], np.float32)
+    picks = {}
+    for op in ("min", "max", "mean"):
+        eng = FakeEngine(lower)
+        picks[op] = bab.select_fsb(eng, 0, Net, prop, None, None, take, [0], k=3, reduce=op)[0]
+        assert eng.asked == [(3, 1), (3, -1), (4, 1), (4, -1), (1, 1), (1, -1)]
+    assert picks == {"min": (0, 4), "max": (0, 1), "mean": (0, 1)}     # min: -5, -3, -4; max: -1, -2, -0.5; mean: -3, -2.5, -2.25
+    # ties within 1e-6 go to the larger BaBSR score; NaN never wins
+    eng = FakeEngine(np.array([-2.0, -2.0, -2.0, -2.0, np.nan, -1.0], np.float32))
+    assert bab.select_fsb(eng, 0, Net, prop, None, None, take, [0], k=3)[0] == (0, 3)
+    # every trial NaN: the depth-keyed fallback picks one of the candidates, the same one every time
+    eng = FakeEngine(np.full(6, np.nan, np.float32))
+    a = bab.select_fsb(eng, 0, Net, prop, None, None, take, [0], k=3)[0]
+    b = bab.select_fsb(eng, 0, Net, prop, None, None, take, [0], k=3)[0]
+    assert a == b and a in [(0, 3), (0, 4), (0, 1)]
+    assert a == [(0, 3), (0, 4), (0, 1)][bab.kfsb_fallback_index(0, 3)]
+    with pytest.raises(ValueError):
+        bab.select_fsb(eng, 0, Net, prop, None, None, take, [0], k=3, reduce="median")
