@@ -513,6 +513,12 @@ int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, float
         return (double)(K + 2) * 1.1102230246251565e-16 * 1.000001;
     };
     auto q_ds = [&](int lin_k) { return (lin_k == 0 && shared_box) ? 0L : np; };
+    // The concretisation rides in the epilogue of Linear_0's contraction when that contraction is a plain tensor-core
+    // launch and nothing joins its result afterwards (no checkpoint, no identity branch ending at the input).
+    const bool fuse_conc = tensor && e->fuse_chain && !ckpt && !net.is_conv(0);
+    int conc_slots = 0;
+    double *conc_part = nullptr;
+    int *conc_bad = nullptr;
     int k_start = L - 1;
     if (fused) {
         const bool timed = e->timing.per_kernel && !e->timing.cev_used;
@@ -570,6 +576,18 @@ int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, float
                 if (!cols) return NYB200_ERR_OOM;
             }
             launch_conv_transpose(e, g, M, cur, p.lda, dst, ldd, nv.W[k], R, zin_lo, zin_hi, zin_ds, p.rpen, cols);
+        } else if (tensor && k == 0 && fuse_conc) {
+            // the last contraction concretises in its epilogue: the finished rows are never written unless asked for
+            ConcFuse cf;
+            cf.on = 1; cf.store = p.keep_final ? 1 : 0; cf.R = R; cf.S = S;
+            cf.slots = 2 * ((N + 255) / 256);
+            cf.in_lo = p.in_lo; cf.in_hi = p.in_hi; cf.box_ds = b.box_stride;
+            cf.part = (double *)ws_get(e, "conc_part", (size_t)M * cf.slots * 16);
+            cf.bad = (int *)ws_get(e, "conc_bad", (size_t)M * 4);
+            if (!cf.part || !cf.bad) return NYB200_ERR_OOM;
+            NYB_CUDA(e, cudaMemsetAsync(cf.bad, 0, (size_t)M * 4, e->stream));
+            NYB_TRY(launch_umma(e, net.umma[k], M, cur, p.lda, dst, ldd, derr, 0, &cf));
+            conc_slots = cf.slots; conc_part = cf.part; conc_bad = cf.bad;
         } else if (tensor) {
             NYB_TRY(launch_umma(e, net.umma[k], M, cur, p.lda, dst, ldd, derr));
         } else {
@@ -587,8 +605,12 @@ int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, float
         float *t = cur; cur = nxt; nxt = t;
     }
     p.a_final = cur;
-    launch_concretize(e, M, R, S, nv.dims[0], cur, p.lda, p.in_lo, p.in_hi, b.box_stride, p.rb, p.rabs, p.rpen, p.flags,
-                      p.out_lo, p.out_hi, p.min_lower, tensor ? e->refine_tol : 0.f);
+    if (conc_part)
+        launch_concretize_fused(e, M, R, S, conc_slots, conc_part, conc_bad, p.rb, p.rabs, p.rpen, p.flags, p.out_lo, p.out_hi,
+                                p.min_lower, tensor ? e->refine_tol : 0.f);
+    else
+        launch_concretize(e, M, R, S, nv.dims[0], cur, p.lda, p.in_lo, p.in_hi, b.box_stride, p.rb, p.rabs, p.rpen, p.flags,
+                          p.out_lo, p.out_hi, p.min_lower, tensor ? e->refine_tol : 0.f);
     NYB_CUDA(e, cudaGetLastError());
     return NYB200_OK;
 }

@@ -379,13 +379,15 @@ __global__ void __launch_bounds__(Cfg<NSUB>::THREADS, 1) k_chain(const __grid_co
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&bars[ACC_EMPTY]));
-                // ---- relaxation, row sums, split, hand-over.  One pass of the loop handles the thread's slices of two
-                // chunks, always out of acc[0 .. 2 CPT); the register array is then shifted down by two slices, so that
-                // the loop body exists once (unrolled over all chunks it does not fit the instruction cache).
+                // ---- relaxation, row sums, split, hand-over, one pair of chunks (one slot of the table ring) at a time.
+                // The loop is unrolled over the pairs so that every accumulator value is read from a fixed register
+                // (a rolled loop has to shift the register array down after every pair, which cost 14 instructions per
+                // coefficient, a quarter of the epilogue).
                 const long tb = (long)d * P.nps + Ly.relu_off;
                 const bool has_bias = Ly.bias != nullptr;
-#pragma unroll 1
-                for (int c2 = 0; c2 < nch && !dead; c2 += 2) {
+#pragma unroll
+                for (int c2 = 0; c2 < MAX_CHUNKS; c2 += 2) {
+                    if (c2 >= nch || dead) break;
                     const unsigned char *ts = nullptr;
                     int tslot = 0;
                     if constexpr (STAGED) {
@@ -420,12 +422,11 @@ __global__ void __launch_bounds__(Cfg<NSUB>::THREADS, 1) k_chain(const __grid_co
                                     }
                                     float4 au = make_float4(t0.x, t1.x, t2.x, t3.x);
                                     if (P.aup) au = *(const float4 *)(P.aup + tb + col);
-                                    const float *za = P.zabs + tb + col;
-                                    const int b0 = h2 * CPT + 4 * g;
-                                    o.x = relax_coeff_fast(upper, dir, dirf, acc[b0], t0, au.x, cj.x, za, bk.x, gi, gb, sp_);
-                                    o.y = relax_coeff_fast(upper, dir, dirf, acc[b0 + 1], t1, au.y, cj.y, za + 1, bk.y, gi, gb, sp_);
-                                    o.z = relax_coeff_fast(upper, dir, dirf, acc[b0 + 2], t2, au.z, cj.z, za + 2, bk.z, gi, gb, sp_);
-                                    o.w = relax_coeff_fast(upper, dir, dirf, acc[b0 + 3], t3, au.w, cj.w, za + 3, bk.w, gi, gb, sp_);
+                                    const int b0 = (c2 + h2) * CPT + 4 * g;
+                                    o.x = relax_coeff_fast(upper, dir, dirf, acc[b0], t0, au.x, cj.x, bk.x, gi, gb, sp_);
+                                    o.y = relax_coeff_fast(upper, dir, dirf, acc[b0 + 1], t1, au.y, cj.y, bk.y, gi, gb, sp_);
+                                    o.z = relax_coeff_fast(upper, dir, dirf, acc[b0 + 2], t2, au.z, cj.z, bk.z, gi, gb, sp_);
+                                    o.w = relax_coeff_fast(upper, dir, dirf, acc[b0 + 3], t3, au.w, cj.w, bk.w, gi, gb, sp_);
                                     if (Ly.to_global) *(float4 *)(P.A_out + m * P.lda + col) = o;
                                 }
                                 v[4 * g] = o.x; v[4 * g + 1] = o.y; v[4 * g + 2] = o.z; v[4 * g + 3] = o.w;
@@ -447,8 +448,6 @@ __global__ void __launch_bounds__(Cfg<NSUB>::THREADS, 1) k_chain(const __grid_co
                         if (lane == 0) mbar_arrive(smem_u32(&bars[T_EMPTY + tslot]));
                         ++tit;
                     }
-#pragma unroll
-                    for (int i = 0; i + 2 * CPT < C::VALS; ++i) acc[i] = acc[i + 2 * CPT];
                 }
             }
             if (dead) break;

@@ -282,7 +282,10 @@ static int crown_bounds_once(nyb200_engine *e, int net_id, const float *spec, in
     BatchPtrs ps;
     NYB_TRY(batch_ptrs(e, *net, bs, ps));
     if (e->error_channel == NYB200_ERRCH_REFERENCE) NYB_TRY(run_backward_ref(e, *net, bs, ps, -1));
-    else NYB_TRY(run_backward(e, *net, bs, ps, nullptr, 0, -1));
+    else {
+        ps.keep_final = true;   // nyb200_crown_input_coeffs reads the final pass's input-level rows
+        NYB_TRY(run_backward(e, *net, bs, ps, nullptr, 0, -1));
+    }
     k_accumulate_loose<<<1, 32, 0, st>>>(ps.min_lower, loose_acc);
     e->launches++;
     k_crown_final<<<(unsigned)((D + 255) / 256), 256, 0, st>>>(D, S, sp_ibp_lo, sp_ibp_hi, sp_f_lo, sp_f_hi, ps.out_lo, ps.out_hi,

@@ -40,6 +40,19 @@ struct ConvGeom {
 
 // Per-layer operands of the tcgen05 contraction: W split into TF32 high/low parts, transposed to
 // [N x kpad] (K contiguous, zero padded to a multiple of 32) with one TMA tensor map each.
+// Concretisation fused into the epilogue of the last contraction (k_umma_tf32x3): every epilogue thread routes its
+// slice of the finished coefficient row against the input box (sign-routed binary64 products, as k_concretize) and
+// leaves the slice's sum and magnitude sum in its own slot; k_concretize_fused adds a row's slots in a fixed order.
+struct ConcFuse {
+    int on = 0;
+    int store = 0;            // also write the coefficient rows (a later call reads them)
+    int R = 0, S = 0, slots = 0;
+    const float *in_lo = nullptr, *in_hi = nullptr;
+    long box_ds = 0;
+    double *part = nullptr;   // [M x slots x 2]
+    int *bad = nullptr;       // [M], cleared by the caller
+};
+
 struct UmmaLayer {
     float *wh = nullptr, *wl = nullptr;
     int K = 0, N = 0, kpad = 0;
@@ -198,6 +211,7 @@ struct BatchPtrs {
     float *out_lo, *out_hi, *min_lower;
     int lda;
     float *a_final = nullptr;  // set by run_backward: the coefficients on the input box, [D*R x lda]
+    bool keep_final = false;   // the caller reads a_final afterwards: the last contraction must store its rows
     float *alpha_up = nullptr; // dual alpha: the upper path's own lower slopes [D x nps], or null (shared with the lower path)
 };
 int batch_ptrs(nyb200_engine *e, const Net &net, const Batch &b, BatchPtrs &p);
@@ -282,7 +296,10 @@ int umma_prepare_layer(nyb200_engine *e, const float *W, int K, int N, UmmaLayer
 // a_plane > 0 selects the transposed-convolution form: GEMM row r = (m, p) with p < a_plane, operand element
 // k at A[m * lda + k * a_plane + p], result column n at C[(m * N + n) * a_plane + p] (ldc unused).
 int launch_umma(nyb200_engine *e, const UmmaLayer &L, int M, const float *A, int lda, float *C, int ldc, int *err,
-                int a_plane = 0);
+                int a_plane = 0, const ConcFuse *cf = nullptr);
+void launch_concretize_fused(nyb200_engine *e, int M, int R, int S, int slots, const double *part, const int *bad,
+                             const double *rb, const double *rabs, const double *rpen, int *flags, float *out_lo,
+                             float *out_hi, float *min_lower, float loose_tol);
 double umma_eps(int K, int chain = 0);
 // Builds the forward-pass operand of Linear_k: the [n_in x 2 n_out] matrix (W+^T | W-^T).
 int umma_prepare_forward_layer(nyb200_engine *e, const float *W, int n_in, int n_out, UmmaLayer *out);

@@ -933,6 +933,45 @@ void launch_concretize(nyb200_engine *e, int M, int R, int S, int n0, const floa
     NYB_COUNT(e);
 }
 
+// Second half of the fused concretisation: a row's slices, left by the last contraction's epilogue, added in slot
+// order (so that the result does not depend on which CTA finished first), then the same closing arithmetic as
+// k_concretize.
+__global__ void k_concretize_fused(int M, int R, int S, int slots, const double *__restrict__ part, const int *__restrict__ badf,
+                                   const double *__restrict__ rb, const double *__restrict__ rabs,
+                                   const double *__restrict__ rpen, float *__restrict__ out_lo, float *__restrict__ out_hi) {
+    int m = blockIdx.x * blockDim.x + threadIdx.x;
+    if (m >= M) return;
+    const int d = m / R, rr = m % R;
+    const bool upper = rr >= S;
+    double s = 0.0, sa = 0.0;
+    for (int i = 0; i < slots; ++i) { s += part[((long)m * slots + i) * 2]; sa += part[((long)m * slots + i) * 2 + 1]; }
+    const bool bad = badf[m] != 0;
+    double tot_abs = sa + rabs[m] + fabs(rb[m]);
+    double slack = tot_abs * 9.094947017729282e-13;  // 2^-40 >> (number of binary64 additions) * 2^-53
+    if (!upper) {
+        double x = rb[m] + s - rpen[m] - slack;
+        out_lo[(long)d * S + rr] = (bad || isnan(x)) ? -INFINITY : __double2float_rd(x);
+    } else {
+        double x = rb[m] + s + rpen[m] + slack;
+        out_hi[(long)d * S + (rr - S)] = (bad || isnan(x)) ? INFINITY : __double2float_ru(x);
+    }
+}
+
+void launch_concretize_fused(nyb200_engine *e, int M, int R, int S, int slots, const double *part, const int *bad,
+                             const double *rb, const double *rabs, const double *rpen, int *flags, float *out_lo,
+                             float *out_hi, float *min_lower, float loose_tol) {
+    k_concretize_fused<<<(unsigned)((M + 255) / 256), 256, 0, e->stream>>>(M, R, S, slots, part, bad, rb, rabs, rpen, out_lo, out_hi);
+    NYB_COUNT(e);
+    int D = M / R;
+    if (loose_tol > 0.f) {
+        k_count_loose<<<(D + 255) / 256, 256, 0, e->stream>>>(D, S, R, out_lo, out_hi, rpen, flags, loose_tol,
+                                                              (int *)min_lower + 4);
+        NYB_COUNT(e);
+    }
+    k_finalize<<<(D * S + 255) / 256, 256, 0, e->stream>>>(D, S, flags, out_lo, out_hi, min_lower);
+    NYB_COUNT(e);
+}
+
 void launch_finalize(nyb200_engine *e, int D, int S, const int *flags, float *out_lo, float *out_hi, float *min_lower) {
     k_finalize<<<(D * S + 255) / 256, 256, 0, e->stream>>>(D, S, flags, out_lo, out_hi, min_lower);
     NYB_COUNT(e);

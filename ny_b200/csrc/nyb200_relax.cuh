@@ -63,12 +63,12 @@ __device__ __forceinline__ float relax_coeff(const bool upper, float a, float4 t
 //     n * 2^-24 times the run's magnitude sum, and that sum is bounded term by term: |nw bias| directly, and
 //     |a * intercept| <= |nw| * max|z| * (1 + 2^-21), because an intercept only applies on the upper line, where the
 //     outward step moves nw away from zero (|nw| >= |a| * slope) and intercept / slope = -l up to rounding.
-//     A product that underflows takes the directed product and pays its exact residual.
+//     A product that underflows to zero becomes the smallest denormal with the outward sign.
 //   * The intercept and bias dot products are accumulated in fp32 (gi, gb: one fused multiply-add per term) over a
 //     short run of columns; the caller adds each run to the row's binary64 bias.
 // dir = +1 for an upper row, -1 for a lower row; dirf the same as a float.
 __device__ __forceinline__ float relax_coeff_fast(const bool upper, const int dir, const float dirf, float a, float4 t, float au,
-                                                  float cj, const float *za_ptr, float bk, float &gi, float &gb, float &sp) {
+                                                  float cj, float bk, float &gi, float &gb, float &sp) {
     const bool pos = a > 0.f;
     const float slope = (pos != upper) ? (upper ? au : t.x) : t.y;
     const float icp = (pos == upper) ? t.z : 0.f;   // times a == 0 it adds nothing
@@ -77,20 +77,17 @@ __device__ __forceinline__ float relax_coeff_fast(const bool upper, const int di
     // one ulp outward on the bit pattern: +dir for a positive product, -dir for a negative one; a zero product (zero
     // slope or zero coefficient: common, every stably inactive neuron has one) stays zero without a branch
     float nw = __int_as_float(pb + dir + 2 * dir * (pb >> 31));
-    const bool zero = prod == 0.f;
-    nw = zero ? 0.f : nw;
-    // a zero product next to a non-zero slope is a zero coefficient or, once in a blue moon, an underflow: the latter
-    // takes the directed product and pays its exact residual
-    if (zero && slope != 0.f) {
-        if (a != 0.f) {
-            nw = upper ? __fmul_ru(a, slope) : __fmul_rd(a, slope);
-            sp = __fmaf_ru(fabsf(fmaf(a, slope, -nw)), *za_ptr, sp);
-        }
-    }
+    // a zero product: exactly zero when the coefficient or the slope is zero (no step: every stably inactive neuron has
+    // one); otherwise the product underflowed, its magnitude is below the smallest denormal, and that denormal with the
+    // outward sign encloses it
+    const float tiny = (fminf(fabsf(a), fabsf(slope)) == 0.f) ? 0.f : dirf * 1.4012985e-45f;
+    nw = (prod == 0.f) ? tiny : nw;
     gi = fmaf(a, icp, gi);
     nw = fmaf(t.w, dirf, nw);   // signed beta: nw + t.w on upper rows, nw - t.w on lower rows (t.w * +-1 is exact)
     gb = fmaf(nw, bk, gb);
-    sp = __fmaf_ru(fabsf(nw), cj, sp);
+    // the floor covers the underflow case, whose gap to the exact product is the whole denormal, not 1.5 ulp:
+    // 2^-148 max|z| <= 1.6e-38 cj because cj >= 1.9e-7 max|z|
+    sp = __fmaf_ru(fmaxf(fabsf(nw), 1.6e-38f), cj, sp);
     return nw;
 }
 

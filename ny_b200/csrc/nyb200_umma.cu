@@ -92,7 +92,8 @@ __global__ void k_split_weights(const float *__restrict__ W, int K, int N, int K
 __global__ void __launch_bounds__(THREADS, 1)
 k_umma_tf32x3(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__ CUtensorMap tm_lo,
               const __grid_constant__ CUtensorMap tm_a, const float *__restrict__ A, int lda, float *__restrict__ C,
-              int ldc, int M, int N, int K, int chunk_stages, int *__restrict__ err, int a_plane, int a_tma) {
+              int ldc, int M, int N, int K, int chunk_stages, int *__restrict__ err, int a_plane, int a_tma,
+              const __grid_constant__ ConcFuse cf) {
     extern __shared__ unsigned char smem_raw[];
     // aligned by an offset (not by a cast through an integer) so that the compiler keeps treating it as shared memory
     unsigned char *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -262,6 +263,40 @@ k_umma_tf32x3(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__
 #pragma unroll
                     for (int j = 0; j < 128; ++j) if (j < ncols) cb[(long)j * a_plane] = sum[j];
                 }
+            }
+            if (cf.on && a_plane == 0 && row < M) {
+                // fused concretisation: this thread's columns of the finished row against the input box
+                double s = 0.0, sa = 0.0;
+                bool bad = false;
+                if (ncols > 0) {
+                    const int d = row / cf.R, rr = row - d * cf.R;
+                    const bool upper = rr >= cf.S;
+                    const float *xl = cf.in_lo + (long)d * cf.box_ds + col0, *xu = cf.in_hi + (long)d * cf.box_ds + col0;
+                    const bool vec = ncols == 128 && (((reinterpret_cast<uintptr_t>(xl) | reinterpret_cast<uintptr_t>(xu)) & 15) == 0);
+                    auto term = [&](float a, float l, float u) {
+                        const bool nonneg = !(__float_as_uint(a) >> 31) || (__float_as_uint(a) & 0x7fffffffu) == 0;
+                        const float x = (nonneg != upper) ? l : u;
+                        bad |= !(fabsf(a) < 1e10f);  // is_crown_coeff_safe, crates/ny-core/src/gemm.rs:127
+                        // a zero factor contributes nothing, whatever the other one is (no 0 * inf)
+                        const double c = (a != 0.f && x != 0.f) ? (double)a * (double)x : 0.0;
+                        s += c; sa += fabs(c);
+                    };
+                    if (vec) {
+#pragma unroll
+                        for (int j = 0; j < 128; j += 4) {
+                            const float4 l = *(const float4 *)(xl + j), u = *(const float4 *)(xu + j);
+                            term(sum[j], l.x, u.x); term(sum[j + 1], l.y, u.y); term(sum[j + 2], l.z, u.z); term(sum[j + 3], l.w, u.w);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 128; ++j) if (j < ncols) term(sum[j], xl[j], xu[j]);
+                    }
+                }
+                double *slot = cf.part + ((long)row * cf.slots + tn * 2 + half) * 2;
+                slot[0] = s; slot[1] = sa;
+                if (bad) cf.bad[row] = 1;
+            }
+            if (a_plane > 0 || (cf.on && !cf.store)) {
             } else if (row < M && ncols > 0) {
                 float *crow = C + (long)row * ldc + col0;
                 if (ncols == 128 && ((reinterpret_cast<uintptr_t>(crow) & 31) == 0)) {
@@ -444,7 +479,7 @@ int umma_prepare_layer(nyb200_engine *e, const float *W, int K, int N, UmmaLayer
 }
 
 int launch_umma(nyb200_engine *e, const UmmaLayer &L, int M, const float *A, int lda, float *C, int ldc, int *err,
-                int a_plane) {
+                int a_plane, const ConcFuse *cf) {
     // the attribute is a per-device property of the function: set it once on every device that launches it
     static std::mutex attr_mu;
     static bool attr_set[64] = {false};
@@ -471,8 +506,10 @@ int launch_umma(nyb200_engine *e, const UmmaLayer &L, int M, const float *A, int
     } else {
         tm_a = *(const CUtensorMap *)L.tm_hi;  // unused by the kernel in this form; any valid map
     }
+    ConcFuse none;
     k_umma_tf32x3<<<grid, THREADS, SMEM_BYTES, e->stream>>>(*(const CUtensorMap *)L.tm_hi, *(const CUtensorMap *)L.tm_lo, tm_a, A,
-                                                            lda, C, ldc, M, L.N, L.K, L.chain > 0 ? L.chain : chunk_stages_cfg(L.K), err, a_plane, a_tma);
+                                                            lda, C, ldc, M, L.N, L.K, L.chain > 0 ? L.chain : chunk_stages_cfg(L.K), err, a_plane, a_tma,
+                                                            cf ? *cf : none);
     e->launches++;
     return NYB200_OK;
 }
