@@ -249,3 +249,26 @@ def test_babsr_scores_and_picks_match_oracle(eng, oracle):
             o = int(offs[relu[d]] + neuron[d])
             assert pl[d][o] < 0 < pu[d][o]
     eng.release_network(nid)
+
+
+
+def test_babsr_on_the_reference_hand_computed_cases(eng):
+    """The device's BaBSR scores and pick on the two hand-computed cases of the reference's branching tests
+    (beta_crown/engine/tests/branching.rs:998-1143): 1.5 / 0.25 with neuron 0 chosen; 0.5 / 2.75 / 0.5 / 2.0 with
+    relu0 neuron 1 chosen at 2.75.  The given pre-activation bounds are taken as they are (clamp-only child bounds)."""
+    from ny_b200 import Network, SPLIT_DTYPE
+    from test_oracle_beta_crown import _babsr_reference_cases
+
+    for ws, bs, spec, lo, hi, scores, pick, best in _babsr_reference_cases():
+        net = Network(ws, bs)
+        nid = eng.register_network(net)
+        n_hidden = int(net.dims[1:-1].sum())
+        box_lo, box_hi = -np.ones(2, np.float32), np.ones(2, np.float32)
+        eng.batch_upload(nid, spec, box_lo, box_hi, lo[:net.n_pre], hi[:net.n_pre], np.zeros((1, 1), SPLIT_DTYPE),
+                         np.zeros(1, np.int32), mode=0)
+        eng.batch_run()
+        relu, neuron, _ = eng.batch_select_branch(2)
+        sc = eng.batch_branch_scores()[0][:n_hidden]
+        assert (int(relu[0]), int(neuron[0])) == pick
+        assert np.allclose(sc, scores, atol=1e-5) and abs(float(sc.max()) - best) < 1e-5
+        eng.release_network(nid)

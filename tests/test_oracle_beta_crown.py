@@ -227,6 +227,32 @@ def test_babsr_scores_hand_case():
     assert sc.tolist() == [0.75, 0.5]
 
 
+def _babsr_reference_cases():
+    """The two hand-computed cases of the reference's own branching tests
+    (crates/ny-propagate/src/beta_crown/engine/tests/branching.rs:998-1143), restated with an identity first layer in
+    front of the reference's leading ReLU: (weights, biases, spec, pre_lo, pre_hi, expected scores per hidden neuron,
+    expected (relu, neuron), expected best score)."""
+    eye = np.eye(2, dtype=np.float32)
+    # relu -> Linear [[-3, -0.5]], box [-1, 1]^2: scores |min(lA, 0) * intercept| = 1.5 and 0.25, pick neuron 0
+    one = ([eye, np.array([[-3.0, -0.5]], np.float32)], [None, None], np.array([[1.0]], np.float32),
+           np.array([-1, -1, -3.5], np.float32), np.array([1, 1, 0.0], np.float32), [1.5, 0.25], (0, 0), 1.5)
+    # relu0 -> Linear [[2,-1],[0,3]] -> relu1 -> Linear [[-1,-4]]; relu1's pre-activation bounds given as [-1, 1]:
+    # coefficients 1.0 / 5.5 at relu0 and 1.0 / 4.0 at relu1, intercept 0.5 everywhere; pick relu0 neuron 1, score 2.75
+    two = ([eye, np.array([[2.0, -1.0], [0.0, 3.0]], np.float32), np.array([[-1.0, -4.0]], np.float32)], [None, None, None],
+           np.array([[1.0]], np.float32), np.array([-1, -1, -1, -1, -10], np.float32), np.array([1, 1, 1, 1, 10], np.float32),
+           [0.5, 2.75, 0.5, 2.0], (0, 1), 2.75)
+    return [one, two]
+
+
+def test_babsr_restatement_matches_the_reference_hand_computed_answers():
+    from oracle import ny_oracle as O
+
+    for ws, bs, spec, lo, hi, scores, pick, best in _babsr_reference_cases():
+        sc, got = O.babsr_scores(ws, bs, spec, lo, hi)
+        assert got == pick
+        assert np.allclose(sc, scores, atol=1e-6) and abs(float(sc.max()) - best) < 1e-6
+
+
 # ---- optimiser restatements pinned to the reference's own known answers (tests/golden/optimizer_reference.json) ----
 def _golden_opt():
     import json
