@@ -409,6 +409,14 @@ int run_forward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int fw
     // a slack-to-width ratio above this marks the domain for the binary64 re-evaluation (same switch as the
     // penalty criterion: 0 disables)
     const float fwd_tol = e->refine_tol;
+    // When the backward pass of this run will be the fused chain, the finish kernel also leaves the chain's charge
+    // weights (one fused multiply-add per table entry here instead of a pass of its own over three arrays).
+    float *cj = nullptr;
+    if (e->path == NYB200_PATH_TF32X3 && e->fuse_chain && fwd_mode != 2 && chain_eligible(net, nv.L) && (nv.nps % 4 == 0)) {
+        cj = (float *)ws_get(e, "chain_cj", (size_t)D * nv.nps * 4);
+        if (!cj) return NYB200_ERR_OOM;
+    }
+    p.cj = cj;
     NYB_CUDA(e, cudaMemsetAsync(p.flags, 0, (size_t)D * 4, e->stream));
     NYB_CUDA(e, cudaMemsetAsync(p.code, 0, (size_t)D * np, e->stream));
     NYB_CUDA(e, cudaMemsetAsync(p.sbeta, 0, (size_t)D * np * 4, e->stream));
@@ -443,7 +451,8 @@ int run_forward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int fw
         launch_ibp_finish(e, nv, k, D, fwd_mode, p.raw_lo, p.raw_hi, raw_ds, fwd_mode == 2 ? nullptr : p.inh_lo,
                           fwd_mode == 2 ? nullptr : p.inh_hi, p.code, p.sbeta, b.has_alpha ? p.alpha : nullptr, p.pre_lo,
                           p.pre_hi, p.zl, p.zu, p.tab, p.zabs, p.flags, tk ? Fl : nullptr, ldf,
-                          tk ? umma_eps(nv.dims[k], 1) * 1.000001 : 0.0, p.q, tk ? fwd_tol : 0.f);
+                          tk ? umma_eps(nv.dims[k], 1) * 1.000001 : 0.0, p.q, tk ? fwd_tol : 0.f, cj,
+                          cj ? chain_cj_eps(net, nv.L, k) : 0.f, chain_kappa());
     }
     NYB_CUDA(e, cudaGetLastError());
     return NYB200_OK;

@@ -501,6 +501,18 @@ double chain_eps(int K) {
     return rep + main_steps + cross_steps + u24 * 1.001;
 }
 
+// The constants of the charge weights (see k_chain_prep): kappa covers the fp32 dot products of the epilogue, which run
+// over at most 16 columns per slice, plus the 2^-40 share of the binary64 additions; the rate of table block `block`
+// is that of the contraction its relaxed coefficients enter (the unfused Linear_0 contraction for block 0, a fused one
+// otherwise, the first fused one for the top block L-1).
+float chain_kappa() { return 16.f * 5.9604645e-8f * 1.001f + 9.1e-13f; }
+float chain_cj_eps(const Net &net, int L, int block) {
+    const NetView &nv = net.v;
+    const double eps = block == 0 ? umma_eps(nv.dims[1]) * 1.000001 : chain_eps(nv.dims[block + 1]) * 1.000001;
+    (void)L;
+    return (float)(eps * 1.0000002);
+}
+
 // Can the pass that starts at Linear_{L-1}'s output (L layers below it) run its contractions k = L-1 .. 1 fused?
 bool chain_eligible(const Net &net, int L) {
     const NetView &nv = net.v;
@@ -531,7 +543,11 @@ int launch_chain(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int L
     P.top_off = nv.pre_off[L - 1];
     P.top_q_ds = nv.nps;
     P.top_eps = (float)(chain_eps(nv.dims[L]) * 1.000001 * 1.0000002);
-    NYB_WS(cj, float *, e, "chain_cj", (size_t)b.D * nv.nps * 4);
+    float *cj = p.cj;   // written by the interval pass of this run, or prepared below
+    if (!cj) {
+        cj = (float *)ws_get(e, "chain_cj", (size_t)b.D * nv.nps * 4);
+        if (!cj) return NYB200_ERR_OOM;
+    }
     P.tab = p.tab; P.zabs = p.zabs; P.q = p.q; P.aup = p.alpha_up; P.nps = nv.nps; P.cj = cj;
     PrepParams PP;
     memset(&PP, 0, sizeof(PP));
@@ -560,8 +576,8 @@ int launch_chain(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int L
     }
     // kappa: the fp32 dot products run over at most 8 columns per slice (CPT of the narrowest epilogue slice is 8, of the
     // widest 16: charge the widest), plus the 2^-40 share of the binary64 additions
-    const float kappa = 16.f * 5.9604645e-8f * 1.001f + 9.1e-13f;
-    {
+    const float kappa = chain_kappa();
+    if (!p.cj) {
         dim3 grid((unsigned)(((long)b.D * max_n + 255) / 256), (unsigned)PP.n_blocks);
         k_chain_prep<<<grid, 256, 0, e->stream>>>(PP, b.D, (long)nv.nps, p.zabs, p.q, kappa, cj);
         e->launches++;

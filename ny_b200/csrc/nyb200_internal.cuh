@@ -168,7 +168,8 @@ void launch_ibp_finish(nyb200_engine *e, const NetView &nv, int k, int D, int mo
                        const float *raw_hi, long raw_dstride, const float *inh_lo, const float *inh_hi,
                        const signed char *code, const float *sbeta, const float *alpha, float *pre_lo, float *pre_hi,
                        float *zl, float *zu, float4 *tab, float *zabs, int *flags, const float *F = nullptr, int ldf = 0,
-                       double eps = 0.0, float *q = nullptr, float fwd_tol = 0.f);
+                       double eps = 0.0, float *q = nullptr, float fwd_tol = 0.f,
+                       float *cj = nullptr, float cj_eps = 0.f, float cj_kappa = 0.f);
 void launch_seed(nyb200_engine *e, const float *spec, int S, int nL, int D, int lda, float *A);
 // A [D*2n x lda] = per domain the n x n identity for the lower rows, then again for the upper rows.
 void launch_seed_identity(nyb200_engine *e, int n, int D, int lda, float *A);
@@ -212,6 +213,7 @@ struct BatchPtrs {
     int lda;
     float *a_final = nullptr;  // set by run_backward: the coefficients on the input box, [D*R x lda]
     bool keep_final = false;   // the caller reads a_final afterwards: the last contraction must store its rows
+    float *cj = nullptr;       // charge weights of the fused chain, when the interval pass already wrote them
     float *alpha_up = nullptr; // dual alpha: the upper path's own lower slopes [D x nps], or null (shared with the lower path)
 };
 int batch_ptrs(nyb200_engine *e, const Net &net, const Batch &b, BatchPtrs &p);
@@ -236,6 +238,8 @@ int prepare_backward_operands(nyb200_engine *e, Net &net);
 // ---- fused backward chain (nyb200_chain.cu) ----
 bool chain_eligible(const Net &net, int L);
 double chain_eps(int K);
+float chain_cj_eps(const Net &net, int L, int block);   // rounding rate folded into the charge weights of table block `block`
+float chain_kappa();
 int launch_chain(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int L, bool identity_seed, bool shared_box,
                  float *A_out, double eps0, int *derr);
 int prepare_transposed(nyb200_engine *e, Net &net, bool tensor);

@@ -209,7 +209,7 @@ __global__ void k_ibp_finish(NetView nv, int k, int D, int mode, int last, const
                              float *__restrict__ pre_lo, float *__restrict__ pre_hi, float *__restrict__ zl,
                              float *__restrict__ zu, float4 *__restrict__ tab, float *__restrict__ zabs,
                              int *__restrict__ flags, const float *__restrict__ F, int ldf, double eps,
-                             float *__restrict__ q, float fwd_tol) {
+                             float *__restrict__ q, float fwd_tol, float *__restrict__ cj, float cj_eps, float cj_kappa) {
     int n = nv.dims[k + 1], off = nv.pre_off[k];
     long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= (long)D * n) return;
@@ -248,7 +248,14 @@ __global__ void k_ibp_finish(NetView nv, int k, int D, int mode, int last, const
             if (tl <= tu) { l = tl; u = tu; } else { l = fminf(l, il); u = fmaxf(u, iu); }
         }
     }
-    if (last) { pre_lo[o] = l; pre_hi[o] = u; return; }
+    // charge weight of the fused backward chain for this table entry (the arithmetic of k_chain_prep): the rounding
+    // of the contraction that consumes the coefficient, the bias product's and, below, the relaxation's own terms
+    float cw = 0.f;
+    if (cj) {
+        cw = __fmul_ru(cj_eps, q[(long)d * raw_ds + off + j]);
+        if (nv.b[k]) cw = __fmaf_ru(cj_kappa, fabsf(nv.b[k][j]), cw);
+    }
+    if (last) { pre_lo[o] = l; pre_hi[o] = u; if (cj) cj[o] = cw; return; }
     int s = code[o];
     if (s > 0) l = (isnan(l)) ? l : fmaxf(l, 0.f);
     else if (s < 0) u = (isnan(u)) ? u : fminf(u, 0.f);
@@ -277,7 +284,9 @@ __global__ void k_ibp_finish(NetView nv, int k, int D, int mode, int last, const
         else ls = (u > -l) ? 1.f : 0.f;  // beta_crown/state/alpha/domain.rs:161
     }
     tab[o] = make_float4(ls, us, ui, sbeta[o]);
-    zabs[o] = fmaxf(fabsf(l), fabsf(u));
+    const float za = fmaxf(fabsf(l), fabsf(u));
+    zabs[o] = za;
+    if (cj) cj[o] = __fmaf_ru(1.9073487e-7f /* 1.6 * 2^-23 */ + cj_kappa * 1.001f, za, cw);
     float pl = fmaxf(l, 0.f), pu = fmaxf(u, 0.f);
     if (s > 0) { pu = u; }
     else if (s < 0) { pl = 0.f; pu = 0.f; }
@@ -837,12 +846,12 @@ void launch_ibp_finish(nyb200_engine *e, const NetView &nv, int k, int D, int mo
                        const float *raw_hi, long raw_dstride, const float *inh_lo, const float *inh_hi,
                        const signed char *code, const float *sbeta, const float *alpha, float *pre_lo, float *pre_hi,
                        float *zl, float *zu, float4 *tab, float *zabs, int *flags, const float *F, int ldf, double eps,
-                       float *q, float fwd_tol) {
+                       float *q, float fwd_tol, float *cj, float cj_eps, float cj_kappa) {
     long total = (long)D * nv.dims[k + 1];
     int last = (k == nv.L - 1);
     k_ibp_finish<<<(unsigned)((total + 255) / 256), 256, 0, e->stream>>>(nv, k, D, mode, last, raw_lo, raw_hi, raw_dstride,
                                                                          inh_lo, inh_hi, code, sbeta, alpha, pre_lo,
-                                                                         pre_hi, zl, zu, tab, zabs, flags, F, ldf, eps, q, fwd_tol);
+                                                                         pre_hi, zl, zu, tab, zabs, flags, F, ldf, eps, q, fwd_tol, cj, cj_eps, cj_kappa);
     NYB_COUNT(e);
 }
 
