@@ -359,9 +359,12 @@ int batch_ptrs(nyb200_engine *e, const Net &net, const Batch &b, BatchPtrs &p) {
     GET(tab, float4 *, "tab", D * np * 16)
     GET(A0, float *, "A0", M * p.lda * 4)
     GET(A1, float *, "A1", M * p.lda * 4)
-    GET(rb, double *, "rb", M * 8)
-    GET(rabs, double *, "rabs", M * 8)
-    GET(rpen, double *, "rpen", M * 8)
+    // the per-row scalars share one block so that a pass clears them with one fill: bias, magnitude sum, rounding
+    // penalty (binary64 each), then the coefficient-safety flags of the fused concretisation
+    GET(rb, double *, "row_scalars", M * 28)
+    p.rabs = p.rb + M;
+    p.rpen = p.rb + 2 * M;
+    p.row_bad = (int *)(p.rb + 3 * M);
     GET(out_lo, float *, "out_lo", D * b.S * 4)
     GET(out_hi, float *, "out_hi", D * b.S * 4)
     GET(min_lower, float *, "min_lower", 256)
@@ -490,9 +493,16 @@ int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, float
     int M = D * R;
     long np = nv.nps;
     bool shared_box = (b.box_stride == 0 && D > 1);
-    NYB_CUDA(e, cudaMemsetAsync(p.rb, 0, (size_t)M * 8, e->stream));
-    NYB_CUDA(e, cudaMemsetAsync(p.rabs, 0, (size_t)M * 8, e->stream));
-    NYB_CUDA(e, cudaMemsetAsync(p.rpen, 0, (size_t)M * 8, e->stream));
+    // rb, rabs, rpen and the safety flags: one fill when they lie back to back for this row count (they do unless the
+    // pointers were taken over from a larger batch, as the re-evaluation of a subset does)
+    if (p.rabs == p.rb + M && p.rpen == p.rb + 2 * (size_t)M && p.row_bad == (int *)(p.rb + 3 * (size_t)M)) {
+        NYB_CUDA(e, cudaMemsetAsync(p.rb, 0, (size_t)M * 28, e->stream));
+    } else {
+        NYB_CUDA(e, cudaMemsetAsync(p.rb, 0, (size_t)M * 8, e->stream));
+        NYB_CUDA(e, cudaMemsetAsync(p.rabs, 0, (size_t)M * 8, e->stream));
+        NYB_CUDA(e, cudaMemsetAsync(p.rpen, 0, (size_t)M * 8, e->stream));
+        NYB_CUDA(e, cudaMemsetAsync(p.row_bad, 0, (size_t)M * 4, e->stream));
+    }
     static const float init_words[8] = {INFINITY, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};  // min lower; loose-domain counter at word 4
     NYB_CUDA(e, cudaMemcpyAsync(p.min_lower, init_words, sizeof(init_words), cudaMemcpyHostToDevice, e->stream));
     float *cur = p.A0, *nxt = p.A1;
@@ -592,9 +602,8 @@ int run_backward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, float
             cf.slots = 2 * ((N + 255) / 256);
             cf.in_lo = p.in_lo; cf.in_hi = p.in_hi; cf.box_ds = b.box_stride;
             cf.part = (double *)ws_get(e, "conc_part", (size_t)M * cf.slots * 16);
-            cf.bad = (int *)ws_get(e, "conc_bad", (size_t)M * 4);
-            if (!cf.part || !cf.bad) return NYB200_ERR_OOM;
-            NYB_CUDA(e, cudaMemsetAsync(cf.bad, 0, (size_t)M * 4, e->stream));
+            cf.bad = p.row_bad;   // cleared with the row scalars at the start of the pass
+            if (!cf.part) return NYB200_ERR_OOM;
             NYB_TRY(launch_umma(e, net.umma[k], M, cur, p.lda, dst, ldd, derr, 0, &cf));
             conc_slots = cf.slots; conc_part = cf.part; conc_bad = cf.bad;
         } else if (tensor) {
@@ -673,6 +682,7 @@ int upload_batch(nyb200_engine *e, int32_t net_id, const float *spec, int32_t S,
 // never reads across the bus).
 __global__ void k_publish_status(const int *__restrict__ derr, const int *__restrict__ loose, int *__restrict__ acc,
                                  volatile int *status, int seq) {
+    pdl_wait();
     if (threadIdx.x != 0 || blockIdx.x != 0) return;
     const int h = derr ? *derr : 0, l = loose ? *loose : 0;
     if (h) acc[0] = h;
@@ -712,9 +722,9 @@ int run_batch(nyb200_engine *e) {
     {
         const bool tensor = e->path == NYB200_PATH_TF32X3;
         int *acc = (int *)ws_get(e, "status_acc", 256);
-        k_publish_status<<<1, 32, 0, e->stream>>>(tensor ? (const int *)ws_get(e, "umma_err", 256) : nullptr,
-                                                  tensor && e->refine_tol > 0.f ? (const int *)p.min_lower + 4 : nullptr, acc,
-                                                  e->status_dev, ++e->run_seq);
+        launch_pdl(k_publish_status, dim3(1), dim3(32), 0, e->stream, tensor ? (const int *)ws_get(e, "umma_err", 256) : (const int *)nullptr,
+                   tensor && e->refine_tol > 0.f ? (const int *)p.min_lower + 4 : (const int *)nullptr, acc, (volatile int *)e->status_dev,
+                   ++e->run_seq);
         e->launches++;
         NYB_CUDA(e, cudaGetLastError());
     }

@@ -153,6 +153,7 @@ __global__ void __launch_bounds__(Cfg<NSUB>::THREADS, 1) k_chain(const __grid_co
     volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
     static_assert((2 * NA + 2 * NW + 2 + 2 * NT) * 8 + 8 <= BAR_BYTES, "barrier block overflows its slots");
 
+    pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_tiles = (P.M + BM - 1) / BM;
 
@@ -173,6 +174,7 @@ __global__ void __launch_bounds__(Cfg<NSUB>::THREADS, 1) k_chain(const __grid_co
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const unsigned tmem_base = *tmem_slot;
+    pdl_wait();   // barriers and tensor memory are set up; from here on the kernel reads what earlier kernels wrote
 
     if (warp < 4) {
         asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(C::REGS_CONTROL));
@@ -600,8 +602,9 @@ int launch_chain(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int L
     const int grid = tiles < sms ? tiles : sms;
     // a 128-row tile spans at most (BM - 2) / R + 2 domains; the table ring holds MAXD of them
     const bool staged = (BM - 2) / b.R + 2 <= MAXD;
-    if (staged) k_chain<4, true><<<grid, Cfg<4>::THREADS, SMEM_BYTES, e->stream>>>(P);
-    else k_chain<4, false><<<grid, Cfg<4>::THREADS, SMEM_BYTES, e->stream>>>(P);
+    cudaError_t ls = staged ? launch_pdl(k_chain<4, true>, dim3(grid), dim3(Cfg<4>::THREADS), SMEM_BYTES, e->stream, P)
+                            : launch_pdl(k_chain<4, false>, dim3(grid), dim3(Cfg<4>::THREADS), SMEM_BYTES, e->stream, P);
+    if (ls != cudaSuccess) return set_err(e, NYB200_ERR_INTERNAL, "fused chain launch failed");
     e->launches++;
     return NYB200_OK;
 }

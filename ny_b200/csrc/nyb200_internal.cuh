@@ -140,6 +140,28 @@ struct nyb200_engine {
     int run_seq = 0;
 };
 
+// Programmatic dependent launch.  A kernel launched through launch_pdl may be scheduled while its predecessor in the
+// stream is still running (the predecessor says when by pdl_trigger, at the latest by finishing); it must call pdl_wait
+// before its first access to memory that any earlier kernel of the stream writes or reads, which returns once the
+// predecessor has completed and its writes are visible.  What overlaps is the launch latency, the scheduling of the
+// CTAs and whatever the kernel does before pdl_wait (barrier set-up, tensor-memory allocation).  Both calls do nothing
+// in a kernel that was launched the ordinary way.
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
+
 #define NYB_TRY(expr)                      \
     do {                                   \
         int _st = (expr);                  \
@@ -209,6 +231,7 @@ struct BatchPtrs {
     float4 *tab;
     float *A0, *A1;
     double *rb, *rabs, *rpen;
+    int *row_bad;
     float *out_lo, *out_hi, *min_lower;
     int lda;
     float *a_final = nullptr;  // set by run_backward: the coefficients on the input box, [D*R x lda]

@@ -43,6 +43,8 @@ __device__ __forceinline__ double warp_sum(double v) {
 __global__ void k_scatter_splits(NetView nv, const nyb200_split *__restrict__ sp, const int *__restrict__ ns,
                                  int max_splits, int D, signed char *__restrict__ code, float *__restrict__ sbeta,
                                  int *__restrict__ flags) {
+    pdl_trigger();
+    pdl_wait();
     long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= (long)D * max_splits) return;
     int d = (int)(t / max_splits), s = (int)(t % max_splits);
@@ -141,6 +143,8 @@ __global__ void __launch_bounds__(256)
 k_ibp_linear_vec(int n_in, int n_out, const float *__restrict__ W, const float *__restrict__ bias,
                  const float *__restrict__ zl, const float *__restrict__ zu, float *__restrict__ raw_lo,
                  float *__restrict__ raw_hi, float *__restrict__ q) {
+    pdl_trigger();
+    pdl_wait();
     int o = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (o >= n_out) return;
     const float *w = W + (long)o * n_in;
@@ -210,6 +214,8 @@ __global__ void k_ibp_finish(NetView nv, int k, int D, int mode, int last, const
                              float *__restrict__ zu, float4 *__restrict__ tab, float *__restrict__ zabs,
                              int *__restrict__ flags, const float *__restrict__ F, int ldf, double eps,
                              float *__restrict__ q, float fwd_tol, float *__restrict__ cj, float cj_eps, float cj_kappa) {
+    pdl_trigger();
+    pdl_wait();
     int n = nv.dims[k + 1], off = nv.pre_off[k];
     long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= (long)D * n) return;
@@ -643,6 +649,8 @@ __device__ __forceinline__ void atomic_min_float(float *addr, float v) {
 __global__ void k_count_loose(int D, int S, int R, const float *__restrict__ out_lo, const float *__restrict__ out_hi,
                               const double *__restrict__ rpen, int *__restrict__ flags, float tol,
                               int *__restrict__ n_loose) {
+    pdl_trigger();
+    pdl_wait();
     int d = blockIdx.x * blockDim.x + threadIdx.x;
     if (d >= D) return;
     const int f = flags[d];
@@ -709,6 +717,8 @@ __global__ void k_min_lower(int D, int S, const float *__restrict__ out_lo, cons
 // (non-finite endpoint or inversion -> [-inf, +inf], concretize.rs:481-488); fold the global minimum.
 __global__ void k_finalize(int D, int S, const int *__restrict__ flags, float *__restrict__ out_lo,
                            float *__restrict__ out_hi, float *__restrict__ min_lower) {
+    pdl_trigger();
+    pdl_wait();
     int t = blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= D * S) return;
     int d = t / S;
@@ -821,9 +831,8 @@ void launch_ibp_linear(nyb200_engine *e, const NetView &nv, int k, int Deff, con
                        long in_dstride, float *raw_lo, float *raw_hi, float *q, long out_dstride) {
     int n_in = nv.dims[k], n_out = nv.dims[k + 1];
     if (Deff == 1) {
-        k_ibp_linear_vec<<<(n_out * 32 + 255) / 256, 256, 0, e->stream>>>(n_in, n_out, nv.W[k], nv.b[k], zl, zu,
-                                                                         raw_lo + nv.pre_off[k], raw_hi + nv.pre_off[k],
-                                                                         q + nv.pre_off[k]);
+        launch_pdl(k_ibp_linear_vec, dim3((n_out * 32 + 255) / 256), dim3(256), 0, e->stream, n_in, n_out, (const float *)nv.W[k],
+                   (const float *)nv.b[k], zl, zu, raw_lo + nv.pre_off[k], raw_hi + nv.pre_off[k], q + nv.pre_off[k]);
         NYB_COUNT(e);
         return;
     }
@@ -849,9 +858,9 @@ void launch_ibp_finish(nyb200_engine *e, const NetView &nv, int k, int D, int mo
                        float *q, float fwd_tol, float *cj, float cj_eps, float cj_kappa) {
     long total = (long)D * nv.dims[k + 1];
     int last = (k == nv.L - 1);
-    k_ibp_finish<<<(unsigned)((total + 255) / 256), 256, 0, e->stream>>>(nv, k, D, mode, last, raw_lo, raw_hi, raw_dstride,
-                                                                         inh_lo, inh_hi, code, sbeta, alpha, pre_lo,
-                                                                         pre_hi, zl, zu, tab, zabs, flags, F, ldf, eps, q, fwd_tol, cj, cj_eps, cj_kappa);
+    launch_pdl(k_ibp_finish, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, e->stream, nv, k, D, mode, last, raw_lo, raw_hi,
+               raw_dstride, inh_lo, inh_hi, code, sbeta, alpha, pre_lo, pre_hi, zl, zu, tab, zabs, flags, F, ldf, eps, q, fwd_tol, cj,
+               cj_eps, cj_kappa);
     NYB_COUNT(e);
 }
 
@@ -948,6 +957,8 @@ void launch_concretize(nyb200_engine *e, int M, int R, int S, int n0, const floa
 __global__ void k_concretize_fused(int M, int R, int S, int slots, const double *__restrict__ part, const int *__restrict__ badf,
                                    const double *__restrict__ rb, const double *__restrict__ rabs,
                                    const double *__restrict__ rpen, float *__restrict__ out_lo, float *__restrict__ out_hi) {
+    pdl_trigger();
+    pdl_wait();
     int m = blockIdx.x * blockDim.x + threadIdx.x;
     if (m >= M) return;
     const int d = m / R, rr = m % R;
@@ -969,15 +980,16 @@ __global__ void k_concretize_fused(int M, int R, int S, int slots, const double 
 void launch_concretize_fused(nyb200_engine *e, int M, int R, int S, int slots, const double *part, const int *bad,
                              const double *rb, const double *rabs, const double *rpen, int *flags, float *out_lo,
                              float *out_hi, float *min_lower, float loose_tol) {
-    k_concretize_fused<<<(unsigned)((M + 255) / 256), 256, 0, e->stream>>>(M, R, S, slots, part, bad, rb, rabs, rpen, out_lo, out_hi);
+    launch_pdl(k_concretize_fused, dim3((unsigned)((M + 255) / 256)), dim3(256), 0, e->stream, M, R, S, slots, part, bad, rb, rabs,
+               rpen, out_lo, out_hi);
     NYB_COUNT(e);
     int D = M / R;
     if (loose_tol > 0.f) {
-        k_count_loose<<<(D + 255) / 256, 256, 0, e->stream>>>(D, S, R, out_lo, out_hi, rpen, flags, loose_tol,
-                                                              (int *)min_lower + 4);
+        launch_pdl(k_count_loose, dim3((D + 255) / 256), dim3(256), 0, e->stream, D, S, R, (const float *)out_lo, (const float *)out_hi,
+                   rpen, flags, loose_tol, (int *)min_lower + 4);
         NYB_COUNT(e);
     }
-    k_finalize<<<(D * S + 255) / 256, 256, 0, e->stream>>>(D, S, flags, out_lo, out_hi, min_lower);
+    launch_pdl(k_finalize, dim3((D * S + 255) / 256), dim3(256), 0, e->stream, D, S, (const int *)flags, out_lo, out_hi, min_lower);
     NYB_COUNT(e);
 }
 

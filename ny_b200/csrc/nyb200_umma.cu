@@ -105,6 +105,7 @@ k_umma_tf32x3(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__
     unsigned *tmem_slot = (unsigned *)(bars + 3 * STAGES + 4 + 2 * RAW_STAGES);
     volatile int *abort_flag = (volatile int *)(tmem_slot + 1);
 
+    pdl_trigger();   // the next kernel of the stream may be scheduled; it waits for this one's completion itself
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     int m_tiles = (M + BM - 1) / BM, n_tiles = (N + BN - 1) / BN;
     int total_tiles = m_tiles * n_tiles;
@@ -135,6 +136,7 @@ k_umma_tf32x3(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    pdl_wait();      // everything above touched only this CTA's shared and tensor memory
     unsigned tmem_base = *tmem_slot;
 
     if (warp < 4) {
@@ -507,9 +509,10 @@ int launch_umma(nyb200_engine *e, const UmmaLayer &L, int M, const float *A, int
         tm_a = *(const CUtensorMap *)L.tm_hi;  // unused by the kernel in this form; any valid map
     }
     ConcFuse none;
-    k_umma_tf32x3<<<grid, THREADS, SMEM_BYTES, e->stream>>>(*(const CUtensorMap *)L.tm_hi, *(const CUtensorMap *)L.tm_lo, tm_a, A,
-                                                            lda, C, ldc, M, L.N, L.K, L.chain > 0 ? L.chain : chunk_stages_cfg(L.K), err, a_plane, a_tma,
-                                                            cf ? *cf : none);
+    if (launch_pdl(k_umma_tf32x3, dim3(grid), dim3(THREADS), SMEM_BYTES, e->stream, *(const CUtensorMap *)L.tm_hi,
+                   *(const CUtensorMap *)L.tm_lo, tm_a, A, lda, C, ldc, M, L.N, L.K, L.chain > 0 ? L.chain : chunk_stages_cfg(L.K), err,
+                   a_plane, a_tma, cf ? *cf : none) != cudaSuccess)
+        return set_err(e, NYB200_ERR_INTERNAL, "contraction kernel launch failed");
     e->launches++;
     return NYB200_OK;
 }
