@@ -378,3 +378,60 @@ def test_projection_block_lowering_bounds(eng, oracle, kind):
     margins = original(xs) @ spec.astype(np.float64).T
     assert np.all(glo[0] <= margins.min(axis=0)) and np.all(ghi[0] >= margins.max(axis=0))
     eng.release_network(nid)
+
+
+@pytest.mark.parametrize("stride", [1, 2])
+def test_wide_convolutions_match_the_native_oracle(eng, oracle, stride):
+    """Convolutions with 32 and 36 channels (the small residual test networks have 4): a 3x3 stride-1 layer (nine taps
+    per output pixel) or a 4x4 stride-2 layer (four stride-parity classes of four taps) against the oracle's native
+    convolution (the sums of layers/convolution/conv2d/bound.rs:601-900), the unsplit domain against sampled
+    executions, and the parameter optimisation's checkpointed passes through the same layers."""
+    from ny_b200 import Conv2d, Network
+
+    g = np.random.Generator(np.random.PCG64(90 + stride))
+    rn = lambda *s: (g.standard_normal(s) * np.sqrt(2.0 / np.prod(s[1:]))).astype(np.float32)
+    c0, c1, c2, nout = 2, 32, 36, 5
+    hw = 8
+    stem = Conv2d(rn(c1, c0, 3, 3), rn(c1), (1, 1), (1, 1), (hw, hw))
+    if stride == 1:
+        mid = Conv2d(rn(c2, c1, 3, 3), rn(c2), (1, 1), (1, 1), (hw, hw))
+    else:
+        mid = Conv2d(rn(c2, c1, 4, 4), rn(c2), (2, 2), (1, 1), (hw, hw))
+    head_w, head_b = rn(nout, mid.out_features), rn(nout)
+    net = Network([stem, mid, head_w], [None, None, head_b])
+    n0 = c0 * hw * hw
+    x0 = g.uniform(0.2, 0.8, n0).astype(np.float32)
+    lo, hi = (x0 - 0.01).astype(np.float32), (x0 + 0.01).astype(np.float32)
+    spec = np.zeros((nout - 1, nout), np.float32)
+    spec[:, 0] = 1.0
+    spec[np.arange(nout - 1), 1 + np.arange(nout - 1)] = -1.0
+    wl = W.Workload("wide-conv", net, x0, lo, hi, spec, 3, 90)
+    nid = eng.register_network(net)
+    nat = oracle.Net(net.weights, net.biases)
+    pl, pu = eng.ibp_forward_gpu(nid, lo, hi)
+    rl, ru = pl[0].copy(), pu[0].copy()
+    D, S = 16, spec.shape[0]
+    splits, ns = W.draw_domains(wl, rl, ru, D)
+    ns = ns.copy()
+    ns[0] = 0
+    glo, ghi, ginf = eng.bab_bound_batch(nid, spec, lo, hi, rl, ru, splits, ns, mode=1)
+    rl2 = np.concatenate([rl, np.full(S, -np.inf, np.float32)])
+    ru2 = np.concatenate([ru, np.full(S, np.inf, np.float32)])
+    olo, ohi, oinf, _ = oracle.bab_bound_batch(nat.with_spec(spec), lo, hi, rl2, ru2, splits, ns, 1)
+    assert np.array_equal(ginf != 0, oinf != 0)
+    f = oinf == 0
+    assert f.sum() > D // 2
+    assert _rel(np.concatenate([glo[f], ghi[f]], axis=1), np.concatenate([olo[f], ohi[f]], axis=1)) <= REL_TOL
+    mn = W.sample_min_margin(wl, 4000, 91, splits[0][:0], chunk=1000)
+    assert np.all(glo[0] <= mn)
+    # and the parameter optimisation, whose checkpointed passes go through the same layers
+    eng.batch_upload(nid, spec, lo, hi, rl, ru, splits, ns, mode=1)
+    eng.batch_run()
+    plo, _, pinf = eng.batch_download()
+    eng.batch_optimize(6, 0.1, 0.05)
+    qlo, _, _ = eng.batch_download()
+    ok = pinf == 0
+    # (the plain run's flagged domains were re-evaluated in binary64, the optimisation's evaluations carry their
+    # rounding charge: equal parameters may come out a few 1e-5 of the scale lower)
+    assert np.all(qlo[ok] >= plo[ok] - 2e-4 * np.abs(plo[ok]).max()) and np.all(qlo[0] <= mn)
+    eng.release_network(nid)
