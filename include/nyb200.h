@@ -180,6 +180,19 @@ int32_t nyb200_bab_bound_batch(nyb200_engine *e, int32_t net_id, const float *sp
 int32_t nyb200_crown_bounds(nyb200_engine *e, int32_t net_id, const float *spec, int32_t S, const float *in_lo,
                             const float *in_hi, int32_t box_stride, int32_t D, float *out_lo, float *out_hi,
                             float *inter_lo, float *inter_hi);
+/* The same pipeline for ReLU-split BaB domains (the per-domain CROWN-tightened intermediate bounds that the graph
+ * engine's constrained forward pass stands in for, crates/ny-propagate/src/beta_crown/engine/graph/propagation/
+ * beta.rs:921-929; collection as above): D domains, one shared box (box_stride = 0) or one box each, every domain with
+ * its own split list.  The interval pass runs under the domains' clamps, every layer's tightened bound is clamped
+ * (active l = max(l, 0), inactive u = min(u, 0)) before its relaxation is taken, the split multipliers are ignored
+ * (plain CROWN carries none).  infeasible [D]: 1 where a clamp empties an interval (bounds of such a domain are
+ * meaningless).  inter_lo / inter_hi are what a caller hands to nyb200_batch_set_inherited to bound the same domains
+ * with tighter relaxations.  Costs one partial pass of 2 n_k rows per domain and hidden layer: a tool for hundreds of
+ * domains, not for the 4096-domain batch.  Default error convention only. */
+int32_t nyb200_crown_bounds_split(nyb200_engine *e, int32_t net_id, const float *spec, int32_t S, const float *in_lo,
+                                  const float *in_hi, int32_t box_stride, const nyb200_split *splits,
+                                  const int32_t *n_splits, int32_t max_splits, int32_t D, float *out_lo, float *out_hi,
+                                  float *inter_lo, float *inter_hi, int32_t *infeasible);
 /* Convention for the certified rounding error of nyb200_crown_bounds.
  *   NYB200_ERRCH_IMMEDIATE (default): every rounding is discharged at the layer where it occurs, against the interval
  *     of the variable the coefficient multiplies.  Sound and tighter than the reference on deep networks (by about
@@ -209,6 +222,11 @@ int32_t nyb200_batch_upload(nyb200_engine *e, int32_t net_id, const float *spec,
                             const float *in_hi, int32_t box_stride, const float *inh_lo, const float *inh_hi,
                             const nyb200_split *splits, const int32_t *n_splits, int32_t max_splits, int32_t D,
                             int32_t mode, const float *alpha);
+/* Per-domain inherited bounds for the resident batch: inh_lo / inh_hi [D x sum_{k>=1} dims[k]] replace the shared
+ * vector given at upload (e.g. the tightened intermediates of nyb200_crown_bounds_split for the same domains).  The
+ * next run intersects every domain's re-propagated bounds with its own row (mode 1) or takes the row as it is (mode
+ * 0).  No counterpart in the reference's trait, whose domain references carry their bounds as baked slopes. */
+int32_t nyb200_batch_set_inherited(nyb200_engine *e, const float *inh_lo, const float *inh_hi);
 int32_t nyb200_batch_run(nyb200_engine *e);
 int32_t nyb200_batch_download(nyb200_engine *e, float *out_lo, float *out_hi, int32_t *infeasible);
 /* Smallest lower bound over all feasible domains and rows of the last run (the per-round global

@@ -340,8 +340,8 @@ int batch_ptrs(nyb200_engine *e, const Net &net, const Batch &b, BatchPtrs &p) {
     GET(spec, float *, "spec", (size_t)b.S * nv.dims[nv.L] * 4)
     GET(in_lo, float *, "in_lo", box * 4)
     GET(in_hi, float *, "in_hi", box * 4)
-    GET(inh_lo, float *, "inh_lo", np * 4)
-    GET(inh_hi, float *, "inh_hi", np * 4)
+    GET(inh_lo, float *, "inh_lo", (b.inh_stride ? D : 1) * np * 4)
+    GET(inh_hi, float *, "inh_hi", (b.inh_stride ? D : 1) * np * 4)
     GET(alpha, float *, "alpha", b.has_alpha ? D * np * 4 : 4)
     GET(splits, nyb200_split *, "splits", D * (size_t)(b.max_splits > 0 ? b.max_splits : 1) * sizeof(nyb200_split))
     GET(nsplits, int *, "nsplits", D * 4)
@@ -415,7 +415,7 @@ int run_forward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int fw
     // When the backward pass of this run will be the fused chain, the finish kernel also leaves the chain's charge
     // weights (one fused multiply-add per table entry here instead of a pass of its own over three arrays).
     float *cj = nullptr;
-    if (e->path == NYB200_PATH_TF32X3 && e->fuse_chain && fwd_mode != 2 && chain_eligible(net, nv.L) && (nv.nps % 4 == 0)) {
+    if (e->path == NYB200_PATH_TF32X3 && e->fuse_chain && fwd_mode < 2 && chain_eligible(net, nv.L) && (nv.nps % 4 == 0)) {
         cj = (float *)ws_get(e, "chain_cj", (size_t)D * nv.nps * 4);
         if (!cj) return NYB200_ERR_OOM;
     }
@@ -451,8 +451,8 @@ int run_forward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int fw
         if (net.skip_of(k) >= 0)  // pre_k = W z + b + relu(pre_j): interval sum, outward
             launch_skip_interval(e, D, nv.dims[k + 1], (long)np, p.raw_lo, p.raw_hi, nv.pre_off[k], p.zl, p.zu,
                                  nv.pre_off[net.skip_of(k)]);
-        launch_ibp_finish(e, nv, k, D, fwd_mode, p.raw_lo, p.raw_hi, raw_ds, fwd_mode == 2 ? nullptr : p.inh_lo,
-                          fwd_mode == 2 ? nullptr : p.inh_hi, p.code, p.sbeta, b.has_alpha ? p.alpha : nullptr, p.pre_lo,
+        launch_ibp_finish(e, nv, k, D, fwd_mode, p.raw_lo, p.raw_hi, raw_ds, fwd_mode >= 2 ? nullptr : p.inh_lo,
+                          fwd_mode >= 2 ? nullptr : p.inh_hi, (long)b.inh_stride, p.code, p.sbeta, b.has_alpha ? p.alpha : nullptr, p.pre_lo,
                           p.pre_hi, p.zl, p.zu, p.tab, p.zabs, p.flags, tk ? Fl : nullptr, ldf,
                           tk ? umma_eps(nv.dims[k], 1) * 1.000001 : 0.0, p.q, tk ? fwd_tol : 0.f, cj,
                           cj ? chain_cj_eps(net, nv.L, k) : 0.f, chain_kappa());
@@ -787,6 +787,13 @@ int refine_subset(nyb200_engine *e, Net &net, BatchPtrs &p) {
         launch_gather_rows(e, sub_alpha, p.alpha, didx, Ds, (long)np);
         ps.alpha = sub_alpha;
     }
+    if (b.inh_stride) {
+        NYB_WS(sub_il, float *, e, "sub_inh_lo", (size_t)Ds * np * 4);
+        NYB_WS(sub_iu, float *, e, "sub_inh_hi", (size_t)Ds * np * 4);
+        launch_gather_rows(e, sub_il, p.inh_lo, didx, Ds, (long)np);
+        launch_gather_rows(e, sub_iu, p.inh_hi, didx, Ds, (long)np);
+        ps.inh_lo = sub_il; ps.inh_hi = sub_iu;
+    }
     if (b.box_stride) {
         NYB_WS(sub_lo, float *, e, "sub_in_lo", (size_t)Ds * nv.dims[0] * 4);
         NYB_WS(sub_hi, float *, e, "sub_in_hi", (size_t)Ds * nv.dims[0] * 4);
@@ -899,6 +906,28 @@ int32_t nyb200_batch_upload(nyb200_engine *e, int32_t net_id, const float *spec,
     std::lock_guard<std::mutex> g(e->mu);
     return upload_batch(e, net_id, spec, S, in_lo, in_hi, box_stride, inh_lo, inh_hi, splits, n_splits, max_splits, D, mode,
                         alpha);
+}
+
+int32_t nyb200_batch_set_inherited(nyb200_engine *e, const float *inh_lo, const float *inh_hi) {
+    if (!e || !inh_lo || !inh_hi) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    NYB_CUDA(e, cudaSetDevice(e->device));
+    if (!e->batch.valid) return set_err(e, NYB200_ERR_INVALID, "no batch uploaded");
+    Net *net;
+    NYB_TRY(find_net(e, e->batch.net_id, &net));
+    const NetView &nv = net->v;
+    e->batch.inh_stride = nv.nps;
+    BatchPtrs p;
+    NYB_TRY(batch_ptrs(e, *net, e->batch, p));
+    const size_t w = (size_t)nv.n_pre * 4, pitch = (size_t)nv.nps * 4;
+    NYB_CUDA(e, cudaMemsetAsync(p.inh_lo, 0, (size_t)e->batch.D * pitch, e->stream));
+    NYB_CUDA(e, cudaMemsetAsync(p.inh_hi, 0, (size_t)e->batch.D * pitch, e->stream));
+    NYB_CUDA(e, cudaMemcpy2DAsync(p.inh_lo, pitch, inh_lo, w, w, (size_t)e->batch.D, cudaMemcpyHostToDevice, e->stream));
+    NYB_CUDA(e, cudaMemcpy2DAsync(p.inh_hi, pitch, inh_hi, w, w, (size_t)e->batch.D, cudaMemcpyHostToDevice, e->stream));
+    NYB_CUDA(e, cudaStreamSynchronize(e->stream));
+    e->batch.ran = false;
+    e->batch.finished = false;
+    return NYB200_OK;
 }
 
 int32_t nyb200_batch_run(nyb200_engine *e) {

@@ -83,11 +83,13 @@ __global__ void k_crown_merge(int D, int n, int off, long stride, int relu, cons
                               const float *__restrict__ f_hi, const float *__restrict__ c_lo,
                               const float *__restrict__ c_hi, const int *__restrict__ lflags, float *__restrict__ t_lo,
                               float *__restrict__ t_hi, float *__restrict__ zl, float *__restrict__ zu,
-                              float4 *__restrict__ tab, float *__restrict__ zabs, int *__restrict__ dflags) {
+                              float4 *__restrict__ tab, float *__restrict__ zabs, int *__restrict__ dflags,
+                              const signed char *__restrict__ code) {
     long t = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= (long)D * n) return;
     int d = (int)(t / n), j = (int)(t % n);
     long o = (long)d * stride + off + j;
+    const int sc = (relu && code) ? (int)code[o] : 0;   // +1 / -1: the domain fixes this neuron active / inactive
     int fl = lflags[d];
     float il = ibp_lo[o], iu = ibp_hi[o];
     float l = il, u = iu;
@@ -98,6 +100,10 @@ __global__ void k_crown_merge(int D, int n, int off, long stride, int relu, cons
         float cl = use_f ? a : c_lo[(long)d * n + j], cu = use_f ? b : c_hi[(long)d * n + j];
         intersect(l, u, cl, cu);
     }
+    // pre-activation clamp of a ReLU split (constraints/lookups.rs:138-185); an emptied interval marks the domain
+    if (sc > 0 && !isnan(l)) l = fmaxf(l, 0.f);
+    if (sc < 0 && !isnan(u)) u = fminf(u, 0.f);
+    if (sc != 0 && l > u) atomicOr(&dflags[d], kFlagInfeasible);
     t_lo[o] = l; t_hi[o] = u;
     if (!relu) { zl[o] = l; zu[o] = u; return; }
     // plain-CROWN relaxation (chord computed in binary64, slope and intercept stepped up)
@@ -125,6 +131,7 @@ __global__ void k_crown_merge(int D, int n, int off, long stride, int relu, cons
         float ql = fmaxf(l, 0.f), qu = fmaxf(u, 0.f);
         intersect(pl, pu, ql, qu);
     }
+    if (sc < 0) { pl = 0.f; pu = 0.f; }   // an inactive split: the output is zero whatever the interval arithmetic says
     zl[o] = pl; zu[o] = pu;
 }
 
@@ -197,15 +204,24 @@ __global__ void k_accumulate_loose(const float *__restrict__ min_lower_block, in
 
 }  // namespace
 
+// Host-side split lists of a ReLU-split batch (multipliers are ignored: plain CROWN keeps them at zero).
+struct CrownSplits {
+    const nyb200_split *splits = nullptr;
+    const int32_t *n_splits = nullptr;
+    int max_splits = 0;
+    int32_t *infeasible = nullptr;   // [D] out
+};
+
 static int crown_bounds_once(nyb200_engine *e, int net_id, const float *spec, int S, const float *in_lo,
                              const float *in_hi, int box_stride, int D, float *out_lo, float *out_hi, float *inter_lo,
-                             float *inter_hi, int *loose_out) {
+                             float *inter_hi, int *loose_out, const CrownSplits *cs = nullptr) {
     Net *net;
     NYB_TRY(find_net(e, net_id, &net));
     const NetView &nv = net->v;
     if (D <= 0 || S <= 0) return set_err(e, NYB200_ERR_SHAPE, "D and S must be positive");
     if (box_stride != 0 && box_stride != nv.dims[0]) return set_err(e, NYB200_ERR_SHAPE, "box_stride must be 0 or dims[0]");
-    if (box_stride == 0 && D != 1) return set_err(e, NYB200_ERR_SHAPE, "a shared box is one domain: D must be 1");
+    const bool split = cs && cs->max_splits > 0;
+    if (box_stride == 0 && D != 1 && !split) return set_err(e, NYB200_ERR_SHAPE, "a shared box is one domain: D must be 1");
     int max_rows = S;
     for (int k = 1; k < nv.L; ++k) max_rows = nv.dims[k] > max_rows ? nv.dims[k] : max_rows;
     if ((long)D * 2 * max_rows > 0x7fffffffL / 64) return set_err(e, NYB200_ERR_UNSUPPORTED, "batch too large for one call");
@@ -214,7 +230,7 @@ static int crown_bounds_once(nyb200_engine *e, int net_id, const float *spec, in
     cudaStream_t st = e->stream;
     // the widest pass decides the workspace: allocate for it once
     Batch b;
-    b.net_id = net_id; b.D = D; b.mode = 1; b.box_stride = box_stride; b.max_splits = 0;
+    b.net_id = net_id; b.D = D; b.mode = 1; b.box_stride = box_stride; b.max_splits = split ? cs->max_splits : 0;
     b.S = max_rows; b.R = 2 * max_rows;
     BatchPtrs p;
     NYB_TRY(batch_ptrs(e, *net, b, p));
@@ -237,8 +253,18 @@ static int crown_bounds_once(nyb200_engine *e, int net_id, const float *spec, in
         if (!derr) return NYB200_ERR_OOM;
         NYB_CUDA(e, cudaMemsetAsync(derr, 0, 4, st));
     }
-    // plain IBP of the whole network (also clears the per-domain flags and the split tables)
-    NYB_TRY(run_forward(e, *net, b, p, 2));
+    if (split) {
+        // the domains' split lists with their multipliers zeroed (plain CROWN carries none)
+        std::vector<nyb200_split> sp((size_t)D * cs->max_splits);
+        memcpy(sp.data(), cs->splits, sp.size() * sizeof(nyb200_split));
+        for (auto &x : sp) x.beta = 0.f;
+        NYB_CUDA(e, cudaMemcpyAsync(p.splits, sp.data(), sp.size() * sizeof(nyb200_split), cudaMemcpyHostToDevice, st));
+        NYB_CUDA(e, cudaMemcpyAsync(p.nsplits, cs->n_splits, (size_t)D * 4, cudaMemcpyHostToDevice, st));
+        NYB_CUDA(e, cudaStreamSynchronize(st));   // sp is a local
+    }
+    // plain IBP of the whole network (also clears the per-domain flags and the split tables); with split lists, the
+    // interval pass under the domains' clamps and no inherited bounds (mode 3)
+    NYB_TRY(run_forward(e, *net, b, p, split ? 3 : 2));
     NYB_CUDA(e, cudaMemcpyAsync(ibp_lo, p.pre_lo, (size_t)D * np * 4, cudaMemcpyDeviceToDevice, st));
     NYB_CUDA(e, cudaMemcpyAsync(ibp_hi, p.pre_hi, (size_t)D * np * 4, cudaMemcpyDeviceToDevice, st));
 
@@ -268,7 +294,7 @@ static int crown_bounds_once(nyb200_engine *e, int net_id, const float *spec, in
         long tot = (long)D * n;
         k_crown_merge<<<(unsigned)((tot + 255) / 256), 256, 0, st>>>(D, n, off, np, relu ? 1 : 0, ibp_lo, ibp_hi, p.raw_lo,
                                                                    p.raw_hi, c_lo, c_hi, lflags, p.pre_lo, p.pre_hi, p.zl, p.zu,
-                                                                   p.tab, p.zabs, p.flags);
+                                                                   p.tab, p.zabs, p.flags, split ? p.code : nullptr);
         e->launches += 2;
     }
     // specification rows: IBP image, forward image of the tightened output, full backward pass, merge
@@ -303,8 +329,15 @@ static int crown_bounds_once(nyb200_engine *e, int net_id, const float *spec, in
         if (derr) NYB_CUDA(e, cudaMemcpyAsync(&herr, derr, 4, cudaMemcpyDeviceToHost, st));
     }
     NYB_CUDA(e, cudaMemcpyAsync(loose_out, loose_acc, 4, cudaMemcpyDeviceToHost, st));
+    if (split && cs->infeasible) NYB_CUDA(e, cudaMemcpyAsync(cs->infeasible, p.flags, (size_t)D * 4, cudaMemcpyDeviceToHost, st));
     NYB_CUDA(e, cudaStreamSynchronize(st));
     if (herr) return set_err(e, NYB200_ERR_INTERNAL, "tcgen05 pipeline wait expired (code " + std::to_string(herr) + ")");
+    if (split && cs->infeasible) {
+        for (int d = 0; d < D; ++d) {
+            if (cs->infeasible[d] & kFlagInvalid) return set_err(e, NYB200_ERR_INVALID, "split entry out of range");
+            cs->infeasible[d] = (cs->infeasible[d] & kFlagInfeasible) ? 1 : 0;
+        }
+    }
     e->batch.crown_a = ps.a_final;
     e->batch.crown_lda = ps.lda; e->batch.crown_D = D; e->batch.crown_S = S; e->batch.crown_n0 = nv.dims[0];
     return NYB200_OK;
@@ -331,26 +364,40 @@ int crown_input_coeffs(nyb200_engine *e, float *lower_a, float *upper_a) {
 // On the fast path, a pass whose rounding charge is visible at the refine tolerance (narrow boxes: bounds much
 // smaller than the terms they are made of) sends the whole pipeline through the binary64 contractions once more,
 // like the batch entry points do.
-int crown_bounds(nyb200_engine *e, int net_id, const float *spec, int S, const float *in_lo, const float *in_hi,
-                 int box_stride, int D, float *out_lo, float *out_hi, float *inter_lo, float *inter_hi) {
+static int crown_bounds_cs(nyb200_engine *e, int net_id, const float *spec, int S, const float *in_lo, const float *in_hi,
+                           int box_stride, int D, float *out_lo, float *out_hi, float *inter_lo, float *inter_hi,
+                           const CrownSplits *cs) {
     if (e->error_channel == NYB200_ERRCH_REFERENCE) {
         // the reference's convention is a binary64 computation throughout (interval products included)
         const int saved = e->path;
         e->path = NYB200_PATH_F64;
         int loose_unused = 0;
-        int st = crown_bounds_once(e, net_id, spec, S, in_lo, in_hi, box_stride, D, out_lo, out_hi, inter_lo, inter_hi, &loose_unused);
+        int st = crown_bounds_once(e, net_id, spec, S, in_lo, in_hi, box_stride, D, out_lo, out_hi, inter_lo, inter_hi, &loose_unused, cs);
         e->path = saved;
         return st;
     }
     int loose = 0;
-    NYB_TRY(crown_bounds_once(e, net_id, spec, S, in_lo, in_hi, box_stride, D, out_lo, out_hi, inter_lo, inter_hi, &loose));
+    NYB_TRY(crown_bounds_once(e, net_id, spec, S, in_lo, in_hi, box_stride, D, out_lo, out_hi, inter_lo, inter_hi, &loose, cs));
     if (loose > 0 && e->path == NYB200_PATH_TF32X3 && e->refine_tol > 0.f) {
         e->path = NYB200_PATH_F64;
-        int st = crown_bounds_once(e, net_id, spec, S, in_lo, in_hi, box_stride, D, out_lo, out_hi, inter_lo, inter_hi, &loose);
+        int st = crown_bounds_once(e, net_id, spec, S, in_lo, in_hi, box_stride, D, out_lo, out_hi, inter_lo, inter_hi, &loose, cs);
         e->path = NYB200_PATH_TF32X3;
         return st;
     }
     return NYB200_OK;
+}
+
+int crown_bounds(nyb200_engine *e, int net_id, const float *spec, int S, const float *in_lo, const float *in_hi,
+                 int box_stride, int D, float *out_lo, float *out_hi, float *inter_lo, float *inter_hi) {
+    return crown_bounds_cs(e, net_id, spec, S, in_lo, in_hi, box_stride, D, out_lo, out_hi, inter_lo, inter_hi, nullptr);
+}
+
+int crown_bounds_split(nyb200_engine *e, int net_id, const float *spec, int S, const float *in_lo, const float *in_hi,
+                       int box_stride, int D, float *out_lo, float *out_hi, float *inter_lo, float *inter_hi,
+                       const nyb200_split *splits, const int32_t *n_splits, int max_splits, int32_t *infeasible) {
+    CrownSplits cs;
+    cs.splits = splits; cs.n_splits = n_splits; cs.max_splits = max_splits; cs.infeasible = infeasible;
+    return crown_bounds_cs(e, net_id, spec, S, in_lo, in_hi, box_stride, D, out_lo, out_hi, inter_lo, inter_hi, &cs);
 }
 
 }  // namespace nyb
@@ -371,4 +418,26 @@ extern "C" int32_t nyb200_crown_bounds(nyb200_engine *e, int32_t net_id, const f
     cudaError_t st = cudaSetDevice(e->device);
     if (st != cudaSuccess) return nyb::check_cuda(e, st, "cudaSetDevice");
     return nyb::crown_bounds(e, net_id, spec, S, in_lo, in_hi, box_stride, D, out_lo, out_hi, inter_lo, inter_hi);
+}
+
+extern "C" int32_t nyb200_crown_bounds_split(nyb200_engine *e, int32_t net_id, const float *spec, int32_t S, const float *in_lo,
+                                             const float *in_hi, int32_t box_stride, const nyb200_split *splits,
+                                             const int32_t *n_splits, int32_t max_splits, int32_t D, float *out_lo,
+                                             float *out_hi, float *inter_lo, float *inter_hi, int32_t *infeasible) {
+    if (!e || !spec || !in_lo || !in_hi || !out_lo || !out_hi || !n_splits || !infeasible) return NYB200_ERR_INVALID;
+    if (max_splits < 0 || (max_splits > 0 && !splits)) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    cudaError_t st = cudaSetDevice(e->device);
+    if (st != cudaSuccess) return nyb::check_cuda(e, st, "cudaSetDevice");
+    if (e->error_channel == NYB200_ERRCH_REFERENCE)
+        return nyb::set_err(e, NYB200_ERR_UNSUPPORTED, "split domains are bounded in the default error convention");
+    for (int d = 0; d < D; ++d)
+        if (n_splits[d] < 0 || n_splits[d] > max_splits) return nyb::set_err(e, NYB200_ERR_INVALID, "n_splits out of range");
+    if (max_splits == 0) {
+        // no split anywhere: the plain pipeline (a shared box is then one domain)
+        for (int d = 0; d < D; ++d) infeasible[d] = 0;
+        return nyb::crown_bounds(e, net_id, spec, S, in_lo, in_hi, box_stride, D, out_lo, out_hi, inter_lo, inter_hi);
+    }
+    return nyb::crown_bounds_split(e, net_id, spec, S, in_lo, in_hi, box_stride, D, out_lo, out_hi, inter_lo, inter_hi, splits,
+                                   n_splits, max_splits, infeasible);
 }

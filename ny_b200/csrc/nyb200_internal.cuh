@@ -93,6 +93,7 @@ struct Batch {
     bool finished = false;  // results of the last run have been checked (and refined if needed)
     int refined = 0;        // domains that triggered the binary64 re-run of the last batch
     int opt_iterations = 0; // iterations of the last parameter optimisation
+    int inh_stride = 0;     // 0: one inherited-bound vector for all domains; nps: one row per domain (nyb200_batch_set_inherited)
     bool external_tables = false;  // relaxation tables, abs-max tables and q were uploaded by a reference-shaped call:
                                    // nothing may re-derive them with an interval pass
     // Left behind by the last plain-CROWN call: the input-level coefficient rows of its final pass
@@ -187,7 +188,7 @@ void launch_ibp_linear(nyb200_engine *e, const NetView &nv, int k, int Deff, con
                        long in_dstride, float *raw_lo, float *raw_hi, float *q, long out_dstride);
 // Per-domain finish of Linear_k's output: intersect / clamp / relaxation tables / post-activation.
 void launch_ibp_finish(nyb200_engine *e, const NetView &nv, int k, int D, int mode, const float *raw_lo,
-                       const float *raw_hi, long raw_dstride, const float *inh_lo, const float *inh_hi,
+                       const float *raw_hi, long raw_dstride, const float *inh_lo, const float *inh_hi, long inh_dstride,
                        const signed char *code, const float *sbeta, const float *alpha, float *pre_lo, float *pre_hi,
                        float *zl, float *zu, float4 *tab, float *zabs, int *flags, const float *F = nullptr, int ldf = 0,
                        double eps = 0.0, float *q = nullptr, float fwd_tol = 0.f,

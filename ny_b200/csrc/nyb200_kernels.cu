@@ -208,7 +208,7 @@ k_ibp_linear_warp(int Deff, int n_in, int n_out, const float *__restrict__ W, co
 // (beta_crown/engine/backward/relu_backward.rs:63-101) and the post-activation interval (:428-548).
 __global__ void k_ibp_finish(NetView nv, int k, int D, int mode, int last, const float *__restrict__ raw_lo,
                              const float *__restrict__ raw_hi, long raw_ds, const float *__restrict__ inh_lo,
-                             const float *__restrict__ inh_hi, const signed char *__restrict__ code,
+                             const float *__restrict__ inh_hi, long inh_ds, const signed char *__restrict__ code,
                              const float *__restrict__ sbeta, const float *__restrict__ alpha,
                              float *__restrict__ pre_lo, float *__restrict__ pre_hi, float *__restrict__ zl,
                              float *__restrict__ zu, float4 *__restrict__ tab, float *__restrict__ zabs,
@@ -246,9 +246,10 @@ __global__ void k_ibp_finish(NetView nv, int k, int D, int mode, int last, const
         l = raw_lo[(long)d * raw_ds + off + j];
         u = raw_hi[(long)d * raw_ds + off + j];
     }
-    if (mode == 0 && inh_lo) { l = inh_lo[off + j]; u = inh_hi[off + j]; }
+    const long io = (long)d * inh_ds + off + j;   // inh_ds = 0: the domains share one inherited vector
+    if (mode == 0 && inh_lo) { l = inh_lo[io]; u = inh_hi[io]; }
     else if (mode == 1 && inh_lo) {
-        float il = inh_lo[off + j], iu = inh_hi[off + j];
+        float il = inh_lo[io], iu = inh_hi[io];
         if (!(isnan(l) || isnan(u) || isnan(il) || isnan(iu))) {
             float tl = fmaxf(l, il), tu = fminf(u, iu);
             if (tl <= tu) { l = tl; u = tu; } else { l = fminf(l, il); u = fmaxf(u, iu); }
@@ -852,14 +853,14 @@ void launch_ibp_linear(nyb200_engine *e, const NetView &nv, int k, int Deff, con
 }
 
 void launch_ibp_finish(nyb200_engine *e, const NetView &nv, int k, int D, int mode, const float *raw_lo,
-                       const float *raw_hi, long raw_dstride, const float *inh_lo, const float *inh_hi,
+                       const float *raw_hi, long raw_dstride, const float *inh_lo, const float *inh_hi, long inh_dstride,
                        const signed char *code, const float *sbeta, const float *alpha, float *pre_lo, float *pre_hi,
                        float *zl, float *zu, float4 *tab, float *zabs, int *flags, const float *F, int ldf, double eps,
                        float *q, float fwd_tol, float *cj, float cj_eps, float cj_kappa) {
     long total = (long)D * nv.dims[k + 1];
     int last = (k == nv.L - 1);
     launch_pdl(k_ibp_finish, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, e->stream, nv, k, D, mode, last, raw_lo, raw_hi,
-               raw_dstride, inh_lo, inh_hi, code, sbeta, alpha, pre_lo, pre_hi, zl, zu, tab, zabs, flags, F, ldf, eps, q, fwd_tol, cj,
+               raw_dstride, inh_lo, inh_hi, inh_dstride, code, sbeta, alpha, pre_lo, pre_hi, zl, zu, tab, zabs, flags, F, ldf, eps, q, fwd_tol, cj,
                cj_eps, cj_kappa);
     NYB_COUNT(e);
 }

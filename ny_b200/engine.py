@@ -33,7 +33,7 @@ ERRCH_IMMEDIATE, ERRCH_REFERENCE = 0, 1
 
 EXPORTS = [
     "nyb200_create", "nyb200_destroy", "nyb200_backend_provenance", "nyb200_last_error", "nyb200_set_stream",
-    "nyb200_set_path", "nyb200_set_refine_tolerance", "nyb200_batch_refined", "nyb200_batch_poll", "nyb200_launch_count", "nyb200_clear_working_set", "nyb200_gemm_f32", "nyb200_net_create",
+    "nyb200_set_path", "nyb200_set_refine_tolerance", "nyb200_batch_refined", "nyb200_batch_poll", "nyb200_crown_bounds_split", "nyb200_batch_set_inherited", "nyb200_launch_count", "nyb200_clear_working_set", "nyb200_gemm_f32", "nyb200_net_create",
     "nyb200_net_destroy", "nyb200_ibp_forward", "nyb200_ibp_forward_noalloc", "nyb200_bab_bound_batch", "nyb200_batch_upload", "nyb200_batch_run",
     "nyb200_batch_download", "nyb200_batch_min_lower", "nyb200_batch_min_lower_device",
     "nyb200_batch_download_pre_bounds", "nyb200_batch_select_branch", "nyb200_timing_enable", "nyb200_timing_reset",
@@ -718,6 +718,40 @@ class B200Engine:
         self._check(self._L.nyb200_crown_bounds(self._h, net_id, _fp(spec), S, _fp(lo), _fp(hi), 0 if one else int(net.dims[0]),
                                                 D, _fp(ol), _fp(ou), _fp(il), _fp(iu)))
         return ol, ou, il, iu
+
+    def crown_bounds_split(self, net_id, spec, in_lo, in_hi, splits, n_splits):
+        """Plain CROWN with CROWN-IBP intermediate bounds for ReLU-split domains: in_lo/in_hi [n0] (one box shared by
+        all domains) or [D, n0]; splits [D, max_splits] of SPLIT_DTYPE, n_splits [D].  Returns (lower [D, S],
+        upper [D, S], inter_lo [D, n_pre], inter_hi [D, n_pre], infeasible [D])."""
+        net = self._nets[net_id]
+        spec, lo, hi = _f32(spec), _f32(in_lo), _f32(in_hi)
+        ns = np.ascontiguousarray(n_splits, np.int32)
+        D = len(ns)
+        sp = np.ascontiguousarray(splits, SPLIT_DTYPE).reshape(D, -1)
+        if spec.ndim != 2 or spec.shape[1] != net.dims[-1]:
+            raise EngineError(SHAPE, f"spec shape {spec.shape}")
+        shared = lo.ndim == 1
+        if lo.shape != hi.shape or lo.shape[-1] != net.dims[0] or (not shared and lo.shape[0] != D):
+            raise EngineError(SHAPE, "crown_bounds_split: box shape")
+        S = spec.shape[0]
+        ol, ou = np.empty((D, S), np.float32), np.empty((D, S), np.float32)
+        il, iu = np.empty((D, net.n_pre), np.float32), np.empty((D, net.n_pre), np.float32)
+        inf = np.zeros(D, np.int32)
+        fn = self._L.nyb200_crown_bounds_split
+        fn.argtypes = [C.c_void_p, C.c_int32, C.POINTER(C.c_float), C.c_int32, C.POINTER(C.c_float), C.POINTER(C.c_float),
+                       C.c_int32, C.c_void_p, C.POINTER(C.c_int32), C.c_int32, C.c_int32, C.POINTER(C.c_float),
+                       C.POINTER(C.c_float), C.POINTER(C.c_float), C.POINTER(C.c_float), C.POINTER(C.c_int32)]
+        self._check(fn(self._h, net_id, _fp(spec), S, _fp(lo), _fp(hi), 0 if shared else int(net.dims[0]), sp.ctypes.data,
+                       ns.ctypes.data_as(C.POINTER(C.c_int32)), int(sp.shape[1]), D, _fp(ol), _fp(ou), _fp(il), _fp(iu),
+                       inf.ctypes.data_as(C.POINTER(C.c_int32))))
+        return ol, ou, il, iu, inf
+
+    def batch_set_inherited(self, inh_lo, inh_hi):
+        """Per-domain inherited bounds [D, n_pre] for the resident batch (see nyb200_batch_set_inherited)."""
+        lo, hi = _f32(inh_lo), _f32(inh_hi)
+        fn = self._L.nyb200_batch_set_inherited
+        fn.argtypes = [C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_float)]
+        self._check(fn(self._h, _fp(lo), _fp(hi)))
 
     def crown_input_coeffs(self, D: int, S: int, n0: int):
         """(lower_a, upper_a), each [D, S, n0]: input-level coefficients of the last crown_bounds call."""

@@ -762,14 +762,51 @@ static int intersect_per_element(float *al, float *au, const float *bl, const fl
     return 1;
 }
 
+/* Pre-activation clamps of a ReLU-split domain on layer k's tightened bounds (constraints/lookups.rs:138-185):
+ * active l = max(l, 0), inactive u = min(u, 0).  Returns 1 when a clamp empties an interval (the domain is infeasible). */
+static int clamp_splits(const nyo_split *splits, int n_splits, int k, float *l, float *u) {
+    int empty = 0;
+    for (int s = 0; s < n_splits; ++s) if (splits[s].relu == k) {
+        int j = splits[s].neuron;
+        if (splits[s].sign > 0) { if (!isnan(l[j])) l[j] = fmaxf(l[j], 0.0f); }
+        else { if (!isnan(u[j])) u[j] = fminf(u[j], 0.0f); }
+        if (l[j] > u[j]) empty = 1;
+    }
+    return empty;
+}
+
+static int crown_impl(const nyo_net *net, const float *in_lo, const float *in_hi, const nyo_split *splits, int n_splits,
+                      float *out_lo, float *out_hi, float *inter_lo, float *inter_hi);
+
 int nyo_crown(const nyo_net *net, const float *in_lo, const float *in_hi, float *out_lo, float *out_hi,
               float *inter_lo, float *inter_hi) {
+    return crown_impl(net, in_lo, in_hi, NULL, 0, out_lo, out_hi, inter_lo, inter_hi);
+}
+
+/* The same pipeline for a ReLU-split domain (the CROWN-IBP collection of network/ibp/crown_ibp.rs:32-420 run under the
+ * domain's clamps): the interval pass is the constrained forward pass without inherited bounds, every layer's tightened
+ * bound is clamped before its relaxation is taken, split multipliers stay at zero.  Returns 1 for an infeasible
+ * domain (outputs untouched), 0 otherwise. */
+int nyo_crown_split(const nyo_net *net, const float *in_lo, const float *in_hi, const nyo_split *splits, int n_splits,
+                    float *out_lo, float *out_hi, float *inter_lo, float *inter_hi) {
+    return crown_impl(net, in_lo, in_hi, splits, n_splits, out_lo, out_hi, inter_lo, inter_hi);
+}
+
+static int crown_impl(const nyo_net *net, const float *in_lo, const float *in_hi, const nyo_split *splits, int n_splits,
+                      float *out_lo, float *out_hi, float *inter_lo, float *inter_hi) {
     if (net_has_skip(net)) return -2;
     int L = net->n_linear;
     size_t total = pre_offset(net, L);
     float *ibp_l = (float *)malloc(4 * total), *ibp_u = (float *)malloc(4 * total);
     float *t_l = (float *)malloc(4 * total), *t_u = (float *)malloc(4 * total);
-    nyo_ibp_forward(net, in_lo, in_hi, ibp_l, ibp_u);
+    if (n_splits > 0) {
+        float *no_l = (float *)calloc(total, 4), *no_u = (float *)calloc(total, 4);   /* no inherited bounds */
+        for (size_t i = 0; i < total; ++i) { no_l[i] = -INFINITY; no_u[i] = INFINITY; }
+        int bad = nyo_domain_bounds(net, in_lo, in_hi, no_l, no_u, splits, n_splits, 1, ibp_l, ibp_u);
+        free(no_l); free(no_u);
+        if (bad) { free(ibp_l); free(ibp_u); free(t_l); free(t_u); return 1; }
+    } else nyo_ibp_forward(net, in_lo, in_hi, ibp_l, ibp_u);
+    int infeasible = 0;
     int maxn = 0;
     for (int k = 0; k <= L; ++k) if (net->dims[k] > maxn) maxn = net->dims[k];
     float *zl = (float *)malloc(4 * (size_t)maxn), *zu = (float *)malloc(4 * (size_t)maxn);
@@ -788,6 +825,7 @@ int nyo_crown(const nyo_net *net, const float *in_lo, const float *in_hi, float 
         for (int j = 0; j < n; ++j) if (!(il[j] >= 0.0f || iu[j] <= 0.0f)) { all_stable = 0; break; }
         if (k < L - 1 && relu_after(net, k) && all_stable) { /* ReLU-stable skip (:113-140) */
             memcpy(t_l + o, il, 4 * (size_t)n); memcpy(t_u + o, iu, 4 * (size_t)n);
+            infeasible |= clamp_splits(splits, n_splits, k, t_l + o, t_u + o);
             continue;
         }
         /* crown_partial.rs:166-182: forward bound of this layer from the tightened prior bounds */
@@ -847,6 +885,11 @@ int nyo_crown(const nyo_net *net, const float *in_lo, const float *in_hi, float 
         /* crown_ibp.rs:186-215: intersect the plain IBP bound with the CROWN bound */
         memcpy(t_l + o, il, 4 * (size_t)n); memcpy(t_u + o, iu, 4 * (size_t)n);
         intersect_per_element(t_l + o, t_u + o, cl, cu, n);
+        if (k < L - 1) infeasible |= clamp_splits(splits, n_splits, k, t_l + o, t_u + o);
+    }
+    if (infeasible) {
+        free(ibp_l); free(ibp_u); free(t_l); free(t_u); free(zl); free(zu); free(fl); free(fu); free(cl); free(cu);
+        return 1;
     }
     /* final backward (crown.rs:262-...) + tighten (crown/tighten.rs:126-190) */
     {

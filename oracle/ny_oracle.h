@@ -75,6 +75,9 @@ int nyo_ibp_forward(const nyo_net *net, const float *in_lo, const float *in_hi,
  * tightened pre-activation bounds (same layout as nyo_ibp_forward). */
 int nyo_crown(const nyo_net *net, const float *in_lo, const float *in_hi,
               float *out_lo, float *out_hi, float *inter_lo, float *inter_hi);
+/* nyo_crown for a ReLU-split domain (clamps on every layer's tightened bound, multipliers at zero); 1 = infeasible. */
+int nyo_crown_split(const nyo_net *net, const float *in_lo, const float *in_hi, const nyo_split *splits, int n_splits,
+                    float *out_lo, float *out_hi, float *inter_lo, float *inter_hi);
 
 /* beta-CROWN bound of one BaB domain given its pre-activation bounds
  * (layout as nyo_ibp_forward, only the first L-1 blocks are read), its split list, and

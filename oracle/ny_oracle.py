@@ -58,6 +58,7 @@ def lib():
         L.nyo_certified_affine_sum.argtypes = [C.c_float, fp, fp, C.c_int, C.c_int]
         L.nyo_ibp_forward.argtypes = [np_, fp, fp, fp, fp]
         L.nyo_crown.argtypes = [np_, fp, fp, fp, fp, fp, fp]
+        L.nyo_crown_split.argtypes = [np_, fp, fp, C.c_void_p, C.c_int, fp, fp, fp, fp]
         L.nyo_beta_crown_bound.argtypes = [np_, fp, fp, fp, fp, C.c_void_p, C.c_int, fp, fp, fp]
         L.nyo_domain_bounds.argtypes = [np_, fp, fp, fp, fp, C.c_void_p, C.c_int, C.c_int, fp, fp]
         L.nyo_bab_bound_batch.argtypes = [np_, fp, fp, fp, fp, C.c_void_p, ip, C.c_int, C.c_int, C.c_int,
@@ -278,6 +279,23 @@ def _crown(net: Net, lo, hi, want_intermediate):
     iu = np.empty(net.n_pre, np.float32) if want_intermediate else None
     lib().nyo_crown(C.byref(net.c), _fp(lo), _fp(hi), _fp(ol), _fp(ou), _fp(il), _fp(iu))
     return (ol, ou, il, iu) if want_intermediate else (ol, ou)
+
+
+def crown_split(net: Net, lo, hi, splits: np.ndarray, error_channel=False):
+    """Plain CROWN with CROWN-IBP intermediates for a ReLU-split domain: (lower, upper, inter_lo, inter_hi, infeasible)."""
+    lo, hi = _f32(lo), _f32(hi)
+    n = int(net.dims[-1])
+    ol, ou = np.empty(n, np.float32), np.empty(n, np.float32)
+    il, iu = np.empty(net.n_pre, np.float32), np.empty(net.n_pre, np.float32)
+    splits = np.ascontiguousarray(splits, SPLIT_DTYPE)
+    lib().nyo_set_error_channel(1 if error_channel else 0)
+    try:
+        st = lib().nyo_crown_split(C.byref(net.c), _fp(lo), _fp(hi), splits.ctypes.data, len(splits), _fp(ol), _fp(ou), _fp(il), _fp(iu))
+    finally:
+        lib().nyo_set_error_channel(1)
+    if st < 0:
+        raise ValueError("nyo_crown_split: unsupported network")
+    return ol, ou, il, iu, bool(st)
 
 
 def make_splits(items) -> np.ndarray:

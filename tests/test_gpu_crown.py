@@ -149,3 +149,61 @@ def test_crown_batch_of_boxes(eng, oracle):
     one_lo, one_hi, _, _ = eng.crown_bounds(nid, wl.spec, lo[5], hi[5])
     assert np.array_equal(one_lo[0], glo[5]) and np.array_equal(one_hi[0], ghi[5])
     eng.release_network(nid)
+
+
+def test_crown_under_relu_splits_matches_oracle_and_tightens_the_batch(eng, oracle):
+    """Per-domain CROWN-tightened intermediate bounds for ReLU-split domains (nyb200_crown_bounds_split: the CROWN-IBP
+    collection of network/ibp/crown_ibp.rs:32-420 under the clamps of constraints/lookups.rs:138-185): bounds,
+    intermediates and infeasibility against the oracle's pipeline with the same clamps, sampled executions that satisfy
+    the splits, the unsplit domain equal to the plain pipeline; then the same domains through the bound batch with
+    their own tightened intermediates as inherited bounds (nyb200_batch_set_inherited), which may only help."""
+    wl = W.config_mlp_bab(seed=57, hidden=40, depth=4, n_in=24, eps=0.03, n_fix=3)
+    onet = oracle.Net(wl.net.weights, wl.net.biases)
+    ospec = onet.with_spec(wl.spec)
+    nid = eng.register_network(wl.net)
+    pl, pu = eng.ibp_forward_gpu(nid, wl.in_lo, wl.in_hi)
+    rl, ru = pl[0].copy(), pu[0].copy()
+    D, S = 24, wl.spec.shape[0]
+    splits, ns = W.draw_domains(wl, rl, ru, D)
+    ns = ns.copy()
+    ns[0] = 0
+    glo, ghi, gil, giu, ginf = eng.crown_bounds_split(nid, wl.spec, wl.in_lo, wl.in_hi, splits, ns)
+    plo, phi, pil, piu = eng.crown_bounds(nid, wl.spec, wl.in_lo, wl.in_hi)
+    assert np.array_equal(glo[0], plo[0]) and np.array_equal(gil[0], pil[0]) and ginf[0] == 0     # no split: the plain pipeline
+    n_pre = wl.net.n_pre
+    checked = 0
+    for d in range(D):
+        sp = splits[d][: ns[d]]
+        olo, ohi, oil, oiu, oinf = oracle.crown_split(ospec, wl.in_lo, wl.in_hi, sp)
+        assert bool(ginf[d]) == oinf, d
+        if oinf:
+            continue
+        scale = max(np.abs(olo).max(), np.abs(ohi).max())
+        assert np.all(np.abs(glo[d] - olo) <= 2e-4 * scale) and np.all(np.abs(ghi[d] - ohi) <= 2e-4 * scale), d
+        iscale = max(np.abs(oil[:n_pre]).max(), np.abs(oiu[:n_pre]).max())
+        assert np.all(np.abs(gil[d] - oil[:n_pre]) <= 2e-4 * iscale) and np.all(np.abs(giu[d] - oiu[:n_pre]) <= 2e-4 * iscale), d
+        for s in sp:                                   # the clamps are visible in the returned intermediates
+            o = int(np.concatenate([[0], np.cumsum(wl.net.dims[1:])])[s["relu"]] + s["neuron"])
+            assert (gil[d][o] >= 0) if s["sign"] > 0 else (giu[d][o] <= 0)
+        mn = W.sample_min_margin(wl, 20000, 400 + d, sp)
+        ok = np.isfinite(mn)
+        assert np.all(glo[d][ok] <= mn[ok]), d
+        checked += 1
+    assert checked > D // 2
+    # the bound batch on the same domains: shared root bounds, then every domain's own tightened intermediates
+    zero_beta = splits.copy()
+    zero_beta["beta"] = 0.0
+    b0, _, inf0 = eng.bab_bound_batch(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, zero_beta, ns, mode=1)
+    eng.batch_upload(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, zero_beta, ns, mode=1)
+    eng.batch_set_inherited(gil, giu)
+    eng.batch_run()
+    b1, _, inf1 = eng.batch_download()
+    ok = (inf0 == 0) & (inf1 == 0) & (ginf == 0)
+    scale = np.abs(b0[ok]).max()
+    assert ok.sum() > D // 2
+    assert np.all(b1[ok] >= b0[ok] - 2e-4 * scale) and b1[ok].sum() > b0[ok].sum()
+    for d in np.flatnonzero(ok)[:6]:
+        mn = W.sample_min_margin(wl, 20000, 400 + d, splits[d][: ns[d]])
+        fin = np.isfinite(mn)
+        assert np.all(b1[d][fin] <= mn[fin]), d
+    eng.release_network(nid)
