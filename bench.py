@@ -682,7 +682,12 @@ def run_search(args, rank, world, local_rank):
     rounds = 40
     opt_it = args.search_iterations
 
+    resident = bool(args.resident) and dist is None and opt_it <= 1
+
     def search():
+        if resident:   # the open domain set stays on the device: one call per round
+            return bab.verify_resident(eng, nid, wl.net, prop, batch=batch, max_rounds=rounds, branching=1, pgd_restarts=64,
+                                       pgd_steps=10)
         return bab.verify(eng, nid, wl.net, prop, batch=batch, max_rounds=rounds, optimize_iterations=opt_it, branching=1,
                           pgd_restarts=64, pgd_steps=10, dist=dist, dist_device=dev)
 
@@ -729,6 +734,8 @@ def run_search(args, rank, world, local_rank):
                                    + (f"{opt_it} optimisation iterations per domain with warm start" if opt_it > 1 else "one bound per domain")
                                    + ", attack and root bound included",
                        "parallelism": f"frontier sharded x{world}",
+                       "frontier": "device-resident (nyb200_frontier_round: pop, bound, prune, branch, push per call)" if resident
+                                   else "host (numpy blocks; upload of the children's split lists every round)",
                        "timing": "wall clock around the search calls, max over ranks", "status": r.status,
                        "domains_per_search": r.domains_bounded, "open_at_stop": r.open_domains},
             "rebalance": moved if world > 1 else None,
@@ -851,6 +858,8 @@ def main():
     ap.add_argument("--workload", default="bab", choices=["bab", "alpha-crown", "cnn", "resnet", "pgd", "pgd-resnet", "bab-search"],
                     help="bab: the headline beta-CROWN batch (default); alpha-crown: the alpha optimisation case; "
                          "cnn: the convolutional case (both 1 GPU)")
+    ap.add_argument("--resident", type=int, default=1,
+                    help="bab-search on one GPU: 1 keeps the frontier on the device (default), 0 runs the host loop")
     ap.add_argument("--search-iterations", type=int, default=0,
                     help="bab-search: optimisation iterations per domain (0 = one bound per domain, the reference's throughput default)")
     ap.add_argument("--domains", type=int, default=D_PER_GPU, help="domains per GPU (profiling runs use a smaller batch)")

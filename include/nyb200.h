@@ -79,6 +79,24 @@ int32_t nyb200_set_fusion(nyb200_engine *e, int32_t on);
  * nyb200_batch_refined reports how many domains of the last run triggered it (0 = fast path only). */
 int32_t nyb200_set_refine_tolerance(nyb200_engine *e, float tol);
 int32_t nyb200_batch_refined(nyb200_engine *e, int32_t *n_domains);
+/* ---- device-resident BaB frontier (the "resident frontier" extension; no counterpart in the reference's traits, whose
+ * search loop keeps its domains on the host: crates/ny-propagate/src/beta_crown/engine/core.rs:492-735).
+ * nyb200_frontier_create: the open set starts as the root domain (no splits).  spec [S x out], thresholds [S] and
+ * owner [S] (the clause a row belongs to, 0 .. n_clauses-1; S <= 64, n_clauses <= 32): a domain is decided when it is
+ * infeasible or when every clause has a row whose lower bound exceeds its threshold.  in_lo / in_hi: the shared box;
+ * inh_lo / inh_hi [sum_{k>=1} dims[k]]: inherited (root) pre-activation bounds.  max_depth: longest split history the
+ * ring can hold; capacity: domains.
+ * nyb200_frontier_round: pops up to `batch` domains from the front, bounds them (constrained forward pass, one bound
+ * per domain, multipliers zero), decides, picks the split neuron of every open domain with the given score
+ * (NYB200_BRANCH_*), appends both children at the back (active child first).  stats_out [6]: bounded, verified,
+ * infeasible, stuck (undecided with no neuron left: the batch then stays in the frontier and nothing is appended),
+ * open domains afterwards, deepest history bounded; *min_lower the smallest lower bound among the round's feasible
+ * domains.  The order of domains is the host loop's, so a search through these calls bounds the same domains. */
+int32_t nyb200_frontier_create(nyb200_engine *e, int32_t net_id, const float *spec, const float *thresholds,
+                               const int32_t *owner, int32_t S, int32_t n_clauses, const float *in_lo, const float *in_hi,
+                               const float *inh_lo, const float *inh_hi, int32_t max_depth, int64_t capacity);
+int32_t nyb200_frontier_round(nyb200_engine *e, int32_t batch, int32_t branching, int64_t *stats_out, float *min_lower);
+void nyb200_frontier_destroy(nyb200_engine *e);
 /* Non-blocking look at the runs launched so far (no counterpart in the reference, whose calls return finished
  * results): every nyb200_batch_run ends with a one-thread kernel that publishes, to mapped host memory, the run's
  * sequence number, the tensor pipeline's error word and the number of domains flagged for the binary64 re-run.

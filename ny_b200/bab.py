@@ -467,6 +467,50 @@ def verify(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: i
     return stop("verified" if total_open == 0 else "unknown")
 
 
+def verify_resident(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: int = 64,
+                    max_domains: int = 1 << 20, pgd_restarts: int = 256, pgd_steps: int = 50, branching: int = 1,
+                    timeout_s: float | None = None) -> VerifyResult:
+    """The search of verify() with the open domain set kept on the device (nyb200_frontier_*): attack and root bound
+    as there, then one device call per round that pops a batch, bounds it (one bound per domain, multipliers at
+    zero), prunes verified and infeasible domains, picks every open domain's split neuron (0 width, 1 intercept,
+    2 BaBSR) and appends both children.  Same order of domains as the host loop, hence the same counts and verdicts;
+    what it leaves out is the optimising search with warm starts, the metrics file and the frontier dump."""
+    t0 = time.time()
+    if not prop.violation:
+        return VerifyResult("verified")
+    spec, thr, owner = _rows(prop)
+    n_clauses = len(prop.violation)
+    ce = attack(eng, net_id, net, prop, pgd_restarts, pgd_steps)
+    if ce is not None:
+        return VerifyResult("violated", ce[0], ce[1])
+    rlo, _, inter_lo, inter_hi = eng.crown_bounds(net_id, spec, prop.in_lo, prop.in_hi)
+    res = VerifyResult("unknown", root_lower=rlo[0].copy(), domains_bounded=1)
+    if _verified_mask(rlo, thr, owner, n_clauses)[0]:
+        res.status = "verified"
+        return res
+    eng.frontier_create(net_id, spec, thr, owner, n_clauses, prop.in_lo, prop.in_hi, inter_lo[0], inter_hi[0],
+                        max_depth=max_rounds + 2, capacity=min(2 * max_domains + 2 * batch, 1 << 22))
+    try:
+        open_now = 1
+        while open_now > 0 and res.rounds < max_rounds:
+            if timeout_s is not None and time.time() - t0 > timeout_s:
+                res.status = "timeout"
+                break
+            bounded, _, _, stuck, open_now, _, _ = eng.frontier_round(batch, branching)
+            res.rounds += 1
+            res.domains_bounded += bounded
+            if stuck:
+                break
+            if open_now > max_domains:
+                break
+        res.open_domains = open_now
+        if open_now == 0:
+            res.status = "verified"
+    finally:
+        eng.frontier_destroy()
+    return res
+
+
 def _rebalance(frontier: "Frontier", dist, device, sharding, stats=None):
     """Levels the ranks' shards.  The shard sizes are gathered first and nothing else happens while they are level;
     otherwise the histories are padded to the deepest one of any rank and moved point to point, the warm-start

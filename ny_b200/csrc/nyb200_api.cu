@@ -81,6 +81,7 @@ void nyb200_destroy(nyb200_engine *e) {
     for (auto &kv : e->ws) if (kv.second.p) cudaFree(kv.second.p);
     for (auto &kv : e->nets) free_net(kv.second);
     if (e->status_host) cudaFreeHost(e->status_host);
+    if (e->frontier) nyb::frontier_free(e->frontier);
     for (int i = 0; i < 3; ++i) if (e->timing.ev[i]) cudaEventDestroy(e->timing.ev[i]);
     for (cudaEvent_t ev : e->timing.kev) cudaEventDestroy(ev);
     for (int i = 0; i < 2; ++i) if (e->timing.cev[i]) cudaEventDestroy(e->timing.cev[i]);
@@ -894,6 +895,7 @@ int download_batch(nyb200_engine *e, float *out_lo, float *out_hi, int32_t *infe
 
 namespace nyb {
 int finish_batch_public(nyb200_engine *e) { return finish_batch(e); }
+int run_batch_public(nyb200_engine *e) { return run_batch(e); }
 }
 
 extern "C" {

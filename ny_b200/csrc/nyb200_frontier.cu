@@ -1,0 +1,261 @@
+// Device-resident BaB frontier: the open domain set of a ReLU-split branch-and-bound search lives on the GPU as a
+// ring of split histories, and one call per round pops a batch, bounds it, decides every domain, picks the split
+// neuron of every open one and appends both children - what BetaCrownVerifier's loop does between engine calls
+// (crates/ny-propagate/src/beta_crown/engine/core.rs:492-735: pop batch, bound, prune verified / infeasible, branch,
+// push children) without the split lists ever visiting the host.  The order is the host loop's: batches leave from
+// the front, the children of the open domains are appended at the back in domain order, active child first, so a
+// search run through this file bounds exactly the domains the host loop (ny_b200/bab.py) bounds.
+//
+// One bound per domain with the multipliers at zero (the reference's throughput default, beta_iterations = 0); the
+// optimising search with warm starts stays on the host loop.
+#include <cstring>
+#include <vector>
+
+#include "nyb200_internal.cuh"
+
+namespace nyb {
+
+constexpr int kMaxRowsF = 64;
+
+struct ResidentFrontier {
+    int net_id = -1, S = 0, maxd = 0, n_clauses = 0;
+    long cap = 0, head = 0, count = 0;
+    nyb200_split *buf = nullptr;   // [cap x maxd]
+    int *ns = nullptr;             // [cap]
+    int *stats = nullptr;          // device: open, verified, infeasible, stuck, (float) min lower
+    float *thr = nullptr;          // device [S]
+    int *owner = nullptr;          // device [S]
+    std::vector<float> spec, in_lo, in_hi, inh_lo, inh_hi;
+    long bounded = 0;
+};
+
+void frontier_free(ResidentFrontier *f) {
+    if (!f) return;
+    cudaFree(f->buf); cudaFree(f->ns); cudaFree(f->stats); cudaFree(f->thr); cudaFree(f->owner);
+    delete f;
+}
+
+namespace {
+
+// done[d] = 1 when the domain needs no children: infeasible, or every clause of the violation has a row whose lower
+// bound is above its threshold (strictly: the verdict predicate of beta_crown/config/tests.rs).  NaN never verifies.
+__global__ void k_frontier_decide(int D, int S, int n_clauses, const float *__restrict__ out_lo, const int *__restrict__ flags,
+                                  const float *__restrict__ thr, const int *__restrict__ owner, int *__restrict__ done,
+                                  int *__restrict__ stats) {
+    int d = blockIdx.x * blockDim.x + threadIdx.x;
+    if (d >= D) return;
+    const int fl = flags[d];
+    if (fl & kFlagInfeasible) { done[d] = 1; atomicAdd(&stats[2], 1); return; }
+    unsigned refuted = 0;
+    float m = INFINITY;
+    for (int s = 0; s < S; ++s) {
+        const float l = out_lo[(long)d * S + s];
+        if (l > thr[s]) refuted |= 1u << owner[s];
+        m = fminf(m, l);
+    }
+    const bool verified = refuted == (n_clauses >= 32 ? 0xffffffffu : ((1u << n_clauses) - 1u));
+    done[d] = verified ? 1 : 0;
+    if (verified) atomicAdd(&stats[1], 1);
+    // global lower bound over feasible domains (float bits as ordered integers: the values are compared as floats
+    // by the host from the per-round minimum the concretisation already keeps; this one is per search round)
+    if (!isnan(m)) {
+        int *p = &stats[4];
+        int old = *p;
+        while (__int_as_float(old) > m) {
+            int prev = atomicCAS(p, old, __float_as_int(m));
+            if (prev == old) break;
+            old = prev;
+        }
+    }
+}
+
+// Exclusive scan of the open flags (single block, D <= 1 << 16), the number of open domains and of stuck ones
+// (undecided, but no neuron left to split).
+__global__ void k_frontier_scan(int D, const int *__restrict__ done, const int *__restrict__ relu, int *__restrict__ pos,
+                                int *__restrict__ stats) {
+    __shared__ int part[1024];
+    const int t = threadIdx.x, per = (D + 1023) / 1024;
+    const int b0 = t * per, b1 = min(D, b0 + per);
+    int c = 0, stuck = 0;
+    for (int d = b0; d < b1; ++d) {
+        const bool open = !done[d];
+        if (open && relu[d] >= 0) ++c;
+        if (open && relu[d] < 0) ++stuck;
+    }
+    part[t] = c;
+    __syncthreads();
+    for (int o = 1; o < 1024; o <<= 1) {   // Hillis-Steele inclusive scan
+        int v = t >= o ? part[t - o] : 0;
+        __syncthreads();
+        part[t] += v;
+        __syncthreads();
+    }
+    int run = part[t] - c;
+    for (int d = b0; d < b1; ++d) {
+        const bool open = !done[d] && relu[d] >= 0;
+        pos[d] = open ? run : -1;
+        if (open) ++run;
+    }
+    if (stuck) atomicAdd(&stats[3], stuck);
+    if (t == 1023) stats[0] = part[1023];
+}
+
+// Both children of every open domain: the parent's history with the new split appended (multiplier 0), the active
+// child at ring slot tail + 2 pos, the inactive one behind it.
+__global__ void k_frontier_children(int D, int maxd, long cap, long tail, const nyb200_split *__restrict__ psplits,
+                                    const int *__restrict__ pns, const int *__restrict__ pos, const int *__restrict__ relu,
+                                    const int *__restrict__ neuron, nyb200_split *__restrict__ buf, int *__restrict__ ns) {
+    const int d = blockIdx.x;
+    if (d >= D || pos[d] < 0) return;
+    const int n = pns[d];
+    const long s0 = (tail + 2L * pos[d]) % cap, s1 = (tail + 2L * pos[d] + 1) % cap;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        nyb200_split r = psplits[(long)d * maxd + i];
+        r.beta = 0.f;
+        buf[s0 * maxd + i] = r;
+        buf[s1 * maxd + i] = r;
+    }
+    if (threadIdx.x == 0) {
+        nyb200_split r;
+        r.relu = relu[d]; r.neuron = neuron[d]; r.sign = 1; r.beta = 0.f;
+        buf[s0 * maxd + n] = r;
+        r.sign = -1;
+        buf[s1 * maxd + n] = r;
+        ns[s0] = n + 1; ns[s1] = n + 1;
+    }
+}
+
+}  // namespace
+
+}  // namespace nyb
+
+using namespace nyb;
+
+extern "C" {
+
+int32_t nyb200_frontier_create(nyb200_engine *e, int32_t net_id, const float *spec, const float *thresholds, const int32_t *owner,
+                               int32_t S, int32_t n_clauses, const float *in_lo, const float *in_hi, const float *inh_lo,
+                               const float *inh_hi, int32_t max_depth, int64_t capacity) {
+    if (!e || !spec || !thresholds || !owner || !in_lo || !in_hi || !inh_lo || !inh_hi) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    NYB_CUDA(e, cudaSetDevice(e->device));
+    Net *net;
+    NYB_TRY(find_net(e, net_id, &net));
+    const NetView &nv = net->v;
+    if (S <= 0 || S > kMaxRowsF || n_clauses <= 0 || n_clauses > 32) return set_err(e, NYB200_ERR_SHAPE, "1..64 rows in 1..32 clauses");
+    if (max_depth <= 0 || capacity < 2) return set_err(e, NYB200_ERR_SHAPE, "max_depth and capacity must be positive");
+    for (int s = 0; s < S; ++s)
+        if (owner[s] < 0 || owner[s] >= n_clauses) return set_err(e, NYB200_ERR_INVALID, "row owner out of range");
+    if (e->frontier) { frontier_free(e->frontier); e->frontier = nullptr; }
+    ResidentFrontier *f = new ResidentFrontier();
+    f->net_id = net_id; f->S = S; f->maxd = max_depth; f->n_clauses = n_clauses; f->cap = capacity;
+    if (cudaMalloc(&f->buf, (size_t)capacity * max_depth * sizeof(nyb200_split)) != cudaSuccess ||
+        cudaMalloc(&f->ns, (size_t)capacity * 4) != cudaSuccess || cudaMalloc(&f->stats, 64) != cudaSuccess ||
+        cudaMalloc(&f->thr, (size_t)S * 4) != cudaSuccess || cudaMalloc(&f->owner, (size_t)S * 4) != cudaSuccess) {
+        frontier_free(f);
+        return set_err(e, NYB200_ERR_OOM, "device allocation failed for the frontier");
+    }
+    NYB_CUDA(e, cudaMemcpy(f->thr, thresholds, (size_t)S * 4, cudaMemcpyHostToDevice));
+    NYB_CUDA(e, cudaMemcpy(f->owner, owner, (size_t)S * 4, cudaMemcpyHostToDevice));
+    f->spec.assign(spec, spec + (size_t)S * nv.dims[nv.L]);
+    f->in_lo.assign(in_lo, in_lo + nv.dims[0]); f->in_hi.assign(in_hi, in_hi + nv.dims[0]);
+    f->inh_lo.assign(inh_lo, inh_lo + nv.n_pre); f->inh_hi.assign(inh_hi, inh_hi + nv.n_pre);
+    // the root: one domain without splits
+    NYB_CUDA(e, cudaMemset(f->ns, 0, 4));
+    f->head = 0; f->count = 1;
+    e->frontier = f;
+    return NYB200_OK;
+}
+
+void nyb200_frontier_destroy(nyb200_engine *e) {
+    if (!e) return;
+    std::lock_guard<std::mutex> g(e->mu);
+    if (e->frontier) { cudaSetDevice(e->device); cudaStreamSynchronize(e->stream); frontier_free(e->frontier); e->frontier = nullptr; }
+}
+
+// stats out: [0] domains bounded this round, [1] verified, [2] infeasible, [3] stuck (undecided, nothing left to
+// split: they stay at the front of the frontier), [4] open domains in the frontier after the round, [5] deepest history
+// bounded; min_lower: smallest lower bound of the round's feasible domains.
+int32_t nyb200_frontier_round(nyb200_engine *e, int32_t batch, int32_t branching, int64_t *stats_out, float *min_lower) {
+    if (!e || !stats_out || !min_lower || batch <= 0) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    NYB_CUDA(e, cudaSetDevice(e->device));
+    ResidentFrontier *f = e->frontier;
+    if (!f) return set_err(e, NYB200_ERR_INVALID, "no frontier");
+    if (branching != NYB200_BRANCH_WIDTH && branching != NYB200_BRANCH_INTERCEPT && branching != NYB200_BRANCH_BABSR)
+        return set_err(e, NYB200_ERR_INVALID, "unknown branching score");
+    if (batch > (1 << 16)) return set_err(e, NYB200_ERR_UNSUPPORTED, "at most 65536 domains per round");
+    for (int i = 0; i < 6; ++i) stats_out[i] = 0;
+    *min_lower = INFINITY;
+    if (f->count == 0) return NYB200_OK;
+    Net *net;
+    NYB_TRY(find_net(e, f->net_id, &net));
+    const NetView &nv = net->v;
+    const int D = (int)(f->count < batch ? f->count : batch);
+    cudaStream_t st = e->stream;
+    Batch b;
+    b.net_id = f->net_id; b.S = f->S; b.R = 2 * f->S; b.D = D; b.mode = 1; b.box_stride = 0; b.max_splits = f->maxd;
+    BatchPtrs p;
+    NYB_TRY(batch_ptrs(e, *net, b, p));
+    NYB_CUDA(e, cudaMemcpyAsync(p.spec, f->spec.data(), f->spec.size() * 4, cudaMemcpyHostToDevice, st));
+    NYB_CUDA(e, cudaMemcpyAsync(p.in_lo, f->in_lo.data(), f->in_lo.size() * 4, cudaMemcpyHostToDevice, st));
+    NYB_CUDA(e, cudaMemcpyAsync(p.in_hi, f->in_hi.data(), f->in_hi.size() * 4, cudaMemcpyHostToDevice, st));
+    NYB_CUDA(e, cudaMemcpyAsync(p.inh_lo, f->inh_lo.data(), f->inh_lo.size() * 4, cudaMemcpyHostToDevice, st));
+    NYB_CUDA(e, cudaMemcpyAsync(p.inh_hi, f->inh_hi.data(), f->inh_hi.size() * 4, cudaMemcpyHostToDevice, st));
+    // the batch: the first D ring slots (two pieces when the ring wraps)
+    const long first = (f->cap - f->head) < D ? (f->cap - f->head) : D;
+    const size_t row = (size_t)f->maxd * sizeof(nyb200_split);
+    NYB_CUDA(e, cudaMemcpyAsync(p.splits, f->buf + f->head * f->maxd, (size_t)first * row, cudaMemcpyDeviceToDevice, st));
+    NYB_CUDA(e, cudaMemcpyAsync(p.nsplits, f->ns + f->head, (size_t)first * 4, cudaMemcpyDeviceToDevice, st));
+    if (first < D) {
+        NYB_CUDA(e, cudaMemcpyAsync(p.splits + first * f->maxd, f->buf, (size_t)(D - first) * row, cudaMemcpyDeviceToDevice, st));
+        NYB_CUDA(e, cudaMemcpyAsync(p.nsplits + first, f->ns, (size_t)(D - first) * 4, cudaMemcpyDeviceToDevice, st));
+    }
+    b.valid = true;
+    e->batch = b;
+    NYB_TRY(run_batch_public(e));
+    NYB_TRY(finish_batch_public(e));   // synchronises; re-evaluates flagged domains in binary64
+    NYB_WS(done, int *, e, "fr_done", (size_t)D * 4);
+    NYB_WS(pos, int *, e, "fr_pos", (size_t)D * 4);
+    NYB_WS(dr, int *, e, "br_relu", (size_t)D * 4);
+    NYB_WS(dn, int *, e, "br_neuron", (size_t)D * 4);
+    NYB_WS(dw, float *, e, "br_width", (size_t)D * 4);
+    static const int init_stats[5] = {0, 0, 0, 0, 0x7f800000};   // +inf as float bits
+    NYB_CUDA(e, cudaMemcpyAsync(f->stats, init_stats, sizeof(init_stats), cudaMemcpyHostToDevice, st));
+    k_frontier_decide<<<(D + 255) / 256, 256, 0, st>>>(D, f->S, f->n_clauses, p.out_lo, p.flags, f->thr, f->owner, done, f->stats);
+    e->launches++;
+    if (branching == NYB200_BRANCH_BABSR) NYB_TRY(babsr_select(e, *net, e->batch, p, dr, dn, dw, nullptr));
+    else launch_select_branch(e, nv, D, p.pre_lo, p.pre_hi, p.code, dr, dn, dw, branching);
+    k_frontier_scan<<<1, 1024, 0, st>>>(D, done, dr, pos, f->stats);
+    e->launches++;
+    int hs[5];
+    NYB_CUDA(e, cudaMemcpyAsync(hs, f->stats, sizeof(hs), cudaMemcpyDeviceToHost, st));
+    std::vector<int> hns((size_t)D);
+    NYB_CUDA(e, cudaMemcpyAsync(hns.data(), p.nsplits, (size_t)D * 4, cudaMemcpyDeviceToHost, st));
+    NYB_CUDA(e, cudaStreamSynchronize(st));
+    const int n_open = hs[0], n_stuck = hs[3];
+    int deepest = 0;
+    for (int d = 0; d < D; ++d) deepest = hns[d] > deepest ? hns[d] : deepest;
+    stats_out[1] = hs[1]; stats_out[2] = hs[2]; stats_out[3] = n_stuck; stats_out[5] = deepest;
+    memcpy(min_lower, &hs[4], 4);
+    if (n_stuck > 0) {
+        // a domain that can be neither decided nor split: the batch goes back untouched and the search ends "unknown"
+        stats_out[0] = 0; stats_out[4] = f->count;
+        return NYB200_OK;
+    }
+    if (n_open > 0 && deepest + 1 > f->maxd) return set_err(e, NYB200_ERR_UNSUPPORTED, "split history deeper than the frontier's max_depth");
+    if (f->count - D + 2L * n_open > f->cap) return set_err(e, NYB200_ERR_OOM, "frontier capacity exceeded");
+    const long tail = (f->head + f->count) % f->cap;
+    if (n_open > 0) {
+        k_frontier_children<<<D, 64, 0, st>>>(D, f->maxd, f->cap, tail, p.splits, p.nsplits, pos, dr, dn, f->buf, f->ns);
+        e->launches++;
+    }
+    NYB_CUDA(e, cudaGetLastError());
+    f->head = (f->head + D) % f->cap;
+    f->count += 2L * n_open - D;
+    f->bounded += D;
+    stats_out[0] = D; stats_out[4] = f->count;
+    return NYB200_OK;
+}
+
+}  // extern "C"

@@ -116,6 +116,9 @@ struct Timing {
 
 }  // namespace nyb
 
+namespace nyb { struct ResidentFrontier; void frontier_free(ResidentFrontier *f); }
+using nyb::ResidentFrontier;
+
 struct nyb200_engine {
     int device = 0;
     cudaStream_t stream = nullptr;
@@ -136,6 +139,7 @@ struct nyb200_engine {
     // Status words of the batch runs in mapped pinned host memory, written by the last kernel of every run:
     // [0] sequence number of the newest completed run, [1] pipeline error word seen by any run since the last finish,
     // [2] domains flagged for the binary64 re-evaluation by any run since the last finish.  See nyb200_batch_poll.
+    struct ResidentFrontier *frontier = nullptr;   // nyb200_frontier_* (nyb200_frontier.cu)
     int *status_host = nullptr;
     int *status_dev = nullptr;
     int run_seq = 0;
@@ -257,6 +261,7 @@ struct RefSeed { const float *lower_a = nullptr, *upper_a = nullptr, *bias = nul
 int run_backward_ref(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int top, const RefSeed *seed = nullptr);
 int create_net(nyb200_engine *e, int32_t n_layers, const nyb200_layer_desc *ld, const float *wflat, const float *bflat, int32_t *net_id);
 int finish_batch_public(nyb200_engine *e);
+int run_batch_public(nyb200_engine *e);
 void launch_dgemm(nyb200_engine *e, int m, int n, int k, const double *a, const double *b, double *c);
 int prepare_backward_operands(nyb200_engine *e, Net &net);
 // ---- fused backward chain (nyb200_chain.cu) ----

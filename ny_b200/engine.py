@@ -33,7 +33,7 @@ ERRCH_IMMEDIATE, ERRCH_REFERENCE = 0, 1
 
 EXPORTS = [
     "nyb200_create", "nyb200_destroy", "nyb200_backend_provenance", "nyb200_last_error", "nyb200_set_stream",
-    "nyb200_set_path", "nyb200_set_refine_tolerance", "nyb200_batch_refined", "nyb200_batch_poll", "nyb200_crown_bounds_split", "nyb200_batch_set_inherited", "nyb200_launch_count", "nyb200_clear_working_set", "nyb200_gemm_f32", "nyb200_net_create",
+    "nyb200_set_path", "nyb200_set_refine_tolerance", "nyb200_batch_refined", "nyb200_batch_poll", "nyb200_crown_bounds_split", "nyb200_batch_set_inherited", "nyb200_frontier_create", "nyb200_frontier_round", "nyb200_frontier_destroy", "nyb200_launch_count", "nyb200_clear_working_set", "nyb200_gemm_f32", "nyb200_net_create",
     "nyb200_net_destroy", "nyb200_ibp_forward", "nyb200_ibp_forward_noalloc", "nyb200_bab_bound_batch", "nyb200_batch_upload", "nyb200_batch_run",
     "nyb200_batch_download", "nyb200_batch_min_lower", "nyb200_batch_min_lower_device",
     "nyb200_batch_download_pre_bounds", "nyb200_batch_select_branch", "nyb200_timing_enable", "nyb200_timing_reset",
@@ -752,6 +752,31 @@ class B200Engine:
         fn = self._L.nyb200_batch_set_inherited
         fn.argtypes = [C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_float)]
         self._check(fn(self._h, _fp(lo), _fp(hi)))
+
+    def frontier_create(self, net_id, spec, thresholds, owner, n_clauses, in_lo, in_hi, inh_lo, inh_hi, max_depth, capacity):
+        """Device-resident BaB frontier holding the root domain (see nyb200_frontier_create)."""
+        spec, thr = _f32(spec), _f32(thresholds)
+        own = np.ascontiguousarray(owner, np.int32)
+        lo, hi, il, iu = _f32(in_lo), _f32(in_hi), _f32(inh_lo), _f32(inh_hi)
+        fn = self._L.nyb200_frontier_create
+        fp = C.POINTER(C.c_float)
+        fn.argtypes = [C.c_void_p, C.c_int32, fp, fp, C.POINTER(C.c_int32), C.c_int32, C.c_int32, fp, fp, fp, fp, C.c_int32, C.c_int64]
+        self._check(fn(self._h, net_id, _fp(spec), _fp(thr), own.ctypes.data_as(C.POINTER(C.c_int32)), int(spec.shape[0]),
+                       int(n_clauses), _fp(lo), _fp(hi), _fp(il), _fp(iu), int(max_depth), int(capacity)))
+
+    def frontier_round(self, batch: int, branching: int = 1):
+        """One search round on the device.  Returns (bounded, verified, infeasible, stuck, open_after, deepest, min_lower)."""
+        st = (C.c_int64 * 6)()
+        ml = C.c_float(0)
+        fn = self._L.nyb200_frontier_round
+        fn.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.POINTER(C.c_int64), C.POINTER(C.c_float)]
+        self._check(fn(self._h, int(batch), int(branching), st, C.byref(ml)))
+        return int(st[0]), int(st[1]), int(st[2]), int(st[3]), int(st[4]), int(st[5]), float(ml.value)
+
+    def frontier_destroy(self):
+        self._L.nyb200_frontier_destroy.argtypes = [C.c_void_p]
+        self._L.nyb200_frontier_destroy.restype = None
+        self._L.nyb200_frontier_destroy(self._h)
 
     def crown_input_coeffs(self, D: int, S: int, n0: int):
         """(lower_a, upper_a), each [D, S, n0]: input-level coefficients of the last crown_bounds call."""

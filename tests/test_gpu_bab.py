@@ -249,3 +249,43 @@ def test_sharded_search_over_nccl(tmp_path):
     one, many = res[0]["one"], res[0]["many"]
     assert one[0] == many[0] == "verified"
     assert many[2] == one[2] and many[1] < one[1]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("branching", [0, 1, 2])
+def test_device_resident_frontier_runs_the_host_loop_search(eng, branching):
+    """The search with the open domain set kept on the device (nyb200_frontier_*: pop, bound, prune, branch, push
+    children in one call per round) against the host loop with the same settings: the same domains in the same order,
+    so the same verdict, the same number of rounds, the same number of domains bounded and left open - on a property
+    the search closes, on one it cannot close in the given rounds, and with batches smaller than the frontier (the
+    ring wraps)."""
+    wl = W.config_mlp_bab(seed=83, hidden=16, depth=3, n_in=6, n_out=4, eps=0.25, n_fix=0)
+    net = wl.net
+    nid = eng.register_network(net)
+    root_lo, _, _, _ = eng.crown_bounds(nid, wl.spec, wl.in_lo, wl.in_hi)
+    mn = W.sample_min_margin(wl, 200000, 3)
+    s = int(np.argmax(mn - root_lo[0]))
+    row = wl.spec[s]
+
+    def prop(t):
+        return formats.Property(wl.in_lo, wl.in_hi, [[formats.Atom(-row, float(t))]])
+
+    cases = [(float(root_lo[0][s] + 0.25 * (mn[s] - root_lo[0][s])), 64, 40),     # closes
+             (float(root_lo[0][s] + 0.9 * (mn[s] - root_lo[0][s])), 48, 12)]      # runs out of rounds, ring wraps
+    for t, batch, rounds in cases:
+        a = bab.verify(eng, nid, net, prop(t), batch=batch, max_rounds=rounds, branching=branching)
+        b = bab.verify_resident(eng, nid, net, prop(t), batch=batch, max_rounds=rounds, branching=branching)
+        assert (a.status, a.rounds, a.domains_bounded, a.open_domains) == (b.status, b.rounds, b.domains_bounded, b.open_domains)
+        assert a.domains_bounded > 3
+    # a small capacity is refused cleanly, not overrun
+    from ny_b200 import EngineError
+
+    p = prop(cases[1][0])
+    spec, thr, owner = bab._rows(p)
+    _, _, il, iu = eng.crown_bounds(nid, spec, p.in_lo, p.in_hi)
+    eng.frontier_create(nid, spec, thr, owner, 1, p.in_lo, p.in_hi, il[0], iu[0], max_depth=30, capacity=8)
+    with pytest.raises(EngineError):
+        for _ in range(20):
+            eng.frontier_round(4, branching)
+    eng.frontier_destroy()
+    eng.release_network(nid)
