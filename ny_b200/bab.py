@@ -336,7 +336,9 @@ def verify(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: i
     dist: an initialised torch.distributed module, one process per GPU: every rank runs this function with the same
     arguments, rank 0 attacks and bounds the root, and from then on every rank bounds its own shard of the frontier;
     per round the ranks exchange one small all-reduce (open domains, stop flags, the global lower bound) and level
-    their shards point to point when they drift apart (ny_b200/sharding.py).  All ranks return the same status."""
+    their shards point to point when they drift apart (ny_b200/sharding.py), warm-start slopes travelling with their
+    split records.  All ranks return the same status.  No frontier dump is written in a multi-rank run (every rank
+    holds only its shard)."""
     from . import sharding
 
     t0 = time.time()
