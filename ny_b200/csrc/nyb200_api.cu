@@ -81,6 +81,8 @@ void nyb200_destroy(nyb200_engine *e) {
     for (auto &kv : e->ws) if (kv.second.p) cudaFree(kv.second.p);
     for (auto &kv : e->nets) free_net(kv.second);
     if (e->status_host) cudaFreeHost(e->status_host);
+    if (e->stage) cudaFreeHost(e->stage);
+    if (e->stage_in_done) cudaEventDestroy(e->stage_in_done);
     if (e->frontier) nyb::frontier_free(e->frontier);
     for (int i = 0; i < 3; ++i) if (e->timing.ev[i]) cudaEventDestroy(e->timing.ev[i]);
     for (cudaEvent_t ev : e->timing.kev) cudaEventDestroy(ev);
@@ -328,6 +330,20 @@ cudaEvent_t next_kev(nyb::Timing &t) {
     return t.kev[t.kev_used++];
 }
 
+
+// Pinned staging of at least kStageIn + out_bytes bytes (grow-only; growing waits for the stream).
+static int ensure_stage(nyb200_engine *e, size_t out_bytes) {
+    const size_t need = kStageIn + out_bytes;
+    if (e->stage && e->stage_bytes >= need) return NYB200_OK;
+    NYB_CUDA(e, cudaStreamSynchronize(e->stream));
+    if (e->stage) cudaFreeHost(e->stage);
+    e->stage = nullptr; e->stage_bytes = 0; e->stage_out_valid = false;
+    const size_t sz = need + need / 2;
+    if (cudaHostAlloc((void **)&e->stage, sz, cudaHostAllocDefault) != cudaSuccess) return set_err(e, NYB200_ERR_OOM, "pinned staging allocation failed");
+    e->stage_bytes = sz;
+    if (!e->stage_in_done) NYB_CUDA(e, cudaEventCreateWithFlags(&e->stage_in_done, cudaEventDisableTiming));
+    return NYB200_OK;
+}
 
 int batch_ptrs(nyb200_engine *e, const Net &net, const Batch &b, BatchPtrs &p) {
     const NetView &nv = net.v;
@@ -662,11 +678,35 @@ int upload_batch(nyb200_engine *e, int32_t net_id, const float *spec, int32_t S,
     size_t np = nv.n_pre;
     size_t box = (size_t)nv.dims[0] * (box_stride ? (size_t)D : 1);
     cudaStream_t s = e->stream;
-    NYB_CUDA(e, cudaMemcpyAsync(p.spec, spec, (size_t)S * nv.dims[nv.L] * 4, cudaMemcpyHostToDevice, s));
-    NYB_CUDA(e, cudaMemcpyAsync(p.in_lo, in_lo, box * 4, cudaMemcpyHostToDevice, s));
-    NYB_CUDA(e, cudaMemcpyAsync(p.in_hi, in_hi, box * 4, cudaMemcpyHostToDevice, s));
-    NYB_CUDA(e, cudaMemcpyAsync(p.inh_lo, inh_lo, np * 4, cudaMemcpyHostToDevice, s));
-    NYB_CUDA(e, cudaMemcpyAsync(p.inh_hi, inh_hi, np * 4, cudaMemcpyHostToDevice, s));
+    // the five small arrays go through the pinned input region when they fit (one host copy each, then asynchronous
+    // transfers); anything larger is handed to the driver as it is
+    {
+        const size_t bs = (size_t)S * nv.dims[nv.L] * 4, bb = box * 4, bi = np * 4;
+        const size_t total = ((bs + 255) & ~(size_t)255) + 2 * ((bb + 255) & ~(size_t)255) + 2 * ((bi + 255) & ~(size_t)255);
+        if (total <= kStageIn && ensure_stage(e, 0) == NYB200_OK) {
+            NYB_CUDA(e, cudaEventSynchronize(e->stage_in_done));   // the previous upload has left the region
+            unsigned char *h = e->stage;
+            auto put = [&](void *dst, const void *src, size_t bytes) -> cudaError_t {
+                memcpy(h, src, bytes);
+                cudaError_t r = cudaMemcpyAsync(dst, h, bytes, cudaMemcpyHostToDevice, s);
+                h += (bytes + 255) & ~(size_t)255;
+                return r;
+            };
+            NYB_CUDA(e, put(p.spec, spec, bs));
+            NYB_CUDA(e, put(p.in_lo, in_lo, bb));
+            NYB_CUDA(e, put(p.in_hi, in_hi, bb));
+            NYB_CUDA(e, put(p.inh_lo, inh_lo, bi));
+            NYB_CUDA(e, put(p.inh_hi, inh_hi, bi));
+            NYB_CUDA(e, cudaEventRecord(e->stage_in_done, s));
+        } else {
+            NYB_CUDA(e, cudaMemcpyAsync(p.spec, spec, bs, cudaMemcpyHostToDevice, s));
+            NYB_CUDA(e, cudaMemcpyAsync(p.in_lo, in_lo, bb, cudaMemcpyHostToDevice, s));
+            NYB_CUDA(e, cudaMemcpyAsync(p.in_hi, in_hi, bb, cudaMemcpyHostToDevice, s));
+            NYB_CUDA(e, cudaMemcpyAsync(p.inh_lo, inh_lo, bi, cudaMemcpyHostToDevice, s));
+            NYB_CUDA(e, cudaMemcpyAsync(p.inh_hi, inh_hi, bi, cudaMemcpyHostToDevice, s));
+        }
+    }
+    e->stage_out_valid = false;
     if (alpha)
         NYB_CUDA(e, cudaMemcpy2DAsync(p.alpha, (size_t)nv.nps * 4, alpha, np * 4, np * 4, (size_t)D, cudaMemcpyHostToDevice, s));
     if (max_splits > 0) {
@@ -828,7 +868,9 @@ int refine_subset(nyb200_engine *e, Net &net, BatchPtrs &p) {
 
 // Completes the last run: waits for it and, if the fast path reported domains whose rounding penalty
 // is visible at the requested tolerance, evaluates the batch again with binary64 contractions.
-int finish_batch(nyb200_engine *e) {
+// prefetch: the caller is about to read the bounds and flags; they travel to the pinned output region ahead of the
+// synchronisation (and stay valid there unless a re-evaluation replaces them).
+int finish_batch(nyb200_engine *e, bool prefetch = false) {
     if (!e->batch.valid || !e->batch.ran) return set_err(e, NYB200_ERR_INVALID, "no batch has been run");
     if (e->batch.finished) return NYB200_OK;
     Net *net;
@@ -836,12 +878,26 @@ int finish_batch(nyb200_engine *e) {
     BatchPtrs p;
     NYB_TRY(batch_ptrs(e, *net, e->batch, p));
     int herr = 0, loose = 0;
+    const size_t nres = (size_t)e->batch.D * e->batch.S * 4, nfl = (size_t)e->batch.D * 4;
+    const bool staged = ensure_stage(e, 256 + 2 * nres + nfl) == NYB200_OK;
+    int *hwords = staged ? (int *)(e->stage + kStageIn) : nullptr;   // [0] pipeline error word, [1] flagged domains
+    if (staged) { hwords[0] = 0; hwords[1] = 0; }
+    e->stage_out_valid = false;
     if (e->path == NYB200_PATH_TF32X3) {
         int *derr = (int *)ws_get(e, "umma_err", 256);
-        if (derr) NYB_CUDA(e, cudaMemcpyAsync(&herr, derr, 4, cudaMemcpyDeviceToHost, e->stream));
-        NYB_CUDA(e, cudaMemcpyAsync(&loose, (int *)p.min_lower + 4, 4, cudaMemcpyDeviceToHost, e->stream));
+        if (derr) NYB_CUDA(e, cudaMemcpyAsync(staged ? &hwords[0] : &herr, derr, 4, cudaMemcpyDeviceToHost, e->stream));
+        NYB_CUDA(e, cudaMemcpyAsync(staged ? &hwords[1] : &loose, (int *)p.min_lower + 4, 4, cudaMemcpyDeviceToHost, e->stream));
+    }
+    if (staged && prefetch) {
+        unsigned char *o = e->stage + kStageIn + 256;
+        NYB_CUDA(e, cudaMemcpyAsync(o, p.out_lo, nres, cudaMemcpyDeviceToHost, e->stream));
+        NYB_CUDA(e, cudaMemcpyAsync(o + nres, p.out_hi, nres, cudaMemcpyDeviceToHost, e->stream));
+        NYB_CUDA(e, cudaMemcpyAsync(o + 2 * nres, p.flags, nfl, cudaMemcpyDeviceToHost, e->stream));
     }
     NYB_CUDA(e, cudaStreamSynchronize(e->stream));
+    if (staged) { herr = hwords[0]; loose = hwords[1]; }
+    const bool will_refine = loose > 0 && e->path == NYB200_PATH_TF32X3 && e->refine_tol > 0.f;
+    e->stage_out_valid = staged && prefetch && !herr && !will_refine;
     if (e->status_host) {  // the stream is idle: whatever earlier runs latched is handled by this call
         int *acc = (int *)ws_get(e, "status_acc", 256);
         if (acc) NYB_CUDA(e, cudaMemsetAsync(acc, 0, 8, e->stream));
@@ -872,7 +928,21 @@ int finish_batch(nyb200_engine *e) {
 }
 
 int download_batch(nyb200_engine *e, float *out_lo, float *out_hi, int32_t *infeasible) {
-    NYB_TRY(finish_batch(e));
+    NYB_TRY(finish_batch(e, true));
+    if (e->stage_out_valid) {   // the results are already on the host
+        const size_t nres = (size_t)e->batch.D * e->batch.S * 4, nfl = (size_t)e->batch.D * 4;
+        const unsigned char *o = e->stage + kStageIn + 256;
+        if (out_lo) memcpy(out_lo, o, nres);
+        if (out_hi) memcpy(out_hi, o + nres, nres);
+        if (infeasible) {
+            memcpy(infeasible, o + 2 * nres, nfl);
+            for (int d = 0; d < e->batch.D; ++d) {
+                if (infeasible[d] & kFlagInvalid) return set_err(e, NYB200_ERR_INVALID, "split entry out of range");
+                infeasible[d] = (infeasible[d] & kFlagInfeasible) ? 1 : 0;
+            }
+        }
+        return NYB200_OK;
+    }
     Net *net;
     NYB_TRY(find_net(e, e->batch.net_id, &net));
     BatchPtrs p;

@@ -140,6 +140,13 @@ struct nyb200_engine {
     // [0] sequence number of the newest completed run, [1] pipeline error word seen by any run since the last finish,
     // [2] domains flagged for the binary64 re-evaluation by any run since the last finish.  See nyb200_batch_poll.
     struct ResidentFrontier *frontier = nullptr;   // nyb200_frontier_* (nyb200_frontier.cu)
+    // Pinned host staging: small inputs of an upload are gathered here so that their copies are truly asynchronous,
+    // and the results of a run are fetched here ahead of the one synchronisation that ends it (a copy into pageable
+    // memory is staged by the driver and blocks).  in: [0, kStageIn), out: the rest (grow-only).
+    unsigned char *stage = nullptr;
+    size_t stage_bytes = 0;
+    cudaEvent_t stage_in_done = nullptr;   // the last upload's copies out of the input region
+    bool stage_out_valid = false;          // the output region holds the resident batch's final results
     int *status_host = nullptr;
     int *status_dev = nullptr;
     int run_seq = 0;
@@ -166,6 +173,8 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 #endif
+
+namespace nyb { constexpr size_t kStageIn = 1 << 20; }
 
 #define NYB_TRY(expr)                      \
     do {                                   \
