@@ -25,13 +25,14 @@ struct ResidentFrontier {
     int *stats = nullptr;          // device: open, verified, infeasible, stuck, (float) min lower
     float *thr = nullptr;          // device [S]
     int *owner = nullptr;          // device [S]
-    std::vector<float> spec, in_lo, in_hi, inh_lo, inh_hi;
+    float *consts = nullptr;       // device copies of spec, box and inherited bounds, back to back
+    size_t n_spec = 0, n_box = 0, n_inh = 0;
     long bounded = 0;
 };
 
 void frontier_free(ResidentFrontier *f) {
     if (!f) return;
-    cudaFree(f->buf); cudaFree(f->ns); cudaFree(f->stats); cudaFree(f->thr); cudaFree(f->owner);
+    cudaFree(f->buf); cudaFree(f->ns); cudaFree(f->stats); cudaFree(f->thr); cudaFree(f->owner); cudaFree(f->consts);
     delete f;
 }
 
@@ -71,17 +72,19 @@ __global__ void k_frontier_decide(int D, int S, int n_clauses, const float *__re
 
 // Exclusive scan of the open flags (single block, D <= 1 << 16), the number of open domains and of stuck ones
 // (undecided, but no neuron left to split).
-__global__ void k_frontier_scan(int D, const int *__restrict__ done, const int *__restrict__ relu, int *__restrict__ pos,
-                                int *__restrict__ stats) {
+__global__ void k_frontier_scan(int D, const int *__restrict__ done, const int *__restrict__ relu, const int *__restrict__ pns,
+                                int *__restrict__ pos, int *__restrict__ stats) {
     __shared__ int part[1024];
     const int t = threadIdx.x, per = (D + 1023) / 1024;
     const int b0 = t * per, b1 = min(D, b0 + per);
-    int c = 0, stuck = 0;
+    int c = 0, stuck = 0, deep = 0;
     for (int d = b0; d < b1; ++d) {
         const bool open = !done[d];
         if (open && relu[d] >= 0) ++c;
         if (open && relu[d] < 0) ++stuck;
+        deep = max(deep, pns[d]);
     }
+    if (deep) atomicMax(&stats[5], deep);   // longest split history in the batch
     part[t] = c;
     __syncthreads();
     for (int o = 1; o < 1024; o <<= 1) {   // Hillis-Steele inclusive scan
@@ -157,9 +160,19 @@ int32_t nyb200_frontier_create(nyb200_engine *e, int32_t net_id, const float *sp
     }
     NYB_CUDA(e, cudaMemcpy(f->thr, thresholds, (size_t)S * 4, cudaMemcpyHostToDevice));
     NYB_CUDA(e, cudaMemcpy(f->owner, owner, (size_t)S * 4, cudaMemcpyHostToDevice));
-    f->spec.assign(spec, spec + (size_t)S * nv.dims[nv.L]);
-    f->in_lo.assign(in_lo, in_lo + nv.dims[0]); f->in_hi.assign(in_hi, in_hi + nv.dims[0]);
-    f->inh_lo.assign(inh_lo, inh_lo + nv.n_pre); f->inh_hi.assign(inh_hi, inh_hi + nv.n_pre);
+    f->n_spec = (size_t)S * nv.dims[nv.L]; f->n_box = (size_t)nv.dims[0]; f->n_inh = (size_t)nv.n_pre;
+    if (cudaMalloc(&f->consts, (f->n_spec + 2 * f->n_box + 2 * f->n_inh) * 4) != cudaSuccess) {
+        frontier_free(f);
+        return set_err(e, NYB200_ERR_OOM, "device allocation failed for the frontier");
+    }
+    {
+        float *c = f->consts;
+        NYB_CUDA(e, cudaMemcpy(c, spec, f->n_spec * 4, cudaMemcpyHostToDevice)); c += f->n_spec;
+        NYB_CUDA(e, cudaMemcpy(c, in_lo, f->n_box * 4, cudaMemcpyHostToDevice)); c += f->n_box;
+        NYB_CUDA(e, cudaMemcpy(c, in_hi, f->n_box * 4, cudaMemcpyHostToDevice)); c += f->n_box;
+        NYB_CUDA(e, cudaMemcpy(c, inh_lo, f->n_inh * 4, cudaMemcpyHostToDevice)); c += f->n_inh;
+        NYB_CUDA(e, cudaMemcpy(c, inh_hi, f->n_inh * 4, cudaMemcpyHostToDevice));
+    }
     // the root: one domain without splits
     NYB_CUDA(e, cudaMemset(f->ns, 0, 4));
     f->head = 0; f->count = 1;
@@ -197,11 +210,14 @@ int32_t nyb200_frontier_round(nyb200_engine *e, int32_t batch, int32_t branching
     b.net_id = f->net_id; b.S = f->S; b.R = 2 * f->S; b.D = D; b.mode = 1; b.box_stride = 0; b.max_splits = f->maxd;
     BatchPtrs p;
     NYB_TRY(batch_ptrs(e, *net, b, p));
-    NYB_CUDA(e, cudaMemcpyAsync(p.spec, f->spec.data(), f->spec.size() * 4, cudaMemcpyHostToDevice, st));
-    NYB_CUDA(e, cudaMemcpyAsync(p.in_lo, f->in_lo.data(), f->in_lo.size() * 4, cudaMemcpyHostToDevice, st));
-    NYB_CUDA(e, cudaMemcpyAsync(p.in_hi, f->in_hi.data(), f->in_hi.size() * 4, cudaMemcpyHostToDevice, st));
-    NYB_CUDA(e, cudaMemcpyAsync(p.inh_lo, f->inh_lo.data(), f->inh_lo.size() * 4, cudaMemcpyHostToDevice, st));
-    NYB_CUDA(e, cudaMemcpyAsync(p.inh_hi, f->inh_hi.data(), f->inh_hi.size() * 4, cudaMemcpyHostToDevice, st));
+    {   // the search's constants, device to device (the workspace arrays may have served another call in between)
+        const float *c = f->consts;
+        NYB_CUDA(e, cudaMemcpyAsync(p.spec, c, f->n_spec * 4, cudaMemcpyDeviceToDevice, st)); c += f->n_spec;
+        NYB_CUDA(e, cudaMemcpyAsync(p.in_lo, c, f->n_box * 4, cudaMemcpyDeviceToDevice, st)); c += f->n_box;
+        NYB_CUDA(e, cudaMemcpyAsync(p.in_hi, c, f->n_box * 4, cudaMemcpyDeviceToDevice, st)); c += f->n_box;
+        NYB_CUDA(e, cudaMemcpyAsync(p.inh_lo, c, f->n_inh * 4, cudaMemcpyDeviceToDevice, st)); c += f->n_inh;
+        NYB_CUDA(e, cudaMemcpyAsync(p.inh_hi, c, f->n_inh * 4, cudaMemcpyDeviceToDevice, st));
+    }
     // the batch: the first D ring slots (two pieces when the ring wraps)
     const long first = (f->cap - f->head) < D ? (f->cap - f->head) : D;
     const size_t row = (size_t)f->maxd * sizeof(nyb200_split);
@@ -220,22 +236,18 @@ int32_t nyb200_frontier_round(nyb200_engine *e, int32_t batch, int32_t branching
     NYB_WS(dr, int *, e, "br_relu", (size_t)D * 4);
     NYB_WS(dn, int *, e, "br_neuron", (size_t)D * 4);
     NYB_WS(dw, float *, e, "br_width", (size_t)D * 4);
-    static const int init_stats[5] = {0, 0, 0, 0, 0x7f800000};   // +inf as float bits
+    static const int init_stats[6] = {0, 0, 0, 0, 0x7f800000, 0};   // +inf as float bits
     NYB_CUDA(e, cudaMemcpyAsync(f->stats, init_stats, sizeof(init_stats), cudaMemcpyHostToDevice, st));
     k_frontier_decide<<<(D + 255) / 256, 256, 0, st>>>(D, f->S, f->n_clauses, p.out_lo, p.flags, f->thr, f->owner, done, f->stats);
     e->launches++;
     if (branching == NYB200_BRANCH_BABSR) NYB_TRY(babsr_select(e, *net, e->batch, p, dr, dn, dw, nullptr));
     else launch_select_branch(e, nv, D, p.pre_lo, p.pre_hi, p.code, dr, dn, dw, branching);
-    k_frontier_scan<<<1, 1024, 0, st>>>(D, done, dr, pos, f->stats);
+    k_frontier_scan<<<1, 1024, 0, st>>>(D, done, dr, p.nsplits, pos, f->stats);
     e->launches++;
-    int hs[5];
+    int hs[6];
     NYB_CUDA(e, cudaMemcpyAsync(hs, f->stats, sizeof(hs), cudaMemcpyDeviceToHost, st));
-    std::vector<int> hns((size_t)D);
-    NYB_CUDA(e, cudaMemcpyAsync(hns.data(), p.nsplits, (size_t)D * 4, cudaMemcpyDeviceToHost, st));
     NYB_CUDA(e, cudaStreamSynchronize(st));
-    const int n_open = hs[0], n_stuck = hs[3];
-    int deepest = 0;
-    for (int d = 0; d < D; ++d) deepest = hns[d] > deepest ? hns[d] : deepest;
+    const int n_open = hs[0], n_stuck = hs[3], deepest = hs[5];
     stats_out[1] = hs[1]; stats_out[2] = hs[2]; stats_out[3] = n_stuck; stats_out[5] = deepest;
     memcpy(min_lower, &hs[4], 4);
     if (n_stuck > 0) {
