@@ -690,6 +690,8 @@ class B200Engine:
         ol, ou = np.empty((D, S), np.float32), np.empty((D, S), np.float32)
         inf = np.zeros(D, np.int32)
         self._check(self._L.nyb200_bab_bound_batch(*args, _fp(ol), _fp(ou), _ip(inf)))
+        self._batch_shape = (D, S, self._nets[net_id].n_pre)
+        self._batch_max_splits = int(np.asarray(splits).shape[1])
         return ol, ou, inf
 
     def batch_upload(self, net_id, spec, in_lo, in_hi, inh_lo, inh_hi, splits, n_splits, mode=1, alpha=None):
