@@ -97,6 +97,15 @@ int32_t nyb200_frontier_create(nyb200_engine *e, int32_t net_id, const float *sp
                                const float *inh_lo, const float *inh_hi, int32_t max_depth, int64_t capacity);
 int32_t nyb200_frontier_round(nyb200_engine *e, int32_t batch, int32_t branching, int64_t *stats_out, float *min_lower);
 void nyb200_frontier_destroy(nyb200_engine *e);
+/* Sharded search (one process per GPU, each with its own frontier): the shards are levelled by moving records between
+ * them, device array to device array (the caller carries them with a point-to-point collective; the reference's
+ * domain distribution is host-side, beta_crown/engine/core.rs:560-640).  nyb200_frontier_take removes up to n records
+ * from the back of the ring into dev_splits [n x max_depth] (nyb200_split) and dev_nsplits [n], both device memory of
+ * this engine's GPU, complete on return; nyb200_frontier_give appends n such records (their contents must be complete:
+ * synchronise the stream or collective that wrote them first).  nyb200_frontier_count: open domains held. */
+int32_t nyb200_frontier_count(nyb200_engine *e, int64_t *open);
+int32_t nyb200_frontier_take(nyb200_engine *e, int64_t n, void *dev_splits, int32_t *dev_nsplits, int64_t *taken);
+int32_t nyb200_frontier_give(nyb200_engine *e, int64_t n, const void *dev_splits, const int32_t *dev_nsplits);
 /* Non-blocking look at the runs launched so far (no counterpart in the reference, whose calls return finished
  * results): every nyb200_batch_run ends with a one-thread kernel that publishes, to mapped host memory, the run's
  * sequence number, the tensor pipeline's error word and the number of domains flagged for the binary64 re-run.

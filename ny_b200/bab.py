@@ -471,17 +471,27 @@ def verify(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: i
 
 def verify_resident(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: int = 64,
                     max_domains: int = 1 << 20, pgd_restarts: int = 256, pgd_steps: int = 50, branching: int = 1,
-                    timeout_s: float | None = None) -> VerifyResult:
+                    timeout_s: float | None = None, dist=None, dist_device=None) -> VerifyResult:
     """The search of verify() with the open domain set kept on the device (nyb200_frontier_*): attack and root bound
     as there, then one device call per round that pops a batch, bounds it (one bound per domain, multipliers at
     zero), prunes verified and infeasible domains, picks every open domain's split neuron (0 width, 1 intercept,
     2 BaBSR) and appends both children.  Same order of domains as the host loop, hence the same counts and verdicts;
-    what it leaves out is the optimising search with warm starts, the metrics file and the frontier dump."""
+    what it leaves out is the optimising search with warm starts, the metrics file and the frontier dump.
+    dist: an initialised torch.distributed module, one process per GPU, every rank calling with the same arguments:
+    each rank keeps its own device frontier (the root starts on rank 0), bounds up to `batch` of its domains per round,
+    and the ranks agree per round on the open total and the stop flags with one small all-gather, whose counts also
+    drive the levelling of the shards: split records move from one GPU's frontier to another's, device to device
+    (sharding.exchange_resident).  All ranks return the same status and the same totals."""
+    from . import sharding
+
     t0 = time.time()
     if not prop.violation:
         return VerifyResult("verified")
     spec, thr, owner = _rows(prop)
     n_clauses = len(prop.violation)
+    world = dist.get_world_size() if dist is not None else 1
+    rank = dist.get_rank() if dist is not None else 0
+    # the root phase is deterministic: every rank runs it and reaches the same verdict and inherited bounds
     ce = attack(eng, net_id, net, prop, pgd_restarts, pgd_steps)
     if ce is not None:
         return VerifyResult("violated", ce[0], ce[1])
@@ -490,23 +500,45 @@ def verify_resident(eng, net_id, net, prop: Property, *, batch: int = 1024, max_
     if _verified_mask(rlo, thr, owner, n_clauses)[0]:
         res.status = "verified"
         return res
+    max_depth = max_rounds + 2
     eng.frontier_create(net_id, spec, thr, owner, n_clauses, prop.in_lo, prop.in_hi, inter_lo[0], inter_hi[0],
-                        max_depth=max_rounds + 2, capacity=min(2 * max_domains + 2 * batch, 1 << 22))
+                        max_depth=max_depth, capacity=min(2 * max_domains + 2 * batch, 1 << 22))
+    exchange = {"exchanges": 0, "records_moved": 0, "bytes_moved": 0} if world > 1 else None
     try:
-        open_now = 1
-        while open_now > 0 and res.rounds < max_rounds:
-            if timeout_s is not None and time.time() - t0 > timeout_s:
-                res.status = "timeout"
-                break
-            bounded, _, _, stuck, open_now, _, _ = eng.frontier_round(batch, branching)
+        if world > 1:
+            import torch
+
+            if rank != 0:   # the root belongs to rank 0's shard
+                scratch = torch.empty((4 * max_depth + 1,), dtype=torch.int32, device=dist_device)
+                eng.frontier_take(1, scratch.data_ptr(), scratch[4 * max_depth:].data_ptr())
+        open_local, total_open = (1 if rank == 0 else 0), 1
+        while total_open > 0 and res.rounds < max_rounds:
+            timed_out = timeout_s is not None and time.time() - t0 > timeout_s
+            bounded = stuck = 0
+            if open_local > 0 and not timed_out:
+                bounded, _, _, stuck, open_local, _, _ = eng.frontier_round(batch, branching)
+            if world > 1:
+                mine = torch.tensor([open_local, bounded, stuck, 1 if timed_out else 0], dtype=torch.int64, device=dist_device)
+                every = [torch.zeros_like(mine) for _ in range(world)]
+                dist.all_gather(every, mine)
+                table = torch.stack(every).cpu().numpy()
+                counts = [int(c) for c in table[:, 0]]
+                total_open, bounded, stuck, timed_out = int(table[:, 0].sum()), int(table[:, 1].sum()), int(table[:, 2].max()), bool(table[:, 3].max())
+            else:
+                total_open = open_local
             res.rounds += 1
             res.domains_bounded += bounded
-            if stuck:
+            if timed_out:
+                res.status = "timeout"
                 break
-            if open_now > max_domains:
+            if stuck or total_open > max_domains:
                 break
-        res.open_domains = open_now
-        if open_now == 0:
+            if world > 1 and total_open > 0:
+                sharding.exchange_resident(eng, max_depth, counts, dist, dist_device, stats=exchange)
+                open_local = eng.frontier_count()
+        res.open_domains = total_open
+        res.exchange = exchange
+        if total_open == 0 and res.status == "unknown":
             res.status = "verified"
     finally:
         eng.frontier_destroy()

@@ -270,4 +270,64 @@ int32_t nyb200_frontier_round(nyb200_engine *e, int32_t batch, int32_t branching
     return NYB200_OK;
 }
 
+int32_t nyb200_frontier_count(nyb200_engine *e, int64_t *open) {
+    if (!e || !open) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    if (!e->frontier) return set_err(e, NYB200_ERR_INVALID, "no frontier");
+    *open = e->frontier->count;
+    return NYB200_OK;
+}
+
+// Up to n records leave from the back of the ring (the domains that would be bounded last) into the caller's device
+// arrays: dev_splits [n x max_depth] records, dev_nsplits [n].  The copies are complete when the call returns, so
+// the caller may hand the arrays to any stream or to a collective.
+int32_t nyb200_frontier_take(nyb200_engine *e, int64_t n, void *dev_splits, int32_t *dev_nsplits, int64_t *taken) {
+    if (!e || !taken || n < 0 || (n > 0 && (!dev_splits || !dev_nsplits))) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    NYB_CUDA(e, cudaSetDevice(e->device));
+    ResidentFrontier *f = e->frontier;
+    if (!f) return set_err(e, NYB200_ERR_INVALID, "no frontier");
+    const long m = n < f->count ? (long)n : f->count;
+    *taken = m;
+    if (m == 0) return NYB200_OK;
+    cudaStream_t st = e->stream;
+    const size_t row = (size_t)f->maxd * sizeof(nyb200_split);
+    const long start = (f->head + f->count - m) % f->cap;           // first of the m last slots
+    const long first = (f->cap - start) < m ? (f->cap - start) : m;  // slots before the ring wraps
+    NYB_CUDA(e, cudaMemcpyAsync(dev_splits, f->buf + start * f->maxd, (size_t)first * row, cudaMemcpyDeviceToDevice, st));
+    NYB_CUDA(e, cudaMemcpyAsync(dev_nsplits, f->ns + start, (size_t)first * 4, cudaMemcpyDeviceToDevice, st));
+    if (first < m) {
+        NYB_CUDA(e, cudaMemcpyAsync((char *)dev_splits + (size_t)first * row, f->buf, (size_t)(m - first) * row, cudaMemcpyDeviceToDevice, st));
+        NYB_CUDA(e, cudaMemcpyAsync(dev_nsplits + first, f->ns, (size_t)(m - first) * 4, cudaMemcpyDeviceToDevice, st));
+    }
+    NYB_CUDA(e, cudaStreamSynchronize(st));
+    f->count -= m;
+    return NYB200_OK;
+}
+
+// n records (same layout, device arrays whose contents are complete: the caller has synchronised the stream or the
+// collective that filled them) are appended at the back of the ring.
+int32_t nyb200_frontier_give(nyb200_engine *e, int64_t n, const void *dev_splits, const int32_t *dev_nsplits) {
+    if (!e || n < 0 || (n > 0 && (!dev_splits || !dev_nsplits))) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    NYB_CUDA(e, cudaSetDevice(e->device));
+    ResidentFrontier *f = e->frontier;
+    if (!f) return set_err(e, NYB200_ERR_INVALID, "no frontier");
+    if (n == 0) return NYB200_OK;
+    if (f->count + n > f->cap) return set_err(e, NYB200_ERR_OOM, "frontier capacity exceeded");
+    cudaStream_t st = e->stream;
+    const size_t row = (size_t)f->maxd * sizeof(nyb200_split);
+    const long tail = (f->head + f->count) % f->cap;
+    const long first = (f->cap - tail) < n ? (f->cap - tail) : (long)n;
+    NYB_CUDA(e, cudaMemcpyAsync(f->buf + tail * f->maxd, dev_splits, (size_t)first * row, cudaMemcpyDeviceToDevice, st));
+    NYB_CUDA(e, cudaMemcpyAsync(f->ns + tail, dev_nsplits, (size_t)first * 4, cudaMemcpyDeviceToDevice, st));
+    if (first < n) {
+        NYB_CUDA(e, cudaMemcpyAsync(f->buf, (const char *)dev_splits + (size_t)first * row, (size_t)(n - first) * row, cudaMemcpyDeviceToDevice, st));
+        NYB_CUDA(e, cudaMemcpyAsync(f->ns, dev_nsplits + first, (size_t)(n - first) * 4, cudaMemcpyDeviceToDevice, st));
+    }
+    NYB_CUDA(e, cudaStreamSynchronize(st));   // the caller may reuse its arrays
+    f->count += n;
+    return NYB200_OK;
+}
+
 }  // extern "C"

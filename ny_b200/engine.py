@@ -33,7 +33,7 @@ ERRCH_IMMEDIATE, ERRCH_REFERENCE = 0, 1
 
 EXPORTS = [
     "nyb200_create", "nyb200_destroy", "nyb200_backend_provenance", "nyb200_last_error", "nyb200_set_stream",
-    "nyb200_set_path", "nyb200_set_refine_tolerance", "nyb200_batch_refined", "nyb200_batch_poll", "nyb200_crown_bounds_split", "nyb200_batch_set_inherited", "nyb200_frontier_create", "nyb200_frontier_round", "nyb200_frontier_destroy", "nyb200_launch_count", "nyb200_clear_working_set", "nyb200_gemm_f32", "nyb200_net_create",
+    "nyb200_set_path", "nyb200_set_refine_tolerance", "nyb200_batch_refined", "nyb200_batch_poll", "nyb200_crown_bounds_split", "nyb200_batch_set_inherited", "nyb200_frontier_create", "nyb200_frontier_round", "nyb200_frontier_destroy", "nyb200_frontier_count", "nyb200_frontier_take", "nyb200_frontier_give", "nyb200_launch_count", "nyb200_clear_working_set", "nyb200_gemm_f32", "nyb200_net_create",
     "nyb200_net_destroy", "nyb200_ibp_forward", "nyb200_ibp_forward_noalloc", "nyb200_bab_bound_batch", "nyb200_batch_upload", "nyb200_batch_run",
     "nyb200_batch_download", "nyb200_batch_min_lower", "nyb200_batch_min_lower_device",
     "nyb200_batch_download_pre_bounds", "nyb200_batch_select_branch", "nyb200_timing_enable", "nyb200_timing_reset",
@@ -774,6 +774,28 @@ class B200Engine:
         fn.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.POINTER(C.c_int64), C.POINTER(C.c_float)]
         self._check(fn(self._h, int(batch), int(branching), st, C.byref(ml)))
         return int(st[0]), int(st[1]), int(st[2]), int(st[3]), int(st[4]), int(st[5]), float(ml.value)
+
+    def frontier_count(self) -> int:
+        n = C.c_int64(0)
+        fn = self._L.nyb200_frontier_count
+        fn.argtypes = [C.c_void_p, C.POINTER(C.c_int64)]
+        self._check(fn(self._h, C.byref(n)))
+        return int(n.value)
+
+    def frontier_take(self, n: int, dev_splits: int, dev_nsplits: int) -> int:
+        """Moves up to n records from the back of the device frontier into device arrays given by address
+        ([n, max_depth] split records of 16 bytes, [n] int32); returns how many left."""
+        got = C.c_int64(0)
+        fn = self._L.nyb200_frontier_take
+        fn.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.POINTER(C.c_int64)]
+        self._check(fn(self._h, int(n), C.c_void_p(dev_splits), C.c_void_p(dev_nsplits), C.byref(got)))
+        return int(got.value)
+
+    def frontier_give(self, n: int, dev_splits: int, dev_nsplits: int):
+        """Appends n records (device arrays by address, contents complete) at the back of the device frontier."""
+        fn = self._L.nyb200_frontier_give
+        fn.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]
+        self._check(fn(self._h, int(n), C.c_void_p(dev_splits), C.c_void_p(dev_nsplits)))
 
     def frontier_destroy(self):
         self._L.nyb200_frontier_destroy.argtypes = [C.c_void_p]

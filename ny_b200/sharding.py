@@ -108,3 +108,37 @@ def exchange_domains(splits: np.ndarray, n_splits: np.ndarray, dist, device="cpu
     if alpha is not None:
         return splits, n_splits, alpha
     return splits, n_splits
+
+
+def exchange_resident(frontier, max_depth: int, counts, dist, device, trigger: float = 1.25, stats: dict | None = None):
+    """Levels device-resident frontiers (one per rank) after `counts` (every rank's open domains, already gathered).
+    `frontier` offers frontier_take(n, splits_address, counts_address) -> taken and frontier_give(n, splits_address,
+    counts_address) over arrays on `device` (ny_b200.engine.B200Engine does, over the GPU's memory).  A move is one
+    point-to-point message of int32 words, [n, 4 * max_depth + 1] (the split records, then the history length), device
+    tensor to device tensor: nothing is staged through the host.  Returns the plan that ran."""
+    import torch
+
+    rank = dist.get_rank()
+    plan = plan_rebalance(counts, trigger)
+    words = 4 * max_depth
+    for src, dst, n in plan:
+        if rank == src:
+            sp = torch.empty((n, words), dtype=torch.int32, device=device)
+            ns = torch.empty((n,), dtype=torch.int32, device=device)
+            taken = frontier.frontier_take(n, sp.data_ptr(), ns.data_ptr())
+            if taken != n:
+                raise RuntimeError(f"rank {rank} holds {taken} of the {n} domains the plan moves")
+            dist.send(torch.cat([sp, ns[:, None]], dim=1).contiguous(), dst)
+        elif rank == dst:
+            msg = torch.empty((n, words + 1), dtype=torch.int32, device=device)
+            dist.recv(msg, src)
+            sp, ns = msg[:, :words].contiguous(), msg[:, words].contiguous()
+            if msg.is_cuda:
+                torch.cuda.current_stream(msg.device).synchronize()   # the arrays are complete before the engine reads them
+            frontier.frontier_give(n, sp.data_ptr(), ns.data_ptr())
+        if stats is not None and rank in (src, dst):
+            stats["records_moved"] = stats.get("records_moved", 0) + n
+            stats["bytes_moved"] = stats.get("bytes_moved", 0) + n * (words + 1) * 4
+    if stats is not None and plan:
+        stats["exchanges"] = stats.get("exchanges", 0) + 1
+    return plan

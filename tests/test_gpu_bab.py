@@ -289,3 +289,122 @@ def test_device_resident_frontier_runs_the_host_loop_search(eng, branching):
             eng.frontier_round(4, branching)
     eng.frontier_destroy()
     eng.release_network(nid)
+
+
+@pytest.mark.gpu
+def test_records_taken_from_the_device_frontier_and_given_back_leave_the_search_unchanged(eng):
+    """nyb200_frontier_take / give (the levelling moves of the sharded search): records leave from the back of the
+    ring into device arrays, keep their contents, and a search that gets them back bounds the same domains."""
+    import torch
+
+    wl = W.config_mlp_bab(seed=83, hidden=16, depth=3, n_in=6, n_out=4, eps=0.25, n_fix=0)
+    nid = eng.register_network(wl.net)
+    root_lo, _, il, iu = eng.crown_bounds(nid, wl.spec, wl.in_lo, wl.in_hi)
+    mn = W.sample_min_margin(wl, 200000, 3)
+    s = int(np.argmax(mn - root_lo[0]))
+    p = formats.Property(wl.in_lo, wl.in_hi, [[formats.Atom(-wl.spec[s], float(root_lo[0][s] + 0.9 * (mn[s] - root_lo[0][s])))]])
+    spec, thr, owner = bab._rows(p)
+    depth, cap = 20, 64     # a small ring, so that the taken range wraps
+
+    def run(interrupt):
+        eng.frontier_create(nid, spec, thr, owner, 1, p.in_lo, p.in_hi, il[0], iu[0], max_depth=depth, capacity=cap)
+        log = []
+        for r in range(9):
+            log.append(eng.frontier_round(6, 1))
+            if interrupt and r in (3, 6):
+                n = eng.frontier_count()
+                k = n - 2
+                sp = torch.full((k, 4 * depth), -7, dtype=torch.int32, device="cuda:0")
+                ns = torch.full((k,), -7, dtype=torch.int32, device="cuda:0")
+                assert eng.frontier_take(k, sp.data_ptr(), ns.data_ptr()) == k and eng.frontier_count() == 2
+                hist = ns.cpu().numpy()
+                assert hist.min() >= 1 and hist.max() <= r + 1
+                rec = sp.cpu().numpy().reshape(k, depth, 4)
+                for i in range(k):   # (relu, neuron, sign, beta) of every used slot
+                    assert np.all(np.abs(rec[i, : hist[i], 2]) == 1) and np.all(rec[i, : hist[i], 0] >= 0)
+                eng.frontier_give(k, sp.data_ptr(), ns.data_ptr())
+                assert eng.frontier_count() == n
+        eng.frontier_destroy()
+        return log
+
+    plain = run(False)
+    assert run(True) == plain and plain[-1][0] > 0
+    # asking for more than the ring holds hands over what is there
+    eng.frontier_create(nid, spec, thr, owner, 1, p.in_lo, p.in_hi, il[0], iu[0], max_depth=depth, capacity=cap)
+    sp = torch.zeros((5, 4 * depth), dtype=torch.int32, device="cuda:0")
+    ns = torch.zeros((5,), dtype=torch.int32, device="cuda:0")
+    assert eng.frontier_take(5, sp.data_ptr(), ns.data_ptr()) == 1 and eng.frontier_count() == 0    # only the root is there
+    assert eng.frontier_round(6, 1)[0] == 0                                                        # nothing to bound
+    eng.frontier_give(1, sp.data_ptr(), ns.data_ptr())
+    assert eng.frontier_count() == 1
+    eng.frontier_destroy()
+
+    eng.release_network(nid)
+
+
+_SHARDED_RESIDENT = r"""
+import json, os, sys
+import numpy as np
+import torch
+import torch.distributed as dist
+from ny_b200 import B200Engine, bab, formats
+from ny_b200 import workloads as W
+
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+lr = int(os.environ["LOCAL_RANK"])
+torch.cuda.set_device(lr)
+dist.init_process_group("nccl")
+eng = B200Engine(lr)
+wl = W.config_mlp_bab(seed=83, hidden=24, depth=3, n_in=4, n_out=3, eps=0.2, n_fix=0)
+nid = eng.register_network(wl.net)
+mn = W.sample_min_margin(wl, 200000, 3)
+root, _, _, _ = eng.crown_bounds(nid, wl.spec, wl.in_lo, wl.in_hi)
+s = int(np.argmax(mn - root[0]))
+out = dict(rank=rank)
+for name, frac, rounds, batch in (("closes", 0.5, 200, 2), ("open", 0.97, 9, 16)):
+    t = float(root[0][s] + frac * (mn[s] - root[0][s]))
+    prop = formats.Property(wl.in_lo, wl.in_hi, [[formats.Atom(-wl.spec[s], t)]])
+    one = bab.verify_resident(eng, nid, wl.net, prop, batch=batch, max_rounds=rounds)
+    many = bab.verify_resident(eng, nid, wl.net, prop, batch=batch, max_rounds=rounds, dist=dist, dist_device=f"cuda:{lr}")
+    out[name] = dict(one=[one.status, one.rounds, one.domains_bounded, one.open_domains],
+                     many=[many.status, many.rounds, many.domains_bounded, many.open_domains], exchange=many.exchange)
+gathered = [None] * world
+dist.all_gather_object(gathered, out)
+if rank == 0:
+    print("RESULT " + json.dumps(gathered))
+dist.destroy_process_group()
+"""
+
+
+def test_sharded_search_on_device_resident_frontiers_over_nccl(tmp_path):
+    """Every rank keeps its own device frontier; records move between the GPUs' rings over NCCL, device to device.
+    Against the single-GPU resident search: the same verdict and, when the search closes, the same domains bounded in
+    fewer rounds (two domains per rank and round); on a search that runs out of rounds, at least as many domains bounded
+    in the same rounds."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    import torch
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = tmp_path / "sharded_resident.py"
+    script.write_text(_SHARDED_RESIDENT)
+    env = dict(os.environ, PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""), NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+                        "127.0.0.1", "--master-port", "29578", str(script)], env=env, cwd=root, capture_output=True, text=True,
+                       timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    line = [ln for ln in r.stdout.splitlines() if ln.startswith("RESULT ")][-1]
+    res = json.loads(line[len("RESULT "):])
+    for name in ("closes", "open"):
+        assert all(x[name]["one"] == res[0][name]["one"] and x[name]["many"] == res[0][name]["many"] for x in res)
+    one, many = res[0]["closes"]["one"], res[0]["closes"]["many"]
+    assert one[0] == many[0] == "verified" and many[2] == one[2] and many[1] < one[1]
+    one, many = res[0]["open"]["one"], res[0]["open"]["many"]
+    assert one[0] == many[0] == "unknown" and many[1] == one[1] and many[2] >= one[2]
+    moved = sum(x["closes"]["exchange"]["records_moved"] for x in res)
+    assert moved > 0 and moved % 2 == 0   # every move is counted by its sender and by its receiver

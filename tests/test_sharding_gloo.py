@@ -236,3 +236,77 @@ def test_sharded_search_reaches_the_single_rank_verdict():
     assert r0["local"] > 0 and r1["local"] > 0                     # the frontier really was shared out
     assert r0["local"] + r1["local"] == r0["bounded"] - 1          # every domain bounded once (+ the root bound)
     assert r0["rounds"] < single["rounds"]                         # two shards per round: fewer rounds
+
+
+class _HostRing:
+    """Stand-in for the engine's device frontier with the same take / give contract over host memory: records leave
+    from the back and arrive at the back, arrays are passed by address."""
+
+    def __init__(self, records, lengths, max_depth):
+        self.max_depth = max_depth
+        self.rec = [np.array(r, np.int32).reshape(4 * max_depth) for r in records]
+        self.len = [int(n) for n in lengths]
+
+    def frontier_take(self, n, sp_addr, ns_addr):
+        import ctypes
+
+        n = min(n, len(self.rec))
+        if n:
+            sp = np.stack(self.rec[len(self.rec) - n:])
+            ns = np.array(self.len[len(self.len) - n:], np.int32)
+            ctypes.memmove(sp_addr, sp.ctypes.data, sp.nbytes)
+            ctypes.memmove(ns_addr, ns.ctypes.data, ns.nbytes)
+            del self.rec[len(self.rec) - n:], self.len[len(self.len) - n:]
+        return n
+
+    def frontier_give(self, n, sp_addr, ns_addr):
+        import ctypes
+
+        sp = np.empty((n, 4 * self.max_depth), np.int32)
+        ns = np.empty(n, np.int32)
+        ctypes.memmove(sp.ctypes.data, sp_addr, sp.nbytes)
+        ctypes.memmove(ns.ctypes.data, ns_addr, ns.nbytes)
+        self.rec += [r.copy() for r in sp]
+        self.len += [int(x) for x in ns]
+
+
+def _worker_resident(rank, world, port, ret):
+    import torch.distributed as dist
+
+    from ny_b200 import sharding
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        depth = 5
+        n_local = 11 if rank == 0 else 0      # the state after the first rounds of a search: rank 0 holds everything
+        recs = [np.full(4 * depth, 1000 * rank + i, np.int32) for i in range(n_local)]
+        ring = _HostRing(recs, [1 + i % depth for i in range(n_local)], depth)
+        stats = {}
+        counts = sharding.gather_counts(len(ring.rec), dist)
+        plan = sharding.exchange_resident(ring, depth, counts, dist, "cpu", stats=stats)
+        counts2 = sharding.gather_counts(len(ring.rec), dist)
+        plan2 = sharding.exchange_resident(ring, depth, counts2, dist, "cpu", stats=stats)   # level: nothing moves
+        ret[rank] = dict(plan=plan, plan2=plan2, n=len(ring.rec), ids=[int(r[0]) for r in ring.rec], lens=list(ring.len),
+                         whole=all(np.all(r == r[0]) for r in ring.rec), stats=stats)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_ranks_level_resident_frontiers_by_address():
+    """The levelling of device-resident frontiers (records taken from one ring and given to another, array addresses
+    in, one message per move) with a host-memory stand-in for the ring."""
+    import torch.multiprocessing as mp
+
+    world = 2
+    port = _free_port()
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_worker_resident, args=(world, port, ret), nprocs=world, join=True)
+        r0, r1 = ret[0], ret[1]
+    assert r0["plan"] == r1["plan"] == [(0, 1, 5)] and r0["plan2"] == r1["plan2"] == []
+    assert (r0["n"], r1["n"]) == (6, 5)
+    assert r0["ids"] == list(range(6)) and r1["ids"] == list(range(6, 11))   # the back of rank 0's ring moved, in order
+    assert r1["lens"] == [1 + i % 5 for i in range(6, 11)] and r0["whole"] and r1["whole"]
+    assert r0["stats"] == r1["stats"] == {"records_moved": 5, "bytes_moved": 5 * 21 * 4, "exchanges": 1}
