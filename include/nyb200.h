@@ -106,6 +106,12 @@ void nyb200_frontier_destroy(nyb200_engine *e);
 int32_t nyb200_frontier_count(nyb200_engine *e, int64_t *open);
 int32_t nyb200_frontier_take(nyb200_engine *e, int64_t n, void *dev_splits, int32_t *dev_nsplits, int64_t *taken);
 int32_t nyb200_frontier_give(nyb200_engine *e, int64_t n, const void *dev_splits, const int32_t *dev_nsplits);
+/* Dump and resume (the reference's search has no checkpoint; its benchmark sweep resumes from metadata).
+ * nyb200_frontier_download copies the open records, front first, into host arrays splits [capacity x max_depth] and
+ * nsplits [capacity] and reports their number (call with capacity 0 to learn it); the frontier keeps them.
+ * nyb200_frontier_upload replaces the frontier's contents by n host records of row length depth <= max_depth. */
+int32_t nyb200_frontier_download(nyb200_engine *e, int64_t capacity, nyb200_split *splits, int32_t *nsplits, int64_t *n_out);
+int32_t nyb200_frontier_upload(nyb200_engine *e, int64_t n, int32_t depth, const nyb200_split *splits, const int32_t *nsplits);
 /* Non-blocking look at the runs launched so far (no counterpart in the reference, whose calls return finished
  * results): every nyb200_batch_run ends with a one-thread kernel that publishes, to mapped host memory, the run's
  * sequence number, the tensor pipeline's error word and the number of domains flagged for the binary64 re-run.

@@ -471,12 +471,13 @@ def verify(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: i
 
 def verify_resident(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: int = 64,
                     max_domains: int = 1 << 20, pgd_restarts: int = 256, pgd_steps: int = 50, branching: int = 1,
-                    timeout_s: float | None = None, dist=None, dist_device=None) -> VerifyResult:
+                    timeout_s: float | None = None, checkpoint=None, resume=None, dist=None, dist_device=None) -> VerifyResult:
     """The search of verify() with the open domain set kept on the device (nyb200_frontier_*): attack and root bound
     as there, then one device call per round that pops a batch, bounds it (one bound per domain, multipliers at
     zero), prunes verified and infeasible domains, picks every open domain's split neuron (0 width, 1 intercept,
     2 BaBSR) and appends both children.  Same order of domains as the host loop, hence the same counts and verdicts;
-    what it leaves out is the optimising search with warm starts, the metrics file and the frontier dump.
+    what it leaves out is the optimising search with warm starts and the metrics file.  checkpoint / resume: as in
+    verify() (same file format: a dump written by either loop resumes in the other); single rank only.
     dist: an initialised torch.distributed module, one process per GPU, every rank calling with the same arguments:
     each rank keeps its own device frontier (the root starts on rank 0), bounds up to `batch` of its domains per round,
     and the ranks agree per round on the open total and the stop flags with one small all-gather, whose counts also
@@ -491,27 +492,40 @@ def verify_resident(eng, net_id, net, prop: Property, *, batch: int = 1024, max_
     n_clauses = len(prop.violation)
     world = dist.get_world_size() if dist is not None else 1
     rank = dist.get_rank() if dist is not None else 0
-    # the root phase is deterministic: every rank runs it and reaches the same verdict and inherited bounds
-    ce = attack(eng, net_id, net, prop, pgd_restarts, pgd_steps)
-    if ce is not None:
-        return VerifyResult("violated", ce[0], ce[1])
-    rlo, _, inter_lo, inter_hi = eng.crown_bounds(net_id, spec, prop.in_lo, prop.in_hi)
-    res = VerifyResult("unknown", root_lower=rlo[0].copy(), domains_bounded=1)
-    if _verified_mask(rlo, thr, owner, n_clauses)[0]:
-        res.status = "verified"
-        return res
-    max_depth = max_rounds + 2
-    eng.frontier_create(net_id, spec, thr, owner, n_clauses, prop.in_lo, prop.in_hi, inter_lo[0], inter_hi[0],
+    resumed = None
+    if resume is not None:
+        if world > 1:
+            raise ValueError("a frontier dump resumes on a single rank")
+        hist, inh_lo, inh_hi, _, b0 = load_frontier(resume, prop)
+        resumed = frontier_to_arrays(hist)
+        res = VerifyResult("unknown", domains_bounded=b0)
+        max_depth = max_rounds + 2 + int(resumed[0].shape[1])
+    else:
+        # the root phase is deterministic: every rank runs it and reaches the same verdict and inherited bounds
+        ce = attack(eng, net_id, net, prop, pgd_restarts, pgd_steps)
+        if ce is not None:
+            return VerifyResult("violated", ce[0], ce[1])
+        rlo, _, inter_lo, inter_hi = eng.crown_bounds(net_id, spec, prop.in_lo, prop.in_hi)
+        res = VerifyResult("unknown", root_lower=rlo[0].copy(), domains_bounded=1)
+        if _verified_mask(rlo, thr, owner, n_clauses)[0]:
+            res.status = "verified"
+            return res
+        inh_lo, inh_hi = inter_lo[0], inter_hi[0]
+        max_depth = max_rounds + 2
+    eng.frontier_create(net_id, spec, thr, owner, n_clauses, prop.in_lo, prop.in_hi, inh_lo, inh_hi,
                         max_depth=max_depth, capacity=min(2 * max_domains + 2 * batch, 1 << 22))
     exchange = {"exchanges": 0, "records_moved": 0, "bytes_moved": 0} if world > 1 else None
     try:
+        if resumed is not None:
+            eng.frontier_upload(*resumed)
         if world > 1:
             import torch
 
             if rank != 0:   # the root belongs to rank 0's shard
                 scratch = torch.empty((4 * max_depth + 1,), dtype=torch.int32, device=dist_device)
                 eng.frontier_take(1, scratch.data_ptr(), scratch[4 * max_depth:].data_ptr())
-        open_local, total_open = (1 if rank == 0 else 0), 1
+        open_local = eng.frontier_count()
+        total_open = max(open_local, 1)
         while total_open > 0 and res.rounds < max_rounds:
             timed_out = timeout_s is not None and time.time() - t0 > timeout_s
             bounded = stuck = 0
@@ -540,6 +554,9 @@ def verify_resident(eng, net_id, net, prop: Property, *, batch: int = 1024, max_
         res.exchange = exchange
         if total_open == 0 and res.status == "unknown":
             res.status = "verified"
+        if checkpoint is not None and world == 1 and total_open > 0:
+            splits, ns = eng.frontier_download(max_depth)
+            save_frontier(checkpoint, [splits[d, : ns[d]] for d in range(len(ns))], inh_lo, inh_hi, prop, res.rounds, res.domains_bounded)
     finally:
         eng.frontier_destroy()
     return res

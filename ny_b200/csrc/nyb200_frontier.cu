@@ -330,4 +330,51 @@ int32_t nyb200_frontier_give(nyb200_engine *e, int64_t n, const void *dev_splits
     return NYB200_OK;
 }
 
+// The open records in ring order (front first) to host arrays [count x max_depth] / [count]; the frontier keeps them.
+int32_t nyb200_frontier_download(nyb200_engine *e, int64_t capacity, nyb200_split *splits, int32_t *nsplits, int64_t *n_out) {
+    if (!e || !n_out || capacity < 0) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    NYB_CUDA(e, cudaSetDevice(e->device));
+    ResidentFrontier *f = e->frontier;
+    if (!f) return set_err(e, NYB200_ERR_INVALID, "no frontier");
+    *n_out = f->count;
+    if (f->count == 0) return NYB200_OK;
+    if (capacity < f->count || !splits || !nsplits) return set_err(e, NYB200_ERR_SHAPE, "host arrays smaller than the frontier");
+    cudaStream_t st = e->stream;
+    const size_t row = (size_t)f->maxd * sizeof(nyb200_split);
+    const long m = f->count;
+    const long first = (f->cap - f->head) < m ? (f->cap - f->head) : m;
+    NYB_CUDA(e, cudaMemcpyAsync(splits, f->buf + f->head * f->maxd, (size_t)first * row, cudaMemcpyDeviceToHost, st));
+    NYB_CUDA(e, cudaMemcpyAsync(nsplits, f->ns + f->head, (size_t)first * 4, cudaMemcpyDeviceToHost, st));
+    if (first < m) {
+        NYB_CUDA(e, cudaMemcpyAsync((char *)splits + (size_t)first * row, f->buf, (size_t)(m - first) * row, cudaMemcpyDeviceToHost, st));
+        NYB_CUDA(e, cudaMemcpyAsync(nsplits + first, f->ns, (size_t)(m - first) * 4, cudaMemcpyDeviceToHost, st));
+    }
+    NYB_CUDA(e, cudaStreamSynchronize(st));
+    return NYB200_OK;
+}
+
+// Replaces the frontier's contents by n host records ([n x depth] with depth <= max_depth, [n]): the resume of a dump.
+int32_t nyb200_frontier_upload(nyb200_engine *e, int64_t n, int32_t depth, const nyb200_split *splits, const int32_t *nsplits) {
+    if (!e || n < 0 || depth <= 0 || (n > 0 && (!splits || !nsplits))) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    NYB_CUDA(e, cudaSetDevice(e->device));
+    ResidentFrontier *f = e->frontier;
+    if (!f) return set_err(e, NYB200_ERR_INVALID, "no frontier");
+    if (n > f->cap) return set_err(e, NYB200_ERR_OOM, "frontier capacity exceeded");
+    if (depth > f->maxd) return set_err(e, NYB200_ERR_SHAPE, "histories deeper than the frontier's max_depth");
+    for (int64_t i = 0; i < n; ++i)
+        if (nsplits[i] < 0 || nsplits[i] > depth) return set_err(e, NYB200_ERR_INVALID, "history length out of range");
+    cudaStream_t st = e->stream;
+    f->head = 0; f->count = 0;
+    if (n > 0) {
+        NYB_CUDA(e, cudaMemcpy2DAsync(f->buf, (size_t)f->maxd * sizeof(nyb200_split), splits, (size_t)depth * sizeof(nyb200_split),
+                                      (size_t)depth * sizeof(nyb200_split), (size_t)n, cudaMemcpyHostToDevice, st));
+        NYB_CUDA(e, cudaMemcpyAsync(f->ns, nsplits, (size_t)n * 4, cudaMemcpyHostToDevice, st));
+        NYB_CUDA(e, cudaStreamSynchronize(st));
+    }
+    f->count = n;
+    return NYB200_OK;
+}
+
 }  // extern "C"

@@ -33,7 +33,7 @@ ERRCH_IMMEDIATE, ERRCH_REFERENCE = 0, 1
 
 EXPORTS = [
     "nyb200_create", "nyb200_destroy", "nyb200_backend_provenance", "nyb200_last_error", "nyb200_set_stream",
-    "nyb200_set_path", "nyb200_set_refine_tolerance", "nyb200_batch_refined", "nyb200_batch_poll", "nyb200_crown_bounds_split", "nyb200_batch_set_inherited", "nyb200_frontier_create", "nyb200_frontier_round", "nyb200_frontier_destroy", "nyb200_frontier_count", "nyb200_frontier_take", "nyb200_frontier_give", "nyb200_launch_count", "nyb200_clear_working_set", "nyb200_gemm_f32", "nyb200_net_create",
+    "nyb200_set_path", "nyb200_set_refine_tolerance", "nyb200_batch_refined", "nyb200_batch_poll", "nyb200_crown_bounds_split", "nyb200_batch_set_inherited", "nyb200_frontier_create", "nyb200_frontier_round", "nyb200_frontier_destroy", "nyb200_frontier_count", "nyb200_frontier_take", "nyb200_frontier_give", "nyb200_frontier_download", "nyb200_frontier_upload", "nyb200_launch_count", "nyb200_clear_working_set", "nyb200_gemm_f32", "nyb200_net_create",
     "nyb200_net_destroy", "nyb200_ibp_forward", "nyb200_ibp_forward_noalloc", "nyb200_bab_bound_batch", "nyb200_batch_upload", "nyb200_batch_run",
     "nyb200_batch_download", "nyb200_batch_min_lower", "nyb200_batch_min_lower_device",
     "nyb200_batch_download_pre_bounds", "nyb200_batch_select_branch", "nyb200_timing_enable", "nyb200_timing_reset",
@@ -796,6 +796,26 @@ class B200Engine:
         fn = self._L.nyb200_frontier_give
         fn.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]
         self._check(fn(self._h, int(n), C.c_void_p(dev_splits), C.c_void_p(dev_nsplits)))
+
+    def frontier_download(self, max_depth: int):
+        """The open records in frontier order as host arrays (splits [n, max_depth], n_splits [n]); the frontier keeps
+        them.  max_depth: the value the frontier was created with."""
+        n = self.frontier_count()
+        splits = np.zeros((n, max_depth), SPLIT_DTYPE)
+        ns = np.zeros(n, np.int32)
+        got = C.c_int64(0)
+        fn = self._L.nyb200_frontier_download
+        fn.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.POINTER(C.c_int64)]
+        self._check(fn(self._h, n, C.c_void_p(splits.ctypes.data), C.c_void_p(ns.ctypes.data), C.byref(got)))
+        return splits, ns
+
+    def frontier_upload(self, splits, n_splits):
+        """Replaces the device frontier's contents by host records (splits [n, depth], n_splits [n])."""
+        ns = np.ascontiguousarray(n_splits, np.int32)
+        splits = np.ascontiguousarray(np.asarray(splits, SPLIT_DTYPE).reshape(len(ns), -1))
+        fn = self._L.nyb200_frontier_upload
+        fn.argtypes = [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p]
+        self._check(fn(self._h, len(ns), int(splits.shape[1]) if len(ns) else 1, C.c_void_p(splits.ctypes.data), C.c_void_p(ns.ctypes.data)))
 
     def frontier_destroy(self):
         self._L.nyb200_frontier_destroy.argtypes = [C.c_void_p]

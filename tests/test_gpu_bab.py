@@ -270,8 +270,8 @@ def test_device_resident_frontier_runs_the_host_loop_search(eng, branching):
     def prop(t):
         return formats.Property(wl.in_lo, wl.in_hi, [[formats.Atom(-row, float(t))]])
 
-    cases = [(float(root_lo[0][s] + 0.25 * (mn[s] - root_lo[0][s])), 64, 40),     # closes
-             (float(root_lo[0][s] + 0.9 * (mn[s] - root_lo[0][s])), 48, 12)]      # runs out of rounds, ring wraps
+    cases = [(float(root_lo[0][s] + 0.25 * (mn[s] - root_lo[0][s])), 64, 40),     # an easy threshold
+             (float(root_lo[0][s] + 0.9 * (mn[s] - root_lo[0][s])), 48, 12)]      # a hard one: runs out of rounds, ring wraps
     for t, batch, rounds in cases:
         a = bab.verify(eng, nid, net, prop(t), batch=batch, max_rounds=rounds, branching=branching)
         b = bab.verify_resident(eng, nid, net, prop(t), batch=batch, max_rounds=rounds, branching=branching)
@@ -408,3 +408,31 @@ def test_sharded_search_on_device_resident_frontiers_over_nccl(tmp_path):
     assert one[0] == many[0] == "unknown" and many[1] == one[1] and many[2] >= one[2]
     moved = sum(x["closes"]["exchange"]["records_moved"] for x in res)
     assert moved > 0 and moved % 2 == 0   # every move is counted by its sender and by its receiver
+
+
+@pytest.mark.gpu
+def test_device_resident_search_dumps_its_frontier_and_resumes(eng, tmp_path):
+    """A resident search stopped by its round limit writes the open records (front first) in the host loop's dump
+    format; resumed from there, by either loop, it ends where the uninterrupted search ends."""
+    wl = W.config_mlp_bab(seed=83, hidden=24, depth=3, n_in=4, n_out=3, eps=0.2, n_fix=0)
+    net = wl.net
+    nid = eng.register_network(net)
+    root_lo, _, _, _ = eng.crown_bounds(nid, wl.spec, wl.in_lo, wl.in_hi)
+    mn = W.sample_min_margin(wl, 200000, 3)
+    s = int(np.argmax(mn - root_lo[0]))
+    p = formats.Property(wl.in_lo, wl.in_hi, [[formats.Atom(-wl.spec[s], float(root_lo[0][s] + 0.5 * (mn[s] - root_lo[0][s])))]])
+    whole = bab.verify_resident(eng, nid, net, p, batch=2, max_rounds=200)
+    assert whole.status == "verified" and whole.rounds > 4
+    dump = tmp_path / "frontier.npz"
+    first = bab.verify_resident(eng, nid, net, p, batch=2, max_rounds=3, checkpoint=dump)
+    assert first.status == "unknown" and first.open_domains > 0 and dump.exists()
+    hist, _, _, rounds, bounded = bab.load_frontier(dump, p)
+    assert len(hist) == first.open_domains and rounds == 3 and bounded == first.domains_bounded
+    rest = bab.verify_resident(eng, nid, net, p, batch=2, max_rounds=200, resume=dump)
+    assert rest.status == "verified" and rest.domains_bounded == whole.domains_bounded and rest.rounds == whole.rounds - 3
+    host = bab.verify(eng, nid, net, p, batch=2, max_rounds=200, resume=dump)
+    assert host.status == "verified" and host.domains_bounded == whole.domains_bounded and host.rounds == rest.rounds
+    other = formats.Property(wl.in_lo, wl.in_hi, [[formats.Atom(-wl.spec[s], float(root_lo[0][s]) - 1.0)]])
+    with pytest.raises(ValueError):
+        bab.verify_resident(eng, nid, net, other, batch=2, max_rounds=3, resume=dump)
+    eng.release_network(nid)
