@@ -58,6 +58,12 @@ const char *nyb200_backend_provenance(void);
 const char *nyb200_last_error(const nyb200_engine *e);
 /* Launch all work of this engine on the given cudaStream_t (NULL = the default stream). */
 int32_t nyb200_set_stream(nyb200_engine *e, void *cuda_stream);
+/* Gives the engine a non-blocking stream of its own (created on first use, destroyed with the engine) and makes it the
+ * engine's stream.  Several engines on one GPU, each with its own stream and its own batches, overlap on the device:
+ * batches are independent, so one batch's latency-bound interval pass runs beside another's tensor-bound chain, and
+ * one's transfers beside another's kernels (ny_b200/pool.py drives that; the reference's counterpart is its per-thread
+ * engine handles, crates/ny-core/src/gemm.rs:568-578). */
+int32_t nyb200_use_own_stream(nyb200_engine *e);
 /* Select the contraction arithmetic (NYB200_PATH_*).  Default NYB200_PATH_TF32X3; NYB200_PATH_F64 is the
  * slower binary64 reference arithmetic on the same device. */
 int32_t nyb200_set_path(nyb200_engine *e, int32_t path);

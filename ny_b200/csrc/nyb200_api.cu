@@ -84,6 +84,7 @@ void nyb200_destroy(nyb200_engine *e) {
     if (e->stage) cudaFreeHost(e->stage);
     if (e->stage_in_done) cudaEventDestroy(e->stage_in_done);
     if (e->frontier) nyb::frontier_free(e->frontier);
+    if (e->own_stream) cudaStreamDestroy(e->own_stream);
     for (int i = 0; i < 3; ++i) if (e->timing.ev[i]) cudaEventDestroy(e->timing.ev[i]);
     for (cudaEvent_t ev : e->timing.kev) cudaEventDestroy(ev);
     for (int i = 0; i < 2; ++i) if (e->timing.cev[i]) cudaEventDestroy(e->timing.cev[i]);
@@ -96,6 +97,16 @@ int32_t nyb200_set_stream(nyb200_engine *e, void *cuda_stream) {
     if (!e) return NYB200_ERR_INVALID;
     std::lock_guard<std::mutex> g(e->mu);
     e->stream = (cudaStream_t)cuda_stream;
+    return NYB200_OK;
+}
+
+int32_t nyb200_use_own_stream(nyb200_engine *e) {
+    if (!e) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    NYB_CUDA(e, cudaSetDevice(e->device));
+    if (!e->own_stream) NYB_CUDA(e, cudaStreamCreateWithFlags(&e->own_stream, cudaStreamNonBlocking));
+    NYB_CUDA(e, cudaStreamSynchronize(e->stream));   // work queued on the previous stream is complete before the switch
+    e->stream = e->own_stream;
     return NYB200_OK;
 }
 

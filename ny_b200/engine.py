@@ -42,7 +42,7 @@ EXPORTS = [
     "nyb200_crown_bounds", "nyb200_batch_download_alpha_upper",
     "nyb200_batch_verdicts", "nyb200_gemm_f64", "nyb200_conv_transpose_2d", "nyb200_set_deadline_ns",
     "nyb200_batch_gradient", "nyb200_point_vjp_batched", "nyb200_crown_input_coeffs", "nyb200_batch_download_branch_scores",
-    "nyb200_set_error_channel", "nyb200_set_fusion", "nyb200_batch_download_opt_evaluations",
+    "nyb200_set_error_channel", "nyb200_set_fusion", "nyb200_use_own_stream", "nyb200_batch_download_opt_evaluations",
     "nyb200_crown_backward", "nyb200_crown_resnet_beta_batched", "nyb200_crown_resnet_beta_batched_adam", "nyb200_gemm_f64_triplet",
 ]
 
@@ -403,6 +403,11 @@ class B200Engine:
 
     def set_stream(self, cuda_stream: int):
         self._check(self._L.nyb200_set_stream(self._h, C.c_void_p(cuda_stream)))
+
+    def use_own_stream(self):
+        """A non-blocking stream of the engine's own (several engines on one GPU then overlap: ny_b200.pool)."""
+        self._L.nyb200_use_own_stream.argtypes = [C.c_void_p]
+        self._check(self._L.nyb200_use_own_stream(self._h))
 
     def set_path(self, path: int):
         self._check(self._L.nyb200_set_path(self._h, path))

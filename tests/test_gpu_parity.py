@@ -358,3 +358,37 @@ def test_domain_major_relaxation_with_ragged_column_slab(eng, oracle):
     assert feas.sum() > 40
     assert _rel(np.concatenate([glo[pick], ghi[pick]], axis=1)[feas], np.concatenate([olo, ohi], axis=1)[feas]) <= REL_TOL
     eng.release_network(nid)
+
+
+def test_batches_in_flight_on_an_engine_pool_match_a_single_engine(oracle):
+    """ny_b200.pool.EnginePool: several engines on one GPU, each with its own stream, workspace and host thread, the
+    batches handed out in turn.  Every batch's bounds are bit-identical to the ones a single engine returns for it."""
+    from ny_b200 import B200Engine
+    from ny_b200.pool import EnginePool
+
+    wl = W.config_mlp_bab(seed=19, hidden=128, depth=4, n_in=96, eps=0.015, n_fix=6)
+    onet = oracle.Net(wl.net.weights, wl.net.biases)
+    rl, ru = oracle.ibp_forward(onet, wl.in_lo, wl.in_hi)
+    batches = []
+    for k in range(7):
+        splits, ns = W.draw_domains(wl, rl, ru, 200 + 37 * k, first=1000 * k)
+        batches.append((wl.spec, wl.in_lo, wl.in_hi, rl, ru, splits, ns, 1))
+    one = B200Engine(0)
+    nid = one.register_network(wl.net)
+    want = [one.bab_bound_batch(nid, *b) for b in batches]
+    one.close()
+    pool = EnginePool(0, 3)
+    h = pool.register_network(wl.net)
+    for _ in range(2):   # the second pass runs on warmed-up workspaces
+        got = pool.bound_batches(h, batches)
+        assert len(got) == len(want)
+        for (gl, gu, gi), (wl_, wu, wi) in zip(got, want):
+            assert np.array_equal(gl, wl_) and np.array_equal(gu, wu) and np.array_equal(gi, wi)
+    # an engine's error surfaces after every thread has ended
+    from ny_b200 import EngineError
+
+    bad = list(batches)
+    bad[4] = bad[4][:5] + (bad[4][5], bad[4][6][:-1], 1)     # n_splits shorter than the batch
+    with pytest.raises(EngineError):
+        pool.bound_batches(h, bad)
+    pool.close()
