@@ -772,8 +772,8 @@ def run_cnn(args, local_rank, kind="cnn"):
 def run_search(args, rank, world, local_rank):
     """Secondary workload (--workload bab-search): the whole branch-and-bound loop (ny_b200/bab.py) on a seeded MLP
     64 -> 4x256 -> 10 with a property it cannot close in the given rounds, so that every round bounds a full batch:
-    with --resident 1 (default) the open domain set lives on the device and a round is one call (pop, bound, prune,
-    branch, push); with --resident 0 or an optimising search the host loop runs: upload of the children's split
+    with --resident 1 (default) the open domain set lives on the device and a round is one call (pop, bound or
+    optimise with warm starts, prune, branch, push); with --resident 0 the host loop runs: upload of the children's split
     lists, bound, download, branching choice, child creation on the host.  One step = one search of `rounds` rounds;
     value = domains bounded per second of wall clock, host work included.
     With N > 1 ranks (one process per GPU) every rank bounds its own shard of the frontier, `batch` domains per rank
@@ -805,12 +805,12 @@ def run_search(args, rank, world, local_rank):
     rounds = 40
     opt_it = args.search_iterations
 
-    resident = bool(args.resident) and opt_it <= 1
+    resident = bool(args.resident)
 
     def search():
         if resident:   # the open domain set stays on the device: one call per round
             return bab.verify_resident(eng, nid, wl.net, prop, batch=batch, max_rounds=rounds, branching=1, pgd_restarts=64,
-                                       pgd_steps=10, dist=dist, dist_device=dev)
+                                       pgd_steps=10, optimize_iterations=opt_it, max_domains=1 << 18, dist=dist, dist_device=dev)
         return bab.verify(eng, nid, wl.net, prop, batch=batch, max_rounds=rounds, optimize_iterations=opt_it, branching=1,
                           pgd_restarts=64, pgd_steps=10, dist=dist, dist_device=dev)
 

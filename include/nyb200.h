@@ -103,6 +103,14 @@ int32_t nyb200_frontier_create(nyb200_engine *e, int32_t net_id, const float *sp
                                const float *inh_lo, const float *inh_hi, int32_t max_depth, int64_t capacity);
 int32_t nyb200_frontier_round(nyb200_engine *e, int32_t batch, int32_t branching, int64_t *stats_out, float *min_lower);
 void nyb200_frontier_destroy(nyb200_engine *e);
+/* The same round with every domain's slopes and split multipliers optimised (cfg as for nyb200_batch_optimize; declared
+ * below) and warm starts: the children inherit the parent's optimised slopes (kept in a ring of [capacity x neurons]
+ * floats that the first such round allocates) and carry its optimised multipliers in their split records; a batch
+ * starts warm when every one of its domains has slopes of its own (the rule of the host loop, ny_b200/bab.py, which
+ * follows beta_crown/engine/core.rs:600-700).  Records that arrive through nyb200_frontier_give / _upload have none. */
+struct nyb200_opt_config;
+int32_t nyb200_frontier_round_optimized(nyb200_engine *e, int32_t batch, int32_t branching, const struct nyb200_opt_config *cfg,
+                                        int64_t *stats_out, float *min_lower);
 /* Sharded search (one process per GPU, each with its own frontier): the shards are levelled by moving records between
  * them, device array to device array (the caller carries them with a point-to-point collective; the reference's
  * domain distribution is host-side, beta_crown/engine/core.rs:560-640).  nyb200_frontier_take removes up to n records

@@ -471,12 +471,15 @@ def verify(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: i
 
 def verify_resident(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: int = 64,
                     max_domains: int = 1 << 20, pgd_restarts: int = 256, pgd_steps: int = 50, branching: int = 1,
-                    timeout_s: float | None = None, checkpoint=None, resume=None, dist=None, dist_device=None) -> VerifyResult:
+                    timeout_s: float | None = None, checkpoint=None, resume=None, optimize_iterations: int = 0,
+                    dist=None, dist_device=None) -> VerifyResult:
     """The search of verify() with the open domain set kept on the device (nyb200_frontier_*): attack and root bound
     as there, then one device call per round that pops a batch, bounds it (one bound per domain, multipliers at
     zero), prunes verified and infeasible domains, picks every open domain's split neuron (0 width, 1 intercept,
     2 BaBSR) and appends both children.  Same order of domains as the host loop, hence the same counts and verdicts;
-    what it leaves out is the optimising search with warm starts and the metrics file.  checkpoint / resume: as in
+    optimize_iterations > 1: every domain's slopes and multipliers are optimised that many steps and children start
+    from their parent's (nyb200_frontier_round_optimized: verify()'s warm-started search; records moved between ranks
+    or resumed from a dump start cold).  What it leaves out is the metrics file.  checkpoint / resume: as in
     verify() (same file format: a dump written by either loop resumes in the other); single rank only.
     dist: an initialised torch.distributed module, one process per GPU, every rank calling with the same arguments:
     each rank keeps its own device frontier (the root starts on rank 0), bounds up to `batch` of its domains per round,
@@ -530,7 +533,10 @@ def verify_resident(eng, net_id, net, prop: Property, *, batch: int = 1024, max_
             timed_out = timeout_s is not None and time.time() - t0 > timeout_s
             bounded = stuck = 0
             if open_local > 0 and not timed_out:
-                bounded, _, _, stuck, open_local, _, _ = eng.frontier_round(batch, branching)
+                if optimize_iterations > 1:
+                    bounded, _, _, stuck, open_local, _, _ = eng.frontier_round_optimized(batch, branching, optimize_iterations, 0.1, 0.05)
+                else:
+                    bounded, _, _, stuck, open_local, _, _ = eng.frontier_round(batch, branching)
             if world > 1:
                 mine = torch.tensor([open_local, bounded, stuck, 1 if timed_out else 0], dtype=torch.int64, device=dist_device)
                 every = [torch.zeros_like(mine) for _ in range(world)]

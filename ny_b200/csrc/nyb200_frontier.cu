@@ -28,11 +28,17 @@ struct ResidentFrontier {
     float *consts = nullptr;       // device copies of spec, box and inherited bounds, back to back
     size_t n_spec = 0, n_box = 0, n_inh = 0;
     long bounded = 0;
+    // warm starts of the optimising search: one row of slopes per ring slot [cap x nps], allocated by the first
+    // optimising round.  The first no_alpha_front records (counted from the front) have no slopes of their own (the
+    // root, records that arrived from outside, children of a round that did not optimise); every record behind has.
+    float *alpha = nullptr;
+    long no_alpha_front = 0;
 };
 
 void frontier_free(ResidentFrontier *f) {
     if (!f) return;
     cudaFree(f->buf); cudaFree(f->ns); cudaFree(f->stats); cudaFree(f->thr); cudaFree(f->owner); cudaFree(f->consts);
+    cudaFree(f->alpha);
     delete f;
 }
 
@@ -128,6 +134,41 @@ __global__ void k_frontier_children(int D, int maxd, long cap, long tail, const 
     }
 }
 
+// The same for the optimising search: the parent's records carry its optimised multipliers (|signed beta| of the
+// relaxation table, beta_crown/state/beta.rs warm start), the new split starts at 0, and both children inherit the
+// parent's optimised slopes (the table's lower slopes) in their slots of the slope ring.
+__global__ void k_frontier_children_warm(NetView nv, int D, int maxd, long cap, long tail, const nyb200_split *__restrict__ psplits,
+                                         const int *__restrict__ pns, const int *__restrict__ pos, const int *__restrict__ relu,
+                                         const int *__restrict__ neuron, const float4 *__restrict__ tab,
+                                         nyb200_split *__restrict__ buf, int *__restrict__ ns, float *__restrict__ alpha) {
+    const int d = blockIdx.x;
+    if (d >= D || pos[d] < 0) return;
+    const int n = pns[d];
+    const long s0 = (tail + 2L * pos[d]) % cap, s1 = (tail + 2L * pos[d] + 1) % cap;
+    const float4 *t = tab + (long)d * nv.nps;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        nyb200_split r = psplits[(long)d * maxd + i];
+        float b = 0.f;
+        if (r.relu >= 0 && r.relu < nv.L - 1 && r.neuron >= 0 && r.neuron < nv.dims[r.relu + 1]) b = fabsf(t[nv.pre_off[r.relu] + r.neuron].w);
+        r.beta = b;
+        buf[s0 * maxd + i] = r;
+        buf[s1 * maxd + i] = r;
+    }
+    for (long j = threadIdx.x; j < nv.nps; j += blockDim.x) {
+        const float a = j < nv.n_pre ? t[j].x : 0.f;
+        alpha[s0 * nv.nps + j] = a;
+        alpha[s1 * nv.nps + j] = a;
+    }
+    if (threadIdx.x == 0) {
+        nyb200_split r;
+        r.relu = relu[d]; r.neuron = neuron[d]; r.sign = 1; r.beta = 0.f;
+        buf[s0 * maxd + n] = r;
+        r.sign = -1;
+        buf[s1 * maxd + n] = r;
+        ns[s0] = n + 1; ns[s1] = n + 1;
+    }
+}
+
 }  // namespace
 
 }  // namespace nyb
@@ -175,7 +216,7 @@ int32_t nyb200_frontier_create(nyb200_engine *e, int32_t net_id, const float *sp
     }
     // the root: one domain without splits
     NYB_CUDA(e, cudaMemset(f->ns, 0, 4));
-    f->head = 0; f->count = 1;
+    f->head = 0; f->count = 1; f->no_alpha_front = 1;
     e->frontier = f;
     return NYB200_OK;
 }
@@ -189,10 +230,12 @@ void nyb200_frontier_destroy(nyb200_engine *e) {
 // stats out: [0] domains bounded this round, [1] verified, [2] infeasible, [3] stuck (undecided, nothing left to
 // split: they stay at the front of the frontier), [4] open domains in the frontier after the round, [5] deepest history
 // bounded; min_lower: smallest lower bound of the round's feasible domains.
-int32_t nyb200_frontier_round(nyb200_engine *e, int32_t batch, int32_t branching, int64_t *stats_out, float *min_lower) {
+static int32_t frontier_round_impl(nyb200_engine *e, int32_t batch, int32_t branching, const nyb200_opt_config *cfg,
+                                   int64_t *stats_out, float *min_lower) {
     if (!e || !stats_out || !min_lower || batch <= 0) return NYB200_ERR_INVALID;
     std::lock_guard<std::mutex> g(e->mu);
     NYB_CUDA(e, cudaSetDevice(e->device));
+    const bool optimise = cfg && cfg->iterations > 1;
     ResidentFrontier *f = e->frontier;
     if (!f) return set_err(e, NYB200_ERR_INVALID, "no frontier");
     if (branching != NYB200_BRANCH_WIDTH && branching != NYB200_BRANCH_INTERCEPT && branching != NYB200_BRANCH_BABSR)
@@ -206,8 +249,15 @@ int32_t nyb200_frontier_round(nyb200_engine *e, int32_t batch, int32_t branching
     const NetView &nv = net->v;
     const int D = (int)(f->count < batch ? f->count : batch);
     cudaStream_t st = e->stream;
+    if (optimise && !f->alpha) {
+        if (cudaMalloc(&f->alpha, (size_t)f->cap * nv.nps * 4) != cudaSuccess)
+            return set_err(e, NYB200_ERR_OOM, "device allocation failed for the frontier's slopes (capacity x neurons)");
+    }
+    // warm start only when every domain of the batch has slopes of its own (the host loop's rule)
+    const bool warm = optimise && f->no_alpha_front == 0;
     Batch b;
     b.net_id = f->net_id; b.S = f->S; b.R = 2 * f->S; b.D = D; b.mode = 1; b.box_stride = 0; b.max_splits = f->maxd;
+    b.has_alpha = warm;
     BatchPtrs p;
     NYB_TRY(batch_ptrs(e, *net, b, p));
     {   // the search's constants, device to device (the workspace arrays may have served another call in between)
@@ -227,9 +277,15 @@ int32_t nyb200_frontier_round(nyb200_engine *e, int32_t batch, int32_t branching
         NYB_CUDA(e, cudaMemcpyAsync(p.splits + first * f->maxd, f->buf, (size_t)(D - first) * row, cudaMemcpyDeviceToDevice, st));
         NYB_CUDA(e, cudaMemcpyAsync(p.nsplits + first, f->ns, (size_t)(D - first) * 4, cudaMemcpyDeviceToDevice, st));
     }
+    if (warm) {
+        NYB_CUDA(e, cudaMemcpyAsync(p.alpha, f->alpha + f->head * nv.nps, (size_t)first * nv.nps * 4, cudaMemcpyDeviceToDevice, st));
+        if (first < D)
+            NYB_CUDA(e, cudaMemcpyAsync(p.alpha + first * nv.nps, f->alpha, (size_t)(D - first) * nv.nps * 4, cudaMemcpyDeviceToDevice, st));
+    }
     b.valid = true;
     e->batch = b;
-    NYB_TRY(run_batch_public(e));
+    if (optimise) NYB_TRY(optimize_batch(e, *cfg));
+    else NYB_TRY(run_batch_public(e));
     NYB_TRY(finish_batch_public(e));   // synchronises; re-evaluates flagged domains in binary64
     NYB_WS(done, int *, e, "fr_done", (size_t)D * 4);
     NYB_WS(pos, int *, e, "fr_pos", (size_t)D * 4);
@@ -259,15 +315,28 @@ int32_t nyb200_frontier_round(nyb200_engine *e, int32_t batch, int32_t branching
     if (f->count - D + 2L * n_open > f->cap) return set_err(e, NYB200_ERR_OOM, "frontier capacity exceeded");
     const long tail = (f->head + f->count) % f->cap;
     if (n_open > 0) {
-        k_frontier_children<<<D, 64, 0, st>>>(D, f->maxd, f->cap, tail, p.splits, p.nsplits, pos, dr, dn, f->buf, f->ns);
+        if (optimise) k_frontier_children_warm<<<D, 128, 0, st>>>(nv, D, f->maxd, f->cap, tail, p.splits, p.nsplits, pos, dr, dn, p.tab, f->buf, f->ns, f->alpha);
+        else k_frontier_children<<<D, 64, 0, st>>>(D, f->maxd, f->cap, tail, p.splits, p.nsplits, pos, dr, dn, f->buf, f->ns);
         e->launches++;
     }
     NYB_CUDA(e, cudaGetLastError());
     f->head = (f->head + D) % f->cap;
     f->count += 2L * n_open - D;
+    f->no_alpha_front = f->no_alpha_front > D ? f->no_alpha_front - D : 0;
+    if (!optimise && n_open > 0) f->no_alpha_front = f->count;   // children without slopes behind whatever was there
     f->bounded += D;
     stats_out[0] = D; stats_out[4] = f->count;
     return NYB200_OK;
+}
+
+int32_t nyb200_frontier_round(nyb200_engine *e, int32_t batch, int32_t branching, int64_t *stats_out, float *min_lower) {
+    return frontier_round_impl(e, batch, branching, nullptr, stats_out, min_lower);
+}
+
+int32_t nyb200_frontier_round_optimized(nyb200_engine *e, int32_t batch, int32_t branching, const nyb200_opt_config *cfg,
+                                        int64_t *stats_out, float *min_lower) {
+    if (!cfg) return NYB200_ERR_INVALID;
+    return frontier_round_impl(e, batch, branching, cfg, stats_out, min_lower);
 }
 
 int32_t nyb200_frontier_count(nyb200_engine *e, int64_t *open) {
@@ -302,6 +371,7 @@ int32_t nyb200_frontier_take(nyb200_engine *e, int64_t n, void *dev_splits, int3
     }
     NYB_CUDA(e, cudaStreamSynchronize(st));
     f->count -= m;
+    if (f->no_alpha_front > f->count) f->no_alpha_front = f->count;
     return NYB200_OK;
 }
 
@@ -327,6 +397,7 @@ int32_t nyb200_frontier_give(nyb200_engine *e, int64_t n, const void *dev_splits
     }
     NYB_CUDA(e, cudaStreamSynchronize(st));   // the caller may reuse its arrays
     f->count += n;
+    f->no_alpha_front = f->count;   // records from outside carry no slopes
     return NYB200_OK;
 }
 
@@ -374,6 +445,7 @@ int32_t nyb200_frontier_upload(nyb200_engine *e, int64_t n, int32_t depth, const
         NYB_CUDA(e, cudaStreamSynchronize(st));
     }
     f->count = n;
+    f->no_alpha_front = n;
     return NYB200_OK;
 }
 

@@ -436,3 +436,29 @@ def test_device_resident_search_dumps_its_frontier_and_resumes(eng, tmp_path):
     with pytest.raises(ValueError):
         bab.verify_resident(eng, nid, net, other, batch=2, max_rounds=3, resume=dump)
     eng.release_network(nid)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("branching", [1, 2])
+def test_device_resident_optimising_search_with_warm_starts_runs_the_host_loop_search(eng, branching):
+    """nyb200_frontier_round_optimized: every domain's slopes and multipliers optimised on the device, children
+    starting from their parent's (slopes in a device ring, multipliers in the split records).  Against the host loop
+    with the same settings (which downloads the parameters and uploads them with the children): the same domains with
+    the same starting points in the same order, so the same verdict, rounds and domain counts - on a threshold that
+    one bound per domain does not close in these rounds."""
+    wl = W.config_mlp_bab(seed=83, hidden=24, depth=3, n_in=4, n_out=3, eps=0.2, n_fix=0)
+    net = wl.net
+    nid = eng.register_network(net)
+    root_lo, _, _, _ = eng.crown_bounds(nid, wl.spec, wl.in_lo, wl.in_hi)
+    mn = W.sample_min_margin(wl, 200000, 3)
+    s = int(np.argmax(mn - root_lo[0]))
+    p = formats.Property(wl.in_lo, wl.in_hi, [[formats.Atom(-wl.spec[s], float(root_lo[0][s] + 0.9 * (mn[s] - root_lo[0][s])))]])
+    for batch, rounds in ((32, 400), (5, 7)):    # closes; stops early with a frontier larger than the batch (ring wraps)
+        a = bab.verify(eng, nid, net, p, batch=batch, max_rounds=rounds, branching=branching, optimize_iterations=6, warm_start=True)
+        b = bab.verify_resident(eng, nid, net, p, batch=batch, max_rounds=rounds, branching=branching, optimize_iterations=6)
+        assert (a.status, a.rounds, a.domains_bounded, a.open_domains) == (b.status, b.rounds, b.domains_bounded, b.open_domains)
+    assert a.domains_bounded > 3
+    plain = bab.verify_resident(eng, nid, net, p, batch=32, max_rounds=400, branching=branching)
+    full = bab.verify_resident(eng, nid, net, p, batch=32, max_rounds=400, branching=branching, optimize_iterations=6)
+    assert full.status == "verified" and (plain.status != "verified" or full.domains_bounded <= plain.domains_bounded)
+    eng.release_network(nid)
