@@ -260,6 +260,8 @@ def run_ours(args, rank, world, local_rank):
 
     eng.set_path(E.PATH_TF32X3 if args.path == "tf32x3" else E.PATH_F64)
     eng.set_fusion(bool(args.fusion))
+    reserve = args.reserve_sms if args.reserve_sms >= 0 else (2 if world > 1 else 0)   # room for the min-reduce beside the kernels
+    eng.set_reserved_sms(reserve)
     eng._path_name = args.path
     wl = W.config_mlp_bab()
     nid = eng.register_network(wl.net)
@@ -358,6 +360,7 @@ def run_ours(args, rank, world, local_rank):
         e_i = B200Engine(local_rank, st_i.cuda_stream)
         e_i.set_path(E.PATH_TF32X3 if args.path == "tf32x3" else E.PATH_F64)
         e_i.set_fusion(bool(args.fusion))
+        e_i.set_reserved_sms(reserve)
         n_i = e_i.register_network(wl.net)
         d_i = W.draw_domains(wl, rl, ru, D, first=(world * i + rank) * D)
         e_i.batch_upload(n_i, wl.spec, wl.in_lo, wl.in_hi, rl, ru, d_i[0], d_i[1], mode=1)
@@ -987,6 +990,8 @@ def main():
                     help="bab-search: optimisation iterations per domain (0 = one bound per domain, the reference's throughput default)")
     ap.add_argument("--in-flight", type=int, default=3,
                     help="resident batches in flight per GPU (one engine and stream each; 1: a single batch, as the kernel profiles use)")
+    ap.add_argument("--reserve-sms", type=int, default=-1,
+                    help="SMs the persistent kernels leave to the min-reduce on the side stream (-1: 2 when N > 1, else 0)")
     ap.add_argument("--domains", type=int, default=D_PER_GPU, help="domains per GPU (profiling runs use a smaller batch)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

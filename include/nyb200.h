@@ -64,6 +64,11 @@ int32_t nyb200_set_stream(nyb200_engine *e, void *cuda_stream);
  * one's transfers beside another's kernels (ny_b200/pool.py drives that; the reference's counterpart is its per-thread
  * engine handles, crates/ny-core/src/gemm.rs:568-578). */
 int32_t nyb200_use_own_stream(nyb200_engine *e);
+/* The persistent kernels (one CTA per SM, tiles dealt out statically) leave n SMs unused.  For callers that run a
+ * collective on another stream beside them (the per-round min-reduce of a sharded search): a collective's CTA that
+ * takes an SM keeps one CTA of a full-width persistent kernel waiting until another retires, which stretches that
+ * kernel by its whole per-CTA share.  Default 0. */
+int32_t nyb200_set_reserved_sms(nyb200_engine *e, int32_t n);
 /* Select the contraction arithmetic (NYB200_PATH_*).  Default NYB200_PATH_TF32X3; NYB200_PATH_F64 is the
  * slower binary64 reference arithmetic on the same device. */
 int32_t nyb200_set_path(nyb200_engine *e, int32_t path);

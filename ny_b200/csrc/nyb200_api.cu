@@ -100,6 +100,13 @@ int32_t nyb200_set_stream(nyb200_engine *e, void *cuda_stream) {
     return NYB200_OK;
 }
 
+int32_t nyb200_set_reserved_sms(nyb200_engine *e, int32_t n) {
+    if (!e || n < 0 || n > 64) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    e->reserve_sms = n;
+    return NYB200_OK;
+}
+
 int32_t nyb200_use_own_stream(nyb200_engine *e) {
     if (!e) return NYB200_ERR_INVALID;
     std::lock_guard<std::mutex> g(e->mu);

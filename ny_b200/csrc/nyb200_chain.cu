@@ -598,6 +598,7 @@ int launch_chain(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int L
     }
     int sms = 0;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, e->device);
+    if (e->reserve_sms > 0 && sms > e->reserve_sms) sms -= e->reserve_sms;   // left to a concurrent collective
     const int tiles = (P.M + BM - 1) / BM;
     const int grid = tiles < sms ? tiles : sms;
     // a 128-row tile spans at most (BM - 2) / R + 2 domains; the table ring holds MAXD of them

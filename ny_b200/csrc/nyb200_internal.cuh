@@ -122,6 +122,7 @@ using nyb::ResidentFrontier;
 struct nyb200_engine {
     int device = 0;
     cudaStream_t stream = nullptr;
+    int reserve_sms = 0;                          // see nyb200_set_reserved_sms
     cudaStream_t own_stream = nullptr;            // created by nyb200_use_own_stream, destroyed with the engine
     int path = NYB200_PATH_TF32X3;
     float refine_tol = 5e-5f;  // see nyb200_set_refine_tolerance

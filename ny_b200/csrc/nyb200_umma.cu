@@ -496,6 +496,7 @@ int launch_umma(nyb200_engine *e, const UmmaLayer &L, int M, const float *A, int
     }
     int sms = 0;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, e->device);
+    if (e->reserve_sms > 0 && sms > e->reserve_sms) sms -= e->reserve_sms;   // left to a concurrent collective
     int tiles = ((M + BM - 1) / BM) * ((L.N + BN - 1) / BN);
     int grid = tiles < sms ? tiles : sms;
     // The fp32 operand goes through TMA when a tensor map can describe it: rows of K contiguous values, base and row

@@ -42,7 +42,7 @@ EXPORTS = [
     "nyb200_crown_bounds", "nyb200_batch_download_alpha_upper",
     "nyb200_batch_verdicts", "nyb200_gemm_f64", "nyb200_conv_transpose_2d", "nyb200_set_deadline_ns",
     "nyb200_batch_gradient", "nyb200_point_vjp_batched", "nyb200_crown_input_coeffs", "nyb200_batch_download_branch_scores",
-    "nyb200_set_error_channel", "nyb200_set_fusion", "nyb200_use_own_stream", "nyb200_batch_download_opt_evaluations",
+    "nyb200_set_error_channel", "nyb200_set_fusion", "nyb200_use_own_stream", "nyb200_set_reserved_sms", "nyb200_batch_download_opt_evaluations",
     "nyb200_crown_backward", "nyb200_crown_resnet_beta_batched", "nyb200_crown_resnet_beta_batched_adam", "nyb200_gemm_f64_triplet",
 ]
 
@@ -408,6 +408,11 @@ class B200Engine:
         """A non-blocking stream of the engine's own (several engines on one GPU then overlap: ny_b200.pool)."""
         self._L.nyb200_use_own_stream.argtypes = [C.c_void_p]
         self._check(self._L.nyb200_use_own_stream(self._h))
+
+    def set_reserved_sms(self, n: int):
+        """SMs the persistent kernels leave to a collective that runs beside them on another stream (default 0)."""
+        self._L.nyb200_set_reserved_sms.argtypes = [C.c_void_p, C.c_int32]
+        self._check(self._L.nyb200_set_reserved_sms(self._h, int(n)))
 
     def set_path(self, path: int):
         self._check(self._L.nyb200_set_path(self._h, path))
