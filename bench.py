@@ -535,6 +535,8 @@ def run_ours(args, rank, world, local_rank):
                                "capture (profiles/traffic.json)") if traffic is not None else "no capture at this batch size on record",
             "kernel": kernel, "kernel_ms": k_ms, "kernel_algorithmic_gflop": k_flops / 1e9,
             "peak_source": peak_src,
+            "kernel_timing": "CUDA events around each launch in the timed region with one batch in flight (with several in "
+                             "flight other batches' kernels run inside a launch's event pair); frac_step uses the reported step",
             "hbm_view": {"achieved_gbs": BYTES_PER_DOMAIN * D / ((fwd_ms + bwd_ms) / 1e3) / 1e9 if (fwd_ms + bwd_ms) > 0 else None,
                          "peak_gbs": peaks["hbm_gbs"]},
             "phase_ms": {"forward": fwd_ms, "backward": bwd_ms, "fused_chain": chain_ms, "per_layer_contractions": gemm_ms},
