@@ -33,6 +33,7 @@ struct ResidentFrontier {
     // root, records that arrived from outside, children of a round that did not optimise); every record behind has.
     float *alpha = nullptr;
     long no_alpha_front = 0;
+    bool optimistic = true;   // queue the decisions behind the bound without waiting (until a round is flagged)
 };
 
 void frontier_free(ResidentFrontier *f) {
@@ -284,25 +285,49 @@ static int32_t frontier_round_impl(nyb200_engine *e, int32_t batch, int32_t bran
     }
     b.valid = true;
     e->batch = b;
-    if (optimise) NYB_TRY(optimize_batch(e, *cfg));
-    else NYB_TRY(run_batch_public(e));
-    NYB_TRY(finish_batch_public(e));   // synchronises; re-evaluates flagged domains in binary64
     NYB_WS(done, int *, e, "fr_done", (size_t)D * 4);
     NYB_WS(pos, int *, e, "fr_pos", (size_t)D * 4);
     NYB_WS(dr, int *, e, "br_relu", (size_t)D * 4);
     NYB_WS(dn, int *, e, "br_neuron", (size_t)D * 4);
     NYB_WS(dw, float *, e, "br_width", (size_t)D * 4);
-    static const int init_stats[6] = {0, 0, 0, 0, 0x7f800000, 0};   // +inf as float bits
-    NYB_CUDA(e, cudaMemcpyAsync(f->stats, init_stats, sizeof(init_stats), cudaMemcpyHostToDevice, st));
-    k_frontier_decide<<<(D + 255) / 256, 256, 0, st>>>(D, f->S, f->n_clauses, p.out_lo, p.flags, f->thr, f->owner, done, f->stats);
-    e->launches++;
-    if (branching == NYB200_BRANCH_BABSR) NYB_TRY(babsr_select(e, *net, e->batch, p, dr, dn, dw, nullptr));
-    else launch_select_branch(e, nv, D, p.pre_lo, p.pre_hi, p.code, dr, dn, dw, branching);
-    k_frontier_scan<<<1, 1024, 0, st>>>(D, done, dr, p.nsplits, pos, f->stats);
-    e->launches++;
     int hs[6];
-    NYB_CUDA(e, cudaMemcpyAsync(hs, f->stats, sizeof(hs), cudaMemcpyDeviceToHost, st));
-    NYB_CUDA(e, cudaStreamSynchronize(st));
+    // decisions, split neurons, the open domains' positions and the round's counters, read with one synchronisation
+    auto evaluate = [&]() -> int {
+        static const int init_stats[6] = {0, 0, 0, 0, 0x7f800000, 0};   // +inf as float bits
+        NYB_CUDA(e, cudaMemcpyAsync(f->stats, init_stats, sizeof(init_stats), cudaMemcpyHostToDevice, st));
+        k_frontier_decide<<<(D + 255) / 256, 256, 0, st>>>(D, f->S, f->n_clauses, p.out_lo, p.flags, f->thr, f->owner, done, f->stats);
+        e->launches++;
+        if (branching == NYB200_BRANCH_BABSR) NYB_TRY(babsr_select(e, *net, e->batch, p, dr, dn, dw, nullptr));
+        else launch_select_branch(e, nv, D, p.pre_lo, p.pre_hi, p.code, dr, dn, dw, branching);
+        k_frontier_scan<<<1, 1024, 0, st>>>(D, done, dr, p.nsplits, pos, f->stats);
+        e->launches++;
+        NYB_CUDA(e, cudaMemcpyAsync(hs, f->stats, sizeof(hs), cudaMemcpyDeviceToHost, st));
+        NYB_CUDA(e, cudaStreamSynchronize(st));
+        return NYB200_OK;
+    };
+    if (optimise) {
+        NYB_TRY(optimize_batch(e, *cfg));
+        NYB_TRY(finish_batch_public(e));   // synchronises; folds a binary64 re-evaluation into the best bounds if flagged
+        NYB_TRY(evaluate());
+    } else if (f->optimistic) {
+        // The decisions are queued behind the bound without waiting for it.  The run's last kernel has published the
+        // pipeline error word and the number of domains flagged for the binary64 re-evaluation to mapped host memory
+        // by the time the counters have arrived; a flagged round pays for a second pass, and the next round waits for
+        // its bound before it decides (searches on narrow boxes flag most rounds).
+        NYB_TRY(run_batch_public(e));
+        NYB_TRY(evaluate());
+        const volatile int *sw = e->status_host;
+        if (sw && (sw[1] != 0 || sw[2] > 0)) {
+            NYB_TRY(finish_batch_public(e));
+            NYB_TRY(evaluate());
+            f->optimistic = false;
+        }
+    } else {
+        NYB_TRY(run_batch_public(e));
+        NYB_TRY(finish_batch_public(e));   // synchronises; re-evaluates flagged domains in binary64
+        NYB_TRY(evaluate());
+        f->optimistic = e->batch.refined == 0;
+    }
     const int n_open = hs[0], n_stuck = hs[3], deepest = hs[5];
     stats_out[1] = hs[1]; stats_out[2] = hs[2]; stats_out[3] = n_stuck; stats_out[5] = deepest;
     memcpy(min_lower, &hs[4], 4);
