@@ -392,3 +392,26 @@ def test_batches_in_flight_on_an_engine_pool_match_a_single_engine(oracle):
     with pytest.raises(EngineError):
         pool.bound_batches(h, bad)
     pool.close()
+
+
+def test_persistent_kernels_with_reserved_sms_return_the_same_bits(oracle):
+    """nyb200_set_reserved_sms: the full-width persistent kernels leave SMs to a concurrent collective; the tiles are
+    dealt to fewer CTAs, every tile is computed as before."""
+    from ny_b200 import B200Engine
+
+    wl = W.config_mlp_bab(seed=23, hidden=256, depth=4, n_in=300, eps=0.01, n_fix=6)
+    onet = oracle.Net(wl.net.weights, wl.net.biases)
+    rl, ru = oracle.ibp_forward(onet, wl.in_lo, wl.in_hi)
+    splits, ns = W.draw_domains(wl, rl, ru, 1500)
+    eng = B200Engine(0)
+    nid = eng.register_network(wl.net)
+    want = eng.bab_bound_batch(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, splits, ns)
+    for n in (1, 2, 40):
+        eng.set_reserved_sms(n)
+        got = eng.bab_bound_batch(nid, wl.spec, wl.in_lo, wl.in_hi, rl, ru, splits, ns)
+        assert all(np.array_equal(a, b) for a, b in zip(got, want))
+    from ny_b200 import EngineError
+
+    with pytest.raises(EngineError):
+        eng.set_reserved_sms(-1)
+    eng.close()
