@@ -836,7 +836,8 @@ class B200Engine:
     def frontier_upload(self, splits, n_splits):
         """Replaces the device frontier's contents by host records (splits [n, depth], n_splits [n])."""
         ns = np.ascontiguousarray(n_splits, np.int32)
-        splits = np.ascontiguousarray(np.asarray(splits, SPLIT_DTYPE).reshape(len(ns), -1))
+        splits = np.asarray(splits, SPLIT_DTYPE)
+        splits = np.ascontiguousarray(splits.reshape(len(ns), -1)) if len(ns) else np.zeros((0, 1), SPLIT_DTYPE)
         fn = self._L.nyb200_frontier_upload
         fn.argtypes = [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p]
         self._check(fn(self._h, len(ns), int(splits.shape[1]) if len(ns) else 1, C.c_void_p(splits.ctypes.data), C.c_void_p(ns.ctypes.data)))

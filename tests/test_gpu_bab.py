@@ -462,3 +462,37 @@ def test_device_resident_optimising_search_with_warm_starts_runs_the_host_loop_s
     full = bab.verify_resident(eng, nid, net, p, batch=32, max_rounds=400, branching=branching, optimize_iterations=6)
     assert full.status == "verified" and (plain.status != "verified" or full.domains_bounded <= plain.domains_bounded)
     eng.release_network(nid)
+
+
+@pytest.mark.gpu
+def test_device_frontier_refuses_what_it_cannot_hold(eng):
+    """Capacity, depth and argument checks of the frontier's transfer calls: refused with a status, nothing overrun."""
+    import torch
+
+    from ny_b200 import SPLIT_DTYPE, EngineError
+
+    wl = W.config_mlp_bab(seed=83, hidden=16, depth=3, n_in=6, n_out=4, eps=0.25, n_fix=0)
+    nid = eng.register_network(wl.net)
+    root_lo, _, il, iu = eng.crown_bounds(nid, wl.spec, wl.in_lo, wl.in_hi)
+    p = formats.Property(wl.in_lo, wl.in_hi, [[formats.Atom(-wl.spec[0], float(root_lo[0][0]) + 1.0)]])
+    spec, thr, owner = bab._rows(p)
+    with pytest.raises(EngineError):
+        eng.frontier_count()                       # no frontier yet
+    eng.frontier_create(nid, spec, thr, owner, 1, p.in_lo, p.in_hi, il[0], iu[0], max_depth=4, capacity=6)
+    sp = torch.zeros((8, 16), dtype=torch.int32, device="cuda:0")
+    ns = torch.ones((8,), dtype=torch.int32, device="cuda:0")
+    with pytest.raises(EngineError):
+        eng.frontier_give(6, sp.data_ptr(), ns.data_ptr())          # 1 + 6 > capacity
+    eng.frontier_give(5, sp.data_ptr(), ns.data_ptr())
+    assert eng.frontier_count() == 6
+    with pytest.raises(EngineError):
+        eng.frontier_upload(np.zeros((2, 5), SPLIT_DTYPE), np.array([1, 5], np.int32))     # deeper than max_depth
+    with pytest.raises(EngineError):
+        eng.frontier_upload(np.zeros((2, 3), SPLIT_DTYPE), np.array([1, 4], np.int32))     # length beyond the row
+    with pytest.raises(EngineError):
+        eng.frontier_upload(np.zeros((7, 2), SPLIT_DTYPE), np.ones(7, np.int32))           # more than capacity
+    assert eng.frontier_count() == 6               # refused calls left the contents alone
+    eng.frontier_upload(np.zeros((0, 1), SPLIT_DTYPE), np.zeros(0, np.int32))
+    assert eng.frontier_count() == 0 and eng.frontier_download(4)[1].shape == (0,)
+    eng.frontier_destroy()
+    eng.release_network(nid)
