@@ -539,6 +539,9 @@ def run_ours(args, rank, world, local_rank):
                              "flight other batches' kernels run inside a launch's event pair); frac_step uses the reported step",
             "hbm_view": {"achieved_gbs": BYTES_PER_DOMAIN * D / ((fwd_ms + bwd_ms) / 1e3) / 1e9 if (fwd_ms + bwd_ms) > 0 else None,
                          "peak_gbs": peaks["hbm_gbs"]},
+            # every algorithmic product is issued as three TF32 products (Ah*Wh + Ah*Wl + Al*Wh): what the tensor pipe does
+            "tensor_view": ({"issued_tflops": 3.0 * achieved, "frac_of_peak": 3.0 * achieved / peak_tf}
+                            if achieved and eng_path_name(eng) != "f64" else None),
             "phase_ms": {"forward": fwd_ms, "backward": bwd_ms, "fused_chain": chain_ms, "per_layer_contractions": gemm_ms},
         }
         line = {
