@@ -815,7 +815,17 @@ def run_search(args, rank, world, local_rank):
 
     resident = bool(args.resident)
 
+    pool = handle = None
+    if resident and dist is None and args.search_engines > 1:
+        from ny_b200.pool import EnginePool
+
+        pool = EnginePool(local_rank, args.search_engines, lambda e: e.set_path(E.PATH_TF32X3 if args.path == "tf32x3" else E.PATH_F64))
+        handle = pool.register_network(wl.net)
+
     def search():
+        if pool is not None:   # one device frontier per engine of the pool, their rounds overlapping on the GPU
+            return bab.verify_resident_pool(pool, handle, wl.net, prop, batch=batch, max_rounds=rounds, branching=1, pgd_restarts=64,
+                                            pgd_steps=10, optimize_iterations=opt_it, max_domains=1 << 18)
         if resident:   # the open domain set stays on the device: one call per round
             return bab.verify_resident(eng, nid, wl.net, prop, batch=batch, max_rounds=rounds, branching=1, pgd_restarts=64,
                                        pgd_steps=10, optimize_iterations=opt_it, max_domains=1 << 18, dist=dist, dist_device=dev)
@@ -832,6 +842,7 @@ def run_search(args, rank, world, local_rank):
     sampler = ClockSampler(local_rank)
     sampler.start()
     l0 = eng.launch_count()
+    l0_pool = sum(e.launch_count() for e in pool.engines) if pool is not None else 0
     barrier()
     t0 = time.perf_counter()
     bounded = 0
@@ -844,6 +855,8 @@ def run_search(args, rank, world, local_rank):
     barrier()
     dt = time.perf_counter() - t0
     launches = eng.launch_count() - l0
+    if pool is not None:
+        launches = sum(e.launch_count() for e in pool.engines) - l0_pool
     clocks = sampler.stop()
     if dist is not None:
         t = torch.tensor([dt], device=dev, dtype=torch.float64)
@@ -865,14 +878,18 @@ def run_search(args, rank, world, local_rank):
                                    + (f"{opt_it} optimisation iterations per domain with warm start" if opt_it > 1 else "one bound per domain")
                                    + ", attack and root bound included",
                        "parallelism": f"frontier sharded x{world}",
-                       "frontier": "device-resident (nyb200_frontier_round: pop, bound, prune, branch, push per call)" if resident
+                       "frontier": (f"device-resident, {args.search_engines} engines on the GPU with a frontier each, up to {batch} domains "
+                                    "per engine and round, levelled ring to ring") if pool is not None
+                                   else "device-resident (nyb200_frontier_round: pop, bound, prune, branch, push per call)" if resident
                                    else "host (numpy blocks; upload of the children's split lists every round)",
                        "timing": "wall clock around the search calls, max over ranks", "status": r.status,
                        "domains_per_search": r.domains_bounded, "open_at_stop": r.open_domains},
-            "rebalance": moved if world > 1 else None,
+            "rebalance": moved if (world > 1 or pool is not None) else None,
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": None, "d2h_bytes_per_step": None, "ms_per_step": dt * 1e3 / args.steps},
             "gpu_launches": int(launches), "clocks": clocks,
         })
+    if pool is not None:
+        pool.close()
     eng.close()
     if dist is not None:
         dist.destroy_process_group()
@@ -991,6 +1008,8 @@ def main():
                          "cnn: the convolutional case (both 1 GPU)")
     ap.add_argument("--resident", type=int, default=1,
                     help="bab-search on one GPU: 1 keeps the frontier on the device (default), 0 runs the host loop")
+    ap.add_argument("--search-engines", type=int, default=2,
+                    help="bab-search on one GPU: engines (device frontiers) sharing the search, their rounds overlapping (1: a single frontier)")
     ap.add_argument("--search-iterations", type=int, default=0,
                     help="bab-search: optimisation iterations per domain (0 = one bound per domain, the reference's throughput default)")
     ap.add_argument("--in-flight", type=int, default=3,

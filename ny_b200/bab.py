@@ -568,6 +568,88 @@ def verify_resident(eng, net_id, net, prop: Property, *, batch: int = 1024, max_
     return res
 
 
+def verify_resident_pool(pool, net_handle, net, prop: Property, *, batch: int = 1024, max_rounds: int = 64,
+                         max_domains: int = 1 << 20, pgd_restarts: int = 256, pgd_steps: int = 50, branching: int = 1,
+                         timeout_s: float | None = None, optimize_iterations: int = 0) -> VerifyResult:
+    """verify_resident over the engines of an EnginePool (ny_b200.pool) on one GPU: one device frontier per engine, the
+    root on the first, every engine bounding up to `batch` of its domains per round on its own stream and host thread,
+    the shards levelled after the round by moving records from ring to ring on the device.  A round of a search is a
+    chain of short launches with the host in between, so the engines' rounds overlap the way independent batches do.
+    Same verdict as verify_resident and, when the search closes, the same domains; `batch` is per engine."""
+    from concurrent.futures import ThreadPoolExecutor
+
+    import torch
+
+    from . import sharding
+
+    t0 = time.time()
+    if not prop.violation:
+        return VerifyResult("verified")
+    spec, thr, owner = _rows(prop)
+    n_clauses = len(prop.violation)
+    engines = pool.engines
+    nids = pool._nets[net_handle]
+    world = len(engines)
+    ce = attack(engines[0], nids[0], net, prop, pgd_restarts, pgd_steps)
+    if ce is not None:
+        return VerifyResult("violated", ce[0], ce[1])
+    rlo, _, inter_lo, inter_hi = engines[0].crown_bounds(nids[0], spec, prop.in_lo, prop.in_hi)
+    res = VerifyResult("unknown", root_lower=rlo[0].copy(), domains_bounded=1)
+    if _verified_mask(rlo, thr, owner, n_clauses)[0]:
+        res.status = "verified"
+        return res
+    max_depth = max_rounds + 2
+    device = torch.device("cuda", torch.cuda.current_device())
+    for e, nid in zip(engines, nids):
+        e.frontier_create(nid, spec, thr, owner, n_clauses, prop.in_lo, prop.in_hi, inter_lo[0], inter_hi[0],
+                          max_depth=max_depth, capacity=min(2 * max_domains + 2 * batch, 1 << 22))
+    exchange = {"exchanges": 0, "records_moved": 0, "bytes_moved": 0}
+
+    def one_round(i):
+        if counts[i] == 0:
+            return (0, 0, 0, 0, 0, 0, float("inf"))
+        if optimize_iterations > 1:
+            return engines[i].frontier_round_optimized(batch, branching, optimize_iterations, 0.1, 0.05)
+        return engines[i].frontier_round(batch, branching)
+
+    try:
+        scratch = torch.empty((4 * max_depth + 1,), dtype=torch.int32, device=device)
+        for e in engines[1:]:     # the root belongs to the first engine
+            e.frontier_take(1, scratch.data_ptr(), scratch[4 * max_depth:].data_ptr())
+        counts = [1] + [0] * (world - 1)
+        total_open = 1
+        with ThreadPoolExecutor(max_workers=world) as workers:
+            while total_open > 0 and res.rounds < max_rounds:
+                if timeout_s is not None and time.time() - t0 > timeout_s:
+                    res.status = "timeout"
+                    break
+                stats = list(workers.map(one_round, range(world)))
+                counts = [st[4] if counts[i] else 0 for i, st in enumerate(stats)]
+                total_open = sum(counts)
+                res.rounds += 1
+                res.domains_bounded += sum(st[0] for st in stats)
+                if any(st[3] for st in stats) or total_open > max_domains:
+                    break
+                for src, dst, n in sharding.plan_rebalance(counts):
+                    sp = torch.empty((n, 4 * max_depth), dtype=torch.int32, device=device)
+                    ns = torch.empty((n,), dtype=torch.int32, device=device)
+                    engines[src].frontier_take(n, sp.data_ptr(), ns.data_ptr())
+                    engines[dst].frontier_give(n, sp.data_ptr(), ns.data_ptr())
+                    counts[src] -= n
+                    counts[dst] += n
+                    exchange["records_moved"] += n
+                    exchange["bytes_moved"] += n * (4 * max_depth + 1) * 4
+                    exchange["exchanges"] += 1
+        res.open_domains = total_open
+        res.exchange = exchange
+        if total_open == 0 and res.status == "unknown":
+            res.status = "verified"
+    finally:
+        for e in engines:
+            e.frontier_destroy()
+    return res
+
+
 def _rebalance(frontier: "Frontier", dist, device, sharding, stats=None):
     """Levels the ranks' shards.  The shard sizes are gathered first and nothing else happens while they are level;
     otherwise the histories are padded to the deepest one of any rank and moved point to point, the warm-start

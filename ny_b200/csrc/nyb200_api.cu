@@ -84,6 +84,7 @@ void nyb200_destroy(nyb200_engine *e) {
     if (e->stage) cudaFreeHost(e->stage);
     if (e->stage_in_done) cudaEventDestroy(e->stage_in_done);
     if (e->frontier) nyb::frontier_free(e->frontier);
+    if (e->frontier_spare) nyb::frontier_free(e->frontier_spare);
     if (e->own_stream) cudaStreamDestroy(e->own_stream);
     for (int i = 0; i < 3; ++i) if (e->timing.ev[i]) cudaEventDestroy(e->timing.ev[i]);
     for (cudaEvent_t ev : e->timing.kev) cudaEventDestroy(ev);
@@ -135,6 +136,7 @@ int32_t nyb200_clear_working_set(nyb200_engine *e) {
     for (auto &kv : e->ws) if (kv.second.p) cudaFree(kv.second.p);
     e->ws.clear();
     e->batch = Batch();
+    if (e->frontier_spare) { nyb::frontier_free(e->frontier_spare); e->frontier_spare = nullptr; }
     // networks registered on behalf of the reference-shaped calls (their weight cache)
     for (auto &kv : e->boundary_nets) {
         auto it = e->nets.find(kv.second);

@@ -33,6 +33,7 @@ struct ResidentFrontier {
     // root, records that arrived from outside, children of a round that did not optimise); every record behind has.
     float *alpha = nullptr;
     long no_alpha_front = 0;
+    size_t buf_bytes = 0, ns_bytes = 0, thr_bytes = 0, consts_bytes = 0, alpha_bytes = 0;   // what the arrays can hold
     bool optimistic = true;   // queue the decisions behind the bound without waiting (until a round is flagged)
 };
 
@@ -191,22 +192,34 @@ int32_t nyb200_frontier_create(nyb200_engine *e, int32_t net_id, const float *sp
     if (max_depth <= 0 || capacity < 2) return set_err(e, NYB200_ERR_SHAPE, "max_depth and capacity must be positive");
     for (int s = 0; s < S; ++s)
         if (owner[s] < 0 || owner[s] >= n_clauses) return set_err(e, NYB200_ERR_INVALID, "row owner out of range");
+    // A search per property creates and destroys its frontier; the arrays of the last one are kept and serve again when
+    // they are large enough (an allocation or a release of this size synchronises the device and costs milliseconds).
     if (e->frontier) { frontier_free(e->frontier); e->frontier = nullptr; }
-    ResidentFrontier *f = new ResidentFrontier();
+    ResidentFrontier *f = e->frontier_spare ? e->frontier_spare : new ResidentFrontier();
+    e->frontier_spare = nullptr;
     f->net_id = net_id; f->S = S; f->maxd = max_depth; f->n_clauses = n_clauses; f->cap = capacity;
-    if (cudaMalloc(&f->buf, (size_t)capacity * max_depth * sizeof(nyb200_split)) != cudaSuccess ||
-        cudaMalloc(&f->ns, (size_t)capacity * 4) != cudaSuccess || cudaMalloc(&f->stats, 64) != cudaSuccess ||
-        cudaMalloc(&f->thr, (size_t)S * 4) != cudaSuccess || cudaMalloc(&f->owner, (size_t)S * 4) != cudaSuccess) {
+    f->bounded = 0; f->optimistic = true;
+    f->n_spec = (size_t)S * nv.dims[nv.L]; f->n_box = (size_t)nv.dims[0]; f->n_inh = (size_t)nv.n_pre;
+    auto fit = [&](void **ptr, size_t *have, size_t need) -> bool {
+        if (*ptr && *have >= need) return true;
+        if (*ptr) { cudaFree(*ptr); *ptr = nullptr; *have = 0; }
+        if (cudaMalloc(ptr, need) != cudaSuccess) return false;
+        *have = need;
+        return true;
+    };
+    const size_t thr_need = (size_t)kMaxRowsF * 4;
+    if (f->alpha && f->alpha_bytes < (size_t)capacity * nv.nps * 4) { cudaFree(f->alpha); f->alpha = nullptr; f->alpha_bytes = 0; }
+    if (!fit((void **)&f->buf, &f->buf_bytes, (size_t)capacity * max_depth * sizeof(nyb200_split)) ||
+        !fit((void **)&f->ns, &f->ns_bytes, (size_t)capacity * 4) ||
+        (!f->stats && cudaMalloc(&f->stats, 64) != cudaSuccess) ||
+        !fit((void **)&f->thr, &f->thr_bytes, thr_need) ||
+        (!f->owner && cudaMalloc(&f->owner, thr_need) != cudaSuccess) ||
+        !fit((void **)&f->consts, &f->consts_bytes, (f->n_spec + 2 * f->n_box + 2 * f->n_inh) * 4)) {
         frontier_free(f);
         return set_err(e, NYB200_ERR_OOM, "device allocation failed for the frontier");
     }
     NYB_CUDA(e, cudaMemcpy(f->thr, thresholds, (size_t)S * 4, cudaMemcpyHostToDevice));
     NYB_CUDA(e, cudaMemcpy(f->owner, owner, (size_t)S * 4, cudaMemcpyHostToDevice));
-    f->n_spec = (size_t)S * nv.dims[nv.L]; f->n_box = (size_t)nv.dims[0]; f->n_inh = (size_t)nv.n_pre;
-    if (cudaMalloc(&f->consts, (f->n_spec + 2 * f->n_box + 2 * f->n_inh) * 4) != cudaSuccess) {
-        frontier_free(f);
-        return set_err(e, NYB200_ERR_OOM, "device allocation failed for the frontier");
-    }
     {
         float *c = f->consts;
         NYB_CUDA(e, cudaMemcpy(c, spec, f->n_spec * 4, cudaMemcpyHostToDevice)); c += f->n_spec;
@@ -225,7 +238,13 @@ int32_t nyb200_frontier_create(nyb200_engine *e, int32_t net_id, const float *sp
 void nyb200_frontier_destroy(nyb200_engine *e) {
     if (!e) return;
     std::lock_guard<std::mutex> g(e->mu);
-    if (e->frontier) { cudaSetDevice(e->device); cudaStreamSynchronize(e->stream); frontier_free(e->frontier); e->frontier = nullptr; }
+    if (e->frontier) {
+        cudaSetDevice(e->device);
+        cudaStreamSynchronize(e->stream);
+        if (e->frontier_spare) frontier_free(e->frontier_spare);
+        e->frontier_spare = e->frontier;   // its arrays serve the next frontier of this engine
+        e->frontier = nullptr;
+    }
 }
 
 // stats out: [0] domains bounded this round, [1] verified, [2] infeasible, [3] stuck (undecided, nothing left to
@@ -253,6 +272,7 @@ static int32_t frontier_round_impl(nyb200_engine *e, int32_t batch, int32_t bran
     if (optimise && !f->alpha) {
         if (cudaMalloc(&f->alpha, (size_t)f->cap * nv.nps * 4) != cudaSuccess)
             return set_err(e, NYB200_ERR_OOM, "device allocation failed for the frontier's slopes (capacity x neurons)");
+        f->alpha_bytes = (size_t)f->cap * nv.nps * 4;
     }
     // warm start only when every domain of the batch has slopes of its own (the host loop's rule)
     const bool warm = optimise && f->no_alpha_front == 0;

@@ -142,6 +142,7 @@ struct nyb200_engine {
     // [0] sequence number of the newest completed run, [1] pipeline error word seen by any run since the last finish,
     // [2] domains flagged for the binary64 re-evaluation by any run since the last finish.  See nyb200_batch_poll.
     struct ResidentFrontier *frontier = nullptr;   // nyb200_frontier_* (nyb200_frontier.cu)
+    struct ResidentFrontier *frontier_spare = nullptr;   // the last destroyed frontier's device arrays, reused by the next
     // Pinned host staging: small inputs of an upload are gathered here so that their copies are truly asynchronous,
     // and the results of a run are fetched here ahead of the one synchronisation that ends it (a copy into pageable
     // memory is staged by the driver and blocks).  in: [0, kStageIn), out: the rest (grow-only).

@@ -496,3 +496,33 @@ def test_device_frontier_refuses_what_it_cannot_hold(eng):
     assert eng.frontier_count() == 0 and eng.frontier_download(4)[1].shape == (0,)
     eng.frontier_destroy()
     eng.release_network(nid)
+
+
+@pytest.mark.gpu
+def test_search_shared_by_the_engines_of_a_pool(eng):
+    """verify_resident_pool: one device frontier per engine of an EnginePool on the same GPU, rounds on their own
+    streams and threads, shards levelled ring to ring.  Against the single-frontier search: the same verdict and, when
+    the search closes, the same domains bounded in fewer rounds; plain and optimising."""
+    from ny_b200.pool import EnginePool
+
+    wl = W.config_mlp_bab(seed=83, hidden=24, depth=3, n_in=4, n_out=3, eps=0.2, n_fix=0)
+    nid = eng.register_network(wl.net)
+    root_lo, _, _, _ = eng.crown_bounds(nid, wl.spec, wl.in_lo, wl.in_hi)
+    mn = W.sample_min_margin(wl, 200000, 3)
+    s = int(np.argmax(mn - root_lo[0]))
+    pool = EnginePool(0, 3)
+    h = pool.register_network(wl.net)
+    for frac, it in ((0.5, 0), (0.9, 6)):
+        p = formats.Property(wl.in_lo, wl.in_hi, [[formats.Atom(-wl.spec[s], float(root_lo[0][s] + frac * (mn[s] - root_lo[0][s])))]])
+        one = bab.verify_resident(eng, nid, wl.net, p, batch=2, max_rounds=300, optimize_iterations=it)
+        many = bab.verify_resident_pool(pool, h, wl.net, p, batch=2, max_rounds=300, optimize_iterations=it)
+        assert one.status == many.status == "verified"
+        assert many.rounds < one.rounds and many.exchange["records_moved"] > 0
+        if it == 0:   # without warm starts the order of a complete search does not change what it bounds
+            assert many.domains_bounded == one.domains_bounded
+    # a search that runs out of rounds reports what is left on all engines
+    p = formats.Property(wl.in_lo, wl.in_hi, [[formats.Atom(-wl.spec[s], float(root_lo[0][s] + 0.97 * (mn[s] - root_lo[0][s])))]])
+    cut = bab.verify_resident_pool(pool, h, wl.net, p, batch=4, max_rounds=6)
+    assert cut.status == "unknown" and cut.open_domains > 0 and cut.rounds == 6
+    pool.close()
+    eng.release_network(nid)
