@@ -361,6 +361,7 @@ def run_ours(args, rank, world, local_rank):
         e_i.set_path(E.PATH_TF32X3 if args.path == "tf32x3" else E.PATH_F64)
         e_i.set_fusion(bool(args.fusion))
         e_i.set_reserved_sms(reserve)
+        e_i.set_launch_overlap(False)
         n_i = e_i.register_network(wl.net)
         d_i = W.draw_domains(wl, rl, ru, D, first=(world * i + rank) * D)
         e_i.batch_upload(n_i, wl.spec, wl.in_lo, wl.in_hi, rl, ru, d_i[0], d_i[1], mode=1)
@@ -368,6 +369,7 @@ def run_ours(args, rank, world, local_rank):
     block_ms_multi = None
     launches_multi = 0
     if B > 1:
+        eng.set_launch_overlap(False)   # dependent launches pay with one batch in flight only (nyb200_set_launch_overlap)
         mins = [min_t] + [torch.as_tensor(_DevPtr(e.batch_min_lower_device(), 1), device=f"cuda:{local_rank}") for e in engs[1:]]
         slots = [[torch.empty(1, device=f"cuda:{local_rank}") for _ in range(2)] for _ in range(B)]
         done = [[None, None] for _ in range(B)]
@@ -425,6 +427,7 @@ def run_ours(args, rank, world, local_rank):
         launches_multi = (sum(e.launch_count() for e in engs) - l0) // blocks
         lo_again = eng.batch_download()[0]
         assert np.array_equal(lo_again, lo), "a batch's bounds changed with other batches in flight"
+        eng.set_launch_overlap(True)
 
     # ---- end-to-end: host buffers in pinned memory through the C-ABI call ------------------
     def pinned(a):

@@ -101,6 +101,13 @@ int32_t nyb200_set_stream(nyb200_engine *e, void *cuda_stream) {
     return NYB200_OK;
 }
 
+int32_t nyb200_set_launch_overlap(nyb200_engine *e, int32_t on) {
+    if (!e) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    e->launch_overlap = on != 0;
+    return NYB200_OK;
+}
+
 int32_t nyb200_set_reserved_sms(nyb200_engine *e, int32_t n) {
     if (!e || n < 0 || n > 64) return NYB200_ERR_INVALID;
     std::lock_guard<std::mutex> g(e->mu);
@@ -783,7 +790,7 @@ int run_batch(nyb200_engine *e) {
     {
         const bool tensor = e->path == NYB200_PATH_TF32X3;
         int *acc = (int *)ws_get(e, "status_acc", 256);
-        launch_pdl(k_publish_status, dim3(1), dim3(32), 0, e->stream, tensor ? (const int *)ws_get(e, "umma_err", 256) : (const int *)nullptr,
+        launch_pdl(k_publish_status, dim3(1), dim3(32), 0, e, tensor ? (const int *)ws_get(e, "umma_err", 256) : (const int *)nullptr,
                    tensor && e->refine_tol > 0.f ? (const int *)p.min_lower + 4 : (const int *)nullptr, acc, (volatile int *)e->status_dev,
                    ++e->run_seq);
         e->launches++;

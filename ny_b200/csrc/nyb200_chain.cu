@@ -603,8 +603,8 @@ int launch_chain(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int L
     const int grid = tiles < sms ? tiles : sms;
     // a 128-row tile spans at most (BM - 2) / R + 2 domains; the table ring holds MAXD of them
     const bool staged = (BM - 2) / b.R + 2 <= MAXD;
-    cudaError_t ls = staged ? launch_pdl(k_chain<4, true>, dim3(grid), dim3(Cfg<4>::THREADS), SMEM_BYTES, e->stream, P)
-                            : launch_pdl(k_chain<4, false>, dim3(grid), dim3(Cfg<4>::THREADS), SMEM_BYTES, e->stream, P);
+    cudaError_t ls = staged ? launch_pdl(k_chain<4, true>, dim3(grid), dim3(Cfg<4>::THREADS), SMEM_BYTES, e, P)
+                            : launch_pdl(k_chain<4, false>, dim3(grid), dim3(Cfg<4>::THREADS), SMEM_BYTES, e, P);
     if (ls != cudaSuccess) return set_err(e, NYB200_ERR_INTERNAL, "fused chain launch failed");
     e->launches++;
     return NYB200_OK;

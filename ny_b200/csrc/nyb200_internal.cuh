@@ -123,6 +123,7 @@ struct nyb200_engine {
     int device = 0;
     cudaStream_t stream = nullptr;
     int reserve_sms = 0;                          // see nyb200_set_reserved_sms
+    bool launch_overlap = true;                   // see nyb200_set_launch_overlap
     cudaStream_t own_stream = nullptr;            // created by nyb200_use_own_stream, destroyed with the engine
     int path = NYB200_PATH_TF32X3;
     float refine_tol = 5e-5f;  // see nyb200_set_refine_tolerance
@@ -160,19 +161,21 @@ struct nyb200_engine {
 // before its first access to memory that any earlier kernel of the stream writes or reads, which returns once the
 // predecessor has completed and its writes are visible.  What overlaps is the launch latency, the scheduling of the
 // CTAs and whatever the kernel does before pdl_wait (barrier set-up, tensor-memory allocation).  Both calls do nothing
-// in a kernel that was launched the ordinary way.
+// in a kernel that was launched the ordinary way.  With several engines on one GPU the early-scheduled CTAs of a
+// full-width kernel hold their SMs' shared memory while they wait, which keeps other engines' kernels off those SMs:
+// nyb200_set_launch_overlap(e, 0) launches the ordinary way.
 #ifdef __CUDACC__
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args) {
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, nyb200_engine *e, Args &&...args) {
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
-    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = e->stream;
     cudaLaunchAttribute at[1];
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = at; cfg.numAttrs = 1;
+    cfg.attrs = at; cfg.numAttrs = e->launch_overlap ? 1 : 0;   // off: an ordinary launch (see nyb200_set_launch_overlap)
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 #endif

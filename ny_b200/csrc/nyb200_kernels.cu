@@ -832,7 +832,7 @@ void launch_ibp_linear(nyb200_engine *e, const NetView &nv, int k, int Deff, con
                        long in_dstride, float *raw_lo, float *raw_hi, float *q, long out_dstride) {
     int n_in = nv.dims[k], n_out = nv.dims[k + 1];
     if (Deff == 1) {
-        launch_pdl(k_ibp_linear_vec, dim3((n_out * 32 + 255) / 256), dim3(256), 0, e->stream, n_in, n_out, (const float *)nv.W[k],
+        launch_pdl(k_ibp_linear_vec, dim3((n_out * 32 + 255) / 256), dim3(256), 0, e, n_in, n_out, (const float *)nv.W[k],
                    (const float *)nv.b[k], zl, zu, raw_lo + nv.pre_off[k], raw_hi + nv.pre_off[k], q + nv.pre_off[k]);
         NYB_COUNT(e);
         return;
@@ -859,7 +859,7 @@ void launch_ibp_finish(nyb200_engine *e, const NetView &nv, int k, int D, int mo
                        float *q, float fwd_tol, float *cj, float cj_eps, float cj_kappa) {
     long total = (long)D * nv.dims[k + 1];
     int last = (k == nv.L - 1);
-    launch_pdl(k_ibp_finish, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, e->stream, nv, k, D, mode, last, raw_lo, raw_hi,
+    launch_pdl(k_ibp_finish, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, e, nv, k, D, mode, last, raw_lo, raw_hi,
                raw_dstride, inh_lo, inh_hi, inh_dstride, code, sbeta, alpha, pre_lo, pre_hi, zl, zu, tab, zabs, flags, F, ldf, eps, q, fwd_tol, cj,
                cj_eps, cj_kappa);
     NYB_COUNT(e);
@@ -981,16 +981,16 @@ __global__ void k_concretize_fused(int M, int R, int S, int slots, const double 
 void launch_concretize_fused(nyb200_engine *e, int M, int R, int S, int slots, const double *part, const int *bad,
                              const double *rb, const double *rabs, const double *rpen, int *flags, float *out_lo,
                              float *out_hi, float *min_lower, float loose_tol) {
-    launch_pdl(k_concretize_fused, dim3((unsigned)((M + 255) / 256)), dim3(256), 0, e->stream, M, R, S, slots, part, bad, rb, rabs,
+    launch_pdl(k_concretize_fused, dim3((unsigned)((M + 255) / 256)), dim3(256), 0, e, M, R, S, slots, part, bad, rb, rabs,
                rpen, out_lo, out_hi);
     NYB_COUNT(e);
     int D = M / R;
     if (loose_tol > 0.f) {
-        launch_pdl(k_count_loose, dim3((D + 255) / 256), dim3(256), 0, e->stream, D, S, R, (const float *)out_lo, (const float *)out_hi,
+        launch_pdl(k_count_loose, dim3((D + 255) / 256), dim3(256), 0, e, D, S, R, (const float *)out_lo, (const float *)out_hi,
                    rpen, flags, loose_tol, (int *)min_lower + 4);
         NYB_COUNT(e);
     }
-    launch_pdl(k_finalize, dim3((D * S + 255) / 256), dim3(256), 0, e->stream, D, S, (const int *)flags, out_lo, out_hi, min_lower);
+    launch_pdl(k_finalize, dim3((D * S + 255) / 256), dim3(256), 0, e, D, S, (const int *)flags, out_lo, out_hi, min_lower);
     NYB_COUNT(e);
 }
 

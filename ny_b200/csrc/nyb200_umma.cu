@@ -510,7 +510,7 @@ int launch_umma(nyb200_engine *e, const UmmaLayer &L, int M, const float *A, int
         tm_a = *(const CUtensorMap *)L.tm_hi;  // unused by the kernel in this form; any valid map
     }
     ConcFuse none;
-    if (launch_pdl(k_umma_tf32x3, dim3(grid), dim3(THREADS), SMEM_BYTES, e->stream, *(const CUtensorMap *)L.tm_hi,
+    if (launch_pdl(k_umma_tf32x3, dim3(grid), dim3(THREADS), SMEM_BYTES, e, *(const CUtensorMap *)L.tm_hi,
                    *(const CUtensorMap *)L.tm_lo, tm_a, A, lda, C, ldc, M, L.N, L.K, L.chain > 0 ? L.chain : chunk_stages_cfg(L.K), err,
                    a_plane, a_tma, cf ? *cf : none) != cudaSuccess)
         return set_err(e, NYB200_ERR_INTERNAL, "contraction kernel launch failed");

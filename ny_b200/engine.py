@@ -42,7 +42,7 @@ EXPORTS = [
     "nyb200_crown_bounds", "nyb200_batch_download_alpha_upper",
     "nyb200_batch_verdicts", "nyb200_gemm_f64", "nyb200_conv_transpose_2d", "nyb200_set_deadline_ns",
     "nyb200_batch_gradient", "nyb200_point_vjp_batched", "nyb200_crown_input_coeffs", "nyb200_batch_download_branch_scores",
-    "nyb200_set_error_channel", "nyb200_set_fusion", "nyb200_use_own_stream", "nyb200_set_reserved_sms", "nyb200_batch_download_opt_evaluations",
+    "nyb200_set_error_channel", "nyb200_set_fusion", "nyb200_use_own_stream", "nyb200_set_reserved_sms", "nyb200_set_launch_overlap", "nyb200_batch_download_opt_evaluations",
     "nyb200_crown_backward", "nyb200_crown_resnet_beta_batched", "nyb200_crown_resnet_beta_batched_adam", "nyb200_gemm_f64_triplet",
 ]
 
@@ -413,6 +413,11 @@ class B200Engine:
         """SMs the persistent kernels leave to a collective that runs beside them on another stream (default 0)."""
         self._L.nyb200_set_reserved_sms.argtypes = [C.c_void_p, C.c_int32]
         self._check(self._L.nyb200_set_reserved_sms(self._h, int(n)))
+
+    def set_launch_overlap(self, on: bool):
+        """Programmatic dependent launch of this engine's kernels (default on; off pays with several engines per GPU)."""
+        self._L.nyb200_set_launch_overlap.argtypes = [C.c_void_p, C.c_int32]
+        self._check(self._L.nyb200_set_launch_overlap(self._h, 1 if on else 0))
 
     def set_path(self, path: int):
         self._check(self._L.nyb200_set_path(self._h, path))

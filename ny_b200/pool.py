@@ -24,6 +24,8 @@ class EnginePool:
         for _ in range(n):
             e = B200Engine(device)
             e.use_own_stream()
+            if n > 1:
+                e.set_launch_overlap(False)   # early-scheduled CTAs of one engine would hold SMs another engine can use
             if configure is not None:
                 configure(e)
             self.engines.append(e)
