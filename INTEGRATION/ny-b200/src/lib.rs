@@ -114,6 +114,7 @@ extern "C" {
     fn nyb200_use_own_stream(e: *mut NyB200Engine) -> i32;
     fn nyb200_set_deadline_ns(e: *mut NyB200Engine, ns_from_now: i64) -> i32;
     fn nyb200_gemm_f32(e: *mut NyB200Engine, m: i32, k: i32, n: i32, a: *const f32, b: *const f32, c: *mut f32) -> i32;
+    fn nyb200_gemm_f32_fast(e: *mut NyB200Engine, m: i32, k: i32, n: i32, a: *const f32, b: *const f32, c: *mut f32) -> i32;
     fn nyb200_gemm_f64(e: *mut NyB200Engine, m: i32, k: i32, n: i32, a: *const f64, b: *const f64, c: *mut f64) -> i32;
     fn nyb200_gemm_f64_triplet(e: *mut NyB200Engine, m: i32, k: i32, n: i32, a: *const *const f64, b: *const *const f64,
                                c: *const *mut f64) -> i32;
@@ -245,7 +246,16 @@ impl GemmEngine for B200Engine {
         Ok(c)
     }
 
-    // gemm_f32_fast: the trait default (= gemm_f32) stands; the library has no reduced-precision product.
+    /// No precision contract (attack / scoring only): always the tensor-core product.  `gemm_f32` above keeps the
+    /// round-to-nearest error model the trait promises (the library takes its binary64-accumulating kernel for k < 21).
+    fn gemm_f32_fast(&self, m: usize, k: usize, n: usize, a: &[f32], b: &[f32]) -> Result<Vec<f32>> {
+        if a.len() != m * k || b.len() != k * n {
+            return Err(NyError::shape_mismatch(vec![m, k, n], vec![a.len(), b.len()]));
+        }
+        let mut c = vec![0f32; m * n];
+        self.check(unsafe { nyb200_gemm_f32_fast(self.h, m as i32, k as i32, n as i32, a.as_ptr(), b.as_ptr(), c.as_mut_ptr()) })?;
+        Ok(c)
+    }
 
     fn gemm_f64(&self, m: usize, k: usize, n: usize, a: &[f64], b: &[f64]) -> Result<Vec<f64>> {
         if a.len() != m * k || b.len() != k * n {

@@ -152,9 +152,16 @@ int64_t nyb200_launch_count(const nyb200_engine *e);
 /* GpuCrownBackward::clear_crown_working_set (crates/ny-core/src/gemm.rs:3205). */
 int32_t nyb200_clear_working_set(nyb200_engine *e);
 
-/* ---- GemmEngine::gemm_f32 (crates/ny-core/src/gemm.rs:325): C[m,n] = A[m,k] * B[k,n], row-major. */
+/* ---- GemmEngine::gemm_f32 (crates/ny-core/src/gemm.rs:325): C[m,n] = A[m,k] * B[k,n], row-major.
+ * The trait's precision contract (:318-324) is the error model of round-to-nearest fp32 arithmetic,
+ * |c - a.b| <= gamma_k sum|a||b|: on NYB200_PATH_TF32X3 the tcgen05 3xTF32 product is used where its certified rate is
+ * below gamma_k (k >= 21), the binary64-accumulating kernel for shorter contractions and on NYB200_PATH_F64.
+ * nyb200_gemm_f32_fast is GemmEngine::gemm_f32_fast (:337, no precision contract, attack and scoring only): always the
+ * tensor-core product on NYB200_PATH_TF32X3.  gemm_interval_sound (:663) stays the trait's default over gemm_f32. */
 int32_t nyb200_gemm_f32(nyb200_engine *e, int32_t m, int32_t k, int32_t n, const float *a, const float *b,
                         float *c_out);
+int32_t nyb200_gemm_f32_fast(nyb200_engine *e, int32_t m, int32_t k, int32_t n, const float *a, const float *b,
+                             float *c_out);
 
 /* ---- network residency -------------------------------------------------------------------
  * Stands in for the Arc<[f32]> pointer-identity cache key of GpuCrownLayer::Linear

@@ -33,7 +33,7 @@ ERRCH_IMMEDIATE, ERRCH_REFERENCE = 0, 1
 
 EXPORTS = [
     "nyb200_create", "nyb200_destroy", "nyb200_backend_provenance", "nyb200_last_error", "nyb200_set_stream",
-    "nyb200_set_path", "nyb200_set_refine_tolerance", "nyb200_batch_refined", "nyb200_batch_poll", "nyb200_crown_bounds_split", "nyb200_batch_set_inherited", "nyb200_frontier_create", "nyb200_frontier_round", "nyb200_frontier_round_optimized", "nyb200_frontier_destroy", "nyb200_frontier_count", "nyb200_frontier_take", "nyb200_frontier_give", "nyb200_frontier_download", "nyb200_frontier_upload", "nyb200_launch_count", "nyb200_clear_working_set", "nyb200_gemm_f32", "nyb200_net_create",
+    "nyb200_set_path", "nyb200_set_refine_tolerance", "nyb200_batch_refined", "nyb200_batch_poll", "nyb200_crown_bounds_split", "nyb200_batch_set_inherited", "nyb200_frontier_create", "nyb200_frontier_round", "nyb200_frontier_round_optimized", "nyb200_frontier_destroy", "nyb200_frontier_count", "nyb200_frontier_take", "nyb200_frontier_give", "nyb200_frontier_download", "nyb200_frontier_upload", "nyb200_launch_count", "nyb200_clear_working_set", "nyb200_gemm_f32", "nyb200_gemm_f32_fast", "nyb200_net_create",
     "nyb200_net_destroy", "nyb200_ibp_forward", "nyb200_ibp_forward_noalloc", "nyb200_bab_bound_batch", "nyb200_batch_upload", "nyb200_batch_run",
     "nyb200_batch_download", "nyb200_batch_min_lower", "nyb200_batch_min_lower_device",
     "nyb200_batch_download_pre_bounds", "nyb200_batch_select_branch", "nyb200_timing_enable", "nyb200_timing_reset",
@@ -126,6 +126,7 @@ def load_library():
     L.nyb200_launch_count.restype = C.c_int64
     L.nyb200_clear_working_set.argtypes = [vp]
     L.nyb200_gemm_f32.argtypes = [vp, C.c_int32, C.c_int32, C.c_int32, fp, fp, fp]
+    L.nyb200_gemm_f32_fast.argtypes = [vp, C.c_int32, C.c_int32, C.c_int32, fp, fp, fp]
     L.nyb200_net_create.argtypes = [vp, C.c_int32, ip, fp, fp, ip, ip]
     L.nyb200_net_create_layers.argtypes = [vp, C.c_int32, C.POINTER(LayerDesc), fp, fp, ip]
     L.nyb200_net_destroy.argtypes = [vp, C.c_int32]
@@ -574,6 +575,15 @@ class B200Engine:
             raise EngineError(SHAPE, f"gemm_f32: expected {m * k} and {k * n} elements, got {a.size} and {b.size}")
         c = np.empty(m * n, np.float32)
         self._check(self._L.nyb200_gemm_f32(self._h, m, k, n, _fp(a), _fp(b), _fp(c)))
+        return c.reshape(m, n)
+
+    def gemm_f32_fast(self, m: int, k: int, n: int, a, b) -> np.ndarray:
+        """GemmEngine::gemm_f32_fast: no precision contract (attack and scoring only); always the tensor-core product."""
+        a, b = _f32(a).reshape(-1), _f32(b).reshape(-1)
+        if a.size != m * k or b.size != k * n:
+            raise EngineError(SHAPE, f"gemm_f32_fast: expected {m * k} and {k * n} elements, got {a.size} and {b.size}")
+        c = np.empty(m * n, np.float32)
+        self._check(self._L.nyb200_gemm_f32_fast(self._h, m, k, n, _fp(a), _fp(b), _fp(c)))
         return c.reshape(m, n)
 
     def gemm_f64(self, m: int, k: int, n: int, a, b) -> np.ndarray:

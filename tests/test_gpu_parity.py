@@ -415,3 +415,24 @@ def test_persistent_kernels_with_reserved_sms_return_the_same_bits(oracle):
     with pytest.raises(EngineError):
         eng.set_reserved_sms(-1)
     eng.close()
+
+
+def test_gemm_f32_keeps_the_round_to_nearest_error_model(eng):
+    """GemmEngine::gemm_f32's precision contract (crates/ny-core/src/gemm.rs:318-324): |c - a.b| <= gamma_k sum|a||b|
+    with gamma_k = k u / (1 - k u), u = 2^-24, for every contraction length - short ones included, where the 3xTF32
+    product's own rate would be above gamma_k; gemm_f32_fast has no such contract and stays close to fp32."""
+    g = np.random.Generator(np.random.PCG64(5))
+    u = 2.0 ** -24
+    for k in (1, 2, 5, 8, 16, 20, 21, 40, 64, 300):
+        a = (g.standard_normal((70, k)) * np.exp(g.uniform(-3, 3, (70, k)))).astype(np.float32)
+        b = (g.standard_normal((k, 33)) * np.exp(g.uniform(-3, 3, (k, 33)))).astype(np.float32)
+        exact = a.astype(np.float64) @ b.astype(np.float64)
+        S = np.abs(a).astype(np.float64) @ np.abs(b).astype(np.float64)
+        gamma = k * u / (1 - k * u)
+        c = eng.gemm_f32(70, k, 33, a, b)
+        # the result's own final rounding to fp32 is part of the model for k = 1 (gamma_1 = u)
+        assert np.all(np.abs(c - exact) <= gamma * S * (1 + 1e-9) + 1e-45), k
+        if k < 21 and eng.path_name != "f64":
+            assert np.array_equal(c, exact.astype(np.float32)), k     # binary64 accumulation, one rounding
+        f = eng.gemm_f32_fast(70, k, 33, a, b)
+        assert np.max(np.abs(f - exact) / S) <= 2e-6, k
