@@ -52,6 +52,10 @@ def main(argv=None) -> int:
             p.add_argument("--branching", choices=("width", "intercept", "babsr", "fsb"), default="intercept")
             p.add_argument("--input-split", action="store_true", help="branch on input dimensions instead of ReLUs")
             p.add_argument("--domain-batch-metrics-jsonl", default=None)
+            p.add_argument("--resident", action="store_true",
+                           help="keep the open domain set on the device (one call per round); width / intercept / babsr "
+                                "branching, split histories up to --max-depth")
+            p.add_argument("--max-depth", type=int, default=128, help="--resident: longest split history")
             p.add_argument("--checkpoint", default=None)
             p.add_argument("--resume", default=None)
         else:
@@ -73,9 +77,16 @@ def main(argv=None) -> int:
                                              timeout_s=args.timeout)
             else:
                 kind = {"width": 0, "intercept": 1, "babsr": 2, "fsb": 3}[args.branching]
-                res = bab.verify(eng, nid, net, prop, batch=args.batch_size, max_domains=args.max_domains, max_rounds=1 << 30,
-                                 optimize_iterations=args.beta_iterations, branching=kind, timeout_s=args.timeout,
-                                 metrics_jsonl=args.domain_batch_metrics_jsonl, checkpoint=args.checkpoint, resume=args.resume)
+                if args.resident:
+                    if kind == 3 or args.domain_batch_metrics_jsonl:
+                        raise ValueError("--resident supports width, intercept and babsr branching and writes no metrics file")
+                    res = bab.verify_resident(eng, nid, net, prop, batch=args.batch_size, max_domains=args.max_domains,
+                                              max_rounds=max(1, args.max_depth - 2), optimize_iterations=args.beta_iterations,
+                                              branching=kind, timeout_s=args.timeout, checkpoint=args.checkpoint, resume=args.resume)
+                else:
+                    res = bab.verify(eng, nid, net, prop, batch=args.batch_size, max_domains=args.max_domains, max_rounds=1 << 30,
+                                     optimize_iterations=args.beta_iterations, branching=kind, timeout_s=args.timeout,
+                                     metrics_jsonl=args.domain_batch_metrics_jsonl, checkpoint=args.checkpoint, resume=args.resume)
         else:
             res = bab.verify_root(eng, nid, net, prop, method=args.method)
         _report(res, prop)

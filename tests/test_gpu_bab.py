@@ -181,6 +181,12 @@ def test_command_line_surface_and_exit_codes(tmp_path):
     assert rc == 1 and "Status: VIOLATED" in out and "Counterexample input" in out
     rc, out = run("beta-crown", str(model), "-p", str(safe), "--input-split")
     assert rc == 0 and "Status: VERIFIED" in out
+    rc, out = run("beta-crown", str(model), "-p", str(safe), "--resident")      # the open set on the device
+    assert rc == 0 and "Status: VERIFIED" in out
+    rc, out = run("beta-crown", str(model), "-p", str(unsafe), "--resident", "--beta-iterations", "0")
+    assert rc == 1 and "Status: VIOLATED" in out
+    rc, out = run("beta-crown", str(model), "-p", str(safe), "--resident", "--branching", "fsb")
+    assert rc == 4
     rc, out = run("verify", str(model), "-p", str(safe), "--method", "crown")
     assert rc == 0
     rc, out = run("verify", str(model), "-p", str(safe), "--method", "ibp")      # the interval pass only reaches y <= 2
