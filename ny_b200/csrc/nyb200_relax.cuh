@@ -63,7 +63,7 @@ __device__ __forceinline__ float relax_coeff(const bool upper, float a, float4 t
 //     n * 2^-24 times the run's magnitude sum, and that sum is bounded term by term: |nw bias| directly, and
 //     |a * intercept| <= |nw| * max|z| * (1 + 2^-21), because an intercept only applies on the upper line, where the
 //     outward step moves nw away from zero (|nw| >= |a| * slope) and intercept / slope = -l up to rounding.
-//     A product that underflows to zero becomes the smallest denormal with the outward sign.
+//     A product that underflows to zero stays zero; the floor of the charge encloses it.
 //   * The intercept and bias dot products are accumulated in fp32 (gi, gb: one fused multiply-add per term) over a
 //     short run of columns; the caller adds each run to the row's binary64 bias.
 // dir = +1 for an upper row, -1 for a lower row; dirf the same as a float.
@@ -76,17 +76,14 @@ __device__ __forceinline__ float relax_coeff_fast(const bool upper, const int di
     const int pb = __float_as_int(prod);
     // one ulp outward on the bit pattern: +dir for a positive product, -dir for a negative one; a zero product (zero
     // slope or zero coefficient: common, every stably inactive neuron has one) stays zero without a branch
-    float nw = __int_as_float(pb + dir + 2 * dir * (pb >> 31));
-    // a zero product: exactly zero when the coefficient or the slope is zero (no step: every stably inactive neuron has
-    // one); otherwise the product underflowed, its magnitude is below the smallest denormal, and that denormal with the
-    // outward sign encloses it
-    const float tiny = (fminf(fabsf(a), fabsf(slope)) == 0.f) ? 0.f : dirf * 1.4012985e-45f;
-    nw = (prod == 0.f) ? tiny : nw;
+    // A zero product stays zero: exactly zero when the coefficient or the slope is zero (no step: every stably inactive
+    // neuron has one); a product that underflowed (|a * slope| <= 2^-150) is enclosed by the floor of the charge below.
+    float nw = __int_as_float((pb << 1) ? pb + dir + 2 * dir * (pb >> 31) : 0);
     gi = fmaf(a, icp, gi);
     nw = fmaf(t.w, dirf, nw);   // signed beta: nw + t.w on upper rows, nw - t.w on lower rows (t.w * +-1 is exact)
     gb = fmaf(nw, bk, gb);
-    // the floor covers the underflow case, whose gap to the exact product is the whole denormal, not 1.5 ulp:
-    // 2^-148 max|z| <= 1.6e-38 cj because cj >= 1.9e-7 max|z|
+    // the floor covers the underflow case, where the coefficient is taken as zero and the exact product is at most
+    // 2^-150: 2^-148 max|z| <= 1.6e-38 cj because cj >= 1.9e-7 max|z| (and cj >= kappa |bias| for the bias product)
     sp = __fmaf_ru(fmaxf(fabsf(nw), 1.6e-38f), cj, sp);
     return nw;
 }
