@@ -817,6 +817,47 @@ k_skip_coeff(int M, int n, float *__restrict__ A, int lda, const float *__restri
     }
 }
 
+// The same with one block per row and four columns per thread and step (rows of tens of thousands of columns, as the
+// convolutional layers of a residual network have, keep a single warp busy for thousands of dependent steps).  The
+// block's shares of the charge are added in a fixed order, so the row's penalty does not depend on scheduling.
+__global__ void __launch_bounds__(256)
+k_skip_coeff_v4(int M, int n, float *__restrict__ A, int lda, const float *__restrict__ S, int lds, int R,
+                const float *__restrict__ zl, const float *__restrict__ zu, long stride, int src_off,
+                double *__restrict__ rpen) {
+    __shared__ double part[8];
+    const int m = blockIdx.x;
+    if (m >= M) return;
+    const int d = m / R;
+    float4 *a4 = (float4 *)(A + (long)m * lda);
+    const float4 *s4 = (const float4 *)(S + (long)m * lds);
+    const float4 *l4 = (const float4 *)(zl + (long)d * stride + src_off), *u4 = (const float4 *)(zu + (long)d * stride + src_off);
+    double pen = 0.0;
+    auto one = [&](float a, float b, float l, float u, float &out) {
+        const float s = a + b;
+        const float bb = s - a;
+        const float err = (a - (s - bb)) + (b - bb);  // exact residual of the rounded sum
+        out = s;
+        if (rpen) pen += fabs((double)err) * (double)fmaxf(fabsf(l), fabsf(u));
+    };
+    for (int j = threadIdx.x; j < n / 4; j += 256) {
+        const float4 a = a4[j], b = s4[j];
+        float4 l = make_float4(0.f, 0.f, 0.f, 0.f), u = l, o;
+        if (rpen) { l = l4[j]; u = u4[j]; }
+        one(a.x, b.x, l.x, u.x, o.x); one(a.y, b.y, l.y, u.y, o.y); one(a.z, b.z, l.z, u.z, o.z); one(a.w, b.w, l.w, u.w, o.w);
+        a4[j] = o;
+    }
+    if (rpen) {
+        pen = warp_sum(pen);
+        if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = pen;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            double t = 0.0;
+            for (int w = 0; w < 8; ++w) t += part[w];
+            if (t != 0.0) atomicAdd(&rpen[m], t);
+        }
+    }
+}
+
 // ---------------------------------------------------------------- launchers
 #define NYB_COUNT(e) ((e)->launches++)
 
@@ -880,8 +921,15 @@ void launch_skip_interval(nyb200_engine *e, int D, int n, long stride, float *ra
 
 void launch_skip_coeff(nyb200_engine *e, int M, int n, float *A, int lda, const float *S, int lds, int R,
                        const float *zl, const float *zu, long stride, int src_off, double *rpen) {
-    long threads = (long)M * 32;
-    k_skip_coeff<<<(unsigned)((threads + 255) / 256), 256, 0, e->stream>>>(M, n, A, lda, S, lds, R, zl, zu, stride, src_off, rpen);
+    const bool vec = n >= 2048 && (n % 4 == 0) && (lda % 4 == 0) && (lds % 4 == 0) && (stride % 4 == 0) && (src_off % 4 == 0) &&
+                     ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(S) | reinterpret_cast<uintptr_t>(zl) |
+                       reinterpret_cast<uintptr_t>(zu)) & 15) == 0;
+    if (vec) {
+        k_skip_coeff_v4<<<(unsigned)M, 256, 0, e->stream>>>(M, n, A, lda, S, lds, R, zl, zu, stride, src_off, rpen);
+    } else {
+        long threads = (long)M * 32;
+        k_skip_coeff<<<(unsigned)((threads + 255) / 256), 256, 0, e->stream>>>(M, n, A, lda, S, lds, R, zl, zu, stride, src_off, rpen);
+    }
     NYB_COUNT(e);
 }
 
