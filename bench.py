@@ -828,10 +828,12 @@ def run_search(args, rank, world, local_rank):
     def search():
         if pool is not None:   # one device frontier per engine of the pool, their rounds overlapping on the GPU
             return bab.verify_resident_pool(pool, handle, wl.net, prop, batch=batch, max_rounds=rounds, branching=1, pgd_restarts=64,
-                                            pgd_steps=10, optimize_iterations=opt_it, max_domains=1 << 18)
+                                            pgd_steps=10, optimize_iterations=opt_it, max_domains=1 << 18,
+                                            refinement=args.search_refinement)
         if resident:   # the open domain set stays on the device: one call per round
             return bab.verify_resident(eng, nid, wl.net, prop, batch=batch, max_rounds=rounds, branching=1, pgd_restarts=64,
-                                       pgd_steps=10, optimize_iterations=opt_it, max_domains=1 << 18, dist=dist, dist_device=dev)
+                                       pgd_steps=10, optimize_iterations=opt_it, max_domains=1 << 18,
+                                       refinement=args.search_refinement, dist=dist, dist_device=dev)
         return bab.verify(eng, nid, wl.net, prop, batch=batch, max_rounds=rounds, optimize_iterations=opt_it, branching=1,
                           pgd_restarts=64, pgd_steps=10, dist=dist, dist_device=dev)
 
@@ -885,6 +887,9 @@ def run_search(args, rank, world, local_rank):
                                     "per engine and round, levelled ring to ring") if pool is not None
                                    else "device-resident (nyb200_frontier_round: pop, bound, prune, branch, push per call)" if resident
                                    else "host (numpy blocks; upload of the children's split lists every round)",
+                       "refinement": ("binary64 re-evaluation of the domains whose verdict the rounding charge could change"
+                                      if (resident and args.search_refinement == "verdict") else
+                                      "binary64 re-evaluation of every domain whose rounding charge is visible at the engine's tolerance"),
                        "timing": "wall clock around the search calls, max over ranks", "status": r.status,
                        "domains_per_search": r.domains_bounded, "open_at_stop": r.open_domains},
             "rebalance": moved if (world > 1 or pool is not None) else None,
@@ -1013,6 +1018,8 @@ def main():
                     help="bab-search on one GPU: 1 keeps the frontier on the device (default), 0 runs the host loop")
     ap.add_argument("--search-engines", type=int, default=2,
                     help="bab-search on one GPU: engines (device frontiers) sharing the search, their rounds overlapping (1: a single frontier)")
+    ap.add_argument("--search-refinement", default="verdict", choices=["verdict", "parity"],
+                    help="bab-search on the device frontier: which domains are re-evaluated in binary64 (see bab.verify_resident)")
     ap.add_argument("--search-iterations", type=int, default=0,
                     help="bab-search: optimisation iterations per domain (0 = one bound per domain, the reference's throughput default)")
     ap.add_argument("--in-flight", type=int, default=3,

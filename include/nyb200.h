@@ -123,6 +123,13 @@ void nyb200_frontier_destroy(nyb200_engine *e);
 struct nyb200_opt_config;
 int32_t nyb200_frontier_round_optimized(nyb200_engine *e, int32_t batch, int32_t branching, const struct nyb200_opt_config *cfg,
                                         int64_t *stats_out, float *min_lower);
+/* Which domains of a round are re-evaluated with binary64 contractions.  0 (default): the engine's rule (every domain
+ * whose rounding charge is visible at nyb200_set_refine_tolerance, so that the bounds stay within the parity bar of the
+ * binary64 path).  1: only the domains whose verdict the charge could change - some row's certified lower bound misses
+ * its threshold by less than twice the row's charge; the others keep the tensor-path bound, which is sound and at most
+ * that charge looser.  The search's verdict is sound either way; with 1 a domain may be split once more than with 0.
+ * Applies to the frontier that exists when it is called. */
+int32_t nyb200_frontier_set_refinement(nyb200_engine *e, int32_t verdict_only);
 /* Sharded search (one process per GPU, each with its own frontier): the shards are levelled by moving records between
  * them, device array to device array (the caller carries them with a point-to-point collective; the reference's
  * domain distribution is host-side, beta_crown/engine/core.rs:560-640).  nyb200_frontier_take removes up to n records

@@ -472,14 +472,18 @@ def verify(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: i
 def verify_resident(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: int = 64,
                     max_domains: int = 1 << 20, pgd_restarts: int = 256, pgd_steps: int = 50, branching: int = 1,
                     timeout_s: float | None = None, checkpoint=None, resume=None, optimize_iterations: int = 0,
-                    dist=None, dist_device=None) -> VerifyResult:
+                    refinement: str = "parity", dist=None, dist_device=None) -> VerifyResult:
     """The search of verify() with the open domain set kept on the device (nyb200_frontier_*): attack and root bound
     as there, then one device call per round that pops a batch, bounds it (one bound per domain, multipliers at
     zero), prunes verified and infeasible domains, picks every open domain's split neuron (0 width, 1 intercept,
     2 BaBSR) and appends both children.  Same order of domains as the host loop, hence the same counts and verdicts;
     optimize_iterations > 1: every domain's slopes and multipliers are optimised that many steps and children start
     from their parent's (nyb200_frontier_round_optimized: verify()'s warm-started search; records moved between ranks
-    or resumed from a dump start cold).  What it leaves out is the metrics file.  checkpoint / resume: as in
+    or resumed from a dump start cold).  refinement: "parity" re-evaluates with binary64 contractions every domain
+    whose rounding charge is visible at the engine's tolerance (bounds as close to the binary64 path as the per-batch
+    calls return them, and the host loop's domain counts); "verdict" only the domains whose verdict the charge could
+    change (sound, and several times faster on narrow boxes, where the first rule flags nearly every domain; a domain
+    may then be split once more).  What it leaves out is the metrics file.  checkpoint / resume: as in
     verify() (same file format: a dump written by either loop resumes in the other); single rank only.
     dist: an initialised torch.distributed module, one process per GPU, every rank calling with the same arguments:
     each rank keeps its own device frontier (the root starts on rank 0), bounds up to `batch` of its domains per round,
@@ -517,6 +521,9 @@ def verify_resident(eng, net_id, net, prop: Property, *, batch: int = 1024, max_
         max_depth = max_rounds + 2
     eng.frontier_create(net_id, spec, thr, owner, n_clauses, prop.in_lo, prop.in_hi, inh_lo, inh_hi,
                         max_depth=max_depth, capacity=min(2 * max_domains + 2 * batch, 1 << 22))
+    if refinement not in ("parity", "verdict"):
+        raise ValueError("refinement: parity or verdict")
+    eng.frontier_set_refinement(refinement == "verdict")
     exchange = {"exchanges": 0, "records_moved": 0, "bytes_moved": 0} if world > 1 else None
     try:
         if resumed is not None:
@@ -570,7 +577,7 @@ def verify_resident(eng, net_id, net, prop: Property, *, batch: int = 1024, max_
 
 def verify_resident_pool(pool, net_handle, net, prop: Property, *, batch: int = 1024, max_rounds: int = 64,
                          max_domains: int = 1 << 20, pgd_restarts: int = 256, pgd_steps: int = 50, branching: int = 1,
-                         timeout_s: float | None = None, optimize_iterations: int = 0) -> VerifyResult:
+                         timeout_s: float | None = None, optimize_iterations: int = 0, refinement: str = "parity") -> VerifyResult:
     """verify_resident over the engines of an EnginePool (ny_b200.pool) on one GPU: one device frontier per engine, the
     root on the first, every engine bounding up to `batch` of its domains per round on its own stream and host thread,
     the shards levelled after the round by moving records from ring to ring on the device.  A round of a search is a
@@ -603,6 +610,7 @@ def verify_resident_pool(pool, net_handle, net, prop: Property, *, batch: int = 
     for e, nid in zip(engines, nids):
         e.frontier_create(nid, spec, thr, owner, n_clauses, prop.in_lo, prop.in_hi, inter_lo[0], inter_hi[0],
                           max_depth=max_depth, capacity=min(2 * max_domains + 2 * batch, 1 << 22))
+        e.frontier_set_refinement(refinement == "verdict")
     exchange = {"exchanges": 0, "records_moved": 0, "bytes_moved": 0}
 
     def one_round(i):

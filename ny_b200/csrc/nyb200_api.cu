@@ -472,7 +472,7 @@ int run_forward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int fw
     size_t np = nv.nps;
     // a slack-to-width ratio above this marks the domain for the binary64 re-evaluation (same switch as the
     // penalty criterion: 0 disables)
-    const float fwd_tol = e->refine_tol;
+    const float fwd_tol = e->decision_thr ? 0.f : e->refine_tol;   // a verdict-only round does not flag on the interval slack
     // When the backward pass of this run will be the fused chain, the finish kernel also leaves the chain's charge
     // weights (one fused multiply-add per table entry here instead of a pass of its own over three arrays).
     float *cj = nullptr;

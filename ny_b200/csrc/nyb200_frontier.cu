@@ -35,6 +35,7 @@ struct ResidentFrontier {
     long no_alpha_front = 0;
     size_t buf_bytes = 0, ns_bytes = 0, thr_bytes = 0, consts_bytes = 0, alpha_bytes = 0;   // what the arrays can hold
     bool optimistic = true;   // queue the decisions behind the bound without waiting (until a round is flagged)
+    bool verdict_refinement = false;   // nyb200_frontier_set_refinement
 };
 
 void frontier_free(ResidentFrontier *f) {
@@ -198,7 +199,7 @@ int32_t nyb200_frontier_create(nyb200_engine *e, int32_t net_id, const float *sp
     ResidentFrontier *f = e->frontier_spare ? e->frontier_spare : new ResidentFrontier();
     e->frontier_spare = nullptr;
     f->net_id = net_id; f->S = S; f->maxd = max_depth; f->n_clauses = n_clauses; f->cap = capacity;
-    f->bounded = 0; f->optimistic = true;
+    f->bounded = 0; f->optimistic = true; f->verdict_refinement = false;
     f->n_spec = (size_t)S * nv.dims[nv.L]; f->n_box = (size_t)nv.dims[0]; f->n_inh = (size_t)nv.n_pre;
     auto fit = [&](void **ptr, size_t *have, size_t need) -> bool {
         if (*ptr && *have >= need) return true;
@@ -325,6 +326,10 @@ static int32_t frontier_round_impl(nyb200_engine *e, int32_t batch, int32_t bran
         NYB_CUDA(e, cudaStreamSynchronize(st));
         return NYB200_OK;
     };
+    // verdict-only refinement: the thresholds decide which domains the binary64 re-evaluation is worth (reset on every
+    // way out of this function)
+    struct ThrGuard { nyb200_engine *e; ~ThrGuard() { e->decision_thr = nullptr; } } thr_guard{e};
+    e->decision_thr = f->verdict_refinement ? f->thr : nullptr;
     if (optimise) {
         NYB_TRY(optimize_batch(e, *cfg));
         NYB_TRY(finish_batch_public(e));   // synchronises; folds a binary64 re-evaluation into the best bounds if flagged
@@ -382,6 +387,14 @@ int32_t nyb200_frontier_round_optimized(nyb200_engine *e, int32_t batch, int32_t
                                         int64_t *stats_out, float *min_lower) {
     if (!cfg) return NYB200_ERR_INVALID;
     return frontier_round_impl(e, batch, branching, cfg, stats_out, min_lower);
+}
+
+int32_t nyb200_frontier_set_refinement(nyb200_engine *e, int32_t verdict_only) {
+    if (!e) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    if (!e->frontier) return set_err(e, NYB200_ERR_INVALID, "no frontier");
+    e->frontier->verdict_refinement = verdict_only != 0;
+    return NYB200_OK;
 }
 
 int32_t nyb200_frontier_count(nyb200_engine *e, int64_t *open) {

@@ -124,6 +124,7 @@ struct nyb200_engine {
     cudaStream_t stream = nullptr;
     int reserve_sms = 0;                          // see nyb200_set_reserved_sms
     bool launch_overlap = true;                   // see nyb200_set_launch_overlap
+    const float *decision_thr = nullptr;          // device [S]: thresholds of the running search round (k_count_loose)
     cudaStream_t own_stream = nullptr;            // created by nyb200_use_own_stream, destroyed with the engine
     int path = NYB200_PATH_TF32X3;
     float refine_tol = 5e-5f;  // see nyb200_set_refine_tolerance

@@ -647,15 +647,29 @@ __device__ __forceinline__ void atomic_min_float(float *addr, float v) {
 // smaller than the charges on its two ends.  The host re-runs
 // the batch on the binary64 path when the count is non-zero, so that the fast path never returns a
 // bound that its own rounding model has visibly loosened.
+// thr != null (a search that only needs verdicts, nyb200_frontier_set_refinement): a domain is flagged only when the
+// charge could change a verdict, i.e. some row's lower bound misses its threshold by less than twice the row's charge
+// (the exact bound lies within that distance above the certified one).
 __global__ void k_count_loose(int D, int S, int R, const float *__restrict__ out_lo, const float *__restrict__ out_hi,
                               const double *__restrict__ rpen, int *__restrict__ flags, float tol,
-                              int *__restrict__ n_loose) {
+                              int *__restrict__ n_loose, const float *__restrict__ thr) {
     pdl_trigger();
     pdl_wait();
     int d = blockIdx.x * blockDim.x + threadIdx.x;
     if (d >= D) return;
     const int f = flags[d];
     if (f & ~(kFlagLooseFwd | kFlagLoose)) return;  // infeasible / degraded / invalid domains are not re-evaluated
+    if (thr) {
+        bool close = false;
+        for (int s = 0; s < S; ++s) {
+            const float l = out_lo[d * S + s];
+            if (!isfinite(l)) continue;
+            const double reach = (double)l + 2.000001 * rpen[(long)d * R + s];
+            if (l <= thr[s] && reach > (double)thr[s]) close = true;
+        }
+        if (close) { atomicAdd(n_loose, 1); flags[d] = f | kFlagLoose; }
+        return;
+    }
     if (f & kFlagLooseFwd) { atomicAdd(n_loose, 1); return; }
     float scale = 0.f;
     for (int s = 0; s < S; ++s) {
@@ -993,7 +1007,7 @@ void launch_concretize(nyb200_engine *e, int M, int R, int S, int n0, const floa
     int D = M / R;
     if (loose_tol > 0.f) {
         k_count_loose<<<(D + 255) / 256, 256, 0, e->stream>>>(D, S, R, out_lo, out_hi, rpen, flags, loose_tol,
-                                                              (int *)min_lower + 4);
+                                                              (int *)min_lower + 4, e->decision_thr);
         NYB_COUNT(e);
     }
     k_finalize<<<(D * S + 255) / 256, 256, 0, e->stream>>>(D, S, flags, out_lo, out_hi, min_lower);
@@ -1035,7 +1049,7 @@ void launch_concretize_fused(nyb200_engine *e, int M, int R, int S, int slots, c
     int D = M / R;
     if (loose_tol > 0.f) {
         launch_pdl(k_count_loose, dim3((D + 255) / 256), dim3(256), 0, e, D, S, R, (const float *)out_lo, (const float *)out_hi,
-                   rpen, flags, loose_tol, (int *)min_lower + 4);
+                   rpen, flags, loose_tol, (int *)min_lower + 4, e->decision_thr);
         NYB_COUNT(e);
     }
     launch_pdl(k_finalize, dim3((D * S + 255) / 256), dim3(256), 0, e, D, S, (const int *)flags, out_lo, out_hi, min_lower);

@@ -33,7 +33,7 @@ ERRCH_IMMEDIATE, ERRCH_REFERENCE = 0, 1
 
 EXPORTS = [
     "nyb200_create", "nyb200_destroy", "nyb200_backend_provenance", "nyb200_last_error", "nyb200_set_stream",
-    "nyb200_set_path", "nyb200_set_refine_tolerance", "nyb200_batch_refined", "nyb200_batch_poll", "nyb200_crown_bounds_split", "nyb200_batch_set_inherited", "nyb200_frontier_create", "nyb200_frontier_round", "nyb200_frontier_round_optimized", "nyb200_frontier_destroy", "nyb200_frontier_count", "nyb200_frontier_take", "nyb200_frontier_give", "nyb200_frontier_download", "nyb200_frontier_upload", "nyb200_launch_count", "nyb200_clear_working_set", "nyb200_gemm_f32", "nyb200_gemm_f32_fast", "nyb200_net_create",
+    "nyb200_set_path", "nyb200_set_refine_tolerance", "nyb200_batch_refined", "nyb200_batch_poll", "nyb200_crown_bounds_split", "nyb200_batch_set_inherited", "nyb200_frontier_create", "nyb200_frontier_round", "nyb200_frontier_round_optimized", "nyb200_frontier_set_refinement", "nyb200_frontier_destroy", "nyb200_frontier_count", "nyb200_frontier_take", "nyb200_frontier_give", "nyb200_frontier_download", "nyb200_frontier_upload", "nyb200_launch_count", "nyb200_clear_working_set", "nyb200_gemm_f32", "nyb200_gemm_f32_fast", "nyb200_net_create",
     "nyb200_net_destroy", "nyb200_ibp_forward", "nyb200_ibp_forward_noalloc", "nyb200_bab_bound_batch", "nyb200_batch_upload", "nyb200_batch_run",
     "nyb200_batch_download", "nyb200_batch_min_lower", "nyb200_batch_min_lower_device",
     "nyb200_batch_download_pre_bounds", "nyb200_batch_select_branch", "nyb200_timing_enable", "nyb200_timing_reset",
@@ -813,6 +813,13 @@ class B200Engine:
         fn.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.POINTER(OptConfig), C.POINTER(C.c_int64), C.POINTER(C.c_float)]
         self._check(fn(self._h, int(batch), int(branching), C.byref(cfg), st, C.byref(ml)))
         return int(st[0]), int(st[1]), int(st[2]), int(st[3]), int(st[4]), int(st[5]), float(ml.value)
+
+    def frontier_set_refinement(self, verdict_only: bool):
+        """Re-evaluate in binary64 only the domains whose verdict the rounding charge could change (True), or every
+        domain whose charge is visible at the refinement tolerance (False, the default)."""
+        fn = self._L.nyb200_frontier_set_refinement
+        fn.argtypes = [C.c_void_p, C.c_int32]
+        self._check(fn(self._h, 1 if verdict_only else 0))
 
     def frontier_count(self) -> int:
         n = C.c_int64(0)

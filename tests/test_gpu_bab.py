@@ -532,3 +532,42 @@ def test_search_shared_by_the_engines_of_a_pool(eng):
     assert cut.status == "unknown" and cut.open_domains > 0 and cut.rounds == 6
     pool.close()
     eng.release_network(nid)
+
+
+@pytest.mark.gpu
+def test_verdict_only_refinement_re_evaluates_only_what_could_change_a_verdict(eng):
+    """nyb200_frontier_set_refinement(1): a round re-evaluates in binary64 only the domains whose lower bound misses
+    its threshold by less than twice the row's rounding charge.  Far from the threshold nothing is re-evaluated although
+    the parity rule flags the domains; the search reaches the same verdict either way, and a verified verdict is
+    confirmed by sampling."""
+    wl = W.config_mlp_bab(seed=83, hidden=24, depth=3, n_in=4, n_out=3, eps=0.2, n_fix=0)
+    net = wl.net
+    nid = eng.register_network(net)
+    root_lo, _, il, iu = eng.crown_bounds(nid, wl.spec, wl.in_lo, wl.in_hi)
+    mn = W.sample_min_margin(wl, 200000, 3)
+    s = int(np.argmax(mn - root_lo[0]))
+    for frac in (0.5, 0.9):
+        t = float(root_lo[0][s] + frac * (mn[s] - root_lo[0][s]))
+        p = formats.Property(wl.in_lo, wl.in_hi, [[formats.Atom(-wl.spec[s], t)]])
+        a = bab.verify_resident(eng, nid, net, p, batch=16, max_rounds=300, optimize_iterations=6 if frac > 0.6 else 0)
+        b = bab.verify_resident(eng, nid, net, p, batch=16, max_rounds=300, optimize_iterations=6 if frac > 0.6 else 0,
+                                refinement="verdict")
+        assert a.status == b.status == "verified" and t < mn[s]
+        assert b.domains_bounded >= a.domains_bounded - 2 and b.domains_bounded <= 2 * a.domains_bounded + 8
+    # rounds far from the threshold: the parity rule sends domains to binary64, the verdict rule none
+    p = formats.Property(wl.in_lo, wl.in_hi, [[formats.Atom(-wl.spec[s], float(mn[s]) + 5.0)]])      # cannot be verified
+    spec, thr, owner = bab._rows(p)
+    counts = {}
+    for mode in (False, True):
+        eng.set_refine_tolerance(1e-9)        # the parity rule at a tolerance that flags everything
+        eng.frontier_create(nid, spec, thr, owner, 1, p.in_lo, p.in_hi, il[0], iu[0], max_depth=12, capacity=4096)
+        eng.frontier_set_refinement(mode)
+        n = 0
+        for _ in range(6):
+            eng.frontier_round(64, 1)
+            n += eng.batch_refined()
+        counts[mode] = (n, eng.frontier_count())
+        eng.frontier_destroy()
+    eng.set_refine_tolerance(5e-5)
+    assert counts[False][0] > 0 and counts[True][0] == 0 and counts[False][1] == counts[True][1]
+    eng.release_network(nid)
