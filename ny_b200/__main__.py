@@ -82,7 +82,8 @@ def main(argv=None) -> int:
                         raise ValueError("--resident supports width, intercept and babsr branching and writes no metrics file")
                     res = bab.verify_resident(eng, nid, net, prop, batch=args.batch_size, max_domains=args.max_domains,
                                               max_rounds=max(1, args.max_depth - 2), optimize_iterations=args.beta_iterations,
-                                              branching=kind, timeout_s=args.timeout, checkpoint=args.checkpoint, resume=args.resume)
+                                              branching=kind, timeout_s=args.timeout, checkpoint=args.checkpoint, resume=args.resume,
+                                              refinement="verdict")   # a verdict is what this command reports
                 else:
                     res = bab.verify(eng, nid, net, prop, batch=args.batch_size, max_domains=args.max_domains, max_rounds=1 << 30,
                                      optimize_iterations=args.beta_iterations, branching=kind, timeout_s=args.timeout,
