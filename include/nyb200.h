@@ -295,6 +295,13 @@ int32_t nyb200_batch_upload(nyb200_engine *e, int32_t net_id, const float *spec,
                             const float *in_hi, int32_t box_stride, const float *inh_lo, const float *inh_hi,
                             const nyb200_split *splits, const int32_t *n_splits, int32_t max_splits, int32_t D,
                             int32_t mode, const float *alpha);
+/* Verdict-only refinement for the uploaded batch (the per-batch counterpart of nyb200_frontier_set_refinement, for
+ * search loops that keep their domains on the host): with thresholds [S] set, the runs of this batch re-evaluate in
+ * binary64 only the domains in which some row's certified lower bound misses its threshold by less than twice the
+ * row's rounding charge; all other bounds stay the tensor path's (sound, at most that charge looser than the binary64
+ * path's).  NULL clears it; the next nyb200_batch_upload clears it too.  No counterpart in the reference, whose device
+ * paths carry their error bounds without a binary64 re-evaluation. */
+int32_t nyb200_batch_set_thresholds(nyb200_engine *e, const float *thresholds, int32_t S);
 /* Per-domain inherited bounds for the resident batch: inh_lo / inh_hi [D x sum_{k>=1} dims[k]] replace the shared
  * vector given at upload (e.g. the tightened intermediates of nyb200_crown_bounds_split for the same domains).  The
  * next run intersects every domain's re-propagated bounds with its own row (mode 1) or takes the row as it is (mode

@@ -321,7 +321,8 @@ def select_fsb(eng, net_id, net, prop: Property, inh_lo, inh_hi, take, open_idx,
 def verify(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: int = 64, max_domains: int = 1 << 20,
            pgd_restarts: int = 256, pgd_steps: int = 50, optimize_iterations: int = 0, branching: int = 1,
            timeout_s: float | None = None, metrics_jsonl=None, checkpoint=None, resume=None,
-           warm_start: bool = True, fsb_k: int = 3, kfsb_reduce: str = "min", dist=None, dist_device="cpu") -> VerifyResult:
+           warm_start: bool = True, fsb_k: int = 3, kfsb_reduce: str = "min", refinement: str = "parity", dist=None,
+           dist_device="cpu") -> VerifyResult:
     """metrics_jsonl: append one JSON record per round; checkpoint: path that receives the open frontier whenever the
     run stops unresolved (round limit, timeout, domain limit); resume: path of such a dump to continue from (the attack
     and the root bound are skipped).
@@ -333,6 +334,9 @@ def verify(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: i
     intercept candidates, the children's margins combined by kfsb_reduce ("min" | "max" | "mean") (2 and 3: Linear
     layers only); warm_start: with optimisation on, children start from their
     parent's optimised slopes and split multipliers instead of the heuristic slopes and zero.
+    refinement: "parity" (every domain whose rounding charge is visible at the engine's tolerance is re-evaluated with
+    binary64 contractions) or "verdict" (only the domains whose verdict the charge could change:
+    nyb200_batch_set_thresholds; sound, several times faster on narrow boxes, a domain may be split once more).
     dist: an initialised torch.distributed module, one process per GPU: every rank runs this function with the same
     arguments, rank 0 attacks and bounds the root, and from then on every rank bounds its own shard of the frontier;
     per round the ranks exchange one small all-reduce (open domains, stop flags, the global lower bound) and level
@@ -423,6 +427,8 @@ def verify(eng, net_id, net, prop: Property, *, batch: int = 1024, max_rounds: i
             if not (warm_start and optimize_iterations > 1):
                 alpha0 = None
             eng.batch_upload(net_id, spec, prop.in_lo, prop.in_hi, inh_lo, inh_hi, splits, ns, mode=1, alpha=alpha0)
+            if refinement == "verdict":
+                eng.batch_set_thresholds(thr)
             alpha1 = beta1 = None
             if optimize_iterations > 1:
                 eng.batch_optimize(optimize_iterations, 0.1, 0.05)

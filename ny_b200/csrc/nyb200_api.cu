@@ -472,7 +472,7 @@ int run_forward(nyb200_engine *e, Net &net, const Batch &b, BatchPtrs &p, int fw
     size_t np = nv.nps;
     // a slack-to-width ratio above this marks the domain for the binary64 re-evaluation (same switch as the
     // penalty criterion: 0 disables)
-    const float fwd_tol = e->decision_thr ? 0.f : e->refine_tol;   // a verdict-only round does not flag on the interval slack
+    const float fwd_tol = b.decision_thr ? 0.f : e->refine_tol;   // a verdict-only round does not flag on the interval slack
     // When the backward pass of this run will be the fused chain, the finish kernel also leaves the chain's charge
     // weights (one fused multiply-add per table entry here instead of a pass of its own over three arrays).
     float *cj = nullptr;
@@ -1022,6 +1022,20 @@ int32_t nyb200_batch_upload(nyb200_engine *e, int32_t net_id, const float *spec,
     std::lock_guard<std::mutex> g(e->mu);
     return upload_batch(e, net_id, spec, S, in_lo, in_hi, box_stride, inh_lo, inh_hi, splits, n_splits, max_splits, D, mode,
                         alpha);
+}
+
+int32_t nyb200_batch_set_thresholds(nyb200_engine *e, const float *thresholds, int32_t S) {
+    if (!e) return NYB200_ERR_INVALID;
+    std::lock_guard<std::mutex> g(e->mu);
+    NYB_CUDA(e, cudaSetDevice(e->device));
+    if (!thresholds) { e->batch.decision_thr = nullptr; return NYB200_OK; }
+    if (!e->batch.valid) return set_err(e, NYB200_ERR_INVALID, "no batch uploaded");
+    if (S != e->batch.S) return set_err(e, NYB200_ERR_SHAPE, "one threshold per specification row of the batch");
+    NYB_WS(dt, float *, e, "decision_thr", (size_t)S * 4);
+    NYB_CUDA(e, cudaMemcpyAsync(dt, thresholds, (size_t)S * 4, cudaMemcpyHostToDevice, e->stream));
+    NYB_CUDA(e, cudaStreamSynchronize(e->stream));   // the caller's array may go away
+    e->batch.decision_thr = dt;
+    return NYB200_OK;
 }
 
 int32_t nyb200_batch_set_inherited(nyb200_engine *e, const float *inh_lo, const float *inh_hi) {

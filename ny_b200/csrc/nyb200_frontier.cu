@@ -305,6 +305,7 @@ static int32_t frontier_round_impl(nyb200_engine *e, int32_t batch, int32_t bran
             NYB_CUDA(e, cudaMemcpyAsync(p.alpha + first * nv.nps, f->alpha, (size_t)(D - first) * nv.nps * 4, cudaMemcpyDeviceToDevice, st));
     }
     b.valid = true;
+    b.decision_thr = f->verdict_refinement ? f->thr : nullptr;   // which domains the binary64 re-evaluation is worth
     e->batch = b;
     NYB_WS(done, int *, e, "fr_done", (size_t)D * 4);
     NYB_WS(pos, int *, e, "fr_pos", (size_t)D * 4);
@@ -326,10 +327,6 @@ static int32_t frontier_round_impl(nyb200_engine *e, int32_t batch, int32_t bran
         NYB_CUDA(e, cudaStreamSynchronize(st));
         return NYB200_OK;
     };
-    // verdict-only refinement: the thresholds decide which domains the binary64 re-evaluation is worth (reset on every
-    // way out of this function)
-    struct ThrGuard { nyb200_engine *e; ~ThrGuard() { e->decision_thr = nullptr; } } thr_guard{e};
-    e->decision_thr = f->verdict_refinement ? f->thr : nullptr;
     if (optimise) {
         NYB_TRY(optimize_batch(e, *cfg));
         NYB_TRY(finish_batch_public(e));   // synchronises; folds a binary64 re-evaluation into the best bounds if flagged

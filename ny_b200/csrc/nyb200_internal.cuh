@@ -100,6 +100,7 @@ struct Batch {
     // ([crown_D * 2 * crown_S x crown_lda], per box S lower rows then S upper rows), until any call reuses the workspace.
     const float *crown_a = nullptr;
     int crown_lda = 0, crown_D = 0, crown_S = 0, crown_n0 = 0;
+    const float *decision_thr = nullptr;   // device [S]: verdict-only refinement (nyb200_batch_set_thresholds, the frontier)
 };
 
 struct Timing {
@@ -124,7 +125,6 @@ struct nyb200_engine {
     cudaStream_t stream = nullptr;
     int reserve_sms = 0;                          // see nyb200_set_reserved_sms
     bool launch_overlap = true;                   // see nyb200_set_launch_overlap
-    const float *decision_thr = nullptr;          // device [S]: thresholds of the running search round (k_count_loose)
     cudaStream_t own_stream = nullptr;            // created by nyb200_use_own_stream, destroyed with the engine
     int path = NYB200_PATH_TF32X3;
     float refine_tol = 5e-5f;  // see nyb200_set_refine_tolerance

@@ -1007,7 +1007,7 @@ void launch_concretize(nyb200_engine *e, int M, int R, int S, int n0, const floa
     int D = M / R;
     if (loose_tol > 0.f) {
         k_count_loose<<<(D + 255) / 256, 256, 0, e->stream>>>(D, S, R, out_lo, out_hi, rpen, flags, loose_tol,
-                                                              (int *)min_lower + 4, e->decision_thr);
+                                                              (int *)min_lower + 4, e->batch.decision_thr);
         NYB_COUNT(e);
     }
     k_finalize<<<(D * S + 255) / 256, 256, 0, e->stream>>>(D, S, flags, out_lo, out_hi, min_lower);
@@ -1049,7 +1049,7 @@ void launch_concretize_fused(nyb200_engine *e, int M, int R, int S, int slots, c
     int D = M / R;
     if (loose_tol > 0.f) {
         launch_pdl(k_count_loose, dim3((D + 255) / 256), dim3(256), 0, e, D, S, R, (const float *)out_lo, (const float *)out_hi,
-                   rpen, flags, loose_tol, (int *)min_lower + 4, e->decision_thr);
+                   rpen, flags, loose_tol, (int *)min_lower + 4, e->batch.decision_thr);
         NYB_COUNT(e);
     }
     launch_pdl(k_finalize, dim3((D * S + 255) / 256), dim3(256), 0, e, D, S, (const int *)flags, out_lo, out_hi, min_lower);

@@ -33,7 +33,7 @@ ERRCH_IMMEDIATE, ERRCH_REFERENCE = 0, 1
 
 EXPORTS = [
     "nyb200_create", "nyb200_destroy", "nyb200_backend_provenance", "nyb200_last_error", "nyb200_set_stream",
-    "nyb200_set_path", "nyb200_set_refine_tolerance", "nyb200_batch_refined", "nyb200_batch_poll", "nyb200_crown_bounds_split", "nyb200_batch_set_inherited", "nyb200_frontier_create", "nyb200_frontier_round", "nyb200_frontier_round_optimized", "nyb200_frontier_set_refinement", "nyb200_frontier_destroy", "nyb200_frontier_count", "nyb200_frontier_take", "nyb200_frontier_give", "nyb200_frontier_download", "nyb200_frontier_upload", "nyb200_launch_count", "nyb200_clear_working_set", "nyb200_gemm_f32", "nyb200_gemm_f32_fast", "nyb200_net_create",
+    "nyb200_set_path", "nyb200_set_refine_tolerance", "nyb200_batch_refined", "nyb200_batch_poll", "nyb200_crown_bounds_split", "nyb200_batch_set_inherited", "nyb200_batch_set_thresholds", "nyb200_frontier_create", "nyb200_frontier_round", "nyb200_frontier_round_optimized", "nyb200_frontier_set_refinement", "nyb200_frontier_destroy", "nyb200_frontier_count", "nyb200_frontier_take", "nyb200_frontier_give", "nyb200_frontier_download", "nyb200_frontier_upload", "nyb200_launch_count", "nyb200_clear_working_set", "nyb200_gemm_f32", "nyb200_gemm_f32_fast", "nyb200_net_create",
     "nyb200_net_destroy", "nyb200_ibp_forward", "nyb200_ibp_forward_noalloc", "nyb200_bab_bound_batch", "nyb200_batch_upload", "nyb200_batch_run",
     "nyb200_batch_download", "nyb200_batch_min_lower", "nyb200_batch_min_lower_device",
     "nyb200_batch_download_pre_bounds", "nyb200_batch_select_branch", "nyb200_timing_enable", "nyb200_timing_reset",
@@ -779,6 +779,16 @@ class B200Engine:
         fn = self._L.nyb200_batch_set_inherited
         fn.argtypes = [C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_float)]
         self._check(fn(self._h, _fp(lo), _fp(hi)))
+
+    def batch_set_thresholds(self, thresholds):
+        """Verdict-only refinement for the uploaded batch: one threshold per specification row (None clears)."""
+        fn = self._L.nyb200_batch_set_thresholds
+        fn.argtypes = [C.c_void_p, C.POINTER(C.c_float), C.c_int32]
+        if thresholds is None:
+            self._check(fn(self._h, None, 0))
+            return
+        t = _f32(thresholds).reshape(-1)
+        self._check(fn(self._h, _fp(t), int(t.size)))
 
     def frontier_create(self, net_id, spec, thresholds, owner, n_clauses, in_lo, in_hi, inh_lo, inh_hi, max_depth, capacity):
         """Device-resident BaB frontier holding the root domain (see nyb200_frontier_create)."""

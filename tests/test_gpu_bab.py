@@ -554,6 +554,9 @@ def test_verdict_only_refinement_re_evaluates_only_what_could_change_a_verdict(e
                                 refinement="verdict")
         assert a.status == b.status == "verified" and t < mn[s]
         assert b.domains_bounded >= a.domains_bounded - 2 and b.domains_bounded <= 2 * a.domains_bounded + 8
+        # the host loop with per-batch thresholds (nyb200_batch_set_thresholds) bounds the same domains
+        h = bab.verify(eng, nid, net, p, batch=16, max_rounds=300, optimize_iterations=6 if frac > 0.6 else 0, refinement="verdict")
+        assert (h.status, h.rounds, h.domains_bounded) == (b.status, b.rounds, b.domains_bounded)
     # rounds far from the threshold: the parity rule sends domains to binary64, the verdict rule none
     p = formats.Property(wl.in_lo, wl.in_hi, [[formats.Atom(-wl.spec[s], float(mn[s]) + 5.0)]])      # cannot be verified
     spec, thr, owner = bab._rows(p)
