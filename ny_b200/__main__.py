@@ -87,7 +87,8 @@ def main(argv=None) -> int:
                 else:
                     res = bab.verify(eng, nid, net, prop, batch=args.batch_size, max_domains=args.max_domains, max_rounds=1 << 30,
                                      optimize_iterations=args.beta_iterations, branching=kind, timeout_s=args.timeout,
-                                     metrics_jsonl=args.domain_batch_metrics_jsonl, checkpoint=args.checkpoint, resume=args.resume)
+                                     metrics_jsonl=args.domain_batch_metrics_jsonl, checkpoint=args.checkpoint, resume=args.resume,
+                                     refinement="verdict")
         else:
             res = bab.verify_root(eng, nid, net, prop, method=args.method)
         _report(res, prop)
